@@ -1,0 +1,393 @@
+// Paged prefill / verify attention on tcgen05 for sm_100a.
+//
+// One CTA = 128 query rows of one (sequence, query head). Per block of BKV keys:
+//   thread X (warp 4, one lane): TMA-loads K and V pages through the block table (3-D tensor map over
+//       the cache, one box per page and 64-column half, 128-byte swizzle), issues S = Q K^T into
+//       TMEM, later O += P V (V is the MN-major B operand, read in place from the same smem tile)
+//   warps 0..3 (thread = query row = TMEM lane): tcgen05.ld S, causal / window mask, online softmax
+//       in base 2, P written to smem as the swizzled K-major A operand of the second MMA, O rescaled
+//       in TMEM (tcgen05.ld / st) when the running maximum moved.
+// K/V tiles are double buffered, so the loads for block i+1 fly during the softmax of block i.
+// Sequence lengths, query offsets and block tables are data; the grid is (q tiles, heads, seqs).
+//
+// Counterparts in the reference: src/cuda/sm80/paged_attn.cuh (paged_prefill_mma, split verify),
+// src/cuda/sm90/paged_attn_wgmma.cu.
+#include "common.cuh"
+#include "kernels.h"
+#include "tmap.cuh"
+
+namespace lb {
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
+      "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]),
+      "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+struct PrefillArgs {
+  const int* cu_q;         // [n_seqs + 1] first query row of each sequence
+  const int* ctx_lens;     // [n_seqs] keys visible after this chunk (cached + chunk)
+  const int* block_table;  // [n_seqs, table_width]
+  int table_width, page;
+  int Hq, Hkv;
+  float scale_log2;        // softmax scale * log2(e)
+  int window;              // 0 = none
+  int causal;
+  __nv_bfloat16* out;      // [T, Hq, D]
+  int* status;
+};
+
+template <int D, int BKV>
+struct PrefillCfg {
+  static constexpr int HALVES = D / 64;               // 64-column (128-byte) halves of a head row
+  static constexpr int Q_BYTES = HALVES * 128 * 128;  // 128 rows x 128 B per half
+  static constexpr int KV_BYTES = HALVES * BKV * 128;
+  static constexpr int P_BYTES = (BKV / 64) * 128 * 128;
+  static constexpr int STAGES = 2;
+  static constexpr int SMEM = Q_BYTES + STAGES * 2 * KV_BYTES + P_BYTES + 1024 + 256;
+  static constexpr int TMEM_RAW = BKV + D;
+  static constexpr int TMEM_COLS = TMEM_RAW <= 128 ? 128 : (TMEM_RAW <= 256 ? 256 : 512);
+};
+
+template <int D, int BKV>
+__global__ void __launch_bounds__(160, 1)
+prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const PrefillArgs a) {
+  using Cfg = PrefillCfg<D, BKV>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_s = smem;
+  uint8_t* kv_s = q_s + Cfg::Q_BYTES;                      // [stage][K | V]
+  uint8_t* p_s = kv_s + Cfg::STAGES * 2 * Cfg::KV_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + Cfg::P_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;   // [2]
+  uint64_t* v_full = bars + 3;   // [2]
+  uint64_t* s_full = bars + 5;
+  uint64_t* p_ready = bars + 6;
+  uint64_t* o_done = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int seq = blockIdx.z;
+  const int head = blockIdx.y;
+  const int q0 = a.cu_q[seq];
+  const int q_len = a.cu_q[seq + 1] - q0;
+  const int tile_row0 = blockIdx.x * 128;
+  if (tile_row0 >= q_len) return;  // uniform per CTA, before any barrier or TMEM use
+  const int ctx = a.ctx_lens[seq];
+  const int kvh = head / (a.Hq / a.Hkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); }
+    mbar_init(s_full, 1);
+    mbar_init(p_ready, 128);
+    mbar_init(o_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 4) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base;
+  const uint32_t tmem_O = tmem_base + BKV;
+
+  // key range visible to this query tile
+  const int pos0 = ctx - q_len + tile_row0;                       // absolute position of tile row 0
+  const int rows_here = min(128, q_len - tile_row0);
+  const int last_pos = pos0 + rows_here - 1;
+  const int kv_hi = a.causal ? min(ctx, last_pos + 1) : ctx;      // exclusive
+  int kv_lo = 0;
+  if (a.window > 0) kv_lo = max(0, pos0 - a.window + 1);
+  const int blk_lo = kv_lo / BKV;
+  const int blk_hi = (kv_hi + BKV - 1) / BKV;                     // exclusive
+  const int n_blk = blk_hi - blk_lo;
+  const int* bt = a.block_table + long(seq) * a.table_width;
+  const int pages_per_blk = BKV / a.page;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      // ------------------------------------------------------------ loads + MMA issue
+      auto load_kv = [&](int blk, int stage) {
+        uint8_t* ks = kv_s + stage * 2 * Cfg::KV_BYTES;
+        uint8_t* vs = ks + Cfg::KV_BYTES;
+        const int tok0 = blk * BKV;
+        mbar_expect_tx(&k_full[stage], Cfg::KV_BYTES);
+        mbar_expect_tx(&v_full[stage], Cfg::KV_BYTES);
+        for (int p = 0; p < pages_per_blk; ++p) {
+          const int tok = tok0 + p * a.page;
+          // pages past the end of the sequence read cell row 0 of a valid page: masked later
+          const int pg = (tok < ctx) ? bt[tok / a.page] : bt[0];
+          const int cell = pg * a.page;
+#pragma unroll
+          for (int h = 0; h < Cfg::HALVES; ++h) {
+            tma_load_3d(ks + h * (BKV * 128) + p * a.page * 128, &tmK, &k_full[stage], h * 64, kvh, cell);
+            tma_load_3d(vs + h * (BKV * 128) + p * a.page * 128, &tmV, &v_full[stage], h * 64, kvh, cell);
+          }
+        }
+      };
+      mbar_expect_tx(q_full, Cfg::Q_BYTES);
+#pragma unroll
+      for (int h = 0; h < Cfg::HALVES; ++h)
+        tma_load_3d(q_s + h * (128 * 128), &tmQ, q_full, h * 64, head, q0 + tile_row0);
+      load_kv(blk_lo, 0);
+      constexpr uint32_t idesc_s = umma_idesc(128, BKV, 1, 1, 0, 0);
+      constexpr uint32_t idesc_o = umma_idesc(128, D, 1, 1, 0, 1);  // B (= V) is MN-major
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      if (!ok) { *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FULL); }
+      for (int i = 0; ok && i < n_blk; ++i) {
+        const int st = i & 1;
+        const uint32_t ph = (i >> 1) & 1;
+        if (!mbar_wait(&k_full[st], ph, abort_flag)) {
+          *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FULL); break;
+        }
+        tc_fence_after();
+        const uint32_t qa = smem_u32(q_s);
+        const uint32_t ka = smem_u32(kv_s + st * 2 * Cfg::KV_BYTES);
+        const uint32_t va = ka + Cfg::KV_BYTES;
+#pragma unroll
+        for (int h = 0; h < Cfg::HALVES; ++h) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t da = umma_desc_k_sw128(qa + h * (128 * 128) + k * 32);
+            const uint64_t db = umma_desc_k_sw128(ka + h * (BKV * 128) + k * 32);
+            umma_f16(tmem_S, da, db, idesc_s, (h | k) ? 1u : 0u);
+          }
+        }
+        umma_commit(s_full);
+        // the other stage is free once the previous block's PV has completed
+        if (i >= 1) {
+          if (!mbar_wait(o_done, (i - 1) & 1, abort_flag)) {
+            *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_EMPTY); break;
+          }
+        }
+        if (i + 1 < n_blk) load_kv(blk_lo + i + 1, st ^ 1);
+        if (!mbar_wait(p_ready, i & 1, abort_flag)) {
+          *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FLAG); break;
+        }
+        if (!mbar_wait(&v_full[st], ph, abort_flag)) {
+          *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FULL); break;
+        }
+        tc_fence_after();
+        const uint32_t pa = smem_u32(p_s);
+#pragma unroll
+        for (int k = 0; k < BKV / 16; ++k) {
+          // A = P: K-major, 64-key halves of 16 KiB; B = V: 16 keys = 16 rows of 128 B per step
+          const uint64_t da = umma_desc_k_sw128(pa + (k / 4) * (128 * 128) + (k % 4) * 32);
+          const uint64_t db = umma_desc_mn_sw128(va + k * 16 * 128, BKV * 128, 1024);
+          umma_f16(tmem_O, da, db, idesc_o, (i | k) ? 1u : 0u);
+        }
+        umma_commit(o_done);
+      }
+    }
+  } else {
+    // -------------------------------------------------------------- softmax warps (thread = row)
+    const int row = warp * 32 + lane;
+    const int qpos = pos0 + row;
+    const bool row_ok = row < rows_here;
+    const uint32_t lane_off = uint32_t(warp * 32) << 16;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int i = 0; i < n_blk; ++i) {
+      if (!__all_sync(0xffffffffu, mbar_wait(s_full, i & 1, abort_flag))) {
+        *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_FULL); ok = false; break;
+      }
+      tc_fence_after();
+      const int key0 = (blk_lo + i) * BKV;
+      int hi = a.causal ? min(ctx, qpos + 1) : ctx;   // exclusive key bound for this row
+      int lo = (a.window > 0) ? max(0, qpos - a.window + 1) : 0;
+      if (!row_ok) { hi = 0; lo = 0; }
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < BKV; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_S + lane_off + c, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int key = key0 + c + j;
+          if (key >= lo && key < hi) mx = fmaxf(mx, __uint_as_float(r[j]));
+        }
+      }
+      const float m_new = fmaxf(m, mx * a.scale_log2);
+      const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
+      // P may be overwritten and O rescaled only after the previous PV has finished
+      if (i >= 1) {
+        if (!__all_sync(0xffffffffu, mbar_wait(o_done, (i - 1) & 1, abort_flag))) {
+          *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_EMPTY); ok = false; break;
+        }
+        tc_fence_after();
+      }
+      // pass 2: probabilities -> swizzled smem
+      float sum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < BKV; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_S + lane_off + c, r);
+        tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float p0 = 0.f, p1 = 0.f;
+          const int key = key0 + c + j;
+          if (key >= lo && key < hi) p0 = exp2f(__uint_as_float(r[j]) * a.scale_log2 - m_new);
+          if (key + 1 >= lo && key + 1 < hi) p1 = exp2f(__uint_as_float(r[j + 1]) * a.scale_log2 - m_new);
+          // sum what the tensor core will see (bf16-rounded) to keep numerator and denominator consistent
+          const __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+          const float2 f = __bfloat1622float2(b);
+          sum += f.x + f.y;
+          packed[j / 2] = *reinterpret_cast<const uint32_t*>(&b);
+        }
+        // 32 columns = 4 chunks of 16 bytes in half (c / 64)
+        uint8_t* half_base = p_s + (c / 64) * (128 * 128) + row * 128;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const int chunk = ((c % 64) / 8 + ch) ^ (row & 7);
+          *reinterpret_cast<uint4*>(half_base + chunk * 16) =
+              make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
+        }
+      }
+      l = l * alpha + sum;
+      m = m_new;
+      if (i >= 1) {
+        // every thread rescales its own O row; skipping when alpha == 1 is the common case late in a row
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+          for (int c = 0; c < D; c += 32) {
+            uint32_t r[32];
+            tmem_ld32(tmem_O + lane_off + c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
+            tmem_st32(tmem_O + lane_off + c, r);
+          }
+          tmem_st_wait();
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(p_ready);
+    }
+    // final: O / l -> out
+    if (ok && n_blk > 0) {
+      if (!__all_sync(0xffffffffu, mbar_wait(o_done, (n_blk - 1) & 1, abort_flag))) {
+        *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_FULL); ok = false;
+      }
+    }
+    if (ok) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* orow = a.out + (long(q0 + tile_row0 + row) * a.Hq + head) * D;
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        uint32_t r[32];
+        if (n_blk > 0) {
+          tmem_ld32(tmem_O + lane_off + c, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0;
+        }
+        if (row_ok) {
+          uint4* dst = reinterpret_cast<uint4*>(orow + c);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]) * inv, __uint_as_float(r[8 * v + 1]) * inv);
+            o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]) * inv, __uint_as_float(r[8 * v + 3]) * inv);
+            o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]) * inv, __uint_as_float(r[8 * v + 5]) * inv);
+            o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]) * inv, __uint_as_float(r[8 * v + 7]) * inv);
+            dst[v] = o;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+namespace {
+thread_local char g_attn_err[256];
+
+template <int D, int BKV>
+int launch_prefill(const CUtensorMap* tq, const CUtensorMap* tk, const CUtensorMap* tv, const PrefillArgs& a,
+                   dim3 grid, cudaStream_t s) {
+  using Cfg = PrefillCfg<D, BKV>;
+  auto kfn = prefill_attn_kernel<D, BKV>;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess) {
+      snprintf(g_attn_err, sizeof(g_attn_err), "prefill attention: cannot set %d bytes of shared memory", Cfg::SMEM);
+      return 1;
+    }
+    attr = true;
+  }
+  kfn<<<grid, 160, Cfg::SMEM, s>>>(*tq, *tk, *tv, a);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    snprintf(g_attn_err, sizeof(g_attn_err), "prefill attention launch: %s", cudaGetErrorString(e));
+    return 1;
+  }
+  return 0;
+}
+}  // namespace
+
+const char* prefill_attn_last_error() { return g_attn_err; }
+
+int prefill_attn_launch(const void* q, long T, const void* k_cache, const void* v_cache, long n_cells,
+                        long cell_stride, const int* cu_q, const int* ctx_lens, const int* block_table,
+                        int table_width, int page, int n_seqs, int max_q_len, int Hq, int Hkv, int D, float scale,
+                        int window, int causal, void* out, int* status, cudaStream_t s) {
+  if (n_seqs <= 0 || max_q_len <= 0) return 0;
+  const int BKV = D > 128 ? 64 : 128;
+  if (page <= 0 || BKV % page != 0 || page % 8 != 0) {
+    snprintf(g_attn_err, sizeof(g_attn_err), "prefill attention: page size %d must be a multiple of 8 dividing %d",
+             page, BKV);
+    return 1;
+  }
+  if (D != 64 && D != 128 && D != 256) {
+    snprintf(g_attn_err, sizeof(g_attn_err), "prefill attention: head dim %d not supported", D);
+    return 1;
+  }
+  // q viewed as [T, Hq, D]; caches as [cells, Hkv, D] with cell pitch cell_stride elements
+  const CUtensorMap* tq = tmap_3d(q, uint64_t(D), uint64_t(Hq), uint64_t(T), uint64_t(D) * 2,
+                                  uint64_t(Hq) * D * 2, 64, 1, 128, TM_BF16, true);
+  const CUtensorMap* tk = tmap_3d(k_cache, uint64_t(D), uint64_t(Hkv), uint64_t(n_cells), uint64_t(D) * 2,
+                                  uint64_t(cell_stride) * 2, 64, 1, uint32_t(page), TM_BF16, true);
+  const CUtensorMap* tv = tmap_3d(v_cache, uint64_t(D), uint64_t(Hkv), uint64_t(n_cells), uint64_t(D) * 2,
+                                  uint64_t(cell_stride) * 2, 64, 1, uint32_t(page), TM_BF16, true);
+  if (!tq || !tk || !tv) {
+    snprintf(g_attn_err, sizeof(g_attn_err), "prefill attention: %s", tmap_last_error());
+    return 1;
+  }
+  PrefillArgs a{};
+  a.cu_q = cu_q; a.ctx_lens = ctx_lens; a.block_table = block_table; a.table_width = table_width; a.page = page;
+  a.Hq = Hq; a.Hkv = Hkv; a.scale_log2 = scale * 1.4426950408889634f; a.window = window; a.causal = causal;
+  a.out = static_cast<__nv_bfloat16*>(out); a.status = status;
+  dim3 grid((max_q_len + 127) / 128, Hq, n_seqs);
+  if (D == 64) return launch_prefill<64, 128>(tq, tk, tv, a, grid, s);
+  if (D == 128) return launch_prefill<128, 128>(tq, tk, tv, a, grid, s);
+  return launch_prefill<256, 64>(tq, tk, tv, a, grid, s);
+}
+
+}  // namespace lb

@@ -1,0 +1,277 @@
+// Python bindings (module legion_b200._C): thin checks + pointer extraction around the launchers.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "comm.h"
+#include "gdn.h"
+#include "gemm_sm100.h"
+#include "kernels.h"
+#include "quant.h"
+
+namespace {
+
+using torch::Tensor;
+using OptT = c10::optional<Tensor>;
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+template <typename T>
+const T* optp(const OptT& t) {
+  return t.has_value() ? reinterpret_cast<const T*>(t->data_ptr()) : nullptr;
+}
+template <typename T>
+T* optpm(const OptT& t) {
+  return t.has_value() ? reinterpret_cast<T*>(t->data_ptr()) : nullptr;
+}
+
+void check_bf16(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.scalar_type() == at::kBFloat16, name, " must be bfloat16");
+  TORCH_CHECK(t.stride(-1) == 1, name, " must be contiguous in its last dimension");
+}
+
+// out[token, feature] = W x (+ epilogue). w: [rows, K]; x: [tokens, K]; out: [out_rows, >= n_feat].
+void wgemm(const Tensor& w, const Tensor& x, Tensor& out, const OptT& residual, const OptT& tok_scale,
+           const OptT& out_rows, int64_t n_feat, bool dual, int64_t dual_offset, int64_t bn, int64_t split_k,
+           const OptT& ws, const OptT& counters, Tensor& status, const OptT& tile_group, const OptT& tile_tok0,
+           const OptT& tile_ntok, const OptT& meta, int64_t max_tiles, int64_t rows_per_group, int64_t n_tok) {
+  check_bf16(w, "w");
+  check_bf16(x, "x");
+  TORCH_CHECK(w.dim() == 2 && x.dim() == 2 && out.dim() == 2, "wgemm expects 2-D tensors");
+  TORCH_CHECK(w.size(1) == x.size(1), "wgemm: K mismatch");
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 || out.scalar_type() == at::kFloat, "wgemm: out must be bf16/f32");
+  TORCH_CHECK(out.stride(1) == 1 && out.size(1) >= n_feat, "wgemm: bad out");
+  c10::cuda::CUDAGuard guard(w.device());
+  lb::WgemmHost h{};
+  h.w = w.data_ptr(); h.w_rows = w.size(0); h.ldw = w.stride(0);
+  h.x = x.data_ptr(); h.x_rows = x.size(0); h.ldx = x.stride(0);
+  h.out = out.data_ptr(); h.ldo = out.stride(0); h.out_f32 = out.scalar_type() == at::kFloat;
+  if (residual.has_value()) {
+    check_bf16(*residual, "residual");
+    h.residual = reinterpret_cast<const __nv_bfloat16*>(residual->data_ptr());
+    h.ldr = residual->stride(0);
+  }
+  h.tok_scale = optp<float>(tok_scale);
+  h.out_rows = optp<int>(out_rows);
+  h.K = int(w.size(1)); h.n_feat = int(n_feat); h.n_tok = int(n_tok);
+  h.bn = int(bn); h.dual = dual;
+  h.tile_group = optp<int>(tile_group); h.tile_tok0 = optp<int>(tile_tok0); h.tile_ntok = optp<int>(tile_ntok);
+  h.n_tiles_dev = optp<int>(meta);
+  h.n_tok_tiles_max = int(max_tiles);
+  h.rows_per_group = int(rows_per_group); h.dual_offset = int(dual_offset);
+  h.split_k = int(split_k);
+  h.ws = optpm<float>(ws);
+  h.counters = optpm<int>(counters);
+  if (h.split_k > 1) {
+    TORCH_CHECK(ws.has_value() && counters.has_value(), "wgemm: split-K needs ws and counters");
+    const int n_tok_tiles = h.tile_group ? h.n_tok_tiles_max : (h.n_tok + h.bn - 1) / h.bn;
+    const int feat_tiles = (h.n_feat + 127) / 128;
+    TORCH_CHECK(size_t(ws->numel()) >= lb::wgemm_workspace_floats(h.bn, dual, n_tok_tiles, feat_tiles, h.split_k),
+                "wgemm: split-K workspace too small");
+    TORCH_CHECK(counters->numel() >= int64_t(n_tok_tiles) * feat_tiles, "wgemm: too few split-K counters");
+  }
+  h.status = reinterpret_cast<int*>(status.data_ptr());
+  TORCH_CHECK(lb::wgemm_launch(h, cur_stream()) == 0, lb::wgemm_last_error());
+}
+
+void rmsnorm(const Tensor& x, const OptT& res_in, const OptT& res_out, const Tensor& w, Tensor& y, double eps,
+             double w_offset) {
+  check_bf16(x, "x");
+  TORCH_CHECK(w.scalar_type() == at::kFloat, "rmsnorm weight must be float32");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int H = int(x.size(-1));
+  const int rows = int(x.numel() / H);
+  auto ld = [&](const Tensor& t) { return t.dim() >= 2 ? t.stride(-2) : long(H); };
+  TORCH_CHECK(lb::rmsnorm_launch(x.data_ptr(), ld(x), res_in.has_value() ? res_in->data_ptr() : nullptr,
+                                 res_in.has_value() ? ld(*res_in) : 0,
+                                 res_out.has_value() ? res_out->data_ptr() : nullptr,
+                                 res_out.has_value() ? ld(*res_out) : 0, w.data_ptr<float>(), y.data_ptr(), ld(y),
+                                 rows, H, float(eps), float(w_offset), cur_stream()) == 0,
+              "rmsnorm launch failed (hidden size must be a multiple of 8)");
+}
+
+void qk_norm_rope_append(const Tensor& qkv, int64_t q_head_stride, int64_t k_off, int64_t v_off, const OptT& qw,
+                         const OptT& kw, double eps, double w_offset, const Tensor& cos_sin, int64_t rot,
+                         const Tensor& positions, const Tensor& slots, Tensor& q_out, Tensor& k_cache,
+                         Tensor& v_cache, int64_t Hq, int64_t Hkv, int64_t D) {
+  check_bf16(qkv, "qkv");
+  TORCH_CHECK(positions.scalar_type() == at::kInt && slots.scalar_type() == at::kLong, "positions i32, slots i64");
+  c10::cuda::CUDAGuard guard(qkv.device());
+  const int T = int(qkv.size(0));
+  const long cell_stride = k_cache.stride(-3);  // [.., page, Hkv, D] -> elements between cells
+  TORCH_CHECK(lb::qk_norm_rope_append_launch(qkv.data_ptr(), qkv.stride(0), int(q_head_stride), int(k_off), int(v_off),
+                                             optp<float>(qw), optp<float>(kw), float(eps), float(w_offset),
+                                             cos_sin.data_ptr<float>(), int(rot), positions.data_ptr<int>(),
+                                             reinterpret_cast<const long*>(slots.data_ptr()), q_out.data_ptr(),
+                                             k_cache.data_ptr(), v_cache.data_ptr(), cell_stride, T, int(Hq), int(Hkv),
+                                             int(D), cur_stream()) == 0,
+              "qk_norm_rope_append: unsupported head dim / rotary dim");
+}
+
+void sigmoid_gate(const Tensor& attn, const Tensor& qkv, int64_t q_head_stride, int64_t D, int64_t Hq, Tensor& out) {
+  c10::cuda::CUDAGuard guard(attn.device());
+  const long T = attn.numel() / (Hq * D);
+  TORCH_CHECK(lb::sigmoid_gate_launch(attn.data_ptr(), qkv.data_ptr(), qkv.stride(0), int(q_head_stride), int(D),
+                                      int(Hq), out.data_ptr(), T, cur_stream()) == 0, "sigmoid_gate failed");
+}
+
+void glu(const Tensor& x, Tensor& out, int64_t F, int64_t act) {
+  check_bf16(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(lb::glu_launch(x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0), int(F), x.size(0), int(act),
+                             cur_stream()) == 0, "glu failed");
+}
+
+void embed(const Tensor& ids, const Tensor& table, Tensor& out) {
+  check_bf16(table, "table");
+  TORCH_CHECK(ids.scalar_type() == at::kInt, "ids must be int32");
+  c10::cuda::CUDAGuard guard(table.device());
+  TORCH_CHECK(lb::embed_launch(ids.data_ptr<int>(), table.data_ptr(), table.stride(0), out.data_ptr(), out.stride(0),
+                               int(ids.numel()), int(table.size(1)), int(table.size(0)), cur_stream()) == 0,
+              "embed failed");
+}
+
+void paged_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_table,
+                  const Tensor& ctx_lens, double scale, int64_t window, int64_t n_splits, Tensor& o_part,
+                  Tensor& ml_part, Tensor& out) {
+  check_bf16(q, "q");
+  c10::cuda::CUDAGuard guard(q.device());
+  const int B = int(q.size(0)), Hq = int(q.size(1)), D = int(q.size(2));
+  const int page = int(k_cache.size(-3)), Hkv = int(k_cache.size(-2));
+  TORCH_CHECK(o_part.numel() >= int64_t(B) * Hq * n_splits * D && ml_part.numel() >= int64_t(B) * Hq * n_splits * 2,
+              "paged_decode: partial buffers too small");
+  const int rc = lb::paged_decode_launch(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), k_cache.stride(-3),
+                                         block_table.data_ptr<int>(), int(block_table.size(1)), page,
+                                         ctx_lens.data_ptr<int>(), float(scale), int(window), B, Hq, Hkv, D,
+                                         int(n_splits), o_part.data_ptr<float>(), ml_part.data_ptr<float>(),
+                                         out.data_ptr(), cur_stream());
+  TORCH_CHECK(rc == 0, "paged_decode: unsupported shape or launch failure (", rc, ")");
+}
+
+void prefill_attn(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& cu_q,
+                  const Tensor& ctx_lens, const Tensor& block_table, int64_t max_q_len, double scale, int64_t window,
+                  bool causal, Tensor& out, Tensor& status) {
+  check_bf16(q, "q");
+  TORCH_CHECK(q.is_contiguous() && out.is_contiguous(), "prefill_attn: q/out must be contiguous [T, Hq, D]");
+  c10::cuda::CUDAGuard guard(q.device());
+  const long T = q.size(0);
+  const int Hq = int(q.size(1)), D = int(q.size(2));
+  const int page = int(k_cache.size(-3)), Hkv = int(k_cache.size(-2));
+  const long n_cells = k_cache.numel() / (long(Hkv) * D);
+  TORCH_CHECK(k_cache.is_contiguous() && v_cache.is_contiguous(), "prefill_attn: caches must be contiguous");
+  const int rc = lb::prefill_attn_launch(q.data_ptr(), T, k_cache.data_ptr(), v_cache.data_ptr(), n_cells,
+                                         long(Hkv) * D, cu_q.data_ptr<int>(), ctx_lens.data_ptr<int>(),
+                                         block_table.data_ptr<int>(), int(block_table.size(1)), page,
+                                         int(ctx_lens.numel()), int(max_q_len), Hq, Hkv, D, float(scale), int(window),
+                                         causal ? 1 : 0, out.data_ptr(), reinterpret_cast<int*>(status.data_ptr()),
+                                         cur_stream());
+  TORCH_CHECK(rc == 0, lb::prefill_attn_last_error());
+}
+
+void router_topk(const Tensor& logits, const OptT& bias, int64_t k, int64_t mode, bool renorm, double route_scale,
+                 int64_t n_group, int64_t topk_group, Tensor& ids, Tensor& wts) {
+  TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.stride(1) == 1, "router logits must be float32");
+  c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(lb::router_topk_launch(logits.data_ptr<float>(), logits.stride(0), optp<float>(bias),
+                                     int(logits.size(1)), int(k), int(mode), renorm ? 1 : 0, float(route_scale),
+                                     int(n_group), int(topk_group), ids.data_ptr<int>(), wts.data_ptr<float>(),
+                                     int(logits.size(0)), cur_stream()) == 0,
+              "router_topk: unsupported (experts <= 512, k <= 32, groups <= 32)");
+}
+
+void moe_plan(const Tensor& ids, const Tensor& wts, int64_t e_lo, int64_t n_local, int64_t bn, Tensor& counts,
+              Tensor& offsets, Tensor& sorted_token, Tensor& sorted_pair, Tensor& sorted_w, Tensor& tile_group,
+              Tensor& tile_tok0, Tensor& tile_ntok, Tensor& meta) {
+  c10::cuda::CUDAGuard guard(ids.device());
+  TORCH_CHECK(lb::moe_plan_launch(ids.data_ptr<int>(), wts.data_ptr<float>(), int(ids.size(0)), int(ids.size(1)),
+                                  int(e_lo), int(n_local), int(bn), counts.data_ptr<int>(), offsets.data_ptr<int>(),
+                                  sorted_token.data_ptr<int>(), sorted_pair.data_ptr<int>(),
+                                  sorted_w.data_ptr<float>(), tile_group.data_ptr<int>(), tile_tok0.data_ptr<int>(),
+                                  tile_ntok.data_ptr<int>(), int(tile_group.numel()), meta.data_ptr<int>(),
+                                  cur_stream()) == 0,
+              "moe_plan failed");
+}
+
+void gather_rows(const Tensor& src, const Tensor& rows, const Tensor& n_rows, Tensor& dst) {
+  check_bf16(src, "src");
+  c10::cuda::CUDAGuard guard(src.device());
+  TORCH_CHECK(lb::gather_rows_launch(src.data_ptr(), src.stride(0), rows.data_ptr<int>(), n_rows.data_ptr<int>(),
+                                     dst.data_ptr(), dst.stride(0), int(src.size(1)), int(dst.size(0)),
+                                     cur_stream()) == 0, "gather_rows failed");
+}
+
+void moe_combine(const Tensor& y, const Tensor& ids, int64_t e_lo, int64_t e_hi, const OptT& shared,
+                 const OptT& shared_gate, const OptT& residual, Tensor& out) {
+  check_bf16(y, "y");
+  c10::cuda::CUDAGuard guard(y.device());
+  TORCH_CHECK(lb::moe_combine_launch(y.data_ptr(), y.stride(0), ids.data_ptr<int>(), int(ids.size(1)), int(e_lo),
+                                     int(e_hi), shared.has_value() ? shared->data_ptr() : nullptr,
+                                     shared.has_value() ? shared->stride(0) : 0, optp<float>(shared_gate),
+                                     residual.has_value() ? residual->data_ptr() : nullptr,
+                                     residual.has_value() ? residual->stride(0) : 0, out.data_ptr(), out.stride(0),
+                                     int(out.size(0)), int(out.size(1)), cur_stream()) == 0,
+              "moe_combine failed");
+}
+
+void argmax(const Tensor& logits, Tensor& pv, Tensor& pi, Tensor& out, const OptT& out_val) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  const int rows = int(logits.size(0)), V = int(logits.size(1));
+  const int nblk = int(pv.numel() / rows);
+  TORCH_CHECK(nblk >= 1, "argmax: partial buffer too small");
+  TORCH_CHECK(lb::argmax_launch(logits.data_ptr(), logits.scalar_type() == at::kFloat, logits.stride(0), rows, V,
+                                pv.data_ptr<float>(), pi.data_ptr<int>(), nblk, out.data_ptr<int>(),
+                                optpm<float>(out_val), cur_stream()) == 0, "argmax failed");
+}
+
+void sample(const Tensor& logits, const Tensor& temperature, const OptT& top_k, const OptT& top_p, const OptT& min_p,
+            const Tensor& seeds, const OptT& steps, Tensor& scratch, Tensor& out) {
+  TORCH_CHECK(logits.scalar_type() == at::kFloat, "sample: logits must be float32");
+  c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(scratch.numel() >= logits.size(0) * logits.size(1), "sample: scratch too small");
+  TORCH_CHECK(lb::sample_launch(logits.data_ptr<float>(), logits.stride(0), int(logits.size(0)), int(logits.size(1)),
+                                temperature.data_ptr<float>(), optp<int>(top_k), optp<float>(top_p),
+                                optp<float>(min_p), reinterpret_cast<const unsigned long long*>(seeds.data_ptr()),
+                                optp<int>(steps), scratch.data_ptr<float>(), out.data_ptr<int>(), cur_stream()) == 0,
+              "sample failed");
+}
+
+void penalties_mask(Tensor& logits, const OptT& counts, const OptT& seen, const OptT& presence, const OptT& frequency,
+                    const OptT& repetition, const OptT& mask) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(lb::penalties_mask_launch(logits.data_ptr<float>(), logits.stride(0), int(logits.size(0)),
+                                        int(logits.size(1)), optp<int>(counts), optp<unsigned char>(seen),
+                                        optp<float>(presence), optp<float>(frequency), optp<float>(repetition),
+                                        optp<unsigned int>(mask), mask.has_value() ? int(mask->size(1)) : 0,
+                                        cur_stream()) == 0, "penalties_mask failed");
+}
+
+}  // namespace
+
+void bind_gdn(pybind11::module_& m);
+void bind_comm(pybind11::module_& m);
+void bind_quant(pybind11::module_& m);
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("wgemm", &wgemm);
+  m.def("rmsnorm", &rmsnorm);
+  m.def("qk_norm_rope_append", &qk_norm_rope_append);
+  m.def("sigmoid_gate", &sigmoid_gate);
+  m.def("glu", &glu);
+  m.def("embed", &embed);
+  m.def("paged_decode", &paged_decode);
+  m.def("prefill_attn", &prefill_attn);
+  m.def("router_topk", &router_topk);
+  m.def("moe_plan", &moe_plan);
+  m.def("gather_rows", &gather_rows);
+  m.def("moe_combine", &moe_combine);
+  m.def("argmax", &argmax);
+  m.def("sample", &sample);
+  m.def("penalties_mask", &penalties_mask);
+  m.def("wgemm_workspace_floats", [](int64_t bn, bool dual, int64_t n_tok_tiles, int64_t feat_tiles, int64_t split_k) {
+    return int64_t(lb::wgemm_workspace_floats(int(bn), dual, int(n_tok_tiles), int(feat_tiles), int(split_k)));
+  });
+  bind_gdn(m);
+  bind_comm(m);
+  bind_quant(m);
+}

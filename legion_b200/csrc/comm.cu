@@ -1,0 +1,298 @@
+// Device-side communication primitives over symmetric (peer-mapped) memory on NVLink / NVSwitch.
+//
+//   * signal / wait: per-source sequence flags in each rank's signal pad, system-scope release and
+//     acquire, every wait bounded by a %globaltimer deadline that raises a status word instead of
+//     hanging the stream.
+//   * all_reduce_fused: one-shot all-reduce for decode-sized rows. Every rank has written its partial
+//     into its own symmetric buffer (the GEMM epilogue writes there directly); the kernel signals,
+//     waits for all peers, sums the peers' rows IN RANK ORDER with plain peer loads (same bits on
+//     every rank), and optionally adds the residual and applies the next RMSNorm in the same pass.
+//   * reduce_scatter_fused / all_gather_copy: the two halves of the two-shot form for large rows.
+//
+// Counterparts in the reference: src/cuda/pair_link.cu, src/cuda/glm_exchange.cu, src/cuda/tp_net.cu
+// (tp_sum in rank order, all_reduce_add_norm).
+#include "comm.h"
+
+#include "common.cuh"
+
+namespace lb {
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Waits until *flag >= want (wrap-safe) or the deadline passes. Returns false on timeout.
+__device__ __forceinline__ bool wait_flag_geq(const uint32_t* flag, uint32_t want, uint64_t budget_ns) {
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (int32_t(ld_acquire_sys(flag) - want) < 0) {
+    if ((++spins & 0x3f) == 0 && globaltimer_ns() - t0 > budget_ns) return false;
+  }
+  return true;
+}
+
+
+// Entry of a collective kernel: the sequence number is DATA (read from *seq_ptr, so a captured CUDA
+// graph can be replayed), block 0 raises this rank's flag on every peer, and every CTA waits until all
+// peers have raised theirs. Returns false (status word set) when a peer did not show up in time.
+__device__ __forceinline__ bool comm_enter(const CommPeers& peers, int slot_base, const uint32_t* seq_ptr,
+                                           uint64_t budget_ns, int* status, int* s_ok, uint32_t* seq_out) {
+  const uint32_t seq = *reinterpret_cast<const volatile uint32_t*>(seq_ptr) + 1;
+  if (threadIdx.x < peers.world && blockIdx.x == 0) {
+    uint32_t* remote = reinterpret_cast<uint32_t*>(peers.signal[threadIdx.x]) + slot_base + peers.rank;
+    __threadfence_system();
+    st_release_sys(remote, seq);
+  }
+  if (threadIdx.x == 0) *s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < peers.world) {
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(peers.signal[peers.rank]) + slot_base + threadIdx.x;
+    if (!wait_flag_geq(mine, seq, budget_ns)) {
+      *s_ok = 0;
+      atomicCAS(status, 0, ST_TIMEOUT_FLAG);
+    }
+  }
+  __syncthreads();
+  *seq_out = seq;
+  return *s_ok != 0;
+}
+// Exit: the last CTA to finish publishes the new sequence number (all CTAs have read the old one).
+__device__ __forceinline__ void comm_exit(uint32_t* seq_ptr, unsigned int* done_ctr, uint32_t seq) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int old = atomicAdd(done_ctr, 1u);
+    if (old == gridDim.x - 1) {
+      *done_ctr = 0;
+      *reinterpret_cast<volatile uint32_t*>(seq_ptr) = seq;
+    }
+  }
+}
+
+// A kernel whose only job is the bounded wait: used by the failure-detection test (a flag that
+// nothing sets must end with ST_TIMEOUT_FLAG in the status word and a live context).
+__global__ void wait_flag_kernel(const uint32_t* flag, uint32_t want, uint64_t budget_ns, int* status) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    if (!wait_flag_geq(flag, want, budget_ns)) atomicCAS(status, 0, ST_TIMEOUT_FLAG);
+  }
+}
+
+int wait_flag_launch(const uint32_t* flag, uint32_t want, uint64_t budget_ns, int* status, cudaStream_t s) {
+  wait_flag_kernel<<<1, 32, 0, s>>>(flag, want, budget_ns, status);
+  return cudaGetLastError() != cudaSuccess;
+}
+
+// Barrier across ranks: write seq into slot [my_rank] of every peer's pad, wait for all slots of mine.
+__global__ void barrier_kernel(CommPeers peers, int slot_base, uint32_t seq, uint64_t budget_ns, int* status) {
+  const int r = threadIdx.x;
+  if (r < peers.world) {
+    uint32_t* remote = reinterpret_cast<uint32_t*>(peers.signal[r]) + slot_base + peers.rank;
+    __threadfence_system();
+    st_release_sys(remote, seq);
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(peers.signal[peers.rank]) + slot_base + r;
+    if (!wait_flag_geq(mine, seq, budget_ns)) atomicCAS(status, 0, ST_TIMEOUT_FLAG);
+  }
+}
+
+int barrier_launch(const CommPeers& peers, int slot_base, uint32_t seq, uint64_t budget_ns, int* status,
+                   cudaStream_t s) {
+  barrier_kernel<<<1, 32, 0, s>>>(peers, slot_base, seq, budget_ns, status);
+  return cudaGetLastError() != cudaSuccess;
+}
+
+// One CTA per row (grid-stride). buf_off: byte offset of the partial rows inside every rank's
+// symmetric buffer; rows are [T, H] bf16 with pitch H.
+__global__ void __launch_bounds__(256) all_reduce_fused_kernel(CommPeers peers, long buf_off, int slot_base,
+                                                               uint32_t* seq_ptr, unsigned int* done_ctr, int T, int H,
+                                                               const __nv_bfloat16* __restrict__ residual, long ldr,
+                                                               __nv_bfloat16* __restrict__ sum_out, long lds,
+                                                               const float* __restrict__ norm_w, float eps,
+                                                               float w_offset, __nv_bfloat16* __restrict__ norm_out,
+                                                               long ldn, uint64_t budget_ns, int* status) {
+  __shared__ int s_ok;
+  __shared__ float red[8];
+  uint32_t seq;
+  const bool entered = comm_enter(peers, slot_base, seq_ptr, budget_ns, status, &s_ok, &seq);
+  if (!entered) { comm_exit(seq_ptr, done_ctr, seq); return; }
+  const int nv = H / 8;
+  for (int row = blockIdx.x; row < T; row += gridDim.x) {
+    float ss = 0.f;
+    for (int v = threadIdx.x; v < nv; v += 256) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int r = 0; r < peers.world; ++r) {
+        const uint4 u = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(peers.buffer[r]) + buf_off +
+                                                       (long(row) * H) * 2)[v];
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(u2[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
+      }
+      if (residual) {
+        const uint4 u = reinterpret_cast<const uint4*>(residual + long(row) * ldr)[v];
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(u2[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
+      }
+      uint4 o;
+      __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        o2[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        const float2 f = __bfloat1622float2(o2[j]);
+        ss += f.x * f.x + f.y * f.y;
+      }
+      reinterpret_cast<uint4*>(sum_out + long(row) * lds)[v] = o;
+    }
+    if (norm_out) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+      __syncthreads();
+      float tot = 0.f;
+      for (int i = 0; i < 8; ++i) tot += red[i];
+      const float inv = rsqrtf(tot / float(H) + eps);
+      for (int v = threadIdx.x; v < nv; v += 256) {
+        uint4 u = reinterpret_cast<const uint4*>(sum_out + long(row) * lds)[v];  // written by this thread above
+        __nv_bfloat162* u2 = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(u2[j]);
+          u2[j] = __floats2bfloat162_rn(f.x * inv * (norm_w[v * 8 + 2 * j] + w_offset),
+                                        f.y * inv * (norm_w[v * 8 + 2 * j + 1] + w_offset));
+        }
+        reinterpret_cast<uint4*>(norm_out + long(row) * ldn)[v] = u;
+      }
+      __syncthreads();
+    }
+  }
+  comm_exit(seq_ptr, done_ctr, seq);
+}
+
+int all_reduce_fused_launch(const CommPeers& peers, long buf_off, int slot_base, uint32_t* seq_ptr, unsigned int* done_ctr, int T,
+                            int H, const void* residual, long ldr, void* sum_out, long lds, const float* norm_w, float eps,
+                            float w_offset, void* norm_out, long ldn, uint64_t budget_ns, int* status,
+                            cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (H % 8 || peers.world > LB_MAX_RANKS) return 1;
+  const int grid = T < 296 ? T : 296;
+  all_reduce_fused_kernel<<<grid, 256, 0, s>>>(peers, buf_off, slot_base, seq_ptr, done_ctr, T, H,
+                                               static_cast<const __nv_bfloat16*>(residual), ldr,
+                                               static_cast<__nv_bfloat16*>(sum_out), lds, norm_w, eps, w_offset,
+                                               static_cast<__nv_bfloat16*>(norm_out), ldn, budget_ns, status);
+  return cudaGetLastError() != cudaSuccess;
+}
+
+// Reduce-scatter half of the two-shot form: this rank sums rows [row0, row0 + n_rows) over all peers in
+// rank order (+ residual), writing the reduced rows into its own symmetric buffer at out_off so the
+// all-gather half can fetch them, and into sum_out when given.
+__global__ void __launch_bounds__(256) reduce_scatter_kernel(CommPeers peers, long buf_off, long out_off,
+                                                             int slot_base, uint32_t* seq_ptr, unsigned int* done_ctr, int row0,
+                                                             int n_rows, int H,
+                                                             const __nv_bfloat16* __restrict__ residual, long ldr,
+                                                             uint64_t budget_ns, int* status) {
+  __shared__ int s_ok;
+  uint32_t seq;
+  const bool entered = comm_enter(peers, slot_base, seq_ptr, budget_ns, status, &s_ok, &seq);
+  if (!entered) { comm_exit(seq_ptr, done_ctr, seq); return; }
+  const int nv = H / 8;
+  char* my = reinterpret_cast<char*>(peers.buffer[peers.rank]);
+  for (long i = long(blockIdx.x) * 256 + threadIdx.x; i < long(n_rows) * nv; i += long(gridDim.x) * 256) {
+    const int row = row0 + int(i / nv);
+    const int v = int(i % nv);
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int r = 0; r < peers.world; ++r) {
+      const uint4 u =
+          reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(peers.buffer[r]) + buf_off + long(row) * H * 2)[v];
+      const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(u2[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    if (residual) {
+      const uint4 u = reinterpret_cast<const uint4*>(residual + long(row) * ldr)[v];
+      const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(u2[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    reinterpret_cast<uint4*>(my + out_off + long(row) * H * 2)[v] = o;
+  }
+  comm_exit(seq_ptr, done_ctr, seq);
+}
+
+int reduce_scatter_launch(const CommPeers& peers, long buf_off, long out_off, int slot_base, uint32_t* seq_ptr, unsigned int* done_ctr,
+                          int row0, int n_rows, int H, const void* residual, long ldr, uint64_t budget_ns, int* status,
+                          cudaStream_t s) {
+  if (H % 8 || peers.world > LB_MAX_RANKS) return 1;
+  long work = long(n_rows) * (H / 8);
+  int grid = int((work + 255) / 256);
+  if (grid < 1) grid = 1;
+  if (grid > 592) grid = 592;
+  reduce_scatter_kernel<<<grid, 256, 0, s>>>(peers, buf_off, out_off, slot_base, seq_ptr, done_ctr, row0, n_rows, H,
+                                             static_cast<const __nv_bfloat16*>(residual), ldr, budget_ns, status);
+  return cudaGetLastError() != cudaSuccess;
+}
+
+// All-gather half: after a signal round, copy every rank's rows [rows_per_rank * r, ...) from its
+// symmetric buffer at src_off into the local dense output.
+__global__ void __launch_bounds__(256) all_gather_kernel(CommPeers peers, long src_off, int slot_base, uint32_t* seq_ptr,
+                                                         unsigned int* done_ctr, int T, int H, __nv_bfloat16* __restrict__ out, long ldo,
+                                                         uint64_t budget_ns, int* status) {
+  __shared__ int s_ok;
+  uint32_t seq;
+  const bool entered = comm_enter(peers, slot_base, seq_ptr, budget_ns, status, &s_ok, &seq);
+  if (!entered) { comm_exit(seq_ptr, done_ctr, seq); return; }
+  const int nv = H / 8;
+  const int per = (T + peers.world - 1) / peers.world;
+  for (long i = long(blockIdx.x) * 256 + threadIdx.x; i < long(T) * nv; i += long(gridDim.x) * 256) {
+    const int row = int(i / nv);
+    const int v = int(i % nv);
+    int owner = row / per;
+    if (owner >= peers.world) owner = peers.world - 1;
+    const uint4 u =
+        reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(peers.buffer[owner]) + src_off + long(row) * H * 2)[v];
+    reinterpret_cast<uint4*>(out + long(row) * ldo)[v] = u;
+  }
+  comm_exit(seq_ptr, done_ctr, seq);
+}
+
+int all_gather_launch(const CommPeers& peers, long src_off, int slot_base, uint32_t* seq_ptr,
+                      unsigned int* done_ctr, int T, int H, void* out,
+                      long ldo, uint64_t budget_ns, int* status, cudaStream_t s) {
+  if (H % 8 || peers.world > LB_MAX_RANKS) return 1;
+  long work = long(T) * (H / 8);
+  int grid = int((work + 255) / 256);
+  if (grid < 1) grid = 1;
+  if (grid > 592) grid = 592;
+  all_gather_kernel<<<grid, 256, 0, s>>>(peers, src_off, slot_base, seq_ptr, done_ctr, T, H, static_cast<__nv_bfloat16*>(out), ldo,
+                                         budget_ns, status);
+  return cudaGetLastError() != cudaSuccess;
+}
+
+}  // namespace lb

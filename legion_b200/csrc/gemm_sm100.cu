@@ -1,0 +1,422 @@
+// Weights-as-M tcgen05 GEMM for sm_100a ("wgemm").
+//
+//   out[token, feature] = sum_k W[group*rows_per_group + feature, k] * X[token, k]
+//
+// The WEIGHT rows are the UMMA M dimension (128 per tile, one TMEM lane each) and the TOKENS are the
+// UMMA N dimension (BN = 32..256 accumulator columns). One orientation serves every linear layer of
+// the engine: a decode step with 1..64 tokens streams each weight tile exactly once at full TMA depth
+// (small BN leaves room for 10+ stages in flight per SM), a prefill chunk uses BN = 256, and the
+// routed-expert GEMM is the same kernel walking a device-built list of (expert, token range) tiles.
+//
+// Roles per CTA (192 threads, persistent over work items):
+//   warp 0      TMA producer: weight tile(s) + token tile per 64-wide k block, 128-byte swizzle
+//   warp 1      tcgen05.mma issuer (one elected thread), accumulators double-buffered in TMEM
+//   warps 2..5  epilogue: tcgen05.ld -> (SwiGLU | row scale | residual) -> global stores; each thread
+//               owns one feature row, so for a given token the 32 lanes of a warp write 64 contiguous
+//               bytes of the token-major output.
+// DUAL mode loads two weight tiles (gate and up rows of the same features) into two accumulators
+// and writes silu(gate) * up. Split-K writes fp32 partials to a workspace; the last CTA to arrive at
+// a tile sums the partials in split order (deterministic) and runs the epilogue.
+//
+// Counterpart in the reference: cuBLAS GEMMs reached through ggml, src/cuda/dense_mv.cu (skinny
+// BF16), src/cuda/moe_gemm.cu (routed experts, >= 64 tokens), src/cuda/expert_mv/ (decode experts).
+#include "common.cuh"
+#include "gemm_sm100.h"
+#include "tmap.cuh"
+
+namespace lb {
+
+static constexpr int BM = 128;        // weight rows per tile
+static constexpr int BK = 64;         // bf16 elements per k block = one 128-byte swizzle row
+static constexpr int UMMA_K = 16;
+static constexpr int W_TILE_BYTES = BM * BK * 2;  // 16 KiB
+static constexpr int SMEM_BUDGET = 200 * 1024;
+
+template <int BN, bool DUAL>
+struct WgemmCfg {
+  static constexpr int X_TILE_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = W_TILE_BYTES * (DUAL ? 2 : 1) + X_TILE_BYTES;
+  static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
+  static constexpr int ACC_COLS = BN * (DUAL ? 2 : 1);
+  static constexpr int TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 512 /*barriers*/;
+  static_assert(TMEM_COLS <= 512, "accumulators do not fit TMEM");
+  static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM column count must be a power of two");
+};
+
+struct WorkItem {
+  int group, tok0, ntok, feat0, ks, tile_id;
+};
+
+template <int BN>
+__device__ __forceinline__ bool decode_work(const WgemmArgs& a, int w, int n_tok_tiles, WorkItem& it) {
+  const int per_tok_tile = a.feat_tiles * a.split_k;
+  const int tt = w / per_tok_tile;
+  if (tt >= n_tok_tiles) return false;
+  const int r = w - tt * per_tok_tile;
+  const int ft = r / a.split_k;
+  it.ks = r - ft * a.split_k;
+  it.feat0 = ft * BM;
+  it.tile_id = tt * a.feat_tiles + ft;
+  if (a.tile_group) {
+    it.group = a.tile_group[tt];
+    it.tok0 = a.tile_tok0[tt];
+    it.ntok = a.tile_ntok[tt];
+  } else {
+    it.group = 0;
+    it.tok0 = tt * BN;
+    it.ntok = min(BN, a.n_tok - it.tok0);
+  }
+  return true;
+}
+
+template <int BN, bool DUAL, bool OUT_F32>
+__global__ void __launch_bounds__(192, 1)
+wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const WgemmArgs a) {
+  using Cfg = WgemmCfg<BN, DUAL>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full = bars;                  // [STAGES]
+  uint64_t* empty = bars + STAGES;        // [STAGES]
+  uint64_t* tfull = bars + 2 * STAGES;    // [2]
+  uint64_t* tempty = bars + 2 * STAGES + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* last_flag = reinterpret_cast<int*>(tmem_slot + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 4);  // one arrive per epilogue warp
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int n_tok_tiles = a.tile_group ? min(*a.n_tiles_dev, a.n_tok_tiles_max) : (a.n_tok + BN - 1) / BN;
+  const int num_kb = (a.K + BK - 1) / BK;
+  const int kb_per_split = (num_kb + a.split_k - 1) / a.split_k;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmW);
+      tma_prefetch_desc(&tmX);
+      int s = 0;
+      uint32_t ph = 0;
+      int issued = 0;
+      bool ok = true;
+      WorkItem it;
+      for (int w = blockIdx.x; ok && decode_work<BN>(a, w, n_tok_tiles, it); w += gridDim.x) {
+        const int kb0 = it.ks * kb_per_split;
+        const int kb1 = min(num_kb, kb0 + kb_per_split);
+        const int wrow = it.group * a.rows_per_group + it.feat0;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) {
+            *abort_flag = 1;
+            atomicCAS(a.status, 0, ST_TIMEOUT_EMPTY);
+            ok = false;
+            break;
+          }
+          uint8_t* st = smem + s * Cfg::STAGE_BYTES;
+          mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+          tma_load_2d(st, &tmW, &full[s], kb * BK, wrow);
+          if (DUAL) tma_load_2d(st + W_TILE_BYTES, &tmW, &full[s], kb * BK, wrow + a.dual_offset);
+          tma_load_2d(st + W_TILE_BYTES * (DUAL ? 2 : 1), &tmX, &full[s], kb * BK, it.tok0);
+          ++issued;
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+      if (!ok) {
+        // Unwinding: give copies already in flight a bounded time to land before smem is released.
+        const int n = issued < STAGES ? issued : STAGES;
+        for (int i = 0; i < n; ++i) {
+          int si = s - 1 - i;
+          uint32_t p = ph;
+          if (si < 0) { si += STAGES; p ^= 1; }
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(&full[si], p) && globaltimer_ns() - t0 < 2000000ull) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(BM, BN, 1, 1, 0, 0);
+      int s = 0;
+      uint32_t ph = 0;
+      int acc = 0;
+      uint32_t acc_ph = 0;
+      bool ok = true;
+      WorkItem it;
+      for (int w = blockIdx.x; ok && decode_work<BN>(a, w, n_tok_tiles, it); w += gridDim.x) {
+        const int kb0 = it.ks * kb_per_split;
+        const int kb1 = min(num_kb, kb0 + kb_per_split);
+        if (!mbar_wait(&tempty[acc], acc_ph ^ 1, abort_flag)) {
+          *abort_flag = 1;
+          atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_EMPTY);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d0 = tmem_base + acc * Cfg::ACC_COLS;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full[s], ph, abort_flag)) {
+            *abort_flag = 1;
+            atomicCAS(a.status, 0, ST_TIMEOUT_FULL);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
+          const uint64_t dw = umma_desc_k_sw128(sa);
+          const uint64_t dw2 = umma_desc_k_sw128(sa + W_TILE_BYTES);
+          const uint64_t dx = umma_desc_k_sw128(sa + W_TILE_BYTES * (DUAL ? 2 : 1));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
+            const uint64_t koff = uint64_t(k * UMMA_K * 2 / 16);
+            umma_f16(d0, dw + koff, dx + koff, idesc, accum);
+            if (DUAL) umma_f16(d0 + BN, dw2 + koff, dx + koff, idesc, accum);
+          }
+          umma_commit(&empty[s]);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull[acc]);
+        if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    WorkItem it;
+    for (int w = blockIdx.x; decode_work<BN>(a, w, n_tok_tiles, it); w += gridDim.x) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&tfull[acc], acc_ph, abort_flag))) {
+        *abort_flag = 1;
+        atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_FULL);
+        break;
+      }
+      tc_fence_after();
+      const int row = q * 32 + lane;               // row within the tile
+      const int feat = it.feat0 + row;
+      const bool feat_ok = feat < a.n_feat;
+      const uint32_t t0 = tmem_base + (uint32_t(q * 32) << 16) + acc * Cfg::ACC_COLS;
+
+      bool finalize = true;
+      if (a.split_k > 1) {
+        // fp32 partials: ws[tile][split][col][128 rows]
+        float* wsp = a.ws + (size_t(it.tile_id) * a.split_k + it.ks) * (Cfg::ACC_COLS * BM);
+#pragma unroll 1
+        for (int c = 0; c < Cfg::ACC_COLS; c += 32) {
+          uint32_t r[32];
+          tmem_ld32(t0 + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) wsp[(c + j) * BM + row] = __uint_as_float(r[j]);
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) {
+          const int old = atomicAdd(&a.counters[it.tile_id], 1);
+          *last_flag = (old == a.split_k - 1) ? 1 : 0;
+          if (old == a.split_k - 1) a.counters[it.tile_id] = 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        finalize = (*last_flag != 0);
+        if (finalize) __threadfence();
+      }
+
+      if (finalize) {
+        const float* wsb = a.split_k > 1 ? a.ws + size_t(it.tile_id) * a.split_k * (Cfg::ACC_COLS * BM) : nullptr;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          if (c >= it.ntok) break;
+          float g[32], u[32];
+          if (a.split_k > 1) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) { g[j] = 0.f; u[j] = 0.f; }
+            for (int sp = 0; sp < a.split_k; ++sp) {
+              const float* p = wsb + size_t(sp) * (Cfg::ACC_COLS * BM);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                g[j] += __ldcg(&p[(c + j) * BM + row]);
+                if (DUAL) u[j] += __ldcg(&p[(BN + c + j) * BM + row]);
+              }
+            }
+          } else {
+            uint32_t r[32];
+            tmem_ld32(t0 + c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) g[j] = __uint_as_float(r[j]);
+            if (DUAL) {
+              tmem_ld32(t0 + BN + c, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) u[j] = __uint_as_float(r[j]);
+            }
+          }
+          if (feat_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int t = c + j;
+              if (t < it.ntok) {
+                const int xrow = it.tok0 + t;
+                float v = g[j];
+                if (DUAL) v = (v / (1.f + __expf(-v))) * u[j];
+                if (a.tok_scale) v *= a.tok_scale[xrow];
+                long orow = xrow;
+                if (a.out_rows) orow = a.out_rows[xrow];
+                if (orow >= 0) {
+                  if (a.residual) v += __bfloat162float(a.residual[orow * a.ldr + feat]);
+                  if (OUT_F32) {
+                    reinterpret_cast<float*>(a.out)[orow * a.ldo + feat] = v;
+                  } else {
+                    reinterpret_cast<__nv_bfloat16*>(a.out)[orow * a.ldo + feat] = __float2bfloat16(v);
+                  }
+                }
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+thread_local char g_gemm_err[512];
+
+template <int BN, bool DUAL, bool OUT_F32>
+int launch(const CUtensorMap* tmW, const CUtensorMap* tmX, const WgemmArgs& a, int grid, cudaStream_t stream) {
+  using Cfg = WgemmCfg<BN, DUAL>;
+  auto kfn = wgemm_kernel<BN, DUAL, OUT_F32>;
+  static bool attr_set = false;  // per instantiation
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) {
+      snprintf(g_gemm_err, sizeof(g_gemm_err), "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+      return 1;
+    }
+    attr_set = true;
+  }
+  kfn<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(*tmW, *tmX, a);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    snprintf(g_gemm_err, sizeof(g_gemm_err), "wgemm launch: %s", cudaGetErrorString(e));
+    return 1;
+  }
+  return 0;
+}
+
+int g_num_sms = 0;
+
+}  // namespace
+
+int wgemm_pick_bn(int n_tok_per_tile_hint, bool dual) {
+  int bn = 32;
+  while (bn < n_tok_per_tile_hint && bn < (dual ? 128 : 256)) bn *= 2;
+  return bn;
+}
+
+size_t wgemm_workspace_floats(int bn, bool dual, int n_tok_tiles, int feat_tiles, int split_k) {
+  if (split_k <= 1) return 0;
+  return size_t(n_tok_tiles) * feat_tiles * split_k * (bn * (dual ? 2 : 1)) * BM;
+}
+
+const char* wgemm_last_error() { return g_gemm_err; }
+
+int wgemm_launch(const WgemmHost& h, cudaStream_t stream) {
+  if (h.K % 8 != 0) {
+    snprintf(g_gemm_err, sizeof(g_gemm_err), "wgemm: K=%d must be a multiple of 8 (16-byte TMA rows)", h.K);
+    return 1;
+  }
+  if ((reinterpret_cast<uintptr_t>(h.w) | reinterpret_cast<uintptr_t>(h.x)) & 15) {
+    snprintf(g_gemm_err, sizeof(g_gemm_err), "wgemm: operand base addresses must be 16-byte aligned");
+    return 1;
+  }
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  const int bn = h.bn;
+  const CUtensorMap* tmW =
+      tmap_2d(h.w, uint64_t(h.w_rows), uint64_t(h.K), uint64_t(h.ldw) * 2, BM, BK, TM_BF16, true);
+  const CUtensorMap* tmX =
+      tmap_2d(h.x, uint64_t(h.x_rows), uint64_t(h.K), uint64_t(h.ldx) * 2, uint32_t(bn), BK, TM_BF16, true);
+  if (!tmW || !tmX) {
+    snprintf(g_gemm_err, sizeof(g_gemm_err), "wgemm: %s", tmap_last_error());
+    return 1;
+  }
+  WgemmArgs a{};
+  a.out = h.out; a.ldo = h.ldo; a.residual = h.residual; a.ldr = h.ldr;
+  a.tok_scale = h.tok_scale; a.out_rows = h.out_rows;
+  a.K = h.K; a.n_feat = h.n_feat; a.feat_tiles = (h.n_feat + BM - 1) / BM;
+  a.n_tok = h.n_tok;
+  a.tile_group = h.tile_group; a.tile_tok0 = h.tile_tok0; a.tile_ntok = h.tile_ntok; a.n_tiles_dev = h.n_tiles_dev;
+  a.n_tok_tiles_max = h.n_tok_tiles_max;
+  a.rows_per_group = h.rows_per_group; a.dual_offset = h.dual_offset;
+  a.split_k = h.split_k < 1 ? 1 : h.split_k;
+  a.ws = h.ws; a.counters = h.counters; a.status = h.status;
+  const int num_kb = (h.K + BK - 1) / BK;
+  if (a.split_k > num_kb) a.split_k = num_kb;
+  while (a.split_k > 1 && (a.split_k - 1) * ((num_kb + a.split_k - 1) / a.split_k) >= num_kb) --a.split_k;
+  if (a.split_k > 1 && (!a.ws || !a.counters)) {
+    snprintf(g_gemm_err, sizeof(g_gemm_err), "wgemm: split-K needs a workspace and counters");
+    return 1;
+  }
+  const int n_tok_tiles = h.tile_group ? h.n_tok_tiles_max : (h.n_tok + bn - 1) / bn;
+  long total = long(n_tok_tiles) * a.feat_tiles * a.split_k;
+  if (total <= 0) return 0;
+  int grid = int(total < g_num_sms ? total : g_num_sms);
+
+#define LB_CASE(BN_, DUAL_)                                                                     \
+  if (bn == BN_ && h.dual == DUAL_) {                                                           \
+    return h.out_f32 ? launch<BN_, DUAL_, true>(tmW, tmX, a, grid, stream)                      \
+                     : launch<BN_, DUAL_, false>(tmW, tmX, a, grid, stream);                    \
+  }
+  LB_CASE(32, false) LB_CASE(64, false) LB_CASE(128, false) LB_CASE(256, false)
+  LB_CASE(32, true) LB_CASE(64, true) LB_CASE(128, true)
+#undef LB_CASE
+  snprintf(g_gemm_err, sizeof(g_gemm_err), "wgemm: unsupported tile bn=%d dual=%d", bn, int(h.dual));
+  return 1;
+}
+
+}  // namespace lb

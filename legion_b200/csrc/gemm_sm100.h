@@ -1,0 +1,53 @@
+// Host interface of the weights-as-M tcgen05 GEMM (gemm_sm100.cu).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+namespace lb {
+
+// Device-side argument block (passed by value to the kernel).
+struct WgemmArgs {
+  void* out;                      // bf16 or f32 [rows, ldo]
+  long ldo;
+  const __nv_bfloat16* residual;  // optional, added in the epilogue (indexed like out)
+  long ldr;
+  const float* tok_scale;         // optional per-activation-row multiplier
+  const int* out_rows;            // optional activation-row -> output-row map (negative = drop)
+  int K, n_feat, feat_tiles, n_tok;
+  const int* tile_group;          // grouped mode: expert of each token tile (nullptr = dense)
+  const int* tile_tok0;           //   first activation row of the tile
+  const int* tile_ntok;           //   valid rows in the tile
+  const int* n_tiles_dev;         //   number of token tiles (device scalar, data of a CUDA graph)
+  int n_tok_tiles_max;
+  int rows_per_group;             // weight rows between consecutive groups
+  int dual_offset;                // DUAL: rows from a feature's gate row to its up row
+  int split_k;
+  float* ws;                      // split-K partials
+  int* counters;                  // split-K arrival counters, zero on entry, left zero on exit
+  int* status;                    // error word (0 = ok)
+};
+
+// Host-side description of one launch.
+struct WgemmHost {
+  const void* w;   long w_rows; long ldw;   // weights [w_rows, K], row pitch ldw elements
+  const void* x;   long x_rows; long ldx;   // activations [x_rows, K]
+  void* out; long ldo; bool out_f32;
+  const __nv_bfloat16* residual; long ldr;
+  const float* tok_scale;
+  const int* out_rows;
+  int K, n_feat, n_tok;
+  int bn; bool dual;
+  const int* tile_group; const int* tile_tok0; const int* tile_ntok; const int* n_tiles_dev;
+  int n_tok_tiles_max;
+  int rows_per_group, dual_offset;
+  int split_k; float* ws; int* counters;
+  int* status;
+};
+
+int wgemm_launch(const WgemmHost& h, cudaStream_t stream);
+int wgemm_pick_bn(int n_tok_per_tile_hint, bool dual);
+size_t wgemm_workspace_floats(int bn, bool dual, int n_tok_tiles, int feat_tiles, int split_k);
+const char* wgemm_last_error();
+
+}  // namespace lb

@@ -1,0 +1,60 @@
+// C++ launch interface of the non-GEMM kernels. Pointers are device pointers; every function
+// returns 0 on success and enqueues on the given stream without synchronising.
+#pragma once
+#include <cuda_runtime.h>
+
+namespace lb {
+
+int rmsnorm_launch(const void* x, long ldx, const void* res_in, long ldri, void* res_out, long ldro, const float* w,
+                   void* y, long ldy, int rows, int H, float eps, float w_offset, cudaStream_t s);
+
+int qk_norm_rope_append_launch(const void* qkv, long ld_qkv, int q_head_stride, int k_off, int v_off, const float* qw,
+                               const float* kw, float eps, float w_offset, const float* cos_sin, int rot,
+                               const int* positions, const long* slots, void* q_out, void* k_cache, void* v_cache,
+                               long cache_cell_stride, int T, int Hq, int Hkv, int D, cudaStream_t s);
+
+int sigmoid_gate_launch(const void* attn, const void* qkv, long ld_qkv, int q_head_stride, int D, int Hq, void* out,
+                        long T, cudaStream_t s);
+
+int glu_launch(const void* x, long ldx, void* out, long ldo, int F, long T, int act, cudaStream_t s);
+
+int embed_launch(const int* ids, const void* table, long ldt, void* out, long ldo, int T, int H, int vocab,
+                 cudaStream_t s);
+
+int paged_decode_launch(const void* q, const void* k_cache, const void* v_cache, long cell_stride,
+                        const int* block_table, int table_width, int page, const int* ctx_lens, float scale, int window,
+                        int B, int Hq, int Hkv, int D, int n_splits, float* o_part, float* ml_part, void* out,
+                        cudaStream_t s);
+
+int prefill_attn_launch(const void* q, long T, const void* k_cache, const void* v_cache, long n_cells,
+                        long cell_stride, const int* cu_q, const int* ctx_lens, const int* block_table,
+                        int table_width, int page, int n_seqs, int max_q_len, int Hq, int Hkv, int D, float scale,
+                        int window, int causal, void* out, int* status, cudaStream_t s);
+const char* prefill_attn_last_error();
+
+int router_topk_launch(const float* logits, long ldl, const float* bias, int E, int k, int mode, int renorm,
+                       float route_scale, int n_group, int topk_group, int* ids, float* wts, int T, cudaStream_t s);
+
+int moe_plan_launch(const int* ids, const float* wts, int n_tokens, int k, int e_lo, int n_local, int bn, int* counts,
+                    int* offsets, int* sorted_token, int* sorted_pair, float* sorted_w, int* tile_group,
+                    int* tile_tok0, int* tile_ntok, int max_tiles, int* meta, cudaStream_t s);
+
+int gather_rows_launch(const void* src, long lds, const int* rows, const int* n_rows, void* dst, long ldd, int H,
+                       int max_rows, cudaStream_t s);
+
+int moe_combine_launch(const void* y, long ldy, const int* ids, int k, int e_lo, int e_hi, const void* shared, long lds,
+                       const float* shared_gate, const void* residual, long ldr, void* out, long ldo, int T, int H,
+                       cudaStream_t s);
+
+int argmax_launch(const void* logits, bool is_f32, long ld, int rows, int V, float* pv, int* pi, int nblk, int* out,
+                  float* out_val, cudaStream_t s);
+
+int sample_launch(const float* logits, long ld, int rows, int V, const float* temperature, const int* top_k,
+                  const float* top_p, const float* min_p, const unsigned long long* seeds, const int* steps,
+                  float* scratch, int* out, cudaStream_t s);
+
+int penalties_mask_launch(float* logits, long ld, int rows, int V, const int* counts, const unsigned char* seen,
+                          const float* presence, const float* frequency, const float* repetition,
+                          const unsigned int* mask, int mask_words, cudaStream_t s);
+
+}  // namespace lb

@@ -1,0 +1,358 @@
+"""Python front-ends of the sm_100a kernels in ``legion_b200/_C.so``.
+
+Every function takes CUDA tensors, enqueues on the current stream and never synchronises; scratch
+(split-K partials, attention split buffers, routing plans) comes from a per-device ``Workspace`` that
+is allocated once, so a decode step captured in a CUDA graph replays without allocator traffic.
+The extension is required on a GPU: there is no silent fallback to eager PyTorch.
+"""
+from __future__ import annotations
+
+import importlib
+import threading
+from typing import Optional
+
+import torch
+
+_C = None
+_C_err: Optional[BaseException] = None
+_lock = threading.Lock()
+
+
+def ext():
+    """Returns the extension module, importing ``legion_b200._C`` on first use."""
+    global _C, _C_err
+    if _C is None and _C_err is None:
+        with _lock:
+            if _C is None and _C_err is None:
+                try:
+                    _C = importlib.import_module("legion_b200._C")
+                except BaseException as e:  # missing .so, ABI mismatch, missing libcudart
+                    _C_err = e
+    if _C is None:
+        raise RuntimeError(
+            "legion_b200._C (the sm_100a extension) is not importable: build it with "
+            "`python -m legion_b200.build_ext`") from _C_err
+    return _C
+
+
+def have_ext() -> bool:
+    try:
+        ext()
+        return True
+    except RuntimeError:
+        return False
+
+
+NUM_SMS = 148
+
+
+class Workspace:
+    """Per-device scratch shared by all kernels on that device's compute stream."""
+
+    _by_device: dict = {}
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.counters = torch.zeros(1 << 16, dtype=torch.int32, device=device)
+        self.splitk = torch.empty(1 << 23, dtype=torch.float32, device=device)  # 32 MiB
+        self._attn: dict = {}
+        self._cache: dict = {}
+
+    @classmethod
+    def get(cls, device) -> "Workspace":
+        device = torch.device(device)
+        if device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        ws = cls._by_device.get(device)
+        if ws is None:
+            ws = cls(device)
+            cls._by_device[device] = ws
+        return ws
+
+    def buf(self, key, shape, dtype):
+        """A cached scratch tensor: same key and size -> same storage (graph-safe)."""
+        k = (key, tuple(shape), dtype)
+        t = self._cache.get(k)
+        if t is None:
+            t = torch.empty(shape, dtype=dtype, device=self.device)
+            self._cache[k] = t
+        return t
+
+    def check(self) -> int:
+        """Synchronises and returns the kernels' status word (0 = ok); clears it."""
+        v = int(self.status[0].item())
+        if v:
+            self.status.zero_()
+        return v
+
+
+def pick_bn(n_tok: int, dual: bool) -> int:
+    bn = 32
+    cap = 128 if dual else 256
+    while bn < n_tok and bn < cap:
+        bn *= 2
+    return bn
+
+
+def _pick_split_k(n_tok_tiles: int, feat_tiles: int, K: int) -> int:
+    """Split K when a skinny GEMM has too few tiles to keep the SMs streaming weights."""
+    tiles = n_tok_tiles * feat_tiles
+    num_kb = (K + 63) // 64
+    if tiles >= NUM_SMS // 2 or num_kb < 8:
+        return 1
+    s = min(NUM_SMS // max(tiles, 1), num_kb // 4, 16)
+    return max(1, s)
+
+
+def linear(x, w, residual=None, out=None, out_dtype=torch.bfloat16, split_k: Optional[int] = None, bn=None):
+    """out[T, N] = x[T, K] @ w[N, K]^T (+ residual)."""
+    C = ext()
+    T, K = x.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty(T, N, dtype=out_dtype, device=x.device)
+    if T == 0:
+        return out
+    ws = Workspace.get(x.device)
+    bn = bn or pick_bn(T, False)
+    n_tt = (T + bn - 1) // bn
+    ft = (N + 127) // 128
+    sk = _pick_split_k(n_tt, ft, K) if split_k is None else split_k
+    if sk > 1:
+        need = C.wgemm_workspace_floats(bn, False, n_tt, ft, sk)
+        if need > ws.splitk.numel() or n_tt * ft > ws.counters.numel():
+            sk = 1
+    C.wgemm(w, x, out, residual, None, None, N, False, 0, bn, sk, ws.splitk if sk > 1 else None,
+            ws.counters if sk > 1 else None, ws.status, None, None, None, None, 0, 0, T)
+    return out
+
+
+def gate_up_act(x, w_gate_up, n_ff: int, out=None, bn=None, split_k: Optional[int] = None):
+    """silu(x @ Wg^T) * (x @ Wu^T) with Wg = w_gate_up[:n_ff], Wu = w_gate_up[n_ff:]."""
+    C = ext()
+    T, K = x.shape
+    if out is None:
+        out = torch.empty(T, n_ff, dtype=torch.bfloat16, device=x.device)
+    if T == 0:
+        return out
+    ws = Workspace.get(x.device)
+    bn = bn or pick_bn(T, True)
+    n_tt = (T + bn - 1) // bn
+    ft = (n_ff + 127) // 128
+    sk = _pick_split_k(n_tt, ft, K) if split_k is None else split_k
+    if sk > 1:
+        need = C.wgemm_workspace_floats(bn, True, n_tt, ft, sk)
+        if need > ws.splitk.numel() or n_tt * ft > ws.counters.numel():
+            sk = 1
+    C.wgemm(w_gate_up, x, out, None, None, None, n_ff, True, n_ff, bn, sk, ws.splitk if sk > 1 else None,
+            ws.counters if sk > 1 else None, ws.status, None, None, None, None, 0, 0, T)
+    return out
+
+
+def rmsnorm(x, w, eps, w_offset=0.0, residual=None, out=None, sum_out=None):
+    """Returns (normed, summed). With a residual the sum x + residual is the new residual stream."""
+    C = ext()
+    if out is None:
+        out = torch.empty_like(x)
+    if residual is not None and sum_out is None:
+        sum_out = torch.empty_like(x)
+    C.rmsnorm(x, residual, sum_out, w, out, eps, w_offset)
+    return out, (sum_out if residual is not None else x)
+
+
+def qk_norm_rope_append(qkv, n_q, n_kv, d, q_norm_w, k_norm_w, eps, w_offset, cos_sin, rot, positions, slots,
+                        k_cache, v_cache, gated_q=False, q_out=None):
+    C = ext()
+    T = qkv.shape[0]
+    if q_out is None:
+        q_out = torch.empty(T, n_q, d, dtype=torch.bfloat16, device=qkv.device)
+    qhs = 2 * d if gated_q else d
+    k_off = n_q * qhs
+    v_off = k_off + n_kv * d
+    C.qk_norm_rope_append(qkv, qhs, k_off, v_off, q_norm_w, k_norm_w, eps, w_offset, cos_sin, rot, positions, slots,
+                          q_out, k_cache, v_cache, n_q, n_kv, d)
+    return q_out
+
+
+def sigmoid_gate(attn, qkv, n_q, d, out=None):
+    C = ext()
+    if out is None:
+        out = torch.empty_like(attn)
+    C.sigmoid_gate(attn, qkv, 2 * d, d, n_q, out)
+    return out
+
+
+def decode_splits(batch: int, n_kv_heads: int, g_tiles: int, max_ctx: int) -> int:
+    """Flash-decoding split count: enough CTAs for ~2 waves of the SMs, at most one per 256 keys."""
+    ctas = max(1, batch * n_kv_heads * g_tiles)
+    want = max(1, (2 * NUM_SMS + ctas - 1) // ctas)
+    cap = max(1, (max_ctx + 255) // 256)
+    return int(min(want, cap, 64))
+
+
+def paged_decode(q, k_cache, v_cache, block_table, ctx_lens, scale, window=0, n_splits=None, max_ctx=None, out=None):
+    C = ext()
+    B, Hq, D = q.shape
+    Hkv = k_cache.shape[2]
+    if n_splits is None:
+        G = Hq // Hkv
+        gt = 8 if G >= 8 else (4 if G > 2 else G)
+        n_splits = decode_splits(B, Hkv, (G + gt - 1) // gt, max_ctx or block_table.shape[1] * k_cache.shape[1])
+    ws = Workspace.get(q.device)
+    o_part = ws.buf("dec_o", (B * Hq * n_splits * D,), torch.float32)
+    ml_part = ws.buf("dec_ml", (B * Hq * n_splits * 2,), torch.float32)
+    if out is None:
+        out = torch.empty_like(q)
+    C.paged_decode(q, k_cache, v_cache, block_table, ctx_lens, scale, window, n_splits, o_part, ml_part, out)
+    return out
+
+
+def prefill_attn(q, k_cache, v_cache, cu_q, ctx_lens, block_table, max_q_len, scale, window=0, causal=True, out=None):
+    C = ext()
+    if out is None:
+        out = torch.empty_like(q)
+    ws = Workspace.get(q.device)
+    C.prefill_attn(q, k_cache, v_cache, cu_q, ctx_lens, block_table, max_q_len, scale, window, causal, out, ws.status)
+    return out
+
+
+def router_topk(logits, k, mode="softmax", renorm=True, route_scale=1.0, bias=None, n_group=1, topk_group=1,
+                ids=None, wts=None):
+    C = ext()
+    T = logits.shape[0]
+    if ids is None:
+        ids = torch.empty(T, k, dtype=torch.int32, device=logits.device)
+        wts = torch.empty(T, k, dtype=torch.float32, device=logits.device)
+    C.router_topk(logits, bias, k, 0 if mode == "softmax" else 1, renorm, route_scale, n_group, topk_group, ids, wts)
+    return ids, wts
+
+
+class MoePlan:
+    """Device buffers of one routing plan (sized for the largest step; reused every step)."""
+
+    def __init__(self, max_tokens: int, k: int, n_local: int, bn: int, device):
+        P = max_tokens * k
+        i32 = dict(dtype=torch.int32, device=device)
+        self.max_tokens, self.k, self.n_local, self.bn = max_tokens, k, n_local, bn
+        self.max_tiles = (P + bn - 1) // bn + n_local
+        self.counts = torch.zeros(n_local, **i32)
+        self.offsets = torch.zeros(n_local + 1, **i32)
+        self.sorted_token = torch.zeros(P, **i32)
+        self.sorted_pair = torch.zeros(P, **i32)
+        self.sorted_w = torch.zeros(P, dtype=torch.float32, device=device)
+        self.tile_group = torch.zeros(self.max_tiles, **i32)
+        self.tile_tok0 = torch.zeros(self.max_tiles, **i32)
+        self.tile_ntok = torch.zeros(self.max_tiles, **i32)
+        self.meta = torch.zeros(2, **i32)  # {n_tiles, n_rows}
+        self.x_sorted = None
+        self.h_sorted = None
+        self.y_pairs = None
+
+
+def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[MoePlan] = None, shared=None,
+                shared_gate=None, residual=None, out=None):
+    """Routed experts over the device routing plan: plan -> gather -> grouped gate/up (+SwiGLU) ->
+    grouped down (x routing weight) -> combine (+ shared expert, + residual).
+
+    w_gate_up: [E_local, 2*n_ff, H]; w_down: [E_local, H, n_ff]; ids/wts: [T, k]. Returns bf16 [T, H]."""
+    C = ext()
+    T, H = x.shape
+    k = ids.shape[1]
+    E_local = w_gate_up.shape[0]
+    ws = Workspace.get(x.device)
+    if plan is None:
+        bn = 32 if T * k <= 32 * E_local else (64 if T * k <= 64 * E_local else 128)
+        key = ("moe_plan", T, k, E_local, bn)
+        plan = ws._cache.get(key)
+        if plan is None:
+            plan = MoePlan(T, k, E_local, bn, x.device)
+            ws._cache[key] = plan
+    P = T * k
+    bn = plan.bn
+    if plan.x_sorted is None or plan.x_sorted.shape[0] < P + bn or plan.x_sorted.shape[1] != H:
+        # padded by one tile so a tile that starts near the end stays inside the tensor map's rows
+        plan.x_sorted = torch.zeros(P + bn, H, dtype=torch.bfloat16, device=x.device)
+        plan.h_sorted = torch.zeros(P + bn, n_ff, dtype=torch.bfloat16, device=x.device)
+        plan.y_pairs = torch.zeros(P, H, dtype=torch.bfloat16, device=x.device)
+    C.moe_plan(ids, wts, e_lo, E_local, bn, plan.counts, plan.offsets, plan.sorted_token, plan.sorted_pair,
+               plan.sorted_w, plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta)
+    C.gather_rows(x, plan.sorted_token, plan.meta[1:2], plan.x_sorted[:P])
+    wgu = w_gate_up.view(E_local * 2 * n_ff, H)
+    C.wgemm(wgu, plan.x_sorted, plan.h_sorted, None, None, None, n_ff, True, n_ff, bn, 1, None, None, ws.status,
+            plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta, plan.max_tiles, 2 * n_ff, 0)
+    wd = w_down.view(E_local * H, n_ff)
+    C.wgemm(wd, plan.h_sorted, plan.y_pairs, None, plan.sorted_w, plan.sorted_pair, H, False, 0, bn, 1, None, None,
+            ws.status, plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta, plan.max_tiles, H, 0)
+    if out is None:
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+    C.moe_combine(plan.y_pairs, ids, e_lo, e_lo + E_local, shared, shared_gate, residual, out)
+    return out
+
+
+def argmax(logits, out=None):
+    C = ext()
+    rows, V = logits.shape
+    ws = Workspace.get(logits.device)
+    nblk = max(1, min(64, (V + 4095) // 4096))
+    pv = ws.buf("argmax_v", (rows * nblk,), torch.float32)
+    pi = ws.buf("argmax_i", (rows * nblk,), torch.int32)
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    C.argmax(logits, pv, pi, out, None)
+    return out
+
+
+def sample(logits, temperature, top_k, top_p, min_p, seeds, steps, out=None):
+    C = ext()
+    rows, V = logits.shape
+    ws = Workspace.get(logits.device)
+    scratch = ws.buf("sample", (rows * V,), torch.float32)
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    C.sample(logits, temperature, top_k, top_p, min_p, seeds, steps, scratch, out)
+    return out
+
+
+def causal_conv1d_silu(x, w, bias, conv_state, cu_seq, slots, write_state=True, out=None):
+    C = ext()
+    if out is None:
+        out = torch.empty_like(x)
+    C.conv1d_silu(x, w, bias, conv_state, cu_seq, slots, out, write_state)
+    return out
+
+
+def gdn_gates(a, b, A, dt_bias):
+    C = ext()
+    g = torch.empty(a.shape, dtype=torch.float32, device=a.device)
+    beta = torch.empty_like(g)
+    C.gdn_gates(a, b, A, dt_bias, g, beta)
+    return g, beta
+
+
+def gdn_recurrent(qkv, g, beta, state, cu_seq, slots, n_k, n_v, dk, dv, tiled_heads, scale, l2_eps=1e-6,
+                  write_state=True, out=None):
+    C = ext()
+    T = qkv.shape[0]
+    if out is None:
+        out = torch.empty(T, n_v, dv, dtype=torch.bfloat16, device=qkv.device)
+    C.gdn_recurrent(qkv, g, beta, state, cu_seq, slots, n_k, n_v, dk, dv, tiled_heads, scale, l2_eps, out,
+                    write_state, True)
+    return out
+
+
+def gated_rmsnorm(o, z, w, eps, act="silu", out=None):
+    C = ext()
+    T, Hv, DV = o.shape
+    if out is None:
+        out = torch.empty_like(o)
+    C.gated_rmsnorm(o, z, w, eps, Hv, DV, 0 if act == "silu" else 1, out)
+    return out
+
+
+def embed(ids, table, out=None):
+    C = ext()
+    if out is None:
+        out = torch.empty(ids.numel(), table.shape[1], dtype=torch.bfloat16, device=table.device)
+    C.embed(ids, table, out)
+    return out

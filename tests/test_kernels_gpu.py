@@ -1,0 +1,275 @@
+"""sm_100a kernels against the fp32 PyTorch reference of the same op (small, ragged and boundary shapes)."""
+import math
+
+import pytest
+import torch
+
+from legion_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def sm():
+    from legion_b200.ops import sm100
+    return sm100
+
+
+def status_ok():
+    from legion_b200.ops.sm100 import Workspace
+    torch.cuda.synchronize()
+    assert Workspace.get(torch.device(DEV)).check() == 0
+
+
+def close(a, b, rtol=2e-2, atol=2e-2):
+    a, b = a.float().cpu(), b.float().cpu()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    assert bool((err <= tol).all()), f"max err {err.max().item():.4g} (ref max {b.abs().max().item():.4g})"
+
+
+def rnd(*shape, scale=1.0):
+    return (torch.randn(*shape, device=DEV) * scale).bfloat16()
+
+
+@pytest.mark.parametrize("T,N,K", [(1, 128, 64), (16, 256, 128), (33, 200, 192), (100, 384, 2048), (300, 130, 72),
+                                   (16, 5120, 2048), (513, 512, 256)])
+@pytest.mark.parametrize("split_k", [1, 3])
+def test_linear(T, N, K, split_k):
+    torch.manual_seed(T * 7 + N)
+    x, w = rnd(T, K), rnd(N, K, scale=K ** -0.5)
+    out = sm().linear(x, w, split_k=split_k)
+    status_ok()
+    close(out, ref.linear(x, w))
+
+
+def test_linear_structured_identity():
+    # one-hot rows localise layout bugs: out[t, n] must be exactly w[n, t]
+    K = 128
+    x = torch.eye(K, device=DEV).bfloat16()
+    w = rnd(256, K)
+    out = sm().linear(x, w, split_k=1)
+    status_ok()
+    assert torch.equal(out, w.t().contiguous())
+
+
+def test_linear_residual_f32_and_repeat():
+    x, w, r = rnd(40, 256), rnd(384, 256, scale=1 / 16), rnd(40, 384)
+    a = sm().linear(x, w, residual=r)
+    b = sm().linear(x, w, residual=r)
+    status_ok()
+    close(a, ref.linear(x, w, residual=r))
+    assert torch.equal(a, b)  # run-to-run determinism
+    f = sm().linear(x, w, out_dtype=torch.float32)
+    close(f, ref.linear(x, w, out_dtype=torch.float32), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("T,F,K,split_k", [(5, 128, 64, 1), (64, 768, 2048, 1), (130, 200, 256, 1), (16, 768, 2048, 4)])
+def test_gate_up_act(T, F, K, split_k):
+    x, w = rnd(T, K), rnd(2 * F, K, scale=K ** -0.5)
+    out = sm().gate_up_act(x, w, F, split_k=split_k)
+    status_ok()
+    close(out, ref.gate_up_act(x, w, F))
+
+
+@pytest.mark.parametrize("T,E,k,H,F", [(4, 8, 2, 256, 128), (16, 128, 8, 512, 256), (300, 16, 4, 256, 192), (1, 8, 2, 128, 64)])
+def test_moe_experts(T, E, k, H, F):
+    torch.manual_seed(E + T)
+    x = rnd(T, H)
+    logits = torch.randn(T, E, device=DEV)
+    ids, wts = sm().router_topk(logits, k)
+    rids, rwts = ref.router_topk(logits, k)
+    assert torch.equal(ids.cpu(), rids.cpu())
+    close(wts, rwts, 1e-4, 1e-5)
+    wgu, wd = rnd(E, 2 * F, H, scale=H ** -0.5), rnd(E, H, F, scale=F ** -0.5)
+    res = rnd(T, H)
+    out = sm().moe_experts(x, ids, wts, wgu, wd, F, residual=res)
+    status_ok()
+    want = ref.moe_experts(x, ids, wts, wgu, wd, F) + res.float()
+    close(out, want, 3e-2, 3e-2)
+    out2 = sm().moe_experts(x, ids, wts, wgu, wd, F, residual=res)
+    assert torch.equal(out, out2)
+
+
+def test_router_group_limited():
+    T, E = 37, 256
+    logits = torch.randn(T, E, device=DEV)
+    bias = torch.randn(E, device=DEV) * 0.1
+    ids, wts = sm().router_topk(logits, 8, mode="sigmoid", renorm=True, route_scale=2.5, bias=bias, n_group=8, topk_group=4)
+    rids, rwts = ref.router_topk(logits, 8, mode="sigmoid", renorm=True, route_scale=2.5, bias=bias, n_group=8, topk_group=4)
+    assert torch.equal(ids.cpu(), rids.cpu())
+    close(wts, rwts, 1e-4, 1e-5)
+
+
+@pytest.mark.parametrize("H", [256, 2048, 5120])
+def test_rmsnorm(H):
+    x, r = rnd(19, H), rnd(19, H)
+    w = torch.rand(H, device=DEV) + 0.5
+    y, s = sm().rmsnorm(x, w, 1e-6, residual=r)
+    ry, rs = ref.rmsnorm(x, w, 1e-6, residual=r)
+    close(y, ry)
+    assert torch.equal(s, rs)
+    y2, _ = sm().rmsnorm(x, w, 1e-6, w_offset=1.0)
+    close(y2, ref.rmsnorm(x, w, 1e-6, w_offset=1.0)[0])
+
+
+def make_cache(n_blocks, page, Hkv, D):
+    return rnd(n_blocks, page, Hkv, D), rnd(n_blocks, page, Hkv, D)
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,rot,gated", [(128, 8, 2, 128, False), (64, 4, 2, 64, False), (256, 4, 1, 64, True)])
+def test_qk_norm_rope_append(D, Hq, Hkv, rot, gated):
+    T, page, n_blocks = 21, 16, 8
+    qw = Hq * D * (2 if gated else 1)
+    qkv = rnd(T, qw + 2 * Hkv * D)
+    qn, kn = torch.rand(D, device=DEV) + 0.5, torch.rand(D, device=DEV) + 0.5
+    cs = ref.rope_cos_sin(512, rot, 1e6, device=DEV)
+    pos = torch.arange(100, 100 + T, device=DEV, dtype=torch.int32)
+    slots = torch.randperm(n_blocks * page, device=DEV)[:T].long()
+    kc, vc = make_cache(n_blocks, page, Hkv, D)
+    kc2, vc2 = kc.clone(), vc.clone()
+    q = sm().qk_norm_rope_append(qkv, Hq, Hkv, D, qn, kn, 1e-6, 0.0, cs, rot, pos, slots, kc, vc, gated_q=gated)
+    rq, rgate = ref.qk_norm_rope_append(qkv, Hq, Hkv, D, qn, kn, 1e-6, 0.0, cs, rot, pos, slots, kc2, vc2, gated_q=gated)
+    close(q, rq)
+    close(kc, kc2)
+    assert torch.equal(vc, vc2)
+    if gated:
+        attn = rnd(T, Hq, D)
+        g = sm().sigmoid_gate(attn, qkv, Hq, D)
+        close(g, attn.float() * torch.sigmoid(rgate.float()))
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,page", [(128, 32, 4, 64), (64, 4, 2, 16), (256, 16, 2, 64), (128, 40, 8, 16), (128, 6, 2, 32)])
+def test_paged_decode(D, Hq, Hkv, page):
+    torch.manual_seed(D + Hq)
+    B = 3
+    ctx = [1, 77, 300]
+    n_blocks = 64
+    kc, vc = make_cache(n_blocks, page, Hkv, D)
+    width = (max(ctx) + page - 1) // page
+    bt = torch.stack([torch.randperm(n_blocks, device=DEV)[:width] for _ in range(B)]).int()
+    q = rnd(B, Hq, D)
+    ctx_t = torch.tensor(ctx, device=DEV, dtype=torch.int32)
+    scale = D ** -0.5
+    for ns in (1, 3):
+        out = sm().paged_decode(q, kc, vc, bt, ctx_t, scale, n_splits=ns)
+        want = ref.paged_attention(q, kc, vc, bt, ctx_t, torch.arange(B + 1), scale)
+        close(out, want)
+    outw = sm().paged_decode(q, kc, vc, bt, ctx_t, scale, window=50, n_splits=2)
+    close(outw, ref.paged_attention(q, kc, vc, bt, ctx_t, torch.arange(B + 1), scale, window=50))
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,page", [(128, 4, 2, 64), (64, 4, 2, 16), (256, 2, 1, 64), (128, 8, 8, 32)])
+def test_prefill_attn(D, Hq, Hkv, page):
+    torch.manual_seed(D + page)
+    q_lens = [5, 130, 257]
+    ctx = [5, 200, 257]          # second sequence has 70 cached tokens before its chunk
+    n_blocks = 48
+    kc, vc = make_cache(n_blocks, page, Hkv, D)
+    width = (max(ctx) + page - 1) // page + 1
+    bt = torch.stack([torch.randperm(n_blocks, device=DEV)[:width] for _ in q_lens]).int()
+    cu = torch.tensor([0, 5, 135, 392], device=DEV, dtype=torch.int32)
+    q = rnd(392, Hq, D)
+    ctx_t = torch.tensor(ctx, device=DEV, dtype=torch.int32)
+    scale = D ** -0.5
+    out = sm().prefill_attn(q, kc, vc, cu, ctx_t, bt, max(q_lens), scale)
+    status_ok()
+    want = ref.paged_attention(q, kc, vc, bt, ctx_t, cu, scale)
+    close(out, want, 3e-2, 3e-2)
+    outw = sm().prefill_attn(q, kc, vc, cu, ctx_t, bt, max(q_lens), scale, window=64)
+    status_ok()
+    close(outw, ref.paged_attention(q, kc, vc, bt, ctx_t, cu, scale, window=64), 3e-2, 3e-2)
+
+
+def test_argmax_and_sample():
+    V = 151936
+    logits = torch.randn(5, V, device=DEV)
+    logits[2, 77] = 50.0
+    logits[3, V - 1] = 60.0
+    assert torch.equal(sm().argmax(logits).cpu(), ref.argmax(logits).cpu())
+    assert torch.equal(sm().argmax(logits.bfloat16()).cpu(), ref.argmax(logits.bfloat16()).cpu())
+    temp = torch.tensor([0.0, 1.0, 1.0, 0.7, 1.0], device=DEV)
+    tk = torch.tensor([0, 1, 50, 0, 0], device=DEV, dtype=torch.int32)
+    tp = torch.tensor([1.0, 1.0, 1.0, 0.5, 1.0], device=DEV)
+    mp = torch.tensor([0.0, 0.0, 0.0, 0.0, 0.0], device=DEV)
+    seeds = torch.arange(5, device=DEV, dtype=torch.int64) + 1234
+    steps = torch.zeros(5, device=DEV, dtype=torch.int32)
+    out = sm().sample(logits, temp, tk, tp, mp, seeds, steps).cpu()
+    am = ref.argmax(logits).cpu()
+    assert out[0] == am[0] and out[1] == am[1] and out[2] == 77 and out[3] == V - 1
+    # unrestricted row: empirical distribution over a tiny vocab matches softmax
+    small = torch.tensor([[2.0, 1.0, 0.0, -1.0]], device=DEV).repeat(4000, 1)
+    t1 = torch.ones(4000, device=DEV)
+    sd = torch.arange(4000, device=DEV, dtype=torch.int64)
+    draws = sm().sample(small, t1, None, None, None, sd, None).cpu()
+    freq = torch.bincount(draws, minlength=4).float() / 4000
+    close(freq, torch.softmax(small[0].cpu(), -1), 0.0, 0.03)
+
+
+@pytest.mark.parametrize("nk,nv,dk,dv,tiled", [(2, 4, 64, 64, False), (2, 4, 128, 128, True), (4, 4, 32, 32, False)])
+def test_gdn(nk, nv, dk, dv, tiled):
+    torch.manual_seed(dk)
+    cu = torch.tensor([0, 1, 9, 40], device=DEV, dtype=torch.int32)
+    slots = torch.tensor([2, 0, 3], device=DEV, dtype=torch.int32)
+    T = 40
+    C = 2 * nk * dk + nv * dv
+    x = rnd(T, C)
+    w = torch.randn(C, 4, device=DEV) * 0.5
+    cst = torch.randn(4, C, 3, device=DEV)
+    cst2 = cst.clone()
+    y = sm().causal_conv1d_silu(x, w, None, cst, cu, slots)
+    ry = ref.causal_conv1d_silu(x, w, None, cst2, cu, slots)
+    close(y, ry)
+    close(cst, cst2, 1e-5, 1e-5)
+    a, b = rnd(T, nv), rnd(T, nv)
+    A = -torch.rand(nv, device=DEV) - 0.1
+    dtb = torch.randn(nv, device=DEV)
+    g, beta = sm().gdn_gates(a, b, A, dtb)
+    rg, rb = ref.gdn_gates(a, b, A, dtb)
+    close(g, rg, 1e-4, 1e-5)
+    close(beta, rb, 1e-4, 1e-5)
+    st = torch.randn(4, nv, dk, dv, device=DEV) * 0.1
+    st2 = st.clone()
+    o = sm().gdn_recurrent(y, g, beta, st, cu, slots, nk, nv, dk, dv, tiled, dk ** -0.5)
+    ro = ref.gdn_recurrent(ry, rg, rb, st2, cu, slots, nk, nv, dk, dv, tiled, dk ** -0.5)
+    close(o, ro, 3e-2, 3e-2)
+    close(st, st2, 2e-2, 2e-2)
+    z = rnd(T, nv * dv)
+    nw = torch.rand(dv, device=DEV) + 0.5
+    n = sm().gated_rmsnorm(o, z, nw, 1e-6)
+    close(n, ref.gated_rmsnorm(o, z.view(T, nv, dv), nw, 1e-6))
+
+
+def test_block_formats_roundtrip():
+    from legion_b200.ops.sm100 import ext
+    C = ext()
+    w = rnd(256, 512, scale=0.02)
+    gs = torch.tensor([float(w.float().abs().max()) / (6 * 448)], device=DEV)
+    codes = torch.empty(256, 256, dtype=torch.uint8, device=DEV)
+    scales = torch.empty(256, 32, dtype=torch.uint8, device=DEV)
+    C.nvfp4_quant(w, gs, codes, scales)
+    back = torch.empty_like(w)
+    C.nvfp4_dequant(codes, scales, gs, back)
+    rel = (back.float() - w.float()).norm() / w.float().norm()
+    assert rel < 0.12, rel
+    q8 = torch.empty(256, 512, dtype=torch.uint8, device=DEV)
+    sc = torch.empty(2, 4, dtype=torch.float32, device=DEV)
+    C.fp8_block_quant(w, 128, 128, q8, sc)
+    back8 = torch.empty_like(w)
+    C.fp8_block_dequant(q8, sc, 128, 128, back8)
+    rel8 = (back8.float() - w.float()).norm() / w.float().norm()
+    assert rel8 < 0.04, rel8
+    want = (q8.view(torch.float8_e4m3fn).float().view(2, 128, 4, 128) * sc[:, None, :, None]).view(256, 512)
+    close(back8, want, 1e-2, 1e-6)
+
+
+def test_wait_deadline_sets_status_and_context_survives():
+    from legion_b200.ops.sm100 import ext
+    C = ext()
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    C.wait_flag(flag, 1, 2_000_000, status)  # 2 ms deadline on a flag nothing sets
+    torch.cuda.synchronize()
+    assert int(status.item()) == 5
+    assert float((torch.ones(4, device=DEV) * 2).sum()) == 8.0
