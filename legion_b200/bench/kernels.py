@@ -1,0 +1,145 @@
+"""Kernel micro-benchmarks: device-timed (CUDA events, warm-up, L2 flush between iterations), reported
+as achieved TFLOP/s or GB/s and as a fraction of the measured peaks in ``MEASURED_PEAKS.json``.
+
+Usage: ``python -m legion_b200.bench.kernels [--only gemm,moe,decode_attn,prefill_attn] [--json out.json]``
+The reference ships one hidden ``legion <kernel>-bench`` command per custom kernel (``src/cli/mod.rs:109-215``);
+this module is their counterpart.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+
+def peaks():
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = os.path.join(here, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+_flush = None
+
+
+def flush_l2():
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _flush.zero_()
+
+
+def timeit(fn, iters=10, warmup=3, flush=True):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush:
+            flush_l2()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def bench_gemm(rows):
+    from legion_b200.ops import sm100
+    hbm, tf, src = peaks()
+    for (T, N, K) in [(8192, 5120, 2048), (8192, 2048, 4096), (4096, 8192, 8192), (16, 5120, 2048), (16, 2048, 4096),
+                      (64, 151936, 2048), (1, 5120, 2048), (256, 17408, 5120)]:
+        x = torch.randn(T, K, device="cuda").bfloat16()
+        w = torch.randn(N, K, device="cuda").bfloat16()
+        out = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+        ms = timeit(lambda: sm100.linear(x, w, out=out))
+        ms_t = timeit(lambda: torch.matmul(x, w.t(), out=out))
+        fl = 2.0 * T * N * K / ms / 1e9
+        gb = (N * K + T * K + T * N) * 2 / ms / 1e6
+        rows.append(dict(kernel="wgemm", T=T, N=N, K=K, ms=ms, tflops=fl, gbs=gb, frac_tflops=fl / tf, frac_hbm=gb / hbm,
+                         cublas_ms=ms_t, peaks=src))
+        print(rows[-1], flush=True)
+
+
+def bench_moe(rows):
+    from legion_b200.ops import sm100
+    hbm, tf, src = peaks()
+    E, k, H, F = 128, 8, 2048, 768
+    wgu = (torch.randn(E, 2 * F, H, device="cuda") * 0.02).bfloat16()
+    wd = (torch.randn(E, H, F, device="cuda") * 0.02).bfloat16()
+    for T in (1, 16, 64, 1024, 8192):
+        x = torch.randn(T, H, device="cuda").bfloat16()
+        logits = torch.randn(T, E, device="cuda")
+        ids, wts = sm100.router_topk(logits, k)
+        ms = timeit(lambda: sm100.moe_experts(x, ids, wts, wgu, wd, F))
+        n_act = int(torch.unique(ids).numel())
+        byts = n_act * 3 * H * F * 2
+        fl = 2.0 * T * k * 3 * H * F / ms / 1e9
+        rows.append(dict(kernel="moe_experts", T=T, active_experts=n_act, ms=ms, tflops=fl, weight_gbs=byts / ms / 1e6,
+                         frac_tflops=fl / tf, frac_hbm=byts / ms / 1e6 / hbm, peaks=src))
+        print(rows[-1], flush=True)
+
+
+def bench_decode_attn(rows):
+    from legion_b200.ops import sm100
+    hbm, tf, src = peaks()
+    Hq, Hkv, D, page = 32, 4, 128, 64
+    for B, ctx in ((1, 8192), (16, 8192), (64, 8192), (16, 1024)):
+        nb = B * ((ctx + page - 1) // page)
+        kc = torch.randn(nb, page, Hkv, D, device="cuda").bfloat16()
+        vc = torch.randn(nb, page, Hkv, D, device="cuda").bfloat16()
+        bt = torch.arange(nb, device="cuda", dtype=torch.int32).view(B, -1)
+        q = torch.randn(B, Hq, D, device="cuda").bfloat16()
+        cl = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
+        ms = timeit(lambda: sm100.paged_decode(q, kc, vc, bt, cl, D ** -0.5, max_ctx=ctx))
+        byts = B * ctx * Hkv * D * 2 * 2
+        rows.append(dict(kernel="paged_decode", B=B, ctx=ctx, ms=ms, gbs=byts / ms / 1e6, frac_hbm=byts / ms / 1e6 / hbm,
+                         peaks=src))
+        print(rows[-1], flush=True)
+
+
+def bench_prefill_attn(rows):
+    from legion_b200.ops import sm100
+    hbm, tf, src = peaks()
+    Hq, Hkv, D, page = 32, 4, 128, 64
+    for n_seq, L in ((1, 8192), (4, 2048), (1, 32768)):
+        nb = n_seq * (L // page)
+        kc = torch.randn(nb, page, Hkv, D, device="cuda").bfloat16()
+        vc = torch.randn(nb, page, Hkv, D, device="cuda").bfloat16()
+        bt = torch.arange(nb, device="cuda", dtype=torch.int32).view(n_seq, -1)
+        q = torch.randn(n_seq * L, Hq, D, device="cuda").bfloat16()
+        cu = torch.arange(0, (n_seq + 1) * L, L, device="cuda", dtype=torch.int32)
+        cl = torch.full((n_seq,), L, device="cuda", dtype=torch.int32)
+        out = torch.empty_like(q)
+        ms = timeit(lambda: sm100.prefill_attn(q, kc, vc, cu, cl, bt, L, D ** -0.5, out=out), iters=5)
+        fl = 4.0 * n_seq * L * L / 2 * D * Hq / ms / 1e9
+        rows.append(dict(kernel="prefill_attn", n_seq=n_seq, L=L, ms=ms, tflops=fl, frac_tflops=fl / tf, peaks=src))
+        print(rows[-1], flush=True)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="gemm,moe,decode_attn,prefill_attn")
+    ap.add_argument("--json", default=None)
+    a = ap.parse_args(argv)
+    rows = []
+    table = {"gemm": bench_gemm, "moe": bench_moe, "decode_attn": bench_decode_attn, "prefill_attn": bench_prefill_attn}
+    for name in a.only.split(","):
+        table[name](rows)
+    from legion_b200.ops.sm100 import Workspace
+    torch.cuda.synchronize()
+    print("status word:", Workspace.get("cuda").check())
+    if a.json:
+        json.dump(rows, open(a.json, "w"), indent=1)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])

@@ -1,0 +1,199 @@
+"""Model hyper-parameters (one dataclass for every supported architecture) and named presets.
+
+The reference keeps these in ``Hparams`` read from GGUF metadata (``src/model/core.rs:170-203``) plus
+per-architecture hooks (``src/model/core/arch.rs:82-526``); here every architecture is a configuration of
+the same block library, selected by ``layer_kinds`` and the MoE / attention fields.
+"""
+from __future__ import annotations
+
+import dataclasses
+import json
+from dataclasses import dataclass, field
+from typing import List, Optional
+
+
+@dataclass
+class ModelConfig:
+    arch: str = "qwen3moe"             # registry key (see models.registry)
+    n_layer: int = 4
+    hidden: int = 256
+    vocab: int = 4096
+    rms_eps: float = 1e-6
+    norm_offset: float = 0.0           # 1.0 for checkpoints that store (weight - 1)
+    tie_embeddings: bool = False
+    max_position: int = 131072
+    # attention
+    n_head: int = 4
+    n_kv_head: int = 2
+    head_dim: int = 64
+    rope_theta: float = 1e6
+    rope_dim: Optional[int] = None     # rotary dims per head (None = head_dim); multiple of 64
+    rope_scaling: Optional[dict] = None
+    qk_norm: bool = True
+    gated_attn: bool = False           # q projection emits [q | gate] per head, out *= sigmoid(gate)
+    sliding_window: int = 0            # window of "swa" layers
+    attn_softcap: float = 0.0
+    logit_softcap: float = 0.0
+    attn_scale: Optional[float] = None
+    # layer pattern: one of "attn", "swa", "gdn", "mla", "mamba2", "kda" per layer
+    layer_kinds: Optional[List[str]] = None
+    full_attention_interval: int = 0   # >0: layer il is "gdn" unless (il + 1) % interval == 0
+    # gated delta net
+    gdn_k_heads: int = 4
+    gdn_v_heads: int = 4
+    gdn_k_dim: int = 64
+    gdn_v_dim: int = 64
+    gdn_conv: int = 4
+    gdn_tiled_heads: bool = False      # value head h reads key head h % n_k (GGUF order) instead of h // (n_v/n_k)
+    gdn_gate_act: str = "silu"         # activation of z in the gated output norm
+    # mamba2 (nemotron-h)
+    ssm_state: int = 128
+    ssm_heads: int = 8
+    ssm_head_dim: int = 64
+    ssm_groups: int = 1
+    ssm_conv: int = 4
+    # MLA
+    q_lora: int = 0
+    kv_lora: int = 0
+    qk_nope_dim: int = 0
+    qk_rope_dim: int = 0
+    v_head_dim: int = 0
+    # feed-forward
+    ffn_act: str = "silu"              # silu | gelu_tanh | relu2
+    dense_ff: int = 0                  # FFN width of dense layers
+    first_dense_layers: int = 0        # leading layers that use the dense FFN in a MoE model
+    n_expert: int = 0
+    top_k: int = 0
+    expert_ff: int = 0
+    shared_ff: int = 0                 # width of the shared expert (0 = none)
+    shared_gate: bool = False          # sigmoid(x . w) gate on the shared expert
+    router_mode: str = "softmax"       # softmax | sigmoid
+    router_bias: bool = False          # selection bias (sigmoid routers)
+    norm_topk: bool = True
+    route_scale: float = 1.0
+    n_group: int = 1
+    topk_group: int = 1
+    # multi-token prediction
+    mtp_layers: int = 0
+    # weights
+    dtype: str = "bf16"                # compute dtype on GPU: bf16; CPU engine uses fp32
+    quant: str = "none"                # none | nvfp4 | fp8_block
+
+    def __post_init__(self):
+        if self.rope_dim is None:
+            self.rope_dim = self.head_dim if not self.qk_rope_dim else self.qk_rope_dim
+        if self.layer_kinds is None:
+            if self.full_attention_interval > 0:
+                self.layer_kinds = ["attn" if (il + 1) % self.full_attention_interval == 0 else "gdn"
+                                    for il in range(self.n_layer)]
+            elif self.kv_lora > 0:
+                self.layer_kinds = ["mla"] * self.n_layer
+            else:
+                self.layer_kinds = ["attn"] * self.n_layer
+        assert len(self.layer_kinds) == self.n_layer
+
+    # ---- derived
+    def is_moe_layer(self, il: int) -> bool:
+        return self.n_expert > 0 and il >= self.first_dense_layers
+
+    def kv_layers(self) -> List[int]:
+        return [i for i, k in enumerate(self.layer_kinds) if k in ("attn", "swa", "mla")]
+
+    def recurrent_layers(self) -> List[int]:
+        return [i for i, k in enumerate(self.layer_kinds) if k in ("gdn", "mamba2", "kda")]
+
+    def kv_dims(self, il: int):
+        """(n_kv_heads, k_dim, v_dim) stored per token for layer il."""
+        if self.layer_kinds[il] == "mla":
+            return 1, self.kv_lora + self.qk_rope_dim, 0
+        return self.n_kv_head, self.head_dim, self.head_dim
+
+    def gdn_conv_channels(self) -> int:
+        return 2 * self.gdn_k_heads * self.gdn_k_dim + self.gdn_v_heads * self.gdn_v_dim
+
+    def to_json(self) -> str:
+        return json.dumps(dataclasses.asdict(self))
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "ModelConfig":
+        names = {f.name for f in dataclasses.fields(cls)}
+        return cls(**{k: v for k, v in d.items() if k in names})
+
+    def param_count(self) -> int:
+        from .models.weights import weight_shapes
+        n = 0
+        for shp in weight_shapes(self).values():
+            m = 1
+            for s in shp:
+                m *= s
+            n += m
+        return n
+
+
+# --------------------------------------------------------------------------------------------------
+# presets
+# --------------------------------------------------------------------------------------------------
+def tiny_hybrid_moe() -> ModelConfig:
+    """4-layer hybrid: 3 Gated DeltaNet layers + 1 gated GQA layer, 8 experts top-2 + shared expert."""
+    return ModelConfig(arch="qwen35moe", n_layer=4, hidden=256, vocab=4096, n_head=4, n_kv_head=2, head_dim=64,
+                       rope_theta=1e6, full_attention_interval=4, gated_attn=True, gdn_k_heads=4, gdn_v_heads=4,
+                       gdn_k_dim=64, gdn_v_dim=64, gdn_conv=4, n_expert=8, top_k=2, expert_ff=512, shared_ff=512,
+                       shared_gate=True)
+
+
+def tiny_gqa_moe() -> ModelConfig:
+    return ModelConfig(arch="qwen3moe", n_layer=2, hidden=256, vocab=1024, n_head=4, n_kv_head=2, head_dim=64,
+                       n_expert=8, top_k=2, expert_ff=128)
+
+
+def tiny_dense() -> ModelConfig:
+    return ModelConfig(arch="qwen3", n_layer=2, hidden=256, vocab=1024, n_head=4, n_kv_head=2, head_dim=64,
+                       dense_ff=512)
+
+
+def tiny_mla_moe() -> ModelConfig:
+    return ModelConfig(arch="deepseek_v3", n_layer=3, hidden=256, vocab=1024, n_head=4, n_kv_head=4, head_dim=96,
+                       q_lora=96, kv_lora=64, qk_nope_dim=32, qk_rope_dim=64, v_head_dim=32, qk_norm=False,
+                       dense_ff=384, first_dense_layers=1, n_expert=8, top_k=2, expert_ff=128, shared_ff=128,
+                       router_mode="sigmoid", router_bias=True, n_group=4, topk_group=2, route_scale=2.5,
+                       mtp_layers=1)
+
+
+def qwen3_30b_a3b() -> ModelConfig:
+    """30B-A3B-shape MoE: 48 layers, 128 experts top-8, no shared expert."""
+    return ModelConfig(arch="qwen3moe", n_layer=48, hidden=2048, vocab=151936, n_head=32, n_kv_head=4, head_dim=128,
+                       rope_theta=1e6, n_expert=128, top_k=8, expert_ff=768)
+
+
+def qwen35_80b_a3b() -> ModelConfig:
+    """80B-A3B-shape hybrid MoE: 3:1 Gated DeltaNet to gated attention, 512 experts top-10 + shared."""
+    return ModelConfig(arch="qwen35moe", n_layer=48, hidden=2048, vocab=151936, n_head=16, n_kv_head=2, head_dim=256,
+                       rope_dim=64, rope_theta=1e7, full_attention_interval=4, gated_attn=True, gdn_k_heads=16,
+                       gdn_v_heads=32, gdn_k_dim=128, gdn_v_dim=128, gdn_conv=4, n_expert=512, top_k=10,
+                       expert_ff=512, shared_ff=512, shared_gate=True, norm_offset=0.0, quant="nvfp4")
+
+
+def deepseek_671b() -> ModelConfig:
+    """671B-shape MLA MoE: 61 layers, 256 routed experts top-8 (8 groups, top-4), 1 shared expert, 1 MTP head."""
+    return ModelConfig(arch="deepseek_v3", n_layer=61, hidden=7168, vocab=129280, n_head=128, n_kv_head=128,
+                       head_dim=192, q_lora=1536, kv_lora=512, qk_nope_dim=128, qk_rope_dim=64, v_head_dim=128,
+                       qk_norm=False, rope_theta=1e4, dense_ff=18432, first_dense_layers=3, n_expert=256, top_k=8,
+                       expert_ff=2048, shared_ff=2048, router_mode="sigmoid", router_bias=True, n_group=8,
+                       topk_group=4, route_scale=2.5, mtp_layers=1, quant="fp8_block")
+
+
+def dense_27b() -> ModelConfig:
+    return ModelConfig(arch="qwen3", n_layer=64, hidden=5120, vocab=151936, n_head=40, n_kv_head=8, head_dim=128,
+                       rope_theta=1e6, dense_ff=17408)
+
+
+PRESETS = {
+    "tiny-hybrid-moe": tiny_hybrid_moe,
+    "tiny-gqa-moe": tiny_gqa_moe,
+    "tiny-dense": tiny_dense,
+    "tiny-mla-moe": tiny_mla_moe,
+    "qwen3-30b-a3b": qwen3_30b_a3b,
+    "qwen35-80b-a3b": qwen35_80b_a3b,
+    "deepseek-671b": deepseek_671b,
+    "dense-27b": dense_27b,
+}

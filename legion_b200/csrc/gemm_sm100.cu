@@ -40,7 +40,8 @@ struct WgemmCfg {
   static constexpr int STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
   static constexpr int ACC_COLS = BN * (DUAL ? 2 : 1);
   static constexpr int TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 512 /*barriers*/;
+  static constexpr int EPI_BYTES = 32 * BM * 4;  // fp32 staging of 32 token columns
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align slack*/ + 512 /*barriers*/;
   static_assert(TMEM_COLS <= 512, "accumulators do not fit TMEM");
   static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM column count must be a power of two");
 };
@@ -78,7 +79,8 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  float* stage = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES + Cfg::EPI_BYTES);
   uint64_t* full = bars;                  // [STAGES]
   uint64_t* empty = bars + STAGES;        // [STAGES]
   uint64_t* tfull = bars + 2 * STAGES;    // [2]
@@ -276,7 +278,55 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
               for (int j = 0; j < 32; ++j) u[j] = __uint_as_float(r[j]);
             }
           }
-          if (feat_ok) {
+          if (!OUT_F32 && a.vec_ok) {
+            // Staged write-out: fp32 values go through shared memory so that every token row leaves as
+            // 16-byte stores covering 256 contiguous bytes per 16 lanes (8 token rows per pass).
+            const int etid = threadIdx.x - 64;  // 0..127 over the four epilogue warps
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float v = g[j];
+              if (DUAL) v = (v / (1.f + __expf(-v))) * u[j];
+              stage[j * BM + row] = v;
+            }
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+            const int f8 = (etid & 15) * 8;          // first of 8 features handled by this thread
+            const int feat8 = it.feat0 + f8;
+#pragma unroll
+            for (int pass = 0; pass < 4; ++pass) {
+              const int j = pass * 8 + (etid >> 4);
+              const int t = c + j;
+              if (t < it.ntok && feat8 < a.n_feat) {
+                const int xrow = it.tok0 + t;
+                long orow = xrow;
+                if (a.out_rows) orow = a.out_rows[xrow];
+                if (orow >= 0) {
+                  const float4 v0 = *reinterpret_cast<const float4*>(&stage[j * BM + f8]);
+                  const float4 v1 = *reinterpret_cast<const float4*>(&stage[j * BM + f8 + 4]);
+                  float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                  if (a.tok_scale) {
+                    const float sc = a.tok_scale[xrow];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[e] *= sc;
+                  }
+                  if (a.residual) {
+                    const uint4 rr = *reinterpret_cast<const uint4*>(a.residual + orow * a.ldr + feat8);
+                    const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rr);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                      const float2 f = __bfloat1622float2(r2[e]);
+                      v[2 * e] += f.x;
+                      v[2 * e + 1] += f.y;
+                    }
+                  }
+                  uint4 o;
+                  o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+                  o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.out) + orow * a.ldo + feat8) = o;
+                }
+              }
+            }
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+          } else if (feat_ok) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const int t = c + j;
@@ -395,6 +445,9 @@ int wgemm_launch(const WgemmHost& h, cudaStream_t stream) {
   a.rows_per_group = h.rows_per_group; a.dual_offset = h.dual_offset;
   a.split_k = h.split_k < 1 ? 1 : h.split_k;
   a.ws = h.ws; a.counters = h.counters; a.status = h.status;
+  a.vec_ok = (!h.out_f32 && h.n_feat % 8 == 0 && h.ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(h.out) & 15) == 0 &&
+              (!h.residual || (h.ldr % 8 == 0 && (reinterpret_cast<uintptr_t>(h.residual) & 15) == 0)))
+                 ? 1 : 0;
   const int num_kb = (h.K + BK - 1) / BK;
   if (a.split_k > num_kb) a.split_k = num_kb;
   while (a.split_k > 1 && (a.split_k - 1) * ((num_kb + a.split_k - 1) / a.split_k) >= num_kb) --a.split_k;

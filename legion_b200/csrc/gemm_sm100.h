@@ -23,6 +23,7 @@ struct WgemmArgs {
   int rows_per_group;             // weight rows between consecutive groups
   int dual_offset;                // DUAL: rows from a feature's gate row to its up row
   int split_k;
+  int vec_ok;                     // output rows may be written as aligned 16-byte vectors
   float* ws;                      // split-K partials
   int* counters;                  // split-K arrival counters, zero on entry, left zero on exit
   int* status;                    // error word (0 = ok)

@@ -1,0 +1,357 @@
+"""Config-driven decoder: every supported architecture is a stack of the blocks below.
+
+One forward serves prefill chunks, decode steps and speculative verify steps: the step is a flat list
+of tokens (``StepBatch``) grouped into sequences by ``cu_q``; attention reads the paged KV cache through
+block tables, recurrent layers read and advance per-sequence state slots. Sequence lengths, block tables
+and positions are tensors (data), so a step's kernel sequence depends only on the batch shape: the
+property the reference gets from paged attention (``src/model/core/paged.rs:10-13``) and that lets the
+GPU engine replay decode steps as CUDA graphs.
+
+Blocks (reference structure in parentheses):
+  attn / swa  GQA attention, per-head QK RMS-norm, RoPE, optional sigmoid output gate
+              (``src/model/core.rs:3996-4092``)
+  gdn         Gated DeltaNet: in-proj -> causal conv1d + SiLU -> L2-normed q,k -> gated delta rule ->
+              gated RMS norm -> out-proj (``src/model/core.rs:3484-3984``)
+  mla         Multi-head latent attention over a cached [latent | rope-key] row per token
+  mamba2      Mamba-2 selective state space layer (``src/model/nemotron_h.rs``)
+  moe         router -> top-k -> routed experts (+ shared expert, + sigmoid shared gate)
+              (``src/model/core.rs:4496-4640``); dense SwiGLU / GELU / ReLU^2 FFN
+  mtp         next-token-prediction head: eh_proj([norm(embed) ; norm(hidden)]) -> one block -> shared
+              head norm -> LM head (``src/model/qwen35/mtp.rs:1-14``)
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+import torch.nn.functional as F
+
+from .. import ops
+from ..config import ModelConfig
+from ..parallel.context import ParallelCtx
+
+
+@dataclass
+class StepBatch:
+    token_ids: torch.Tensor          # [T] int32
+    positions: torch.Tensor          # [T] int32
+    cu_q: torch.Tensor               # [n_seqs + 1] int32
+    ctx_lens: torch.Tensor           # [n_seqs] int32: cached tokens + this step's tokens
+    block_table: torch.Tensor        # [n_seqs, width] int32
+    slots: torch.Tensor              # [T] int64 flat KV cell of each token (block * page + offset), -1 = skip
+    state_slots: torch.Tensor        # [n_seqs] int32 recurrent-state slot of each sequence
+    logit_rows: Optional[torch.Tensor] = None   # [R] int64 rows whose logits are wanted (None = all)
+    max_q_len: int = 1
+    max_ctx: int = 0
+    write_state: bool = True         # recurrent layers advance their state (False for verify steps)
+    embeds: Optional[torch.Tensor] = None       # input rows instead of the token embedding
+    capture_layers: Optional[List[int]] = None  # layer outputs to return (EAGLE-3 features)
+    cu_q_host: Optional[List[int]] = None
+    decode_splits: Optional[int] = None
+
+    @property
+    def n_seqs(self) -> int:
+        return self.ctx_lens.shape[0]
+
+
+@dataclass
+class StepOutput:
+    hidden: torch.Tensor                     # [R, H] final-normed rows (logit rows)
+    logits: Optional[torch.Tensor] = None    # [R, vocab] float32
+    last_hidden: Optional[torch.Tensor] = None   # [T, H] residual stream before the final norm (MTP input)
+    captures: Dict[int, torch.Tensor] = field(default_factory=dict)
+
+
+class KvCache:
+    """Per-layer paged K/V tensors ``[n_blocks, page, kv_heads, dim]`` (MLA layers: one latent row)."""
+
+    def __init__(self, cfg: ModelConfig, n_blocks: int, page: int, device, dtype, kv_heads_local: Optional[int] = None,
+                 extra_layers: int = 0):
+        self.page, self.n_blocks = page, n_blocks
+        self.k: Dict[int, torch.Tensor] = {}
+        self.v: Dict[int, torch.Tensor] = {}
+        layers = list(cfg.kv_layers())
+        kinds = {il: cfg.layer_kinds[il] for il in layers}
+        for j in range(extra_layers):  # MTP blocks keep their own KV in the same block layout
+            layers.append(cfg.n_layer + j)
+            kinds[cfg.n_layer + j] = "mla" if cfg.kv_lora > 0 else "attn"
+        for il in layers:
+            if kinds[il] == "mla":
+                self.k[il] = torch.zeros(n_blocks, page, 1, cfg.kv_lora + cfg.qk_rope_dim, device=device, dtype=dtype)
+                self.v[il] = self.k[il]
+            else:
+                hk = kv_heads_local or cfg.n_kv_head
+                self.k[il] = torch.zeros(n_blocks, page, hk, cfg.head_dim, device=device, dtype=dtype)
+                self.v[il] = torch.zeros(n_blocks, page, hk, cfg.head_dim, device=device, dtype=dtype)
+
+    def bytes_per_block(self) -> int:
+        n = 0
+        for il, k in self.k.items():
+            n += k[0].numel() * k.element_size()
+            if self.v[il] is not k:
+                n += self.v[il][0].numel() * k.element_size()
+        return n
+
+    def copy_blocks(self, src: List[int], dst: List[int]):
+        if not src:
+            return
+        s = torch.tensor(src, device=next(iter(self.k.values())).device)
+        d = torch.tensor(dst, device=s.device)
+        for il in self.k:
+            self.k[il][d] = self.k[il][s]
+            if self.v[il] is not self.k[il]:
+                self.v[il][d] = self.v[il][s]
+
+
+class StatePool:
+    """Recurrent state in fixed slots: conv history + delta-rule / SSM state, float32
+    (``src/model/core/state.rs:1297``)."""
+
+    def __init__(self, cfg: ModelConfig, n_slots: int, device, tp: int = 1):
+        self.n_slots = n_slots
+        self.conv: Dict[int, torch.Tensor] = {}
+        self.ssm: Dict[int, torch.Tensor] = {}
+        for il in cfg.recurrent_layers():
+            kind = cfg.layer_kinds[il]
+            if kind == "gdn":
+                C = cfg.gdn_conv_channels() // tp
+                self.conv[il] = torch.zeros(n_slots, C, cfg.gdn_conv - 1, device=device, dtype=torch.float32)
+                self.ssm[il] = torch.zeros(n_slots, cfg.gdn_v_heads // tp, cfg.gdn_k_dim, cfg.gdn_v_dim, device=device,
+                                           dtype=torch.float32)
+            elif kind == "mamba2":
+                di = cfg.ssm_heads * cfg.ssm_head_dim
+                C = di + 2 * cfg.ssm_groups * cfg.ssm_state
+                self.conv[il] = torch.zeros(n_slots, C, cfg.ssm_conv - 1, device=device, dtype=torch.float32)
+                self.ssm[il] = torch.zeros(n_slots, cfg.ssm_heads, cfg.ssm_head_dim, cfg.ssm_state, device=device,
+                                           dtype=torch.float32)
+
+    def clear(self, slot: int):
+        for t in list(self.conv.values()) + list(self.ssm.values()):
+            t[slot].zero_()
+
+    def copy(self, src: int, dst: int):
+        for t in list(self.conv.values()) + list(self.ssm.values()):
+            t[dst].copy_(t[src])
+
+    def bytes_per_slot(self) -> int:
+        return sum(t[0].numel() * 4 for t in list(self.conv.values()) + list(self.ssm.values()))
+
+
+class Decoder:
+    """Weights + forward. ``weights`` uses the canonical names of ``models.weights``."""
+
+    def __init__(self, cfg: ModelConfig, weights: Dict[str, torch.Tensor], pctx: Optional[ParallelCtx] = None,
+                 max_position: Optional[int] = None):
+        self.cfg = cfg
+        self.w = weights
+        self.pctx = pctx or ParallelCtx.single()
+        dev = weights["tok_embd"].device
+        self.device = dev
+        self.dtype = weights["tok_embd"].dtype
+        mp = max_position or cfg.max_position
+        self.cos_sin = ops.reference.rope_cos_sin(mp, cfg.rope_dim, cfg.rope_theta, cfg.rope_scaling, device=dev)
+        tp = self.pctx.tp
+        self.n_head_l = cfg.n_head // tp
+        self.n_kv_l = max(1, cfg.n_kv_head // tp)
+        self.gdn_k_l = max(1, cfg.gdn_k_heads // tp)
+        self.gdn_v_l = max(1, cfg.gdn_v_heads // tp)
+        self.lm_head = weights.get("output", weights["tok_embd"])
+
+    # ------------------------------------------------------------------ blocks
+    def _attn(self, p: str, il: int, x, b: StepBatch, kv: KvCache, window: int):
+        cfg, w = self.cfg, self.w
+        D = cfg.head_dim
+        qkv = ops.linear(x, w[f"{p}.attn.qkv"])
+        q, gate = ops.qk_norm_rope_append(qkv, self.n_head_l, self.n_kv_l, D, w.get(f"{p}.attn.q_norm"),
+                                          w.get(f"{p}.attn.k_norm"), cfg.rms_eps, cfg.norm_offset, self.cos_sin,
+                                          cfg.rope_dim, b.positions, b.slots, kv.k[il], kv.v[il], cfg.gated_attn)
+        scale = cfg.attn_scale or D ** -0.5
+        o = ops.paged_attention(q, kv.k[il], kv.v[il], b.block_table, b.ctx_lens, b.cu_q, b.max_q_len, scale,
+                                window=window, decode_splits=b.decode_splits, max_ctx=b.max_ctx or None)
+        if cfg.gated_attn:
+            o = ops.apply_output_gate(o, gate, self.n_head_l, D)
+        return ops.linear(o.reshape(o.shape[0], -1), w[f"{p}.attn.o"])
+
+    def _gdn(self, p: str, il: int, x, b: StepBatch, st: StatePool):
+        cfg, w = self.cfg, self.w
+        nk, nv, dk, dv = self.gdn_k_l, self.gdn_v_l, cfg.gdn_k_dim, cfg.gdn_v_dim
+        mixed = ops.linear(x, w[f"{p}.gdn.in_qkv"])
+        z = ops.linear(x, w[f"{p}.gdn.in_z"])
+        ba = ops.linear(x, w[f"{p}.gdn.in_ba"])
+        conv = ops.causal_conv1d_silu(mixed, w[f"{p}.gdn.conv_w"], None, st.conv[il], b.cu_q, b.state_slots,
+                                      write_state=b.write_state)
+        g, beta = ops.gdn_gates(ba[:, nv:], ba[:, :nv], w[f"{p}.gdn.A"], w[f"{p}.gdn.dt_bias"])
+        o = ops.gdn_recurrent(conv, g, beta, st.ssm[il], b.cu_q, b.state_slots, nk, nv, dk, dv, cfg.gdn_tiled_heads,
+                              dk ** -0.5, 1e-6, write_state=b.write_state)
+        n = ops.gated_rmsnorm(o, z, w[f"{p}.gdn.norm"], cfg.rms_eps, cfg.gdn_gate_act)
+        return ops.linear(n.reshape(n.shape[0], -1), w[f"{p}.gdn.out"])
+
+    def _mla(self, p: str, il: int, x, b: StepBatch, kv: KvCache):
+        """Latent attention: cache row = [rmsnorm(c_kv) | rope(k_pe)]; keys/values are expanded from
+        the cached latents of each sequence (prefill form), queries carry [nope | rope] parts."""
+        cfg, w = self.cfg, self.w
+        nh, dn, dr, dvh, L = self.n_head_l, cfg.qk_nope_dim, cfg.qk_rope_dim, cfg.v_head_dim, cfg.kv_lora
+        T = x.shape[0]
+        if cfg.q_lora > 0:
+            qa = ops.linear(x, w[f"{p}.mla.q_a"])
+            qa, _ = ops.rmsnorm(qa, w[f"{p}.mla.q_a_norm"], cfg.rms_eps, cfg.norm_offset)
+            q = ops.linear(qa, w[f"{p}.mla.q_b"])
+        else:
+            q = ops.linear(x, w[f"{p}.mla.q"])
+        q = q.view(T, nh, dn + dr)
+        kva = ops.linear(x, w[f"{p}.mla.kv_a"])
+        ckv, _ = ops.rmsnorm(kva[:, :L].contiguous(), w[f"{p}.mla.kv_a_norm"], cfg.rms_eps, cfg.norm_offset)
+        k_pe = ops.reference.apply_rope(kva[:, L:].reshape(T, 1, dr), self.cos_sin, b.positions, dr)
+        q_pe = ops.reference.apply_rope(q[..., dn:], self.cos_sin, b.positions, dr)
+        row = torch.cat([ckv, k_pe.reshape(T, dr)], dim=-1).to(kv.k[il].dtype)
+        valid = b.slots >= 0
+        kv.k[il].view(-1, L + dr)[b.slots[valid]] = row[valid]
+        wkv_b = w[f"{p}.mla.kv_b"].view(nh, dn + dvh, L)
+        scale = cfg.attn_scale or (dn + dr) ** -0.5
+        out = torch.empty(T, nh, dvh, device=x.device, dtype=x.dtype)
+        cu = b.cu_q_host if b.cu_q_host is not None else b.cu_q.tolist()
+        ctxs = b.ctx_lens.tolist()
+        page = kv.page
+        for i in range(b.n_seqs):
+            q0, q1 = cu[i], cu[i + 1]
+            if q1 <= q0:
+                continue
+            ctx = ctxs[i]
+            nb = (ctx + page - 1) // page
+            lat = kv.k[il][b.block_table[i, :nb].long()].reshape(-1, L + dr)[:ctx].float()
+            c, kp = lat[:, :L], lat[:, L:]
+            # absorbed form: scores = (q_nope W_uk) . c + q_pe . k_pe ; out = (p . c) W_uv
+            q_abs = torch.einsum("qhd,hdl->qhl", q[q0:q1, :, :dn].float(), wkv_b[:, :dn].float())
+            s = (torch.einsum("qhl,kl->hqk", q_abs, c) + torch.einsum("qhd,kd->hqk", q_pe[q0:q1].float(), kp)) * scale
+            qpos = torch.arange(ctx - (q1 - q0), ctx, device=x.device)[:, None]
+            kpos = torch.arange(ctx, device=x.device)[None, :]
+            s = s.masked_fill((kpos > qpos)[None], float("-inf"))
+            pr = torch.softmax(s, dim=-1)
+            o_lat = torch.einsum("hqk,kl->qhl", pr, c)
+            out[q0:q1] = torch.einsum("qhl,hvl->qhv", o_lat, wkv_b[:, dn:].float()).to(x.dtype)
+        return ops.linear(out.reshape(T, nh * dvh), w[f"{p}.mla.o"])
+
+    def _mamba2(self, p: str, il: int, x, b: StepBatch, st: StatePool):
+        """Mamba-2 (SSD) layer, token-serial reference form on both back-ends."""
+        cfg, w = self.cfg, self.w
+        nh, hd, ng, ds = cfg.ssm_heads, cfg.ssm_head_dim, cfg.ssm_groups, cfg.ssm_state
+        di = nh * hd
+        T = x.shape[0]
+        proj = ops.linear(x, w[f"{p}.ssm.in"])
+        z, xbc, dt = proj[:, :di], proj[:, di:2 * di + 2 * ng * ds], proj[:, 2 * di + 2 * ng * ds:]
+        xbc = ops.causal_conv1d_silu(xbc.contiguous(), w[f"{p}.ssm.conv_w"], w[f"{p}.ssm.conv_b"], st.conv[il], b.cu_q,
+                                     b.state_slots, write_state=b.write_state)
+        xs = xbc[:, :di].float().view(T, nh, hd)
+        Bm = xbc[:, di:di + ng * ds].float().view(T, ng, ds)
+        Cm = xbc[:, di + ng * ds:].float().view(T, ng, ds)
+        dtv = F.softplus(dt.float() + w[f"{p}.ssm.dt_bias"])
+        A = w[f"{p}.ssm.A"].float()
+        Dp = w[f"{p}.ssm.D"].float()
+        y = torch.empty(T, nh, hd, device=x.device, dtype=torch.float32)
+        cu = b.cu_q_host if b.cu_q_host is not None else b.cu_q.tolist()
+        slots = b.state_slots.tolist()
+        hg = nh // ng
+        for i in range(b.n_seqs):
+            S = st.ssm[il][slots[i]].clone()
+            for t in range(cu[i], cu[i + 1]):
+                dA = torch.exp(dtv[t] * A)[:, None, None]
+                Bt = Bm[t].repeat_interleave(hg, dim=0)
+                Ct = Cm[t].repeat_interleave(hg, dim=0)
+                S = S * dA + (dtv[t][:, None] * xs[t])[:, :, None] * Bt[:, None, :]
+                y[t] = torch.einsum("hds,hs->hd", S, Ct) + Dp[:, None] * xs[t]
+            if b.write_state:
+                st.ssm[il][slots[i]] = S
+        yz = y.view(T, di) * F.silu(z.float())
+        yn = yz * torch.rsqrt(yz.pow(2).mean(-1, keepdim=True) + cfg.rms_eps) * w[f"{p}.ssm.norm"].float()
+        return ops.linear(yn.to(x.dtype), w[f"{p}.ssm.out"])
+
+    def _ffn(self, p: str, il_moe: bool, x, residual):
+        """Returns the FFN output with the residual already added when ``residual`` is given and TP == 1."""
+        cfg, w, pc = self.cfg, self.w, self.pctx
+        fuse_res = residual is not None and pc.tp == 1
+        if il_moe:
+            logits = ops.linear(x, w[f"{p}.moe.router"], out_dtype=torch.float32)
+            ids, wts = ops.router_topk(logits, cfg.top_k, cfg.router_mode, cfg.norm_topk, cfg.route_scale,
+                                       w.get(f"{p}.moe.router_bias"), cfg.n_group, cfg.topk_group)
+            shared = gate = None
+            if cfg.shared_ff > 0:
+                fs = w[f"{p}.moe.sh_down"].shape[1]
+                hs = ops.gate_up_act(x, w[f"{p}.moe.sh_gate_up"], fs, cfg.ffn_act)
+                shared = ops.linear(hs, w[f"{p}.moe.sh_down"])
+                if cfg.shared_gate:
+                    gate = ops.linear(x, w[f"{p}.moe.sh_gate"], out_dtype=torch.float32).reshape(-1).contiguous()
+            e_lo, _ = pc.expert_range(cfg.n_expert)
+            n_ff = w[f"{p}.moe.down"].shape[2]
+            return pc.moe(x, ids, wts, w[f"{p}.moe.gate_up"], w[f"{p}.moe.down"], n_ff, cfg.ffn_act, e_lo, shared, gate,
+                          residual if fuse_res else None), fuse_res
+        n_ff = w[f"{p}.mlp.down"].shape[1]
+        h = ops.gate_up_act(x, w[f"{p}.mlp.gate_up"], n_ff, cfg.ffn_act)
+        return ops.linear(h, w[f"{p}.mlp.down"], residual=residual if fuse_res else None), fuse_res
+
+    def _layer(self, p: str, il: int, kind: str, moe: bool, x, resid, b, kv, st):
+        """x is the (possibly rank-partial) output of the previous sub-layer, resid the residual stream."""
+        cfg, w, pc = self.cfg, self.w, self.pctx
+        h, resid = pc.reduce_norm(x, resid, w[f"{p}.attn_norm"], cfg.rms_eps, cfg.norm_offset)
+        if kind in ("attn", "swa"):
+            a = self._attn(p, il, h, b, kv, cfg.sliding_window if kind == "swa" else 0)
+        elif kind == "gdn":
+            a = self._gdn(p, il, h, b, st)
+        elif kind == "mla":
+            a = self._mla(p, il, h, b, kv)
+        elif kind == "mamba2":
+            a = self._mamba2(p, il, h, b, st)
+        else:
+            raise ValueError(kind)
+        h, resid = pc.reduce_norm(a, resid, w[f"{p}.ffn_norm"], cfg.rms_eps, cfg.norm_offset)
+        f, fused = self._ffn(p, moe, h, resid)
+        if fused:
+            return None, f          # residual already folded in: f is the new residual stream
+        return f, resid
+
+    # ------------------------------------------------------------------ forward
+    def embed(self, token_ids):
+        return ops.embed(token_ids, self.w["tok_embd"])
+
+    def forward(self, b: StepBatch, kv: KvCache, st: Optional[StatePool], want_logits: bool = True) -> StepOutput:
+        cfg, w, pc = self.cfg, self.w, self.pctx
+        x = b.embeds if b.embeds is not None else self.embed(b.token_ids)
+        resid = None
+        x_partial = False
+        captures: Dict[int, torch.Tensor] = {}
+        cur, res = x, None
+        # The stream is carried as (cur, res): hidden = cur (+ res). After the embedding res is None.
+        for il in range(cfg.n_layer):
+            cur, res = self._layer(f"l{il}", il, cfg.layer_kinds[il], cfg.is_moe_layer(il), cur, res, b, kv, st)
+            if b.capture_layers and il in b.capture_layers:
+                captures[il] = pc.full_hidden(cur, res)
+        last = pc.full_hidden(cur, res)
+        rows = last if b.logit_rows is None else last.index_select(0, b.logit_rows)
+        hidden, _ = ops.rmsnorm(rows, w["output_norm"], cfg.rms_eps, cfg.norm_offset)
+        out = StepOutput(hidden=hidden, last_hidden=last, captures=captures)
+        if want_logits:
+            out.logits = self.logits(hidden)
+        _ = (resid, x_partial)
+        return out
+
+    def logits(self, hidden):
+        lg = ops.linear(hidden, self.lm_head, out_dtype=torch.float32)
+        if self.cfg.logit_softcap > 0:
+            lg = torch.tanh(lg / self.cfg.logit_softcap) * self.cfg.logit_softcap
+        return lg
+
+    # ------------------------------------------------------------------ MTP head
+    def mtp_forward(self, j: int, b: StepBatch, prev_hidden, kv: KvCache, st: Optional[StatePool]) -> StepOutput:
+        """Draft head j: tokens b.token_ids at positions b.positions with the target's (or the head's own)
+        hidden row of the previous position in ``prev_hidden`` [T, H]."""
+        cfg, w, pc = self.cfg, self.w, self.pctx
+        p = f"mtp{j}"
+        e, _ = ops.rmsnorm(self.embed(b.token_ids), w[f"{p}.enorm"], cfg.rms_eps, cfg.norm_offset)
+        hprev, _ = ops.rmsnorm(prev_hidden, w[f"{p}.hnorm"], cfg.rms_eps, cfg.norm_offset)
+        x = ops.linear(torch.cat([e, hprev], dim=-1), w[f"{p}.eh_proj"])
+        kind = "mla" if cfg.kv_lora > 0 else "attn"
+        cur, res = self._layer(f"{p}.l", cfg.n_layer + j, kind, cfg.n_expert > 0, x, None, b, kv, st)
+        last = pc.full_hidden(cur, res)
+        rows = last if b.logit_rows is None else last.index_select(0, b.logit_rows)
+        hidden, _ = ops.rmsnorm(rows, w[f"{p}.shared_head_norm"], cfg.rms_eps, cfg.norm_offset)
+        return StepOutput(hidden=hidden, logits=self.logits(hidden), last_hidden=last)

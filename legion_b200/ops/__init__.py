@@ -1,2 +1,135 @@
-"""Ops: one function per kernel family. CUDA tensors run the sm_100a kernels, CPU tensors the fp32 reference."""
-from . import reference  # noqa: F401
+"""Ops: one function per kernel family.
+
+CUDA tensors run the hand-written sm_100a kernels (``ops.sm100``; the extension is required, there is
+no eager fallback on a GPU). CPU tensors run the float32 PyTorch reference (``ops.reference``), which
+is both the test oracle and the back-end of the CPU engine used by the scheduler / cache / speculative
+decoding tests.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import reference as _ref
+from . import sm100 as _sm
+
+reference = _ref
+sm100 = _sm
+
+
+def _cuda(t) -> bool:
+    return t.is_cuda
+
+
+def linear(x, w, residual=None, out_dtype=None):
+    if _cuda(x):
+        return _sm.linear(x, w, residual=residual, out_dtype=out_dtype or torch.bfloat16)
+    return _ref.linear(x, w, residual=residual, out_dtype=out_dtype)
+
+
+def gate_up_act(x, w_gate_up, n_ff, act="silu"):
+    if _cuda(x):
+        if act == "silu":
+            return _sm.gate_up_act(x, w_gate_up, n_ff)
+        h = _sm.linear(x, w_gate_up)
+        out = torch.empty(x.shape[0], n_ff, dtype=torch.bfloat16, device=x.device)
+        _sm.ext().glu(h, out, n_ff, {"gelu_tanh": 1, "relu2": 2}[act])
+        return out
+    return _ref.gate_up_act(x, w_gate_up, n_ff, act)
+
+
+def rmsnorm(x, w, eps, w_offset=0.0, residual=None):
+    """Returns (normed, summed)."""
+    if _cuda(x):
+        return _sm.rmsnorm(x, w, eps, w_offset, residual)
+    return _ref.rmsnorm(x, w, eps, w_offset, residual)
+
+
+def qk_norm_rope_append(qkv, n_q, n_kv, d, q_norm_w, k_norm_w, eps, w_offset, cos_sin, rot, positions, slots, k_cache,
+                        v_cache, gated_q=False):
+    """Returns (q [T, n_q, d], gate handle). On CUDA the gate stays inside ``qkv`` (handle = qkv)."""
+    if _cuda(qkv):
+        q = _sm.qk_norm_rope_append(qkv, n_q, n_kv, d, q_norm_w, k_norm_w, eps, w_offset, cos_sin, rot, positions,
+                                    slots, k_cache, v_cache, gated_q)
+        return q, (qkv if gated_q else None)
+    return _ref.qk_norm_rope_append(qkv, n_q, n_kv, d, q_norm_w, k_norm_w, eps, w_offset, cos_sin, rot, positions,
+                                    slots, k_cache, v_cache, gated_q)
+
+
+def apply_output_gate(attn, gate, n_q, d):
+    """attn [T, n_q, d] * sigmoid(gate)."""
+    if _cuda(attn):
+        return _sm.sigmoid_gate(attn, gate, n_q, d)
+    return (attn.float() * torch.sigmoid(gate.float())).to(attn.dtype)
+
+
+def paged_attention(q, k_cache, v_cache, block_table, ctx_lens, cu_q, max_q_len, scale, window=0, causal=True,
+                    decode_splits=None, max_ctx=None):
+    """Varlen paged attention; ``max_q_len == 1`` selects the flash-decoding kernel on CUDA."""
+    if _cuda(q):
+        if max_q_len == 1 and causal:
+            return _sm.paged_decode(q, k_cache, v_cache, block_table, ctx_lens, scale, window, decode_splits, max_ctx)
+        return _sm.prefill_attn(q, k_cache, v_cache, cu_q, ctx_lens, block_table, max_q_len, scale, window, causal)
+    return _ref.paged_attention(q, k_cache, v_cache, block_table, ctx_lens, cu_q, scale, window, causal)
+
+
+def router_topk(logits, k, mode="softmax", renorm=True, route_scale=1.0, bias=None, n_group=1, topk_group=1):
+    if _cuda(logits):
+        return _sm.router_topk(logits, k, mode, renorm, route_scale, bias, n_group, topk_group)
+    return _ref.router_topk(logits, k, mode, renorm, route_scale, bias, n_group, topk_group)
+
+
+def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, act="silu", e_lo=0, shared=None, shared_gate=None,
+                residual=None):
+    """Routed experts (+ optional shared-expert output with sigmoid gate logits, + residual). Returns [T, H]."""
+    if _cuda(x):
+        if act != "silu":
+            raise NotImplementedError("grouped expert kernel implements SwiGLU experts")
+        return _sm.moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, None, shared, shared_gate, residual)
+    out = _ref.moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, act, e_lo, e_lo + w_gate_up.shape[0])
+    if shared is not None:
+        s = shared.float()
+        if shared_gate is not None:
+            s = s * torch.sigmoid(shared_gate.float())[:, None]
+        out = out + s
+    if residual is not None:
+        out = out + residual.float()
+    return out.to(x.dtype)
+
+
+def argmax(logits):
+    if _cuda(logits):
+        return _sm.argmax(logits)
+    return _ref.argmax(logits)
+
+
+def embed(ids, table):
+    if _cuda(table):
+        return _sm.embed(ids.int(), table)
+    return table[ids.long()]
+
+
+def causal_conv1d_silu(x, w, bias, conv_state, cu_seq, slots, write_state=True):
+    if _cuda(x):
+        return _sm.causal_conv1d_silu(x, w, bias, conv_state, cu_seq, slots, write_state)
+    return _ref.causal_conv1d_silu(x, w, bias, conv_state, cu_seq, slots, write_state)
+
+
+def gdn_gates(a, b, A, dt_bias):
+    if _cuda(a):
+        return _sm.gdn_gates(a, b, A, dt_bias)
+    return _ref.gdn_gates(a, b, A, dt_bias)
+
+
+def gdn_recurrent(qkv, g, beta, state, cu_seq, slots, n_k, n_v, dk, dv, tiled_heads, scale, l2_eps=1e-6,
+                  write_state=True):
+    if _cuda(qkv):
+        return _sm.gdn_recurrent(qkv, g, beta, state, cu_seq, slots, n_k, n_v, dk, dv, tiled_heads, scale, l2_eps,
+                                 write_state)
+    return _ref.gdn_recurrent(qkv, g, beta, state, cu_seq, slots, n_k, n_v, dk, dv, tiled_heads, scale, l2_eps,
+                              write_state)
+
+
+def gated_rmsnorm(o, z, w, eps, act="silu"):
+    if _cuda(o):
+        return _sm.gated_rmsnorm(o, z, w, eps, act)
+    return _ref.gated_rmsnorm(o, z.view(o.shape), w, eps, act)
