@@ -1,0 +1,148 @@
+"""CUDA-graph replay of decode steps.
+
+A decode step's kernel sequence depends only on the number of rows: block tables, positions, lengths,
+KV cells and state slots are tensors the kernels read. So one graph is captured per batch-size bucket
+and replayed with new data: every step is ONE packed host-to-device copy of the step's integers from
+pinned memory, one graph launch, and one small device-to-host copy of the picked tokens.
+
+Reference counterpart: kept graphs per ``GroupShape`` and stage CUDA graphs with packed pinned inputs
+(``src/model/core.rs:607-657``, ``src/ggml/stage_graph.rs:1-40``, ``src/ggml/pinned_io.rs``).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from .. import ops
+from ..models.decoder import StepBatch
+
+BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+
+
+class _Entry:
+    __slots__ = ("graph", "B", "W", "pack_h", "pack_d", "batch", "picks", "picks_h", "logits", "n_ints")
+
+
+class DecodeGraphs:
+    def __init__(self, engine, want_logits: bool = False):
+        self.eng = engine
+        self.entries: Dict[int, _Entry] = {}
+        self.want_logits = want_logits
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self.replays = 0
+        self.pad_slot = engine.cfg.max_seqs + (engine.cfg.prefix_cache_states if engine.saved is not None else 0)
+
+    def bucket(self, n: int) -> Optional[int]:
+        for b in BUCKETS:
+            if n <= b:
+                return b
+        return None
+
+    def _layout(self, B: int, W: int):
+        # int32 words: slots (int64 -> 2 words each) first so the int64 view is 8-byte aligned
+        off = {}
+        o = 0
+        for name, n in (("slots", 2 * B), ("token_ids", B), ("positions", B), ("cu_q", B + 1), ("ctx_lens", B),
+                        ("state_slots", B), ("block_table", B * W)):
+            off[name] = (o, n)
+            o += n
+        return off, o
+
+    def _capture(self, B: int) -> _Entry:
+        eng = self.eng
+        dev = eng.device
+        W = eng.pool.blocks_for(eng.cfg.ctx_size)
+        off, total = self._layout(B, W)
+        e = _Entry()
+        e.B, e.W, e.n_ints = B, W, total
+        e.pack_h = torch.zeros(total, dtype=torch.int32).pin_memory()
+        e.pack_d = torch.zeros(total, dtype=torch.int32, device=dev)
+
+        def view(name):
+            o, n = off[name]
+            return e.pack_d[o:o + n]
+
+        Hkv = eng.model.n_kv_l
+        G = max(1, eng.model.n_head_l // Hkv)
+        gt = 8 if G >= 8 else (4 if G > 2 else G)
+        splits = ops.sm100.decode_splits(B, Hkv, (G + gt - 1) // gt, eng.cfg.ctx_size)
+        e.batch = StepBatch(
+            token_ids=view("token_ids"), positions=view("positions"), cu_q=view("cu_q"), ctx_lens=view("ctx_lens"),
+            block_table=view("block_table").view(B, W), slots=view("slots").view(torch.int64),
+            state_slots=view("state_slots"), logit_rows=None, max_q_len=1, max_ctx=eng.cfg.ctx_size,
+            write_state=True, cu_q_host=list(range(B + 1)), decode_splits=splits)
+        # neutral contents for warm-up and capture: every row is a padding row
+        self._fill_padding(e, 0)
+        e.pack_d.copy_(e.pack_h)
+        e.picks = torch.zeros(B, dtype=torch.int32, device=dev)
+        e.picks_h = torch.zeros(B, dtype=torch.int32).pin_memory()
+        e.logits = None
+        s = torch.cuda.Stream(device=dev)
+        s.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(s):
+            for _ in range(2):   # warm-up outside capture: allocates workspaces, tensor maps, attributes
+                out = eng.model.forward(e.batch, eng.kv, eng.states)
+                ops.sm100.argmax(out.logits, out=e.picks)
+        torch.cuda.current_stream(dev).wait_stream(s)
+        torch.cuda.synchronize(dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = eng.model.forward(e.batch, eng.kv, eng.states)
+            ops.sm100.argmax(out.logits, out=e.picks)
+            e.logits = out.logits
+        e.graph = g
+        self.entries[B] = e
+        return e
+
+    def _fill_padding(self, e: _Entry, n_real: int):
+        off, _ = self._layout(e.B, e.W)
+        h = e.pack_h
+        o, n = off["slots"]
+        h[o + 2 * n_real:o + n].view(torch.int64).fill_(-1)
+        for name, val in (("token_ids", 0), ("positions", 0), ("ctx_lens", 1), ("state_slots", self.pad_slot)):
+            o, n = off[name]
+            h[o + n_real:o + n] = val
+        o, n = off["block_table"]
+        h[o + n_real * e.W:o + n] = 0
+
+    def run(self, rows) -> Tuple[Optional[List[int]], Optional[torch.Tensor]]:
+        """rows: [(seq, position, 1)]. Returns (picked token per row, logits [n, V]) or (None, None) when the
+        batch does not fit a bucket."""
+        n = len(rows)
+        B = self.bucket(n)
+        if B is None:
+            return None, None
+        e = self.entries.get(B) or self._capture(B)
+        eng = self.eng
+        off, _ = self._layout(B, e.W)
+        h = e.pack_h
+        pool = eng.pool
+        sl = h[off["slots"][0]:off["slots"][0] + 2 * B].view(torch.int64)
+        tk = h[off["token_ids"][0]:off["token_ids"][0] + B]
+        ps = h[off["positions"][0]:off["positions"][0] + B]
+        cl = h[off["ctx_lens"][0]:off["ctx_lens"][0] + B]
+        ss = h[off["state_slots"][0]:off["state_slots"][0] + B]
+        bt = h[off["block_table"][0]:off["block_table"][0] + B * e.W].view(B, e.W)
+        cu = h[off["cu_q"][0]:off["cu_q"][0] + B + 1]
+        cu.copy_(torch.arange(B + 1, dtype=torch.int32))
+        for i, (s, p0, _) in enumerate(rows):
+            sl[i] = s.table.slot(pool, p0)
+            tk[i] = s.tokens[-1]
+            ps[i] = p0
+            cl[i] = p0 + 1
+            ss[i] = s.slot
+            nb = pool.blocks_for(p0 + 1)
+            bt[i, :nb] = torch.tensor(s.table.blocks[:nb], dtype=torch.int32)
+        self._fill_padding(e, n)
+        e.pack_d.copy_(e.pack_h, non_blocking=True)
+        e.graph.replay()
+        e.picks_h.copy_(e.picks, non_blocking=True)
+        torch.cuda.current_stream(eng.device).synchronize()
+        self.h2d_bytes += e.n_ints * 4
+        self.d2h_bytes += B * 4
+        self.replays += 1
+        need_logits = any(not (s.req.sampling.greedy and s.req.sampling.plain and s.constraint is None)
+                          for s, _, _ in rows)
+        return e.picks_h[:n].tolist(), (e.logits[:n] if need_logits else None)

@@ -1,0 +1,782 @@
+"""LmEngine: the continuous-batching scheduler around one model.
+
+One engine thread owns the model, the KV pool, the recurrent-state pool and the prefix cache. Callers
+tokenise on their own thread (``prepare``) and hand a job to the engine thread, which loops:
+
+    drain arrivals -> cancellations -> admit (prefix match, state restore, KV reserve / on-demand)
+    -> plan a step (all decoding sequences, 1 + drafts rows each; prompt chunks under the token budget,
+       cut at prefix-cache save points) -> one forward -> sample / verify -> stream text -> commit
+       recurrent state, save snapshots, insert finished prompts into the radix cache, draft for the
+       next step.
+
+Reference structure: ``src/engine/lm.rs`` (Worker::run :6709-6950, admit :6955, place :7059-7184, step
+:8034-8164, plan_step :8170-8512, finish_step :8519-9158), admission modes ``docs/serving.md:662-693``,
+preemption by recompute ``src/engine/lm/preempt.rs:1-25``.
+"""
+from __future__ import annotations
+
+import queue
+import threading
+import time
+import traceback
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..config import ModelConfig
+from ..kv.blocks import BlockPool, BlockTable, OutOfBlocks
+from ..kv.radix import RadixCache
+from ..kv.saved_states import SavedStates
+from ..loaders import chat_template as chat_tpl
+from ..loaders.tokenizer import ByteTokenizer, Tokenizer
+from ..models.decoder import Decoder, KvCache, StatePool, StepBatch
+from ..parallel.context import ParallelCtx
+from .queue import WaitQueue
+from .sampling import Sampler, top_logprobs
+from .text import IncrementalDetokenizer, ReasoningSplitter, StopChecker, ToolCallParser
+from .types import (CancelToken, Engine, EngineOverloaded, EngineStats, FinishReason, GenerateRequest, KvOverflow,
+                    SamplingParams, TokenEvent, TokenLogprob, TokenStream, Usage, now_ms)
+
+
+@dataclass
+class EngineConfig:
+    ctx_size: int = 8192
+    max_seqs: int = 16
+    max_batch_tokens: int = 1024
+    prefill_chunk: int = 512
+    block_size: int = 64
+    kv_cache_tokens: Optional[int] = None       # None: max_seqs * ctx_size
+    prefix_cache: bool = True
+    prefix_cache_states: int = 8
+    prefix_cache_interval: int = 0
+    max_waiting: int = 1024
+    default_max_tokens: int = 4096
+    scheduling_policy: str = "fcfs"
+    fair_share: bool = False
+    kv_admission: str = "reserve"               # reserve | on-demand
+    spec: str = "none"                          # none | ngram | mtp | draft | eagle3 | suffix
+    spec_k: int = 4
+    spec_max_batch: int = 8
+    spec_ngram_min: int = 2
+    spec_ngram_max: int = 4
+    deterministic: bool = False
+    device: str = "cpu"
+    seed: int = 0
+    cuda_graphs: bool = True
+    model_name: str = "legion-b200"
+    tool_format: str = "hermes"
+    reasoning: bool = True
+    itl_target_ms: float = 0.0
+    ttft_target_ms: float = 0.0
+
+
+class Seq:
+    __slots__ = ("req", "stream", "tokens", "n_prompt", "n_computed", "table", "slot", "sampler", "detok", "stop",
+                 "reason", "tools", "phase", "arrival_ms", "admit_ms", "first_ms", "usage", "radix_handle", "drafts",
+                 "save_points", "finished", "priority", "key", "n_out", "held_logprobs", "constraint", "resumed",
+                 "orig_prompt", "last_hidden", "draft_state")
+
+    def __init__(self, req: GenerateRequest, stream: TokenStream, tokens: List[int]):
+        self.req, self.stream = req, stream
+        self.tokens = list(tokens)
+        self.n_prompt = len(tokens)
+        self.orig_prompt = len(tokens)
+        self.n_computed = 0
+        self.table = BlockTable()
+        self.slot = -1
+        self.phase = "wait"
+        self.arrival_ms = now_ms()
+        self.admit_ms = 0.0
+        self.first_ms = 0.0
+        self.usage = Usage(prompt_tokens=len(tokens))
+        self.radix_handle = None
+        self.drafts: List[int] = []
+        self.save_points: List[int] = []
+        self.finished = False
+        self.priority = req.priority
+        self.key = req.share_key
+        self.n_out = 0
+        self.held_logprobs: List[TokenLogprob] = []
+        self.constraint = None
+        self.resumed = 0
+        self.last_hidden = None
+        self.draft_state = None
+        self.sampler = None
+        self.detok = None
+        self.stop = None
+        self.reason = None
+        self.tools = None
+
+
+class LmEngine(Engine):
+    def __init__(self, model: Decoder, tokenizer: Tokenizer, cfg: Optional[EngineConfig] = None, drafter=None,
+                 start: bool = True):
+        self.model = model
+        self.mcfg: ModelConfig = model.cfg
+        self.tok = tokenizer
+        self.cfg = cfg or EngineConfig()
+        c = self.cfg
+        dev = model.device
+        self.device = dev
+        self.hybrid = bool(self.mcfg.recurrent_layers())
+        kv_tokens = c.kv_cache_tokens or c.max_seqs * c.ctx_size
+        n_blocks = max(4, (kv_tokens + c.block_size - 1) // c.block_size)
+        self.pool = BlockPool(n_blocks, c.block_size)
+        extra = self.mcfg.mtp_layers if c.spec == "mtp" else 0
+        self.kv = KvCache(self.mcfg, n_blocks, c.block_size, dev, model.dtype, kv_heads_local=model.n_kv_l,
+                          extra_layers=extra)
+        n_saved = c.prefix_cache_states if (self.hybrid and c.prefix_cache) else 0
+        self.states = StatePool(self.mcfg, c.max_seqs + n_saved + 1, dev, tp=model.pctx.tp) if self.hybrid else None
+        self._free_slots = list(range(c.max_seqs - 1, -1, -1))
+        self.radix = RadixCache(self.pool) if c.prefix_cache else None
+        self.saved = SavedStates(range(c.max_seqs, c.max_seqs + n_saved), c.block_size) if n_saved else None
+        self.waiting = WaitQueue(c.scheduling_policy, c.fair_share, c.max_waiting)
+        self.running: List[Seq] = []
+        self._inbox: "queue.Queue" = queue.Queue()
+        self._stats = EngineStats(kv_blocks_total=n_blocks)
+        self._warming = False
+        self._stop = threading.Event()
+        self._thread: Optional[threading.Thread] = None
+        self._fail: Optional[str] = None
+        self.drafter = drafter
+        if self.drafter is None and c.spec != "none":
+            from ..spec import make_drafter
+            self.drafter = make_drafter(c.spec, self)
+        self.eos_ids = tuple(self.tok.eos_ids)
+        self._graphs = None
+        if dev.type == "cuda" and c.cuda_graphs and not any(k in ("mla", "mamba2") for k in self.mcfg.layer_kinds):
+            from .cuda_graphs import DecodeGraphs
+            self._graphs = DecodeGraphs(self)
+        self.step_hook: Optional[Callable] = None    # tests observe (batch description) per step
+        if start:
+            self.start()
+
+    # ------------------------------------------------------------------ Engine interface
+    def models(self):
+        return [{"id": self.cfg.model_name, "object": "model", "owned_by": "legion-b200",
+                 "context_length": self.cfg.ctx_size}]
+
+    def start(self):
+        if self._thread is None:
+            self._thread = threading.Thread(target=self._run, name="legion-engine", daemon=True)
+            self._thread.start()
+
+    def shutdown(self):
+        self._stop.set()
+        self._inbox.put(None)
+        if self._thread is not None:
+            self._thread.join(timeout=30)
+            self._thread = None
+
+    def set_warming(self, on: bool):
+        self._warming = on
+        self._stats.warming = on
+
+    def stats(self) -> EngineStats:
+        s = self._stats
+        s.running, s.waiting = len(self.running), len(self.waiting)
+        s.waiting_by_priority = self.waiting.by_priority()
+        s.waiting_keys = self.waiting.n_keys()
+        s.kv_blocks_used = self.pool.used
+        if self.radix is not None:
+            s.prefix_cache_hit_tokens = self.radix.hit_tokens
+            s.prefix_cache_lookup_tokens = self.radix.lookup_tokens
+        return s
+
+    def check_response_format(self, fmt):
+        if fmt:
+            from ..grammar import compile_response_format
+            compile_response_format(fmt, self.tok)
+
+    def tokenize_request(self, req: GenerateRequest) -> List[int]:
+        if req.prompt_tokens is not None:
+            return list(req.prompt_tokens)
+        if req.messages is not None:
+            tpl = self.tok.chat_template
+            if not tpl:
+                raise ValueError("model has no chat template")
+            kwargs = {}
+            if req.enable_thinking is not None:
+                kwargs["enable_thinking"] = req.enable_thinking
+            text = chat_tpl.render(tpl, req.messages, tools=req.tools, add_generation_prompt=req.add_generation_prompt,
+                                   **kwargs)
+            return self.tok.encode(text, add_special=True)
+        return self.tok.encode(req.prompt or "", add_special=True)
+
+    def count_tokens(self, req: GenerateRequest) -> int:
+        return len(self.tokenize_request(req))
+
+    def prepare(self, req: GenerateRequest) -> Seq:
+        """Caller-thread half of ``generate``: template, tokenise, validate, compile the grammar."""
+        req.sampling.validate()
+        tokens = self.tokenize_request(req)
+        if not tokens:
+            tokens = [self.tok.bos_id if self.tok.bos_id is not None else 0]
+        c = self.cfg
+        if len(tokens) + 1 > c.ctx_size:
+            raise KvOverflow(f"prompt of {len(tokens)} tokens does not fit the context of {c.ctx_size}")
+        sp = req.sampling
+        sp.max_tokens = min(sp.max_tokens, c.ctx_size - len(tokens))
+        need = self.pool.blocks_for(len(tokens) + (sp.max_tokens if c.kv_admission == "reserve" else 1))
+        if need > self.pool.total:
+            raise KvOverflow(f"request needs {need} KV blocks, the cache has {self.pool.total}")
+        seq = Seq(req, TokenStream(CancelToken()), tokens)
+        if req.response_format and req.response_format.get("type") not in (None, "text"):
+            from ..grammar import compile_response_format
+            seq.constraint = compile_response_format(req.response_format, self.tok)
+        return seq
+
+    def generate(self, req: GenerateRequest) -> TokenStream:
+        if self._fail:
+            raise RuntimeError(self._fail)
+        if self.waiting.full():
+            raise EngineOverloaded("waiting queue is full")
+        seq = self.prepare(req)
+        self._inbox.put(seq)
+        return seq.stream
+
+    # ------------------------------------------------------------------ engine thread
+    def _run(self):
+        try:
+            while not self._stop.is_set():
+                idle = not self.running and len(self.waiting) == 0
+                self._drain(block=idle)
+                if self._stop.is_set():
+                    break
+                self._handle_cancels()
+                self._admit()
+                if self.running:
+                    self.step()
+        except BaseException as e:  # a failed step ends every request with an error event
+            self._fail = f"engine failed: {e!r}"
+            traceback.print_exc()
+            self._fail_all(self._fail)
+
+    def _drain(self, block: bool):
+        try:
+            item = self._inbox.get(timeout=0.2) if block else self._inbox.get_nowait()
+        except queue.Empty:
+            return
+        while True:
+            if item is None:
+                return
+            self.waiting.push(item, item.priority, item.key)
+            try:
+                item = self._inbox.get_nowait()
+            except queue.Empty:
+                return
+
+    def _fail_all(self, msg: str):
+        for s in self.running + self.waiting.items():
+            s.stream.put(TokenEvent(kind="error", error=msg, status=500))
+        self.running.clear()
+
+    def _handle_cancels(self):
+        for s in list(self.running):
+            if s.stream.cancel_token.cancelled:
+                self._finish(s, FinishReason.CANCELLED)
+        for s in self.waiting.remove(lambda q: q.stream.cancel_token.cancelled):
+            s.stream.put(TokenEvent(kind="finished", finish_reason=FinishReason.CANCELLED, usage=s.usage))
+
+    # ------------------------------------------------------------------ admission
+    def _blocks_needed(self, seq: Seq, cached_blocks: int) -> int:
+        total = seq.n_prompt + (seq.req.sampling.max_tokens - seq.n_out if self.cfg.kv_admission == "reserve"
+                                else self.cfg.spec_k + 2)
+        return max(0, self.pool.blocks_for(total) - cached_blocks)
+
+    def _make_room(self, need: int) -> bool:
+        if self.pool.free >= need:
+            return True
+        if self.radix is not None:
+            self.radix.evict(need - self.pool.free)
+        if self.pool.free < need and self.saved is not None:
+            for s in sorted(self.saved.entries(), key=lambda e: e.tick):
+                if s.tail_block is not None:
+                    self.pool.decref(s.tail_block)
+                    s.tail_block = None
+                    self.saved.drop(s)
+                    if self.pool.free >= need:
+                        break
+        return self.pool.free >= need
+
+    def _admit(self):
+        c = self.cfg
+        while len(self.waiting) and len(self.running) < c.max_seqs and self._free_slots:
+            seq: Seq = self.waiting.peek()
+            if not self._place(seq):
+                break
+            self.waiting.pop()
+
+    def _place(self, seq: Seq) -> bool:
+        """Prefix match + state restore + KV reservation. Returns False when the KV cache is too full."""
+        bs = self.cfg.block_size
+        prompt = seq.tokens
+        limit = len(prompt) - 1           # at least one prompt token is always recomputed
+        blocks: List[int] = []
+        matched = 0
+        handle = None
+        if self.radix is not None and limit >= bs:
+            blocks, matched, handle = self.radix.match_prefix(prompt, lock=True, max_tokens=limit)
+        resume = matched
+        saved = None
+        tail_block = None
+        if self.hybrid:
+            resume = 0
+            if self.saved is not None:
+                cand = self.saved.find(prompt, limit)
+                if cand is not None:
+                    full = (cand.n_tokens // bs) * bs
+                    if full <= matched and (cand.n_tokens == full or cand.tail_block is not None):
+                        saved, resume = cand, cand.n_tokens
+                        tail_block = cand.tail_block if cand.n_tokens != full else None
+        use_blocks = blocks[:resume // bs]
+        need = self._blocks_needed(seq, len(use_blocks) + (1 if tail_block is not None else 0))
+        if not self._make_room(need):
+            if handle is not None:
+                self.radix.unlock(handle)
+            if not self.running:
+                # nothing will ever free memory for it
+                self.waiting.remove(lambda q: q is seq)
+                seq.stream.put(TokenEvent(kind="error", error="request does not fit the KV cache", status=400))
+            return False
+        seq.table = BlockTable.from_shared(self.pool, use_blocks, resume)
+        if tail_block is not None:
+            # the tail save is taken over by this sequence: its block moves into the table
+            self.pool.incref(tail_block)
+            seq.table.blocks.append(tail_block)
+            self.pool.decref(tail_block)          # the snapshot's own reference
+            saved.tail_block = None
+        try:
+            total = seq.n_prompt + (seq.req.sampling.max_tokens - seq.n_out if self.cfg.kv_admission == "reserve" else 1)
+            seq.table.ensure(self.pool, total)
+        except OutOfBlocks:
+            seq.table.free(self.pool)
+            if handle is not None:
+                self.radix.unlock(handle)
+            return False
+        seq.radix_handle = handle
+        seq.slot = self._free_slots.pop()
+        if self.states is not None:
+            if saved is not None:
+                self.states.copy(saved.slot, seq.slot)
+                if saved.kind == "tail":
+                    self.saved.drop(saved)
+            else:
+                self.states.clear(seq.slot)
+        seq.n_computed = resume
+        seq.resumed = resume
+        seq.usage.cached_tokens = resume
+        seq.phase = "prefill"
+        seq.admit_ms = now_ms()
+        seq.usage.queue_ms = seq.admit_ms - seq.arrival_ms
+        if self.saved is not None:
+            seq.save_points = self.saved.save_points(seq.n_prompt, resume, self.cfg.prefix_cache_interval)
+        sp = seq.req.sampling
+        if seq.sampler is None:     # a preempted sequence keeps its sampler and text state
+            seq.sampler = Sampler(sp, prompt, fallback_seed=self.cfg.seed)
+            seq.detok = IncrementalDetokenizer(lambda ids: self.tok.decode(ids, skip_special=True))
+            seq.stop = StopChecker(sp.stop)
+            seq.reason = ReasoningSplitter() if self.cfg.reasoning else None
+            seq.tools = ToolCallParser(self.cfg.tool_format) if seq.req.tools else None
+        if seq.n_out == 0:
+            seq.stream.put(TokenEvent(kind="started", prompt_tokens=seq.orig_prompt))
+        self.running.append(seq)
+        self._stats.prompt_tokens += seq.n_prompt - resume
+        return True
+
+    # ------------------------------------------------------------------ preemption (on-demand admission)
+    def _preempt_one(self, protect: Seq) -> bool:
+        """Frees the cheapest running sequence (lowest priority, fewest computed tokens, latest arrival);
+        it is re-queued and recomputed later, its stream stays open."""
+        cands = [s for s in self.running if s is not protect]
+        if not cands:
+            return False
+        victim = min(cands, key=lambda s: (s.priority, s.n_computed, -s.arrival_ms))
+        self._release(victim)
+        self.running.remove(victim)
+        victim.n_prompt = len(victim.tokens)
+        victim.n_computed = 0
+        victim.phase = "wait"
+        victim.drafts = []
+        self.waiting.requeue(victim, victim.priority, victim.key)
+        self._stats.kv_preemptions += 1
+        return True
+
+    def _grow(self, seq: Seq, n_tokens: int) -> bool:
+        while True:
+            try:
+                seq.table.ensure(self.pool, n_tokens)
+                return True
+            except OutOfBlocks:
+                need = self.pool.blocks_for(n_tokens) - len(seq.table.blocks)
+                if self._make_room(need):
+                    continue
+                if not self._preempt_one(seq):
+                    return False
+
+    # ------------------------------------------------------------------ one step
+    def step(self):
+        t0 = time.perf_counter()
+        c = self.cfg
+        decode = [s for s in self.running if s.phase == "decode"]
+        prefill = [s for s in self.running if s.phase == "prefill"]
+        # drafts for this step (model-free drafters propose now; model drafters proposed after the last step)
+        use_spec = self.drafter is not None and 0 < len(decode) <= c.spec_max_batch
+        for s in decode:
+            if not use_spec or s.constraint is not None:
+                s.drafts = []
+            elif self.drafter.model_free:
+                s.drafts = self.drafter.propose(s, c.spec_k)
+            room = s.req.sampling.max_tokens - s.n_out - 1
+            s.drafts = s.drafts[:max(0, min(room, c.ctx_size - len(s.tokens) - 1))]
+        rows: List[Tuple[Seq, int, int]] = []   # (seq, first position, n tokens)
+        for s in list(decode):
+            n = 1 + len(s.drafts)
+            if c.kv_admission != "reserve" and not self._grow(s, len(s.tokens) + n):
+                self._finish(s, FinishReason.LENGTH)
+                continue
+            if s not in self.running:
+                continue
+            rows.append((s, len(s.tokens) - 1, n))
+        budget = c.max_batch_tokens - sum(r[2] for r in rows)
+        for s in prefill:
+            if s not in self.running:
+                continue
+            if budget <= 0:
+                break
+            take = min(c.prefill_chunk, s.n_prompt - s.n_computed, budget)
+            for sp in s.save_points:            # end the chunk at the next snapshot position
+                if s.n_computed < sp < s.n_computed + take:
+                    take = sp - s.n_computed
+                    break
+            if c.kv_admission != "reserve" and not self._grow(s, s.n_computed + take + 1):
+                continue
+            if s not in self.running:
+                continue
+            rows.append((s, s.n_computed, take))
+            budget -= take
+        rows = [r for r in rows if r[0] in self.running]
+        if not rows:
+            return
+        verify_rows = [r for r in rows if r[0].phase == "decode" and r[2] > 1]
+        if self.hybrid and verify_rows:
+            # speculative rows must not advance recurrent state: they run as their own pass with replay
+            self._forward_and_finish(verify_rows, verify=True)
+            rest = [r for r in rows if r not in verify_rows]
+            if rest:
+                self._forward_and_finish(rest, verify=False)
+        else:
+            self._forward_and_finish(rows, verify=False)
+        dt = (time.perf_counter() - t0) * 1000
+        st = self._stats
+        st.steps += 1
+        st.step_ms_ewma = dt if st.step_ms_ewma == 0 else 0.8 * st.step_ms_ewma + 0.2 * dt
+
+    def build_batch(self, rows: Sequence[Tuple[Seq, int, int]], write_state: bool = True) -> StepBatch:
+        dev = self.device
+        tok: List[int] = []
+        pos: List[int] = []
+        slots: List[int] = []
+        cu = [0]
+        ctx: List[int] = []
+        logit_rows: List[int] = []
+        width = 1
+        for s, p0, n in rows:
+            if s.phase == "decode":
+                toks = [s.tokens[-1]] + s.drafts[:n - 1]
+            else:
+                toks = s.tokens[p0:p0 + n]
+            tok.extend(toks)
+            pos.extend(range(p0, p0 + n))
+            slots.extend(s.table.slots(self.pool, p0, n))
+            base = cu[-1]
+            cu.append(base + n)
+            ctx.append(p0 + n)
+            width = max(width, self.pool.blocks_for(p0 + n))
+            if s.phase == "decode":
+                logit_rows.extend(range(base, base + n))
+            elif p0 + n == s.n_prompt:
+                logit_rows.append(base + n - 1)
+        bt = torch.zeros(len(rows), width, dtype=torch.int32)
+        for i, (s, p0, n) in enumerate(rows):
+            nb = self.pool.blocks_for(p0 + n)
+            bt[i, :nb] = torch.tensor(s.table.blocks[:nb], dtype=torch.int32)
+        i32 = dict(dtype=torch.int32, device=dev)
+        return StepBatch(
+            token_ids=torch.tensor(tok, **i32), positions=torch.tensor(pos, **i32), cu_q=torch.tensor(cu, **i32),
+            ctx_lens=torch.tensor(ctx, **i32), block_table=bt.to(dev),
+            slots=torch.tensor(slots, dtype=torch.int64, device=dev),
+            state_slots=torch.tensor([s.slot for s, _, _ in rows], **i32),
+            logit_rows=torch.tensor(logit_rows, dtype=torch.int64, device=dev),
+            max_q_len=max(n for _, _, n in rows), max_ctx=max(ctx), write_state=write_state, cu_q_host=cu)
+
+    def _forward_and_finish(self, rows, verify: bool):
+        all_decode_1 = all(s.phase == "decode" and n == 1 for s, _, n in rows)
+        need_hidden = self.drafter is not None and getattr(self.drafter, "needs_hidden", False)
+        if self._graphs is not None and all_decode_1 and not need_hidden:
+            picked, logits = self._graphs.run(rows)
+            if picked is not None:
+                self._finish_rows(rows, None, logits, None, verify, picked=picked)
+                return
+        b = self.build_batch(rows, write_state=not verify)
+        if verify and self.hybrid:
+            b.replay = {}
+        if need_hidden:
+            b.capture_layers = getattr(self.drafter, "capture_layers", None)
+        out = self.model.forward(b, self.kv, self.states)
+        if self.step_hook is not None:
+            self.step_hook([(s.req.request_id, p0, n, s.phase) for s, p0, n in rows])
+        self._finish_rows(rows, b, out.logits, out, verify)
+
+    # ------------------------------------------------------------------ sampling / verification
+    def _pick(self, s: Seq, logits_row: torch.Tensor, device_pick: Optional[int] = None) -> Tuple[int, Optional[TokenLogprob]]:
+        sp = s.req.sampling
+        mask = s.constraint.mask() if s.constraint is not None else None
+        if device_pick is not None and sp.greedy and sp.plain and mask is None:
+            return device_pick, None
+        tok, lg = s.sampler.sample(logits_row, mask, self.eos_ids if not sp.ignore_eos else (), s.n_out)
+        lp = None
+        if sp.logprobs:
+            v, top = top_logprobs(lg, tok, sp.top_logprobs)
+            lp = TokenLogprob(self.tok.decode([tok]), tok, v,
+                              [TokenLogprob(self.tok.decode([i]), i, x) for i, x in top])
+        return tok, lp
+
+    def _finish_rows(self, rows, b: Optional[StepBatch], logits, out, verify: bool, picked=None):
+        r = 0
+        commits: List[Tuple[int, int]] = []     # (row index in batch, kept tokens) for replay
+        all_plain = all(s.req.sampling.greedy and s.req.sampling.plain and s.constraint is None for s, _, _ in rows)
+        device_picks = picked
+        if device_picks is None and logits is not None and logits.shape[0] and all_plain:
+            from .. import ops
+            device_picks = ops.argmax(logits).tolist()
+        logits_host = None
+        if logits is not None and not all_plain:
+            logits_host = logits.float().cpu()
+        for bi, (s, p0, n) in enumerate(rows):
+            if s.phase == "prefill":
+                s.n_computed = p0 + n
+                s.table.n_tokens = s.n_computed
+                if self.saved is not None and s.n_computed in s.save_points:
+                    self._snapshot(s, s.n_computed, "anchor")
+                if s.n_computed < s.n_prompt:
+                    continue
+                # prompt done: cache its full blocks, sample the first token
+                if self.radix is not None:
+                    self.radix.insert(s.tokens[:s.n_prompt], s.table.blocks)
+                row = logits_host[r] if logits_host is not None else None
+                tok, lp = self._pick(s, row, device_picks[r] if device_picks is not None else None)
+                r += 1
+                s.phase = "decode"
+                if s.first_ms == 0.0:
+                    s.first_ms = now_ms()
+                    s.usage.prefill_ms = s.first_ms - s.admit_ms
+                if out is not None and self.drafter is not None:
+                    self.drafter.on_prefill_done(s, out, b, bi)
+                self._advance(s, [tok], [lp])
+                continue
+            # decode / verify rows: n = 1 + drafts
+            accepted: List[int] = []
+            lps: List[Optional[TokenLogprob]] = []
+            k = n - 1
+            for j in range(n):
+                row = logits_host[r + j] if logits_host is not None else None
+                dp = device_picks[r + j] if device_picks is not None else None
+                if j < k:
+                    ok, tok, lp = self._verify_one(s, row, dp, s.drafts[j])
+                    accepted.append(tok)
+                    lps.append(lp)
+                    if not ok:
+                        break
+                else:
+                    tok, lp = self._pick(s, row, dp)
+                    accepted.append(tok)
+                    lps.append(lp)
+            r += n
+            if k:
+                self._stats.spec_draft_tokens += k
+                self._stats.spec_accepted_tokens += len(accepted) - 1
+                self._stats.spec_verify_steps += 1
+                s.usage.draft_tokens += k
+                s.usage.accepted_tokens += len(accepted) - 1
+            kept = len(accepted)              # rows of this step whose KV / state are valid
+            s.n_computed = p0 + kept
+            s.table.n_tokens = s.n_computed
+            if verify:
+                commits.append((bi, kept))
+            if out is not None and self.drafter is not None:
+                self.drafter.on_verified(s, out, b, bi, kept)
+            self._advance(s, accepted, lps)
+        if verify and self.hybrid and b is not None and commits:
+            self.model.commit_replay(b, self.states, commits)
+        if self.drafter is not None and not self.drafter.model_free:
+            live = [s for s, _, _ in rows if s in self.running and s.phase == "decode"]
+            if live and len(live) <= self.cfg.spec_max_batch:
+                self.drafter.draft_batch(live, self.cfg.spec_k)
+
+    def _verify_one(self, s: Seq, row, device_pick, draft: int):
+        """One draft token against the target's row: greedy = must equal the arg-max; sampled = exact
+        rejection sampling against a point-mass draft (accept with probability p(draft), otherwise draw
+        from the distribution with the draft removed)."""
+        sp = s.req.sampling
+        if sp.greedy and sp.plain and device_pick is not None:
+            return device_pick == draft, device_pick, None
+        mask = s.constraint.mask() if s.constraint is not None else None
+        lg = s.sampler.adjusted(row, mask, self.eos_ids if not sp.ignore_eos else (), s.n_out)
+        lp = None
+        if sp.greedy:
+            tok = int(torch.argmax(lg))
+            ok = tok == draft
+        else:
+            dist = s.sampler.distribution(lg)
+            if s.sampler.rng.uniform() < float(dist[draft]):
+                tok, ok = draft, True
+            else:
+                resid = dist.clone()
+                resid[draft] = 0
+                tok = s.sampler.draw(resid / resid.sum()) if float(resid.sum()) > 0 else draft
+                ok = False
+        if sp.logprobs:
+            v, top = top_logprobs(lg, tok, sp.top_logprobs)
+            lp = TokenLogprob(self.tok.decode([tok]), tok, v,
+                              [TokenLogprob(self.tok.decode([i]), i, x) for i, x in top])
+        return ok, tok, lp
+
+    # ------------------------------------------------------------------ token bookkeeping / streaming
+    def _advance(self, s: Seq, toks: List[int], lps, constrained_done: bool = False):
+        sp = s.req.sampling
+        text_out, ids_out, lp_out = "", [], []
+        reason: Optional[FinishReason] = None
+        for tok, lp in zip(toks, lps):
+            s.tokens.append(tok)
+            s.n_out += 1
+            s.sampler.accept(tok)
+            if s.constraint is not None and not constrained_done:
+                s.constraint.advance(tok)
+            self._stats.completion_tokens += 1
+            s.usage.completion_tokens += 1
+            is_eos = (tok in self.eos_ids or tok in sp.stop_token_ids) and not sp.ignore_eos \
+                and s.n_out > sp.min_tokens
+            if is_eos:
+                reason = FinishReason.STOP
+                break
+            piece = s.detok.push(tok)
+            ids_out.append(tok)
+            if lp is not None:
+                lp_out.append(lp)
+            if piece:
+                shown = s.stop.push(piece)
+                text_out += shown
+                if s.stop.hit is not None:
+                    reason = FinishReason.STOP_SEQUENCE
+                    break
+            if s.constraint is not None and s.constraint.finished():
+                reason = FinishReason.STOP
+                break
+            if s.n_out >= sp.max_tokens or len(s.tokens) >= self.cfg.ctx_size:
+                reason = FinishReason.LENGTH
+                break
+        self._emit(s, text_out, ids_out, lp_out)
+        if reason is not None:
+            # drop tokens generated past the stopping point of a multi-token step
+            if reason in (FinishReason.STOP, FinishReason.STOP_SEQUENCE, FinishReason.LENGTH):
+                pass
+            self._finish(s, reason)
+
+    def _emit(self, s: Seq, text: str, ids: List[int], lps):
+        if not text and not ids:
+            return
+        segments = [("text", text)]
+        if s.reason is not None and text:
+            segments = s.reason.push(text)
+        first = True
+        for channel, seg in segments:
+            calls = []
+            if channel == "text" and s.tools is not None:
+                seg, calls = s.tools.push(seg)
+            if seg or (first and ids):
+                s.stream.put(TokenEvent(kind="reasoning" if channel == "reasoning" else "text", text=seg,
+                                        token_ids=ids if first else [], logprobs=lps if first else []))
+                first = False
+            for call in calls:
+                s.stream.put(TokenEvent(kind="tool_call", tool_call=call))
+        if first and ids:
+            s.stream.put(TokenEvent(kind="text", text="", token_ids=ids, logprobs=lps))
+
+    def _snapshot(self, s: Seq, n_tokens: int, kind: str, tail_block: Optional[int] = None):
+        slot, evicted = self.saved.reserve()
+        if slot is None:
+            return
+        if evicted is not None and evicted.tail_block is not None:
+            self.pool.decref(evicted.tail_block)
+        self.states.copy(s.slot, slot)
+        if tail_block is not None:
+            self.pool.incref(tail_block)
+        self.saved.store(s.tokens, n_tokens, slot, kind, tail_block)
+
+    def _release(self, s: Seq):
+        if s.radix_handle is not None and self.radix is not None:
+            self.radix.unlock(s.radix_handle)
+            s.radix_handle = None
+        s.table.free(self.pool)
+        if s.slot >= 0:
+            self._free_slots.append(s.slot)
+            s.slot = -1
+        if self.drafter is not None:
+            self.drafter.release(s)
+
+    def _finish(self, s: Seq, reason: FinishReason):
+        if s.finished:
+            return
+        s.finished = True
+        tail = s.stop.flush() if (s.stop is not None and reason != FinishReason.STOP_SEQUENCE) else ""
+        if tail:
+            self._emit(s, tail, [], [])
+        if s.reason is not None:
+            for channel, seg in s.reason.flush():
+                s.stream.put(TokenEvent(kind="reasoning" if channel == "reasoning" else "text", text=seg))
+        if s.tools is not None:
+            seg, calls = s.tools.flush()
+            if seg:
+                s.stream.put(TokenEvent(kind="text", text=seg))
+            for call in calls:
+                s.stream.put(TokenEvent(kind="tool_call", tool_call=call))
+            if s.tools.calls and reason == FinishReason.STOP:
+                reason = FinishReason.TOOL_CALLS
+        # end-of-reply save: the computed part of the conversation stays reusable by the next turn
+        if reason not in (FinishReason.CANCELLED, FinishReason.ERROR) and s.phase == "decode" and s.slot >= 0:
+            n = s.n_computed
+            if self.radix is not None:
+                self.radix.insert(s.tokens[:n], s.table.blocks)
+            if self.saved is not None and n > 0:
+                bs = self.cfg.block_size
+                tail_block = s.table.blocks[n // bs] if n % bs and n // bs < len(s.table.blocks) else None
+                self._snapshot(s, n, "tail" if n % bs else "anchor", tail_block)
+        now = now_ms()
+        s.usage.decode_ms = max(0.0, now - (s.first_ms or now))
+        if s in self.running:
+            self.running.remove(s)
+        self._release(s)
+        self.waiting.charge(s.key, s.usage.total_tokens)
+        s.stream.put(TokenEvent(kind="finished", finish_reason=reason, usage=s.usage))
+
+    # ------------------------------------------------------------------ convenience
+    def generate_text(self, prompt=None, tokens=None, **sampling) -> "Completion":
+        req = GenerateRequest(prompt=prompt, prompt_tokens=tokens, sampling=SamplingParams(**sampling))
+        return self.generate(req).collect()
+
+
+def build_engine(cfg: ModelConfig, weights=None, engine_cfg: Optional[EngineConfig] = None, tokenizer=None,
+                 device="cpu", dtype=None, pctx: Optional[ParallelCtx] = None, seed: int = 0, start: bool = True) -> LmEngine:
+    """Random-init (or given) weights -> Decoder -> LmEngine."""
+    from ..models.weights import random_weights
+    dev = torch.device(device)
+    if dtype is None:
+        dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    if weights is None:
+        weights = random_weights(cfg, dev, dtype, seed=seed)
+    ec = engine_cfg or EngineConfig()
+    ec.device = str(dev)
+    model = Decoder(cfg, weights, pctx, max_position=ec.ctx_size + 8)
+    return LmEngine(model, tokenizer or ByteTokenizer(cfg.vocab), ec, start=start)

@@ -1,0 +1,254 @@
+"""Tokenizers: byte-level BPE built from GGUF metadata (``tokenizer.ggml.*``) or an HF
+``tokenizer.json``, and a plain byte tokenizer for the tiny random-weight test models.
+
+The BPE follows GPT-2's scheme the way llama.cpp applies it (``src/tokenizer.rs:177-762`` in the
+reference): regex pre-tokenisation per ``tokenizer.ggml.pre``, bytes mapped to printable code points,
+lowest-rank merge first, special tokens matched verbatim before pre-tokenisation.
+"""
+from __future__ import annotations
+
+import json
+import os
+from functools import lru_cache
+from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+
+try:
+    import regex as _re
+except ImportError:  # pragma: no cover
+    import re as _re
+
+
+class Tokenizer:
+    vocab_size: int = 0
+    bos_id: Optional[int] = None
+    eos_ids: Tuple[int, ...] = ()
+    chat_template: Optional[str] = None
+    add_bos: bool = False
+
+    def encode(self, text: str, add_special: bool = False, parse_special: bool = True) -> List[int]:
+        raise NotImplementedError
+
+    def decode(self, ids: Sequence[int], skip_special: bool = False) -> str:
+        raise NotImplementedError
+
+    def token_bytes(self, tid: int) -> bytes:
+        """Raw bytes of one token (used by the grammar matcher)."""
+        return self.decode([tid]).encode("utf-8", "ignore")
+
+    def special_token(self, name: str) -> Optional[str]:
+        return None
+
+
+class ByteTokenizer(Tokenizer):
+    """ids 0..255 are bytes; 256 = <bos>, 257 = <eos>, 258.. = <|im_start|>, <|im_end|>, <think>, </think>,
+    <tool_call>, </tool_call>; the rest of the vocabulary is unused filler."""
+
+    SPECIALS = ["<bos>", "<eos>", "<|im_start|>", "<|im_end|>", "<think>", "</think>", "<tool_call>", "</tool_call>"]
+
+    def __init__(self, vocab_size: int = 4096):
+        self.vocab_size = vocab_size
+        self.bos_id, self.eos_ids = 256, (257, 259)
+        self._sp = {s: 256 + i for i, s in enumerate(self.SPECIALS)}
+        self._sp_inv = {v: k for k, v in self._sp.items()}
+        self.chat_template = DEFAULT_CHATML_TEMPLATE
+
+    def encode(self, text, add_special=False, parse_special=True):
+        ids: List[int] = [self.bos_id] if add_special and self.add_bos else []
+        i = 0
+        while i < len(text):
+            if parse_special and text[i] == "<":
+                hit = next((s for s in self.SPECIALS if text.startswith(s, i)), None)
+                if hit:
+                    ids.append(self._sp[hit])
+                    i += len(hit)
+                    continue
+            ids.extend(text[i].encode("utf-8"))
+            i += 1
+        return ids
+
+    def decode(self, ids, skip_special=False):
+        out = bytearray()
+        for t in ids:
+            if t < 256:
+                out.append(t)
+            elif t in self._sp_inv:
+                if not skip_special:
+                    out.extend(self._sp_inv[t].encode())
+            else:
+                out.extend(f"<0x{t:X}>".encode())
+        return out.decode("utf-8", "replace")
+
+    def token_bytes(self, tid):
+        if tid < 256:
+            return bytes([tid])
+        return self._sp_inv.get(tid, f"<0x{tid:X}>").encode()
+
+
+@lru_cache(maxsize=1)
+def _byte_to_unicode() -> Dict[int, str]:
+    bs = list(range(ord("!"), ord("~") + 1)) + list(range(ord("¡"), ord("¬") + 1)) + list(range(ord("®"), ord("ÿ") + 1))
+    cs = bs[:]
+    n = 0
+    for b in range(256):
+        if b not in bs:
+            bs.append(b)
+            cs.append(256 + n)
+            n += 1
+    return {b: chr(c) for b, c in zip(bs, cs)}
+
+
+PRE_PATTERNS = {
+    "gpt2": r"'s|'t|'re|'ve|'m|'ll|'d| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+",
+    "llama3": r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+",
+    "qwen2": r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+",
+    "deepseek-v3": r"\p{N}{1,3}|[一-龥぀-ゟ゠-ヿ]+|[!\"#$%&'()*+,\-./:;<=>?@\[\\\]^_`{|}~][A-Za-z]+|[^\r\n\p{L}\p{P}\p{S}]?[\p{L}\p{M}]+| ?[\p{P}\p{S}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+",
+}
+PRE_PATTERNS["default"] = PRE_PATTERNS["gpt2"]
+PRE_PATTERNS["qwen35"] = PRE_PATTERNS["qwen2"]
+
+
+class BpeTokenizer(Tokenizer):
+    def __init__(self, tokens: Sequence[str], merges: Sequence[str], pre: str = "gpt2",
+                 token_types: Optional[Sequence[int]] = None, bos_id=None, eos_ids=(), add_bos=False,
+                 chat_template=None, extra_special: Iterable[str] = ()):
+        self.tokens = list(tokens)
+        self.vocab_size = len(self.tokens)
+        self.vocab = {t: i for i, t in enumerate(self.tokens)}
+        self.ranks = {}
+        for r, m in enumerate(merges):
+            a, _, b = m.partition(" ")
+            self.ranks[(a, b)] = r
+        self.pat = _re.compile(PRE_PATTERNS.get(pre, PRE_PATTERNS["default"]))
+        self.bos_id, self.eos_ids, self.add_bos, self.chat_template = bos_id, tuple(eos_ids), add_bos, chat_template
+        b2u = _byte_to_unicode()
+        self._b2u = b2u
+        self._u2b = {v: k for k, v in b2u.items()}
+        # GGUF token types: 3 = control, 4 = user defined
+        sp = set(extra_special)
+        if token_types is not None:
+            sp |= {self.tokens[i] for i, t in enumerate(token_types) if t in (3, 4)}
+        self.special = {s: self.vocab[s] for s in sp if s in self.vocab}
+        self._special_ids = set(self.special.values())
+        self._sp_re = None
+        if self.special:
+            alts = sorted(self.special, key=len, reverse=True)
+            self._sp_re = _re.compile("|".join(_re.escape(a) for a in alts))
+        self._cache: Dict[str, List[int]] = {}
+
+    def _bpe(self, word: str) -> List[int]:
+        hit = self._cache.get(word)
+        if hit is not None:
+            return hit
+        parts = list(word)
+        while len(parts) > 1:
+            best, bi = None, -1
+            for i in range(len(parts) - 1):
+                r = self.ranks.get((parts[i], parts[i + 1]))
+                if r is not None and (best is None or r < best):
+                    best, bi = r, i
+            if best is None:
+                break
+            parts[bi:bi + 2] = [parts[bi] + parts[bi + 1]]
+        ids = []
+        for p in parts:
+            t = self.vocab.get(p)
+            if t is None:   # unknown piece: fall back to its bytes' single-symbol tokens
+                ids.extend(self.vocab[c] for c in p if c in self.vocab)
+            else:
+                ids.append(t)
+        if len(self._cache) < 65536:
+            self._cache[word] = ids
+        return ids
+
+    def _encode_plain(self, text: str) -> List[int]:
+        out: List[int] = []
+        for m in self.pat.finditer(text):
+            word = "".join(self._b2u[b] for b in m.group(0).encode("utf-8"))
+            out.extend(self._bpe(word))
+        return out
+
+    def encode(self, text, add_special=False, parse_special=True):
+        ids: List[int] = [self.bos_id] if (add_special and self.add_bos and self.bos_id is not None) else []
+        if parse_special and self._sp_re is not None:
+            pos = 0
+            for m in self._sp_re.finditer(text):
+                if m.start() > pos:
+                    ids.extend(self._encode_plain(text[pos:m.start()]))
+                ids.append(self.special[m.group(0)])
+                pos = m.end()
+            if pos < len(text):
+                ids.extend(self._encode_plain(text[pos:]))
+        else:
+            ids.extend(self._encode_plain(text))
+        return ids
+
+    def token_bytes(self, tid):
+        t = self.tokens[tid]
+        if tid in self._special_ids:
+            return t.encode("utf-8")
+        return bytes(self._u2b.get(c, ord("?")) for c in t)
+
+    def decode(self, ids, skip_special=False):
+        out = bytearray()
+        for t in ids:
+            if t < 0 or t >= self.vocab_size:
+                continue
+            if t in self._special_ids:
+                if not skip_special:
+                    out.extend(self.tokens[t].encode("utf-8"))
+            else:
+                out.extend(self.token_bytes(t))
+        return out.decode("utf-8", "replace")
+
+    @classmethod
+    def from_gguf_metadata(cls, md: dict) -> "BpeTokenizer":
+        eos = [md[k] for k in ("tokenizer.ggml.eos_token_id", "tokenizer.ggml.eot_token_id") if k in md]
+        return cls(md["tokenizer.ggml.tokens"], md.get("tokenizer.ggml.merges", []),
+                   pre=md.get("tokenizer.ggml.pre", "gpt2"), token_types=md.get("tokenizer.ggml.token_type"),
+                   bos_id=md.get("tokenizer.ggml.bos_token_id"), eos_ids=eos,
+                   add_bos=bool(md.get("tokenizer.ggml.add_bos_token", False)),
+                   chat_template=md.get("tokenizer.chat_template"))
+
+    @classmethod
+    def from_hf_dir(cls, path: str) -> "BpeTokenizer":
+        tj = json.load(open(os.path.join(path, "tokenizer.json"), encoding="utf-8"))
+        model = tj["model"]
+        vocab = model["vocab"]
+        added = {a["content"]: a["id"] for a in tj.get("added_tokens", [])}
+        size = max(list(vocab.values()) + list(added.values())) + 1
+        tokens = [f"<unused{i}>" for i in range(size)]
+        for t, i in vocab.items():
+            tokens[i] = t
+        for t, i in added.items():
+            tokens[i] = t
+        merges = [m if isinstance(m, str) else " ".join(m) for m in model.get("merges", [])]
+        cfg = {}
+        tc = os.path.join(path, "tokenizer_config.json")
+        if os.path.exists(tc):
+            cfg = json.load(open(tc, encoding="utf-8"))
+        def tok_id(name):
+            v = cfg.get(name)
+            if isinstance(v, dict):
+                v = v.get("content")
+            return added.get(v, vocab.get(v)) if v else None
+        eos = [i for i in [tok_id("eos_token")] if i is not None]
+        return cls(tokens, merges, pre="qwen2", bos_id=tok_id("bos_token"), eos_ids=eos,
+                   chat_template=cfg.get("chat_template"), extra_special=added.keys())
+
+
+DEFAULT_CHATML_TEMPLATE = (
+    "{%- if tools %}{{- '<|im_start|>system\\n' }}{%- if messages[0].role == 'system' %}{{- messages[0].content + '\\n\\n' }}{%- endif %}"
+    "{{- '# Tools\\n\\nYou may call one or more functions to assist with the user query.\\n\\n<tools>' }}"
+    "{%- for tool in tools %}{{- '\\n' }}{{- tool | tojson }}{%- endfor %}"
+    "{{- '\\n</tools>\\n\\nFor each function call, return a json object with function name and arguments within "
+    "<tool_call></tool_call> XML tags:\\n<tool_call>\\n{\"name\": <function-name>, \"arguments\": <args-json-object>}\\n</tool_call><|im_end|>\\n' }}"
+    "{%- else %}{%- if messages[0].role == 'system' %}{{- '<|im_start|>system\\n' + messages[0].content + '<|im_end|>\\n' }}{%- endif %}{%- endif %}"
+    "{%- for message in messages %}"
+    "{%- if message.role == 'user' or (message.role == 'system' and not loop.first) %}{{- '<|im_start|>' + message.role + '\\n' + message.content + '<|im_end|>\\n' }}"
+    "{%- elif message.role == 'assistant' %}{{- '<|im_start|>assistant\\n' }}{%- if message.content %}{{- message.content }}{%- endif %}"
+    "{%- if message.tool_calls %}{%- for tc in message.tool_calls %}{{- '\\n<tool_call>\\n{\"name\": \"' + tc.function.name + '\", \"arguments\": ' }}"
+    "{{- tc.function.arguments if tc.function.arguments is string else tc.function.arguments | tojson }}{{- '}\\n</tool_call>' }}{%- endfor %}{%- endif %}{{- '<|im_end|>\\n' }}"
+    "{%- elif message.role == 'tool' %}{{- '<|im_start|>user\\n<tool_response>\\n' + message.content + '\\n</tool_response><|im_end|>\\n' }}"
+    "{%- endif %}{%- endfor %}"
+    "{%- if add_generation_prompt %}{{- '<|im_start|>assistant\\n' }}{%- if enable_thinking is defined and enable_thinking is false %}{{- '<think>\\n\\n</think>\\n\\n' }}{%- endif %}{%- endif %}"
+)

@@ -49,6 +49,7 @@ class StepBatch:
     capture_layers: Optional[List[int]] = None  # layer outputs to return (EAGLE-3 features)
     cu_q_host: Optional[List[int]] = None
     decode_splits: Optional[int] = None
+    replay: Optional[dict] = None                # verify steps: per-layer recurrent inputs kept for commit
 
     @property
     def n_seqs(self) -> int:
@@ -171,7 +172,7 @@ class Decoder:
                                 window=window, decode_splits=b.decode_splits, max_ctx=b.max_ctx or None)
         if cfg.gated_attn:
             o = ops.apply_output_gate(o, gate, self.n_head_l, D)
-        return ops.linear(o.reshape(o.shape[0], -1), w[f"{p}.attn.o"])
+        return ops.linear(o.reshape(o.shape[0], -1), w[f"{p}.attn.o"], out=self.pctx.partial_out(o.shape[0], cfg.hidden))
 
     def _gdn(self, p: str, il: int, x, b: StepBatch, st: StatePool):
         cfg, w = self.cfg, self.w
@@ -182,10 +183,12 @@ class Decoder:
         conv = ops.causal_conv1d_silu(mixed, w[f"{p}.gdn.conv_w"], None, st.conv[il], b.cu_q, b.state_slots,
                                       write_state=b.write_state)
         g, beta = ops.gdn_gates(ba[:, nv:], ba[:, :nv], w[f"{p}.gdn.A"], w[f"{p}.gdn.dt_bias"])
+        if b.replay is not None:
+            b.replay[il] = (mixed, g, beta)
         o = ops.gdn_recurrent(conv, g, beta, st.ssm[il], b.cu_q, b.state_slots, nk, nv, dk, dv, cfg.gdn_tiled_heads,
                               dk ** -0.5, 1e-6, write_state=b.write_state)
         n = ops.gated_rmsnorm(o, z, w[f"{p}.gdn.norm"], cfg.rms_eps, cfg.gdn_gate_act)
-        return ops.linear(n.reshape(n.shape[0], -1), w[f"{p}.gdn.out"])
+        return ops.linear(n.reshape(n.shape[0], -1), w[f"{p}.gdn.out"], out=self.pctx.partial_out(n.shape[0], cfg.hidden))
 
     def _mla(self, p: str, il: int, x, b: StepBatch, kv: KvCache):
         """Latent attention: cache row = [rmsnorm(c_kv) | rope(k_pe)]; keys/values are expanded from
@@ -287,7 +290,8 @@ class Decoder:
                           residual if fuse_res else None), fuse_res
         n_ff = w[f"{p}.mlp.down"].shape[1]
         h = ops.gate_up_act(x, w[f"{p}.mlp.gate_up"], n_ff, cfg.ffn_act)
-        return ops.linear(h, w[f"{p}.mlp.down"], residual=residual if fuse_res else None), fuse_res
+        return ops.linear(h, w[f"{p}.mlp.down"], residual=residual if fuse_res else None,
+                          out=pc.partial_out(h.shape[0], cfg.hidden)), fuse_res
 
     def _layer(self, p: str, il: int, kind: str, moe: bool, x, resid, b, kv, st):
         """x is the (possibly rank-partial) output of the previous sub-layer, resid the residual stream."""
@@ -331,6 +335,7 @@ class Decoder:
         out = StepOutput(hidden=hidden, last_hidden=last, captures=captures)
         if want_logits:
             out.logits = self.logits(hidden)
+        pc.end_step()
         _ = (resid, x_partial)
         return out
 
@@ -339,6 +344,36 @@ class Decoder:
         if self.cfg.logit_softcap > 0:
             lg = torch.tanh(lg / self.cfg.logit_softcap) * self.cfg.logit_softcap
         return lg
+
+    def commit_replay(self, b: StepBatch, st: StatePool, commits):
+        """After a verify step (state not advanced): replays the kept tokens of each sequence through the
+        conv window and the delta rule so the state equals sequential decoding of exactly those tokens.
+        ``commits`` = [(sequence index in the batch, kept tokens)]. The reference does the same with a
+        replay pool of (q, k, v, g, beta) rows (``src/model/core/spec.rs:1-12``, ``Executor::commit``)."""
+        if not b.replay:
+            return
+        cfg, w = self.cfg, self.w
+        cu = b.cu_q_host if b.cu_q_host is not None else b.cu_q.tolist()
+        rows, new_cu, seqs = [], [0], []
+        for bi, kept in commits:
+            if kept <= 0:
+                continue
+            rows.extend(range(cu[bi], cu[bi] + kept))
+            new_cu.append(new_cu[-1] + kept)
+            seqs.append(bi)
+        if not rows:
+            return
+        dev = b.token_ids.device
+        idx = torch.tensor(rows, dtype=torch.long, device=dev)
+        cu_t = torch.tensor(new_cu, dtype=torch.int32, device=dev)
+        slots = b.state_slots[torch.tensor(seqs, dtype=torch.long, device=dev)].contiguous()
+        for il, (mixed, g, beta) in b.replay.items():
+            p = f"l{il}"
+            conv = ops.causal_conv1d_silu(mixed.index_select(0, idx).contiguous(), w[f"{p}.gdn.conv_w"], None,
+                                          st.conv[il], cu_t, slots, write_state=True)
+            ops.gdn_recurrent(conv, g.index_select(0, idx).contiguous(), beta.index_select(0, idx).contiguous(),
+                              st.ssm[il], cu_t, slots, self.gdn_k_l, self.gdn_v_l, cfg.gdn_k_dim, cfg.gdn_v_dim,
+                              cfg.gdn_tiled_heads, cfg.gdn_k_dim ** -0.5, 1e-6, write_state=True)
 
     # ------------------------------------------------------------------ MTP head
     def mtp_forward(self, j: int, b: StepBatch, prev_hidden, kv: KvCache, st: Optional[StatePool]) -> StepOutput:

@@ -20,10 +20,14 @@ def _cuda(t) -> bool:
     return t.is_cuda
 
 
-def linear(x, w, residual=None, out_dtype=None):
+def linear(x, w, residual=None, out_dtype=None, out=None):
     if _cuda(x):
-        return _sm.linear(x, w, residual=residual, out_dtype=out_dtype or torch.bfloat16)
-    return _ref.linear(x, w, residual=residual, out_dtype=out_dtype)
+        return _sm.linear(x, w, residual=residual, out=out, out_dtype=out_dtype or torch.bfloat16)
+    y = _ref.linear(x, w, residual=residual, out_dtype=out_dtype)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
 
 
 def gate_up_act(x, w_gate_up, n_ff, act="silu"):
@@ -79,12 +83,12 @@ def router_topk(logits, k, mode="softmax", renorm=True, route_scale=1.0, bias=No
 
 
 def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, act="silu", e_lo=0, shared=None, shared_gate=None,
-                residual=None):
+                residual=None, out=None):
     """Routed experts (+ optional shared-expert output with sigmoid gate logits, + residual). Returns [T, H]."""
     if _cuda(x):
         if act != "silu":
             raise NotImplementedError("grouped expert kernel implements SwiGLU experts")
-        return _sm.moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, None, shared, shared_gate, residual)
+        return _sm.moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, None, shared, shared_gate, residual, out)
     out = _ref.moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, act, e_lo, e_lo + w_gate_up.shape[0])
     if shared is not None:
         s = shared.float()

@@ -18,6 +18,31 @@ _C_err: Optional[BaseException] = None
 _lock = threading.Lock()
 
 
+# kernels launched by one call of each binding (for the launch counter)
+KERNELS_PER_CALL = {"moe_plan": 3, "paged_decode": 2, "argmax": 2, "wgemm_workspace_floats": 0}
+LAUNCHES = {"n": 0}
+
+
+class _Counting:
+    """Proxy of the extension module that counts kernel launches (``LAUNCHES['n']``)."""
+
+    def __init__(self, mod):
+        self._mod = mod
+        self._cache = {}
+
+    def __getattr__(self, name):
+        f = self._cache.get(name)
+        if f is None:
+            raw = getattr(self._mod, name)
+            k = KERNELS_PER_CALL.get(name, 1)
+
+            def f(*a, _raw=raw, _k=k, **kw):
+                LAUNCHES["n"] += _k
+                return _raw(*a, **kw)
+            self._cache[name] = f
+        return f
+
+
 def ext():
     """Returns the extension module, importing ``legion_b200._C`` on first use."""
     global _C, _C_err
@@ -25,7 +50,7 @@ def ext():
         with _lock:
             if _C is None and _C_err is None:
                 try:
-                    _C = importlib.import_module("legion_b200._C")
+                    _C = _Counting(importlib.import_module("legion_b200._C"))
                 except BaseException as e:  # missing .so, ABI mismatch, missing libcudart
                     _C_err = e
     if _C is None:

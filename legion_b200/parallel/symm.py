@@ -1,0 +1,131 @@
+"""Symmetric-memory communicator: the host side of the fused reduction kernels (``csrc/comm.cu``).
+
+Every rank allocates the same buffer through ``torch.distributed._symmetric_memory`` (CUDA VMM
+allocations exchanged between the processes and mapped into every rank's address space), which gives
+each rank the peer-mapped base pointer of every other rank's buffer and signal pad. The buffer holds
+a small ring of "partial" slots: the o-proj / down-proj GEMM writes its rank-partial output straight
+into the next slot (``next_partial``) and ``all_reduce_add_norm`` launches ONE kernel that signals the
+peers, waits for them (bounded), sums all ranks' slots in rank order with NVLink peer loads, adds the
+residual and applies the next RMSNorm. Sequence numbers live in device memory, so the calls can be
+captured in a CUDA graph and replayed.
+
+Slots rotate so that a rank never overwrites a slot a slower peer may still be reading: two different
+slots for consecutive reductions, and ``end_step`` pads a step to an even number of reductions so the
+rotation also holds across graph replays. Failure handling: a peer that does not arrive within the
+deadline sets the status word (``check``); the communicator is then final (every later call raises),
+like the reference's "first error is final" communicator (``src/tp_net/comm.rs:12-16``).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..ops.sm100 import ext
+
+
+class CommError(RuntimeError):
+    pass
+
+
+class SymmComm:
+    N_SLOTS = 2
+    TWO_SHOT_ROWS = 512
+
+    def __init__(self, group, rank: int, world: int, device: torch.device, max_rows: int, hidden: int,
+                 budget_ns: int = 5_000_000_000):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.rank, self.world, self.device = rank, world, device
+        self.max_rows, self.hidden = max_rows, hidden
+        self.slot_bytes = max_rows * hidden * 2
+        nbytes = self.slot_bytes * (self.N_SLOTS + 1)      # + one region for reduce-scatter results
+        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        self.handle = symm_mem.rendezvous(self.buf, group=group)
+        self.buffer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.signal_ptrs = [int(p) for p in self.handle.signal_pad_ptrs]
+        self.base = self.buf.data_ptr()
+        assert self.base == self.buffer_ptrs[rank]
+        self.seq = torch.zeros(1, dtype=torch.int32, device=device)
+        self.done = torch.zeros(1, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.budget_ns = budget_ns
+        self._next = 0
+        self._calls_in_step = 0
+        self._failed: Optional[str] = None
+        self.buf.zero_()
+        torch.cuda.synchronize(device)
+        import torch.distributed as dist
+        dist.barrier(group=group)
+
+    # ------------------------------------------------------------------ slots
+    def next_partial(self, rows: int, cols: int) -> Optional[torch.Tensor]:
+        if rows > self.max_rows or cols != self.hidden:
+            return None
+        off = self._next * self.slot_bytes
+        return self.buf[off:off + rows * cols * 2].view(torch.bfloat16).view(rows, cols)
+
+    def owns(self, t: torch.Tensor) -> bool:
+        p = t.data_ptr()
+        return self.base <= p < self.base + self.slot_bytes * self.N_SLOTS and t.is_contiguous()
+
+    def _advance(self):
+        self._next = (self._next + 1) % self.N_SLOTS
+        self._calls_in_step += 1
+
+    # ------------------------------------------------------------------ collectives
+    def all_reduce_add_norm(self, cur, res, w, eps, w_offset):
+        """cur must live in the current slot. Returns (normed, summed)."""
+        if self._failed:
+            raise CommError(self._failed)
+        T, H = cur.shape
+        off = cur.data_ptr() - self.base
+        summed = torch.empty(T, H, dtype=torch.bfloat16, device=self.device)
+        if T >= self.TWO_SHOT_ROWS and self.world > 2:
+            # two-shot: each rank reduces its block of rows (+ residual) into its own result region,
+            # then every rank gathers all blocks; the norm runs on the gathered rows.
+            per = (T + self.world - 1) // self.world
+            row0 = min(T, self.rank * per)
+            n_rows = max(0, min(T, row0 + per) - row0)
+            out_off = self.N_SLOTS * self.slot_bytes
+            C = ext()
+            C.reduce_scatter_fused(self.buffer_ptrs, self.signal_ptrs, self.rank, off, out_off, 0, self.seq, self.done,
+                                   row0, n_rows, H, res, self.budget_ns, self.status)
+            C.all_gather_fused(self.buffer_ptrs, self.signal_ptrs, self.rank, out_off, 0, self.seq, self.done, T, H,
+                               summed, self.budget_ns, self.status)
+            self._advance()
+            normed = None
+            if w is not None:
+                from ..ops import sm100
+                normed, _ = sm100.rmsnorm(summed, w, eps, w_offset)
+            return normed, summed
+        normed = torch.empty_like(summed) if w is not None else None
+        ext().all_reduce_fused(self.buffer_ptrs, self.signal_ptrs, self.rank, off, 0, self.seq, self.done, T, H, res,
+                               summed, w, eps, w_offset, normed, self.budget_ns, self.status)
+        self._advance()
+        return normed, summed
+
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        T, H = x.shape
+        if not self.owns(x):
+            slot = self.next_partial(T, H)
+            if slot is None:
+                raise CommError(f"all_reduce of {tuple(x.shape)} exceeds the symmetric buffer")
+            slot.copy_(x)
+            x = slot
+        _, summed = self.all_reduce_add_norm(x, None, None, 0.0, 0.0)
+        return summed
+
+    def end_step(self):
+        """Pads the step to an even number of reductions (slot rotation across graph replays)."""
+        if self._calls_in_step % self.N_SLOTS:
+            z = self.next_partial(1, self.hidden)
+            z.zero_()
+            self.all_reduce_add_norm(z, None, None, 0.0, 0.0)
+        self._calls_in_step = 0
+
+    def check(self):
+        """Synchronises and raises if a bounded wait ran out; after that the communicator stays failed."""
+        v = int(self.status.item())
+        if v:
+            self._failed = f"collective failed with device status {v} (a peer did not arrive in time)"
+            raise CommError(self._failed)
