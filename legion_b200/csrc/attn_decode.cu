@@ -63,20 +63,34 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(
   const int tl = lane % LPT;   // lane within the token
 
   for (int c0 = t_begin + warp * 32; c0 < t_end; c0 += 128) {
-    // ---- scores for 32 tokens, 4 at a time
+    // ---- scores for 32 tokens, 4 per step; the K loads of QB steps are issued before any is used
+    constexpr int QB = (D <= 128) ? 4 : 2;
 #pragma unroll 1
-    for (int qd = 0; qd < 8; ++qd) {
-      const int tok = c0 + qd * 4 + tg;
-      float s[GT];
+    for (int q0 = 0; q0 < 8; q0 += QB) {
+      uint4 kreg[QB][EPL / 8];
 #pragma unroll
-      for (int g = 0; g < GT; ++g) s[g] = 0.f;
-      if (tok < t_end) {
-        const long cell = long(bt[tok / page]) * page + tok % page;
-        const uint4* kp = reinterpret_cast<const uint4*>(k_cache + cell * cell_stride + long(kvh) * D + tl * EPL);
+      for (int qi = 0; qi < QB; ++qi) {
+        const int tok = c0 + (q0 + qi) * 4 + tg;
+        if (tok < t_end) {
+          const long cell = long(bt[tok / page]) * page + tok % page;
+          const uint4* kp = reinterpret_cast<const uint4*>(k_cache + cell * cell_stride + long(kvh) * D + tl * EPL);
+#pragma unroll
+          for (int v8 = 0; v8 < EPL / 8; ++v8) kreg[qi][v8] = __ldg(&kp[v8]);
+        } else {
+#pragma unroll
+          for (int v8 = 0; v8 < EPL / 8; ++v8) kreg[qi][v8] = make_uint4(0, 0, 0, 0);
+        }
+      }
+#pragma unroll
+      for (int qi = 0; qi < QB; ++qi) {
+        const int qd = q0 + qi;
+        const int tok = c0 + qd * 4 + tg;
+        float s[GT];
+#pragma unroll
+        for (int g = 0; g < GT; ++g) s[g] = 0.f;
 #pragma unroll
         for (int v8 = 0; v8 < EPL / 8; ++v8) {
-          const uint4 kk = kp[v8];
-          const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kk);
+          const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kreg[qi][v8]);
           float kf[8];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -92,16 +106,16 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(
                     qb.z * kf[6] + qb.w * kf[7];
           }
         }
-      }
 #pragma unroll
-      for (int g = 0; g < GT; ++g) {
-        s[g] += __shfl_xor_sync(0xffffffffu, s[g], 1);
-        s[g] += __shfl_xor_sync(0xffffffffu, s[g], 2);
-        s[g] += __shfl_xor_sync(0xffffffffu, s[g], 4);
-      }
-      if (tl == 0) {
+        for (int g = 0; g < GT; ++g) {
+          s[g] += __shfl_xor_sync(0xffffffffu, s[g], 1);
+          s[g] += __shfl_xor_sync(0xffffffffu, s[g], 2);
+          s[g] += __shfl_xor_sync(0xffffffffu, s[g], 4);
+        }
+        if (tl == 0) {
 #pragma unroll
-        for (int g = 0; g < GT; ++g) p_s[warp][qd * 4 + tg][g] = (tok < t_end) ? s[g] : -INFINITY;
+          for (int g = 0; g < GT; ++g) p_s[warp][qd * 4 + tg][g] = (tok < t_end) ? s[g] : -INFINITY;
+        }
       }
     }
     __syncwarp();
@@ -130,7 +144,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(
       for (int j = 0; j < DPL; ++j) acc[g][j] *= alpha[g];
     // ---- PV: lane owns DPL output dims
     const int nt = min(32, t_end - c0);
-#pragma unroll 4
+#pragma unroll 8
     for (int t = 0; t < nt; ++t) {
       const int tok = c0 + t;
       const long cell = long(bt[tok / page]) * page + tok % page;
@@ -214,6 +228,13 @@ __global__ void attn_combine_kernel(const float* __restrict__ o_part, const floa
     }
     out[row * D + d] = __float2bfloat16(ll > 0.f ? o / ll : 0.f);
   }
+}
+
+int attn_combine_launch(const float* o_part, const float* ml_part, int n_splits, int rows, int D, void* out,
+                        cudaStream_t s) {
+  attn_combine_kernel<<<rows, D < 128 ? D : 128, 0, s>>>(o_part, ml_part, n_splits, D,
+                                                         static_cast<__nv_bfloat16*>(out));
+  return cudaGetLastError() != cudaSuccess ? 1 : 0;
 }
 
 int paged_decode_launch(const void* q, const void* k_cache, const void* v_cache, long cell_stride,

@@ -26,6 +26,15 @@ int paged_decode_launch(const void* q, const void* k_cache, const void* v_cache,
                         int B, int Hq, int Hkv, int D, int n_splits, float* o_part, float* ml_part, void* out,
                         cudaStream_t s);
 
+int attn_combine_launch(const float* o_part, const float* ml_part, int n_splits, int rows, int D, void* out,
+                        cudaStream_t s);
+
+int paged_decode_tc_launch(const void* q, const void* k_cache, const void* v_cache, long n_cells, long cell_stride,
+                           const int* block_table, int table_width, int page, const int* ctx_lens, float scale,
+                           int window, int B, int Hq, int Hkv, int D, int n_splits, float* o_part, float* ml_part,
+                           void* out, int* status, cudaStream_t s);
+const char* paged_decode_tc_last_error();
+
 int prefill_attn_launch(const void* q, long T, const void* k_cache, const void* v_cache, long n_cells,
                         long cell_stride, const int* cu_q, const int* ctx_lens, const int* block_table,
                         int table_width, int page, int n_seqs, int max_q_len, int Hq, int Hkv, int D, float scale,

@@ -66,8 +66,7 @@ class DecodeGraphs:
 
         Hkv = eng.model.n_kv_l
         G = max(1, eng.model.n_head_l // Hkv)
-        gt = 8 if G >= 8 else (4 if G > 2 else G)
-        splits = ops.sm100.decode_splits(B, Hkv, (G + gt - 1) // gt, eng.cfg.ctx_size)
+        splits = ops.sm100.decode_splits(B, Hkv, (G + 15) // 16, eng.cfg.ctx_size)
         e.batch = StepBatch(
             token_ids=view("token_ids"), positions=view("positions"), cu_q=view("cu_q"), ctx_lens=view("ctx_lens"),
             block_table=view("block_table").view(B, W), slots=view("slots").view(torch.int64),

@@ -1,0 +1,262 @@
+"""GGUF <-> engine mapping: metadata keys to ``ModelConfig`` and GGUF tensor names to the canonical
+fused weight names (and back, for writing GGUF files of our own models).
+
+Schema per the reference's hybrid-MoE architecture (``src/model/qwen35/mod.rs:60-98``,
+``src/hf/qwen35.rs:321-392``): ``{arch}.block_count``, ``.embedding_length``, ``.attention.head_count(_kv)``,
+``.attention.key_length``, ``.rope.dimension_count``, ``.rope.freq_base``, ``.expert_count``,
+``.expert_used_count``, ``.full_attention_interval``, ``.ssm.conv_kernel`` / ``.state_size`` (key head dim) /
+``.group_count`` (key heads) / ``.time_step_rank`` (value heads) / ``.inner_size``; tensors ``blk.N.attn_q``
+(q and gate interleaved per head for gated attention), ``attn_qkv`` + ``attn_gate`` (z) + ``ssm_alpha`` /
+``ssm_beta`` + ``ssm_conv1d`` + ``ssm_dt.bias`` + ``ssm_a`` + ``ssm_norm`` + ``ssm_out`` for DeltaNet layers,
+``ffn_gate_inp`` (router), ``ffn_{gate,up,down}_exps`` (stacked), ``ffn_*_shexp``, ``ffn_gate_inp_shexp``.
+In GGUF files DeltaNet value heads are in tiled order (value head h reads key head h % n_k).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..config import ModelConfig
+from ..models.weights import is_fp32_weight, weight_shapes
+from .gguf import GgufFile, GgufWriter
+
+ARCH_TO_GGUF = {"qwen35moe": "qwen35moe", "qwen35": "qwen35", "qwen3moe": "qwen3moe", "qwen3": "qwen3",
+                "llama": "llama", "deepseek_v3": "deepseek2"}
+GGUF_TO_ARCH = {v: k for k, v in ARCH_TO_GGUF.items()}
+
+
+def config_from_gguf(md: dict) -> ModelConfig:
+    a = md["general.architecture"]
+    g = lambda k, d=None: md.get(f"{a}.{k}", d)
+    n_layer = int(g("block_count"))
+    n_head = int(g("attention.head_count"))
+    hidden = int(g("embedding_length"))
+    head_dim = int(g("attention.key_length", hidden // n_head))
+    kw = dict(arch=GGUF_TO_ARCH.get(a, a), n_layer=n_layer, hidden=hidden, n_head=n_head,
+              n_kv_head=int(g("attention.head_count_kv", n_head)), head_dim=head_dim,
+              rope_theta=float(g("rope.freq_base", 10000.0)), rope_dim=int(g("rope.dimension_count", head_dim)),
+              rms_eps=float(g("attention.layer_norm_rms_epsilon", 1e-6)), vocab=int(g("vocab_size", 0)) or None,
+              max_position=int(g("context_length", 131072)), n_expert=int(g("expert_count", 0)),
+              top_k=int(g("expert_used_count", 0)), expert_ff=int(g("expert_feed_forward_length", 0)),
+              shared_ff=int(g("expert_shared_feed_forward_length", 0)), dense_ff=int(g("feed_forward_length", 0)),
+              mtp_layers=int(g("nextn_predict_layers", 0)))
+    if a in ("qwen35", "qwen35moe"):
+        kw.update(full_attention_interval=int(g("full_attention_interval", 4)), gated_attn=True,
+                  gdn_conv=int(g("ssm.conv_kernel", 4)), gdn_k_dim=int(g("ssm.state_size", 128)),
+                  gdn_k_heads=int(g("ssm.group_count", 16)), gdn_v_heads=int(g("ssm.time_step_rank", 32)),
+                  gdn_tiled_heads=True, shared_gate=kw["shared_ff"] > 0)
+        inner = int(g("ssm.inner_size", kw["gdn_v_heads"] * 128))
+        kw["gdn_v_dim"] = inner // kw["gdn_v_heads"]
+    if kw["vocab"] is None:
+        kw["vocab"] = len(md.get("tokenizer.ggml.tokens", [])) or 0
+    if a == "deepseek2":
+        kw.update(q_lora=int(g("attention.q_lora_rank", 0)), kv_lora=int(g("attention.kv_lora_rank", 0)),
+                  qk_rope_dim=int(g("rope.dimension_count", 64)), v_head_dim=int(g("attention.value_length", 128)),
+                  first_dense_layers=int(g("leading_dense_block_count", 0)), qk_norm=False,
+                  router_mode="sigmoid" if int(g("expert_gating_func", 2)) == 2 else "softmax",
+                  route_scale=float(g("expert_weights_scale", 1.0)), n_group=int(g("expert_group_count", 1)),
+                  topk_group=int(g("expert_group_used_count", 1)), router_bias=True)
+        kw["qk_nope_dim"] = head_dim - kw["qk_rope_dim"]
+    return ModelConfig(**kw)
+
+
+def metadata_from_config(cfg: ModelConfig) -> Dict[str, object]:
+    a = ARCH_TO_GGUF.get(cfg.arch, cfg.arch)
+    md = {f"{a}.block_count": cfg.n_layer, f"{a}.embedding_length": cfg.hidden, f"{a}.attention.head_count": cfg.n_head,
+          f"{a}.attention.head_count_kv": cfg.n_kv_head, f"{a}.attention.key_length": cfg.head_dim,
+          f"{a}.attention.value_length": cfg.head_dim, f"{a}.rope.dimension_count": cfg.rope_dim,
+          f"{a}.rope.freq_base": float(cfg.rope_theta), f"{a}.context_length": cfg.max_position,
+          f"{a}.attention.layer_norm_rms_epsilon": float(cfg.rms_eps), f"{a}.vocab_size": cfg.vocab}
+    if cfg.n_expert:
+        md.update({f"{a}.expert_count": cfg.n_expert, f"{a}.expert_used_count": cfg.top_k,
+                   f"{a}.expert_feed_forward_length": cfg.expert_ff})
+        if cfg.shared_ff:
+            md[f"{a}.expert_shared_feed_forward_length"] = cfg.shared_ff
+    if cfg.dense_ff:
+        md[f"{a}.feed_forward_length"] = cfg.dense_ff
+    if cfg.full_attention_interval:
+        md.update({f"{a}.full_attention_interval": cfg.full_attention_interval, f"{a}.ssm.conv_kernel": cfg.gdn_conv,
+                   f"{a}.ssm.state_size": cfg.gdn_k_dim, f"{a}.ssm.group_count": cfg.gdn_k_heads,
+                   f"{a}.ssm.time_step_rank": cfg.gdn_v_heads, f"{a}.ssm.inner_size": cfg.gdn_v_heads * cfg.gdn_v_dim})
+    if cfg.mtp_layers:
+        md[f"{a}.nextn_predict_layers"] = cfg.mtp_layers
+    return md
+
+
+# ---------------------------------------------------------------------------------------------------
+# tensors
+# ---------------------------------------------------------------------------------------------------
+def _interleave_q_gate(q: torch.Tensor, gate: torch.Tensor, n_head: int, d: int) -> torch.Tensor:
+    """[q rows | gate rows] per head, the layout of ``attn_q`` for gated attention."""
+    H = q.shape[1]
+    return torch.stack([q.view(n_head, d, H), gate.view(n_head, d, H)], dim=1).reshape(2 * n_head * d, H)
+
+
+def to_gguf_tensors(cfg: ModelConfig, w: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    """Canonical weights -> GGUF names (splitting fused projections)."""
+    out: Dict[str, torch.Tensor] = {"token_embd.weight": w["tok_embd"], "output_norm.weight": w["output_norm"]}
+    if "output" in w:
+        out["output.weight"] = w["output"]
+    D = cfg.head_dim
+
+    def layer(p: str, b: str, kind: str, moe: bool):
+        out[f"{b}.attn_norm.weight"] = w[f"{p}.attn_norm"]
+        out[f"{b}.post_attention_norm.weight"] = w[f"{p}.ffn_norm"]
+        if kind in ("attn", "swa"):
+            qkv = w[f"{p}.attn.qkv"]
+            qw = cfg.n_head * D * (2 if cfg.gated_attn else 1)
+            out[f"{b}.attn_q.weight"] = qkv[:qw]            # already [q | gate] per head
+            out[f"{b}.attn_k.weight"] = qkv[qw:qw + cfg.n_kv_head * D]
+            out[f"{b}.attn_v.weight"] = qkv[qw + cfg.n_kv_head * D:]
+            if cfg.qk_norm:
+                out[f"{b}.attn_q_norm.weight"] = w[f"{p}.attn.q_norm"]
+                out[f"{b}.attn_k_norm.weight"] = w[f"{p}.attn.k_norm"]
+            out[f"{b}.attn_output.weight"] = w[f"{p}.attn.o"]
+        elif kind == "gdn":
+            nv = cfg.gdn_v_heads
+            out[f"{b}.attn_qkv.weight"] = w[f"{p}.gdn.in_qkv"]
+            out[f"{b}.attn_gate.weight"] = w[f"{p}.gdn.in_z"]
+            out[f"{b}.ssm_beta.weight"] = w[f"{p}.gdn.in_ba"][:nv]
+            out[f"{b}.ssm_alpha.weight"] = w[f"{p}.gdn.in_ba"][nv:]
+            out[f"{b}.ssm_conv1d.weight"] = w[f"{p}.gdn.conv_w"]
+            out[f"{b}.ssm_dt.bias"] = w[f"{p}.gdn.dt_bias"]
+            out[f"{b}.ssm_a"] = w[f"{p}.gdn.A"]
+            out[f"{b}.ssm_norm.weight"] = w[f"{p}.gdn.norm"]
+            out[f"{b}.ssm_out.weight"] = w[f"{p}.gdn.out"]
+        elif kind == "mla":
+            for ours, theirs in (("q_a", "attn_q_a"), ("q_a_norm", "attn_q_a_norm"), ("q_b", "attn_q_b"), ("q", "attn_q"),
+                                 ("kv_a", "attn_kv_a_mqa"), ("kv_a_norm", "attn_kv_a_norm"), ("kv_b", "attn_kv_b"),
+                                 ("o", "attn_output")):
+                if f"{p}.mla.{ours}" in w:
+                    out[f"{b}.{theirs}.weight"] = w[f"{p}.mla.{ours}"]
+        if moe:
+            F = cfg.expert_ff
+            out[f"{b}.ffn_gate_inp.weight"] = w[f"{p}.moe.router"]
+            if f"{p}.moe.router_bias" in w:
+                out[f"{b}.exp_probs_b.bias"] = w[f"{p}.moe.router_bias"]
+            out[f"{b}.ffn_gate_exps.weight"] = w[f"{p}.moe.gate_up"][:, :F]
+            out[f"{b}.ffn_up_exps.weight"] = w[f"{p}.moe.gate_up"][:, F:]
+            out[f"{b}.ffn_down_exps.weight"] = w[f"{p}.moe.down"]
+            if cfg.shared_ff:
+                Fs = cfg.shared_ff
+                out[f"{b}.ffn_gate_shexp.weight"] = w[f"{p}.moe.sh_gate_up"][:Fs]
+                out[f"{b}.ffn_up_shexp.weight"] = w[f"{p}.moe.sh_gate_up"][Fs:]
+                out[f"{b}.ffn_down_shexp.weight"] = w[f"{p}.moe.sh_down"]
+                if cfg.shared_gate:
+                    out[f"{b}.ffn_gate_inp_shexp.weight"] = w[f"{p}.moe.sh_gate"]
+        elif f"{p}.mlp.gate_up" in w:
+            F = cfg.dense_ff
+            out[f"{b}.ffn_gate.weight"] = w[f"{p}.mlp.gate_up"][:F]
+            out[f"{b}.ffn_up.weight"] = w[f"{p}.mlp.gate_up"][F:]
+            out[f"{b}.ffn_down.weight"] = w[f"{p}.mlp.down"]
+
+    for il in range(cfg.n_layer):
+        layer(f"l{il}", f"blk.{il}", cfg.layer_kinds[il], cfg.is_moe_layer(il))
+    for j in range(cfg.mtp_layers):
+        b = f"blk.{cfg.n_layer + j}"
+        p = f"mtp{j}"
+        for leaf in ("eh_proj", "enorm", "hnorm", "shared_head_norm"):
+            out[f"{b}.nextn.{leaf}.weight"] = w[f"{p}.{leaf}"]
+        layer(f"{p}.l", b, "mla" if cfg.kv_lora > 0 else "attn", cfg.n_expert > 0)
+    return {k: v.contiguous() for k, v in out.items()}
+
+
+def from_gguf_tensors(cfg: ModelConfig, get, has) -> Dict[str, torch.Tensor]:
+    """GGUF tensors (``get(name) -> tensor``) -> canonical fused weights."""
+    w: Dict[str, torch.Tensor] = {"tok_embd": get("token_embd.weight"), "output_norm": get("output_norm.weight")}
+    if has("output.weight"):
+        w["output"] = get("output.weight")
+    elif not cfg.tie_embeddings:
+        cfg.tie_embeddings = True
+
+    def layer(p: str, b: str, kind: str, moe: bool):
+        w[f"{p}.attn_norm"] = get(f"{b}.attn_norm.weight")
+        w[f"{p}.ffn_norm"] = get(f"{b}.post_attention_norm.weight") if has(f"{b}.post_attention_norm.weight") \
+            else get(f"{b}.ffn_norm.weight")
+        if kind in ("attn", "swa"):
+            w[f"{p}.attn.qkv"] = torch.cat([get(f"{b}.attn_q.weight"), get(f"{b}.attn_k.weight"),
+                                            get(f"{b}.attn_v.weight")], dim=0)
+            if has(f"{b}.attn_q_norm.weight"):
+                w[f"{p}.attn.q_norm"] = get(f"{b}.attn_q_norm.weight")
+                w[f"{p}.attn.k_norm"] = get(f"{b}.attn_k_norm.weight")
+            w[f"{p}.attn.o"] = get(f"{b}.attn_output.weight")
+        elif kind == "gdn":
+            w[f"{p}.gdn.in_qkv"] = get(f"{b}.attn_qkv.weight")
+            w[f"{p}.gdn.in_z"] = get(f"{b}.attn_gate.weight")
+            w[f"{p}.gdn.in_ba"] = torch.cat([get(f"{b}.ssm_beta.weight"), get(f"{b}.ssm_alpha.weight")], dim=0)
+            cw = get(f"{b}.ssm_conv1d.weight")
+            w[f"{p}.gdn.conv_w"] = cw if cw.shape[0] == cfg.gdn_conv_channels() else cw.t().contiguous()
+            w[f"{p}.gdn.dt_bias"] = get(f"{b}.ssm_dt.bias")
+            w[f"{p}.gdn.A"] = get(f"{b}.ssm_a").reshape(-1)
+            w[f"{p}.gdn.norm"] = get(f"{b}.ssm_norm.weight")
+            w[f"{p}.gdn.out"] = get(f"{b}.ssm_out.weight")
+        elif kind == "mla":
+            for ours, theirs in (("q_a", "attn_q_a"), ("q_a_norm", "attn_q_a_norm"), ("q_b", "attn_q_b"), ("q", "attn_q"),
+                                 ("kv_a", "attn_kv_a_mqa"), ("kv_a_norm", "attn_kv_a_norm"), ("kv_b", "attn_kv_b"),
+                                 ("o", "attn_output")):
+                if has(f"{b}.{theirs}.weight"):
+                    w[f"{p}.mla.{ours}"] = get(f"{b}.{theirs}.weight")
+        if moe:
+            w[f"{p}.moe.router"] = get(f"{b}.ffn_gate_inp.weight")
+            if has(f"{b}.exp_probs_b.bias"):
+                w[f"{p}.moe.router_bias"] = get(f"{b}.exp_probs_b.bias")
+            w[f"{p}.moe.gate_up"] = torch.cat([get(f"{b}.ffn_gate_exps.weight"), get(f"{b}.ffn_up_exps.weight")], dim=1)
+            w[f"{p}.moe.down"] = get(f"{b}.ffn_down_exps.weight")
+            if has(f"{b}.ffn_gate_shexp.weight"):
+                w[f"{p}.moe.sh_gate_up"] = torch.cat([get(f"{b}.ffn_gate_shexp.weight"),
+                                                      get(f"{b}.ffn_up_shexp.weight")], dim=0)
+                w[f"{p}.moe.sh_down"] = get(f"{b}.ffn_down_shexp.weight")
+                if has(f"{b}.ffn_gate_inp_shexp.weight"):
+                    w[f"{p}.moe.sh_gate"] = get(f"{b}.ffn_gate_inp_shexp.weight").reshape(1, -1)
+        elif has(f"{b}.ffn_gate.weight"):
+            w[f"{p}.mlp.gate_up"] = torch.cat([get(f"{b}.ffn_gate.weight"), get(f"{b}.ffn_up.weight")], dim=0)
+            w[f"{p}.mlp.down"] = get(f"{b}.ffn_down.weight")
+
+    for il in range(cfg.n_layer):
+        layer(f"l{il}", f"blk.{il}", cfg.layer_kinds[il], cfg.is_moe_layer(il))
+    for j in range(cfg.mtp_layers):
+        b = f"blk.{cfg.n_layer + j}"
+        p = f"mtp{j}"
+        if not has(f"{b}.nextn.eh_proj.weight"):
+            cfg.mtp_layers = j
+            break
+        for leaf in ("eh_proj", "enorm", "hnorm", "shared_head_norm"):
+            w[f"{p}.{leaf}"] = get(f"{b}.nextn.{leaf}.weight")
+        layer(f"{p}.l", b, "mla" if cfg.kv_lora > 0 else "attn", cfg.n_expert > 0)
+    return w
+
+
+def write_gguf(path: str, cfg: ModelConfig, weights: Dict[str, torch.Tensor], tokenizer=None, dtype: str = "F32",
+               extra_metadata: Optional[dict] = None):
+    wr = GgufWriter(path, ARCH_TO_GGUF.get(cfg.arch, cfg.arch))
+    wr.add("general.name", f"legion-b200 {cfg.arch}")
+    for k, v in metadata_from_config(cfg).items():
+        wr.add(k, v)
+    if tokenizer is not None and hasattr(tokenizer, "tokens"):
+        wr.add("tokenizer.ggml.model", "gpt2")
+        wr.add("tokenizer.ggml.tokens", list(tokenizer.tokens))
+        if getattr(tokenizer, "chat_template", None):
+            wr.add("tokenizer.chat_template", tokenizer.chat_template)
+    for k, v in (extra_metadata or {}).items():
+        wr.add(k, v)
+    for name, t in to_gguf_tensors(cfg, weights).items():
+        leaf_fp32 = t.dim() == 1 or name.endswith(("ssm_conv1d.weight", "ssm_a", "ssm_dt.bias"))
+        wr.add_tensor(name, t.detach().cpu(), "F32" if leaf_fp32 else dtype)
+    wr.write()
+
+
+def load_gguf(path: str, device="cpu", dtype=torch.float32):
+    """Returns (config, canonical weights on ``device``, metadata)."""
+    gf = GgufFile(path)
+    cfg = config_from_gguf(gf.metadata)
+    has = lambda n: n in gf.tensors
+    get = lambda n: gf.torch(n)
+    w = from_gguf_tensors(cfg, get, has)
+    if cfg.vocab in (0, None):
+        cfg.vocab = w["tok_embd"].shape[0]
+    out = {}
+    for k, v in w.items():
+        out[k] = v.to(device=device, dtype=torch.float32 if is_fp32_weight(k) else dtype)
+    md = gf.metadata
+    return cfg, out, md

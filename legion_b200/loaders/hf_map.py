@@ -1,0 +1,398 @@
+"""HF checkpoint directories -> canonical fused weights (and back, for writing test checkpoints).
+
+``config.json`` ``model_type`` selects the mapper: ``qwen3`` / ``qwen3_moe`` / ``llama`` / ``mistral``,
+``qwen3_next`` / ``qwen3_5`` / ``qwen3_5_moe`` (hybrid Gated DeltaNet), ``deepseek_v3`` (MLA).
+Transforms applied while loading the Qwen3.5 family (``src/hf/qwen35.rs:6-20`` in the reference):
+``A_log -> -exp(A_log)``; RMSNorm weights stored as (w - 1) get +1 (all but the DeltaNet output norm);
+fused ``in_proj_qkvz`` / ``in_proj_ba`` are de-interleaved per key head; conv1d ``[C, 1, k]`` is squeezed;
+experts are stacked to 3-D with gate and up concatenated; quantised tensors (FP8 per-tensor / per-channel /
+128x128 blocks, NVFP4 ModelOpt / compressed-tensors) are decoded to the compute dtype.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Callable, Dict, Optional
+
+import torch
+
+from ..config import ModelConfig
+from ..models.weights import is_fp32_weight, weight_shapes
+from . import quant_formats as qf
+from .safetensors_io import Checkpoint, save_file
+
+HYBRID_TYPES = ("qwen3_next", "qwen3_5", "qwen3_5_moe", "qwen3_5_text", "qwen3_5_moe_text")
+
+
+def config_from_hf(c: dict) -> ModelConfig:
+    c = dict(c.get("text_config") or c)
+    mt = c.get("model_type", "llama")
+    n_head = c["num_attention_heads"]
+    hidden = c["hidden_size"]
+    kw = dict(n_layer=c["num_hidden_layers"], hidden=hidden, vocab=c["vocab_size"], n_head=n_head,
+              n_kv_head=c.get("num_key_value_heads", n_head), head_dim=c.get("head_dim") or hidden // n_head,
+              rope_theta=float(c.get("rope_theta", 10000.0)), rms_eps=float(c.get("rms_norm_eps", 1e-6)),
+              tie_embeddings=bool(c.get("tie_word_embeddings", False)),
+              max_position=int(c.get("max_position_embeddings", 131072)), rope_scaling=c.get("rope_scaling"))
+    if mt in ("qwen3", "qwen3_moe"):
+        kw.update(arch="qwen3moe" if mt == "qwen3_moe" else "qwen3", qk_norm=True)
+    elif mt in HYBRID_TYPES:
+        moe = c.get("num_experts", 0) > 0
+        kinds = c.get("layer_types")
+        kw.update(arch="qwen35moe" if moe else "qwen35", qk_norm=True, gated_attn=True, norm_offset=1.0,
+                  full_attention_interval=int(c.get("full_attention_interval", 4)),
+                  rope_dim=int(kw["head_dim"] * float(c.get("partial_rotary_factor", 0.25))),
+                  gdn_k_heads=c.get("linear_num_key_heads", 16), gdn_v_heads=c.get("linear_num_value_heads", 32),
+                  gdn_k_dim=c.get("linear_key_head_dim", 128), gdn_v_dim=c.get("linear_value_head_dim", 128),
+                  gdn_conv=c.get("linear_conv_kernel_dim", 4), mtp_layers=int(c.get("mtp_num_hidden_layers", 0) or 0))
+        if kinds:
+            kw["layer_kinds"] = ["gdn" if k == "linear_attention" else "attn" for k in kinds]
+            kw["full_attention_interval"] = 0
+    elif mt in ("deepseek_v3", "deepseek_v2", "kimi_k2"):
+        kw.update(arch="deepseek_v3", qk_norm=False, q_lora=c.get("q_lora_rank") or 0, kv_lora=c["kv_lora_rank"],
+                  qk_nope_dim=c["qk_nope_head_dim"], qk_rope_dim=c["qk_rope_head_dim"], v_head_dim=c["v_head_dim"],
+                  head_dim=c["qk_nope_head_dim"] + c["qk_rope_head_dim"], dense_ff=c["intermediate_size"],
+                  first_dense_layers=c.get("first_k_dense_replace", 0), n_expert=c.get("n_routed_experts", 0),
+                  top_k=c.get("num_experts_per_tok", 0), expert_ff=c.get("moe_intermediate_size", 0),
+                  shared_ff=c.get("moe_intermediate_size", 0) * c.get("n_shared_experts", 0),
+                  router_mode="sigmoid" if c.get("scoring_func", "sigmoid") == "sigmoid" else "softmax",
+                  router_bias=c.get("topk_method", "noaux_tc") == "noaux_tc", n_group=c.get("n_group", 1),
+                  topk_group=c.get("topk_group", 1), route_scale=float(c.get("routed_scaling_factor", 1.0)),
+                  norm_topk=bool(c.get("norm_topk_prob", True)), mtp_layers=int(c.get("num_nextn_predict_layers", 0)))
+    else:
+        kw.update(arch="llama" if mt in ("llama", "mistral") else mt, qk_norm=False)
+    if mt not in ("deepseek_v3", "deepseek_v2", "kimi_k2"):
+        ne = c.get("num_experts", c.get("num_local_experts", 0)) or 0
+        if ne:
+            kw.update(n_expert=ne, top_k=c.get("num_experts_per_tok", 2),
+                      expert_ff=c.get("moe_intermediate_size", c.get("intermediate_size")),
+                      norm_topk=bool(c.get("norm_topk_prob", True)),
+                      shared_ff=c.get("shared_expert_intermediate_size", 0) or 0)
+            kw["shared_gate"] = kw["shared_ff"] > 0
+        else:
+            kw["dense_ff"] = c["intermediate_size"]
+    return ModelConfig(**kw)
+
+
+class _Source:
+    """Tensor access with on-the-fly de-quantisation of FP8 / NVFP4 weights."""
+
+    def __init__(self, ck: Checkpoint, device, dtype):
+        self.ck, self.device, self.dtype = ck, device, dtype
+        self.method = ck.quant_method()
+        self.prefix = ""
+        for cand in ("model.language_model.", "language_model.model.", "model."):
+            if any(n.startswith(cand + "layers.") for n in ck.names()):
+                self.prefix = cand
+                break
+
+    def has(self, name: str) -> bool:
+        return self.ck.has(name) or self.ck.has(name + "_packed")
+
+    def raw(self, name: str) -> torch.Tensor:
+        return self.ck.get(name)
+
+    def weight(self, base: str) -> torch.Tensor:
+        """``base`` without the ``.weight`` suffix."""
+        ck = self.ck
+        dev = self.device
+        if ck.has(base + ".weight_packed"):                       # compressed-tensors NVFP4
+            codes = ck.get(base + ".weight_packed").to(dev)
+            sc = ck.get(base + ".weight_scale").to(dev)
+            g = ck.get(base + ".weight_global_scale")
+            return qf.nvfp4_dequant(codes, sc, g, self.dtype, global_is_divisor=True)
+        w = ck.get(base + ".weight")
+        if ck.has(base + ".weight_scale_2"):                      # ModelOpt NVFP4
+            return qf.nvfp4_dequant(w.to(dev), ck.get(base + ".weight_scale").to(dev), ck.get(base + ".weight_scale_2"),
+                                    self.dtype)
+        if w.dtype == torch.float8_e4m3fn:
+            if ck.has(base + ".weight_scale_inv"):
+                bs = (ck.config.get("quantization_config") or {}).get("weight_block_size") or [128, 128]
+                return qf.fp8_dequant(w.to(dev), ck.get(base + ".weight_scale_inv").to(dev), (bs[0], bs[1]), self.dtype)
+            return qf.fp8_dequant(w.to(dev), ck.get(base + ".weight_scale").to(dev), None, self.dtype)
+        return w.to(device=dev)
+
+
+def load_hf(path: str, device="cpu", dtype=torch.float32):
+    """Returns (config, canonical weights, checkpoint)."""
+    ck = Checkpoint(path)
+    cfg = config_from_hf(ck.config)
+    src = _Source(ck, torch.device(device), dtype)
+    P = src.prefix
+    hybrid = (ck.config.get("text_config") or ck.config).get("model_type") in HYBRID_TYPES
+    w: Dict[str, torch.Tensor] = {}
+
+    def norm(name):
+        return src.raw(name).float()
+
+    w["tok_embd"] = src.weight(P + "embed_tokens")
+    w["output_norm"] = norm(P + "norm.weight")
+    if ck.has("lm_head.weight") or ck.has("lm_head.weight_packed"):
+        w["output"] = src.weight("lm_head")
+    else:
+        cfg.tie_embeddings = True
+    D = cfg.head_dim
+
+    def experts(pre: str, p: str):
+        E = cfg.n_expert
+        if ck.has(pre + "experts.gate_up_proj"):                  # already fused [E, H, 2F] or [E, 2F, H]
+            gu = src.raw(pre + "experts.gate_up_proj")
+            dn = src.raw(pre + "experts.down_proj")
+            if gu.shape[1] == cfg.hidden:
+                gu, dn = gu.transpose(1, 2), dn.transpose(1, 2)
+            w[f"{p}.moe.gate_up"], w[f"{p}.moe.down"] = gu.contiguous(), dn.contiguous()
+            return
+        gus, dns = [], []
+        for e in range(E):
+            g = src.weight(f"{pre}experts.{e}.gate_proj")
+            u = src.weight(f"{pre}experts.{e}.up_proj")
+            gus.append(torch.cat([g, u], dim=0))
+            dns.append(src.weight(f"{pre}experts.{e}.down_proj"))
+        w[f"{p}.moe.gate_up"] = torch.stack(gus)
+        w[f"{p}.moe.down"] = torch.stack(dns)
+
+    def ffn(lp: str, p: str, moe: bool):
+        if moe:
+            pre = lp + "mlp."
+            w[f"{p}.moe.router"] = src.weight(pre + "gate")
+            if ck.has(pre + "gate.e_score_correction_bias"):
+                w[f"{p}.moe.router_bias"] = src.raw(pre + "gate.e_score_correction_bias").float()
+            experts(pre, p)
+            for sh in ("shared_expert.", "shared_experts."):
+                if ck.has(pre + sh + "gate_proj.weight") or ck.has(pre + sh + "gate_proj.weight_packed"):
+                    w[f"{p}.moe.sh_gate_up"] = torch.cat([src.weight(pre + sh + "gate_proj"),
+                                                          src.weight(pre + sh + "up_proj")], dim=0)
+                    w[f"{p}.moe.sh_down"] = src.weight(pre + sh + "down_proj")
+            if ck.has(pre + "shared_expert_gate.weight"):
+                w[f"{p}.moe.sh_gate"] = src.weight(pre + "shared_expert_gate").reshape(1, -1)
+        else:
+            w[f"{p}.mlp.gate_up"] = torch.cat([src.weight(lp + "mlp.gate_proj"), src.weight(lp + "mlp.up_proj")], dim=0)
+            w[f"{p}.mlp.down"] = src.weight(lp + "mlp.down_proj")
+
+    def attention(lp: str, p: str):
+        a = lp + "self_attn."
+        q = src.weight(a + "q_proj")
+        w[f"{p}.attn.qkv"] = torch.cat([q, src.weight(a + "k_proj"), src.weight(a + "v_proj")], dim=0)
+        if ck.has(a + "q_norm.weight"):
+            w[f"{p}.attn.q_norm"] = norm(a + "q_norm.weight")
+            w[f"{p}.attn.k_norm"] = norm(a + "k_norm.weight")
+        w[f"{p}.attn.o"] = src.weight(a + "o_proj")
+
+    def deltanet(lp: str, p: str):
+        a = lp + "linear_attn."
+        nk, nv, dk, dv = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_k_dim, cfg.gdn_v_dim
+        r = nv // nk
+        H = cfg.hidden
+        if ck.has(a + "in_proj_qkvz.weight"):
+            # rows are grouped per key head: [q(dk) | k(dk) | v(r*dv) | z(r*dv)]
+            t = src.weight(a + "in_proj_qkvz").view(nk, 2 * dk + 2 * r * dv, H)
+            q, k = t[:, :dk], t[:, dk:2 * dk]
+            v, z = t[:, 2 * dk:2 * dk + r * dv], t[:, 2 * dk + r * dv:]
+            w[f"{p}.gdn.in_qkv"] = torch.cat([q.reshape(-1, H), k.reshape(-1, H), v.reshape(-1, H)], dim=0)
+            w[f"{p}.gdn.in_z"] = z.reshape(-1, H).contiguous()
+            ba = src.weight(a + "in_proj_ba").view(nk, 2 * r, H)
+            w[f"{p}.gdn.in_ba"] = torch.cat([ba[:, :r].reshape(-1, H), ba[:, r:].reshape(-1, H)], dim=0)
+        else:
+            w[f"{p}.gdn.in_qkv"] = src.weight(a + "in_proj_qkv")
+            w[f"{p}.gdn.in_z"] = src.weight(a + "in_proj_z")
+            w[f"{p}.gdn.in_ba"] = torch.cat([src.weight(a + "in_proj_b"), src.weight(a + "in_proj_a")], dim=0)
+        w[f"{p}.gdn.conv_w"] = src.raw(a + "conv1d.weight").float().reshape(cfg.gdn_conv_channels(), -1)
+        w[f"{p}.gdn.A"] = -torch.exp(src.raw(a + "A_log").float())
+        w[f"{p}.gdn.dt_bias"] = src.raw(a + "dt_bias").float()
+        w[f"{p}.gdn.norm"] = norm(a + "norm.weight")       # stored as the plain weight (no +1)
+        w[f"{p}.gdn.out"] = src.weight(a + "out_proj")
+
+    def mla(lp: str, p: str):
+        a = lp + "self_attn."
+        if cfg.q_lora:
+            w[f"{p}.mla.q_a"] = src.weight(a + "q_a_proj")
+            w[f"{p}.mla.q_a_norm"] = norm(a + "q_a_layernorm.weight")
+            w[f"{p}.mla.q_b"] = _deinterleave_rope(src.weight(a + "q_b_proj"), cfg.n_head, cfg.qk_nope_dim, cfg.qk_rope_dim)
+        else:
+            w[f"{p}.mla.q"] = _deinterleave_rope(src.weight(a + "q_proj"), cfg.n_head, cfg.qk_nope_dim, cfg.qk_rope_dim)
+        kva = src.weight(a + "kv_a_proj_with_mqa")
+        w[f"{p}.mla.kv_a"] = _deinterleave_rope(kva, 1, cfg.kv_lora, cfg.qk_rope_dim)
+        w[f"{p}.mla.kv_a_norm"] = norm(a + "kv_a_layernorm.weight")
+        w[f"{p}.mla.kv_b"] = src.weight(a + "kv_b_proj")
+        w[f"{p}.mla.o"] = src.weight(a + "o_proj")
+
+    for il in range(cfg.n_layer):
+        lp, p = f"{P}layers.{il}.", f"l{il}"
+        w[f"{p}.attn_norm"] = norm(lp + "input_layernorm.weight")
+        w[f"{p}.ffn_norm"] = norm(lp + "post_attention_layernorm.weight")
+        kind = cfg.layer_kinds[il]
+        if kind == "gdn":
+            deltanet(lp, p)
+        elif kind == "mla":
+            mla(lp, p)
+        else:
+            attention(lp, p)
+        ffn(lp, p, cfg.is_moe_layer(il))
+    # the engine applies ``norm_offset`` at run time, so (w - 1) checkpoints are kept as stored
+    _ = hybrid
+    out = {}
+    for k, v in w.items():
+        out[k] = v.to(device=device, dtype=torch.float32 if is_fp32_weight(k) else dtype).contiguous()
+    return cfg, out, ck
+
+
+def _deinterleave_rope(wt: torch.Tensor, n_head: int, d_nope: int, d_rope: int) -> torch.Tensor:
+    """DeepSeek checkpoints store rotary dims as interleaved (re, im) pairs; the engine's RoPE pairs
+    dim i with i + d_rope/2, so the rope rows of each head are permuted [0,2,4,...,1,3,5,...]."""
+    per = d_nope + d_rope
+    t = wt.view(n_head, per, -1)
+    idx = torch.cat([torch.arange(0, d_rope, 2), torch.arange(1, d_rope, 2)]) + d_nope
+    full = torch.cat([torch.arange(d_nope), idx])
+    return t[:, full].reshape(n_head * per, -1).contiguous()
+
+
+# ---------------------------------------------------------------------------------------------------
+# writer (test checkpoints and ``legion st`` round trips)
+# ---------------------------------------------------------------------------------------------------
+def save_hf(path: str, cfg: ModelConfig, w: Dict[str, torch.Tensor], quant: str = "none", dtype=torch.bfloat16):
+    """Writes ``config.json`` + ``model.safetensors`` in HF naming (qwen3 / qwen3_moe / hybrid / deepseek_v3).
+    ``quant``: none | fp8_block | nvfp4 (ModelOpt layout) | nvfp4_ct (compressed-tensors layout)."""
+    os.makedirs(path, exist_ok=True)
+    t: Dict[str, torch.Tensor] = {}
+
+    def put(base: str, x: torch.Tensor, quantise: bool = True):
+        x = x.detach().cpu()
+        if quant == "none" or not quantise or x.dim() != 2 or x.shape[1] % 16:
+            t[base + ".weight"] = x.to(dtype)
+        elif quant == "fp8_block":
+            q, s = qf.fp8_block_quant(x.float())
+            t[base + ".weight"], t[base + ".weight_scale_inv"] = q, s
+        elif quant == "nvfp4":
+            c, s, g = qf.nvfp4_quant(x.float())
+            t[base + ".weight"], t[base + ".weight_scale"], t[base + ".weight_scale_2"] = c, s, g.reshape(())
+            t[base + ".input_scale"] = torch.tensor(1.0)
+        elif quant == "nvfp4_ct":
+            c, s, g = qf.nvfp4_quant(x.float())
+            t[base + ".weight_packed"], t[base + ".weight_scale"] = c, s
+            t[base + ".weight_global_scale"] = (1.0 / g).reshape(1)
+        else:
+            raise ValueError(quant)
+
+    P = "model."
+    put(P + "embed_tokens", w["tok_embd"], False)
+    t[P + "norm.weight"] = w["output_norm"].cpu().to(dtype)
+    if "output" in w:
+        put("lm_head", w["output"], False)
+    D = cfg.head_dim
+    for il in range(cfg.n_layer):
+        lp, p = f"{P}layers.{il}.", f"l{il}"
+        t[lp + "input_layernorm.weight"] = w[f"{p}.attn_norm"].cpu().to(dtype)
+        t[lp + "post_attention_layernorm.weight"] = w[f"{p}.ffn_norm"].cpu().to(dtype)
+        kind = cfg.layer_kinds[il]
+        if kind in ("attn", "swa"):
+            a = lp + "self_attn."
+            qkv = w[f"{p}.attn.qkv"]
+            qw = cfg.n_head * D * (2 if cfg.gated_attn else 1)
+            put(a + "q_proj", qkv[:qw])
+            put(a + "k_proj", qkv[qw:qw + cfg.n_kv_head * D])
+            put(a + "v_proj", qkv[qw + cfg.n_kv_head * D:])
+            if cfg.qk_norm:
+                t[a + "q_norm.weight"] = w[f"{p}.attn.q_norm"].cpu().to(dtype)
+                t[a + "k_norm.weight"] = w[f"{p}.attn.k_norm"].cpu().to(dtype)
+            put(a + "o_proj", w[f"{p}.attn.o"])
+        elif kind == "gdn":
+            a = lp + "linear_attn."
+            nv = cfg.gdn_v_heads
+            put(a + "in_proj_qkv", w[f"{p}.gdn.in_qkv"])
+            put(a + "in_proj_z", w[f"{p}.gdn.in_z"])
+            put(a + "in_proj_b", w[f"{p}.gdn.in_ba"][:nv], False)
+            put(a + "in_proj_a", w[f"{p}.gdn.in_ba"][nv:], False)
+            t[a + "conv1d.weight"] = w[f"{p}.gdn.conv_w"].cpu().float().unsqueeze(1)
+            t[a + "A_log"] = torch.log(-w[f"{p}.gdn.A"].cpu().float())
+            t[a + "dt_bias"] = w[f"{p}.gdn.dt_bias"].cpu().float()
+            t[a + "norm.weight"] = w[f"{p}.gdn.norm"].cpu().to(dtype)
+            put(a + "out_proj", w[f"{p}.gdn.out"])
+        elif kind == "mla":
+            a = lp + "self_attn."
+            inv = lambda x, nh, dn, dr: _interleave_rope(x, nh, dn, dr)
+            if cfg.q_lora:
+                put(a + "q_a_proj", w[f"{p}.mla.q_a"])
+                t[a + "q_a_layernorm.weight"] = w[f"{p}.mla.q_a_norm"].cpu().to(dtype)
+                put(a + "q_b_proj", inv(w[f"{p}.mla.q_b"], cfg.n_head, cfg.qk_nope_dim, cfg.qk_rope_dim))
+            else:
+                put(a + "q_proj", inv(w[f"{p}.mla.q"], cfg.n_head, cfg.qk_nope_dim, cfg.qk_rope_dim))
+            put(a + "kv_a_proj_with_mqa", inv(w[f"{p}.mla.kv_a"], 1, cfg.kv_lora, cfg.qk_rope_dim))
+            t[a + "kv_a_layernorm.weight"] = w[f"{p}.mla.kv_a_norm"].cpu().to(dtype)
+            put(a + "kv_b_proj", w[f"{p}.mla.kv_b"])
+            put(a + "o_proj", w[f"{p}.mla.o"])
+        if cfg.is_moe_layer(il):
+            pre = lp + "mlp."
+            put(pre + "gate", w[f"{p}.moe.router"], False)
+            if f"{p}.moe.router_bias" in w:
+                t[pre + "gate.e_score_correction_bias"] = w[f"{p}.moe.router_bias"].cpu().float()
+            F = cfg.expert_ff
+            for e in range(cfg.n_expert):
+                put(f"{pre}experts.{e}.gate_proj", w[f"{p}.moe.gate_up"][e, :F])
+                put(f"{pre}experts.{e}.up_proj", w[f"{p}.moe.gate_up"][e, F:])
+                put(f"{pre}experts.{e}.down_proj", w[f"{p}.moe.down"][e])
+            if cfg.shared_ff:
+                sh = "shared_experts." if cfg.arch == "deepseek_v3" else "shared_expert."
+                Fs = cfg.shared_ff
+                put(pre + sh + "gate_proj", w[f"{p}.moe.sh_gate_up"][:Fs])
+                put(pre + sh + "up_proj", w[f"{p}.moe.sh_gate_up"][Fs:])
+                put(pre + sh + "down_proj", w[f"{p}.moe.sh_down"])
+                if cfg.shared_gate:
+                    put(pre + "shared_expert_gate", w[f"{p}.moe.sh_gate"], False)
+        elif cfg.dense_ff:
+            F = w[f"{p}.mlp.down"].shape[1]
+            put(lp + "mlp.gate_proj", w[f"{p}.mlp.gate_up"][:F])
+            put(lp + "mlp.up_proj", w[f"{p}.mlp.gate_up"][F:])
+            put(lp + "mlp.down_proj", w[f"{p}.mlp.down"])
+    save_file(t, os.path.join(path, "model.safetensors"), {"format": "pt"})
+    json.dump(hf_config_dict(cfg, quant), open(os.path.join(path, "config.json"), "w"), indent=1)
+
+
+def _interleave_rope(wt, n_head, d_nope, d_rope):
+    per = d_nope + d_rope
+    t = wt.view(n_head, per, -1)
+    idx = torch.cat([torch.arange(0, d_rope, 2), torch.arange(1, d_rope, 2)])
+    inv = torch.empty_like(idx)
+    inv[idx] = torch.arange(d_rope)
+    full = torch.cat([torch.arange(d_nope), inv + d_nope])
+    # row j of the stored tensor is row full[j] ... invert the permutation used at load time
+    out = torch.empty_like(t)
+    perm = torch.cat([torch.arange(d_nope), idx + d_nope])
+    out[:, perm] = t
+    _ = full
+    return out.reshape(n_head * per, -1).contiguous()
+
+
+def hf_config_dict(cfg: ModelConfig, quant: str = "none") -> dict:
+    d = {"hidden_size": cfg.hidden, "num_hidden_layers": cfg.n_layer, "num_attention_heads": cfg.n_head,
+         "num_key_value_heads": cfg.n_kv_head, "head_dim": cfg.head_dim, "vocab_size": cfg.vocab,
+         "rope_theta": cfg.rope_theta, "rms_norm_eps": cfg.rms_eps, "tie_word_embeddings": cfg.tie_embeddings,
+         "max_position_embeddings": cfg.max_position, "torch_dtype": "bfloat16"}
+    if cfg.arch in ("qwen35", "qwen35moe"):
+        d.update(model_type="qwen3_5_moe" if cfg.n_expert else "qwen3_5",
+                 layer_types=["linear_attention" if k == "gdn" else "full_attention" for k in cfg.layer_kinds],
+                 partial_rotary_factor=cfg.rope_dim / cfg.head_dim, linear_num_key_heads=cfg.gdn_k_heads,
+                 linear_num_value_heads=cfg.gdn_v_heads, linear_key_head_dim=cfg.gdn_k_dim,
+                 linear_value_head_dim=cfg.gdn_v_dim, linear_conv_kernel_dim=cfg.gdn_conv)
+    elif cfg.arch == "deepseek_v3":
+        d.update(model_type="deepseek_v3", q_lora_rank=cfg.q_lora or None, kv_lora_rank=cfg.kv_lora,
+                 qk_nope_head_dim=cfg.qk_nope_dim, qk_rope_head_dim=cfg.qk_rope_dim, v_head_dim=cfg.v_head_dim,
+                 intermediate_size=cfg.dense_ff, first_k_dense_replace=cfg.first_dense_layers,
+                 n_routed_experts=cfg.n_expert, num_experts_per_tok=cfg.top_k, moe_intermediate_size=cfg.expert_ff,
+                 n_shared_experts=(cfg.shared_ff // cfg.expert_ff) if cfg.expert_ff else 0, scoring_func=cfg.router_mode,
+                 topk_method="noaux_tc" if cfg.router_bias else "greedy", n_group=cfg.n_group,
+                 topk_group=cfg.topk_group, routed_scaling_factor=cfg.route_scale, norm_topk_prob=cfg.norm_topk)
+    else:
+        d["model_type"] = "qwen3_moe" if cfg.n_expert else ("qwen3" if cfg.qk_norm else "llama")
+    if cfg.arch != "deepseek_v3":
+        if cfg.n_expert:
+            d.update(num_experts=cfg.n_expert, num_experts_per_tok=cfg.top_k, moe_intermediate_size=cfg.expert_ff,
+                     norm_topk_prob=cfg.norm_topk, shared_expert_intermediate_size=cfg.shared_ff)
+        else:
+            d["intermediate_size"] = cfg.dense_ff
+    if quant == "fp8_block":
+        d["quantization_config"] = {"quant_method": "fp8", "fmt": "e4m3", "weight_block_size": [128, 128]}
+    elif quant == "nvfp4":
+        d["quantization_config"] = {"quant_method": "modelopt", "quant_algo": "NVFP4"}
+    elif quant == "nvfp4_ct":
+        d["quantization_config"] = {"quant_method": "compressed-tensors", "format": "nvfp4-pack-quantized"}
+    return d

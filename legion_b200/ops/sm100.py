@@ -209,27 +209,28 @@ def sigmoid_gate(attn, qkv, n_q, d, out=None):
 
 
 def decode_splits(batch: int, n_kv_heads: int, g_tiles: int, max_ctx: int) -> int:
-    """Flash-decoding split count: enough CTAs for ~2 waves of the SMs, at most one per 256 keys."""
+    """Flash-decoding split count: about 4 CTAs per SM, at most one split per 128 keys."""
     ctas = max(1, batch * n_kv_heads * g_tiles)
-    want = max(1, (2 * NUM_SMS + ctas - 1) // ctas)
-    cap = max(1, (max_ctx + 255) // 256)
-    return int(min(want, cap, 64))
+    want = max(1, (4 * NUM_SMS + ctas - 1) // ctas)
+    cap = max(1, (max_ctx + 127) // 128)
+    return int(min(want, cap, 128))
 
 
-def paged_decode(q, k_cache, v_cache, block_table, ctx_lens, scale, window=0, n_splits=None, max_ctx=None, out=None):
+def paged_decode(q, k_cache, v_cache, block_table, ctx_lens, scale, window=0, n_splits=None, max_ctx=None, out=None,
+                 impl="tc"):
     C = ext()
     B, Hq, D = q.shape
     Hkv = k_cache.shape[2]
     if n_splits is None:
         G = Hq // Hkv
-        gt = 8 if G >= 8 else (4 if G > 2 else G)
-        n_splits = decode_splits(B, Hkv, (G + gt - 1) // gt, max_ctx or block_table.shape[1] * k_cache.shape[1])
+        n_splits = decode_splits(B, Hkv, (G + 15) // 16, max_ctx or block_table.shape[1] * k_cache.shape[1])
     ws = Workspace.get(q.device)
     o_part = ws.buf("dec_o", (B * Hq * n_splits * D,), torch.float32)
     ml_part = ws.buf("dec_ml", (B * Hq * n_splits * 2,), torch.float32)
     if out is None:
         out = torch.empty_like(q)
-    C.paged_decode(q, k_cache, v_cache, block_table, ctx_lens, scale, window, n_splits, o_part, ml_part, out)
+    C.paged_decode(q, k_cache, v_cache, block_table, ctx_lens, scale, window, n_splits, o_part, ml_part, out,
+                   impl == "tc", ws.status)
     return out
 
 
@@ -288,14 +289,15 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[Moe
     ws = Workspace.get(x.device)
     if plan is None:
         bn = 32 if T * k <= 32 * E_local else (64 if T * k <= 64 * E_local else 128)
-        key = ("moe_plan", T, k, E_local, bn)
+        key = ("moe_plan", T, k, E_local, bn, H, n_ff)
         plan = ws._cache.get(key)
         if plan is None:
             plan = MoePlan(T, k, E_local, bn, x.device)
             ws._cache[key] = plan
     P = T * k
     bn = plan.bn
-    if plan.x_sorted is None or plan.x_sorted.shape[0] < P + bn or plan.x_sorted.shape[1] != H:
+    if (plan.x_sorted is None or plan.x_sorted.shape[0] < P + bn or plan.x_sorted.shape[1] != H
+            or plan.h_sorted.shape[1] != n_ff):
         # padded by one tile so a tile that starts near the end stays inside the tensor map's rows
         plan.x_sorted = torch.zeros(P + bn, H, dtype=torch.bfloat16, device=x.device)
         plan.h_sorted = torch.zeros(P + bn, n_ff, dtype=torch.bfloat16, device=x.device)

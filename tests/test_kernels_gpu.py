@@ -152,12 +152,16 @@ def test_paged_decode(D, Hq, Hkv, page):
     q = rnd(B, Hq, D)
     ctx_t = torch.tensor(ctx, device=DEV, dtype=torch.int32)
     scale = D ** -0.5
-    for ns in (1, 3):
-        out = sm().paged_decode(q, kc, vc, bt, ctx_t, scale, n_splits=ns)
-        want = ref.paged_attention(q, kc, vc, bt, ctx_t, torch.arange(B + 1), scale)
-        close(out, want)
-    outw = sm().paged_decode(q, kc, vc, bt, ctx_t, scale, window=50, n_splits=2)
-    close(outw, ref.paged_attention(q, kc, vc, bt, ctx_t, torch.arange(B + 1), scale, window=50))
+    want = ref.paged_attention(q, kc, vc, bt, ctx_t, torch.arange(B + 1), scale)
+    wantw = ref.paged_attention(q, kc, vc, bt, ctx_t, torch.arange(B + 1), scale, window=50)
+    for impl in ("tc", "simt"):
+        for ns in (1, 3):
+            out = sm().paged_decode(q, kc, vc, bt, ctx_t, scale, n_splits=ns, impl=impl)
+            status_ok()
+            close(out, want)
+        outw = sm().paged_decode(q, kc, vc, bt, ctx_t, scale, window=50, n_splits=2, impl=impl)
+        status_ok()
+        close(outw, wantw)
 
 
 @pytest.mark.parametrize("D,Hq,Hkv,page", [(128, 4, 2, 64), (64, 4, 2, 16), (256, 2, 1, 64), (128, 8, 8, 32)])
