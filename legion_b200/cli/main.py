@@ -1,0 +1,419 @@
+"""``legion`` command line: ``serve | run | bench | chat | top | gguf | st | info | tokenize | ep-place | completions``
+plus ``kernel-bench`` (the per-kernel developer benchmarks). Same verbs and flag names as the reference CLI
+(``src/cli/mod.rs:83-216``, flags ``docs/serving.md:20-414``); flags that only select between the reference's
+ggml-compatible kernel variants have no meaning here and are not present.
+
+    python -m legion_b200 serve --model random:tiny-hybrid-moe --port 8090
+    python -m legion_b200 run --model model.gguf -p "Hello" -n 64
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import logging
+import os
+import sys
+import time
+from typing import List, Optional
+
+
+def _add_engine_args(ap: argparse.ArgumentParser):
+    g = ap.add_argument_group("model")
+    g.add_argument("--model", "-m", help="a .gguf file, an HF checkpoint directory or random:<preset>")
+    g.add_argument("--hfmodel", help="HF checkpoint directory (same as --model for a directory)")
+    g.add_argument("--device", default=None, help="cpu | cuda | cuda:N (default: cuda when available)")
+    g.add_argument("--alias", default=None, help="model id reported by /v1/models")
+    g = ap.add_argument_group("engine")
+    g.add_argument("--ctx-size", type=int, default=8192)
+    g.add_argument("--max-seqs", type=int, default=16)
+    g.add_argument("--max-batch-tokens", type=int, default=None)
+    g.add_argument("--prefill-chunk", type=int, default=None)
+    g.add_argument("--kv-cache-tokens", type=int, default=None)
+    g.add_argument("--kv-block", type=int, default=None, help="tokens per KV block (64 on GPU, 16 on CPU)")
+    g.add_argument("--no-prefix-cache", action="store_true")
+    g.add_argument("--prefix-cache-states", type=int, default=8)
+    g.add_argument("--prefix-cache-interval", type=int, default=0)
+    g.add_argument("--max-waiting", type=int, default=1024)
+    g.add_argument("--default-max-tokens", type=int, default=4096)
+    g.add_argument("--scheduling-policy", choices=["fcfs", "priority"], default="fcfs")
+    g.add_argument("--fair-share", action="store_true")
+    g.add_argument("--kv-admission", choices=["reserve", "on-demand"], default="reserve")
+    g.add_argument("--itl-target", type=float, default=0.0, help="inter-token latency target (ms) for the prompt budget")
+    g.add_argument("--ttft-target", type=float, default=0.0)
+    g.add_argument("--deterministic", action="store_true")
+    g.add_argument("--seed", type=int, default=0)
+    g.add_argument("--no-cuda-graphs", action="store_true")
+    g = ap.add_argument_group("speculative decoding")
+    g.add_argument("--spec", choices=["none", "ngram", "suffix", "mtp", "draft", "eagle3", "dflash"], default="none")
+    g.add_argument("--spec-k", type=int, default=4)
+    g.add_argument("--spec-max-batch", type=int, default=8)
+    g.add_argument("--spec-draft-model", default=None)
+    g.add_argument("--spec-p-min", type=float, default=0.5)
+    g = ap.add_argument_group("parallelism")
+    g.add_argument("--tp", type=int, default=1, help="tensor-parallel ranks (one process per GPU, spawned by serve)")
+    g.add_argument("--gpus", type=int, default=None, help="alias of --tp on a single node")
+    g.add_argument("--tp-moe-ep", action="store_true", help="shard whole experts over the ranks instead of their rows")
+    g.add_argument("--tp-comm", choices=["fused", "nccl"], default="fused")
+    g.add_argument("--tp-replicas", type=int, default=1, help="data-parallel engine replicas")
+    g.add_argument("--experts", choices=["auto", "device", "host", "cache"], default="auto")
+    g.add_argument("--expert-cache-gib", type=float, default=0.0)
+    g = ap.add_argument_group("sampling defaults")
+    g.add_argument("--temp", type=float, default=None)
+    g.add_argument("--top-p", type=float, default=None)
+    g.add_argument("--top-k", type=int, default=None)
+    g.add_argument("--min-p", type=float, default=None)
+    g.add_argument("--tool-format", choices=["hermes", "qwen3_coder"], default="hermes")
+
+
+def build_engine_from_args(a, start: bool = True):
+    import torch
+
+    from ..engine.lm import EngineConfig, LmEngine
+    from ..engine.mock import MockEngine
+    from ..loaders.model import load_model
+    from ..models.decoder import Decoder
+    from ..parallel import dist as pdist
+
+    path = a.model or a.hfmodel
+    if not path:
+        return MockEngine(a.alias or "mock")
+    device = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    rank, local_rank, world = pdist.env_world()
+    if world > 1 and device.startswith("cuda"):
+        device = f"cuda:{local_rank}"
+    on_gpu = device.startswith("cuda")
+    ec = EngineConfig(
+        ctx_size=a.ctx_size, max_seqs=a.max_seqs,
+        max_batch_tokens=a.max_batch_tokens or (8192 if on_gpu else 1024),
+        prefill_chunk=a.prefill_chunk or (4096 if on_gpu else 512), block_size=a.kv_block or (64 if on_gpu else 16),
+        kv_cache_tokens=a.kv_cache_tokens, prefix_cache=not a.no_prefix_cache,
+        prefix_cache_states=a.prefix_cache_states, prefix_cache_interval=a.prefix_cache_interval,
+        max_waiting=a.max_waiting, default_max_tokens=a.default_max_tokens, scheduling_policy=a.scheduling_policy,
+        fair_share=a.fair_share, kv_admission=a.kv_admission, spec=a.spec, spec_k=a.spec_k,
+        spec_max_batch=a.spec_max_batch, deterministic=a.deterministic, device=device, seed=a.seed,
+        cuda_graphs=not a.no_cuda_graphs, model_name=a.alias or os.path.basename(path.rstrip("/")),
+        tool_format=a.tool_format, itl_target_ms=a.itl_target, ttft_target_ms=a.ttft_target)
+    pctx = None
+    if world > 1:
+        from ..config import PRESETS  # noqa: F401
+        pctx = pdist.init_from_env(device, comm=a.tp_comm, expert_parallel=a.tp_moe_ep, max_rows=ec.max_batch_tokens,
+                                   hidden=0)
+    cfg, w, tok, info = load_model(path, device, rank=rank, world=world, expert_parallel=a.tp_moe_ep, seed=a.seed)
+    if pctx is not None and pctx.symm is None and a.tp_comm == "fused" and on_gpu:
+        from ..parallel.symm import SymmComm
+        import torch.distributed as dist
+        pctx.symm = SymmComm(dist.group.WORLD, rank, world, torch.device(device), ec.max_batch_tokens, cfg.hidden)
+        pctx.comm = "fused"
+    model = Decoder(cfg, w, pctx, max_position=ec.ctx_size + 8)
+    eng = LmEngine(model, tok, ec, start=start)
+    logging.getLogger("legion").info("loaded %s: %s, %d layers, %.2fB parameters on %s", path, cfg.arch, cfg.n_layer,
+                                     sum(t.numel() for t in w.values()) / 1e9, device)
+    if a.tp_replicas > 1:
+        from ..engine.replicas import ReplicaEngine
+        return ReplicaEngine([eng] + [LmEngine(model, tok, ec) for _ in range(a.tp_replicas - 1)])
+    return eng
+
+
+def sampling_defaults(a) -> dict:
+    return {k: v for k, v in (("temperature", a.temp), ("top_p", a.top_p), ("top_k", a.top_k), ("min_p", a.min_p))
+            if v is not None}
+
+
+# ------------------------------------------------------------------------------------------------ commands
+def cmd_serve(a):
+    from ..server.app import ServerConfig, serve
+    tp = a.gpus or a.tp
+    if tp > 1 and "RANK" not in os.environ:
+        # one process per GPU: re-launch this command under torch.distributed.run; rank 0 serves HTTP
+        import subprocess
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={tp}",
+               "--master-addr", "127.0.0.1", "--master-port", str(a.master_port), "-m", "legion_b200"] + sys.argv[1:]
+        return subprocess.call(cmd)
+    logging.basicConfig(level=getattr(logging, a.log_level.upper()), format="%(asctime)s %(levelname)s %(name)s: %(message)s")
+    eng = build_engine_from_args(a)
+    eng.set_warming(True)
+    if a.warmup and hasattr(eng, "generate_text"):
+        for n in (64, 16):
+            eng.generate_text(tokens=list(range(1, n + 1)), max_tokens=2, ignore_eos=True)
+    eng.set_warming(False)
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        from ..parallel.spmd import follower_loop
+        return follower_loop(eng)
+    keys = list(a.api_key or [])
+    if os.environ.get("LEGION_API_KEY"):
+        keys.append(os.environ["LEGION_API_KEY"])
+    cfg = ServerConfig(api_keys=keys, max_request_mb=a.max_request_mb, default_max_tokens=a.default_max_tokens,
+                       sampling_defaults=sampling_defaults(a), shutdown_timeout_s=a.shutdown_timeout_secs,
+                       fair_share=a.fair_share)
+    if a.tui:
+        from ..server.dashboard import start_tui
+        start_tui(eng)
+    print(f"legion-b200 listening on http://{a.host}:{a.port}", flush=True)
+    serve(eng, a.host, a.port, cfg, a.tls_cert, a.tls_key, a.log_level)
+    return 0
+
+
+def cmd_run(a):
+    from ..engine.types import ChatMessage, GenerateRequest, SamplingParams
+    eng = build_engine_from_args(a)
+    sp = SamplingParams(temperature=a.temp if a.temp is not None else 0.0, top_p=a.top_p or 1.0, top_k=a.top_k or 0,
+                        min_p=a.min_p or 0.0, max_tokens=a.n_predict, ignore_eos=a.ignore_eos, seed=a.seed)
+    if a.chat:
+        req = GenerateRequest(messages=[ChatMessage("user", a.prompt)], sampling=sp)
+    else:
+        req = GenerateRequest(prompt=a.prompt, sampling=sp)
+    t0 = time.time()
+    n = 0
+    usage = None
+    for ev in eng.generate(req):
+        if ev.kind in ("text", "reasoning"):
+            sys.stdout.write(ev.text)
+            sys.stdout.flush()
+            n += len(ev.token_ids)
+        elif ev.kind == "finished":
+            usage = ev.usage
+        elif ev.kind == "error":
+            print(f"\nerror: {ev.error}", file=sys.stderr)
+            return 1
+    dt = time.time() - t0
+    if usage:
+        print(f"\n\n[{usage.prompt_tokens} prompt tokens ({usage.cached_tokens} cached), {usage.completion_tokens} generated, "
+              f"prefill {usage.prefill_ms:.0f} ms, decode {usage.decode_ms:.0f} ms, {n / max(dt, 1e-9):.1f} tok/s]",
+              file=sys.stderr)
+    eng.shutdown()
+    return 0
+
+
+def cmd_chat(a):
+    import urllib.request
+    history = []
+    print("legion chat - empty line to quit")
+    while True:
+        try:
+            line = input("> ").strip()
+        except EOFError:
+            break
+        if not line:
+            break
+        history.append({"role": "user", "content": line})
+        body = json.dumps({"model": "default", "messages": history, "stream": True, "max_tokens": a.n_predict}).encode()
+        req = urllib.request.Request(a.url.rstrip("/") + "/v1/chat/completions", data=body,
+                                     headers={"content-type": "application/json",
+                                              **({"authorization": f"Bearer {a.api_key}"} if a.api_key else {})})
+        reply = ""
+        with urllib.request.urlopen(req) as r:
+            for raw in r:
+                raw = raw.decode().strip()
+                if not raw.startswith("data: ") or raw == "data: [DONE]":
+                    continue
+                d = json.loads(raw[6:])
+                for c in d.get("choices", []):
+                    t = c.get("delta", {}).get("content") or ""
+                    reply += t
+                    sys.stdout.write(t)
+                    sys.stdout.flush()
+        print()
+        history.append({"role": "assistant", "content": reply})
+    return 0
+
+
+def cmd_bench(a):
+    from ..bench.client import run_bench
+    return run_bench(a)
+
+
+def cmd_gguf(a):
+    from ..loaders.gguf import GgufFile
+    if a.action == "inspect":
+        g = GgufFile(a.file)
+        print(f"{a.file}: arch={g.arch} tensors={len(g.tensors)} metadata={len(g.metadata)}")
+        for k, v in g.metadata.items():
+            s = repr(v)
+            print(f"  {k} = {s if len(s) < 100 else s[:97] + '...'}")
+        if a.tensors:
+            for t in g.tensors.values():
+                print(f"  {t.name:48s} {t.type_name:6s} {list(t.shape)}")
+        return 0
+    if a.action == "diff":
+        g1, g2 = GgufFile(a.file), GgufFile(a.other)
+        rc = 0
+        for k in sorted(set(g1.metadata) | set(g2.metadata)):
+            if g1.metadata.get(k) != g2.metadata.get(k) and not k.startswith("general."):
+                print(f"metadata {k}: {g1.metadata.get(k)!r} != {g2.metadata.get(k)!r}")
+                rc = 1
+        import numpy as np
+        for n in sorted(set(g1.tensors) | set(g2.tensors)):
+            if n not in g1.tensors or n not in g2.tensors:
+                print(f"tensor {n}: only in {'first' if n in g1.tensors else 'second'}")
+                rc = 1
+                continue
+            x, y = g1.numpy(n), g2.numpy(n)
+            if x.shape != y.shape:
+                print(f"tensor {n}: shape {x.shape} != {y.shape}")
+                rc = 1
+            else:
+                d = float(np.abs(x.astype(np.float64) - y.astype(np.float64)).max()) if x.size else 0.0
+                if d > a.tol:
+                    print(f"tensor {n}: max abs diff {d:.3g}")
+                    rc = 1
+        print("identical" if rc == 0 else "different")
+        return rc
+    if a.action == "check":
+        from ..loaders.gguf_map import load_gguf
+        cfg, w, _ = load_gguf(a.file)
+        from ..models.weights import weight_shapes
+        want = weight_shapes(cfg)
+        bad = [k for k, s in want.items() if k not in w or tuple(w[k].shape) != tuple(s)]
+        for k in bad:
+            print(f"{k}: expected {want[k]}, file has {tuple(w[k].shape) if k in w else 'nothing'}")
+        print(f"{cfg.arch}: {len(want) - len(bad)}/{len(want)} tensors ok")
+        return 1 if bad else 0
+    return 2
+
+
+def cmd_st(a):
+    from ..loaders.safetensors_io import Checkpoint
+    ck = Checkpoint(a.path)
+    print(f"{a.path}: {len(ck.where)} tensors, quantisation: {ck.quant_method()}")
+    if ck.config:
+        print(f"  model_type={ck.config.get('model_type')} layers={ck.config.get('num_hidden_layers')}")
+    if a.tensors:
+        for n in sorted(ck.where):
+            dt, shp = ck._open(ck.where[n]).info(n)
+            print(f"  {n:72s} {dt:8s} {list(shp)}")
+    return 0
+
+
+def cmd_info(a):
+    from ..hw.gpu import system_report
+    print(json.dumps(system_report(), indent=1))
+    return 0
+
+
+def cmd_tokenize(a):
+    from ..loaders.model import load_model
+    _, _, tok, _ = load_model(a.model, "cpu") if not a.model.startswith("random:") else (None, None, __import__(
+        "legion_b200.loaders.tokenizer", fromlist=["ByteTokenizer"]).ByteTokenizer(4096), None)
+    ids = tok.encode(a.text, add_special=a.add_special)
+    print(json.dumps({"ids": ids, "n": len(ids), "pieces": [tok.decode([i]) for i in ids]} if a.pieces else ids))
+    return 0
+
+
+def cmd_ep_place(a):
+    from ..parallel.ep_place import place_from_record
+    plan = place_from_record(a.record, a.ranks)
+    json.dump(plan, open(a.out, "w") if a.out else sys.stdout, indent=1)
+    return 0
+
+
+def cmd_completions(a):
+    subs = ["serve", "run", "bench", "chat", "top", "gguf", "st", "info", "tokenize", "ep-place", "completions",
+            "kernel-bench"]
+    if a.shell == "bash":
+        print("complete -W '" + " ".join(subs) + "' legion")
+    else:
+        print("#compdef legion\n_arguments '1: :(" + " ".join(subs) + ")'")
+    return 0
+
+
+def cmd_top(a):
+    from ..server.dashboard import run_top
+    return run_top(a.url, a.api_key, a.interval, a.once)
+
+
+def cmd_kernel_bench(a):
+    from ..bench.kernels import main as kmain
+    argv = ["--only", a.only] + (["--json", a.json] if a.json else [])
+    return kmain(argv)
+
+
+def make_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="legion", description="legion-b200: a Blackwell-native MoE inference engine")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    s = sub.add_parser("serve", help="serve the OpenAI / Anthropic compatible HTTP API")
+    _add_engine_args(s)
+    s.add_argument("--host", default="127.0.0.1")
+    s.add_argument("--port", type=int, default=8090)
+    s.add_argument("--api-key", action="append")
+    s.add_argument("--max-request-mb", type=int, default=64)
+    s.add_argument("--shutdown-timeout-secs", type=float, default=30.0)
+    s.add_argument("--tls-cert")
+    s.add_argument("--tls-key")
+    s.add_argument("--tui", action="store_true")
+    s.add_argument("--no-warmup", dest="warmup", action="store_false")
+    s.add_argument("--log-level", default="info")
+    s.add_argument("--master-port", type=int, default=29533)
+    s.set_defaults(fn=cmd_serve)
+    s = sub.add_parser("run", help="generate once and print the text")
+    _add_engine_args(s)
+    s.add_argument("--prompt", "-p", required=True)
+    s.add_argument("--n-predict", "-n", type=int, default=128)
+    s.add_argument("--chat", action="store_true", help="wrap the prompt in the chat template")
+    s.add_argument("--ignore-eos", action="store_true")
+    s.set_defaults(fn=cmd_run)
+    s = sub.add_parser("chat", help="terminal chat against a running server")
+    s.add_argument("--url", default="http://127.0.0.1:8090")
+    s.add_argument("--api-key")
+    s.add_argument("--n-predict", "-n", type=int, default=1024)
+    s.set_defaults(fn=cmd_chat)
+    s = sub.add_parser("bench", help="benchmark client: bench | chats | prefill | mixed | bandwidth")
+    s.add_argument("workload", nargs="?", default="bench", choices=["bench", "chats", "prefill", "mixed", "bandwidth"])
+    s.add_argument("--url", default="http://127.0.0.1:8090")
+    s.add_argument("--api-key")
+    s.add_argument("--api", choices=["openai", "anthropic"], default="openai")
+    s.add_argument("--concurrency", default="1,4,16")
+    s.add_argument("--prompt-tokens", type=int, default=512)
+    s.add_argument("--max-tokens", type=int, default=256)
+    s.add_argument("--prefill-sizes", default="8192,32768")
+    s.add_argument("--rounds", type=int, default=1)
+    s.add_argument("--save")
+    s.set_defaults(fn=cmd_bench)
+    s = sub.add_parser("top", help="live view of a running server's /v1/stats")
+    s.add_argument("--url", default="http://127.0.0.1:8090")
+    s.add_argument("--api-key")
+    s.add_argument("--interval", type=float, default=1.0)
+    s.add_argument("--once", action="store_true")
+    s.set_defaults(fn=cmd_top)
+    s = sub.add_parser("gguf", help="inspect | diff | check a GGUF file")
+    s.add_argument("action", choices=["inspect", "diff", "check"])
+    s.add_argument("file")
+    s.add_argument("other", nargs="?")
+    s.add_argument("--tensors", action="store_true")
+    s.add_argument("--tol", type=float, default=0.0)
+    s.set_defaults(fn=cmd_gguf)
+    s = sub.add_parser("st", help="inspect a safetensors checkpoint")
+    s.add_argument("action", choices=["inspect"])
+    s.add_argument("path")
+    s.add_argument("--tensors", action="store_true")
+    s.set_defaults(fn=cmd_st)
+    s = sub.add_parser("info", help="hardware report: GPUs, NVLink, measured rooflines")
+    s.set_defaults(fn=cmd_info)
+    s = sub.add_parser("tokenize", help="tokenise text with a model's tokenizer")
+    s.add_argument("--model", "-m", required=True)
+    s.add_argument("text")
+    s.add_argument("--add-special", action="store_true")
+    s.add_argument("--pieces", action="store_true")
+    s.set_defaults(fn=cmd_tokenize)
+    s = sub.add_parser("ep-place", help="co-activation aware expert placement from a route record")
+    s.add_argument("record")
+    s.add_argument("--ranks", type=int, default=8)
+    s.add_argument("--out")
+    s.set_defaults(fn=cmd_ep_place)
+    s = sub.add_parser("completions", help="shell completion script")
+    s.add_argument("shell", choices=["bash", "zsh"])
+    s.set_defaults(fn=cmd_completions)
+    s = sub.add_parser("kernel-bench", help="device-timed micro-benchmarks of the sm_100a kernels")
+    s.add_argument("--only", default="gemm,moe,decode_attn,prefill_attn")
+    s.add_argument("--json")
+    s.set_defaults(fn=cmd_kernel_bench)
+    return ap
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    a = make_parser().parse_args(argv)
+    return int(a.fn(a) or 0)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

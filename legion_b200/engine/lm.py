@@ -511,6 +511,33 @@ class LmEngine(Engine):
             logit_rows=torch.tensor(logit_rows, dtype=torch.int64, device=dev),
             max_q_len=max(n for _, _, n in rows), max_ctx=max(ctx), write_state=write_state, cu_q_host=cu)
 
+    def build_batch_explicit(self, items, all_logits: bool = False) -> StepBatch:
+        """items = [(seq, first position, token list)]: a batch over the sequences' own block tables with
+        explicit tokens (drafters fill their KV and chain drafts with it). Logits: last row of each item."""
+        dev = self.device
+        tok, pos, slots, cu, ctx, lrows = [], [], [], [0], [], []
+        width = 1
+        for s, p0, toks in items:
+            n = len(toks)
+            tok.extend(toks)
+            pos.extend(range(p0, p0 + n))
+            slots.extend(s.table.slots(self.pool, p0, n))
+            cu.append(cu[-1] + n)
+            ctx.append(p0 + n)
+            width = max(width, self.pool.blocks_for(p0 + n))
+            lrows.extend(range(cu[-2], cu[-1]) if all_logits else [cu[-1] - 1])
+        bt = torch.zeros(len(items), width, dtype=torch.int32)
+        for i, (s, p0, toks) in enumerate(items):
+            nb = self.pool.blocks_for(p0 + len(toks))
+            bt[i, :nb] = torch.tensor(s.table.blocks[:nb], dtype=torch.int32)
+        i32 = dict(dtype=torch.int32, device=dev)
+        return StepBatch(token_ids=torch.tensor(tok, **i32), positions=torch.tensor(pos, **i32),
+                         cu_q=torch.tensor(cu, **i32), ctx_lens=torch.tensor(ctx, **i32), block_table=bt.to(dev),
+                         slots=torch.tensor(slots, dtype=torch.int64, device=dev),
+                         state_slots=torch.tensor([s.slot for s, _, _ in items], **i32),
+                         logit_rows=torch.tensor(lrows, dtype=torch.int64, device=dev),
+                         max_q_len=max(len(t) for _, _, t in items), max_ctx=max(ctx), cu_q_host=cu)
+
     def _forward_and_finish(self, rows, verify: bool):
         all_decode_1 = all(s.phase == "decode" and n == 1 for s, _, n in rows)
         need_hidden = self.drafter is not None and getattr(self.drafter, "needs_hidden", False)
@@ -546,6 +573,8 @@ class LmEngine(Engine):
     def _finish_rows(self, rows, b: Optional[StepBatch], logits, out, verify: bool, picked=None):
         r = 0
         commits: List[Tuple[int, int]] = []     # (row index in batch, kept tokens) for replay
+        fed = [([s.tokens[-1]] + s.drafts[:n - 1]) if s.phase == "decode" else s.tokens[p0:p0 + n] for s, p0, n in rows]
+        step_items = []                          # (seq, first position, fed tokens, kept rows, batch index)
         all_plain = all(s.req.sampling.greedy and s.req.sampling.plain and s.constraint is None for s, _, _ in rows)
         device_picks = picked
         if device_picks is None and logits is not None and logits.shape[0] and all_plain:
@@ -558,6 +587,7 @@ class LmEngine(Engine):
             if s.phase == "prefill":
                 s.n_computed = p0 + n
                 s.table.n_tokens = s.n_computed
+                step_items.append((s, p0, fed[bi], n, bi))
                 if self.saved is not None and s.n_computed in s.save_points:
                     self._snapshot(s, s.n_computed, "anchor")
                 if s.n_computed < s.n_prompt:
@@ -572,8 +602,6 @@ class LmEngine(Engine):
                 if s.first_ms == 0.0:
                     s.first_ms = now_ms()
                     s.usage.prefill_ms = s.first_ms - s.admit_ms
-                if out is not None and self.drafter is not None:
-                    self.drafter.on_prefill_done(s, out, b, bi)
                 self._advance(s, [tok], [lp])
                 continue
             # decode / verify rows: n = 1 + drafts
@@ -605,12 +633,13 @@ class LmEngine(Engine):
             s.table.n_tokens = s.n_computed
             if verify:
                 commits.append((bi, kept))
-            if out is not None and self.drafter is not None:
-                self.drafter.on_verified(s, out, b, bi, kept)
+            step_items.append((s, p0, fed[bi], kept, bi))
             self._advance(s, accepted, lps)
         if verify and self.hybrid and b is not None and commits:
             self.model.commit_replay(b, self.states, commits)
         if self.drafter is not None and not self.drafter.model_free:
+            if out is not None:
+                self.drafter.on_step(step_items, b, out)
             live = [s for s, _, _ in rows if s in self.running and s.phase == "decode"]
             if live and len(live) <= self.cfg.spec_max_batch:
                 self.drafter.draft_batch(live, self.cfg.spec_k)

@@ -1,0 +1,56 @@
+"""One entry point to open a model: a ``.gguf`` file, an HF checkpoint directory (safetensors, BF16 / FP8 /
+NVFP4), or ``random:<preset>`` for random-init weights of a named shape (benchmarks and tests).
+
+Returns the hyper-parameters, canonical weights (this rank's shard under TP / EP) and a tokenizer, the way
+the reference's ``LmEngine::load`` opens GGUF directly and HF directories through its converter
+(``src/engine/lm.rs:3932``, ``src/hf/mod.rs:64``).
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from ..config import PRESETS, ModelConfig
+from ..models.weights import Shard, random_weights
+from .tokenizer import BpeTokenizer, ByteTokenizer, Tokenizer
+
+
+def load_model(path: str, device="cpu", dtype=None, rank: int = 0, world: int = 1, expert_parallel: bool = False,
+               seed: int = 0) -> Tuple[ModelConfig, Dict[str, torch.Tensor], Tokenizer, dict]:
+    dev = torch.device(device)
+    if dtype is None:
+        dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    info: dict = {"source": path}
+    if path.startswith("random:"):
+        cfg = PRESETS[path.split(":", 1)[1]]()
+        shard = Shard(cfg, rank, world, expert_parallel) if world > 1 else None
+        w = random_weights(cfg, dev, dtype, seed=seed, shard=shard)
+        return cfg, w, ByteTokenizer(cfg.vocab), info
+    if os.path.isdir(path):
+        from .hf_map import load_hf
+        cfg, w, ck = load_hf(path, "cpu" if world > 1 else dev, dtype)
+        info["quant_method"] = ck.quant_method()
+        tok: Tokenizer
+        if os.path.exists(os.path.join(path, "tokenizer.json")):
+            tok = BpeTokenizer.from_hf_dir(path)
+        else:
+            tok = ByteTokenizer(cfg.vocab)
+    elif path.endswith(".gguf"):
+        from .gguf_map import load_gguf
+        cfg, w, md = load_gguf(path, "cpu" if world > 1 else dev, dtype)
+        info["gguf_arch"] = md.get("general.architecture")
+        if "tokenizer.ggml.tokens" in md and md.get("tokenizer.ggml.model", "gpt2") == "gpt2" \
+                and "tokenizer.ggml.merges" in md:
+            tok = BpeTokenizer.from_gguf_metadata(md)
+        else:
+            tok = ByteTokenizer(cfg.vocab)
+            if md.get("tokenizer.chat_template"):
+                tok.chat_template = md["tokenizer.chat_template"]
+    else:
+        raise ValueError(f"cannot tell what kind of model {path!r} is (expected .gguf, an HF directory or random:<preset>)")
+    if world > 1:
+        sh = Shard(cfg, rank, world, expert_parallel)
+        w = {k: sh.slice(k, v).to(dev) for k, v in w.items()}
+    return cfg, w, tok, info

@@ -1,0 +1,380 @@
+"""Drafters. Model-free ones implement ``propose(seq, k)``; model drafters implement ``on_step`` (see every
+target step: keep their own KV in step with the sequence) and ``draft_batch`` (chain k drafts after a step).
+
+Reference: ``src/spec/ngram.rs``, ``suffix.rs``, ``draft.rs``, ``eagle3.rs`` (+ ``eagle3/config.rs:22-62``),
+``dflash.rs``, MTP in the executor (``src/model/core/exec.rs:1864``, ``src/model/qwen35/mtp.rs:1-14``).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import ops
+from ..config import ModelConfig
+from ..models.decoder import Decoder, KvCache, StatePool
+
+
+class Drafter:
+    model_free = True
+    needs_hidden = False
+    capture_layers: Optional[List[int]] = None
+
+    def propose(self, seq, k: int) -> List[int]:
+        return []
+
+    def on_step(self, items, batch, out):
+        pass
+
+    def draft_batch(self, seqs, k: int):
+        pass
+
+    def release(self, seq):
+        pass
+
+
+class NgramDrafter(Drafter):
+    """Prompt lookup: find the most recent earlier occurrence of the sequence's last n tokens (longest n
+    first) and propose what followed it."""
+
+    def __init__(self, n_min: int = 2, n_max: int = 4):
+        self.n_min, self.n_max = n_min, n_max
+
+    def propose(self, seq, k):
+        t = seq.tokens
+        L = len(t)
+        for n in range(min(self.n_max, L - 1), self.n_min - 1, -1):
+            tail = t[L - n:]
+            for i in range(L - n - 1, -1, -1):
+                if t[i:i + n] == tail:
+                    return list(t[i + n:i + n + k])
+        return []
+
+
+class SuffixDrafter(Drafter):
+    """Suffix index over everything seen: the running sequence plus finished replies of earlier requests
+    (a cross-request cache). Proposes the continuation of the longest suffix that occurred before."""
+
+    def __init__(self, max_suffix: int = 8, cache_tokens: int = 1 << 18):
+        self.max_suffix, self.cache_tokens = max_suffix, cache_tokens
+        self.index: Dict[tuple, tuple] = {}      # n-gram -> (corpus id, position after it)
+        self.corpus: Dict[int, List[int]] = {}
+        self._next_id = 0
+        self._size = 0
+
+    def _add(self, toks: List[int]):
+        cid = self._next_id
+        self._next_id += 1
+        self.corpus[cid] = list(toks)
+        self._size += len(toks)
+        for n in range(2, self.max_suffix + 1):
+            for i in range(0, len(toks) - n):
+                self.index[tuple(toks[i:i + n])] = (cid, i + n)
+        while self._size > self.cache_tokens and self.corpus:
+            old = min(self.corpus)
+            self._size -= len(self.corpus.pop(old))
+
+    def propose(self, seq, k):
+        t = seq.tokens
+        own = NgramDrafter(2, self.max_suffix).propose(seq, k)
+        if own:
+            return own
+        for n in range(min(self.max_suffix, len(t)), 1, -1):
+            hit = self.index.get(tuple(t[-n:]))
+            if hit and hit[0] in self.corpus:
+                c = self.corpus[hit[0]]
+                return c[hit[1]:hit[1] + k]
+        return []
+
+    def release(self, seq):
+        if seq.n_out > 0:
+            self._add(seq.tokens)
+
+
+class _ModelDrafter(Drafter):
+    model_free = False
+    needs_hidden = True
+
+    def __init__(self, engine):
+        self.eng = engine
+        self.prev: Dict[int, torch.Tensor] = {}    # id(seq) -> hidden row paired with the next token
+
+    def release(self, seq):
+        self.prev.pop(id(seq), None)
+
+    def _zeros(self, H):
+        return torch.zeros(H, device=self.eng.device, dtype=self.eng.model.dtype)
+
+
+class MtpDrafter(_ModelDrafter):
+    """The model's own MTP head: input row for position p = eh_proj([norm(embed(tok_p)); norm(h_{p-1})]) where
+    h is the target's residual stream (or, when chaining, the head's own output). The head's KV lives in the
+    target's blocks (an extra layer of the KV cache), so prefix-cache hits cover it too."""
+
+    def __init__(self, engine):
+        super().__init__(engine)
+        assert engine.mcfg.mtp_layers > 0, "--spec mtp needs a model with an MTP head"
+
+    def on_step(self, items, b, out):
+        eng = self.eng
+        H = eng.mcfg.hidden
+        cu = b.cu_q_host
+        fill, prevs = [], []
+        for s, p0, fed, kept, bi in items:
+            if kept <= 0:
+                continue
+            rows = out.last_hidden[cu[bi]:cu[bi] + kept]
+            first = self.prev.get(id(s))
+            if first is None:
+                first = self._zeros(H)
+            prevs.append(torch.cat([first[None], rows[:kept - 1]], dim=0))
+            fill.append((s, p0, fed[:kept]))
+            self.prev[id(s)] = rows[kept - 1].clone()
+        if fill:
+            mb = eng.build_batch_explicit(fill)
+            eng.model.mtp_forward(0, mb, torch.cat(prevs, dim=0), eng.kv, eng.states)
+
+    def draft_batch(self, seqs, k):
+        eng = self.eng
+        live = [s for s in seqs if id(s) in self.prev]
+        for s in live:
+            s.drafts = []
+        hidden = {id(s): self.prev[id(s)] for s in live}
+        for j in range(k):
+            items, prevs = [], []
+            for s in live:
+                pos = len(s.tokens) - 1 + j
+                if pos + 2 >= eng.cfg.ctx_size or pos >= s.table.capacity(eng.pool):
+                    continue
+                tok = s.tokens[-1] if j == 0 else s.drafts[j - 1]
+                items.append((s, pos, [tok]))
+                prevs.append(hidden[id(s)][None])
+            if not items:
+                break
+            mb = eng.build_batch_explicit(items)
+            o = eng.model.mtp_forward(0, mb, torch.cat(prevs, dim=0), eng.kv, eng.states)
+            picks = ops.argmax(o.logits).tolist()
+            for (s, _, _), t, row in zip(items, picks, o.last_hidden):
+                s.drafts.append(int(t))
+                hidden[id(s)] = row
+
+
+class DraftModelDrafter(_ModelDrafter):
+    """A separate (smaller) model with the target's vocabulary. It sees every token the target sees (own KV in
+    the same block ids) and then runs k greedy steps ahead."""
+
+    def __init__(self, engine, draft: Optional[Decoder] = None):
+        super().__init__(engine)
+        self.draft = draft if draft is not None else engine.model
+        if self.draft.cfg.vocab != engine.mcfg.vocab:
+            raise ValueError("the draft model must use the target's vocabulary")
+        self.kv = KvCache(self.draft.cfg, engine.pool.total, engine.cfg.block_size, engine.device, self.draft.dtype,
+                          kv_heads_local=self.draft.n_kv_l)
+        self.hybrid = bool(self.draft.cfg.recurrent_layers())
+        self.states = StatePool(self.draft.cfg, engine.cfg.max_seqs + 1, engine.device) if self.hybrid else None
+        self.state_saved = StatePool(self.draft.cfg, engine.cfg.max_seqs + 1, engine.device) if self.hybrid else None
+        self.filled: Dict[int, int] = {}
+
+    def on_step(self, items, b, out):
+        eng = self.eng
+        fill = []
+        for s, p0, fed, kept, bi in items:
+            if kept <= 0:
+                continue
+            done = self.filled.get(id(s), 0)
+            if done < p0:       # resumed from the prefix cache: the draft model has to read the prefix itself
+                fill.append((s, done, s.tokens[done:p0] + fed[:kept]))
+            else:
+                fill.append((s, p0, fed[:kept]))
+            self.filled[id(s)] = p0 + kept
+            self.prev[id(s)] = True
+        if fill:
+            mb = eng.build_batch_explicit(fill)
+            self.draft.forward(mb, self.kv, self.states, want_logits=False)
+
+    def draft_batch(self, seqs, k):
+        eng = self.eng
+        live = [s for s in seqs if id(s) in self.prev]
+        if self.hybrid:
+            for s in live:
+                # recurrent draft models: snapshot the state, draft ahead, restore
+                for t_src, t_dst in zip(list(self.states.conv.values()) + list(self.states.ssm.values()),
+                                        list(self.state_saved.conv.values()) + list(self.state_saved.ssm.values())):
+                    t_dst[s.slot].copy_(t_src[s.slot])
+        for s in live:
+            s.drafts = []
+        for j in range(k):
+            items = []
+            for s in live:
+                pos = len(s.tokens) - 1 + j
+                if pos + 2 >= eng.cfg.ctx_size or pos >= s.table.capacity(eng.pool):
+                    continue
+                items.append((s, pos, [s.tokens[-1] if j == 0 else s.drafts[j - 1]]))
+            if not items:
+                break
+            mb = eng.build_batch_explicit(items)
+            o = self.draft.forward(mb, self.kv, self.states)
+            for (s, _, _), t in zip(items, ops.argmax(o.logits).tolist()):
+                s.drafts.append(int(t))
+        if self.hybrid:
+            for s in live:
+                for t_src, t_dst in zip(list(self.state_saved.conv.values()) + list(self.state_saved.ssm.values()),
+                                        list(self.states.conv.values()) + list(self.states.ssm.values())):
+                    t_dst[s.slot].copy_(t_src[s.slot])
+
+    def release(self, seq):
+        super().release(seq)
+        self.filled.pop(id(seq), None)
+
+
+class Eagle3Head:
+    """EAGLE-3 style draft head (``src/spec/eagle3/config.rs:22-62``): target hidden states of three layers
+    (low / middle / high) are fused by ``fc`` into one feature g; the single decoder layer attends over
+    ``[norm(embed(token)) ; norm(g)]`` rows (input width 2H) with its own KV; its output feeds the LM head
+    (optionally a reduced draft vocabulary mapped back through ``d2t``) and serves as g when chaining."""
+
+    def __init__(self, cfg: ModelConfig, device, dtype, seed: int = 1, draft_vocab: int = 0, weights=None):
+        self.cfg = cfg
+        H, D = cfg.hidden, cfg.head_dim
+        nq, nkv = cfg.n_head, cfg.n_kv_head
+        F = cfg.dense_ff or 4 * H
+        g = torch.Generator().manual_seed(seed)
+        r = lambda *shape: (torch.randn(*shape, generator=g) * 0.02).to(device=device, dtype=dtype)
+        one = lambda n: torch.ones(n, device=device, dtype=torch.float32)
+        self.draft_vocab = draft_vocab or cfg.vocab
+        self.w = weights or {
+            "fc": r(H, 3 * H), "enorm": one(H), "hnorm": one(H), "qkv": r((nq + 2 * nkv) * D, 2 * H), "o": r(H, nq * D),
+            "ffn_norm": one(H), "gate_up": r(2 * F, H), "down": r(H, F), "out_norm": one(H),
+            "lm_head": r(self.draft_vocab, H)}
+        self.d2t = None if self.draft_vocab == cfg.vocab else torch.arange(self.draft_vocab, device=device)
+        self.n_ff = F
+
+    def fuse(self, feats: List[torch.Tensor]) -> torch.Tensor:
+        return ops.linear(torch.cat(feats, dim=-1), self.w["fc"])
+
+    def forward(self, tokens_embed, g, b, kv_k, kv_v, cos_sin):
+        cfg, w = self.cfg, self.w
+        e, _ = ops.rmsnorm(tokens_embed, w["enorm"], cfg.rms_eps)
+        gn, _ = ops.rmsnorm(g, w["hnorm"], cfg.rms_eps)
+        x = torch.cat([e, gn], dim=-1).contiguous()
+        qkv = ops.linear(x, w["qkv"])
+        q, _ = ops.qk_norm_rope_append(qkv, cfg.n_head, cfg.n_kv_head, cfg.head_dim, None, None, cfg.rms_eps, 0.0,
+                                       cos_sin, cfg.rope_dim, b.positions, b.slots, kv_k, kv_v, False)
+        o = ops.paged_attention(q, kv_k, kv_v, b.block_table, b.ctx_lens, b.cu_q, b.max_q_len, cfg.head_dim ** -0.5,
+                                max_ctx=b.max_ctx or None)
+        h = ops.linear(o.reshape(o.shape[0], -1), w["o"], residual=g)
+        hn, _ = ops.rmsnorm(h, w["ffn_norm"], cfg.rms_eps)
+        f = ops.linear(ops.gate_up_act(hn, w["gate_up"], self.n_ff), w["down"], residual=h)
+        out, _ = ops.rmsnorm(f, w["out_norm"], cfg.rms_eps)
+        return f, out
+
+    def logits(self, normed):
+        return ops.linear(normed, self.w["lm_head"], out_dtype=torch.float32)
+
+
+class Eagle3Drafter(_ModelDrafter):
+    def __init__(self, engine, head: Optional[Eagle3Head] = None, layer_ids: Optional[List[int]] = None):
+        super().__init__(engine)
+        cfg = engine.mcfg
+        n = cfg.n_layer
+        self.capture_layers = layer_ids or sorted({min(2, n - 1), n // 2, max(0, n - 3)})
+        while len(self.capture_layers) < 3:
+            self.capture_layers = sorted(set(self.capture_layers) | {len(self.capture_layers)})[:3] \
+                if n >= 3 else (self.capture_layers + [self.capture_layers[-1]])
+        self.head = head or Eagle3Head(cfg, engine.device, engine.model.dtype)
+        nb = engine.pool.total
+        shape = (nb, engine.cfg.block_size, cfg.n_kv_head, cfg.head_dim)
+        self.k = torch.zeros(shape, device=engine.device, dtype=engine.model.dtype)
+        self.v = torch.zeros(shape, device=engine.device, dtype=engine.model.dtype)
+
+    def _features(self, out, lo, hi):
+        return self.head.fuse([out.captures[l][lo:hi] for l in self.capture_layers[:3]])
+
+    def on_step(self, items, b, out):
+        eng = self.eng
+        cu = b.cu_q_host
+        fill, gs = [], []
+        for s, p0, fed, kept, bi in items:
+            if kept <= 0:
+                continue
+            g_rows = self._features(out, cu[bi], cu[bi] + kept)      # g_p for positions p0 .. p0+kept-1
+            first = self.prev.get(id(s))
+            if first is None:
+                first = self._zeros(eng.mcfg.hidden)
+            # the row for position p pairs token p with the feature of position p - 1
+            gs.append(torch.cat([first[None], g_rows[:kept - 1]], dim=0))
+            fill.append((s, p0, fed[:kept]))
+            self.prev[id(s)] = g_rows[kept - 1].clone()
+        if fill:
+            mb = eng.build_batch_explicit(fill)
+            self.head.forward(eng.model.embed(mb.token_ids), torch.cat(gs, dim=0), mb, self.k, self.v, eng.model.cos_sin)
+
+    def draft_batch(self, seqs, k):
+        eng = self.eng
+        live = [s for s in seqs if id(s) in self.prev]
+        for s in live:
+            s.drafts = []
+        feat = {id(s): self.prev[id(s)] for s in live}
+        for j in range(k):
+            items, gs = [], []
+            for s in live:
+                pos = len(s.tokens) - 1 + j
+                if pos + 2 >= eng.cfg.ctx_size or pos >= s.table.capacity(eng.pool):
+                    continue
+                items.append((s, pos, [s.tokens[-1] if j == 0 else s.drafts[j - 1]]))
+                gs.append(feat[id(s)][None])
+            if not items:
+                break
+            mb = eng.build_batch_explicit(items)
+            raw, normed = self.head.forward(eng.model.embed(mb.token_ids), torch.cat(gs, dim=0), mb, self.k, self.v,
+                                            eng.model.cos_sin)
+            picks = ops.argmax(self.head.logits(normed))
+            if self.head.d2t is not None:
+                picks = self.head.d2t[picks.long()]
+            for (s, _, _), t, row in zip(items, picks.tolist(), raw):
+                s.drafts.append(int(t))
+                feat[id(s)] = row
+
+
+class DflashDrafter(_ModelDrafter):
+    """Block drafter: ONE pass proposes a whole block of k tokens from the target's last hidden row. Each
+    block position j gets ``proj(h) + pos_emb[j]``; one bidirectional self-attention layer over the block and
+    an FFN mix the positions; the target's LM head scores them (``src/spec/dflash.rs:1-75``: one pass per
+    block, no chaining)."""
+
+    def __init__(self, engine, block: int = 8, seed: int = 2):
+        super().__init__(engine)
+        cfg = engine.mcfg
+        H = cfg.hidden
+        g = torch.Generator().manual_seed(seed)
+        r = lambda *shape: (torch.randn(*shape, generator=g) * 0.02).to(device=engine.device, dtype=engine.model.dtype)
+        self.block = block
+        self.w = {"proj": r(H, H), "pos": r(block, H), "qkv": r(3 * H, H), "o": r(H, H), "gate_up": r(4 * H, H),
+                  "down": r(H, 2 * H), "norm": torch.ones(H, device=engine.device)}
+
+    def on_step(self, items, b, out):
+        cu = b.cu_q_host
+        for s, p0, fed, kept, bi in items:
+            if kept > 0:
+                self.prev[id(s)] = out.last_hidden[cu[bi] + kept - 1].clone()
+
+    def draft_batch(self, seqs, k):
+        eng = self.eng
+        live = [s for s in seqs if id(s) in self.prev]
+        if not live:
+            return
+        k = min(k, self.block)
+        w = self.w
+        H = eng.mcfg.hidden
+        h = torch.stack([self.prev[id(s)] for s in live])                       # [n, H]
+        x = (ops.linear(h, w["proj"]).float()[:, None, :] + w["pos"][:k].float()[None]).to(h.dtype)   # [n, k, H]
+        n = x.shape[0]
+        qkv = ops.linear(x.reshape(n * k, H), w["qkv"]).float().view(n, k, 3, H)
+        att = torch.softmax(qkv[:, :, 0] @ qkv[:, :, 1].transpose(1, 2) * H ** -0.5, dim=-1) @ qkv[:, :, 2]
+        y = ops.linear(att.reshape(n * k, H).to(h.dtype), w["o"], residual=x.reshape(n * k, H))
+        f = ops.linear(ops.gate_up_act(y, w["gate_up"], 2 * H), w["down"], residual=y)
+        normed, _ = ops.rmsnorm(f, w["norm"], eng.mcfg.rms_eps)
+        picks = ops.argmax(eng.model.logits(normed)).view(n, k).tolist()
+        for s, p in zip(live, picks):
+            room = eng.cfg.ctx_size - len(s.tokens) - 2
+            s.drafts = [int(t) for t in p[:max(0, room)]]
