@@ -266,3 +266,44 @@ int penalties_mask_launch(float* logits, long ld, int rows, int V, const int* co
 }
 
 }  // namespace lb
+
+// ---------------------------------------------------------------------------------------------
+// Arg-max for callers that cannot allocate device memory (declared in noalloc.h).
+// ---------------------------------------------------------------------------------------------
+#include "noalloc.h"
+
+namespace {
+
+// Partial (value, index) pairs of the two-stage arg-max: LB_NOALLOC_MAX_ROWS rows x LB_NOALLOC_BLOCKS
+// blocks x 8 bytes = 128 KiB, held by every device that loads this library until the process exits.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[LB_NOALLOC_MAX_ROWS * LB_NOALLOC_BLOCKS * 8];
+
+// Device address of g_noalloc_scratch per device ordinal. In host code the array's name is only a
+// stand-in for the symbol, so the real address is looked up once per device with that device current.
+void* g_noalloc_ptr[LB_NOALLOC_MAX_DEVICES] = {};
+
+}  // namespace
+
+extern "C" int lb_argmax_noalloc(const float* logits, long ld, int rows, int vocab, int* out, void* stream) {
+  if (!logits || !out || rows < 0 || vocab <= 0 || ld < vocab) return LB_NOALLOC_BAD_ARGS;
+  if (rows > LB_NOALLOC_MAX_ROWS) return LB_NOALLOC_TOO_LARGE;
+  if (rows == 0) return LB_NOALLOC_OK;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= LB_NOALLOC_MAX_DEVICES) return LB_NOALLOC_CUDA_ERROR;
+  if (!g_noalloc_ptr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p) return LB_NOALLOC_CUDA_ERROR;
+    g_noalloc_ptr[dev] = p;
+  }
+  float* pv = static_cast<float*>(g_noalloc_ptr[dev]);
+  int* pi = reinterpret_cast<int*>(pv + LB_NOALLOC_MAX_ROWS * LB_NOALLOC_BLOCKS);
+  int nblk = (vocab + 4095) / 4096;
+  if (nblk < 1) nblk = 1;
+  if (nblk > LB_NOALLOC_BLOCKS) nblk = LB_NOALLOC_BLOCKS;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // Every partial that the join kernel reads is written by the first kernel of the same call, so
+  // nothing in the scratch has to start at zero.
+  lb::argmax_part_kernel<float><<<dim3(nblk, rows), 256, 0, s>>>(logits, ld, vocab, nblk, pv, pi);
+  lb::argmax_join_kernel<<<rows, 32, 0, s>>>(pv, pi, nblk, out, nullptr);
+  return cudaGetLastError() == cudaSuccess ? LB_NOALLOC_OK : LB_NOALLOC_CUDA_ERROR;
+}
