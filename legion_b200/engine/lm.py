@@ -639,7 +639,7 @@ class LmEngine(Engine):
             self.model.commit_replay(b, self.states, commits)
         if self.drafter is not None and not self.drafter.model_free:
             if out is not None:
-                self.drafter.on_step(step_items, b, out)
+                self.drafter.on_step([it for it in step_items if not it[0].finished], b, out)
             live = [s for s, _, _ in rows if s in self.running and s.phase == "decode"]
             if live and len(live) <= self.cfg.spec_max_batch:
                 self.drafter.draft_batch(live, self.cfg.spec_k)

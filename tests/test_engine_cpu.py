@@ -1,0 +1,200 @@
+"""Scheduler invariants on the CPU engine (fp32 reference ops, tiny random models): whatever the batching,
+chunking, caching, speculation or preemption, greedy output equals a plain single-request run token for token.
+Mirrors the reference's integration tests (tests/qwen35_engine.rs, spec_engine.rs, kv_on_demand.rs)."""
+import threading
+
+import pytest
+import torch
+
+from legion_b200.config import tiny_dense, tiny_gqa_moe, tiny_hybrid_moe, tiny_mla_moe
+from legion_b200.engine.lm import EngineConfig, build_engine
+from legion_b200.engine.types import FinishReason, GenerateRequest, SamplingParams
+from legion_b200.models.weights import random_weights
+
+CFGS = {"hybrid": tiny_hybrid_moe, "gqa_moe": tiny_gqa_moe, "dense": tiny_dense, "mla": tiny_mla_moe}
+
+
+def prompt(n, seed=1, vocab=255):
+    return torch.randint(0, vocab, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def engine(name, weights=None, **kw):
+    cfg = CFGS[name]()
+    base = dict(ctx_size=512, max_seqs=4, block_size=16, prefill_chunk=64, max_batch_tokens=128)
+    base.update(kw)
+    if weights is None:
+        weights = random_weights(cfg, "cpu", torch.float32, seed=0, std=0.05)
+    return build_engine(cfg, weights=weights, engine_cfg=EngineConfig(**base))
+
+
+def run(eng, toks, n=24, **sp):
+    return eng.generate_text(tokens=toks, max_tokens=n, ignore_eos=True, **sp)
+
+
+@pytest.fixture(scope="module")
+def golden():
+    out = {}
+    for name in CFGS:
+        eng = engine(name, prefix_cache=False)
+        out[name] = [run(eng, prompt(100, s)).token_ids for s in (1, 2, 3)]
+        eng.shutdown()
+    return out
+
+
+@pytest.mark.parametrize("name", list(CFGS))
+def test_batched_equals_single(name, golden):
+    eng = engine(name, prefix_cache=False)
+    streams = [eng.generate(GenerateRequest(prompt_tokens=prompt(100, s), sampling=SamplingParams(max_tokens=24, ignore_eos=True)))
+               for s in (1, 2, 3)]
+    got = [s.collect().token_ids for s in streams]
+    eng.shutdown()
+    assert got == golden[name]
+
+
+@pytest.mark.parametrize("name", ["hybrid", "gqa_moe"])
+@pytest.mark.parametrize("chunk", [16, 100, 512])
+def test_chunked_prefill_equals_one_pass(name, chunk, golden):
+    eng = engine(name, prefix_cache=False, prefill_chunk=chunk, max_batch_tokens=max(chunk, 16))
+    got = run(eng, prompt(100, 1)).token_ids
+    eng.shutdown()
+    assert got == golden[name][0]
+
+
+@pytest.mark.parametrize("name", list(CFGS))
+def test_prefix_cache_hit_equals_cold(name, golden):
+    eng = engine(name)
+    a = run(eng, prompt(100, 1))
+    b = run(eng, prompt(100, 1))
+    # a longer prompt sharing the first 64 tokens
+    p2 = prompt(100, 1)[:64] + prompt(40, 9)
+    cold = engine(name, prefix_cache=False)
+    want2 = run(cold, p2).token_ids
+    cold.shutdown()
+    c = run(eng, p2)
+    st = eng.stats()
+    eng.shutdown()
+    assert a.token_ids == golden[name][0] and b.token_ids == golden[name][0]
+    assert a.usage.cached_tokens == 0 and b.usage.cached_tokens >= 96
+    assert c.token_ids == want2
+    assert c.usage.cached_tokens >= (48 if name != "hybrid" else 0)
+    assert st.prefix_cache_hit_tokens > 0
+
+
+def test_multi_turn_resumes_from_end_of_reply_state():
+    """Hybrid model: the second turn extends prompt + reply of the first; the end-of-reply snapshot (recurrent
+    state + partly filled tail block) lets it resume mid-block."""
+    eng = engine("hybrid")
+    p1 = prompt(70, 4)
+    a = run(eng, p1, n=13)
+    turn2 = p1 + a.token_ids[:-1] + prompt(20, 5)
+    b = run(eng, turn2, n=8)
+    cold = engine("hybrid", prefix_cache=False)
+    want = run(cold, turn2, n=8).token_ids
+    cold.shutdown()
+    eng.shutdown()
+    assert b.token_ids == want
+    assert b.usage.cached_tokens == 70 + 12      # everything the first turn computed
+
+
+@pytest.mark.parametrize("name,spec", [("gqa_moe", "ngram"), ("hybrid", "ngram"), ("gqa_moe", "suffix"), ("gqa_moe", "draft"),
+                                       ("hybrid", "draft"), ("mla", "mtp"), ("gqa_moe", "eagle3"), ("dense", "dflash")])
+def test_speculative_equals_plain_greedy(name, spec, golden):
+    eng = engine(name, prefix_cache=False, spec=spec, spec_k=3)
+    # a repetitive prompt so that n-gram drafters actually propose
+    rep = (prompt(20, 1) * 5)
+    plain = engine(name, prefix_cache=False)
+    want = [run(plain, prompt(100, 1)).token_ids, run(plain, rep).token_ids]
+    plain.shutdown()
+    got = [run(eng, prompt(100, 1)).token_ids, run(eng, rep).token_ids]
+    st = eng.stats()
+    eng.shutdown()
+    assert got == want
+    if spec == "draft":          # the draft model is the target itself: every draft is accepted
+        assert st.spec_draft_tokens > 0
+        if name == "gqa_moe":
+            assert st.spec_accepted_tokens == st.spec_draft_tokens
+        else:   # recurrent layers: one-token draft steps and multi-token verify steps round differently
+            assert st.spec_accepted_tokens >= 0.85 * st.spec_draft_tokens
+    if spec in ("mtp", "eagle3", "dflash", "draft"):
+        assert st.spec_verify_steps > 0
+
+
+def test_on_demand_admission_preempts_and_recomputes(golden):
+    # 3 prompts of 100 tokens + 24 outputs need 24 blocks of 16; two fit at admission (7 blocks each) but not when they grow to 8: one is preempted
+    eng = engine("gqa_moe", prefix_cache=False, kv_admission="on-demand", kv_cache_tokens=15 * 16)
+    streams = [eng.generate(GenerateRequest(prompt_tokens=prompt(100, s), sampling=SamplingParams(max_tokens=24, ignore_eos=True)))
+               for s in (1, 2, 3)]
+    got = [s.collect().token_ids for s in streams]
+    st = eng.stats()
+    eng.shutdown()
+    assert got == golden["gqa_moe"]
+    assert st.kv_preemptions >= 1
+
+
+def test_reserve_admission_queues_until_space(golden):
+    eng = engine("gqa_moe", prefix_cache=False, kv_cache_tokens=10 * 16)    # one request at a time fits
+    streams = [eng.generate(GenerateRequest(prompt_tokens=prompt(100, s), sampling=SamplingParams(max_tokens=24, ignore_eos=True)))
+               for s in (1, 2)]
+    got = [s.collect().token_ids for s in streams]
+    eng.shutdown()
+    assert got == golden["gqa_moe"][:2]
+
+
+def test_oversize_request_is_refused():
+    eng = engine("dense", kv_cache_tokens=64)
+    with pytest.raises(ValueError):
+        eng.generate(GenerateRequest(prompt_tokens=prompt(100), sampling=SamplingParams(max_tokens=200)))
+    eng.shutdown()
+
+
+def test_stop_string_max_tokens_and_cancel():
+    eng = engine("dense")
+    full = run(eng, prompt(30, 2), n=16)
+    assert full.finish_reason == FinishReason.LENGTH and len(full.token_ids) == 16
+    text = full.text
+    if len(text) > 6:
+        stop = text[3:6]
+        cut = eng.generate_text(tokens=prompt(30, 2), max_tokens=16, ignore_eos=True, stop=[stop])
+        assert cut.finish_reason == FinishReason.STOP_SEQUENCE
+        assert cut.text == text[:text.index(stop)]
+    s = eng.generate(GenerateRequest(prompt_tokens=prompt(30, 2), sampling=SamplingParams(max_tokens=400, ignore_eos=True)))
+    n = 0
+    for ev in s:
+        if ev.kind == "text":
+            n += 1
+            if n == 3:
+                s.cancel()
+        if ev.kind == "finished":
+            assert ev.finish_reason == FinishReason.CANCELLED
+    assert n < 400
+    eng.shutdown()
+
+
+def test_sampling_is_seeded_and_respects_top_k():
+    eng = engine("dense")
+    a = eng.generate_text(tokens=prompt(20), max_tokens=12, ignore_eos=True, temperature=1.0, seed=7)
+    b = eng.generate_text(tokens=prompt(20), max_tokens=12, ignore_eos=True, temperature=1.0, seed=7)
+    c = eng.generate_text(tokens=prompt(20), max_tokens=12, ignore_eos=True, temperature=1.0, seed=8)
+    g = eng.generate_text(tokens=prompt(20), max_tokens=12, ignore_eos=True)
+    k1 = eng.generate_text(tokens=prompt(20), max_tokens=12, ignore_eos=True, temperature=1.5, top_k=1, seed=3)
+    lp = eng.generate_text(tokens=prompt(20), max_tokens=4, ignore_eos=True, logprobs=True, top_logprobs=3)
+    eng.shutdown()
+    assert a.token_ids == b.token_ids and a.token_ids != c.token_ids
+    assert k1.token_ids == g.token_ids           # top_k = 1 is greedy whatever the temperature
+    assert len(lp.logprobs) == 4 and all(len(x.top) == 3 and x.logprob <= 0 for x in lp.logprobs)
+    assert lp.token_ids == g.token_ids[:4]
+
+
+def test_priority_and_fair_share_order():
+    from legion_b200.engine.queue import WaitQueue
+    q = WaitQueue("priority")
+    q.push("lo", 0)
+    q.push("hi", 5)
+    q.push("lo2", 0)
+    q.requeue("pre", 0)
+    assert [q.pop() for _ in range(4)] == ["hi", "pre", "lo", "lo2"]
+    f = WaitQueue("fcfs", fair_share=True)
+    f.charge("a", 1000)
+    f.push("a1", key="a")
+    f.push("b1", key="b")
+    assert f.pop() == "b1"
