@@ -1,0 +1,231 @@
+"""Checkpoint formats: GGUF write/read round trip and block de-quantisation, safetensors / HF directories with
+BF16, block-scaled FP8 and NVFP4 (ModelOpt and compressed-tensors layouts), tokenizer and chat template."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from legion_b200.config import tiny_hybrid_moe, tiny_mla_moe, tiny_gqa_moe
+from legion_b200.loaders import gguf as G
+from legion_b200.loaders import quant_formats as qf
+from legion_b200.loaders.gguf_map import load_gguf, write_gguf
+from legion_b200.loaders.hf_map import load_hf, save_hf
+from legion_b200.loaders.model import load_model
+from legion_b200.loaders.safetensors_io import Checkpoint, SafetensorsFile, save_file
+from legion_b200.loaders.tokenizer import BpeTokenizer, ByteTokenizer
+from legion_b200.loaders import chat_template as ct
+from legion_b200.models.weights import random_weights
+
+
+def test_gguf_roundtrip_hybrid_model(tmp_path):
+    cfg = tiny_hybrid_moe()
+    w = random_weights(cfg, "cpu", torch.float32, seed=0)
+    path = str(tmp_path / "m.gguf")
+    write_gguf(path, cfg, w)
+    cfg2, w2, md = load_gguf(path)
+    assert md["general.architecture"] == "qwen35moe"
+    assert cfg2.layer_kinds == cfg.layer_kinds and cfg2.n_expert == 8 and cfg2.gdn_v_heads == 4
+    assert set(w2) == set(w)
+    for k in w:
+        assert torch.equal(w[k], w2[k]), k
+
+
+def test_gguf_model_runs_same_tokens(tmp_path):
+    from legion_b200.engine.lm import EngineConfig, build_engine
+    cfg = tiny_hybrid_moe()
+    w = random_weights(cfg, "cpu", torch.float32, seed=0, std=0.05)
+    path = str(tmp_path / "m.gguf")
+    write_gguf(path, cfg, w)
+    cfg2, w2, tok, _ = load_model(path, "cpu")
+    cfg2.gdn_tiled_heads = cfg.gdn_tiled_heads     # this file was written from ungrouped (HF-order) heads
+    prompt = list(range(1, 129))
+    outs = []
+    for c, ww in ((cfg, w), (cfg2, w2)):
+        e = build_engine(c, weights=ww, engine_cfg=EngineConfig(ctx_size=256, max_seqs=2, block_size=16))
+        outs.append(e.generate_text(tokens=prompt, max_tokens=8, ignore_eos=True).token_ids)
+        e.shutdown()
+    assert outs[0] == outs[1]
+
+
+def _ref_dequant(name, blk):
+    """Scalar re-statement of the block formats (independent of the vectorised code)."""
+    f16 = lambda b: float(np.frombuffer(bytes(b), dtype=np.float16)[0])
+    out = []
+    if name == "Q8_0":
+        d = f16(blk[0:2])
+        return [d * int(np.int8(x)) for x in blk[2:34]]
+    if name == "Q4_0":
+        d = f16(blk[0:2])
+        q = blk[2:18]
+        return [d * ((int(x) & 15) - 8) for x in q] + [d * ((int(x) >> 4) - 8) for x in q]
+    def sm(j, s):
+        if j < 4:
+            return s[j] & 63, s[j + 4] & 63
+        return (s[j + 4] & 15) | ((s[j - 4] >> 6) << 4), (s[j + 4] >> 4) | ((s[j] >> 6) << 4)
+    if name == "Q4_K":
+        d, dmin, s, q = f16(blk[0:2]), f16(blk[2:4]), [int(x) for x in blk[4:16]], [int(x) for x in blk[16:144]]
+        for i in range(4):
+            sc1, m1 = sm(2 * i, s)
+            sc2, m2 = sm(2 * i + 1, s)
+            ch = q[32 * i:32 * i + 32]
+            out += [d * sc1 * (x & 15) - dmin * m1 for x in ch] + [d * sc2 * (x >> 4) - dmin * m2 for x in ch]
+        return out
+    if name == "Q5_K":
+        d, dmin, s = f16(blk[0:2]), f16(blk[2:4]), [int(x) for x in blk[4:16]]
+        qh, q = [int(x) for x in blk[16:48]], [int(x) for x in blk[48:176]]
+        for i in range(4):
+            sc1, m1 = sm(2 * i, s)
+            sc2, m2 = sm(2 * i + 1, s)
+            ch = q[32 * i:32 * i + 32]
+            out += [d * sc1 * ((x & 15) + (16 if qh[l] & (1 << (2 * i)) else 0)) - dmin * m1 for l, x in enumerate(ch)]
+            out += [d * sc2 * ((x >> 4) + (16 if qh[l] & (2 << (2 * i)) else 0)) - dmin * m2 for l, x in enumerate(ch)]
+        return out
+    if name == "Q6_K":
+        ql, qh = [int(x) for x in blk[0:128]], [int(x) for x in blk[128:192]]
+        sc = [int(np.int8(x)) for x in blk[192:208]]
+        d = f16(blk[208:210])
+        y = [0.0] * 256
+        for n in range(2):
+            for l in range(32):
+                i = l // 16
+                a, b, c, e = ql[64 * n + l], ql[64 * n + l + 32], qh[32 * n + l], sc[8 * n:8 * n + 8]
+                y[128 * n + l] = d * e[i] * (((a & 15) | ((c & 3) << 4)) - 32)
+                y[128 * n + l + 32] = d * e[i + 2] * (((b & 15) | (((c >> 2) & 3) << 4)) - 32)
+                y[128 * n + l + 64] = d * e[i + 4] * (((a >> 4) | (((c >> 4) & 3) << 4)) - 32)
+                y[128 * n + l + 96] = d * e[i + 6] * (((b >> 4) | (((c >> 6) & 3) << 4)) - 32)
+        return y
+    raise AssertionError(name)
+
+
+@pytest.mark.parametrize("name", ["Q8_0", "Q4_0", "Q4_K", "Q5_K", "Q6_K"])
+def test_gguf_dequant_matches_scalar_reference(name):
+    rng = np.random.default_rng(3)
+    tid = G.TYPE_ID[name]
+    _, be, bb = G.GGML_TYPES[tid]
+    raw = rng.integers(0, 256, size=(6, bb), dtype=np.uint8)
+    # keep the f16 scale fields finite
+    for off in ([0] if name in ("Q8_0", "Q4_0") else ([0, 2] if name in ("Q4_K", "Q5_K") else [208])):
+        raw[:, off:off + 2] = np.frombuffer(np.float16(rng.uniform(-2, 2, 6)).tobytes(), dtype=np.uint8).reshape(6, 2)
+    got = G.dequantize(raw.reshape(-1), tid, (6, be))
+    want = np.array([_ref_dequant(name, row) for row in raw], dtype=np.float32)
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5)
+    try:
+        from gguf import quants as gq
+        lib = gq.dequantize(raw, tid)
+        np.testing.assert_allclose(got, lib.reshape(6, be), rtol=1e-5, atol=1e-5)
+    except Exception:
+        pass
+
+
+def test_gguf_quantised_write_read(tmp_path):
+    x = np.random.default_rng(0).standard_normal((8, 64)).astype(np.float32)
+    wr = G.GgufWriter(str(tmp_path / "q.gguf"), "test")
+    wr.add("test.ints", [1, 2, 3])
+    wr.add("test.name", "héllo")
+    wr.add_tensor("a", x, "Q8_0")
+    wr.add_tensor("b", x, "Q4_0")
+    wr.add_tensor("c", torch.from_numpy(x).bfloat16())
+    wr.add_tensor("d", x, "F16")
+    wr.write()
+    g = G.GgufFile(str(tmp_path / "q.gguf"))
+    assert g.metadata["test.ints"] == [1, 2, 3] and g.metadata["test.name"] == "héllo"
+    assert g.tensors["a"].type_name == "Q8_0" and g.tensors["a"].shape == (8, 64)
+    assert np.abs(g.numpy("a") - x).max() < 0.03
+    assert np.abs(g.numpy("b") - x).max() < 0.5
+    assert np.abs(g.numpy("c") - x).max() < 0.02 and np.abs(g.numpy("d") - x).max() < 2e-3
+
+
+def test_safetensors_roundtrip(tmp_path):
+    t = {"a": torch.randn(3, 5), "b": torch.randn(4, 4).bfloat16(), "c": torch.arange(6, dtype=torch.int32),
+         "d": torch.randn(8, 16).to(torch.float8_e4m3fn), "e": torch.randint(0, 255, (2, 8), dtype=torch.uint8)}
+    p = str(tmp_path / "x.safetensors")
+    save_file(t, p, {"format": "pt"})
+    f = SafetensorsFile(p)
+    assert f.metadata == {"format": "pt"}
+    for k, v in t.items():
+        got = f.tensor(k)
+        assert got.dtype == v.dtype and torch.equal(got.view(torch.uint8) if v.dtype == torch.float8_e4m3fn else got,
+                                                    v.view(torch.uint8) if v.dtype == torch.float8_e4m3fn else v)
+    from safetensors.torch import load_file      # the reference implementation reads our file
+    lib = load_file(p)
+    assert torch.equal(lib["a"], t["a"]) and torch.equal(lib["b"], t["b"])
+
+
+def test_nvfp4_and_fp8_golden_vectors():
+    # codes 0..15 with scale 1 decode to the E2M1 table
+    codes = torch.tensor([[0x10, 0x32, 0x54, 0x76, 0x98, 0xBA, 0xDC, 0xFE]], dtype=torch.uint8)
+    one = torch.tensor([[1.0]]).to(torch.float8_e4m3fn)
+    out = qf.nvfp4_dequant(codes, one, 2.0)
+    assert out.tolist() == [[0, 1, 2, 3, 4, 6, 8, 12, -0.0, -1, -2, -3, -4, -6, -8, -12]]
+    out_ct = qf.nvfp4_dequant(codes, one, 0.5, global_is_divisor=True)
+    assert torch.equal(out, out_ct)
+    w = torch.randn(32, 64) * 0.02
+    c, s, g = qf.nvfp4_quant(w)
+    back = qf.nvfp4_dequant(c, s, g)
+    assert (back - w).norm() / w.norm() < 0.12
+    q, sc = qf.fp8_block_quant(torch.randn(200, 300))
+    assert q.shape == (200, 300) and sc.shape == (2, 3)
+    w8 = torch.randn(200, 300)
+    q, sc = qf.fp8_block_quant(w8)
+    assert (qf.fp8_dequant(q, sc, (128, 128)) - w8).norm() / w8.norm() < 0.04
+    xq, xs = qf.fp8_act_quant(torch.randn(5, 256))
+    assert xs.shape == (5, 2)
+
+
+@pytest.mark.parametrize("quant,tol", [("none", 0.01), ("fp8_block", 0.05), ("nvfp4", 0.15), ("nvfp4_ct", 0.15)])
+@pytest.mark.parametrize("mk", [tiny_hybrid_moe, tiny_mla_moe, tiny_gqa_moe])
+def test_hf_directory_roundtrip(tmp_path, mk, quant, tol):
+    cfg = mk()
+    cfg.mtp_layers = 0
+    w = random_weights(cfg, "cpu", torch.float32, seed=1)
+    d = str(tmp_path / "ck")
+    save_hf(d, cfg, w, quant=quant, dtype=torch.float32 if quant == "none" else torch.bfloat16)
+    ck = Checkpoint(d)
+    assert ck.quant_method() == {"none": "none", "fp8_block": "fp8_block", "nvfp4": "nvfp4", "nvfp4_ct": "nvfp4_ct"}[quant]
+    cfg2, w2, _ = load_hf(d)
+    assert cfg2.layer_kinds == cfg.layer_kinds and cfg2.n_expert == cfg.n_expert and cfg2.kv_lora == cfg.kv_lora
+    assert set(w2) == set(w)
+    for k in w:
+        a, b = w[k].float(), w2[k].float()
+        assert a.shape == b.shape, k
+        if a.dim() >= 2 and quant != "none":
+            assert (a - b).norm() <= tol * a.norm() + 1e-6, k
+        else:
+            assert torch.allclose(a, b, atol=2e-3, rtol=1e-2), k
+
+
+def test_byte_tokenizer_and_bpe():
+    t = ByteTokenizer(512)
+    ids = t.encode("hi<|im_end|>é")
+    assert ids[:2] == [104, 105] and ids[2] == 259 and t.decode(ids) == "hi<|im_end|>é"
+    assert t.decode(ids, skip_special=True) == "hié"
+    # a small BPE: bytes + merges "h e" "he l" "l o"
+    from legion_b200.loaders.tokenizer import _byte_to_unicode
+    b2u = _byte_to_unicode()
+    tokens = [b2u[i] for i in range(256)] + ["he", "hel", "lo", "Ġw", "<|eot|>"]
+    bpe = BpeTokenizer(tokens, ["h e", "he l", "l o", "Ġ w"], token_types=[1] * 260 + [3], eos_ids=[260])
+    ids = bpe.encode("hello world<|eot|>")
+    assert [bpe.tokens[i] for i in ids[:2]] == ["hel", "lo"] and ids[-1] == 260
+    assert bpe.decode(ids) == "hello world<|eot|>" and bpe.decode(ids, skip_special=True) == "hello world"
+    assert bpe.token_bytes(ids[0]) == b"hel"
+    md = {"tokenizer.ggml.tokens": tokens, "tokenizer.ggml.merges": ["h e"], "tokenizer.ggml.eos_token_id": 260,
+          "tokenizer.ggml.token_type": [1] * 260 + [3]}
+    assert BpeTokenizer.from_gguf_metadata(md).eos_ids == (260,)
+
+
+def test_chat_template_rendering():
+    from legion_b200.loaders.tokenizer import DEFAULT_CHATML_TEMPLATE
+    msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi"}]
+    out = ct.render(DEFAULT_CHATML_TEMPLATE, msgs)
+    assert out == "<|im_start|>system\nbe brief<|im_end|>\n<|im_start|>user\nhi<|im_end|>\n<|im_start|>assistant\n"
+    no_think = ct.render(DEFAULT_CHATML_TEMPLATE, msgs, enable_thinking=False)
+    assert no_think.endswith("<think>\n\n</think>\n\n")
+    tools = [{"type": "function", "function": {"name": "f", "parameters": {"type": "object"}}}]
+    with_tools = ct.render(DEFAULT_CHATML_TEMPLATE, msgs + [
+        {"role": "assistant", "content": "", "tool_calls": [{"id": "1", "function": {"name": "f", "arguments": "{\"a\": 1}"}}]},
+        {"role": "tool", "content": "42"}], tools=tools)
+    assert "<tools>" in with_tools and '"name": "f", "arguments": {"a": 1}' in with_tools and "<tool_response>\n42" in with_tools
+    with pytest.raises(ct.TemplateError):
+        ct.render("{{ raise_exception('nope') }}", msgs)
