@@ -1,0 +1,152 @@
+"""HTTP surface over the mock engine: every route, SSE framing, error shapes, auth, overload, metrics; and one
+end-to-end pass over a real (tiny, CPU) engine."""
+import json
+
+import pytest
+from fastapi.testclient import TestClient
+
+from legion_b200.engine.mock import MockEngine
+from legion_b200.server.app import ServerConfig, create_app
+
+
+def client(**kw):
+    eng = kw.pop("engine", None) or MockEngine("mock")
+    return TestClient(create_app(eng, ServerConfig(**kw)))
+
+
+def sse(text):
+    out = []
+    ev = None
+    for line in text.splitlines():
+        if line.startswith("event: "):
+            ev = line[7:]
+        elif line.startswith("data: "):
+            d = line[6:]
+            out.append((ev, d if d == "[DONE]" else json.loads(d)))
+            ev = None
+    return out
+
+
+def test_health_models_stats_metrics_webui():
+    c = client()
+    assert c.get("/health").json()["status"] == "ok"
+    assert c.get("/v1/models").json()["data"][0]["id"] == "mock"
+    assert c.get("/models").json()["object"] == "list"
+    assert c.get("/v1/models/mock").json()["id"] == "mock"
+    r = c.get("/v1/models/nope")
+    assert r.status_code == 404 and r.json()["error"]["type"] == "not_found_error"
+    assert c.get("/v1/stats").json()["schema"] == 1
+    c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "a b c"}]})
+    m = c.get("/metrics").text
+    assert "legion_http_requests_total" in m and "legion_completion_tokens_total 3.0" in m
+    assert "legion_engine_kv_blocks_total" in m and "legion_time_to_first_token_bucket" in m
+    assert "<title>legion-b200</title>" in c.get("/").text
+    assert "x-request-id" in c.get("/health").headers
+
+
+def test_chat_completion_and_stream():
+    c = client()
+    r = c.post("/v1/chat/completions", json={"model": "whatever", "messages": [{"role": "user", "content": "one two three"}],
+                                             "unknown_field": 1, "logprobs": True, "top_logprobs": 1})
+    j = r.json()
+    assert r.status_code == 200 and j["object"] == "chat.completion" and j["model"] == "mock"
+    assert j["choices"][0]["message"]["content"] == "one two three" and j["choices"][0]["finish_reason"] == "stop"
+    assert j["usage"]["completion_tokens"] == 3 and "timings" in j and len(j["choices"][0]["logprobs"]["content"]) == 3
+    r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "a b"}], "stream": True,
+                                             "stream_options": {"include_usage": True}})
+    ev = sse(r.text)
+    assert ev[-1][1] == "[DONE]"
+    chunks = [d for _, d in ev[:-1]]
+    assert chunks[0]["choices"][0]["delta"]["role"] == "assistant"
+    assert "".join(ch["choices"][0]["delta"].get("content", "") for ch in chunks if ch["choices"]) == "a b"
+    assert chunks[-2]["choices"][0]["finish_reason"] == "stop" and chunks[-1]["usage"]["completion_tokens"] == 2
+    # length, stop sequences, tools
+    r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "a b c d"}], "max_tokens": 2})
+    assert r.json()["choices"][0]["finish_reason"] == "length"
+    r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "a b STOP d"}], "stop": "STOP"})
+    assert r.json()["choices"][0]["message"]["content"] == "a b "
+    tools = [{"type": "function", "function": {"name": "get", "parameters": {"type": "object"}}}]
+    r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": '/tool get {"x": 1}'}], "tools": tools})
+    msg = r.json()["choices"][0]
+    assert msg["finish_reason"] == "tool_calls" and msg["message"]["tool_calls"][0]["function"]["name"] == "get"
+    r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "response_format": {"type": "json_object"}})
+    assert json.loads(r.json()["choices"][0]["message"]["content"]) == {"echo": "x"}
+
+
+def test_completions_anthropic_responses():
+    c = client()
+    r = c.post("/v1/completions", json={"prompt": "say this", "max_tokens": 8, "echo": True})
+    assert r.json()["choices"][0]["text"] == "say thissay this" and r.json()["object"] == "text_completion"
+    r = c.post("/v1/completions", json={"prompt": "a b", "stream": True})
+    assert sse(r.text)[-1][1] == "[DONE]"
+    r = c.post("/v1/messages", json={"model": "m", "max_tokens": 16, "system": "s",
+                                     "messages": [{"role": "user", "content": [{"type": "text", "text": "hey there"}]}]})
+    j = r.json()
+    assert j["type"] == "message" and j["content"][0]["text"] == "hey there" and j["stop_reason"] == "end_turn"
+    r = c.post("/v1/messages", json={"max_tokens": 16, "stream": True, "messages": [{"role": "user", "content": "a b"}]})
+    names = [e for e, _ in sse(r.text)]
+    assert names[:3] == ["message_start", "ping", "content_block_start"]
+    assert names[-3:] == ["content_block_stop", "message_delta", "message_stop"] and "content_block_delta" in names
+    assert c.post("/v1/messages/count_tokens", json={"messages": [{"role": "user", "content": "a b c"}]}).json()["input_tokens"] > 0
+    r = c.post("/v1/responses", json={"input": "hello you", "instructions": "be nice"})
+    j = r.json()
+    assert j["object"] == "response" and j["status"] == "completed" and j["output_text"] == "hello you"
+    r = c.post("/v1/responses", json={"input": "x y", "stream": True})
+    names = [e for e, _ in sse(r.text)]
+    assert names[0] == "response.created" and names[-1] == "response.completed"
+    assert c.post("/v1/responses", json={"input": "x", "previous_response_id": "r1"}).status_code == 400
+    assert c.post("/v1/responses", json={"input": "x", "store": True}).status_code == 400
+
+
+def test_validation_errors_in_the_callers_shape():
+    c = client()
+    for body in ({"messages": []}, {"messages": [{"role": "user", "content": "x"}], "temperature": 3},
+                 {"messages": [{"role": "user", "content": "x"}], "top_p": 0},
+                 {"messages": [{"role": "user", "content": "x"}], "top_logprobs": 21},
+                 {"messages": [{"role": "user", "content": "x"}], "min_tokens": 9, "max_tokens": 2},
+                 {"messages": [{"role": "wizard", "content": "x"}]},
+                 {"messages": [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "http://x/y.png"}}]}]},
+                 {"messages": [{"role": "user", "content": "x"}], "chat_template_kwargs": {"enable_thinking": "yes"}}):
+        r = c.post("/v1/chat/completions", json=body)
+        assert r.status_code == 400 and r.json()["error"]["type"] == "invalid_request_error", body
+    r = c.post("/v1/chat/completions", content=b"{not json", headers={"content-type": "application/json"})
+    assert r.status_code == 400 and "invalid JSON" in r.json()["error"]["message"]
+    r = c.post("/v1/messages", json={"max_tokens": 5, "temperature": 1.5, "messages": [{"role": "user", "content": "x"}]})
+    assert r.status_code == 400 and r.json()["type"] == "error" and r.json()["error"]["type"] == "invalid_request_error"
+
+
+def test_auth_body_limit_overload():
+    c = client(api_keys=["sekret"])
+    assert c.get("/health").status_code == 200
+    assert c.get("/v1/models").status_code == 401
+    assert c.get("/v1/models", headers={"authorization": "Bearer sekret"}).status_code == 200
+    assert c.get("/v1/models", headers={"x-api-key": "sekret"}).status_code == 200
+    r = c.post("/v1/messages", json={}, headers={"x-api-key": "bad"})
+    assert r.status_code == 401 and r.json()["error"]["type"] == "authentication_error"
+    c = client(max_request_mb=0)
+    assert c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x" * 100}]}).status_code == 413
+    busy = MockEngine("mock", max_in_flight=0)
+    c = client(engine=busy)
+    r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}]})
+    assert r.status_code == 429
+    r = c.post("/v1/messages", json={"max_tokens": 4, "messages": [{"role": "user", "content": "x"}]})
+    assert r.status_code == 529 and r.json()["error"]["type"] == "overloaded_error"
+
+
+def test_real_engine_behind_the_server():
+    from legion_b200.config import tiny_hybrid_moe
+    from legion_b200.engine.lm import EngineConfig, build_engine
+    eng = build_engine(tiny_hybrid_moe(), engine_cfg=EngineConfig(ctx_size=256, max_seqs=2, block_size=16))
+    c = client(engine=eng)
+    body = {"messages": [{"role": "user", "content": "hello"}], "max_tokens": 6, "temperature": 0, "ignore_eos": True}
+    a = c.post("/v1/chat/completions", json=body).json()
+    b = c.post("/v1/chat/completions", json=body).json()
+    assert a["usage"]["completion_tokens"] == 6 and a["choices"][0]["finish_reason"] == "length"
+    assert a["choices"][0]["message"]["content"] == b["choices"][0]["message"]["content"]
+    assert b["usage"]["prompt_tokens_details"]["cached_tokens"] > 0
+    r = c.post("/v1/chat/completions", json=dict(body, max_tokens=100000))
+    assert r.status_code == 200     # max_tokens is clamped to the context
+    r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x" * 400}], "max_tokens": 4})
+    assert r.status_code == 400 and "context" in r.json()["error"]["message"]
+    assert c.get("/v1/stats").json()["engine"]["prefix_cache_hit_tokens"] > 0
+    eng.shutdown()
