@@ -96,8 +96,8 @@ def build_engine_from_args(a, start: bool = True):
     pctx = None
     if world > 1:
         from ..config import PRESETS  # noqa: F401
-        pctx = pdist.init_from_env(device, comm=a.tp_comm, expert_parallel=a.tp_moe_ep, max_rows=ec.max_batch_tokens,
-                                   hidden=0)
+        pctx = pdist.init_from_env(device, comm="nccl", expert_parallel=a.tp_moe_ep)   # symmetric memory is attached
+        # below, once the model's hidden size is known
     cfg, w, tok, info = load_model(path, device, rank=rank, world=world, expert_parallel=a.tp_moe_ep, seed=a.seed)
     if pctx is not None and pctx.symm is None and a.tp_comm == "fused" and on_gpu:
         from ..parallel.symm import SymmComm
@@ -130,16 +130,21 @@ def cmd_serve(a):
                "--master-addr", "127.0.0.1", "--master-port", str(a.master_port), "-m", "legion_b200"] + sys.argv[1:]
         return subprocess.call(cmd)
     logging.basicConfig(level=getattr(logging, a.log_level.upper()), format="%(asctime)s %(levelname)s %(name)s: %(message)s")
-    eng = build_engine_from_args(a)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    eng = build_engine_from_args(a, start=world == 1)
+    if world > 1:
+        from ..parallel import spmd
+        spmd.attach(eng, int(os.environ.get("RANK", "0")), world)
+        eng.start()
     eng.set_warming(True)
-    if a.warmup and hasattr(eng, "generate_text"):
+    if a.warmup and hasattr(eng, "generate_text") and world == 1:
         for n in (64, 16):
             eng.generate_text(tokens=list(range(1, n + 1)), max_tokens=2, ignore_eos=True)
     eng.set_warming(False)
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
-        from ..parallel.spmd import follower_loop
-        return follower_loop(eng)
+        from ..parallel.spmd import follower_wait
+        return follower_wait(eng)
     keys = list(a.api_key or [])
     if os.environ.get("LEGION_API_KEY"):
         keys.append(os.environ["LEGION_API_KEY"])

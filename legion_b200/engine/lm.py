@@ -149,6 +149,8 @@ class LmEngine(Engine):
             from .cuda_graphs import DecodeGraphs
             self._graphs = DecodeGraphs(self)
         self.step_hook: Optional[Callable] = None    # tests observe (batch description) per step
+        self.channel = None                          # parallel.spmd.StepChannel when several ranks serve together
+        self._by_id: Dict[str, Seq] = {}
         if start:
             self.start()
 
@@ -241,10 +243,15 @@ class LmEngine(Engine):
         try:
             while not self._stop.is_set():
                 idle = not self.running and len(self.waiting) == 0
-                self._drain(block=idle)
+                if self.channel is not None:
+                    self._sync_ranks(idle)
+                else:
+                    self._drain(block=idle)
+                    if self._stop.is_set():
+                        break
+                    self._handle_cancels()
                 if self._stop.is_set():
                     break
-                self._handle_cancels()
                 self._admit()
                 if self.running:
                     self.step()
@@ -266,6 +273,52 @@ class LmEngine(Engine):
                 item = self._inbox.get_nowait()
             except queue.Empty:
                 return
+
+    def _sync_ranks(self, idle: bool):
+        """Several ranks, one scheduler each: rank 0 publishes the requests and cancellations it saw since the
+        last step; every rank applies them at the same step boundary, so all ranks plan the same steps."""
+        import pickle
+        ch = self.channel
+        msgs = None
+        if ch.rank == 0:
+            msgs = []
+            try:
+                item = self._inbox.get(timeout=0.2) if idle else self._inbox.get_nowait()
+                while True:
+                    if item is None:
+                        msgs.append(("shutdown", None))
+                        break
+                    if not item.req.request_id:
+                        item.req.request_id = f"r{id(item):x}"
+                    self._by_id[item.req.request_id] = item
+                    msgs.append(("req", pickle.dumps(item.req)))
+                    item = self._inbox.get_nowait()
+            except queue.Empty:
+                pass
+            for s in list(self.running) + self.waiting.items():
+                if s.stream.cancel_token.cancelled and not s.finished:
+                    msgs.append(("cancel", s.req.request_id))
+        for kind, payload in ch.exchange(msgs):
+            if kind == "shutdown":
+                self._stop.set()
+                return
+            if kind == "req":
+                req = pickle.loads(payload)
+                seq = self._by_id.get(req.request_id) if ch.rank == 0 else None
+                if seq is None:
+                    seq = self.prepare(req)
+                    self._by_id[req.request_id] = seq
+                self.waiting.push(seq, seq.priority, seq.key)
+            elif kind == "cancel":
+                seq = self._by_id.get(payload)
+                if seq is None or seq.finished:
+                    continue
+                if seq in self.running:
+                    self._finish(seq, FinishReason.CANCELLED)
+                else:
+                    self.waiting.remove(lambda q: q is seq)
+                    seq.finished = True
+                    seq.stream.put(TokenEvent(kind="finished", finish_reason=FinishReason.CANCELLED, usage=seq.usage))
 
     def _fail_all(self, msg: str):
         for s in self.running + self.waiting.items():
@@ -789,6 +842,7 @@ class LmEngine(Engine):
         self._release(s)
         self.waiting.charge(s.key, s.usage.total_tokens)
         s.stream.put(TokenEvent(kind="finished", finish_reason=reason, usage=s.usage))
+        self._by_id.pop(s.req.request_id, None)
 
     # ------------------------------------------------------------------ convenience
     def generate_text(self, prompt=None, tokens=None, **sampling) -> "Completion":

@@ -89,3 +89,57 @@ def test_shard_shapes_cover_the_full_weights():
             assert n_local in (v.numel(), v.numel() * world), k       # split exactly once, or mirrored
         ep = [Shard(cfg, r, world, expert_parallel=True) for r in range(world)]
         assert [e.expert_range() for e in ep] == [(r * 8 // world, (r + 1) * 8 // world) for r in range(world)]
+
+
+def _serve_worker(rank, world, port, out_path):
+    import datetime
+    import time
+
+    import torch.distributed as dist
+    from legion_b200.engine.lm import EngineConfig, build_engine
+    from legion_b200.engine.types import GenerateRequest, SamplingParams
+    from legion_b200.models.weights import Shard, random_weights
+    from legion_b200.parallel import spmd
+    from legion_b200.parallel.context import ParallelCtx
+    torch.set_num_threads(2)
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=120))
+    cfg = CFGS["gqa_moe"]()
+    full = random_weights(cfg, "cpu", torch.float32, seed=0, std=0.05)
+    pctx = ParallelCtx(rank, world, dist.group.WORLD, False, "nccl")
+    eng = build_engine(cfg, weights=Shard(cfg, rank, world).shard_all(full), pctx=pctx, start=False,
+                       engine_cfg=EngineConfig(ctx_size=256, max_seqs=2, block_size=16, prefill_chunk=64, prefix_cache=False))
+    spmd.attach(eng, rank, world, timeout_s=60)
+    eng.start()
+    if rank == 0:
+        # requests arrive only at rank 0, at different times; one is cancelled mid-way
+        a = eng.generate(GenerateRequest(prompt_tokens=_prompt(90, 1), sampling=SamplingParams(max_tokens=10, ignore_eos=True)))
+        time.sleep(0.3)
+        b = eng.generate(GenerateRequest(prompt_tokens=_prompt(90, 2), sampling=SamplingParams(max_tokens=10, ignore_eos=True)))
+        c = eng.generate(GenerateRequest(prompt_tokens=_prompt(50, 3), sampling=SamplingParams(max_tokens=200, ignore_eos=True)))
+        n = 0
+        for ev in c:
+            if ev.kind == "text":
+                n += 1
+                if n == 2:
+                    c.cancel()
+        torch.save({"tokens": [a.collect().token_ids, b.collect().token_ids], "cancelled_after": n}, out_path)
+        eng.shutdown()          # broadcasts the shutdown message
+    else:
+        spmd.follower_wait(eng)
+    dist.destroy_process_group()
+
+
+def test_lock_step_serving_over_two_ranks(tmp_path):
+    from legion_b200.engine.lm import EngineConfig, build_engine
+    from legion_b200.models.weights import random_weights
+    cfg = CFGS["gqa_moe"]()
+    eng = build_engine(cfg, weights=random_weights(cfg, "cpu", torch.float32, seed=0, std=0.05),
+                       engine_cfg=EngineConfig(ctx_size=256, max_seqs=2, block_size=16, prefill_chunk=64, prefix_cache=False))
+    want = [eng.generate_text(tokens=_prompt(90, s), max_tokens=10, ignore_eos=True).token_ids for s in (1, 2)]
+    eng.shutdown()
+    out = str(tmp_path / "serve.pt")
+    mp.spawn(_serve_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    got = torch.load(out)
+    assert got["tokens"] == want
+    assert 2 <= got["cancelled_after"] < 200
