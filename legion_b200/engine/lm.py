@@ -145,7 +145,8 @@ class LmEngine(Engine):
             self.drafter = make_drafter(c.spec, self)
         self.eos_ids = tuple(self.tok.eos_ids)
         self._graphs = None
-        if dev.type == "cuda" and c.cuda_graphs and not any(k in ("mla", "mamba2") for k in self.mcfg.layer_kinds):
+        if dev.type == "cuda" and c.cuda_graphs and not model.expert_cache \
+                and not any(k in ("mla", "mamba2") for k in self.mcfg.layer_kinds):
             from .cuda_graphs import DecodeGraphs
             self._graphs = DecodeGraphs(self)
         self.step_hook: Optional[Callable] = None    # tests observe (batch description) per step

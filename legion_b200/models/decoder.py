@@ -158,6 +158,17 @@ class Decoder:
         self.gdn_k_l = max(1, cfg.gdn_k_heads // tp)
         self.gdn_v_l = max(1, cfg.gdn_v_heads // tp)
         self.lm_head = weights.get("output", weights["tok_embd"])
+        self.expert_cache: Dict[str, object] = {}     # layer prefix -> residency.ExpertCache (offload modes)
+
+    def offload_experts(self, n_slots: int, profile: Optional[dict] = None):
+        """Moves every MoE layer's routed experts to pinned host memory behind ``n_slots`` HBM slots."""
+        from ..residency.experts import ExpertCache
+        for il in range(self.cfg.n_layer):
+            if not self.cfg.is_moe_layer(il):
+                continue
+            p = f"l{il}"
+            gu, dn = self.w.pop(f"{p}.moe.gate_up"), self.w.pop(f"{p}.moe.down")
+            self.expert_cache[p] = ExpertCache(gu, dn, n_slots, self.device, profile=(profile or {}).get(p))
 
     # ------------------------------------------------------------------ blocks
     def _attn(self, p: str, il: int, x, b: StepBatch, kv: KvCache, window: int):
@@ -285,8 +296,16 @@ class Decoder:
                 if cfg.shared_gate:
                     gate = ops.linear(x, w[f"{p}.moe.sh_gate"], out_dtype=torch.float32).reshape(-1).contiguous()
             e_lo, _ = pc.expert_range(cfg.n_expert)
-            n_ff = w[f"{p}.moe.down"].shape[2]
-            return pc.moe(x, ids, wts, w[f"{p}.moe.gate_up"], w[f"{p}.moe.down"], n_ff, cfg.ffn_act, e_lo, shared, gate,
+            cache = self.expert_cache.get(p)
+            if cache is not None:
+                # offloaded experts: make this step's experts resident, then route by slot number
+                ids = cache.prepare(ids)
+                w_gu, w_dn = cache.weights()
+                e_lo = 0
+            else:
+                w_gu, w_dn = w[f"{p}.moe.gate_up"], w[f"{p}.moe.down"]
+            n_ff = w_dn.shape[2]
+            return pc.moe(x, ids, wts, w_gu, w_dn, n_ff, cfg.ffn_act, e_lo, shared, gate,
                           residual if fuse_res else None), fuse_res
         n_ff = w[f"{p}.mlp.down"].shape[1]
         h = ops.gate_up_act(x, w[f"{p}.mlp.gate_up"], n_ff, cfg.ffn_act)

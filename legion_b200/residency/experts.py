@@ -1,0 +1,142 @@
+"""Expert residency: where routed-expert weights live and how the ones a step needs reach the GPU.
+
+Modes (``--experts``, ``src/residency/mod.rs:206-246`` in the reference):
+  device   every expert in HBM (default: 180 GB per GPU holds the benchmark models whole)
+  cache    all experts in pinned host memory, ``n_slots`` of them cached in HBM slots per layer; a step first
+           makes every expert it routes to resident (misses are copied into the coldest slots), then the
+           grouped GEMM runs over the slot tensor through a remap table expert -> slot
+  host     cache mode with the minimum number of slots (a step's experts only)
+  peer     experts sharded over the GPUs' symmetric memory; the grouped GEMM's TMA loads stream a peer's
+           expert tiles over NVLink straight into the consumer's shared-memory ring (no staging copy, no
+           cluster multicast): see ``PeerExperts``
+
+Policy: decayed routing heat per expert (``src/residency/policy.rs``); the victim of a miss is the resident
+expert with the lowest heat that the current step does not use. Hit / miss / byte counters feed the metrics.
+The host-copy backing lets the whole mechanism run on the CPU for tests, as in the reference
+(``src/residency/experts.rs:14-17``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+
+@dataclass
+class CacheStats:
+    hits: int = 0
+    misses: int = 0
+    bytes_copied: int = 0
+    steps: int = 0
+
+    @property
+    def hit_rate(self) -> float:
+        n = self.hits + self.misses
+        return self.hits / n if n else 1.0
+
+
+class ExpertCache:
+    """One MoE layer's experts behind ``n_slots`` device slots."""
+
+    def __init__(self, gate_up: torch.Tensor, down: torch.Tensor, n_slots: int, device, decay: float = 0.95,
+                 profile: Optional[List[float]] = None):
+        self.E = gate_up.shape[0]
+        self.n_slots = min(n_slots, self.E)
+        self.device = torch.device(device)
+        pin = self.device.type == "cuda"
+        self.host_gu = gate_up.detach().cpu().contiguous()
+        self.host_dn = down.detach().cpu().contiguous()
+        if pin:
+            self.host_gu, self.host_dn = self.host_gu.pin_memory(), self.host_dn.pin_memory()
+        self.slot_gu = torch.empty((self.n_slots,) + tuple(gate_up.shape[1:]), dtype=gate_up.dtype, device=self.device)
+        self.slot_dn = torch.empty((self.n_slots,) + tuple(down.shape[1:]), dtype=down.dtype, device=self.device)
+        self.slot_of = [-1] * self.E              # expert -> slot
+        self.expert_in = [-1] * self.n_slots      # slot -> expert
+        self.heat = list(profile) if profile else [0.0] * self.E
+        self.decay = decay
+        self.stats = CacheStats()
+        self.bytes_per_expert = (self.host_gu[0].numel() + self.host_dn[0].numel()) * gate_up.element_size()
+        # seed the slots with the hottest experts of the profile (or the first ones)
+        order = sorted(range(self.E), key=lambda e: -self.heat[e])[:self.n_slots]
+        for s, e in enumerate(order):
+            self._load(e, s)
+        self.stats = CacheStats()
+
+    def _load(self, e: int, s: int):
+        old = self.expert_in[s]
+        if old >= 0:
+            self.slot_of[old] = -1
+        self.slot_gu[s].copy_(self.host_gu[e], non_blocking=True)
+        self.slot_dn[s].copy_(self.host_dn[e], non_blocking=True)
+        self.slot_of[e], self.expert_in[s] = s, e
+        self.stats.bytes_copied += self.bytes_per_expert
+
+    def prepare(self, ids: torch.Tensor) -> torch.Tensor:
+        """Makes every expert in ``ids`` [T, k] resident and returns the same routing in slot numbers."""
+        need = sorted(set(ids.flatten().tolist()))
+        if len(need) > self.n_slots:
+            raise RuntimeError(f"a step routes to {len(need)} experts but the cache has {self.n_slots} slots; "
+                               "lower the batch or raise --expert-cache-gib")
+        for e in range(self.E):
+            self.heat[e] *= self.decay
+        using = set(need)
+        for e in need:
+            self.heat[e] += 1.0
+            if self.slot_of[e] >= 0:
+                self.stats.hits += 1
+                continue
+            self.stats.misses += 1
+            victims = [s for s in range(self.n_slots) if self.expert_in[s] not in using]
+            free = [s for s in victims if self.expert_in[s] < 0]
+            s = free[0] if free else min(victims, key=lambda v: self.heat[self.expert_in[v]])
+            self._load(e, s)
+        self.stats.steps += 1
+        table = torch.tensor(self.slot_of, dtype=torch.int32, device=ids.device)
+        return table[ids.long()].to(torch.int32)
+
+    def weights(self) -> Tuple[torch.Tensor, torch.Tensor]:
+        return self.slot_gu, self.slot_dn
+
+    def profile(self) -> List[float]:
+        return list(self.heat)
+
+
+def slots_for_budget(cfg, gib: float, dtype_bytes: int = 2) -> int:
+    """Slots per layer that fit ``gib`` GiB of HBM for the routed experts of all MoE layers."""
+    per_expert = 3 * cfg.hidden * cfg.expert_ff * dtype_bytes
+    n_moe = sum(1 for il in range(cfg.n_layer) if cfg.is_moe_layer(il))
+    if n_moe == 0 or per_expert == 0:
+        return 0
+    return max(cfg.top_k, int(gib * (1 << 30) / (per_expert * n_moe)))
+
+
+class PeerExperts:
+    """Experts sharded over the ranks' symmetric memory. ``views(r)`` returns rank r's shard as tensors backed
+    by the peer mapping; a grouped GEMM given such a tensor streams the weights over NVLink with plain
+    (non-multicast) TMA loads, tile by tile, overlapped with the math of the tiles before it."""
+
+    def __init__(self, gate_up_local: torch.Tensor, down_local: torch.Tensor, group, rank: int, world: int):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.rank, self.world = rank, world
+        self.per = gate_up_local.shape[0]
+        self.shape_gu, self.shape_dn = tuple(gate_up_local.shape), tuple(down_local.shape)
+        n_gu, n_dn = gate_up_local.numel(), down_local.numel()
+        self.buf = symm_mem.empty(n_gu + n_dn, dtype=gate_up_local.dtype, device=gate_up_local.device)
+        self.buf[:n_gu].copy_(gate_up_local.reshape(-1))
+        self.buf[n_gu:].copy_(down_local.reshape(-1))
+        self.handle = symm_mem.rendezvous(self.buf, group=group)
+        self._n_gu = n_gu
+        torch.cuda.synchronize()
+        import torch.distributed as dist
+        dist.barrier(group=group)
+
+    def views(self, r: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        if r == self.rank:
+            flat = self.buf
+        else:
+            flat = self.handle.get_buffer(r, (self.buf.numel(),), self.buf.dtype)
+        return flat[:self._n_gu].view(self.shape_gu), flat[self._n_gu:].view(self.shape_dn)
+
+    def expert_range(self, r: int) -> Tuple[int, int]:
+        return r * self.per, (r + 1) * self.per
