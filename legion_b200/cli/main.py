@@ -105,6 +105,10 @@ def build_engine_from_args(a, start: bool = True):
         pctx.symm = SymmComm(dist.group.WORLD, rank, world, torch.device(device), ec.max_batch_tokens, cfg.hidden)
         pctx.comm = "fused"
     model = Decoder(cfg, w, pctx, max_position=ec.ctx_size + 8)
+    if a.experts in ("cache", "host") and cfg.n_expert:
+        from ..residency.experts import slots_for_budget
+        slots = cfg.top_k * ec.max_seqs if a.experts == "host" else slots_for_budget(cfg, a.expert_cache_gib or 8.0)
+        model.offload_experts(max(slots, cfg.top_k))
     eng = LmEngine(model, tok, ec, start=start)
     logging.getLogger("legion").info("loaded %s: %s, %d layers, %.2fB parameters on %s", path, cfg.arch, cfg.n_layer,
                                      sum(t.numel() for t in w.values()) / 1e9, device)

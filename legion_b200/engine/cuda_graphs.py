@@ -21,7 +21,8 @@ BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 
 
 class _Entry:
-    __slots__ = ("graph", "B", "W", "pack_h", "pack_d", "batch", "picks", "picks_h", "logits", "n_ints")
+    __slots__ = ("graph", "B", "W", "pack_h", "pack_d", "batch", "picks", "picks_h", "logits", "n_ints", "arange",
+                 "bt_key")
 
 
 class DecodeGraphs:
@@ -57,6 +58,8 @@ class DecodeGraphs:
         off, total = self._layout(B, W)
         e = _Entry()
         e.B, e.W, e.n_ints = B, W, total
+        e.arange = torch.arange(B + 1, dtype=torch.int32)
+        e.bt_key = [None] * B
         e.pack_h = torch.zeros(total, dtype=torch.int32).pin_memory()
         e.pack_d = torch.zeros(total, dtype=torch.int32, device=dev)
 
@@ -125,15 +128,24 @@ class DecodeGraphs:
         ss = h[off["state_slots"][0]:off["state_slots"][0] + B]
         bt = h[off["block_table"][0]:off["block_table"][0] + B * e.W].view(B, e.W)
         cu = h[off["cu_q"][0]:off["cu_q"][0] + B + 1]
-        cu.copy_(torch.arange(B + 1, dtype=torch.int32))
+        cu.copy_(e.arange)
+        bs = pool.block_size
+        p0s = [p0 for _, p0, _ in rows]
+        sl[:n] = torch.tensor([s.table.blocks[p0 // bs] * bs + p0 % bs for s, p0, _ in rows], dtype=torch.int64)
+        tk[:n] = torch.tensor([s.tokens[-1] for s, _, _ in rows], dtype=torch.int32)
+        pt = torch.tensor(p0s, dtype=torch.int32)
+        ps[:n] = pt
+        cl[:n] = pt + 1
+        ss[:n] = torch.tensor([s.slot for s, _, _ in rows], dtype=torch.int32)
         for i, (s, p0, _) in enumerate(rows):
-            sl[i] = s.table.slot(pool, p0)
-            tk[i] = s.tokens[-1]
-            ps[i] = p0
-            cl[i] = p0 + 1
-            ss[i] = s.slot
-            nb = pool.blocks_for(p0 + 1)
-            bt[i, :nb] = torch.tensor(s.table.blocks[:nb], dtype=torch.int32)
+            # a sequence's block table only changes when it crosses into a new block
+            key = (id(s), len(s.table.blocks), s.table.blocks[0], s.table.blocks[-1])
+            if e.bt_key[i] != key:
+                nb = len(s.table.blocks)
+                bt[i, :nb] = torch.tensor(s.table.blocks, dtype=torch.int32)
+                e.bt_key[i] = key
+        for i in range(n, B):
+            e.bt_key[i] = None
         self._fill_padding(e, n)
         e.pack_d.copy_(e.pack_h, non_blocking=True)
         e.graph.replay()
