@@ -226,8 +226,15 @@ def main(argv=None):
         s.cancel()
     if world > 1:
         import torch.distributed as dist
+        eng.release_graphs()
+        torch.cuda.synchronize()
         dist.barrier()
+        # the JSON line is out; a teardown that blocks must not hold the launcher
+        guard = threading.Timer(20.0, lambda: os._exit(0))
+        guard.daemon = True
+        guard.start()
         dist.destroy_process_group()
+        guard.cancel()
     return 0
 
 

@@ -25,6 +25,7 @@ def peaks():
 
 
 _flush = None
+CASE = {"tokens": None, "attn": None, "gemm": None}
 
 
 def flush_l2():
@@ -34,7 +35,12 @@ def flush_l2():
     _flush.zero_()
 
 
+ITERS = {"iters": None, "warmup": None}
+
+
 def timeit(fn, iters=10, warmup=3, flush=True):
+    iters = ITERS["iters"] or iters
+    warmup = ITERS["warmup"] if ITERS["warmup"] is not None else warmup
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
@@ -55,7 +61,7 @@ def timeit(fn, iters=10, warmup=3, flush=True):
 def bench_gemm(rows):
     from legion_b200.ops import sm100
     hbm, tf, src = peaks()
-    for (T, N, K) in [(8192, 5120, 2048), (8192, 2048, 4096), (4096, 8192, 8192), (16, 5120, 2048), (16, 2048, 4096),
+    for (T, N, K) in CASE["gemm"] or [(8192, 5120, 2048), (8192, 2048, 4096), (4096, 8192, 8192), (16, 5120, 2048), (16, 2048, 4096),
                       (64, 151936, 2048), (1, 5120, 2048), (256, 17408, 5120)]:
         x = torch.randn(T, K, device="cuda").bfloat16()
         w = torch.randn(N, K, device="cuda").bfloat16()
@@ -75,7 +81,7 @@ def bench_moe(rows):
     E, k, H, F = 128, 8, 2048, 768
     wgu = (torch.randn(E, 2 * F, H, device="cuda") * 0.02).bfloat16()
     wd = (torch.randn(E, H, F, device="cuda") * 0.02).bfloat16()
-    for T in (1, 16, 64, 1024, 8192):
+    for T in (CASE["tokens"] or (1, 16, 64, 1024, 8192)):
         x = torch.randn(T, H, device="cuda").bfloat16()
         logits = torch.randn(T, E, device="cuda")
         ids, wts = sm100.router_topk(logits, k)
@@ -92,7 +98,7 @@ def bench_decode_attn(rows):
     from legion_b200.ops import sm100
     hbm, tf, src = peaks()
     Hq, Hkv, D, page = 32, 4, 128, 64
-    for B, ctx in ((1, 8192), (16, 8192), (64, 8192), (16, 1024)):
+    for B, ctx in (CASE["attn"] or ((1, 8192), (16, 8192), (64, 8192), (16, 1024))):
         nb = B * ((ctx + page - 1) // page)
         kc = torch.randn(nb, page, Hkv, D, device="cuda").bfloat16()
         vc = torch.randn(nb, page, Hkv, D, device="cuda").bfloat16()
@@ -110,7 +116,7 @@ def bench_prefill_attn(rows):
     from legion_b200.ops import sm100
     hbm, tf, src = peaks()
     Hq, Hkv, D, page = 32, 4, 128, 64
-    for n_seq, L in ((1, 8192), (4, 2048), (1, 32768)):
+    for n_seq, L in (CASE["attn"] or ((1, 8192), (4, 2048), (1, 32768))):
         nb = n_seq * (L // page)
         kc = torch.randn(nb, page, Hkv, D, device="cuda").bfloat16()
         vc = torch.randn(nb, page, Hkv, D, device="cuda").bfloat16()
@@ -129,7 +135,19 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default="gemm,moe,decode_attn,prefill_attn")
     ap.add_argument("--json", default=None)
+    ap.add_argument("--tokens", default=None, help="moe: comma list of token counts")
+    ap.add_argument("--attn", default=None, help="attention: BxCTX[,BxCTX...] (decode) or SEQSxLEN (prefill)")
+    ap.add_argument("--gemm", default=None, help="gemm: TxNxK[,TxNxK...]")
+    ap.add_argument("--iters", type=int, default=None)
+    ap.add_argument("--warmup-iters", type=int, default=None)
     a = ap.parse_args(argv)
+    ITERS["iters"], ITERS["warmup"] = a.iters, a.warmup_iters
+    if a.tokens:
+        CASE["tokens"] = tuple(int(x) for x in a.tokens.split(","))
+    if a.attn:
+        CASE["attn"] = tuple(tuple(int(y) for y in x.split("x")) for x in a.attn.split(","))
+    if a.gemm:
+        CASE["gemm"] = [tuple(int(y) for y in x.split("x")) for x in a.gemm.split(",")]
     rows = []
     table = {"gemm": bench_gemm, "moe": bench_moe, "decode_attn": bench_decode_attn, "prefill_attn": bench_prefill_attn}
     for name in a.only.split(","):

@@ -35,7 +35,8 @@ void check_bf16(const Tensor& t, const char* name) {
 void wgemm(const Tensor& w, const Tensor& x, Tensor& out, const OptT& residual, const OptT& tok_scale,
            const OptT& out_rows, int64_t n_feat, bool dual, int64_t dual_offset, int64_t bn, int64_t split_k,
            const OptT& ws, const OptT& counters, Tensor& status, const OptT& tile_group, const OptT& tile_tok0,
-           const OptT& tile_ntok, const OptT& meta, int64_t max_tiles, int64_t rows_per_group, int64_t n_tok) {
+           const OptT& tile_ntok, const OptT& meta, int64_t max_tiles, int64_t rows_per_group, int64_t n_tok,
+           std::vector<int64_t> out_peer) {
   check_bf16(w, "w");
   check_bf16(x, "x");
   TORCH_CHECK(w.dim() == 2 && x.dim() == 2 && out.dim() == 2, "wgemm expects 2-D tensors");
@@ -72,6 +73,9 @@ void wgemm(const Tensor& w, const Tensor& x, Tensor& out, const OptT& residual, 
     TORCH_CHECK(counters->numel() >= int64_t(n_tok_tiles) * feat_tiles, "wgemm: too few split-K counters");
   }
   h.status = reinterpret_cast<int*>(status.data_ptr());
+  TORCH_CHECK(out_peer.size() <= 8, "wgemm: at most 8 peer outputs");
+  h.n_out_peer = int(out_peer.size());
+  for (size_t i = 0; i < out_peer.size(); ++i) h.out_peer[i] = reinterpret_cast<void*>(out_peer[i]);
   TORCH_CHECK(lb::wgemm_launch(h, cur_stream()) == 0, lb::wgemm_last_error());
 }
 
@@ -261,6 +265,7 @@ void penalties_mask(Tensor& logits, const OptT& counts, const OptT& seen, const 
 void bind_gdn(pybind11::module_& m);
 void bind_comm(pybind11::module_& m);
 void bind_quant(pybind11::module_& m);
+void bind_ep(pybind11::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("wgemm", &wgemm);
@@ -284,4 +289,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   bind_gdn(m);
   bind_comm(m);
   bind_quant(m);
+  bind_ep(m);
 }

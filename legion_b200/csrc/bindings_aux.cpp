@@ -4,6 +4,7 @@
 #include <torch/extension.h>
 
 #include "comm.h"
+#include "ep.h"
 #include "gdn.h"
 #include "quant.h"
 
@@ -125,6 +126,64 @@ void bind_comm(pybind11::module_& m) {
                                       out.data_ptr(), out.stride(0), uint64_t(budget_ns),
                                       reinterpret_cast<int*>(status.data_ptr()), cur_stream()) == 0,
                 "all_gather_fused failed");
+  });
+}
+
+namespace {
+lb::EpPeers make_ep(const std::vector<int64_t>& buffers, const std::vector<int64_t>& signals, int64_t rank) {
+  TORCH_CHECK(buffers.size() == signals.size() && buffers.size() <= EP_MAX_RANKS, "bad EP peer table");
+  lb::EpPeers p{};
+  p.world = int(buffers.size());
+  p.rank = int(rank);
+  for (size_t i = 0; i < buffers.size(); ++i) {
+    p.buffer[i] = reinterpret_cast<void*>(buffers[i]);
+    p.signal[i] = reinterpret_cast<void*>(signals[i]);
+  }
+  return p;
+}
+}  // namespace
+
+void bind_ep(pybind11::module_& m) {
+  m.def("ep_publish_counts", [](std::vector<int64_t> buffers, std::vector<int64_t> signals, int64_t rank,
+                                const Tensor& counts, int64_t counts_off, Tensor& seq, Tensor& dest_base,
+                                Tensor& recv_counts, Tensor& meta, int64_t cap, int64_t budget_ns, Tensor& status) {
+    c10::cuda::CUDAGuard guard(counts.device());
+    auto p = make_ep(buffers, signals, rank);
+    TORCH_CHECK(lb::ep_publish_counts_launch(p, counts.data_ptr<int>(), int(counts.numel()), counts_off,
+                                             reinterpret_cast<const uint32_t*>(seq.data_ptr()),
+                                             dest_base.data_ptr<int>(), recv_counts.data_ptr<int>(),
+                                             meta.data_ptr<int>(), int(cap), uint64_t(budget_ns),
+                                             reinterpret_cast<int*>(status.data_ptr()), cur_stream()) == 0,
+                "ep_publish_counts: experts must divide by the ranks and be <= 512");
+  });
+  m.def("ep_push", [](std::vector<int64_t> buffers, std::vector<int64_t> signals, int64_t rank, const Tensor& x,
+                      const Tensor& sorted_token, const Tensor& sorted_pair, const Tensor& sorted_w,
+                      const Tensor& offsets, const Tensor& dest_base, int64_t E, int64_t cap, int64_t rx_off,
+                      int64_t rsrc_off, int64_t rw_off, Tensor& seq, Tensor& done_ctr) {
+    c10::cuda::CUDAGuard guard(x.device());
+    auto p = make_ep(buffers, signals, rank);
+    TORCH_CHECK(lb::ep_push_launch(p, x.data_ptr(), x.stride(0), int(x.size(1)), sorted_token.data_ptr<int>(),
+                                   sorted_pair.data_ptr<int>(), sorted_w.data_ptr<float>(), offsets.data_ptr<int>(),
+                                   dest_base.data_ptr<int>(), int(E), int(cap), rx_off, rsrc_off, rw_off,
+                                   reinterpret_cast<const uint32_t*>(seq.data_ptr()),
+                                   reinterpret_cast<unsigned int*>(done_ctr.data_ptr()), int(sorted_token.numel()),
+                                   cur_stream()) == 0, "ep_push failed");
+  });
+  m.def("ep_sync", [](std::vector<int64_t> buffers, std::vector<int64_t> signals, int64_t rank, int64_t slot_base,
+                      bool signal_first, Tensor& seq, bool bump, int64_t budget_ns, Tensor& status) {
+    c10::cuda::CUDAGuard guard(seq.device());
+    auto p = make_ep(buffers, signals, rank);
+    TORCH_CHECK(lb::ep_sync_launch(p, int(slot_base), signal_first ? 1 : 0,
+                                   reinterpret_cast<uint32_t*>(seq.data_ptr()), bump ? 1 : 0, uint64_t(budget_ns),
+                                   reinterpret_cast<int*>(status.data_ptr()), cur_stream()) == 0, "ep_sync failed");
+  });
+  m.def("moe_tiles", [](const Tensor& counts, int64_t bn, Tensor& offsets, Tensor& tile_group, Tensor& tile_tok0,
+                        Tensor& tile_ntok, Tensor& meta) {
+    c10::cuda::CUDAGuard guard(counts.device());
+    TORCH_CHECK(lb::moe_tiles_launch(counts.data_ptr<int>(), int(counts.numel()), int(bn), offsets.data_ptr<int>(),
+                                     tile_group.data_ptr<int>(), tile_tok0.data_ptr<int>(), tile_ntok.data_ptr<int>(),
+                                     int(tile_group.numel()), meta.data_ptr<int>(), cur_stream()) == 0,
+                "moe_tiles failed");
   });
 }
 

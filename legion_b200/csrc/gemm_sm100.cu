@@ -300,6 +300,11 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                 long orow = xrow;
                 if (a.out_rows) orow = a.out_rows[xrow];
                 if (orow >= 0) {
+                  __nv_bfloat16* obase = reinterpret_cast<__nv_bfloat16*>(a.out);
+                  if (a.n_out_peer > 0) {
+                    obase = reinterpret_cast<__nv_bfloat16*>(a.out_peer[(orow >> 24) & 7]);
+                    orow &= 0xffffff;
+                  }
                   const float4 v0 = *reinterpret_cast<const float4*>(&stage[j * BM + f8]);
                   const float4 v1 = *reinterpret_cast<const float4*>(&stage[j * BM + f8 + 4]);
                   float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
@@ -321,7 +326,7 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                   uint4 o;
                   o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
                   o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
-                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.out) + orow * a.ldo + feat8) = o;
+                  *reinterpret_cast<uint4*>(obase + orow * a.ldo + feat8) = o;
                 }
               }
             }
@@ -338,11 +343,16 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
                 long orow = xrow;
                 if (a.out_rows) orow = a.out_rows[xrow];
                 if (orow >= 0) {
+                  void* obase = a.out;
+                  if (a.n_out_peer > 0) {
+                    obase = a.out_peer[(orow >> 24) & 7];
+                    orow &= 0xffffff;
+                  }
                   if (a.residual) v += __bfloat162float(a.residual[orow * a.ldr + feat]);
                   if (OUT_F32) {
-                    reinterpret_cast<float*>(a.out)[orow * a.ldo + feat] = v;
+                    reinterpret_cast<float*>(obase)[orow * a.ldo + feat] = v;
                   } else {
-                    reinterpret_cast<__nv_bfloat16*>(a.out)[orow * a.ldo + feat] = __float2bfloat16(v);
+                    reinterpret_cast<__nv_bfloat16*>(obase)[orow * a.ldo + feat] = __float2bfloat16(v);
                   }
                 }
               }
@@ -445,6 +455,8 @@ int wgemm_launch(const WgemmHost& h, cudaStream_t stream) {
   a.rows_per_group = h.rows_per_group; a.dual_offset = h.dual_offset;
   a.split_k = h.split_k < 1 ? 1 : h.split_k;
   a.ws = h.ws; a.counters = h.counters; a.status = h.status;
+  a.n_out_peer = h.n_out_peer;
+  for (int i = 0; i < 8; ++i) a.out_peer[i] = h.out_peer[i];
   a.vec_ok = (!h.out_f32 && h.n_feat % 8 == 0 && h.ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(h.out) & 15) == 0 &&
               (!h.residual || (h.ldr % 8 == 0 && (reinterpret_cast<uintptr_t>(h.residual) & 15) == 0)))
                  ? 1 : 0;

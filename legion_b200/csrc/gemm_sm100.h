@@ -27,6 +27,8 @@ struct WgemmArgs {
   float* ws;                      // split-K partials
   int* counters;                  // split-K arrival counters, zero on entry, left zero on exit
   int* status;                    // error word (0 = ok)
+  void* out_peer[8];              // EP combine: per-rank output bases (peer-mapped); used when n_out_peer > 0,
+  int n_out_peer;                 //   out_rows[] then holds (rank << 24) | row
 };
 
 // Host-side description of one launch.
@@ -44,6 +46,7 @@ struct WgemmHost {
   int rows_per_group, dual_offset;
   int split_k; float* ws; int* counters;
   int* status;
+  void* out_peer[8]; int n_out_peer;
 };
 
 int wgemm_launch(const WgemmHost& h, cudaStream_t stream);

@@ -7,6 +7,7 @@
 // Counterparts in the reference: src/cuda/fused.cu (router_topk, router_weights, moe_combine,
 // shexp_gate), src/cuda/moe_gemm.cu (prep, plan, scatter, reduce).
 #include "common.cuh"
+#include "ep.h"
 #include "kernels.h"
 
 namespace lb {
@@ -260,6 +261,13 @@ int moe_plan_launch(const int* ids, const float* wts, int n_tokens, int k, int e
   moe_count_kernel<<<n_local, 256, 0, s>>>(ids, n_pairs, e_lo, counts);
   moe_scan_kernel<<<1, 512, 0, s>>>(counts, n_local, bn, offsets, tile_group, tile_tok0, tile_ntok, max_tiles, meta);
   moe_fill_kernel<<<n_local, 256, 0, s>>>(ids, wts, n_pairs, k, e_lo, offsets, sorted_token, sorted_pair, sorted_w);
+  return cudaGetLastError() != cudaSuccess;
+}
+
+int moe_tiles_launch(const int* counts, int n_local, int bn, int* offsets, int* tile_group, int* tile_tok0,
+                     int* tile_ntok, int max_tiles, int* meta, cudaStream_t s) {
+  if (n_local <= 0 || n_local > 512) return 1;
+  moe_scan_kernel<<<1, 512, 0, s>>>(counts, n_local, bn, offsets, tile_group, tile_tok0, tile_ntok, max_tiles, meta);
   return cudaGetLastError() != cudaSuccess;
 }
 

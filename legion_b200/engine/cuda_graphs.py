@@ -41,6 +41,14 @@ class DecodeGraphs:
                 return b
         return None
 
+    def release(self):
+        """Destroys every captured graph and its private memory pool."""
+        import gc
+        if self.entries and torch.cuda.is_available():
+            torch.cuda.synchronize(self.eng.device)
+        self.entries.clear()
+        gc.collect()
+
     def _layout(self, B: int, W: int):
         # int32 words: slots (int64 -> 2 words each) first so the int64 view is 8-byte aligned
         off = {}

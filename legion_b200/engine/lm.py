@@ -171,6 +171,13 @@ class LmEngine(Engine):
         if self._thread is not None:
             self._thread.join(timeout=30)
             self._thread = None
+        self.release_graphs()
+
+    def release_graphs(self):
+        """Drops the captured decode graphs. Graphs that captured NCCL collectives must be gone before the
+        process group is destroyed (tearing the communicator down under live graphs can block)."""
+        if self._graphs is not None:
+            self._graphs.release()
 
     def set_warming(self, on: bool):
         self._warming = on

@@ -149,7 +149,7 @@ def linear(x, w, residual=None, out=None, out_dtype=torch.bfloat16, split_k: Opt
         if need > ws.splitk.numel() or n_tt * ft > ws.counters.numel():
             sk = 1
     C.wgemm(w, x, out, residual, None, None, N, False, 0, bn, sk, ws.splitk if sk > 1 else None,
-            ws.counters if sk > 1 else None, ws.status, None, None, None, None, 0, 0, T)
+            ws.counters if sk > 1 else None, ws.status, None, None, None, None, 0, 0, T, [])
     return out
 
 
@@ -171,7 +171,7 @@ def gate_up_act(x, w_gate_up, n_ff: int, out=None, bn=None, split_k: Optional[in
         if need > ws.splitk.numel() or n_tt * ft > ws.counters.numel():
             sk = 1
     C.wgemm(w_gate_up, x, out, None, None, None, n_ff, True, n_ff, bn, sk, ws.splitk if sk > 1 else None,
-            ws.counters if sk > 1 else None, ws.status, None, None, None, None, 0, 0, T)
+            ws.counters if sk > 1 else None, ws.status, None, None, None, None, 0, 0, T, [])
     return out
 
 
@@ -307,10 +307,10 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[Moe
     C.gather_rows(x, plan.sorted_token, plan.meta[1:2], plan.x_sorted[:P])
     wgu = w_gate_up.view(E_local * 2 * n_ff, H)
     C.wgemm(wgu, plan.x_sorted, plan.h_sorted, None, None, None, n_ff, True, n_ff, bn, 1, None, None, ws.status,
-            plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta, plan.max_tiles, 2 * n_ff, 0)
+            plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta, plan.max_tiles, 2 * n_ff, 0, [])
     wd = w_down.view(E_local * H, n_ff)
     C.wgemm(wd, plan.h_sorted, plan.y_pairs, None, plan.sorted_w, plan.sorted_pair, H, False, 0, bn, 1, None, None,
-            ws.status, plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta, plan.max_tiles, H, 0)
+            ws.status, plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta, plan.max_tiles, H, 0, [])
     if out is None:
         out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
     C.moe_combine(plan.y_pairs, ids, e_lo, e_lo + E_local, shared, shared_gate, residual, out)

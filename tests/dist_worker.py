@@ -1,0 +1,164 @@
+"""Worker of the multi-GPU tests: one process per GPU, started by ``torch.distributed.run`` from
+``test_comm_gpu.py``. Usage: ``dist_worker.py <case> <out_path>``. Every stage is logged to
+``<out_path>.r<rank>.log`` and a watchdog dumps all stacks and exits if the case takes too long, so a stall shows
+where it happened instead of running into the caller's limit."""
+import datetime
+import faulthandler
+import os
+import sys
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+import torch.distributed as dist
+
+RANK = int(os.environ["RANK"])
+WORLD = int(os.environ["WORLD_SIZE"])
+CASE, OUT = sys.argv[1], sys.argv[2]
+LOG = open(f"{OUT}.r{RANK}.log", "w", buffering=1)
+T0 = time.time()
+faulthandler.enable(LOG)
+faulthandler.dump_traceback_later(int(os.environ.get("LB_TEST_WATCHDOG_S", "150")), exit=True, file=LOG)
+
+
+def say(*a):
+    print(f"[{time.time() - T0:7.2f}]", *a, file=LOG, flush=True)
+
+
+def case_comm(dev):
+    from legion_b200.ops import reference as ref
+    from legion_b200.ops import sm100
+    from legion_b200.parallel.symm import SymmComm
+    H = 512
+    comm = SymmComm(dist.group.WORLD, RANK, WORLD, dev, max_rows=2048, hidden=H, budget_ns=2_000_000_000)
+    say("communicator up")
+    torch.manual_seed(7)
+    errs = []
+    for T in (1, 16, 600, 2048):           # one-shot sizes and (world > 2) two-shot sizes
+        parts = [(torch.randn(T, H, device=dev) * 0.5).bfloat16() for _ in range(WORLD)]     # same on every rank
+        res = torch.randn(T, H, device=dev).bfloat16()
+        w = torch.rand(H, device=dev) + 0.5
+        slot = comm.next_partial(T, H)
+        slot.copy_(parts[RANK])
+        normed, summed = comm.all_reduce_add_norm(slot, res, w, 1e-6, 0.0)
+        total = sum(p.float() for p in parts) + res.float()
+        want_n, _ = ref.rmsnorm(total.bfloat16(), w, 1e-6)
+        errs.append(float((summed.float() - total).abs().max()))
+        errs.append(float((normed.float() - want_n.float()).abs().max()))
+        comm.check()
+        gathered = [torch.empty_like(summed) for _ in range(WORLD)]   # rank-order sums: same bits everywhere
+        dist.all_gather(gathered, summed)
+        assert all(torch.equal(g, gathered[0]) for g in gathered)
+        say("rows", T, "ok")
+    # GEMM epilogue writes straight into the slot, then the fused reduction
+    x = (torch.randn(24, 256, device=dev) * 0.3).bfloat16()
+    wts = [(torch.randn(H, 256, device=dev) * 0.05).bfloat16() for _ in range(WORLD)]
+    res = torch.randn(24, H, device=dev).bfloat16()
+    slot = comm.next_partial(24, H)
+    sm100.linear(x, wts[RANK], out=slot)
+    assert comm.owns(slot)
+    _, summed = comm.all_reduce_add_norm(slot, res, None, 0.0, 0.0)
+    want = sum(ref.linear(x, wt).float() for wt in wts) + res.float()
+    errs.append(float((summed.float() - want).abs().max()))
+    comm.end_step()
+    comm.check()
+    assert sm100.Workspace.get(dev).check() == 0
+    return {"errs": errs}
+
+
+def case_ep(dev):
+    from legion_b200.ops import reference as ref
+    from legion_b200.ops import sm100
+    from legion_b200.parallel.ep import EpDispatcher
+    E, k, F, H = 8, 2, 256, 512
+    ep = EpDispatcher(dist.group.WORLD, RANK, WORLD, dev, E, k, H, F, max_tokens=64, budget_ns=2_000_000_000)
+    say("dispatcher up, tile", ep.bn, "capacity", ep.cap)
+    g = torch.Generator().manual_seed(3)
+    gu_all = (torch.randn(E, 2 * F, H, generator=g) * 0.05).bfloat16()
+    dn_all = (torch.randn(E, H, F, generator=g) * 0.05).bfloat16()
+    per = E // WORLD
+    gu = gu_all[RANK * per:(RANK + 1) * per].to(dev).contiguous()
+    dn = dn_all[RANK * per:(RANK + 1) * per].to(dev).contiguous()
+    errs = []
+    for it, T in enumerate((5, 64, 33, 1)):       # every rank brings different tokens
+        gg = torch.Generator().manual_seed(100 + it * 8 + RANK)
+        x = (torch.randn(T, H, generator=gg) * 0.5).bfloat16().to(dev)
+        logits = torch.randn(T, E, generator=gg).to(dev)
+        ids, wts = sm100.router_topk(logits, k)
+        y = ep.forward(x, ids, wts, gu, dn)
+        ep.check()
+        want = ref.moe_experts(x.cpu(), ids.cpu(), wts.cpu(), gu_all, dn_all, F)
+        errs.append(float((y.cpu().float() - want.float()).abs().max()))
+        say("tokens", T, "err", errs[-1])
+    assert sm100.Workspace.get(dev).check() == 0
+    all_errs = [None] * WORLD
+    dist.all_gather_object(all_errs, errs)
+    return {"errs": [e for es in all_errs for e in es]}
+
+
+def case_engine(dev, comm_kind):
+    from legion_b200.config import ModelConfig
+    from legion_b200.engine.lm import EngineConfig, build_engine
+    from legion_b200.engine.types import GenerateRequest, SamplingParams
+    from legion_b200.models.weights import Shard, random_weights
+    from legion_b200.parallel.context import ParallelCtx
+    from legion_b200.parallel.symm import SymmComm
+    cfg = ModelConfig(arch="qwen3moe", n_layer=3, hidden=512, vocab=2048, n_head=8, n_kv_head=2, head_dim=128,
+                      n_expert=8, top_k=2, expert_ff=256)
+    full = random_weights(cfg, "cpu", torch.float32, seed=0, std=0.05)
+    full = {k: (v.bfloat16() if v.dim() > 1 else v) for k, v in full.items()}
+    w = {k: v.to(dev) for k, v in Shard(cfg, RANK, WORLD).shard_all(full).items()}
+    symm = None
+    if comm_kind == "fused":
+        symm = SymmComm(dist.group.WORLD, RANK, WORLD, dev, 1024, cfg.hidden, budget_ns=2_000_000_000)
+    pctx = ParallelCtx(RANK, WORLD, dist.group.WORLD, False, comm_kind, symm)
+    eng = build_engine(cfg, weights=w, device=str(dev), pctx=pctx, start=False,
+                       engine_cfg=EngineConfig(ctx_size=512, max_seqs=2, block_size=64, prefill_chunk=256,
+                                               prefix_cache=False))
+    say("engine built")
+    prompt = torch.randint(0, 255, (200,), generator=torch.Generator().manual_seed(1)).tolist()
+    s = eng.generate(GenerateRequest(prompt_tokens=prompt, sampling=SamplingParams(max_tokens=12, ignore_eos=True)))
+    eng._drain(block=False)
+    for i in range(100):
+        eng._admit()
+        if not eng.running and len(eng.waiting) == 0:
+            break
+        eng.step()
+        if symm is not None:
+            symm.check()
+        say("step", i)
+    toks = s.collect().token_ids
+    replays = eng._graphs.replays if eng._graphs else 0
+    eng.shutdown()          # graphs that captured NCCL collectives go before the process group does
+    return {"tokens": toks, "graph_replays": replays}
+
+
+def main():
+    torch.cuda.set_device(RANK)
+    dev = torch.device("cuda", RANK)
+    dist.init_process_group("nccl", timeout=datetime.timedelta(seconds=60), device_id=dev)
+    say("process group up")
+    if CASE == "comm":
+        res = case_comm(dev)
+    elif CASE == "ep":
+        res = case_ep(dev)
+    elif CASE in ("engine_nccl", "engine_fused"):
+        res = case_engine(dev, CASE.split("_")[1])
+    else:
+        raise SystemExit(f"unknown case {CASE}")
+    torch.cuda.synchronize()
+    if RANK == 0:
+        torch.save(res, OUT)
+    say("result saved")
+    dist.barrier()
+    say("barrier passed")
+    faulthandler.cancel_dump_traceback_later()
+    faulthandler.dump_traceback_later(20, exit=True, file=LOG)
+    dist.destroy_process_group()
+    faulthandler.cancel_dump_traceback_later()
+    say("done")
+
+
+if __name__ == "__main__":
+    main()
