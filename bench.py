@@ -91,6 +91,9 @@ def main(argv=None):
     ap.add_argument("--users", type=int, default=16)
     ap.add_argument("--prompt-len", type=int, default=8192)
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--profile-range", action="store_true",
+                    help="after the timed region, replay one decode step between cudaProfilerStart/Stop "
+                         "(for a profiler started with --profile-from-start off)")
     ap.add_argument("--layers", type=int, default=0, help="debug only: truncate the model (result marked invalid)")
     a = ap.parse_args(argv)
     if a.impl == "reference":
@@ -122,7 +125,9 @@ def main(argv=None):
     weights = random_weights(cfg, dev, torch.bfloat16, seed=0, shard=shard)
     torch.cuda.synchronize()
     load_s = time.time() - t0
-    ec = EngineConfig(ctx_size=L + W + K + 72, max_seqs=U, max_batch_tokens=8192, prefill_chunk=8192, block_size=64,
+    # early sequences already decode while the later prompts prefill: leave room for those steps too
+    gen_budget = W + K + 16 + U * ((L + 8191) // 8192 + 1)
+    ec = EngineConfig(ctx_size=L + gen_budget + 64, max_seqs=U, max_batch_tokens=8192, prefill_chunk=8192, block_size=64,
                       prefix_cache=False, device=str(dev), model_name=a.model)
     model = Decoder(cfg, weights, pctx, max_position=ec.ctx_size + 8)
     eng = LmEngine(model, ByteTokenizer(cfg.vocab), ec, start=False)
@@ -133,7 +138,7 @@ def main(argv=None):
     streams = []
     for u in range(U):
         req = GenerateRequest(prompt_tokens=prompts[u].tolist(), request_id=f"u{u}",
-                              sampling=SamplingParams(temperature=0.0, max_tokens=W + K + 8, ignore_eos=True))
+                              sampling=SamplingParams(temperature=0.0, max_tokens=gen_budget, ignore_eos=True))
         streams.append(eng.generate(req))
 
     # ---- prefill: drive the engine on this thread until every sequence decodes (device-timed)
@@ -173,6 +178,8 @@ def main(argv=None):
     h2d_per = (graphs.h2d_bytes - h2d0) / max(1, replays)
     d2h_per = (graphs.d2h_bytes - d2h0) / max(1, replays)
     assert replays == n_e2e, "decode steps did not run through the captured graph"
+    assert len(eng.running) == U and all(not s.finished for s in eng.running), \
+        "a sequence finished inside the timed region: the step no longer carries the full batch"
 
     # ---- device-timed steps: K replays of the decode-step graph with the current inputs
     entry = graphs.entries[graphs.bucket(U)]
@@ -194,6 +201,11 @@ def main(argv=None):
     pdist.barrier()
     dev_ms = pdist.all_reduce_max(ev0.elapsed_time(ev1), dev)
     clk = clocks.stop()
+    if a.profile_range:
+        torch.cuda.profiler.start()
+        entry.graph.replay()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
     status = sm100.Workspace.get(dev).check()
     comm_status = 0
     if pctx.symm is not None:

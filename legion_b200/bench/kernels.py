@@ -29,10 +29,12 @@ CASE = {"tokens": None, "attn": None, "gemm": None}
 
 
 def flush_l2():
+    """Evicts L2 by READING a buffer twice its size: the lines it leaves behind are clean, so the timed kernel
+    does not pay for write-backs of the flush itself."""
     global _flush
     if _flush is None:
-        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    _flush.zero_()
+        _flush = torch.zeros(64 << 20, dtype=torch.int32, device="cuda")
+    _flush.sum()
 
 
 ITERS = {"iters": None, "warmup": None}
@@ -56,6 +58,100 @@ def timeit(fn, iters=10, warmup=3, flush=True):
         ts.append(a.elapsed_time(b))
     ts.sort()
     return ts[len(ts) // 2]
+
+
+def timeit_graph(fn, iters=20, warmup=3):
+    """Device time of one call of ``fn`` replayed from a CUDA graph (no host launch cost in the number), L2
+    flushed before every replay."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    ts = []
+    for _ in range(ITERS["iters"] or iters):
+        flush_l2()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def bench_layer_parts(rows):
+    """The pieces of one decode step of a 30B-A3B-shaped layer (16 users, 8K context), each replayed from a CUDA
+    graph: which kernel the step time goes to."""
+    from legion_b200.ops import sm100
+    hbm, tf, src = peaks()
+    T, H, E, k, F, Hq, Hkv, D, page, ctx = 16, 2048, 128, 8, 768, 32, 4, 128, 64, 8256
+    dev = "cuda"
+    x = torch.randn(T, H, device=dev).bfloat16()
+    res = torch.randn(T, H, device=dev).bfloat16()
+    nw = torch.ones(H, device=dev)
+    w_qkv = (torch.randn((Hq + 2 * Hkv) * D, H, device=dev) * 0.02).bfloat16()
+    w_o = (torch.randn(H, Hq * D, device=dev) * 0.02).bfloat16()
+    w_r = (torch.randn(E, H, device=dev) * 0.02).bfloat16()
+    wgu = (torch.randn(E, 2 * F, H, device=dev) * 0.02).bfloat16()
+    wd = (torch.randn(E, H, F, device=dev) * 0.02).bfloat16()
+    attn_in = torch.randn(T, Hq * D, device=dev).bfloat16()
+    nb = T * ((ctx + page - 1) // page)
+    kc = torch.randn(nb, page, Hkv, D, device=dev).bfloat16()
+    vc = torch.randn(nb, page, Hkv, D, device=dev).bfloat16()
+    bt = torch.arange(nb, device=dev, dtype=torch.int32).view(T, -1)
+    q = torch.randn(T, Hq, D, device=dev).bfloat16()
+    cl = torch.full((T,), ctx, device=dev, dtype=torch.int32)
+    routing = sm100.router(x, w_r, k)
+    ids, wts = routing
+
+    def add(name, fn, byts=0):
+        ms = timeit_graph(fn)
+        rows.append(dict(kernel="layer_part", part=name, us=ms * 1e3, gbs=byts / ms / 1e6 if byts else 0.0,
+                         frac_hbm=byts / ms / 1e6 / hbm if byts else 0.0, peaks=src))
+        print(rows[-1], flush=True)
+
+    add("rmsnorm", lambda: sm100.rmsnorm(x, nw, 1e-6, residual=res))
+    add("qkv_gemm", lambda: sm100.linear(x, w_qkv), w_qkv.numel() * 2)
+    add("o_gemm", lambda: sm100.linear(attn_in, w_o, residual=res), w_o.numel() * 2)
+    kv_bytes = T * ctx * Hkv * D * 2 * 2
+    for s in (CASE["tokens"] or (4, 8, 9, 10, 12, 16, 22, 33)):
+        add(f"decode_attn_splits{s}", lambda: sm100.paged_decode(q, kc, vc, bt, cl, D ** -0.5, n_splits=s,
+                                                                   max_ctx=ctx), kv_bytes)
+    add("router_route", lambda: sm100.router(x, w_r, k), w_r.numel() * 2)
+    add("norm_router_route", lambda: sm100.router(x, w_r, k, norm=(nw, 1e-6, 0.0)), w_r.numel() * 2)
+    n_act = int(torch.unique(ids).numel())
+    add("moe_experts_dense", lambda: sm100.moe_experts(x, ids, wts, wgu, wd, F, residual=res, norm=(nw, 1e-6, 0.0),
+                                                       routing=routing), n_act * 3 * H * F * 2)
+    add("moe_experts_gather", lambda: sm100.moe_experts(x, ids, wts, wgu, wd, F, residual=res, norm=(nw, 1e-6, 0.0)),
+        n_act * 3 * H * F * 2)
+    # the MoE pieces on their own
+    C = sm100.ext()
+    ws = sm100.Workspace.get(torch.device(dev))
+    plan = sm100.MoePlan(T, k, E, 32, dev)
+    P = T * k
+    plan.x_sorted = torch.zeros(P + 32, H, dtype=torch.bfloat16, device=dev)
+    plan.h_sorted = torch.zeros(P + 32, F, dtype=torch.bfloat16, device=dev)
+    plan.y_pairs = torch.zeros(P, H, dtype=torch.bfloat16, device=dev)
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    normed = torch.empty_like(out)
+    f_plan = lambda: C.moe_plan_gather(ids, wts, 0, E, 32, plan.counts, plan.offsets, plan.sorted_token,
+                                       plan.sorted_pair, plan.sorted_w, plan.tile_group, plan.tile_tok0,
+                                       plan.tile_ntok, plan.meta, x, plan.x_sorted)
+    f_gu = lambda: C.wgemm(wgu.view(E * 2 * F, H), plan.x_sorted, plan.h_sorted, None, None, None, F, True, F, 32, 1,
+                           None, None, ws.status, plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta,
+                           plan.max_tiles, 2 * F, 0, [])
+    f_dn = lambda: C.wgemm(wd.view(E * H, F), plan.h_sorted, plan.y_pairs, None, plan.sorted_w, plan.sorted_pair, H,
+                           False, 0, 32, 1, None, None, ws.status, plan.tile_group, plan.tile_tok0, plan.tile_ntok,
+                           plan.meta, plan.max_tiles, H, 0, [])
+    f_cb = lambda: C.moe_combine(plan.y_pairs, ids, 0, E, None, None, res, out, nw, 1e-6, 0.0, normed)
+    f_plan()
+    add("moe.plan_gather", f_plan)
+    add("moe.gate_up", f_gu, n_act * 2 * H * F * 2)
+    add("moe.down", f_dn, n_act * H * F * 2)
+    add("moe.combine_norm", f_cb)
 
 
 def bench_gemm(rows):
@@ -149,7 +245,7 @@ def main(argv=None):
     if a.gemm:
         CASE["gemm"] = [tuple(int(y) for y in x.split("x")) for x in a.gemm.split(",")]
     rows = []
-    table = {"gemm": bench_gemm, "moe": bench_moe, "decode_attn": bench_decode_attn, "prefill_attn": bench_prefill_attn}
+    table = {"layer_parts": bench_layer_parts, "gemm": bench_gemm, "moe": bench_moe, "decode_attn": bench_decode_attn, "prefill_attn": bench_prefill_attn}
     for name in a.only.split(","):
         table[name](rows)
     from legion_b200.ops.sm100 import Workspace

@@ -36,7 +36,7 @@ void wgemm(const Tensor& w, const Tensor& x, Tensor& out, const OptT& residual, 
            const OptT& out_rows, int64_t n_feat, bool dual, int64_t dual_offset, int64_t bn, int64_t split_k,
            const OptT& ws, const OptT& counters, Tensor& status, const OptT& tile_group, const OptT& tile_tok0,
            const OptT& tile_ntok, const OptT& meta, int64_t max_tiles, int64_t rows_per_group, int64_t n_tok,
-           std::vector<int64_t> out_peer) {
+           std::vector<int64_t> out_peer, const OptT& tile_out0) {
   check_bf16(w, "w");
   check_bf16(x, "x");
   TORCH_CHECK(w.dim() == 2 && x.dim() == 2 && out.dim() == 2, "wgemm expects 2-D tensors");
@@ -59,6 +59,7 @@ void wgemm(const Tensor& w, const Tensor& x, Tensor& out, const OptT& residual, 
   h.bn = int(bn); h.dual = dual;
   h.tile_group = optp<int>(tile_group); h.tile_tok0 = optp<int>(tile_tok0); h.tile_ntok = optp<int>(tile_ntok);
   h.n_tiles_dev = optp<int>(meta);
+  h.tile_out0 = optp<int>(tile_out0);
   h.n_tok_tiles_max = int(max_tiles);
   h.rows_per_group = int(rows_per_group); h.dual_offset = int(dual_offset);
   h.split_k = int(split_k);
@@ -194,6 +195,32 @@ void router_topk(const Tensor& logits, const OptT& bias, int64_t k, int64_t mode
               "router_topk: unsupported (experts <= 512, k <= 32, groups <= 32)");
 }
 
+void moe_route_small(const Tensor& x, const OptT& norm_w, double eps, double w_offset, const OptT& x_normed,
+                     const Tensor& w, const OptT& bias, int64_t k, int64_t mode, bool renorm, double route_scale,
+                     int64_t n_group, int64_t topk_group, Tensor& logits, Tensor& ids, Tensor& wts, int64_t bn,
+                     Tensor& tile_group, Tensor& slot_base, Tensor& tile_ntok, Tensor& meta, Tensor& out_rows,
+                     Tensor& tok_scale, Tensor& done_ctr) {
+  check_bf16(x, "x");
+  check_bf16(w, "w");
+  const int64_t T = x.size(0), E = w.size(0);
+  TORCH_CHECK(x.size(1) == w.size(1) && x.stride(1) == 1 && w.stride(1) == 1, "moe_route_small: shape mismatch");
+  TORCH_CHECK(norm_w.has_value() == x_normed.has_value(), "moe_route_small: norm weight and output go together");
+  TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.numel() >= T * E, "moe_route_small: logits too small");
+  TORCH_CHECK(tile_group.numel() >= E && slot_base.numel() >= E && tile_ntok.numel() >= E && meta.numel() >= 2 &&
+                  out_rows.numel() >= E * bn && tok_scale.numel() >= E * bn, "moe_route_small: tables too small");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(lb::moe_route_small_launch(
+                  x.data_ptr(), x.stride(0), optp<float>(norm_w), float(eps), float(w_offset),
+                  x_normed.has_value() ? x_normed->data_ptr() : nullptr,
+                  x_normed.has_value() ? x_normed->stride(0) : 0, w.data_ptr(), w.stride(0), int(x.size(1)),
+                  logits.data_ptr<float>(), optp<float>(bias), int(E), int(k), int(mode), renorm ? 1 : 0,
+                  float(route_scale), int(n_group), int(topk_group), ids.data_ptr<int>(), wts.data_ptr<float>(),
+                  int(T), int(bn), tile_group.data_ptr<int>(), slot_base.data_ptr<int>(), tile_ntok.data_ptr<int>(),
+                  meta.data_ptr<int>(), out_rows.data_ptr<int>(), tok_scale.data_ptr<float>(),
+                  reinterpret_cast<unsigned int*>(done_ctr.data_ptr()), cur_stream()) == 0,
+              "moe_route_small: unsupported (tokens <= 64 and <= bn, pairs <= 1024, experts <= 512, k <= 32)");
+}
+
 void moe_plan(const Tensor& ids, const Tensor& wts, int64_t e_lo, int64_t n_local, int64_t bn, Tensor& counts,
               Tensor& offsets, Tensor& sorted_token, Tensor& sorted_pair, Tensor& sorted_w, Tensor& tile_group,
               Tensor& tile_tok0, Tensor& tile_ntok, Tensor& meta) {
@@ -207,6 +234,23 @@ void moe_plan(const Tensor& ids, const Tensor& wts, int64_t e_lo, int64_t n_loca
               "moe_plan failed");
 }
 
+void moe_plan_gather(const Tensor& ids, const Tensor& wts, int64_t e_lo, int64_t n_local, int64_t bn, Tensor& counts,
+                     Tensor& offsets, Tensor& sorted_token, Tensor& sorted_pair, Tensor& sorted_w, Tensor& tile_group,
+                     Tensor& tile_tok0, Tensor& tile_ntok, Tensor& meta, const Tensor& x, Tensor& x_sorted) {
+  check_bf16(x, "x");
+  check_bf16(x_sorted, "x_sorted");
+  c10::cuda::CUDAGuard guard(ids.device());
+  TORCH_CHECK(x_sorted.size(0) >= ids.numel() && x_sorted.size(1) == x.size(1), "moe_plan_gather: x_sorted too small");
+  TORCH_CHECK(lb::moe_plan_gather_small_launch(
+                  ids.data_ptr<int>(), wts.data_ptr<float>(), int(ids.size(0)), int(ids.size(1)), int(e_lo),
+                  int(n_local), int(bn), counts.data_ptr<int>(), offsets.data_ptr<int>(),
+                  sorted_token.data_ptr<int>(), sorted_pair.data_ptr<int>(), sorted_w.data_ptr<float>(),
+                  tile_group.data_ptr<int>(), tile_tok0.data_ptr<int>(), tile_ntok.data_ptr<int>(),
+                  int(tile_group.numel()), meta.data_ptr<int>(), x.data_ptr(), x.stride(0), x_sorted.data_ptr(),
+                  x_sorted.stride(0), int(x.size(1)), cur_stream()) == 0,
+              "moe_plan_gather: at most 1024 pairs and 512 local experts");
+}
+
 void gather_rows(const Tensor& src, const Tensor& rows, const Tensor& n_rows, Tensor& dst) {
   check_bf16(src, "src");
   c10::cuda::CUDAGuard guard(src.device());
@@ -216,16 +260,20 @@ void gather_rows(const Tensor& src, const Tensor& rows, const Tensor& n_rows, Te
 }
 
 void moe_combine(const Tensor& y, const Tensor& ids, int64_t e_lo, int64_t e_hi, const OptT& shared,
-                 const OptT& shared_gate, const OptT& residual, Tensor& out) {
+                 const OptT& shared_gate, const OptT& residual, Tensor& out, const OptT& norm_w, double eps,
+                 double w_offset, const OptT& norm_out) {
   check_bf16(y, "y");
   c10::cuda::CUDAGuard guard(y.device());
+  TORCH_CHECK(norm_w.has_value() == norm_out.has_value(), "moe_combine: norm weight and output go together");
   TORCH_CHECK(lb::moe_combine_launch(y.data_ptr(), y.stride(0), ids.data_ptr<int>(), int(ids.size(1)), int(e_lo),
                                      int(e_hi), shared.has_value() ? shared->data_ptr() : nullptr,
                                      shared.has_value() ? shared->stride(0) : 0, optp<float>(shared_gate),
                                      residual.has_value() ? residual->data_ptr() : nullptr,
                                      residual.has_value() ? residual->stride(0) : 0, out.data_ptr(), out.stride(0),
-                                     int(out.size(0)), int(out.size(1)), cur_stream()) == 0,
-              "moe_combine failed");
+                                     int(out.size(0)), int(out.size(1)), optp<float>(norm_w), float(eps),
+                                     float(w_offset), norm_out.has_value() ? norm_out->data_ptr() : nullptr,
+                                     norm_out.has_value() ? norm_out->stride(0) : 0, cur_stream()) == 0,
+              "moe_combine failed (hidden % 8 == 0, k <= 32)");
 }
 
 void argmax(const Tensor& logits, Tensor& pv, Tensor& pi, Tensor& out, const OptT& out_val) {
@@ -268,7 +316,12 @@ void bind_quant(pybind11::module_& m);
 void bind_ep(pybind11::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
-  m.def("wgemm", &wgemm);
+  m.def("wgemm", &wgemm, pybind11::arg("w"), pybind11::arg("x"), pybind11::arg("out"), pybind11::arg("residual"),
+        pybind11::arg("tok_scale"), pybind11::arg("out_rows"), pybind11::arg("n_feat"), pybind11::arg("dual"),
+        pybind11::arg("dual_offset"), pybind11::arg("bn"), pybind11::arg("split_k"), pybind11::arg("ws"),
+        pybind11::arg("counters"), pybind11::arg("status"), pybind11::arg("tile_group"), pybind11::arg("tile_tok0"),
+        pybind11::arg("tile_ntok"), pybind11::arg("meta"), pybind11::arg("max_tiles"), pybind11::arg("rows_per_group"),
+        pybind11::arg("n_tok"), pybind11::arg("out_peer"), pybind11::arg("tile_out0") = pybind11::none());
   m.def("rmsnorm", &rmsnorm);
   m.def("qk_norm_rope_append", &qk_norm_rope_append);
   m.def("sigmoid_gate", &sigmoid_gate);
@@ -277,7 +330,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("paged_decode", &paged_decode);
   m.def("prefill_attn", &prefill_attn);
   m.def("router_topk", &router_topk);
+  m.def("moe_route_small", &moe_route_small);
   m.def("moe_plan", &moe_plan);
+  m.def("moe_plan_gather", &moe_plan_gather);
   m.def("gather_rows", &gather_rows);
   m.def("moe_combine", &moe_combine);
   m.def("argmax", &argmax);

@@ -47,7 +47,7 @@ struct WgemmCfg {
 };
 
 struct WorkItem {
-  int group, tok0, ntok, feat0, ks, tile_id;
+  int group, tok0, out0, ntok, feat0, ks, tile_id;   // tok0: first x row; out0: first output row
 };
 
 template <int BN>
@@ -63,10 +63,12 @@ __device__ __forceinline__ bool decode_work(const WgemmArgs& a, int w, int n_tok
   if (a.tile_group) {
     it.group = a.tile_group[tt];
     it.tok0 = a.tile_tok0[tt];
+    it.out0 = a.tile_out0 ? a.tile_out0[tt] : it.tok0;
     it.ntok = a.tile_ntok[tt];
   } else {
     it.group = 0;
     it.tok0 = tt * BN;
+    it.out0 = it.tok0;
     it.ntok = min(BN, a.n_tok - it.tok0);
   }
   return true;
@@ -296,7 +298,7 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
               const int j = pass * 8 + (etid >> 4);
               const int t = c + j;
               if (t < it.ntok && feat8 < a.n_feat) {
-                const int xrow = it.tok0 + t;
+                const int xrow = it.out0 + t;
                 long orow = xrow;
                 if (a.out_rows) orow = a.out_rows[xrow];
                 if (orow >= 0) {
@@ -336,7 +338,7 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
             for (int j = 0; j < 32; ++j) {
               const int t = c + j;
               if (t < it.ntok) {
-                const int xrow = it.tok0 + t;
+                const int xrow = it.out0 + t;
                 float v = g[j];
                 if (DUAL) v = (v / (1.f + __expf(-v))) * u[j];
                 if (a.tok_scale) v *= a.tok_scale[xrow];
@@ -450,7 +452,7 @@ int wgemm_launch(const WgemmHost& h, cudaStream_t stream) {
   a.tok_scale = h.tok_scale; a.out_rows = h.out_rows;
   a.K = h.K; a.n_feat = h.n_feat; a.feat_tiles = (h.n_feat + BM - 1) / BM;
   a.n_tok = h.n_tok;
-  a.tile_group = h.tile_group; a.tile_tok0 = h.tile_tok0; a.tile_ntok = h.tile_ntok; a.n_tiles_dev = h.n_tiles_dev;
+  a.tile_group = h.tile_group; a.tile_tok0 = h.tile_tok0; a.tile_out0 = h.tile_out0; a.tile_ntok = h.tile_ntok; a.n_tiles_dev = h.n_tiles_dev;
   a.n_tok_tiles_max = h.n_tok_tiles_max;
   a.rows_per_group = h.rows_per_group; a.dual_offset = h.dual_offset;
   a.split_k = h.split_k < 1 ? 1 : h.split_k;

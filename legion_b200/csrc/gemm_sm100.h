@@ -17,6 +17,7 @@ struct WgemmArgs {
   int K, n_feat, feat_tiles, n_tok;
   const int* tile_group;          // grouped mode: expert of each token tile (nullptr = dense)
   const int* tile_tok0;           //   first activation row of the tile
+  const int* tile_out0;           //   first output row of the tile (nullptr = same as tile_tok0)
   const int* tile_ntok;           //   valid rows in the tile
   const int* n_tiles_dev;         //   number of token tiles (device scalar, data of a CUDA graph)
   int n_tok_tiles_max;
@@ -42,6 +43,7 @@ struct WgemmHost {
   int K, n_feat, n_tok;
   int bn; bool dual;
   const int* tile_group; const int* tile_tok0; const int* tile_ntok; const int* n_tiles_dev;
+  const int* tile_out0;
   int n_tok_tiles_max;
   int rows_per_group, dual_offset;
   int split_k; float* ws; int* counters;

@@ -44,6 +44,15 @@ const char* prefill_attn_last_error();
 int router_topk_launch(const float* logits, long ldl, const float* bias, int E, int k, int mode, int renorm,
                        float route_scale, int n_group, int topk_group, int* ids, float* wts, int T, cudaStream_t s);
 
+int moe_route_small_launch(const void* x, long ldx, const float* norm_w, float eps, float w_offset, void* x_normed,
+                           long ldn, const void* w, long ldw, int H, float* logits, const float* bias, int E, int k,
+                           int mode, int renorm, float route_scale, int n_group, int topk_group, int* ids, float* wts,
+                           int T, int bn, int* tile_group, int* slot_base, int* tile_ntok, int* meta, int* out_rows,
+                           float* tok_scale, unsigned int* done_ctr, cudaStream_t s);
+int moe_plan_gather_small_launch(const int* ids, const float* wts, int n_tokens, int k, int e_lo, int n_local, int bn,
+                                 int* counts, int* offsets, int* sorted_token, int* sorted_pair, float* sorted_w,
+                                 int* tile_group, int* tile_tok0, int* tile_ntok, int max_tiles, int* meta,
+                                 const void* x, long ldx, void* x_sorted, long ldxs, int H, cudaStream_t s);
 int moe_plan_launch(const int* ids, const float* wts, int n_tokens, int k, int e_lo, int n_local, int bn, int* counts,
                     int* offsets, int* sorted_token, int* sorted_pair, float* sorted_w, int* tile_group,
                     int* tile_tok0, int* tile_ntok, int max_tiles, int* meta, cudaStream_t s);
@@ -53,7 +62,7 @@ int gather_rows_launch(const void* src, long lds, const int* rows, const int* n_
 
 int moe_combine_launch(const void* y, long ldy, const int* ids, int k, int e_lo, int e_hi, const void* shared, long lds,
                        const float* shared_gate, const void* residual, long ldr, void* out, long ldo, int T, int H,
-                       cudaStream_t s);
+                       const float* norm_w, float eps, float w_offset, void* norm_out, long ldn, cudaStream_t s);
 
 int argmax_launch(const void* logits, bool is_f32, long ld, int rows, int V, float* pv, int* pi, int nblk, int* out,
                   float* out_val, cudaStream_t s);

@@ -17,20 +17,18 @@ namespace lb {
 // keep topk_group groups ranked by the sum of their two best biased scores), weights = unbiased
 // scores of the chosen experts, renormalised and multiplied by route_scale.
 template <int MAXE>
-__global__ void __launch_bounds__(128) router_topk_kernel(const float* __restrict__ logits, long ldl,
-                                                          const float* __restrict__ bias, int E, int k, int mode,
-                                                          int renorm, float route_scale, int n_group, int topk_group,
-                                                          int* __restrict__ ids, float* __restrict__ wts, int T) {
+__device__ __forceinline__ void router_topk_row(const float* logits, long ldl, const float* __restrict__ bias, int E,
+                                                int k, int mode, int renorm, float route_scale, int n_group,
+                                                int topk_group, int* __restrict__ ids, float* __restrict__ wts,
+                                                int t) {
   constexpr int PER = MAXE / 32;
   const int lane = threadIdx.x & 31;
-  const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  if (t >= T) return;
   float sc[PER], sel[PER];
   float mx = -INFINITY;
 #pragma unroll
   for (int j = 0; j < PER; ++j) {
     const int e = lane + 32 * j;
-    sc[j] = (e < E) ? logits[t * ldl + e] : -INFINITY;
+    sc[j] = (e < E) ? __ldcg(logits + t * ldl + e) : -INFINITY;   // L2 read: the row may come from other CTAs
     mx = fmaxf(mx, sc[j]);
   }
   if (mode == 0) {
@@ -138,6 +136,206 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const float* __restric
     ids[t * k + lane] = my_id;
     wts[t * k + lane] = w * route_scale;
   }
+}
+
+template <int MAXE>
+__global__ void __launch_bounds__(128) router_topk_kernel(const float* __restrict__ logits, long ldl,
+                                                          const float* __restrict__ bias, int E, int k, int mode,
+                                                          int renorm, float route_scale, int n_group, int topk_group,
+                                                          int* __restrict__ ids, float* __restrict__ wts, int T) {
+  const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (t >= T) return;
+  router_topk_row<MAXE>(logits, ldl, bias, E, k, mode, renorm, route_scale, n_group, topk_group, ids, wts, t);
+}
+
+// Decode-sized MoE front end in ONE launch (T <= 64 tokens, T * k <= 1024 pairs):
+//   (optional) RMSNorm of the residual stream -> router logits -> top-k -> dense routing tables.
+// CTA e computes expert e's logit for every token; when norm_w is given it first derives each token's inverse
+// RMS from the rows it reads anyway, and the CTAs share the job of writing the normalised rows out (row t by CTA
+// t mod grid). The last CTA to finish selects the top-k of every token and builds the DENSE routing: every
+// active expert becomes one token tile that covers ALL T tokens (the GEMMs are weight-bandwidth bound, so the
+// extra columns are free), which removes the gather: the gate/up GEMM reads the activations in place and writes
+// rows slot * bn + t, the down GEMM drops the rows whose out_rows entry is -1.
+//   tile_group[slot] = expert, slot_base[slot] = slot * bn, tile_ntok[slot] = T, meta = {n_active, n_active * bn}
+//   out_rows[slot * bn + t] = pair index t * k + c (or -1), tok_scale[slot * bn + t] = routing weight
+template <int MAXE>
+__global__ void __launch_bounds__(256) moe_route_small_kernel(
+    const __nv_bfloat16* __restrict__ x, long ldx, const float* __restrict__ norm_w, float eps, float w_offset,
+    __nv_bfloat16* __restrict__ x_normed, long ldn, const __nv_bfloat16* __restrict__ w, long ldw, int H,
+    float* logits, const float* __restrict__ bias, int E, int k, int mode, int renorm, float route_scale, int n_group,
+    int topk_group, int* ids, float* wts, int T, int bn, int* __restrict__ tile_group, int* __restrict__ slot_base,
+    int* __restrict__ tile_ntok, int* __restrict__ meta, int* __restrict__ out_rows, float* __restrict__ tok_scale,
+    unsigned int* done_ctr) {
+  __shared__ float red[8][8];
+  __shared__ float s_inv[8];
+  __shared__ int s_last;
+  __shared__ int s_ids[1024];
+  __shared__ int s_wsum[9];
+  const int e = blockIdx.x;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint4* w4 = reinterpret_cast<const uint4*>(w + long(e) * ldw);
+  const int nv = H / 8;
+  for (int t0 = 0; t0 < T; t0 += 8) {
+    if (norm_w) {
+      float ssq[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ssq[j] = 0.f;
+      for (int v = tid; v < nv; v += 256) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (t0 + j < T) {
+            const uint4 xu = reinterpret_cast<const uint4*>(x + long(t0 + j) * ldx)[v];
+            const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xu);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 xf = __bfloat1622float2(xp[i]);
+              ssq[j] += xf.x * xf.x + xf.y * xf.y;
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ssq[j] += __shfl_xor_sync(0xffffffffu, ssq[j], o);
+        if (lane == 0) red[warp][j] = ssq[j];
+      }
+      __syncthreads();
+      if (tid < 8) {
+        float tot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) tot += red[i][tid];
+        s_inv[tid] = rsqrtf(tot / float(H) + eps);
+      }
+      __syncthreads();
+    }
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int v = tid; v < nv; v += 256) {
+      const uint4 wu = w4[v];
+      const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wu);
+      float2 wf[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) wf[i] = __bfloat1622float2(wp[i]);
+      float nw[8];
+      if (norm_w) {
+        const float4 n0 = reinterpret_cast<const float4*>(norm_w)[2 * v];
+        const float4 n1 = reinterpret_cast<const float4*>(norm_w)[2 * v + 1];
+        nw[0] = n0.x + w_offset; nw[1] = n0.y + w_offset; nw[2] = n0.z + w_offset; nw[3] = n0.w + w_offset;
+        nw[4] = n1.x + w_offset; nw[5] = n1.y + w_offset; nw[6] = n1.z + w_offset; nw[7] = n1.w + w_offset;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (t0 + j < T) {
+          uint4 xu = reinterpret_cast<const uint4*>(x + long(t0 + j) * ldx)[v];
+          __nv_bfloat162* xp = reinterpret_cast<__nv_bfloat162*>(&xu);
+          if (norm_w) {
+            const float inv = s_inv[j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 xf = __bfloat1622float2(xp[i]);
+              xp[i] = __floats2bfloat162_rn(xf.x * inv * nw[2 * i], xf.y * inv * nw[2 * i + 1]);
+            }
+            if ((t0 + j) % gridDim.x == blockIdx.x) reinterpret_cast<uint4*>(x_normed + long(t0 + j) * ldn)[v] = xu;
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 xf = __bfloat1622float2(xp[i]);
+            acc[j] = fmaf(wf[i].x, xf.x, acc[j]);
+            acc[j] = fmaf(wf[i].y, xf.y, acc[j]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+      if (lane == 0) red[warp][j] = acc[j];
+    }
+    __syncthreads();
+    if (tid < 8 && t0 + tid < T) {
+      float tot = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) tot += red[i][tid];
+      logits[long(t0 + tid) * E + e] = tot;
+    }
+    __syncthreads();
+  }
+  if (tid == 0) {
+    __threadfence();
+    const unsigned int old = atomicAdd(done_ctr, 1u);
+    s_last = (old == gridDim.x - 1);
+    if (s_last) *done_ctr = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // ---- last CTA: top-k of every token (one warp per token)
+  for (int t = warp; t < T; t += 8)
+    router_topk_row<MAXE>(logits, E, bias, E, k, mode, renorm, route_scale, n_group, topk_group, ids, wts, t);
+  __syncthreads();
+  const int P = T * k;
+  for (int p = tid; p < P; p += 256) s_ids[p] = ids[p];
+  __syncthreads();
+  // ---- dense routing tables: experts in index order, one slot per active expert
+  int slot_carry = 0;
+  for (int e0 = 0; e0 < E; e0 += 256) {
+    const int ee = e0 + tid;
+    int cnt = 0;
+    if (ee < E)
+      for (int p = 0; p < P; ++p) cnt += (s_ids[p] == ee);
+    const unsigned bal = __ballot_sync(0xffffffffu, cnt > 0);
+    if (lane == 0) s_wsum[warp] = __popc(bal);
+    __syncthreads();
+    int before = slot_carry;
+    for (int i = 0; i < warp; ++i) before += s_wsum[i];
+    int total = 0;
+    for (int i = 0; i < 8; ++i) total += s_wsum[i];
+    if (cnt > 0) {
+      const int slot = before + __popc(bal & ((1u << lane) - 1));
+      tile_group[slot] = ee;
+      slot_base[slot] = slot * bn;
+      tile_ntok[slot] = T;
+      for (int t = 0; t < bn; ++t) out_rows[slot * bn + t] = -1;
+      for (int p = 0; p < P; ++p) {
+        if (s_ids[p] == ee) {
+          const int t = p / k;
+          out_rows[slot * bn + t] = p;
+          tok_scale[slot * bn + t] = wts[p];
+        }
+      }
+    }
+    slot_carry += total;
+    __syncthreads();
+  }
+  if (tid == 0) {
+    meta[0] = slot_carry;
+    meta[1] = slot_carry * bn;
+  }
+}
+
+int moe_route_small_launch(const void* x, long ldx, const float* norm_w, float eps, float w_offset, void* x_normed,
+                           long ldn, const void* w, long ldw, int H, float* logits, const float* bias, int E, int k,
+                           int mode, int renorm, float route_scale, int n_group, int topk_group, int* ids, float* wts,
+                           int T, int bn, int* tile_group, int* slot_base, int* tile_ntok, int* meta, int* out_rows,
+                           float* tok_scale, unsigned int* done_ctr, cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (k > 32 || E > 512 || n_group > 32 || H % 8 || T > 64 || T * k > 1024 || T > bn) return 1;
+  auto xb = static_cast<const __nv_bfloat16*>(x);
+  auto xn = static_cast<__nv_bfloat16*>(x_normed);
+  auto wb = static_cast<const __nv_bfloat16*>(w);
+#define LB_ROUTE(MAXE)                                                                                              \
+  moe_route_small_kernel<MAXE><<<E, 256, 0, s>>>(xb, ldx, norm_w, eps, w_offset, xn, ldn, wb, ldw, H, logits, bias, \
+                                                 E, k, mode, renorm, route_scale, n_group, topk_group, ids, wts, T, \
+                                                 bn, tile_group, slot_base, tile_ntok, meta, out_rows, tok_scale,   \
+                                                 done_ctr)
+  if (E <= 128) LB_ROUTE(128);
+  else if (E <= 256) LB_ROUTE(256);
+  else LB_ROUTE(512);
+#undef LB_ROUTE
+  return cudaGetLastError() != cudaSuccess;
 }
 
 int router_topk_launch(const float* logits, long ldl, const float* bias, int E, int k, int mode, int renorm,
@@ -264,6 +462,112 @@ int moe_plan_launch(const int* ids, const float* wts, int n_tokens, int k, int e
   return cudaGetLastError() != cudaSuccess;
 }
 
+// Decode-sized steps (at most 1024 pairs): the whole plan AND the row gather in ONE launch. Every CTA rebuilds
+// the plan in shared memory (a few hundred comparisons per thread - cheaper than three more launches and their
+// dependencies), CTA 0 publishes it, and all CTAs then copy their share of the rows into expert order. The
+// result is bit-identical to the count / scan / fill / gather sequence.
+__global__ void __launch_bounds__(512) moe_plan_gather_small_kernel(
+    const int* __restrict__ ids, const float* __restrict__ wts, int n_pairs, int k, int e_lo, int n_local, int bn,
+    int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ sorted_token,
+    int* __restrict__ sorted_pair, float* __restrict__ sorted_w, int* __restrict__ tile_group,
+    int* __restrict__ tile_tok0, int* __restrict__ tile_ntok, int max_tiles, int* __restrict__ meta,
+    const __nv_bfloat16* __restrict__ x, long ldx, __nv_bfloat16* __restrict__ x_sorted, long ldxs, int H) {
+  __shared__ int s_ids[1024], s_tok[1024], s_cnt[512], s_off[513], s_toff[513];
+  const int tid = threadIdx.x;
+  const bool pub = blockIdx.x == 0;
+  const int bn_shift = 31 - __clz(bn);   // bn is a power of two
+  for (int p = tid; p < n_pairs; p += 512) s_ids[p] = ids[p];
+  __syncthreads();
+  const int e = e_lo + tid;
+  int c = 0;
+  if (tid < n_local)
+    for (int p = 0; p < n_pairs; ++p) c += (s_ids[p] == e);
+  s_cnt[tid] = c;
+  __syncthreads();
+  // exclusive scans of the counts and of the tile counts: warp 0, 16 experts per lane + shuffle scan
+  if (tid < 32) {
+    int o = 0, to = 0;
+    const int e0 = tid * 16;
+#pragma unroll 4
+    for (int i = 0; i < 16; ++i) {
+      const int cc = (e0 + i < n_local) ? s_cnt[e0 + i] : 0;
+      o += cc;
+      to += (cc + bn - 1) >> bn_shift;
+    }
+    int io = o, ito = to;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int a = __shfl_up_sync(0xffffffffu, io, d), b = __shfl_up_sync(0xffffffffu, ito, d);
+      if (tid >= d) { io += a; ito += b; }
+    }
+    int xo = io - o, xto = ito - to;     // exclusive prefixes of this lane's 16 experts
+#pragma unroll 4
+    for (int i = 0; i < 16; ++i) {
+      if (e0 + i <= n_local) { s_off[e0 + i] = xo; s_toff[e0 + i] = xto; }
+      const int cc = (e0 + i < n_local) ? s_cnt[e0 + i] : 0;
+      xo += cc;
+      xto += (cc + bn - 1) >> bn_shift;
+    }
+    if (tid == 31) { s_off[n_local] = io; s_toff[n_local] = ito; }
+    if (pub && tid == 31) {
+      meta[0] = ito < max_tiles ? ito : max_tiles;
+      meta[1] = io;
+      offsets[n_local] = io;
+    }
+  }
+  __syncthreads();
+  if (tid < n_local) {
+    int pos = s_off[tid];
+    if (c > 0) {
+      for (int p = 0; p < n_pairs; ++p) {
+        if (s_ids[p] == e) {
+          const int t = p / k;
+          s_tok[pos] = t;
+          if (pub) {
+            sorted_token[pos] = t;
+            sorted_pair[pos] = p;
+            sorted_w[pos] = wts[p];
+          }
+          ++pos;
+        }
+      }
+    }
+    if (pub) {
+      counts[tid] = c;
+      offsets[tid] = s_off[tid];
+      const int nt = (c + bn - 1) >> bn_shift;
+      for (int i = 0; i < nt; ++i) {
+        const int ti = s_toff[tid] + i;
+        if (ti < max_tiles) {
+          tile_group[ti] = tid;
+          tile_tok0[ti] = s_off[tid] + i * bn;
+          tile_ntok[ti] = min(bn, c - i * bn);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const int n_rows = s_off[n_local];
+  for (int i = blockIdx.x; i < n_rows; i += gridDim.x) {
+    const uint4* s4 = reinterpret_cast<const uint4*>(x + long(s_tok[i]) * ldx);
+    uint4* d4 = reinterpret_cast<uint4*>(x_sorted + long(i) * ldxs);
+    for (int j = tid; j < H / 8; j += 512) d4[j] = s4[j];
+  }
+}
+
+int moe_plan_gather_small_launch(const int* ids, const float* wts, int n_tokens, int k, int e_lo, int n_local, int bn,
+                                 int* counts, int* offsets, int* sorted_token, int* sorted_pair, float* sorted_w,
+                                 int* tile_group, int* tile_tok0, int* tile_ntok, int max_tiles, int* meta,
+                                 const void* x, long ldx, void* x_sorted, long ldxs, int H, cudaStream_t s) {
+  const int n_pairs = n_tokens * k;
+  if (n_local <= 0 || n_local > 512 || n_pairs > 1024 || n_pairs <= 0 || H % 8 || (bn & (bn - 1))) return 1;
+  moe_plan_gather_small_kernel<<<n_pairs, 512, 0, s>>>(
+      ids, wts, n_pairs, k, e_lo, n_local, bn, counts, offsets, sorted_token, sorted_pair, sorted_w, tile_group,
+      tile_tok0, tile_ntok, max_tiles, meta, static_cast<const __nv_bfloat16*>(x), ldx,
+      static_cast<__nv_bfloat16*>(x_sorted), ldxs, H);
+  return cudaGetLastError() != cudaSuccess;
+}
+
 int moe_tiles_launch(const int* counts, int n_local, int bn, int* offsets, int* tile_group, int* tile_tok0,
                      int* tile_ntok, int max_tiles, int* meta, cudaStream_t s) {
   if (n_local <= 0 || n_local > 512) return 1;
@@ -294,27 +598,45 @@ int gather_rows_launch(const void* src, long lds, const int* rows, const int* n_
 
 // out[t, :] = (residual[t, :]) + sum_j y[t*k + j, :] (rows whose expert is outside [e_lo, e_hi) are skipped)
 //             + shared[t, :] * (shared_gate ? sigmoid(shared_gate[t]) : 1)
-__global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, long ldy, const int* __restrict__ ids, int k,
-                                   int e_lo, int e_hi, const __nv_bfloat16* __restrict__ shared, long lds,
-                                   const float* __restrict__ shared_gate, const __nv_bfloat16* __restrict__ residual,
-                                   long ldr, __nv_bfloat16* __restrict__ out, long ldo, int H) {
+// and, when norm_out is given, norm_out[t, :] = rmsnorm(out[t, :]) * (norm_w + w_offset): the next layer's input
+// norm rides on the combine instead of a launch of its own. One CTA per token; the k row loads of a vector are
+// issued together (the expert ids sit in shared memory) and summed in choice order, so the result is deterministic.
+__global__ void __launch_bounds__(256) moe_combine_kernel(
+    const __nv_bfloat16* __restrict__ y, long ldy, const int* __restrict__ ids, int k, int e_lo, int e_hi,
+    const __nv_bfloat16* __restrict__ shared, long lds, const float* __restrict__ shared_gate,
+    const __nv_bfloat16* __restrict__ residual, long ldr, __nv_bfloat16* __restrict__ out, long ldo, int H,
+    const float* __restrict__ norm_w, float eps, float w_offset, __nv_bfloat16* __restrict__ norm_out, long ldn) {
+  __shared__ int s_on[32];
+  __shared__ float red[8];
   const long t = blockIdx.x;
+  if (threadIdx.x < k) {
+    const int e = ids[t * k + threadIdx.x];
+    s_on[threadIdx.x] = (e >= e_lo && e < e_hi);
+  }
+  __syncthreads();
   float sg = 1.f;
   if (shared && shared_gate) sg = 1.f / (1.f + __expf(-shared_gate[t]));
-  for (int v = threadIdx.x; v < H / 8; v += blockDim.x) {
+  float ss = 0.f;
+  for (int v = threadIdx.x; v < H / 8; v += 256) {
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int c = 0; c < k; ++c) {
-      const int e = ids[t * k + c];
-      if (e < e_lo || e >= e_hi) continue;
-      const uint4 u = reinterpret_cast<const uint4*>(y + (t * k + c) * ldy)[v];
-      const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+    for (int c0 = 0; c0 < k; c0 += 4) {
+      uint4 u[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __bfloat1622float2(u2[j]);
-        acc[2 * j] += f.x;
-        acc[2 * j + 1] += f.y;
+      for (int i = 0; i < 4; ++i) {
+        u[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (c0 + i < k && s_on[c0 + i]) u[i] = reinterpret_cast<const uint4*>(y + (t * k + c0 + i) * ldy)[v];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u[i]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(u2[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
       }
     }
     if (shared) {
@@ -340,20 +662,45 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, long ldy
     uint4 o;
     __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    for (int j = 0; j < 4; ++j) {
+      o2[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      const float2 f = __bfloat1622float2(o2[j]);
+      ss += f.x * f.x + f.y * f.y;
+    }
     reinterpret_cast<uint4*>(out + t * ldo)[v] = o;
+  }
+  if (!norm_out) return;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float inv = rsqrtf(tot / float(H) + eps);
+  for (int v = threadIdx.x; v < H / 8; v += 256) {
+    uint4 u = reinterpret_cast<const uint4*>(out + t * ldo)[v];   // written by this thread above
+    __nv_bfloat162* u2 = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(u2[j]);
+      u2[j] = __floats2bfloat162_rn(f.x * inv * (norm_w[v * 8 + 2 * j] + w_offset),
+                                    f.y * inv * (norm_w[v * 8 + 2 * j + 1] + w_offset));
+    }
+    reinterpret_cast<uint4*>(norm_out + t * ldn)[v] = u;
   }
 }
 
 int moe_combine_launch(const void* y, long ldy, const int* ids, int k, int e_lo, int e_hi, const void* shared, long lds,
                        const float* shared_gate, const void* residual, long ldr, void* out, long ldo, int T, int H,
-                       cudaStream_t s) {
+                       const float* norm_w, float eps, float w_offset, void* norm_out, long ldn, cudaStream_t s) {
   if (T <= 0) return 0;
-  if (H % 8) return 1;
-  moe_combine_kernel<<<T, 128, 0, s>>>(static_cast<const __nv_bfloat16*>(y), ldy, ids, k, e_lo, e_hi,
+  if (H % 8 || k > 32) return 1;
+  moe_combine_kernel<<<T, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(y), ldy, ids, k, e_lo, e_hi,
                                        static_cast<const __nv_bfloat16*>(shared), lds, shared_gate,
                                        static_cast<const __nv_bfloat16*>(residual), ldr,
-                                       static_cast<__nv_bfloat16*>(out), ldo, H);
+                                       static_cast<__nv_bfloat16*>(out), ldo, H, norm_w, eps, w_offset,
+                                       static_cast<__nv_bfloat16*>(norm_out), ldn);
   return cudaGetLastError() != cudaSuccess;
 }
 

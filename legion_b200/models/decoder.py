@@ -280,14 +280,15 @@ class Decoder:
         yn = yz * torch.rsqrt(yz.pow(2).mean(-1, keepdim=True) + cfg.rms_eps) * w[f"{p}.ssm.norm"].float()
         return ops.linear(yn.to(x.dtype), w[f"{p}.ssm.out"])
 
-    def _ffn(self, p: str, il_moe: bool, x, residual):
-        """Returns the FFN output with the residual already added when ``residual`` is given and TP == 1."""
+    def _ffn(self, p: str, il_moe: bool, x, residual, next_norm=None):
+        """Returns (out, fused, normed). ``fused``: the residual is already added (TP == 1). ``normed``: the
+        next layer's input norm of ``out`` when ``next_norm`` was given and the MoE combine could carry it."""
         cfg, w, pc = self.cfg, self.w, self.pctx
         fuse_res = residual is not None and pc.tp == 1
         if il_moe:
-            logits = ops.linear(x, w[f"{p}.moe.router"], out_dtype=torch.float32)
-            ids, wts = ops.router_topk(logits, cfg.top_k, cfg.router_mode, cfg.norm_topk, cfg.route_scale,
-                                       w.get(f"{p}.moe.router_bias"), cfg.n_group, cfg.topk_group)
+            routing = ops.router(x, w[f"{p}.moe.router"], cfg.top_k, cfg.router_mode, cfg.norm_topk,
+                                 cfg.route_scale, w.get(f"{p}.moe.router_bias"), cfg.n_group, cfg.topk_group)
+            ids, wts = routing
             shared = gate = None
             if cfg.shared_ff > 0:
                 fs = w[f"{p}.moe.sh_down"].shape[1]
@@ -302,20 +303,30 @@ class Decoder:
                 ids = cache.prepare(ids)
                 w_gu, w_dn = cache.weights()
                 e_lo = 0
+                routing = None
             else:
                 w_gu, w_dn = w[f"{p}.moe.gate_up"], w[f"{p}.moe.down"]
             n_ff = w_dn.shape[2]
+            if fuse_res and next_norm is not None:
+                out, normed = pc.moe(x, ids, wts, w_gu, w_dn, n_ff, cfg.ffn_act, e_lo, shared, gate, residual,
+                                     norm=(next_norm, cfg.rms_eps, cfg.norm_offset), routing=routing)
+                return out, True, normed
             return pc.moe(x, ids, wts, w_gu, w_dn, n_ff, cfg.ffn_act, e_lo, shared, gate,
-                          residual if fuse_res else None), fuse_res
+                          residual if fuse_res else None, routing=routing), fuse_res, None
         n_ff = w[f"{p}.mlp.down"].shape[1]
         h = ops.gate_up_act(x, w[f"{p}.mlp.gate_up"], n_ff, cfg.ffn_act)
         return ops.linear(h, w[f"{p}.mlp.down"], residual=residual if fuse_res else None,
-                          out=pc.partial_out(h.shape[0], cfg.hidden)), fuse_res
+                          out=pc.partial_out(h.shape[0], cfg.hidden)), fuse_res, None
 
-    def _layer(self, p: str, il: int, kind: str, moe: bool, x, resid, b, kv, st):
-        """x is the (possibly rank-partial) output of the previous sub-layer, resid the residual stream."""
+    def _layer(self, p: str, il: int, kind: str, moe: bool, x, resid, b, kv, st, pre_normed=None, next_norm=None):
+        """x is the (possibly rank-partial) output of the previous sub-layer, resid the residual stream.
+        ``pre_normed``: this layer's input norm, already computed by the previous layer's combine.
+        Returns (cur, res, normed_for_next_layer or None)."""
         cfg, w, pc = self.cfg, self.w, self.pctx
-        h, resid = pc.reduce_norm(x, resid, w[f"{p}.attn_norm"], cfg.rms_eps, cfg.norm_offset)
+        if pre_normed is not None:
+            h = pre_normed
+        else:
+            h, resid = pc.reduce_norm(x, resid, w[f"{p}.attn_norm"], cfg.rms_eps, cfg.norm_offset)
         if kind in ("attn", "swa"):
             a = self._attn(p, il, h, b, kv, cfg.sliding_window if kind == "swa" else 0)
         elif kind == "gdn":
@@ -327,10 +338,10 @@ class Decoder:
         else:
             raise ValueError(kind)
         h, resid = pc.reduce_norm(a, resid, w[f"{p}.ffn_norm"], cfg.rms_eps, cfg.norm_offset)
-        f, fused = self._ffn(p, moe, h, resid)
+        f, fused, normed = self._ffn(p, moe, h, resid, next_norm)
         if fused:
-            return None, f          # residual already folded in: f is the new residual stream
-        return f, resid
+            return None, f, normed  # residual already folded in: f is the new residual stream
+        return f, resid, None
 
     # ------------------------------------------------------------------ forward
     def embed(self, token_ids):
@@ -344,8 +355,11 @@ class Decoder:
         captures: Dict[int, torch.Tensor] = {}
         cur, res = x, None
         # The stream is carried as (cur, res): hidden = cur (+ res). After the embedding res is None.
+        normed = None
         for il in range(cfg.n_layer):
-            cur, res = self._layer(f"l{il}", il, cfg.layer_kinds[il], cfg.is_moe_layer(il), cur, res, b, kv, st)
+            nxt = w[f"l{il + 1}.attn_norm"] if il + 1 < cfg.n_layer else None
+            cur, res, normed = self._layer(f"l{il}", il, cfg.layer_kinds[il], cfg.is_moe_layer(il), cur, res, b, kv,
+                                           st, normed, nxt)
             if b.capture_layers and il in b.capture_layers:
                 captures[il] = pc.full_hidden(cur, res)
         last = pc.full_hidden(cur, res)
@@ -404,7 +418,7 @@ class Decoder:
         hprev, _ = ops.rmsnorm(prev_hidden, w[f"{p}.hnorm"], cfg.rms_eps, cfg.norm_offset)
         x = ops.linear(torch.cat([e, hprev], dim=-1), w[f"{p}.eh_proj"])
         kind = "mla" if cfg.kv_lora > 0 else "attn"
-        cur, res = self._layer(f"{p}.l", cfg.n_layer + j, kind, cfg.n_expert > 0, x, None, b, kv, st)
+        cur, res, _ = self._layer(f"{p}.l", cfg.n_layer + j, kind, cfg.n_expert > 0, x, None, b, kv, st)
         last = pc.full_hidden(cur, res)
         rows = last if b.logit_rows is None else last.index_select(0, b.logit_rows)
         hidden, _ = ops.rmsnorm(rows, w[f"{p}.shared_head_norm"], cfg.rms_eps, cfg.norm_offset)

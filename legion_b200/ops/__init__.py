@@ -82,22 +82,36 @@ def router_topk(logits, k, mode="softmax", renorm=True, route_scale=1.0, bias=No
     return _ref.router_topk(logits, k, mode, renorm, route_scale, bias, n_group, topk_group)
 
 
+def router(x, w_router, k, mode="softmax", renorm=True, route_scale=1.0, bias=None, n_group=1, topk_group=1):
+    """Router projection + top-k. Returns an object that unpacks as ``ids, wts`` ([T, k] int32 / float32); on the
+    GPU it may also carry the dense routing tables of a decode-sized step (pass it on as ``routing=``)."""
+    if _cuda(x):
+        return _sm.router(x, w_router, k, mode, renorm, route_scale, bias, n_group, topk_group)
+    logits = _ref.linear(x, w_router, out_dtype=torch.float32)
+    return _ref.router_topk(logits, k, mode, renorm, route_scale, bias, n_group, topk_group)
+
+
 def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, act="silu", e_lo=0, shared=None, shared_gate=None,
-                residual=None, out=None):
-    """Routed experts (+ optional shared-expert output with sigmoid gate logits, + residual). Returns [T, H]."""
+                residual=None, out=None, norm=None, routing=None):
+    """Routed experts (+ optional shared-expert output with sigmoid gate logits, + residual). Returns [T, H];
+    with ``norm=(weight, eps, w_offset)`` returns (out, rmsnorm(out)): on the GPU the norm rides on the combine."""
     if _cuda(x):
         if act != "silu":
             raise NotImplementedError("grouped expert kernel implements SwiGLU experts")
-        return _sm.moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, None, shared, shared_gate, residual, out)
-    out = _ref.moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, act, e_lo, e_lo + w_gate_up.shape[0])
+        return _sm.moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, None, shared, shared_gate, residual, out,
+                               norm, routing if isinstance(routing, _sm.Routing) else None)
+    y = _ref.moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, act, e_lo, e_lo + w_gate_up.shape[0])
     if shared is not None:
         s = shared.float()
         if shared_gate is not None:
             s = s * torch.sigmoid(shared_gate.float())[:, None]
-        out = out + s
+        y = y + s
     if residual is not None:
-        out = out + residual.float()
-    return out.to(x.dtype)
+        y = y + residual.float()
+    y = y.to(x.dtype)
+    if norm is None:
+        return y
+    return y, _ref.rmsnorm(y, norm[0], norm[1], norm[2])[0]
 
 
 def argmax(logits):

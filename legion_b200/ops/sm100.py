@@ -8,6 +8,7 @@ The extension is required on a GPU: there is no silent fallback to eager PyTorch
 from __future__ import annotations
 
 import importlib
+import os
 import threading
 from typing import Optional
 
@@ -69,6 +70,12 @@ def have_ext() -> bool:
 
 
 NUM_SMS = 148
+
+# tuning knobs (environment: LB_TUNE="decode_waves=2,fused_plan=1,fused_router=1")
+TUNE = {"decode_waves": 2, "fused_plan": 1, "fused_router": 1, "dense_route": 1}
+for _kv in os.environ.get("LB_TUNE", "").split(","):
+    if "=" in _kv:
+        TUNE[_kv.split("=")[0].strip()] = int(_kv.split("=")[1])
 
 
 class Workspace:
@@ -208,12 +215,18 @@ def sigmoid_gate(attn, qkv, n_q, d, out=None):
     return out
 
 
-def decode_splits(batch: int, n_kv_heads: int, g_tiles: int, max_ctx: int) -> int:
-    """Flash-decoding split count: about 4 CTAs per SM, at most one split per 128 keys."""
+def decode_splits(batch: int, n_kv_heads: int, g_tiles: int, max_ctx: int, head_dim: int = 128) -> int:
+    """Flash-decoding split count. The grid is (batch x kv heads x head tiles x splits) CTAs, a split covers
+    ceil(tiles / splits) 128-key tiles, and an SM holds 1 / 2 / 4 CTAs (head dim 256 / 128 / 64: shared-memory
+    bound). One CTA is a latency-bound chain of tiles, so the grid aims at two full waves of resident CTAs and
+    never a fraction more (2.2 waves cost as much as 3); counts that would leave the last split empty are
+    rounded to the number of splits that actually get keys."""
     ctas = max(1, batch * n_kv_heads * g_tiles)
-    want = max(1, (4 * NUM_SMS + ctas - 1) // ctas)
-    cap = max(1, (max_ctx + 127) // 128)
-    return int(min(want, cap, 128))
+    slots = NUM_SMS * (1 if head_dim > 128 else (2 if head_dim > 64 else 4))
+    tiles = max(1, (max_ctx + 127) // 128)
+    s = max(1, min(tiles, 128, (TUNE["decode_waves"] * slots) // ctas))
+    per = (tiles + s - 1) // s
+    return (tiles + per - 1) // per
 
 
 def paged_decode(q, k_cache, v_cache, block_table, ctx_lens, scale, window=0, n_splits=None, max_ctx=None, out=None,
@@ -223,7 +236,7 @@ def paged_decode(q, k_cache, v_cache, block_table, ctx_lens, scale, window=0, n_
     Hkv = k_cache.shape[2]
     if n_splits is None:
         G = Hq // Hkv
-        n_splits = decode_splits(B, Hkv, (G + 15) // 16, max_ctx or block_table.shape[1] * k_cache.shape[1])
+        n_splits = decode_splits(B, Hkv, (G + 15) // 16, max_ctx or block_table.shape[1] * k_cache.shape[1], D)
     ws = Workspace.get(q.device)
     o_part = ws.buf("dec_o", (B * Hq * n_splits * D,), torch.float32)
     ml_part = ws.buf("dec_ml", (B * Hq * n_splits * 2,), torch.float32)
@@ -254,6 +267,72 @@ def router_topk(logits, k, mode="softmax", renorm=True, route_scale=1.0, bias=No
     return ids, wts
 
 
+class Routing:
+    """Router result of one step: ``ids`` / ``wts`` [T, k] and, for decode-sized steps, the dense routing tables
+    (``dense``) that let the expert GEMMs run without a gather. Unpacks as ``ids, wts = routing``."""
+    __slots__ = ("ids", "wts", "dense", "x_normed")
+
+    def __init__(self, ids, wts, dense=None, x_normed=None):
+        self.ids, self.wts, self.dense, self.x_normed = ids, wts, dense, x_normed
+
+    def __iter__(self):
+        yield self.ids
+        yield self.wts
+
+
+class DenseRoute:
+    """Device tables of the dense routing (one token tile per active expert covering all T tokens)."""
+
+    def __init__(self, E: int, bn: int, device):
+        i32 = dict(dtype=torch.int32, device=device)
+        self.E, self.bn = E, bn
+        self.tile_group = torch.zeros(E, **i32)
+        self.slot_base = torch.zeros(E, **i32)
+        self.zeros = torch.zeros(E, **i32)
+        self.tile_ntok = torch.zeros(E, **i32)
+        self.meta = torch.zeros(2, **i32)
+        self.out_rows = torch.full((E * bn,), -1, **i32)
+        self.tok_scale = torch.zeros(E * bn, dtype=torch.float32, device=device)
+        self.h_all = None
+        self.y_pairs = None
+
+
+def router(x, w_router, k, mode="softmax", renorm=True, route_scale=1.0, bias=None, n_group=1, topk_group=1,
+           norm=None):
+    """Router logits and top-k selection -> ``Routing``. Decode-sized steps (<= 64 tokens, <= 1024 pairs) run as
+    ONE launch that also builds the dense routing tables; with ``norm=(weight, eps, w_offset)`` that launch first
+    applies the RMSNorm to ``x`` (the raw residual stream) and ``Routing.x_normed`` is the normalised input.
+    Larger steps use the GEMM and the selection kernel."""
+    T, E = x.shape[0], w_router.shape[0]
+    small = T <= 64 and T * k <= 1024 and TUNE["fused_router"]
+    if not small:
+        xn = None
+        if norm is not None:
+            xn, _ = rmsnorm(x, norm[0], norm[1], norm[2])
+        logits = linear(x if xn is None else xn, w_router, out_dtype=torch.float32)
+        ids, wts = router_topk(logits, k, mode, renorm, route_scale, bias, n_group, topk_group)
+        return Routing(ids, wts, None, xn)
+    C = ext()
+    ws = Workspace.get(x.device)
+    logits = ws.buf("router_logits", (64 * 512,), torch.float32)
+    ctr = ws._cache.get("router_ctr")
+    if ctr is None:
+        ctr = torch.zeros(1, dtype=torch.int32, device=x.device)
+        ws._cache["router_ctr"] = ctr
+    bn = 32 if T <= 32 else 64
+    dr = ws._cache.get(("dense_route", E, bn))
+    if dr is None:
+        dr = DenseRoute(E, bn, x.device)
+        ws._cache[("dense_route", E, bn)] = dr
+    ids = torch.empty(T, k, dtype=torch.int32, device=x.device)
+    wts = torch.empty(T, k, dtype=torch.float32, device=x.device)
+    xn = torch.empty_like(x) if norm is not None else None
+    C.moe_route_small(x, norm[0] if norm else None, norm[1] if norm else 0.0, norm[2] if norm else 0.0, xn, w_router,
+                      bias, k, 0 if mode == "softmax" else 1, renorm, route_scale, n_group, topk_group, logits, ids, wts,
+                      bn, dr.tile_group, dr.slot_base, dr.tile_ntok, dr.meta, dr.out_rows, dr.tok_scale, ctr)
+    return Routing(ids, wts, dr, xn)
+
+
 class MoePlan:
     """Device buffers of one routing plan (sized for the largest step; reused every step)."""
 
@@ -277,16 +356,40 @@ class MoePlan:
 
 
 def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[MoePlan] = None, shared=None,
-                shared_gate=None, residual=None, out=None):
+                shared_gate=None, residual=None, out=None, norm=None, routing: Optional[Routing] = None):
     """Routed experts over the device routing plan: plan -> gather -> grouped gate/up (+SwiGLU) ->
     grouped down (x routing weight) -> combine (+ shared expert, + residual).
 
-    w_gate_up: [E_local, 2*n_ff, H]; w_down: [E_local, H, n_ff]; ids/wts: [T, k]. Returns bf16 [T, H]."""
+    w_gate_up: [E_local, 2*n_ff, H]; w_down: [E_local, H, n_ff]; ids/wts: [T, k]. Returns bf16 [T, H]; with
+    ``norm=(weight, eps, w_offset)`` the combine also applies that RMSNorm and (out, normed) is returned."""
     C = ext()
     T, H = x.shape
     k = ids.shape[1]
     E_local = w_gate_up.shape[0]
     ws = Workspace.get(x.device)
+    if (routing is not None and routing.dense is not None and routing.dense.E == E_local and e_lo == 0
+            and routing.ids is ids and TUNE["dense_route"]):
+        # decode-sized step: every active expert runs over all T tokens in place (no plan, no gather)
+        dr = routing.dense
+        P = T * k
+        if dr.h_all is None or dr.h_all.shape[1] != n_ff:
+            dr.h_all = torch.zeros(E_local * dr.bn, n_ff, dtype=torch.bfloat16, device=x.device)
+        if dr.y_pairs is None or dr.y_pairs.shape[0] < P or dr.y_pairs.shape[1] != H:
+            dr.y_pairs = torch.zeros(max(P, 64 * k), H, dtype=torch.bfloat16, device=x.device)
+        C.wgemm(w_gate_up.view(E_local * 2 * n_ff, H), x, dr.h_all, None, None, None, n_ff, True, n_ff, dr.bn, 1,
+                None, None, ws.status, dr.tile_group, dr.zeros, dr.tile_ntok, dr.meta, E_local, 2 * n_ff, 0, [],
+                dr.slot_base)
+        C.wgemm(w_down.view(E_local * H, n_ff), dr.h_all, dr.y_pairs, None, dr.tok_scale, dr.out_rows, H, False, 0,
+                dr.bn, 1, None, None, ws.status, dr.tile_group, dr.slot_base, dr.tile_ntok, dr.meta, E_local, H, 0, [])
+        if out is None:
+            out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+        y = dr.y_pairs[:P]
+        if norm is None:
+            C.moe_combine(y, ids, 0, E_local, shared, shared_gate, residual, out, None, 0.0, 0.0, None)
+            return out
+        normed = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+        C.moe_combine(y, ids, 0, E_local, shared, shared_gate, residual, out, norm[0], norm[1], norm[2], normed)
+        return out, normed
     if plan is None:
         bn = 32 if T * k <= 32 * E_local else (64 if T * k <= 64 * E_local else 128)
         key = ("moe_plan", T, k, E_local, bn, H, n_ff)
@@ -302,9 +405,15 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[Moe
         plan.x_sorted = torch.zeros(P + bn, H, dtype=torch.bfloat16, device=x.device)
         plan.h_sorted = torch.zeros(P + bn, n_ff, dtype=torch.bfloat16, device=x.device)
         plan.y_pairs = torch.zeros(P, H, dtype=torch.bfloat16, device=x.device)
-    C.moe_plan(ids, wts, e_lo, E_local, bn, plan.counts, plan.offsets, plan.sorted_token, plan.sorted_pair,
-               plan.sorted_w, plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta)
-    C.gather_rows(x, plan.sorted_token, plan.meta[1:2], plan.x_sorted[:P])
+    if P <= 1024 and E_local <= 512 and TUNE["fused_plan"]:
+        # decode-sized step: plan and gather in one launch
+        C.moe_plan_gather(ids, wts, e_lo, E_local, bn, plan.counts, plan.offsets, plan.sorted_token,
+                          plan.sorted_pair, plan.sorted_w, plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta,
+                          x, plan.x_sorted)
+    else:
+        C.moe_plan(ids, wts, e_lo, E_local, bn, plan.counts, plan.offsets, plan.sorted_token, plan.sorted_pair,
+                   plan.sorted_w, plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta)
+        C.gather_rows(x, plan.sorted_token, plan.meta[1:2], plan.x_sorted[:P])
     wgu = w_gate_up.view(E_local * 2 * n_ff, H)
     C.wgemm(wgu, plan.x_sorted, plan.h_sorted, None, None, None, n_ff, True, n_ff, bn, 1, None, None, ws.status,
             plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta, plan.max_tiles, 2 * n_ff, 0, [])
@@ -313,8 +422,13 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[Moe
             ws.status, plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta, plan.max_tiles, H, 0, [])
     if out is None:
         out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
-    C.moe_combine(plan.y_pairs, ids, e_lo, e_lo + E_local, shared, shared_gate, residual, out)
-    return out
+    if norm is None:
+        C.moe_combine(plan.y_pairs, ids, e_lo, e_lo + E_local, shared, shared_gate, residual, out, None, 0.0, 0.0, None)
+        return out
+    normed = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+    C.moe_combine(plan.y_pairs, ids, e_lo, e_lo + E_local, shared, shared_gate, residual, out, norm[0], norm[1],
+                  norm[2], normed)
+    return out, normed
 
 
 def argmax(logits, out=None):

@@ -97,8 +97,9 @@ class ParallelCtx:
             cur = self.all_reduce(cur)
         return (cur.float() + res.float()).to(res.dtype)
 
-    def moe(self, x, ids, wts, w_gate_up, w_down, n_ff, act, e_lo, shared, shared_gate, residual):
+    def moe(self, x, ids, wts, w_gate_up, w_down, n_ff, act, e_lo, shared, shared_gate, residual, norm=None, routing=None):
         """Routed experts of this rank: all experts with their FFN rows split (TP) or whole local
         experts (EP). Either way the result is a partial sum that the next ``reduce_norm`` completes."""
         return ops.moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, act, e_lo, shared, shared_gate, residual,
-                               out=self.partial_out(x.shape[0], x.shape[1]) if x.is_cuda else None)
+                               out=self.partial_out(x.shape[0], x.shape[1]) if x.is_cuda else None, norm=norm,
+                               routing=routing)

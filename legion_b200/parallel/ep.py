@@ -120,7 +120,7 @@ class EpDispatcher:
         C.ep_sync(*peers, 48, True, self.seq, True, self.budget_ns, self.status)            # all results landed
         if out is None:
             out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
-        C.moe_combine(self.y_pairs[:P], ids, 0, self.E, shared, shared_gate, residual, out)
+        C.moe_combine(self.y_pairs[:P], ids, 0, self.E, shared, shared_gate, residual, out, None, 0.0, 0.0, None)
         return out
 
     def check(self):

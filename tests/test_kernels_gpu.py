@@ -92,6 +92,97 @@ def test_moe_experts(T, E, k, H, F):
     assert torch.equal(out, out2)
 
 
+@pytest.mark.parametrize("T,E,k,e_lo,n_local", [(1, 128, 8, 0, 128), (16, 128, 8, 0, 128), (100, 64, 6, 16, 32),
+                                                  (128, 8, 8, 0, 8)])
+def test_moe_plan_fused_equals_three_pass(T, E, k, e_lo, n_local):
+    """The single-launch plan + gather of decode-sized steps gives the same plan and rows as count/scan/fill/gather."""
+    from legion_b200.ops.sm100 import MoePlan, ext
+    C = ext()
+    H, bn = 256, 32
+    x = rnd(T, H)
+    ids, wts = sm().router_topk(torch.randn(T, E, device=DEV), k)
+    a, b = MoePlan(T, k, n_local, bn, DEV), MoePlan(T, k, n_local, bn, DEV)
+    xa = torch.zeros(T * k + bn, H, dtype=torch.bfloat16, device=DEV)
+    xb = torch.zeros_like(xa)
+    C.moe_plan(ids, wts, e_lo, n_local, bn, a.counts, a.offsets, a.sorted_token, a.sorted_pair, a.sorted_w,
+               a.tile_group, a.tile_tok0, a.tile_ntok, a.meta)
+    C.gather_rows(x, a.sorted_token, a.meta[1:2], xa[:T * k])
+    C.moe_plan_gather(ids, wts, e_lo, n_local, bn, b.counts, b.offsets, b.sorted_token, b.sorted_pair, b.sorted_w,
+                      b.tile_group, b.tile_tok0, b.tile_ntok, b.meta, x, xb)
+    n_tiles, n_rows = a.meta.tolist()
+    assert b.meta.tolist() == [n_tiles, n_rows]
+    assert torch.equal(a.counts, b.counts) and torch.equal(a.offsets, b.offsets)
+    for name in ("sorted_token", "sorted_pair", "sorted_w"):
+        assert torch.equal(getattr(a, name)[:n_rows], getattr(b, name)[:n_rows]), name
+    for name in ("tile_group", "tile_tok0", "tile_ntok"):
+        assert torch.equal(getattr(a, name)[:n_tiles], getattr(b, name)[:n_tiles]), name
+    assert torch.equal(xa, xb)
+
+
+@pytest.mark.parametrize("T,E,k,H,mode", [(1, 128, 8, 2048, "softmax"), (16, 128, 8, 2048, "softmax"),
+                                          (37, 256, 8, 512, "sigmoid"), (64, 8, 2, 256, "softmax")])
+def test_router_fused(T, E, k, H, mode):
+    """One-launch router (logits + top-k) against fp32 logits and the reference selection."""
+    torch.manual_seed(T + E)
+    x, w = rnd(T, H), rnd(E, H, scale=H ** -0.5)
+    bias = torch.randn(E, device=DEV) * 0.05 if mode == "sigmoid" else None
+    kw = dict(mode=mode, renorm=True, route_scale=1.5, bias=bias)
+    if mode == "sigmoid":
+        kw.update(n_group=8, topk_group=4)
+    for _ in range(2):      # the done counter must be left ready for the next call
+        routing = sm().router(x, w, k, **kw)
+    ids, wts = routing
+    assert routing.dense is not None
+    logits = x.float() @ w.float().t()
+    rids, rwts = ref.router_topk(logits, k, **kw)
+    # near-ties may swap under a different summation order: compare as sets through the gathered logits
+    same = (ids.cpu().sort(1).values == rids.cpu().sort(1).values).all(1)
+    assert same.float().mean() >= 0.95
+    rows = same.nonzero().flatten()
+    o1, o2 = ids.cpu()[rows].sort(1).indices, rids.cpu()[rows].sort(1).indices
+    close(wts.cpu()[rows].gather(1, o1), rwts.cpu()[rows].gather(1, o2), 2e-3, 1e-4)
+
+
+@pytest.mark.parametrize("T,E,k,H,F", [(1, 128, 8, 512, 256), (16, 128, 8, 2048, 768), (33, 16, 4, 256, 192),
+                                       (64, 8, 2, 256, 128)])
+def test_moe_dense_route(T, E, k, H, F):
+    """Decode-sized path: norm + router + top-k + dense tables in one launch, expert GEMMs without a gather."""
+    torch.manual_seed(T * 3 + E)
+    hidden, res = rnd(T, H), rnd(T, H)
+    nw = torch.rand(H, device=DEV) + 0.5
+    w_r = rnd(E, H, scale=H ** -0.5)
+    wgu, wd = rnd(E, 2 * F, H, scale=H ** -0.5), rnd(E, H, F, scale=F ** -0.5)
+    r = sm().router(hidden, w_r, k, norm=(nw, 1e-6, 0.0))
+    want_x, _ = ref.rmsnorm(hidden, nw, 1e-6, 0.0)
+    close(r.x_normed, want_x, 1e-2, 1e-2)
+    x = r.x_normed
+    out = sm().moe_experts(x, r.ids, r.wts, wgu, wd, F, residual=res, routing=r)
+    status_ok()
+    want = ref.moe_experts(x, r.ids, r.wts, wgu, wd, F) + res.float()
+    close(out, want, 3e-2, 3e-2)
+    plan_path = sm().moe_experts(x, r.ids, r.wts, wgu, wd, F, residual=res)       # gather path, same routing
+    close(out, plan_path, 1e-2, 1e-2)
+    n_act = int(torch.unique(r.ids).numel())
+    assert r.dense.meta.tolist() == [n_act, n_act * r.dense.bn]
+    out2 = sm().moe_experts(x, r.ids, r.wts, wgu, wd, F, residual=res, routing=r)
+    assert torch.equal(out, out2)
+
+
+def test_moe_combine_with_norm():
+    T, E, k, H, F = 16, 32, 4, 512, 128
+    x = rnd(T, H)
+    ids, wts = sm().router_topk(torch.randn(T, E, device=DEV), k)
+    wgu, wd = rnd(E, 2 * F, H, scale=H ** -0.5), rnd(E, H, F, scale=F ** -0.5)
+    res = rnd(T, H)
+    nw = torch.rand(H, device=DEV) + 0.5
+    out, normed = sm().moe_experts(x, ids, wts, wgu, wd, F, residual=res, norm=(nw, 1e-6, 0.0))
+    plain = sm().moe_experts(x, ids, wts, wgu, wd, F, residual=res)
+    status_ok()
+    assert torch.equal(out, plain)
+    want, _ = ref.rmsnorm(out, nw, 1e-6, 0.0)
+    close(normed, want, 2e-2, 2e-2)
+
+
 def test_router_group_limited():
     T, E = 37, 256
     logits = torch.randn(T, E, device=DEV)
