@@ -139,20 +139,21 @@ void embed(const Tensor& ids, const Tensor& table, Tensor& out) {
 
 void paged_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_table,
                   const Tensor& ctx_lens, double scale, int64_t window, int64_t n_splits, Tensor& o_part,
-                  Tensor& ml_part, Tensor& out, bool use_tc, Tensor& status) {
+                  Tensor& ml_part, Tensor& out, bool use_tc, Tensor& status, Tensor& counters) {
   check_bf16(q, "q");
   c10::cuda::CUDAGuard guard(q.device());
   const int B = int(q.size(0)), Hq = int(q.size(1)), D = int(q.size(2));
   const int page = int(k_cache.size(-3)), Hkv = int(k_cache.size(-2));
   TORCH_CHECK(o_part.numel() >= int64_t(B) * Hq * n_splits * D && ml_part.numel() >= int64_t(B) * Hq * n_splits * 2,
               "paged_decode: partial buffers too small");
-  if (use_tc && k_cache.is_contiguous() && v_cache.is_contiguous() && q.is_contiguous()) {
+  if (use_tc && k_cache.is_contiguous() && v_cache.is_contiguous() && q.is_contiguous() && out.is_contiguous()) {
     const long n_cells = k_cache.numel() / (long(Hkv) * D);
     const int rc = lb::paged_decode_tc_launch(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), n_cells,
                                               long(Hkv) * D, block_table.data_ptr<int>(), int(block_table.size(1)),
                                               page, ctx_lens.data_ptr<int>(), float(scale), int(window), B, Hq, Hkv,
                                               D, int(n_splits), o_part.data_ptr<float>(), ml_part.data_ptr<float>(),
-                                              out.data_ptr(), reinterpret_cast<int*>(status.data_ptr()), cur_stream());
+                                              out.data_ptr(), counters.data_ptr<int>(), int(counters.numel()),
+                                              reinterpret_cast<int*>(status.data_ptr()), cur_stream());
     TORCH_CHECK(rc <= 0, lb::paged_decode_tc_last_error());
     if (rc == 0) return;
   }

@@ -32,7 +32,7 @@ int attn_combine_launch(const float* o_part, const float* ml_part, int n_splits,
 int paged_decode_tc_launch(const void* q, const void* k_cache, const void* v_cache, long n_cells, long cell_stride,
                            const int* block_table, int table_width, int page, const int* ctx_lens, float scale,
                            int window, int B, int Hq, int Hkv, int D, int n_splits, float* o_part, float* ml_part,
-                           void* out, int* status, cudaStream_t s);
+                           void* out, int* group_ctr, int n_group_ctr, int* status, cudaStream_t s);
 const char* paged_decode_tc_last_error();
 
 int prefill_attn_launch(const void* q, long T, const void* k_cache, const void* v_cache, long n_cells,

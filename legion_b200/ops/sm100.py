@@ -20,7 +20,7 @@ _lock = threading.Lock()
 
 
 # kernels launched by one call of each binding (for the launch counter)
-KERNELS_PER_CALL = {"moe_plan": 3, "paged_decode": 2, "argmax": 2, "wgemm_workspace_floats": 0}
+KERNELS_PER_CALL = {"moe_plan": 3, "paged_decode": 1, "argmax": 2, "wgemm_workspace_floats": 0}
 LAUNCHES = {"n": 0}
 
 
@@ -71,8 +71,8 @@ def have_ext() -> bool:
 
 NUM_SMS = 148
 
-# tuning knobs (environment: LB_TUNE="decode_waves=2,fused_plan=1,fused_router=1")
-TUNE = {"decode_waves": 2, "fused_plan": 1, "fused_router": 1, "dense_route": 1}
+# tuning knobs (environment: LB_TUNE="decode_fixed_tiles=2,dense_route=1")
+TUNE = {"decode_fixed_tiles": 2, "fused_plan": 1, "fused_router": 1, "dense_route": 1}
 for _kv in os.environ.get("LB_TUNE", "").split(","):
     if "=" in _kv:
         TUNE[_kv.split("=")[0].strip()] = int(_kv.split("=")[1])
@@ -216,17 +216,24 @@ def sigmoid_gate(attn, qkv, n_q, d, out=None):
 
 
 def decode_splits(batch: int, n_kv_heads: int, g_tiles: int, max_ctx: int, head_dim: int = 128) -> int:
-    """Flash-decoding split count. The grid is (batch x kv heads x head tiles x splits) CTAs, a split covers
-    ceil(tiles / splits) 128-key tiles, and an SM holds 1 / 2 / 4 CTAs (head dim 256 / 128 / 64: shared-memory
-    bound). One CTA is a latency-bound chain of tiles, so the grid aims at two full waves of resident CTAs and
-    never a fraction more (2.2 waves cost as much as 3); counts that would leave the last split empty are
-    rounded to the number of splits that actually get keys."""
+    """Flash-decoding split count. The grid is (batch x kv heads x head tiles x splits) CTAs, one resident per SM
+    (its K/V rings take most of the shared memory), and a split covers ceil(tiles / splits) 128-key tiles. The
+    count minimises waves x (tiles per split + fixed cost per CTA): 2.2 waves cost as much as 3, and a count
+    that leaves the last split empty only adds idle CTAs."""
     ctas = max(1, batch * n_kv_heads * g_tiles)
-    slots = NUM_SMS * (1 if head_dim > 128 else (2 if head_dim > 64 else 4))
+    slots = NUM_SMS
     tiles = max(1, (max_ctx + 127) // 128)
-    s = max(1, min(tiles, 128, (TUNE["decode_waves"] * slots) // ctas))
-    per = (tiles + s - 1) // s
-    return (tiles + per - 1) // per
+    fixed = TUNE["decode_fixed_tiles"]
+    best, best_cost = 1, None
+    for s in range(1, min(128, tiles) + 1):
+        per = (tiles + s - 1) // s
+        if (tiles + per - 1) // per != s:
+            continue
+        waves = (ctas * s + slots - 1) // slots
+        cost = waves * (per + fixed)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = s, cost
+    return best
 
 
 def paged_decode(q, k_cache, v_cache, block_table, ctx_lens, scale, window=0, n_splits=None, max_ctx=None, out=None,
@@ -243,7 +250,7 @@ def paged_decode(q, k_cache, v_cache, block_table, ctx_lens, scale, window=0, n_
     if out is None:
         out = torch.empty_like(q)
     C.paged_decode(q, k_cache, v_cache, block_table, ctx_lens, scale, window, n_splits, o_part, ml_part, out,
-                   impl == "tc", ws.status)
+                   impl == "tc", ws.status, ws.counters)
     return out
 
 
