@@ -154,6 +154,26 @@ def bench_layer_parts(rows):
     add("moe.combine_norm", f_cb)
 
 
+def bench_decode_pages(rows):
+    """Decode attention at 16 x 8K context for several KV page sizes and head groupings (graph-replayed)."""
+    from legion_b200.ops import sm100
+    hbm, tf, src = peaks()
+    B, D, ctx = 16, 128, 8256
+    for (Hq, Hkv, page, splits) in ((32, 4, 32, 2), (32, 4, 64, 2), (32, 4, 128, 2), (32, 8, 64, 1), (64, 4, 64, 2),
+                                    (32, 4, 64, 1), (32, 4, 128, 1)):
+        nb = B * ((ctx + page - 1) // page)
+        kc = torch.randn(nb, page, Hkv, D, device="cuda").bfloat16()
+        vc = torch.randn(nb, page, Hkv, D, device="cuda").bfloat16()
+        bt = torch.arange(nb, device="cuda", dtype=torch.int32).view(B, -1)
+        q = torch.randn(B, Hq, D, device="cuda").bfloat16()
+        cl = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
+        ms = timeit_graph(lambda: sm100.paged_decode(q, kc, vc, bt, cl, D ** -0.5, n_splits=splits, max_ctx=ctx))
+        byts = B * ctx * Hkv * D * 2 * 2
+        rows.append(dict(kernel="paged_decode", Hq=Hq, Hkv=Hkv, page=page, splits=splits, us=ms * 1e3,
+                         gbs=byts / ms / 1e6, frac_hbm=byts / ms / 1e6 / hbm, peaks=src))
+        print(rows[-1], flush=True)
+
+
 def bench_gemm(rows):
     from legion_b200.ops import sm100
     hbm, tf, src = peaks()
@@ -245,7 +265,7 @@ def main(argv=None):
     if a.gemm:
         CASE["gemm"] = [tuple(int(y) for y in x.split("x")) for x in a.gemm.split(",")]
     rows = []
-    table = {"layer_parts": bench_layer_parts, "gemm": bench_gemm, "moe": bench_moe, "decode_attn": bench_decode_attn, "prefill_attn": bench_prefill_attn}
+    table = {"layer_parts": bench_layer_parts, "decode_pages": bench_decode_pages, "gemm": bench_gemm, "moe": bench_moe, "decode_attn": bench_decode_attn, "prefill_attn": bench_prefill_attn}
     for name in a.only.split(","):
         table[name](rows)
     from legion_b200.ops.sm100 import Workspace

@@ -9,13 +9,15 @@
 // O^T). Column maxima over the 128 keys use redux.sync on order-preserving integer images of the
 // scores, row sums stay thread-local until the end, O^T is rescaled in TMEM only when a maximum grew
 // by more than 2^8 (probabilities are taken relative to a slightly stale maximum otherwise).
-// Warp 4, one lane: both MMAs. S^T has two TMEM buffers and P two shared-memory buffers, so the scores of
-// tile i+1 are on the tensor core while the softmax of tile i runs, and the PV product of tile i overlaps the
-// softmax of tile i+1. Warp 5, one lane: TMA loads of K and V pages through the block table into rings of
-// 3 + 3 stages (head dim 128), released by tcgen05.commit as soon as the MMAs have read them.
-// One CTA per SM streams up to 192 KB of K/V at a time. The splits of a (sequence, kv head) group count
-// themselves in when their partials are visible and the last one merges them into the output, so there is no
-// combine launch. Split count is a launch constant, lengths and tables are data.
+// Two softmax warpgroups (warps 0..3 and 4..7) take alternate tiles; each is an independent flash-decoding
+// stream with its own S^T buffer, P buffer, O^T accumulator, reference maxima and row sums, so the two
+// per-tile dependency chains (TMEM load -> exponentials -> P -> barrier) run side by side and share only the
+// K/V rings. Warp 8, one lane: both MMAs (scores two tiles ahead of the softmax that consumes them).
+// Warp 9: TMA loads of K and V pages through the block table into rings of 3 + 3 stages (head dim 128),
+// released by tcgen05.commit as soon as the MMAs have read them. One CTA per SM streams up to 192 KB of K/V at
+// a time. Every warpgroup of every split writes one partial (2 x splits per head); the splits of a (sequence,
+// kv head) group count themselves in when their partials are visible and the last one merges them into the
+// output, so there is no combine launch. Split count is a launch constant, lengths and tables are data.
 //
 // Counterpart in the reference: src/cuda/paged_attn/common.cuh (paged_decode, paged_combine).
 #include "common.cuh"
@@ -47,8 +49,8 @@ struct DecodeTcArgs {
   int Hq, Hkv, n_splits;
   float scale_log2;
   int window;
-  float* o_part;   // [B, Hq, n_splits, D]
-  float* ml_part;  // [B, Hq, n_splits, 2] (reference maximum in natural-log units, sum)
+  float* o_part;   // [B, Hq, 2 * n_splits, D]   (part = split * 2 + warpgroup)
+  float* ml_part;  // [B, Hq, 2 * n_splits, 2] (reference maximum in natural-log units, sum)
   __nv_bfloat16* out;   // [B, Hq, D]
   int* group_ctr;  // [B * gridDim.x] arrival counters of the splits, zero on entry, left zero on exit
   int* status;
@@ -65,9 +67,9 @@ struct DecodeTcCfg {
   static constexpr int K_STAGES = D <= 64 ? 4 : (D <= 128 ? 3 : 2);
   static constexpr int V_STAGES = D <= 64 ? 4 : (D <= 128 ? 3 : 1);
   static constexpr int MT = D <= 128 ? 1 : D / 128;        // 128-row M tiles of O^T
-  static constexpr int TMEM_COLS = 64;                     // S x 2 (16 columns each) + O (MT x 16)
-  static constexpr int SMEM = (K_STAGES + V_STAGES) * KV_BYTES + Q_BYTES + 2 * P_BYTES + 1024 + 1280;
-  static_assert(2 * NQ + MT * NQ <= TMEM_COLS, "accumulators do not fit the TMEM allocation");
+  static constexpr int TMEM_COLS = (2 * NQ + 2 * MT * NQ <= 64) ? 64 : 128;   // S x 2 + O x 2 (MT x 16 each)
+  static constexpr int SMEM = (K_STAGES + V_STAGES) * KV_BYTES + Q_BYTES + 2 * P_BYTES + 1024 + 1536;
+  static_assert(2 * NQ + 2 * MT * NQ <= TMEM_COLS, "accumulators do not fit the TMEM allocation");
   static_assert(SMEM <= 227 * 1024, "shared memory budget");
 };
 
@@ -77,7 +79,7 @@ struct DecodeTcCfg {
 static constexpr float DEC_RESCALE_LOG2 = 8.f;
 
 template <int D>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                        const __grid_constant__ CUtensorMap tmV, const DecodeTcArgs a) {
   using Cfg = DecodeTcCfg<D>;
@@ -101,8 +103,8 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_islast = reinterpret_cast<int*>(tmem_slot + 2);
-  float* smax = reinterpret_cast<float*>(bars + 32);       // [2][NQ][4 warps], 16-byte aligned
-  float* ssum = smax + 2 * NQ * 4;                         // [NQ][4]
+  float* smax = reinterpret_cast<float*>(bars + 32);       // [2 warpgroups][NQ][4 warps], 16-byte aligned
+  float* ssum = smax + 2 * NQ * 4;                         // [2][NQ][4]
 
   const int G = a.Hq / a.Hkv;
   const int gtiles = (G + NQ - 1) / NQ;
@@ -125,10 +127,11 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 
   if (threadIdx.x == 0) *abort_flag = 0;
   if (n_blk == 0) {  // empty split: neutral partials, no barriers or TMEM touched
-    for (int i = threadIdx.x; i < gn * D; i += blockDim.x) {
-      const long row = (long(b) * a.Hq + head0 + i / D) * a.n_splits + split;
-      a.o_part[row * D + i % D] = 0.f;
-      if (i % D == 0) { a.ml_part[row * 2] = -INFINITY; a.ml_part[row * 2 + 1] = 0.f; }
+    for (int i = threadIdx.x; i < 2 * gn * D; i += blockDim.x) {
+      const int wgp = i / (gn * D), j = i % (gn * D);
+      const long row = (long(b) * a.Hq + head0 + j / D) * (2 * a.n_splits) + split * 2 + wgp;
+      a.o_part[row * D + j % D] = 0.f;
+      if (j % D == 0) { a.ml_part[row * 2] = -INFINITY; a.ml_part[row * 2 + 1] = 0.f; }
     }
   } else {
     if (threadIdx.x == 0) {
@@ -146,7 +149,7 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       }
       mbar_fence_init();
     }
-    if (warp == 4) {
+    if (warp == 8) {
       tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
       tmem_relinquish();
     }
@@ -154,12 +157,12 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_S = tmem_base;             // two buffers of NQ columns
-    const uint32_t tmem_O = tmem_base + 2 * NQ;
+    const uint32_t tmem_S = tmem_base;             // two buffers of NQ columns (one per warpgroup)
+    const uint32_t tmem_O = tmem_base + 2 * NQ;    // two accumulators of MT x NQ columns
     const int* bt = a.block_table + long(b) * a.table_width;
     const int pages_per_blk = BKV / a.page;
 
-    if (warp == 5) {
+    if (warp == 9) {
       // ---------------------------------------------------------------- TMA producer
       // The whole warp walks the tiles: the lanes fetch the next 32 block-table entries with one coalesced
       // load and hand them to lane 0 by shuffle, so no TMA issue waits on a table lookup of its own.
@@ -201,7 +204,7 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           }
         }
       }
-    } else if (warp == 4) {
+    } else if (warp == 8) {
       // ---------------------------------------------------------------- MMA issuer
       if (lane == 0) {
         constexpr uint32_t idesc_s = umma_idesc(128, NQ, 1, 1, 0, 0);
@@ -227,14 +230,11 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         };
         bool ok = mbar_wait(q_full, 0, abort_flag);
         ok = ok && issue_s(0);
+        if (ok && n_blk > 1) ok = issue_s(1);
         if (!ok) { *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FULL); }
         for (int i = 0; ok && i < n_blk; ++i) {
-          // S(i+1) goes to the tensor core before the softmax of tile i has finished: its buffer was released
-          // by the softmax of tile i-1, whose p_ready this thread has already seen
-          if (i + 1 < n_blk && !issue_s(i + 1)) {
-            *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FULL); break;
-          }
-          if (!mbar_wait(&p_ready[i & 1], (i >> 1) & 1, abort_flag)) {
+          const int wgp = i & 1;
+          if (!mbar_wait(&p_ready[wgp], (i >> 1) & 1, abort_flag)) {
             *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FLAG); break;
           }
           const int vs = i % VS;
@@ -243,7 +243,7 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           }
           tc_fence_after();
           const uint32_t va = smem_u32(v_s + vs * Cfg::KV_BYTES);
-          const uint32_t pa = smem_u32(p_s + (i & 1) * Cfg::P_BYTES);
+          const uint32_t pa = smem_u32(p_s + wgp * Cfg::P_BYTES);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
@@ -253,45 +253,57 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
               const uint32_t lbo = (D == 64) ? 0u : uint32_t(BKV * 128);
               const uint64_t da = umma_desc_mn_sw128(va + mt * 2 * (BKV * 128) + k * 16 * 128, lbo, 1024);
               const uint64_t db = umma_desc_k_sw128(pa + (k / 4) * (NQ * 128) + (k % 4) * 32);
-              umma_f16(tmem_O + mt * NQ, da, db, idesc_o, (i | k) ? 1u : 0u);
+              umma_f16(tmem_O + (wgp * MT + mt) * NQ, da, db, idesc_o, ((i >> 1) | k) ? 1u : 0u);
             }
           }
-          umma_commit(&o_done[i & 1]);
+          umma_commit(&o_done[wgp]);
           umma_commit(&v_empty[vs]);
+          // the softmax of tile i has read S[wgp]: the scores of tile i+2 go there, two tiles ahead of their use
+          if (i + 2 < n_blk && !issue_s(i + 2)) {
+            *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FULL); break;
+          }
         }
       }
     } else {
-      // ---------------------------------------------------------------- softmax + epilogue (warps 0..3)
-      const int tl = warp * 32 + lane;            // key within the block, later output dim within a tile
-      const uint32_t lane_off = uint32_t(warp * 32) << 16;
+      // ---------------------------------------------------------------- softmax + epilogue (warps 0..7)
+      const int wgp = warp >> 2;                   // warpgroup: tiles wgp, wgp + 2, ...
+      const int wq = warp & 3;                     // TMEM lane quarter of this warp
+      const int tl = wq * 32 + lane;               // key within the block, later output dim within a tile
+      const uint32_t lane_off = uint32_t(wq * 32) << 16;
+      const uint32_t my_S = tmem_S + wgp * NQ + lane_off;
+      const uint32_t my_O = tmem_O + wgp * MT * NQ + lane_off;
+      const int bar_id = 1 + wgp;
+      float* smx = smax + wgp * (NQ * 4);
+      float* ssm = ssum + wgp * (NQ * 4);
+      uint8_t* my_p = p_s + wgp * Cfg::P_BYTES;
       float m_ref[NQ], l_run[NQ];
 #pragma unroll
       for (int q = 0; q < NQ; ++q) { m_ref[q] = -INFINITY; l_run[q] = 0.f; }
-      // rows of the padded heads are never written again: zero both P buffers once (finite B operand)
-      for (int j = tl; j < 2 * Cfg::P_BYTES / 16; j += 128) reinterpret_cast<uint4*>(p_s)[j] = make_uint4(0u, 0u, 0u, 0u);
+      // rows of the padded heads are never written again: zero the P buffer once (finite B operand)
+      for (int j = tl; j < Cfg::P_BYTES / 16; j += 128) reinterpret_cast<uint4*>(my_p)[j] = make_uint4(0u, 0u, 0u, 0u);
       fence_proxy_async_smem();
       // A wait that runs out does not leave the loop: the warp keeps taking part in the named barriers and the
       // p_ready arrivals (without touching TMEM or waiting again), so the other warps can never be left behind.
       bool ok = true;
       auto fail = [&](int code) { *abort_flag = 1; atomicCAS(a.status, 0, code); ok = false; };
-      for (int i = 0; i < n_blk; ++i) {
-        if (ok && !__all_sync(0xffffffffu, mbar_wait(&s_full[i & 1], (i >> 1) & 1, abort_flag)))
-          fail(ST_TIMEOUT_TMEM_FULL);
+      int n_mine = 0;
+      for (int i = wgp; i < n_blk; i += 2, ++n_mine) {
+        const uint32_t ph = (i >> 1) & 1;
+        if (ok && !__all_sync(0xffffffffu, mbar_wait(&s_full[wgp], ph, abort_flag))) fail(ST_TIMEOUT_TMEM_FULL);
         uint32_t r[16];
 #pragma unroll
         for (int q = 0; q < 16; ++q) r[q] = 0u;
         if (ok) {
           tc_fence_after();
-          tmem_ld16(tmem_S + (i & 1) * NQ + lane_off, r);
+          tmem_ld16(my_S, r);
           tmem_ld_wait();
         }
         const int tok = (blk_lo + i) * BKV + tl;
         const bool valid = tok >= start && tok < ctx;
-        float* smx = smax + (i & 1) * (NQ * 4);
-        int* sflag = reinterpret_cast<int*>(ssum + NQ * 4) + (i & 1) * 4;
         // Only the gn real heads are processed (the MMA's N is padded to 16). The common case needs no column
         // maxima at all: as long as no score exceeds its column's reference maximum by more than the rescale
-        // threshold, the probabilities are taken relative to the (stale) reference.
+        // threshold, the probabilities are taken relative to the (stale) reference. The "any score over"
+        // vote of the 128 threads rides on the named barrier itself (bar.red.or).
         float s[NQ];
         bool over = false;
 #pragma unroll
@@ -302,13 +314,14 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             over |= s[q] > m_ref[q] + DEC_RESCALE_LOG2;
           }
         }
-        const bool warp_over = __any_sync(0xffffffffu, over);
-        if (lane == 0) sflag[warp] = warp_over ? 1 : 0;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        const int4 f4 = *reinterpret_cast<const int4*>(sflag);
-        const bool rescale = (f4.x | f4.y | f4.z | f4.w) != 0;      // uniform over the 128 threads
-        // P buffer i&1 was last read by the PV of tile i-2
-        if (ok && i >= 2 && !__all_sync(0xffffffffu, mbar_wait(&o_done[i & 1], ((i - 2) >> 1) & 1, abort_flag)))
+        uint32_t any_over;
+        asm volatile(
+            "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.or.pred q, %2, 128, p;\n\t"
+            "selp.u32 %0, 1, 0, q;\n\t}"
+            : "=r"(any_over) : "r"(over ? 1u : 0u), "r"(bar_id) : "memory");
+        const bool rescale = any_over != 0;          // uniform over the warpgroup
+        // this warpgroup's previous PV (tile i-2) must be done: it read the P buffer and wrote O^T
+        if (ok && n_mine >= 1 && !__all_sync(0xffffffffu, mbar_wait(&o_done[wgp], ((i - 2) >> 1) & 1, abort_flag)))
           fail(ST_TIMEOUT_TMEM_EMPTY);
         if (rescale) {
           float alpha[NQ];
@@ -316,10 +329,10 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           for (int q = 0; q < NQ; ++q) {
             if (q < gn) {
               const int wm = __reduce_max_sync(0xffffffffu, f2ord(s[q]));
-              if (lane == q) smx[q * 4 + warp] = ord2f(wm);
+              if (lane == q) smx[q * 4 + wq] = ord2f(wm);
             }
           }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
+          asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
 #pragma unroll
           for (int q = 0; q < NQ; ++q) {
             alpha[q] = 1.f;
@@ -333,26 +346,22 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
               l_run[q] *= alpha[q];
             }
           }
-          // O^T may be touched only after the PV of tile i-1 has finished
-          if (ok && i >= 1 &&
-              !__all_sync(0xffffffffu, mbar_wait(&o_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag)))
-            fail(ST_TIMEOUT_TMEM_EMPTY);
-          if (ok && i >= 1) {
+          if (ok && n_mine >= 1) {
             tc_fence_after();
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
               uint32_t o[16];
-              tmem_ld16(tmem_O + mt * NQ + lane_off, o);
+              tmem_ld16(my_O + mt * NQ, o);
               tmem_ld_wait();
 #pragma unroll
               for (int q = 0; q < NQ; ++q) o[q] = __float_as_uint(__uint_as_float(o[q]) * alpha[q]);
-              tmem_st16(tmem_O + mt * NQ + lane_off, o);
+              tmem_st16(my_O + mt * NQ, o);
             }
             tmem_st_wait2();
           }
         }
         // probabilities: P[q][key] bf16, K-major rows of 128 bytes per 64-key half, 128-byte swizzle
-        uint8_t* prow = p_s + (i & 1) * Cfg::P_BYTES + (tl / 64) * (NQ * 128);
+        uint8_t* prow = my_p + (tl / 64) * (NQ * 128);
         const int kc = tl % 64;
 #pragma unroll
         for (int q = 0; q < NQ; ++q) {
@@ -367,40 +376,47 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         }
         fence_proxy_async_smem();
         tc_fence_before();
-        mbar_arrive(&p_ready[i & 1]);
+        mbar_arrive(&p_ready[wgp]);
       }
-      if (ok && !__all_sync(0xffffffffu, mbar_wait(&o_done[(n_blk - 1) & 1], ((n_blk - 1) >> 1) & 1, abort_flag)))
-        fail(ST_TIMEOUT_TMEM_FULL);
+      if (ok && n_mine >= 1) {
+        const int last = wgp + 2 * (n_mine - 1);
+        if (!__all_sync(0xffffffffu, mbar_wait(&o_done[wgp], (last >> 1) & 1, abort_flag))) fail(ST_TIMEOUT_TMEM_FULL);
+      }
       // total row sums: warp shuffle, then across the 4 warps through shared memory
 #pragma unroll
       for (int q = 0; q < NQ; ++q) {
         float v = l_run[q];
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == q) ssum[q * 4 + warp] = v;
+        if (lane == q) ssm[q * 4 + wq] = v;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
       if (ok) {
+        const int part = split * 2 + wgp, n_parts = 2 * a.n_splits;
         tc_fence_after();
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           uint32_t o[16];
-          tmem_ld16(tmem_O + mt * NQ + lane_off, o);
-          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 16; ++q) o[q] = 0u;
+          if (n_mine >= 1) {
+            tmem_ld16(my_O + mt * NQ, o);
+            tmem_ld_wait();
+          }
           const int d = mt * 128 + tl;
           if (d < D) {
 #pragma unroll
             for (int q = 0; q < NQ; ++q) {
               if (q < gn) {
-                const long row = (long(b) * a.Hq + head0 + q) * a.n_splits + split;
+                const long row = (long(b) * a.Hq + head0 + q) * n_parts + part;
                 a.o_part[row * D + d] = __uint_as_float(o[q]);
               }
             }
           }
         }
         if (tl < gn) {
-          const float4 s4 = *reinterpret_cast<const float4*>(&ssum[tl * 4]);
-          const long row = (long(b) * a.Hq + head0 + tl) * a.n_splits + split;
+          const float4 s4 = *reinterpret_cast<const float4*>(&ssm[tl * 4]);
+          const long row = (long(b) * a.Hq + head0 + tl) * n_parts + part;
           // every thread holds the same m_ref; pick column tl without dynamic register indexing
           float mq = -INFINITY;
 #pragma unroll
@@ -412,7 +428,7 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) {
+    if (warp == 8) {
       tc_fence_after();
       tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }
@@ -433,15 +449,15 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   if (!*s_islast || *abort_flag) return;
   __threadfence();
   // scratch in the (now idle) K stage memory: weights of every (head, split) and the heads' denominators
-  float* s_w = reinterpret_cast<float*>(k_s);          // [gn][n_splits]
-  float* s_l = s_w + NQ * 128;                         // [gn]
-  const int ns = a.n_splits;
+  float* s_w = reinterpret_cast<float*>(k_s);          // [gn][parts]
+  const int ns = 2 * a.n_splits;                       // parts per head: (split, warpgroup)
+  float* s_l = s_w + NQ * 256;                         // [gn]
   for (int idx = threadIdx.x; idx < gn * ns; idx += blockDim.x) {
     const long row = (long(b) * a.Hq + head0 + idx / ns) * ns + idx % ns;
     s_w[idx] = __ldcg(&a.ml_part[row * 2]);
   }
   __syncthreads();
-  for (int q = warp; q < gn; q += 6) {
+  for (int q = warp; q < gn; q += 10) {
     float mm = -INFINITY;
     for (int sidx = lane; sidx < ns; sidx += 32) mm = fmaxf(mm, s_w[q * ns + sidx]);
 #pragma unroll
@@ -488,7 +504,7 @@ int launch_decode_tc(const CUtensorMap* tq, const CUtensorMap* tk, const CUtenso
     }
     attr = true;
   }
-  kfn<<<grid, 192, Cfg::SMEM, s>>>(*tq, *tk, *tv, a);
+  kfn<<<grid, 320, Cfg::SMEM, s>>>(*tq, *tk, *tv, a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     snprintf(g_dec_err, sizeof(g_dec_err), "decode attention launch: %s", cudaGetErrorString(e));

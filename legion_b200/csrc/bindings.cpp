@@ -144,7 +144,8 @@ void paged_decode(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
   c10::cuda::CUDAGuard guard(q.device());
   const int B = int(q.size(0)), Hq = int(q.size(1)), D = int(q.size(2));
   const int page = int(k_cache.size(-3)), Hkv = int(k_cache.size(-2));
-  TORCH_CHECK(o_part.numel() >= int64_t(B) * Hq * n_splits * D && ml_part.numel() >= int64_t(B) * Hq * n_splits * 2,
+  const int64_t parts = n_splits * (use_tc ? 2 : 1);   // the tensor-core kernel writes two partials per split
+  TORCH_CHECK(o_part.numel() >= int64_t(B) * Hq * parts * D && ml_part.numel() >= int64_t(B) * Hq * parts * 2,
               "paged_decode: partial buffers too small");
   if (use_tc && k_cache.is_contiguous() && v_cache.is_contiguous() && q.is_contiguous() && out.is_contiguous()) {
     const long n_cells = k_cache.numel() / (long(Hkv) * D);

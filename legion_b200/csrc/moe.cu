@@ -20,7 +20,7 @@ template <int MAXE>
 __device__ __forceinline__ void router_topk_row(const float* logits, long ldl, const float* __restrict__ bias, int E,
                                                 int k, int mode, int renorm, float route_scale, int n_group,
                                                 int topk_group, int* __restrict__ ids, float* __restrict__ wts,
-                                                int t) {
+                                                int t, int* sm_ids = nullptr, float* sm_wts = nullptr) {
   constexpr int PER = MAXE / 32;
   const int lane = threadIdx.x & 31;
   float sc[PER], sel[PER];
@@ -135,6 +135,10 @@ __device__ __forceinline__ void router_topk_row(const float* logits, long ldl, c
     if (renorm) w = w / fmaxf(wsum, 6.1e-5f);
     ids[t * k + lane] = my_id;
     wts[t * k + lane] = w * route_scale;
+    if (sm_ids) {     // copy for a caller that goes on working on the selection in shared memory
+      sm_ids[t * k + lane] = my_id;
+      sm_wts[t * k + lane] = w * route_scale;
+    }
   }
 }
 
@@ -159,28 +163,33 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const float* __restric
 //   tile_group[slot] = expert, slot_base[slot] = slot * bn, tile_ntok[slot] = T, meta = {n_active, n_active * bn}
 //   out_rows[slot * bn + t] = pair index t * k + c (or -1), tok_scale[slot * bn + t] = routing weight
 template <int MAXE>
-__global__ void __launch_bounds__(256) moe_route_small_kernel(
+__global__ void __launch_bounds__(512) moe_route_small_kernel(
     const __nv_bfloat16* __restrict__ x, long ldx, const float* __restrict__ norm_w, float eps, float w_offset,
     __nv_bfloat16* __restrict__ x_normed, long ldn, const __nv_bfloat16* __restrict__ w, long ldw, int H,
     float* logits, const float* __restrict__ bias, int E, int k, int mode, int renorm, float route_scale, int n_group,
     int topk_group, int* ids, float* wts, int T, int bn, int* __restrict__ tile_group, int* __restrict__ slot_base,
     int* __restrict__ tile_ntok, int* __restrict__ meta, int* __restrict__ out_rows, float* __restrict__ tok_scale,
     unsigned int* done_ctr) {
-  __shared__ float red[8][8];
-  __shared__ float s_inv[8];
+  __shared__ float red[2][8][8];
+  __shared__ float s_inv[2][8];
   __shared__ int s_last;
   __shared__ int s_ids[1024];
-  __shared__ int s_wsum[9];
+  __shared__ float s_wts[1024];
+  __shared__ int s_wsum[17];
+  __shared__ int s_slot[512];
   const int e = blockIdx.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // the two halves of the CTA take 8 tokens each per pass
+  const int half = tid >> 8, htid = tid & 255, hwarp = warp & 7;
   const uint4* w4 = reinterpret_cast<const uint4*>(w + long(e) * ldw);
   const int nv = H / 8;
-  for (int t0 = 0; t0 < T; t0 += 8) {
+  for (int base = 0; base < T; base += 16) {
+    const int t0 = base + half * 8;
     if (norm_w) {
       float ssq[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) ssq[j] = 0.f;
-      for (int v = tid; v < nv; v += 256) {
+      for (int v = htid; v < nv; v += 256) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           if (t0 + j < T) {
@@ -198,21 +207,21 @@ __global__ void __launch_bounds__(256) moe_route_small_kernel(
       for (int j = 0; j < 8; ++j) {
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ssq[j] += __shfl_xor_sync(0xffffffffu, ssq[j], o);
-        if (lane == 0) red[warp][j] = ssq[j];
+        if (lane == 0) red[half][hwarp][j] = ssq[j];
       }
       __syncthreads();
-      if (tid < 8) {
+      if (htid < 8) {
         float tot = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) tot += red[i][tid];
-        s_inv[tid] = rsqrtf(tot / float(H) + eps);
+        for (int i = 0; i < 8; ++i) tot += red[half][i][htid];
+        s_inv[half][htid] = rsqrtf(tot / float(H) + eps);
       }
       __syncthreads();
     }
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int v = tid; v < nv; v += 256) {
+    for (int v = htid; v < nv; v += 256) {
       const uint4 wu = w4[v];
       const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wu);
       float2 wf[4];
@@ -225,19 +234,25 @@ __global__ void __launch_bounds__(256) moe_route_small_kernel(
         nw[0] = n0.x + w_offset; nw[1] = n0.y + w_offset; nw[2] = n0.z + w_offset; nw[3] = n0.w + w_offset;
         nw[4] = n1.x + w_offset; nw[5] = n1.y + w_offset; nw[6] = n1.z + w_offset; nw[7] = n1.w + w_offset;
       }
+      uint4 xu[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        xu[j] = make_uint4(0u, 0u, 0u, 0u);
+        if (t0 + j < T) xu[j] = reinterpret_cast<const uint4*>(x + long(t0 + j) * ldx)[v];
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         if (t0 + j < T) {
-          uint4 xu = reinterpret_cast<const uint4*>(x + long(t0 + j) * ldx)[v];
-          __nv_bfloat162* xp = reinterpret_cast<__nv_bfloat162*>(&xu);
+          __nv_bfloat162* xp = reinterpret_cast<__nv_bfloat162*>(&xu[j]);
           if (norm_w) {
-            const float inv = s_inv[j];
+            const float inv = s_inv[half][j];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               const float2 xf = __bfloat1622float2(xp[i]);
               xp[i] = __floats2bfloat162_rn(xf.x * inv * nw[2 * i], xf.y * inv * nw[2 * i + 1]);
             }
-            if ((t0 + j) % gridDim.x == blockIdx.x) reinterpret_cast<uint4*>(x_normed + long(t0 + j) * ldn)[v] = xu;
+            if ((t0 + j) % gridDim.x == blockIdx.x)
+              reinterpret_cast<uint4*>(x_normed + long(t0 + j) * ldn)[v] = xu[j];
           }
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -252,14 +267,14 @@ __global__ void __launch_bounds__(256) moe_route_small_kernel(
     for (int j = 0; j < 8; ++j) {
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
-      if (lane == 0) red[warp][j] = acc[j];
+      if (lane == 0) red[half][hwarp][j] = acc[j];
     }
     __syncthreads();
-    if (tid < 8 && t0 + tid < T) {
+    if (htid < 8 && t0 + htid < T) {
       float tot = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) tot += red[i][tid];
-      logits[long(t0 + tid) * E + e] = tot;
+      for (int i = 0; i < 8; ++i) tot += red[half][i][htid];
+      logits[long(t0 + htid) * E + e] = tot;
     }
     __syncthreads();
   }
@@ -272,47 +287,50 @@ __global__ void __launch_bounds__(256) moe_route_small_kernel(
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  // ---- last CTA: top-k of every token (one warp per token)
-  for (int t = warp; t < T; t += 8)
-    router_topk_row<MAXE>(logits, E, bias, E, k, mode, renorm, route_scale, n_group, topk_group, ids, wts, t);
+  // ---- last CTA: top-k of every token (one warp per token), kept in shared memory for the table build
+  for (int t = warp; t < T; t += 16) {
+    router_topk_row<MAXE>(logits, E, bias, E, k, mode, renorm, route_scale, n_group, topk_group, ids, wts, t, s_ids,
+                          s_wts);
+  }
   __syncthreads();
   const int P = T * k;
-  for (int p = tid; p < P; p += 256) s_ids[p] = ids[p];
+  // ---- dense routing tables: experts in index order, one slot per active expert. Every step is one
+  // operation per thread: count by shared-memory atomics (one thread per pair), rank the active experts by
+  // ballot + warp totals, clear the used part of out_rows with coalesced stores, scatter the pairs.
+  for (int i = tid; i < E; i += 512) s_slot[i] = 0;
   __syncthreads();
-  // ---- dense routing tables: experts in index order, one slot per active expert
-  int slot_carry = 0;
-  for (int e0 = 0; e0 < E; e0 += 256) {
-    const int ee = e0 + tid;
-    int cnt = 0;
-    if (ee < E)
-      for (int p = 0; p < P; ++p) cnt += (s_ids[p] == ee);
+  for (int p = tid; p < P; p += 512) atomicAdd(&s_slot[s_ids[p]], 1);
+  __syncthreads();
+  int n_active = 0;
+  {
+    const int cnt = (tid < E) ? s_slot[tid] : 0;
     const unsigned bal = __ballot_sync(0xffffffffu, cnt > 0);
     if (lane == 0) s_wsum[warp] = __popc(bal);
     __syncthreads();
-    int before = slot_carry;
+    int before = 0;
     for (int i = 0; i < warp; ++i) before += s_wsum[i];
-    int total = 0;
-    for (int i = 0; i < 8; ++i) total += s_wsum[i];
+    for (int i = 0; i < 16; ++i) n_active += s_wsum[i];
+    int slot = -1;
     if (cnt > 0) {
-      const int slot = before + __popc(bal & ((1u << lane) - 1));
-      tile_group[slot] = ee;
+      slot = before + __popc(bal & ((1u << lane) - 1));
+      tile_group[slot] = tid;
       slot_base[slot] = slot * bn;
       tile_ntok[slot] = T;
-      for (int t = 0; t < bn; ++t) out_rows[slot * bn + t] = -1;
-      for (int p = 0; p < P; ++p) {
-        if (s_ids[p] == ee) {
-          const int t = p / k;
-          out_rows[slot * bn + t] = p;
-          tok_scale[slot * bn + t] = wts[p];
-        }
-      }
     }
-    slot_carry += total;
-    __syncthreads();
+    __syncthreads();                 // every thread has read its count before the slot numbers replace them
+    if (tid < E) s_slot[tid] = slot;
+  }
+  for (int i = tid; i < n_active * bn; i += 512) out_rows[i] = -1;
+  __syncthreads();
+  for (int p = tid; p < P; p += 512) {
+    const int slot = s_slot[s_ids[p]];
+    const int t = p / k;
+    out_rows[slot * bn + t] = p;
+    tok_scale[slot * bn + t] = s_wts[p];
   }
   if (tid == 0) {
-    meta[0] = slot_carry;
-    meta[1] = slot_carry * bn;
+    meta[0] = n_active;
+    meta[1] = n_active * bn;
   }
 }
 
@@ -327,7 +345,7 @@ int moe_route_small_launch(const void* x, long ldx, const float* norm_w, float e
   auto xn = static_cast<__nv_bfloat16*>(x_normed);
   auto wb = static_cast<const __nv_bfloat16*>(w);
 #define LB_ROUTE(MAXE)                                                                                              \
-  moe_route_small_kernel<MAXE><<<E, 256, 0, s>>>(xb, ldx, norm_w, eps, w_offset, xn, ldn, wb, ldw, H, logits, bias, \
+  moe_route_small_kernel<MAXE><<<E, 512, 0, s>>>(xb, ldx, norm_w, eps, w_offset, xn, ldn, wb, ldw, H, logits, bias, \
                                                  E, k, mode, renorm, route_scale, n_group, topk_group, ids, wts, T, \
                                                  bn, tile_group, slot_base, tile_ntok, meta, out_rows, tok_scale,   \
                                                  done_ctr)

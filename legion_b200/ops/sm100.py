@@ -245,8 +245,8 @@ def paged_decode(q, k_cache, v_cache, block_table, ctx_lens, scale, window=0, n_
         G = Hq // Hkv
         n_splits = decode_splits(B, Hkv, (G + 15) // 16, max_ctx or block_table.shape[1] * k_cache.shape[1], D)
     ws = Workspace.get(q.device)
-    o_part = ws.buf("dec_o", (B * Hq * n_splits * D,), torch.float32)
-    ml_part = ws.buf("dec_ml", (B * Hq * n_splits * 2,), torch.float32)
+    o_part = ws.buf("dec_o", (B * Hq * n_splits * 2 * D,), torch.float32)
+    ml_part = ws.buf("dec_ml", (B * Hq * n_splits * 2 * 2,), torch.float32)
     if out is None:
         out = torch.empty_like(q)
     C.paged_decode(q, k_cache, v_cache, block_table, ctx_lens, scale, window, n_splits, o_part, ml_part, out,
