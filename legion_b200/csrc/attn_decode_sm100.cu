@@ -115,6 +115,8 @@ paged_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   const int split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+  griddep_wait();
+  griddep_launch();
   const int ctx = a.ctx_lens[b];
   const int start = (a.window > 0 && ctx > a.window) ? ctx - a.window : 0;
   const int blk_first = start / BKV;
@@ -504,7 +506,7 @@ int launch_decode_tc(const CUtensorMap* tq, const CUtensorMap* tk, const CUtenso
     }
     attr = true;
   }
-  kfn<<<grid, 320, Cfg::SMEM, s>>>(*tq, *tk, *tv, a);
+  launch_pdl(kfn, grid, dim3(320), Cfg::SMEM, s, *tq, *tk, *tv, a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     snprintf(g_dec_err, sizeof(g_dec_err), "decode attention launch: %s", cudaGetErrorString(e));

@@ -7,6 +7,10 @@
 #include "gdn.h"
 #include "gemm_sm100.h"
 #include "kernels.h"
+namespace lb {
+bool pdl_enabled();
+void set_pdl(bool on);
+}  // namespace lb
 #include "quant.h"
 
 namespace {
@@ -343,6 +347,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("wgemm_workspace_floats", [](int64_t bn, bool dual, int64_t n_tok_tiles, int64_t feat_tiles, int64_t split_k) {
     return int64_t(lb::wgemm_workspace_floats(int(bn), dual, int(n_tok_tiles), int(feat_tiles), int(split_k)));
   });
+  m.def("set_pdl", [](bool on) { lb::set_pdl(on); });
+  m.def("pdl_enabled", []() { return lb::pdl_enabled(); });
   bind_gdn(m);
   bind_comm(m);
   bind_quant(m);

@@ -9,6 +9,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <utility>
 
 namespace lb {
 
@@ -88,6 +89,37 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       if (globaltimer_ns() - t0 > budget_ns) return false;
     }
   }
+}
+
+// ----------------------------------------------------------------------------------------------
+// Programmatic dependent launch: a kernel launched with launch_pdl() may become resident while its
+// predecessor in the stream is still draining; it must call griddep_wait() before its first access to
+// global memory (the wait returns once the predecessor grids have completed and their writes are visible).
+// griddep_launch() lets the successor's CTAs be scheduled as soon as every CTA of this grid has passed it.
+// Without the launch attribute both are no-ops, so kernels stay correct under ordinary launches.
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool pdl_enabled();
+void set_pdl(bool on);
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (pdl_enabled()) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
 // ----------------------------------------------------------------------------------------------

@@ -39,6 +39,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const __nv_bfloat16* __res
                                                       const float* __restrict__ w, __nv_bfloat16* __restrict__ y,
                                                       long ldy, int H, float eps, float w_offset) {
   __shared__ float red[8];
+  griddep_wait();
+  griddep_launch();
   const long row = blockIdx.x;
   const uint4* xv = reinterpret_cast<const uint4*>(x + row * ldx);
   const uint4* rv = res_in ? reinterpret_cast<const uint4*>(res_in + row * ldri) : nullptr;
@@ -101,11 +103,9 @@ int rmsnorm_launch(const void* x, long ldx, const void* res_in, long ldri, void*
                    void* y, long ldy, int rows, int H, float eps, float w_offset, cudaStream_t s) {
   if (rows <= 0) return 0;
   if (H % 8) return 1;
-  rmsnorm_kernel<<<rows, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), ldx,
-                                      static_cast<const __nv_bfloat16*>(res_in), ldri,
-                                      static_cast<__nv_bfloat16*>(res_out), ldro, w, static_cast<__nv_bfloat16*>(y),
-                                      ldy, H, eps, w_offset);
-  return cudaGetLastError() != cudaSuccess;
+  return launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, s, static_cast<const __nv_bfloat16*>(x), ldx,
+                    static_cast<const __nv_bfloat16*>(res_in), ldri, static_cast<__nv_bfloat16*>(res_out), ldro, w,
+                    static_cast<__nv_bfloat16*>(y), ldy, H, eps, w_offset) != cudaSuccess;
 }
 
 // One warp per (token, head). Heads 0..Hq-1 are queries, then Hkv keys, then Hkv values, read from
@@ -120,6 +120,8 @@ __global__ void __launch_bounds__(128) qk_norm_rope_append_kernel(
     __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
     long cache_cell_stride, int T, int Hq, int Hkv) {
   constexpr int N = D / 32;
+  griddep_wait();
+  griddep_launch();
   const int lane = threadIdx.x & 31;
   const long gw = (long(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int heads = Hq + 2 * Hkv;
@@ -189,11 +191,11 @@ int qk_norm_rope_append_launch(const void* qkv, long ld_qkv, int q_head_stride, 
   const int blocks = int((warps * 32 + 127) / 128);
 #define LB_D(DD)                                                                                                   \
   if (D == DD) {                                                                                                   \
-    qk_norm_rope_append_kernel<DD><<<blocks, 128, 0, s>>>(                                                         \
-        static_cast<const __nv_bfloat16*>(qkv), ld_qkv, q_head_stride, k_off, v_off, qw, kw, eps, w_offset,        \
-        cos_sin, rot, positions, slots, static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),  \
-        static_cast<__nv_bfloat16*>(v_cache), cache_cell_stride, T, Hq, Hkv);                                      \
-    return cudaGetLastError() != cudaSuccess;                                                                      \
+    return launch_pdl(qk_norm_rope_append_kernel<DD>, dim3(blocks), dim3(128), 0, s,                              \
+                      static_cast<const __nv_bfloat16*>(qkv), ld_qkv, q_head_stride, k_off, v_off, qw, kw, eps,    \
+                      w_offset, cos_sin, rot, positions, slots, static_cast<__nv_bfloat16*>(q_out),                \
+                      static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache),                  \
+                      cache_cell_stride, T, Hq, Hkv) != cudaSuccess;                                               \
   }
   LB_D(64) LB_D(128) LB_D(256)
 #undef LB_D

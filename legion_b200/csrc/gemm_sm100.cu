@@ -114,6 +114,9 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // barriers, TMEM and descriptors are set up: from here on global memory is touched
+  griddep_wait();
+  griddep_launch();
 
   const int n_tok_tiles = a.tile_group ? min(*a.n_tiles_dev, a.n_tok_tiles_max) : (a.n_tok + BN - 1) / BN;
   const int num_kb = (a.K + BK - 1) / BK;
@@ -397,7 +400,7 @@ int launch(const CUtensorMap* tmW, const CUtensorMap* tmX, const WgemmArgs& a, i
     }
     attr_set = true;
   }
-  kfn<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(*tmW, *tmX, a);
+  launch_pdl(kfn, dim3(grid), dim3(192), Cfg::SMEM_BYTES, stream, *tmW, *tmX, a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     snprintf(g_gemm_err, sizeof(g_gemm_err), "wgemm launch: %s", cudaGetErrorString(e));

@@ -177,6 +177,8 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
   __shared__ float s_wts[1024];
   __shared__ int s_wsum[17];
   __shared__ int s_slot[512];
+  griddep_wait();
+  griddep_launch();
   const int e = blockIdx.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // the two halves of the CTA take 8 tokens each per pass
@@ -345,10 +347,9 @@ int moe_route_small_launch(const void* x, long ldx, const float* norm_w, float e
   auto xn = static_cast<__nv_bfloat16*>(x_normed);
   auto wb = static_cast<const __nv_bfloat16*>(w);
 #define LB_ROUTE(MAXE)                                                                                              \
-  moe_route_small_kernel<MAXE><<<E, 512, 0, s>>>(xb, ldx, norm_w, eps, w_offset, xn, ldn, wb, ldw, H, logits, bias, \
-                                                 E, k, mode, renorm, route_scale, n_group, topk_group, ids, wts, T, \
-                                                 bn, tile_group, slot_base, tile_ntok, meta, out_rows, tok_scale,   \
-                                                 done_ctr)
+  launch_pdl(moe_route_small_kernel<MAXE>, dim3(E), dim3(512), 0, s, xb, ldx, norm_w, eps, w_offset, xn, ldn, wb,  \
+             ldw, H, logits, bias, E, k, mode, renorm, route_scale, n_group, topk_group, ids, wts, T, bn,           \
+             tile_group, slot_base, tile_ntok, meta, out_rows, tok_scale, done_ctr)
   if (E <= 128) LB_ROUTE(128);
   else if (E <= 256) LB_ROUTE(256);
   else LB_ROUTE(512);
@@ -626,6 +627,8 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(
     const float* __restrict__ norm_w, float eps, float w_offset, __nv_bfloat16* __restrict__ norm_out, long ldn) {
   __shared__ int s_on[32];
   __shared__ float red[8];
+  griddep_wait();
+  griddep_launch();
   const long t = blockIdx.x;
   if (threadIdx.x < k) {
     const int e = ids[t * k + threadIdx.x];
@@ -714,12 +717,10 @@ int moe_combine_launch(const void* y, long ldy, const int* ids, int k, int e_lo,
                        const float* norm_w, float eps, float w_offset, void* norm_out, long ldn, cudaStream_t s) {
   if (T <= 0) return 0;
   if (H % 8 || k > 32) return 1;
-  moe_combine_kernel<<<T, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(y), ldy, ids, k, e_lo, e_hi,
-                                       static_cast<const __nv_bfloat16*>(shared), lds, shared_gate,
-                                       static_cast<const __nv_bfloat16*>(residual), ldr,
-                                       static_cast<__nv_bfloat16*>(out), ldo, H, norm_w, eps, w_offset,
-                                       static_cast<__nv_bfloat16*>(norm_out), ldn);
-  return cudaGetLastError() != cudaSuccess;
+  return launch_pdl(moe_combine_kernel, dim3(T), dim3(256), 0, s, static_cast<const __nv_bfloat16*>(y), ldy, ids, k,
+                    e_lo, e_hi, static_cast<const __nv_bfloat16*>(shared), lds, shared_gate,
+                    static_cast<const __nv_bfloat16*>(residual), ldr, static_cast<__nv_bfloat16*>(out), ldo, H, norm_w,
+                    eps, w_offset, static_cast<__nv_bfloat16*>(norm_out), ldn) != cudaSuccess;
 }
 
 }  // namespace lb

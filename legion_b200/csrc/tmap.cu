@@ -111,4 +111,10 @@ const CUtensorMap* tmap_3d(const void* base, uint64_t d0, uint64_t d1, uint64_t 
   return encode(k, 3, base, dims, strides, box, dtype, swizzle128);
 }
 
+namespace {
+bool g_pdl = true;
+}
+bool pdl_enabled() { return g_pdl; }
+void set_pdl(bool on) { g_pdl = on; }
+
 }  // namespace lb

@@ -51,7 +51,9 @@ def ext():
         with _lock:
             if _C is None and _C_err is None:
                 try:
-                    _C = _Counting(importlib.import_module("legion_b200._C"))
+                    mod = importlib.import_module("legion_b200._C")
+                    mod.set_pdl(bool(TUNE["pdl"]))
+                    _C = _Counting(mod)
                 except BaseException as e:  # missing .so, ABI mismatch, missing libcudart
                     _C_err = e
     if _C is None:
@@ -72,7 +74,7 @@ def have_ext() -> bool:
 NUM_SMS = 148
 
 # tuning knobs (environment: LB_TUNE="decode_fixed_tiles=2,dense_route=1")
-TUNE = {"decode_fixed_tiles": 2, "fused_plan": 1, "fused_router": 1, "dense_route": 1}
+TUNE = {"decode_fixed_tiles": 2, "fused_plan": 1, "fused_router": 1, "dense_route": 1, "pdl": 1}
 for _kv in os.environ.get("LB_TUNE", "").split(","):
     if "=" in _kv:
         TUNE[_kv.split("=")[0].strip()] = int(_kv.split("=")[1])
