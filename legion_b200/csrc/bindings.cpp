@@ -84,6 +84,56 @@ void wgemm(const Tensor& w, const Tensor& x, Tensor& out, const OptT& residual, 
   TORCH_CHECK(lb::wgemm_launch(h, cur_stream()) == 0, lb::wgemm_last_error());
 }
 
+// Dense GEMM whose kernel tail all-reduces the output over the ranks' symmetric buffers (+ residual, + RMSNorm).
+// `slot` must be this rank's partial slot inside its symmetric buffer (byte offset buf_off).
+void wgemm_allreduce(const Tensor& w, const Tensor& x, Tensor& slot, int64_t bn, int64_t split_k, const OptT& ws,
+                     const OptT& counters, Tensor& status, std::vector<int64_t> buffers, std::vector<int64_t> signals,
+                     int64_t rank, int64_t buf_off, int64_t slot_base, Tensor& seq, Tensor& ctrs, const OptT& residual,
+                     Tensor& sum_out, const OptT& norm_w, double eps, double w_offset, const OptT& norm_out,
+                     int64_t budget_ns, Tensor& comm_status) {
+  check_bf16(w, "w");
+  check_bf16(x, "x");
+  check_bf16(slot, "slot");
+  TORCH_CHECK(w.dim() == 2 && x.dim() == 2 && slot.dim() == 2 && w.size(1) == x.size(1), "wgemm_allreduce: shapes");
+  TORCH_CHECK(slot.is_contiguous() && slot.size(0) == x.size(0) && slot.size(1) == w.size(0),
+              "wgemm_allreduce: the slot must be a contiguous [tokens, features] view");
+  TORCH_CHECK(buffers.size() == signals.size() && buffers.size() <= LB_MAX_RANKS && ctrs.numel() >= 2,
+              "wgemm_allreduce: bad peer table");
+  TORCH_CHECK(norm_w.has_value() == norm_out.has_value(), "wgemm_allreduce: norm weight and output go together");
+  c10::cuda::CUDAGuard guard(w.device());
+  lb::WgemmHost h{};
+  h.w = w.data_ptr(); h.w_rows = w.size(0); h.ldw = w.stride(0);
+  h.x = x.data_ptr(); h.x_rows = x.size(0); h.ldx = x.stride(0);
+  h.out = slot.data_ptr(); h.ldo = slot.stride(0); h.out_f32 = false;
+  h.K = int(w.size(1)); h.n_feat = int(w.size(0)); h.n_tok = int(x.size(0));
+  h.bn = int(bn); h.dual = false;
+  h.split_k = int(split_k);
+  h.ws = optpm<float>(ws);
+  h.counters = optpm<int>(counters);
+  h.status = reinterpret_cast<int*>(status.data_ptr());
+  auto& c = h.comm;
+  c.enabled = 1;
+  c.peers.world = int(buffers.size());
+  c.peers.rank = int(rank);
+  for (size_t i = 0; i < buffers.size(); ++i) {
+    c.peers.buffer[i] = reinterpret_cast<void*>(buffers[i]);
+    c.peers.signal[i] = reinterpret_cast<void*>(signals[i]);
+  }
+  c.buf_off = buf_off; c.slot_base = int(slot_base);
+  c.seq_ptr = reinterpret_cast<uint32_t*>(seq.data_ptr());
+  c.ctrs = reinterpret_cast<unsigned int*>(ctrs.data_ptr());
+  c.T = int(x.size(0)); c.H = int(w.size(0));
+  c.residual = residual.has_value() ? reinterpret_cast<const __nv_bfloat16*>(residual->data_ptr()) : nullptr;
+  c.ldr = residual.has_value() ? residual->stride(0) : 0;
+  c.sum_out = reinterpret_cast<__nv_bfloat16*>(sum_out.data_ptr()); c.lds = sum_out.stride(0);
+  c.norm_w = optp<float>(norm_w); c.eps = float(eps); c.w_offset = float(w_offset);
+  c.norm_out = norm_out.has_value() ? reinterpret_cast<__nv_bfloat16*>(norm_out->data_ptr()) : nullptr;
+  c.ldn = norm_out.has_value() ? norm_out->stride(0) : 0;
+  c.budget_ns = static_cast<unsigned long long>(budget_ns);
+  c.status = reinterpret_cast<int*>(comm_status.data_ptr());
+  TORCH_CHECK(lb::wgemm_launch(h, cur_stream()) == 0, lb::wgemm_last_error());
+}
+
 void rmsnorm(const Tensor& x, const OptT& res_in, const OptT& res_out, const Tensor& w, Tensor& y, double eps,
              double w_offset) {
   check_bf16(x, "x");
@@ -328,6 +378,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         pybind11::arg("counters"), pybind11::arg("status"), pybind11::arg("tile_group"), pybind11::arg("tile_tok0"),
         pybind11::arg("tile_ntok"), pybind11::arg("meta"), pybind11::arg("max_tiles"), pybind11::arg("rows_per_group"),
         pybind11::arg("n_tok"), pybind11::arg("out_peer"), pybind11::arg("tile_out0") = pybind11::none());
+  m.def("wgemm_allreduce", &wgemm_allreduce);
   m.def("rmsnorm", &rmsnorm);
   m.def("qk_norm_rope_append", &qk_norm_rope_append);
   m.def("sigmoid_gate", &sigmoid_gate);

@@ -20,6 +20,7 @@
 //
 // Counterpart in the reference: cuBLAS GEMMs reached through ggml, src/cuda/dense_mv.cu (skinny
 // BF16), src/cuda/moe_gemm.cu (routed experts, >= 64 tokens), src/cuda/expert_mv/ (decode experts).
+#include "comm_dev.cuh"
 #include "common.cuh"
 #include "gemm_sm100.h"
 #include "tmap.cuh"
@@ -378,6 +379,54 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
+
+  // ------------------------------------------------------------------ fused reduction over the ranks
+  // The output tiles written above are this rank's PARTIAL result inside its symmetric buffer. All CTAs of this
+  // (persistent, fully resident) grid count themselves in; the last one raises this rank's flag on every peer;
+  // every CTA then waits (bounded) for all ranks' flags and reduces its share of the rows over NVLink peer
+  // loads in rank order, adding the residual and applying the next RMSNorm: GEMM and all-reduce are one launch.
+  if (a.comm.enabled) {
+    const WgemmCommTail& c = a.comm;
+    float* red = stage;                         // epilogue staging memory is idle now
+    __threadfence_system();                     // this thread's partial stores, system scope
+    __syncthreads();
+    const uint32_t seq = *reinterpret_cast<const volatile uint32_t*>(c.seq_ptr) + 1;
+    if (threadIdx.x == 0) {
+      const unsigned int old = atomicAdd(&c.ctrs[0], 1u);
+      *last_flag = (old == gridDim.x - 1);
+      if (old == gridDim.x - 1) c.ctrs[0] = 0;
+    }
+    __syncthreads();
+    if (*last_flag && threadIdx.x < c.peers.world) {
+      __threadfence_system();
+      st_release_sys(reinterpret_cast<uint32_t*>(c.peers.signal[threadIdx.x]) + c.slot_base + c.peers.rank, seq);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *last_flag = 1;       // reused as "all peers arrived"
+    __syncthreads();
+    if (threadIdx.x < c.peers.world) {
+      const uint32_t* mine =
+          reinterpret_cast<const uint32_t*>(c.peers.signal[c.peers.rank]) + c.slot_base + threadIdx.x;
+      if (!wait_flag_geq(mine, seq, c.budget_ns)) {
+        *last_flag = 0;
+        atomicCAS(c.status, 0, ST_TIMEOUT_FLAG);
+      }
+    }
+    __syncthreads();
+    if (*last_flag)
+      reduce_rows_rank_order(c.peers, c.buf_off, c.T, c.H, c.residual, c.ldr, c.sum_out, c.lds, c.norm_w, c.eps,
+                             c.w_offset, c.norm_out, c.ldn, red);
+    // the last CTA to finish publishes the new sequence number (every CTA has read the old one)
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      const unsigned int old = atomicAdd(&c.ctrs[1], 1u);
+      if (old == gridDim.x - 1) {
+        c.ctrs[1] = 0;
+        *reinterpret_cast<volatile uint32_t*>(c.seq_ptr) = seq;
+      }
+    }
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -455,6 +504,7 @@ int wgemm_launch(const WgemmHost& h, cudaStream_t stream) {
   a.tok_scale = h.tok_scale; a.out_rows = h.out_rows;
   a.K = h.K; a.n_feat = h.n_feat; a.feat_tiles = (h.n_feat + BM - 1) / BM;
   a.n_tok = h.n_tok;
+  a.comm = h.comm;
   a.tile_group = h.tile_group; a.tile_tok0 = h.tile_tok0; a.tile_out0 = h.tile_out0; a.tile_ntok = h.tile_ntok; a.n_tiles_dev = h.n_tiles_dev;
   a.n_tok_tiles_max = h.n_tok_tiles_max;
   a.rows_per_group = h.rows_per_group; a.dual_offset = h.dual_offset;

@@ -1,5 +1,6 @@
 // Host interface of the weights-as-M tcgen05 GEMM (gemm_sm100.cu).
 #pragma once
+#include "comm.h"
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stddef.h>
@@ -7,6 +8,24 @@
 namespace lb {
 
 // Device-side argument block (passed by value to the kernel).
+// Optional tail of the GEMM kernel: all-reduce of the output over the ranks' symmetric buffers (+ residual, + the
+// next RMSNorm). The GEMM's output must be this rank's partial slot at byte offset buf_off of its symmetric buffer.
+struct WgemmCommTail {
+  int enabled;
+  CommPeers peers;
+  long buf_off;
+  int slot_base;
+  uint32_t* seq_ptr;              // sequence number (device data: graph-replayable)
+  unsigned int* ctrs;             // [2] arrival / exit counters, zero on entry, left zero
+  int T, H;
+  const __nv_bfloat16* residual; long ldr;
+  __nv_bfloat16* sum_out; long lds;
+  const float* norm_w; float eps, w_offset;
+  __nv_bfloat16* norm_out; long ldn;
+  unsigned long long budget_ns;
+  int* status;                    // communicator status word
+};
+
 struct WgemmArgs {
   void* out;                      // bf16 or f32 [rows, ldo]
   long ldo;
@@ -30,6 +49,7 @@ struct WgemmArgs {
   int* status;                    // error word (0 = ok)
   void* out_peer[8];              // EP combine: per-rank output bases (peer-mapped); used when n_out_peer > 0,
   int n_out_peer;                 //   out_rows[] then holds (rank << 24) | row
+  WgemmCommTail comm;
 };
 
 // Host-side description of one launch.
@@ -49,6 +69,7 @@ struct WgemmHost {
   int split_k; float* ws; int* counters;
   int* status;
   void* out_peer[8]; int n_out_peer;
+  WgemmCommTail comm;
 };
 
 int wgemm_launch(const WgemmHost& h, cudaStream_t stream);

@@ -183,7 +183,7 @@ class Decoder:
                                 window=window, decode_splits=b.decode_splits, max_ctx=b.max_ctx or None)
         if cfg.gated_attn:
             o = ops.apply_output_gate(o, gate, self.n_head_l, D)
-        return ops.linear(o.reshape(o.shape[0], -1), w[f"{p}.attn.o"], out=self.pctx.partial_out(o.shape[0], cfg.hidden))
+        return self.pctx.defer_linear(o.reshape(o.shape[0], -1), w[f"{p}.attn.o"])
 
     def _gdn(self, p: str, il: int, x, b: StepBatch, st: StatePool):
         cfg, w = self.cfg, self.w
@@ -199,7 +199,7 @@ class Decoder:
         o = ops.gdn_recurrent(conv, g, beta, st.ssm[il], b.cu_q, b.state_slots, nk, nv, dk, dv, cfg.gdn_tiled_heads,
                               dk ** -0.5, 1e-6, write_state=b.write_state)
         n = ops.gated_rmsnorm(o, z, w[f"{p}.gdn.norm"], cfg.rms_eps, cfg.gdn_gate_act)
-        return ops.linear(n.reshape(n.shape[0], -1), w[f"{p}.gdn.out"], out=self.pctx.partial_out(n.shape[0], cfg.hidden))
+        return self.pctx.defer_linear(n.reshape(n.shape[0], -1), w[f"{p}.gdn.out"])
 
     def _mla(self, p: str, il: int, x, b: StepBatch, kv: KvCache):
         """Latent attention: cache row = [rmsnorm(c_kv) | rope(k_pe)]; keys/values are expanded from
@@ -315,8 +315,9 @@ class Decoder:
                           residual if fuse_res else None, routing=routing), fuse_res, None
         n_ff = w[f"{p}.mlp.down"].shape[1]
         h = ops.gate_up_act(x, w[f"{p}.mlp.gate_up"], n_ff, cfg.ffn_act)
-        return ops.linear(h, w[f"{p}.mlp.down"], residual=residual if fuse_res else None,
-                          out=pc.partial_out(h.shape[0], cfg.hidden)), fuse_res, None
+        if fuse_res:
+            return ops.linear(h, w[f"{p}.mlp.down"], residual=residual), True, None
+        return pc.defer_linear(h, w[f"{p}.mlp.down"]), False, None
 
     def _layer(self, p: str, il: int, kind: str, moe: bool, x, resid, b, kv, st, pre_normed=None, next_norm=None):
         """x is the (possibly rank-partial) output of the previous sub-layer, resid the residual stream.

@@ -47,6 +47,7 @@ class SymmComm:
         assert self.base == self.buffer_ptrs[rank]
         self.seq = torch.zeros(1, dtype=torch.int32, device=device)
         self.done = torch.zeros(1, dtype=torch.int32, device=device)
+        self.gemm_ctrs = torch.zeros(2, dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.budget_ns = budget_ns
         self._next = 0
@@ -101,6 +102,37 @@ class SymmComm:
         normed = torch.empty_like(summed) if w is not None else None
         ext().all_reduce_fused(self.buffer_ptrs, self.signal_ptrs, self.rank, off, 0, self.seq, self.done, T, H, res,
                                summed, w, eps, w_offset, normed, self.budget_ns, self.status)
+        self._advance()
+        return normed, summed
+
+    def fits_gemm_tail(self, rows: int, cols: int) -> bool:
+        """One-shot sizes only: large steps keep the two-shot reduce-scatter + all-gather kernels."""
+        return (rows <= self.max_rows and cols == self.hidden
+                and not (rows >= self.TWO_SHOT_ROWS and self.world > 2))
+
+    def linear_reduce_norm(self, x, w, res, norm_w, eps, w_offset):
+        """(normed, summed) of sum_ranks(x @ w^T) + res in ONE launch: the GEMM writes this rank's partial tiles
+        into the current slot and the same kernel's tail signals the peers, waits for them (bounded), sums all
+        ranks' slots in rank order over NVLink peer loads, adds the residual and applies the norm."""
+        if self._failed:
+            raise CommError(self._failed)
+        from ..ops import sm100
+        T, N = x.shape[0], w.shape[0]
+        slot = self.next_partial(T, N)
+        off = slot.data_ptr() - self.base
+        ws = sm100.Workspace.get(self.device)
+        bn = sm100.pick_bn(T, False)
+        n_tt, ft = (T + bn - 1) // bn, (N + 127) // 128
+        sk = sm100._pick_split_k(n_tt, ft, x.shape[1])
+        C = ext()
+        if sk > 1 and (C.wgemm_workspace_floats(bn, False, n_tt, ft, sk) > ws.splitk.numel()
+                       or n_tt * ft > ws.counters.numel()):
+            sk = 1
+        summed = torch.empty(T, N, dtype=torch.bfloat16, device=self.device)
+        normed = torch.empty_like(summed) if norm_w is not None else None
+        C.wgemm_allreduce(w, x, slot, bn, sk, ws.splitk if sk > 1 else None, ws.counters if sk > 1 else None,
+                          ws.status, self.buffer_ptrs, self.signal_ptrs, self.rank, off, 0, self.seq, self.gemm_ctrs,
+                          res, summed, norm_w, eps, w_offset, normed, self.budget_ns, self.status)
         self._advance()
         return normed, summed
 

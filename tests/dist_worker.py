@@ -110,9 +110,12 @@ def case_engine(dev, comm_kind):
     full = {k: (v.bfloat16() if v.dim() > 1 else v) for k, v in full.items()}
     w = {k: v.to(dev) for k, v in Shard(cfg, RANK, WORLD).shard_all(full).items()}
     symm = None
+    tail = comm_kind == "tail"          # o-proj GEMM and its all-reduce as one kernel
+    if tail:
+        comm_kind = "fused"
     if comm_kind == "fused":
         symm = SymmComm(dist.group.WORLD, RANK, WORLD, dev, 1024, cfg.hidden, budget_ns=2_000_000_000)
-    pctx = ParallelCtx(RANK, WORLD, dist.group.WORLD, False, comm_kind, symm)
+    pctx = ParallelCtx(RANK, WORLD, dist.group.WORLD, False, comm_kind, symm, gemm_tail=tail)
     eng = build_engine(cfg, weights=w, device=str(dev), pctx=pctx, start=False,
                        engine_cfg=EngineConfig(ctx_size=512, max_seqs=2, block_size=64, prefill_chunk=256,
                                                prefix_cache=False))
@@ -143,7 +146,7 @@ def main():
         res = case_comm(dev)
     elif CASE == "ep":
         res = case_ep(dev)
-    elif CASE in ("engine_nccl", "engine_fused"):
+    elif CASE in ("engine_nccl", "engine_fused", "engine_tail"):
         res = case_engine(dev, CASE.split("_")[1])
     else:
         raise SystemExit(f"unknown case {CASE}")

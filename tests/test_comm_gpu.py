@@ -69,3 +69,5 @@ def test_tp_engine_fused_equals_nccl(tmp_path):
     assert len(b["tokens"]) == 12
     assert b["tokens"] == a["tokens"]
     assert b["graph_replays"] > 0
+    c = _run("engine_tail", 2, tmp_path)        # GEMM + all-reduce + residual + norm in one kernel
+    assert c["tokens"] == a["tokens"]
