@@ -55,6 +55,12 @@ def _add_engine_args(ap: argparse.ArgumentParser):
     g.add_argument("--tp-moe-ep", action="store_true", help="shard whole experts over the ranks instead of their rows")
     g.add_argument("--tp-comm", choices=["fused", "nccl"], default="fused")
     g.add_argument("--tp-replicas", type=int, default=1, help="data-parallel engine replicas")
+    g.add_argument("--tp-gemm-tail", action="store_true",
+                   help="run o-proj / down-proj and their all-reduce as one kernel (fused communicator)")
+    g.add_argument("--pp", type=int, default=1, help="pipeline stages (layers split over the GPUs, one process each)")
+    g.add_argument("--layer-split", default=None, help="layers per pipeline stage, e.g. 7,7,7,7,7,7,7,6")
+    g.add_argument("--split-last-extra", type=int, default=0, help="layers' worth of room kept free on the last stage")
+    g.add_argument("--pipeline-micro", type=int, default=2048, help="tokens per micro-chunk of a pipelined prompt")
     g.add_argument("--experts", choices=["auto", "device", "host", "cache"], default="auto")
     g.add_argument("--expert-cache-gib", type=float, default=0.0)
     g = ap.add_argument_group("sampling defaults")
@@ -94,6 +100,20 @@ def build_engine_from_args(a, start: bool = True):
         cuda_graphs=not a.no_cuda_graphs, model_name=a.alias or os.path.basename(path.rstrip("/")),
         tool_format=a.tool_format, itl_target_ms=a.itl_target, ttft_target_ms=a.ttft_target)
     pctx = None
+    if world > 1 and getattr(a, "pp", 1) > 1:
+        # pipeline stages: every rank loads only its layers, the residual travels by send / recv
+        import torch.distributed as dist
+        from ..config import PRESETS
+        from ..parallel.pipeline import PipeStage
+        pdist.init_from_env(device, comm="nccl")
+        n_layer = PRESETS[path.split(":", 1)[1]]().n_layer if path.startswith("random:") else None
+        if n_layer is None:
+            n_layer = load_model(path, "cpu", keep_layers=lambda il: False)[0].n_layer
+        split = [int(x) for x in a.layer_split.split(",")] if a.layer_split else None
+        pipe = PipeStage(rank, world, dist.group.WORLD, n_layer, split, a.pipeline_micro, a.split_last_extra)
+        cfg, w, tok, info = load_model(path, device, seed=a.seed, keep_layers=pipe.owns)
+        model = Decoder(cfg, w, None, max_position=ec.ctx_size + 8, pipe=pipe)
+        return LmEngine(model, tok, ec, start=start)
     if world > 1:
         from ..config import PRESETS  # noqa: F401
         pctx = pdist.init_from_env(device, comm="nccl", expert_parallel=a.tp_moe_ep)   # symmetric memory is attached
@@ -104,6 +124,7 @@ def build_engine_from_args(a, start: bool = True):
         import torch.distributed as dist
         pctx.symm = SymmComm(dist.group.WORLD, rank, world, torch.device(device), ec.max_batch_tokens, cfg.hidden)
         pctx.comm = "fused"
+        pctx.gemm_tail = bool(getattr(a, "tp_gemm_tail", False))
     model = Decoder(cfg, w, pctx, max_position=ec.ctx_size + 8)
     if a.experts in ("cache", "host") and cfg.n_expert:
         from ..residency.experts import slots_for_budget
@@ -126,7 +147,7 @@ def sampling_defaults(a) -> dict:
 # ------------------------------------------------------------------------------------------------ commands
 def cmd_serve(a):
     from ..server.app import ServerConfig, serve
-    tp = a.gpus or a.tp
+    tp = max(a.gpus or a.tp, getattr(a, "pp", 1))
     if tp > 1 and "RANK" not in os.environ:
         # one process per GPU: re-launch this command under torch.distributed.run; rank 0 serves HTTP
         import subprocess

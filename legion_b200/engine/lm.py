@@ -124,10 +124,12 @@ class LmEngine(Engine):
         n_blocks = max(4, (kv_tokens + c.block_size - 1) // c.block_size)
         self.pool = BlockPool(n_blocks, c.block_size)
         extra = self.mcfg.mtp_layers if c.spec == "mtp" else 0
+        owns = model.pipe.owns if getattr(model, "pipe", None) is not None else None
         self.kv = KvCache(self.mcfg, n_blocks, c.block_size, dev, model.dtype, kv_heads_local=model.n_kv_l,
-                          extra_layers=extra)
+                          extra_layers=extra, owns=owns)
         n_saved = c.prefix_cache_states if (self.hybrid and c.prefix_cache) else 0
-        self.states = StatePool(self.mcfg, c.max_seqs + n_saved + 1, dev, tp=model.pctx.tp) if self.hybrid else None
+        self.states = (StatePool(self.mcfg, c.max_seqs + n_saved + 1, dev, tp=model.pctx.tp, owns=owns)
+                       if self.hybrid else None)
         self._free_slots = list(range(c.max_seqs - 1, -1, -1))
         self.radix = RadixCache(self.pool) if c.prefix_cache else None
         self.saved = SavedStates(range(c.max_seqs, c.max_seqs + n_saved), c.block_size) if n_saved else None
@@ -145,7 +147,7 @@ class LmEngine(Engine):
             self.drafter = make_drafter(c.spec, self)
         self.eos_ids = tuple(self.tok.eos_ids)
         self._graphs = None
-        if dev.type == "cuda" and c.cuda_graphs and not model.expert_cache \
+        if dev.type == "cuda" and c.cuda_graphs and not model.expert_cache and getattr(model, "pipe", None) is None \
                 and not any(k in ("mla", "mamba2") for k in self.mcfg.layer_kinds):
             from .cuda_graphs import DecodeGraphs
             self._graphs = DecodeGraphs(self)

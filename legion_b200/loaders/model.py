@@ -18,7 +18,12 @@ from .tokenizer import BpeTokenizer, ByteTokenizer, Tokenizer
 
 
 def load_model(path: str, device="cpu", dtype=None, rank: int = 0, world: int = 1, expert_parallel: bool = False,
-               seed: int = 0) -> Tuple[ModelConfig, Dict[str, torch.Tensor], Tokenizer, dict]:
+               seed: int = 0, keep_layers=None) -> Tuple[ModelConfig, Dict[str, torch.Tensor], Tokenizer, dict]:
+    """``keep_layers(il)``: a pipeline stage keeps only the layers it owns (plus embeddings and head)."""
+    from ..models.weights import layer_of
+    keep = None
+    if keep_layers is not None:
+        keep = lambda name: layer_of(name) is None or keep_layers(layer_of(name))   # noqa: E731
     dev = torch.device(device)
     if dtype is None:
         dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
@@ -26,7 +31,7 @@ def load_model(path: str, device="cpu", dtype=None, rank: int = 0, world: int = 
     if path.startswith("random:"):
         cfg = PRESETS[path.split(":", 1)[1]]()
         shard = Shard(cfg, rank, world, expert_parallel) if world > 1 else None
-        w = random_weights(cfg, dev, dtype, seed=seed, shard=shard)
+        w = random_weights(cfg, dev, dtype, seed=seed, shard=shard, keep=keep)
         return cfg, w, ByteTokenizer(cfg.vocab), info
     if os.path.isdir(path):
         from .hf_map import load_hf
@@ -50,6 +55,8 @@ def load_model(path: str, device="cpu", dtype=None, rank: int = 0, world: int = 
                 tok.chat_template = md["tokenizer.chat_template"]
     else:
         raise ValueError(f"cannot tell what kind of model {path!r} is (expected .gguf, an HF directory or random:<preset>)")
+    if keep is not None:
+        w = {k: v for k, v in w.items() if keep(k)}
     if world > 1:
         sh = Shard(cfg, rank, world, expert_parallel)
         w = {k: sh.slice(k, v).to(dev) for k, v in w.items()}

@@ -68,11 +68,11 @@ class KvCache:
     """Per-layer paged K/V tensors ``[n_blocks, page, kv_heads, dim]`` (MLA layers: one latent row)."""
 
     def __init__(self, cfg: ModelConfig, n_blocks: int, page: int, device, dtype, kv_heads_local: Optional[int] = None,
-                 extra_layers: int = 0):
+                 extra_layers: int = 0, owns=None):
         self.page, self.n_blocks = page, n_blocks
         self.k: Dict[int, torch.Tensor] = {}
         self.v: Dict[int, torch.Tensor] = {}
-        layers = list(cfg.kv_layers())
+        layers = [il for il in cfg.kv_layers() if owns is None or owns(il)]   # pipeline stage: own layers only
         kinds = {il: cfg.layer_kinds[il] for il in layers}
         for j in range(extra_layers):  # MTP blocks keep their own KV in the same block layout
             layers.append(cfg.n_layer + j)
@@ -109,11 +109,13 @@ class StatePool:
     """Recurrent state in fixed slots: conv history + delta-rule / SSM state, float32
     (``src/model/core/state.rs:1297``)."""
 
-    def __init__(self, cfg: ModelConfig, n_slots: int, device, tp: int = 1):
+    def __init__(self, cfg: ModelConfig, n_slots: int, device, tp: int = 1, owns=None):
         self.n_slots = n_slots
         self.conv: Dict[int, torch.Tensor] = {}
         self.ssm: Dict[int, torch.Tensor] = {}
         for il in cfg.recurrent_layers():
+            if owns is not None and not owns(il):
+                continue
             kind = cfg.layer_kinds[il]
             if kind == "gdn":
                 C = cfg.gdn_conv_channels() // tp
@@ -143,10 +145,11 @@ class Decoder:
     """Weights + forward. ``weights`` uses the canonical names of ``models.weights``."""
 
     def __init__(self, cfg: ModelConfig, weights: Dict[str, torch.Tensor], pctx: Optional[ParallelCtx] = None,
-                 max_position: Optional[int] = None):
+                 max_position: Optional[int] = None, pipe=None):
         self.cfg = cfg
         self.w = weights
         self.pctx = pctx or ParallelCtx.single()
+        self.pipe = pipe          # parallel.pipeline.PipeStage: this rank runs layers [pipe.lo, pipe.hi)
         dev = weights["tok_embd"].device
         self.device = dev
         self.dtype = weights["tok_embd"].dtype
@@ -348,7 +351,56 @@ class Decoder:
     def embed(self, token_ids):
         return ops.embed(token_ids, self.w["tok_embd"])
 
+    def _forward_pipe(self, b: StepBatch, kv: KvCache, st: Optional[StatePool], want_logits: bool) -> StepOutput:
+        """Pipeline-parallel forward: this rank's layers over the step's micro-chunks. The receive of micro-chunk
+        c+1 is posted before c is computed and sends are asynchronous, so neighbouring stages overlap."""
+        cfg, w, pc, pipe = self.cfg, self.w, self.pctx, self.pipe
+        chunks = pipe.plan(b)
+        sizes = [int(c.token_ids.shape[0]) if c.embeds is None else int(c.embeds.shape[0]) for c in chunks]
+        recvs, sends, outs = {}, [], []
+        if not pipe.first:
+            recvs[0] = pipe.irecv(sizes[0], cfg.hidden, self.dtype, self.device)
+        for i, c in enumerate(chunks):
+            if pipe.first:
+                cur, res = (c.embeds if c.embeds is not None else self.embed(c.token_ids)), None
+            else:
+                buf, work = recvs.pop(i)
+                if i + 1 < len(chunks):
+                    recvs[i + 1] = pipe.irecv(sizes[i + 1], cfg.hidden, self.dtype, self.device)
+                work.wait()
+                cur, res = None, buf
+            normed = None
+            for il in range(pipe.lo, pipe.hi):
+                nxt = w[f"l{il + 1}.attn_norm"] if il + 1 < pipe.hi else None
+                cur, res, normed = self._layer(f"l{il}", il, cfg.layer_kinds[il], cfg.is_moe_layer(il), cur, res, c, kv,
+                                               st, normed, nxt)
+            hid = pc.full_hidden(cur, res)
+            if pipe.last:
+                outs.append(hid)
+            else:
+                sends.append((hid, pipe.isend(hid)))
+        for _, work in sends:
+            work.wait()
+        T = sum(sizes)
+        R = T if b.logit_rows is None else int(b.logit_rows.shape[0])
+        if pipe.last:
+            last = outs[0] if len(outs) == 1 else torch.cat(outs, 0)
+            rows = last if b.logit_rows is None else last.index_select(0, b.logit_rows)
+            hidden, _ = ops.rmsnorm(rows, w["output_norm"], cfg.rms_eps, cfg.norm_offset)
+            logits = self.logits(hidden) if want_logits else None
+        else:
+            last = None
+            hidden = torch.empty(R, cfg.hidden, dtype=self.dtype, device=self.device)
+            logits = torch.empty(R, cfg.vocab, dtype=torch.float32, device=self.device) if want_logits else None
+        pipe.broadcast_from_last(hidden)
+        if want_logits:
+            pipe.broadcast_from_last(logits)
+        pc.end_step()
+        return StepOutput(hidden=hidden, logits=logits, last_hidden=last, captures={})
+
     def forward(self, b: StepBatch, kv: KvCache, st: Optional[StatePool], want_logits: bool = True) -> StepOutput:
+        if self.pipe is not None:
+            return self._forward_pipe(b, kv, st, want_logits)
         cfg, w, pc = self.cfg, self.w, self.pctx
         x = b.embeds if b.embeds is not None else self.embed(b.token_ids)
         resid = None

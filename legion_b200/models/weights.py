@@ -115,10 +115,18 @@ def is_fp32_weight(name: str) -> bool:
     return leaf.endswith("norm") or leaf in ("A", "D", "dt_bias", "conv_w", "conv_b", "router_bias")
 
 
+def layer_of(name: str) -> Optional[int]:
+    """Layer index of a canonical weight name (``l12.attn.qkv`` -> 12), None for embeddings / head / MTP."""
+    if name.startswith("l") and "." in name and name[1:name.index(".")].isdigit():
+        return int(name[1:name.index(".")])
+    return None
+
+
 def random_weights(cfg: ModelConfig, device="cpu", dtype=torch.float32, seed: int = 0, std: float = 0.02,
-                   shard: Optional["Shard"] = None) -> Dict[str, torch.Tensor]:
+                   shard: Optional["Shard"] = None, keep=None) -> Dict[str, torch.Tensor]:
     """N(0, std) matrices; norm weights 1, A in (-1, -0.1), dt_bias small. With ``shard`` only this rank's
-    slices are created (device-side generation for models too large for the host)."""
+    slices are created (device-side generation for models too large for the host). ``keep(name)`` drops
+    tensors a pipeline stage does not own; the kept ones equal those of the full model."""
     device = torch.device(device)
     out: Dict[str, torch.Tensor] = {}
     g = torch.Generator(device="cpu").manual_seed(seed)
@@ -128,6 +136,9 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=torch.float32, seed: in
         wd = torch.float32 if is_fp32_weight(name) else dtype
         if shard is not None:
             shp = shard.local_shape(name, shp)
+        dropped = keep is not None and not keep(name)
+        if dropped and (leaf.endswith("norm") or leaf == "D" or (device.type == "cuda" and wd == torch.bfloat16)):
+            continue                      # nothing drawn from the host generator for these
         if leaf.endswith("norm"):
             t = torch.ones(shp, dtype=torch.float32, device=device) - cfg.norm_offset
         elif leaf == "A":
@@ -144,7 +155,8 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=torch.float32, seed: in
             ext().randn_bf16(t, std, seed * 1000003 + idx)
         else:
             t = (torch.randn(shp, generator=g) * std).to(device=device, dtype=wd)
-        out[name] = t.to(wd)
+        if not dropped:                   # dropped host-generated tensors still advanced the generator
+            out[name] = t.to(wd)
     return out
 
 

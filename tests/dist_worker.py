@@ -137,6 +137,48 @@ def case_engine(dev, comm_kind):
     return {"tokens": toks, "graph_replays": replays}
 
 
+def case_pp(dev):
+    """Pipeline stages over NCCL send / recv: same tokens as the whole model on one GPU."""
+    from legion_b200.config import ModelConfig
+    from legion_b200.engine.lm import EngineConfig, LmEngine, build_engine
+    from legion_b200.engine.types import GenerateRequest, SamplingParams
+    from legion_b200.loaders.tokenizer import ByteTokenizer
+    from legion_b200.models.decoder import Decoder
+    from legion_b200.models.weights import layer_of, random_weights
+    from legion_b200.parallel.pipeline import PipeStage
+    cfg = ModelConfig(arch="qwen3moe", n_layer=4, hidden=512, vocab=2048, n_head=8, n_kv_head=2, head_dim=128,
+                      n_expert=8, top_k=2, expert_ff=256)
+    full = random_weights(cfg, "cpu", torch.float32, seed=0, std=0.05)
+    full = {k: (v.bfloat16() if v.dim() > 1 else v) for k, v in full.items()}
+    ecfg = dict(ctx_size=1024, max_seqs=2, block_size=64, prefill_chunk=512, prefix_cache=False)
+    prompt = torch.randint(0, 255, (300,), generator=torch.Generator().manual_seed(1)).tolist()
+
+    def run(eng):
+        s = eng.generate(GenerateRequest(prompt_tokens=prompt, sampling=SamplingParams(max_tokens=10, ignore_eos=True)))
+        eng._drain(block=False)
+        for _ in range(100):
+            eng._admit()
+            if not eng.running and len(eng.waiting) == 0:
+                break
+            eng.step()
+        return s.collect().token_ids
+
+    res = {}
+    for micro in (4096, 128):
+        pipe = PipeStage(RANK, WORLD, dist.group.WORLD, cfg.n_layer, micro_tokens=micro)
+        w = {k: v.to(dev) for k, v in full.items() if layer_of(k) is None or pipe.owns(layer_of(k))}
+        model = Decoder(cfg, w, None, max_position=1032, pipe=pipe)
+        eng = LmEngine(model, ByteTokenizer(cfg.vocab), EngineConfig(device=str(dev), **ecfg), start=False)
+        res[f"pp_micro{micro}"] = run(eng)
+        res[f"chunks_micro{micro}"] = pipe.stats["micro_chunks"]
+        say("pipeline run, micro", micro, "chunks", pipe.stats["micro_chunks"])
+    if RANK == 0:
+        eng = build_engine(cfg, weights={k: v.to(dev) for k, v in full.items()}, device=str(dev), start=False,
+                           engine_cfg=EngineConfig(cuda_graphs=False, **ecfg))
+        res["single"] = run(eng)
+    return res
+
+
 def main():
     torch.cuda.set_device(RANK)
     dev = torch.device("cuda", RANK)
@@ -146,6 +188,8 @@ def main():
         res = case_comm(dev)
     elif CASE == "ep":
         res = case_ep(dev)
+    elif CASE == "pp":
+        res = case_pp(dev)
     elif CASE in ("engine_nccl", "engine_fused", "engine_tail"):
         res = case_engine(dev, CASE.split("_")[1])
     else:

@@ -71,3 +71,10 @@ def test_tp_engine_fused_equals_nccl(tmp_path):
     assert b["graph_replays"] > 0
     c = _run("engine_tail", 2, tmp_path)        # GEMM + all-reduce + residual + norm in one kernel
     assert c["tokens"] == a["tokens"]
+
+
+def test_pipeline_stages_over_nccl_p2p(tmp_path):
+    res = _run("pp", 2, tmp_path)
+    assert res["pp_micro4096"] == res["single"] and len(res["single"]) == 10
+    assert res["chunks_micro128"] >= 3
+    assert res["pp_micro128"][0] == res["single"][0]      # micro-chunked prefill: same first token
