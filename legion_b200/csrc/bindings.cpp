@@ -398,6 +398,25 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("wgemm_workspace_floats", [](int64_t bn, bool dual, int64_t n_tok_tiles, int64_t feat_tiles, int64_t split_k) {
     return int64_t(lb::wgemm_workspace_floats(int(bn), dual, int(n_tok_tiles), int(feat_tiles), int(split_k)));
   });
+  m.def("token_logprobs", [](const Tensor& logits, const Tensor& chosen, int64_t n_top, Tensor& chosen_lp,
+                             Tensor& top_ids, Tensor& top_lp) {
+    TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.stride(1) == 1, "token_logprobs: float32 logits");
+    c10::cuda::CUDAGuard guard(logits.device());
+    TORCH_CHECK(lb::token_logprobs_launch(logits.data_ptr<float>(), logits.stride(0), int(logits.size(0)),
+                                          int(logits.size(1)), chosen.data_ptr<int>(), int(n_top),
+                                          chosen_lp.data_ptr<float>(), top_ids.data_ptr<int>(),
+                                          top_lp.data_ptr<float>(), cur_stream()) == 0,
+                "token_logprobs: at most 20 alternatives");
+  });
+  m.def("spec_accept", [](const Tensor& target, const Tensor& cu, const Tensor& draft, const Tensor& n_draft,
+                          Tensor& accepted, Tensor& bonus, Tensor& any_rejected) {
+    c10::cuda::CUDAGuard guard(target.device());
+    TORCH_CHECK(draft.dim() == 2 && draft.is_contiguous(), "spec_accept: draft [B, k]");
+    TORCH_CHECK(lb::spec_accept_launch(target.data_ptr<int>(), cu.data_ptr<int>(), draft.data_ptr<int>(),
+                                       int(draft.size(1)), n_draft.data_ptr<int>(), int(draft.size(0)),
+                                       accepted.data_ptr<int>(), bonus.data_ptr<int>(), any_rejected.data_ptr<int>(),
+                                       cur_stream()) == 0, "spec_accept failed");
+  });
   m.def("set_pdl", [](bool on) { lb::set_pdl(on); });
   m.def("pdl_enabled", []() { return lb::pdl_enabled(); });
   bind_gdn(m);

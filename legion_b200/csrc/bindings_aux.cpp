@@ -215,6 +215,13 @@ void bind_quant(pybind11::module_& m) {
                                            reinterpret_cast<uint8_t*>(out.data_ptr()), scale.data_ptr<float>(),
                                            cur_stream()) == 0, "fp8_block_quant failed");
   });
+  m.def("gguf_dequant", [](const Tensor& raw, int64_t ggml_type, Tensor& out) {
+    TORCH_CHECK(raw.scalar_type() == at::kByte && raw.is_contiguous() && out.scalar_type() == at::kBFloat16 &&
+                    out.is_contiguous(), "gguf_dequant: raw uint8 -> bf16");
+    c10::cuda::CUDAGuard guard(raw.device());
+    TORCH_CHECK(lb::gguf_dequant_launch(raw.data_ptr(), int(ggml_type), out.numel(), out.data_ptr(), cur_stream()) == 0,
+                "gguf_dequant: unsupported tensor type or size");
+  });
   m.def("randn_bf16", [](Tensor& out, double stdv, int64_t seed) {
     c10::cuda::CUDAGuard guard(out.device());
     TORCH_CHECK(lb::randn_bf16_launch(out.data_ptr(), out.numel(), float(stdv), uint64_t(seed), cur_stream()) == 0,

@@ -75,4 +75,9 @@ int penalties_mask_launch(float* logits, long ld, int rows, int V, const int* co
                           const float* presence, const float* frequency, const float* repetition,
                           const unsigned int* mask, int mask_words, cudaStream_t s);
 
+int token_logprobs_launch(const float* logits, long ld, int rows, int V, const int* chosen, int n_top,
+                          float* chosen_lp, int* top_ids, float* top_lp, cudaStream_t s);
+int spec_accept_launch(const int* target, const int* cu, const int* draft, int max_draft, const int* n_draft, int B,
+                       int* accepted, int* bonus, int* any_rejected, cudaStream_t s);
+
 }  // namespace lb

@@ -148,10 +148,20 @@ class GgufFile:
         ti = self.tensors[name]
         return dequantize(self.raw(name), ti.ggml_type, ti.shape)
 
-    def torch(self, name: str, dtype=None):
+    DEVICE_TYPES = {2, 8, 12, 13, 14, 20}       # block formats with a device de-quantisation kernel
+
+    def torch(self, name: str, dtype=None, device=None):
+        """``device``: a CUDA device moves the raw block bytes there and expands them to bf16 with the
+        ``gguf_dequant`` kernel (the host never touches the elements); other tensors go through numpy."""
         import torch
         ti = self.tensors[name]
         raw = self.raw(name)
+        if device is not None and torch.device(device).type == "cuda" and ti.ggml_type in self.DEVICE_TYPES:
+            from ..ops.sm100 import ext
+            dev_raw = torch.from_numpy(np.array(raw, copy=True)).to(device, non_blocking=True)
+            out = torch.empty(ti.shape, dtype=torch.bfloat16, device=device)
+            ext().gguf_dequant(dev_raw, ti.ggml_type, out)
+            return out.to(dtype) if dtype is not None else out
         if ti.type_name == "BF16":
             t = torch.frombuffer(bytearray(raw.tobytes()), dtype=torch.bfloat16).view(ti.shape)
         else:

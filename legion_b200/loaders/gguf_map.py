@@ -251,7 +251,7 @@ def load_gguf(path: str, device="cpu", dtype=torch.float32):
     gf = GgufFile(path)
     cfg = config_from_gguf(gf.metadata)
     has = lambda n: n in gf.tensors
-    get = lambda n: gf.torch(n)
+    get = lambda n: gf.torch(n, device=device if torch.device(device).type == "cuda" else None)
     w = from_gguf_tensors(cfg, get, has)
     if cfg.vocab in (0, None):
         cfg.vocab = w["tok_embd"].shape[0]

@@ -440,6 +440,29 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[Moe
     return out, normed
 
 
+def token_logprobs(logits, chosen, n_top: int = 0):
+    """(log-probability of chosen[r] in row r, top-n token ids [R, n], their log-probabilities [R, n])."""
+    C = ext()
+    R = logits.shape[0]
+    lp = torch.empty(R, dtype=torch.float32, device=logits.device)
+    ids = torch.empty(R, max(n_top, 1), dtype=torch.int32, device=logits.device)
+    tl = torch.empty(R, max(n_top, 1), dtype=torch.float32, device=logits.device)
+    C.token_logprobs(logits, chosen.int(), n_top, lp, ids, tl)
+    return lp, ids[:, :n_top], tl[:, :n_top]
+
+
+def spec_accept(target, cu, draft, n_draft):
+    """Greedy acceptance on the device: (accepted drafts per sequence, the token after the accepted prefix,
+    flag: some draft was rejected)."""
+    C = ext()
+    B = draft.shape[0]
+    acc = torch.empty(B, dtype=torch.int32, device=target.device)
+    bonus = torch.empty(B, dtype=torch.int32, device=target.device)
+    rej = torch.zeros(1, dtype=torch.int32, device=target.device)
+    C.spec_accept(target.int(), cu.int(), draft.int().contiguous(), n_draft.int(), acc, bonus, rej)
+    return acc, bonus, rej
+
+
 def argmax(logits, out=None):
     C = ext()
     rows, V = logits.shape

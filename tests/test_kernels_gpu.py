@@ -368,3 +368,49 @@ def test_wait_deadline_sets_status_and_context_survives():
     torch.cuda.synchronize()
     assert int(status.item()) == 5
     assert float((torch.ones(4, device=DEV) * 2).sum()) == 8.0
+
+
+def test_token_logprobs_and_spec_accept():
+    torch.manual_seed(5)
+    R, V, n = 7, 151936, 5
+    logits = torch.randn(R, V, device=DEV) * 3
+    chosen = torch.randint(0, V, (R,), device=DEV, dtype=torch.int32)
+    lp, ids, tl = sm().token_logprobs(logits, chosen, n)
+    ref_lp = torch.log_softmax(logits.double(), -1)
+    close(lp, ref_lp.gather(1, chosen.long()[:, None])[:, 0], 1e-4, 1e-4)
+    tv, ti = ref_lp.topk(n, -1)
+    assert torch.equal(ids.long().cpu(), ti.cpu())
+    close(tl, tv, 1e-4, 1e-4)
+    # greedy acceptance: 3 sequences with 4, 2 and 0 drafts
+    cu = torch.tensor([0, 5, 8, 9], device=DEV, dtype=torch.int32)
+    target = torch.tensor([11, 12, 13, 99, 15, 21, 22, 23, 31], device=DEV, dtype=torch.int32)
+    draft = torch.tensor([[11, 12, 13, 14], [21, 22, 0, 0], [0, 0, 0, 0]], device=DEV, dtype=torch.int32)
+    nd = torch.tensor([4, 2, 0], device=DEV, dtype=torch.int32)
+    acc, bonus, rej = sm().spec_accept(target, cu, draft, nd)
+    assert acc.tolist() == [3, 2, 0] and bonus.tolist() == [99, 23, 31] and int(rej.item()) == 1
+
+
+@pytest.mark.parametrize("tname", ["Q8_0", "Q4_0", "Q4_K", "Q5_K", "Q6_K", "IQ4_NL"])
+def test_gguf_dequant_kernel_matches_host(tname):
+    """Random block bytes (with sane fp16 scales) expand to the same values on the device as in numpy."""
+    import numpy as np
+    from legion_b200.loaders.gguf import GGML_TYPES, TYPE_ID, dequantize
+    from legion_b200.ops.sm100 import ext
+    tid = TYPE_ID[tname]
+    _, be, bb = GGML_TYPES[tid]
+    n_blocks = 64 * (256 // be)
+    rng = np.random.default_rng(3)
+    raw = rng.integers(0, 256, size=(n_blocks, bb), dtype=np.uint8)
+    scale = (rng.random(n_blocks) * 0.1 + 0.01).astype(np.float16).view(np.uint8).reshape(-1, 2)
+    if tname in ("Q8_0", "Q4_0", "IQ4_NL"):
+        raw[:, 0:2] = scale
+    elif tname in ("Q4_K", "Q5_K"):
+        raw[:, 0:2] = scale
+        raw[:, 2:4] = scale[::-1]
+    else:
+        raw[:, 208:210] = scale
+    shape = (n_blocks * be // 256, 256)
+    want = dequantize(raw.reshape(-1), tid, shape)
+    out = torch.empty(shape, dtype=torch.bfloat16, device=DEV)
+    ext().gguf_dequant(torch.from_numpy(raw.reshape(-1).copy()).to(DEV), tid, out)
+    close(out, torch.from_numpy(want).bfloat16(), 1e-2, 1e-3)
