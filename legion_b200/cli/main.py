@@ -49,6 +49,9 @@ def _add_engine_args(ap: argparse.ArgumentParser):
     g.add_argument("--spec-max-batch", type=int, default=8)
     g.add_argument("--spec-draft-model", default=None)
     g.add_argument("--spec-p-min", type=float, default=0.5)
+    g.add_argument("--spec-policy", choices=["fixed", "cost"], default="fixed",
+                   help="cost: pick the draft depth per step from the measured acceptance rate and batch size")
+    g.add_argument("--no-even-chunks", action="store_true", help="full prompt chunks plus a short tail")
     g = ap.add_argument_group("parallelism")
     g.add_argument("--tp", type=int, default=1, help="tensor-parallel ranks (one process per GPU, spawned by serve)")
     g.add_argument("--gpus", type=int, default=None, help="alias of --tp on a single node")
@@ -98,7 +101,8 @@ def build_engine_from_args(a, start: bool = True):
         fair_share=a.fair_share, kv_admission=a.kv_admission, spec=a.spec, spec_k=a.spec_k,
         spec_max_batch=a.spec_max_batch, deterministic=a.deterministic, device=device, seed=a.seed,
         cuda_graphs=not a.no_cuda_graphs, model_name=a.alias or os.path.basename(path.rstrip("/")),
-        tool_format=a.tool_format, itl_target_ms=a.itl_target, ttft_target_ms=a.ttft_target)
+        tool_format=a.tool_format, itl_target_ms=a.itl_target, ttft_target_ms=a.ttft_target,
+        spec_policy=getattr(a, "spec_policy", "fixed"), even_chunks=not getattr(a, "no_even_chunks", False))
     pctx = None
     if world > 1 and getattr(a, "pp", 1) > 1:
         # pipeline stages: every rank loads only its layers, the residual travels by send / recv

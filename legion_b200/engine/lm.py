@@ -68,6 +68,8 @@ class EngineConfig:
     tool_format: str = "hermes"
     reasoning: bool = True
     itl_target_ms: float = 0.0
+    even_chunks: bool = True           # cut a prompt into equal chunks instead of full chunks + a short tail
+    spec_policy: str = "fixed"        # fixed | cost: choose the draft depth per step from measured acceptance
     ttft_target_ms: float = 0.0
 
 
@@ -131,6 +133,7 @@ class LmEngine(Engine):
         self.states = (StatePool(self.mcfg, c.max_seqs + n_saved + 1, dev, tp=model.pctx.tp, owns=owns)
                        if self.hybrid else None)
         self._free_slots = list(range(c.max_seqs - 1, -1, -1))
+        self._slo = {"decode_ms": 0.0, "ms_per_prompt_token": 0.0}
         self.radix = RadixCache(self.pool) if c.prefix_cache else None
         self.saved = SavedStates(range(c.max_seqs, c.max_seqs + n_saved), c.block_size) if n_saved else None
         self.waiting = WaitQueue(c.scheduling_policy, c.fair_share, c.max_waiting)
@@ -365,6 +368,10 @@ class LmEngine(Engine):
 
     def _admit(self):
         c = self.cfg
+        if c.deterministic and self.running:
+            # admission waves: a batch is formed only when the engine is idle and runs to completion, so what a
+            # request is batched with does not depend on when its neighbours arrived (``src/engine/lm/waves.rs``)
+            return
         while len(self.waiting) and len(self.running) < c.max_seqs and self._free_slots:
             seq: Seq = self.waiting.peek()
             if not self._place(seq):
@@ -479,6 +486,57 @@ class LmEngine(Engine):
                     return False
 
     # ------------------------------------------------------------------ one step
+    # ------------------------------------------------------------------ step-time model (SLO budget, spec depth)
+    def _observe_step(self, n_decode_rows: int, n_prompt_tokens: int, ms: float):
+        """Two-parameter model of the step time: base (a decode-only step) + cost per prompt token, both EWMAs
+        of what was measured (the reference's ``slo.rs`` fits the same shape from its step log)."""
+        m = self._slo
+        if n_prompt_tokens == 0:
+            m["decode_ms"] = ms if m["decode_ms"] == 0 else 0.8 * m["decode_ms"] + 0.2 * ms
+        elif n_prompt_tokens >= 32:
+            per = max(0.0, ms - m["decode_ms"] * (1 if n_decode_rows else 0)) / n_prompt_tokens
+            m["ms_per_prompt_token"] = per if m["ms_per_prompt_token"] == 0 else 0.8 * m["ms_per_prompt_token"] + 0.2 * per
+
+    def slo_budget(self, n_decoding: int, first_chunk: bool) -> int:
+        """Prompt tokens a step may carry so that decoding sequences keep ``itl_target_ms`` between tokens (or, with
+        nothing decoding, so that a first chunk meets ``ttft_target_ms``). 0 = no limit known yet."""
+        c, m = self.cfg, self._slo
+        per = m["ms_per_prompt_token"]
+        if per <= 0:
+            return 0
+        if n_decoding and c.itl_target_ms > 0:
+            return max(16, int((c.itl_target_ms - m["decode_ms"]) / per))
+        if first_chunk and c.ttft_target_ms > 0:
+            return max(16, int(c.ttft_target_ms / per))
+        return 0
+
+    def _chunk_len(self, remaining: int, cap: int) -> int:
+        """Length of the next prompt chunk: at most ``cap``; with even chunks the prompt's remainder is cut into
+        equal parts (no short tail step, ``src/engine/lm/even.rs``)."""
+        if remaining <= cap or not self.cfg.even_chunks:
+            return min(remaining, cap)
+        parts = -(-remaining // cap)
+        return -(-remaining // parts)
+
+    def _spec_depth(self, n_decode: int) -> int:
+        """Draft depth for this step. ``cost`` policy: expected tokens per step with depth k is
+        sum_{i<=k} p^i for acceptance rate p; a verify step of k extra rows per sequence costs about
+        (1 + k * n_decode * row_cost) decode steps, so pick the k with the best tokens / cost ratio."""
+        c = self.cfg
+        if c.spec_policy != "cost":
+            return c.spec_k
+        st = self._stats
+        drafted = max(1, st.spec_draft_tokens)
+        p = min(0.98, max(0.05, st.spec_accepted_tokens / drafted)) if drafted > 32 else 0.6
+        row_cost = 0.02                      # relative cost of one more verify row next to a decode step
+        best_k, best = 0, 1.0
+        for k in range(1, c.spec_k + 1):
+            tokens = sum(p ** i for i in range(0, k + 1))
+            cost = 1.0 + k * n_decode * row_cost
+            if tokens / cost > best:
+                best_k, best = k, tokens / cost
+        return best_k
+
     def step(self):
         t0 = time.perf_counter()
         c = self.cfg
@@ -486,11 +544,14 @@ class LmEngine(Engine):
         prefill = [s for s in self.running if s.phase == "prefill"]
         # drafts for this step (model-free drafters propose now; model drafters proposed after the last step)
         use_spec = self.drafter is not None and 0 < len(decode) <= c.spec_max_batch
+        depth = self._spec_depth(len(decode)) if use_spec else 0
         for s in decode:
-            if not use_spec or s.constraint is not None:
+            if not use_spec or s.constraint is not None or depth == 0:
                 s.drafts = []
             elif self.drafter.model_free:
-                s.drafts = self.drafter.propose(s, c.spec_k)
+                s.drafts = self.drafter.propose(s, depth)
+            else:
+                s.drafts = s.drafts[:depth]
             room = s.req.sampling.max_tokens - s.n_out - 1
             s.drafts = s.drafts[:max(0, min(room, c.ctx_size - len(s.tokens) - 1))]
         rows: List[Tuple[Seq, int, int]] = []   # (seq, first position, n tokens)
@@ -503,12 +564,15 @@ class LmEngine(Engine):
                 continue
             rows.append((s, len(s.tokens) - 1, n))
         budget = c.max_batch_tokens - sum(r[2] for r in rows)
+        slo = self.slo_budget(len(rows), first_chunk=bool(prefill) and prefill[0].n_computed == 0)
+        if slo:
+            budget = min(budget, slo)
         for s in prefill:
             if s not in self.running:
                 continue
             if budget <= 0:
                 break
-            take = min(c.prefill_chunk, s.n_prompt - s.n_computed, budget)
+            take = min(self._chunk_len(s.n_prompt - s.n_computed, c.prefill_chunk), budget)
             for sp in s.save_points:            # end the chunk at the next snapshot position
                 if s.n_computed < sp < s.n_computed + take:
                     take = sp - s.n_computed
@@ -532,6 +596,8 @@ class LmEngine(Engine):
         else:
             self._forward_and_finish(rows, verify=False)
         dt = (time.perf_counter() - t0) * 1000
+        self._observe_step(sum(1 for r in rows if r[0].phase == "decode" or r[2] == 1),
+                           sum(r[2] for r in rows if r[2] > 1 and r not in verify_rows), dt)
         st = self._stats
         st.steps += 1
         st.step_ms_ewma = dt if st.step_ms_ewma == 0 else 0.8 * st.step_ms_ewma + 0.2 * dt

@@ -198,3 +198,49 @@ def test_priority_and_fair_share_order():
     f.push("a1", key="a")
     f.push("b1", key="b")
     assert f.pop() == "b1"
+
+
+def test_even_chunks_slo_budget_and_waves():
+    """Prompt chunking rules, the step-time model behind --itl-target, deterministic admission waves and the
+    cost-based draft depth."""
+    from legion_b200.config import tiny_dense
+    from legion_b200.engine.lm import EngineConfig, build_engine
+    from legion_b200.engine.types import GenerateRequest, SamplingParams
+    cfg = tiny_dense()
+    eng = build_engine(cfg, engine_cfg=EngineConfig(ctx_size=512, max_seqs=4, block_size=16, prefill_chunk=64,
+                                                    prefix_cache=False, deterministic=True, itl_target_ms=50.0),
+                       start=False)
+    # even chunks: 130 tokens at cap 64 -> 3 chunks of 44/43/43 instead of 64/64/2
+    assert eng._chunk_len(130, 64) == 44 and eng._chunk_len(86, 64) == 43 and eng._chunk_len(43, 64) == 43
+    eng.cfg.even_chunks = False
+    assert eng._chunk_len(130, 64) == 64
+    eng.cfg.even_chunks = True
+    # step-time model: 10 ms decode steps, 0.5 ms per prompt token -> 80 prompt tokens fit a 50 ms ITL target
+    for _ in range(20):
+        eng._observe_step(4, 0, 10.0)
+        eng._observe_step(4, 100, 60.0)
+    assert 70 <= eng.slo_budget(4, False) <= 90
+    assert eng.slo_budget(0, False) == 0
+    # waves: the second request is not admitted while the first one runs
+    prompt = list(range(1, 40))
+    s1 = eng.generate(GenerateRequest(prompt_tokens=prompt, sampling=SamplingParams(max_tokens=4, ignore_eos=True)))
+    eng._drain(block=False)
+    eng._admit()
+    eng.step()
+    s2 = eng.generate(GenerateRequest(prompt_tokens=prompt, sampling=SamplingParams(max_tokens=4, ignore_eos=True)))
+    eng._drain(block=False)
+    eng._admit()
+    assert len(eng.running) == 1 and len(eng.waiting) == 1
+    for _ in range(50):
+        eng._admit()
+        if not eng.running and len(eng.waiting) == 0:
+            break
+        eng.step()
+    assert s1.collect().token_ids == s2.collect().token_ids
+    # draft depth: high acceptance and few sequences -> deep drafts; low acceptance and many -> none
+    eng.cfg.spec_policy, eng.cfg.spec_k = "cost", 6
+    eng._stats.spec_draft_tokens, eng._stats.spec_accepted_tokens = 1000, 900
+    deep = eng._spec_depth(1)
+    eng._stats.spec_accepted_tokens = 100
+    shallow = eng._spec_depth(8)
+    assert deep >= 4 and shallow <= 1
