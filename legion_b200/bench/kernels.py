@@ -125,6 +125,15 @@ def bench_layer_parts(rows):
     n_act = int(torch.unique(ids).numel())
     add("moe_experts_dense", lambda: sm100.moe_experts(x, ids, wts, wgu, wd, F, residual=res, norm=(nw, 1e-6, 0.0),
                                                        routing=routing), n_act * 3 * H * F * 2)
+    from legion_b200.ops.sm100 import QWeight
+    qgu = QWeight(torch.randint(0, 256, (E, 2 * F, H // 2), device=dev, dtype=torch.uint8),
+                  torch.randint(48, 64, (E, 2 * F, H // 16), device=dev, dtype=torch.uint8),
+                  torch.ones(2 * E, device=dev))
+    qd = QWeight(torch.randint(0, 256, (E, H, F // 2), device=dev, dtype=torch.uint8),
+                 torch.randint(48, 64, (E, H, F // 16), device=dev, dtype=torch.uint8), torch.ones(E, device=dev))
+    add("moe_experts_dense_nvfp4", lambda: sm100.moe_experts(x, ids, wts, qgu, qd, F, residual=res,
+                                                            norm=(nw, 1e-6, 0.0), routing=routing),
+        n_act * 3 * H * F * 9 // 16)
     add("moe_experts_gather", lambda: sm100.moe_experts(x, ids, wts, wgu, wd, F, residual=res, norm=(nw, 1e-6, 0.0)),
         n_act * 3 * H * F * 2)
     # the MoE pieces on their own
@@ -172,6 +181,29 @@ def bench_decode_pages(rows):
         rows.append(dict(kernel="paged_decode", Hq=Hq, Hkv=Hkv, page=page, splits=splits, us=ms * 1e3,
                          gbs=byts / ms / 1e6, frac_hbm=byts / ms / 1e6 / hbm, peaks=src))
         print(rows[-1], flush=True)
+
+
+def bench_moe_nvfp4(rows):
+    """Routed experts of a 30B-A3B-shaped layer at 16 tokens with the weights kept in NVFP4 (graph-replayed)."""
+    from legion_b200.ops import sm100
+    from legion_b200.ops.sm100 import QWeight
+    hbm, tf, src = peaks()
+    T, H, E, k, F = 16, 2048, 128, 8, 768
+    dev = "cuda"
+    x = torch.randn(T, H, device=dev).bfloat16()
+    w_r = (torch.randn(E, H, device=dev) * 0.02).bfloat16()
+    routing = sm100.router(x, w_r, k)
+    n_act = int(torch.unique(routing.ids).numel())
+    qgu = QWeight(torch.randint(0, 256, (E, 2 * F, H // 2), device=dev, dtype=torch.uint8),
+                  torch.randint(48, 64, (E, 2 * F, H // 16), device=dev, dtype=torch.uint8),
+                  torch.ones(2 * E, device=dev))
+    qd = QWeight(torch.randint(0, 256, (E, H, F // 2), device=dev, dtype=torch.uint8),
+                 torch.randint(48, 64, (E, H, F // 16), device=dev, dtype=torch.uint8), torch.ones(E, device=dev))
+    ms = timeit_graph(lambda: sm100.moe_experts(x, routing.ids, routing.wts, qgu, qd, F, routing=routing))
+    byts = n_act * 3 * H * F * 9 // 16
+    rows.append(dict(kernel="moe_experts_nvfp4", T=T, active_experts=n_act, us=ms * 1e3, gbs=byts / ms / 1e6,
+                     frac_hbm=byts / ms / 1e6 / hbm, peaks=src))
+    print(rows[-1], flush=True)
 
 
 def bench_gemm(rows):
@@ -265,7 +297,7 @@ def main(argv=None):
     if a.gemm:
         CASE["gemm"] = [tuple(int(y) for y in x.split("x")) for x in a.gemm.split(",")]
     rows = []
-    table = {"layer_parts": bench_layer_parts, "decode_pages": bench_decode_pages, "gemm": bench_gemm, "moe": bench_moe, "decode_attn": bench_decode_attn, "prefill_attn": bench_prefill_attn}
+    table = {"moe_nvfp4": bench_moe_nvfp4, "layer_parts": bench_layer_parts, "decode_pages": bench_decode_pages, "gemm": bench_gemm, "moe": bench_moe, "decode_attn": bench_decode_attn, "prefill_attn": bench_prefill_attn}
     for name in a.only.split(","):
         table[name](rows)
     from legion_b200.ops.sm100 import Workspace

@@ -66,6 +66,8 @@ def _add_engine_args(ap: argparse.ArgumentParser):
     g.add_argument("--pipeline-micro", type=int, default=2048, help="tokens per micro-chunk of a pipelined prompt")
     g.add_argument("--experts", choices=["auto", "device", "host", "cache"], default="auto")
     g.add_argument("--expert-cache-gib", type=float, default=0.0)
+    g.add_argument("--expert-weights", choices=["bf16", "nvfp4"], default="bf16",
+                   help="nvfp4: keep the routed experts in 4 bits in HBM (expanded inside the grouped GEMM)")
     g = ap.add_argument_group("sampling defaults")
     g.add_argument("--temp", type=float, default=None)
     g.add_argument("--top-p", type=float, default=None)
@@ -130,6 +132,9 @@ def build_engine_from_args(a, start: bool = True):
         pctx.comm = "fused"
         pctx.gemm_tail = bool(getattr(a, "tp_gemm_tail", False))
     model = Decoder(cfg, w, pctx, max_position=ec.ctx_size + 8)
+    if getattr(a, "expert_weights", "bf16") == "nvfp4" and on_gpu and cfg.n_expert:
+        saved = model.quantize_experts_nvfp4()
+        logging.getLogger("legion").info("routed experts re-encoded to NVFP4: %.1f GiB of HBM saved", saved / 2 ** 30)
     if a.experts in ("cache", "host") and cfg.n_expert:
         from ..residency.experts import slots_for_budget
         slots = cfg.top_k * ec.max_seqs if a.experts == "host" else slots_for_budget(cfg, a.expert_cache_gib or 8.0)

@@ -40,11 +40,18 @@ void wgemm(const Tensor& w, const Tensor& x, Tensor& out, const OptT& residual, 
            const OptT& out_rows, int64_t n_feat, bool dual, int64_t dual_offset, int64_t bn, int64_t split_k,
            const OptT& ws, const OptT& counters, Tensor& status, const OptT& tile_group, const OptT& tile_tok0,
            const OptT& tile_ntok, const OptT& meta, int64_t max_tiles, int64_t rows_per_group, int64_t n_tok,
-           std::vector<int64_t> out_peer, const OptT& tile_out0) {
-  check_bf16(w, "w");
+           std::vector<int64_t> out_peer, const OptT& tile_out0, const OptT& w_scales, const OptT& w_gscale) {
+  const bool fp4 = w_scales.has_value();     // w = NVFP4 codes [rows, K/2] uint8, w_scales = e4m3 bytes [rows, K/16]
+  if (fp4) {
+    TORCH_CHECK(w.scalar_type() == at::kByte && w_scales->is_contiguous() && w_scales->element_size() == 1 &&
+                    w.stride(1) == 1, "wgemm: NVFP4 weights are uint8 codes with 1-byte block scales");
+    TORCH_CHECK(w_scales->size(0) == w.size(0) && w_scales->size(1) * 8 == w.size(1), "wgemm: NVFP4 scale shape");
+  } else {
+    check_bf16(w, "w");
+  }
   check_bf16(x, "x");
   TORCH_CHECK(w.dim() == 2 && x.dim() == 2 && out.dim() == 2, "wgemm expects 2-D tensors");
-  TORCH_CHECK(w.size(1) == x.size(1), "wgemm: K mismatch");
+  TORCH_CHECK(w.size(1) * (fp4 ? 2 : 1) == x.size(1), "wgemm: K mismatch");
   TORCH_CHECK(out.scalar_type() == at::kBFloat16 || out.scalar_type() == at::kFloat, "wgemm: out must be bf16/f32");
   TORCH_CHECK(out.stride(1) == 1 && out.size(1) >= n_feat, "wgemm: bad out");
   c10::cuda::CUDAGuard guard(w.device());
@@ -59,7 +66,9 @@ void wgemm(const Tensor& w, const Tensor& x, Tensor& out, const OptT& residual, 
   }
   h.tok_scale = optp<float>(tok_scale);
   h.out_rows = optp<int>(out_rows);
-  h.K = int(w.size(1)); h.n_feat = int(n_feat); h.n_tok = int(n_tok);
+  h.K = int(x.size(1)); h.n_feat = int(n_feat); h.n_tok = int(n_tok);
+  h.w_scales = fp4 ? w_scales->data_ptr() : nullptr;
+  h.w_gscale = optp<float>(w_gscale);
   h.bn = int(bn); h.dual = dual;
   h.tile_group = optp<int>(tile_group); h.tile_tok0 = optp<int>(tile_tok0); h.tile_ntok = optp<int>(tile_ntok);
   h.n_tiles_dev = optp<int>(meta);
@@ -377,7 +386,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         pybind11::arg("dual_offset"), pybind11::arg("bn"), pybind11::arg("split_k"), pybind11::arg("ws"),
         pybind11::arg("counters"), pybind11::arg("status"), pybind11::arg("tile_group"), pybind11::arg("tile_tok0"),
         pybind11::arg("tile_ntok"), pybind11::arg("meta"), pybind11::arg("max_tiles"), pybind11::arg("rows_per_group"),
-        pybind11::arg("n_tok"), pybind11::arg("out_peer"), pybind11::arg("tile_out0") = pybind11::none());
+        pybind11::arg("n_tok"), pybind11::arg("out_peer"), pybind11::arg("tile_out0") = pybind11::none(),
+        pybind11::arg("w_scales") = pybind11::none(), pybind11::arg("w_gscale") = pybind11::none());
   m.def("wgemm_allreduce", &wgemm_allreduce);
   m.def("rmsnorm", &rmsnorm);
   m.def("qk_norm_rope_append", &qk_norm_rope_append);

@@ -20,6 +20,8 @@
 //
 // Counterpart in the reference: cuBLAS GEMMs reached through ggml, src/cuda/dense_mv.cu (skinny
 // BF16), src/cuda/moe_gemm.cu (routed experts, >= 64 tokens), src/cuda/expert_mv/ (decode experts).
+#include <cuda_fp16.h>
+
 #include "comm_dev.cuh"
 #include "common.cuh"
 #include "gemm_sm100.h"
@@ -33,16 +35,26 @@ static constexpr int UMMA_K = 16;
 static constexpr int W_TILE_BYTES = BM * BK * 2;  // 16 KiB
 static constexpr int SMEM_BUDGET = 200 * 1024;
 
-template <int BN, bool DUAL>
+static constexpr int W_RAW_BYTES = BM * BK / 2;   // NVFP4: 128 rows x 32 bytes of packed e2m1 codes per k block
+static constexpr int W_SC_BYTES = BM * 16;        //        128 rows x 16 e4m3 block scales (4 k blocks of 64)
+
+template <int BN, bool DUAL, bool WFP4 = false>
 struct WgemmCfg {
+  static constexpr int NW = DUAL ? 2 : 1;
   static constexpr int X_TILE_BYTES = BN * BK * 2;
-  static constexpr int STAGE_BYTES = W_TILE_BYTES * (DUAL ? 2 : 1) + X_TILE_BYTES;
+  static constexpr int X_OFF = W_TILE_BYTES * NW;                 // operand tiles first (1024-byte aligned)
+  static constexpr int RAW_OFF = X_OFF + X_TILE_BYTES;            // NVFP4 only: packed codes, then block scales
+  static constexpr int SC_OFF = RAW_OFF + W_RAW_BYTES * NW;
+  static constexpr int STAGE_BYTES = WFP4 ? SC_OFF + W_SC_BYTES * NW : RAW_OFF;
+  static constexpr int THREADS = WFP4 ? 448 : 192;                // NVFP4 adds 8 de-quantisation warps
+  static constexpr int LUT_BYTES = WFP4 ? 512 : 0;                // e4m3 byte -> f16 table
   static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
   static constexpr int ACC_COLS = BN * (DUAL ? 2 : 1);
   static constexpr int TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;
   static constexpr int EPI_BYTES = 32 * BM * 4;  // fp32 staging of 32 token columns
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align slack*/ + 512 /*barriers*/;
+  static constexpr int SMEM_BYTES =
+      STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align slack*/ + 512 /*barriers*/ + LUT_BYTES;
   static_assert(TMEM_COLS <= 512, "accumulators do not fit TMEM");
   static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM column count must be a power of two");
 };
@@ -75,10 +87,35 @@ __device__ __forceinline__ bool decode_work(const WgemmArgs& a, int w, int n_tok
   return true;
 }
 
-template <int BN, bool DUAL, bool OUT_F32>
-__global__ void __launch_bounds__(192, 1)
-wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const WgemmArgs a) {
-  using Cfg = WgemmCfg<BN, DUAL>;
+// e4m3 (fn) byte -> f16 bits; every e4m3 value is exact in f16
+__device__ __forceinline__ uint32_t e4m3_f16_bits(uint32_t b) {
+  const uint32_t e = (b >> 3) & 15u, m = b & 7u;
+  float v;
+  if (e == 0u) v = float(m) * 0.001953125f;                     // subnormals: m * 2^-9
+  else if (e == 15u && m == 7u) v = 0.f;                         // NaN pattern: treated as 0
+  else v = __uint_as_float(((e + 120u) << 23) | (m << 20));
+  return uint32_t(__half_as_ushort(__float2half_rn(v))) | ((b & 0x80u) << 8);
+}
+// four bytes of e2m1 code pairs -> four f16x2 words (hardware conversion, exact)
+__device__ __forceinline__ void e2m1x8_to_f16x2(uint32_t pk, uint32_t (&o)[4]) {
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\tmov.b32 {b0, b1, b2, b3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\tcvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\tcvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+      : "=r"(o[0]), "=r"(o[1]), "=r"(o[2]), "=r"(o[3]) : "r"(pk));
+}
+// bf16x2 -> f16x2, clamped to the f16 range
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
+  const float lo = fminf(fmaxf(__uint_as_float(v << 16), -65504.f), 65504.f);
+  const float hi = fminf(fmaxf(__uint_as_float(v & 0xFFFF0000u), -65504.f), 65504.f);
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <int BN, bool DUAL, bool OUT_F32, bool WFP4>
+__global__ void __launch_bounds__(WFP4 ? 448 : 192, 1)
+wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+             const __grid_constant__ CUtensorMap tmS, const WgemmArgs a) {
+  using Cfg = WgemmCfg<BN, DUAL, WFP4>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -88,7 +125,9 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
   uint64_t* empty = bars + STAGES;        // [STAGES]
   uint64_t* tfull = bars + 2 * STAGES;    // [2]
   uint64_t* tempty = bars + 2 * STAGES + 2;  // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  uint64_t* wready = bars + 2 * STAGES + 4;  // [STAGES] NVFP4: operand tile of the stage has been expanded
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + (WFP4 ? STAGES : 0));
+  uint16_t* lut_sc = reinterpret_cast<uint16_t*>(smem + STAGES * Cfg::STAGE_BYTES + Cfg::EPI_BYTES + 512);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* last_flag = reinterpret_cast<int*>(tmem_slot + 2);
 
@@ -99,6 +138,7 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
+      if (WFP4) mbar_init(&wready[s], 256);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tfull[i], 1);
@@ -110,6 +150,10 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
   if (warp == 1) {
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
     tmem_relinquish();
+  }
+  if (WFP4 && threadIdx.x >= 192) {      // conversion tables, built by the de-quantisation warps
+    const uint32_t b = threadIdx.x - 192;                       // 0..255
+    lut_sc[b] = uint16_t(e4m3_f16_bits(b));
   }
   tc_fence_before();
   __syncthreads();
@@ -145,10 +189,22 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
             break;
           }
           uint8_t* st = smem + s * Cfg::STAGE_BYTES;
-          mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
-          tma_load_2d(st, &tmW, &full[s], kb * BK, wrow);
-          if (DUAL) tma_load_2d(st + W_TILE_BYTES, &tmW, &full[s], kb * BK, wrow + a.dual_offset);
-          tma_load_2d(st + W_TILE_BYTES * (DUAL ? 2 : 1), &tmX, &full[s], kb * BK, it.tok0);
+          if (WFP4) {
+            // packed codes of this k block; the block scales come 4 k blocks (16 bytes per row) at a time
+            const bool sc = (kb % 4 == 0) || kb == kb0;
+            mbar_expect_tx(&full[s], Cfg::X_TILE_BYTES + Cfg::NW * (W_RAW_BYTES + (sc ? W_SC_BYTES : 0)));
+            tma_load_2d(st + Cfg::RAW_OFF, &tmW, &full[s], kb * (BK / 2), wrow);
+            if (DUAL) tma_load_2d(st + Cfg::RAW_OFF + W_RAW_BYTES, &tmW, &full[s], kb * (BK / 2), wrow + a.dual_offset);
+            if (sc) {
+              tma_load_2d(st + Cfg::SC_OFF, &tmS, &full[s], (kb / 4) * 16, wrow);
+              if (DUAL) tma_load_2d(st + Cfg::SC_OFF + W_SC_BYTES, &tmS, &full[s], (kb / 4) * 16, wrow + a.dual_offset);
+            }
+          } else {
+            mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+            tma_load_2d(st, &tmW, &full[s], kb * BK, wrow);
+            if (DUAL) tma_load_2d(st + W_TILE_BYTES, &tmW, &full[s], kb * BK, wrow + a.dual_offset);
+          }
+          tma_load_2d(st + Cfg::X_OFF, &tmX, &full[s], kb * BK, it.tok0);
           ++issued;
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
@@ -168,7 +224,8 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(BM, BN, 1, 1, 0, 0);
+      constexpr uint32_t idesc = WFP4 ? umma_idesc(BM, BN, 0, 0, 0, 0)      // f16 operand tiles (see the de-quantiser)
+                                      : umma_idesc(BM, BN, 1, 1, 0, 0);
       int s = 0;
       uint32_t ph = 0;
       int acc = 0;
@@ -186,7 +243,7 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
         tc_fence_after();
         const uint32_t d0 = tmem_base + acc * Cfg::ACC_COLS;
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(&full[s], ph, abort_flag)) {
+          if (!mbar_wait(&full[s], ph, abort_flag) || (WFP4 && !mbar_wait(&wready[s], ph, abort_flag))) {
             *abort_flag = 1;
             atomicCAS(a.status, 0, ST_TIMEOUT_FULL);
             ok = false;
@@ -196,7 +253,7 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
           const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
           const uint64_t dw = umma_desc_k_sw128(sa);
           const uint64_t dw2 = umma_desc_k_sw128(sa + W_TILE_BYTES);
-          const uint64_t dx = umma_desc_k_sw128(sa + W_TILE_BYTES * (DUAL ? 2 : 1));
+          const uint64_t dx = umma_desc_k_sw128(sa + Cfg::X_OFF);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
@@ -210,6 +267,83 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
         if (!ok) break;
         umma_commit(&tfull[acc]);
         if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+      }
+    }
+  } else if (WFP4 && warp >= 6) {
+    // ------------------------------------------------------------------ NVFP4 de-quantisation (warps 6..13)
+    // The 256 threads expand every weight tile of a stage (128 rows x 64 codes) into the bf16, 128-byte-swizzled
+    // operand tile the MMA reads. A task is one 16-byte chunk (8 codes = 4 packed bytes): lane -> (row, chunk)
+    // such that a warp reads 128 contiguous bytes of codes and writes four complete 128-byte rows, so neither
+    // side has a shared-memory bank conflict. Codes become f16 pairs with the hardware conversion
+    // (cvt.rn.f16x2.e2m1x2) and are multiplied by the block scale as f16x2 (exact: 1 + 3 mantissa bits, range
+    // 2^-10 .. 2688); the MMA of this variant runs on f16 operands, so the bf16 activation tile of the stage is
+    // converted in place as well (clamped to the f16 range).
+    const int d = threadIdx.x - 192;
+    const int dw = d >> 5, dl = d & 31;
+    const int chunk = dl & 7;
+    const int row0 = dw * 4 + (dl >> 3);           // rows row0 + 32 * i, i = 0..3
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    uint32_t scw[Cfg::NW][4][4];                   // [tile][row i][k block within the group of 4]: 4 scale bytes
+#pragma unroll
+    for (int t = 0; t < Cfg::NW; ++t)
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) scw[t][i][k] = 0u;
+    WorkItem it;
+    for (int w = blockIdx.x; decode_work<BN>(a, w, n_tok_tiles, it); w += gridDim.x) {
+      const int kb0 = it.ks * kb_per_split;
+      const int kb1 = min(num_kb, kb0 + kb_per_split);
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (ok && !mbar_wait(&full[s], ph, abort_flag)) {
+          *abort_flag = 1;
+          atomicCAS(a.status, 0, ST_TIMEOUT_FULL);
+          ok = false;      // keep arriving so that nobody is left waiting on wready
+        }
+        uint8_t* st = smem + s * Cfg::STAGE_BYTES;
+        if (ok) {
+          const bool new_sc = (kb % 4 == 0) || kb == kb0;
+          const int kq = kb & 3;
+#pragma unroll
+          for (int t = 0; t < Cfg::NW; ++t) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int row = row0 + 32 * i;
+              if (new_sc) {
+                const uint4 v = *reinterpret_cast<const uint4*>(st + Cfg::SC_OFF + t * W_SC_BYTES + row * 16);
+                scw[t][i][0] = v.x; scw[t][i][1] = v.y; scw[t][i][2] = v.z; scw[t][i][3] = v.w;
+              }
+              const uint32_t sw = kq == 0 ? scw[t][i][0] : (kq == 1 ? scw[t][i][1] : (kq == 2 ? scw[t][i][2] : scw[t][i][3]));
+              const uint32_t sb = lut_sc[(sw >> (8 * (chunk >> 1))) & 0xFFu];     // scale of this chunk's 16 block
+              const uint32_t sc2 = sb | (sb << 16);
+              const uint32_t pk = *reinterpret_cast<const uint32_t*>(st + Cfg::RAW_OFF + t * W_RAW_BYTES + row * 32 + chunk * 4);
+              uint32_t o[4];
+              e2m1x8_to_f16x2(pk, o);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&o[j]),
+                                          *reinterpret_cast<const __half2*>(&sc2));
+                o[j] = *reinterpret_cast<const uint32_t*>(&r);
+              }
+              *reinterpret_cast<uint4*>(st + t * W_TILE_BYTES + row * 128 + ((chunk ^ (row & 7)) * 16)) =
+                  make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          }
+          // the activations arrive as bf16: convert the X tile in place (chunk positions are unchanged)
+          uint4* xt = reinterpret_cast<uint4*>(st + Cfg::X_OFF);
+#pragma unroll
+          for (int idx = d; idx < BN * 8; idx += 256) {
+            uint4 v = xt[idx];
+            v.x = bf16x2_to_f16x2(v.x); v.y = bf16x2_to_f16x2(v.y);
+            v.z = bf16x2_to_f16x2(v.z); v.w = bf16x2_to_f16x2(v.w);
+            xt[idx] = v;
+          }
+          fence_proxy_async_smem();
+        }
+        mbar_arrive(&wready[s]);
+        if (++s == STAGES) { s = 0; ph ^= 1; }
       }
     }
   } else {
@@ -282,6 +416,14 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
               tmem_ld_wait();
 #pragma unroll
               for (int j = 0; j < 32; ++j) u[j] = __uint_as_float(r[j]);
+            }
+          }
+          if (WFP4 && a.w_gscale) {          // per-tensor (per-expert) scale of the NVFP4 encoding
+            const float gs0 = a.w_gscale[it.group * Cfg::NW], gs1 = DUAL ? a.w_gscale[it.group * 2 + 1] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              g[j] *= gs0;
+              if (DUAL) u[j] *= gs1;
             }
           }
           if (!OUT_F32 && a.vec_ok) {
@@ -436,10 +578,11 @@ namespace {
 
 thread_local char g_gemm_err[512];
 
-template <int BN, bool DUAL, bool OUT_F32>
-int launch(const CUtensorMap* tmW, const CUtensorMap* tmX, const WgemmArgs& a, int grid, cudaStream_t stream) {
-  using Cfg = WgemmCfg<BN, DUAL>;
-  auto kfn = wgemm_kernel<BN, DUAL, OUT_F32>;
+template <int BN, bool DUAL, bool OUT_F32, bool WFP4 = false>
+int launch(const CUtensorMap* tmW, const CUtensorMap* tmX, const CUtensorMap* tmS, const WgemmArgs& a, int grid,
+           cudaStream_t stream) {
+  using Cfg = WgemmCfg<BN, DUAL, WFP4>;
+  auto kfn = wgemm_kernel<BN, DUAL, OUT_F32, WFP4>;
   static bool attr_set = false;  // per instantiation
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
@@ -449,7 +592,7 @@ int launch(const CUtensorMap* tmW, const CUtensorMap* tmX, const WgemmArgs& a, i
     }
     attr_set = true;
   }
-  launch_pdl(kfn, dim3(grid), dim3(192), Cfg::SMEM_BYTES, stream, *tmW, *tmX, a);
+  launch_pdl(kfn, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM_BYTES, stream, *tmW, *tmX, *tmS, a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     snprintf(g_gemm_err, sizeof(g_gemm_err), "wgemm launch: %s", cudaGetErrorString(e));
@@ -491,11 +634,20 @@ int wgemm_launch(const WgemmHost& h, cudaStream_t stream) {
     if (g_num_sms <= 0) g_num_sms = 148;
   }
   const int bn = h.bn;
-  const CUtensorMap* tmW =
-      tmap_2d(h.w, uint64_t(h.w_rows), uint64_t(h.K), uint64_t(h.ldw) * 2, BM, BK, TM_BF16, true);
+  const bool fp4 = h.w_scales != nullptr;
+  if (fp4 && (h.K % 64 != 0 || h.out_f32 || (reinterpret_cast<uintptr_t>(h.w_scales) & 15) || (h.K / 16) % 16 != 0)) {
+    snprintf(g_gemm_err, sizeof(g_gemm_err), "wgemm: NVFP4 weights need K %% 256 == 0, bf16 output, aligned scales");
+    return 1;
+  }
+  // NVFP4: h.w = packed codes [rows, K / 2] bytes (row pitch h.ldw bytes), h.w_scales = e4m3 [rows, K / 16]
+  const CUtensorMap* tmW = fp4 ? tmap_2d(h.w, uint64_t(h.w_rows), uint64_t(h.K / 2), uint64_t(h.ldw), BM, BK / 2, TM_U8, false)
+                               : tmap_2d(h.w, uint64_t(h.w_rows), uint64_t(h.K), uint64_t(h.ldw) * 2, BM, BK, TM_BF16, true);
+  const CUtensorMap* tmS = fp4 ? tmap_2d(h.w_scales, uint64_t(h.w_rows), uint64_t(h.K / 16), uint64_t(h.K / 16), BM, 16,
+                                         TM_U8, false)
+                               : tmW;
   const CUtensorMap* tmX =
       tmap_2d(h.x, uint64_t(h.x_rows), uint64_t(h.K), uint64_t(h.ldx) * 2, uint32_t(bn), BK, TM_BF16, true);
-  if (!tmW || !tmX) {
+  if (!tmW || !tmX || !tmS) {
     snprintf(g_gemm_err, sizeof(g_gemm_err), "wgemm: %s", tmap_last_error());
     return 1;
   }
@@ -505,6 +657,7 @@ int wgemm_launch(const WgemmHost& h, cudaStream_t stream) {
   a.K = h.K; a.n_feat = h.n_feat; a.feat_tiles = (h.n_feat + BM - 1) / BM;
   a.n_tok = h.n_tok;
   a.comm = h.comm;
+  a.w_gscale = h.w_gscale;
   a.tile_group = h.tile_group; a.tile_tok0 = h.tile_tok0; a.tile_out0 = h.tile_out0; a.tile_ntok = h.tile_ntok; a.n_tiles_dev = h.n_tiles_dev;
   a.n_tok_tiles_max = h.n_tok_tiles_max;
   a.rows_per_group = h.rows_per_group; a.dual_offset = h.dual_offset;
@@ -529,8 +682,9 @@ int wgemm_launch(const WgemmHost& h, cudaStream_t stream) {
 
 #define LB_CASE(BN_, DUAL_)                                                                     \
   if (bn == BN_ && h.dual == DUAL_) {                                                           \
-    return h.out_f32 ? launch<BN_, DUAL_, true>(tmW, tmX, a, grid, stream)                      \
-                     : launch<BN_, DUAL_, false>(tmW, tmX, a, grid, stream);                    \
+    if (fp4) return launch<BN_, DUAL_, false, true>(tmW, tmX, tmS, a, grid, stream);            \
+    return h.out_f32 ? launch<BN_, DUAL_, true>(tmW, tmX, tmS, a, grid, stream)                 \
+                     : launch<BN_, DUAL_, false>(tmW, tmX, tmS, a, grid, stream);               \
   }
   LB_CASE(32, false) LB_CASE(64, false) LB_CASE(128, false) LB_CASE(256, false)
   LB_CASE(32, true) LB_CASE(64, true) LB_CASE(128, true)

@@ -50,6 +50,7 @@ struct WgemmArgs {
   void* out_peer[8];              // EP combine: per-rank output bases (peer-mapped); used when n_out_peer > 0,
   int n_out_peer;                 //   out_rows[] then holds (rank << 24) | row
   WgemmCommTail comm;
+  const float* w_gscale;          // NVFP4 weights: per-group (x2 for DUAL: gate, up) tensor scale, applied in the epilogue
 };
 
 // Host-side description of one launch.
@@ -70,6 +71,8 @@ struct WgemmHost {
   int* status;
   void* out_peer[8]; int n_out_peer;
   WgemmCommTail comm;
+  const void* w_scales;           // non-null: w holds NVFP4 codes [rows, K/2] bytes, this the e4m3 block scales [rows, K/16]
+  const float* w_gscale;
 };
 
 int wgemm_launch(const WgemmHost& h, cudaStream_t stream);

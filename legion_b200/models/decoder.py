@@ -173,6 +173,26 @@ class Decoder:
             gu, dn = self.w.pop(f"{p}.moe.gate_up"), self.w.pop(f"{p}.moe.down")
             self.expert_cache[p] = ExpertCache(gu, dn, n_slots, self.device, profile=(profile or {}).get(p))
 
+    def quantize_experts_nvfp4(self) -> int:
+        """Re-encodes the routed experts of every MoE layer to NVFP4 in place (3.5x less HBM for the bulk of a MoE
+        model). The grouped GEMM then streams the 4-bit codes and expands them inside the kernel
+        (``ops.sm100.QWeight``). Returns the number of bytes saved. GPU only."""
+        from ..ops.sm100 import QWeight
+        saved = 0
+        for il in range(self.cfg.n_layer):
+            p = f"l{il}"
+            if not self.cfg.is_moe_layer(il) or f"{p}.moe.gate_up" not in self.w:
+                continue
+            gu, dn = self.w[f"{p}.moe.gate_up"], self.w[f"{p}.moe.down"]
+            if isinstance(gu, QWeight) or gu.shape[-1] % 256 or dn.shape[-1] % 256:
+                continue
+            before = gu.numel() * 2 + dn.numel() * 2
+            self.w[f"{p}.moe.gate_up"] = QWeight.quantize_cuda(gu, dual_rows=gu.shape[1] // 2)
+            self.w[f"{p}.moe.down"] = QWeight.quantize_cuda(dn)
+            del gu, dn
+            saved += before - before * 9 // 32
+        return saved
+
     # ------------------------------------------------------------------ blocks
     def _attn(self, p: str, il: int, x, b: StepBatch, kv: KvCache, window: int):
         cfg, w = self.cfg, self.w

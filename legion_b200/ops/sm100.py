@@ -121,6 +121,92 @@ class Workspace:
         return v
 
 
+class QWeight:
+    """NVFP4 weight kept in its 4-bit encoding: ``codes`` uint8 [..., rows, K/2] (two e2m1 values per byte, low
+    nibble first), ``scales`` uint8 e4m3 bit patterns [..., rows, K/16], ``gscale`` float32 per tensor (per expert;
+    for a fused gate/up tensor two values per expert: gate, up). The GEMM streams the 4-bit bytes and expands
+    them to bf16 operand tiles inside the kernel (``csrc/gemm_sm100.cu``), so a decode step reads 0.56 bytes per
+    weight instead of 2."""
+    __slots__ = ("codes", "scales", "gscale")
+
+    def __init__(self, codes, scales, gscale):
+        self.codes, self.scales, self.gscale = codes, scales.view(torch.uint8), gscale.float().reshape(-1).contiguous()
+
+    @property
+    def shape(self):
+        return tuple(self.codes.shape[:-1]) + (self.codes.shape[-1] * 2,)
+
+    @property
+    def device(self):
+        return self.codes.device
+
+    def dim(self):
+        return self.codes.dim()
+
+    def view2d(self):
+        return self.codes.reshape(-1, self.codes.shape[-1]), self.scales.reshape(-1, self.scales.shape[-1])
+
+    @classmethod
+    def quantize(cls, w: torch.Tensor, dual_rows: int = 0):
+        """Encodes a bf16/fp32 weight [..., rows, K] (tests, synthetic checkpoints). ``dual_rows`` > 0: the tensor is
+        a fused [gate | up] stack of 2 * dual_rows rows and each half gets its own tensor scale."""
+        from ..loaders.quant_formats import nvfp4_quant
+        lead = w.shape[:-2]
+        flat = w.reshape(-1, w.shape[-2], w.shape[-1])
+        codes, scales, gs = [], [], []
+        for t in flat:
+            parts = [t] if not dual_rows else [t[:dual_rows], t[dual_rows:]]
+            cs, ss = [], []
+            for part in parts:
+                c, sc, g = nvfp4_quant(part.float().cpu())
+                cs.append(c)
+                ss.append(sc.view(torch.uint8))
+                gs.append(float(g))
+            codes.append(torch.cat(cs, 0))
+            scales.append(torch.cat(ss, 0))
+        dev = w.device
+        return cls(torch.stack(codes).reshape(*lead, *codes[0].shape).to(dev),
+                   torch.stack(scales).reshape(*lead, *scales[0].shape).to(dev),
+                   torch.tensor(gs, dtype=torch.float32, device=dev))
+
+    @classmethod
+    def quantize_cuda(cls, w: torch.Tensor, dual_rows: int = 0):
+        """Device-side encoding of a CUDA bf16 weight [..., rows, K] (``csrc/quant.cu::nvfp4_quant``): one tensor
+        scale per leading index (two with ``dual_rows``: gate rows, up rows)."""
+        C = ext()
+        rows, K = w.shape[-2], w.shape[-1]
+        flat = w.reshape(-1, rows, K)
+        n = flat.shape[0]
+        codes = torch.empty(n, rows, K // 2, dtype=torch.uint8, device=w.device)
+        scales = torch.empty(n, rows, K // 16, dtype=torch.uint8, device=w.device)
+        per = 2 if dual_rows else 1
+        gs = torch.empty(n * per, dtype=torch.float32, device=w.device)
+        for t in range(n):
+            for h in range(per):
+                r0, r1 = (0, rows) if not dual_rows else (h * dual_rows, (h + 1) * dual_rows)
+                part = flat[t, r0:r1]
+                g = (part.float().abs().max() / (6.0 * 448.0)).clamp_min(1e-12).reshape(1)
+                gs[t * per + h] = g[0]
+                C.nvfp4_quant(part.contiguous(), g, codes[t, r0:r1], scales[t, r0:r1])
+        lead = tuple(w.shape[:-2])
+        return cls(codes.reshape(*lead, rows, K // 2), scales.reshape(*lead, rows, K // 16), gs)
+
+    def dequantize(self, dtype=torch.bfloat16):
+        from ..loaders.quant_formats import nvfp4_dequant
+        c2, s2 = self.view2d()
+        rows = self.codes.shape[-2]
+        n_t = c2.shape[0] // rows
+        per = self.gscale.numel() // n_t
+        out = torch.empty(c2.shape[0], c2.shape[1] * 2, dtype=dtype, device=self.device)
+        for t in range(n_t):
+            for h in range(per):
+                r0 = t * rows + h * (rows // per)
+                r1 = r0 + rows // per
+                out[r0:r1] = nvfp4_dequant(c2[r0:r1].cpu(), s2[r0:r1].cpu(), float(self.gscale[t * per + h]),
+                                           out_dtype=dtype).to(self.device)
+        return out.reshape(self.shape)
+
+
 def pick_bn(n_tok: int, dual: bool) -> int:
     bn = 32
     cap = 128 if dual else 256
@@ -144,6 +230,9 @@ def linear(x, w, residual=None, out=None, out_dtype=torch.bfloat16, split_k: Opt
     C = ext()
     T, K = x.shape
     N = w.shape[0]
+    q = isinstance(w, QWeight)
+    if q and out_dtype != torch.bfloat16:
+        raise ValueError("NVFP4 weights produce bf16 outputs")
     if out is None:
         out = torch.empty(T, N, dtype=out_dtype, device=x.device)
     if T == 0:
@@ -157,8 +246,9 @@ def linear(x, w, residual=None, out=None, out_dtype=torch.bfloat16, split_k: Opt
         need = C.wgemm_workspace_floats(bn, False, n_tt, ft, sk)
         if need > ws.splitk.numel() or n_tt * ft > ws.counters.numel():
             sk = 1
-    C.wgemm(w, x, out, residual, None, None, N, False, 0, bn, sk, ws.splitk if sk > 1 else None,
-            ws.counters if sk > 1 else None, ws.status, None, None, None, None, 0, 0, T, [])
+    C.wgemm(w.codes if q else w, x, out, residual, None, None, N, False, 0, bn, sk, ws.splitk if sk > 1 else None,
+            ws.counters if sk > 1 else None, ws.status, None, None, None, None, 0, 0, T, [], None,
+            w.scales if q else None, w.gscale if q else None)
     return out
 
 
@@ -179,8 +269,10 @@ def gate_up_act(x, w_gate_up, n_ff: int, out=None, bn=None, split_k: Optional[in
         need = C.wgemm_workspace_floats(bn, True, n_tt, ft, sk)
         if need > ws.splitk.numel() or n_tt * ft > ws.counters.numel():
             sk = 1
-    C.wgemm(w_gate_up, x, out, None, None, None, n_ff, True, n_ff, bn, sk, ws.splitk if sk > 1 else None,
-            ws.counters if sk > 1 else None, ws.status, None, None, None, None, 0, 0, T, [])
+    q = isinstance(w_gate_up, QWeight)
+    C.wgemm(w_gate_up.codes if q else w_gate_up, x, out, None, None, None, n_ff, True, n_ff, bn, sk,
+            ws.splitk if sk > 1 else None, ws.counters if sk > 1 else None, ws.status, None, None, None, None, 0, 0, T,
+            [], None, w_gate_up.scales if q else None, w_gate_up.gscale if q else None)
     return out
 
 
@@ -376,6 +468,15 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[Moe
     k = ids.shape[1]
     E_local = w_gate_up.shape[0]
     ws = Workspace.get(x.device)
+    # expert weights as 2-D operands (+ NVFP4 block scales / tensor scales when kept in 4 bits)
+    if isinstance(w_gate_up, QWeight):
+        (gu2, gu_sc), gu_gs = w_gate_up.view2d(), w_gate_up.gscale
+    else:
+        gu2, gu_sc, gu_gs = w_gate_up.view(E_local * 2 * n_ff, H), None, None
+    if isinstance(w_down, QWeight):
+        (dn2, dn_sc), dn_gs = w_down.view2d(), w_down.gscale
+    else:
+        dn2, dn_sc, dn_gs = w_down.view(E_local * H, n_ff), None, None
     if (routing is not None and routing.dense is not None and routing.dense.E == E_local and e_lo == 0
             and routing.ids is ids and TUNE["dense_route"]):
         # decode-sized step: every active expert runs over all T tokens in place (no plan, no gather)
@@ -385,11 +486,12 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[Moe
             dr.h_all = torch.zeros(E_local * dr.bn, n_ff, dtype=torch.bfloat16, device=x.device)
         if dr.y_pairs is None or dr.y_pairs.shape[0] < P or dr.y_pairs.shape[1] != H:
             dr.y_pairs = torch.zeros(max(P, 64 * k), H, dtype=torch.bfloat16, device=x.device)
-        C.wgemm(w_gate_up.view(E_local * 2 * n_ff, H), x, dr.h_all, None, None, None, n_ff, True, n_ff, dr.bn, 1,
+        C.wgemm(gu2, x, dr.h_all, None, None, None, n_ff, True, n_ff, dr.bn, 1,
                 None, None, ws.status, dr.tile_group, dr.zeros, dr.tile_ntok, dr.meta, E_local, 2 * n_ff, 0, [],
-                dr.slot_base)
-        C.wgemm(w_down.view(E_local * H, n_ff), dr.h_all, dr.y_pairs, None, dr.tok_scale, dr.out_rows, H, False, 0,
-                dr.bn, 1, None, None, ws.status, dr.tile_group, dr.slot_base, dr.tile_ntok, dr.meta, E_local, H, 0, [])
+                dr.slot_base, gu_sc, gu_gs)
+        C.wgemm(dn2, dr.h_all, dr.y_pairs, None, dr.tok_scale, dr.out_rows, H, False, 0,
+                dr.bn, 1, None, None, ws.status, dr.tile_group, dr.slot_base, dr.tile_ntok, dr.meta, E_local, H, 0, [],
+                None, dn_sc, dn_gs)
         if out is None:
             out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
         y = dr.y_pairs[:P]
@@ -423,12 +525,12 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[Moe
         C.moe_plan(ids, wts, e_lo, E_local, bn, plan.counts, plan.offsets, plan.sorted_token, plan.sorted_pair,
                    plan.sorted_w, plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta)
         C.gather_rows(x, plan.sorted_token, plan.meta[1:2], plan.x_sorted[:P])
-    wgu = w_gate_up.view(E_local * 2 * n_ff, H)
-    C.wgemm(wgu, plan.x_sorted, plan.h_sorted, None, None, None, n_ff, True, n_ff, bn, 1, None, None, ws.status,
-            plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta, plan.max_tiles, 2 * n_ff, 0, [])
-    wd = w_down.view(E_local * H, n_ff)
-    C.wgemm(wd, plan.h_sorted, plan.y_pairs, None, plan.sorted_w, plan.sorted_pair, H, False, 0, bn, 1, None, None,
-            ws.status, plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta, plan.max_tiles, H, 0, [])
+    C.wgemm(gu2, plan.x_sorted, plan.h_sorted, None, None, None, n_ff, True, n_ff, bn, 1, None, None, ws.status,
+            plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta, plan.max_tiles, 2 * n_ff, 0, [], None,
+            gu_sc, gu_gs)
+    C.wgemm(dn2, plan.h_sorted, plan.y_pairs, None, plan.sorted_w, plan.sorted_pair, H, False, 0, bn, 1, None, None,
+            ws.status, plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta, plan.max_tiles, H, 0, [], None,
+            dn_sc, dn_gs)
     if out is None:
         out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
     if norm is None:

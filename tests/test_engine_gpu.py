@@ -51,3 +51,28 @@ def test_gpu_engine_matches_cpu_logits(idx, graphs):
     assert b2.usage.cached_tokens >= 128
     from legion_b200.ops.sm100 import Workspace
     assert Workspace.get("cuda").check() == 0
+
+
+def test_engine_with_nvfp4_experts():
+    """Routed experts re-encoded to NVFP4 in HBM: the engine (CUDA graphs included) generates the same tokens as
+    with the de-quantised copy of those weights expanded to bf16."""
+    from legion_b200.config import ModelConfig
+    from legion_b200.engine.lm import EngineConfig, build_engine
+    from legion_b200.models.weights import random_weights
+    from legion_b200.ops.sm100 import QWeight
+    cfg = ModelConfig(arch="qwen3moe", n_layer=2, hidden=512, vocab=2048, n_head=8, n_kv_head=2, head_dim=128,
+                      n_expert=8, top_k=2, expert_ff=256)
+    w = random_weights(cfg, "cuda", torch.bfloat16, seed=0, std=0.05)
+    ecfg = dict(ctx_size=512, max_seqs=2, block_size=64, prefill_chunk=256, prefix_cache=False)
+    eng_q = build_engine(cfg, weights=dict(w), device="cuda", engine_cfg=EngineConfig(**ecfg))
+    assert eng_q.model.quantize_experts_nvfp4() > 0
+    w_deq = dict(w)
+    for k, v in eng_q.model.w.items():
+        if isinstance(v, QWeight):
+            w_deq[k] = v.dequantize()
+    eng_d = build_engine(cfg, weights=w_deq, device="cuda", engine_cfg=EngineConfig(**ecfg))
+    prompt = list(range(3, 150))
+    a = eng_q.generate_text(tokens=prompt, max_tokens=12, ignore_eos=True).token_ids
+    b = eng_d.generate_text(tokens=prompt, max_tokens=12, ignore_eos=True).token_ids
+    eng_q.shutdown(); eng_d.shutdown()
+    assert len(a) == 12 and a == b

@@ -414,3 +414,41 @@ def test_gguf_dequant_kernel_matches_host(tname):
     out = torch.empty(shape, dtype=torch.bfloat16, device=DEV)
     ext().gguf_dequant(torch.from_numpy(raw.reshape(-1).copy()).to(DEV), tid, out)
     close(out, torch.from_numpy(want).bfloat16(), 1e-2, 1e-3)
+
+
+@pytest.mark.parametrize("T,N,K,split_k", [(1, 128, 256, 1), (16, 384, 512, 1), (16, 384, 1024, 3), (300, 256, 768, 1),
+                                            (40, 5120, 2048, None)])
+def test_linear_nvfp4_weights(T, N, K, split_k):
+    """GEMM over weights kept in NVFP4 (expanded to bf16 operand tiles inside the kernel) against the fp32 product
+    with the de-quantised weights."""
+    from legion_b200.ops.sm100 import QWeight
+    torch.manual_seed(T + N)
+    x = rnd(T, K)
+    w = rnd(N, K, scale=K ** -0.5)
+    qw = QWeight.quantize(w)
+    deq = qw.dequantize()
+    assert (deq.float() - w.float()).abs().max() < 0.3 * w.float().abs().max()      # sanity of the encoding itself
+    out = sm().linear(x, qw, split_k=split_k)
+    status_ok()
+    close(out, ref.linear(x, deq))
+    res = rnd(T, N)
+    out = sm().linear(x, qw, residual=res, split_k=split_k)
+    close(out, ref.linear(x, deq).float() + res.float())
+
+
+def test_moe_nvfp4_weights():
+    from legion_b200.ops.sm100 import QWeight
+    torch.manual_seed(11)
+    E, k, H, F = 16, 4, 512, 256
+    wgu, wd = rnd(E, 2 * F, H, scale=H ** -0.5), rnd(E, H, F, scale=F ** -0.5)
+    qgu, qd = QWeight.quantize(wgu, dual_rows=F), QWeight.quantize(wd)
+    dgu, dd = qgu.dequantize(), qd.dequantize()
+    x1 = rnd(7, H)
+    close(sm().gate_up_act(x1, QWeight(qgu.codes[0], qgu.scales[0], qgu.gscale[:2]), F), ref.gate_up_act(x1, dgu[0], F))
+    for T in (16, 200):                       # dense-routing path and plan + gather path
+        x = rnd(T, H)
+        w_r = rnd(E, H, scale=H ** -0.5)
+        r = sm().router(x, w_r, k)
+        out = sm().moe_experts(x, r.ids, r.wts, qgu, qd, F, routing=r)
+        status_ok()
+        close(out, ref.moe_experts(x, r.ids, r.wts, dgu, dd, F), 3e-2, 3e-2)
