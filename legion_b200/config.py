@@ -34,8 +34,9 @@ class ModelConfig:
     sliding_window: int = 0            # window of "swa" layers
     attn_softcap: float = 0.0
     logit_softcap: float = 0.0
+    logit_scale: float = 1.0           # multiplies the logits before the soft cap (muse-glimmer)
     attn_scale: Optional[float] = None
-    # layer pattern: one of "attn", "swa", "gdn", "mla", "mamba2", "kda" per layer
+    # layer pattern: one of "attn", "swa", "nope" (attention without RoPE), "gdn", "mla", "mamba2", "kda" per layer
     layer_kinds: Optional[List[str]] = None
     full_attention_interval: int = 0   # >0: layer il is "gdn" unless (il + 1) % interval == 0
     # gated delta net
@@ -97,7 +98,7 @@ class ModelConfig:
         return self.n_expert > 0 and il >= self.first_dense_layers
 
     def kv_layers(self) -> List[int]:
-        return [i for i, k in enumerate(self.layer_kinds) if k in ("attn", "swa", "mla")]
+        return [i for i, k in enumerate(self.layer_kinds) if k in ("attn", "swa", "nope", "mla")]
 
     def recurrent_layers(self) -> List[int]:
         return [i for i, k in enumerate(self.layer_kinds) if k in ("gdn", "mamba2", "kda")]
@@ -187,7 +188,35 @@ def dense_27b() -> ModelConfig:
                        rope_theta=1e6, dense_ff=17408)
 
 
+def tiny_muse() -> ModelConfig:
+    """muse-glimmer shape: dense, sliding-window RoPE layers with every third layer global without RoPE, QK norm,
+    sigmoid output gate, logit scale + soft cap (``src/model/muse.rs:1-25`` in the reference)."""
+    return ModelConfig(arch="muse-glimmer", n_layer=6, hidden=256, vocab=4096, n_head=4, n_kv_head=2, head_dim=64,
+                       layer_kinds=["swa", "swa", "nope", "swa", "swa", "nope"], sliding_window=32, gated_attn=True,
+                       dense_ff=512, logit_scale=0.5, logit_softcap=30.0)
+
+
+def tiny_gemma() -> ModelConfig:
+    """Gemma-style: alternating sliding-window / global attention, GELU-gated FFN, (weight - 1) norm storage,
+    tied embeddings, logit soft cap 30 (``src/model/gemma4.rs:1-30``; per-layer head sizes and shared-KV layers of
+    Gemma 4 are not modelled)."""
+    return ModelConfig(arch="gemma4", n_layer=4, hidden=256, vocab=4096, n_head=4, n_kv_head=2, head_dim=64,
+                       layer_kinds=["swa", "attn", "swa", "attn"], sliding_window=48, ffn_act="gelu_tanh",
+                       dense_ff=512, norm_offset=1.0, tie_embeddings=True, logit_softcap=30.0)
+
+
+def tiny_nemotron_h() -> ModelConfig:
+    """Nemotron-H style hybrid: Mamba-2 layers with a few attention layers without RoPE, squared-ReLU FFN
+    (``src/model/nemotron_h.rs:1-20``; latent MoE and per-layer expert counts are not modelled)."""
+    return ModelConfig(arch="nemotron_h", n_layer=4, hidden=256, vocab=4096, n_head=4, n_kv_head=2, head_dim=64,
+                       layer_kinds=["mamba2", "mamba2", "nope", "mamba2"], qk_norm=False, ffn_act="relu2",
+                       dense_ff=512, ssm_state=32, ssm_heads=8, ssm_head_dim=32, ssm_groups=1, ssm_conv=4)
+
+
 PRESETS = {
+    "tiny-muse": tiny_muse,
+    "tiny-gemma": tiny_gemma,
+    "tiny-nemotron-h": tiny_nemotron_h,
     "tiny-hybrid-moe": tiny_hybrid_moe,
     "tiny-gqa-moe": tiny_gqa_moe,
     "tiny-dense": tiny_dense,

@@ -105,7 +105,7 @@ def model_bytes_per_step(cfg, n_seqs: int, ctx: int, tp: int = 1, dtype_bytes: i
     experts = 0
     kv = 0
     for il, kind in enumerate(cfg.layer_kinds):
-        if kind in ("attn", "swa"):
+        if kind in ("attn", "swa", "nope"):
             qw = cfg.n_head * cfg.head_dim * (2 if cfg.gated_attn else 1)
             dense += (qw + 2 * cfg.n_kv_head * cfg.head_dim) * H + H * cfg.n_head * cfg.head_dim
             kv += 2 * cfg.n_kv_head * cfg.head_dim * ctx * n_seqs

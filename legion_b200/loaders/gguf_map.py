@@ -103,7 +103,7 @@ def to_gguf_tensors(cfg: ModelConfig, w: Dict[str, torch.Tensor]) -> Dict[str, t
     def layer(p: str, b: str, kind: str, moe: bool):
         out[f"{b}.attn_norm.weight"] = w[f"{p}.attn_norm"]
         out[f"{b}.post_attention_norm.weight"] = w[f"{p}.ffn_norm"]
-        if kind in ("attn", "swa"):
+        if kind in ("attn", "swa", "nope"):
             qkv = w[f"{p}.attn.qkv"]
             qw = cfg.n_head * D * (2 if cfg.gated_attn else 1)
             out[f"{b}.attn_q.weight"] = qkv[:qw]            # already [q | gate] per head
@@ -174,7 +174,7 @@ def from_gguf_tensors(cfg: ModelConfig, get, has) -> Dict[str, torch.Tensor]:
         w[f"{p}.attn_norm"] = get(f"{b}.attn_norm.weight")
         w[f"{p}.ffn_norm"] = get(f"{b}.post_attention_norm.weight") if has(f"{b}.post_attention_norm.weight") \
             else get(f"{b}.ffn_norm.weight")
-        if kind in ("attn", "swa"):
+        if kind in ("attn", "swa", "nope"):
             w[f"{p}.attn.qkv"] = torch.cat([get(f"{b}.attn_q.weight"), get(f"{b}.attn_k.weight"),
                                             get(f"{b}.attn_v.weight")], dim=0)
             if has(f"{b}.attn_q_norm.weight"):

@@ -284,7 +284,7 @@ def save_hf(path: str, cfg: ModelConfig, w: Dict[str, torch.Tensor], quant: str 
         t[lp + "input_layernorm.weight"] = w[f"{p}.attn_norm"].cpu().to(dtype)
         t[lp + "post_attention_layernorm.weight"] = w[f"{p}.ffn_norm"].cpu().to(dtype)
         kind = cfg.layer_kinds[il]
-        if kind in ("attn", "swa"):
+        if kind in ("attn", "swa", "nope"):
             a = lp + "self_attn."
             qkv = w[f"{p}.attn.qkv"]
             qw = cfg.n_head * D * (2 if cfg.gated_attn else 1)

@@ -194,13 +194,14 @@ class Decoder:
         return saved
 
     # ------------------------------------------------------------------ blocks
-    def _attn(self, p: str, il: int, x, b: StepBatch, kv: KvCache, window: int):
+    def _attn(self, p: str, il: int, x, b: StepBatch, kv: KvCache, window: int, rope: bool = True):
         cfg, w = self.cfg, self.w
         D = cfg.head_dim
         qkv = ops.linear(x, w[f"{p}.attn.qkv"])
         q, gate = ops.qk_norm_rope_append(qkv, self.n_head_l, self.n_kv_l, D, w.get(f"{p}.attn.q_norm"),
                                           w.get(f"{p}.attn.k_norm"), cfg.rms_eps, cfg.norm_offset, self.cos_sin,
-                                          cfg.rope_dim, b.positions, b.slots, kv.k[il], kv.v[il], cfg.gated_attn)
+                                          cfg.rope_dim if rope else 0, b.positions, b.slots, kv.k[il], kv.v[il],
+                                          cfg.gated_attn)
         scale = cfg.attn_scale or D ** -0.5
         o = ops.paged_attention(q, kv.k[il], kv.v[il], b.block_table, b.ctx_lens, b.cu_q, b.max_q_len, scale,
                                 window=window, decode_splits=b.decode_splits, max_ctx=b.max_ctx or None)
@@ -351,8 +352,8 @@ class Decoder:
             h = pre_normed
         else:
             h, resid = pc.reduce_norm(x, resid, w[f"{p}.attn_norm"], cfg.rms_eps, cfg.norm_offset)
-        if kind in ("attn", "swa"):
-            a = self._attn(p, il, h, b, kv, cfg.sliding_window if kind == "swa" else 0)
+        if kind in ("attn", "swa", "nope"):
+            a = self._attn(p, il, h, b, kv, cfg.sliding_window if kind == "swa" else 0, rope=kind != "nope")
         elif kind == "gdn":
             a = self._gdn(p, il, h, b, st)
         elif kind == "mla":
@@ -447,6 +448,8 @@ class Decoder:
 
     def logits(self, hidden):
         lg = ops.linear(hidden, self.lm_head, out_dtype=torch.float32)
+        if self.cfg.logit_scale != 1.0:
+            lg = lg * self.cfg.logit_scale
         if self.cfg.logit_softcap > 0:
             lg = torch.tanh(lg / self.cfg.logit_softcap) * self.cfg.logit_softcap
         return lg

@@ -24,7 +24,7 @@ def layer_weight_shapes(cfg: ModelConfig, il: int, prefix: Optional[str] = None,
     moe = cfg.is_moe_layer(il) if moe is None else moe
     H = cfg.hidden
     s: Dict[str, Tuple[int, ...]] = {f"{p}.attn_norm": (H,), f"{p}.ffn_norm": (H,)}
-    if kind in ("attn", "swa"):
+    if kind in ("attn", "swa", "nope"):
         D = cfg.head_dim
         qw = cfg.n_head * D * (2 if cfg.gated_attn else 1)
         s[f"{p}.attn.qkv"] = (qw + 2 * cfg.n_kv_head * D, H)

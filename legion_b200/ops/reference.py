@@ -36,6 +36,8 @@ def linear(x, w, residual=None, out_dtype=None):
 def gate_up_act(x, w_gate_up, n_ff: int, act: str = "silu"):
     """w_gate_up rows: [gate(n_ff) | up(n_ff)]; returns act(gate) * up."""
     h = x.float() @ w_gate_up.float().t()
+    if w_gate_up.shape[0] == n_ff:            # un-gated FFN (squared ReLU): only the up projection exists
+        return activation(h, act).to(x.dtype)
     g, u = h[:, :n_ff], h[:, n_ff:2 * n_ff]
     return (activation(g, act) * u).to(x.dtype)
 

@@ -244,3 +244,24 @@ def test_even_chunks_slo_budget_and_waves():
     eng._stats.spec_accepted_tokens = 100
     shallow = eng._spec_depth(8)
     assert deep >= 4 and shallow <= 1
+
+
+@pytest.mark.parametrize("preset", ["tiny-muse", "tiny-gemma", "tiny-nemotron-h"])
+def test_more_architectures_generate_and_reuse_prefix(preset):
+    """Architectures that are configurations of the same block library (NoPE / sliding-window attention, GELU and
+    squared-ReLU FFNs, Mamba-2, logit scale / soft cap, (w - 1) norms, tied embeddings): chunked prefill equals one
+    shot prefill, and a re-sent prompt decodes the same tokens."""
+    from legion_b200.config import PRESETS
+    from legion_b200.engine.lm import EngineConfig, build_engine
+    cfg = PRESETS[preset]()
+    prompt = torch.randint(0, 255, (100,), generator=torch.Generator().manual_seed(4)).tolist()
+    outs = []
+    for chunk in (128, 32):
+        eng = build_engine(cfg, engine_cfg=EngineConfig(ctx_size=256, max_seqs=2, block_size=16, prefill_chunk=chunk),
+                           seed=1)
+        a = eng.generate_text(tokens=prompt, max_tokens=8, ignore_eos=True).token_ids
+        b = eng.generate_text(tokens=prompt, max_tokens=8, ignore_eos=True).token_ids
+        eng.shutdown()
+        assert a == b and len(a) == 8
+        outs.append(a)
+    assert outs[0] == outs[1]
