@@ -91,6 +91,9 @@ def main(argv=None):
     ap.add_argument("--users", type=int, default=16)
     ap.add_argument("--prompt-len", type=int, default=8192)
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--moe-ep", action="store_true",
+                    help="N > 1: whole experts per rank (tokens mirrored, partial outputs meet in the layer's "
+                         "reduction) instead of slicing every expert's FFN rows")
     ap.add_argument("--profile-range", action="store_true",
                     help="after the timed region, replay one decode step between cudaProfilerStart/Stop "
                          "(for a profiler started with --profile-from-start off)")
@@ -119,8 +122,9 @@ def main(argv=None):
         cfg.n_layer = a.layers
         cfg.layer_kinds = cfg.layer_kinds[:a.layers]
     W, K, U, L = max(3, a.warmup), a.steps, a.users, a.prompt_len
-    pctx = pdist.init_from_env("cuda", comm=a.comm, max_rows=8192, hidden=cfg.hidden)
-    shard = Shard(cfg, rank, world) if world > 1 else None
+    ep = bool(a.moe_ep) and world > 1
+    pctx = pdist.init_from_env("cuda", comm=a.comm, max_rows=8192, hidden=cfg.hidden, expert_parallel=ep)
+    shard = Shard(cfg, rank, world, expert_parallel=ep) if world > 1 else None
     t0 = time.time()
     weights = random_weights(cfg, dev, torch.bfloat16, seed=0, shard=shard)
     torch.cuda.synchronize()
@@ -220,7 +224,7 @@ def main(argv=None):
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": round(value / BASELINE_DECODE_16, 3), "dtype": "bf16", "data": "synthetic",
         "config": {"model": a.model + ("" if not a.layers else f"-TRUNCATED-{a.layers}L-INVALID"), "global_batch": U,
-                   "seq_len": L, "parallelism": f"tp{a.gpus}", "users": U, "comm": a.comm if a.gpus > 1 else "none",
+                   "seq_len": L, "parallelism": f"tp{a.gpus}" + ("+ep(experts whole per rank)" if a.moe_ep and a.gpus > 1 else ""), "users": U, "comm": a.comm if a.gpus > 1 else "none",
                    "l2": "inputs larger than L2 (each step streams >40 GB of weights and KV)", "page": 64},
         "clocks": clk,
         "e2e": {"value": round(e2e_value, 2), "unit": "tok/s", "h2d_bytes_per_step": int(h2d_per),

@@ -264,7 +264,7 @@ void moe_route_small(const Tensor& x, const OptT& norm_w, double eps, double w_o
                      const Tensor& w, const OptT& bias, int64_t k, int64_t mode, bool renorm, double route_scale,
                      int64_t n_group, int64_t topk_group, Tensor& logits, Tensor& ids, Tensor& wts, int64_t bn,
                      Tensor& tile_group, Tensor& slot_base, Tensor& tile_ntok, Tensor& meta, Tensor& out_rows,
-                     Tensor& tok_scale, Tensor& done_ctr) {
+                     Tensor& tok_scale, Tensor& done_ctr, int64_t e_lo, int64_t n_local) {
   check_bf16(x, "x");
   check_bf16(w, "w");
   const int64_t T = x.size(0), E = w.size(0);
@@ -282,7 +282,7 @@ void moe_route_small(const Tensor& x, const OptT& norm_w, double eps, double w_o
                   float(route_scale), int(n_group), int(topk_group), ids.data_ptr<int>(), wts.data_ptr<float>(),
                   int(T), int(bn), tile_group.data_ptr<int>(), slot_base.data_ptr<int>(), tile_ntok.data_ptr<int>(),
                   meta.data_ptr<int>(), out_rows.data_ptr<int>(), tok_scale.data_ptr<float>(),
-                  reinterpret_cast<unsigned int*>(done_ctr.data_ptr()), cur_stream()) == 0,
+                  reinterpret_cast<unsigned int*>(done_ctr.data_ptr()), int(e_lo), int(n_local), cur_stream()) == 0,
               "moe_route_small: unsupported (tokens <= 64 and <= bn, pairs <= 1024, experts <= 512, k <= 32)");
 }
 

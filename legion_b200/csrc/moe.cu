@@ -169,7 +169,7 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
     float* logits, const float* __restrict__ bias, int E, int k, int mode, int renorm, float route_scale, int n_group,
     int topk_group, int* ids, float* wts, int T, int bn, int* __restrict__ tile_group, int* __restrict__ slot_base,
     int* __restrict__ tile_ntok, int* __restrict__ meta, int* __restrict__ out_rows, float* __restrict__ tok_scale,
-    unsigned int* done_ctr) {
+    unsigned int* done_ctr, int e_lo, int n_local) {
   __shared__ float red[2][8][8];
   __shared__ float s_inv[2][8];
   __shared__ int s_last;
@@ -305,7 +305,8 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
   __syncthreads();
   int n_active = 0;
   {
-    const int cnt = (tid < E) ? s_slot[tid] : 0;
+    // only this rank's experts [e_lo, e_lo + n_local) become tiles (expert parallelism with mirrored tokens)
+    const int cnt = (tid < E && tid >= e_lo && tid < e_lo + n_local) ? s_slot[tid] : 0;
     const unsigned bal = __ballot_sync(0xffffffffu, cnt > 0);
     if (lane == 0) s_wsum[warp] = __popc(bal);
     __syncthreads();
@@ -315,7 +316,7 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
     int slot = -1;
     if (cnt > 0) {
       slot = before + __popc(bal & ((1u << lane) - 1));
-      tile_group[slot] = tid;
+      tile_group[slot] = tid - e_lo;
       slot_base[slot] = slot * bn;
       tile_ntok[slot] = T;
     }
@@ -326,6 +327,7 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
   __syncthreads();
   for (int p = tid; p < P; p += 512) {
     const int slot = s_slot[s_ids[p]];
+    if (slot < 0) continue;          // the pair belongs to another rank's expert
     const int t = p / k;
     out_rows[slot * bn + t] = p;
     tok_scale[slot * bn + t] = s_wts[p];
@@ -340,7 +342,7 @@ int moe_route_small_launch(const void* x, long ldx, const float* norm_w, float e
                            long ldn, const void* w, long ldw, int H, float* logits, const float* bias, int E, int k,
                            int mode, int renorm, float route_scale, int n_group, int topk_group, int* ids, float* wts,
                            int T, int bn, int* tile_group, int* slot_base, int* tile_ntok, int* meta, int* out_rows,
-                           float* tok_scale, unsigned int* done_ctr, cudaStream_t s) {
+                           float* tok_scale, unsigned int* done_ctr, int e_lo, int n_local, cudaStream_t s) {
   if (T <= 0) return 0;
   if (k > 32 || E > 512 || n_group > 32 || H % 8 || T > 64 || T * k > 1024 || T > bn) return 1;
   auto xb = static_cast<const __nv_bfloat16*>(x);
@@ -349,7 +351,7 @@ int moe_route_small_launch(const void* x, long ldx, const float* norm_w, float e
 #define LB_ROUTE(MAXE)                                                                                              \
   launch_pdl(moe_route_small_kernel<MAXE>, dim3(E), dim3(512), 0, s, xb, ldx, norm_w, eps, w_offset, xn, ldn, wb,  \
              ldw, H, logits, bias, E, k, mode, renorm, route_scale, n_group, topk_group, ids, wts, T, bn,           \
-             tile_group, slot_base, tile_ntok, meta, out_rows, tok_scale, done_ctr)
+             tile_group, slot_base, tile_ntok, meta, out_rows, tok_scale, done_ctr, e_lo, n_local)
   if (E <= 128) LB_ROUTE(128);
   else if (E <= 256) LB_ROUTE(256);
   else LB_ROUTE(512);

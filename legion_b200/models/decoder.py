@@ -310,8 +310,10 @@ class Decoder:
         cfg, w, pc = self.cfg, self.w, self.pctx
         fuse_res = residual is not None and pc.tp == 1
         if il_moe:
+            e_lo, e_hi = pc.expert_range(cfg.n_expert)
             routing = ops.router(x, w[f"{p}.moe.router"], cfg.top_k, cfg.router_mode, cfg.norm_topk,
-                                 cfg.route_scale, w.get(f"{p}.moe.router_bias"), cfg.n_group, cfg.topk_group)
+                                 cfg.route_scale, w.get(f"{p}.moe.router_bias"), cfg.n_group, cfg.topk_group,
+                                 e_lo=e_lo, n_local=e_hi - e_lo)
             ids, wts = routing
             shared = gate = None
             if cfg.shared_ff > 0:

@@ -82,11 +82,13 @@ def router_topk(logits, k, mode="softmax", renorm=True, route_scale=1.0, bias=No
     return _ref.router_topk(logits, k, mode, renorm, route_scale, bias, n_group, topk_group)
 
 
-def router(x, w_router, k, mode="softmax", renorm=True, route_scale=1.0, bias=None, n_group=1, topk_group=1):
+def router(x, w_router, k, mode="softmax", renorm=True, route_scale=1.0, bias=None, n_group=1, topk_group=1,
+           e_lo=0, n_local=None):
     """Router projection + top-k. Returns an object that unpacks as ``ids, wts`` ([T, k] int32 / float32); on the
-    GPU it may also carry the dense routing tables of a decode-sized step (pass it on as ``routing=``)."""
+    GPU it may also carry the dense routing tables of a decode-sized step for the experts
+    [e_lo, e_lo + n_local) of this rank (pass it on as ``routing=``)."""
     if _cuda(x):
-        return _sm.router(x, w_router, k, mode, renorm, route_scale, bias, n_group, topk_group)
+        return _sm.router(x, w_router, k, mode, renorm, route_scale, bias, n_group, topk_group, None, e_lo, n_local)
     logits = _ref.linear(x, w_router, out_dtype=torch.float32)
     return _ref.router_topk(logits, k, mode, renorm, route_scale, bias, n_group, topk_group)
 

@@ -371,10 +371,11 @@ def router_topk(logits, k, mode="softmax", renorm=True, route_scale=1.0, bias=No
 class Routing:
     """Router result of one step: ``ids`` / ``wts`` [T, k] and, for decode-sized steps, the dense routing tables
     (``dense``) that let the expert GEMMs run without a gather. Unpacks as ``ids, wts = routing``."""
-    __slots__ = ("ids", "wts", "dense", "x_normed")
+    __slots__ = ("ids", "wts", "dense", "x_normed", "e_lo", "n_local")
 
-    def __init__(self, ids, wts, dense=None, x_normed=None):
+    def __init__(self, ids, wts, dense=None, x_normed=None, e_lo=0, n_local=None):
         self.ids, self.wts, self.dense, self.x_normed = ids, wts, dense, x_normed
+        self.e_lo, self.n_local = e_lo, n_local      # expert range the dense tables were built for
 
     def __iter__(self):
         yield self.ids
@@ -399,7 +400,7 @@ class DenseRoute:
 
 
 def router(x, w_router, k, mode="softmax", renorm=True, route_scale=1.0, bias=None, n_group=1, topk_group=1,
-           norm=None):
+           norm=None, e_lo: int = 0, n_local: Optional[int] = None):
     """Router logits and top-k selection -> ``Routing``. Decode-sized steps (<= 64 tokens, <= 1024 pairs) run as
     ONE launch that also builds the dense routing tables; with ``norm=(weight, eps, w_offset)`` that launch first
     applies the RMSNorm to ``x`` (the raw residual stream) and ``Routing.x_normed`` is the normalised input.
@@ -430,8 +431,9 @@ def router(x, w_router, k, mode="softmax", renorm=True, route_scale=1.0, bias=No
     xn = torch.empty_like(x) if norm is not None else None
     C.moe_route_small(x, norm[0] if norm else None, norm[1] if norm else 0.0, norm[2] if norm else 0.0, xn, w_router,
                       bias, k, 0 if mode == "softmax" else 1, renorm, route_scale, n_group, topk_group, logits, ids, wts,
-                      bn, dr.tile_group, dr.slot_base, dr.tile_ntok, dr.meta, dr.out_rows, dr.tok_scale, ctr)
-    return Routing(ids, wts, dr, xn)
+                      bn, dr.tile_group, dr.slot_base, dr.tile_ntok, dr.meta, dr.out_rows, dr.tok_scale, ctr,
+                      e_lo, E if n_local is None else n_local)
+    return Routing(ids, wts, dr, xn, e_lo, E if n_local is None else n_local)
 
 
 class MoePlan:
@@ -477,7 +479,7 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[Moe
         (dn2, dn_sc), dn_gs = w_down.view2d(), w_down.gscale
     else:
         dn2, dn_sc, dn_gs = w_down.view(E_local * H, n_ff), None, None
-    if (routing is not None and routing.dense is not None and routing.dense.E == E_local and e_lo == 0
+    if (routing is not None and routing.dense is not None and routing.n_local == E_local and routing.e_lo == e_lo
             and routing.ids is ids and TUNE["dense_route"]):
         # decode-sized step: every active expert runs over all T tokens in place (no plan, no gather)
         dr = routing.dense
@@ -496,10 +498,11 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[Moe
             out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
         y = dr.y_pairs[:P]
         if norm is None:
-            C.moe_combine(y, ids, 0, E_local, shared, shared_gate, residual, out, None, 0.0, 0.0, None)
+            C.moe_combine(y, ids, e_lo, e_lo + E_local, shared, shared_gate, residual, out, None, 0.0, 0.0, None)
             return out
         normed = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
-        C.moe_combine(y, ids, 0, E_local, shared, shared_gate, residual, out, norm[0], norm[1], norm[2], normed)
+        C.moe_combine(y, ids, e_lo, e_lo + E_local, shared, shared_gate, residual, out, norm[0], norm[1], norm[2],
+                      normed)
         return out, normed
     if plan is None:
         bn = 32 if T * k <= 32 * E_local else (64 if T * k <= 64 * E_local else 128)
