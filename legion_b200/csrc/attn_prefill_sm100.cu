@@ -7,7 +7,12 @@
 //   warps 0..3 (thread = query row = TMEM lane): tcgen05.ld S, causal / window mask, online softmax
 //       in base 2, P written to smem as the swizzled K-major A operand of the second MMA, O rescaled
 //       in TMEM (tcgen05.ld / st) when the running maximum moved.
-// K/V tiles are double buffered, so the loads for block i+1 fly during the softmax of block i.
+// K/V tiles are double buffered, so the loads for block i+1 fly during the softmax of block i. Head dim 128 runs
+// with 64-key blocks, two K stages and ONE V stage (V of block i is fetched while the softmax of block i runs):
+// 97 KB of shared memory and 256 TMEM columns per CTA, so two CTAs share an SM and one's softmax overlaps the
+// other's MMAs. The softmax keeps the 64 scores of a row in registers (one TMEM read), skips the mask
+// comparisons on blocks that are entirely visible, and rescales O only when the row maximum grew by more than
+// 2^8 (probabilities are then relative to a slightly stale maximum).
 // Sequence lengths, query offsets and block tables are data; the grid is (q tiles, heads, seqs).
 //
 // Counterparts in the reference: src/cuda/sm80/paged_attn.cuh (paged_prefill_mma, split verify),
@@ -44,28 +49,33 @@ struct PrefillArgs {
   int* status;
 };
 
+static constexpr float PREFILL_RESCALE_LOG2 = 8.f;
+
 template <int D, int BKV>
 struct PrefillCfg {
+  static constexpr bool VSINGLE = (D == 128 && BKV == 64);   // one V stage: two CTAs per SM
   static constexpr int HALVES = D / 64;               // 64-column (128-byte) halves of a head row
   static constexpr int Q_BYTES = HALVES * 128 * 128;  // 128 rows x 128 B per half
   static constexpr int KV_BYTES = HALVES * BKV * 128;
   static constexpr int P_BYTES = (BKV / 64) * 128 * 128;
   static constexpr int STAGES = 2;
-  static constexpr int SMEM = Q_BYTES + STAGES * 2 * KV_BYTES + P_BYTES + 1024 + 256;
+  static constexpr int VSTAGES = VSINGLE ? 1 : STAGES;
+  static constexpr int SMEM = Q_BYTES + (STAGES + VSTAGES) * KV_BYTES + P_BYTES + 1024 + 256;
   static constexpr int TMEM_RAW = BKV + D;
   static constexpr int TMEM_COLS = TMEM_RAW <= 128 ? 128 : (TMEM_RAW <= 256 ? 256 : 512);
 };
 
 template <int D, int BKV>
-__global__ void __launch_bounds__(160, 1)
+__global__ void __launch_bounds__(160, (D == 128 && BKV == 64) ? 2 : 1)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const PrefillArgs a) {
   using Cfg = PrefillCfg<D, BKV>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_s = smem;
-  uint8_t* kv_s = q_s + Cfg::Q_BYTES;                      // [stage][K | V]
-  uint8_t* p_s = kv_s + Cfg::STAGES * 2 * Cfg::KV_BYTES;
+  uint8_t* k_s = q_s + Cfg::Q_BYTES;                       // [STAGES] K tiles
+  uint8_t* v_s = k_s + Cfg::STAGES * Cfg::KV_BYTES;        // [VSTAGES] V tiles
+  uint8_t* p_s = v_s + Cfg::VSTAGES * Cfg::KV_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + Cfg::P_BYTES);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;   // [2]
@@ -122,29 +132,27 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (warp == 4) {
     if (lane == 0) {
       // ------------------------------------------------------------ loads + MMA issue
-      auto load_kv = [&](int blk, int stage) {
-        uint8_t* ks = kv_s + stage * 2 * Cfg::KV_BYTES;
-        uint8_t* vs = ks + Cfg::KV_BYTES;
+      auto load_tile = [&](const CUtensorMap* tm, uint8_t* dst, uint64_t* bar, int blk) {
         const int tok0 = blk * BKV;
-        mbar_expect_tx(&k_full[stage], Cfg::KV_BYTES);
-        mbar_expect_tx(&v_full[stage], Cfg::KV_BYTES);
+        mbar_expect_tx(bar, Cfg::KV_BYTES);
         for (int p = 0; p < pages_per_blk; ++p) {
           const int tok = tok0 + p * a.page;
           // pages past the end of the sequence read cell row 0 of a valid page: masked later
           const int pg = (tok < ctx) ? bt[tok / a.page] : bt[0];
           const int cell = pg * a.page;
 #pragma unroll
-          for (int h = 0; h < Cfg::HALVES; ++h) {
-            tma_load_3d(ks + h * (BKV * 128) + p * a.page * 128, &tmK, &k_full[stage], h * 64, kvh, cell);
-            tma_load_3d(vs + h * (BKV * 128) + p * a.page * 128, &tmV, &v_full[stage], h * 64, kvh, cell);
-          }
+          for (int h = 0; h < Cfg::HALVES; ++h)
+            tma_load_3d(dst + h * (BKV * 128) + p * a.page * 128, tm, bar, h * 64, kvh, cell);
         }
       };
+      auto load_k = [&](int blk, int stage) { load_tile(&tmK, k_s + stage * Cfg::KV_BYTES, &k_full[stage], blk); };
+      auto load_v = [&](int blk, int stage) { load_tile(&tmV, v_s + stage * Cfg::KV_BYTES, &v_full[stage], blk); };
       mbar_expect_tx(q_full, Cfg::Q_BYTES);
 #pragma unroll
       for (int h = 0; h < Cfg::HALVES; ++h)
         tma_load_3d(q_s + h * (128 * 128), &tmQ, q_full, h * 64, head, q0 + tile_row0);
-      load_kv(blk_lo, 0);
+      load_k(blk_lo, 0);
+      load_v(blk_lo, 0);
       constexpr uint32_t idesc_s = umma_idesc(128, BKV, 1, 1, 0, 0);
       constexpr uint32_t idesc_o = umma_idesc(128, D, 1, 1, 0, 1);  // B (= V) is MN-major
       bool ok = mbar_wait(q_full, 0, abort_flag);
@@ -157,8 +165,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         tc_fence_after();
         const uint32_t qa = smem_u32(q_s);
-        const uint32_t ka = smem_u32(kv_s + st * 2 * Cfg::KV_BYTES);
-        const uint32_t va = ka + Cfg::KV_BYTES;
+        const int vst = Cfg::VSINGLE ? 0 : st;
+        const uint32_t vph = Cfg::VSINGLE ? uint32_t(i & 1) : ph;
+        const uint32_t ka = smem_u32(k_s + st * Cfg::KV_BYTES);
+        const uint32_t va = smem_u32(v_s + vst * Cfg::KV_BYTES);
 #pragma unroll
         for (int h = 0; h < Cfg::HALVES; ++h) {
 #pragma unroll
@@ -175,11 +185,17 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_EMPTY); break;
           }
         }
-        if (i + 1 < n_blk) load_kv(blk_lo + i + 1, st ^ 1);
+        if (i + 1 < n_blk) load_k(blk_lo + i + 1, st ^ 1);
+        if (Cfg::VSINGLE) {
+          // the single V buffer is free now (PV of block i-1 is done): fetch V of THIS block under its softmax
+          if (i >= 1) load_v(blk_lo + i, 0);
+        } else if (i + 1 < n_blk) {
+          load_v(blk_lo + i + 1, st ^ 1);
+        }
         if (!mbar_wait(p_ready, i & 1, abort_flag)) {
           *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FLAG); break;
         }
-        if (!mbar_wait(&v_full[st], ph, abort_flag)) {
+        if (!mbar_wait(&v_full[vst], vph, abort_flag)) {
           *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FULL); break;
         }
         tc_fence_after();
@@ -211,61 +227,121 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       int hi = a.causal ? min(ctx, qpos + 1) : ctx;   // exclusive key bound for this row
       int lo = (a.window > 0) ? max(0, qpos - a.window + 1) : 0;
       if (!row_ok) { hi = 0; lo = 0; }
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < BKV; c += 32) {
-        uint32_t r[32];
-        tmem_ld32(tmem_S + lane_off + c, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int key = key0 + c + j;
-          if (key >= lo && key < hi) mx = fmaxf(mx, __uint_as_float(r[j]));
-        }
-      }
-      const float m_new = fmaxf(m, mx * a.scale_log2);
-      const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
-      // P may be overwritten and O rescaled only after the previous PV has finished
-      if (i >= 1) {
-        if (!__all_sync(0xffffffffu, mbar_wait(o_done, (i - 1) & 1, abort_flag))) {
-          *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_EMPTY); ok = false; break;
-        }
-        tc_fence_after();
-      }
-      // pass 2: probabilities -> swizzled smem
+      // blocks entirely inside every row's visible range need no per-element mask (all interior blocks of a
+      // causal prompt): uniform over the CTA
+      const bool full_blk = a.window == 0 && rows_here == 128 && key0 + BKV <= (a.causal ? min(ctx, pos0 + 1) : ctx);
+      float alpha = 1.f;
       float sum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < BKV; c += 32) {
-        uint32_t r[32];
-        tmem_ld32(tmem_S + lane_off + c, r);
+      if (BKV <= 64) {
+        // ---- one TMEM read: the row's scores stay in registers between the maximum and the exponentials
+        uint32_t r[BKV <= 64 ? BKV : 1];
+#pragma unroll
+        for (int c = 0; c < BKV; c += 32) tmem_ld32(tmem_S + lane_off + c, *reinterpret_cast<uint32_t(*)[32]>(&r[c]));
         tmem_ld_wait();
-        uint32_t packed[16];
+        float mx = -INFINITY;
+        if (full_blk) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float p0 = 0.f, p1 = 0.f;
-          const int key = key0 + c + j;
-          if (key >= lo && key < hi) p0 = exp2f(__uint_as_float(r[j]) * a.scale_log2 - m_new);
-          if (key + 1 >= lo && key + 1 < hi) p1 = exp2f(__uint_as_float(r[j + 1]) * a.scale_log2 - m_new);
-          // sum what the tensor core will see (bf16-rounded) to keep numerator and denominator consistent
-          const __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
-          const float2 f = __bfloat1622float2(b);
-          sum += f.x + f.y;
-          packed[j / 2] = *reinterpret_cast<const uint32_t*>(&b);
+          for (int j = 0; j < BKV; ++j) mx = fmaxf(mx, __uint_as_float(r[j]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < BKV; ++j) {
+            const int key = key0 + j;
+            if (key >= lo && key < hi) mx = fmaxf(mx, __uint_as_float(r[j]));
+          }
         }
-        // 32 columns = 4 chunks of 16 bytes in half (c / 64)
-        uint8_t* half_base = p_s + (c / 64) * (128 * 128) + row * 128;
+        const float m_blk = mx * a.scale_log2;
+        if (m_blk > m + PREFILL_RESCALE_LOG2 || (m == -INFINITY && m_blk != -INFINITY)) {
+          alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_blk);
+          m = m_blk;
+        }
+        // P may be overwritten and O rescaled only after the previous PV has finished
+        if (i >= 1) {
+          if (!__all_sync(0xffffffffu, mbar_wait(o_done, (i - 1) & 1, abort_flag))) {
+            *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_EMPTY); ok = false; break;
+          }
+          tc_fence_after();
+        }
+        const float neg_m = (m == -INFINITY) ? 0.f : -m;
+        uint32_t packed[BKV <= 64 ? BKV / 2 : 1];
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          const int chunk = ((c % 64) / 8 + ch) ^ (row & 7);
+        for (int j = 0; j < BKV; j += 2) {
+          float p0 = exp2f(fmaf(__uint_as_float(r[j]), a.scale_log2, neg_m));
+          float p1 = exp2f(fmaf(__uint_as_float(r[j + 1]), a.scale_log2, neg_m));
+          if (!full_blk) {
+            const int key = key0 + j;
+            if (!(key >= lo && key < hi)) p0 = 0.f;
+            if (!(key + 1 >= lo && key + 1 < hi)) p1 = 0.f;
+          }
+          // sum what the tensor core will see (bf16-rounded) to keep numerator and denominator consistent
+          const __nv_bfloat162 bb = __floats2bfloat162_rn(p0, p1);
+          const float2 f = __bfloat1622float2(bb);
+          sum += f.x + f.y;
+          packed[j / 2] = *reinterpret_cast<const uint32_t*>(&bb);
+        }
+        uint8_t* half_base = p_s + row * 128;
+#pragma unroll
+        for (int ch = 0; ch < BKV / 8; ++ch) {
+          const int chunk = ch ^ (row & 7);
           *reinterpret_cast<uint4*>(half_base + chunk * 16) =
               make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
         }
+      } else {
+        // ---- two TMEM passes (128-key blocks): row maximum, then probabilities -> swizzled smem
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (int c = 0; c < BKV; c += 32) {
+          uint32_t r[32];
+          tmem_ld32(tmem_S + lane_off + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int key = key0 + c + j;
+            if (full_blk || (key >= lo && key < hi)) mx = fmaxf(mx, __uint_as_float(r[j]));
+          }
+        }
+        const float m_blk = mx * a.scale_log2;
+        if (m_blk > m + PREFILL_RESCALE_LOG2 || (m == -INFINITY && m_blk != -INFINITY)) {
+          alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_blk);
+          m = m_blk;
+        }
+        if (i >= 1) {
+          if (!__all_sync(0xffffffffu, mbar_wait(o_done, (i - 1) & 1, abort_flag))) {
+            *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_EMPTY); ok = false; break;
+          }
+          tc_fence_after();
+        }
+        const float neg_m = (m == -INFINITY) ? 0.f : -m;
+#pragma unroll 1
+        for (int c = 0; c < BKV; c += 32) {
+          uint32_t r[32];
+          tmem_ld32(tmem_S + lane_off + c, r);
+          tmem_ld_wait();
+          uint32_t packed[16];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float p0 = exp2f(fmaf(__uint_as_float(r[j]), a.scale_log2, neg_m));
+            float p1 = exp2f(fmaf(__uint_as_float(r[j + 1]), a.scale_log2, neg_m));
+            const int key = key0 + c + j;
+            if (!full_blk && !(key >= lo && key < hi)) p0 = 0.f;
+            if (!full_blk && !(key + 1 >= lo && key + 1 < hi)) p1 = 0.f;
+            const __nv_bfloat162 bb = __floats2bfloat162_rn(p0, p1);
+            const float2 f = __bfloat1622float2(bb);
+            sum += f.x + f.y;
+            packed[j / 2] = *reinterpret_cast<const uint32_t*>(&bb);
+          }
+          // 32 columns = 4 chunks of 16 bytes in half (c / 64)
+          uint8_t* half_base = p_s + (c / 64) * (128 * 128) + row * 128;
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            const int chunk = ((c % 64) / 8 + ch) ^ (row & 7);
+            *reinterpret_cast<uint4*>(half_base + chunk * 16) =
+                make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
+          }
+        }
       }
       l = l * alpha + sum;
-      m = m_new;
       if (i >= 1) {
-        // every thread rescales its own O row; skipping when alpha == 1 is the common case late in a row
+        // every thread rescales its own O row; with the lazy threshold this is rare after the first blocks
         if (__any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll 1
           for (int c = 0; c < D; c += 32) {
@@ -359,7 +435,7 @@ int prefill_attn_launch(const void* q, long T, const void* k_cache, const void* 
                         int table_width, int page, int n_seqs, int max_q_len, int Hq, int Hkv, int D, float scale,
                         int window, int causal, void* out, int* status, cudaStream_t s) {
   if (n_seqs <= 0 || max_q_len <= 0) return 0;
-  const int BKV = D > 128 ? 64 : 128;
+  const int BKV = D >= 128 ? 64 : 128;
   if (page <= 0 || BKV % page != 0 || page % 8 != 0) {
     snprintf(g_attn_err, sizeof(g_attn_err), "prefill attention: page size %d must be a multiple of 8 dividing %d",
              page, BKV);
@@ -386,7 +462,7 @@ int prefill_attn_launch(const void* q, long T, const void* k_cache, const void* 
   a.out = static_cast<__nv_bfloat16*>(out); a.status = status;
   dim3 grid((max_q_len + 127) / 128, Hq, n_seqs);
   if (D == 64) return launch_prefill<64, 128>(tq, tk, tv, a, grid, s);
-  if (D == 128) return launch_prefill<128, 128>(tq, tk, tv, a, grid, s);
+  if (D == 128) return launch_prefill<128, 64>(tq, tk, tv, a, grid, s);
   return launch_prefill<256, 64>(tq, tk, tv, a, grid, s);
 }
 

@@ -143,6 +143,51 @@ void wgemm_allreduce(const Tensor& w, const Tensor& x, Tensor& slot, int64_t bn,
   TORCH_CHECK(lb::wgemm_launch(h, cur_stream()) == 0, lb::wgemm_last_error());
 }
 
+// Dense GEMM whose kernel head all-gathers the activation rows from the ranks' symmetric buffers into x_full.
+void wgemm_allgather(const Tensor& w, Tensor& x_full, Tensor& out, const OptT& residual, int64_t bn, int64_t split_k,
+                     const OptT& ws, const OptT& counters, Tensor& status, std::vector<int64_t> buffers,
+                     std::vector<int64_t> signals, int64_t rank, int64_t src_off, int64_t slot_base, Tensor& seq,
+                     Tensor& ctrs, int64_t rows_per_rank, int64_t budget_ns, Tensor& comm_status) {
+  check_bf16(w, "w");
+  check_bf16(x_full, "x_full");
+  TORCH_CHECK(w.dim() == 2 && x_full.dim() == 2 && out.dim() == 2 && w.size(1) == x_full.size(1) &&
+                  x_full.is_contiguous(), "wgemm_allgather: shapes");
+  TORCH_CHECK(out.size(0) == x_full.size(0) && out.size(1) >= w.size(0) && out.stride(1) == 1, "wgemm_allgather: out");
+  TORCH_CHECK(buffers.size() == signals.size() && buffers.size() <= LB_MAX_RANKS && ctrs.numel() >= 2 &&
+                  x_full.size(1) % 8 == 0, "wgemm_allgather: bad peer table");
+  c10::cuda::CUDAGuard guard(w.device());
+  lb::WgemmHost h{};
+  h.w = w.data_ptr(); h.w_rows = w.size(0); h.ldw = w.stride(0);
+  h.x = x_full.data_ptr(); h.x_rows = x_full.size(0); h.ldx = x_full.stride(0);
+  h.out = out.data_ptr(); h.ldo = out.stride(0); h.out_f32 = out.scalar_type() == at::kFloat;
+  if (residual.has_value()) {
+    h.residual = reinterpret_cast<const __nv_bfloat16*>(residual->data_ptr());
+    h.ldr = residual->stride(0);
+  }
+  h.K = int(w.size(1)); h.n_feat = int(w.size(0)); h.n_tok = int(x_full.size(0));
+  h.bn = int(bn); h.dual = false;
+  h.split_k = int(split_k);
+  h.ws = optpm<float>(ws);
+  h.counters = optpm<int>(counters);
+  h.status = reinterpret_cast<int*>(status.data_ptr());
+  auto& c = h.head;
+  c.enabled = 1;
+  c.peers.world = int(buffers.size());
+  c.peers.rank = int(rank);
+  for (size_t i = 0; i < buffers.size(); ++i) {
+    c.peers.buffer[i] = reinterpret_cast<void*>(buffers[i]);
+    c.peers.signal[i] = reinterpret_cast<void*>(signals[i]);
+  }
+  c.src_off = src_off; c.slot_base = int(slot_base);
+  c.seq_ptr = reinterpret_cast<uint32_t*>(seq.data_ptr());
+  c.ctrs = reinterpret_cast<unsigned int*>(ctrs.data_ptr());
+  c.T = int(x_full.size(0)); c.K = int(x_full.size(1)); c.rows_per_rank = int(rows_per_rank);
+  c.x_local = reinterpret_cast<__nv_bfloat16*>(x_full.data_ptr());
+  c.budget_ns = static_cast<unsigned long long>(budget_ns);
+  c.status = reinterpret_cast<int*>(comm_status.data_ptr());
+  TORCH_CHECK(lb::wgemm_launch(h, cur_stream()) == 0, lb::wgemm_last_error());
+}
+
 void rmsnorm(const Tensor& x, const OptT& res_in, const OptT& res_out, const Tensor& w, Tensor& y, double eps,
              double w_offset) {
   check_bf16(x, "x");
@@ -389,6 +434,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         pybind11::arg("n_tok"), pybind11::arg("out_peer"), pybind11::arg("tile_out0") = pybind11::none(),
         pybind11::arg("w_scales") = pybind11::none(), pybind11::arg("w_gscale") = pybind11::none());
   m.def("wgemm_allreduce", &wgemm_allreduce);
+  m.def("wgemm_allgather", &wgemm_allgather);
   m.def("rmsnorm", &rmsnorm);
   m.def("qk_norm_rope_append", &qk_norm_rope_append);
   m.def("sigmoid_gate", &sigmoid_gate);

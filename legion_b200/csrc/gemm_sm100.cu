@@ -163,6 +163,64 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
   griddep_wait();
   griddep_launch();
 
+  // ------------------------------------------------------------------ fused all-gather of the activation rows
+  // Flag round with the peers (their shards were written by earlier kernels), then all CTAs of this persistent
+  // grid copy the ranks' row blocks over NVLink peer loads into the local operand tensor, meet at a grid-wide
+  // arrive, and only then do the TMA loads of X start: all-gather and GEMM are one launch.
+  if (a.head.enabled) {
+    const WgemmCommHead& hd = a.head;
+    const uint32_t seq = *reinterpret_cast<const volatile uint32_t*>(hd.seq_ptr) + 1;
+    if (blockIdx.x == 0 && threadIdx.x < hd.peers.world) {
+      __threadfence_system();
+      st_release_sys(reinterpret_cast<uint32_t*>(hd.peers.signal[threadIdx.x]) + hd.slot_base + hd.peers.rank, seq);
+    }
+    if (threadIdx.x == 0) *last_flag = 1;
+    __syncthreads();
+    if (threadIdx.x < hd.peers.world) {
+      const uint32_t* mine =
+          reinterpret_cast<const uint32_t*>(hd.peers.signal[hd.peers.rank]) + hd.slot_base + threadIdx.x;
+      if (!wait_flag_geq(mine, seq, hd.budget_ns)) {
+        *last_flag = 0;
+        atomicCAS(hd.status, 0, ST_TIMEOUT_FLAG);
+      }
+    }
+    __syncthreads();
+    if (*last_flag) {
+      const int nv = hd.K / 8;
+      const long total = long(hd.T) * nv;
+      for (long i = long(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += long(gridDim.x) * blockDim.x) {
+        const int row = int(i / nv), v = int(i % nv);
+        int owner = row / hd.rows_per_rank;
+        if (owner >= hd.peers.world) owner = hd.peers.world - 1;
+        const uint4 u = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(hd.peers.buffer[owner]) +
+                                                       hd.src_off + long(row) * hd.K * 2)[v];
+        reinterpret_cast<uint4*>(hd.x_local + long(row) * hd.K)[v] = u;
+      }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      atomicAdd(&hd.ctrs[0], 1u);
+      const uint64_t t0 = globaltimer_ns();
+      uint32_t spins = 0;
+      while (*reinterpret_cast<volatile unsigned int*>(&hd.ctrs[0]) < gridDim.x) {     // every CTA has copied
+        if ((++spins & 0x3f) == 0 && globaltimer_ns() - t0 > hd.budget_ns) {
+          atomicCAS(hd.status, 0, ST_TIMEOUT_FLAG);
+          break;
+        }
+      }
+      __threadfence();
+      const unsigned int old = atomicAdd(&hd.ctrs[1], 1u);       // last one out resets and publishes the sequence
+      if (old == gridDim.x - 1) {
+        hd.ctrs[0] = 0;
+        hd.ctrs[1] = 0;
+        *reinterpret_cast<volatile uint32_t*>(hd.seq_ptr) = seq;
+      }
+    }
+    __syncthreads();
+    asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy stores above -> TMA reads below
+  }
+
   const int n_tok_tiles = a.tile_group ? min(*a.n_tiles_dev, a.n_tok_tiles_max) : (a.n_tok + BN - 1) / BN;
   const int num_kb = (a.K + BK - 1) / BK;
   const int kb_per_split = (num_kb + a.split_k - 1) / a.split_k;
@@ -657,6 +715,7 @@ int wgemm_launch(const WgemmHost& h, cudaStream_t stream) {
   a.K = h.K; a.n_feat = h.n_feat; a.feat_tiles = (h.n_feat + BM - 1) / BM;
   a.n_tok = h.n_tok;
   a.comm = h.comm;
+  a.head = h.head;
   a.w_gscale = h.w_gscale;
   a.tile_group = h.tile_group; a.tile_tok0 = h.tile_tok0; a.tile_out0 = h.tile_out0; a.tile_ntok = h.tile_ntok; a.n_tiles_dev = h.n_tiles_dev;
   a.n_tok_tiles_max = h.n_tok_tiles_max;

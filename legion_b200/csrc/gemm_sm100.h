@@ -26,6 +26,22 @@ struct WgemmCommTail {
   int* status;                    // communicator status word
 };
 
+// Optional head of the GEMM kernel: all-gather of the activation rows. Rank r has written rows
+// [r * rows_per_rank, ...) of the [T, K] activation into ITS OWN symmetric buffer at byte offset src_off (row pitch
+// K elements); the kernel gathers all ranks' rows into the local tensor the X tensor map points at, then multiplies.
+struct WgemmCommHead {
+  int enabled;
+  CommPeers peers;
+  long src_off;
+  int slot_base;
+  uint32_t* seq_ptr;
+  unsigned int* ctrs;             // [2] arrival / exit counters, zero on entry, left zero
+  int T, K, rows_per_rank;
+  __nv_bfloat16* x_local;         // [T, K] gather destination (= the GEMM's activation operand)
+  unsigned long long budget_ns;
+  int* status;
+};
+
 struct WgemmArgs {
   void* out;                      // bf16 or f32 [rows, ldo]
   long ldo;
@@ -50,6 +66,7 @@ struct WgemmArgs {
   void* out_peer[8];              // EP combine: per-rank output bases (peer-mapped); used when n_out_peer > 0,
   int n_out_peer;                 //   out_rows[] then holds (rank << 24) | row
   WgemmCommTail comm;
+  WgemmCommHead head;
   const float* w_gscale;          // NVFP4 weights: per-group (x2 for DUAL: gate, up) tensor scale, applied in the epilogue
 };
 
@@ -71,6 +88,7 @@ struct WgemmHost {
   int* status;
   void* out_peer[8]; int n_out_peer;
   WgemmCommTail comm;
+  WgemmCommHead head;
   const void* w_scales;           // non-null: w holds NVFP4 codes [rows, K/2] bytes, this the e4m3 block scales [rows, K/16]
   const float* w_gscale;
 };

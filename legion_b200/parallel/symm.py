@@ -136,6 +136,46 @@ class SymmComm:
         self._advance()
         return normed, summed
 
+    # ------------------------------------------------------------------ all-gather -> GEMM in one kernel
+    def shard_rows(self, T: int):
+        """(first row, row count, rows per rank) of this rank's block of a [T, hidden] activation."""
+        per = (T + self.world - 1) // self.world
+        row0 = min(T, self.rank * per)
+        return row0, max(0, min(T, row0 + per) - row0), per
+
+    def shard_view(self, T: int) -> torch.Tensor:
+        """Where this rank writes its block of rows (inside its symmetric buffer) before ``all_gather_linear``."""
+        row0, n, _ = self.shard_rows(T)
+        off = self.N_SLOTS * self.slot_bytes + row0 * self.hidden * 2
+        return self.buf[off:off + n * self.hidden * 2].view(torch.bfloat16).view(n, self.hidden)
+
+    def all_gather_linear(self, T: int, w: torch.Tensor, residual=None, out_dtype=torch.bfloat16):
+        """out[T, N] = gather_ranks(x)[T, hidden] @ w[N, hidden]^T (+ residual) in ONE launch: the GEMM kernel's head
+        exchanges flags with the peers, copies every rank's row block over NVLink peer loads into its local
+        operand tensor, and then runs the tcgen05 main loop over it. Each rank must have written its block into
+        ``shard_view(T)``. Returns (out, gathered activations)."""
+        if self._failed:
+            raise CommError(self._failed)
+        if T > self.max_rows or w.shape[1] != self.hidden:
+            raise CommError("all_gather_linear outside the communicator's shape")
+        from ..ops import sm100
+        C = ext()
+        N = w.shape[0]
+        ws = sm100.Workspace.get(self.device)
+        x_full = ws.buf("ag_x", (self.max_rows, self.hidden), torch.bfloat16)[:T]
+        out = torch.empty(T, N, dtype=out_dtype, device=self.device)
+        bn = sm100.pick_bn(T, False)
+        n_tt, ft = (T + bn - 1) // bn, (N + 127) // 128
+        sk = sm100._pick_split_k(n_tt, ft, self.hidden)
+        if sk > 1 and (C.wgemm_workspace_floats(bn, False, n_tt, ft, sk) > ws.splitk.numel()
+                       or n_tt * ft > ws.counters.numel()):
+            sk = 1
+        _, _, per = self.shard_rows(T)
+        C.wgemm_allgather(w, x_full, out, residual, bn, sk, ws.splitk if sk > 1 else None,
+                          ws.counters if sk > 1 else None, ws.status, self.buffer_ptrs, self.signal_ptrs, self.rank,
+                          self.N_SLOTS * self.slot_bytes, 0, self.seq, self.gemm_ctrs, per, self.budget_ns, self.status)
+        return out, x_full
+
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         T, H = x.shape
         if not self.owns(x):

@@ -63,6 +63,17 @@ def case_comm(dev):
     errs.append(float((summed.float() - want).abs().max()))
     comm.end_step()
     comm.check()
+    # all-gather -> GEMM in one kernel: every rank contributes its block of rows
+    for T in (16, 300):
+        xs = (torch.randn(T, H, device=dev) * 0.3).bfloat16()          # same on every rank
+        wq = (torch.randn(384, H, device=dev) * 0.05).bfloat16()
+        row0, n, _ = comm.shard_rows(T)
+        comm.shard_view(T).copy_(xs[row0:row0 + n])
+        out, gathered = comm.all_gather_linear(T, wq)
+        comm.check()
+        assert torch.equal(gathered, xs)
+        errs.append(float((out.float() - ref.linear(xs, wq).float()).abs().max()))
+        say("all-gather GEMM rows", T, "ok")
     assert sm100.Workspace.get(dev).check() == 0
     return {"errs": errs}
 
