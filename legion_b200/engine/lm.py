@@ -55,6 +55,7 @@ class EngineConfig:
     scheduling_policy: str = "fcfs"
     fair_share: bool = False
     kv_admission: str = "reserve"               # reserve | on-demand
+    kv_swap_gib: float = 0.0                    # host tier for preempted sequences (0 = recompute instead)
     spec: str = "none"                          # none | ngram | mtp | draft | eagle3 | suffix
     spec_k: int = 4
     spec_max_batch: int = 8
@@ -73,10 +74,19 @@ class EngineConfig:
     ttft_target_ms: float = 0.0
 
 
+class _Swapped:
+    """A preempted sequence's cache contents in host memory."""
+    __slots__ = ("n_tokens", "nbytes", "k", "v", "conv", "ssm")
+
+    def __init__(self, n_tokens: int, nbytes: int):
+        self.n_tokens, self.nbytes = n_tokens, nbytes
+        self.k, self.v, self.conv, self.ssm = {}, {}, {}, {}
+
+
 class Seq:
     __slots__ = ("req", "stream", "tokens", "n_prompt", "n_computed", "table", "slot", "sampler", "detok", "stop",
                  "reason", "tools", "phase", "arrival_ms", "admit_ms", "first_ms", "usage", "radix_handle", "drafts",
-                 "save_points", "finished", "priority", "key", "n_out", "held_logprobs", "constraint", "resumed",
+                 "save_points", "finished", "priority", "key", "n_out", "held_logprobs", "constraint", "resumed", "swapped",
                  "orig_prompt", "last_hidden", "draft_state")
 
     def __init__(self, req: GenerateRequest, stream: TokenStream, tokens: List[int]):
@@ -85,6 +95,7 @@ class Seq:
         self.n_prompt = len(tokens)
         self.orig_prompt = len(tokens)
         self.n_computed = 0
+        self.swapped = None               # _Swapped: KV blocks + recurrent state parked in host memory
         self.table = BlockTable()
         self.slot = -1
         self.phase = "wait"
@@ -134,6 +145,7 @@ class LmEngine(Engine):
                        if self.hybrid else None)
         self._free_slots = list(range(c.max_seqs - 1, -1, -1))
         self._slo = {"decode_ms": 0.0, "ms_per_prompt_token": 0.0}
+        self._swap_bytes = 0
         self.radix = RadixCache(self.pool) if c.prefix_cache else None
         self.saved = SavedStates(range(c.max_seqs, c.max_seqs + n_saved), c.block_size) if n_saved else None
         self.waiting = WaitQueue(c.scheduling_policy, c.fair_share, c.max_waiting)
@@ -386,14 +398,14 @@ class LmEngine(Engine):
         blocks: List[int] = []
         matched = 0
         handle = None
-        if self.radix is not None and limit >= bs:
+        if self.radix is not None and limit >= bs and seq.swapped is None:
             blocks, matched, handle = self.radix.match_prefix(prompt, lock=True, max_tokens=limit)
         resume = matched
         saved = None
         tail_block = None
         if self.hybrid:
             resume = 0
-            if self.saved is not None:
+            if self.saved is not None and seq.swapped is None:
                 cand = self.saved.find(prompt, limit)
                 if cand is not None:
                     full = (cand.n_tokens // bs) * bs
@@ -434,6 +446,9 @@ class LmEngine(Engine):
                     self.saved.drop(saved)
             else:
                 self.states.clear(seq.slot)
+        if seq.swapped is not None:
+            resume = self._swap_in(seq)          # KV blocks and recurrent state come back from the host tier
+            seq.table.n_tokens = resume
         seq.n_computed = resume
         seq.resumed = resume
         seq.usage.cached_tokens = resume
@@ -463,6 +478,7 @@ class LmEngine(Engine):
         if not cands:
             return False
         victim = min(cands, key=lambda s: (s.priority, s.n_computed, -s.arrival_ms))
+        self._swap_out(victim)
         self._release(victim)
         self.running.remove(victim)
         victim.n_prompt = len(victim.tokens)
@@ -472,6 +488,58 @@ class LmEngine(Engine):
         self.waiting.requeue(victim, victim.priority, victim.key)
         self._stats.kv_preemptions += 1
         return True
+
+    # ------------------------------------------------------------------ host tier for preempted sequences
+    def _swap_out(self, s: Seq):
+        """Parks the computed KV blocks (and the recurrent state) of a sequence about to be preempted in pinned
+        host memory when the ``kv_swap_gib`` budget allows, so that re-admission copies them back instead of
+        recomputing the prefix (the reference's ``KvTier``, ``src/model/core/kv_pool.rs``)."""
+        c = self.cfg
+        n = min(s.n_computed, len(s.tokens) - 1)
+        if c.kv_swap_gib <= 0 or n < c.block_size or self.drafter is not None:
+            return
+        nb = self.pool.blocks_for(n)
+        nbytes = nb * self.kv.bytes_per_block() + (self.states.bytes_per_slot() if self.states is not None else 0)
+        if self._swap_bytes + nbytes > c.kv_swap_gib * (1 << 30):
+            return
+        idx = torch.tensor(s.table.blocks[:nb], dtype=torch.long, device=self.device)
+        pin = self.device.type == "cuda"
+
+        def park(t):
+            h = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=pin)
+            h.copy_(t, non_blocking=pin)
+            return h
+        sw = _Swapped(n, nbytes)
+        for il, k in self.kv.k.items():
+            sw.k[il] = park(k.index_select(0, idx))
+            if self.kv.v[il] is not k:
+                sw.v[il] = park(self.kv.v[il].index_select(0, idx))
+        if self.states is not None and s.slot >= 0:
+            sw.conv = {il: park(t[s.slot]) for il, t in self.states.conv.items()}
+            sw.ssm = {il: park(t[s.slot]) for il, t in self.states.ssm.items()}
+        if pin:
+            torch.cuda.current_stream(self.device).synchronize()
+        s.swapped = sw
+        self._swap_bytes += nbytes
+        self._stats.kv_swap_out += 1
+
+    def _swap_in(self, s: Seq):
+        """Copies a parked sequence back into its freshly reserved blocks / state slot. Returns the resumed length."""
+        sw, s.swapped = s.swapped, None
+        self._swap_bytes -= sw.nbytes
+        nb = self.pool.blocks_for(sw.n_tokens)
+        idx = torch.tensor(s.table.blocks[:nb], dtype=torch.long, device=self.device)
+        for il, k in self.kv.k.items():
+            k.index_copy_(0, idx, sw.k[il].to(self.device, non_blocking=True))
+            if il in sw.v:
+                self.kv.v[il].index_copy_(0, idx, sw.v[il].to(self.device, non_blocking=True))
+        if self.states is not None:
+            for il, t in sw.conv.items():
+                self.states.conv[il][s.slot].copy_(t, non_blocking=True)
+            for il, t in sw.ssm.items():
+                self.states.ssm[il][s.slot].copy_(t, non_blocking=True)
+        self._stats.kv_swap_in += 1
+        return sw.n_tokens
 
     def _grow(self, seq: Seq, n_tokens: int) -> bool:
         while True:

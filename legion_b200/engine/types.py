@@ -255,6 +255,8 @@ class EngineStats:
     kv_blocks_used: int = 0
     kv_blocks_total: int = 0
     kv_preemptions: int = 0
+    kv_swap_out: int = 0               # preempted sequences whose KV / state went to the host tier
+    kv_swap_in: int = 0                # ... and came back instead of being recomputed
     prefix_cache_hit_tokens: int = 0
     prefix_cache_lookup_tokens: int = 0
     prompt_tokens: int = 0

@@ -131,6 +131,21 @@ def test_on_demand_admission_preempts_and_recomputes(golden):
     assert st.kv_preemptions >= 1
 
 
+@pytest.mark.parametrize("name", ["gqa_moe", "hybrid"])
+def test_preempted_sequences_swap_to_host_and_back(golden, name):
+    """With a host tier the preempted sequence's KV blocks (and recurrent state) are parked and copied back:
+    same tokens as an undisturbed run, and nothing is recomputed."""
+    eng = engine(name, prefix_cache=False, kv_admission="on-demand", kv_cache_tokens=15 * 16, kv_swap_gib=1.0)
+    streams = [eng.generate(GenerateRequest(prompt_tokens=prompt(100, s), sampling=SamplingParams(max_tokens=24, ignore_eos=True)))
+               for s in (1, 2, 3)]
+    got = [s.collect().token_ids for s in streams]
+    st = eng.stats()
+    eng.shutdown()
+    assert got == golden[name]
+    assert st.kv_preemptions >= 1 and st.kv_swap_out >= 1 and st.kv_swap_in == st.kv_swap_out
+    assert eng._swap_bytes == 0
+
+
 def test_reserve_admission_queues_until_space(golden):
     eng = engine("gqa_moe", prefix_cache=False, kv_cache_tokens=10 * 16)    # one request at a time fits
     streams = [eng.generate(GenerateRequest(prompt_tokens=prompt(100, s), sampling=SamplingParams(max_tokens=24, ignore_eos=True)))
