@@ -206,6 +206,28 @@ def bench_moe_nvfp4(rows):
     print(rows[-1], flush=True)
 
 
+def bench_gdn(rows):
+    """Gated DeltaNet recurrence over a prompt (80B-A3B hybrid shape: 16 key / 32 value heads of dim 128) and over a
+    decode step of 16 sequences: tokens per second of the state update."""
+    from legion_b200.ops import sm100
+    hbm, tf, src = peaks()
+    nk, nv, dk, dv = 16, 32, 128, 128
+    C = 2 * nk * dk + nv * dv
+    for n_seq, L in (CASE["attn"] or ((1, 8192), (16, 1))):
+        T = n_seq * L
+        qkv = (torch.randn(T, C, device="cuda") * 0.3).bfloat16()
+        g = -torch.rand(T, nv, device="cuda") * 0.1
+        beta = torch.rand(T, nv, device="cuda")
+        state = torch.zeros(n_seq, nv, dk, dv, device="cuda")
+        cu = torch.arange(0, (n_seq + 1) * L, L, device="cuda", dtype=torch.int32)
+        slots = torch.arange(n_seq, device="cuda", dtype=torch.int32)
+        ms = timeit(lambda: sm100.gdn_recurrent(qkv, g, beta, state, cu, slots, nk, nv, dk, dv, False, dk ** -0.5),
+                    iters=5, flush=False)
+        rows.append(dict(kernel="gdn_recurrent", n_seq=n_seq, L=L, ms=ms, tok_s=T / ms * 1e3,
+                         state_gbs=n_seq * nv * dk * dv * 4 * 2 / ms / 1e6, peaks=src))
+        print(rows[-1], flush=True)
+
+
 def bench_gemm(rows):
     from legion_b200.ops import sm100
     hbm, tf, src = peaks()
@@ -297,7 +319,7 @@ def main(argv=None):
     if a.gemm:
         CASE["gemm"] = [tuple(int(y) for y in x.split("x")) for x in a.gemm.split(",")]
     rows = []
-    table = {"moe_nvfp4": bench_moe_nvfp4, "layer_parts": bench_layer_parts, "decode_pages": bench_decode_pages, "gemm": bench_gemm, "moe": bench_moe, "decode_attn": bench_decode_attn, "prefill_attn": bench_prefill_attn}
+    table = {"gdn": bench_gdn, "moe_nvfp4": bench_moe_nvfp4, "layer_parts": bench_layer_parts, "decode_pages": bench_decode_pages, "gemm": bench_gemm, "moe": bench_moe, "decode_attn": bench_decode_attn, "prefill_attn": bench_prefill_attn}
     for name in a.only.split(","):
         table[name](rows)
     from legion_b200.ops.sm100 import Workspace

@@ -45,6 +45,9 @@ def _add_engine_args(ap: argparse.ArgumentParser):
     g.add_argument("--deterministic", action="store_true")
     g.add_argument("--seed", type=int, default=0)
     g.add_argument("--no-cuda-graphs", action="store_true")
+    g.add_argument("--nvtx", action="store_true", help="NVTX range around every eager step")
+    g.add_argument("--op-profile", action="store_true",
+                   help="time every kernel call between CUDA events (use with --no-cuda-graphs); table at exit of run")
     g = ap.add_argument_group("speculative decoding")
     g.add_argument("--spec", choices=["none", "ngram", "suffix", "mtp", "draft", "eagle3", "dflash"], default="none")
     g.add_argument("--spec-k", type=int, default=4)
@@ -106,7 +109,7 @@ def build_engine_from_args(a, start: bool = True):
         spec_max_batch=a.spec_max_batch, deterministic=a.deterministic, device=device, seed=a.seed,
         cuda_graphs=not a.no_cuda_graphs, model_name=a.alias or os.path.basename(path.rstrip("/")),
         tool_format=a.tool_format, itl_target_ms=a.itl_target, ttft_target_ms=a.ttft_target,
-        kv_swap_gib=getattr(a, "kv_swap_gib", 0.0), spec_policy=getattr(a, "spec_policy", "fixed"), even_chunks=not getattr(a, "no_even_chunks", False))
+        nvtx=getattr(a, "nvtx", False), kv_swap_gib=getattr(a, "kv_swap_gib", 0.0), spec_policy=getattr(a, "spec_policy", "fixed"), even_chunks=not getattr(a, "no_even_chunks", False))
     pctx = None
     if world > 1 and getattr(a, "pp", 1) > 1:
         # pipeline stages: every rank loads only its layers, the residual travels by send / recv
@@ -197,6 +200,9 @@ def cmd_serve(a):
 
 def cmd_run(a):
     from ..engine.types import ChatMessage, GenerateRequest, SamplingParams
+    if getattr(a, "op_profile", False):
+        from ..ops import sm100
+        sm100.op_profile(True)
     eng = build_engine_from_args(a)
     sp = SamplingParams(temperature=a.temp if a.temp is not None else 0.0, top_p=a.top_p or 1.0, top_k=a.top_k or 0,
                         min_p=a.min_p or 0.0, max_tokens=a.n_predict, ignore_eos=a.ignore_eos, seed=a.seed)
@@ -218,6 +224,11 @@ def cmd_run(a):
             print(f"\nerror: {ev.error}", file=sys.stderr)
             return 1
     dt = time.time() - t0
+    if getattr(a, "op_profile", False):
+        from ..ops import sm100
+        print("\n\nop                        calls   total ms   mean us   share")
+        for name, calls, ms, us, share in sm100.op_profile_report():
+            print(f"{name:24s} {calls:6d} {ms:10.3f} {us:9.1f} {share * 100:6.1f}%")
     if usage:
         print(f"\n\n[{usage.prompt_tokens} prompt tokens ({usage.cached_tokens} cached), {usage.completion_tokens} generated, "
               f"prefill {usage.prefill_ms:.0f} ms, decode {usage.decode_ms:.0f} ms, {n / max(dt, 1e-9):.1f} tok/s]",
@@ -332,6 +343,33 @@ def cmd_info(a):
     return 0
 
 
+def cmd_determinism(a):
+    """Runs the same prompts on two freshly built engines (and twice on each: cold, then through the prefix cache)
+    and compares the generated token ids byte for byte (the reference's ``scripts/determinism.py``)."""
+    import torch
+
+    from ..engine.types import GenerateRequest, SamplingParams
+    prompts = []
+    g = torch.Generator().manual_seed(a.seed)
+    for i in range(a.prompts):
+        n = int(torch.randint(a.prompt_len // 2, a.prompt_len + 1, (1,), generator=g))
+        prompts.append(torch.randint(1, 255, (n,), generator=g).tolist())
+    runs = []
+    for r in range(2):
+        eng = build_engine_from_args(a)
+        for rep_ in range(2):
+            streams = [eng.generate(GenerateRequest(prompt_tokens=p, sampling=SamplingParams(
+                temperature=0.0, max_tokens=a.n_predict, ignore_eos=True))) for p in prompts]
+            runs.append([s.collect().token_ids for s in streams])
+        eng.shutdown()
+    ok = all(r == runs[0] for r in runs[1:])
+    for i, r in enumerate(runs[1:], 1):
+        diff = sum(1 for x, y in zip(r, runs[0]) if x != y)
+        print(f"run {i} vs run 0: {'identical' if diff == 0 else f'{diff} of {len(r)} sequences differ'}")
+    print("deterministic" if ok else "NOT deterministic")
+    return 0 if ok else 1
+
+
 def cmd_tokenize(a):
     from ..loaders.model import load_model
     _, _, tok, _ = load_model(a.model, "cpu") if not a.model.startswith("random:") else (None, None, __import__(
@@ -430,6 +468,12 @@ def make_parser() -> argparse.ArgumentParser:
     s.set_defaults(fn=cmd_st)
     s = sub.add_parser("info", help="hardware report: GPUs, NVLink, measured rooflines")
     s.set_defaults(fn=cmd_info)
+    s = sub.add_parser("determinism", help="byte-compare the tokens of repeated runs (fresh engines, prefix-cache reuse)")
+    _add_engine_args(s)
+    s.add_argument("--prompts", type=int, default=4)
+    s.add_argument("--prompt-len", type=int, default=96)
+    s.add_argument("--n-predict", "-n", type=int, default=16)
+    s.set_defaults(fn=cmd_determinism)
     s = sub.add_parser("tokenize", help="tokenise text with a model's tokenizer")
     s.add_argument("--model", "-m", required=True)
     s.add_argument("text")

@@ -55,6 +55,7 @@ class EngineConfig:
     scheduling_policy: str = "fcfs"
     fair_share: bool = False
     kv_admission: str = "reserve"               # reserve | on-demand
+    nvtx: bool = False                          # NVTX range around every eager step (for external profilers)
     kv_swap_gib: float = 0.0                    # host tier for preempted sequences (0 = recompute instead)
     spec: str = "none"                          # none | ngram | mtp | draft | eagle3 | suffix
     spec_k: int = 4
@@ -654,6 +655,7 @@ class LmEngine(Engine):
         rows = [r for r in rows if r[0] in self.running]
         if not rows:
             return
+        self._stats.host_ms["plan"] += (time.perf_counter() - t0) * 1e3
         verify_rows = [r for r in rows if r[0].phase == "decode" and r[2] > 1]
         if self.hybrid and verify_rows:
             # speculative rows must not advance recurrent state: they run as their own pass with replay
@@ -738,20 +740,35 @@ class LmEngine(Engine):
     def _forward_and_finish(self, rows, verify: bool):
         all_decode_1 = all(s.phase == "decode" and n == 1 for s, _, n in rows)
         need_hidden = self.drafter is not None and getattr(self.drafter, "needs_hidden", False)
+        hm = self._stats.host_ms
+        t0 = time.perf_counter()
         if self._graphs is not None and all_decode_1 and not need_hidden:
             picked, logits = self._graphs.run(rows)
             if picked is not None:
+                t1 = time.perf_counter()
+                hm["forward"] += (t1 - t0) * 1e3
                 self._finish_rows(rows, None, logits, None, verify, picked=picked)
+                hm["finish"] += (time.perf_counter() - t1) * 1e3
                 return
+        nvtx = self.cfg.nvtx and self.device.type == "cuda"
+        if nvtx:
+            torch.cuda.nvtx.range_push(f"step {len(rows)} seqs {sum(r[2] for r in rows)} tokens")
         b = self.build_batch(rows, write_state=not verify)
         if verify and self.hybrid:
             b.replay = {}
         if need_hidden:
             b.capture_layers = getattr(self.drafter, "capture_layers", None)
+        t1 = time.perf_counter()
         out = self.model.forward(b, self.kv, self.states)
         if self.step_hook is not None:
             self.step_hook([(s.req.request_id, p0, n, s.phase) for s, p0, n in rows])
+        t2 = time.perf_counter()
         self._finish_rows(rows, b, out.logits, out, verify)
+        if nvtx:
+            torch.cuda.nvtx.range_pop()
+        hm["build"] += (t1 - t0) * 1e3
+        hm["forward"] += (t2 - t1) * 1e3
+        hm["finish"] += (time.perf_counter() - t2) * 1e3
 
     # ------------------------------------------------------------------ sampling / verification
     def _pick(self, s: Seq, logits_row: torch.Tensor, device_pick: Optional[int] = None) -> Tuple[int, Optional[TokenLogprob]]:

@@ -268,8 +268,10 @@ class EngineStats:
     spec_mean_k: float = 0.0
     model_bytes_step: int = 0
     step_ms_ewma: float = 0.0
+    # host time per step by phase, accumulated ms (plan = drafts + row planning, build = batch tensors + H2D,
+    # forward = launches (+ wait for logits), finish = sampling / verification / text / stream events)
+    host_ms: dict = field(default_factory=lambda: {"plan": 0.0, "build": 0.0, "forward": 0.0, "finish": 0.0})
     warming: bool = False
-    host_ms: Dict[str, float] = field(default_factory=dict)
 
     @property
     def spec_acceptance_rate(self) -> float:

@@ -25,7 +25,10 @@ LAUNCHES = {"n": 0}
 
 
 class _Counting:
-    """Proxy of the extension module that counts kernel launches (``LAUNCHES['n']``)."""
+    """Proxy of the extension module that counts kernel launches (``LAUNCHES['n']``) and, with ``LB_OP_PROFILE=1``
+    (or ``op_profile(True)``), times every op between two CUDA events: the per-op table of the reference's
+    ``LEGION_OP_PROFILE`` (``src/ggml/op_profile.rs:1-16``). Profiling is for eager steps (run with
+    ``--no-cuda-graphs``); captured graphs replay without passing through here."""
 
     def __init__(self, mod):
         self._mod = mod
@@ -37,11 +40,40 @@ class _Counting:
             raw = getattr(self._mod, name)
             k = KERNELS_PER_CALL.get(name, 1)
 
-            def f(*a, _raw=raw, _k=k, **kw):
+            def f(*a, _raw=raw, _k=k, _name=name, **kw):
                 LAUNCHES["n"] += _k
-                return _raw(*a, **kw)
+                if not OP_PROFILE["on"] or _k == 0 or torch.cuda.is_current_stream_capturing():
+                    return _raw(*a, **kw)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                out = _raw(*a, **kw)
+                e1.record()
+                OP_PROFILE["events"].append((_name, e0, e1))
+                return out
             self._cache[name] = f
         return f
+
+
+OP_PROFILE = {"on": os.environ.get("LB_OP_PROFILE", "0") == "1", "events": []}
+
+
+def op_profile(on: bool):
+    OP_PROFILE["on"] = bool(on)
+    OP_PROFILE["events"].clear()
+
+
+def op_profile_report(reset: bool = True):
+    """Rows (op, calls, total ms, mean us, share) of the ops timed since the last report, slowest first."""
+    torch.cuda.synchronize()
+    agg = {}
+    for name, e0, e1 in OP_PROFILE["events"]:
+        c = agg.setdefault(name, [0, 0.0])
+        c[0] += 1
+        c[1] += e0.elapsed_time(e1)
+    if reset:
+        OP_PROFILE["events"].clear()
+    total = sum(v[1] for v in agg.values()) or 1.0
+    return [(n, c, ms, ms / c * 1e3, ms / total) for n, (c, ms) in sorted(agg.items(), key=lambda kv: -kv[1][1])]
 
 
 def ext():
