@@ -44,14 +44,14 @@ void bind_gdn(pybind11::module_& m) {
   m.def("gdn_recurrent", [](const Tensor& qkv, const Tensor& g, const Tensor& beta, Tensor& state,
                             const Tensor& cu_seq, const Tensor& slots, int64_t Hk, int64_t Hv, int64_t DK, int64_t DV,
                             bool tiled_heads, double scale, double l2_eps, Tensor& out, bool write_state,
-                            bool write_out) {
+                            bool write_out, bool prompt_rows) {
     c10::cuda::CUDAGuard guard(qkv.device());
     TORCH_CHECK(qkv.scalar_type() == at::kBFloat16 && state.scalar_type() == at::kFloat, "gdn_recurrent dtypes");
     TORCH_CHECK(lb::gdn_recurrent_launch(qkv.data_ptr(), qkv.stride(0), g.data_ptr<float>(), beta.data_ptr<float>(),
                                          state.data_ptr<float>(), cu_seq.data_ptr<int>(), slots.data_ptr<int>(),
                                          int(slots.numel()), int(Hk), int(Hv), int(DK), int(DV), tiled_heads ? 1 : 0,
                                          float(scale), float(l2_eps), out.data_ptr(), write_state ? 1 : 0,
-                                         write_out ? 1 : 0, cur_stream()) == 0,
+                                         write_out ? 1 : 0, prompt_rows ? 1 : 0, cur_stream()) == 0,
                 "gdn_recurrent: unsupported head dims");
   });
   m.def("gdn_gates", [](const Tensor& a, const Tensor& b, const Tensor& A, const Tensor& dt_bias, Tensor& g,

@@ -146,11 +146,144 @@ __global__ void __launch_bounds__(2 * DV) gdn_recurrent_kernel(
   }
 }
 
+// Prompt-sized recurrence: one state COLUMN per thread. The columns of S (fixed value index c) evolve independently
+// given k, q, beta, g, so a thread that keeps S[:, c] in registers (DK floats) needs no cross-thread reduction at
+// all: kv = S[:, c] . k, delta, rank-1 update and o = S[:, c] . q are thread-local. A CTA is two warps: warp 0 owns
+// 32 columns of one value head, warp 1 stages chunks of 8 tokens ahead (loads q, k, v, g, beta, L2-normalises q and
+// k, converts to fp32) into a double-buffered shared-memory ring, so the consumer never waits for global memory.
+// Grid = (value heads x DV / 32, sequences): 4x the CTAs of the decode kernel and no block-wide barriers per token.
+template <int DK>
+__global__ void __launch_bounds__(64) gdn_scan_cols_kernel(
+    const __nv_bfloat16* __restrict__ qkv, long ld, const float* __restrict__ g, const float* __restrict__ beta,
+    float* __restrict__ state, const int* __restrict__ cu_seq, const int* __restrict__ slots, int Hk, int Hv, int DV,
+    int tiled_heads, float scale, float l2_eps, __nv_bfloat16* __restrict__ out, int write_state, int write_out) {
+  constexpr int CH = 8;
+  constexpr int PER = DK / 32;                  // q / k elements per producer lane
+  __shared__ __align__(16) float q_s[2][CH][DK];
+  __shared__ __align__(16) float k_s[2][CH][DK];
+  __shared__ float v_s[2][CH][32];
+  __shared__ float g_s[2][CH], b_s[2][CH];
+  const int tiles = DV / 32;
+  const int h = blockIdx.x / tiles, c0 = (blockIdx.x % tiles) * 32;
+  const int seq = blockIdx.y;
+  const int kh = tiled_heads ? (h % Hk) : (h / (Hv / Hk));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t0 = cu_seq[seq], t1 = cu_seq[seq + 1];
+  const int n_chunks = (t1 - t0 + CH - 1) / CH;
+  const long q_off = long(kh) * DK, k_off = long(Hk) * DK + long(kh) * DK, v_off = 2L * Hk * DK + long(h) * DV + c0;
+  // named barriers: 1 + buf = "chunk buf filled", 3 + buf = "chunk buf consumed"
+  if (warp == 1) {
+    for (int ck = 0; ck < n_chunks; ++ck) {
+      const int buf = ck & 1;
+      if (ck >= 2) asm volatile("bar.sync %0, 64;" ::"r"(3 + buf) : "memory");
+      float qv[CH][PER], kv[CH][PER], vv[CH];
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {            // all loads of the chunk are in flight together
+        const int t = t0 + ck * CH + j;
+        const bool ok = t < t1;
+        const __nv_bfloat16* row = qkv + long(ok ? t : t0) * ld;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+          qv[j][i] = ok ? __bfloat162float(row[q_off + lane + 32 * i]) : 0.f;
+          kv[j][i] = ok ? __bfloat162float(row[k_off + lane + 32 * i]) : 0.f;
+        }
+        vv[j] = ok ? __bfloat162float(row[v_off + lane]) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        const int t = t0 + ck * CH + j;
+        float qq = 0.f, kk = 0.f;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) { qq += qv[j][i] * qv[j][i]; kk += kv[j][i] * kv[j][i]; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          qq += __shfl_xor_sync(0xffffffffu, qq, o);
+          kk += __shfl_xor_sync(0xffffffffu, kk, o);
+        }
+        const float qn = rsqrtf(qq + l2_eps) * scale, kn = rsqrtf(kk + l2_eps);
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+          q_s[buf][j][lane + 32 * i] = qv[j][i] * qn;
+          k_s[buf][j][lane + 32 * i] = kv[j][i] * kn;
+        }
+        v_s[buf][j][lane] = vv[j];
+        if (lane == 0) {
+          g_s[buf][j] = t < t1 ? __expf(g[long(t) * Hv + h]) : 1.f;
+          b_s[buf][j] = t < t1 ? beta[long(t) * Hv + h] : 0.f;
+        }
+      }
+      __threadfence_block();
+      asm volatile("bar.arrive %0, 64;" ::"r"(1 + buf) : "memory");
+    }
+  } else {
+    float S[DK];
+    const int slot = slots[seq];
+    float* sp = state + ((long(slot) * Hv + h) * DK) * DV + c0 + lane;
+#pragma unroll
+    for (int i = 0; i < DK; ++i) S[i] = sp[long(i) * DV];
+    for (int ck = 0; ck < n_chunks; ++ck) {
+      const int buf = ck & 1;
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + buf) : "memory");
+      const int nt = min(CH, t1 - t0 - ck * CH);
+      for (int j = 0; j < nt; ++j) {
+        const float gt = g_s[buf][j], bt = b_s[buf][j], vc = v_s[buf][j][lane];
+        const float4* k4 = reinterpret_cast<const float4*>(k_s[buf][j]);
+        const float4* q4 = reinterpret_cast<const float4*>(q_s[buf][j]);
+        // four independent accumulators per dot product: the FMA chains are the critical path of a single warp
+        float kv0 = 0.f, kv1 = 0.f, kv2 = 0.f, kv3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < DK / 4; ++i) {
+          const float4 kq = k4[i];
+          kv0 = fmaf(S[4 * i], kq.x, kv0);
+          kv1 = fmaf(S[4 * i + 1], kq.y, kv1);
+          kv2 = fmaf(S[4 * i + 2], kq.z, kv2);
+          kv3 = fmaf(S[4 * i + 3], kq.w, kv3);
+        }
+        const float kvd = (kv0 + kv1) + (kv2 + kv3);
+        const float delta = (vc - gt * kvd) * bt;
+        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < DK / 4; ++i) {
+          const float4 kq = k4[i];
+          const float4 qq = q4[i];
+          S[4 * i] = fmaf(gt, S[4 * i], kq.x * delta);
+          S[4 * i + 1] = fmaf(gt, S[4 * i + 1], kq.y * delta);
+          S[4 * i + 2] = fmaf(gt, S[4 * i + 2], kq.z * delta);
+          S[4 * i + 3] = fmaf(gt, S[4 * i + 3], kq.w * delta);
+          o0 = fmaf(S[4 * i], qq.x, o0);
+          o1 = fmaf(S[4 * i + 1], qq.y, o1);
+          o2 = fmaf(S[4 * i + 2], qq.z, o2);
+          o3 = fmaf(S[4 * i + 3], qq.w, o3);
+        }
+        const float o = (o0 + o1) + (o2 + o3);
+        if (write_out) out[(long(t0 + ck * CH + j) * Hv + h) * DV + c0 + lane] = __float2bfloat16(o);
+      }
+      if (ck + 2 < n_chunks) asm volatile("bar.arrive %0, 64;" ::"r"(3 + buf) : "memory");
+    }
+    if (write_state) {
+#pragma unroll
+      for (int i = 0; i < DK; ++i) sp[long(i) * DV] = S[i];
+    }
+  }
+}
+
 int gdn_recurrent_launch(const void* qkv, long ld, const float* g, const float* beta, float* state,
                          const int* cu_seq, const int* slots, int n_seqs, int Hk, int Hv, int DK, int DV,
                          int tiled_heads, float scale, float l2_eps, void* out, int write_state, int write_out,
-                         cudaStream_t s) {
+                         int prompt_rows, cudaStream_t s) {
   if (n_seqs <= 0) return 0;
+  if (prompt_rows && (DK == 128 || DK == 64) && DV % 32 == 0) {
+    dim3 grid2(Hv * (DV / 32), n_seqs);
+    if (DK == 128)
+      gdn_scan_cols_kernel<128><<<grid2, 64, 0, s>>>(static_cast<const __nv_bfloat16*>(qkv), ld, g, beta, state, cu_seq,
+                                                     slots, Hk, Hv, DV, tiled_heads, scale, l2_eps,
+                                                     static_cast<__nv_bfloat16*>(out), write_state, write_out);
+    else
+      gdn_scan_cols_kernel<64><<<grid2, 64, 0, s>>>(static_cast<const __nv_bfloat16*>(qkv), ld, g, beta, state, cu_seq,
+                                                    slots, Hk, Hv, DV, tiled_heads, scale, l2_eps,
+                                                    static_cast<__nv_bfloat16*>(out), write_state, write_out);
+    return cudaGetLastError() != cudaSuccess;
+  }
   dim3 grid(Hv, n_seqs);
 #define LB_G(K_, V_)                                                                                               \
   if (DK == K_ && DV == V_) {                                                                                      \

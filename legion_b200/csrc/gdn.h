@@ -11,7 +11,7 @@ int conv1d_silu_launch(const void* x, long ldx, const float* w, const float* bia
 int gdn_recurrent_launch(const void* qkv, long ld, const float* g, const float* beta, float* state,
                          const int* cu_seq, const int* slots, int n_seqs, int Hk, int Hv, int DK, int DV,
                          int tiled_heads, float scale, float l2_eps, void* out, int write_state, int write_out,
-                         cudaStream_t s);
+                         int prompt_rows, cudaStream_t s);
 
 int gdn_gates_launch(const void* a, long lda, const void* b, long ldb, const float* A, const float* dt_bias, int Hv,
                      long T, float* g, float* beta, cudaStream_t s);

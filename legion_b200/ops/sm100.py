@@ -646,8 +646,10 @@ def gdn_recurrent(qkv, g, beta, state, cu_seq, slots, n_k, n_v, dk, dv, tiled_he
     T = qkv.shape[0]
     if out is None:
         out = torch.empty(T, n_v, dv, dtype=torch.bfloat16, device=qkv.device)
+    # prompt chunks (many rows per sequence) run the column-per-thread kernel, decode rows the state-streaming one
+    prompt_rows = T >= 16 * max(1, slots.numel())
     C.gdn_recurrent(qkv, g, beta, state, cu_seq, slots, n_k, n_v, dk, dv, tiled_heads, scale, l2_eps, out,
-                    write_state, True)
+                    write_state, True, prompt_rows)
     return out
 
 

@@ -452,3 +452,30 @@ def test_moe_nvfp4_weights():
         out = sm().moe_experts(x, r.ids, r.wts, qgu, qd, F, routing=r)
         status_ok()
         close(out, ref.moe_experts(x, r.ids, r.wts, dgu, dd, F), 3e-2, 3e-2)
+
+
+@pytest.mark.parametrize("nk,nv,dk,dv,tiled", [(2, 4, 128, 128, False), (2, 4, 128, 128, True), (2, 2, 64, 64, False),
+                                                (1, 2, 64, 128, False)])
+def test_gdn_prompt_kernel(nk, nv, dk, dv, tiled):
+    """Prompt-sized chunks run the column-per-thread recurrence (one state column in registers per thread, token
+    chunks staged by a producer warp): same outputs and final state as the fp32 reference, ragged lengths."""
+    torch.manual_seed(dk + dv)
+    lens = [70, 33, 9]
+    cu = torch.tensor([0, 70, 103, 112], device=DEV, dtype=torch.int32)
+    slots = torch.tensor([1, 3, 0], device=DEV, dtype=torch.int32)
+    T = sum(lens)
+    C = 2 * nk * dk + nv * dv
+    x = rnd(T, C, scale=0.5)
+    g = -torch.rand(T, nv, device=DEV) * 0.2
+    beta = torch.rand(T, nv, device=DEV)
+    st = torch.randn(4, nv, dk, dv, device=DEV) * 0.1
+    st2 = st.clone()
+    o = sm().gdn_recurrent(x, g, beta, st, cu, slots, nk, nv, dk, dv, tiled, dk ** -0.5)
+    ro = ref.gdn_recurrent(x, g, beta, st2, cu, slots, nk, nv, dk, dv, tiled, dk ** -0.5)
+    close(o, ro, 3e-2, 3e-2)
+    close(st, st2, 2e-2, 2e-2)
+    # verify rows: outputs without touching the state
+    st3 = st2.clone()
+    o2 = sm().gdn_recurrent(x, g, beta, st3, cu, slots, nk, nv, dk, dv, tiled, dk ** -0.5, write_state=False)
+    assert torch.equal(st3, st2)
+    assert o2.shape == o.shape
