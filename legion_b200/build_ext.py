@@ -103,5 +103,33 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     return TARGET
 
 
+HOST_SRC = ROOT / "csrc_host"
+HOST_TARGET = ROOT / "_host.so"
+
+
+def build_host(force: bool = False) -> Path:
+    """The native host runtime ``legion_b200/_host.so`` (block pool, radix cache, step packing): plain C++17 with
+    pybind11, no CUDA and no torch, so it also loads in processes that never touch a GPU."""
+    import pybind11
+    srcs = sorted(HOST_SRC.glob("*.cpp"))
+    h = hashlib.sha256()
+    for s in srcs:
+        h.update(s.read_bytes())
+    stamp = HOST_SRC / "build" / f"host.{h.hexdigest()[:16]}.stamp"
+    if not force and HOST_TARGET.exists() and stamp.exists():
+        return HOST_TARGET
+    stamp.parent.mkdir(parents=True, exist_ok=True)
+    for old in stamp.parent.glob("host.*.stamp"):
+        old.unlink()
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-w",
+           f"-I{pybind11.get_include()}", f"-I{sysconfig.get_paths()['include']}",
+           *map(str, srcs), "-o", str(HOST_TARGET)]
+    _run(cmd)
+    stamp.write_text("ok")
+    print(f"[build_ext] linked {HOST_TARGET}", file=sys.stderr)
+    return HOST_TARGET
+
+
 if __name__ == "__main__":
     build(verbose="-v" in sys.argv, force="-f" in sys.argv)
+    build_host(force="-f" in sys.argv)

@@ -15,6 +15,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from .. import ops
+from ..kv import blocks as kv_blocks
 from ..models.decoder import StepBatch
 
 BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
@@ -22,7 +23,7 @@ BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 
 class _Entry:
     __slots__ = ("graph", "B", "W", "pack_h", "pack_d", "batch", "picks", "picks_h", "logits", "n_ints", "arange",
-                 "bt_key")
+                 "bt_key", "pack_np")
 
 
 class DecodeGraphs:
@@ -69,6 +70,7 @@ class DecodeGraphs:
         e.arange = torch.arange(B + 1, dtype=torch.int32)
         e.bt_key = [None] * B
         e.pack_h = torch.zeros(total, dtype=torch.int32).pin_memory()
+        e.pack_np = e.pack_h.numpy()          # the same pinned words, as the view the native packer writes
         e.pack_d = torch.zeros(total, dtype=torch.int32, device=dev)
 
         def view(name):
@@ -126,9 +128,16 @@ class DecodeGraphs:
             return None, None
         e = self.entries.get(B) or self._capture(B)
         eng = self.eng
+        pool = eng.pool
+        native = kv_blocks.NATIVE
+        if native is not None:
+            # the whole record is written by one call of the native host runtime
+            native.pack_decode(e.pack_np, B, e.W, pool.block_size, self.pad_slot,
+                               [s.tokens[-1] for s, _, _ in rows], [p0 for _, p0, _ in rows],
+                               [s.slot for s, _, _ in rows], [s.table.blocks for s, _, _ in rows])
+            return self._replay(e, rows, n, B)
         off, _ = self._layout(B, e.W)
         h = e.pack_h
-        pool = eng.pool
         sl = h[off["slots"][0]:off["slots"][0] + 2 * B].view(torch.int64)
         tk = h[off["token_ids"][0]:off["token_ids"][0] + B]
         ps = h[off["positions"][0]:off["positions"][0] + B]
@@ -155,6 +164,10 @@ class DecodeGraphs:
         for i in range(n, B):
             e.bt_key[i] = None
         self._fill_padding(e, n)
+        return self._replay(e, rows, n, B)
+
+    def _replay(self, e: _Entry, rows, n: int, B: int):
+        eng = self.eng
         e.pack_d.copy_(e.pack_h, non_blocking=True)
         e.graph.replay()
         e.picks_h.copy_(e.picks, non_blocking=True)

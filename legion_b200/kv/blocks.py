@@ -15,7 +15,9 @@ class OutOfBlocks(Exception):
     pass
 
 
-class BlockPool:
+class PyBlockPool:
+    """Pure-Python pool: the fallback when the native host runtime is not built, and its executable specification."""
+
     def __init__(self, n_blocks: int, block_size: int, n_slow: int = 0):
         self.block_size = block_size
         self.n_blocks = n_blocks           # fast blocks: ids [0, n_blocks)
@@ -78,6 +80,24 @@ class BlockPool:
             self.decref(b)
 
 
+def _native():
+    """The native host runtime (``legion_b200/_host.so``, built by ``build_ext.build_host``) unless
+    ``LB_NATIVE_HOST=0``; None when it is not built."""
+    import os
+    if os.environ.get("LB_NATIVE_HOST", "1") == "0":
+        return None
+    try:
+        from .. import _host
+    except ImportError:
+        return None
+    _host.set_out_of_blocks(OutOfBlocks)
+    return _host
+
+
+NATIVE = _native()
+BlockPool = NATIVE.BlockPool if NATIVE is not None else PyBlockPool
+
+
 @dataclass
 class CopyOp:
     src: int
@@ -114,6 +134,8 @@ class BlockTable:
 
     def slots(self, pool: BlockPool, start: int, n: int) -> List[int]:
         bs = pool.block_size
+        if NATIVE is not None and n > 16:
+            return NATIVE.table_slots(self.blocks, bs, start, n).tolist()
         return [self.blocks[p // bs] * bs + p % bs for p in range(start, start + n)]
 
     def truncate(self, pool: BlockPool, n_tokens: int):

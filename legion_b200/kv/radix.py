@@ -9,7 +9,7 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional, Sequence, Tuple
 
-from .blocks import BlockPool
+from .blocks import NATIVE, BlockPool, PyBlockPool
 
 
 class _Node:
@@ -24,7 +24,9 @@ class _Node:
         self.tick = 0
 
 
-class RadixCache:
+class PyRadixCache:
+    """Pure-Python tree: the fallback when the native host runtime is not built, and its executable specification."""
+
     def __init__(self, pool: BlockPool):
         self.pool = pool
         self.bs = pool.block_size
@@ -163,3 +165,10 @@ class RadixCache:
 
     def clear(self):
         self.evict(self.n_cached_blocks + 1)
+
+
+def RadixCache(pool):
+    """The native tree over a native pool, the Python tree over a Python pool."""
+    if NATIVE is not None and isinstance(pool, NATIVE.BlockPool):
+        return NATIVE.RadixCache(pool)
+    return PyRadixCache(pool)

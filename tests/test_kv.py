@@ -3,12 +3,51 @@ import random
 
 import pytest
 
-from legion_b200.kv.blocks import BlockPool, BlockTable, OutOfBlocks
+from legion_b200.kv import blocks as kv_blocks
+from legion_b200.kv.blocks import BlockTable, OutOfBlocks, PyBlockPool
 from legion_b200.kv.radix import RadixCache
 from legion_b200.kv.saved_states import SavedStates, prefix_hash_at, prefix_hashes
 
+IMPLS = ["python"] + (["native"] if kv_blocks.NATIVE is not None else [])
 
-def test_pool_refcounts_and_lifo():
+
+@pytest.fixture(params=IMPLS)
+def BlockPool(request):
+    """Both implementations of the pool (and, through it, of the radix tree) run the same assertions."""
+    return PyBlockPool if request.param == "python" else kv_blocks.NATIVE.BlockPool
+
+
+def test_native_host_runtime_is_the_default():
+    """With the extension built, the engine's pool and prefix cache are the C++ ones."""
+    if kv_blocks.NATIVE is None:
+        pytest.skip("native host runtime not built")
+    assert kv_blocks.BlockPool is kv_blocks.NATIVE.BlockPool
+    p = kv_blocks.BlockPool(4, 4)
+    assert type(RadixCache(p)).__module__.endswith("_host")
+    t = BlockTable()
+    t.ensure(p, 16)
+    assert t.slots(p, 0, 16) == [t.blocks[i // 4] * 4 + i % 4 for i in range(16)]
+
+
+def test_native_pack_decode_record():
+    """The packed decode record: int64 KV cells, tokens, positions, cu_q, context lengths, state slots, block table;
+    padding rows write no cell, read context length 1 and use the spare state slot."""
+    if kv_blocks.NATIVE is None:
+        pytest.skip("native host runtime not built")
+    import torch
+    B, W, bs = 4, 5, 4
+    buf = torch.full((2 * B + B + B + B + 1 + B + B + B * W,), 77, dtype=torch.int32)
+    kv_blocks.NATIVE.pack_decode(buf.numpy(), B, W, bs, 9, [7, 8], [5, 2], [0, 1], [[3, 4], [6]])
+    assert buf[:2 * B].view(torch.int64).tolist() == [4 * 4 + 1, 6 * 4 + 2, -1, -1]
+    rest = buf[2 * B:].tolist()
+    assert rest[:4] == [7, 8, 0, 0] and rest[4:8] == [5, 2, 0, 0] and rest[8:13] == [0, 1, 2, 3, 4]
+    assert rest[13:17] == [6, 3, 1, 1] and rest[17:21] == [0, 1, 9, 9]
+    assert rest[21:] == [3, 4, 0, 0, 0, 6, 0, 0, 0, 0] + [0] * 10
+    with pytest.raises(IndexError):
+        kv_blocks.NATIVE.pack_decode(buf.numpy(), B, W, bs, 9, [7], [40], [0], [[3, 4]])
+
+
+def test_pool_refcounts_and_lifo(BlockPool):
     p = BlockPool(4, 16, n_slow=2)
     a = p.alloc(3)
     assert a == [0, 1, 2] and p.free == 3 and p.free_fast == 1
@@ -25,7 +64,7 @@ def test_pool_refcounts_and_lifo():
         p.decref(5)
 
 
-def test_block_table_grow_truncate_cow():
+def test_block_table_grow_truncate_cow(BlockPool):
     p = BlockPool(8, 4)
     t = BlockTable()
     t.ensure(p, 10)
@@ -42,7 +81,7 @@ def test_block_table_grow_truncate_cow():
     assert p.free == 8
 
 
-def test_radix_match_insert_split_evict():
+def test_radix_match_insert_split_evict(BlockPool):
     p = BlockPool(32, 4)
     r = RadixCache(p)
     toks = list(range(20))
@@ -68,7 +107,7 @@ def test_radix_match_insert_split_evict():
     assert r.match_prefix(toks)[1] == 0
 
 
-def test_radix_random_against_dict_model():
+def test_radix_random_against_dict_model(BlockPool):
     rng = random.Random(0)
     p = BlockPool(4096, 2)
     r = RadixCache(p)
