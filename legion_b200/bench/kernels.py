@@ -183,6 +183,32 @@ def bench_decode_pages(rows):
         print(rows[-1], flush=True)
 
 
+def bench_mla(rows):
+    """Latent attention, absorbed form: decode at 16 and 64 users x 8K context with 128 heads (graph-replayed).
+    FLOPs per key row = 2 * heads * (576 + 512); bytes per key row = 1152."""
+    from legion_b200.ops import sm100
+    hbm, tf, src = peaks()
+    nh, page = 128, 64
+    cases = ((16, 8192, 1), (64, 8192, 1), (1, 8192, 512))
+    if CASE.get("attn"):
+        cases = tuple((c[0], c[1], c[2] if len(c) > 2 else 1) for c in CASE["attn"])
+    for (B, ctx, q_len) in cases:
+        nb = B * ((ctx + page - 1) // page)
+        cache = (torch.randn(nb, page, 1, 576, device="cuda") * 0.5).bfloat16()
+        bt = torch.arange(nb, device="cuda", dtype=torch.int32).view(B, -1)
+        q = (torch.randn(B * q_len, nh, 576, device="cuda") * 0.5).bfloat16()
+        cu = torch.arange(0, (B + 1) * q_len, q_len, device="cuda", dtype=torch.int32)
+        cl = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
+        splits = sm100.mla_splits(B, q_len, nh, ctx)
+        ms = timeit_graph(lambda: sm100.mla_attn(q, cache, cu, cl, bt, page, q_len, 192 ** -0.5, n_splits=splits))
+        keys = B * (ctx * q_len - q_len * (q_len - 1) // 2)
+        flops = 2.0 * nh * (576 + 512) * keys
+        byts = B * ctx * 1152
+        rows.append(dict(kernel="mla_attn", B=B, ctx=ctx, q_len=q_len, splits=splits, us=ms * 1e3,
+                         tflops=flops / ms / 1e9, frac_tc=flops / ms / 1e9 / tf, gbs=byts / ms / 1e6, peaks=src))
+        print(rows[-1], flush=True)
+
+
 def bench_moe_nvfp4(rows):
     """Routed experts of a 30B-A3B-shaped layer at 16 tokens with the weights kept in NVFP4 (graph-replayed)."""
     from legion_b200.ops import sm100
@@ -319,7 +345,7 @@ def main(argv=None):
     if a.gemm:
         CASE["gemm"] = [tuple(int(y) for y in x.split("x")) for x in a.gemm.split(",")]
     rows = []
-    table = {"gdn": bench_gdn, "moe_nvfp4": bench_moe_nvfp4, "layer_parts": bench_layer_parts, "decode_pages": bench_decode_pages, "gemm": bench_gemm, "moe": bench_moe, "decode_attn": bench_decode_attn, "prefill_attn": bench_prefill_attn}
+    table = {"gdn": bench_gdn, "mla": bench_mla, "moe_nvfp4": bench_moe_nvfp4, "layer_parts": bench_layer_parts, "decode_pages": bench_decode_pages, "gemm": bench_gemm, "moe": bench_moe, "decode_attn": bench_decode_attn, "prefill_attn": bench_prefill_attn}
     for name in a.only.split(","):
         table[name](rows)
     from legion_b200.ops.sm100 import Workspace

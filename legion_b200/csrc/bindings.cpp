@@ -294,6 +294,52 @@ void prefill_attn(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache,
   TORCH_CHECK(rc == 0, lb::prefill_attn_last_error());
 }
 
+void mla_attn(const Tensor& q_abs, const Tensor& cache, const Tensor& cu_q, const Tensor& ctx_lens,
+              const Tensor& block_table, int64_t page, int64_t max_q_len, double scale, int64_t n_splits,
+              const OptT& o_part, const OptT& ml_part, Tensor& out, Tensor& status) {
+  check_bf16(q_abs, "q_abs");
+  check_bf16(cache, "cache");
+  TORCH_CHECK(q_abs.dim() == 3 && q_abs.size(2) == 576 && q_abs.is_contiguous(), "mla_attn: q_abs must be [T, heads, 576]");
+  TORCH_CHECK(cache.size(-1) == 576 && cache.is_contiguous(), "mla_attn: cache rows must be [.., 576]");
+  TORCH_CHECK(out.is_contiguous() && out.size(-1) == 512 && out.numel() == q_abs.size(0) * q_abs.size(1) * 512,
+              "mla_attn: out must be [T, heads, 512]");
+  const long T = q_abs.size(0);
+  const int nh = int(q_abs.size(1));
+  if (n_splits > 1) {
+    TORCH_CHECK(o_part.has_value() && ml_part.has_value() && o_part->numel() >= T * nh * n_splits * 512 &&
+                    ml_part->numel() >= T * nh * n_splits * 2, "mla_attn: partial workspaces too small");
+  }
+  c10::cuda::CUDAGuard guard(q_abs.device());
+  const int rc = lb::mla_attn_launch(q_abs.data_ptr(), T, cache.data_ptr(), cache.numel() / 576, 576,
+                                     cu_q.data_ptr<int>(), ctx_lens.data_ptr<int>(), block_table.data_ptr<int>(),
+                                     int(block_table.size(1)), int(page), int(ctx_lens.numel()), int(max_q_len), nh,
+                                     float(scale), int(n_splits), optpm<float>(o_part), optpm<float>(ml_part),
+                                     out.data_ptr(), reinterpret_cast<int*>(status.data_ptr()), cur_stream());
+  TORCH_CHECK(rc == 0, lb::mla_attn_last_error());
+}
+
+void mla_prep(const Tensor& kva, const Tensor& norm_w, double eps, double w_offset, const Tensor& q, int64_t q_pe_off,
+              const Tensor& cos_sin, const Tensor& positions, const Tensor& slots, Tensor& cache, Tensor& q_abs) {
+  check_bf16(kva, "kva");
+  check_bf16(q, "q");
+  check_bf16(cache, "cache");
+  TORCH_CHECK(kva.dim() == 2 && kva.size(1) == 576 && kva.stride(1) == 1, "mla_prep: kva must be [T, 576]");
+  TORCH_CHECK(q.dim() == 3 && q.stride(2) == 1 && q_pe_off + 64 <= q.size(2), "mla_prep: q must be [T, heads, dn + 64]");
+  TORCH_CHECK(norm_w.scalar_type() == at::kFloat && norm_w.numel() == 512, "mla_prep: norm weight float32[512]");
+  TORCH_CHECK(cos_sin.scalar_type() == at::kFloat && cos_sin.size(-1) == 64 && cos_sin.is_contiguous(),
+              "mla_prep: cos_sin must be float32 [positions, 64]");
+  TORCH_CHECK(positions.scalar_type() == at::kInt && slots.scalar_type() == at::kLong, "positions i32, slots i64");
+  TORCH_CHECK(cache.is_contiguous() && cache.size(-1) == 576, "mla_prep: cache rows must be [.., 576]");
+  TORCH_CHECK(q_abs.is_contiguous() && q_abs.size(0) == q.size(0) && q_abs.size(1) == q.size(1) && q_abs.size(2) == 576,
+              "mla_prep: q_abs must be [T, heads, 576]");
+  c10::cuda::CUDAGuard guard(kva.device());
+  TORCH_CHECK(lb::mla_prep_launch(kva.data_ptr(), kva.stride(0), norm_w.data_ptr<float>(), float(eps), float(w_offset),
+                                  q.data_ptr(), q.stride(0), int(q.stride(1)), int(q_pe_off), int(q.size(1)),
+                                  cos_sin.data_ptr<float>(), positions.data_ptr<int>(), slots.data_ptr<long>(),
+                                  cache.data_ptr(), 576, q_abs.data_ptr(), int(kva.size(0)), cur_stream()) == 0,
+              "mla_prep launch failed");
+}
+
 void router_topk(const Tensor& logits, const OptT& bias, int64_t k, int64_t mode, bool renorm, double route_scale,
                  int64_t n_group, int64_t topk_group, Tensor& ids, Tensor& wts) {
   TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.stride(1) == 1, "router logits must be float32");
@@ -442,6 +488,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embed", &embed);
   m.def("paged_decode", &paged_decode);
   m.def("prefill_attn", &prefill_attn);
+  m.def("mla_attn", &mla_attn);
+  m.def("mla_prep", &mla_prep);
   m.def("router_topk", &router_topk);
   m.def("moe_route_small", &moe_route_small);
   m.def("moe_plan", &moe_plan);

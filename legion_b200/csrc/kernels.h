@@ -41,6 +41,17 @@ int prefill_attn_launch(const void* q, long T, const void* k_cache, const void* 
                         int window, int causal, void* out, int* status, cudaStream_t s);
 const char* prefill_attn_last_error();
 
+// Latent attention (absorbed form) over the paged latent cache: attn_mla_sm100.cu
+int mla_attn_launch(const void* q_abs, long T, const void* cache, long n_cells, long cell_stride, const int* cu_q,
+                    const int* ctx_lens, const int* block_table, int table_width, int page, int n_seqs,
+                    int max_q_len, int nh, float scale, int n_splits, float* o_part, float* ml_part, void* out,
+                    int* status, cudaStream_t s);
+const char* mla_attn_last_error();
+int mla_prep_launch(const void* kva, long ld_kva, const float* norm_w, float eps, float w_offset, const void* q,
+                    long ld_q_tok, int q_head_stride, int q_pe_off, int nh, const float* cos_sin,
+                    const int* positions, const long* slots, void* cache, long cell_stride, void* q_abs, int T,
+                    cudaStream_t s);
+
 int router_topk_launch(const float* logits, long ldl, const float* bias, int E, int k, int mode, int renorm,
                        float route_scale, int n_group, int topk_group, int* ids, float* wts, int T, cudaStream_t s);
 

@@ -164,7 +164,7 @@ class LmEngine(Engine):
         self.eos_ids = tuple(self.tok.eos_ids)
         self._graphs = None
         if dev.type == "cuda" and c.cuda_graphs and not model.expert_cache and getattr(model, "pipe", None) is None \
-                and not any(k in ("mla", "mamba2") for k in self.mcfg.layer_kinds):
+                and "mamba2" not in self.mcfg.layer_kinds and self._mla_graphable(model, c):
             from .cuda_graphs import DecodeGraphs
             self._graphs = DecodeGraphs(self)
         self.step_hook: Optional[Callable] = None    # tests observe (batch description) per step
@@ -671,6 +671,14 @@ class LmEngine(Engine):
         st = self._stats
         st.steps += 1
         st.step_ms_ewma = dt if st.step_ms_ewma == 0 else 0.8 * st.step_ms_ewma + 0.2 * dt
+
+    def _mla_graphable(self, model, c) -> bool:
+        """Latent-attention layers replay in a CUDA graph only through the tensor-core kernel (the fallback form
+        reads lengths on the host)."""
+        if "mla" not in self.mcfg.layer_kinds:
+            return True
+        from ..ops import sm100
+        return sm100.mla_supported(model.n_head_l, self.mcfg.kv_lora, self.mcfg.qk_rope_dim, c.block_size)
 
     def build_batch(self, rows: Sequence[Tuple[Seq, int, int]], write_state: bool = True) -> StepBatch:
         dev = self.device

@@ -29,7 +29,7 @@ import torch.nn.functional as F
 
 from .. import ops
 from ..config import ModelConfig
-from ..parallel.context import ParallelCtx
+from ..parallel.context import ParallelCtx, PendingLinear
 
 
 @dataclass
@@ -207,7 +207,7 @@ class Decoder:
                                 window=window, decode_splits=b.decode_splits, max_ctx=b.max_ctx or None)
         if cfg.gated_attn:
             o = ops.apply_output_gate(o, gate, self.n_head_l, D)
-        return self.pctx.defer_linear(o.reshape(o.shape[0], -1), w[f"{p}.attn.o"])
+        return self.pctx.defer_linear(o.reshape(o.shape[0], -1), w[f"{p}.attn.o"], lazy=True)
 
     def _gdn(self, p: str, il: int, x, b: StepBatch, st: StatePool):
         cfg, w = self.cfg, self.w
@@ -223,7 +223,7 @@ class Decoder:
         o = ops.gdn_recurrent(conv, g, beta, st.ssm[il], b.cu_q, b.state_slots, nk, nv, dk, dv, cfg.gdn_tiled_heads,
                               dk ** -0.5, 1e-6, write_state=b.write_state)
         n = ops.gated_rmsnorm(o, z, w[f"{p}.gdn.norm"], cfg.rms_eps, cfg.gdn_gate_act)
-        return self.pctx.defer_linear(n.reshape(n.shape[0], -1), w[f"{p}.gdn.out"])
+        return self.pctx.defer_linear(n.reshape(n.shape[0], -1), w[f"{p}.gdn.out"], lazy=True)
 
     def _mla(self, p: str, il: int, x, b: StepBatch, kv: KvCache):
         """Latent attention: cache row = [rmsnorm(c_kv) | rope(k_pe)]; keys/values are expanded from
@@ -239,14 +239,24 @@ class Decoder:
             q = ops.linear(x, w[f"{p}.mla.q"])
         q = q.view(T, nh, dn + dr)
         kva = ops.linear(x, w[f"{p}.mla.kv_a"])
+        wkv_b = w[f"{p}.mla.kv_b"].view(nh, dn + dvh, L)
+        scale = cfg.attn_scale or (dn + dr) ** -0.5
+        if x.is_cuda and x.dtype == torch.bfloat16 and ops.sm100.mla_supported(nh, L, dr, kv.page):
+            # absorbed form on the tensor cores: q_abs = [q_nope W_uk | rope(q_pe)], o = (softmax . c_kv) W_uv
+            q_abs = torch.empty(T, nh, L + dr, dtype=x.dtype, device=x.device)
+            q_abs[..., :L] = torch.bmm(q[..., :dn].transpose(0, 1), wkv_b[:, :dn]).transpose(0, 1)
+            ops.sm100.mla_prep(kva, w[f"{p}.mla.kv_a_norm"], cfg.rms_eps, cfg.norm_offset, q, dn, self.cos_sin,
+                               b.positions, b.slots, kv.k[il], q_abs)
+            o_lat = ops.sm100.mla_attn(q_abs, kv.k[il], b.cu_q, b.ctx_lens, b.block_table, kv.page, b.max_q_len,
+                                       scale, max_ctx=b.max_ctx or None)
+            out = torch.bmm(o_lat.transpose(0, 1), wkv_b[:, dn:].transpose(1, 2)).transpose(0, 1)
+            return ops.linear(out.reshape(T, nh * dvh), w[f"{p}.mla.o"])
         ckv, _ = ops.rmsnorm(kva[:, :L].contiguous(), w[f"{p}.mla.kv_a_norm"], cfg.rms_eps, cfg.norm_offset)
         k_pe = ops.reference.apply_rope(kva[:, L:].reshape(T, 1, dr), self.cos_sin, b.positions, dr)
         q_pe = ops.reference.apply_rope(q[..., dn:], self.cos_sin, b.positions, dr)
         row = torch.cat([ckv, k_pe.reshape(T, dr)], dim=-1).to(kv.k[il].dtype)
         valid = b.slots >= 0
         kv.k[il].view(-1, L + dr)[b.slots[valid]] = row[valid]
-        wkv_b = w[f"{p}.mla.kv_b"].view(nh, dn + dvh, L)
-        scale = cfg.attn_scale or (dn + dr) ** -0.5
         out = torch.empty(T, nh, dvh, device=x.device, dtype=x.dtype)
         cu = b.cu_q_host if b.cu_q_host is not None else b.cu_q.tolist()
         ctxs = b.ctx_lens.tolist()
@@ -304,16 +314,22 @@ class Decoder:
         yn = yz * torch.rsqrt(yz.pow(2).mean(-1, keepdim=True) + cfg.rms_eps) * w[f"{p}.ssm.norm"].float()
         return ops.linear(yn.to(x.dtype), w[f"{p}.ssm.out"])
 
-    def _ffn(self, p: str, il_moe: bool, x, residual, next_norm=None):
+    def _route(self, p: str, x, norm=None):
+        cfg, w, pc = self.cfg, self.w, self.pctx
+        e_lo, e_hi = pc.expert_range(cfg.n_expert)
+        return ops.router(x, w[f"{p}.moe.router"], cfg.top_k, cfg.router_mode, cfg.norm_topk,
+                          cfg.route_scale, w.get(f"{p}.moe.router_bias"), cfg.n_group, cfg.topk_group,
+                          e_lo=e_lo, n_local=e_hi - e_lo, norm=norm)
+
+    def _ffn(self, p: str, il_moe: bool, x, residual, next_norm=None, routing=None):
         """Returns (out, fused, normed). ``fused``: the residual is already added (TP == 1). ``normed``: the
-        next layer's input norm of ``out`` when ``next_norm`` was given and the MoE combine could carry it."""
+        next layer's input norm of ``out`` when ``next_norm`` was given and the MoE combine could carry it.
+        ``routing``: the router's result when the caller already ran it (with the FFN norm inside)."""
         cfg, w, pc = self.cfg, self.w, self.pctx
         fuse_res = residual is not None and pc.tp == 1
         if il_moe:
-            e_lo, e_hi = pc.expert_range(cfg.n_expert)
-            routing = ops.router(x, w[f"{p}.moe.router"], cfg.top_k, cfg.router_mode, cfg.norm_topk,
-                                 cfg.route_scale, w.get(f"{p}.moe.router_bias"), cfg.n_group, cfg.topk_group,
-                                 e_lo=e_lo, n_local=e_hi - e_lo)
+            if routing is None:
+                routing = self._route(p, x)
             ids, wts = routing
             shared = gate = None
             if cfg.shared_ff > 0:
@@ -364,8 +380,15 @@ class Decoder:
             a = self._mamba2(p, il, h, b, st)
         else:
             raise ValueError(kind)
-        h, resid = pc.reduce_norm(a, resid, w[f"{p}.ffn_norm"], cfg.rms_eps, cfg.norm_offset)
-        f, fused, normed = self._ffn(p, moe, h, resid, next_norm)
+        routing = None
+        if moe and pc.world == 1 and isinstance(a, PendingLinear) and resid is not None and ops.sm100.TUNE["route_norm"]:
+            # single rank: the projection's epilogue adds the residual and the routing launch applies the FFN norm
+            resid = ops.linear(a.x, a.w, residual=resid)
+            routing = self._route(p, resid, norm=(w[f"{p}.ffn_norm"], cfg.rms_eps, cfg.norm_offset))
+            h = routing.x_normed
+        else:
+            h, resid = pc.reduce_norm(a, resid, w[f"{p}.ffn_norm"], cfg.rms_eps, cfg.norm_offset)
+        f, fused, normed = self._ffn(p, moe, h, resid, next_norm, routing)
         if fused:
             return None, f, normed  # residual already folded in: f is the new residual stream
         return f, resid, None

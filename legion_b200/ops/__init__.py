@@ -83,14 +83,20 @@ def router_topk(logits, k, mode="softmax", renorm=True, route_scale=1.0, bias=No
 
 
 def router(x, w_router, k, mode="softmax", renorm=True, route_scale=1.0, bias=None, n_group=1, topk_group=1,
-           e_lo=0, n_local=None):
+           e_lo=0, n_local=None, norm=None):
     """Router projection + top-k. Returns an object that unpacks as ``ids, wts`` ([T, k] int32 / float32); on the
     GPU it may also carry the dense routing tables of a decode-sized step for the experts
-    [e_lo, e_lo + n_local) of this rank (pass it on as ``routing=``)."""
+    [e_lo, e_lo + n_local) of this rank (pass it on as ``routing=``). With ``norm=(weight, eps, w_offset)`` ``x`` is
+    the raw residual stream: the RMSNorm runs first (inside the routing launch for decode-sized steps on the GPU)
+    and the result's ``x_normed`` is the normalised input for the experts."""
     if _cuda(x):
-        return _sm.router(x, w_router, k, mode, renorm, route_scale, bias, n_group, topk_group, None, e_lo, n_local)
-    logits = _ref.linear(x, w_router, out_dtype=torch.float32)
-    return _ref.router_topk(logits, k, mode, renorm, route_scale, bias, n_group, topk_group)
+        return _sm.router(x, w_router, k, mode, renorm, route_scale, bias, n_group, topk_group, norm, e_lo, n_local)
+    xn = None
+    if norm is not None:
+        xn, _ = _ref.rmsnorm(x, norm[0], norm[1], norm[2])
+    logits = _ref.linear(x if xn is None else xn, w_router, out_dtype=torch.float32)
+    ids, wts = _ref.router_topk(logits, k, mode, renorm, route_scale, bias, n_group, topk_group)
+    return _sm.Routing(ids, wts, None, xn)
 
 
 def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, act="silu", e_lo=0, shared=None, shared_gate=None,

@@ -106,7 +106,7 @@ def have_ext() -> bool:
 NUM_SMS = 148
 
 # tuning knobs (environment: LB_TUNE="decode_fixed_tiles=2,dense_route=1")
-TUNE = {"decode_fixed_tiles": 2, "fused_plan": 1, "fused_router": 1, "dense_route": 1, "pdl": 1}
+TUNE = {"decode_fixed_tiles": 2, "fused_plan": 1, "fused_router": 1, "dense_route": 1, "pdl": 1, "route_norm": 0}
 for _kv in os.environ.get("LB_TUNE", "").split(","):
     if "=" in _kv:
         TUNE[_kv.split("=")[0].strip()] = int(_kv.split("=")[1])
@@ -386,6 +386,45 @@ def prefill_attn(q, k_cache, v_cache, cu_q, ctx_lens, block_table, max_q_len, sc
         out = torch.empty_like(q)
     ws = Workspace.get(q.device)
     C.prefill_attn(q, k_cache, v_cache, cu_q, ctx_lens, block_table, max_q_len, scale, window, causal, out, ws.status)
+    return out
+
+
+def mla_splits(n_seqs: int, max_q_len: int, nh: int, max_ctx: int) -> int:
+    """Key splits of the latent-attention kernel: enough CTAs (64 query rows each) to cover the SMs, at least four
+    64-key tiles per split."""
+    g = min(nh, 64)
+    tiles = max(1, n_seqs * ((max_q_len + 64 // g - 1) // (64 // g)) * max(1, nh // 64))
+    by_sm = max(1, NUM_SMS // tiles)
+    by_len = max(1, (max_ctx + 255) // 256)
+    return int(max(1, min(by_sm, by_len, 32)))
+
+
+def mla_supported(nh: int, kv_lora: int, rope_dim: int, page: int) -> bool:
+    return kv_lora == 512 and rope_dim == 64 and page % 8 == 0 and 64 % page == 0 and \
+        ((nh >= 64 and nh % 64 == 0) or (0 < nh < 64 and 64 % nh == 0))
+
+
+def mla_prep(kva, norm_w, eps, w_offset, q, q_pe_off, cos_sin, positions, slots, cache, q_abs):
+    """Cache row [rmsnorm(c_kv) | rope(k_pe)] written at each token's cell and rope(q_pe) written into
+    q_abs[..., 512:] in one launch."""
+    ext().mla_prep(kva, norm_w, eps, w_offset, q, q_pe_off, cos_sin, positions, slots, cache, q_abs)
+
+
+def mla_attn(q_abs, cache, cu_q, ctx_lens, block_table, page, max_q_len, scale, n_splits=None, max_ctx=None, out=None):
+    """Latent attention, absorbed form: q_abs [T, heads, 576], cache rows [.., 576] -> [T, heads, 512]."""
+    C = ext()
+    T, nh, _ = q_abs.shape
+    if n_splits is None:
+        n_splits = mla_splits(int(ctx_lens.numel()), max_q_len, nh, max_ctx or block_table.shape[1] * page)
+    ws = Workspace.get(q_abs.device)
+    o_part = ml_part = None
+    if n_splits > 1:
+        o_part = ws.buf("mla_o", (T * nh * n_splits * 512,), torch.float32)
+        ml_part = ws.buf("mla_ml", (T * nh * n_splits * 2,), torch.float32)
+    if out is None:
+        out = torch.empty(T, nh, 512, dtype=torch.bfloat16, device=q_abs.device)
+    C.mla_attn(q_abs, cache, cu_q, ctx_lens, block_table, page, max_q_len, scale, n_splits, o_part, ml_part, out,
+               ws.status)
     return out
 
 

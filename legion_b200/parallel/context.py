@@ -78,11 +78,14 @@ class ParallelCtx:
             return self.symm.next_partial(rows, cols)
         return None
 
-    def defer_linear(self, x, w):
+    def defer_linear(self, x, w, lazy: bool = False):
         """x @ w^T whose output is rank-partial. With the fused communicator on a GPU the GEMM is deferred to the
         next ``reduce_norm`` (GEMM + all-reduce + residual + norm in one launch); otherwise it runs now, writing
-        into the symmetric slot when there is one."""
+        into the symmetric slot when there is one. ``lazy``: on a single rank the projection is also kept
+        unevaluated, so that its consumer can run it with the residual added in the GEMM epilogue."""
         rows, cols = x.shape[0], w.shape[0]
+        if lazy and self.world == 1:
+            return PendingLinear(x, w)
         if (self.world > 1 and self.comm == "fused" and self.symm is not None and x.is_cuda and self.gemm_tail
                 and self.symm.fits_gemm_tail(rows, cols)):
             return PendingLinear(x, w)
@@ -105,6 +108,10 @@ class ParallelCtx:
         if cur is None:
             normed, _ = ops.rmsnorm(res, w, eps, w_offset)
             return normed, res
+        if isinstance(cur, PendingLinear) and self.world == 1:
+            hidden = ops.linear(cur.x, cur.w, residual=res)
+            normed, _ = ops.rmsnorm(hidden, w, eps, w_offset)
+            return normed, hidden
         if isinstance(cur, PendingLinear):
             if res is not None:
                 self.stats["all_reduce"] += 1
@@ -123,6 +130,8 @@ class ParallelCtx:
         return ops.rmsnorm(cur, w, eps, w_offset, residual=res)
 
     def full_hidden(self, cur, res):
+        if isinstance(cur, PendingLinear) and self.world == 1 and res is not None:
+            return ops.linear(cur.x, cur.w, residual=res)
         cur = self._materialize(cur)
         if cur is None:
             return res

@@ -479,3 +479,75 @@ def test_gdn_prompt_kernel(nk, nv, dk, dv, tiled):
     o2 = sm().gdn_recurrent(x, g, beta, st3, cu, slots, nk, nv, dk, dv, tiled, dk ** -0.5, write_state=False)
     assert torch.equal(st3, st2)
     assert o2.shape == o.shape
+
+
+def _mla_reference(q_abs, cache, bt, ctx, cu, page, scale):
+    """fp32 latent attention from the paged rows: softmax(q_abs . row) . row[:512], causal inside the step."""
+    T, nh, _ = q_abs.shape
+    out = torch.zeros(T, nh, 512, device=q_abs.device)
+    rows = cache.reshape(-1, 576).float()
+    for i in range(len(ctx)):
+        q0, q1 = cu[i], cu[i + 1]
+        c = ctx[i]
+        nb = (c + page - 1) // page
+        idx = (bt[i, :nb].long()[:, None] * page + torch.arange(page, device=q_abs.device)[None]).reshape(-1)[:c]
+        lat = rows[idx]
+        s = torch.einsum("qhd,kd->hqk", q_abs[q0:q1].float(), lat) * scale
+        qpos = torch.arange(c - (q1 - q0), c, device=q_abs.device)[:, None]
+        kpos = torch.arange(c, device=q_abs.device)[None]
+        s = s.masked_fill((kpos > qpos)[None], float("-inf"))
+        out[q0:q1] = torch.einsum("hqk,kl->qhl", torch.softmax(s, -1), lat[:, :512])
+    return out
+
+
+@pytest.mark.parametrize("nh,page,q_lens,ctx,splits", [
+    (128, 64, [1, 1, 1], [70, 300, 1000], 1),       # decode, 2 head blocks per token
+    (128, 16, [1, 1, 1], [70, 300, 1000], 3),       # split keys + combine, small pages
+    (16, 64, [5, 1, 130], [5, 260, 200], 1),        # 4 tokens per tile: verify rows and a prompt chunk
+    (64, 32, [3, 2], [515, 64], 2),
+])
+def test_mla_attn(nh, page, q_lens, ctx, splits):
+    """tcgen05 latent attention (M = 64 tiles, S and O interleaved in TMEM) against the fp32 form."""
+    torch.manual_seed(nh + page)
+    n_blocks = 80
+    cache = (torch.randn(n_blocks, page, 1, 576, device=DEV) * 0.5).bfloat16()
+    width = (max(ctx) + page - 1) // page + 1
+    bt = torch.stack([torch.randperm(n_blocks, device=DEV)[:width] for _ in q_lens]).int()
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    T = cu[-1]
+    q_abs = (torch.randn(T, nh, 576, device=DEV) * 0.5).bfloat16()
+    scale = 192 ** -0.5
+    out = sm().mla_attn(q_abs, cache, torch.tensor(cu, device=DEV, dtype=torch.int32),
+                        torch.tensor(ctx, device=DEV, dtype=torch.int32), bt, page, max(q_lens), scale,
+                        n_splits=splits)
+    status_ok()
+    want = _mla_reference(q_abs, cache, bt, ctx, cu, page, scale)
+    close(out, want, 3e-2, 3e-2)
+
+
+def test_mla_prep():
+    """Latent row norm + key rope + cache write + query rope in one launch against the reference ops."""
+    torch.manual_seed(3)
+    T, nh, dn = 7, 16, 32
+    kva = rnd(T, 576)
+    q = rnd(T, nh, dn + 64)
+    nw = torch.rand(512, device=DEV) + 0.5
+    cos_sin = ref.rope_cos_sin(256, 64, 10000.0, None, device=DEV)
+    pos = torch.tensor([0, 5, 9, 100, 101, 255, 3], device=DEV, dtype=torch.int32)
+    slots = torch.tensor([4, 130, -1, 17, 18, 0, 77], device=DEV, dtype=torch.int64)
+    cache = torch.zeros(4, 64, 1, 576, device=DEV, dtype=torch.bfloat16)
+    q_abs = torch.zeros(T, nh, 576, device=DEV, dtype=torch.bfloat16)
+    sm().mla_prep(kva, nw, 1e-6, 0.0, q, dn, cos_sin, pos, slots, cache, q_abs)
+    ckv, _ = ref.rmsnorm(kva[:, :512].contiguous(), nw, 1e-6, 0.0)
+    kpe = ref.apply_rope(kva[:, 512:].reshape(T, 1, 64), cos_sin, pos, 64).reshape(T, 64)
+    qpe = ref.apply_rope(q[..., dn:], cos_sin, pos, 64)
+    rows = cache.view(-1, 576)
+    for t in range(T):
+        if slots[t] >= 0:
+            close(rows[slots[t], :512], ckv[t], 2e-2, 2e-2)
+            close(rows[slots[t], 512:], kpe[t], 2e-2, 2e-2)
+    assert rows[2].abs().sum() == 0                       # the padding row wrote nothing
+    close(q_abs[..., 512:], qpe, 2e-2, 2e-2)
+    assert q_abs[..., :512].abs().sum() == 0
