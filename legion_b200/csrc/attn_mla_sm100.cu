@@ -81,11 +81,11 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;    // [2]
   uint64_t* kv_empty = bars + 3;   // [2]
-  uint64_t* s_full = bars + 5;
-  uint64_t* s_free = bars + 6;
-  uint64_t* p_ready = bars + 7;
-  uint64_t* o_done = bars + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* s_full = bars + 5;     // [2] S buffers
+  uint64_t* s_free = bars + 7;     // [2]
+  uint64_t* p_ready = bars + 9;
+  uint64_t* o_done = bars + 10;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int seq = blockIdx.y;
@@ -103,8 +103,7 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
-    mbar_init(s_full, 1);
-    mbar_init(s_free, 128);
+    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 128); }
     mbar_init(p_ready, 128);
     mbar_init(o_done, 1);
     *abort_flag = 0;
@@ -119,7 +118,7 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_O = tmem_base;                      // lanes 0..15 of each subpartition, 512 columns
-  const uint32_t tmem_S = tmem_base + (16u << 16);        // lanes 16..31, columns 0..63
+  const uint32_t tmem_S = tmem_base + (16u << 16);        // lanes 16..31, columns 0..127: two S buffers
 
   // keys visible to the tile: up to the position of its last valid token
   const int toks_here = min(a.TQ, q_len - tok0);
@@ -163,20 +162,34 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // ---------------------------------------------------------------- MMA issue
       constexpr uint32_t idesc_s = umma_idesc(64, MLA_BKV, 1, 1, 0, 0);
       constexpr uint32_t idesc_o = umma_idesc(64, 256, 1, 1, 0, 1);   // B (= latent tile as V) is MN-major
-      const uint32_t qa = smem_u32(q_s);
-      const uint32_t pa = smem_u32(p_s);
+      const uint64_t dq0 = umma_desc_k_sw128(smem_u32(q_s));
+      const uint64_t dp0 = umma_desc_k_sw128(smem_u32(p_s));
       auto issue_s = [&](int j) {
-        const uint32_t ka = smem_u32(kv_s + (j & 1) * MLA_KV_BYTES);
+        // descriptors differ only in the start address (units of 16 bytes, low bits): base + constant
+        const uint64_t dk0 = umma_desc_k_sw128(smem_u32(kv_s + (j & 1) * MLA_KV_BYTES));
 #pragma unroll
         for (int h = 0; h < MLA_HALVES; ++h) {
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const uint64_t da = umma_desc_k_sw128(qa + h * (MLA_ROWS * 128) + k * 32);
-            const uint64_t db = umma_desc_k_sw128(ka + h * (MLA_BKV * 128) + k * 32);
-            umma_f16(tmem_S, da, db, idesc_s, (h | k) ? 1u : 0u);
+            const uint64_t off = uint64_t((h * (MLA_ROWS * 128) + k * 32) >> 4);
+            umma_f16(tmem_S + (j & 1) * MLA_BKV, dq0 + off, dk0 + off, idesc_s, (h | k) ? 1u : 0u);
           }
         }
-        umma_commit(s_full);
+        umma_commit(&s_full[j & 1]);
+      };
+      auto issue_pv = [&](int j) {
+        const uint64_t dv0 = umma_desc_mn_sw128(smem_u32(kv_s + (j & 1) * MLA_KV_BYTES), MLA_BKV * 128, 1024);
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+#pragma unroll
+          for (int k = 0; k < MLA_BKV / 16; ++k) {
+            // A = P (K-major, 16 keys = 32 B per step); B = 256 latent columns (4 halves) of 16 key rows
+            const uint64_t db = dv0 + uint64_t((n * 4 * (MLA_BKV * 128) + k * 16 * 128) >> 4);
+            umma_f16(tmem_O + n * 256, dp0 + uint64_t((k * 32) >> 4), db, idesc_o, (j | k) ? 1u : 0u);
+          }
+        }
+        umma_commit(&kv_empty[j & 1]);
+        umma_commit(o_done);
       };
       bool ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(&kv_full[0], 0, abort_flag);
       if (!ok) { *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FULL); }
@@ -185,42 +198,27 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         issue_s(0);
       }
       for (int j = 0; ok && j < n_blk; ++j) {
-        // S of tile j+1 goes first only when its tile has already landed and the softmax has released the S
-        // buffer; otherwise PV of tile j must not queue behind that load (the stage of tile j+1 was freed by PV of
-        // tile j-1 only a moment ago), so it is issued first and S follows.
-        bool s_issued = j + 1 >= n_blk;
-        if (!s_issued && mbar_try_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1) && mbar_try_wait(s_free, j & 1)) {
-          tc_fence_after();
-          issue_s(j + 1);
-          s_issued = true;
-        }
-        if (!mbar_wait(p_ready, j & 1, abort_flag)) {
-          *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FLAG); break;
-        }
-        tc_fence_after();
-        const uint32_t va = smem_u32(kv_s + (j & 1) * MLA_KV_BYTES);
-#pragma unroll
-        for (int n = 0; n < 2; ++n) {
-#pragma unroll
-          for (int k = 0; k < MLA_BKV / 16; ++k) {
-            // A = P (K-major, 16 keys = 32 B per step); B = 256 latent columns (4 halves) of 16 key rows
-            const uint64_t da = umma_desc_k_sw128(pa + k * 32);
-            const uint64_t db = umma_desc_mn_sw128(va + n * 4 * (MLA_BKV * 128) + k * 16 * 128, MLA_BKV * 128, 1024);
-            umma_f16(tmem_O + n * 256, da, db, idesc_o, (j | k) ? 1u : 0u);
+        // Two things are owed in this round, in whichever order their inputs arrive: S of tile j+1 (its latent
+        // tile has landed and the softmax of tile j-1 has released that S buffer) and PV of tile j (P is ready).
+        // Neither waits behind the other: the softmax of tile j may itself wait for S of tile j+1 before a rescale.
+        bool s_owed = j + 1 < n_blk, pv_owed = true;
+        const uint64_t t0 = globaltimer_ns();
+        uint32_t spins = 0;
+        while (s_owed || pv_owed) {
+          if (s_owed && mbar_test_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1) &&
+              (j < 1 || mbar_test_wait(&s_free[(j + 1) & 1], (((j + 1) >> 1) - 1) & 1))) {
+            tc_fence_after();
+            issue_s(j + 1);
+            s_owed = false;
           }
-        }
-        umma_commit(&kv_empty[j & 1]);
-        umma_commit(o_done);
-        if (!s_issued) {
-          if (!mbar_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag)) {
-            *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FULL); break;
+          if (pv_owed && mbar_test_wait(p_ready, j & 1)) {
+            tc_fence_after();
+            issue_pv(j);
+            pv_owed = false;
           }
-          // the softmax has read S of tile j (and finished any rescale of O)
-          if (!mbar_wait(s_free, j & 1, abort_flag)) {
-            *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_EMPTY); break;
+          if ((++spins & 0x3ff) == 0 && (*abort_flag || globaltimer_ns() - t0 > LB_WAIT_NS)) {
+            *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FLAG); ok = false; break;
           }
-          tc_fence_after();
-          issue_s(j + 1);
         }
       }
     }
@@ -236,60 +234,74 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_blk; ++j) {
-      if (!__all_sync(0xffffffffu, mbar_wait(s_full, j & 1, abort_flag))) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag))) {
         *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_FULL); ok = false; break;
       }
       tc_fence_after();
       const int key0 = (blk_lo + j) * MLA_BKV;
-      uint32_t r[MLA_BKV];
-      tmem_ld32(tmem_base + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
-      tmem_ld32(tmem_base + lane_off + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
-      tmem_ld_wait();
-      // the row's probabilities are computed into registers first: nothing here depends on the previous PV
-      float alpha = 1.f;
-      uint32_t packed[MLA_BKV / 2];
-      if (s_lane) {
-        const bool full = key0 + MLA_BKV <= hi;             // every key of the tile is visible to this row
-        float mx = -INFINITY;
-        if (full) {
+      const uint32_t s_col = uint32_t(j & 1) * MLA_BKV;
+      // S of row i sits in lane 16 + i: that lane keeps columns 32..63 and hands columns 0..31 to lane i, so both
+      // halves of the warp share the exponentials of a row
+      uint32_t v[32];
+      {
+        uint32_t r[MLA_BKV];
+        tmem_ld32(tmem_base + lane_off + s_col, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+        tmem_ld32(tmem_base + lane_off + s_col + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+        tmem_ld_wait();
 #pragma unroll
-          for (int c = 0; c < MLA_BKV; ++c) mx = fmaxf(mx, __uint_as_float(r[c]));
-        } else {
-#pragma unroll
-          for (int c = 0; c < MLA_BKV; ++c)
-            if (key0 + c < hi) mx = fmaxf(mx, __uint_as_float(r[c]));
+        for (int c = 0; c < 32; ++c) {
+          const uint32_t got = __shfl_down_sync(0xffffffffu, r[c], 16);
+          v[c] = s_lane ? r[32 + c] : got;
         }
-        const float m_blk = mx * a.scale_log2;
-        if (m_blk > m + MLA_RESCALE_LOG2 || (m == -INFINITY && m_blk != -INFINITY)) {
-          alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_blk);
-          m = m_blk;
-        }
-        const float neg_m = (m == -INFINITY) ? 0.f : -m;
-        float sum = 0.f;
-#pragma unroll
-        for (int c = 0; c < MLA_BKV; c += 2) {
-          float p0 = exp2f(fmaf(__uint_as_float(r[c]), a.scale_log2, neg_m));
-          float p1 = exp2f(fmaf(__uint_as_float(r[c + 1]), a.scale_log2, neg_m));
-          if (!full) {
-            if (key0 + c >= hi) p0 = 0.f;
-            if (key0 + c + 1 >= hi) p1 = 0.f;
-          }
-          // sum what the tensor core will see (bf16-rounded): numerator and denominator stay consistent
-          const __nv_bfloat162 bb = __floats2bfloat162_rn(p0, p1);
-          const float2 ff = __bfloat1622float2(bb);
-          sum += ff.x + ff.y;
-          packed[c / 2] = *reinterpret_cast<const uint32_t*>(&bb);
-        }
-        l = l * alpha + sum;
       }
-      // the factor of S row (lane 16 + i) belongs to the O row held by lane i
-      const float alpha_o = __shfl_down_sync(0xffffffffu, alpha, 16);
-      const float f = s_lane ? 1.f : alpha_o;
+      // the row's probabilities are computed into registers first: nothing here depends on the previous PV
+      const int kc = key0 + (s_lane ? 32 : 0);              // first key of this lane's 32 columns
+      const bool full = key0 + MLA_BKV <= hi;               // every key of the tile is visible to this row
+      float mx = -INFINITY;
+      if (full) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) mx = fmaxf(mx, __uint_as_float(v[c]));
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c)
+          if (kc + c < hi) mx = fmaxf(mx, __uint_as_float(v[c]));
+      }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+      float alpha = 1.f;
+      const float m_blk = mx * a.scale_log2;
+      if (m_blk > m + MLA_RESCALE_LOG2 || (m == -INFINITY && m_blk != -INFINITY)) {
+        alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_blk);
+        m = m_blk;
+      }
+      const float neg_m = (m == -INFINITY) ? 0.f : -m;
+      float sum = 0.f;
+      uint32_t packed[16];
+#pragma unroll
+      for (int c = 0; c < 32; c += 2) {
+        float p0 = exp2f(fmaf(__uint_as_float(v[c]), a.scale_log2, neg_m));
+        float p1 = exp2f(fmaf(__uint_as_float(v[c + 1]), a.scale_log2, neg_m));
+        if (!full) {
+          if (kc + c >= hi) p0 = 0.f;
+          if (kc + c + 1 >= hi) p1 = 0.f;
+        }
+        // sum what the tensor core will see (bf16-rounded): numerator and denominator stay consistent
+        const __nv_bfloat162 bb = __floats2bfloat162_rn(p0, p1);
+        const float2 ff = __bfloat1622float2(bb);
+        sum += ff.x + ff.y;
+        packed[c / 2] = *reinterpret_cast<const uint32_t*>(&bb);
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+      l = l * alpha + sum;                                  // (m, l) are kept alike in both lanes of a row
+      // lanes 0..15 hold the O rows; lanes 16..31 rewrite S / unused cells unchanged
+      const float f = s_lane ? 1.f : alpha;
       bool waited = false;
       if (j >= 1 && __any_sync(0xffffffffu, f != 1.f)) {
-        // O is rescaled only while no MMA is in flight: PV of tile j-1 has finished and S of tile j+1 waits for
-        // s_free. Lanes 16..31 rewrite what they read (columns 0..63 hold the consumed S tile, the rest is unused).
-        if (!__all_sync(0xffffffffu, mbar_wait(o_done, (j - 1) & 1, abort_flag))) {
+        // O is rescaled only while no MMA is in flight: PV of tile j-1 has finished, S of tile j+1 (the only S that
+        // can be on its way) has completed, S of tile j+2 waits for this tile's s_free and PV of tile j for p_ready.
+        // Lanes 16..31 rewrite what they read (columns 0..127 hold the two S buffers, the rest is unused).
+        bool done = mbar_wait(o_done, (j - 1) & 1, abort_flag);
+        if (done && j + 1 < n_blk) done = mbar_wait(&s_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag);
+        if (!__all_sync(0xffffffffu, done)) {
           *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_EMPTY); ok = false; break;
         }
         tc_fence_after();
@@ -306,7 +318,7 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mla_tmem_st_wait();
       }
       tc_fence_before();
-      mbar_arrive(s_free);
+      mbar_arrive(&s_free[j & 1]);
       // P is overwritten only after the previous PV has read it
       if (j >= 1 && !waited) {
         if (!__all_sync(0xffffffffu, mbar_wait(o_done, (j - 1) & 1, abort_flag))) {
@@ -314,11 +326,12 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         tc_fence_after();
       }
-      if (s_lane) {
+      {
         uint8_t* prow = p_s + row * 128;
+        const int ch0 = s_lane ? 4 : 0;                     // 16-byte chunks of this lane's 32 columns
 #pragma unroll
-        for (int ch = 0; ch < MLA_BKV / 8; ++ch) {
-          const int chunk = ch ^ (row & 7);
+        for (int ch = 0; ch < 4; ++ch) {
+          const int chunk = (ch0 + ch) ^ (row & 7);
           *reinterpret_cast<uint4*>(prow + chunk * 16) =
               make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
         }
@@ -334,9 +347,7 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     if (ok) {
       tc_fence_after();
-      // (m, l) of a row live in its S lane: hand them to the O lane
-      const float m_o = __shfl_down_sync(0xffffffffu, m, 16);
-      const float l_o = __shfl_down_sync(0xffffffffu, l, 16);
+      const float m_o = m, l_o = l;
       const long grow = long(q0 + tok0 + tq) * a.nh + head;         // global (token, head) row
       const bool write = !s_lane && row_ok;
       if (a.n_splits == 1) {

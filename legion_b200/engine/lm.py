@@ -134,6 +134,15 @@ class LmEngine(Engine):
         dev = model.device
         self.device = dev
         self.hybrid = bool(self.mcfg.recurrent_layers())
+        # data-parallel attention: this rank runs attention only for the sequences it owns (state slot % ranks)
+        self.dp_world = getattr(model.pctx, "dp_world", 1)
+        self.dp_rank = getattr(model.pctx, "dp_rank", 0)
+        if self.dp_world > 1:
+            if c.spec != "none" or drafter is not None:
+                raise ValueError("speculative decoding is not available with data-parallel attention")
+            # a cached prefix lives in its first owner's KV only, and the graph runner packs global rows
+            c.prefix_cache = False
+            c.cuda_graphs = False
         kv_tokens = c.kv_cache_tokens or c.max_seqs * c.ctx_size
         n_blocks = max(4, (kv_tokens + c.block_size - 1) // c.block_size)
         self.pool = BlockPool(n_blocks, c.block_size)
@@ -745,7 +754,47 @@ class LmEngine(Engine):
                          logit_rows=torch.tensor(lrows, dtype=torch.int64, device=dev),
                          max_q_len=max(len(t) for _, _, t in items), max_ctx=max(ctx), cu_q_host=cu)
 
+    def _dp_forward_and_finish(self, rows, verify: bool):
+        """One step under data-parallel attention. Every rank plans the same global rows; this rank runs the model
+        on the rows it owns (a padding row when it owns none, so that it still meets the others in every MoE
+        layer's exchange), then the logit rows of all ranks are gathered into the global order and every rank
+        samples all of them alike."""
+        import torch.distributed as dist
+        W, R = self.dp_world, self.dp_rank
+        own = [r for r in rows if r[0].slot % W == R]
+        if own:
+            b = self.build_batch(own, write_state=not verify)
+        else:
+            i32 = dict(dtype=torch.int32, device=self.device)
+            pad_slot = self.cfg.max_seqs + (self.cfg.prefix_cache_states if self.saved is not None else 0)
+            b = StepBatch(token_ids=torch.zeros(1, **i32), positions=torch.zeros(1, **i32),
+                          cu_q=torch.tensor([0, 1], **i32), ctx_lens=torch.ones(1, **i32),
+                          block_table=torch.zeros(1, 1, **i32),
+                          slots=torch.full((1,), -1, dtype=torch.int64, device=self.device),
+                          state_slots=torch.full((1,), pad_slot, **i32),
+                          logit_rows=torch.zeros(1, dtype=torch.int64, device=self.device), max_q_len=1, max_ctx=1,
+                          write_state=False, cu_q_host=[0, 1])
+        out = self.model.forward(b, self.kv, self.states)
+        counts = [n if s.phase == "decode" else (1 if p0 + n == s.n_prompt else 0) for s, p0, n in rows]
+        per_owner, where = [0] * W, []
+        for (s, _, _), c in zip(rows, counts):
+            o = s.slot % W
+            where.append((o, per_owner[o]))
+            per_owner[o] += c
+        M, V = max(1, max(per_owner)), out.logits.shape[1]
+        local = torch.zeros(M, V, dtype=torch.float32, device=self.device)
+        if own and per_owner[R]:
+            local[:per_owner[R]] = out.logits[:per_owner[R]].float()
+        parts = [torch.empty_like(local) for _ in range(W)]
+        dist.all_gather(parts, local, group=self.model.pctx.dp_group)
+        idx = [o * M + off + j for (o, off), c in zip(where, counts) for j in range(c)]
+        logits = torch.cat(parts, 0).index_select(0, torch.tensor(idx, dtype=torch.int64, device=self.device))
+        self._stats.dp_gather_bytes = getattr(self._stats, "dp_gather_bytes", 0) + W * M * V * 4
+        self._finish_rows(rows, None, logits, None, verify)
+
     def _forward_and_finish(self, rows, verify: bool):
+        if self.dp_world > 1:
+            return self._dp_forward_and_finish(rows, verify)
         all_decode_1 = all(s.phase == "decode" and n == 1 for s, _, n in rows)
         need_hidden = self.drafter is not None and getattr(self.drafter, "needs_hidden", False)
         hm = self._stats.host_ms

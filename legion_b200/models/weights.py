@@ -163,8 +163,13 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=torch.float32, seed: in
 class Shard:
     """Tensor-parallel (attention / dense FFN / shared expert) and expert-parallel slicing of weights."""
 
-    def __init__(self, cfg: ModelConfig, rank: int, world: int, expert_parallel: bool = False):
-        self.cfg, self.rank, self.world, self.ep = cfg, rank, world, expert_parallel
+    def __init__(self, cfg: ModelConfig, rank: int, world: int, expert_parallel: bool = False,
+                 dp_attention: bool = False):
+        self.cfg, self.rank, self.world, self.ep = cfg, rank, world, expert_parallel or dp_attention
+        self.dp_attention = dp_attention     # only the routed experts are split; everything else is whole
+        if dp_attention:
+            self.kv_rep = 1
+            return
         assert cfg.n_head % world == 0, "query heads must divide by the TP degree"
         self.kv_rep = 1
         if cfg.n_kv_head % world != 0:
@@ -189,6 +194,8 @@ class Shard:
         leaf = name.split(".", 1)[1] if "." in name else name
         leaf = leaf.replace("l.", "", 1) if name.startswith("mtp") and leaf.startswith("l.") else leaf
         if w == 1:
+            return None
+        if self.dp_attention and leaf not in ("moe.gate_up", "moe.down"):
             return None
         if leaf == "attn.qkv":
             D = cfg.head_dim

@@ -147,3 +147,69 @@ class ParallelCtx:
         return ops.moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, act, e_lo, shared, shared_gate, residual,
                                out=self.partial_out(x.shape[0], x.shape[1]) if x.is_cuda else None, norm=norm,
                                routing=routing)
+
+
+class DpEpCtx(ParallelCtx):
+    """Data-parallel attention with expert parallelism: every rank holds the attention / dense / shared-expert
+    weights whole and ``E / world`` routed experts, runs attention only for the sequences it owns, and meets the
+    other ranks inside each MoE layer, where tokens travel to their experts' owners and the results come back
+    (``parallel.ep.EpDispatcher`` on GPUs: dispatch and combine are peer stores fused into the grouped GEMM
+    pipeline; on CPU ranks the same exchange is an all-gather of the padded tokens, local experts over all of
+    them, and a sum). To the decoder it looks like a single rank: no layer output is a partial sum.
+
+    Reference counterpart: none (the reference mirrors tokens on every rank, ``src/model/core/tp_ep.rs:8-11``)."""
+
+    def __init__(self, rank: int, world: int, group, dispatcher=None):
+        super().__init__(0, 1)
+        self.dp_rank, self.dp_world, self.dp_group = rank, world, group
+        self.dispatcher = dispatcher
+        self.ep = world > 1
+
+    def expert_range(self, n_expert: int):
+        per = n_expert // self.dp_world
+        return self.dp_rank * per, (self.dp_rank + 1) * per
+
+    def moe(self, x, ids, wts, w_gate_up, w_down, n_ff, act, e_lo, shared, shared_gate, residual, norm=None,
+            routing=None):
+        if x.is_cuda:
+            if act != "silu":
+                raise NotImplementedError("the expert-parallel exchange implements SwiGLU experts")
+            y = self.dispatcher.forward(x, ids, wts, w_gate_up, w_down, shared, shared_gate, residual)
+        else:
+            y = self._moe_gathered(x, ids, wts, w_gate_up, w_down, n_ff, act, e_lo)
+            if shared is not None:
+                sh = shared.float()
+                if shared_gate is not None:
+                    sh = sh * torch.sigmoid(shared_gate.float())[:, None]
+                y = y + sh
+            if residual is not None:
+                y = y + residual.float()
+            y = y.to(x.dtype)
+        if norm is None:
+            return y
+        normed, _ = ops.rmsnorm(y, norm[0], norm[1], norm[2])
+        return y, normed
+
+    def _moe_gathered(self, x, ids, wts, w_gate_up, w_down, n_ff, act, e_lo):
+        """CPU ranks: all tokens to all ranks, local experts over all of them, sum, keep the own rows."""
+        import torch.distributed as dist
+        W, R, g = self.dp_world, self.dp_rank, self.dp_group
+        T = x.shape[0]
+        sizes = [torch.zeros(1, dtype=torch.int64) for _ in range(W)]
+        dist.all_gather(sizes, torch.tensor([T], dtype=torch.int64), group=g)
+        sizes = [int(t.item()) for t in sizes]
+        M = max(sizes)
+
+        def gather(t, fill=0):
+            pad = torch.full((M,) + tuple(t.shape[1:]), fill, dtype=t.dtype)
+            pad[:T] = t
+            outs = [torch.empty_like(pad) for _ in range(W)]
+            dist.all_gather(outs, pad, group=g)
+            return torch.cat([o[:n] for o, n in zip(outs, sizes)], 0)
+
+        xa, ia, wa = gather(x.float()), gather(ids, -1), gather(wts.float())
+        ya = ops.reference.moe_experts(xa.to(x.dtype), ia, wa, w_gate_up, w_down, n_ff, act, e_lo,
+                                       e_lo + w_gate_up.shape[0])
+        dist.all_reduce(ya, group=g)
+        off = sum(sizes[:R])
+        return ya[off:off + T]

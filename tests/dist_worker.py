@@ -148,6 +148,50 @@ def case_engine(dev, comm_kind):
     return {"tokens": toks, "graph_replays": replays}
 
 
+def case_engine_dp(dev):
+    """Data-parallel attention + expert-parallel exchange on GPUs against one GPU holding the whole model."""
+    from legion_b200.config import ModelConfig
+    from legion_b200.engine.lm import EngineConfig, build_engine
+    from legion_b200.engine.types import GenerateRequest, SamplingParams
+    from legion_b200.models.weights import Shard, random_weights
+    from legion_b200.parallel.context import DpEpCtx
+    from legion_b200.parallel.ep import EpDispatcher
+    cfg = ModelConfig(arch="qwen3moe", n_layer=3, hidden=512, vocab=2048, n_head=8, n_kv_head=2, head_dim=128,
+                      n_expert=8, top_k=2, expert_ff=256)
+    full = random_weights(cfg, "cpu", torch.float32, seed=0, std=0.05)
+    full = {k: (v.bfloat16() if v.dim() > 1 else v) for k, v in full.items()}
+    ecfg = dict(ctx_size=512, max_seqs=4, block_size=64, prefill_chunk=128, max_batch_tokens=256, prefix_cache=False)
+
+    def run(eng):
+        prompts = [torch.randint(0, 255, (n,), generator=torch.Generator().manual_seed(sd)).tolist()
+                   for n, sd in ((200, 1), (70, 2), (131, 3))]
+        streams = [eng.generate(GenerateRequest(prompt_tokens=p, sampling=SamplingParams(max_tokens=10, ignore_eos=True)))
+                   for p in prompts]
+        eng._drain(block=False)
+        for i in range(200):
+            eng._admit()
+            if not eng.running and len(eng.waiting) == 0:
+                break
+            eng.step()
+        return [s.collect().token_ids for s in streams]
+
+    single = build_engine(cfg, weights={k: v.to(dev) for k, v in full.items()}, device=str(dev), start=False,
+                          engine_cfg=EngineConfig(cuda_graphs=False, **ecfg))
+    want = run(single)
+    single.shutdown()
+    say("single-GPU run done")
+    w = {k: v.to(dev) for k, v in Shard(cfg, RANK, WORLD, dp_attention=True).shard_all(full).items()}
+    ep = EpDispatcher(dist.group.WORLD, RANK, WORLD, dev, cfg.n_expert, cfg.top_k, cfg.hidden, cfg.expert_ff,
+                      max_tokens=256, budget_ns=2_000_000_000)
+    eng = build_engine(cfg, weights=w, device=str(dev), pctx=DpEpCtx(RANK, WORLD, dist.group.WORLD, ep), start=False,
+                       engine_cfg=EngineConfig(**ecfg))
+    say("dp engine built")
+    got = run(eng)
+    ep.check()
+    eng.shutdown()
+    return {"tokens": got, "single": want}
+
+
 def case_pp(dev):
     """Pipeline stages over NCCL send / recv: same tokens as the whole model on one GPU."""
     from legion_b200.config import ModelConfig
@@ -201,6 +245,8 @@ def main():
         res = case_ep(dev)
     elif CASE == "pp":
         res = case_pp(dev)
+    elif CASE == "engine_dp":
+        res = case_engine_dp(dev)
     elif CASE in ("engine_nccl", "engine_fused", "engine_tail"):
         res = case_engine(dev, CASE.split("_")[1])
     else:

@@ -73,6 +73,13 @@ def test_tp_engine_fused_equals_nccl(tmp_path):
     assert c["tokens"] == a["tokens"]
 
 
+def test_dp_attention_with_expert_exchange(tmp_path):
+    """Each GPU runs attention for its own sequences; tokens meet their experts through the fused dispatch / combine."""
+    res = _run("engine_dp", 2, tmp_path)
+    assert len(res["tokens"]) == 3 and all(len(t) == 10 for t in res["tokens"])
+    assert res["tokens"] == res["single"]
+
+
 def test_pipeline_stages_over_nccl_p2p(tmp_path):
     res = _run("pp", 2, tmp_path)
     assert res["pp_micro4096"] == res["single"] and len(res["single"]) == 10
