@@ -91,7 +91,9 @@ def main(argv=None):
     ap.add_argument("--users", type=int, default=16)
     ap.add_argument("--prompt-len", type=int, default=8192)
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
-    ap.add_argument("--moe", default="auto", choices=["auto", "tp", "ep"],
+    ap.add_argument("--ep-capacity", type=float, default=0.0,
+                    help="--moe dp: receive room per rank as a multiple of its own routed pairs (0 = worst case)")
+    ap.add_argument("--moe", default="auto", choices=["auto", "tp", "ep", "dp"],
                     help="N > 1: slice every expert's FFN rows over the ranks (tp) or keep whole experts per rank "
                          "with mirrored tokens, partial outputs meeting in the layer's reduction (ep). auto: ep "
                          "from 4 GPUs (measured 6.67 vs 7.15 ms per step at 4 GPUs, 6.28 vs 7.11 ms at 8)")
@@ -125,8 +127,21 @@ def main(argv=None):
         cfg.layer_kinds = cfg.layer_kinds[:a.layers]
     W, K, U, L = max(3, a.warmup), a.steps, a.users, a.prompt_len
     ep = world > 1 and (a.moe_ep or a.moe == "ep" or (a.moe == "auto" and world >= 4))
-    pctx = pdist.init_from_env("cuda", comm=a.comm, max_rows=8192, hidden=cfg.hidden, expert_parallel=ep)
-    shard = Shard(cfg, rank, world, expert_parallel=ep) if world > 1 else None
+    dp = world > 1 and a.moe == "dp"
+    if dp:
+        # data-parallel attention: every rank runs attention for its own users, tokens meet their experts through
+        # the fused dispatch / combine of each MoE layer
+        import torch.distributed as dist
+        from legion_b200.parallel.context import DpEpCtx
+        from legion_b200.parallel.ep import EpDispatcher
+        pdist.init_from_env("cuda", comm="nccl")
+        disp = EpDispatcher(dist.group.WORLD, rank, world, dev, cfg.n_expert, cfg.top_k, cfg.hidden, cfg.expert_ff,
+                            8192, a.ep_capacity or None)
+        pctx = DpEpCtx(rank, world, dist.group.WORLD, disp)
+        shard = Shard(cfg, rank, world, dp_attention=True)
+    else:
+        pctx = pdist.init_from_env("cuda", comm=a.comm, max_rows=8192, hidden=cfg.hidden, expert_parallel=ep)
+        shard = Shard(cfg, rank, world, expert_parallel=ep) if world > 1 else None
     t0 = time.time()
     weights = random_weights(cfg, dev, torch.bfloat16, seed=0, shard=shard)
     torch.cuda.synchronize()
@@ -188,20 +203,25 @@ def main(argv=None):
         "a sequence finished inside the timed region: the step no longer carries the full batch"
 
     # ---- device-timed steps: K replays of the decode-step graph with the current inputs
-    entry = graphs.entries[graphs.bucket(U)]
+    entry = graphs.entries[graphs.bucket((U + world - 1) // world if dp else U)]
     # kernels per step: count them once with an eager run of the same step on the same inputs
     sm100.LAUNCHES["n"] = 0
     eng.model.forward(entry.batch, eng.kv, eng.states)
     sm100.argmax(torch.zeros(U, cfg.vocab, device=dev))
     torch.cuda.synchronize()
     launches_per_step = sm100.LAUNCHES["n"]
-    for _ in range(W):
+    def replay_step():
         entry.graph.replay()
+        if dp:      # the step's picks of all ranks, as the engine gathers them
+            dist.all_gather_into_tensor(entry.all_picks, entry.picks, group=pctx.dp_group)
+
+    for _ in range(W):
+        replay_step()
     clocks.start()
     pdist.barrier(); torch.cuda.synchronize()
     ev0.record()
     for _ in range(K):
-        entry.graph.replay()
+        replay_step()
     ev1.record()
     torch.cuda.synchronize()
     pdist.barrier()
@@ -216,6 +236,8 @@ def main(argv=None):
     comm_status = 0
     if pctx.symm is not None:
         comm_status = int(pctx.symm.status.item())
+    if dp:
+        comm_status = int(disp.status.item())
 
     ms_per_step = dev_ms / K
     value = U * 1000.0 / ms_per_step
@@ -226,7 +248,9 @@ def main(argv=None):
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": round(value / BASELINE_DECODE_16, 3), "dtype": "bf16", "data": "synthetic",
         "config": {"model": a.model + ("" if not a.layers else f"-TRUNCATED-{a.layers}L-INVALID"), "global_batch": U,
-                   "seq_len": L, "parallelism": f"tp{a.gpus}" + ("+ep(experts whole per rank)" if ep else ""), "users": U, "comm": a.comm if a.gpus > 1 else "none",
+                   "seq_len": L, "parallelism": (f"dp{a.gpus}(attention)+ep{a.gpus}(token dispatch)" if dp else
+                                                    f"tp{a.gpus}" + ("+ep(experts whole per rank)" if ep else "")),
+                   "users": U, "comm": ("fused" if dp else a.comm) if a.gpus > 1 else "none",
                    "l2": "inputs larger than L2 (each step streams >40 GB of weights and KV)", "page": 64},
         "clocks": clk,
         "e2e": {"value": round(e2e_value, 2), "unit": "tok/s", "h2d_bytes_per_step": int(h2d_per),

@@ -62,6 +62,11 @@ def _add_engine_args(ap: argparse.ArgumentParser):
     g.add_argument("--gpus", type=int, default=None, help="alias of --tp on a single node")
     g.add_argument("--tp-moe-ep", action="store_true", help="shard whole experts over the ranks instead of their rows")
     g.add_argument("--tp-comm", choices=["fused", "nccl"], default="fused")
+    g.add_argument("--dp-attention", action="store_true",
+                   help="with --tp N: every rank holds attention whole and runs it for its own sequences; routed "
+                        "experts are split over the ranks and tokens travel to them inside each MoE layer")
+    g.add_argument("--ep-capacity", type=float, default=0.0,
+                   help="--dp-attention: receive room per rank as a multiple of its own routed pairs (0 = worst case)")
     g.add_argument("--tp-replicas", type=int, default=1, help="data-parallel engine replicas")
     g.add_argument("--tp-gemm-tail", action="store_true",
                    help="run o-proj / down-proj and their all-reduce as one kernel (fused communicator)")
@@ -124,6 +129,18 @@ def build_engine_from_args(a, start: bool = True):
         pipe = PipeStage(rank, world, dist.group.WORLD, n_layer, split, a.pipeline_micro, a.split_last_extra)
         cfg, w, tok, info = load_model(path, device, seed=a.seed, keep_layers=pipe.owns)
         model = Decoder(cfg, w, None, max_position=ec.ctx_size + 8, pipe=pipe)
+        return LmEngine(model, tok, ec, start=start)
+    if world > 1 and getattr(a, "dp_attention", False):
+        import torch.distributed as dist
+        from ..parallel.context import DpEpCtx
+        pdist.init_from_env(device, comm="nccl")
+        cfg, w, tok, info = load_model(path, device, rank=rank, world=world, seed=a.seed, dp_attention=True)
+        disp = None
+        if on_gpu and cfg.n_expert:
+            from ..parallel.ep import EpDispatcher
+            disp = EpDispatcher(dist.group.WORLD, rank, world, torch.device(device), cfg.n_expert, cfg.top_k, cfg.hidden,
+                                cfg.expert_ff, ec.max_batch_tokens, a.ep_capacity or None)
+        model = Decoder(cfg, w, DpEpCtx(rank, world, dist.group.WORLD, disp), max_position=ec.ctx_size + 8)
         return LmEngine(model, tok, ec, start=start)
     if world > 1:
         from ..config import PRESETS  # noqa: F401

@@ -23,7 +23,7 @@ BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 
 class _Entry:
     __slots__ = ("graph", "B", "W", "pack_h", "pack_d", "batch", "picks", "picks_h", "logits", "n_ints", "arange",
-                 "bt_key", "pack_np")
+                 "bt_key", "pack_np", "all_picks", "all_picks_h")
 
 
 class DecodeGraphs:
@@ -69,6 +69,7 @@ class DecodeGraphs:
         e.B, e.W, e.n_ints = B, W, total
         e.arange = torch.arange(B + 1, dtype=torch.int32)
         e.bt_key = [None] * B
+        e.all_picks = e.all_picks_h = None
         e.pack_h = torch.zeros(total, dtype=torch.int32).pin_memory()
         e.pack_np = e.pack_h.numpy()          # the same pinned words, as the view the native packer writes
         e.pack_d = torch.zeros(total, dtype=torch.int32, device=dev)
@@ -119,11 +120,13 @@ class DecodeGraphs:
         o, n = off["block_table"]
         h[o + n_real * e.W:o + n] = 0
 
-    def run(self, rows) -> Tuple[Optional[List[int]], Optional[torch.Tensor]]:
+    def run(self, rows, B: Optional[int] = None, gather=None) -> Tuple[Optional[List[int]], Optional[torch.Tensor]]:
         """rows: [(seq, position, 1)]. Returns (picked token per row, logits [n, V]) or (None, None) when the
-        batch does not fit a bucket."""
+        batch does not fit a bucket. ``B`` forces the bucket (data-parallel attention: every rank replays the
+        bucket of the fullest rank, possibly with no row of its own) and ``gather=(group, world)`` makes the
+        result the picks of ALL ranks, ``world * B`` values in rank order."""
         n = len(rows)
-        B = self.bucket(n)
+        B = B or self.bucket(n)
         if B is None:
             return None, None
         e = self.entries.get(B) or self._capture(B)
@@ -135,7 +138,7 @@ class DecodeGraphs:
             native.pack_decode(e.pack_np, B, e.W, pool.block_size, self.pad_slot,
                                [s.tokens[-1] for s, _, _ in rows], [p0 for _, p0, _ in rows],
                                [s.slot for s, _, _ in rows], [s.table.blocks for s, _, _ in rows])
-            return self._replay(e, rows, n, B)
+            return self._replay(e, rows, n, B, gather)
         off, _ = self._layout(B, e.W)
         h = e.pack_h
         sl = h[off["slots"][0]:off["slots"][0] + 2 * B].view(torch.int64)
@@ -164,12 +167,25 @@ class DecodeGraphs:
         for i in range(n, B):
             e.bt_key[i] = None
         self._fill_padding(e, n)
-        return self._replay(e, rows, n, B)
+        return self._replay(e, rows, n, B, gather)
 
-    def _replay(self, e: _Entry, rows, n: int, B: int):
+    def _replay(self, e: _Entry, rows, n: int, B: int, gather=None):
         eng = self.eng
         e.pack_d.copy_(e.pack_h, non_blocking=True)
         e.graph.replay()
+        if gather is not None:
+            import torch.distributed as dist
+            group, world = gather
+            if e.all_picks is None:
+                e.all_picks = torch.zeros(world * B, dtype=torch.int32, device=eng.device)
+                e.all_picks_h = torch.zeros(world * B, dtype=torch.int32).pin_memory()
+            dist.all_gather_into_tensor(e.all_picks, e.picks, group=group)
+            e.all_picks_h.copy_(e.all_picks, non_blocking=True)
+            torch.cuda.current_stream(eng.device).synchronize()
+            self.h2d_bytes += e.n_ints * 4
+            self.d2h_bytes += world * B * 4
+            self.replays += 1
+            return e.all_picks_h.tolist(), None
         e.picks_h.copy_(e.picks, non_blocking=True)
         torch.cuda.current_stream(eng.device).synchronize()
         self.h2d_bytes += e.n_ints * 4

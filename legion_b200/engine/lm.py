@@ -140,9 +140,8 @@ class LmEngine(Engine):
         if self.dp_world > 1:
             if c.spec != "none" or drafter is not None:
                 raise ValueError("speculative decoding is not available with data-parallel attention")
-            # a cached prefix lives in its first owner's KV only, and the graph runner packs global rows
+            # a cached prefix lives in its first owner's KV only
             c.prefix_cache = False
-            c.cuda_graphs = False
         kv_tokens = c.kv_cache_tokens or c.max_seqs * c.ctx_size
         n_blocks = max(4, (kv_tokens + c.block_size - 1) // c.block_size)
         self.pool = BlockPool(n_blocks, c.block_size)
@@ -762,6 +761,20 @@ class LmEngine(Engine):
         import torch.distributed as dist
         W, R = self.dp_world, self.dp_rank
         own = [r for r in rows if r[0].slot % W == R]
+        if self._graphs is not None and all(
+                s.phase == "decode" and n == 1 and s.req.sampling.greedy and s.req.sampling.plain and s.constraint is None
+                for s, _, n in rows):
+            # decode step from the graphs: every rank replays the bucket of the fullest rank, the picked tokens of
+            # all ranks are gathered (one small collective) and mapped back to the global row order
+            per_owner, where = [0] * W, []
+            for s, _, _ in rows:
+                where.append((s.slot % W, per_owner[s.slot % W]))
+                per_owner[s.slot % W] += 1
+            Bg = self._graphs.bucket(max(per_owner))
+            if Bg is not None:
+                picks, _ = self._graphs.run(own, B=Bg, gather=(self.model.pctx.dp_group, W))
+                self._finish_rows(rows, None, None, None, verify, picked=[picks[o * Bg + off] for o, off in where])
+                return
         if own:
             b = self.build_batch(own, write_state=not verify)
         else:

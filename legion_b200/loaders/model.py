@@ -18,7 +18,7 @@ from .tokenizer import BpeTokenizer, ByteTokenizer, Tokenizer
 
 
 def load_model(path: str, device="cpu", dtype=None, rank: int = 0, world: int = 1, expert_parallel: bool = False,
-               seed: int = 0, keep_layers=None) -> Tuple[ModelConfig, Dict[str, torch.Tensor], Tokenizer, dict]:
+               seed: int = 0, keep_layers=None, dp_attention: bool = False) -> Tuple[ModelConfig, Dict[str, torch.Tensor], Tokenizer, dict]:
     """``keep_layers(il)``: a pipeline stage keeps only the layers it owns (plus embeddings and head)."""
     from ..models.weights import layer_of
     keep = None
@@ -30,7 +30,7 @@ def load_model(path: str, device="cpu", dtype=None, rank: int = 0, world: int = 
     info: dict = {"source": path}
     if path.startswith("random:"):
         cfg = PRESETS[path.split(":", 1)[1]]()
-        shard = Shard(cfg, rank, world, expert_parallel) if world > 1 else None
+        shard = Shard(cfg, rank, world, expert_parallel, dp_attention) if world > 1 else None
         w = random_weights(cfg, dev, dtype, seed=seed, shard=shard, keep=keep)
         return cfg, w, ByteTokenizer(cfg.vocab), info
     if os.path.isdir(path):
@@ -58,6 +58,6 @@ def load_model(path: str, device="cpu", dtype=None, rank: int = 0, world: int = 
     if keep is not None:
         w = {k: v for k, v in w.items() if keep(k)}
     if world > 1:
-        sh = Shard(cfg, rank, world, expert_parallel)
+        sh = Shard(cfg, rank, world, expert_parallel, dp_attention)
         w = {k: sh.slice(k, v).to(dev) for k, v in w.items()}
     return cfg, w, tok, info

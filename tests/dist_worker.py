@@ -188,8 +188,9 @@ def case_engine_dp(dev):
     say("dp engine built")
     got = run(eng)
     ep.check()
+    replays = eng._graphs.replays if eng._graphs else 0
     eng.shutdown()
-    return {"tokens": got, "single": want}
+    return {"tokens": got, "single": want, "graph_replays": replays}
 
 
 def case_pp(dev):

@@ -78,6 +78,7 @@ def test_dp_attention_with_expert_exchange(tmp_path):
     res = _run("engine_dp", 2, tmp_path)
     assert len(res["tokens"]) == 3 and all(len(t) == 10 for t in res["tokens"])
     assert res["tokens"] == res["single"]
+    assert res["graph_replays"] > 0          # decode steps ran from CUDA graphs with the exchange captured inside
 
 
 def test_pipeline_stages_over_nccl_p2p(tmp_path):
