@@ -148,6 +148,38 @@ def case_engine(dev, comm_kind):
     return {"tokens": toks, "graph_replays": replays}
 
 
+def case_peer_experts(dev):
+    """Experts sharded over the ranks' symmetric memory; a rank's grouped GEMM streams a PEER's expert tiles over
+    NVLink with plain (non-multicast) TMA loads. Every rank computes the whole MoE layer from all shards."""
+    from legion_b200.ops import reference as ref
+    from legion_b200.ops import sm100
+    from legion_b200.residency.experts import PeerExperts
+    E, k, F, H = 8, 2, 256, 512
+    g = torch.Generator().manual_seed(5)
+    gu_all = (torch.randn(E, 2 * F, H, generator=g) * 0.05).bfloat16()
+    dn_all = (torch.randn(E, H, F, generator=g) * 0.05).bfloat16()
+    per = E // WORLD
+    pe = PeerExperts(gu_all[RANK * per:(RANK + 1) * per].to(dev).contiguous(),
+                     dn_all[RANK * per:(RANK + 1) * per].to(dev).contiguous(), dist.group.WORLD, RANK, WORLD)
+    say("peer shards mapped")
+    errs = []
+    for T in (7, 100):
+        gg = torch.Generator().manual_seed(40 + T)
+        x = (torch.randn(T, H, generator=gg) * 0.5).bfloat16().to(dev)
+        ids, wts = sm100.router_topk(torch.randn(T, E, generator=gg).to(dev), k)
+        y = torch.zeros(T, H, device=dev)
+        for r in range(WORLD):
+            gu, dn = pe.views(r)
+            y += sm100.moe_experts(x, ids, wts, gu, dn, F, e_lo=pe.expert_range(r)[0]).float()
+        torch.cuda.synchronize()
+        want = ref.moe_experts(x.cpu(), ids.cpu(), wts.cpu(), gu_all, dn_all, F)
+        errs.append(float((y.cpu() - want.float()).abs().max()))
+        say("tokens", T, "err", errs[-1])
+    assert sm100.Workspace.get(dev).check() == 0
+    dist.barrier()          # no rank frees its shard while a peer may still read it
+    return {"errs": errs}
+
+
 def case_engine_dp(dev):
     """Data-parallel attention + expert-parallel exchange on GPUs against one GPU holding the whole model."""
     from legion_b200.config import ModelConfig
@@ -246,6 +278,8 @@ def main():
         res = case_ep(dev)
     elif CASE == "pp":
         res = case_pp(dev)
+    elif CASE == "peer_experts":
+        res = case_peer_experts(dev)
     elif CASE == "engine_dp":
         res = case_engine_dp(dev)
     elif CASE in ("engine_nccl", "engine_fused", "engine_tail"):

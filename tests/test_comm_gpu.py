@@ -73,6 +73,12 @@ def test_tp_engine_fused_equals_nccl(tmp_path):
     assert c["tokens"] == a["tokens"]
 
 
+def test_peer_expert_fetch_in_the_gemm(tmp_path):
+    """The grouped expert GEMM reads a peer GPU's expert tiles with plain TMA loads (no copy first)."""
+    res = _run("peer_experts", 2, tmp_path)
+    assert max(res["errs"]) < 0.03, res
+
+
 def test_dp_attention_with_expert_exchange(tmp_path):
     """Each GPU runs attention for its own sequences; tokens meet their experts through the fused dispatch / combine."""
     res = _run("engine_dp", 2, tmp_path)
