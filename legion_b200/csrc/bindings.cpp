@@ -93,6 +93,58 @@ void wgemm(const Tensor& w, const Tensor& x, Tensor& out, const OptT& residual, 
   TORCH_CHECK(lb::wgemm_launch(h, cur_stream()) == 0, lb::wgemm_last_error());
 }
 
+// Block-scaled FP8: w [rows, K] and x [tokens, K] hold e4m3 bytes; w_bscale [rows / 128, K / 128] and x_bscale
+// [tokens, K / 128] are fp32. Same tile / grouping / epilogue options as wgemm; out is bf16.
+void wgemm_fp8(const Tensor& w, const Tensor& w_bscale, const Tensor& x, const Tensor& x_bscale, Tensor& out,
+               const OptT& residual, const OptT& tok_scale, const OptT& out_rows, int64_t n_feat, bool dual,
+               int64_t dual_offset, int64_t bn, int64_t split_k, const OptT& ws, const OptT& counters, Tensor& status,
+               const OptT& tile_group, const OptT& tile_tok0, const OptT& tile_ntok, const OptT& meta, int64_t max_tiles,
+               int64_t rows_per_group, int64_t n_tok, const OptT& tile_out0) {
+  TORCH_CHECK(w.is_cuda() && x.is_cuda() && w.element_size() == 1 && x.element_size() == 1 && w.dim() == 2 &&
+                  x.dim() == 2 && w.stride(1) == 1 && x.stride(1) == 1 && w.size(1) == x.size(1),
+              "wgemm_fp8: w [rows, K] and x [tokens, K] must be 1-byte e4m3 tensors with the same K");
+  const int64_t K = x.size(1);
+  TORCH_CHECK(w_bscale.scalar_type() == at::kFloat && w_bscale.is_contiguous() &&
+                  w_bscale.numel() == ((w.size(0) + 127) / 128) * (K / 128), "wgemm_fp8: weight block scales");
+  TORCH_CHECK(x_bscale.scalar_type() == at::kFloat && x_bscale.is_contiguous() && x_bscale.numel() == x.size(0) * (K / 128),
+              "wgemm_fp8: activation group scales");
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.dim() == 2 && out.stride(1) == 1 && out.size(1) >= n_feat,
+              "wgemm_fp8: out must be bf16 [rows, >= n_feat]");
+  c10::cuda::CUDAGuard guard(w.device());
+  lb::WgemmHost h{};
+  h.w = w.data_ptr(); h.w_rows = w.size(0); h.ldw = w.stride(0);
+  h.x = x.data_ptr(); h.x_rows = x.size(0); h.ldx = x.stride(0);
+  h.w_bscale = w_bscale.data_ptr<float>(); h.x_bscale = x_bscale.data_ptr<float>();
+  h.out = out.data_ptr(); h.ldo = out.stride(0); h.out_f32 = false;
+  if (residual.has_value()) {
+    check_bf16(*residual, "residual");
+    h.residual = reinterpret_cast<const __nv_bfloat16*>(residual->data_ptr());
+    h.ldr = residual->stride(0);
+  }
+  h.tok_scale = optp<float>(tok_scale);
+  h.out_rows = optp<int>(out_rows);
+  h.K = int(K); h.n_feat = int(n_feat); h.n_tok = int(n_tok);
+  h.bn = int(bn); h.dual = dual;
+  h.tile_group = optp<int>(tile_group); h.tile_tok0 = optp<int>(tile_tok0); h.tile_ntok = optp<int>(tile_ntok);
+  h.n_tiles_dev = optp<int>(meta);
+  h.tile_out0 = optp<int>(tile_out0);
+  h.n_tok_tiles_max = int(max_tiles);
+  h.rows_per_group = int(rows_per_group); h.dual_offset = int(dual_offset);
+  h.split_k = int(split_k);
+  h.ws = optpm<float>(ws);
+  h.counters = optpm<int>(counters);
+  if (h.split_k > 1) {
+    TORCH_CHECK(ws.has_value() && counters.has_value(), "wgemm_fp8: split-K needs ws and counters");
+    const int n_tok_tiles = h.tile_group ? h.n_tok_tiles_max : (h.n_tok + h.bn - 1) / h.bn;
+    const int feat_tiles = (h.n_feat + 127) / 128;
+    TORCH_CHECK(size_t(ws->numel()) >= lb::wgemm_workspace_floats(h.bn, dual, n_tok_tiles, feat_tiles, h.split_k),
+                "wgemm_fp8: split-K workspace too small");
+    TORCH_CHECK(counters->numel() >= int64_t(n_tok_tiles) * feat_tiles, "wgemm_fp8: too few split-K counters");
+  }
+  h.status = reinterpret_cast<int*>(status.data_ptr());
+  TORCH_CHECK(lb::wgemm_launch(h, cur_stream()) == 0, lb::wgemm_last_error());
+}
+
 // Dense GEMM whose kernel tail all-reduces the output over the ranks' symmetric buffers (+ residual, + RMSNorm).
 // `slot` must be this rank's partial slot inside its symmetric buffer (byte offset buf_off).
 void wgemm_allreduce(const Tensor& w, const Tensor& x, Tensor& slot, int64_t bn, int64_t split_k, const OptT& ws,
@@ -479,6 +531,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         pybind11::arg("tile_ntok"), pybind11::arg("meta"), pybind11::arg("max_tiles"), pybind11::arg("rows_per_group"),
         pybind11::arg("n_tok"), pybind11::arg("out_peer"), pybind11::arg("tile_out0") = pybind11::none(),
         pybind11::arg("w_scales") = pybind11::none(), pybind11::arg("w_gscale") = pybind11::none());
+  m.def("wgemm_fp8", &wgemm_fp8);
   m.def("wgemm_allreduce", &wgemm_allreduce);
   m.def("wgemm_allgather", &wgemm_allgather);
   m.def("rmsnorm", &rmsnorm);

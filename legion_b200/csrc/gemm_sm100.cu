@@ -38,7 +38,7 @@ static constexpr int SMEM_BUDGET = 200 * 1024;
 static constexpr int W_RAW_BYTES = BM * BK / 2;   // NVFP4: 128 rows x 32 bytes of packed e2m1 codes per k block
 static constexpr int W_SC_BYTES = BM * 16;        //        128 rows x 16 e4m3 block scales (4 k blocks of 64)
 
-template <int BN, bool DUAL, bool WFP4 = false>
+template <int BN, bool DUAL, bool WFP4 = false, bool WFP8 = false>
 struct WgemmCfg {
   static constexpr int NW = DUAL ? 2 : 1;
   static constexpr int X_TILE_BYTES = BN * BK * 2;
@@ -51,7 +51,10 @@ struct WgemmCfg {
   static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
   static constexpr int ACC_COLS = BN * (DUAL ? 2 : 1);
-  static constexpr int TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;
+  // bf16 / NVFP4: two accumulators (one drains while the next tile runs). FP8: a ring of four PARTIAL accumulators,
+  // one per 128-wide k block, which the epilogue warps scale and add up in registers
+  static constexpr int NACC = WFP8 ? 4 : 2;
+  static constexpr int TMEM_COLS = NACC * ACC_COLS < 32 ? 32 : NACC * ACC_COLS;
   static constexpr int EPI_BYTES = 32 * BM * 4;  // fp32 staging of 32 token columns
   static constexpr int SMEM_BYTES =
       STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align slack*/ + 512 /*barriers*/ + LUT_BYTES;
@@ -111,22 +114,24 @@ __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-template <int BN, bool DUAL, bool OUT_F32, bool WFP4>
+template <int BN, bool DUAL, bool OUT_F32, bool WFP4, bool WFP8 = false>
 __global__ void __launch_bounds__(WFP4 ? 448 : 192, 1)
 wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
              const __grid_constant__ CUtensorMap tmS, const WgemmArgs a) {
-  using Cfg = WgemmCfg<BN, DUAL, WFP4>;
+  using Cfg = WgemmCfg<BN, DUAL, WFP4, WFP8>;
   constexpr int STAGES = Cfg::STAGES;
+  constexpr int NACC = Cfg::NACC;
+  constexpr int KBE = WFP8 ? 128 : BK;     // elements per k block: one 128-byte swizzle row of e4m3 or bf16
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* stage = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES + Cfg::EPI_BYTES);
   uint64_t* full = bars;                  // [STAGES]
   uint64_t* empty = bars + STAGES;        // [STAGES]
-  uint64_t* tfull = bars + 2 * STAGES;    // [2]
-  uint64_t* tempty = bars + 2 * STAGES + 2;  // [2]
-  uint64_t* wready = bars + 2 * STAGES + 4;  // [STAGES] NVFP4: operand tile of the stage has been expanded
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + (WFP4 ? STAGES : 0));
+  uint64_t* tfull = bars + 2 * STAGES;    // [NACC]
+  uint64_t* tempty = bars + 2 * STAGES + 4;  // [NACC]
+  uint64_t* wready = bars + 2 * STAGES + 8;  // [STAGES] NVFP4: operand tile of the stage has been expanded
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 8 + (WFP4 ? STAGES : 0));
   uint16_t* lut_sc = reinterpret_cast<uint16_t*>(smem + STAGES * Cfg::STAGE_BYTES + Cfg::EPI_BYTES + 512);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* last_flag = reinterpret_cast<int*>(tmem_slot + 2);
@@ -140,7 +145,7 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
       mbar_init(&empty[s], 1);
       if (WFP4) mbar_init(&wready[s], 256);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < NACC; ++i) {
       mbar_init(&tfull[i], 1);
       mbar_init(&tempty[i], 4);  // one arrive per epilogue warp
     }
@@ -222,7 +227,7 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
   }
 
   const int n_tok_tiles = a.tile_group ? min(*a.n_tiles_dev, a.n_tok_tiles_max) : (a.n_tok + BN - 1) / BN;
-  const int num_kb = (a.K + BK - 1) / BK;
+  const int num_kb = (a.K + KBE - 1) / KBE;
   const int kb_per_split = (num_kb + a.split_k - 1) / a.split_k;
 
   if (warp == 0) {
@@ -259,10 +264,10 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
             }
           } else {
             mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
-            tma_load_2d(st, &tmW, &full[s], kb * BK, wrow);
-            if (DUAL) tma_load_2d(st + W_TILE_BYTES, &tmW, &full[s], kb * BK, wrow + a.dual_offset);
+            tma_load_2d(st, &tmW, &full[s], kb * KBE, wrow);
+            if (DUAL) tma_load_2d(st + W_TILE_BYTES, &tmW, &full[s], kb * KBE, wrow + a.dual_offset);
           }
-          tma_load_2d(st + Cfg::X_OFF, &tmX, &full[s], kb * BK, it.tok0);
+          tma_load_2d(st + Cfg::X_OFF, &tmX, &full[s], kb * KBE, it.tok0);
           ++issued;
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
@@ -282,8 +287,8 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = WFP4 ? umma_idesc(BM, BN, 0, 0, 0, 0)      // f16 operand tiles (see the de-quantiser)
-                                      : umma_idesc(BM, BN, 1, 1, 0, 0);
+      constexpr uint32_t idesc = (WFP4 || WFP8) ? umma_idesc(BM, BN, 0, 0, 0, 0)   // f16 tiles (de-quantiser) / e4m3
+                                                : umma_idesc(BM, BN, 1, 1, 0, 0);
       int s = 0;
       uint32_t ph = 0;
       int acc = 0;
@@ -293,13 +298,14 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
       for (int w = blockIdx.x; ok && decode_work<BN>(a, w, n_tok_tiles, it); w += gridDim.x) {
         const int kb0 = it.ks * kb_per_split;
         const int kb1 = min(num_kb, kb0 + kb_per_split);
-        if (!mbar_wait(&tempty[acc], acc_ph ^ 1, abort_flag)) {
-          *abort_flag = 1;
-          atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_EMPTY);
-          break;
+        if (!WFP8) {
+          if (!mbar_wait(&tempty[acc], acc_ph ^ 1, abort_flag)) {
+            *abort_flag = 1;
+            atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_EMPTY);
+            break;
+          }
+          tc_fence_after();
         }
-        tc_fence_after();
-        const uint32_t d0 = tmem_base + acc * Cfg::ACC_COLS;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full[s], ph, abort_flag) || (WFP4 && !mbar_wait(&wready[s], ph, abort_flag))) {
             *abort_flag = 1;
@@ -307,24 +313,43 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
             ok = false;
             break;
           }
+          if (WFP8 && !mbar_wait(&tempty[acc], acc_ph ^ 1, abort_flag)) {   // this k block's partial accumulator
+            *abort_flag = 1;
+            atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_EMPTY);
+            ok = false;
+            break;
+          }
           tc_fence_after();
+          const uint32_t d0 = tmem_base + acc * Cfg::ACC_COLS;
           const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
           const uint64_t dw = umma_desc_k_sw128(sa);
           const uint64_t dw2 = umma_desc_k_sw128(sa + W_TILE_BYTES);
           const uint64_t dx = umma_desc_k_sw128(sa + Cfg::X_OFF);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
+            // one instruction covers 32 bytes of K: 16 bf16 / f16 or 32 e4m3
             const uint64_t koff = uint64_t(k * UMMA_K * 2 / 16);
-            umma_f16(d0, dw + koff, dx + koff, idesc, accum);
-            if (DUAL) umma_f16(d0 + BN, dw2 + koff, dx + koff, idesc, accum);
+            if (WFP8) {
+              umma_f8(d0, dw + koff, dx + koff, idesc, k > 0 ? 1u : 0u);
+              if (DUAL) umma_f8(d0 + BN, dw2 + koff, dx + koff, idesc, k > 0 ? 1u : 0u);
+            } else {
+              const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
+              umma_f16(d0, dw + koff, dx + koff, idesc, accum);
+              if (DUAL) umma_f16(d0 + BN, dw2 + koff, dx + koff, idesc, accum);
+            }
           }
           umma_commit(&empty[s]);
           if (++s == STAGES) { s = 0; ph ^= 1; }
+          if (WFP8) {
+            umma_commit(&tfull[acc]);
+            if (++acc == NACC) { acc = 0; acc_ph ^= 1; }
+          }
         }
         if (!ok) break;
-        umma_commit(&tfull[acc]);
-        if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+        if (!WFP8) {
+          umma_commit(&tfull[acc]);
+          if (++acc == NACC) { acc = 0; acc_ph ^= 1; }
+        }
       }
     }
   } else if (WFP4 && warp >= 6) {
@@ -411,16 +436,82 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
     uint32_t acc_ph = 0;
     WorkItem it;
     for (int w = blockIdx.x; decode_work<BN>(a, w, n_tok_tiles, it); w += gridDim.x) {
-      if (!__all_sync(0xffffffffu, mbar_wait(&tfull[acc], acc_ph, abort_flag))) {
-        *abort_flag = 1;
-        atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_FULL);
-        break;
-      }
-      tc_fence_after();
       const int row = q * 32 + lane;               // row within the tile
       const int feat = it.feat0 + row;
       const bool feat_ok = feat < a.n_feat;
+      // FP8: the tile's result is built here, in registers: every 128-wide k block arrives as its own partial
+      // accumulator and is added with the product of the weight block's scale and the token's group scale
+      float accg[WFP8 ? BN : 1], accu[(WFP8 && DUAL) ? BN : 1];
+      if constexpr (WFP8) {
+#pragma unroll
+        for (int j = 0; j < BN; ++j) {
+          accg[j] = 0.f;
+          if (DUAL) accu[j] = 0.f;
+        }
+        const int kb0 = it.ks * kb_per_split;
+        const int kb1 = min(num_kb, kb0 + kb_per_split);
+        const long wblk = long((it.group * a.rows_per_group + it.feat0) >> 7) * num_kb;
+        const long wblk2 = long((it.group * a.rows_per_group + it.feat0 + a.dual_offset) >> 7) * num_kb;
+        bool failed = false;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!__all_sync(0xffffffffu, mbar_wait(&tfull[acc], acc_ph, abort_flag))) {
+            *abort_flag = 1;
+            atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_FULL);
+            failed = true;
+            break;
+          }
+          tc_fence_after();
+          const float sw = a.w_bscale[wblk + kb];
+          const float sw2 = DUAL ? a.w_bscale[wblk2 + kb] : 0.f;
+          const uint32_t tp = tmem_base + (uint32_t(q * 32) << 16) + acc * Cfg::ACC_COLS;
+#pragma unroll
+          for (int c = 0; c < BN; c += 32) {
+            uint32_t r[32], r2[32];
+            tmem_ld32(tp + c, r);
+            if (DUAL) tmem_ld32(tp + BN + c, r2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float xs = (c + j < it.ntok) ? __ldg(&a.x_bscale[long(it.tok0 + c + j) * num_kb + kb]) : 0.f;
+              accg[c + j] = fmaf(__uint_as_float(r[j]), sw * xs, accg[c + j]);
+              if (DUAL) accu[c + j] = fmaf(__uint_as_float(r2[j]), sw2 * xs, accu[c + j]);
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty[acc]);
+          if (++acc == NACC) { acc = 0; acc_ph ^= 1; }
+        }
+        if (failed) break;
+      } else {
+        if (!__all_sync(0xffffffffu, mbar_wait(&tfull[acc], acc_ph, abort_flag))) {
+          *abort_flag = 1;
+          atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_FULL);
+          break;
+        }
+        tc_fence_after();
+      }
       const uint32_t t0 = tmem_base + (uint32_t(q * 32) << 16) + acc * Cfg::ACC_COLS;
+      // 32 accumulator columns starting at column c: from TMEM, or (FP8) from the registers above
+      auto load_cols = [&](int c, uint32_t (&r)[32]) {
+        if constexpr (WFP8) {
+#pragma unroll
+          for (int cc = 0; cc < Cfg::ACC_COLS; cc += 32) {
+            if (cc == c) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                float v = 0.f;
+                if (cc < BN) v = accg[(cc + j) % BN];
+                else if constexpr (DUAL) v = accu[(cc + j) % BN];
+                r[j] = __float_as_uint(v);
+              }
+            }
+          }
+        } else {
+          tmem_ld32(t0 + c, r);
+          tmem_ld_wait();
+        }
+      };
 
       bool finalize = true;
       if (a.split_k > 1) {
@@ -429,8 +520,7 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
 #pragma unroll 1
         for (int c = 0; c < Cfg::ACC_COLS; c += 32) {
           uint32_t r[32];
-          tmem_ld32(t0 + c, r);
-          tmem_ld_wait();
+          load_cols(c, r);
 #pragma unroll
           for (int j = 0; j < 32; ++j) wsp[(c + j) * BM + row] = __uint_as_float(r[j]);
         }
@@ -465,13 +555,11 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
             }
           } else {
             uint32_t r[32];
-            tmem_ld32(t0 + c, r);
-            tmem_ld_wait();
+            load_cols(c, r);
 #pragma unroll
             for (int j = 0; j < 32; ++j) g[j] = __uint_as_float(r[j]);
             if (DUAL) {
-              tmem_ld32(t0 + BN + c, r);
-              tmem_ld_wait();
+              load_cols(BN + c, r);
 #pragma unroll
               for (int j = 0; j < 32; ++j) u[j] = __uint_as_float(r[j]);
             }
@@ -566,10 +654,12 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty[acc]);
-      if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+      if (!WFP8) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[acc]);
+        if (++acc == NACC) { acc = 0; acc_ph ^= 1; }
+      }
     }
   }
 
@@ -636,11 +726,11 @@ namespace {
 
 thread_local char g_gemm_err[512];
 
-template <int BN, bool DUAL, bool OUT_F32, bool WFP4 = false>
+template <int BN, bool DUAL, bool OUT_F32, bool WFP4 = false, bool WFP8 = false>
 int launch(const CUtensorMap* tmW, const CUtensorMap* tmX, const CUtensorMap* tmS, const WgemmArgs& a, int grid,
            cudaStream_t stream) {
-  using Cfg = WgemmCfg<BN, DUAL, WFP4>;
-  auto kfn = wgemm_kernel<BN, DUAL, OUT_F32, WFP4>;
+  using Cfg = WgemmCfg<BN, DUAL, WFP4, WFP8>;
+  auto kfn = wgemm_kernel<BN, DUAL, OUT_F32, WFP4, WFP8>;
   static bool attr_set = false;  // per instantiation
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
@@ -693,18 +783,30 @@ int wgemm_launch(const WgemmHost& h, cudaStream_t stream) {
   }
   const int bn = h.bn;
   const bool fp4 = h.w_scales != nullptr;
+  const bool fp8 = h.w_bscale != nullptr;
+  if (fp8) {
+    // e4m3 operands straight into the f8f6f4 MMA; scales per 128 x 128 weight block and per token and 128 columns
+    if (fp4 || !h.x_bscale || h.K % 128 != 0 || h.out_f32 || (bn != 32 && bn != 64) || h.rows_per_group % 128 != 0 ||
+        (h.dual && h.dual_offset % 128 != 0) || h.ldw % 16 != 0 || h.ldx % 16 != 0 || h.comm.enabled || h.head.enabled) {
+      snprintf(g_gemm_err, sizeof(g_gemm_err),
+               "wgemm: FP8 needs K %% 128 == 0, token tiles of 32 or 64, bf16 output, 128-row aligned groups");
+      return 1;
+    }
+  }
   if (fp4 && (h.K % 64 != 0 || h.out_f32 || (reinterpret_cast<uintptr_t>(h.w_scales) & 15) || (h.K / 16) % 16 != 0)) {
     snprintf(g_gemm_err, sizeof(g_gemm_err), "wgemm: NVFP4 weights need K %% 256 == 0, bf16 output, aligned scales");
     return 1;
   }
   // NVFP4: h.w = packed codes [rows, K / 2] bytes (row pitch h.ldw bytes), h.w_scales = e4m3 [rows, K / 16]
   const CUtensorMap* tmW = fp4 ? tmap_2d(h.w, uint64_t(h.w_rows), uint64_t(h.K / 2), uint64_t(h.ldw), BM, BK / 2, TM_U8, false)
+                           : fp8 ? tmap_2d(h.w, uint64_t(h.w_rows), uint64_t(h.K), uint64_t(h.ldw), BM, 128, TM_U8, true)
                                : tmap_2d(h.w, uint64_t(h.w_rows), uint64_t(h.K), uint64_t(h.ldw) * 2, BM, BK, TM_BF16, true);
   const CUtensorMap* tmS = fp4 ? tmap_2d(h.w_scales, uint64_t(h.w_rows), uint64_t(h.K / 16), uint64_t(h.K / 16), BM, 16,
                                          TM_U8, false)
                                : tmW;
   const CUtensorMap* tmX =
-      tmap_2d(h.x, uint64_t(h.x_rows), uint64_t(h.K), uint64_t(h.ldx) * 2, uint32_t(bn), BK, TM_BF16, true);
+      fp8 ? tmap_2d(h.x, uint64_t(h.x_rows), uint64_t(h.K), uint64_t(h.ldx), uint32_t(bn), 128, TM_U8, true)
+          : tmap_2d(h.x, uint64_t(h.x_rows), uint64_t(h.K), uint64_t(h.ldx) * 2, uint32_t(bn), BK, TM_BF16, true);
   if (!tmW || !tmX || !tmS) {
     snprintf(g_gemm_err, sizeof(g_gemm_err), "wgemm: %s", tmap_last_error());
     return 1;
@@ -717,6 +819,7 @@ int wgemm_launch(const WgemmHost& h, cudaStream_t stream) {
   a.comm = h.comm;
   a.head = h.head;
   a.w_gscale = h.w_gscale;
+  a.w_bscale = h.w_bscale; a.x_bscale = h.x_bscale;
   a.tile_group = h.tile_group; a.tile_tok0 = h.tile_tok0; a.tile_out0 = h.tile_out0; a.tile_ntok = h.tile_ntok; a.n_tiles_dev = h.n_tiles_dev;
   a.n_tok_tiles_max = h.n_tok_tiles_max;
   a.rows_per_group = h.rows_per_group; a.dual_offset = h.dual_offset;
@@ -727,7 +830,7 @@ int wgemm_launch(const WgemmHost& h, cudaStream_t stream) {
   a.vec_ok = (!h.out_f32 && h.n_feat % 8 == 0 && h.ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(h.out) & 15) == 0 &&
               (!h.residual || (h.ldr % 8 == 0 && (reinterpret_cast<uintptr_t>(h.residual) & 15) == 0)))
                  ? 1 : 0;
-  const int num_kb = (h.K + BK - 1) / BK;
+  const int num_kb = fp8 ? h.K / 128 : (h.K + BK - 1) / BK;
   if (a.split_k > num_kb) a.split_k = num_kb;
   while (a.split_k > 1 && (a.split_k - 1) * ((num_kb + a.split_k - 1) / a.split_k) >= num_kb) --a.split_k;
   if (a.split_k > 1 && (!a.ws || !a.counters)) {
@@ -742,6 +845,9 @@ int wgemm_launch(const WgemmHost& h, cudaStream_t stream) {
 #define LB_CASE(BN_, DUAL_)                                                                     \
   if (bn == BN_ && h.dual == DUAL_) {                                                           \
     if (fp4) return launch<BN_, DUAL_, false, true>(tmW, tmX, tmS, a, grid, stream);            \
+    if (fp8) {                                                                                  \
+      if constexpr (BN_ <= 64) return launch<BN_, DUAL_, false, false, true>(tmW, tmX, tmS, a, grid, stream); \
+    }                                                                                           \
     return h.out_f32 ? launch<BN_, DUAL_, true>(tmW, tmX, tmS, a, grid, stream)                 \
                      : launch<BN_, DUAL_, false>(tmW, tmX, tmS, a, grid, stream);               \
   }

@@ -68,6 +68,8 @@ struct WgemmArgs {
   WgemmCommTail comm;
   WgemmCommHead head;
   const float* w_gscale;          // NVFP4 weights: per-group (x2 for DUAL: gate, up) tensor scale, applied in the epilogue
+  const float* w_bscale;          // FP8 weights: fp32 scale per 128 x 128 block, [w_rows / 128, K / 128]
+  const float* x_bscale;          // FP8 activations: fp32 scale per row and 128 columns, [x_rows, K / 128]
 };
 
 // Host-side description of one launch.
@@ -91,6 +93,10 @@ struct WgemmHost {
   WgemmCommHead head;
   const void* w_scales;           // non-null: w holds NVFP4 codes [rows, K/2] bytes, this the e4m3 block scales [rows, K/16]
   const float* w_gscale;
+  // non-null: block-scaled FP8. w and x hold e4m3 bytes ([w_rows, K] / [x_rows, K], pitches ldw / ldx in bytes),
+  // w_bscale the fp32 weight scales per 128 x 128 block, x_bscale the fp32 activation scales per row and 128 columns
+  const float* w_bscale;
+  const float* x_bscale;
 };
 
 int wgemm_launch(const WgemmHost& h, cudaStream_t stream);

@@ -257,6 +257,85 @@ def _pick_split_k(n_tok_tiles: int, feat_tiles: int, K: int) -> int:
     return max(1, s)
 
 
+class Fp8Weight:
+    """Block-scaled FP8 weight kept in its 8-bit encoding: ``data`` uint8 e4m3 bit patterns [..., rows, K] and
+    ``scale`` float32 per 128 x 128 block [..., ceil(rows / 128), K / 128] (the layout of FP8 checkpoints with
+    ``weight_block_size = [128, 128]``; ``weight_scale_inv`` is this scale). The GEMM feeds the bytes straight to
+    the e4m3 tensor-core instruction, with the activations quantised per token and 128 columns, and adds each
+    128-wide k block with its two scales in fp32 (``csrc/gemm_sm100.cu``, FP8 mode): a decode step reads one byte
+    per weight instead of two."""
+    __slots__ = ("data", "scale")
+
+    def __init__(self, data, scale):
+        self.data, self.scale = data.view(torch.uint8), scale.float().contiguous()
+
+    @property
+    def shape(self):
+        return tuple(self.data.shape)
+
+    @property
+    def device(self):
+        return self.data.device
+
+    def dim(self):
+        return self.data.dim()
+
+    def view2d(self):
+        return self.data.reshape(-1, self.data.shape[-1]), self.scale.reshape(-1, self.scale.shape[-1])
+
+    @classmethod
+    def quantize(cls, w: torch.Tensor):
+        """Device-side encoding of a CUDA bf16 weight [..., rows, K] (rows a multiple of 128 when stacked)."""
+        C = ext()
+        rows, K = w.shape[-2], w.shape[-1]
+        if K % 128 or (w.dim() > 2 and rows % 128):
+            raise ValueError("FP8 block scaling needs K % 128 == 0 and 128-row aligned stacks")
+        flat = w.reshape(-1, K).contiguous()
+        data = torch.empty(flat.shape, dtype=torch.uint8, device=w.device)
+        scale = torch.empty((flat.shape[0] + 127) // 128, K // 128, dtype=torch.float32, device=w.device)
+        C.fp8_block_quant(flat, 128, 128, data, scale)
+        lead = tuple(w.shape[:-2])
+        return cls(data.view(*lead, rows, K), scale.view(*lead, (rows + 127) // 128, K // 128) if lead else scale)
+
+    def dequantize(self, dtype=torch.bfloat16):
+        C = ext()
+        d2, s2 = self.view2d()
+        out = torch.empty(d2.shape, dtype=torch.bfloat16, device=d2.device)
+        C.fp8_block_dequant(d2.contiguous(), s2.contiguous(), 128, 128, out)
+        return out.view(self.shape).to(dtype)
+
+
+def fp8_quant_act(x, out=None, scale=None):
+    """bf16 activations [T, K] -> (e4m3 bytes [T, K], fp32 scale per row and 128 columns [T, K / 128])."""
+    C = ext()
+    T, K = x.shape
+    if out is None:
+        out = torch.empty(T, K, dtype=torch.uint8, device=x.device)
+        scale = torch.empty(T, K // 128, dtype=torch.float32, device=x.device)
+    C.fp8_block_quant(x, 1, 128, out, scale)
+    return out, scale
+
+
+def _linear_fp8(x, w: "Fp8Weight", residual, out, dual: bool, n_feat: int):
+    C = ext()
+    T, K = x.shape
+    ws = Workspace.get(x.device)
+    x8, xs = fp8_quant_act(x)
+    bn = 32 if T <= 32 else 64
+    n_tt = (T + bn - 1) // bn
+    ft = (n_feat + 127) // 128
+    sk = _pick_split_k(n_tt, ft, K)
+    if sk > 1:
+        need = C.wgemm_workspace_floats(bn, dual, n_tt, ft, sk)
+        if need > ws.splitk.numel() or n_tt * ft > ws.counters.numel():
+            sk = 1
+    w2, s2 = w.view2d()
+    C.wgemm_fp8(w2, s2, x8, xs, out, residual, None, None, n_feat, dual, n_feat if dual else 0, bn, sk,
+                ws.splitk if sk > 1 else None, ws.counters if sk > 1 else None, ws.status, None, None, None, None, 0, 0,
+                T, None)
+    return out
+
+
 def linear(x, w, residual=None, out=None, out_dtype=torch.bfloat16, split_k: Optional[int] = None, bn=None):
     """out[T, N] = x[T, K] @ w[N, K]^T (+ residual)."""
     C = ext()
@@ -269,6 +348,10 @@ def linear(x, w, residual=None, out=None, out_dtype=torch.bfloat16, split_k: Opt
         out = torch.empty(T, N, dtype=out_dtype, device=x.device)
     if T == 0:
         return out
+    if isinstance(w, Fp8Weight):
+        if out_dtype != torch.bfloat16:
+            raise ValueError("FP8 weights produce bf16 outputs")
+        return _linear_fp8(x, w, residual, out, False, N)
     ws = Workspace.get(x.device)
     bn = bn or pick_bn(T, False)
     n_tt = (T + bn - 1) // bn
@@ -292,6 +375,8 @@ def gate_up_act(x, w_gate_up, n_ff: int, out=None, bn=None, split_k: Optional[in
         out = torch.empty(T, n_ff, dtype=torch.bfloat16, device=x.device)
     if T == 0:
         return out
+    if isinstance(w_gate_up, Fp8Weight):
+        return _linear_fp8(x, w_gate_up, None, out, True, n_ff)
     ws = Workspace.get(x.device)
     bn = bn or pick_bn(T, True)
     n_tt = (T + bn - 1) // bn
@@ -541,6 +626,9 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[Moe
     k = ids.shape[1]
     E_local = w_gate_up.shape[0]
     ws = Workspace.get(x.device)
+    if isinstance(w_gate_up, Fp8Weight):
+        return _moe_experts_fp8(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, shared, shared_gate, residual, out, norm,
+                                routing)
     # expert weights as 2-D operands (+ NVFP4 block scales / tensor scales when kept in 4 bits)
     if isinstance(w_gate_up, QWeight):
         (gu2, gu_sc), gu_gs = w_gate_up.view2d(), w_gate_up.gscale
@@ -613,6 +701,65 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[Moe
     normed = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
     C.moe_combine(plan.y_pairs, ids, e_lo, e_lo + E_local, shared, shared_gate, residual, out, norm[0], norm[1],
                   norm[2], normed)
+    return out, normed
+
+
+def _moe_experts_fp8(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, shared, shared_gate, residual, out, norm, routing):
+    """Routed experts with block-scaled FP8 weights: the same two grouped GEMMs in FP8 mode; activations (the
+    layer input and the SwiGLU output) are quantised per row and 128 columns before each of them."""
+    C = ext()
+    T, H = x.shape
+    k = ids.shape[1]
+    E_local = w_gate_up.shape[0]
+    ws = Workspace.get(x.device)
+    gu2, gu_s = w_gate_up.view2d()
+    dn2, dn_s = w_down.view2d()
+    P = T * k
+    if out is None:
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+    dense = (routing is not None and routing.dense is not None and routing.n_local == E_local
+             and routing.e_lo == e_lo and routing.ids is ids and TUNE["dense_route"])
+    if dense:
+        dr = routing.dense
+        if dr.h_all is None or dr.h_all.shape[1] != n_ff:
+            dr.h_all = torch.zeros(E_local * dr.bn, n_ff, dtype=torch.bfloat16, device=x.device)
+        if dr.y_pairs is None or dr.y_pairs.shape[0] < P or dr.y_pairs.shape[1] != H:
+            dr.y_pairs = torch.zeros(max(P, 64 * k), H, dtype=torch.bfloat16, device=x.device)
+        x8, xs = fp8_quant_act(x)
+        C.wgemm_fp8(gu2, gu_s, x8, xs, dr.h_all, None, None, None, n_ff, True, n_ff, dr.bn, 1, None, None, ws.status,
+                    dr.tile_group, dr.zeros, dr.tile_ntok, dr.meta, E_local, 2 * n_ff, 0, dr.slot_base)
+        h8, hs = fp8_quant_act(dr.h_all)
+        C.wgemm_fp8(dn2, dn_s, h8, hs, dr.y_pairs, None, dr.tok_scale, dr.out_rows, H, False, 0, dr.bn, 1, None, None,
+                    ws.status, dr.tile_group, dr.slot_base, dr.tile_ntok, dr.meta, E_local, H, 0, None)
+        y = dr.y_pairs[:P]
+    else:
+        bn = 32 if P <= 32 * E_local else 64
+        key = ("moe_plan", T, k, E_local, bn, H, n_ff)
+        plan = ws._cache.get(key)
+        if plan is None:
+            plan = MoePlan(T, k, E_local, bn, x.device)
+            ws._cache[key] = plan
+        if (plan.x_sorted is None or plan.x_sorted.shape[0] < P + bn or plan.x_sorted.shape[1] != H
+                or plan.h_sorted.shape[1] != n_ff):
+            plan.x_sorted = torch.zeros(P + bn, H, dtype=torch.bfloat16, device=x.device)
+            plan.h_sorted = torch.zeros(P + bn, n_ff, dtype=torch.bfloat16, device=x.device)
+            plan.y_pairs = torch.zeros(P, H, dtype=torch.bfloat16, device=x.device)
+        C.moe_plan(ids, wts, e_lo, E_local, bn, plan.counts, plan.offsets, plan.sorted_token, plan.sorted_pair,
+                   plan.sorted_w, plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta)
+        C.gather_rows(x, plan.sorted_token, plan.meta[1:2], plan.x_sorted[:P])
+        x8, xs = fp8_quant_act(plan.x_sorted)
+        C.wgemm_fp8(gu2, gu_s, x8, xs, plan.h_sorted, None, None, None, n_ff, True, n_ff, bn, 1, None, None, ws.status,
+                    plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta, plan.max_tiles, 2 * n_ff, 0, None)
+        h8, hs = fp8_quant_act(plan.h_sorted)
+        C.wgemm_fp8(dn2, dn_s, h8, hs, plan.y_pairs, None, plan.sorted_w, plan.sorted_pair, H, False, 0, bn, 1, None,
+                    None, ws.status, plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta, plan.max_tiles, H, 0,
+                    None)
+        y = plan.y_pairs
+    if norm is None:
+        C.moe_combine(y, ids, e_lo, e_lo + E_local, shared, shared_gate, residual, out, None, 0.0, 0.0, None)
+        return out
+    normed = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+    C.moe_combine(y, ids, e_lo, e_lo + E_local, shared, shared_gate, residual, out, norm[0], norm[1], norm[2], normed)
     return out, normed
 
 

@@ -551,3 +551,58 @@ def test_mla_prep():
     assert rows[2].abs().sum() == 0                       # the padding row wrote nothing
     close(q_abs[..., 512:], qpe, 2e-2, 2e-2)
     assert q_abs[..., :512].abs().sum() == 0
+
+
+def _fp8_ref_linear(x, wq):
+    """fp32 product of the de-quantised operands the FP8 GEMM sees (activations per row and 128 columns)."""
+    x8, xs = sm().fp8_quant_act(x)
+    xd = x8.view(torch.float8_e4m3fn).float() * xs.repeat_interleave(128, dim=1)
+    d2, s2 = wq.view2d()
+    wd = d2.view(torch.float8_e4m3fn).float() * \
+        s2.repeat_interleave(128, dim=0)[:d2.shape[0]].repeat_interleave(128, dim=1)
+    return xd, wd
+
+
+@pytest.mark.parametrize("T,N,K", [(16, 5120, 2048), (1, 256, 128), (40, 384, 256), (100, 640, 1024), (33, 200, 384)])
+def test_fp8_block_scaled_linear(T, N, K):
+    """e4m3 weights with 128 x 128 block scales and e4m3 activations with 1 x 128 scales on the f8f6f4 tensor-core
+    path, each 128-wide k block promoted into fp32 with its two scales (split-K included for the skinny shapes)."""
+    torch.manual_seed(T + N)
+    x = rnd(T, K)
+    w = rnd(N, K, scale=0.05)
+    res = rnd(T, N)
+    wq = sm().Fp8Weight.quantize(w)
+    out = sm().linear(x, wq, residual=res)
+    status_ok()
+    xd, wd = _fp8_ref_linear(x, wq)
+    want = xd @ wd.t() + res.float()
+    close(out, want, 1e-2, 1e-2)
+    # and the quantisation itself stays near the bf16 product
+    ref_full = x.float() @ w.float().t() + res.float()
+    assert (out.float() - ref_full).abs().max() < 0.08 * ref_full.abs().max() + 0.05
+
+
+def test_fp8_gate_up_and_experts():
+    torch.manual_seed(11)
+    T, H, F, E, k = 16, 512, 256, 8, 2
+    x = rnd(T, H)
+    wgu = rnd(2 * F, H, scale=0.05)
+    q = sm().Fp8Weight.quantize(wgu)
+    out = sm().gate_up_act(x, q, F)
+    status_ok()
+    xd, wd = _fp8_ref_linear(x, q)
+    hh = xd @ wd.t()
+    close(out, torch.nn.functional.silu(hh[:, :F]) * hh[:, F:], 2e-2, 2e-2)
+    # routed experts: decode-sized step (dense routing tables) and a larger step (plan + gather)
+    gu = rnd(E, 2 * F, H, scale=0.05)
+    dn = rnd(E, H, F, scale=0.05)
+    gq, dq = sm().Fp8Weight.quantize(gu), sm().Fp8Weight.quantize(dn)
+    w_r = rnd(E, H, scale=0.1)
+    for T2 in (16, 150):
+        x2 = rnd(T2, H)
+        routing = sm().router(x2, w_r, k)
+        y = sm().moe_experts(x2, routing.ids, routing.wts, gq, dq, F, routing=routing)
+        status_ok()
+        want = ref.moe_experts(x2, routing.ids, routing.wts, gq.dequantize(), dq.dequantize(), F)
+        err = (y.float() - want.float()).abs().max().item()
+        assert err < 0.06 * want.abs().max().item() + 0.03, (T2, err)
