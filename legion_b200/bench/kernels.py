@@ -209,6 +209,36 @@ def bench_mla(rows):
         print(rows[-1], flush=True)
 
 
+def bench_moe_fp8(rows):
+    """Routed experts of a 30B-A3B-shaped layer at 16 tokens, bf16 against block-scaled FP8 weights (graph-replayed),
+    plus the qkv-sized dense projection."""
+    from legion_b200.ops import sm100
+    from legion_b200.ops.sm100 import Fp8Weight
+    hbm, tf, src = peaks()
+    T, H, E, k, F = 16, 2048, 128, 8, 768
+    dev = "cuda"
+    x = torch.randn(T, H, device=dev).bfloat16()
+    w_r = (torch.randn(E, H, device=dev) * 0.02).bfloat16()
+    routing = sm100.router(x, w_r, k)
+    n_act = int(torch.unique(routing.ids).numel())
+    gu = (torch.randn(E, 2 * F, H, device=dev) * 0.02).bfloat16()
+    dn = (torch.randn(E, H, F, device=dev) * 0.02).bfloat16()
+    gq, dq = Fp8Weight.quantize(gu), Fp8Weight.quantize(dn)
+    for name, a, b, bytes_per in (("bf16", gu, dn, 2), ("fp8", gq, dq, 1)):
+        ms = timeit_graph(lambda: sm100.moe_experts(x, routing.ids, routing.wts, a, b, F, routing=routing))
+        byts = n_act * 3 * H * F * bytes_per
+        rows.append(dict(kernel="moe_experts_" + name, T=T, active_experts=n_act, us=ms * 1e3, gbs=byts / ms / 1e6,
+                         frac_hbm=byts / ms / 1e6 / hbm, peaks=src))
+        print(rows[-1], flush=True)
+    wq = (torch.randn(5120, H, device=dev) * 0.02).bfloat16()
+    wq8 = Fp8Weight.quantize(wq)
+    for name, w, bytes_per in (("bf16", wq, 2), ("fp8", wq8, 1)):
+        ms = timeit_graph(lambda: sm100.linear(x, w))
+        byts = wq.numel() * bytes_per
+        rows.append(dict(kernel="linear_5120x2048_" + name, T=T, us=ms * 1e3, gbs=byts / ms / 1e6, peaks=src))
+        print(rows[-1], flush=True)
+
+
 def bench_moe_nvfp4(rows):
     """Routed experts of a 30B-A3B-shaped layer at 16 tokens with the weights kept in NVFP4 (graph-replayed)."""
     from legion_b200.ops import sm100
@@ -345,7 +375,7 @@ def main(argv=None):
     if a.gemm:
         CASE["gemm"] = [tuple(int(y) for y in x.split("x")) for x in a.gemm.split(",")]
     rows = []
-    table = {"gdn": bench_gdn, "mla": bench_mla, "moe_nvfp4": bench_moe_nvfp4, "layer_parts": bench_layer_parts, "decode_pages": bench_decode_pages, "gemm": bench_gemm, "moe": bench_moe, "decode_attn": bench_decode_attn, "prefill_attn": bench_prefill_attn}
+    table = {"gdn": bench_gdn, "moe_fp8": bench_moe_fp8, "mla": bench_mla, "moe_nvfp4": bench_moe_nvfp4, "layer_parts": bench_layer_parts, "decode_pages": bench_decode_pages, "gemm": bench_gemm, "moe": bench_moe, "decode_attn": bench_decode_attn, "prefill_attn": bench_prefill_attn}
     for name in a.only.split(","):
         table[name](rows)
     from legion_b200.ops.sm100 import Workspace

@@ -76,8 +76,11 @@ def _add_engine_args(ap: argparse.ArgumentParser):
     g.add_argument("--pipeline-micro", type=int, default=2048, help="tokens per micro-chunk of a pipelined prompt")
     g.add_argument("--experts", choices=["auto", "device", "host", "cache"], default="auto")
     g.add_argument("--expert-cache-gib", type=float, default=0.0)
-    g.add_argument("--expert-weights", choices=["bf16", "nvfp4"], default="bf16",
-                   help="nvfp4: keep the routed experts in 4 bits in HBM (expanded inside the grouped GEMM)")
+    g.add_argument("--expert-weights", choices=["bf16", "nvfp4", "fp8"], default="bf16",
+                   help="nvfp4: keep the routed experts in 4 bits in HBM (expanded inside the grouped GEMM); "
+                        "fp8: block-scaled e4m3 experts on the FP8 tensor-core path")
+    g.add_argument("--weights", choices=["bf16", "fp8"], default="bf16",
+                   help="fp8: re-encode all projection weights to block-scaled e4m3 (128 x 128 scales) after loading")
     g = ap.add_argument_group("sampling defaults")
     g.add_argument("--temp", type=float, default=None)
     g.add_argument("--top-p", type=float, default=None)
@@ -157,6 +160,9 @@ def build_engine_from_args(a, start: bool = True):
     if getattr(a, "expert_weights", "bf16") == "nvfp4" and on_gpu and cfg.n_expert:
         saved = model.quantize_experts_nvfp4()
         logging.getLogger("legion").info("routed experts re-encoded to NVFP4: %.1f GiB of HBM saved", saved / 2 ** 30)
+    if on_gpu and (getattr(a, "weights", "bf16") == "fp8" or getattr(a, "expert_weights", "bf16") == "fp8"):
+        saved = model.quantize_weights_fp8(experts_only=getattr(a, "weights", "bf16") != "fp8")
+        logging.getLogger("legion").info("weights re-encoded to block-scaled FP8: %.1f GiB of HBM saved", saved / 2 ** 30)
     if a.experts in ("cache", "host") and cfg.n_expert:
         from ..residency.experts import slots_for_budget
         slots = cfg.top_k * ec.max_seqs if a.experts == "host" else slots_for_budget(cfg, a.expert_cache_gib or 8.0)

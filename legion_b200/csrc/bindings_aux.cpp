@@ -215,6 +215,16 @@ void bind_quant(pybind11::module_& m) {
                                            reinterpret_cast<uint8_t*>(out.data_ptr()), scale.data_ptr<float>(),
                                            cur_stream()) == 0, "fp8_block_quant failed");
   });
+  m.def("fp8_act_quant", [](const Tensor& x, Tensor& out, Tensor& scale) {
+    TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1 && out.is_contiguous() &&
+                    out.element_size() == 1 && out.numel() == x.numel() && scale.scalar_type() == at::kFloat &&
+                    scale.is_contiguous() && scale.numel() == x.size(0) * (x.size(1) / 128),
+                "fp8_act_quant: x bf16 [T, K], out bytes [T, K], scale f32 [T, K / 128]");
+    c10::cuda::CUDAGuard guard(x.device());
+    TORCH_CHECK(lb::fp8_act_quant_launch(x.data_ptr(), x.stride(0), x.size(0), x.size(1),
+                                         reinterpret_cast<uint8_t*>(out.data_ptr()), scale.data_ptr<float>(),
+                                         cur_stream()) == 0, "fp8_act_quant: K must be a multiple of 128, rows 8-byte aligned");
+  });
   m.def("gguf_dequant", [](const Tensor& raw, int64_t ggml_type, Tensor& out) {
     TORCH_CHECK(raw.scalar_type() == at::kByte && raw.is_contiguous() && out.scalar_type() == at::kBFloat16 &&
                     out.is_contiguous(), "gguf_dequant: raw uint8 -> bf16");

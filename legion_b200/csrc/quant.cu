@@ -159,6 +159,40 @@ int fp8_block_quant_launch(const void* x, long ldx, long rows, long K, int br, i
   return cudaGetLastError() != cudaSuccess;
 }
 
+// Activation quantisation to e4m3 with one fp32 scale per row and 128 columns: one warp per group (lane = 4
+// consecutive elements, one 8-byte load and one 4-byte store), eight groups per CTA.
+__global__ void __launch_bounds__(256)
+fp8_act_quant_kernel(const __nv_bfloat16* __restrict__ x, long ldx, long rows, int groups_per_row,
+                     uint8_t* __restrict__ out, float* __restrict__ scale) {
+  const long g = long(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (g >= rows * groups_per_row) return;
+  const int lane = threadIdx.x & 31;
+  const long r = g / groups_per_row;
+  const int kb = int(g % groups_per_row);
+  const uint2 raw = *reinterpret_cast<const uint2*>(x + r * ldx + kb * 128 + lane * 4);
+  const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+  const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  const float2 a = __bfloat1622float2(p0), b = __bfloat1622float2(p1);
+  float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float sc = amax > 0.f ? amax / 448.f : 1.f;
+  const float inv = 1.f / sc;
+  const uint32_t q = uint32_t(float_to_e4m3(a.x * inv)) | (uint32_t(float_to_e4m3(a.y * inv)) << 8) |
+                     (uint32_t(float_to_e4m3(b.x * inv)) << 16) | (uint32_t(float_to_e4m3(b.y * inv)) << 24);
+  *reinterpret_cast<uint32_t*>(out + r * (long(groups_per_row) * 128) + kb * 128 + lane * 4) = q;
+  if (lane == 0) scale[g] = sc;
+}
+
+int fp8_act_quant_launch(const void* x, long ldx, long rows, long K, uint8_t* out, float* scale, cudaStream_t s) {
+  if (rows <= 0 || K <= 0) return 0;
+  if (K % 128 != 0 || ldx % 4 != 0 || (reinterpret_cast<uintptr_t>(x) & 7)) return 1;
+  const long groups = rows * (K / 128);
+  fp8_act_quant_kernel<<<unsigned((groups + 7) / 8), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), ldx, rows,
+                                                                  int(K / 128), out, scale);
+  return cudaGetLastError() != cudaSuccess;
+}
+
 // Deterministic N(0, std) weights from a counter-based generator (Box-Muller on two hashed words).
 __device__ __forceinline__ uint32_t hash32(uint64_t x) {
   x ^= x >> 33; x *= 0xff51afd7ed558ccdull; x ^= x >> 33; x *= 0xc4ceb9fe1a85ec53ull; x ^= x >> 33;

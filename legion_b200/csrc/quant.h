@@ -13,6 +13,7 @@ int fp8_block_dequant_launch(const uint8_t* w, const float* scale, long rows, lo
                              cudaStream_t s);
 int fp8_block_quant_launch(const void* x, long ldx, long rows, long K, int br, int bk, uint8_t* out, float* scale,
                            cudaStream_t s);
+int fp8_act_quant_launch(const void* x, long ldx, long rows, long K, uint8_t* out, float* scale, cudaStream_t s);
 int gguf_dequant_launch(const void* raw, int ggml_type, long n_elements, void* out_bf16, cudaStream_t s);
 int randn_bf16_launch(void* out, long n, float stdv, uint64_t seed, cudaStream_t s);
 

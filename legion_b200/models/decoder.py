@@ -193,6 +193,34 @@ class Decoder:
             saved += before - before * 9 // 32
         return saved
 
+    FP8_LEAVES = ("attn.qkv", "attn.o", "mlp.gate_up", "mlp.down", "moe.gate_up", "moe.down", "moe.sh_gate_up",
+                  "moe.sh_down", "mla.q_a", "mla.q_b", "mla.q", "mla.kv_a", "mla.o", "gdn.in_qkv", "gdn.in_z", "gdn.out")
+
+    def quantize_weights_fp8(self, experts_only: bool = False) -> int:
+        """Re-encodes the projection weights (routed experts, dense and shared FFNs, attention / latent-attention /
+        linear-attention projections) to block-scaled FP8 in place: e4m3 with one fp32 scale per 128 x 128 block,
+        the encoding of FP8 checkpoints. The GEMMs then run on the e4m3 tensor-core path with activations
+        quantised per token and 128 columns (``ops.sm100.Fp8Weight``). Embedding, head, router, norms and the small
+        gate projections stay as they are. Returns the number of bytes saved. GPU only."""
+        from ..ops.sm100 import Fp8Weight
+        saved = 0
+        for name in list(self.w):
+            t = self.w[name]
+            leaf = name.split(".", 1)[1] if "." in name else name
+            if leaf not in self.FP8_LEAVES or not isinstance(t, torch.Tensor) or t.dtype != torch.bfloat16:
+                continue
+            if experts_only and leaf not in ("moe.gate_up", "moe.down"):
+                continue
+            rows, K = t.shape[-2], t.shape[-1]
+            if K % 128 or rows % 128:
+                continue
+            if leaf.endswith("gate_up") and (rows // 2) % 128:
+                continue                      # the gate and the up half must start on block boundaries
+            self.w[name] = Fp8Weight.quantize(t)
+            saved += t.numel()
+            del t
+        return saved
+
     # ------------------------------------------------------------------ blocks
     def _attn(self, p: str, il: int, x, b: StepBatch, kv: KvCache, window: int, rope: bool = True):
         cfg, w = self.cfg, self.w

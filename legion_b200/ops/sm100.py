@@ -312,7 +312,7 @@ def fp8_quant_act(x, out=None, scale=None):
     if out is None:
         out = torch.empty(T, K, dtype=torch.uint8, device=x.device)
         scale = torch.empty(T, K // 128, dtype=torch.float32, device=x.device)
-    C.fp8_block_quant(x, 1, 128, out, scale)
+    C.fp8_act_quant(x, out, scale)
     return out, scale
 
 

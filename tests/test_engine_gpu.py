@@ -97,3 +97,45 @@ def test_engine_with_nvfp4_experts():
     eng_g.shutdown()
     assert len(a.token_ids) == 12 and a.token_ids == b2.token_ids and replays > 0
     assert Workspace.get("cuda").check() == 0
+
+
+def test_engine_with_fp8_weights():
+    """All projection weights re-encoded to block-scaled FP8 (e4m3, 128 x 128 scales). Dense model: first-step
+    logits stay close to the bf16 model's (weights and activations both lose precision; a routed model would also
+    flip expert choices, so closeness is checked without routing). MoE model: the engine generates through CUDA
+    graphs on the FP8 tensor-core path, reproducibly."""
+    from legion_b200.config import ModelConfig
+    from legion_b200.engine.lm import EngineConfig, build_engine
+    from legion_b200.engine.types import GenerateRequest, SamplingParams
+    from legion_b200.models.weights import random_weights
+    from legion_b200.ops.sm100 import Fp8Weight, Workspace
+    ecfg = dict(ctx_size=512, max_seqs=2, block_size=64, prefill_chunk=256, prefix_cache=False)
+    prompt = list(range(3, 150))
+    dense = ModelConfig(arch="qwen3", n_layer=2, hidden=512, vocab=2048, n_head=8, n_kv_head=2, head_dim=128,
+                        dense_ff=1024)
+    w = random_weights(dense, "cuda", torch.bfloat16, seed=0, std=0.05)
+    eng_q = build_engine(dense, weights=dict(w), device="cuda", engine_cfg=EngineConfig(**ecfg), start=False)
+    assert eng_q.model.quantize_weights_fp8() > 0
+    assert sum(isinstance(v, Fp8Weight) for v in eng_q.model.w.values()) == 4 * dense.n_layer
+    eng_d = build_engine(dense, weights=dict(w), device="cuda", engine_cfg=EngineConfig(**ecfg), start=False)
+    outs = []
+    for eng in (eng_q, eng_d):
+        seq = eng.prepare(GenerateRequest(prompt_tokens=prompt, sampling=SamplingParams(max_tokens=4, ignore_eos=True)))
+        eng.waiting.push(seq)
+        eng._admit()
+        b = eng.build_batch([(seq, 0, len(prompt))])
+        outs.append(eng.model.forward(b, eng.kv, eng.states).logits.float().cpu())
+    err = (outs[0] - outs[1]).abs().max().item()
+    ref = outs[1].abs().max().item()
+    assert err < 0.15 * ref + 0.1, (err, ref)
+    moe = ModelConfig(arch="qwen3moe", n_layer=2, hidden=512, vocab=2048, n_head=8, n_kv_head=2, head_dim=128,
+                      n_expert=8, top_k=2, expert_ff=256)
+    eng_g = build_engine(moe, weights=random_weights(moe, "cuda", torch.bfloat16, seed=0, std=0.05), device="cuda",
+                         engine_cfg=EngineConfig(**ecfg))
+    eng_g.model.quantize_weights_fp8()
+    a = eng_g.generate_text(tokens=prompt, max_tokens=12, ignore_eos=True)
+    b2 = eng_g.generate_text(tokens=prompt, max_tokens=12, ignore_eos=True)
+    replays = eng_g._graphs.replays
+    eng_g.shutdown()
+    assert len(a.token_ids) == 12 and a.token_ids == b2.token_ids and replays > 0
+    assert Workspace.get("cuda").check() == 0
