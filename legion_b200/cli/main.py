@@ -79,8 +79,10 @@ def _add_engine_args(ap: argparse.ArgumentParser):
     g.add_argument("--expert-weights", choices=["bf16", "nvfp4", "fp8"], default="bf16",
                    help="nvfp4: keep the routed experts in 4 bits in HBM (expanded inside the grouped GEMM); "
                         "fp8: block-scaled e4m3 experts on the FP8 tensor-core path")
-    g.add_argument("--weights", choices=["bf16", "fp8"], default="bf16",
-                   help="fp8: re-encode all projection weights to block-scaled e4m3 (128 x 128 scales) after loading")
+    g.add_argument("--weights", choices=["auto", "bf16", "fp8"], default="auto",
+                   help="fp8: keep all projection weights in block-scaled e4m3 (128 x 128 scales) in HBM and run them "
+                        "on the FP8 tensor-core path; auto: fp8 for checkpoints shipped in block-scaled FP8 (the "
+                        "re-encoding of their expanded blocks reproduces the shipped bytes), bf16 otherwise")
     g = ap.add_argument_group("sampling defaults")
     g.add_argument("--temp", type=float, default=None)
     g.add_argument("--top-p", type=float, default=None)
@@ -160,8 +162,11 @@ def build_engine_from_args(a, start: bool = True):
     if getattr(a, "expert_weights", "bf16") == "nvfp4" and on_gpu and cfg.n_expert:
         saved = model.quantize_experts_nvfp4()
         logging.getLogger("legion").info("routed experts re-encoded to NVFP4: %.1f GiB of HBM saved", saved / 2 ** 30)
-    if on_gpu and (getattr(a, "weights", "bf16") == "fp8" or getattr(a, "expert_weights", "bf16") == "fp8"):
-        saved = model.quantize_weights_fp8(experts_only=getattr(a, "weights", "bf16") != "fp8")
+    wmode = getattr(a, "weights", "auto")
+    if wmode == "auto":
+        wmode = "fp8" if info.get("quant_method") == "fp8_block" else "bf16"
+    if on_gpu and (wmode == "fp8" or getattr(a, "expert_weights", "bf16") == "fp8"):
+        saved = model.quantize_weights_fp8(experts_only=wmode != "fp8")
         logging.getLogger("legion").info("weights re-encoded to block-scaled FP8: %.1f GiB of HBM saved", saved / 2 ** 30)
     if a.experts in ("cache", "host") and cfg.n_expert:
         from ..residency.experts import slots_for_budget
