@@ -309,6 +309,73 @@ static void pack_decode(py::array_t<int32_t, py::array::c_style> buf, int B, int
   }
 }
 
+// Byte-pair merges of one pre-tokenised word (byte-to-unicode mapped text): lowest-rank adjacent pair first, until no
+// pair has a rank; pieces that are not in the vocabulary fall back to their single symbols.
+// Same procedure as BpeTokenizer._bpe in legion_b200/loaders/tokenizer.py (reference: src/tokenizer/bpe.rs).
+class BpeMerger {
+ public:
+  BpeMerger(const std::vector<std::string>& tokens, const std::vector<std::pair<std::string, std::string>>& merges) {
+    vocab_.reserve(tokens.size() * 2);
+    for (size_t i = 0; i < tokens.size(); ++i) vocab_.emplace(tokens[i], int(i));
+    ranks_.reserve(merges.size() * 2);
+    for (size_t r = 0; r < merges.size(); ++r) ranks_.emplace(key(merges[r].first, merges[r].second), int(r));
+  }
+
+  std::vector<int> encode_word(const std::string& word) const {
+    std::vector<std::string> parts;
+    for (size_t i = 0; i < word.size();) {        // split into UTF-8 symbols
+      const unsigned char c = static_cast<unsigned char>(word[i]);
+      const size_t n = c < 0x80 ? 1 : (c >> 5) == 6 ? 2 : (c >> 4) == 14 ? 3 : 4;
+      parts.emplace_back(word.substr(i, n));
+      i += n;
+    }
+    while (parts.size() > 1) {
+      int best = -1;
+      size_t bi = 0;
+      for (size_t i = 0; i + 1 < parts.size(); ++i) {
+        auto it = ranks_.find(key(parts[i], parts[i + 1]));
+        if (it != ranks_.end() && (best < 0 || it->second < best)) { best = it->second; bi = i; }
+      }
+      if (best < 0) break;
+      parts[bi] += parts[bi + 1];
+      parts.erase(parts.begin() + long(bi) + 1);
+    }
+    std::vector<int> ids;
+    for (const auto& p : parts) {
+      auto it = vocab_.find(p);
+      if (it != vocab_.end()) { ids.push_back(it->second); continue; }
+      for (size_t i = 0; i < p.size();) {
+        const unsigned char c = static_cast<unsigned char>(p[i]);
+        const size_t n = c < 0x80 ? 1 : (c >> 5) == 6 ? 2 : (c >> 4) == 14 ? 3 : 4;
+        auto s = vocab_.find(p.substr(i, n));
+        if (s != vocab_.end()) ids.push_back(s->second);
+        i += n;
+      }
+    }
+    return ids;
+  }
+
+  std::vector<int> encode_words(const std::vector<std::string>& words) const {
+    std::vector<int> out;
+    for (const auto& w : words) {
+      auto ids = encode_word(w);
+      out.insert(out.end(), ids.begin(), ids.end());
+    }
+    return out;
+  }
+
+ private:
+  static std::string key(const std::string& a, const std::string& b) {
+    std::string k;
+    k.reserve(a.size() + b.size() + 1);
+    k += a;
+    k += ' ';            // byte-to-unicode mapped pieces never contain a plain space
+    k += b;
+    return k;
+  }
+  std::unordered_map<std::string, int> vocab_, ranks_;
+};
+
 PYBIND11_MODULE(_host, m) {
   m.doc() = "legion_b200 native host runtime (KV block pool, radix prefix cache, step packing)";
   m.def("set_out_of_blocks", [](py::object t) { oob_type() = std::move(t); });
@@ -341,6 +408,10 @@ PYBIND11_MODULE(_host, m) {
       .def_readwrite("lookup_tokens", &RadixCache::lookup_tokens)
       .def_property_readonly("pool", &RadixCache::pool)
       .def_property_readonly("bs", &RadixCache::bs);
+  py::class_<BpeMerger>(m, "BpeMerger")
+      .def(py::init<const std::vector<std::string>&, const std::vector<std::pair<std::string, std::string>>&>())
+      .def("encode_word", &BpeMerger::encode_word)
+      .def("encode_words", &BpeMerger::encode_words);
   m.def("table_slots", &table_slots);
   m.def("pack_decode", &pack_decode);
 }

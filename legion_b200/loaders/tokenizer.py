@@ -134,11 +134,21 @@ class BpeTokenizer(Tokenizer):
             alts = sorted(self.special, key=len, reverse=True)
             self._sp_re = _re.compile("|".join(_re.escape(a) for a in alts))
         self._cache: Dict[str, List[int]] = {}
+        # the merge loop runs in the native host runtime when it is built (same procedure, same result)
+        self._native = None
+        from ..kv.blocks import NATIVE
+        if NATIVE is not None and hasattr(NATIVE, "BpeMerger") and all(" " not in t for t in self.tokens):
+            self._native = NATIVE.BpeMerger(self.tokens, [tuple(k) for k in self.ranks])
 
     def _bpe(self, word: str) -> List[int]:
         hit = self._cache.get(word)
         if hit is not None:
             return hit
+        if self._native is not None:
+            ids = self._native.encode_word(word)
+            if len(self._cache) < 65536:
+                self._cache[word] = ids
+            return ids
         parts = list(word)
         while len(parts) > 1:
             best, bi = None, -1

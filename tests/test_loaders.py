@@ -229,3 +229,26 @@ def test_chat_template_rendering():
     assert "<tools>" in with_tools and '"name": "f", "arguments": {"a": 1}' in with_tools and "<tool_response>\n42" in with_tools
     with pytest.raises(ct.TemplateError):
         ct.render("{{ raise_exception('nope') }}", msgs)
+
+
+def test_native_bpe_merges_equal_python():
+    """The C++ merge loop of the host runtime and the Python one give the same ids (unknown pieces included)."""
+    import random
+    from legion_b200.loaders.tokenizer import BpeTokenizer, _byte_to_unicode
+    b2u = _byte_to_unicode()
+    rng = random.Random(0)
+    toks = [b2u[i] for i in range(256) if i != ord("z")]          # 'z' is unknown: falls out of the ids
+    merges = []
+    for _ in range(2000):
+        a, b = rng.choice(toks), rng.choice(toks)
+        if a + b not in toks and len(a + b) < 10:
+            toks.append(a + b)
+            merges.append(a + " " + b)
+    t = BpeTokenizer(toks, merges)
+    if t._native is None:
+        pytest.skip("native host runtime not built")
+    text = "".join(rng.choice("abcdefghij klmnop\nqrstuvz 0123 éü漢字") for _ in range(5000))
+    got = t.encode(text)
+    t._native = None
+    t._cache.clear()
+    assert got == t.encode(text) and len(got) > 1000
