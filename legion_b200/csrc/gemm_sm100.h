@@ -59,6 +59,8 @@ struct WgemmArgs {
   int rows_per_group;             // weight rows between consecutive groups
   int dual_offset;                // DUAL: rows from a feature's gate row to its up row
   int split_k;
+  int tail_split;                 // > 1 (with split_k == 1): tiles of the last, partly filled round of the persistent
+                                  //   grid are split along K over the idle CTAs (at most this many parts each)
   int vec_ok;                     // output rows may be written as aligned 16-byte vectors
   float* ws;                      // split-K partials
   int* counters;                  // split-K arrival counters, zero on entry, left zero on exit
@@ -87,6 +89,7 @@ struct WgemmHost {
   int n_tok_tiles_max;
   int rows_per_group, dual_offset;
   int split_k; float* ws; int* counters;
+  int tail_split;                 // see WgemmArgs; needs ws for one partial per CTA and one counter per CTA
   int* status;
   void* out_peer[8]; int n_out_peer;
   WgemmCommTail comm;
