@@ -640,14 +640,21 @@ class LmEngine(Engine):
             if s not in self.running:
                 continue
             rows.append((s, len(s.tokens) - 1, n))
-        budget = c.max_batch_tokens - sum(r[2] for r in rows)
+        # token budget of the step: one for the whole step, or (data-parallel attention) one per owning rank, since
+        # every rank runs only its own rows
+        W = self.dp_world
+        budgets = [c.max_batch_tokens - sum(r[2] for r in rows if W == 1 or r[0].slot % W == o) for o in range(W)]
         slo = self.slo_budget(len(rows), first_chunk=bool(prefill) and prefill[0].n_computed == 0)
         if slo:
-            budget = min(budget, slo)
+            budgets = [min(b, slo) for b in budgets]
         for s in prefill:
             if s not in self.running:
                 continue
+            o = s.slot % W if W > 1 else 0
+            budget = budgets[o]
             if budget <= 0:
+                if W > 1:
+                    continue
                 break
             take = min(self._chunk_len(s.n_prompt - s.n_computed, c.prefill_chunk), budget)
             for sp in s.save_points:            # end the chunk at the next snapshot position
@@ -659,7 +666,7 @@ class LmEngine(Engine):
             if s not in self.running:
                 continue
             rows.append((s, s.n_computed, take))
-            budget -= take
+            budgets[o] -= take
         rows = [r for r in rows if r[0] in self.running]
         if not rows:
             return
