@@ -74,8 +74,11 @@ def _add_engine_args(ap: argparse.ArgumentParser):
     g.add_argument("--layer-split", default=None, help="layers per pipeline stage, e.g. 7,7,7,7,7,7,7,6")
     g.add_argument("--split-last-extra", type=int, default=0, help="layers' worth of room kept free on the last stage")
     g.add_argument("--pipeline-micro", type=int, default=2048, help="tokens per micro-chunk of a pipelined prompt")
-    g.add_argument("--experts", choices=["auto", "device", "host", "cache"], default="auto")
+    g.add_argument("--experts", choices=["auto", "device", "host", "cache", "ssd"], default="auto")
     g.add_argument("--expert-cache-gib", type=float, default=0.0)
+    g.add_argument("--expert-dir", default=None, help="--experts ssd: directory of the per-layer expert files")
+    g.add_argument("--expert-ram-gib", type=float, default=8.0,
+                   help="--experts ssd: host memory for recently used experts between the files and the HBM slots")
     g.add_argument("--expert-weights", choices=["bf16", "nvfp4", "fp8"], default="bf16",
                    help="nvfp4: keep the routed experts in 4 bits in HBM (expanded inside the grouped GEMM); "
                         "fp8: block-scaled e4m3 experts on the FP8 tensor-core path")
@@ -168,10 +171,16 @@ def build_engine_from_args(a, start: bool = True):
     if on_gpu and (wmode == "fp8" or getattr(a, "expert_weights", "bf16") == "fp8"):
         saved = model.quantize_weights_fp8(experts_only=wmode != "fp8")
         logging.getLogger("legion").info("weights re-encoded to block-scaled FP8: %.1f GiB of HBM saved", saved / 2 ** 30)
-    if a.experts in ("cache", "host") and cfg.n_expert:
+    if a.experts in ("cache", "host", "ssd") and cfg.n_expert:
         from ..residency.experts import slots_for_budget
         slots = cfg.top_k * ec.max_seqs if a.experts == "host" else slots_for_budget(cfg, a.expert_cache_gib or 8.0)
-        model.offload_experts(max(slots, cfg.top_k))
+        if a.experts == "ssd":
+            if not a.expert_dir:
+                raise SystemExit("--experts ssd needs --expert-dir")
+            model.offload_experts(max(slots, cfg.top_k), ssd_dir=a.expert_dir,
+                                  ram_experts=slots_for_budget(cfg, a.expert_ram_gib))
+        else:
+            model.offload_experts(max(slots, cfg.top_k))
     eng = LmEngine(model, tok, ec, start=start)
     logging.getLogger("legion").info("loaded %s: %s, %d layers, %.2fB parameters on %s", path, cfg.arch, cfg.n_layer,
                                      sum(t.numel() for t in w.values()) / 1e9, device)

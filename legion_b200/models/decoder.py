@@ -163,15 +163,23 @@ class Decoder:
         self.lm_head = weights.get("output", weights["tok_embd"])
         self.expert_cache: Dict[str, object] = {}     # layer prefix -> residency.ExpertCache (offload modes)
 
-    def offload_experts(self, n_slots: int, profile: Optional[dict] = None):
-        """Moves every MoE layer's routed experts to pinned host memory behind ``n_slots`` HBM slots."""
+    def offload_experts(self, n_slots: int, profile: Optional[dict] = None, ssd_dir: Optional[str] = None,
+                        ram_experts: int = 0):
+        """Moves every MoE layer's routed experts to pinned host memory behind ``n_slots`` HBM slots; with
+        ``ssd_dir`` to one file per layer in that directory, behind ``ram_experts`` experts per layer in host
+        memory and the HBM slots."""
+        import os
         from ..residency.experts import ExpertCache
+        if ssd_dir:
+            os.makedirs(ssd_dir, exist_ok=True)
         for il in range(self.cfg.n_layer):
             if not self.cfg.is_moe_layer(il):
                 continue
             p = f"l{il}"
             gu, dn = self.w.pop(f"{p}.moe.gate_up"), self.w.pop(f"{p}.moe.down")
-            self.expert_cache[p] = ExpertCache(gu, dn, n_slots, self.device, profile=(profile or {}).get(p))
+            self.expert_cache[p] = ExpertCache(gu, dn, n_slots, self.device, profile=(profile or {}).get(p),
+                                               ssd_path=os.path.join(ssd_dir, f"{p}.experts.bin") if ssd_dir else None,
+                                               ram_experts=ram_experts)
 
     def quantize_experts_nvfp4(self) -> int:
         """Re-encodes the routed experts of every MoE layer to NVFP4 in place (3.5x less HBM for the bulk of a MoE

@@ -6,6 +6,9 @@ Modes (``--experts``, ``src/residency/mod.rs:206-246`` in the reference):
            makes every expert it routes to resident (misses are copied into the coldest slots), then the
            grouped GEMM runs over the slot tensor through a remap table expert -> slot
   host     cache mode with the minimum number of slots (a step's experts only)
+  ssd      cache mode whose backing store is a file per layer on disk (``--expert-dir``), read through a memory map,
+           with a bounded tier of recently used experts in (pinned) host memory in between (``--expert-ram-gib``):
+           HBM slots <- RAM tier <- file (``src/residency/ssd_experts.rs``, ``host_tier.rs`` in the reference)
   peer     experts sharded over the GPUs' symmetric memory; the grouped GEMM's TMA loads stream a peer's
            expert tiles over NVLink straight into the consumer's shared-memory ring (no staging copy, no
            cluster multicast): see ``PeerExperts``
@@ -29,6 +32,9 @@ class CacheStats:
     misses: int = 0
     bytes_copied: int = 0
     steps: int = 0
+    ram_hits: int = 0          # ssd mode: misses served from the RAM tier
+    ssd_reads: int = 0         # ssd mode: misses read from the file
+    ssd_bytes: int = 0
 
     @property
     def hit_rate(self) -> float:
@@ -40,15 +46,32 @@ class ExpertCache:
     """One MoE layer's experts behind ``n_slots`` device slots."""
 
     def __init__(self, gate_up: torch.Tensor, down: torch.Tensor, n_slots: int, device, decay: float = 0.95,
-                 profile: Optional[List[float]] = None):
+                 profile: Optional[List[float]] = None, ssd_path: Optional[str] = None, ram_experts: int = 0):
         self.E = gate_up.shape[0]
         self.n_slots = min(n_slots, self.E)
         self.device = torch.device(device)
         pin = self.device.type == "cuda"
-        self.host_gu = gate_up.detach().cpu().contiguous()
-        self.host_dn = down.detach().cpu().contiguous()
-        if pin:
-            self.host_gu, self.host_dn = self.host_gu.pin_memory(), self.host_dn.pin_memory()
+        self.ssd = None
+        self.ram: "Dict[int, Tuple[torch.Tensor, torch.Tensor]]" = {}     # ssd mode: expert -> (gate_up, down), LRU order
+        self.ram_experts = max(0, ram_experts)
+        if ssd_path is not None:
+            # the layer's experts as raw 16- or 32-bit words in one file: [E, gate_up words | down words]
+            import numpy as np
+            wt = {2: torch.int16, 4: torch.int32}[gate_up.element_size()]
+            flat = torch.cat([gate_up.detach().cpu().contiguous().view(self.E, -1).view(wt),
+                              down.detach().cpu().contiguous().view(self.E, -1).view(wt)], dim=1).contiguous()
+            flat.numpy().tofile(ssd_path)
+            self.ssd = np.memmap(ssd_path, dtype=flat.numpy().dtype, mode="r", shape=tuple(flat.shape))
+            self._shape_gu, self._shape_dn = tuple(gate_up.shape[1:]), tuple(down.shape[1:])
+            self._n_gu = gate_up[0].numel()
+            self._dtype = gate_up.dtype
+            self.host_gu = self.host_dn = None
+            del flat
+        else:
+            self.host_gu = gate_up.detach().cpu().contiguous()
+            self.host_dn = down.detach().cpu().contiguous()
+            if pin:
+                self.host_gu, self.host_dn = self.host_gu.pin_memory(), self.host_dn.pin_memory()
         self.slot_gu = torch.empty((self.n_slots,) + tuple(gate_up.shape[1:]), dtype=gate_up.dtype, device=self.device)
         self.slot_dn = torch.empty((self.n_slots,) + tuple(down.shape[1:]), dtype=down.dtype, device=self.device)
         self.slot_of = [-1] * self.E              # expert -> slot
@@ -56,19 +79,43 @@ class ExpertCache:
         self.heat = list(profile) if profile else [0.0] * self.E
         self.decay = decay
         self.stats = CacheStats()
-        self.bytes_per_expert = (self.host_gu[0].numel() + self.host_dn[0].numel()) * gate_up.element_size()
+        self.bytes_per_expert = (gate_up[0].numel() + down[0].numel()) * gate_up.element_size()
         # seed the slots with the hottest experts of the profile (or the first ones)
         order = sorted(range(self.E), key=lambda e: -self.heat[e])[:self.n_slots]
         for s, e in enumerate(order):
             self._load(e, s)
         self.stats = CacheStats()
 
+    def _host_copy(self, e: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """The expert's weights in host memory: the resident copy, or (ssd mode) the RAM tier, filled from the file."""
+        if self.ssd is None:
+            return self.host_gu[e], self.host_dn[e]
+        hit = self.ram.pop(e, None)
+        if hit is not None:
+            self.stats.ram_hits += 1
+            self.ram[e] = hit                      # most recently used last
+            return hit
+        import numpy as np
+        row = torch.from_numpy(np.array(self.ssd[e]))          # one sequential read of the expert's bytes
+        self.stats.ssd_reads += 1
+        self.stats.ssd_bytes += self.bytes_per_expert
+        gu = row[:self._n_gu].view(self._dtype).view(self._shape_gu)
+        dn = row[self._n_gu:].view(self._dtype).view(self._shape_dn)
+        if self.device.type == "cuda":
+            gu, dn = gu.pin_memory(), dn.pin_memory()
+        if self.ram_experts > 0:
+            while len(self.ram) >= self.ram_experts:
+                self.ram.pop(next(iter(self.ram)))
+            self.ram[e] = (gu, dn)
+        return gu, dn
+
     def _load(self, e: int, s: int):
         old = self.expert_in[s]
         if old >= 0:
             self.slot_of[old] = -1
-        self.slot_gu[s].copy_(self.host_gu[e], non_blocking=True)
-        self.slot_dn[s].copy_(self.host_dn[e], non_blocking=True)
+        gu, dn = self._host_copy(e)
+        self.slot_gu[s].copy_(gu, non_blocking=self.ssd is None)
+        self.slot_dn[s].copy_(dn, non_blocking=self.ssd is None)
         self.slot_of[e], self.expert_in[s] = s, e
         self.stats.bytes_copied += self.bytes_per_expert
 

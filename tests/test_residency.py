@@ -48,3 +48,25 @@ def test_engine_with_offloaded_experts_matches_resident():
     b.shutdown()
     assert got == want
     assert all(s.steps > 0 for s in stats)
+
+
+def test_engine_with_ssd_expert_tier_matches_resident(tmp_path):
+    """Experts in one file per layer, a small RAM tier, fewer HBM slots than experts: same tokens as all-resident."""
+    cfg = tiny_gqa_moe()
+    w = random_weights(cfg, "cpu", torch.float32, seed=0, std=0.05)
+    prompt = torch.randint(0, 255, (60,), generator=torch.Generator().manual_seed(1)).tolist()
+    ec = dict(ctx_size=256, max_seqs=2, block_size=16, prefill_chunk=2, max_batch_tokens=2, prefix_cache=False)
+    a = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(**ec))
+    want = a.generate_text(tokens=prompt, max_tokens=10, ignore_eos=True).token_ids
+    a.shutdown()
+    b = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(**ec), start=False)
+    b.model.offload_experts(n_slots=5, ssd_dir=str(tmp_path / "experts"), ram_experts=3)
+    b.start()
+    got = b.generate_text(tokens=prompt, max_tokens=10, ignore_eos=True).token_ids
+    caches = list(b.model.expert_cache.values())
+    b.shutdown()
+    assert got == want
+    assert all(c.ssd is not None and c.host_gu is None for c in caches)
+    assert sum(c.stats.ssd_reads for c in caches) > 0 and sum(c.stats.ram_hits for c in caches) > 0
+    assert all(len(c.ram) <= 3 for c in caches)
+    assert len(list((tmp_path / "experts").iterdir())) == len(caches)
