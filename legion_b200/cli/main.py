@@ -40,6 +40,9 @@ def _add_engine_args(ap: argparse.ArgumentParser):
     g.add_argument("--kv-admission", choices=["reserve", "on-demand"], default="reserve")
     g.add_argument("--kv-swap-gib", type=float, default=0.0,
                    help="pinned host memory for the KV / state of preempted sequences (0: recompute them)")
+    g.add_argument("--prefix-cache-host-gib", type=float, default=0.0,
+                   help="pinned host memory that keeps the contents of prefix-cache blocks evicted from HBM; a later "
+                        "prompt with that prefix copies them back instead of recomputing (0: evicted blocks are dropped)")
     g.add_argument("--itl-target", type=float, default=0.0, help="inter-token latency target (ms) for the prompt budget")
     g.add_argument("--ttft-target", type=float, default=0.0)
     g.add_argument("--deterministic", action="store_true")
@@ -122,7 +125,8 @@ def build_engine_from_args(a, start: bool = True):
         spec_max_batch=a.spec_max_batch, deterministic=a.deterministic, device=device, seed=a.seed,
         cuda_graphs=not a.no_cuda_graphs, model_name=a.alias or os.path.basename(path.rstrip("/")),
         tool_format=a.tool_format, itl_target_ms=a.itl_target, ttft_target_ms=a.ttft_target,
-        nvtx=getattr(a, "nvtx", False), kv_swap_gib=getattr(a, "kv_swap_gib", 0.0), spec_policy=getattr(a, "spec_policy", "fixed"), even_chunks=not getattr(a, "no_even_chunks", False))
+        nvtx=getattr(a, "nvtx", False), kv_swap_gib=getattr(a, "kv_swap_gib", 0.0),
+        prefix_host_gib=getattr(a, "prefix_cache_host_gib", 0.0), spec_policy=getattr(a, "spec_policy", "fixed"), even_chunks=not getattr(a, "no_even_chunks", False))
     pctx = None
     if world > 1 and getattr(a, "pp", 1) > 1:
         # pipeline stages: every rank loads only its layers, the residual travels by send / recv

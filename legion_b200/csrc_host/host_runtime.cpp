@@ -183,8 +183,10 @@ class RadixCache {
     return adopted;
   }
 
-  int evict(int n_blocks) {
+  // on_evict(prefix_tokens, block) is called for every block before it is released (None: no callback)
+  int evict(int n_blocks, py::object on_evict) {
     int freed = 0;
+    const bool cb = !on_evict.is_none();
     while (freed < n_blocks) {
       Node* leaf = nullptr;
       for (auto& kv : nodes_) {
@@ -193,8 +195,18 @@ class RadixCache {
         if (leaf == nullptr || n->tick < leaf->tick) leaf = n;
       }
       if (leaf == nullptr) break;
+      std::vector<int> path;
+      if (cb) {
+        std::vector<Node*> chain;
+        for (Node* n = leaf; n != nullptr && n != root_; n = n->parent) chain.push_back(n);
+        for (auto it = chain.rbegin(); it != chain.rend(); ++it) path.insert(path.end(), (*it)->key.begin(), (*it)->key.end());
+      }
       while (!leaf->blocks.empty() && freed < n_blocks) {
         const int b = leaf->blocks.back();
+        if (cb) {
+          on_evict(path, b);
+          path.resize(path.size() - size_t(bs_));
+        }
         leaf->blocks.pop_back();
         leaf->key.resize(leaf->blocks.size() * size_t(bs_));
         pool_->decref(b);
@@ -212,7 +224,7 @@ class RadixCache {
     }
     return freed;
   }
-  void clear() { evict(int(n_cached_blocks) + 1); }
+  void clear() { evict(int(n_cached_blocks) + 1, py::none()); }
 
   long n_cached_blocks = 0, hit_tokens = 0, lookup_tokens = 0;
   std::shared_ptr<BlockPool> pool() const { return pool_; }
@@ -401,7 +413,7 @@ PYBIND11_MODULE(_host, m) {
            py::arg("max_tokens") = py::none())
       .def("unlock", &RadixCache::unlock)
       .def("insert", &RadixCache::insert)
-      .def("evict", &RadixCache::evict)
+      .def("evict", &RadixCache::evict, py::arg("n_blocks"), py::arg("on_evict") = py::none())
       .def("clear", &RadixCache::clear)
       .def_readwrite("n_cached_blocks", &RadixCache::n_cached_blocks)
       .def_readwrite("hit_tokens", &RadixCache::hit_tokens)

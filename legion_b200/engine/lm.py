@@ -57,6 +57,8 @@ class EngineConfig:
     kv_admission: str = "reserve"               # reserve | on-demand
     nvtx: bool = False                          # NVTX range around every eager step (for external profilers)
     kv_swap_gib: float = 0.0                    # host tier for preempted sequences (0 = recompute instead)
+    prefix_host_gib: float = 0.0                # host tier of the prefix cache: evicted blocks keep their contents
+                                                # in pinned memory and come back on a later hit (0 = dropped)
     spec: str = "none"                          # none | ngram | mtp | draft | eagle3 | suffix
     spec_k: int = 4
     spec_max_batch: int = 8
@@ -156,6 +158,9 @@ class LmEngine(Engine):
         self._slo = {"decode_ms": 0.0, "ms_per_prompt_token": 0.0}
         self._swap_bytes = 0
         self.radix = RadixCache(self.pool) if c.prefix_cache else None
+        # host tier of the prefix cache: prefix hash -> (K rows, V rows) of one block over all layers, LRU order
+        self._host_prefix: "Dict[bytes, Tuple[torch.Tensor, Optional[torch.Tensor]]]" = {}
+        self._host_prefix_bytes = 0
         self.saved = SavedStates(range(c.max_seqs, c.max_seqs + n_saved), c.block_size) if n_saved else None
         self.waiting = WaitQueue(c.scheduling_policy, c.fair_share, c.max_waiting)
         self.running: List[Seq] = []
@@ -376,7 +381,8 @@ class LmEngine(Engine):
         if self.pool.free >= need:
             return True
         if self.radix is not None:
-            self.radix.evict(need - self.pool.free)
+            spill = self._spill_prefix_block if (self.cfg.prefix_host_gib > 0 and not self.hybrid) else None
+            self.radix.evict(need - self.pool.free, spill)
         if self.pool.free < need and self.saved is not None:
             for s in sorted(self.saved.entries(), key=lambda e: e.tick):
                 if s.tail_block is not None:
@@ -386,6 +392,68 @@ class LmEngine(Engine):
                     if self.pool.free >= need:
                         break
         return self.pool.free >= need
+
+    # ------------------------------------------------------------------ prefix cache, host tier
+    def _spill_prefix_block(self, prefix_tokens, block: int):
+        """Eviction hook of the radix cache: the block's K/V rows of every layer go to pinned host memory under the
+        hash of the prefix the block ends (``src/engine/lm/host_tier.rs`` keeps whole KV tails there; here the tier
+        serves the prefix cache). Only blocks nobody else holds are kept: their contents are final."""
+        from ..kv.saved_states import prefix_hashes
+        if self.pool.refcount(block) != 1:
+            return
+        bs = self.cfg.block_size
+        key = prefix_hashes(prefix_tokens, bs)[-1]
+        if key in self._host_prefix:
+            return
+        layers = sorted(self.kv.k)
+        k = torch.stack([self.kv.k[il][block] for il in layers]).cpu()
+        shared = all(self.kv.v[il] is self.kv.k[il] for il in layers)
+        v = None if shared else torch.stack([self.kv.v[il][block] for il in layers]).cpu()
+        if self.device.type == "cuda":
+            k = k.pin_memory()
+            v = v.pin_memory() if v is not None else None
+        nbytes = k.numel() * k.element_size() * (1 if v is None else 2)
+        budget = self.cfg.prefix_host_gib * (1 << 30)
+        while self._host_prefix and self._host_prefix_bytes + nbytes > budget:
+            old_k, old_v = self._host_prefix.pop(next(iter(self._host_prefix)))
+            self._host_prefix_bytes -= old_k.numel() * old_k.element_size() * (1 if old_v is None else 2)
+        if nbytes > budget:
+            return
+        self._host_prefix[key] = (k, v)
+        self._host_prefix_bytes += nbytes
+        self._stats.prefix_host_spilled += 1
+
+    def _restore_prefix_blocks(self, prompt, matched: int, limit: int, blocks: List[int]) -> int:
+        """Continues a radix match from the host tier: while the next full block of the prompt is kept there, a
+        device block is allocated, filled and inserted into the radix tree. Returns the number of blocks restored."""
+        from ..kv.saved_states import prefix_hashes
+        bs = self.cfg.block_size
+        n_full = limit // bs
+        if not self._host_prefix or matched // bs >= n_full:
+            return 0
+        hs = prefix_hashes(prompt[:n_full * bs], bs)
+        layers = sorted(self.kv.k)
+        new_blocks: List[int] = []
+        i = matched // bs
+        while i < n_full and hs[i] in self._host_prefix and self._make_room(1):
+            if hs[i] not in self._host_prefix:          # making room spilled other blocks and pushed this one out
+                break
+            k, v = self._host_prefix.pop(hs[i])
+            self._host_prefix[hs[i]] = (k, v)                       # most recently used last
+            b = self.pool.alloc(1)[0]
+            kd = k.to(self.device, non_blocking=True)
+            vd = v.to(self.device, non_blocking=True) if v is not None else None
+            for j, il in enumerate(layers):
+                self.kv.k[il][b].copy_(kd[j])
+                if vd is not None:
+                    self.kv.v[il][b].copy_(vd[j])
+            new_blocks.append(b)
+            i += 1
+        if new_blocks:
+            self.radix.insert(prompt[:i * bs], list(blocks) + new_blocks)
+            self.pool.release(new_blocks)                           # the tree holds them now
+            self._stats.prefix_host_restored += len(new_blocks)
+        return len(new_blocks)
 
     def _admit(self):
         c = self.cfg
@@ -409,6 +477,9 @@ class LmEngine(Engine):
         handle = None
         if self.radix is not None and limit >= bs and seq.swapped is None:
             blocks, matched, handle = self.radix.match_prefix(prompt, lock=True, max_tokens=limit)
+            if self._host_prefix and not self.hybrid and self._restore_prefix_blocks(prompt, matched, limit, blocks):
+                self.radix.unlock(handle)
+                blocks, matched, handle = self.radix.match_prefix(prompt, lock=True, max_tokens=limit)
         resume = matched
         saved = None
         tail_block = None

@@ -257,6 +257,8 @@ class EngineStats:
     kv_preemptions: int = 0
     kv_swap_out: int = 0               # preempted sequences whose KV / state went to the host tier
     kv_swap_in: int = 0                # ... and came back instead of being recomputed
+    prefix_host_spilled: int = 0       # prefix-cache blocks whose contents went to the host tier when evicted
+    prefix_host_restored: int = 0      # ... and were copied back for a later prompt with that prefix
     prefix_cache_hit_tokens: int = 0
     prefix_cache_lookup_tokens: int = 0
     prompt_tokens: int = 0

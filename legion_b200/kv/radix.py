@@ -141,17 +141,34 @@ class PyRadixCache:
             stack.extend(n.children.values())
         return out
 
-    def evict(self, n_blocks: int) -> int:
+    def _path_tokens(self, node: _Node) -> List[int]:
+        parts = []
+        n = node
+        while n is not None and n is not self.root:
+            parts.append(n.key)
+            n = n.parent
+        out: List[int] = []
+        for k in reversed(parts):
+            out.extend(k)
+        return out
+
+    def evict(self, n_blocks: int, on_evict=None) -> int:
         """Frees up to n_blocks cached blocks, least recently used unlocked leaves first. A leaf is
-        trimmed from its tail, so a partially evicted edge keeps its prefix."""
+        trimmed from its tail, so a partially evicted edge keeps its prefix. ``on_evict(prefix_tokens, block)``
+        is called for every block before it is released, with the tokens of the whole prefix the block ends
+        (a lower tier can keep the block's contents under that key)."""
         freed = 0
         while freed < n_blocks:
             leaves = [l for l in self._leaves() if l.locks == 0]
             if not leaves:
                 break
             leaf = min(leaves, key=lambda l: l.tick)
+            path = self._path_tokens(leaf) if on_evict is not None else None
             while leaf.blocks and freed < n_blocks:
                 b = leaf.blocks.pop()
+                if on_evict is not None:
+                    on_evict(path, b)
+                    path = path[:len(path) - self.bs]
                 leaf.key = leaf.key[:len(leaf.blocks) * self.bs]
                 self.pool.decref(b)
                 self.n_cached_blocks -= 1

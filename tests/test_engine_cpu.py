@@ -280,3 +280,29 @@ def test_more_architectures_generate_and_reuse_prefix(preset):
         assert a == b and len(a) == 8
         outs.append(a)
     assert outs[0] == outs[1]
+
+
+def test_prefix_cache_host_tier_restores_evicted_blocks():
+    """A small KV pool: the first prompt's cached blocks are evicted by later prompts, their contents go to the
+    host tier, and the first prompt sent again gets them back (cached tokens, same output) instead of recomputing."""
+    cfg = tiny_gqa_moe()
+    w = random_weights(cfg, "cpu", torch.float32, seed=0, std=0.05)
+    ec = dict(ctx_size=128, max_seqs=1, block_size=16, prefill_chunk=64, kv_cache_tokens=160, prefix_cache=True)
+    eng = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(prefix_host_gib=0.01, **ec))
+    base = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(**ec))
+    pa = torch.randint(0, 255, (100,), generator=torch.Generator().manual_seed(1)).tolist()
+    others = [torch.randint(0, 255, (100,), generator=torch.Generator().manual_seed(s)).tolist() for s in (2, 3)]
+    first = eng.generate_text(tokens=pa, max_tokens=6, ignore_eos=True)
+    for p in others:
+        eng.generate_text(tokens=p, max_tokens=6, ignore_eos=True)
+        base.generate_text(tokens=p, max_tokens=6, ignore_eos=True)
+    st = eng.stats()
+    assert st.prefix_host_spilled > 0
+    again = eng.generate_text(tokens=pa, max_tokens=6, ignore_eos=True)
+    st = eng.stats()
+    want = base.generate_text(tokens=pa, max_tokens=6, ignore_eos=True)       # recomputed from scratch there
+    eng.shutdown()
+    base.shutdown()
+    assert again.token_ids == first.token_ids == want.token_ids
+    assert st.prefix_host_restored > 0 and again.usage.cached_tokens >= 32
+    assert want.usage.cached_tokens < again.usage.cached_tokens
