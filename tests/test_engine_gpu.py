@@ -139,3 +139,25 @@ def test_engine_with_fp8_weights():
     eng_g.shutdown()
     assert len(a.token_ids) == 12 and a.token_ids == b2.token_ids and replays > 0
     assert Workspace.get("cuda").check() == 0
+
+
+def test_prefix_cache_host_tier_on_gpu():
+    """Evicted prefix-cache blocks go to pinned host memory and come back for a later prompt with that prefix."""
+    from legion_b200.config import ModelConfig
+    from legion_b200.engine.lm import EngineConfig, build_engine
+    from legion_b200.models.weights import random_weights
+    cfg = ModelConfig(arch="qwen3", n_layer=2, hidden=256, vocab=1024, n_head=4, n_kv_head=2, head_dim=128, dense_ff=512)
+    w = random_weights(cfg, "cuda", torch.bfloat16, seed=0, std=0.05)
+    ec = dict(ctx_size=512, max_seqs=1, block_size=64, prefill_chunk=256, kv_cache_tokens=640, prefix_cache=True)
+    eng = build_engine(cfg, weights=dict(w), device="cuda", engine_cfg=EngineConfig(prefix_host_gib=0.05, **ec))
+    pa = torch.randint(0, 255, (400,), generator=torch.Generator().manual_seed(1)).tolist()
+    first = eng.generate_text(tokens=pa, max_tokens=6, ignore_eos=True)
+    for sd in (2, 3):
+        eng.generate_text(tokens=torch.randint(0, 255, (400,), generator=torch.Generator().manual_seed(sd)).tolist(),
+                          max_tokens=6, ignore_eos=True)
+    assert eng.stats().prefix_host_spilled > 0
+    again = eng.generate_text(tokens=pa, max_tokens=6, ignore_eos=True)
+    st = eng.stats()
+    eng.shutdown()
+    assert again.token_ids == first.token_ids
+    assert st.prefix_host_restored > 0 and again.usage.cached_tokens >= 128
