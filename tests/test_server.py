@@ -150,3 +150,58 @@ def test_real_engine_behind_the_server():
     assert r.status_code == 400 and "context" in r.json()["error"]["message"]
     assert c.get("/v1/stats").json()["engine"]["prefix_cache_hit_tokens"] > 0
     eng.shutdown()
+
+
+def test_tls_listener_serves_https(tmp_path):
+    """`--tls-cert / --tls-key`: the listener speaks TLS; a client that trusts the certificate gets the API, a plain
+    HTTP client does not."""
+    import datetime
+    import socket
+    import threading
+    import time
+
+    import requests
+    import uvicorn
+    from cryptography import x509
+    from cryptography.hazmat.primitives import hashes, serialization
+    from cryptography.hazmat.primitives.asymmetric import rsa
+    from cryptography.x509.oid import NameOID
+    import ipaddress
+
+    key = rsa.generate_private_key(public_exponent=65537, key_size=2048)
+    name = x509.Name([x509.NameAttribute(NameOID.COMMON_NAME, "127.0.0.1")])
+    now = datetime.datetime.now(datetime.timezone.utc)
+    cert = (x509.CertificateBuilder().subject_name(name).issuer_name(name).public_key(key.public_key())
+            .serial_number(x509.random_serial_number()).not_valid_before(now - datetime.timedelta(minutes=1))
+            .not_valid_after(now + datetime.timedelta(hours=1))
+            .add_extension(x509.SubjectAlternativeName([x509.IPAddress(ipaddress.ip_address("127.0.0.1"))]), False)
+            .sign(key, hashes.SHA256()))
+    cert_path, key_path = tmp_path / "cert.pem", tmp_path / "key.pem"
+    cert_path.write_bytes(cert.public_bytes(serialization.Encoding.PEM))
+    key_path.write_bytes(key.private_bytes(serialization.Encoding.PEM, serialization.PrivateFormat.TraditionalOpenSSL,
+                                           serialization.NoEncryption()))
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    app = create_app(MockEngine("mock"), ServerConfig())
+    server = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=port, log_level="error",
+                                           ssl_certfile=str(cert_path), ssl_keyfile=str(key_path)))
+    th = threading.Thread(target=server.run, daemon=True)
+    th.start()
+    try:
+        for _ in range(100):
+            if server.started:
+                break
+            time.sleep(0.05)
+        assert server.started
+        r = requests.get(f"https://127.0.0.1:{port}/v1/models", verify=str(cert_path), timeout=10)
+        assert r.status_code == 200 and r.json()["data"][0]["id"] == "mock"
+        r = requests.post(f"https://127.0.0.1:{port}/v1/chat/completions", verify=str(cert_path), timeout=10,
+                          json={"model": "mock", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 4})
+        assert r.status_code == 200 and r.json()["choices"][0]["message"]["content"]
+        with pytest.raises(requests.exceptions.RequestException):
+            requests.get(f"http://127.0.0.1:{port}/v1/models", timeout=5)
+    finally:
+        server.should_exit = True
+        th.join(timeout=10)
