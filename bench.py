@@ -33,7 +33,7 @@ BASELINE_DECODE_16 = 262.3   # reference's best published 16-user decode tok/s (
 def reference_arm():
     print(json.dumps({"impl": "reference",
                       "unavailable": "reference is a Rust crate over a ggml submodule that is empty here; no cargo/rustc "
-                                     "in the image, so it cannot be installed or run (pip install of /root/reference has "
+                                     "in the image, so it cannot be installed or run (pip install of the reference tree has "
                                      "no Python package to build)"}))
     return 0
 
