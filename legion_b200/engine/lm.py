@@ -90,7 +90,7 @@ class Seq:
     __slots__ = ("req", "stream", "tokens", "n_prompt", "n_computed", "table", "slot", "sampler", "detok", "stop",
                  "reason", "tools", "phase", "arrival_ms", "admit_ms", "first_ms", "usage", "radix_handle", "drafts",
                  "save_points", "finished", "priority", "key", "n_out", "held_logprobs", "constraint", "resumed", "swapped",
-                 "orig_prompt", "last_hidden", "draft_state")
+                 "orig_prompt", "last_hidden", "draft_state", "owner")
 
     def __init__(self, req: GenerateRequest, stream: TokenStream, tokens: List[int]):
         self.req, self.stream = req, stream
@@ -101,6 +101,7 @@ class Seq:
         self.swapped = None               # _Swapped: KV blocks + recurrent state parked in host memory
         self.table = BlockTable()
         self.slot = -1
+        self.owner = -1                   # data-parallel attention: the rank that runs this sequence's attention
         self.phase = "wait"
         self.arrival_ms = now_ms()
         self.admit_ms = 0.0
@@ -136,14 +137,18 @@ class LmEngine(Engine):
         dev = model.device
         self.device = dev
         self.hybrid = bool(self.mcfg.recurrent_layers())
-        # data-parallel attention: this rank runs attention only for the sequences it owns (state slot % ranks)
+        # data-parallel attention: this rank runs attention only for the sequences it owns. A sequence that reuses a
+        # cached prefix belongs to the rank that computed the prefix (the blocks' contents exist only there);
+        # otherwise to the rank with the fewest sequences.
         self.dp_world = getattr(model.pctx, "dp_world", 1)
         self.dp_rank = getattr(model.pctx, "dp_rank", 0)
+        self._block_owner: Dict[int, int] = {}
         if self.dp_world > 1:
             if c.spec != "none" or drafter is not None:
                 raise ValueError("speculative decoding is not available with data-parallel attention")
-            # a cached prefix lives in its first owner's KV only
-            c.prefix_cache = False
+            c.prefix_host_gib = 0.0
+            if self.hybrid:
+                c.prefix_cache = False        # recurrent snapshots are not owner-aware
         kv_tokens = c.kv_cache_tokens or c.max_seqs * c.ctx_size
         n_blocks = max(4, (kv_tokens + c.block_size - 1) // c.block_size)
         self.pool = BlockPool(n_blocks, c.block_size)
@@ -519,6 +524,12 @@ class LmEngine(Engine):
             return False
         seq.radix_handle = handle
         seq.slot = self._free_slots.pop()
+        if self.dp_world > 1 and not (seq.swapped is not None and seq.owner >= 0):
+            if use_blocks:
+                seq.owner = self._block_owner.get(use_blocks[0], 0)
+            else:
+                load = [sum(1 for r in self.running if r.owner == o) for o in range(self.dp_world)]
+                seq.owner = load.index(min(load))
         if self.states is not None:
             if saved is not None:
                 self.states.copy(saved.slot, seq.slot)
@@ -714,14 +725,14 @@ class LmEngine(Engine):
         # token budget of the step: one for the whole step, or (data-parallel attention) one per owning rank, since
         # every rank runs only its own rows
         W = self.dp_world
-        budgets = [c.max_batch_tokens - sum(r[2] for r in rows if W == 1 or r[0].slot % W == o) for o in range(W)]
+        budgets = [c.max_batch_tokens - sum(r[2] for r in rows if W == 1 or r[0].owner == o) for o in range(W)]
         slo = self.slo_budget(len(rows), first_chunk=bool(prefill) and prefill[0].n_computed == 0)
         if slo:
             budgets = [min(b, slo) for b in budgets]
         for s in prefill:
             if s not in self.running:
                 continue
-            o = s.slot % W if W > 1 else 0
+            o = s.owner if W > 1 else 0
             budget = budgets[o]
             if budget <= 0:
                 if W > 1:
@@ -831,6 +842,12 @@ class LmEngine(Engine):
                          logit_rows=torch.tensor(lrows, dtype=torch.int64, device=dev),
                          max_q_len=max(len(t) for _, _, t in items), max_ctx=max(ctx), cu_q_host=cu)
 
+    def _own_blocks(self, s: Seq):
+        """Data-parallel attention: blocks that enter the prefix cache remember which rank holds their contents."""
+        if self.dp_world > 1:
+            for b in s.table.blocks:
+                self._block_owner[b] = s.owner
+
     def _dp_forward_and_finish(self, rows, verify: bool):
         """One step under data-parallel attention. Every rank plans the same global rows; this rank runs the model
         on the rows it owns (a padding row when it owns none, so that it still meets the others in every MoE
@@ -838,7 +855,7 @@ class LmEngine(Engine):
         samples all of them alike."""
         import torch.distributed as dist
         W, R = self.dp_world, self.dp_rank
-        own = [r for r in rows if r[0].slot % W == R]
+        own = [r for r in rows if r[0].owner == R]
         if self._graphs is not None and all(
                 s.phase == "decode" and n == 1 and s.req.sampling.greedy and s.req.sampling.plain and s.constraint is None
                 for s, _, n in rows):
@@ -846,8 +863,8 @@ class LmEngine(Engine):
             # all ranks are gathered (one small collective) and mapped back to the global row order
             per_owner, where = [0] * W, []
             for s, _, _ in rows:
-                where.append((s.slot % W, per_owner[s.slot % W]))
-                per_owner[s.slot % W] += 1
+                where.append((s.owner, per_owner[s.owner]))
+                per_owner[s.owner] += 1
             Bg = self._graphs.bucket(max(per_owner))
             if Bg is not None:
                 picks, _ = self._graphs.run(own, B=Bg, gather=(self.model.pctx.dp_group, W))
@@ -869,7 +886,7 @@ class LmEngine(Engine):
         counts = [n if s.phase == "decode" else (1 if p0 + n == s.n_prompt else 0) for s, p0, n in rows]
         per_owner, where = [0] * W, []
         for (s, _, _), c in zip(rows, counts):
-            o = s.slot % W
+            o = s.owner
             where.append((o, per_owner[o]))
             per_owner[o] += c
         M, V = max(1, max(per_owner)), out.logits.shape[1]
@@ -956,6 +973,7 @@ class LmEngine(Engine):
                     continue
                 # prompt done: cache its full blocks, sample the first token
                 if self.radix is not None:
+                    self._own_blocks(s)
                     self.radix.insert(s.tokens[:s.n_prompt], s.table.blocks)
                 row = logits_host[r] if logits_host is not None else None
                 tok, lp = self._pick(s, row, device_picks[r] if device_picks is not None else None)
@@ -1139,6 +1157,7 @@ class LmEngine(Engine):
         if reason not in (FinishReason.CANCELLED, FinishReason.ERROR) and s.phase == "decode" and s.slot >= 0:
             n = s.n_computed
             if self.radix is not None:
+                self._own_blocks(s)
                 self.radix.insert(s.tokens[:n], s.table.blocks)
             if self.saved is not None and n > 0:
                 bs = self.cfg.block_size
