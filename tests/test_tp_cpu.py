@@ -143,3 +143,43 @@ def test_lock_step_serving_over_two_ranks(tmp_path):
     got = torch.load(out)
     assert got["tokens"] == want
     assert 2 <= got["cancelled_after"] < 200
+
+
+def _leaver(rank, world, port, out_path):
+    """Rank 1 leaves between steps (no collective of its own in flight); rank 0's next collective must end with an
+    error within the group's timeout instead of hanging, and the error is what the host sees."""
+    import datetime
+    import time
+
+    import torch.distributed as dist
+    from legion_b200.parallel.context import ParallelCtx
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=8))
+    pctx = ParallelCtx(rank, world, dist.group.WORLD, comm="nccl")
+    x = torch.ones(4, 8)
+    y = pctx.all_reduce(x.clone())                    # step 1: both ranks
+    assert float(y[0, 0]) == world
+    dist.barrier()
+    if rank == 1:
+        os._exit(0)                                   # gone before step 2
+    t0 = time.time()
+    err = None
+    try:
+        pctx.all_reduce(x.clone())                    # step 2: the peer never joins
+    except Exception as e:                            # noqa: BLE001
+        err = f"{type(e).__name__}: {e}"
+    torch.save({"error": err, "seconds": time.time() - t0}, out_path)
+    os._exit(0)
+
+
+def test_a_rank_that_leaves_ends_the_next_collective_with_an_error(tmp_path):
+    out = str(tmp_path / "r0.pt")
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_leaver, args=(r, 2, (port := _free_port()) if r == 0 else port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=90)
+        assert not p.is_alive(), "a rank hung after its peer left"
+    got = torch.load(out)
+    assert got["error"] is not None and got["seconds"] < 30, got
