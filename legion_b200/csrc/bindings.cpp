@@ -41,7 +41,7 @@ void wgemm(const Tensor& w, const Tensor& x, Tensor& out, const OptT& residual, 
            const OptT& ws, const OptT& counters, Tensor& status, const OptT& tile_group, const OptT& tile_tok0,
            const OptT& tile_ntok, const OptT& meta, int64_t max_tiles, int64_t rows_per_group, int64_t n_tok,
            std::vector<int64_t> out_peer, const OptT& tile_out0, const OptT& w_scales, const OptT& w_gscale,
-           int64_t tail_split) {
+           int64_t tail_split, int64_t x_group_col, int64_t k_override) {
   const bool fp4 = w_scales.has_value();     // w = NVFP4 codes [rows, K/2] uint8, w_scales = e4m3 bytes [rows, K/16]
   if (fp4) {
     TORCH_CHECK(w.scalar_type() == at::kByte && w_scales->is_contiguous() && w_scales->element_size() == 1 &&
@@ -52,7 +52,7 @@ void wgemm(const Tensor& w, const Tensor& x, Tensor& out, const OptT& residual, 
   }
   check_bf16(x, "x");
   TORCH_CHECK(w.dim() == 2 && x.dim() == 2 && out.dim() == 2, "wgemm expects 2-D tensors");
-  TORCH_CHECK(w.size(1) * (fp4 ? 2 : 1) == x.size(1), "wgemm: K mismatch");
+  TORCH_CHECK(k_override > 0 || w.size(1) * (fp4 ? 2 : 1) == x.size(1), "wgemm: K mismatch");
   TORCH_CHECK(out.scalar_type() == at::kBFloat16 || out.scalar_type() == at::kFloat, "wgemm: out must be bf16/f32");
   TORCH_CHECK(out.stride(1) == 1 && out.size(1) >= n_feat, "wgemm: bad out");
   c10::cuda::CUDAGuard guard(w.device());
@@ -68,6 +68,12 @@ void wgemm(const Tensor& w, const Tensor& x, Tensor& out, const OptT& residual, 
   h.tok_scale = optp<float>(tok_scale);
   h.out_rows = optp<int>(out_rows);
   h.K = int(x.size(1)); h.n_feat = int(n_feat); h.n_tok = int(n_tok);
+  if (k_override > 0) {          // per-group slices of a wider activation tensor: K is the weight's width
+    TORCH_CHECK(!fp4 && w.size(1) == k_override && x_group_col > 0, "wgemm: per-group columns need K == w.size(1)");
+    h.K = int(k_override);
+    h.x_cols = x.size(1);
+    h.x_group_col = int(x_group_col);
+  }
   h.w_scales = fp4 ? w_scales->data_ptr() : nullptr;
   h.w_gscale = optp<float>(w_gscale);
   h.bn = int(bn); h.dual = dual;
@@ -536,7 +542,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         pybind11::arg("tile_ntok"), pybind11::arg("meta"), pybind11::arg("max_tiles"), pybind11::arg("rows_per_group"),
         pybind11::arg("n_tok"), pybind11::arg("out_peer"), pybind11::arg("tile_out0") = pybind11::none(),
         pybind11::arg("w_scales") = pybind11::none(), pybind11::arg("w_gscale") = pybind11::none(),
-        pybind11::arg("tail_split") = 0);
+        pybind11::arg("tail_split") = 0, pybind11::arg("x_group_col") = 0, pybind11::arg("k_override") = 0);
   m.def("wgemm_fp8", &wgemm_fp8);
   m.def("wgemm_allreduce", &wgemm_allreduce);
   m.def("wgemm_allgather", &wgemm_allgather);

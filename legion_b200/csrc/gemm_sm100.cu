@@ -291,7 +291,7 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
             tma_load_2d(st, &tmW, &full[s], kb * KBE, wrow);
             if (DUAL) tma_load_2d(st + W_TILE_BYTES, &tmW, &full[s], kb * KBE, wrow + a.dual_offset);
           }
-          tma_load_2d(st + Cfg::X_OFF, &tmX, &full[s], kb * KBE, it.tok0);
+          tma_load_2d(st + Cfg::X_OFF, &tmX, &full[s], it.group * a.x_group_col + kb * KBE, it.tok0);
           ++issued;
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
@@ -833,7 +833,8 @@ int wgemm_launch(const WgemmHost& h, cudaStream_t stream) {
                                : tmW;
   const CUtensorMap* tmX =
       fp8 ? tmap_2d(h.x, uint64_t(h.x_rows), uint64_t(h.K), uint64_t(h.ldx), uint32_t(bn), 128, TM_U8, true)
-          : tmap_2d(h.x, uint64_t(h.x_rows), uint64_t(h.K), uint64_t(h.ldx) * 2, uint32_t(bn), BK, TM_BF16, true);
+          : tmap_2d(h.x, uint64_t(h.x_rows), uint64_t(h.x_cols > 0 ? h.x_cols : h.K), uint64_t(h.ldx) * 2, uint32_t(bn),
+                    BK, TM_BF16, true);
   if (!tmW || !tmX || !tmS) {
     snprintf(g_gemm_err, sizeof(g_gemm_err), "wgemm: %s", tmap_last_error());
     return 1;
@@ -850,6 +851,12 @@ int wgemm_launch(const WgemmHost& h, cudaStream_t stream) {
   a.tile_group = h.tile_group; a.tile_tok0 = h.tile_tok0; a.tile_out0 = h.tile_out0; a.tile_ntok = h.tile_ntok; a.n_tiles_dev = h.n_tiles_dev;
   a.n_tok_tiles_max = h.n_tok_tiles_max;
   a.rows_per_group = h.rows_per_group; a.dual_offset = h.dual_offset;
+  a.x_group_col = h.x_group_col;
+  if (h.x_group_col != 0 && (h.x_group_col % 8 != 0 || h.K % BK != 0 || fp8 || fp4 || !h.tile_group)) {
+    snprintf(g_gemm_err, sizeof(g_gemm_err),
+             "wgemm: per-group activation columns need grouped bf16 mode, K %% 64 == 0 and 16-byte aligned offsets");
+    return 1;
+  }
   a.split_k = h.split_k < 1 ? 1 : h.split_k;
   a.tail_split = (h.tail_split > 1 && a.split_k == 1 && h.ws && h.counters && !h.comm.enabled) ? h.tail_split : 0;
   a.ws = h.ws; a.counters = h.counters; a.status = h.status;

@@ -57,6 +57,8 @@ struct WgemmArgs {
   const int* n_tiles_dev;         //   number of token tiles (device scalar, data of a CUDA graph)
   int n_tok_tiles_max;
   int rows_per_group;             // weight rows between consecutive groups
+  int x_group_col;                // grouped mode: first activation column of group g is g * x_group_col (per-head
+                                  //   projections read their head's slice of a [tokens, heads * width] tensor in place)
   int dual_offset;                // DUAL: rows from a feature's gate row to its up row
   int split_k;
   int tail_split;                 // > 1 (with split_k == 1): tiles of the last, partly filled round of the persistent
@@ -88,6 +90,7 @@ struct WgemmHost {
   const int* tile_out0;
   int n_tok_tiles_max;
   int rows_per_group, dual_offset;
+  int x_group_col; long x_cols;   // see WgemmArgs::x_group_col; x_cols: columns of the activation tensor (0 = K)
   int split_k; float* ws; int* counters;
   int tail_split;                 // see WgemmArgs; needs ws for one partial per CTA and one counter per CTA
   int* status;

@@ -162,6 +162,7 @@ class Decoder:
         self.gdn_v_l = max(1, cfg.gdn_v_heads // tp)
         self.lm_head = weights.get("output", weights["tok_embd"])
         self.expert_cache: Dict[str, object] = {}     # layer prefix -> residency.ExpertCache (offload modes)
+        self._mla_uk: Dict[str, torch.Tensor] = {}    # layer prefix -> W_uk^T per head (absorb projection, K-major)
 
     def offload_experts(self, n_slots: int, profile: Optional[dict] = None, ssd_dir: Optional[str] = None,
                         ram_experts: int = 0):
@@ -280,12 +281,28 @@ class Decoder:
         if x.is_cuda and x.dtype == torch.bfloat16 and ops.sm100.mla_supported(nh, L, dr, kv.page):
             # absorbed form on the tensor cores: q_abs = [q_nope W_uk | rope(q_pe)], o = (softmax . c_kv) W_uv
             q_abs = torch.empty(T, nh, L + dr, dtype=x.dtype, device=x.device)
-            q_abs[..., :L] = torch.bmm(q[..., :dn].transpose(0, 1), wkv_b[:, :dn]).transpose(0, 1)
+            own = (ops.sm100.TUNE["mla_head_gemm"] and dn % 64 == 0 and dvh % 8 == 0 and (dn + dr) % 8 == 0
+                   and isinstance(w[f"{p}.mla.kv_b"], torch.Tensor))
+            if own:
+                # per-head absorb and value projections on the grouped tcgen05 GEMM (group = head), each head's
+                # slice read and written in place
+                uk = self._mla_uk.get(p)
+                if uk is None:
+                    uk = wkv_b[:, :dn].transpose(1, 2).contiguous().view(nh * L, dn)     # W_uk^T per head, K-major
+                    self._mla_uk[p] = uk
+                ops.sm100.head_linear(q.view(T, nh * (dn + dr)), uk, nh, L, L, dn, dn + dr, q_abs.view(T * nh, L + dr))
+            else:
+                q_abs[..., :L] = torch.bmm(q[..., :dn].transpose(0, 1), wkv_b[:, :dn]).transpose(0, 1)
             ops.sm100.mla_prep(kva, w[f"{p}.mla.kv_a_norm"], cfg.rms_eps, cfg.norm_offset, q, dn, self.cos_sin,
                                b.positions, b.slots, kv.k[il], q_abs)
             o_lat = ops.sm100.mla_attn(q_abs, kv.k[il], b.cu_q, b.ctx_lens, b.block_table, kv.page, b.max_q_len,
                                        scale, max_ctx=b.max_ctx or None)
-            out = torch.bmm(o_lat.transpose(0, 1), wkv_b[:, dn:].transpose(1, 2)).transpose(0, 1)
+            if own:
+                out = torch.empty(T, nh * dvh, dtype=x.dtype, device=x.device)
+                w_uv = w[f"{p}.mla.kv_b"].view(nh * (dn + dvh), L)[dn:]                   # head h: rows h*(dn+dvh)..+dvh
+                ops.sm100.head_linear(o_lat.view(T, nh * L), w_uv, nh, dn + dvh, dvh, L, L, out.view(T * nh, dvh))
+            else:
+                out = torch.bmm(o_lat.transpose(0, 1), wkv_b[:, dn:].transpose(1, 2)).transpose(0, 1)
             return ops.linear(out.reshape(T, nh * dvh), w[f"{p}.mla.o"])
         ckv, _ = ops.rmsnorm(kva[:, :L].contiguous(), w[f"{p}.mla.kv_a_norm"], cfg.rms_eps, cfg.norm_offset)
         k_pe = ops.reference.apply_rope(kva[:, L:].reshape(T, 1, dr), self.cos_sin, b.positions, dr)

@@ -106,7 +106,7 @@ def have_ext() -> bool:
 NUM_SMS = 148
 
 # tuning knobs (environment: LB_TUNE="decode_fixed_tiles=2,dense_route=1")
-TUNE = {"decode_fixed_tiles": 2, "fused_plan": 1, "fused_router": 1, "dense_route": 1, "pdl": 1, "route_norm": 0, "tail_split": 0}
+TUNE = {"decode_fixed_tiles": 2, "fused_plan": 1, "fused_router": 1, "dense_route": 1, "pdl": 1, "route_norm": 0, "tail_split": 0, "mla_head_gemm": 0}
 for _kv in os.environ.get("LB_TUNE", "").split(","):
     if "=" in _kv:
         TUNE[_kv.split("=")[0].strip()] = int(_kv.split("=")[1])
@@ -472,6 +472,38 @@ def prefill_attn(q, k_cache, v_cache, cu_q, ctx_lens, block_table, max_q_len, sc
     ws = Workspace.get(q.device)
     C.prefill_attn(q, k_cache, v_cache, cu_q, ctx_lens, block_table, max_q_len, scale, window, causal, out, ws.status)
     return out
+
+
+def head_linear(x, w2d, n_heads: int, rows_per_group: int, n_feat: int, K: int, x_group_col: int, out2d):
+    """Per-head projections read and written in place: for every head h
+    ``out2d[t * n_heads + h, :n_feat] = W_h @ x[t, h * x_group_col : h * x_group_col + K]`` with
+    ``W_h = w2d[h * rows_per_group : h * rows_per_group + n_feat]``. One grouped launch of the tcgen05 GEMM (group =
+    head); the activation tile of a head is fetched from its column slice of ``x`` by the TMA load, the output rows
+    go through a row map, so nothing is transposed or copied."""
+    C = ext()
+    T = x.shape[0]
+    ws = Workspace.get(x.device)
+    bn = pick_bn(T, False)
+    key = ("head_linear", T, n_heads, bn)
+    tab = ws._cache.get(key)
+    if tab is None:
+        n_tt = (T + bn - 1) // bn
+        Tp = n_tt * bn
+        h = torch.arange(n_heads).repeat_interleave(n_tt)
+        tt = torch.arange(n_tt).repeat(n_heads)
+        rows = torch.full((n_heads * Tp,), -1, dtype=torch.int32)
+        t = torch.arange(T)
+        for hh in range(n_heads):
+            rows[hh * Tp: hh * Tp + T] = (t * n_heads + hh).int()
+        i32 = dict(dtype=torch.int32, device=x.device)
+        tab = (h.to(**i32), (tt * bn).to(**i32), torch.clamp(T - tt * bn, max=bn).to(**i32),
+               (h * Tp + tt * bn).to(**i32), rows.to(x.device),
+               torch.tensor([n_heads * n_tt, 0], **i32), n_heads * n_tt)
+        ws._cache[key] = tab
+    tile_group, tile_tok0, tile_ntok, tile_out0, out_rows, meta, n_tiles = tab
+    C.wgemm(w2d, x, out2d, None, None, out_rows, n_feat, False, 0, bn, 1, None, None, ws.status, tile_group, tile_tok0,
+            tile_ntok, meta, n_tiles, rows_per_group, 0, [], tile_out0, None, None, 0, x_group_col, K)
+    return out2d
 
 
 def mla_splits(n_seqs: int, max_q_len: int, nh: int, max_ctx: int) -> int:

@@ -16,8 +16,8 @@ def _cfgs():
         tiny_hybrid_moe(),
         ModelConfig(arch="qwen3", n_layer=2, hidden=256, vocab=1024, n_head=4, n_kv_head=2, head_dim=128, dense_ff=512),
         # latent attention with the 512 + 64 cache row the tcgen05 kernel implements, MoE with grouped sigmoid routing
-        ModelConfig(arch="deepseek_v3", n_layer=3, hidden=256, vocab=1024, n_head=16, n_kv_head=16, head_dim=96,
-                    q_lora=96, kv_lora=512, qk_nope_dim=32, qk_rope_dim=64, v_head_dim=32, qk_norm=False,
+        ModelConfig(arch="deepseek_v3", n_layer=3, hidden=256, vocab=1024, n_head=16, n_kv_head=16, head_dim=128,
+                    q_lora=96, kv_lora=512, qk_nope_dim=64, qk_rope_dim=64, v_head_dim=64, qk_norm=False,
                     dense_ff=384, first_dense_layers=1, n_expert=8, top_k=2, expert_ff=128, shared_ff=128,
                     router_mode="sigmoid", router_bias=True, n_group=4, topk_group=2, route_scale=2.5),
     ]

@@ -606,3 +606,22 @@ def test_fp8_gate_up_and_experts():
         want = ref.moe_experts(x2, routing.ids, routing.wts, gq.dequantize(), dq.dequantize(), F)
         err = (y.float() - want.float()).abs().max().item()
         assert err < 0.06 * want.abs().max().item() + 0.03, (T2, err)
+
+
+@pytest.mark.parametrize("T,nh,K,xcol,rpg,nf", [(16, 16, 128, 192, 512, 512), (70, 8, 512, 512, 256, 128),
+                                                (300, 4, 64, 128, 128, 128)])
+def test_head_linear_in_place_slices(T, nh, K, xcol, rpg, nf):
+    """Per-head projections through one grouped GEMM launch: each head's activation slice is read in place (column
+    offset in the TMA coordinate) and its output rows go through the row map."""
+    torch.manual_seed(T)
+    x = rnd(T, nh * xcol)
+    w = rnd(nh * rpg, K, scale=0.1)
+    ldo = nf + 64
+    out = torch.zeros(T * nh, ldo, device=DEV, dtype=torch.bfloat16)
+    sm().head_linear(x, w, nh, rpg, nf, K, xcol, out)
+    status_ok()
+    xs = x.view(T, nh, xcol)[:, :, :K].float()
+    wh = w.view(nh, rpg, K)[:, :nf].float()
+    want = torch.einsum("thk,hfk->thf", xs, wh).reshape(T * nh, nf)
+    close(out[:, :nf], want, 2e-2, 2e-2)
+    assert out[:, nf:].abs().sum() == 0
