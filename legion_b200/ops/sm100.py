@@ -106,7 +106,7 @@ def have_ext() -> bool:
 NUM_SMS = 148
 
 # tuning knobs (environment: LB_TUNE="decode_fixed_tiles=2,dense_route=1")
-TUNE = {"decode_fixed_tiles": 2, "fused_plan": 1, "fused_router": 1, "dense_route": 1, "pdl": 1, "route_norm": 0, "tail_split": 0, "mla_head_gemm": 0}
+TUNE = {"decode_fixed_tiles": 2, "fused_plan": 1, "fused_router": 1, "dense_route": 1, "pdl": 1, "route_norm": 0, "tail_split": 0, "mla_head_gemm": 1}
 for _kv in os.environ.get("LB_TUNE", "").split(","):
     if "=" in _kv:
         TUNE[_kv.split("=")[0].strip()] = int(_kv.split("=")[1])
