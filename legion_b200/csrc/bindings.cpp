@@ -41,7 +41,7 @@ void wgemm(const Tensor& w, const Tensor& x, Tensor& out, const OptT& residual, 
            const OptT& ws, const OptT& counters, Tensor& status, const OptT& tile_group, const OptT& tile_tok0,
            const OptT& tile_ntok, const OptT& meta, int64_t max_tiles, int64_t rows_per_group, int64_t n_tok,
            std::vector<int64_t> out_peer, const OptT& tile_out0, const OptT& w_scales, const OptT& w_gscale,
-           int64_t tail_split, int64_t x_group_col, int64_t k_override) {
+           int64_t x_group_col, int64_t k_override) {
   const bool fp4 = w_scales.has_value();     // w = NVFP4 codes [rows, K/2] uint8, w_scales = e4m3 bytes [rows, K/16]
   if (fp4) {
     TORCH_CHECK(w.scalar_type() == at::kByte && w_scales->is_contiguous() && w_scales->element_size() == 1 &&
@@ -92,10 +92,6 @@ void wgemm(const Tensor& w, const Tensor& x, Tensor& out, const OptT& residual, 
     TORCH_CHECK(size_t(ws->numel()) >= lb::wgemm_workspace_floats(h.bn, dual, n_tok_tiles, feat_tiles, h.split_k),
                 "wgemm: split-K workspace too small");
     TORCH_CHECK(counters->numel() >= int64_t(n_tok_tiles) * feat_tiles, "wgemm: too few split-K counters");
-  }
-  if (tail_split > 1 && h.split_k <= 1 && ws.has_value() && counters.has_value() &&
-      ws->numel() >= int64_t(256) * 128 * (dual ? 2 : 1) * bn && counters->numel() >= 256) {
-    h.tail_split = int(tail_split);      // room for one partial tile and one counter per CTA of the persistent grid
   }
   h.status = reinterpret_cast<int*>(status.data_ptr());
   TORCH_CHECK(out_peer.size() <= 8, "wgemm: at most 8 peer outputs");
@@ -542,7 +538,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         pybind11::arg("tile_ntok"), pybind11::arg("meta"), pybind11::arg("max_tiles"), pybind11::arg("rows_per_group"),
         pybind11::arg("n_tok"), pybind11::arg("out_peer"), pybind11::arg("tile_out0") = pybind11::none(),
         pybind11::arg("w_scales") = pybind11::none(), pybind11::arg("w_gscale") = pybind11::none(),
-        pybind11::arg("tail_split") = 0, pybind11::arg("x_group_col") = 0, pybind11::arg("k_override") = 0);
+        pybind11::arg("x_group_col") = 0, pybind11::arg("k_override") = 0);
   m.def("wgemm_fp8", &wgemm_fp8);
   m.def("wgemm_allreduce", &wgemm_allreduce);
   m.def("wgemm_allgather", &wgemm_allgather);

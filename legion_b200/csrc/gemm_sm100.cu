@@ -64,40 +64,16 @@ struct WgemmCfg {
 
 struct WorkItem {
   int group, tok0, out0, ntok, feat0, ks, tile_id;   // tok0: first x row; out0: first output row
-  int nsplit, ws_tile;   // parts this tile's K range is split into; index of its partial-sum slots and counter
 };
 
 template <int BN>
-__device__ __forceinline__ bool decode_work(const WgemmArgs& a, int w, int n_tok_tiles, int num_kb, WorkItem& it) {
-  int tt, ft;
-  if (a.tail_split > 1 && a.split_k == 1) {
-    // Whole tiles go round-robin over the persistent grid; the tiles of the last round, which would leave most
-    // CTAs idle, are split along K over all of them (their partial sums meet in the split-K reduction).
-    const int total = n_tok_tiles * a.feat_tiles, G = int(gridDim.x);
-    const int full = (total / G) * G, r = total - full;
-    int sp = r > 0 ? min(a.tail_split, G / r) : 1;
-    while (sp > 1 && (sp - 1) * ((num_kb + sp - 1) / sp) >= num_kb) --sp;     // no empty part
-    int t;
-    if (w < full) {
-      t = w; it.ks = 0; it.nsplit = 1; it.ws_tile = 0;
-    } else {
-      const int idx = w - full;
-      t = full + idx / sp;
-      if (t >= total) return false;
-      it.ks = idx - (idx / sp) * sp; it.nsplit = sp; it.ws_tile = t - full;
-    }
-    tt = t / a.feat_tiles;
-    ft = t - tt * a.feat_tiles;
-  } else {
-    const int per_tok_tile = a.feat_tiles * a.split_k;
-    tt = w / per_tok_tile;
-    if (tt >= n_tok_tiles) return false;
-    const int r = w - tt * per_tok_tile;
-    ft = r / a.split_k;
-    it.ks = r - ft * a.split_k;
-    it.nsplit = a.split_k;
-    it.ws_tile = tt * a.feat_tiles + ft;
-  }
+__device__ __forceinline__ bool decode_work(const WgemmArgs& a, int w, int n_tok_tiles, WorkItem& it) {
+  const int per_tok_tile = a.feat_tiles * a.split_k;
+  const int tt = w / per_tok_tile;
+  if (tt >= n_tok_tiles) return false;
+  const int r = w - tt * per_tok_tile;
+  const int ft = r / a.split_k;
+  it.ks = r - ft * a.split_k;
   it.feat0 = ft * BM;
   it.tile_id = tt * a.feat_tiles + ft;
   if (a.tile_group) {
@@ -252,6 +228,7 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
 
   const int n_tok_tiles = a.tile_group ? min(*a.n_tiles_dev, a.n_tok_tiles_max) : (a.n_tok + BN - 1) / BN;
   const int num_kb = (a.K + KBE - 1) / KBE;
+  const int kb_per_split = (num_kb + a.split_k - 1) / a.split_k;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -263,8 +240,7 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
       int issued = 0;
       bool ok = true;
       WorkItem it;
-      for (int w = blockIdx.x; ok && decode_work<BN>(a, w, n_tok_tiles, num_kb, it); w += gridDim.x) {
-        const int kb_per_split = (num_kb + it.nsplit - 1) / it.nsplit;
+      for (int w = blockIdx.x; ok && decode_work<BN>(a, w, n_tok_tiles, it); w += gridDim.x) {
         const int kb0 = it.ks * kb_per_split;
         const int kb1 = min(num_kb, kb0 + kb_per_split);
         const int wrow = it.group * a.rows_per_group + it.feat0;
@@ -319,8 +295,7 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
       uint32_t acc_ph = 0;
       bool ok = true;
       WorkItem it;
-      for (int w = blockIdx.x; ok && decode_work<BN>(a, w, n_tok_tiles, num_kb, it); w += gridDim.x) {
-        const int kb_per_split = (num_kb + it.nsplit - 1) / it.nsplit;
+      for (int w = blockIdx.x; ok && decode_work<BN>(a, w, n_tok_tiles, it); w += gridDim.x) {
         const int kb0 = it.ks * kb_per_split;
         const int kb1 = min(num_kb, kb0 + kb_per_split);
         if (!WFP8) {
@@ -401,8 +376,7 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
 #pragma unroll
         for (int k = 0; k < 4; ++k) scw[t][i][k] = 0u;
     WorkItem it;
-    for (int w = blockIdx.x; decode_work<BN>(a, w, n_tok_tiles, num_kb, it); w += gridDim.x) {
-      const int kb_per_split = (num_kb + it.nsplit - 1) / it.nsplit;
+    for (int w = blockIdx.x; decode_work<BN>(a, w, n_tok_tiles, it); w += gridDim.x) {
       const int kb0 = it.ks * kb_per_split;
       const int kb1 = min(num_kb, kb0 + kb_per_split);
       for (int kb = kb0; kb < kb1; ++kb) {
@@ -461,7 +435,7 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
     int acc = 0;
     uint32_t acc_ph = 0;
     WorkItem it;
-    for (int w = blockIdx.x; decode_work<BN>(a, w, n_tok_tiles, num_kb, it); w += gridDim.x) {
+    for (int w = blockIdx.x; decode_work<BN>(a, w, n_tok_tiles, it); w += gridDim.x) {
       const int row = q * 32 + lane;               // row within the tile
       const int feat = it.feat0 + row;
       const bool feat_ok = feat < a.n_feat;
@@ -474,7 +448,6 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
           accg[j] = 0.f;
           if (DUAL) accu[j] = 0.f;
         }
-        const int kb_per_split = (num_kb + it.nsplit - 1) / it.nsplit;
         const int kb0 = it.ks * kb_per_split;
         const int kb1 = min(num_kb, kb0 + kb_per_split);
         const long wblk = long((it.group * a.rows_per_group + it.feat0) >> 7) * num_kb;
@@ -541,9 +514,9 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
       };
 
       bool finalize = true;
-      if (it.nsplit > 1) {
+      if (a.split_k > 1) {
         // fp32 partials: ws[tile][split][col][128 rows]
-        float* wsp = a.ws + (size_t(it.ws_tile) * it.nsplit + it.ks) * (Cfg::ACC_COLS * BM);
+        float* wsp = a.ws + (size_t(it.tile_id) * a.split_k + it.ks) * (Cfg::ACC_COLS * BM);
 #pragma unroll 1
         for (int c = 0; c < Cfg::ACC_COLS; c += 32) {
           uint32_t r[32];
@@ -554,9 +527,9 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (threadIdx.x == 64) {
-          const int old = atomicAdd(&a.counters[it.ws_tile], 1);
-          *last_flag = (old == it.nsplit - 1) ? 1 : 0;
-          if (old == it.nsplit - 1) a.counters[it.ws_tile] = 0;
+          const int old = atomicAdd(&a.counters[it.tile_id], 1);
+          *last_flag = (old == a.split_k - 1) ? 1 : 0;
+          if (old == a.split_k - 1) a.counters[it.tile_id] = 0;
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         finalize = (*last_flag != 0);
@@ -564,15 +537,15 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
       }
 
       if (finalize) {
-        const float* wsb = it.nsplit > 1 ? a.ws + size_t(it.ws_tile) * it.nsplit * (Cfg::ACC_COLS * BM) : nullptr;
+        const float* wsb = a.split_k > 1 ? a.ws + size_t(it.tile_id) * a.split_k * (Cfg::ACC_COLS * BM) : nullptr;
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
           if (c >= it.ntok) break;
           float g[32], u[32];
-          if (it.nsplit > 1) {
+          if (a.split_k > 1) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) { g[j] = 0.f; u[j] = 0.f; }
-            for (int sp = 0; sp < it.nsplit; ++sp) {
+            for (int sp = 0; sp < a.split_k; ++sp) {
               const float* p = wsb + size_t(sp) * (Cfg::ACC_COLS * BM);
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
@@ -858,7 +831,6 @@ int wgemm_launch(const WgemmHost& h, cudaStream_t stream) {
     return 1;
   }
   a.split_k = h.split_k < 1 ? 1 : h.split_k;
-  a.tail_split = (h.tail_split > 1 && a.split_k == 1 && h.ws && h.counters && !h.comm.enabled) ? h.tail_split : 0;
   a.ws = h.ws; a.counters = h.counters; a.status = h.status;
   a.n_out_peer = h.n_out_peer;
   for (int i = 0; i < 8; ++i) a.out_peer[i] = h.out_peer[i];

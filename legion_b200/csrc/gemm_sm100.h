@@ -61,8 +61,6 @@ struct WgemmArgs {
                                   //   projections read their head's slice of a [tokens, heads * width] tensor in place)
   int dual_offset;                // DUAL: rows from a feature's gate row to its up row
   int split_k;
-  int tail_split;                 // > 1 (with split_k == 1): tiles of the last, partly filled round of the persistent
-                                  //   grid are split along K over the idle CTAs (at most this many parts each)
   int vec_ok;                     // output rows may be written as aligned 16-byte vectors
   float* ws;                      // split-K partials
   int* counters;                  // split-K arrival counters, zero on entry, left zero on exit
@@ -92,7 +90,6 @@ struct WgemmHost {
   int rows_per_group, dual_offset;
   int x_group_col; long x_cols;   // see WgemmArgs::x_group_col; x_cols: columns of the activation tensor (0 = K)
   int split_k; float* ws; int* counters;
-  int tail_split;                 // see WgemmArgs; needs ws for one partial per CTA and one counter per CTA
   int* status;
   void* out_peer[8]; int n_out_peer;
   WgemmCommTail comm;

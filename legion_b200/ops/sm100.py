@@ -106,7 +106,7 @@ def have_ext() -> bool:
 NUM_SMS = 148
 
 # tuning knobs (environment: LB_TUNE="decode_fixed_tiles=2,dense_route=1")
-TUNE = {"decode_fixed_tiles": 2, "fused_plan": 1, "fused_router": 1, "dense_route": 1, "pdl": 1, "route_norm": 0, "tail_split": 0, "mla_head_gemm": 1}
+TUNE = {"decode_fixed_tiles": 2, "fused_plan": 1, "fused_router": 1, "dense_route": 1, "pdl": 1, "route_norm": 0, "mla_head_gemm": 1}
 for _kv in os.environ.get("LB_TUNE", "").split(","):
     if "=" in _kv:
         TUNE[_kv.split("=")[0].strip()] = int(_kv.split("=")[1])
@@ -502,7 +502,7 @@ def head_linear(x, w2d, n_heads: int, rows_per_group: int, n_feat: int, K: int, 
         ws._cache[key] = tab
     tile_group, tile_tok0, tile_ntok, tile_out0, out_rows, meta, n_tiles = tab
     C.wgemm(w2d, x, out2d, None, None, out_rows, n_feat, False, 0, bn, 1, None, None, ws.status, tile_group, tile_tok0,
-            tile_ntok, meta, n_tiles, rows_per_group, 0, [], tile_out0, None, None, 0, x_group_col, K)
+            tile_ntok, meta, n_tiles, rows_per_group, 0, [], tile_out0, None, None, x_group_col, K)
     return out2d
 
 
@@ -679,15 +679,12 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[Moe
             dr.h_all = torch.zeros(E_local * dr.bn, n_ff, dtype=torch.bfloat16, device=x.device)
         if dr.y_pairs is None or dr.y_pairs.shape[0] < P or dr.y_pairs.shape[1] != H:
             dr.y_pairs = torch.zeros(max(P, 64 * k), H, dtype=torch.bfloat16, device=x.device)
-        # optional (LB_TUNE=tail_split=4): tiles of the grid's last, partly filled round split along K over the idle
-        # CTAs. Off: the grouped GEMMs are HBM-bound (86 % of copy bandwidth), so balancing CTAs gains nothing
-        ts = TUNE["tail_split"]
         C.wgemm(gu2, x, dr.h_all, None, None, None, n_ff, True, n_ff, dr.bn, 1,
-                ws.splitk if ts > 1 else None, ws.counters if ts > 1 else None, ws.status, dr.tile_group, dr.zeros,
-                dr.tile_ntok, dr.meta, E_local, 2 * n_ff, 0, [], dr.slot_base, gu_sc, gu_gs, ts)
+                None, None, ws.status, dr.tile_group, dr.zeros, dr.tile_ntok, dr.meta, E_local, 2 * n_ff, 0, [],
+                dr.slot_base, gu_sc, gu_gs)
         C.wgemm(dn2, dr.h_all, dr.y_pairs, None, dr.tok_scale, dr.out_rows, H, False, 0,
-                dr.bn, 1, ws.splitk if ts > 1 else None, ws.counters if ts > 1 else None, ws.status, dr.tile_group,
-                dr.slot_base, dr.tile_ntok, dr.meta, E_local, H, 0, [], None, dn_sc, dn_gs, ts)
+                dr.bn, 1, None, None, ws.status, dr.tile_group, dr.slot_base, dr.tile_ntok, dr.meta, E_local, H, 0, [],
+                None, dn_sc, dn_gs)
         if out is None:
             out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
         y = dr.y_pairs[:P]
