@@ -10,6 +10,9 @@
 // Contract
 //   * logits: device pointer, float32, `rows` rows of `vocab` values with pitch `ld` elements.
 //     out: device pointer to `rows` int32 results (index of the largest value, ties to the lower index).
+//   * A row that holds only NaN has no largest value: its result is 0x7fffffff (the regular arg-max
+//     op answers the same), which is outside every vocabulary, so check for it if NaN rows can occur.
+//     A row of -inf only answers 0.
 //   * rows <= LB_NOALLOC_MAX_ROWS (256); more returns LB_NOALLOC_TOO_LARGE and launches nothing.
 //   * The work is enqueued on `stream` (a cudaStream_t; 0 = default stream); nothing is synchronised.
 //   * No cudaMalloc / cudaFree / allocator call is made, here or in anything it calls.

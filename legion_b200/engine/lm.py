@@ -382,7 +382,9 @@ class LmEngine(Engine):
                                 else self.cfg.spec_k + 2)
         return max(0, self.pool.blocks_for(total) - cached_blocks)
 
-    def _make_room(self, need: int) -> bool:
+    def _make_room(self, need: int, keep=None) -> bool:
+        """Frees KV blocks until ``need`` are available: radix leaves first, then saved snapshots that pin a tail
+        block (oldest first). ``keep`` is a snapshot the caller is about to resume from: it is never dropped."""
         if self.pool.free >= need:
             return True
         if self.radix is not None:
@@ -390,7 +392,7 @@ class LmEngine(Engine):
             self.radix.evict(need - self.pool.free, spill)
         if self.pool.free < need and self.saved is not None:
             for s in sorted(self.saved.entries(), key=lambda e: e.tick):
-                if s.tail_block is not None:
+                if s.tail_block is not None and s is not keep:
                     self.pool.decref(s.tail_block)
                     s.tail_block = None
                     self.saved.drop(s)
@@ -498,8 +500,15 @@ class LmEngine(Engine):
                         saved, resume = cand, cand.n_tokens
                         tail_block = cand.tail_block if cand.n_tokens != full else None
         use_blocks = blocks[:resume // bs]
+        if handle is not None and len(use_blocks) < len(blocks):
+            # matched blocks past the resume point are recomputed: do not keep them locked against eviction
+            self.radix.unlock(handle)
+            handle = None
+            if use_blocks:
+                blocks, matched, handle = self.radix.match_prefix(prompt, lock=True, max_tokens=len(use_blocks) * bs)
+                use_blocks = blocks[:resume // bs]
         need = self._blocks_needed(seq, len(use_blocks) + (1 if tail_block is not None else 0))
-        if not self._make_room(need):
+        if not self._make_room(need, keep=saved):
             if handle is not None:
                 self.radix.unlock(handle)
             if not self.running:
@@ -1122,7 +1131,11 @@ class LmEngine(Engine):
         self.states.copy(s.slot, slot)
         if tail_block is not None:
             self.pool.incref(tail_block)
-        self.saved.store(s.tokens, n_tokens, slot, kind, tail_block)
+        self.saved.store(s.tokens, n_tokens, slot, kind, tail_block, on_replace=self._drop_tail_ref)
+
+    def _drop_tail_ref(self, old):
+        if old.tail_block is not None:
+            self.pool.decref(old.tail_block)
 
     def _release(self, s: Seq):
         if s.radix_handle is not None and self.radix is not None:

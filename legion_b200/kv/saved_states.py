@@ -111,7 +111,11 @@ class SavedStates:
         return victim.slot, victim
 
     def store(self, tokens: Sequence[int], n_tokens: int, slot: int, kind: str = "anchor",
-              tail_block: Optional[int] = None) -> Saved:
+              tail_block: Optional[int] = None, on_replace=None) -> Saved:
+        """Records a snapshot. An entry with the same position and prefix is replaced: its slot goes back to the
+        free list and ``on_replace(old)`` lets the owner of the KV pool give back the reference that the old
+        entry held on its tail block (without it every repeat of the same conversation would pin one more block).
+        """
         if n_tokens % self.block == 0 and kind != "tail":
             key = prefix_hashes(tokens[:n_tokens], self.block)[-1]
         else:
@@ -120,6 +124,9 @@ class SavedStates:
         old = self._by_key.get((n_tokens, key))
         if old is not None:
             self._free.append(old.slot)
+            if on_replace is not None:
+                on_replace(old)
+            old.tail_block = None
         s = Saved(slot, n_tokens, key, kind, tail_block)
         self._by_key[(n_tokens, key)] = s
         self._touch(s)

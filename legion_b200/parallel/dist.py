@@ -16,6 +16,14 @@ import torch
 from .context import ParallelCtx
 
 
+def no_multicast_default():
+    """Call before the first symmetric-memory rendezvous of a process. No kernel of this library uses multimem, so
+    the buffers need no NVLink multicast binding; a rank that dies while its memory is bound to a multicast object
+    can raise NVLink faults on its peers' GPUs. ``TORCH_SYMM_MEM_DISABLE_MULTICAST=0`` in the environment keeps
+    PyTorch's default."""
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+
+
 def env_world():
     return int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
 
@@ -38,6 +46,7 @@ def init_from_env(device: Optional[str] = None, comm: str = "fused", expert_para
         dist.init_process_group("nccl" if use_cuda else "gloo", rank=rank, world_size=world,
                                 timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
     symm = None
+    no_multicast_default()
     if comm == "fused" and use_cuda:
         from .symm import SymmComm
         symm = SymmComm(dist.group.WORLD, rank, world, torch.device("cuda", local_rank), max_rows, hidden)

@@ -39,6 +39,8 @@ class EpDispatcher:
 
     def __init__(self, group, rank: int, world: int, device: torch.device, n_expert: int, top_k: int, hidden: int,
                  n_ff: int, max_tokens: int, cap_factor: Optional[float] = None, budget_ns: int = 5_000_000_000):
+        from .dist import no_multicast_default
+        no_multicast_default()
         import torch.distributed._symmetric_memory as symm_mem
         if n_expert % world:
             raise ValueError("experts must divide evenly over the ranks")

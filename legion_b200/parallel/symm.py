@@ -34,11 +34,18 @@ class SymmComm:
 
     def __init__(self, group, rank: int, world: int, device: torch.device, max_rows: int, hidden: int,
                  budget_ns: int = 5_000_000_000):
+        from .dist import no_multicast_default
+        no_multicast_default()
         import torch.distributed._symmetric_memory as symm_mem
         self.rank, self.world, self.device = rank, world, device
         self.max_rows, self.hidden = max_rows, hidden
         self.slot_bytes = max_rows * hidden * 2
-        nbytes = self.slot_bytes * (self.N_SLOTS + 1)      # + one region for reduce-scatter results
+        # regions after the partial slots: one for the two-shot reduce-scatter results, two that the all-gather
+        # shards alternate between (see shard_view)
+        self.rs_off = self.N_SLOTS * self.slot_bytes
+        self.ag_off = (self.rs_off + self.slot_bytes, self.rs_off + 2 * self.slot_bytes)
+        self._ag_half = 0
+        nbytes = self.slot_bytes * (self.N_SLOTS + 3)
         self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
         self.handle = symm_mem.rendezvous(self.buf, group=group)
         self.buffer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
@@ -87,7 +94,7 @@ class SymmComm:
             per = (T + self.world - 1) // self.world
             row0 = min(T, self.rank * per)
             n_rows = max(0, min(T, row0 + per) - row0)
-            out_off = self.N_SLOTS * self.slot_bytes
+            out_off = self.rs_off      # rewritten only after the next call's flag round: every peer has left this one
             C = ext()
             C.reduce_scatter_fused(self.buffer_ptrs, self.signal_ptrs, self.rank, off, out_off, 0, self.seq, self.done,
                                    row0, n_rows, H, res, self.budget_ns, self.status)
@@ -144,9 +151,15 @@ class SymmComm:
         return row0, max(0, min(T, row0 + per) - row0), per
 
     def shard_view(self, T: int) -> torch.Tensor:
-        """Where this rank writes its block of rows (inside its symmetric buffer) before ``all_gather_linear``."""
+        """Where this rank writes its block of rows (inside its symmetric buffer) before ``all_gather_linear``.
+
+        Ordering contract: write the block into ``shard_view(T)``, then call ``all_gather_linear(T, ...)``, once each,
+        in that order on the compute stream. Consecutive calls alternate between two regions. The kernel's head only
+        waits for the peers to ENTER call n, so a fast rank may leave call n while a slower peer still copies its
+        rows; it then writes call n+1's block into the OTHER region, and can reach the first region again (call
+        n+2) only after call n+1's flag round, which every peer raises after it has finished call n."""
         row0, n, _ = self.shard_rows(T)
-        off = self.N_SLOTS * self.slot_bytes + row0 * self.hidden * 2
+        off = self.ag_off[self._ag_half] + row0 * self.hidden * 2
         return self.buf[off:off + n * self.hidden * 2].view(torch.bfloat16).view(n, self.hidden)
 
     def all_gather_linear(self, T: int, w: torch.Tensor, residual=None, out_dtype=torch.bfloat16):
@@ -173,7 +186,8 @@ class SymmComm:
         _, _, per = self.shard_rows(T)
         C.wgemm_allgather(w, x_full, out, residual, bn, sk, ws.splitk if sk > 1 else None,
                           ws.counters if sk > 1 else None, ws.status, self.buffer_ptrs, self.signal_ptrs, self.rank,
-                          self.N_SLOTS * self.slot_bytes, 0, self.seq, self.gemm_ctrs, per, self.budget_ns, self.status)
+                          self.ag_off[self._ag_half], 0, self.seq, self.gemm_ctrs, per, self.budget_ns, self.status)
+        self._ag_half ^= 1
         return out, x_full
 
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:

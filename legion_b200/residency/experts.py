@@ -164,6 +164,8 @@ class PeerExperts:
     (non-multicast) TMA loads, tile by tile, overlapped with the math of the tiles before it."""
 
     def __init__(self, gate_up_local: torch.Tensor, down_local: torch.Tensor, group, rank: int, world: int):
+        from ..parallel.dist import no_multicast_default
+        no_multicast_default()
         import torch.distributed._symmetric_memory as symm_mem
         self.rank, self.world = rank, world
         self.per = gate_up_local.shape[0]

@@ -63,15 +63,25 @@ def case_comm(dev):
     errs.append(float((summed.float() - want).abs().max()))
     comm.end_step()
     comm.check()
-    # all-gather -> GEMM in one kernel: every rank contributes its block of rows
-    for T in (16, 300):
+    # all-gather -> GEMM in one kernel: every rank contributes its block of rows. Calls of different sizes run back
+    # to back with no host synchronisation in between (a fast rank may start writing the next call's block while
+    # a slower peer still copies this call's rows: the two alternating regions keep them apart); the gathered
+    # rows are compared bit for bit afterwards.
+    kept = []
+    for it, T in enumerate((16, 300, 64, 1000, 16, 300, 7)):
         xs = (torch.randn(T, H, device=dev) * 0.3).bfloat16()          # same on every rank
         wq = (torch.randn(384, H, device=dev) * 0.05).bfloat16()
         row0, n, _ = comm.shard_rows(T)
         comm.shard_view(T).copy_(xs[row0:row0 + n])
         out, gathered = comm.all_gather_linear(T, wq)
-        comm.check()
-        assert torch.equal(gathered, xs)
+        kept.append((T, xs, wq, out, gathered.clone()))
+        if it == 3:      # a two-shot all-reduce in between shares the buffer but not the regions
+            slot = comm.next_partial(600, H)
+            slot.copy_((torch.randn(600, H, device=dev) * 0.5).bfloat16())
+            comm.all_reduce_add_norm(slot, None, None, 0.0, 0.0)
+    comm.check()
+    for T, xs, wq, out, gathered in kept:
+        assert torch.equal(gathered, xs), f"gathered rows differ at T={T}"
         errs.append(float((out.float() - ref.linear(xs, wq).float()).abs().max()))
         say("all-gather GEMM rows", T, "ok")
     assert sm100.Workspace.get(dev).check() == 0

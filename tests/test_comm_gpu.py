@@ -1,8 +1,10 @@
 """Fused collectives over symmetric memory on 2+ GPUs: the all-reduce + residual + RMSNorm kernel (one- and
 two-shot), a GEMM whose epilogue writes into the symmetric slot, the expert-parallel dispatch / combine fused with
 the grouped GEMMs, and a TP engine (fused == NCCL). Each case runs ``tests/dist_worker.py`` as one process per
-GPU under ``torch.distributed.run`` with a hard time limit; NVLS is off so a rank that fails cannot disturb its
-peers' GPUs."""
+GPU under ``torch.distributed.run`` with a hard time limit. NVLS is off in NCCL (``NCCL_NVLS_ENABLE=0``) and the
+symmetric-memory rendezvous is told not to bind the buffers to an NVLink multicast object
+(``TORCH_SYMM_MEM_DISABLE_MULTICAST=1``; no kernel here uses multimem), so a rank that is ended by the watchdog or
+the time limit does not take a multicast binding down with it."""
 import os
 import socket
 import subprocess
@@ -28,7 +30,7 @@ def _run(case, world, tmp_path, limit=180):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     out = str(tmp_path / f"{case}.pt")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", LB_TEST_WATCHDOG_S="120")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1", LB_TEST_WATCHDOG_S="120")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "dist_worker.py"),
            case, out]

@@ -306,3 +306,52 @@ def test_prefix_cache_host_tier_restores_evicted_blocks():
     assert again.token_ids == first.token_ids == want.token_ids
     assert st.prefix_host_restored > 0 and again.usage.cached_tokens >= 32
     assert want.usage.cached_tokens < again.usage.cached_tokens
+
+
+def test_repeated_conversation_does_not_pin_more_blocks():
+    """Hybrid model, same prompt answered again and again: every reply saves the same ragged tail. The replaced
+    snapshot must give its tail block back, so the number of free KV blocks settles instead of shrinking by one
+    block per repeat."""
+    eng = engine("hybrid", max_seqs=1)
+    p = prompt(70, 4)
+    free = []
+    for _ in range(5):
+        run(eng, p, n=13)
+        free.append(eng.pool.free)
+    eng.shutdown()
+    assert free[2] == free[3] == free[4], free
+
+
+def test_saved_state_store_reports_the_replaced_entry():
+    from legion_b200.kv.saved_states import SavedStates
+    ss = SavedStates(slots=[0, 1, 2], block=16)
+    toks = list(range(40))
+    gone = []
+    s1, _ = ss.reserve()
+    ss.store(toks, 37, s1, "tail", tail_block=7, on_replace=gone.append)
+    s2, _ = ss.reserve()
+    ss.store(toks, 37, s2, "tail", tail_block=9, on_replace=gone.append)
+    assert [g.slot for g in gone] == [s1] and len(ss) == 1
+    assert ss.find(toks, 39).tail_block == 9
+    assert sorted(ss._free) == sorted({0, 1, 2} - {s2})
+
+
+def test_resume_snapshot_survives_making_room():
+    """A KV pool so small that admitting the second turn has to drop saved snapshots: the snapshot chosen for the
+    resume must not be the one that is dropped (its tail block and state slot are about to be taken over)."""
+    cfg = CFGS["hybrid"]()
+    w = random_weights(cfg, "cpu", torch.float32, seed=0, std=0.05)
+    ec = dict(ctx_size=160, max_seqs=1, block_size=16, prefill_chunk=64, max_batch_tokens=128, kv_cache_tokens=176)
+    eng = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(**ec))
+    p1 = prompt(70, 4)
+    a = run(eng, p1, n=13)
+    # other conversations leave their own tail saves behind and fill the pool
+    for s in (11, 12):
+        run(eng, prompt(20, s), n=5)
+    turn2 = p1 + a.token_ids[:-1] + prompt(60, 5)
+    b = run(eng, turn2, n=8)
+    cold = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(prefix_cache=False, **ec))
+    want = run(cold, turn2, n=8).token_ids
+    cold.shutdown()
+    eng.shutdown()
+    assert b.token_ids == want
