@@ -6,6 +6,7 @@
 #include "comm.h"
 #include "ep.h"
 #include "gdn.h"
+#include "gemm_nvfp4_sm100.h"
 #include "quant.h"
 
 namespace {
@@ -15,6 +16,10 @@ cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
 template <typename T>
 const T* optp(const OptT& t) {
   return t.has_value() ? reinterpret_cast<const T*>(t->data_ptr()) : nullptr;
+}
+template <typename T>
+T* optpm(const OptT& t) {
+  return t.has_value() ? reinterpret_cast<T*>(t->data_ptr()) : nullptr;
 }
 
 lb::CommPeers make_peers(const std::vector<int64_t>& buffers, const std::vector<int64_t>& signals, int64_t rank) {
@@ -224,6 +229,95 @@ void bind_quant(pybind11::module_& m) {
     TORCH_CHECK(lb::fp8_act_quant_launch(x.data_ptr(), x.stride(0), x.size(0), x.size(1),
                                          reinterpret_cast<uint8_t*>(out.data_ptr()), scale.data_ptr<float>(),
                                          cur_stream()) == 0, "fp8_act_quant: K must be a multiple of 128, rows 8-byte aligned");
+  });
+  // ---- native NVFP4 (W4A4): scale atoms, activation quantiser, GEMM
+  m.def("nv4_sf_bytes", [](int64_t rows, int64_t K) { return int64_t(lb::nv4_sf_bytes(rows, K)); });
+  m.def("nv4_pack_scales", [](const Tensor& scales, Tensor& atoms) {
+    TORCH_CHECK(scales.dim() == 2 && scales.is_contiguous() && scales.element_size() == 1 && atoms.is_contiguous() &&
+                    atoms.element_size() == 1, "nv4_pack_scales: scales [rows, K / 16] bytes");
+    const long rows = scales.size(0), K = scales.size(1) * 16;
+    TORCH_CHECK(size_t(atoms.numel()) >= lb::nv4_sf_bytes(rows, K), "nv4_pack_scales: atom buffer too small");
+    c10::cuda::CUDAGuard guard(scales.device());
+    TORCH_CHECK(lb::nv4_pack_scales_launch(reinterpret_cast<const uint8_t*>(scales.data_ptr()), rows, K,
+                                           reinterpret_cast<uint8_t*>(atoms.data_ptr()), cur_stream()) == 0,
+                "nv4_pack_scales failed");
+  });
+  m.def("nv4_unpack_scales", [](const Tensor& atoms, Tensor& scales) {
+    TORCH_CHECK(scales.dim() == 2 && scales.is_contiguous() && scales.element_size() == 1 && atoms.is_contiguous(),
+                "nv4_unpack_scales: scales [rows, K / 16] bytes");
+    const long rows = scales.size(0), K = scales.size(1) * 16;
+    TORCH_CHECK(size_t(atoms.numel()) >= lb::nv4_sf_bytes(rows, K), "nv4_unpack_scales: atom buffer too small");
+    c10::cuda::CUDAGuard guard(scales.device());
+    TORCH_CHECK(lb::nv4_unpack_scales_launch(reinterpret_cast<const uint8_t*>(atoms.data_ptr()), rows, K,
+                                             reinterpret_cast<uint8_t*>(scales.data_ptr()), cur_stream()) == 0,
+                "nv4_unpack_scales failed");
+  });
+  m.def("nv4_act_quant", [](const Tensor& x, const OptT& residual, const OptT& sum_out, const OptT& norm_w, double eps,
+                            double w_offset, const OptT& normed_out, const OptT& gscale_static, Tensor& codes,
+                            Tensor& sf_atoms, const OptT& row_gscale) {
+    TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "nv4_act_quant: x bf16 [T, K]");
+    const long rows = x.size(0), K = x.size(1);
+    TORCH_CHECK(codes.element_size() == 1 && codes.dim() == 2 && codes.stride(1) == 1 && codes.size(0) >= rows &&
+                    codes.size(1) * 2 == K, "nv4_act_quant: codes [T, K / 2] bytes");
+    TORCH_CHECK(sf_atoms.is_contiguous() && size_t(sf_atoms.numel()) >= lb::nv4_sf_bytes(rows, K),
+                "nv4_act_quant: scale atom buffer too small");
+    TORCH_CHECK(gscale_static.has_value() || (row_gscale.has_value() && row_gscale->numel() >= rows),
+                "nv4_act_quant: a static scale or a row-scale output is needed");
+    c10::cuda::CUDAGuard guard(x.device());
+    TORCH_CHECK(lb::nv4_act_quant_launch(x.data_ptr(), x.stride(0), residual.has_value() ? residual->data_ptr() : nullptr,
+                                         residual.has_value() ? residual->stride(0) : 0,
+                                         sum_out.has_value() ? sum_out->data_ptr() : nullptr,
+                                         sum_out.has_value() ? sum_out->stride(0) : 0, optp<float>(norm_w), float(eps),
+                                         float(w_offset), normed_out.has_value() ? normed_out->data_ptr() : nullptr,
+                                         normed_out.has_value() ? normed_out->stride(0) : 0, rows, K,
+                                         optp<float>(gscale_static), reinterpret_cast<uint8_t*>(codes.data_ptr()),
+                                         codes.stride(0), reinterpret_cast<uint8_t*>(sf_atoms.data_ptr()),
+                                         optpm<float>(row_gscale), cur_stream()) == 0,
+                "nv4_act_quant: K must be a multiple of 16 and at most 8192, rows 16-byte aligned");
+  });
+  m.def("wgemm_nv4", [](const Tensor& w, const Tensor& w_sf, const OptT& w_gscale, const Tensor& x, const Tensor& x_sf,
+                        const OptT& x_gscale, int64_t x_gs_stride, const OptT& out, const OptT& residual,
+                        const OptT& tok_scale, const OptT& out_rows, int64_t n_feat, bool dual, int64_t dual_offset,
+                        int64_t act, int64_t bn, Tensor& status, const OptT& tile_group, const OptT& tile_tok0,
+                        const OptT& tile_ntok, const OptT& meta, int64_t max_tiles, int64_t rows_per_group, int64_t n_tok,
+                        const OptT& tile_out0, const OptT& q_codes, const OptT& q_sf, const OptT& q_gscale) {
+    TORCH_CHECK(w.is_cuda() && w.dim() == 2 && x.dim() == 2 && w.element_size() == 1 && x.element_size() == 1 &&
+                    w.stride(1) == 1 && x.stride(1) == 1 && w.size(1) == x.size(1),
+                "wgemm_nv4: w [rows, K / 2] and x [tokens, K / 2] are packed e2m1 bytes with the same K");
+    const long K = x.size(1) * 2;
+    TORCH_CHECK(w_sf.is_contiguous() && size_t(w_sf.numel()) >= lb::nv4_sf_bytes(w.size(0), K) && x_sf.is_contiguous() &&
+                    size_t(x_sf.numel()) >= lb::nv4_sf_bytes(x.size(0), K), "wgemm_nv4: scale atom buffers too small");
+    c10::cuda::CUDAGuard guard(w.device());
+    lb::Nv4Host h{};
+    h.w = reinterpret_cast<const uint8_t*>(w.data_ptr()); h.w_rows = w.size(0); h.ldw = w.stride(0);
+    h.w_sf = reinterpret_cast<const uint8_t*>(w_sf.data_ptr()); h.w_gscale = optp<float>(w_gscale);
+    h.x = reinterpret_cast<const uint8_t*>(x.data_ptr()); h.x_rows = x.size(0); h.ldx = x.stride(0);
+    h.x_sf = reinterpret_cast<const uint8_t*>(x_sf.data_ptr());
+    h.x_gscale = optp<float>(x_gscale); h.x_gs_stride = int(x_gs_stride);
+    if (out.has_value()) {
+      TORCH_CHECK(out->scalar_type() == at::kBFloat16 && out->dim() == 2 && out->stride(1) == 1 && out->size(1) >= n_feat,
+                  "wgemm_nv4: out must be bf16 [rows, >= n_feat]");
+      h.out = out->data_ptr(); h.ldo = out->stride(0);
+    }
+    if (residual.has_value()) {
+      TORCH_CHECK(residual->scalar_type() == at::kBFloat16 && residual->stride(1) == 1, "wgemm_nv4: residual bf16");
+      h.residual = reinterpret_cast<const __nv_bfloat16*>(residual->data_ptr()); h.ldr = residual->stride(0);
+    }
+    h.tok_scale = optp<float>(tok_scale); h.out_rows = optp<int>(out_rows);
+    if (q_codes.has_value()) {
+      TORCH_CHECK(q_sf.has_value() && q_gscale.has_value() && q_codes->dim() == 2 && q_codes->stride(1) == 1 &&
+                      q_codes->size(1) * 2 >= n_feat && q_sf->is_contiguous() &&
+                      size_t(q_sf->numel()) >= lb::nv4_sf_bytes(q_codes->size(0), n_feat),
+                  "wgemm_nv4: quantised output needs codes [rows, n_feat / 2], scale atoms and a tensor scale");
+      h.q_codes = reinterpret_cast<uint8_t*>(q_codes->data_ptr()); h.q_ld = q_codes->stride(0);
+      h.q_sf = reinterpret_cast<uint8_t*>(q_sf->data_ptr()); h.q_gscale = q_gscale->data_ptr<float>();
+    }
+    h.K = int(K); h.n_feat = int(n_feat); h.n_tok = int(n_tok); h.bn = int(bn); h.dual = dual; h.act = int(act);
+    h.tile_group = optp<int>(tile_group); h.tile_tok0 = optp<int>(tile_tok0); h.tile_ntok = optp<int>(tile_ntok);
+    h.n_tiles_dev = optp<int>(meta); h.tile_out0 = optp<int>(tile_out0); h.n_tok_tiles_max = int(max_tiles);
+    h.rows_per_group = int(rows_per_group); h.dual_offset = int(dual_offset);
+    h.status = reinterpret_cast<int*>(status.data_ptr());
+    TORCH_CHECK(lb::wgemm_nv4_launch(h, cur_stream()) == 0, lb::wgemm_nv4_last_error());
   });
   m.def("gguf_dequant", [](const Tensor& raw, int64_t ggml_type, Tensor& out) {
     TORCH_CHECK(raw.scalar_type() == at::kByte && raw.is_contiguous() && out.scalar_type() == at::kBFloat16 &&

@@ -239,6 +239,144 @@ class QWeight:
         return out.reshape(self.shape)
 
 
+class Nv4Weight:
+    """NVFP4 weight in the layout of the native block-scaled GEMM (``csrc/gemm_nvfp4_sm100.cu``): ``codes`` uint8
+    [..., rows, K/2] exactly as shipped (two e2m1 values per byte, low nibble first), ``sf`` the UE4M3 block scales
+    re-ordered into 512-byte atoms (128 rows x 4 blocks, the order tcgen05.cp wants; same bytes, other order),
+    ``gscale`` float32 per tensor (per expert; two per expert for a fused gate/up stack). Rows per leading index
+    must be a multiple of 128. Activations are quantised to NVFP4 as well (W4A4), so the tensor cores run the
+    e2m1 x e2m1 block-scaled instruction and nothing is expanded."""
+    __slots__ = ("codes", "sf", "gscale", "scales_lin")
+
+    def __init__(self, codes, sf, gscale, scales_lin=None):
+        self.codes, self.sf, self.gscale = codes, sf, gscale.float().reshape(-1).contiguous()
+        self.scales_lin = scales_lin          # kept only when asked for (tests / de-quantisation)
+
+    @property
+    def shape(self):
+        return tuple(self.codes.shape[:-1]) + (self.codes.shape[-1] * 2,)
+
+    @property
+    def device(self):
+        return self.codes.device
+
+    def dim(self):
+        return self.codes.dim()
+
+    def view2d(self):
+        return self.codes.reshape(-1, self.codes.shape[-1])
+
+    @classmethod
+    def from_parts(cls, codes, scales, gscale, keep_linear: bool = False):
+        """From the checkpoint tensors: codes [..., rows, K/2], scales e4m3 bytes [..., rows, K/16], tensor scale(s)."""
+        C = ext()
+        rows = codes.shape[-2]
+        if codes.dim() > 2 and rows % 128:
+            raise ValueError("stacked NVFP4 weights need a multiple of 128 rows per slice")
+        c2 = codes.reshape(-1, codes.shape[-1]).contiguous()
+        s2 = scales.view(torch.uint8).reshape(-1, scales.shape[-1]).contiguous()
+        K = c2.shape[1] * 2
+        atoms = torch.zeros(C.nv4_sf_bytes(c2.shape[0], K), dtype=torch.uint8, device=codes.device)
+        C.nv4_pack_scales(s2, atoms)
+        return cls(codes.contiguous(), atoms, gscale, s2 if keep_linear else None)
+
+    @classmethod
+    def from_qweight(cls, q: "QWeight", keep_linear: bool = False):
+        return cls.from_parts(q.codes, q.scales, q.gscale, keep_linear)
+
+    @classmethod
+    def quantize_cuda(cls, w: torch.Tensor, dual_rows: int = 0, keep_linear: bool = False):
+        return cls.from_qweight(QWeight.quantize_cuda(w, dual_rows), keep_linear)
+
+    def dequantize(self, dtype=torch.bfloat16):
+        C = ext()
+        c2 = self.view2d()
+        K = c2.shape[1] * 2
+        lin = torch.empty(c2.shape[0], K // 16, dtype=torch.uint8, device=self.device)
+        C.nv4_unpack_scales(self.sf, lin)
+        return QWeight(self.codes, lin.view(*self.codes.shape[:-1], K // 16), self.gscale).dequantize(dtype)
+
+
+class Nv4Act:
+    """NVFP4-encoded activation rows: codes [T, K/2], scale atoms, and the fp32 scale (one per row, or one device
+    scalar for all rows when ``stride`` is 0)."""
+    __slots__ = ("codes", "sf", "gscale", "stride", "normed", "summed")
+
+    def __init__(self, codes, sf, gscale, stride, normed=None, summed=None):
+        self.codes, self.sf, self.gscale, self.stride, self.normed, self.summed = codes, sf, gscale, stride, normed, summed
+
+    def dequantize(self):
+        C = ext()
+        T, K = self.codes.shape[0], self.codes.shape[1] * 2
+        lin = torch.empty(T, K // 16, dtype=torch.uint8, device=self.codes.device)
+        C.nv4_unpack_scales(self.sf, lin)
+        from ..loaders.quant_formats import nvfp4_dequant
+        out = nvfp4_dequant(self.codes.cpu(), lin.cpu(), 1.0, out_dtype=torch.float32).to(self.codes.device)
+        g = self.gscale.reshape(-1)[:1] if self.stride == 0 else self.gscale[:T]
+        return out * g.reshape(-1, 1)
+
+
+def nv4_quant_act(x, norm=None, residual=None, static_scale=None, want_normed: bool = False, key=None):
+    """bf16 rows [T, K] -> ``Nv4Act``. ``norm=(weight, eps, w_offset)`` fuses the RMSNorm that produces the rows
+    (and ``residual`` the add before it: ``summed`` is then the new residual stream); ``static_scale`` is a device
+    scalar used for every row instead of the per-row amax scale. ``key``: reuse the same output storage on every
+    call with that key (graph-safe)."""
+    C = ext()
+    T, K = x.shape
+    ws = Workspace.get(x.device)
+    if key is not None:
+        codes = ws.buf((key, "c"), (T, K // 2), torch.uint8)
+        sf = ws.buf((key, "s"), (C.nv4_sf_bytes(T, K),), torch.uint8)
+        gs = ws.buf((key, "g"), (max(T, 1),), torch.float32) if static_scale is None else static_scale
+    else:
+        codes = torch.empty(T, K // 2, dtype=torch.uint8, device=x.device)
+        sf = torch.empty(C.nv4_sf_bytes(T, K), dtype=torch.uint8, device=x.device)
+        gs = torch.empty(max(T, 1), dtype=torch.float32, device=x.device) if static_scale is None else static_scale
+    normed = torch.empty_like(x) if (want_normed and norm is not None) else None
+    summed = torch.empty_like(x) if residual is not None else None
+    C.nv4_act_quant(x, residual, summed, norm[0] if norm else None, norm[1] if norm else 0.0, norm[2] if norm else 0.0,
+                    normed, static_scale, codes, sf, None if static_scale is not None else gs)
+    return Nv4Act(codes, sf, gs, 0 if static_scale is not None else 1, normed, summed)
+
+
+def linear_nv4(xq: "Nv4Act", w: "Nv4Weight", residual=None, out=None, bn=None):
+    """out[T, N] = dequant(xq) @ dequant(w)^T (+ residual) on the native NVFP4 tensor-core path."""
+    C = ext()
+    T = xq.codes.shape[0]
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty(T, N, dtype=torch.bfloat16, device=xq.codes.device)
+    if T == 0:
+        return out
+    ws = Workspace.get(xq.codes.device)
+    bn = bn or (32 if T <= 32 else (64 if T <= 64 else 128))
+    C.wgemm_nv4(w.view2d(), w.sf, w.gscale, xq.codes, xq.sf, xq.gscale, xq.stride, out, residual, None, None, N, False,
+                0, 0, bn, ws.status, None, None, None, None, 0, 0, T, None, None, None, None)
+    return out
+
+
+def gate_up_nv4(xq: "Nv4Act", w: "Nv4Weight", n_ff: int, act: str = "silu", out=None, q_scale=None, bn=None):
+    """act(x Wg^T) * (x Wu^T) with Wg = w[:n_ff], Wu = w[n_ff:]. With ``q_scale`` (device scalar) the result is
+    returned NVFP4-encoded (``Nv4Act`` with that static tensor scale) for the next GEMM."""
+    C = ext()
+    T = xq.codes.shape[0]
+    dev = xq.codes.device
+    ws = Workspace.get(dev)
+    bn = bn or (32 if T <= 32 else 64)
+    a = 0 if act == "silu" else 1
+    if q_scale is not None:
+        qc = torch.empty(T, n_ff // 2, dtype=torch.uint8, device=dev)
+        qs = torch.zeros(C.nv4_sf_bytes(T, n_ff), dtype=torch.uint8, device=dev)
+        C.wgemm_nv4(w.view2d(), w.sf, w.gscale, xq.codes, xq.sf, xq.gscale, xq.stride, None, None, None, None, n_ff,
+                    True, n_ff, a, bn, ws.status, None, None, None, None, 0, 0, T, None, qc, qs, q_scale)
+        return Nv4Act(qc, qs, q_scale, 0)
+    if out is None:
+        out = torch.empty(T, n_ff, dtype=torch.bfloat16, device=dev)
+    C.wgemm_nv4(w.view2d(), w.sf, w.gscale, xq.codes, xq.sf, xq.gscale, xq.stride, out, None, None, None, n_ff, True,
+                n_ff, a, bn, ws.status, None, None, None, None, 0, 0, T, None, None, None, None)
+    return out
+
+
 def pick_bn(n_tok: int, dual: bool) -> int:
     bn = 32
     cap = 128 if dual else 256

@@ -1,0 +1,102 @@
+"""Native NVFP4 (W4A4) path: scale-atom layout, activation quantiser (plain and fused with RMSNorm), and the
+block-scaled tcgen05 GEMM in its dense, gate/up (+ SwiGLU), grouped and quantised-output forms, each against the
+fp32 product of the de-quantised operands."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda")
+
+
+def _w(rows, K, seed, std=0.05):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(rows, K, generator=g) * std).bfloat16().to(_dev())
+
+
+def test_scale_atoms_round_trip():
+    from legion_b200.ops import sm100
+    C = sm100.ext()
+    for rows, K in ((128, 256), (300, 2048), (512, 192)):
+        lin = torch.randint(1, 127, (rows, K // 16), dtype=torch.uint8, device=_dev())
+        atoms = torch.zeros(C.nv4_sf_bytes(rows, K), dtype=torch.uint8, device=_dev())
+        C.nv4_pack_scales(lin, atoms)
+        back = torch.zeros_like(lin)
+        C.nv4_unpack_scales(atoms, back)
+        assert torch.equal(back, lin)
+        # spot check of the documented position: row r, block b
+        r, b = rows - 3, K // 16 - 1
+        k4 = ((K + 255) // 256) * 4
+        off = ((r >> 7) * k4 + (b >> 2)) * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4 + (b & 3)
+        assert int(atoms[off]) == int(lin[r, b])
+
+
+def test_activation_quantiser_plain_and_with_rmsnorm():
+    from legion_b200.ops import reference as ref
+    from legion_b200.ops import sm100
+    torch.manual_seed(0)
+    for T, K in ((5, 2048), (40, 512), (130, 4096)):
+        x = (torch.randn(T, K, device=_dev()) * torch.rand(T, 1, device=_dev()) * 3).bfloat16()
+        q = sm100.nv4_quant_act(x)
+        deq = q.dequantize()
+        blk = x.float().view(T, K // 16, 16).abs().amax(-1, keepdim=True).expand(T, K // 16, 16).reshape(T, K)
+        err = (deq - x.float()).abs()
+        assert float((err - 0.19 * blk).max()) <= 1e-6          # half of the coarsest e2m1 step (+ scale rounding)
+        assert float(err.mean() / x.float().abs().mean()) < 0.12
+        # fused residual add + RMSNorm + quantisation
+        res = torch.randn(T, K, device=_dev()).bfloat16()
+        w = torch.rand(K, device=_dev()) + 0.5
+        q2 = sm100.nv4_quant_act(x, norm=(w, 1e-6, 0.0), residual=res, want_normed=True)
+        summed = (x.float() + res.float()).bfloat16()
+        want_n, _ = ref.rmsnorm(summed, w, 1e-6)
+        assert torch.equal(q2.summed, summed)
+        assert float((q2.normed.float() - want_n.float()).abs().max()) < 0.04
+        q3 = sm100.nv4_quant_act(q2.normed)
+        assert torch.equal(q3.codes, q2.codes) and torch.equal(q3.gscale[:T], q2.gscale[:T])
+
+
+@pytest.mark.parametrize("T,N,K,bn", [(16, 256, 2048, 32), (50, 384, 512, 64), (1, 128, 256, 32), (200, 512, 1024, 128),
+                                      (33, 256, 320, 64)])
+def test_dense_linear_matches_dequantised_product(T, N, K, bn):
+    from legion_b200.ops import sm100
+    w = _w(N, K, 1)
+    x = (torch.randn(T, K, device=_dev()) * 0.7).bfloat16()
+    qw = sm100.Nv4Weight.quantize_cuda(w)
+    qx = sm100.nv4_quant_act(x)
+    res = torch.randn(T, N, device=_dev()).bfloat16()
+    out = sm100.linear_nv4(qx, qw, residual=res, bn=bn)
+    want = qx.dequantize() @ qw.dequantize(torch.float32).t() + res.float()
+    assert sm100.Workspace.get(_dev()).check() == 0
+    assert float((out.float() - want).abs().max()) < 0.02 * float(want.abs().max()) + 1e-3
+    # the quantised product itself is close to the bf16 one (4-bit noise)
+    full = x.float() @ w.float().t() + res.float()
+    assert float((out.float() - full).abs().mean() / full.abs().mean()) < 0.2
+
+
+@pytest.mark.parametrize("T,F,K,bn", [(16, 512, 2048, 32), (64, 256, 512, 64)])
+def test_gate_up_swiglu_bf16_and_quantised_output(T, F, K, bn):
+    from legion_b200.ops import sm100
+    w = _w(2 * F, K, 2)
+    x = (torch.randn(T, K, device=_dev()) * 0.7).bfloat16()
+    qw = sm100.Nv4Weight.quantize_cuda(w, dual_rows=F)
+    qx = sm100.nv4_quant_act(x)
+    h = sm100.gate_up_nv4(qx, qw, F, bn=bn)
+    wd = qw.dequantize(torch.float32)
+    xd = qx.dequantize()
+    g, u = xd @ wd[:F].t(), xd @ wd[F:].t()
+    want = torch.nn.functional.silu(g) * u
+    assert float((h.float() - want).abs().max()) < 0.02 * float(want.abs().max()) + 1e-3
+    # re-encoded output: de-quantising it gives the SwiGLU result up to 4-bit rounding, and a down projection from
+    # it equals the product of the de-quantised operands
+    qs = torch.tensor([float(want.abs().max()) / (6 * 448)], device=_dev())
+    hq = sm100.gate_up_nv4(qx, qw, F, bn=bn, q_scale=qs)
+    hd = hq.dequantize()
+    blk = want.view(T, F // 16, 16).abs().amax(-1, keepdim=True).expand(T, F // 16, 16).reshape(T, F)
+    assert float(((hd - want).abs() - 0.2 * blk).max()) <= 2e-3
+    wdn = sm100.Nv4Weight.quantize_cuda(_w(256, F, 3))
+    y = sm100.linear_nv4(hq, wdn)
+    want_y = hd @ wdn.dequantize(torch.float32).t()
+    assert sm100.Workspace.get(_dev()).check() == 0
+    assert float((y.float() - want_y).abs().max()) < 0.02 * float(want_y.abs().max()) + 1e-3
