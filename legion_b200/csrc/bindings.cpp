@@ -414,15 +414,24 @@ void moe_route_small(const Tensor& x, const OptT& norm_w, double eps, double w_o
                      const Tensor& w, const OptT& bias, int64_t k, int64_t mode, bool renorm, double route_scale,
                      int64_t n_group, int64_t topk_group, Tensor& logits, Tensor& ids, Tensor& wts, int64_t bn,
                      Tensor& tile_group, Tensor& slot_base, Tensor& tile_ntok, Tensor& meta, Tensor& out_rows,
-                     Tensor& tok_scale, Tensor& done_ctr, int64_t e_lo, int64_t n_local) {
+                     Tensor& tok_scale, Tensor& done_ctr, int64_t e_lo, int64_t n_local, const OptT& sh_gate_w,
+                     const OptT& sh_logit, bool shared_slot) {
   check_bf16(x, "x");
   check_bf16(w, "w");
   const int64_t T = x.size(0), E = w.size(0);
+  if (sh_gate_w.has_value()) {
+    check_bf16(*sh_gate_w, "sh_gate_w");
+    TORCH_CHECK(sh_gate_w->numel() == x.size(1) && sh_gate_w->is_contiguous() && sh_logit.has_value() &&
+                    sh_logit->scalar_type() == at::kFloat && sh_logit->numel() >= T && shared_slot,
+                "moe_route_small: the shared gate is one row of the hidden width with a float [T] scratch");
+  }
   TORCH_CHECK(x.size(1) == w.size(1) && x.stride(1) == 1 && w.stride(1) == 1, "moe_route_small: shape mismatch");
   TORCH_CHECK(norm_w.has_value() == x_normed.has_value(), "moe_route_small: norm weight and output go together");
   TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.numel() >= T * E, "moe_route_small: logits too small");
-  TORCH_CHECK(tile_group.numel() >= E && slot_base.numel() >= E && tile_ntok.numel() >= E && meta.numel() >= 2 &&
-                  out_rows.numel() >= E * bn && tok_scale.numel() >= E * bn, "moe_route_small: tables too small");
+  const int64_t max_slots = std::min<int64_t>(E, n_local) + (shared_slot ? 1 : 0);
+  TORCH_CHECK(tile_group.numel() >= max_slots && slot_base.numel() >= max_slots && tile_ntok.numel() >= max_slots &&
+                  meta.numel() >= 2 && out_rows.numel() >= max_slots * bn && tok_scale.numel() >= max_slots * bn,
+              "moe_route_small: tables too small");
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(lb::moe_route_small_launch(
                   x.data_ptr(), x.stride(0), optp<float>(norm_w), float(eps), float(w_offset),
@@ -432,7 +441,9 @@ void moe_route_small(const Tensor& x, const OptT& norm_w, double eps, double w_o
                   float(route_scale), int(n_group), int(topk_group), ids.data_ptr<int>(), wts.data_ptr<float>(),
                   int(T), int(bn), tile_group.data_ptr<int>(), slot_base.data_ptr<int>(), tile_ntok.data_ptr<int>(),
                   meta.data_ptr<int>(), out_rows.data_ptr<int>(), tok_scale.data_ptr<float>(),
-                  reinterpret_cast<unsigned int*>(done_ctr.data_ptr()), int(e_lo), int(n_local), cur_stream()) == 0,
+                  reinterpret_cast<unsigned int*>(done_ctr.data_ptr()), int(e_lo), int(n_local),
+                  sh_gate_w.has_value() ? sh_gate_w->data_ptr() : nullptr, optpm<float>(sh_logit), shared_slot ? 1 : 0,
+                  cur_stream()) == 0,
               "moe_route_small: unsupported (tokens <= 64 and <= bn, pairs <= 1024, experts <= 512, k <= 32)");
 }
 

@@ -169,7 +169,8 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
     float* logits, const float* __restrict__ bias, int E, int k, int mode, int renorm, float route_scale, int n_group,
     int topk_group, int* ids, float* wts, int T, int bn, int* __restrict__ tile_group, int* __restrict__ slot_base,
     int* __restrict__ tile_ntok, int* __restrict__ meta, int* __restrict__ out_rows, float* __restrict__ tok_scale,
-    unsigned int* done_ctr, int e_lo, int n_local) {
+    unsigned int* done_ctr, int e_lo, int n_local, const __nv_bfloat16* __restrict__ sh_gate_w, float* sh_logit,
+    int shared_slot) {
   __shared__ float red[2][8][8];
   __shared__ float s_inv[2][8];
   __shared__ int s_last;
@@ -183,7 +184,9 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // the two halves of the CTA take 8 tokens each per pass
   const int half = tid >> 8, htid = tid & 255, hwarp = warp & 7;
-  const uint4* w4 = reinterpret_cast<const uint4*>(w + long(e) * ldw);
+  // CTA E (present when the shared expert has a sigmoid gate) computes that gate's logit like one more router row
+  const bool is_gate = e >= E;
+  const uint4* w4 = reinterpret_cast<const uint4*>(is_gate ? sh_gate_w : w + long(e) * ldw);
   const int nv = H / 8;
   for (int base = 0; base < T; base += 16) {
     const int t0 = base + half * 8;
@@ -276,7 +279,8 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
       float tot = 0.f;
 #pragma unroll
       for (int i = 0; i < 8; ++i) tot += red[half][i][htid];
-      logits[long(t0 + htid) * E + e] = tot;
+      if (is_gate) sh_logit[t0 + htid] = tot;
+      else logits[long(t0 + htid) * E + e] = tot;
     }
     __syncthreads();
   }
@@ -323,7 +327,10 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
     __syncthreads();                 // every thread has read its count before the slot numbers replace them
     if (tid < E) s_slot[tid] = slot;
   }
-  for (int i = tid; i < n_active * bn; i += 512) out_rows[i] = -1;
+  // The shared expert (stacked behind this rank's routed experts as group n_local) takes one more slot that every
+  // token uses: its output rows are the pairs P .. P + T - 1, weighted by the sigmoid of its gate (or 1).
+  const int n_slots = n_active + (shared_slot ? 1 : 0);
+  for (int i = tid; i < n_slots * bn; i += 512) out_rows[i] = -1;
   __syncthreads();
   for (int p = tid; p < P; p += 512) {
     const int slot = s_slot[s_ids[p]];
@@ -332,9 +339,20 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
     out_rows[slot * bn + t] = p;
     tok_scale[slot * bn + t] = s_wts[p];
   }
+  if (shared_slot) {
+    for (int t = tid; t < T; t += 512) {
+      out_rows[n_active * bn + t] = P + t;
+      tok_scale[n_active * bn + t] = sh_gate_w ? 1.f / (1.f + __expf(-__ldcg(&sh_logit[t]))) : 1.f;
+    }
+  }
   if (tid == 0) {
-    meta[0] = n_active;
-    meta[1] = n_active * bn;
+    if (shared_slot) {
+      tile_group[n_active] = n_local;
+      slot_base[n_active] = n_active * bn;
+      tile_ntok[n_active] = T;
+    }
+    meta[0] = n_slots;
+    meta[1] = n_slots * bn;
   }
 }
 
@@ -342,16 +360,21 @@ int moe_route_small_launch(const void* x, long ldx, const float* norm_w, float e
                            long ldn, const void* w, long ldw, int H, float* logits, const float* bias, int E, int k,
                            int mode, int renorm, float route_scale, int n_group, int topk_group, int* ids, float* wts,
                            int T, int bn, int* tile_group, int* slot_base, int* tile_ntok, int* meta, int* out_rows,
-                           float* tok_scale, unsigned int* done_ctr, int e_lo, int n_local, cudaStream_t s) {
+                           float* tok_scale, unsigned int* done_ctr, int e_lo, int n_local, const void* sh_gate_w,
+                           float* sh_logit, int shared_slot, cudaStream_t s) {
   if (T <= 0) return 0;
   if (k > 32 || E > 512 || n_group > 32 || H % 8 || T > 64 || T * k > 1024 || T > bn) return 1;
+  if (sh_gate_w && (!sh_logit || !shared_slot)) return 1;
+  auto sg = static_cast<const __nv_bfloat16*>(sh_gate_w);
+  const int grid = E + (sh_gate_w ? 1 : 0);
   auto xb = static_cast<const __nv_bfloat16*>(x);
   auto xn = static_cast<__nv_bfloat16*>(x_normed);
   auto wb = static_cast<const __nv_bfloat16*>(w);
 #define LB_ROUTE(MAXE)                                                                                              \
-  launch_pdl(moe_route_small_kernel<MAXE>, dim3(E), dim3(512), 0, s, xb, ldx, norm_w, eps, w_offset, xn, ldn, wb,  \
-             ldw, H, logits, bias, E, k, mode, renorm, route_scale, n_group, topk_group, ids, wts, T, bn,           \
-             tile_group, slot_base, tile_ntok, meta, out_rows, tok_scale, done_ctr, e_lo, n_local)
+  launch_pdl(moe_route_small_kernel<MAXE>, dim3(grid), dim3(512), 0, s, xb, ldx, norm_w, eps, w_offset, xn, ldn,   \
+             wb, ldw, H, logits, bias, E, k, mode, renorm, route_scale, n_group, topk_group, ids, wts, T, bn,       \
+             tile_group, slot_base, tile_ntok, meta, out_rows, tok_scale, done_ctr, e_lo, n_local, sg, sh_logit,    \
+             shared_slot)
   if (E <= 128) LB_ROUTE(128);
   else if (E <= 256) LB_ROUTE(256);
   else LB_ROUTE(512);

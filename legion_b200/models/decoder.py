@@ -141,6 +141,74 @@ class StatePool:
         return sum(t[0].numel() * 4 for t in list(self.conv.values()) + list(self.ssm.values()))
 
 
+def fold_shared_expert(w: Dict[str, object], p: str, cfg: ModelConfig) -> bool:
+    """Stacks the shared expert of layer ``p`` behind the routed experts: ``{p}.moe.gate_up_s`` / ``down_s`` hold
+    E + 1 groups, and ``gate_up`` / ``down`` / ``sh_gate_up`` / ``sh_down`` become views of them (so prompt-sized
+    steps, which run the shared expert as a dense FFN, share the storage). Plain bf16 tensors only: quantise after
+    folding."""
+    gu, dn = w.get(f"{p}.moe.gate_up"), w.get(f"{p}.moe.down")
+    sgu, sdn = w.get(f"{p}.moe.sh_gate_up"), w.get(f"{p}.moe.sh_down")
+    if (not isinstance(gu, torch.Tensor) or not isinstance(sgu, torch.Tensor) or f"{p}.moe.gate_up_s" in w
+            or not gu.is_cuda or sgu.shape[0] != gu.shape[1] or sdn.shape[1] != dn.shape[2]):
+        return False
+    E = gu.shape[0]
+    gus = torch.empty(E + 1, *gu.shape[1:], dtype=gu.dtype, device=gu.device)
+    gus[:E].copy_(gu)
+    gus[E].copy_(sgu)
+    del gu
+    w[f"{p}.moe.gate_up"] = None
+    dns = torch.empty(E + 1, *dn.shape[1:], dtype=dn.dtype, device=dn.device)
+    dns[:E].copy_(dn)
+    dns[E].copy_(sdn)
+    w[f"{p}.moe.gate_up_s"], w[f"{p}.moe.down_s"] = gus, dns
+    w[f"{p}.moe.gate_up"], w[f"{p}.moe.down"] = gus[:E], dns[:E]
+    w[f"{p}.moe.sh_gate_up"], w[f"{p}.moe.sh_down"] = gus[E], dns[E]
+    return True
+
+
+def quantize_moe_layer_nvfp4(w: Dict[str, object], p: str, native: bool = True) -> int:
+    """NVFP4-encodes the expert tensors of MoE layer ``p`` in place (stacked form when the shared expert was
+    folded in, else the routed experts and the shared expert separately). Returns the bytes saved."""
+    from ..ops.sm100 import Nv4Weight, QWeight
+    cls = Nv4Weight if native else QWeight
+    saved = 0
+
+    def enc(t, dual):
+        nonlocal saved
+        rows, K = t.shape[-2], t.shape[-1]
+        ok = isinstance(t, torch.Tensor) and t.dtype == torch.bfloat16 and K % 256 == 0 and rows % 128 == 0 and \
+            (not dual or (rows // 2) % 128 == 0)
+        if not ok:
+            return None
+        saved += t.numel() * 2 - t.numel() * 9 // 16
+        return cls.quantize_cuda(t, dual_rows=rows // 2 if dual else 0)
+
+    if f"{p}.moe.gate_up_s" in w:
+        gus, dns = w[f"{p}.moe.gate_up_s"], w[f"{p}.moe.down_s"]
+        if not isinstance(gus, torch.Tensor):
+            return 0
+        E = gus.shape[0] - 1
+        for k in ("gate_up", "down", "sh_gate_up", "sh_down"):
+            w[f"{p}.moe.{k}"] = None
+        qg, qd = enc(gus, True), enc(dns, False)
+        if qg is None or qd is None:
+            w[f"{p}.moe.gate_up"], w[f"{p}.moe.down"] = gus[:E], dns[:E]
+            w[f"{p}.moe.sh_gate_up"], w[f"{p}.moe.sh_down"] = gus[E], dns[E]
+            return 0
+        w[f"{p}.moe.gate_up_s"], w[f"{p}.moe.down_s"] = qg, qd
+        w[f"{p}.moe.gate_up"], w[f"{p}.moe.down"] = qg.narrow(0, E), qd.narrow(0, E)
+        w[f"{p}.moe.sh_gate_up"] = qg.narrow(E, E + 1).squeeze0()
+        w[f"{p}.moe.sh_down"] = qd.narrow(E, E + 1).squeeze0()
+        return saved
+    for k, dual in (("gate_up", True), ("down", False), ("sh_gate_up", True), ("sh_down", False)):
+        t = w.get(f"{p}.moe.{k}")
+        if isinstance(t, torch.Tensor):
+            q = enc(t, dual)
+            if q is not None:
+                w[f"{p}.moe.{k}"] = q
+    return saved
+
+
 class Decoder:
     """Weights + forward. ``weights`` uses the canonical names of ``models.weights``."""
 
@@ -182,25 +250,27 @@ class Decoder:
                                                ssd_path=os.path.join(ssd_dir, f"{p}.experts.bin") if ssd_dir else None,
                                                ram_experts=ram_experts)
 
-    def quantize_experts_nvfp4(self) -> int:
-        """Re-encodes the routed experts of every MoE layer to NVFP4 in place (3.5x less HBM for the bulk of a MoE
-        model). The grouped GEMM then streams the 4-bit codes and expands them inside the kernel
-        (``ops.sm100.QWeight``). Returns the number of bytes saved. GPU only."""
-        from ..ops.sm100 import QWeight
+    def quantize_experts_nvfp4(self, native: bool = True) -> int:
+        """Re-encodes the routed experts (and the shared expert) of every MoE layer to NVFP4 in place: 3.5x less
+        HBM for the bulk of a MoE model. ``native``: the layout of the block-scaled tensor-core GEMM
+        (``ops.sm100.Nv4Weight``: activations are quantised to NVFP4 too and nothing is expanded); otherwise the
+        grouped GEMM streams the 4-bit codes and expands them inside the kernel (``ops.sm100.QWeight``).
+        Returns the number of bytes saved. GPU only."""
         saved = 0
         for il in range(self.cfg.n_layer):
-            p = f"l{il}"
-            if not self.cfg.is_moe_layer(il) or f"{p}.moe.gate_up" not in self.w:
-                continue
-            gu, dn = self.w[f"{p}.moe.gate_up"], self.w[f"{p}.moe.down"]
-            if isinstance(gu, QWeight) or gu.shape[-1] % 256 or dn.shape[-1] % 256:
-                continue
-            before = gu.numel() * 2 + dn.numel() * 2
-            self.w[f"{p}.moe.gate_up"] = QWeight.quantize_cuda(gu, dual_rows=gu.shape[1] // 2)
-            self.w[f"{p}.moe.down"] = QWeight.quantize_cuda(dn)
-            del gu, dn
-            saved += before - before * 9 // 32
+            if self.cfg.is_moe_layer(il):
+                saved += quantize_moe_layer_nvfp4(self.w, f"l{il}", native)
         return saved
+
+    def fold_shared_experts(self) -> int:
+        """Stacks every MoE layer's shared expert behind its routed experts (when both have the same width) so that
+        decode-sized steps run it as one more slot of the grouped GEMMs instead of three launches of its own.
+        Returns the number of layers folded."""
+        n = 0
+        for il in range(self.cfg.n_layer):
+            if self.cfg.is_moe_layer(il) and fold_shared_expert(self.w, f"l{il}", self.cfg):
+                n += 1
+        return n
 
     FP8_LEAVES = ("attn.qkv", "attn.o", "mlp.gate_up", "mlp.down", "moe.gate_up", "moe.down", "moe.sh_gate_up",
                   "moe.sh_down", "mla.q_a", "mla.q_b", "mla.q", "mla.kv_a", "mla.o", "gdn.in_qkv", "gdn.in_z", "gdn.out")
@@ -370,9 +440,16 @@ class Decoder:
     def _route(self, p: str, x, norm=None):
         cfg, w, pc = self.cfg, self.w, self.pctx
         e_lo, e_hi = pc.expert_range(cfg.n_expert)
+        kw = {}
+        if x.is_cuda:
+            stacked = w.get(f"{p}.moe.gate_up_s")
+            if stacked is not None:     # the shared expert rides in the grouped GEMMs of decode-sized steps
+                kw = dict(shared_slot=True, sh_gate=w.get(f"{p}.moe.sh_gate") if cfg.shared_gate else None)
+            if isinstance(stacked if stacked is not None else w.get(f"{p}.moe.gate_up"), ops.sm100.Nv4Weight):
+                kw["slot_stride"] = 128
         return ops.router(x, w[f"{p}.moe.router"], cfg.top_k, cfg.router_mode, cfg.norm_topk,
                           cfg.route_scale, w.get(f"{p}.moe.router_bias"), cfg.n_group, cfg.topk_group,
-                          e_lo=e_lo, n_local=e_hi - e_lo, norm=norm)
+                          e_lo=e_lo, n_local=e_hi - e_lo, norm=norm, **kw)
 
     def _ffn(self, p: str, il_moe: bool, x, residual, next_norm=None, routing=None):
         """Returns (out, fused, normed). ``fused``: the residual is already added (TP == 1). ``normed``: the
@@ -385,7 +462,8 @@ class Decoder:
                 routing = self._route(p, x)
             ids, wts = routing
             shared = gate = None
-            if cfg.shared_ff > 0:
+            folded = bool(getattr(routing, "shared_slot", False))
+            if cfg.shared_ff > 0 and not folded:
                 fs = w[f"{p}.moe.sh_down"].shape[1]
                 hs = ops.gate_up_act(x, w[f"{p}.moe.sh_gate_up"], fs, cfg.ffn_act)
                 shared = ops.linear(hs, w[f"{p}.moe.sh_down"])
@@ -399,6 +477,8 @@ class Decoder:
                 w_gu, w_dn = cache.weights()
                 e_lo = 0
                 routing = None
+            elif folded:
+                w_gu, w_dn = w[f"{p}.moe.gate_up_s"], w[f"{p}.moe.down_s"]
             else:
                 w_gu, w_dn = w[f"{p}.moe.gate_up"], w[f"{p}.moe.down"]
             n_ff = w_dn.shape[2]

@@ -83,14 +83,15 @@ def router_topk(logits, k, mode="softmax", renorm=True, route_scale=1.0, bias=No
 
 
 def router(x, w_router, k, mode="softmax", renorm=True, route_scale=1.0, bias=None, n_group=1, topk_group=1,
-           e_lo=0, n_local=None, norm=None):
+           e_lo=0, n_local=None, norm=None, **gpu_kw):
     """Router projection + top-k. Returns an object that unpacks as ``ids, wts`` ([T, k] int32 / float32); on the
     GPU it may also carry the dense routing tables of a decode-sized step for the experts
     [e_lo, e_lo + n_local) of this rank (pass it on as ``routing=``). With ``norm=(weight, eps, w_offset)`` ``x`` is
     the raw residual stream: the RMSNorm runs first (inside the routing launch for decode-sized steps on the GPU)
     and the result's ``x_normed`` is the normalised input for the experts."""
     if _cuda(x):
-        return _sm.router(x, w_router, k, mode, renorm, route_scale, bias, n_group, topk_group, norm, e_lo, n_local)
+        return _sm.router(x, w_router, k, mode, renorm, route_scale, bias, n_group, topk_group, norm, e_lo, n_local,
+                          **gpu_kw)
     xn = None
     if norm is not None:
         xn, _ = _ref.rmsnorm(x, norm[0], norm[1], norm[2])

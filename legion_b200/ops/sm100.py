@@ -178,6 +178,15 @@ class QWeight:
     def view2d(self):
         return self.codes.reshape(-1, self.codes.shape[-1]), self.scales.reshape(-1, self.scales.shape[-1])
 
+    def narrow(self, lo: int, hi: int) -> "QWeight":
+        """Groups [lo, hi) of a stacked weight (a view: no copy). hi == lo + 1 with ``squeeze`` semantics is
+        ``narrow(lo, lo + 1).squeeze0()``."""
+        per = self.gscale.numel() // self.codes.shape[0]
+        return QWeight(self.codes[lo:hi], self.scales[lo:hi], self.gscale[lo * per:hi * per])
+
+    def squeeze0(self) -> "QWeight":
+        return QWeight(self.codes[0], self.scales[0], self.gscale)
+
     @classmethod
     def quantize(cls, w: torch.Tensor, dual_rows: int = 0):
         """Encodes a bf16/fp32 weight [..., rows, K] (tests, synthetic checkpoints). ``dual_rows`` > 0: the tensor is
@@ -288,13 +297,34 @@ class Nv4Weight:
     def quantize_cuda(cls, w: torch.Tensor, dual_rows: int = 0, keep_linear: bool = False):
         return cls.from_qweight(QWeight.quantize_cuda(w, dual_rows), keep_linear)
 
+    def narrow(self, lo: int, hi: int) -> "Nv4Weight":
+        """Groups [lo, hi) of a stacked weight (views of the same storage)."""
+        n, rows = self.codes.shape[0], self.codes.shape[-2]
+        per = self.gscale.numel() // n
+        bpg = self.sf.numel() // n                    # scale-atom bytes per group (rows are a multiple of 128)
+        lin = None
+        if self.scales_lin is not None:
+            lin = self.scales_lin[lo * rows:hi * rows]
+        return Nv4Weight(self.codes[lo:hi], self.sf[lo * bpg:hi * bpg], self.gscale[lo * per:hi * per], lin)
+
+    def squeeze0(self) -> "Nv4Weight":
+        return Nv4Weight(self.codes[0], self.sf, self.gscale, self.scales_lin)
+
+    def as_qweight(self) -> "QWeight":
+        """The same weight with its block scales in the checkpoint's linear order (for the de-quantising GEMM that
+        serves prompt-sized steps); the linear copy is made on first use and kept."""
+        if self.scales_lin is None:
+            C = ext()
+            c2 = self.view2d()
+            K = c2.shape[1] * 2
+            lin = torch.empty(c2.shape[0], K // 16, dtype=torch.uint8, device=self.device)
+            C.nv4_unpack_scales(self.sf, lin)
+            self.scales_lin = lin
+        K16 = self.codes.shape[-1] // 8
+        return QWeight(self.codes, self.scales_lin.view(*self.codes.shape[:-1], K16), self.gscale)
+
     def dequantize(self, dtype=torch.bfloat16):
-        C = ext()
-        c2 = self.view2d()
-        K = c2.shape[1] * 2
-        lin = torch.empty(c2.shape[0], K // 16, dtype=torch.uint8, device=self.device)
-        C.nv4_unpack_scales(self.sf, lin)
-        return QWeight(self.codes, lin.view(*self.codes.shape[:-1], K // 16), self.gscale).dequantize(dtype)
+        return self.as_qweight().dequantize(dtype)
 
 
 class Nv4Act:
@@ -421,6 +451,12 @@ class Fp8Weight:
     def view2d(self):
         return self.data.reshape(-1, self.data.shape[-1]), self.scale.reshape(-1, self.scale.shape[-1])
 
+    def narrow(self, lo: int, hi: int) -> "Fp8Weight":
+        return Fp8Weight(self.data[lo:hi], self.scale[lo:hi])
+
+    def squeeze0(self) -> "Fp8Weight":
+        return Fp8Weight(self.data[0], self.scale[0])
+
     @classmethod
     def quantize(cls, w: torch.Tensor):
         """Device-side encoding of a CUDA bf16 weight [..., rows, K] (rows a multiple of 128 when stacked)."""
@@ -490,6 +526,10 @@ def linear(x, w, residual=None, out=None, out_dtype=torch.bfloat16, split_k: Opt
         if out_dtype != torch.bfloat16:
             raise ValueError("FP8 weights produce bf16 outputs")
         return _linear_fp8(x, w, residual, out, False, N)
+    if isinstance(w, Nv4Weight):
+        if out_dtype != torch.bfloat16:
+            raise ValueError("NVFP4 weights produce bf16 outputs")
+        return linear_nv4(x if isinstance(x, Nv4Act) else nv4_quant_act(x), w, residual=residual, out=out)
     ws = Workspace.get(x.device)
     bn = bn or pick_bn(T, False)
     n_tt = (T + bn - 1) // bn
@@ -515,6 +555,8 @@ def gate_up_act(x, w_gate_up, n_ff: int, out=None, bn=None, split_k: Optional[in
         return out
     if isinstance(w_gate_up, Fp8Weight):
         return _linear_fp8(x, w_gate_up, None, out, True, n_ff)
+    if isinstance(w_gate_up, Nv4Weight):
+        return gate_up_nv4(x if isinstance(x, Nv4Act) else nv4_quant_act(x), w_gate_up, n_ff, out=out)
     ws = Workspace.get(x.device)
     bn = bn or pick_bn(T, True)
     n_tt = (T + bn - 1) // bn
@@ -697,11 +739,12 @@ def router_topk(logits, k, mode="softmax", renorm=True, route_scale=1.0, bias=No
 class Routing:
     """Router result of one step: ``ids`` / ``wts`` [T, k] and, for decode-sized steps, the dense routing tables
     (``dense``) that let the expert GEMMs run without a gather. Unpacks as ``ids, wts = routing``."""
-    __slots__ = ("ids", "wts", "dense", "x_normed", "e_lo", "n_local")
+    __slots__ = ("ids", "wts", "dense", "x_normed", "e_lo", "n_local", "shared_slot")
 
     def __init__(self, ids, wts, dense=None, x_normed=None, e_lo=0, n_local=None):
         self.ids, self.wts, self.dense, self.x_normed = ids, wts, dense, x_normed
         self.e_lo, self.n_local = e_lo, n_local      # expert range the dense tables were built for
+        self.shared_slot = False                     # the shared expert has a slot of its own in the dense tables
 
     def __iter__(self):
         yield self.ids
@@ -709,28 +752,37 @@ class Routing:
 
 
 class DenseRoute:
-    """Device tables of the dense routing (one token tile per active expert covering all T tokens)."""
+    """Device tables of the dense routing (one token tile per active expert covering all T tokens). ``bn`` is the
+    token tile of the GEMMs, ``stride`` the distance between the rows of consecutive slots in the intermediate
+    tensor (= bn, or 128 for the NVFP4 path whose 32-token tiles must start a 128-row scale atom), ``n_slots`` the
+    most slots a step can have (local experts, + 1 when the shared expert is stacked behind them)."""
 
-    def __init__(self, E: int, bn: int, device):
+    def __init__(self, n_slots: int, bn: int, device, stride: Optional[int] = None):
         i32 = dict(dtype=torch.int32, device=device)
-        self.E, self.bn = E, bn
-        self.tile_group = torch.zeros(E, **i32)
-        self.slot_base = torch.zeros(E, **i32)
-        self.zeros = torch.zeros(E, **i32)
-        self.tile_ntok = torch.zeros(E, **i32)
+        self.n_slots, self.bn, self.stride = n_slots, bn, stride or bn
+        self.E = n_slots
+        self.tile_group = torch.zeros(n_slots, **i32)
+        self.slot_base = torch.zeros(n_slots, **i32)
+        self.zeros = torch.zeros(n_slots, **i32)
+        self.tile_ntok = torch.zeros(n_slots, **i32)
         self.meta = torch.zeros(2, **i32)
-        self.out_rows = torch.full((E * bn,), -1, **i32)
-        self.tok_scale = torch.zeros(E * bn, dtype=torch.float32, device=device)
+        self.out_rows = torch.full((n_slots * self.stride,), -1, **i32)
+        self.tok_scale = torch.zeros(n_slots * self.stride, dtype=torch.float32, device=device)
+        self.sh_logit = torch.zeros(64, dtype=torch.float32, device=device)
         self.h_all = None
+        self.hq = None
         self.y_pairs = None
 
 
 def router(x, w_router, k, mode="softmax", renorm=True, route_scale=1.0, bias=None, n_group=1, topk_group=1,
-           norm=None, e_lo: int = 0, n_local: Optional[int] = None):
+           norm=None, e_lo: int = 0, n_local: Optional[int] = None, slot_stride: Optional[int] = None, sh_gate=None,
+           shared_slot: bool = False):
     """Router logits and top-k selection -> ``Routing``. Decode-sized steps (<= 64 tokens, <= 1024 pairs) run as
     ONE launch that also builds the dense routing tables; with ``norm=(weight, eps, w_offset)`` that launch first
     applies the RMSNorm to ``x`` (the raw residual stream) and ``Routing.x_normed`` is the normalised input.
-    Larger steps use the GEMM and the selection kernel."""
+    ``shared_slot``: the shared expert is stacked behind the local routed experts and gets a slot of its own that
+    every token uses (weight sigmoid(x . sh_gate) when ``sh_gate`` [1, H] is given, else 1); its output rows are
+    the pairs T * k .. T * k + T - 1. Larger steps use the GEMM and the selection kernel."""
     T, E = x.shape[0], w_router.shape[0]
     small = T <= 64 and T * k <= 1024 and TUNE["fused_router"]
     if not small:
@@ -748,18 +800,24 @@ def router(x, w_router, k, mode="softmax", renorm=True, route_scale=1.0, bias=No
         ctr = torch.zeros(1, dtype=torch.int32, device=x.device)
         ws._cache["router_ctr"] = ctr
     bn = 32 if T <= 32 else 64
-    dr = ws._cache.get(("dense_route", E, bn))
+    stride = slot_stride or bn
+    nl = E if n_local is None else n_local
+    n_slots = nl + (1 if shared_slot else 0)
+    dr = ws._cache.get(("dense_route", n_slots, bn, stride))
     if dr is None:
-        dr = DenseRoute(E, bn, x.device)
-        ws._cache[("dense_route", E, bn)] = dr
+        dr = DenseRoute(n_slots, bn, x.device, stride)
+        ws._cache[("dense_route", n_slots, bn, stride)] = dr
     ids = torch.empty(T, k, dtype=torch.int32, device=x.device)
     wts = torch.empty(T, k, dtype=torch.float32, device=x.device)
     xn = torch.empty_like(x) if norm is not None else None
     C.moe_route_small(x, norm[0] if norm else None, norm[1] if norm else 0.0, norm[2] if norm else 0.0, xn, w_router,
                       bias, k, 0 if mode == "softmax" else 1, renorm, route_scale, n_group, topk_group, logits, ids, wts,
-                      bn, dr.tile_group, dr.slot_base, dr.tile_ntok, dr.meta, dr.out_rows, dr.tok_scale, ctr,
-                      e_lo, E if n_local is None else n_local)
-    return Routing(ids, wts, dr, xn, e_lo, E if n_local is None else n_local)
+                      stride, dr.tile_group, dr.slot_base, dr.tile_ntok, dr.meta, dr.out_rows, dr.tok_scale, ctr,
+                      e_lo, nl, sh_gate.reshape(-1) if sh_gate is not None else None,
+                      dr.sh_logit if sh_gate is not None else None, bool(shared_slot))
+    r = Routing(ids, wts, dr, xn, e_lo, nl)
+    r.shared_slot = bool(shared_slot)
+    return r
 
 
 class MoePlan:
@@ -784,6 +842,75 @@ class MoePlan:
         self.y_pairs = None
 
 
+def _dense_ok(routing, n_groups: int, e_lo: int, ids) -> bool:
+    return (routing is not None and routing.dense is not None and routing.e_lo == e_lo and routing.ids is ids
+            and routing.n_local + int(routing.shared_slot) == n_groups and bool(TUNE["dense_route"]))
+
+
+def _dense_pairs(dr: DenseRoute, P: int, T: int, k: int, H: int, device):
+    """Output rows of the down projection: one per (token, expert) pair, then one per token for the shared slot."""
+    if dr.y_pairs is None or dr.y_pairs.shape[0] < P + T or dr.y_pairs.shape[1] != H:
+        dr.y_pairs = torch.zeros(max(P, 64 * k) + 64, H, dtype=torch.bfloat16, device=device)
+    return dr.y_pairs
+
+
+def _dense_combine(dr: DenseRoute, routing, ids, e_lo, T, k, H, shared, shared_gate, residual, out, norm, device):
+    C = ext()
+    P = T * k
+    y = dr.y_pairs[:P]
+    if routing.shared_slot:
+        # the shared expert ran as a slot of the grouped GEMMs; its gate is already applied
+        shared, shared_gate = dr.y_pairs[P:P + T], None
+    if out is None:
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=device)
+    if norm is None:
+        C.moe_combine(y, ids, e_lo, e_lo + routing.n_local, shared, shared_gate, residual, out, None, 0.0, 0.0, None)
+        return out
+    normed = torch.empty(T, H, dtype=torch.bfloat16, device=device)
+    C.moe_combine(y, ids, e_lo, e_lo + routing.n_local, shared, shared_gate, residual, out, norm[0], norm[1], norm[2],
+                  normed)
+    return out, normed
+
+
+def _moe_experts_nv4(x, ids, wts, w_gate_up: "Nv4Weight", w_down: "Nv4Weight", n_ff, e_lo, shared, shared_gate,
+                     residual, out, norm, routing, xq: Optional["Nv4Act"] = None, h_scale=None):
+    """Routed experts on the native NVFP4 path (decode-sized steps over the dense routing): the layer input is
+    quantised once (or arrives quantised as ``xq``), the gate/up GEMM re-encodes its SwiGLU output to NVFP4 in its
+    epilogue (static tensor scale ``h_scale``), and the down GEMM reads that. Three launches + the combine."""
+    C = ext()
+    T, H = x.shape
+    k = ids.shape[1]
+    n_groups = w_gate_up.shape[0]
+    ws = Workspace.get(x.device)
+    dr = routing.dense
+    P = T * k
+    if xq is None:
+        xq = nv4_quant_act(x, key="moe_x")
+    if h_scale is None:
+        h_scale = ws._cache.get("nv4_h_scale")
+        if h_scale is None:
+            h_scale = torch.tensor([NV4_H_AMAX / (6.0 * 448.0)], dtype=torch.float32, device=x.device)
+            ws._cache["nv4_h_scale"] = h_scale
+    rows = dr.n_slots * dr.stride
+    if dr.hq is None or dr.hq[0].shape[1] * 2 != n_ff:
+        dr.hq = (torch.zeros(rows, n_ff // 2, dtype=torch.uint8, device=x.device),
+                 torch.zeros(C.nv4_sf_bytes(rows, n_ff), dtype=torch.uint8, device=x.device))
+    hq_codes, hq_sf = dr.hq
+    y_pairs = _dense_pairs(dr, P, T, k, H, x.device)
+    C.wgemm_nv4(w_gate_up.view2d(), w_gate_up.sf, w_gate_up.gscale, xq.codes, xq.sf, xq.gscale, xq.stride, None, None,
+                None, None, n_ff, True, n_ff, 0, dr.bn, ws.status, dr.tile_group, dr.zeros, dr.tile_ntok, dr.meta,
+                dr.n_slots, 2 * n_ff, 0, dr.slot_base, hq_codes, hq_sf, h_scale)
+    C.wgemm_nv4(w_down.view2d(), w_down.sf, w_down.gscale, hq_codes, hq_sf, h_scale, 0, y_pairs, None, dr.tok_scale,
+                dr.out_rows, H, False, 0, 0, dr.bn, ws.status, dr.tile_group, dr.slot_base, dr.tile_ntok, dr.meta,
+                dr.n_slots, H, 0, None, None, None, None)
+    return _dense_combine(dr, routing, ids, e_lo, T, k, H, shared, shared_gate, residual, out, norm, x.device)
+
+
+# largest |SwiGLU output| the static scale of the re-encoded intermediate is laid out for (checkpoints bring their
+# own calibrated input scale; this is the default for weights quantised here)
+NV4_H_AMAX = 32.0
+
+
 def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[MoePlan] = None, shared=None,
                 shared_gate=None, residual=None, out=None, norm=None, routing: Optional[Routing] = None):
     """Routed experts over the device routing plan: plan -> gather -> grouped gate/up (+SwiGLU) ->
@@ -799,6 +926,18 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[Moe
     if isinstance(w_gate_up, Fp8Weight):
         return _moe_experts_fp8(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, shared, shared_gate, residual, out, norm,
                                 routing)
+    if isinstance(w_gate_up, Nv4Weight):
+        if _dense_ok(routing, E_local, e_lo, ids):
+            return _moe_experts_nv4(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, shared, shared_gate, residual, out,
+                                    norm, routing)
+        # larger steps: the de-quantising grouped GEMM over the routing plan (same codes, linear scale order)
+        w_gate_up, w_down = w_gate_up.as_qweight(), w_down.as_qweight()
+    if routing is not None and routing.shared_slot and not _dense_ok(routing, E_local, e_lo, ids):
+        raise ValueError("the routing carries a shared-expert slot that these expert weights do not have")
+    if routing is None or not routing.shared_slot:
+        n_routed = E_local
+    else:
+        n_routed = E_local - 1
     # expert weights as 2-D operands (+ NVFP4 block scales / tensor scales when kept in 4 bits)
     if isinstance(w_gate_up, QWeight):
         (gu2, gu_sc), gu_gs = w_gate_up.view2d(), w_gate_up.gscale
@@ -808,31 +947,21 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[Moe
         (dn2, dn_sc), dn_gs = w_down.view2d(), w_down.gscale
     else:
         dn2, dn_sc, dn_gs = w_down.view(E_local * H, n_ff), None, None
-    if (routing is not None and routing.dense is not None and routing.n_local == E_local and routing.e_lo == e_lo
-            and routing.ids is ids and TUNE["dense_route"]):
+    if _dense_ok(routing, E_local, e_lo, ids):
         # decode-sized step: every active expert runs over all T tokens in place (no plan, no gather)
         dr = routing.dense
         P = T * k
         if dr.h_all is None or dr.h_all.shape[1] != n_ff:
-            dr.h_all = torch.zeros(E_local * dr.bn, n_ff, dtype=torch.bfloat16, device=x.device)
-        if dr.y_pairs is None or dr.y_pairs.shape[0] < P or dr.y_pairs.shape[1] != H:
-            dr.y_pairs = torch.zeros(max(P, 64 * k), H, dtype=torch.bfloat16, device=x.device)
+            dr.h_all = torch.zeros(dr.n_slots * dr.stride, n_ff, dtype=torch.bfloat16, device=x.device)
+        y_pairs = _dense_pairs(dr, P, T, k, H, x.device)
         C.wgemm(gu2, x, dr.h_all, None, None, None, n_ff, True, n_ff, dr.bn, 1,
-                None, None, ws.status, dr.tile_group, dr.zeros, dr.tile_ntok, dr.meta, E_local, 2 * n_ff, 0, [],
+                None, None, ws.status, dr.tile_group, dr.zeros, dr.tile_ntok, dr.meta, dr.n_slots, 2 * n_ff, 0, [],
                 dr.slot_base, gu_sc, gu_gs)
-        C.wgemm(dn2, dr.h_all, dr.y_pairs, None, dr.tok_scale, dr.out_rows, H, False, 0,
-                dr.bn, 1, None, None, ws.status, dr.tile_group, dr.slot_base, dr.tile_ntok, dr.meta, E_local, H, 0, [],
+        C.wgemm(dn2, dr.h_all, y_pairs, None, dr.tok_scale, dr.out_rows, H, False, 0,
+                dr.bn, 1, None, None, ws.status, dr.tile_group, dr.slot_base, dr.tile_ntok, dr.meta, dr.n_slots, H, 0, [],
                 None, dn_sc, dn_gs)
-        if out is None:
-            out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
-        y = dr.y_pairs[:P]
-        if norm is None:
-            C.moe_combine(y, ids, e_lo, e_lo + E_local, shared, shared_gate, residual, out, None, 0.0, 0.0, None)
-            return out
-        normed = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
-        C.moe_combine(y, ids, e_lo, e_lo + E_local, shared, shared_gate, residual, out, norm[0], norm[1], norm[2],
-                      normed)
-        return out, normed
+        return _dense_combine(dr, routing, ids, e_lo, T, k, H, shared, shared_gate, residual, out, norm, x.device)
+    E_local = n_routed
     if plan is None:
         bn = 32 if T * k <= 32 * E_local else (64 if T * k <= 64 * E_local else 128)
         key = ("moe_plan", T, k, E_local, bn, H, n_ff)
@@ -887,22 +1016,19 @@ def _moe_experts_fp8(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, shared, shared_
     P = T * k
     if out is None:
         out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
-    dense = (routing is not None and routing.dense is not None and routing.n_local == E_local
-             and routing.e_lo == e_lo and routing.ids is ids and TUNE["dense_route"])
-    if dense:
+    if _dense_ok(routing, E_local, e_lo, ids):
         dr = routing.dense
         if dr.h_all is None or dr.h_all.shape[1] != n_ff:
-            dr.h_all = torch.zeros(E_local * dr.bn, n_ff, dtype=torch.bfloat16, device=x.device)
-        if dr.y_pairs is None or dr.y_pairs.shape[0] < P or dr.y_pairs.shape[1] != H:
-            dr.y_pairs = torch.zeros(max(P, 64 * k), H, dtype=torch.bfloat16, device=x.device)
+            dr.h_all = torch.zeros(dr.n_slots * dr.stride, n_ff, dtype=torch.bfloat16, device=x.device)
+        y_pairs = _dense_pairs(dr, P, T, k, H, x.device)
         x8, xs = fp8_quant_act(x)
         C.wgemm_fp8(gu2, gu_s, x8, xs, dr.h_all, None, None, None, n_ff, True, n_ff, dr.bn, 1, None, None, ws.status,
-                    dr.tile_group, dr.zeros, dr.tile_ntok, dr.meta, E_local, 2 * n_ff, 0, dr.slot_base)
+                    dr.tile_group, dr.zeros, dr.tile_ntok, dr.meta, dr.n_slots, 2 * n_ff, 0, dr.slot_base)
         h8, hs = fp8_quant_act(dr.h_all)
-        C.wgemm_fp8(dn2, dn_s, h8, hs, dr.y_pairs, None, dr.tok_scale, dr.out_rows, H, False, 0, dr.bn, 1, None, None,
-                    ws.status, dr.tile_group, dr.slot_base, dr.tile_ntok, dr.meta, E_local, H, 0, None)
-        y = dr.y_pairs[:P]
-    else:
+        C.wgemm_fp8(dn2, dn_s, h8, hs, y_pairs, None, dr.tok_scale, dr.out_rows, H, False, 0, dr.bn, 1, None, None,
+                    ws.status, dr.tile_group, dr.slot_base, dr.tile_ntok, dr.meta, dr.n_slots, H, 0, None)
+        return _dense_combine(dr, routing, ids, e_lo, T, k, H, shared, shared_gate, residual, out, norm, x.device)
+    if True:
         bn = 32 if P <= 32 * E_local else 64
         key = ("moe_plan", T, k, E_local, bn, H, n_ff)
         plan = ws._cache.get(key)

@@ -100,3 +100,72 @@ def test_gate_up_swiglu_bf16_and_quantised_output(T, F, K, bn):
     want_y = hd @ wdn.dequantize(torch.float32).t()
     assert sm100.Workspace.get(_dev()).check() == 0
     assert float((y.float() - want_y).abs().max()) < 0.02 * float(want_y.abs().max()) + 1e-3
+
+
+def _moe_setup(T, E, k, H, F, seed):
+    torch.manual_seed(seed)
+    dev = _dev()
+    x = (torch.randn(T, H, device=dev) * 0.8).bfloat16()
+    res = torch.randn(T, H, device=dev).bfloat16()
+    w_r = (torch.randn(E, H, device=dev) * H ** -0.5).bfloat16()
+    wgu = (torch.randn(E + 1, 2 * F, H, device=dev) * H ** -0.5).bfloat16()      # last group = shared expert
+    wd = (torch.randn(E + 1, H, F, device=dev) * F ** -0.5).bfloat16()
+    sh_gate = (torch.randn(1, H, device=dev) * H ** -0.5).bfloat16()
+    return x, res, w_r, wgu, wd, sh_gate
+
+
+def _moe_reference(x, ids, wts, wgu, wd, F, sh_gate, res, E):
+    from legion_b200.ops import reference as ref
+    y = ref.moe_experts(x, ids, wts, wgu[:E], wd[:E], F)
+    hs = ref.gate_up_act(x, wgu[E], F, "silu")
+    sh = ref.linear(hs, wd[E]).float()
+    gate = torch.sigmoid(ref.linear(x, sh_gate, out_dtype=torch.float32).reshape(-1))
+    return y.float() + sh * gate[:, None] + res.float()
+
+
+@pytest.mark.parametrize("T,E,k,H,F", [(16, 64, 4, 512, 256), (1, 16, 2, 256, 128), (40, 32, 6, 512, 256)])
+def test_shared_expert_as_a_slot_of_the_grouped_gemms_bf16(T, E, k, H, F):
+    """The shared expert stacked behind the routed experts runs as one more slot of the dense routing; its sigmoid
+    gate comes out of the routing launch."""
+    from legion_b200.ops import sm100
+    x, res, w_r, wgu, wd, sh_gate = _moe_setup(T, E, k, H, F, 5)
+    r = sm100.router(x, w_r, k, shared_slot=True, sh_gate=sh_gate)
+    assert r.shared_slot and r.dense is not None
+    out = sm100.moe_experts(x, r.ids, r.wts, wgu, wd, F, residual=res, routing=r)
+    assert sm100.Workspace.get(_dev()).check() == 0
+    want = _moe_reference(x, r.ids, r.wts, wgu, wd, F, sh_gate, res, E)
+    assert float((out.float() - want).abs().max()) < 0.03 * float(want.abs().max()) + 0.03
+    n_act = int(torch.unique(r.ids).numel())
+    assert r.dense.meta.tolist() == [n_act + 1, (n_act + 1) * r.dense.stride]
+
+
+@pytest.mark.parametrize("T,E,k,H,F", [(16, 64, 4, 512, 256), (3, 16, 2, 256, 256), (48, 32, 6, 1024, 512)])
+def test_moe_block_native_nvfp4_with_shared_slot(T, E, k, H, F):
+    """Routed + shared experts on the W4A4 path: quantised input, gate/up with re-encoded SwiGLU output, down,
+    combine; against the fp32 computation over the de-quantised weights and activations."""
+    from legion_b200.ops import reference as ref
+    from legion_b200.ops import sm100
+    x, res, w_r, wgu, wd, sh_gate = _moe_setup(T, E, k, H, F, 9)
+    qgu = sm100.Nv4Weight.quantize_cuda(wgu, dual_rows=F)
+    qdn = sm100.Nv4Weight.quantize_cuda(wd)
+    r = sm100.router(x, w_r, k, shared_slot=True, sh_gate=sh_gate, slot_stride=128)
+    out = sm100.moe_experts(x, r.ids, r.wts, qgu, qdn, F, residual=res, routing=r)
+    assert sm100.Workspace.get(_dev()).check() == 0
+    # reference: same quantised operands, intermediate re-encoded with the same static scale
+    xd = sm100.nv4_quant_act(x).dequantize().bfloat16()
+    gud, dnd = qgu.dequantize(torch.float32), qdn.dequantize(torch.float32)
+    want_exact = _moe_reference(xd, r.ids, r.wts, gud.bfloat16(), dnd.bfloat16(), F, sh_gate, res, E)
+    rel = float((out.float() - want_exact).abs().mean() / want_exact.abs().mean())
+    assert rel < 0.08, rel                      # 4-bit rounding of the intermediate is the only difference
+    full = _moe_reference(x, r.ids, r.wts, wgu, wd, F, sh_gate, res, E)
+    assert float((out.float() - full).abs().mean() / full.abs().mean()) < 0.2
+    out2 = sm100.moe_experts(x, r.ids, r.wts, qgu, qdn, F, residual=res, routing=r)
+    assert torch.equal(out, out2)
+    # a prompt-sized step with the same weights takes the plan path (de-quantising GEMM), routed experts only
+    T2 = 200
+    x2 = (torch.randn(T2, H, device=_dev()) * 0.8).bfloat16()
+    r2 = sm100.router(x2, w_r, k)
+    y2 = sm100.moe_experts(x2, r2.ids, r2.wts, qgu.narrow(0, E), qdn.narrow(0, E), F)
+    want2 = ref.moe_experts(x2, r2.ids, r2.wts, gud[:E].bfloat16(), dnd[:E].bfloat16(), F)
+    assert sm100.Workspace.get(_dev()).check() == 0
+    assert float((y2.float() - want2.float()).abs().max()) < 0.03 * float(want2.abs().max()) + 0.03
