@@ -60,26 +60,43 @@ def timeit(fn, iters=10, warmup=3, flush=True):
     return ts[len(ts) // 2]
 
 
-def timeit_graph(fn, iters=20, warmup=3):
-    """Device time of one call of ``fn`` replayed from a CUDA graph (no host launch cost in the number), L2
-    flushed before every replay."""
+_flush_graph_ms = {}
+
+
+def timeit_graph(fn, iters=5, warmup=3, reps=20):
+    """Device time of one call of ``fn`` replayed from a CUDA graph (no host launch cost in the number) with a cold
+    L2. One graph holds ``reps`` x (L2 flush, fn) back to back so the GPU stays busy and at its working clocks (a
+    lone kernel between two synchronisations runs at idle clocks and reads several times too slow); the time of a
+    graph of ``reps`` flushes alone is subtracted."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
-    g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g):
-        fn()
-    ts = []
-    for _ in range(ITERS["iters"] or iters):
-        flush_l2()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        g.replay()
-        b.record()
-        torch.cuda.synchronize()
-        ts.append(a.elapsed_time(b))
-    ts.sort()
-    return ts[len(ts) // 2]
+
+    def capture(body):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(reps):
+                flush_l2()
+                body()
+        return g
+
+    def run(g):
+        ts = []
+        for _ in range(ITERS["iters"] or iters):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g.replay()                      # brings the clocks up
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        ts.sort()
+        return ts[len(ts) // 2]
+    flush_l2()
+    if reps not in _flush_graph_ms:
+        _flush_graph_ms[reps] = run(capture(lambda: None))
+    total = run(capture(fn))
+    return max(0.0, total - _flush_graph_ms[reps]) / reps
 
 
 def bench_layer_parts(rows):
@@ -262,6 +279,76 @@ def bench_moe_nvfp4(rows):
     print(rows[-1], flush=True)
 
 
+def bench_moe_nv4(rows):
+    """MoE block at decode size on the native NVFP4 (W4A4) path, graph-replayed, whole and by piece, for the
+    30B-A3B expert shape (128 experts top-8, FFN 768) and the 80B-A3B one (512 experts top-10, FFN 512, shared
+    expert stacked behind the routed ones). Bytes = the quantised bytes of the active experts (codes + scales)."""
+    from legion_b200.ops import sm100
+    from legion_b200.ops.sm100 import Nv4Weight
+    hbm, tf, src = peaks()
+    dev = "cuda"
+    C = sm100.ext()
+    for (name, T, H, E, k, F, shared) in (("30b-a3b", 16, 2048, 128, 8, 768, False),
+                                          ("80b-a3b", 16, 2048, 512, 10, 512, True),
+                                          ("80b-a3b", 64, 2048, 512, 10, 512, True),
+                                          ("80b-a3b", 1, 2048, 512, 10, 512, True)):
+        if CASE["tokens"] and T not in CASE["tokens"]:
+            continue
+        G = E + (1 if shared else 0)
+        x = torch.randn(T, H, device=dev).bfloat16()
+        res = torch.randn(T, H, device=dev).bfloat16()
+        nw = torch.ones(H, device=dev)
+        w_r = (torch.randn(E, H, device=dev) * 0.02).bfloat16()
+        sh_gate = (torch.randn(1, H, device=dev) * 0.02).bfloat16() if shared else None
+
+        def rand_w(rows_, K):
+            codes = torch.randint(0, 256, (G, rows_, K // 2), device=dev, dtype=torch.uint8)
+            lin = torch.randint(48, 64, (G * rows_, K // 16), device=dev, dtype=torch.uint8)
+            atoms = torch.zeros(C.nv4_sf_bytes(G * rows_, K), dtype=torch.uint8, device=dev)
+            C.nv4_pack_scales(lin, atoms)
+            return codes, atoms
+        gc, gs = rand_w(2 * F, H)
+        dc, ds = rand_w(H, F)
+        qgu = Nv4Weight(gc, gs, torch.full((2 * G,), 1e-3, device=dev))
+        qdn = Nv4Weight(dc, ds, torch.full((G,), 1e-3, device=dev))
+        kw = dict(shared_slot=shared, sh_gate=sh_gate, slot_stride=128)
+        routing = sm100.router(x, w_r, k, **kw)
+        n_act = int(torch.unique(routing.ids).numel()) + (1 if shared else 0)
+        byts = n_act * 3 * H * F * 9 // 16
+
+        def block():
+            xq = sm100.nv4_quant_act(x, norm=(nw, 1e-6, 0.0), residual=res, want_normed=True, key="bench_x")
+            r = sm100.router(xq.normed, w_r, k, **kw)
+            return sm100._moe_experts_nv4(xq.normed, r.ids, r.wts, qgu, qdn, F, 0, None, None, xq.summed, None,
+                                          (nw, 1e-6, 0.0), r, xq=xq)
+
+        def add(part, fn, b=0):
+            ms = timeit_graph(fn)
+            rows.append(dict(kernel="moe_nv4", shape=name, T=T, part=part, active=n_act, us=ms * 1e3,
+                             gbs=b / ms / 1e6 if b else 0.0, frac_hbm=b / ms / 1e6 / hbm if b else 0.0, peaks=src))
+            print(rows[-1], flush=True)
+        add("block(addnorm+quant, route, gate_up, down, combine+norm)", block, byts)
+        xq = sm100.nv4_quant_act(x, key="bench_x2")
+        ws = sm100.Workspace.get(torch.device(dev))
+        dr = routing.dense
+        hs = torch.tensor([32.0 / 2688.0], device=dev)
+        rows_h = dr.n_slots * dr.stride
+        hq = torch.zeros(rows_h, F // 2, dtype=torch.uint8, device=dev)
+        hsf = torch.zeros(C.nv4_sf_bytes(rows_h, F), dtype=torch.uint8, device=dev)
+        y = torch.zeros(T * k + 64, H, dtype=torch.bfloat16, device=dev)
+        add("addnorm_quant", lambda: sm100.nv4_quant_act(x, norm=(nw, 1e-6, 0.0), residual=res, want_normed=True,
+                                                         key="bench_x3"))
+        add("route", lambda: sm100.router(x, w_r, k, **kw), w_r.numel() * 2)
+        add("gate_up", lambda: C.wgemm_nv4(qgu.view2d(), qgu.sf, qgu.gscale, xq.codes, xq.sf, xq.gscale, 1, None, None,
+                                           None, None, F, True, F, 0, dr.bn, ws.status, dr.tile_group, dr.zeros,
+                                           dr.tile_ntok, dr.meta, dr.n_slots, 2 * F, 0, dr.slot_base, hq, hsf, hs),
+            n_act * 2 * H * F * 9 // 16)
+        add("down", lambda: C.wgemm_nv4(qdn.view2d(), qdn.sf, qdn.gscale, hq, hsf, hs, 0, y, None, dr.tok_scale,
+                                        dr.out_rows, H, False, 0, 0, dr.bn, ws.status, dr.tile_group, dr.slot_base,
+                                        dr.tile_ntok, dr.meta, dr.n_slots, H, 0, None, None, None, None),
+            n_act * H * F * 9 // 16)
+
+
 def bench_gdn(rows):
     """Gated DeltaNet recurrence over a prompt (80B-A3B hybrid shape: 16 key / 32 value heads of dim 128) and over a
     decode step of 16 sequences: tokens per second of the state update."""
@@ -375,7 +462,7 @@ def main(argv=None):
     if a.gemm:
         CASE["gemm"] = [tuple(int(y) for y in x.split("x")) for x in a.gemm.split(",")]
     rows = []
-    table = {"gdn": bench_gdn, "moe_fp8": bench_moe_fp8, "mla": bench_mla, "moe_nvfp4": bench_moe_nvfp4, "layer_parts": bench_layer_parts, "decode_pages": bench_decode_pages, "gemm": bench_gemm, "moe": bench_moe, "decode_attn": bench_decode_attn, "prefill_attn": bench_prefill_attn}
+    table = {"moe_nv4": bench_moe_nv4, "gdn": bench_gdn, "moe_fp8": bench_moe_fp8, "mla": bench_mla, "moe_nvfp4": bench_moe_nvfp4, "layer_parts": bench_layer_parts, "decode_pages": bench_decode_pages, "gemm": bench_gemm, "moe": bench_moe, "decode_attn": bench_decode_attn, "prefill_attn": bench_prefill_attn}
     for name in a.only.split(","):
         table[name](rows)
     from legion_b200.ops.sm100 import Workspace

@@ -309,8 +309,32 @@ wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     uint32_t acc_ph = 0;
     Work it;
     const float q_gs = QOUT ? *a.q_gscale : 1.f;
+    const float xs_all = (a.x_gscale && a.x_gs_stride == 0) ? __ldg(a.x_gscale) : 1.f;
     for (int w = blockIdx.x; decode_work<BN>(a, w, n_tok_tiles, it); w += gridDim.x) {
       const int row = q * 32 + lane;
+      // Row bookkeeping of the first 32 token columns is fetched BEFORE the accumulator is waited for, so these
+      // (dependent, L2-latency) loads overlap the tile's MMAs instead of sitting between them and the stores:
+      // the output row and routing weight of the four rows this thread writes, the activation scale of column
+      // `lane` (handed round by shuffles).
+      long orow_p[4];
+      float sc_p[4];
+      float xs_lane = xs_all;
+      auto prefetch_rows = [&](int c) {
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) {
+          const int t = c + pass * 8 + (etid >> 4);
+          const int xrow = it.out0 + t;
+          orow_p[pass] = -1;
+          sc_p[pass] = 1.f;
+          if (!QOUT && t < it.ntok) {
+            orow_p[pass] = a.out_rows ? long(a.out_rows[xrow]) : long(xrow);
+            if (a.tok_scale) sc_p[pass] = a.tok_scale[xrow];
+          }
+        }
+        if (a.x_gscale && a.x_gs_stride != 0)
+          xs_lane = (c + lane < it.ntok) ? __ldg(&a.x_gscale[long(it.tok0 + c + lane) * a.x_gs_stride]) : 1.f;
+      };
+      prefetch_rows(0);
       if (!__all_sync(0xffffffffu, mbar_wait(&tfull[acc], acc_ph, abort_flag))) {
         *abort_flag = 1;
         atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_FULL);
@@ -323,6 +347,7 @@ wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         if (c >= it.ntok) break;
+        if (c > 0) prefetch_rows(c);
         uint32_t r[32];
         float g[32];
         tmem_ld32(t0 + c, r);
@@ -335,8 +360,7 @@ wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         }
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          const int t = c + j;
-          const float xs = (a.x_gscale && t < it.ntok) ? __ldg(&a.x_gscale[long(it.tok0 + t) * a.x_gs_stride]) : 1.f;
+          const float xs = __shfl_sync(0xffffffffu, xs_lane, j);
           float v = g[j] * gs0 * xs;
           if (DUAL) {
             const float u = __uint_as_float(r[j]) * gs1 * xs;
@@ -371,14 +395,11 @@ wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
               if ((etid & 1) == 0) a.q_sf[sf_atom_byte(xrow, feat8 >> 4, a.q_k4)] = uint8_t(sb);
             }
           } else if (live) {
-            long orow = xrow;
-            if (a.out_rows) orow = a.out_rows[xrow];
+            const long orow = orow_p[pass];
             if (orow >= 0) {
-              if (a.tok_scale) {
-                const float sc = a.tok_scale[xrow];
+              const float sc = sc_p[pass];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] *= sc;
-              }
+              for (int e = 0; e < 8; ++e) v[e] *= sc;
               if (a.vec_ok) {
                 if (a.residual) {
                   const uint4 rr = *reinterpret_cast<const uint4*>(a.residual + orow * a.ldr + feat8);

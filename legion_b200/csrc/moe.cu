@@ -31,22 +31,21 @@ __device__ __forceinline__ void router_topk_row(const float* logits, long ldl, c
     sc[j] = (e < E) ? __ldcg(logits + t * ldl + e) : -INFINITY;   // L2 read: the row may come from other CTAs
     mx = fmaxf(mx, sc[j]);
   }
+  float inv_sum = 1.f;
   if (mode == 0) {
+    // selection by the logits themselves (softmax is monotonic); the partition sum is needed only when the chosen
+    // weights are not renormalised
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    float sum = 0.f;
+    for (int j = 0; j < PER; ++j) sel[j] = sc[j];
+    if (!renorm) {
 #pragma unroll
-    for (int j = 0; j < PER; ++j) {
-      sc[j] = (lane + 32 * j < E) ? __expf(sc[j] - mx) : 0.f;
-      sum += sc[j];
-    }
+      for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      float sum = 0.f;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    const float inv = 1.f / sum;
+      for (int j = 0; j < PER; ++j) sum += (lane + 32 * j < E) ? __expf(sc[j] - mx) : 0.f;
 #pragma unroll
-    for (int j = 0; j < PER; ++j) {
-      sc[j] *= inv;
-      sel[j] = (lane + 32 * j < E) ? sc[j] : -INFINITY;
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      inv_sum = 1.f / sum;
     }
   } else {
 #pragma unroll
@@ -102,36 +101,64 @@ __device__ __forceinline__ void router_topk_row(const float* logits, long ldl, c
       }
     }
   }
-  // iterative arg-max, ties to the lower expert index
-  float wsum = 0.f;
-  float my_w = 0.f;
+  // Selection: every lane sorts its PER candidates once (bitonic network on packed keys: order-preserving bits of
+  // the biased score above, inverted expert index below, so the larger key is the better score and, on equal
+  // scores, the lower index), then each of the k rounds is two warp-wide integer maxima over the lanes' heads and
+  // a pop on the winning lane: a short dependent chain per round instead of PER compares and ten shuffles.
+  unsigned long long key[PER];
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int e = lane + 32 * j;
+    const uint32_t u = __float_as_uint(sel[j]);
+    const uint32_t ord = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    key[j] = (e < E) ? ((static_cast<unsigned long long>(ord) << 32) | (0xFFFFFFFFu - uint32_t(e))) : 0ull;
+  }
+#pragma unroll
+  for (int k2 = 2; k2 <= PER; k2 <<= 1) {
+#pragma unroll
+    for (int j2 = k2 >> 1; j2 > 0; j2 >>= 1) {
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        const int l = i ^ j2;
+        if (l > i) {
+          const bool desc = (i & k2) == 0;          // this block ends up descending
+          const unsigned long long a = key[i], b = key[l];
+          const bool sw = desc ? (a < b) : (a > b);
+          key[i] = sw ? b : a;
+          key[l] = sw ? a : b;
+        }
+      }
+    }
+  }
   int my_id = 0;
   for (int i = 0; i < k; ++i) {
-    float bv = -INFINITY;
-    int be = 0x7fffffff;
+    const uint32_t hi = uint32_t(key[0] >> 32), lo = uint32_t(key[0]);
+    const uint32_t ghi = __reduce_max_sync(0xffffffffu, hi);
+    const uint32_t glo = __reduce_max_sync(0xffffffffu, hi == ghi ? lo : 0u);
+    const int be = int(0xFFFFFFFFu - glo);
+    if (lane == (be & 31)) {
 #pragma unroll
-    for (int j = 0; j < PER; ++j) {
-      const int e = lane + 32 * j;
-      if (sel[j] > bv) { bv = sel[j]; be = e; }
+      for (int j = 0; j + 1 < PER; ++j) key[j] = key[j + 1];
+      key[PER - 1] = 0ull;
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
-      if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
-    }
-    // fetch the unbiased score of the winner
-    float w = 0.f;
-#pragma unroll
-    for (int j = 0; j < PER; ++j) {
-      if (lane + 32 * j == be) { w = sc[j]; sel[j] = -INFINITY; }
-    }
-    w = __shfl_sync(0xffffffffu, w, be & 31);
-    wsum += w;
-    if (lane == i) { my_w = w; my_id = be; }
+    if (lane == i) my_id = be;
   }
+  // weights of the chosen experts from their logits (lane i < k holds choice i)
+  float w = 0.f;
   if (lane < k) {
-    float w = my_w;
+    const float l = __ldcg(logits + t * ldl + my_id);
+    if (mode == 0) w = renorm ? l : __expf(l - mx) * inv_sum;
+    else w = 1.f / (1.f + __expf(-l));
+  }
+  if (mode == 0 && renorm) {
+    // softmax followed by renormalisation over the chosen experts = softmax over the chosen logits alone
+    const float l0 = __shfl_sync(0xffffffffu, w, 0);      // choice 0 has the largest logit
+    w = lane < k ? __expf(w - l0) : 0.f;
+  }
+  float wsum = w;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
+  if (lane < k) {
     if (renorm) w = w / fmaxf(wsum, 6.1e-5f);
     ids[t * k + lane] = my_id;
     wts[t * k + lane] = w * route_scale;
@@ -154,12 +181,16 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const float* __restric
 
 // Decode-sized MoE front end in ONE launch (T <= 64 tokens, T * k <= 1024 pairs):
 //   (optional) RMSNorm of the residual stream -> router logits -> top-k -> dense routing tables.
-// CTA e computes expert e's logit for every token; when norm_w is given it first derives each token's inverse
-// RMS from the rows it reads anyway, and the CTAs share the job of writing the normalised rows out (row t by CTA
-// t mod grid). The last CTA to finish selects the top-k of every token and builds the DENSE routing: every
-// active expert becomes one token tile that covers ALL T tokens (the GEMMs are weight-bandwidth bound, so the
-// extra columns are free), which removes the gather: the gate/up GEMM reads the activations in place and writes
-// rows slot * bn + t, the down GEMM drops the rows whose out_rows entry is -1.
+// A CTA owns `epc` consecutive router rows (the shared expert's gate row counts as row E). Per pass of up to 16
+// tokens it stages the token rows in shared memory once (normalising them on the way when norm_w is given: warp i
+// takes token i; the CTA numbered t mod grid also writes row t of x_normed), then every warp streams one weight
+// row from HBM and accumulates its share of the pass's tokens against the staged rows. Staging per CTA instead of
+// re-reading the tokens per expert keeps the L2 traffic on the few hot token lines at grid x T rows; with one CTA
+// per expert (512 of them) those lines were the bottleneck. The last CTA to finish selects the top-k of every
+// token and builds the DENSE routing: every active expert becomes one token tile that covers ALL T tokens (the
+// GEMMs are weight-bandwidth bound, so the extra columns are free), which removes the gather: the gate/up GEMM
+// reads the activations in place and writes rows slot * bn + t, the down GEMM drops the rows whose out_rows entry
+// is -1.
 //   tile_group[slot] = expert, slot_base[slot] = slot * bn, tile_ntok[slot] = T, meta = {n_active, n_active * bn}
 //   out_rows[slot * bn + t] = pair index t * k + c (or -1), tok_scale[slot * bn + t] = routing weight
 template <int MAXE>
@@ -170,9 +201,8 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
     int topk_group, int* ids, float* wts, int T, int bn, int* __restrict__ tile_group, int* __restrict__ slot_base,
     int* __restrict__ tile_ntok, int* __restrict__ meta, int* __restrict__ out_rows, float* __restrict__ tok_scale,
     unsigned int* done_ctr, int e_lo, int n_local, const __nv_bfloat16* __restrict__ sh_gate_w, float* sh_logit,
-    int shared_slot) {
-  __shared__ float red[2][8][8];
-  __shared__ float s_inv[2][8];
+    int shared_slot, int epc, int tpp) {
+  extern __shared__ uint4 xs_rows[];          // [tpp][H / 8] token rows of the current pass
   __shared__ int s_last;
   __shared__ int s_ids[1024];
   __shared__ float s_wts[1024];
@@ -180,107 +210,110 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
   __shared__ int s_slot[512];
   griddep_wait();
   griddep_launch();
-  const int e = blockIdx.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // the two halves of the CTA take 8 tokens each per pass
-  const int half = tid >> 8, htid = tid & 255, hwarp = warp & 7;
-  // CTA E (present when the shared expert has a sigmoid gate) computes that gate's logit like one more router row
-  const bool is_gate = e >= E;
-  const uint4* w4 = reinterpret_cast<const uint4*>(is_gate ? sh_gate_w : w + long(e) * ldw);
   const int nv = H / 8;
-  for (int base = 0; base < T; base += 16) {
-    const int t0 = base + half * 8;
-    if (norm_w) {
-      float ssq[8];
+  const int wpe = 16 / epc;                   // warps per router row
+  const int tpw = tpp / wpe;                  // tokens of a pass per warp
+  const int e = blockIdx.x * epc + warp / wpe;
+  const int tq = warp % wpe;
+  const bool is_gate = e >= E;                // row E: the sigmoid gate of the shared expert
+  const bool row_ok = e < E + (sh_gate_w ? 1 : 0);
+  const uint4* w4 = reinterpret_cast<const uint4*>(is_gate ? sh_gate_w : w + long(e) * ldw);
+  for (int base = 0; base < T; base += tpp) {
+    if (warp < tpp && base + warp < T) {
+      const int t = base + warp;
+      const uint4* xr = reinterpret_cast<const uint4*>(x + long(t) * ldx);
+      uint4* dst = xs_rows + warp * nv;
+      float ssq = 0.f;
+      for (int v0 = lane; v0 < nv; v0 += 256) {       // eight loads in flight per lane
+        uint4 u[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) ssq[j] = 0.f;
-      for (int v = htid; v < nv; v += 256) {
+        for (int i = 0; i < 8; ++i)
+          if (v0 + 32 * i < nv) u[i] = xr[v0 + 32 * i];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          if (t0 + j < T) {
-            const uint4 xu = reinterpret_cast<const uint4*>(x + long(t0 + j) * ldx)[v];
-            const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xu);
+        for (int i = 0; i < 8; ++i) {
+          if (v0 + 32 * i < nv) {
+            dst[v0 + 32 * i] = u[i];
+            if (norm_w) {
+              const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&u[i]);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float2 xf = __bfloat1622float2(xp[i]);
-              ssq[j] += xf.x * xf.x + xf.y * xf.y;
+              for (int c = 0; c < 4; ++c) {
+                const float2 f = __bfloat1622float2(xp[c]);
+                ssq += f.x * f.x + f.y * f.y;
+              }
             }
           }
         }
       }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ssq[j] += __shfl_xor_sync(0xffffffffu, ssq[j], o);
-        if (lane == 0) red[half][hwarp][j] = ssq[j];
-      }
-      __syncthreads();
-      if (htid < 8) {
-        float tot = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) tot += red[half][i][htid];
-        s_inv[half][htid] = rsqrtf(tot / float(H) + eps);
-      }
-      __syncthreads();
-    }
-    float acc[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int v = htid; v < nv; v += 256) {
-      const uint4 wu = w4[v];
-      const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wu);
-      float2 wf[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) wf[i] = __bfloat1622float2(wp[i]);
-      float nw[8];
       if (norm_w) {
-        const float4 n0 = reinterpret_cast<const float4*>(norm_w)[2 * v];
-        const float4 n1 = reinterpret_cast<const float4*>(norm_w)[2 * v + 1];
-        nw[0] = n0.x + w_offset; nw[1] = n0.y + w_offset; nw[2] = n0.z + w_offset; nw[3] = n0.w + w_offset;
-        nw[4] = n1.x + w_offset; nw[5] = n1.y + w_offset; nw[6] = n1.z + w_offset; nw[7] = n1.w + w_offset;
-      }
-      uint4 xu[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        xu[j] = make_uint4(0u, 0u, 0u, 0u);
-        if (t0 + j < T) xu[j] = reinterpret_cast<const uint4*>(x + long(t0 + j) * ldx)[v];
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        if (t0 + j < T) {
-          __nv_bfloat162* xp = reinterpret_cast<__nv_bfloat162*>(&xu[j]);
-          if (norm_w) {
-            const float inv = s_inv[half][j];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float2 xf = __bfloat1622float2(xp[i]);
-              xp[i] = __floats2bfloat162_rn(xf.x * inv * nw[2 * i], xf.y * inv * nw[2 * i + 1]);
-            }
-            if ((t0 + j) % gridDim.x == blockIdx.x)
-              reinterpret_cast<uint4*>(x_normed + long(t0 + j) * ldn)[v] = xu[j];
-          }
+        for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+        const float inv = rsqrtf(ssq / float(H) + eps);
+        const bool writer = (t % gridDim.x) == blockIdx.x;
+        for (int v = lane; v < nv; v += 32) {
+          uint4 u = dst[v];                    // written by this lane above
+          __nv_bfloat162* xp = reinterpret_cast<__nv_bfloat162*>(&u);
+          const float4 n0 = reinterpret_cast<const float4*>(norm_w)[2 * v];
+          const float4 n1 = reinterpret_cast<const float4*>(norm_w)[2 * v + 1];
+          const float nw[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const float2 xf = __bfloat1622float2(xp[i]);
-            acc[j] = fmaf(wf[i].x, xf.x, acc[j]);
-            acc[j] = fmaf(wf[i].y, xf.y, acc[j]);
+            const float2 f = __bfloat1622float2(xp[i]);
+            xp[i] = __floats2bfloat162_rn(f.x * inv * (nw[2 * i] + w_offset), f.y * inv * (nw[2 * i + 1] + w_offset));
           }
+          dst[v] = u;
+          if (writer) reinterpret_cast<uint4*>(x_normed + long(t) * ldn)[v] = u;
         }
       }
     }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
-      if (lane == 0) red[half][hwarp][j] = acc[j];
-    }
     __syncthreads();
-    if (htid < 8 && t0 + htid < T) {
-      float tot = 0.f;
+    if (row_ok) {
+      float acc[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) tot += red[half][i][htid];
-      if (is_gate) sh_logit[t0 + htid] = tot;
-      else logits[long(t0 + htid) * E + e] = tot;
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int v0 = lane; v0 < nv; v0 += 256) {       // eight weight vectors in flight per lane
+        uint4 wu[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (v0 + 32 * i < nv) wu[i] = w4[v0 + 32 * i];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int v = v0 + 32 * i;
+          if (v < nv) {
+            const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wu[i]);
+            float2 wf[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) wf[c] = __bfloat1622float2(wp[c]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int tok = tq * tpw + j;
+              if (j < tpw && base + tok < T) {
+                const uint4 xu = xs_rows[tok * nv + v];
+                const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xu);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                  const float2 xf = __bfloat1622float2(xp[c]);
+                  acc[j] = fmaf(wf[c].x, xf.x, acc[j]);
+                  acc[j] = fmaf(wf[c].y, xf.y, acc[j]);
+                }
+              }
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int tok = tq * tpw + j;
+        if (j < tpw && base + tok < T) {
+          float a = acc[j];
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+          if (lane == 0) {
+            if (is_gate) sh_logit[base + tok] = a;
+            else logits[long(base + tok) * E + e] = a;
+          }
+        }
+      }
     }
     __syncthreads();
   }
@@ -330,7 +363,7 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
   // The shared expert (stacked behind this rank's routed experts as group n_local) takes one more slot that every
   // token uses: its output rows are the pairs P .. P + T - 1, weighted by the sigmoid of its gate (or 1).
   const int n_slots = n_active + (shared_slot ? 1 : 0);
-  for (int i = tid; i < n_slots * bn; i += 512) out_rows[i] = -1;
+  for (int i = tid; i < n_slots * T; i += 512) out_rows[(i / T) * bn + i % T] = -1;   // tiles cover T rows per slot
   __syncthreads();
   for (int p = tid; p < P; p += 512) {
     const int slot = s_slot[s_ids[p]];
@@ -366,18 +399,31 @@ int moe_route_small_launch(const void* x, long ldx, const float* norm_w, float e
   if (k > 32 || E > 512 || n_group > 32 || H % 8 || T > 64 || T * k > 1024 || T > bn) return 1;
   if (sh_gate_w && (!sh_logit || !shared_slot)) return 1;
   auto sg = static_cast<const __nv_bfloat16*>(sh_gate_w);
-  const int grid = E + (sh_gate_w ? 1 : 0);
   auto xb = static_cast<const __nv_bfloat16*>(x);
   auto xn = static_cast<__nv_bfloat16*>(x_normed);
   auto wb = static_cast<const __nv_bfloat16*>(w);
+  const int epc = E >= 256 ? 8 : 4;                              // router rows per CTA
+  const int tpp = size_t(16) * H * 2 <= 192 * 1024 ? 16 : 8;     // tokens staged per pass
+  if (size_t(tpp) * H * 2 > 200 * 1024) return 1;
+  const int smem = tpp * H * 2;
+  const int grid = (E + (sh_gate_w ? 1 : 0) + epc - 1) / epc;
 #define LB_ROUTE(MAXE)                                                                                              \
-  launch_pdl(moe_route_small_kernel<MAXE>, dim3(grid), dim3(512), 0, s, xb, ldx, norm_w, eps, w_offset, xn, ldn,   \
-             wb, ldw, H, logits, bias, E, k, mode, renorm, route_scale, n_group, topk_group, ids, wts, T, bn,       \
-             tile_group, slot_base, tile_ntok, meta, out_rows, tok_scale, done_ctr, e_lo, n_local, sg, sh_logit,    \
-             shared_slot)
-  if (E <= 128) LB_ROUTE(128);
-  else if (E <= 256) LB_ROUTE(256);
-  else LB_ROUTE(512);
+  {                                                                                                                 \
+    static int smem_set = 0;                                                                                        \
+    if (smem > smem_set) {                                                                                          \
+      if (cudaFuncSetAttribute(moe_route_small_kernel<MAXE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=  \
+          cudaSuccess)                                                                                              \
+        return 1;                                                                                                   \
+      smem_set = smem;                                                                                              \
+    }                                                                                                               \
+    launch_pdl(moe_route_small_kernel<MAXE>, dim3(grid), dim3(512), smem, s, xb, ldx, norm_w, eps, w_offset, xn,   \
+               ldn, wb, ldw, H, logits, bias, E, k, mode, renorm, route_scale, n_group, topk_group, ids, wts, T,    \
+               bn, tile_group, slot_base, tile_ntok, meta, out_rows, tok_scale, done_ctr, e_lo, n_local, sg,        \
+               sh_logit, shared_slot, epc, tpp);                                                                    \
+  }
+  if (E <= 128) LB_ROUTE(128)
+  else if (E <= 256) LB_ROUTE(256)
+  else LB_ROUTE(512)
 #undef LB_ROUTE
   return cudaGetLastError() != cudaSuccess;
 }
