@@ -1,19 +1,26 @@
 #!/usr/bin/env python
-"""Headline benchmark: decode tokens/s of the 30B-A3B-shape MoE (48 layers, hidden 2048, 32 q / 4 kv heads,
-128 experts top-8, FFN 768, vocab 151936) in bf16 with random-init weights and synthetic token ids, at
-16 concurrent users with 8K-token prompts, tensor-parallel over N GPUs of one node (strong scaling).
+"""Headline benchmark: decode tokens/s at 1 / 16 / 64 concurrent users and tokens/s of a 32K-token prefill, on one of
+the named model configurations, random-init weights and synthetic token ids, over N GPUs of one node.
 
-    python bench.py --gpus N --steps K --warmup W          (N > 1: launched by torch.distributed.run)
+    python bench.py --gpus N --steps K --warmup W [--config 3]      (N > 1: launched by torch.distributed.run)
+
+Configurations (``--config``):
+  3  (default) 80B-A3B-shape hybrid MoE, experts in NVFP4 (native W4A4 tensor-core path): 48 layers, 3:1 Gated
+     DeltaNet to gated attention, 512 experts top-10 + shared expert, 1K-token prompts for the decode rows.
+  2  30B-A3B-shape MoE in bf16: 48 layers, 128 experts top-8, 8K-token prompts.
+  5  dense 27B-shape model in bf16, 1K-token prompts.
+The ONE parsed number (``value``) is decode tokens/s at 16 users of the selected configuration; the other rows of
+the grid (1 and 64 users, 32K prefill) are under ``extra``.
 
 What is timed
-  value        K decode steps of the whole batch, device-timed with CUDA events around K replays of the
-               captured decode-step graph (every kernel of the step: 48 layers, LM head, arg-max), max over
-               ranks. A step reads ~50 GB of weights + KV, far more than L2, so no L2 flush is needed.
-  e2e          the same K steps through the public engine API (LmEngine.generate streams): each step packs
-               that step's token ids / positions / block tables in pinned host memory, copies them to the
-               device, replays the graph and reads the picked tokens back. Wall clock on rank 0 between the
-               step after the last first-token and the last finish.
-  prefill      tokens/s of prefilling the prompts (reported in "extra", device-timed).
+  value        K decode steps of the whole batch, device-timed with CUDA events around K replays of the captured
+               decode-step graph (every kernel of the step: all layers, LM head, arg-max), max over ranks; the
+               K-step region is repeated ``--repeats`` times and the median is reported (min / max under extra).
+               A step streams several GB of weights and state, far more than L2, so no L2 flush is needed.
+  e2e          the same K steps through the public engine API (LmEngine.generate streams): each step packs that
+               step's token ids / positions / block tables in pinned host memory, copies them to the device,
+               replays the graph and reads the picked tokens back. Wall clock on rank 0.
+  prefill      one prompt of ``--prefill-len`` tokens through the engine in chunks, device-timed to its first token.
 ``--impl reference`` reports that the reference cannot be built here (no Rust toolchain, empty ggml submodule).
 """
 from __future__ import annotations
@@ -26,8 +33,6 @@ import subprocess
 import sys
 import threading
 import time
-
-BASELINE_DECODE_16 = 262.3   # reference's best published 16-user decode tok/s (NVFP4 hybrid MoE, 2x DGX Spark TP)
 
 
 def reference_arm():
@@ -59,7 +64,7 @@ class ClockSampler:
                         self.rows.append([c.strip() for c in line.split(",")])
                 except Exception:
                     pass
-                self._stop.wait(0.2)
+                self._stop.wait(0.1)
         self._t = threading.Thread(target=loop, daemon=True)
         self._t.start()
 
@@ -81,23 +86,61 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+CONFIGS = {
+    2: dict(model="qwen3-30b-a3b", prompt_len=8192, weights="bf16", dtype="bf16"),
+    3: dict(model="qwen35-80b-a3b", prompt_len=1024, weights="nvfp4", dtype="nvfp4 experts (W4A4), bf16 elsewhere"),
+    5: dict(model="dense-27b", prompt_len=1024, weights="bf16", dtype="bf16"),
+}
+
+
+def build_model(a, cfg, dev, pctx, shard, weights_mode):
+    """Random-init weights generated on the device; NVFP4 configurations are folded and quantised layer by layer
+    while they are generated (their bf16 form would not fit one GPU)."""
+    import torch
+    from legion_b200.models.decoder import Decoder, fold_shared_expert, quantize_moe_layer_nvfp4
+    from legion_b200.models.weights import layer_of, random_weights
+    world = pctx.world
+    post = None
+    if weights_mode == "nvfp4":
+        def post(name, out):
+            # the last expert tensor of a layer has arrived: stack the shared expert behind the routed ones
+            # (single GPU) and encode the layer
+            il = layer_of(name)
+            if il is None or not cfg.is_moe_layer(il):
+                return
+            last = "moe.sh_gate" if (cfg.shared_ff > 0 and cfg.shared_gate) else ("moe.sh_down" if cfg.shared_ff > 0
+                                                                                   else "moe.down")
+            if not name.endswith(last):
+                return
+            p = f"l{il}"
+            if world == 1 and not a.no_fold:
+                fold_shared_expert(out, p, cfg)
+            quantize_moe_layer_nvfp4(out, p, native=not a.nvfp4_expand)
+    weights = random_weights(cfg, dev, torch.bfloat16, seed=0, shard=shard, post=post)
+    torch.cuda.synchronize()
+    return weights
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--model", default="qwen3-30b-a3b")
-    ap.add_argument("--users", type=int, default=16)
-    ap.add_argument("--prompt-len", type=int, default=8192)
+    ap.add_argument("--config", type=int, default=3, choices=sorted(CONFIGS))
+    ap.add_argument("--users", type=int, default=16, help="users of the headline row")
+    ap.add_argument("--grid", default="1,64", help="other user counts reported under extra ('' = none)")
+    ap.add_argument("--prompt-len", type=int, default=0, help="prompt length of the decode rows (0 = the config's)")
+    ap.add_argument("--prefill-len", type=int, default=32768, help="length of the single-prompt prefill row (0 = skip)")
+    ap.add_argument("--repeats", type=int, default=5, help="how often the K-step timed region is repeated")
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
-    ap.add_argument("--ep-capacity", type=float, default=0.0,
-                    help="--moe dp: receive room per rank as a multiple of its own routed pairs (0 = worst case)")
-    ap.add_argument("--moe", default="auto", choices=["auto", "tp", "ep", "dp"],
+    ap.add_argument("--moe", default="auto", choices=["auto", "tp", "ep"],
                     help="N > 1: slice every expert's FFN rows over the ranks (tp) or keep whole experts per rank "
                          "with mirrored tokens, partial outputs meeting in the layer's reduction (ep). auto: ep "
-                         "from 4 GPUs (measured 6.67 vs 7.15 ms per step at 4 GPUs, 6.28 vs 7.11 ms at 8)")
-    ap.add_argument("--moe-ep", action="store_true", help="same as --moe ep")
+                         "from 4 GPUs for bf16 experts, always for NVFP4 experts")
+    ap.add_argument("--no-fold", action="store_true", help="keep the shared expert as a dense FFN of its own")
+    ap.add_argument("--nvfp4-expand", action="store_true",
+                    help="NVFP4 experts on the de-quantising GEMM (W4A16) instead of the native W4A4 path")
     ap.add_argument("--profile-range", action="store_true",
                     help="after the timed region, replay one decode step between cudaProfilerStart/Stop "
                          "(for a profiler started with --profile-from-start off)")
@@ -113,7 +156,7 @@ def main(argv=None):
     from legion_b200.engine.types import GenerateRequest, SamplingParams
     from legion_b200.loaders.tokenizer import ByteTokenizer
     from legion_b200.models.decoder import Decoder
-    from legion_b200.models.weights import Shard, random_weights
+    from legion_b200.models.weights import Shard
     from legion_b200.ops import sm100
     from legion_b200.parallel import dist as pdist
 
@@ -121,151 +164,176 @@ def main(argv=None):
     assert world == a.gpus or (a.gpus == 1 and world == 1), f"--gpus {a.gpus} but WORLD_SIZE={world}"
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
-    cfg = PRESETS[a.model]()
+    spec = CONFIGS[a.config]
+    cfg = PRESETS[spec["model"]]()
     if a.layers:
         cfg.n_layer = a.layers
         cfg.layer_kinds = cfg.layer_kinds[:a.layers]
-    W, K, U, L = max(3, a.warmup), a.steps, a.users, a.prompt_len
-    ep = world > 1 and (a.moe_ep or a.moe == "ep" or (a.moe == "auto" and world >= 4))
-    dp = world > 1 and a.moe == "dp"
-    if dp:
-        # data-parallel attention: every rank runs attention for its own users, tokens meet their experts through
-        # the fused dispatch / combine of each MoE layer
-        import torch.distributed as dist
-        from legion_b200.parallel.context import DpEpCtx
-        from legion_b200.parallel.ep import EpDispatcher
-        pdist.init_from_env("cuda", comm="nccl")
-        disp = EpDispatcher(dist.group.WORLD, rank, world, dev, cfg.n_expert, cfg.top_k, cfg.hidden, cfg.expert_ff,
-                            8192, a.ep_capacity or None)
-        pctx = DpEpCtx(rank, world, dist.group.WORLD, disp)
-        shard = Shard(cfg, rank, world, dp_attention=True)
-    else:
-        pctx = pdist.init_from_env("cuda", comm=a.comm, max_rows=8192, hidden=cfg.hidden, expert_parallel=ep)
-        shard = Shard(cfg, rank, world, expert_parallel=ep) if world > 1 else None
+    W, K, L = max(3, a.warmup), a.steps, a.prompt_len or spec["prompt_len"]
+    grid = [int(u) for u in a.grid.split(",") if u.strip()]
+    all_users = sorted(set(grid + [a.users]))
+    U_max = max(all_users)
+    nvfp4 = spec["weights"] == "nvfp4"
+    ep = world > 1 and cfg.n_expert > 0 and (a.moe == "ep" or (a.moe == "auto" and (world >= 4 or nvfp4)))
+    pctx = pdist.init_from_env("cuda", comm=a.comm, max_rows=8192, hidden=cfg.hidden, expert_parallel=ep)
+    shard = Shard(cfg, rank, world, expert_parallel=ep) if world > 1 else None
     t0 = time.time()
-    weights = random_weights(cfg, dev, torch.bfloat16, seed=0, shard=shard)
-    torch.cuda.synchronize()
+    weights = build_model(a, cfg, dev, pctx, shard, spec["weights"])
     load_s = time.time() - t0
-    # early sequences already decode while the later prompts prefill: leave room for those steps too
-    gen_budget = W + K + 16 + U * ((L + 8191) // 8192 + 1)
-    ec = EngineConfig(ctx_size=L + gen_budget + 64, max_seqs=U, max_batch_tokens=8192, prefill_chunk=8192, block_size=64,
-                      prefix_cache=False, device=str(dev), model_name=a.model)
-    model = Decoder(cfg, weights, pctx, max_position=ec.ctx_size + 8)
-    eng = LmEngine(model, ByteTokenizer(cfg.vocab), ec, start=False)
-
-    # ---- prompts: synthetic uniform-random token ids in pinned host memory
+    tok = ByteTokenizer(cfg.vocab)
     g = torch.Generator().manual_seed(1234)
-    prompts = torch.randint(0, cfg.vocab, (U, L), generator=g, dtype=torch.int32).pin_memory()
-    streams = []
-    for u in range(U):
-        req = GenerateRequest(prompt_tokens=prompts[u].tolist(), request_id=f"u{u}",
-                              sampling=SamplingParams(temperature=0.0, max_tokens=gen_budget, ignore_eos=True))
-        streams.append(eng.generate(req))
-
-    # ---- prefill: drive the engine on this thread until every sequence decodes (device-timed)
-    eng._drain(block=False)
+    extra = {"weights_init_s": round(load_s, 1)}
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    pdist.barrier(); torch.cuda.synchronize()
-    ev0.record()
-    guard = 0
-    while True:
-        eng._admit()
-        if eng.running and all(s.phase == "decode" for s in eng.running) and len(eng.waiting) == 0:
-            break
-        eng.step()
-        guard += 1
-        assert guard < 10000
-    ev1.record()
-    torch.cuda.synchronize()
-    prefill_ms = pdist.all_reduce_max(ev0.elapsed_time(ev1), dev)
-    assert len(eng.running) == U
 
-    # ---- e2e decode through the engine's step (pinned H2D of inputs + D2H of picks every step)
-    for _ in range(W):
-        eng.step()
-    clocks = ClockSampler(local_rank)
-    pdist.barrier(); torch.cuda.synchronize()
-    graphs = eng._graphs
-    h2d0, d2h0, rep0 = graphs.h2d_bytes, graphs.d2h_bytes, graphs.replays
-    launches0 = sm100.LAUNCHES["n"]
-    t_e2e0 = time.perf_counter()
-    n_e2e = K
-    for _ in range(n_e2e):
-        eng.step()
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t_e2e0
-    e2e_s = pdist.all_reduce_max(e2e_s, dev)
-    replays = graphs.replays - rep0
-    h2d_per = (graphs.h2d_bytes - h2d0) / max(1, replays)
-    d2h_per = (graphs.d2h_bytes - d2h0) / max(1, replays)
-    assert replays == n_e2e, "decode steps did not run through the captured graph"
-    assert len(eng.running) == U and all(not s.finished for s in eng.running), \
-        "a sequence finished inside the timed region: the step no longer carries the full batch"
-
-    # ---- device-timed steps: K replays of the decode-step graph with the current inputs
-    entry = graphs.entries[graphs.bucket((U + world - 1) // world if dp else U)]
-    # kernels per step: count them once with an eager run of the same step on the same inputs
-    sm100.LAUNCHES["n"] = 0
-    eng.model.forward(entry.batch, eng.kv, eng.states)
-    sm100.argmax(torch.zeros(U, cfg.vocab, device=dev))
-    torch.cuda.synchronize()
-    launches_per_step = sm100.LAUNCHES["n"]
-    def replay_step():
-        entry.graph.replay()
-        if dp:      # the step's picks of all ranks, as the engine gathers them
-            dist.all_gather_into_tensor(entry.all_picks, entry.picks, group=pctx.dp_group)
-
-    for _ in range(W):
-        replay_step()
-    clocks.start()
-    pdist.barrier(); torch.cuda.synchronize()
-    ev0.record()
-    for _ in range(K):
-        replay_step()
-    ev1.record()
-    torch.cuda.synchronize()
-    pdist.barrier()
-    dev_ms = pdist.all_reduce_max(ev0.elapsed_time(ev1), dev)
-    clk = clocks.stop()
-    if a.profile_range:
-        torch.cuda.profiler.start()
-        entry.graph.replay()
+    def drive_prefill(eng, n_seqs):
+        """Steps the engine on this thread until every sequence decodes; returns the device time in ms."""
+        eng._drain(block=False)
+        pdist.barrier(); torch.cuda.synchronize()
+        ev0.record()
+        guard = 0
+        while True:
+            eng._admit()
+            if eng.running and all(s.phase == "decode" for s in eng.running) and len(eng.waiting) == 0:
+                break
+            eng.step()
+            guard += 1
+            assert guard < 10000
+        ev1.record()
         torch.cuda.synchronize()
-        torch.cuda.profiler.stop()
-    status = sm100.Workspace.get(dev).check()
-    comm_status = 0
-    if pctx.symm is not None:
-        comm_status = int(pctx.symm.status.item())
-    if dp:
-        comm_status = int(disp.status.item())
+        assert len(eng.running) == n_seqs
+        return pdist.all_reduce_max(ev0.elapsed_time(ev1), dev)
 
-    ms_per_step = dev_ms / K
-    value = U * 1000.0 / ms_per_step
-    e2e_value = U * n_e2e / e2e_s
+    # ------------------------------------------------------------------ one long prompt: prefill tokens/s
+    if a.prefill_len > 0:
+        PL = a.prefill_len
+        ec = EngineConfig(ctx_size=PL + 64, max_seqs=1, max_batch_tokens=8192, prefill_chunk=8192, block_size=64,
+                          prefix_cache=False, device=str(dev), model_name=spec["model"], cuda_graphs=False)
+        model = Decoder(cfg, weights, pctx, max_position=ec.ctx_size + 8)
+        eng = LmEngine(model, tok, ec, start=False)
+        times = []
+        for rep in range(3):
+            prompt = torch.randint(0, cfg.vocab, (PL,), generator=g, dtype=torch.int32).tolist()
+            st = eng.generate(GenerateRequest(prompt_tokens=prompt, request_id=f"p{rep}",
+                                              sampling=SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)))
+            times.append(drive_prefill(eng, 1))
+            st.cancel()
+            eng._handle_cancels()
+            for _ in range(2):
+                eng.step()
+            assert not eng.running
+        ms = statistics.median(times[1:]) if len(times) > 1 else times[0]     # the first pass also sizes workspaces
+        extra["prefill_32k"] = {"prompt_len": PL, "tok_s": round(PL / (ms / 1000.0), 1), "ms": round(ms, 1),
+                                "ms_all": [round(t, 1) for t in times], "chunk": 8192}
+        del eng, model
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+
+    # ------------------------------------------------------------------ decode rows
+    gen_budget = (len(all_users) + 1) * ((W + K) * (a.repeats + 2) + 64) + 2 * U_max
+    ec = EngineConfig(ctx_size=L + gen_budget + 64, max_seqs=U_max, max_batch_tokens=8192, prefill_chunk=8192,
+                      block_size=64, prefix_cache=False, device=str(dev), model_name=spec["model"])
+    model = Decoder(cfg, weights, pctx, max_position=ec.ctx_size + 8)
+    eng = LmEngine(model, tok, ec, start=False)
+    graphs = eng._graphs
+    assert graphs is not None, "decode steps must run from captured CUDA graphs"
+    rows = {}
+    headline = None
+    clk = None
+    for U in all_users:
+        prompts = torch.randint(0, cfg.vocab, (U, L), generator=g, dtype=torch.int32).pin_memory()
+        streams = [eng.generate(GenerateRequest(prompt_tokens=prompts[u].tolist(), request_id=f"u{U}_{u}",
+                                                sampling=SamplingParams(temperature=0.0, max_tokens=gen_budget,
+                                                                        ignore_eos=True))) for u in range(U)]
+        prefill_ms = drive_prefill(eng, U)
+        for _ in range(W):
+            eng.step()
+        is_head = U == a.users
+        row = {"users": U, "prompt_len": L, "prefill_ms": round(prefill_ms, 1)}
+        if is_head:
+            # ---- e2e through the engine's step (pinned H2D of inputs + D2H of picks every step)
+            pdist.barrier(); torch.cuda.synchronize()
+            h2d0, d2h0, rep0 = graphs.h2d_bytes, graphs.d2h_bytes, graphs.replays
+            t_e2e0 = time.perf_counter()
+            for _ in range(K):
+                eng.step()
+            torch.cuda.synchronize()
+            e2e_s = pdist.all_reduce_max(time.perf_counter() - t_e2e0, dev)
+            replays = graphs.replays - rep0
+            assert replays == K, "decode steps did not run through the captured graph"
+            row["e2e"] = {"value": round(U * K / e2e_s, 2), "unit": "tok/s",
+                          "h2d_bytes_per_step": int((graphs.h2d_bytes - h2d0) / replays),
+                          "d2h_bytes_per_step": int((graphs.d2h_bytes - d2h0) / replays), "steps": K}
+        assert len(eng.running) == U and all(not s.finished for s in eng.running), \
+            "a sequence finished before the timed region: the step no longer carries the full batch"
+        entry = graphs.entries[graphs.bucket(U)]
+        if is_head:
+            # kernels per step: counted once with an eager run of the same step on the same inputs
+            sm100.LAUNCHES["n"] = 0
+            eng.model.forward(entry.batch, eng.kv, eng.states)
+            sm100.argmax(torch.zeros(U, cfg.vocab, device=dev))
+            torch.cuda.synchronize()
+            row["launches_per_step"] = sm100.LAUNCHES["n"]
+        for _ in range(W):
+            entry.graph.replay()
+        clocks = ClockSampler(local_rank) if is_head else None
+        if clocks:
+            clocks.start()
+        reps = []
+        for _ in range(max(1, a.repeats)):
+            pdist.barrier(); torch.cuda.synchronize()
+            ev0.record()
+            for _ in range(K):
+                entry.graph.replay()
+            ev1.record()
+            torch.cuda.synchronize()
+            pdist.barrier()
+            reps.append(pdist.all_reduce_max(ev0.elapsed_time(ev1), dev) / K)
+        if clocks:
+            clk = clocks.stop()
+        if a.profile_range and is_head:
+            torch.cuda.profiler.start()
+            entry.graph.replay()
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+        ms = statistics.median(reps)
+        row.update({"ms_per_step": round(ms, 4), "tok_s": round(U * 1000.0 / ms, 2),
+                    "ms_min": round(min(reps), 4), "ms_max": round(max(reps), 4), "repeats": len(reps), "steps": K})
+        rows[U] = row
+        if is_head:
+            headline = row
+        for s in streams:
+            s.cancel()
+        eng._handle_cancels()
+        for _ in range(2):
+            eng.step()
+        assert not eng.running, "cancelled sequences are still running"
+    status = sm100.Workspace.get(dev).check()
+    comm_status = int(pctx.symm.status.item()) if pctx.symm is not None else 0
+
+    par = "single GPU" if world == 1 else (f"tp{world}" + ("+ep(experts whole per rank, tokens mirrored)" if ep else ""))
+    extra.update({"decode": {str(u): rows[u] for u in all_users}, "kernel_status_word": status,
+                  "comm_status_word": comm_status, "launches_per_step": headline.get("launches_per_step"),
+                  "shared_expert": ("stacked behind the routed experts (one slot of the grouped GEMMs)"
+                                    if (nvfp4 and world == 1 and not a.no_fold and cfg.shared_ff) else "dense FFN"),
+                  "region": f"median of {len(reps)} regions of {K} steps; min / max per row"})
     out = {
-        "metric": "decode tok/s @16 users (8K-token prompts), device-timed",
-        "value": round(value, 2), "unit": "tok/s", "n_gpus": a.gpus, "steps": K, "warmup": W,
-        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": round(value / BASELINE_DECODE_16, 3), "dtype": "bf16", "data": "synthetic",
-        "config": {"model": a.model + ("" if not a.layers else f"-TRUNCATED-{a.layers}L-INVALID"), "global_batch": U,
-                   "seq_len": L, "parallelism": (f"dp{a.gpus}(attention)+ep{a.gpus}(token dispatch)" if dp else
-                                                    f"tp{a.gpus}" + ("+ep(experts whole per rank)" if ep else "")),
-                   "users": U, "comm": ("fused" if dp else a.comm) if a.gpus > 1 else "none",
-                   "l2": "inputs larger than L2 (each step streams >40 GB of weights and KV)", "page": 64},
+        "metric": f"decode tok/s @{a.users} users ({L}-token prompts), device-timed",
+        "value": headline["tok_s"], "unit": "tok/s", "n_gpus": a.gpus, "steps": K, "warmup": W,
+        "ms_per_step": headline["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": spec["dtype"], "data": "synthetic",
+        "config": {"model": spec["model"] + ("" if not a.layers else f"-TRUNCATED-{a.layers}L-INVALID"),
+                   "baseline_config": a.config, "global_batch": a.users, "seq_len": L, "parallelism": par,
+                   "users": a.users, "comm": a.comm if a.gpus > 1 else "none",
+                   "l2": "inputs larger than L2 (each step streams several GB of weights, recurrent state and KV)",
+                   "page": 64, "weights": spec["weights"]},
         "clocks": clk,
-        "e2e": {"value": round(e2e_value, 2), "unit": "tok/s", "h2d_bytes_per_step": int(h2d_per),
-                "d2h_bytes_per_step": int(d2h_per), "steps": n_e2e},
-        "gpu_launches": int(launches_per_step * K),
-        "extra": {"prefill_tok_s": round(U * L / (prefill_ms / 1000.0), 1), "prefill_ms": round(prefill_ms, 1),
-                  "launches_per_step": launches_per_step, "weights_init_s": round(load_s, 1),
-                  "kernel_status_word": status, "comm_status_word": comm_status,
-                  "baseline_note": "vs_baseline divides by the reference's best published 16-user decode rate "
-                                   "(262.3 tok/s, NVFP4 hybrid MoE on 2x DGX Spark); no B200 number is published"},
+        "e2e": headline.get("e2e"),
+        "gpu_launches": int(headline.get("launches_per_step", 0) * K * max(1, a.repeats)),
+        "extra": extra,
     }
     if rank == 0:
         print(json.dumps(out), flush=True)
-    for s in streams:
-        s.cancel()
     if world > 1:
         import torch.distributed as dist
         eng.release_graphs()

@@ -514,7 +514,21 @@ class Decoder:
         else:
             raise ValueError(kind)
         routing = None
-        if moe and pc.world == 1 and isinstance(a, PendingLinear) and resid is not None and ops.sm100.TUNE["route_norm"]:
+        nv4_decode = False
+        if moe and isinstance(a, PendingLinear) and resid is not None and a.x.is_cuda and a.x.shape[0] <= 64 \
+                and pc.world == 1 and self.expert_cache.get(p) is None:
+            wg = w.get(f"{p}.moe.gate_up_s")
+            nv4_decode = isinstance(wg if wg is not None else w.get(f"{p}.moe.gate_up"), ops.sm100.Nv4Weight)
+        if nv4_decode:
+            # decode-sized step on NVFP4 experts: one launch adds the residual, applies the FFN norm and encodes the
+            # normalised rows for the expert GEMMs; the router reads the bf16 copy
+            att = ops.linear(a.x, a.w)
+            xq = ops.sm100.nv4_quant_act(att, norm=(w[f"{p}.ffn_norm"], cfg.rms_eps, cfg.norm_offset), residual=resid,
+                                         want_normed=True, key="ffn_in")
+            resid, h = xq.summed, xq.normed
+            routing = self._route(p, h)
+            routing.xq = xq
+        elif moe and pc.world == 1 and isinstance(a, PendingLinear) and resid is not None and ops.sm100.TUNE["route_norm"]:
             # single rank: the projection's epilogue adds the residual and the routing launch applies the FFN norm
             resid = ops.linear(a.x, a.w, residual=resid)
             routing = self._route(p, resid, norm=(w[f"{p}.ffn_norm"], cfg.rms_eps, cfg.norm_offset))

@@ -123,10 +123,12 @@ def layer_of(name: str) -> Optional[int]:
 
 
 def random_weights(cfg: ModelConfig, device="cpu", dtype=torch.float32, seed: int = 0, std: float = 0.02,
-                   shard: Optional["Shard"] = None, keep=None) -> Dict[str, torch.Tensor]:
+                   shard: Optional["Shard"] = None, keep=None, post=None) -> Dict[str, torch.Tensor]:
     """N(0, std) matrices; norm weights 1, A in (-1, -0.1), dt_bias small. With ``shard`` only this rank's
     slices are created (device-side generation for models too large for the host). ``keep(name)`` drops
-    tensors a pipeline stage does not own; the kept ones equal those of the full model."""
+    tensors a pipeline stage does not own; the kept ones equal those of the full model. ``post(name, weights)``
+    runs after every tensor and may replace entries of the dictionary (a model whose bf16 form does not fit the
+    device is quantised layer by layer while it is generated)."""
     device = torch.device(device)
     out: Dict[str, torch.Tensor] = {}
     g = torch.Generator(device="cpu").manual_seed(seed)
@@ -157,6 +159,9 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=torch.float32, seed: in
             t = (torch.randn(shp, generator=g) * std).to(device=device, dtype=wd)
         if not dropped:                   # dropped host-generated tensors still advanced the generator
             out[name] = t.to(wd)
+            if post is not None:
+                del t
+                post(name, out)
     return out
 
 

@@ -739,12 +739,13 @@ def router_topk(logits, k, mode="softmax", renorm=True, route_scale=1.0, bias=No
 class Routing:
     """Router result of one step: ``ids`` / ``wts`` [T, k] and, for decode-sized steps, the dense routing tables
     (``dense``) that let the expert GEMMs run without a gather. Unpacks as ``ids, wts = routing``."""
-    __slots__ = ("ids", "wts", "dense", "x_normed", "e_lo", "n_local", "shared_slot")
+    __slots__ = ("ids", "wts", "dense", "x_normed", "e_lo", "n_local", "shared_slot", "xq")
 
     def __init__(self, ids, wts, dense=None, x_normed=None, e_lo=0, n_local=None):
         self.ids, self.wts, self.dense, self.x_normed = ids, wts, dense, x_normed
         self.e_lo, self.n_local = e_lo, n_local      # expert range the dense tables were built for
         self.shared_slot = False                     # the shared expert has a slot of its own in the dense tables
+        self.xq = None                               # the experts' input already NVFP4-encoded (Nv4Act)
 
     def __iter__(self):
         yield self.ids
@@ -929,7 +930,7 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[Moe
     if isinstance(w_gate_up, Nv4Weight):
         if _dense_ok(routing, E_local, e_lo, ids):
             return _moe_experts_nv4(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, shared, shared_gate, residual, out,
-                                    norm, routing)
+                                    norm, routing, xq=routing.xq)
         # larger steps: the de-quantising grouped GEMM over the routing plan (same codes, linear scale order)
         w_gate_up, w_down = w_gate_up.as_qweight(), w_down.as_qweight()
     if routing is not None and routing.shared_slot and not _dense_ok(routing, E_local, e_lo, ids):
