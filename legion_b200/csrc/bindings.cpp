@@ -415,7 +415,7 @@ void moe_route_small(const Tensor& x, const OptT& norm_w, double eps, double w_o
                      int64_t n_group, int64_t topk_group, Tensor& logits, Tensor& ids, Tensor& wts, int64_t bn,
                      Tensor& tile_group, Tensor& slot_base, Tensor& tile_ntok, Tensor& meta, Tensor& out_rows,
                      Tensor& tok_scale, Tensor& done_ctr, int64_t e_lo, int64_t n_local, const OptT& sh_gate_w,
-                     const OptT& sh_logit, bool shared_slot) {
+                     const OptT& sh_logit, bool shared_slot, Tensor& status, Tensor& active) {
   check_bf16(x, "x");
   check_bf16(w, "w");
   const int64_t T = x.size(0), E = w.size(0);
@@ -428,6 +428,8 @@ void moe_route_small(const Tensor& x, const OptT& norm_w, double eps, double w_o
   TORCH_CHECK(x.size(1) == w.size(1) && x.stride(1) == 1 && w.stride(1) == 1, "moe_route_small: shape mismatch");
   TORCH_CHECK(norm_w.has_value() == x_normed.has_value(), "moe_route_small: norm weight and output go together");
   TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.numel() >= T * E, "moe_route_small: logits too small");
+  TORCH_CHECK(done_ctr.numel() >= 2 && done_ctr.element_size() == 4, "moe_route_small: two int32 counters");
+  TORCH_CHECK(active.scalar_type() == at::kInt && active.numel() >= n_local, "moe_route_small: active flags [n_local]");
   const int64_t max_slots = std::min<int64_t>(E, n_local) + (shared_slot ? 1 : 0);
   TORCH_CHECK(tile_group.numel() >= max_slots && slot_base.numel() >= max_slots && tile_ntok.numel() >= max_slots &&
                   meta.numel() >= 2 && out_rows.numel() >= max_slots * bn && tok_scale.numel() >= max_slots * bn,
@@ -443,7 +445,7 @@ void moe_route_small(const Tensor& x, const OptT& norm_w, double eps, double w_o
                   meta.data_ptr<int>(), out_rows.data_ptr<int>(), tok_scale.data_ptr<float>(),
                   reinterpret_cast<unsigned int*>(done_ctr.data_ptr()), int(e_lo), int(n_local),
                   sh_gate_w.has_value() ? sh_gate_w->data_ptr() : nullptr, optpm<float>(sh_logit), shared_slot ? 1 : 0,
-                  cur_stream()) == 0,
+                  reinterpret_cast<int*>(status.data_ptr()), active.data_ptr<int>(), cur_stream()) == 0,
               "moe_route_small: unsupported (tokens <= 64 and <= bn, pairs <= 1024, experts <= 512, k <= 32)");
 }
 

@@ -60,7 +60,7 @@ int moe_route_small_launch(const void* x, long ldx, const float* norm_w, float e
                            int mode, int renorm, float route_scale, int n_group, int topk_group, int* ids, float* wts,
                            int T, int bn, int* tile_group, int* slot_base, int* tile_ntok, int* meta, int* out_rows,
                            float* tok_scale, unsigned int* done_ctr, int e_lo, int n_local, const void* sh_gate_w, float* sh_logit,
-                           int shared_slot, cudaStream_t s);
+                           int shared_slot, int* status, int* active, cudaStream_t s);
 int moe_plan_gather_small_launch(const int* ids, const float* wts, int n_tokens, int k, int e_lo, int n_local, int bn,
                                  int* counts, int* offsets, int* sorted_token, int* sorted_pair, float* sorted_w,
                                  int* tile_group, int* tile_tok0, int* tile_ntok, int max_tiles, int* meta,

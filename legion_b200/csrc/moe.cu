@@ -201,17 +201,19 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
     int topk_group, int* ids, float* wts, int T, int bn, int* __restrict__ tile_group, int* __restrict__ slot_base,
     int* __restrict__ tile_ntok, int* __restrict__ meta, int* __restrict__ out_rows, float* __restrict__ tok_scale,
     unsigned int* done_ctr, int e_lo, int n_local, const __nv_bfloat16* __restrict__ sh_gate_w, float* sh_logit,
-    int shared_slot, int epc, int tpp) {
+    int shared_slot, int epc, int tpp, int* status, int* __restrict__ active) {
   extern __shared__ uint4 xs_rows[];          // [tpp][H / 8] token rows of the current pass
   __shared__ int s_last;
-  __shared__ int s_ids[1024];
-  __shared__ float s_wts[1024];
+  __shared__ float s_logit[512];
+  __shared__ float s_red[16];
+  __shared__ unsigned long long s_cand[16 * 32];
   __shared__ int s_wsum[17];
-  __shared__ int s_slot[512];
+  __shared__ int s_chosen[512];
   griddep_wait();
   griddep_launch();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nv = H / 8;
+
   const int wpe = 16 / epc;                   // warps per router row
   const int tpw = tpp / wpe;                  // tokens of a pass per warp
   const int e = blockIdx.x * epc + warp / wpe;
@@ -315,75 +317,180 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
         }
       }
     }
+    if (lane == 0) __threadfence();   // the writer publishes; the counter is raised after the CTA's barrier
     __syncthreads();
   }
+  // ---- every CTA has written its logits: count it in. The CTAs that own tokens (token t belongs to CTA t mod grid)
+  // wait for the whole grid (bounded; the grid is far smaller than the number of SMs, so all CTAs are resident),
+  // then each selects the top-k of its tokens with all sixteen warps, so the selections of a step run on up to T
+  // SMs at once instead of one after the other on the last one.
+  const int n_tok_ctas = T < int(gridDim.x) ? T : int(gridDim.x);
   if (tid == 0) {
     __threadfence();
-    const unsigned int old = atomicAdd(done_ctr, 1u);
-    s_last = (old == gridDim.x - 1);
-    if (s_last) *done_ctr = 0;
+    atomicAdd(&done_ctr[0], 1u);
+    s_last = 1;
+    if (int(blockIdx.x) < n_tok_ctas) {
+      const uint64_t t_start = globaltimer_ns();
+      uint32_t spins = 0;
+      while (*reinterpret_cast<volatile unsigned int*>(&done_ctr[0]) < gridDim.x) {
+        if ((++spins & 0x3f) == 0 && globaltimer_ns() - t_start > 2000000000ull) {
+          atomicCAS(status, 0, ST_TIMEOUT_FLAG);
+          break;
+        }
+      }
+    }
+  }
+  if (int(blockIdx.x) >= n_tok_ctas) return;
+  __syncthreads();
+  __threadfence();
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    if (n_group > 1) {
+      // group-limited routing: the one-warp form (it ranks the groups inside a warp)
+      if (warp == 0)
+        router_topk_row<MAXE>(logits, E, bias, E, k, mode, renorm, route_scale, n_group, topk_group, ids, wts, t);
+      continue;
+    }
+    // thread e holds expert e: score, packed key (score bits above, inverted index below)
+    const int e = tid;
+    const float l = e < E ? __ldcg(logits + long(t) * E + e) : -INFINITY;
+    float selv = l;
+    if (mode == 1) selv = 1.f / (1.f + __expf(-l)) + (bias && e < E ? bias[e] : 0.f);
+    s_logit[e] = l;
+    float mxv = 0.f, inv_sum = 1.f;
+    if (mode == 0 && !renorm) {
+      // softmax weights without renormalisation need the partition sum over all experts
+      float m = l;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      if (lane == 0) s_red[warp] = m;
+      __syncthreads();
+      mxv = s_red[0];
+      for (int i = 1; i < 16; ++i) mxv = fmaxf(mxv, s_red[i]);
+      __syncthreads();
+      float sm = e < E ? __expf(l - mxv) : 0.f;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
+      if (lane == 0) s_red[warp] = sm;
+      __syncthreads();
+      float tot = 0.f;
+      for (int i = 0; i < 16; ++i) tot += s_red[i];
+      inv_sum = 1.f / tot;
+    }
+    const uint32_t u = __float_as_uint(selv);
+    const uint32_t ord = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    uint32_t khi = e < E ? ord : 0u, klo = e < E ? 0xFFFFFFFFu - uint32_t(e) : 0u;
+    // the warp's own best k, in order (lane i keeps choice i)
+    uint32_t mhi = 0u, mlo = 0u;
+    for (int i = 0; i < k; ++i) {
+      const uint32_t ghi = __reduce_max_sync(0xffffffffu, khi);
+      const uint32_t glo = __reduce_max_sync(0xffffffffu, khi == ghi ? klo : 0u);
+      if (khi == ghi && klo == glo) { khi = 0u; klo = 0u; }
+      if (lane == i) { mhi = ghi; mlo = glo; }
+    }
+    s_cand[warp * 32 + lane] = (static_cast<unsigned long long>(mhi) << 32) | mlo;
+    __syncthreads();
+    if (warp == 0) {
+      // merge of the sixteen sorted lists: lane l < 16 walks list l
+      int ptr = 0;
+      unsigned long long head = lane < 16 ? s_cand[lane * 32] : 0ull;
+      int my_id = 0;
+      for (int i = 0; i < k; ++i) {
+        const uint32_t hi = uint32_t(head >> 32), lo = uint32_t(head);
+        const uint32_t ghi = __reduce_max_sync(0xffffffffu, hi);
+        const uint32_t glo = __reduce_max_sync(0xffffffffu, hi == ghi ? lo : 0u);
+        if (hi == ghi && lo == glo && lane < 16) {
+          ++ptr;
+          head = ptr < k ? s_cand[lane * 32 + ptr] : 0ull;
+        }
+        if (lane == i) my_id = int(0xFFFFFFFFu - glo);
+      }
+      float w = 0.f;
+      if (lane < k) {
+        const float lg = s_logit[my_id];
+        if (mode == 0) w = renorm ? lg : __expf(lg - mxv) * inv_sum;
+        else w = 1.f / (1.f + __expf(-lg));
+      }
+      if (mode == 0 && renorm) {
+        const float l0 = __shfl_sync(0xffffffffu, w, 0);
+        w = lane < k ? __expf(w - l0) : 0.f;
+      }
+      float wsum = w;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
+      if (lane < k) {
+        if (renorm) w = w / fmaxf(wsum, 6.1e-5f);
+        ids[t * k + lane] = my_id;
+        wts[t * k + lane] = w * route_scale;
+      }
+    }
+    __syncthreads();
+  }
+  // ---- dense routing tables, indexed by local expert: rows e * bn + t of the intermediate belong to expert e and
+  // token t. Each token CTA writes its token's column of out_rows / tok_scale (pair index t * k + c where the
+  // token chose the expert, -1 elsewhere) and marks the experts it chose as active.
+  const int P = T * k;
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    s_chosen[tid] = -1;
+    __syncthreads();
+    if (tid < k) {
+      const int e = ids[t * k + tid];                   // written by this CTA above
+      s_chosen[e] = t * k + tid;
+      s_logit[e] = wts[t * k + tid];
+    }
+    __syncthreads();
+    const int local = tid - e_lo;
+    if (tid < E && local >= 0 && local < n_local) {
+      const int pr = s_chosen[tid];
+      out_rows[local * bn + t] = pr;
+      if (pr >= 0) {
+        tok_scale[local * bn + t] = s_logit[tid];
+        active[local] = 1;
+      }
+    }
+    if (shared_slot && tid == 0) {
+      // the shared expert (stacked behind this rank's routed experts as group n_local) is used by every token:
+      // its output rows are the pairs P .. P + T - 1, weighted by the sigmoid of its gate (or 1)
+      out_rows[n_local * bn + t] = P + t;
+      tok_scale[n_local * bn + t] = sh_gate_w ? 1.f / (1.f + __expf(-__ldcg(&sh_logit[t]))) : 1.f;
+    }
+    __syncthreads();
+  }
+  // ---- the last token CTA to finish compacts the active experts into the tile list
+  if (tid == 0) {
+    __threadfence();
+    const unsigned int old = atomicAdd(&done_ctr[1], 1u);
+    s_last = (old == unsigned(n_tok_ctas) - 1u);
+    if (s_last) {
+      done_ctr[0] = 0;
+      done_ctr[1] = 0;
+    }
   }
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  // ---- last CTA: top-k of every token (one warp per token), kept in shared memory for the table build
-  for (int t = warp; t < T; t += 16) {
-    router_topk_row<MAXE>(logits, E, bias, E, k, mode, renorm, route_scale, n_group, topk_group, ids, wts, t, s_ids,
-                          s_wts);
+  const int act = tid < n_local ? __ldcg(active + tid) : 0;
+  if (tid < n_local) active[tid] = 0;                   // ready for the next step
+  const unsigned bal = __ballot_sync(0xffffffffu, act != 0);
+  if (lane == 0) s_wsum[warp] = __popc(bal);
+  __syncthreads();
+  int before = 0, n_active = 0;
+  for (int i = 0; i < 16; ++i) {
+    if (i < warp) before += s_wsum[i];
+    n_active += s_wsum[i];
   }
-  __syncthreads();
-  const int P = T * k;
-  // ---- dense routing tables: experts in index order, one slot per active expert. Every step is one
-  // operation per thread: count by shared-memory atomics (one thread per pair), rank the active experts by
-  // ballot + warp totals, clear the used part of out_rows with coalesced stores, scatter the pairs.
-  for (int i = tid; i < E; i += 512) s_slot[i] = 0;
-  __syncthreads();
-  for (int p = tid; p < P; p += 512) atomicAdd(&s_slot[s_ids[p]], 1);
-  __syncthreads();
-  int n_active = 0;
-  {
-    // only this rank's experts [e_lo, e_lo + n_local) become tiles (expert parallelism with mirrored tokens)
-    const int cnt = (tid < E && tid >= e_lo && tid < e_lo + n_local) ? s_slot[tid] : 0;
-    const unsigned bal = __ballot_sync(0xffffffffu, cnt > 0);
-    if (lane == 0) s_wsum[warp] = __popc(bal);
-    __syncthreads();
-    int before = 0;
-    for (int i = 0; i < warp; ++i) before += s_wsum[i];
-    for (int i = 0; i < 16; ++i) n_active += s_wsum[i];
-    int slot = -1;
-    if (cnt > 0) {
-      slot = before + __popc(bal & ((1u << lane) - 1));
-      tile_group[slot] = tid - e_lo;
-      slot_base[slot] = slot * bn;
-      tile_ntok[slot] = T;
-    }
-    __syncthreads();                 // every thread has read its count before the slot numbers replace them
-    if (tid < E) s_slot[tid] = slot;
-  }
-  // The shared expert (stacked behind this rank's routed experts as group n_local) takes one more slot that every
-  // token uses: its output rows are the pairs P .. P + T - 1, weighted by the sigmoid of its gate (or 1).
-  const int n_slots = n_active + (shared_slot ? 1 : 0);
-  for (int i = tid; i < n_slots * T; i += 512) out_rows[(i / T) * bn + i % T] = -1;   // tiles cover T rows per slot
-  __syncthreads();
-  for (int p = tid; p < P; p += 512) {
-    const int slot = s_slot[s_ids[p]];
-    if (slot < 0) continue;          // the pair belongs to another rank's expert
-    const int t = p / k;
-    out_rows[slot * bn + t] = p;
-    tok_scale[slot * bn + t] = s_wts[p];
-  }
-  if (shared_slot) {
-    for (int t = tid; t < T; t += 512) {
-      out_rows[n_active * bn + t] = P + t;
-      tok_scale[n_active * bn + t] = sh_gate_w ? 1.f / (1.f + __expf(-__ldcg(&sh_logit[t]))) : 1.f;
-    }
+  if (act) {
+    const int slot = before + __popc(bal & ((1u << lane) - 1));
+    tile_group[slot] = tid;
+    slot_base[slot] = tid * bn;
+    tile_ntok[slot] = T;
   }
   if (tid == 0) {
     if (shared_slot) {
       tile_group[n_active] = n_local;
-      slot_base[n_active] = n_active * bn;
+      slot_base[n_active] = n_local * bn;
       tile_ntok[n_active] = T;
     }
+    const int n_slots = n_active + (shared_slot ? 1 : 0);
     meta[0] = n_slots;
     meta[1] = n_slots * bn;
   }
@@ -394,7 +501,7 @@ int moe_route_small_launch(const void* x, long ldx, const float* norm_w, float e
                            int mode, int renorm, float route_scale, int n_group, int topk_group, int* ids, float* wts,
                            int T, int bn, int* tile_group, int* slot_base, int* tile_ntok, int* meta, int* out_rows,
                            float* tok_scale, unsigned int* done_ctr, int e_lo, int n_local, const void* sh_gate_w,
-                           float* sh_logit, int shared_slot, cudaStream_t s) {
+                           float* sh_logit, int shared_slot, int* status, int* active, cudaStream_t s) {
   if (T <= 0) return 0;
   if (k > 32 || E > 512 || n_group > 32 || H % 8 || T > 64 || T * k > 1024 || T > bn) return 1;
   if (sh_gate_w && (!sh_logit || !shared_slot)) return 1;
@@ -419,7 +526,7 @@ int moe_route_small_launch(const void* x, long ldx, const float* norm_w, float e
     launch_pdl(moe_route_small_kernel<MAXE>, dim3(grid), dim3(512), smem, s, xb, ldx, norm_w, eps, w_offset, xn,   \
                ldn, wb, ldw, H, logits, bias, E, k, mode, renorm, route_scale, n_group, topk_group, ids, wts, T,    \
                bn, tile_group, slot_base, tile_ntok, meta, out_rows, tok_scale, done_ctr, e_lo, n_local, sg,        \
-               sh_logit, shared_slot, epc, tpp);                                                                    \
+               sh_logit, shared_slot, epc, tpp, status, active);                                                    \
   }
   if (E <= 128) LB_ROUTE(128)
   else if (E <= 256) LB_ROUTE(256)

@@ -770,6 +770,7 @@ class DenseRoute:
         self.out_rows = torch.full((n_slots * self.stride,), -1, **i32)
         self.tok_scale = torch.zeros(n_slots * self.stride, dtype=torch.float32, device=device)
         self.sh_logit = torch.zeros(64, dtype=torch.float32, device=device)
+        self.active = torch.zeros(n_slots, **i32)      # per local expert: chosen by some token of the step
         self.h_all = None
         self.hq = None
         self.y_pairs = None
@@ -798,7 +799,7 @@ def router(x, w_router, k, mode="softmax", renorm=True, route_scale=1.0, bias=No
     logits = ws.buf("router_logits", (64 * 512,), torch.float32)
     ctr = ws._cache.get("router_ctr")
     if ctr is None:
-        ctr = torch.zeros(1, dtype=torch.int32, device=x.device)
+        ctr = torch.zeros(4, dtype=torch.int32, device=x.device)
         ws._cache["router_ctr"] = ctr
     bn = 32 if T <= 32 else 64
     stride = slot_stride or bn
@@ -815,7 +816,7 @@ def router(x, w_router, k, mode="softmax", renorm=True, route_scale=1.0, bias=No
                       bias, k, 0 if mode == "softmax" else 1, renorm, route_scale, n_group, topk_group, logits, ids, wts,
                       stride, dr.tile_group, dr.slot_base, dr.tile_ntok, dr.meta, dr.out_rows, dr.tok_scale, ctr,
                       e_lo, nl, sh_gate.reshape(-1) if sh_gate is not None else None,
-                      dr.sh_logit if sh_gate is not None else None, bool(shared_slot))
+                      dr.sh_logit if sh_gate is not None else None, bool(shared_slot), ws.status, dr.active)
     r = Routing(ids, wts, dr, xn, e_lo, nl)
     r.shared_slot = bool(shared_slot)
     return r
