@@ -209,6 +209,7 @@ def main(argv=None):
         ec = EngineConfig(ctx_size=PL + 64, max_seqs=1, max_batch_tokens=8192, prefill_chunk=8192, block_size=64,
                           prefix_cache=False, device=str(dev), model_name=spec["model"], cuda_graphs=False)
         model = Decoder(cfg, weights, pctx, max_position=ec.ctx_size + 8)
+        model.fuse_gdn_in_proj()
         eng = LmEngine(model, tok, ec, start=False)
         times = []
         for rep in range(3):
@@ -234,6 +235,7 @@ def main(argv=None):
     ec = EngineConfig(ctx_size=L + gen_budget + 64, max_seqs=U_max, max_batch_tokens=8192, prefill_chunk=8192,
                       block_size=64, prefix_cache=False, device=str(dev), model_name=spec["model"])
     model = Decoder(cfg, weights, pctx, max_position=ec.ctx_size + 8)
+    model.fuse_gdn_in_proj()
     eng = LmEngine(model, tok, ec, start=False)
     graphs = eng._graphs
     assert graphs is not None, "decode steps must run from captured CUDA graphs"

@@ -166,7 +166,11 @@ def build_engine_from_args(a, start: bool = True):
         pctx.comm = "fused"
         pctx.gemm_tail = bool(getattr(a, "tp_gemm_tail", False))
     model = Decoder(cfg, w, pctx, max_position=ec.ctx_size + 8)
+    if on_gpu:
+        model.fuse_gdn_in_proj()
     if getattr(a, "expert_weights", "bf16") == "nvfp4" and on_gpu and cfg.n_expert:
+        if pctx.world == 1 and a.experts not in ("cache", "host", "ssd"):
+            model.fold_shared_experts()      # the shared expert rides in the grouped GEMMs of decode steps
         saved = model.quantize_experts_nvfp4()
         logging.getLogger("legion").info("routed experts re-encoded to NVFP4: %.1f GiB of HBM saved", saved / 2 ** 30)
     wmode = getattr(a, "weights", "auto")

@@ -202,7 +202,7 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         // tile has landed and the softmax of tile j-1 has released that S buffer) and PV of tile j (P is ready).
         // Neither waits behind the other: the softmax of tile j may itself wait for S of tile j+1 before a rescale.
         bool s_owed = j + 1 < n_blk, pv_owed = true;
-        const uint64_t t0 = globaltimer_ns();
+        uint64_t t0 = 0;                     // the clock (a slow read) only once the round has lasted a while
         uint32_t spins = 0;
         while (s_owed || pv_owed) {
           if (s_owed && mbar_test_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1) &&
@@ -216,8 +216,12 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             issue_pv(j);
             pv_owed = false;
           }
-          if ((++spins & 0x3ff) == 0 && (*abort_flag || globaltimer_ns() - t0 > LB_WAIT_NS)) {
-            *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FLAG); ok = false; break;
+          if ((++spins & 0x3ff) == 0) {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            if (*abort_flag || now - t0 > LB_WAIT_NS) {
+              *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FLAG); ok = false; break;
+            }
           }
         }
       }

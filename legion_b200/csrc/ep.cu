@@ -32,10 +32,14 @@ __device__ __forceinline__ uint32_t ep_ld_acquire(const uint32_t* p) {
   return v;
 }
 __device__ __forceinline__ bool ep_wait_geq(const uint32_t* flag, uint32_t want, uint64_t budget_ns) {
-  const uint64_t t0 = globaltimer_ns();
+  uint64_t t0 = 0;                           // the clock (a slow read) only once the wait has lasted a while
   uint32_t spins = 0;
   while (int32_t(ep_ld_acquire(flag) - want) < 0) {
-    if ((++spins & 0x3f) == 0 && globaltimer_ns() - t0 > budget_ns) return false;
+    if ((++spins & 0x3f) == 0) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > budget_ns) return false;
+    }
   }
   return true;
 }

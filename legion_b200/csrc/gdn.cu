@@ -297,6 +297,143 @@ int gdn_recurrent_launch(const void* qkv, long ld, const float* g, const float* 
   return 1;
 }
 
+// Decode step of a Gated DeltaNet layer in ONE launch: causal conv + SiLU of this token's q / k / v channels (with
+// the carried history), gates, the delta-rule update of the state, and the gated RMS norm of the output. One CTA
+// per (key head, sequence) serves the r = Hv / Hk value heads that share the key head (256 threads each), so the
+// q / k convolution, their L2 norms and the conv-history update are done once and nobody reads a history another
+// CTA is rewriting. Every sequence contributes exactly one token (row `seq` of proj).
+//   proj row = [q (Hk*DK) | k (Hk*DK) | v (Hv*DV) | z (Hv*DV) | b (Hv) | a (Hv)]  (the fused input projection)
+// Intermediate values are rounded to bf16 where the separate kernels store them as bf16 (conv outputs, the
+// recurrence output), so a decode step gives the same numbers as the multi-kernel path used for verify rows.
+template <int DK, int DV, int KC>
+__global__ void __launch_bounds__(1024) gdn_decode_fused_kernel(
+    const __nv_bfloat16* __restrict__ proj, long ld, const float* __restrict__ conv_w, float* __restrict__ conv_state,
+    const float* __restrict__ A, const float* __restrict__ dt_bias, const float* __restrict__ norm_w, float eps,
+    int act, float* __restrict__ state, const int* __restrict__ slots, int Hk, int Hv, int tiled_heads, float scale,
+    float l2_eps, __nv_bfloat16* __restrict__ out) {
+  static_assert(DK == DV, "thread layout assumes square heads");
+  constexpr int HALF = DK / 2;
+  constexpr int GT = 2 * DV;                     // threads per value head
+  constexpr int MAXR = 4;
+  griddep_wait();
+  griddep_launch();
+  const int kh = blockIdx.x, seq = blockIdx.y;
+  const int r = Hv / Hk;
+  const int j = threadIdx.x / GT, tid = threadIdx.x % GT;
+  const int h = tiled_heads ? kh + j * Hk : kh * r + j;
+  const int c = tid % DV, half = tid / DV;
+  const int C = 2 * Hk * DK + Hv * DV;
+  const int slot = slots[seq];
+  const __nv_bfloat16* row = proj + long(seq) * ld;
+  __shared__ float q_s[DK], k_s[DK], v_s[MAXR][DV], part[MAXR][2][DV], red[2 * DK / 32], red2[MAXR][DV / 32];
+  __shared__ float qn_s, kn_s;
+  // state of this thread's half column: the loads are in flight while the convolution runs
+  float S[HALF];
+  float* sp = state + ((long(slot) * Hv + h) * DK + half * HALF) * DV + c;
+#pragma unroll
+  for (int i = 0; i < HALF; ++i) S[i] = sp[long(i) * DV];
+
+  auto conv = [&](int ch) -> float {
+    float wv[KC], hh[KC - 1];
+#pragma unroll
+    for (int i = 0; i < KC; ++i) wv[i] = conv_w[ch * KC + i];
+    float* st = conv_state + (long(slot) * C + ch) * (KC - 1);
+#pragma unroll
+    for (int i = 0; i < KC - 1; ++i) hh[i] = st[i];
+    const float xv = __bfloat162float(row[ch]);
+    float acc = wv[KC - 1] * xv;
+#pragma unroll
+    for (int i = 0; i < KC - 1; ++i) acc += wv[i] * hh[i];
+#pragma unroll
+    for (int i = 0; i < KC - 2; ++i) st[i] = hh[i + 1];
+    st[KC - 2] = xv;
+    return __bfloat162float(__float2bfloat16(acc / (1.f + __expf(-acc))));
+  };
+  float qq = 0.f, kk = 0.f;
+  if (j == 0) {
+    // threads 0 .. DK-1: q channel, DK .. 2 DK-1: k channel of this key head
+    const float v = conv((half == 0 ? 0 : Hk * DK) + kh * DK + c);
+    if (half == 0) { q_s[c] = v; qq = v * v; } else { k_s[c] = v; kk = v * v; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      qq += __shfl_xor_sync(0xffffffffu, qq, o);
+      kk += __shfl_xor_sync(0xffffffffu, kk, o);
+    }
+    if ((tid & 31) == 0) red[tid >> 5] = half == 0 ? qq : kk;
+  }
+  if (half == 0) v_s[j][c] = conv(2 * Hk * DK + h * DV + c);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = 0.f, b = 0.f;
+    for (int i = 0; i < DK / 32; ++i) { a += red[i]; b += red[DK / 32 + i]; }
+    qn_s = rsqrtf(a + l2_eps) * scale;
+    kn_s = rsqrtf(b + l2_eps);
+  }
+  // gates of this value head (every thread computes them: two loads and a few operations)
+  const float av = __bfloat162float(row[C + Hv * DV + Hv + h]) + dt_bias[h];
+  const float spv = av > 20.f ? av : log1pf(__expf(av));
+  const float gt = __expf(A[h] * spv);
+  const float bt = 1.f / (1.f + __expf(-__bfloat162float(row[C + Hv * DV + h])));
+  __syncthreads();
+  const float qn = qn_s, kn = kn_s;
+  float kv = 0.f;
+#pragma unroll
+  for (int i = 0; i < HALF; ++i) kv += S[i] * k_s[half * HALF + i];
+  part[j][half][c] = kv * kn;
+  __syncthreads();
+  const float delta = (v_s[j][c] - gt * (part[j][0][c] + part[j][1][c])) * bt;
+  __syncthreads();
+  float o = 0.f;
+#pragma unroll
+  for (int i = 0; i < HALF; ++i) {
+    S[i] = gt * S[i] + k_s[half * HALF + i] * kn * delta;
+    o += S[i] * q_s[half * HALF + i];
+  }
+  part[j][half][c] = o * qn;
+#pragma unroll
+  for (int i = 0; i < HALF; ++i) sp[long(i) * DV] = S[i];
+  __syncthreads();
+  // gated RMS norm over the head's DV outputs
+  float ov = 0.f, ss = 0.f;
+  if (half == 0) {
+    ov = __bfloat162float(__float2bfloat16(part[j][0][c] + part[j][1][c]));
+    ss = ov * ov;
+#pragma unroll
+    for (int k = 16; k > 0; k >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, k);
+    if ((c & 31) == 0) red2[j][c >> 5] = ss;
+  }
+  __syncthreads();
+  if (half == 0) {
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < DV / 32; ++i) tot += red2[j][i];
+    const float inv = rsqrtf(tot / float(DV) + eps);
+    const float zv = __bfloat162float(row[C + h * DV + c]);
+    const float sg = 1.f / (1.f + __expf(-zv));
+    out[(long(seq) * Hv + h) * DV + c] = __float2bfloat16(ov * inv * norm_w[c] * (act == 0 ? zv * sg : sg));
+  }
+}
+
+int gdn_decode_fused_launch(const void* proj, long ld, const float* conv_w, float* conv_state, int KC, const float* A,
+                            const float* dt_bias, const float* norm_w, float eps, int act, float* state,
+                            const int* slots, int n_seqs, int Hk, int Hv, int DK, int DV, int tiled_heads, float scale,
+                            float l2_eps, void* out, cudaStream_t s) {
+  if (n_seqs <= 0) return 0;
+  if (Hk <= 0 || Hv % Hk || Hv / Hk > 4 || KC != 4) return 1;
+  const int r = Hv / Hk;
+  dim3 grid(Hk, n_seqs);
+#define LB_GF(D_)                                                                                                   \
+  if (DK == D_ && DV == D_) {                                                                                       \
+    launch_pdl(gdn_decode_fused_kernel<D_, D_, 4>, grid, dim3(2 * D_ * r), 0, s,                                    \
+               static_cast<const __nv_bfloat16*>(proj), ld, conv_w, conv_state, A, dt_bias, norm_w, eps, act, state, \
+               slots, Hk, Hv, tiled_heads, scale, l2_eps, static_cast<__nv_bfloat16*>(out));                        \
+    return cudaGetLastError() != cudaSuccess;                                                                       \
+  }
+  LB_GF(128) LB_GF(64)
+#undef LB_GF
+  return 1;
+}
+
 // g = -exp(A_log) * softplus(a + dt_bias) (A passed as -exp(A_log)), beta = sigmoid(b). a, b: [T, Hv] bf16.
 __global__ void gdn_gates_kernel(const __nv_bfloat16* __restrict__ a, long lda, const __nv_bfloat16* __restrict__ b,
                                  long ldb, const float* __restrict__ A, const float* __restrict__ dt_bias, int Hv,

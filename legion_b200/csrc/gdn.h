@@ -13,6 +13,12 @@ int gdn_recurrent_launch(const void* qkv, long ld, const float* g, const float* 
                          int tiled_heads, float scale, float l2_eps, void* out, int write_state, int write_out,
                          int prompt_rows, cudaStream_t s);
 
+// One launch per decode step of a Gated DeltaNet layer (conv + gates + delta rule + gated norm); see gdn.cu.
+int gdn_decode_fused_launch(const void* proj, long ld, const float* conv_w, float* conv_state, int KC, const float* A,
+                            const float* dt_bias, const float* norm_w, float eps, int act, float* state,
+                            const int* slots, int n_seqs, int Hk, int Hv, int DK, int DV, int tiled_heads, float scale,
+                            float l2_eps, void* out, cudaStream_t s);
+
 int gdn_gates_launch(const void* a, long lda, const void* b, long ldb, const float* A, const float* dt_bias, int Hv,
                      long T, float* g, float* beta, cudaStream_t s);
 

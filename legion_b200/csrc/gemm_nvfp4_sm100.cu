@@ -37,7 +37,7 @@ constexpr int SMEM_BUDGET = 200 * 1024;
 
 constexpr int pow2_ge(int v) { return v <= 32 ? 32 : (v <= 64 ? 64 : (v <= 128 ? 128 : (v <= 256 ? 256 : 512))); }
 
-template <int BN, bool DUAL>
+template <int BN, bool DUAL, int FT = 1>
 struct Cfg {
   static constexpr int NW = DUAL ? 2 : 1;
   static constexpr int X_TILE = BN * KB_BYTES;
@@ -47,8 +47,12 @@ struct Cfg {
   static constexpr int STAGE_BYTES = SFX_OFF + SF_TILE;
   static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-  static constexpr int ACC_COLS = BN * NW;
-  static constexpr int NACC = 2;
+  // A work item is FT consecutive 128-feature tiles of one token tile, accumulated side by side in one TMEM
+  // buffer and handed to the epilogue together: a tile of a short-K GEMM (K = 512: two stages) is too little work
+  // per hand-over (measured ~1 us of fixed cost per work item in every role).
+  static constexpr int SUB_COLS = BN * NW;              // accumulator columns of one 128-feature tile
+  static constexpr int ACC_COLS = SUB_COLS * FT;
+  static constexpr int NACC = (2 * ACC_COLS + NW * 16 + 16 <= 512) ? 2 : 1;
   static constexpr int SFA_COL = NACC * ACC_COLS;       // 16 columns per weight tile: 4 k steps x 4 row groups
   static constexpr int SFB_COL = SFA_COL + NW * 16;     // 16 columns for the token tile
   static constexpr int TMEM_COLS = pow2_ge(SFB_COL + 16);
@@ -74,11 +78,12 @@ struct Args {
 
 struct Work { int group, tok0, out0, ntok, feat0; };
 
-template <int BN>
+template <int BN, int FT>
 __device__ __forceinline__ bool decode_work(const Args& a, int w, int n_tok_tiles, Work& it) {
-  const int tt = w / a.feat_tiles;
+  const int items = (a.feat_tiles + FT - 1) / FT;       // work items per token tile
+  const int tt = w / items;
   if (tt >= n_tok_tiles) return false;
-  it.feat0 = (w - tt * a.feat_tiles) * BM;
+  it.feat0 = (w - tt * items) * (BM * FT);
   if (a.tile_group) {
     it.group = a.tile_group[tt];
     it.tok0 = a.tile_tok0[tt];
@@ -142,10 +147,10 @@ __device__ __forceinline__ long sf_atom_byte(long row, int blk16, int k4) {
   return ((row >> 7) * k4 + (blk16 >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (blk16 & 3);
 }
 
-template <int BN, bool DUAL, bool QOUT>
+template <int BN, bool DUAL, bool QOUT, int FT>
 __global__ void __launch_bounds__(192, 1)
 wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const Args a) {
-  using C = Cfg<BN, DUAL>;
+  using C = Cfg<BN, DUAL, FT>;
   constexpr int STAGES = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -154,8 +159,8 @@ wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   uint64_t* full = bars;
   uint64_t* empty = bars + STAGES;
   uint64_t* tfull = bars + 2 * STAGES;
-  uint64_t* tempty = bars + 2 * STAGES + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  uint64_t* tempty = bars + 2 * STAGES + C::NACC;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * C::NACC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -197,29 +202,35 @@ wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       uint32_t ph = 0;
       int issued = 0;
       bool ok = true;
-      Work it;
-      for (int w = blockIdx.x; ok && decode_work<BN>(a, w, n_tok_tiles, it); w += gridDim.x) {
-        const int wrow = it.group * a.rows_per_group + it.feat0;
-        const uint8_t* sfw = a.w_sf + long(wrow >> 7) * a.k4 * 512;
-        const uint8_t* sfw2 = DUAL ? a.w_sf + long((wrow + a.dual_offset) >> 7) * a.k4 * 512 : nullptr;
+      // the next item's table entries are fetched while the current one is processed (every role does this)
+      Work it, nx;
+      bool have = decode_work<BN, FT>(a, blockIdx.x, n_tok_tiles, it);
+      for (int w = blockIdx.x; ok && have; w += gridDim.x, it = nx) {
+        have = decode_work<BN, FT>(a, w + gridDim.x, n_tok_tiles, nx);
         const uint8_t* sfx = a.x_sf + long(it.tok0 >> 7) * a.k4 * 512;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) {
-            *abort_flag = 1;
-            atomicCAS(a.status, 0, ST_TIMEOUT_EMPTY);
-            ok = false;
-            break;
+        for (int f = 0; ok && f < FT; ++f) {
+          if (it.feat0 + f * BM >= a.n_feat) break;
+          const int wrow = it.group * a.rows_per_group + it.feat0 + f * BM;
+          const uint8_t* sfw = a.w_sf + long(wrow >> 7) * a.k4 * 512;
+          const uint8_t* sfw2 = DUAL ? a.w_sf + long((wrow + a.dual_offset) >> 7) * a.k4 * 512 : nullptr;
+          for (int kb = 0; kb < num_kb; ++kb) {
+            if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) {
+              *abort_flag = 1;
+              atomicCAS(a.status, 0, ST_TIMEOUT_EMPTY);
+              ok = false;
+              break;
+            }
+            uint8_t* st = smem + s * C::STAGE_BYTES;
+            mbar_expect_tx(&full[s], C::STAGE_BYTES);
+            tma_load_2d(st, &tmW, &full[s], kb * KB_BYTES, wrow);
+            if (DUAL) tma_load_2d(st + W_TILE, &tmW, &full[s], kb * KB_BYTES, wrow + a.dual_offset);
+            tma_load_2d(st + C::X_OFF, &tmX, &full[s], kb * KB_BYTES, it.tok0);
+            bulk_load(st + C::SFW_OFF, sfw + long(kb) * SF_TILE, SF_TILE, &full[s]);
+            if (DUAL) bulk_load(st + C::SFW_OFF + SF_TILE, sfw2 + long(kb) * SF_TILE, SF_TILE, &full[s]);
+            bulk_load(st + C::SFX_OFF, sfx + long(kb) * SF_TILE, SF_TILE, &full[s]);
+            ++issued;
+            if (++s == STAGES) { s = 0; ph ^= 1; }
           }
-          uint8_t* st = smem + s * C::STAGE_BYTES;
-          mbar_expect_tx(&full[s], C::STAGE_BYTES);
-          tma_load_2d(st, &tmW, &full[s], kb * KB_BYTES, wrow);
-          if (DUAL) tma_load_2d(st + W_TILE, &tmW, &full[s], kb * KB_BYTES, wrow + a.dual_offset);
-          tma_load_2d(st + C::X_OFF, &tmX, &full[s], kb * KB_BYTES, it.tok0);
-          bulk_load(st + C::SFW_OFF, sfw + long(kb) * SF_TILE, SF_TILE, &full[s]);
-          if (DUAL) bulk_load(st + C::SFW_OFF + SF_TILE, sfw2 + long(kb) * SF_TILE, SF_TILE, &full[s]);
-          bulk_load(st + C::SFX_OFF, sfx + long(kb) * SF_TILE, SF_TILE, &full[s]);
-          ++issued;
-          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
       if (!ok) {
@@ -244,15 +255,16 @@ wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       int acc = 0;
       uint32_t acc_ph = 0;
       bool ok = true;
-      Work it;
-      for (int w = blockIdx.x; ok && decode_work<BN>(a, w, n_tok_tiles, it); w += gridDim.x) {
+      Work it, nx;
+      bool have = decode_work<BN, FT>(a, blockIdx.x, n_tok_tiles, it);
+      for (int w = blockIdx.x; ok && have; w += gridDim.x, it = nx) {
+        have = decode_work<BN, FT>(a, w + gridDim.x, n_tok_tiles, nx);
         if (!mbar_wait(&tempty[acc], acc_ph ^ 1, abort_flag)) {
           *abort_flag = 1;
           atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_EMPTY);
           break;
         }
         tc_fence_after();
-        const uint32_t d0 = tmem_base + acc * C::ACC_COLS;
         // Row group of the token tile inside its 128-row scale atom = column offset of its scale factors. Only
         // offsets that are multiples of two columns are used (64-token tiles on 64-row boundaries); a 32-token
         // tile must start a 128-row atom. An odd column offset raised "misaligned address" on B200.
@@ -263,38 +275,42 @@ wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           break;
         }
         const uint32_t sfb_col = sfb_t + grp;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&full[s], ph, abort_flag)) {
-            *abort_flag = 1;
-            atomicCAS(a.status, 0, ST_TIMEOUT_FULL);
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t sa = smem_u32(smem + s * C::STAGE_BYTES);
-          const int nk = kb == num_kb - 1 ? k_steps_last : 4;
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            if (k < nk) {
-              sf_copy(sfa_t + k * 4, sf_desc(sa + C::SFW_OFF + k * 512));
-              if (DUAL) sf_copy(sfa_t + 16 + k * 4, sf_desc(sa + C::SFW_OFF + SF_TILE + k * 512));
-              sf_copy(sfb_t + k * 4, sf_desc(sa + C::SFX_OFF + k * 512));
+        for (int f = 0; ok && f < FT; ++f) {
+          if (it.feat0 + f * BM >= a.n_feat) break;
+          const uint32_t d0 = tmem_base + acc * C::ACC_COLS + f * C::SUB_COLS;
+          for (int kb = 0; kb < num_kb; ++kb) {
+            if (!mbar_wait(&full[s], ph, abort_flag)) {
+              *abort_flag = 1;
+              atomicCAS(a.status, 0, ST_TIMEOUT_FULL);
+              ok = false;
+              break;
             }
-          }
-          const uint64_t dw = umma_desc_k_sw128(sa);
-          const uint64_t dw2 = umma_desc_k_sw128(sa + W_TILE);
-          const uint64_t dx = umma_desc_k_sw128(sa + C::X_OFF);
+            tc_fence_after();
+            const uint32_t sa = smem_u32(smem + s * C::STAGE_BYTES);
+            const int nk = kb == num_kb - 1 ? k_steps_last : 4;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            if (k < nk) {
-              const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
-              const uint64_t koff = uint64_t(k * 2);            // 32 bytes of codes per K = 64 step
-              umma_nvf4(d0, dw + koff, dx + koff, idesc, sfa_t + k * 4, sfb_col + k * 4, accum);
-              if (DUAL) umma_nvf4(d0 + BN, dw2 + koff, dx + koff, idesc, sfa_t + 16 + k * 4, sfb_col + k * 4, accum);
+            for (int k = 0; k < 4; ++k) {
+              if (k < nk) {
+                sf_copy(sfa_t + k * 4, sf_desc(sa + C::SFW_OFF + k * 512));
+                if (DUAL) sf_copy(sfa_t + 16 + k * 4, sf_desc(sa + C::SFW_OFF + SF_TILE + k * 512));
+                sf_copy(sfb_t + k * 4, sf_desc(sa + C::SFX_OFF + k * 512));
+              }
             }
+            const uint64_t dw = umma_desc_k_sw128(sa);
+            const uint64_t dw2 = umma_desc_k_sw128(sa + W_TILE);
+            const uint64_t dx = umma_desc_k_sw128(sa + C::X_OFF);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              if (k < nk) {
+                const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+                const uint64_t koff = uint64_t(k * 2);            // 32 bytes of codes per K = 64 step
+                umma_nvf4(d0, dw + koff, dx + koff, idesc, sfa_t + k * 4, sfb_col + k * 4, accum);
+                if (DUAL) umma_nvf4(d0 + BN, dw2 + koff, dx + koff, idesc, sfa_t + 16 + k * 4, sfb_col + k * 4, accum);
+              }
+            }
+            umma_commit(&empty[s]);
+            if (++s == STAGES) { s = 0; ph ^= 1; }
           }
-          umma_commit(&empty[s]);
-          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
         if (!ok) break;
         umma_commit(&tfull[acc]);
@@ -307,10 +323,12 @@ wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     const int etid = threadIdx.x - 64;
     int acc = 0;
     uint32_t acc_ph = 0;
-    Work it;
+    Work it, nx;
     const float q_gs = QOUT ? *a.q_gscale : 1.f;
     const float xs_all = (a.x_gscale && a.x_gs_stride == 0) ? __ldg(a.x_gscale) : 1.f;
-    for (int w = blockIdx.x; decode_work<BN>(a, w, n_tok_tiles, it); w += gridDim.x) {
+    bool have = decode_work<BN, FT>(a, blockIdx.x, n_tok_tiles, it);
+    for (int w = blockIdx.x; have; w += gridDim.x, it = nx) {
+      have = decode_work<BN, FT>(a, w + gridDim.x, n_tok_tiles, nx);
       const int row = q * 32 + lane;
       // Row bookkeeping of the first 32 token columns is fetched BEFORE the accumulator is waited for, so these
       // (dependent, L2-latency) loads overlap the tile's MMAs instead of sitting between them and the stores:
@@ -341,13 +359,18 @@ wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         break;
       }
       tc_fence_after();
-      const uint32_t t0 = tmem_base + (uint32_t(q * 32) << 16) + acc * C::ACC_COLS;
       const float gs0 = a.w_gscale ? a.w_gscale[it.group * C::NW] : 1.f;
       const float gs1 = (DUAL && a.w_gscale) ? a.w_gscale[it.group * 2 + 1] : 1.f;
+      const int item_feat0 = it.feat0;
+#pragma unroll 1
+      for (int f = 0; f < FT; ++f) {
+      it.feat0 = item_feat0 + f * BM;
+      if (it.feat0 >= a.n_feat) break;
+      const uint32_t t0 = tmem_base + (uint32_t(q * 32) << 16) + acc * C::ACC_COLS + f * C::SUB_COLS;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         if (c >= it.ntok) break;
-        if (c > 0) prefetch_rows(c);
+        if (c > 0 || (f > 0 && BN > 32)) prefetch_rows(c);
         uint32_t r[32];
         float g[32];
         tmem_ld32(t0 + c, r);
@@ -430,6 +453,7 @@ wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         }
         asm volatile("bar.sync 2, 128;" ::: "memory");
       }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
@@ -448,10 +472,10 @@ wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 thread_local char g_err[512];
 int g_sms = 0;
 
-template <int BN, bool DUAL, bool QOUT>
+template <int BN, bool DUAL, bool QOUT, int FT>
 int launch(const CUtensorMap* tmW, const CUtensorMap* tmX, const Args& a, int grid, cudaStream_t stream) {
-  using C = Cfg<BN, DUAL>;
-  auto kfn = wgemm_nv4_kernel<BN, DUAL, QOUT>;
+  using C = Cfg<BN, DUAL, FT>;
+  auto kfn = wgemm_nv4_kernel<BN, DUAL, QOUT, FT>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
@@ -526,13 +550,21 @@ int wgemm_nv4_launch(const Nv4Host& h, cudaStream_t stream) {
   a.vec_ok = (!qout && h.n_feat % 8 == 0 && h.ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(h.out) & 15) == 0 &&
               (!h.residual || (h.ldr % 8 == 0 && (reinterpret_cast<uintptr_t>(h.residual) & 15) == 0))) ? 1 : 0;
   const int n_tok_tiles = h.tile_group ? h.n_tok_tiles_max : (h.n_tok + bn - 1) / bn;
-  const long total = long(n_tok_tiles) * a.feat_tiles;
+  // Feature tiles per work item: short-K GEMMs with many feature tiles (the down projection of an expert: K = 512,
+  // 16 tiles) take four at a time, the gate / up pair two; everything else one.
+  const int num_kb = (h.K + 255) / 256;
+  int ft = 1;
+  if (bn == 32 && !h.dual && !qout && num_kb <= 4 && a.feat_tiles >= 8) ft = 4;
+  else if (bn == 32 && h.dual && a.feat_tiles >= 2 && a.feat_tiles % 2 == 0 && long(n_tok_tiles) * a.feat_tiles >= 2L * g_sms) ft = 2;
+  const long total = long(n_tok_tiles) * ((a.feat_tiles + ft - 1) / ft);
   if (total <= 0) return 0;
   const int grid = int(total < g_sms ? total : g_sms);
-#define LB_NV4(BN_, DUAL_)                                                              \
-  if (bn == BN_ && h.dual == DUAL_)                                                     \
-    return qout ? launch<BN_, DUAL_, true>(tmW, tmX, a, grid, stream) : launch<BN_, DUAL_, false>(tmW, tmX, a, grid, stream);
-  LB_NV4(32, false) LB_NV4(64, false) LB_NV4(128, false) LB_NV4(32, true) LB_NV4(64, true)
+#define LB_NV4(BN_, DUAL_, FT_)                                                             \
+  if (bn == BN_ && h.dual == DUAL_ && ft == FT_)                                            \
+    return qout ? launch<BN_, DUAL_, true, FT_>(tmW, tmX, a, grid, stream)                  \
+                : launch<BN_, DUAL_, false, FT_>(tmW, tmX, a, grid, stream);
+  LB_NV4(32, false, 1) LB_NV4(32, false, 4) LB_NV4(64, false, 1) LB_NV4(128, false, 1)
+  LB_NV4(32, true, 1) LB_NV4(32, true, 2) LB_NV4(64, true, 1)
 #undef LB_NV4
   snprintf(g_err, sizeof(g_err), "wgemm_nv4: unsupported tile bn=%d dual=%d", bn, int(h.dual));
   return 1;

@@ -206,12 +206,16 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
     __syncthreads();
     if (threadIdx.x == 0) {
       atomicAdd(&hd.ctrs[0], 1u);
-      const uint64_t t0 = globaltimer_ns();
+      uint64_t t0 = 0;
       uint32_t spins = 0;
       while (*reinterpret_cast<volatile unsigned int*>(&hd.ctrs[0]) < gridDim.x) {     // every CTA has copied
-        if ((++spins & 0x3f) == 0 && globaltimer_ns() - t0 > hd.budget_ns) {
-          atomicCAS(hd.status, 0, ST_TIMEOUT_FLAG);
-          break;
+        if ((++spins & 0x3f) == 0) {
+          const uint64_t now = globaltimer_ns();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > hd.budget_ns) {
+            atomicCAS(hd.status, 0, ST_TIMEOUT_FLAG);
+            break;
+          }
         }
       }
       __threadfence();

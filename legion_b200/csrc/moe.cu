@@ -330,12 +330,16 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
     atomicAdd(&done_ctr[0], 1u);
     s_last = 1;
     if (int(blockIdx.x) < n_tok_ctas) {
-      const uint64_t t_start = globaltimer_ns();
+      uint64_t t_start = 0;                  // the clock is read only once the wait has lasted a while
       uint32_t spins = 0;
       while (*reinterpret_cast<volatile unsigned int*>(&done_ctr[0]) < gridDim.x) {
-        if ((++spins & 0x3f) == 0 && globaltimer_ns() - t_start > 2000000000ull) {
-          atomicCAS(status, 0, ST_TIMEOUT_FLAG);
-          break;
+        if ((++spins & 0xff) == 0) {
+          const uint64_t now = globaltimer_ns();
+          if (t_start == 0) t_start = now;
+          else if (now - t_start > 2000000000ull) {
+            atomicCAS(status, 0, ST_TIMEOUT_FLAG);
+            break;
+          }
         }
       }
     }

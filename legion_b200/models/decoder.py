@@ -319,9 +319,24 @@ class Decoder:
     def _gdn(self, p: str, il: int, x, b: StepBatch, st: StatePool):
         cfg, w = self.cfg, self.w
         nk, nv, dk, dv = self.gdn_k_l, self.gdn_v_l, cfg.gdn_k_dim, cfg.gdn_v_dim
-        mixed = ops.linear(x, w[f"{p}.gdn.in_qkv"])
-        z = ops.linear(x, w[f"{p}.gdn.in_z"])
-        ba = ops.linear(x, w[f"{p}.gdn.in_ba"])
+        w_all = w.get(f"{p}.gdn.in_all")
+        if w_all is not None:
+            # one GEMM for the three input projections; the pieces are column slices of its output
+            C = 2 * nk * dk + nv * dv
+            proj = ops.linear(x, w_all)
+            if (x.is_cuda and b.max_q_len == 1 and b.write_state and b.replay is None
+                    and proj.shape[0] == b.state_slots.shape[0] and ops.sm100.gdn_decode_fused_ok(nk, nv, dk, dv, cfg.gdn_conv)):
+                # decode step: conv, gates, delta rule and gated norm in one launch
+                n = ops.sm100.gdn_decode_fused(proj, w[f"{p}.gdn.conv_w"], st.conv[il], w[f"{p}.gdn.A"],
+                                               w[f"{p}.gdn.dt_bias"], w[f"{p}.gdn.norm"], cfg.rms_eps, cfg.gdn_gate_act,
+                                               st.ssm[il], b.state_slots, nk, nv, dk, dv, cfg.gdn_tiled_heads,
+                                               dk ** -0.5, 1e-6)
+                return self.pctx.defer_linear(n, w[f"{p}.gdn.out"], lazy=True)
+            mixed, z, ba = proj[:, :C], proj[:, C:C + nv * dv], proj[:, C + nv * dv:]
+        else:
+            mixed = ops.linear(x, w[f"{p}.gdn.in_qkv"])
+            z = ops.linear(x, w[f"{p}.gdn.in_z"])
+            ba = ops.linear(x, w[f"{p}.gdn.in_ba"])
         conv = ops.causal_conv1d_silu(mixed, w[f"{p}.gdn.conv_w"], None, st.conv[il], b.cu_q, b.state_slots,
                                       write_state=b.write_state)
         g, beta = ops.gdn_gates(ba[:, nv:], ba[:, :nv], w[f"{p}.gdn.A"], w[f"{p}.gdn.dt_bias"])
@@ -331,6 +346,26 @@ class Decoder:
                               dk ** -0.5, 1e-6, write_state=b.write_state)
         n = ops.gated_rmsnorm(o, z, w[f"{p}.gdn.norm"], cfg.rms_eps, cfg.gdn_gate_act)
         return self.pctx.defer_linear(n.reshape(n.shape[0], -1), w[f"{p}.gdn.out"], lazy=True)
+
+    def fuse_gdn_in_proj(self) -> int:
+        """Stacks the three input projections of every Gated DeltaNet layer (q/k/v, z, b/a) into one weight
+        ``gdn.in_all`` so that a layer needs one GEMM for them; the separate names stay as views of its rows.
+        Returns the number of layers fused."""
+        n = 0
+        for il in self.cfg.recurrent_layers():
+            p = f"l{il}"
+            parts = [self.w.get(f"{p}.gdn.{k}") for k in ("in_qkv", "in_z", "in_ba")]
+            if f"{p}.gdn.in_all" in self.w or any(not isinstance(t, torch.Tensor) or t.dtype != torch.bfloat16 for t in parts):
+                continue
+            allw = torch.cat(parts, 0)
+            r0 = 0
+            for k, t in zip(("in_qkv", "in_z", "in_ba"), parts):
+                self.w[f"{p}.gdn.{k}"] = allw[r0:r0 + t.shape[0]]
+                r0 += t.shape[0]
+            del parts
+            self.w[f"{p}.gdn.in_all"] = allw
+            n += 1
+        return n
 
     def _mla(self, p: str, il: int, x, b: StepBatch, kv: KvCache):
         """Latent attention: cache row = [rmsnorm(c_kv) | rope(k_pe)]; keys/values are expanded from

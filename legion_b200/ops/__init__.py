@@ -159,4 +159,4 @@ def gdn_recurrent(qkv, g, beta, state, cu_seq, slots, n_k, n_v, dk, dv, tiled_he
 def gated_rmsnorm(o, z, w, eps, act="silu"):
     if _cuda(o):
         return _sm.gated_rmsnorm(o, z, w, eps, act)
-    return _ref.gated_rmsnorm(o, z.view(o.shape), w, eps, act)
+    return _ref.gated_rmsnorm(o, z.reshape(o.shape), w, eps, act)

@@ -1137,6 +1137,24 @@ def gdn_recurrent(qkv, g, beta, state, cu_seq, slots, n_k, n_v, dk, dv, tiled_he
     return out
 
 
+def gdn_decode_fused_ok(n_k, n_v, dk, dv, conv_k) -> bool:
+    return dk == dv and dk in (64, 128) and conv_k == 4 and n_k > 0 and n_v % n_k == 0 and n_v // n_k <= 4
+
+
+def gdn_decode_fused(proj, conv_w, conv_state, A, dt_bias, norm_w, eps, act, state, slots, n_k, n_v, dk, dv,
+                     tiled_heads, scale, l2_eps=1e-6, out=None):
+    """One launch for the decode step of a Gated DeltaNet layer: conv + SiLU with history update, gates, delta rule
+    with state update, gated RMS norm. ``proj`` [n_seqs, q|k|v|z|b|a] is the fused input projection of the step's
+    tokens (one per sequence, in sequence order). Returns bf16 [n_seqs, n_v * dv]."""
+    C = ext()
+    n = slots.numel()
+    if out is None:
+        out = torch.empty(n, n_v * dv, dtype=torch.bfloat16, device=proj.device)
+    C.gdn_decode_fused(proj, conv_w, conv_state, A, dt_bias, norm_w, eps, 0 if act == "silu" else 1, state, slots,
+                       n_k, n_v, dk, dv, bool(tiled_heads), scale, l2_eps, out)
+    return out
+
+
 def gated_rmsnorm(o, z, w, eps, act="silu", out=None):
     C = ext()
     T, Hv, DV = o.shape

@@ -625,3 +625,41 @@ def test_head_linear_in_place_slices(T, nh, K, xcol, rpg, nf):
     want = torch.einsum("thk,hfk->thf", xs, wh).reshape(T * nh, nf)
     close(out[:, :nf], want, 2e-2, 2e-2)
     assert out[:, nf:].abs().sum() == 0
+
+
+@pytest.mark.parametrize("nk,nv,d,tiled,n_seq", [(2, 4, 128, False, 5), (4, 8, 64, True, 16), (2, 2, 128, False, 1),
+                                                (16, 32, 128, False, 3)])
+def test_gdn_decode_fused_matches_the_separate_kernels(nk, nv, d, tiled, n_seq):
+    """One launch (conv + gates + delta rule + gated norm) against the four-kernel path and the fp32 reference,
+    outputs and both carried states, over two consecutive decode steps."""
+    torch.manual_seed(nk * 7 + n_seq)
+    C = 2 * nk * d + nv * d
+    W = C + nv * d + 2 * nv
+    conv_w = torch.randn(C, 4, device=DEV) * 0.5
+    A = -torch.rand(nv, device=DEV) - 0.1
+    dtb = torch.randn(nv, device=DEV)
+    nw = torch.rand(d, device=DEV) + 0.5
+    slots = torch.randperm(n_seq + 2, device=DEV)[:n_seq].int()
+    cu = torch.arange(n_seq + 1, device=DEV, dtype=torch.int32)
+    cst = [torch.randn(n_seq + 2, C, 3, device=DEV) for _ in range(3)]
+    cst[1].copy_(cst[0]); cst[2].copy_(cst[0])
+    sst = [torch.randn(n_seq + 2, nv, d, d, device=DEV) * 0.1 for _ in range(3)]
+    sst[1].copy_(sst[0]); sst[2].copy_(sst[0])
+    for step in range(2):
+        proj = rnd(n_seq, W)
+        out = sm().gdn_decode_fused(proj, conv_w, cst[0], A, dtb, nw, 1e-6, "silu", sst[0], slots, nk, nv, d, d, tiled,
+                                    d ** -0.5)
+        status_ok()
+        mixed, z, ba = proj[:, :C], proj[:, C:C + nv * d], proj[:, C + nv * d:]
+        outs = []
+        for impl, k in ((sm(), 1), (ref, 2)):
+            y = impl.causal_conv1d_silu(mixed, conv_w, None, cst[k], cu, slots)
+            g, beta = impl.gdn_gates(ba[:, nv:], ba[:, :nv], A, dtb)
+            o = impl.gdn_recurrent(y, g, beta, sst[k], cu, slots, nk, nv, d, d, tiled, d ** -0.5)
+            zz = z if impl is not ref else z.reshape(n_seq, nv, d)
+            outs.append(impl.gated_rmsnorm(o, zz, nw, 1e-6).reshape(n_seq, nv * d))
+        close(out, outs[0], 1e-2, 1e-2)
+        close(out, outs[1], 4e-2, 4e-2)
+        close(cst[0], cst[1], 1e-6, 1e-6)
+        close(sst[0][slots.long()], sst[1][slots.long()], 1e-3, 1e-3)
+        close(sst[0][slots.long()], sst[2][slots.long()], 2e-2, 2e-2)
