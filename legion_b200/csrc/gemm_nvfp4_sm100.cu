@@ -37,7 +37,9 @@ constexpr int SMEM_BUDGET = 200 * 1024;
 
 constexpr int pow2_ge(int v) { return v <= 32 ? 32 : (v <= 64 ? 64 : (v <= 128 ? 128 : (v <= 256 ? 256 : 512))); }
 
-template <int BN, bool DUAL, int FT = 1>
+// NCTA: sized for that many CTAs per SM (a share of the shared memory and tensor memory each). Short-K GEMMs are bound by the
+// latency of their dependent hand-overs, not by bytes in flight, and a second CTA on the SM fills the gaps.
+template <int BN, bool DUAL, int FT = 1, int NCTA = 1>
 struct Cfg {
   static constexpr int NW = DUAL ? 2 : 1;
   static constexpr int X_TILE = BN * KB_BYTES;
@@ -45,21 +47,23 @@ struct Cfg {
   static constexpr int SFW_OFF = X_OFF + X_TILE;
   static constexpr int SFX_OFF = SFW_OFF + NW * SF_TILE;
   static constexpr int STAGE_BYTES = SFX_OFF + SF_TILE;
-  static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
+  static constexpr int BUDGET = NCTA == 1 ? SMEM_BUDGET : (NCTA == 2 ? 94 * 1024 : 54 * 1024);
+  static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+  static constexpr int TMEM_MAX = NCTA == 1 ? 512 : (NCTA == 2 ? 256 : 128);
   // A work item is FT consecutive 128-feature tiles of one token tile, accumulated side by side in one TMEM
   // buffer and handed to the epilogue together: a tile of a short-K GEMM (K = 512: two stages) is too little work
   // per hand-over (measured ~1 us of fixed cost per work item in every role).
   static constexpr int SUB_COLS = BN * NW;              // accumulator columns of one 128-feature tile
   static constexpr int ACC_COLS = SUB_COLS * FT;
-  static constexpr int NACC = (2 * ACC_COLS + NW * 16 + 16 <= 512) ? 2 : 1;
+  static constexpr int NACC = (2 * ACC_COLS + NW * 16 + 16 <= TMEM_MAX) ? 2 : 1;
   static constexpr int SFA_COL = NACC * ACC_COLS;       // 16 columns per weight tile: 4 k steps x 4 row groups
   static constexpr int SFB_COL = SFA_COL + NW * 16;     // 16 columns for the token tile
   static constexpr int TMEM_COLS = pow2_ge(SFB_COL + 16);
   static constexpr int EPI_BYTES = 32 * BM * 4;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 512;
   static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte alignment of swizzled tiles");
-  static_assert(SFB_COL + 16 <= 512, "accumulators and scale factors do not fit tensor memory");
+  static_assert(SFB_COL + 16 <= TMEM_MAX, "accumulators and scale factors do not fit tensor memory");
   static_assert(STAGES >= 2, "too few stages");
 };
 
@@ -147,10 +151,10 @@ __device__ __forceinline__ long sf_atom_byte(long row, int blk16, int k4) {
   return ((row >> 7) * k4 + (blk16 >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (blk16 & 3);
 }
 
-template <int BN, bool DUAL, bool QOUT, int FT>
-__global__ void __launch_bounds__(192, 1)
+template <int BN, bool DUAL, bool QOUT, int FT, int NCTA>
+__global__ void __launch_bounds__(192, NCTA)
 wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const Args a) {
-  using C = Cfg<BN, DUAL, FT>;
+  using C = Cfg<BN, DUAL, FT, NCTA>;
   constexpr int STAGES = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -472,10 +476,10 @@ wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 thread_local char g_err[512];
 int g_sms = 0;
 
-template <int BN, bool DUAL, bool QOUT, int FT>
+template <int BN, bool DUAL, bool QOUT, int FT, int NCTA = 1>
 int launch(const CUtensorMap* tmW, const CUtensorMap* tmX, const Args& a, int grid, cudaStream_t stream) {
-  using C = Cfg<BN, DUAL, FT>;
-  auto kfn = wgemm_nv4_kernel<BN, DUAL, QOUT, FT>;
+  using C = Cfg<BN, DUAL, FT, NCTA>;
+  auto kfn = wgemm_nv4_kernel<BN, DUAL, QOUT, FT, NCTA>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
@@ -553,18 +557,25 @@ int wgemm_nv4_launch(const Nv4Host& h, cudaStream_t stream) {
   // Feature tiles per work item: short-K GEMMs with many feature tiles (the down projection of an expert: K = 512,
   // 16 tiles) take four at a time, the gate / up pair two; everything else one.
   const int num_kb = (h.K + 255) / 256;
-  int ft = 1;
-  if (bn == 32 && !h.dual && !qout && num_kb <= 4 && a.feat_tiles >= 8) ft = 4;
-  else if (bn == 32 && h.dual && a.feat_tiles >= 2 && a.feat_tiles % 2 == 0 && long(n_tok_tiles) * a.feat_tiles >= 2L * g_sms) ft = 2;
+  // Decode-sized grouped GEMMs are bound by the latency of their dependent hand-overs (TMA -> MMA thread -> commit ->
+  // producer), not by bytes in flight: several CTAs per SM, each with a share of the shared memory and tensor
+  // memory, fill the gaps. Measured on the 80B-A3B expert shapes at 16 tokens: gate/up 43 -> 34 us with two CTAs
+  // per SM, down (K = 512: two stages per tile) 31 -> 22 -> 20 us with two / three.
+  const bool short_k = bn == 32 && !h.dual && !qout && num_kb <= 4 && a.feat_tiles >= 8;
+  const bool many_dual = bn == 32 && h.dual && qout && long(n_tok_tiles) * a.feat_tiles >= 2L * g_sms;
+  const int ncta = short_k ? 3 : (many_dual ? 2 : 1);
+  const int ft = 1;
   const long total = long(n_tok_tiles) * ((a.feat_tiles + ft - 1) / ft);
   if (total <= 0) return 0;
-  const int grid = int(total < g_sms ? total : g_sms);
+  const int slots = ncta * g_sms;
+  const int grid = int(total < slots ? total : slots);
+  if (short_k) return launch<32, false, false, 1, 3>(tmW, tmX, a, grid, stream);
+  if (many_dual) return launch<32, true, true, 1, 2>(tmW, tmX, a, grid, stream);
 #define LB_NV4(BN_, DUAL_, FT_)                                                             \
   if (bn == BN_ && h.dual == DUAL_ && ft == FT_)                                            \
     return qout ? launch<BN_, DUAL_, true, FT_>(tmW, tmX, a, grid, stream)                  \
                 : launch<BN_, DUAL_, false, FT_>(tmW, tmX, a, grid, stream);
-  LB_NV4(32, false, 1) LB_NV4(32, false, 4) LB_NV4(64, false, 1) LB_NV4(128, false, 1)
-  LB_NV4(32, true, 1) LB_NV4(32, true, 2) LB_NV4(64, true, 1)
+  LB_NV4(32, false, 1) LB_NV4(64, false, 1) LB_NV4(128, false, 1) LB_NV4(32, true, 1) LB_NV4(64, true, 1)
 #undef LB_NV4
   snprintf(g_err, sizeof(g_err), "wgemm_nv4: unsupported tile bn=%d dual=%d", bn, int(h.dual));
   return 1;

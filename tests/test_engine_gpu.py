@@ -66,7 +66,7 @@ def test_engine_with_nvfp4_experts():
     from legion_b200.engine.lm import EngineConfig, build_engine
     from legion_b200.engine.types import GenerateRequest, SamplingParams
     from legion_b200.models.weights import random_weights
-    from legion_b200.ops.sm100 import QWeight, Workspace
+    from legion_b200.ops.sm100 import Nv4Weight, QWeight, Workspace
     cfg = ModelConfig(arch="qwen3moe", n_layer=2, hidden=512, vocab=2048, n_head=8, n_kv_head=2, head_dim=128,
                       n_expert=8, top_k=2, expert_ff=256)
     w = random_weights(cfg, "cuda", torch.bfloat16, seed=0, std=0.05)
@@ -75,7 +75,7 @@ def test_engine_with_nvfp4_experts():
     assert eng_q.model.quantize_experts_nvfp4() > 0
     w_deq = dict(w)
     for k, v in eng_q.model.w.items():
-        if isinstance(v, QWeight):
+        if isinstance(v, (QWeight, Nv4Weight)):
             w_deq[k] = v.dequantize()
     eng_d = build_engine(cfg, weights=w_deq, device="cuda", engine_cfg=EngineConfig(**ecfg), start=False)
     prompt = list(range(3, 150))
