@@ -78,6 +78,32 @@ void bind_gdn(pybind11::module_& m) {
                                             out.data_ptr(), cur_stream()) == 0,
                 "gdn_decode_fused: needs square heads of 64 or 128, conv width 4, at most 4 value heads per key head");
   });
+  m.def("gdn_chunk_scratch_bytes", [](int64_t n_blocks, int64_t Hv) {
+    return int64_t(lb::gdn_chunk_scratch_bytes(int(n_blocks), int(Hv)));
+  });
+  m.def("gdn_chunk", [](const Tensor& qkv, const Tensor& g, const Tensor& beta, Tensor& state, const Tensor& blk_t0,
+                        const Tensor& blk_n, const Tensor& seq_blk0, const Tensor& seq_nchunk, const Tensor& seq_t0,
+                        const Tensor& seq_len, const Tensor& slots, int64_t Hk, int64_t Hv, int64_t DK, int64_t DV,
+                        bool tiled_heads, double scale, double l2_eps, Tensor& out, bool write_state, Tensor& scratch,
+                        Tensor& status) {
+    c10::cuda::CUDAGuard guard(qkv.device());
+    TORCH_CHECK(qkv.scalar_type() == at::kBFloat16 && qkv.dim() == 2 && qkv.stride(1) == 1 &&
+                    g.scalar_type() == at::kFloat && g.is_contiguous() && beta.scalar_type() == at::kFloat &&
+                    beta.is_contiguous() && state.scalar_type() == at::kFloat && out.scalar_type() == at::kBFloat16 &&
+                    out.is_contiguous(), "gdn_chunk dtypes / layout");
+    const int n_blocks = int(blk_t0.numel()), n_seqs = int(slots.numel());
+    TORCH_CHECK(size_t(scratch.numel()) * scratch.element_size() >= lb::gdn_chunk_scratch_bytes(n_blocks, int(Hv)),
+                "gdn_chunk: scratch too small");
+    TORCH_CHECK(lb::gdn_chunk_launch(qkv.data_ptr(), qkv.stride(0), qkv.size(0), g.data_ptr<float>(),
+                                     beta.data_ptr<float>(), state.data_ptr<float>(), blk_t0.data_ptr<int>(),
+                                     blk_n.data_ptr<int>(), n_blocks, seq_blk0.data_ptr<int>(),
+                                     seq_nchunk.data_ptr<int>(), seq_t0.data_ptr<int>(), seq_len.data_ptr<int>(),
+                                     slots.data_ptr<int>(), n_seqs, int(Hk), int(Hv), int(DK), int(DV),
+                                     tiled_heads ? 1 : 0, float(scale), float(l2_eps), out.data_ptr(),
+                                     write_state ? 1 : 0, scratch.data_ptr(), reinterpret_cast<int*>(status.data_ptr()),
+                                     cur_stream()) == 0,
+                "gdn_chunk: needs heads of 128 x 128 and 16-byte aligned rows");
+  });
   m.def("gdn_gates", [](const Tensor& a, const Tensor& b, const Tensor& A, const Tensor& dt_bias, Tensor& g,
                         Tensor& beta) {
     c10::cuda::CUDAGuard guard(a.device());

@@ -106,7 +106,7 @@ def have_ext() -> bool:
 NUM_SMS = 148
 
 # tuning knobs (environment: LB_TUNE="decode_fixed_tiles=2,dense_route=1")
-TUNE = {"decode_fixed_tiles": 2, "fused_plan": 1, "fused_router": 1, "dense_route": 1, "pdl": 1, "route_norm": 0, "mla_head_gemm": 1}
+TUNE = {"gdn_chunk": 1, "decode_fixed_tiles": 2, "fused_plan": 1, "fused_router": 1, "dense_route": 1, "pdl": 1, "route_norm": 0, "mla_head_gemm": 1}
 for _kv in os.environ.get("LB_TUNE", "").split(","):
     if "=" in _kv:
         TUNE[_kv.split("=")[0].strip()] = int(_kv.split("=")[1])
@@ -1124,14 +1124,57 @@ def gdn_gates(a, b, A, dt_bias):
     return g, beta
 
 
-def gdn_recurrent(qkv, g, beta, state, cu_seq, slots, n_k, n_v, dk, dv, tiled_heads, scale, l2_eps=1e-6,
-                  write_state=True, out=None):
+def gdn_chunk_plan(cu_host, device):
+    """Host-side tables of the chunked scan for one step: 128-token blocks and per-sequence chunk ranges."""
+    blk_t0, blk_n, seq_blk0, seq_nchunk, seq_t0, seq_len = [], [], [], [], [], []
+    for i in range(len(cu_host) - 1):
+        t0, n = cu_host[i], cu_host[i + 1] - cu_host[i]
+        seq_blk0.append(len(blk_t0))
+        seq_nchunk.append((n + 63) // 64)
+        seq_t0.append(t0)
+        seq_len.append(n)
+        for b in range(0, n, 128):
+            blk_t0.append(t0 + b)
+            blk_n.append(min(128, n - b))
+    i32 = dict(dtype=torch.int32, device=device)
+    return tuple(torch.tensor(v, **i32) for v in (blk_t0, blk_n, seq_blk0, seq_nchunk, seq_t0, seq_len))
+
+
+def gdn_chunked(qkv, g, beta, state, cu_host, slots, n_k, n_v, dk, dv, tiled_heads, scale, l2_eps=1e-6,
+                write_state=True, out=None):
+    """Gated delta rule over prompt-sized rows on the tensor cores (64-token chunks, ``csrc/gdn_chunk_sm100.cu``).
+    ``cu_host``: the sequence boundaries as a Python list. Heads of 128 x 128 only."""
     C = ext()
     T = qkv.shape[0]
+    ws = Workspace.get(qkv.device)
+    blk_t0, blk_n, seq_blk0, seq_nchunk, seq_t0, seq_len = gdn_chunk_plan(cu_host, qkv.device)
+    nb = int(blk_t0.numel())
+    need = C.gdn_chunk_scratch_bytes(nb, n_v)
+    scratch = ws._cache.get("gdn_chunk_scratch")
+    if scratch is None or scratch.numel() < need:
+        scratch = torch.empty(need, dtype=torch.uint8, device=qkv.device)
+        ws._cache["gdn_chunk_scratch"] = scratch
     if out is None:
         out = torch.empty(T, n_v, dv, dtype=torch.bfloat16, device=qkv.device)
-    # prompt chunks (many rows per sequence) run the column-per-thread kernel, decode rows the state-streaming one
+    C.gdn_chunk(qkv, g.contiguous(), beta.contiguous(), state, blk_t0, blk_n, seq_blk0, seq_nchunk, seq_t0, seq_len,
+                slots, n_k, n_v, dk, dv, bool(tiled_heads), scale, l2_eps, out, bool(write_state), scratch, ws.status)
+    return out
+
+
+def gdn_recurrent(qkv, g, beta, state, cu_seq, slots, n_k, n_v, dk, dv, tiled_heads, scale, l2_eps=1e-6,
+                  write_state=True, out=None, cu_host=None):
+    C = ext()
+    T = qkv.shape[0]
+    # prompt chunks (many rows per sequence): the chunked tensor-core scan when the heads are 128 x 128, else the
+    # column-per-thread kernel; decode rows run the state-streaming one
     prompt_rows = T >= 16 * max(1, slots.numel())
+    if prompt_rows and dk == 128 and dv == 128 and T >= 64 and TUNE["gdn_chunk"] and qkv.stride(0) % 8 == 0:
+        if cu_host is None:
+            cu_host = cu_seq.tolist()
+        return gdn_chunked(qkv, g, beta, state, cu_host, slots, n_k, n_v, dk, dv, tiled_heads, scale, l2_eps,
+                           write_state, out)
+    if out is None:
+        out = torch.empty(T, n_v, dv, dtype=torch.bfloat16, device=qkv.device)
     C.gdn_recurrent(qkv, g, beta, state, cu_seq, slots, n_k, n_v, dk, dv, tiled_heads, scale, l2_eps, out,
                     write_state, True, prompt_rows)
     return out

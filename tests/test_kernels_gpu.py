@@ -663,3 +663,43 @@ def test_gdn_decode_fused_matches_the_separate_kernels(nk, nv, d, tiled, n_seq):
         close(cst[0], cst[1], 1e-6, 1e-6)
         close(sst[0][slots.long()], sst[1][slots.long()], 1e-3, 1e-3)
         close(sst[0][slots.long()], sst[2][slots.long()], 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("nk,nv,tiled,lens", [(2, 4, False, [200]), (2, 2, True, [64, 130, 333]), (4, 8, False, [1000, 65]),
+                                             (1, 2, False, [128])])
+def test_gdn_chunked_scan_matches_token_serial(nk, nv, tiled, lens):
+    """Chunked (64-token) tensor-core scan against the fp32 reference and the token-serial kernel: outputs of every
+    token and the carried state, ragged lengths, non-zero initial state, a second step that continues from the
+    written state."""
+    torch.manual_seed(sum(lens) + nk)
+    d = 128
+    C = 2 * nk * d + nv * d
+    n_seq = len(lens)
+    slots = torch.randperm(n_seq + 1, device=DEV)[:n_seq].int()
+    st = [torch.randn(n_seq + 1, nv, d, d, device=DEV) * 0.05 for _ in range(3)]
+    st[1].copy_(st[0]); st[2].copy_(st[0])
+    for step in range(2):
+        T = sum(lens)
+        cu_h = [0]
+        for n in lens:
+            cu_h.append(cu_h[-1] + n)
+        cu = torch.tensor(cu_h, device=DEV, dtype=torch.int32)
+        qkv = rnd(T, C, scale=0.5)
+        g = -torch.rand(T, nv, device=DEV) * 0.15
+        beta = torch.rand(T, nv, device=DEV)
+        out = sm().gdn_chunked(qkv, g, beta, st[0], cu_h, slots, nk, nv, d, d, tiled, d ** -0.5)
+        status_ok()
+        want = ref.gdn_recurrent(qkv, g, beta, st[1], cu, slots, nk, nv, d, d, tiled, d ** -0.5)
+        import legion_b200.ops.sm100 as S
+        S.TUNE["gdn_chunk"] = 0
+        try:
+            serial = sm().gdn_recurrent(qkv, g, beta, st[2], cu, slots, nk, nv, d, d, tiled, d ** -0.5)
+        finally:
+            S.TUNE["gdn_chunk"] = 1
+        scale = float(want.float().abs().max())
+        assert float((out.float() - want.float()).abs().max()) < 0.03 * scale + 2e-3, "outputs vs reference"
+        assert float((out.float() - serial.float()).abs().max()) < 0.03 * scale + 2e-3, "outputs vs token-serial kernel"
+        sl = slots.long()
+        ss = float(st[1][sl].abs().max())
+        assert float((st[0][sl] - st[1][sl]).abs().max()) < 0.02 * ss + 2e-3, "state vs reference"
+        lens = [max(1, n // 2 + 3) for n in lens]       # the next step continues every sequence
