@@ -37,13 +37,13 @@ lb::CommPeers make_peers(const std::vector<int64_t>& buffers, const std::vector<
 
 void bind_gdn(pybind11::module_& m) {
   m.def("conv1d_silu", [](const Tensor& x, const Tensor& w, const OptT& bias, Tensor& conv_state, const Tensor& cu_seq,
-                          const Tensor& slots, Tensor& out, bool write_state) {
+                          const Tensor& slots, Tensor& out, bool write_state, int64_t max_len) {
     c10::cuda::CUDAGuard guard(x.device());
     TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kFloat, "conv1d_silu dtypes");
     TORCH_CHECK(lb::conv1d_silu_launch(x.data_ptr(), x.stride(0), w.data_ptr<float>(), optp<float>(bias),
                                        conv_state.data_ptr<float>(), cu_seq.data_ptr<int>(), slots.data_ptr<int>(),
                                        int(slots.numel()), int(x.size(1)), int(w.size(1)), out.data_ptr(),
-                                       out.stride(0), write_state ? 1 : 0, cur_stream()) == 0,
+                                       out.stride(0), write_state ? 1 : 0, cur_stream(), int(max_len)) == 0,
                 "conv1d_silu: unsupported kernel width");
   });
   m.def("gdn_recurrent", [](const Tensor& qkv, const Tensor& g, const Tensor& beta, Tensor& state,

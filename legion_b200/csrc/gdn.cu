@@ -52,16 +52,99 @@ __global__ void __launch_bounds__(128) conv1d_silu_kernel(const __nv_bfloat16* _
   }
 }
 
+// Prompt-sized form: tokens in parallel. A CTA covers 128 channels x TOK consecutive tokens of one sequence; a thread
+// walks its channel over those tokens with the KC - 1 previous inputs in registers (taken from the tensor itself, or
+// from the carried history for the first tokens of the sequence). The CTA that holds the sequence's last token
+// writes the new history. Reads of x are coalesced across the 128 channels of a token row.
+template <int KC>
+__global__ void __launch_bounds__(128) conv1d_silu_prompt_kernel(const __nv_bfloat16* __restrict__ x, long ldx,
+                                                                 const float* __restrict__ w,
+                                                                 const float* __restrict__ bias,
+                                                                 float* __restrict__ conv_state,
+                                                                 const int* __restrict__ cu_seq,
+                                                                 const int* __restrict__ slots, int C, int tok_per_cta,
+                                                                 __nv_bfloat16* __restrict__ out, long ldo,
+                                                                 int write_state) {
+  const int c = blockIdx.x * 128 + threadIdx.x;
+  const int seq = blockIdx.z;
+  const int t0 = cu_seq[seq], t1 = cu_seq[seq + 1];
+  const int ta = t0 + blockIdx.y * tok_per_cta;
+  if (c >= C || ta >= t1) return;
+  const int tb = min(t1, ta + tok_per_cta);
+  const int slot = slots[seq];
+  float wv[KC], h[KC - 1];
+#pragma unroll
+  for (int j = 0; j < KC; ++j) wv[j] = w[c * KC + j];
+  float* st = conv_state + (long(slot) * C + c) * (KC - 1);
+  // h[j] = input of token ta - (KC - 1) + j: from x when that token belongs to this step, else from the history
+#pragma unroll
+  for (int j = 0; j < KC - 1; ++j) {
+    const int t = ta - (KC - 1) + j;
+    h[j] = t >= t0 ? __bfloat162float(x[long(t) * ldx + c]) : st[(KC - 1) + (t - t0)];
+  }
+  const float b = bias ? bias[c] : 0.f;
+  for (int t = ta; t < tb; ++t) {
+    const float xv = __bfloat162float(x[long(t) * ldx + c]);
+    float acc = b + wv[KC - 1] * xv;
+#pragma unroll
+    for (int j = 0; j < KC - 1; ++j) acc += wv[j] * h[j];
+#pragma unroll
+    for (int j = 0; j < KC - 2; ++j) h[j] = h[j + 1];
+    h[KC - 2] = xv;
+    out[long(t) * ldo + c] = __float2bfloat16(acc / (1.f + __expf(-acc)));
+  }
+  (void)write_state;   // the history is replaced by conv1d_state_kernel after this kernel
+}
+
+// History update of the prompt form: one thread per (sequence, channel) after the main kernel.
+template <int KC>
+__global__ void __launch_bounds__(128) conv1d_state_kernel(const __nv_bfloat16* __restrict__ x, long ldx,
+                                                           float* __restrict__ conv_state,
+                                                           const int* __restrict__ cu_seq,
+                                                           const int* __restrict__ slots, int C) {
+  const int c = blockIdx.x * 128 + threadIdx.x;
+  const int seq = blockIdx.y;
+  if (c >= C) return;
+  const int t0 = cu_seq[seq], t1 = cu_seq[seq + 1];
+  if (t1 <= t0) return;
+  float* st = conv_state + (long(slots[seq]) * C + c) * (KC - 1);
+  float h[KC - 1];
+#pragma unroll
+  for (int j = 0; j < KC - 1; ++j) {
+    const int t = t1 - (KC - 1) + j;
+    h[j] = t >= t0 ? __bfloat162float(x[long(t) * ldx + c]) : st[(KC - 1) + (t - t0)];
+  }
+#pragma unroll
+  for (int j = 0; j < KC - 1; ++j) st[j] = h[j];
+}
+
 int conv1d_silu_launch(const void* x, long ldx, const float* w, const float* bias, float* conv_state,
                        const int* cu_seq, const int* slots, int n_seqs, int C, int KC, void* out, long ldo,
-                       int write_state, cudaStream_t s) {
+                       int write_state, cudaStream_t s, int max_len) {
   if (n_seqs <= 0) return 0;
+  auto xb = static_cast<const __nv_bfloat16*>(x);
+  auto ob = static_cast<__nv_bfloat16*>(out);
+  if (max_len >= 64) {
+    // prompt rows: tokens in parallel, then the history update as a second small launch (stream order keeps the
+    // main kernel's reads of the old history before its replacement)
+    const int tok = 32;
+    dim3 grid((C + 127) / 128, (max_len + tok - 1) / tok, n_seqs), grid2((C + 127) / 128, n_seqs);
+#define LB_KCP(K_)                                                                                             \
+  if (KC == K_) {                                                                                              \
+    conv1d_silu_prompt_kernel<K_><<<grid, 128, 0, s>>>(xb, ldx, w, bias, conv_state, cu_seq, slots, C, tok, ob, \
+                                                       ldo, write_state);                                      \
+    if (write_state) conv1d_state_kernel<K_><<<grid2, 128, 0, s>>>(xb, ldx, conv_state, cu_seq, slots, C);      \
+    return cudaGetLastError() != cudaSuccess;                                                                  \
+  }
+    LB_KCP(2) LB_KCP(3) LB_KCP(4) LB_KCP(5) LB_KCP(6) LB_KCP(7) LB_KCP(8)
+#undef LB_KCP
+    return 1;
+  }
   dim3 grid((C + 127) / 128, n_seqs);
 #define LB_KC(K_)                                                                                              \
   if (KC == K_) {                                                                                              \
-    conv1d_silu_kernel<K_><<<grid, 128, 0, s>>>(static_cast<const __nv_bfloat16*>(x), ldx, w, bias,            \
-                                                conv_state, cu_seq, slots, C,                                  \
-                                                static_cast<__nv_bfloat16*>(out), ldo, write_state);           \
+    conv1d_silu_kernel<K_><<<grid, 128, 0, s>>>(xb, ldx, w, bias, conv_state, cu_seq, slots, C, ob, ldo,       \
+                                                write_state);                                                  \
     return cudaGetLastError() != cudaSuccess;                                                                  \
   }
   LB_KC(2) LB_KC(3) LB_KC(4) LB_KC(5) LB_KC(6) LB_KC(7) LB_KC(8)

@@ -7,7 +7,7 @@ namespace lb {
 
 int conv1d_silu_launch(const void* x, long ldx, const float* w, const float* bias, float* conv_state,
                        const int* cu_seq, const int* slots, int n_seqs, int C, int KC, void* out, long ldo,
-                       int write_state, cudaStream_t s);
+                       int write_state, cudaStream_t s, int max_len = 0);   // max_len >= 64: the token-parallel form
 
 int gdn_recurrent_launch(const void* qkv, long ld, const float* g, const float* beta, float* state,
                          const int* cu_seq, const int* slots, int n_seqs, int Hk, int Hv, int DK, int DV,

@@ -338,12 +338,12 @@ class Decoder:
             z = ops.linear(x, w[f"{p}.gdn.in_z"])
             ba = ops.linear(x, w[f"{p}.gdn.in_ba"])
         conv = ops.causal_conv1d_silu(mixed, w[f"{p}.gdn.conv_w"], None, st.conv[il], b.cu_q, b.state_slots,
-                                      write_state=b.write_state)
+                                      write_state=b.write_state, max_len=b.max_q_len)
         g, beta = ops.gdn_gates(ba[:, nv:], ba[:, :nv], w[f"{p}.gdn.A"], w[f"{p}.gdn.dt_bias"])
         if b.replay is not None:
             b.replay[il] = (mixed, g, beta)
         o = ops.gdn_recurrent(conv, g, beta, st.ssm[il], b.cu_q, b.state_slots, nk, nv, dk, dv, cfg.gdn_tiled_heads,
-                              dk ** -0.5, 1e-6, write_state=b.write_state)
+                              dk ** -0.5, 1e-6, write_state=b.write_state, cu_host=b.cu_q_host)
         n = ops.gated_rmsnorm(o, z, w[f"{p}.gdn.norm"], cfg.rms_eps, cfg.gdn_gate_act)
         return self.pctx.defer_linear(n.reshape(n.shape[0], -1), w[f"{p}.gdn.out"], lazy=True)
 

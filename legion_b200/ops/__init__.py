@@ -135,9 +135,9 @@ def embed(ids, table):
     return table[ids.long()]
 
 
-def causal_conv1d_silu(x, w, bias, conv_state, cu_seq, slots, write_state=True):
+def causal_conv1d_silu(x, w, bias, conv_state, cu_seq, slots, write_state=True, max_len=None):
     if _cuda(x):
-        return _sm.causal_conv1d_silu(x, w, bias, conv_state, cu_seq, slots, write_state)
+        return _sm.causal_conv1d_silu(x, w, bias, conv_state, cu_seq, slots, write_state, max_len=max_len)
     return _ref.causal_conv1d_silu(x, w, bias, conv_state, cu_seq, slots, write_state)
 
 
@@ -148,10 +148,10 @@ def gdn_gates(a, b, A, dt_bias):
 
 
 def gdn_recurrent(qkv, g, beta, state, cu_seq, slots, n_k, n_v, dk, dv, tiled_heads, scale, l2_eps=1e-6,
-                  write_state=True):
+                  write_state=True, cu_host=None):
     if _cuda(qkv):
         return _sm.gdn_recurrent(qkv, g, beta, state, cu_seq, slots, n_k, n_v, dk, dv, tiled_heads, scale, l2_eps,
-                                 write_state)
+                                 write_state, cu_host=cu_host)
     return _ref.gdn_recurrent(qkv, g, beta, state, cu_seq, slots, n_k, n_v, dk, dv, tiled_heads, scale, l2_eps,
                               write_state)
 

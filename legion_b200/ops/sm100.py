@@ -1108,11 +1108,16 @@ def sample(logits, temperature, top_k, top_p, min_p, seeds, steps, out=None):
     return out
 
 
-def causal_conv1d_silu(x, w, bias, conv_state, cu_seq, slots, write_state=True, out=None):
+def causal_conv1d_silu(x, w, bias, conv_state, cu_seq, slots, write_state=True, out=None, max_len=None):
+    """``max_len``: longest sequence of the step when known on the host; prompt-sized steps (>= 64 rows per
+    sequence) run the token-parallel kernel."""
     C = ext()
     if out is None:
         out = torch.empty_like(x)
-    C.conv1d_silu(x, w, bias, conv_state, cu_seq, slots, out, write_state)
+    T, n = x.shape[0], max(1, slots.numel())
+    if max_len is None:
+        max_len = T if T >= 64 * n else 0          # without the host figure: only clearly prompt-sized steps
+    C.conv1d_silu(x, w, bias, conv_state, cu_seq, slots, out, write_state, int(max_len) if max_len >= 64 else 0)
     return out
 
 

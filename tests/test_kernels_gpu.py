@@ -703,3 +703,25 @@ def test_gdn_chunked_scan_matches_token_serial(nk, nv, tiled, lens):
         ss = float(st[1][sl].abs().max())
         assert float((st[0][sl] - st[1][sl]).abs().max()) < 0.02 * ss + 2e-3, "state vs reference"
         lens = [max(1, n // 2 + 3) for n in lens]       # the next step continues every sequence
+
+
+@pytest.mark.parametrize("lens", [[200], [70, 2, 1, 129], [64]])
+def test_conv1d_token_parallel_form(lens):
+    """Prompt-sized steps run the token-parallel convolution: outputs and carried history equal the reference,
+    including sequences shorter than the kernel width."""
+    torch.manual_seed(len(lens))
+    C = 384
+    T = sum(lens)
+    cu_h = [0]
+    for n in lens:
+        cu_h.append(cu_h[-1] + n)
+    cu = torch.tensor(cu_h, device=DEV, dtype=torch.int32)
+    slots = torch.randperm(len(lens) + 1, device=DEV)[:len(lens)].int()
+    x = rnd(T, C)
+    w = torch.randn(C, 4, device=DEV) * 0.5
+    cst = torch.randn(len(lens) + 1, C, 3, device=DEV)
+    cst2 = cst.clone()
+    y = sm().causal_conv1d_silu(x, w, None, cst, cu, slots, max_len=max(max(lens), 64))
+    ry = ref.causal_conv1d_silu(x, w, None, cst2, cu, slots)
+    close(y, ry)
+    close(cst, cst2, 1e-5, 1e-5)
