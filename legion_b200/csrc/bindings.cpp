@@ -462,6 +462,21 @@ void moe_plan(const Tensor& ids, const Tensor& wts, int64_t e_lo, int64_t n_loca
               "moe_plan failed");
 }
 
+void moe_plan_aligned(const Tensor& ids, const Tensor& wts, int64_t e_lo, int64_t n_local, int64_t bn, int64_t align,
+                      Tensor& counts2, Tensor& offsets, Tensor& sorted_token, Tensor& sorted_pair, Tensor& sorted_w,
+                      Tensor& tile_group, Tensor& tile_tok0, Tensor& tile_ntok, Tensor& meta) {
+  c10::cuda::CUDAGuard guard(ids.device());
+  TORCH_CHECK(counts2.numel() >= 2 * n_local && offsets.numel() > n_local && sorted_pair.numel() >= sorted_token.numel() &&
+                  sorted_w.numel() >= sorted_token.numel(), "moe_plan_aligned: buffers too small");
+  TORCH_CHECK(lb::moe_plan_aligned_launch(ids.data_ptr<int>(), wts.data_ptr<float>(), int(ids.size(0)), int(ids.size(1)),
+                                          int(e_lo), int(n_local), int(bn), int(align), counts2.data_ptr<int>(),
+                                          offsets.data_ptr<int>(), sorted_token.data_ptr<int>(), sorted_token.numel(),
+                                          sorted_pair.data_ptr<int>(), sorted_w.data_ptr<float>(),
+                                          tile_group.data_ptr<int>(), tile_tok0.data_ptr<int>(), tile_ntok.data_ptr<int>(),
+                                          int(tile_group.numel()), meta.data_ptr<int>(), cur_stream()) == 0,
+              "moe_plan_aligned: at most 512 local experts; sorted rows must cover pairs + experts * (align - 1)");
+}
+
 void moe_plan_gather(const Tensor& ids, const Tensor& wts, int64_t e_lo, int64_t n_local, int64_t bn, Tensor& counts,
                      Tensor& offsets, Tensor& sorted_token, Tensor& sorted_pair, Tensor& sorted_w, Tensor& tile_group,
                      Tensor& tile_tok0, Tensor& tile_ntok, Tensor& meta, const Tensor& x, Tensor& x_sorted) {
@@ -568,6 +583,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_route_small", &moe_route_small);
   m.def("moe_plan", &moe_plan);
   m.def("moe_plan_gather", &moe_plan_gather);
+  m.def("moe_plan_aligned", &moe_plan_aligned);
   m.def("gather_rows", &gather_rows);
   m.def("moe_combine", &moe_combine);
   m.def("argmax", &argmax);

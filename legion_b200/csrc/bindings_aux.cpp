@@ -320,6 +320,24 @@ void bind_quant(pybind11::module_& m) {
                                          optpm<float>(row_gscale), cur_stream()) == 0,
                 "nv4_act_quant: K must be a multiple of 16 and at most 8192, rows 16-byte aligned");
   });
+  m.def("nv4_gather_rows", [](const Tensor& codes, const Tensor& sf, const OptT& gscale, const Tensor& rows,
+                              const OptT& n_rows, Tensor& dst_codes, Tensor& dst_sf, const OptT& dst_gscale) {
+    TORCH_CHECK(codes.dim() == 2 && dst_codes.dim() == 2 && codes.stride(1) == 1 && dst_codes.stride(1) == 1 &&
+                    codes.size(1) == dst_codes.size(1) && rows.scalar_type() == at::kInt && rows.is_contiguous() &&
+                    dst_codes.size(0) >= rows.numel(), "nv4_gather_rows: codes [T, K / 2] -> [rows, K / 2]");
+    const long K = codes.size(1) * 2;
+    TORCH_CHECK(size_t(dst_sf.numel()) >= lb::nv4_sf_bytes(rows.numel(), K) && sf.is_contiguous() && dst_sf.is_contiguous(),
+                "nv4_gather_rows: scale atom buffer too small");
+    TORCH_CHECK(gscale.has_value() == dst_gscale.has_value() &&
+                    (!dst_gscale.has_value() || dst_gscale->numel() >= rows.numel()), "nv4_gather_rows: row scales");
+    c10::cuda::CUDAGuard guard(codes.device());
+    TORCH_CHECK(lb::nv4_gather_rows_launch(reinterpret_cast<const uint8_t*>(codes.data_ptr()), codes.stride(0),
+                                           reinterpret_cast<const uint8_t*>(sf.data_ptr()), optp<float>(gscale), K,
+                                           rows.data_ptr<int>(), optp<int>(n_rows), rows.numel(),
+                                           reinterpret_cast<uint8_t*>(dst_codes.data_ptr()), dst_codes.stride(0),
+                                           reinterpret_cast<uint8_t*>(dst_sf.data_ptr()), optpm<float>(dst_gscale),
+                                           cur_stream()) == 0, "nv4_gather_rows: K % 64, 16-byte aligned rows");
+  });
   m.def("wgemm_nv4", [](const Tensor& w, const Tensor& w_sf, const OptT& w_gscale, const Tensor& x, const Tensor& x_sf,
                         const OptT& x_gscale, int64_t x_gs_stride, const OptT& out, const OptT& residual,
                         const OptT& tok_scale, const OptT& out_rows, int64_t n_feat, bool dual, int64_t dual_offset,

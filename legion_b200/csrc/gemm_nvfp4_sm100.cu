@@ -576,6 +576,7 @@ int wgemm_nv4_launch(const Nv4Host& h, cudaStream_t stream) {
     return qout ? launch<BN_, DUAL_, true, FT_>(tmW, tmX, a, grid, stream)                  \
                 : launch<BN_, DUAL_, false, FT_>(tmW, tmX, a, grid, stream);
   LB_NV4(32, false, 1) LB_NV4(64, false, 1) LB_NV4(128, false, 1) LB_NV4(32, true, 1) LB_NV4(64, true, 1)
+  LB_NV4(128, true, 1)
 #undef LB_NV4
   snprintf(g_err, sizeof(g_err), "wgemm_nv4: unsupported tile bn=%d dual=%d", bn, int(h.dual));
   return 1;
@@ -727,7 +728,44 @@ __global__ void __launch_bounds__(128) act_quant_kernel(const __nv_bfloat16* __r
   }
 }
 
+// One warp per destination row: dst row i = source row rows[i] (codes, the row's scale bytes inside their atoms, the
+// row scale). rows[i] < 0: a padding row, left as it is.
+__global__ void __launch_bounds__(256) nv4_gather_kernel(const uint8_t* __restrict__ codes, long ldc,
+                                                         const uint8_t* __restrict__ sf, const float* __restrict__ gs,
+                                                         int K, int k4, const int* __restrict__ rows,
+                                                         const int* __restrict__ n_rows, long max_rows,
+                                                         uint8_t* __restrict__ dcodes, long ldd, uint8_t* __restrict__ dsf,
+                                                         float* __restrict__ dgs) {
+  const int lane = threadIdx.x & 31;
+  const long n = n_rows ? min(long(*n_rows), max_rows) : max_rows;
+  const int vec = K / 32;                        // 16-byte vectors of codes per row
+  for (long i = long(blockIdx.x) * 8 + (threadIdx.x >> 5); i < n; i += long(gridDim.x) * 8) {
+    const int t = rows[i];
+    if (t < 0) continue;
+    const uint4* s4 = reinterpret_cast<const uint4*>(codes + long(t) * ldc);
+    uint4* d4 = reinterpret_cast<uint4*>(dcodes + i * ldd);
+    for (int j = lane; j < vec; j += 32) d4[j] = s4[j];
+    for (int a = lane; a < k4; a += 32)
+      *reinterpret_cast<uint32_t*>(dsf + sf_atom_byte(i, a * 4, k4)) =
+          *reinterpret_cast<const uint32_t*>(sf + sf_atom_byte(t, a * 4, k4));
+    if (lane == 0 && gs) dgs[i] = gs[t];
+  }
+}
+
 }  // namespace
+
+int nv4_gather_rows_launch(const uint8_t* codes, long ldc, const uint8_t* sf, const float* row_gscale, long K,
+                           const int* rows, const int* n_rows, long max_rows, uint8_t* dst_codes, long ldd,
+                           uint8_t* dst_sf, float* dst_gscale, cudaStream_t s) {
+  if (K % 64 || (ldc % 16) || (ldd % 16) || ((reinterpret_cast<uintptr_t>(codes) | reinterpret_cast<uintptr_t>(dst_codes)) & 15))
+    return 1;
+  if (max_rows <= 0) return 0;
+  const long ctas = (max_rows + 7) / 8;
+  nv4_gather_kernel<<<unsigned(ctas < 8192 ? ctas : 8192), 256, 0, s>>>(codes, ldc, sf, row_gscale, int(K), nv4_sf_k4(K),
+                                                                       rows, n_rows, max_rows, dst_codes, ldd, dst_sf,
+                                                                       dst_gscale);
+  return cudaGetLastError() != cudaSuccess;
+}
 
 int nv4_pack_scales_launch(const uint8_t* scales, long rows, long K, uint8_t* atoms, cudaStream_t s) {
   if (K % 16) return 1;

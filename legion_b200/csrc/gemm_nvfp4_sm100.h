@@ -58,6 +58,13 @@ int nv4_unpack_scales_launch(const uint8_t* atoms, long rows, long K, uint8_t* s
 // produce the rows: x (+ residual) -> sum_out; normed = rmsnorm(sum) * (w + w_offset) -> normed_out (bf16, optional)
 // and its encoding. gscale_static != nullptr: every row uses that device scalar (and row_gscale is not written);
 // otherwise row_gscale[r] = amax(row) / (6 * 448).
+// dst row i = source row rows[i] of an encoded activation (codes, scale bytes inside their atoms, row scale), for
+// i < min(*n_rows, max_rows); rows[i] < 0 skips the row. Brings token rows into the expert-sorted order of a
+// routing plan without decoding them.
+int nv4_gather_rows_launch(const uint8_t* codes, long ldc, const uint8_t* sf, const float* row_gscale, long K,
+                           const int* rows, const int* n_rows, long max_rows, uint8_t* dst_codes, long ldd,
+                           uint8_t* dst_sf, float* dst_gscale, cudaStream_t s);
+
 int nv4_act_quant_launch(const void* x, long ldx, const void* residual, long ldr, void* sum_out, long lds,
                          const float* norm_w, float eps, float w_offset, void* normed_out, long ldn, long rows, long K,
                          const float* gscale_static, uint8_t* codes, long ldc, uint8_t* sf_atoms, float* row_gscale,

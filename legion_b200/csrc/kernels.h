@@ -68,6 +68,12 @@ int moe_plan_gather_small_launch(const int* ids, const float* wts, int n_tokens,
 int moe_plan_launch(const int* ids, const float* wts, int n_tokens, int k, int e_lo, int n_local, int bn, int* counts,
                     int* offsets, int* sorted_token, int* sorted_pair, float* sorted_w, int* tile_group,
                     int* tile_tok0, int* tile_ntok, int max_tiles, int* meta, cudaStream_t s);
+// Prompt-sized steps: histogram / scan / scatter with atomics; segments start on multiples of `align` rows, padding
+// rows carry sorted_token = -1, the order inside a segment is unspecified. counts2: 2 * n_local ints of scratch.
+int moe_plan_aligned_launch(const int* ids, const float* wts, int n_tokens, int k, int e_lo, int n_local, int bn, int align,
+                            int* counts2, int* offsets, int* sorted_token, long sorted_rows, int* sorted_pair,
+                            float* sorted_w, int* tile_group, int* tile_tok0, int* tile_ntok, int max_tiles, int* meta,
+                            cudaStream_t s);
 
 int gather_rows_launch(const void* src, long lds, const int* rows, const int* n_rows, void* dst, long ldd, int H,
                        int max_rows, cudaStream_t s);

@@ -663,6 +663,98 @@ int moe_plan_launch(const int* ids, const float* wts, int n_tokens, int k, int e
   return cudaGetLastError() != cudaSuccess;
 }
 
+// Prompt-sized steps: histogram, scan and scatter with atomics instead of one pass over all pairs per expert. The
+// rows of an expert are contiguous and start on a multiple of `align` rows (the block-scaled 4-bit GEMM needs its
+// token tiles on scale-atom boundaries); rows between two segments have sorted_token = -1. The order of the rows
+// inside a segment is whatever the atomics give: every row's result lands in its own pair row, so nothing
+// downstream depends on it.
+__global__ void __launch_bounds__(256) moe_hist_kernel(const int* __restrict__ ids, int n_pairs, int e_lo, int n_local,
+                                                       int* __restrict__ counts) {
+  __shared__ int h[512];
+  for (int i = threadIdx.x; i < n_local; i += 256) h[i] = 0;
+  __syncthreads();
+  for (int p = blockIdx.x * 256 + threadIdx.x; p < n_pairs; p += gridDim.x * 256) {
+    const int e = ids[p] - e_lo;
+    if (unsigned(e) < unsigned(n_local)) atomicAdd(&h[e], 1);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_local; i += 256)
+    if (h[i]) atomicAdd(&counts[i], h[i]);
+}
+__global__ void __launch_bounds__(512) moe_scan_aligned_kernel(const int* __restrict__ counts, int n_local, int bn,
+                                                               int align, int* __restrict__ offsets,
+                                                               int* __restrict__ tile_group, int* __restrict__ tile_tok0,
+                                                               int* __restrict__ tile_ntok, int max_tiles,
+                                                               int* __restrict__ meta) {
+  __shared__ int w_rows[16], w_tiles[16];
+  const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
+  const int c = e < n_local ? counts[e] : 0;
+  const int rows = (c + align - 1) / align * align;
+  const int nt = (c + bn - 1) / bn;
+  int ir = rows, it = nt;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int a = __shfl_up_sync(0xffffffffu, ir, d), b = __shfl_up_sync(0xffffffffu, it, d);
+    if (lane >= d) { ir += a; it += b; }
+  }
+  if (lane == 31) { w_rows[warp] = ir; w_tiles[warp] = it; }
+  __syncthreads();
+  int br = 0, bt = 0;
+  for (int w = 0; w < warp; ++w) { br += w_rows[w]; bt += w_tiles[w]; }
+  const int off = br + ir - rows, toff = bt + it - nt;
+  if (e < n_local) {
+    offsets[e] = off;
+    for (int i = 0; i < nt; ++i) {
+      const int ti = toff + i;
+      if (ti < max_tiles) {
+        tile_group[ti] = e;
+        tile_tok0[ti] = off + i * bn;
+        tile_ntok[ti] = min(bn, c - i * bn);
+      }
+    }
+  }
+  if (e == 511) {
+    offsets[n_local] = br + ir;
+    meta[0] = min(bt + it, max_tiles);
+    meta[1] = br + ir;
+  }
+}
+__global__ void __launch_bounds__(256) moe_scatter_kernel(const int* __restrict__ ids, const float* __restrict__ wts,
+                                                          int n_pairs, int k, int e_lo, int n_local,
+                                                          const int* __restrict__ offsets, int* __restrict__ cursor,
+                                                          int* __restrict__ sorted_token, int* __restrict__ sorted_pair,
+                                                          float* __restrict__ sorted_w) {
+  const int p = blockIdx.x * 256 + threadIdx.x;
+  if (p >= n_pairs) return;
+  const int e = ids[p] - e_lo;
+  if (unsigned(e) >= unsigned(n_local)) return;
+  const int dst = offsets[e] + atomicAdd(&cursor[e], 1);
+  sorted_token[dst] = p / k;
+  sorted_pair[dst] = p;
+  sorted_w[dst] = wts[p];
+}
+
+int moe_plan_aligned_launch(const int* ids, const float* wts, int n_tokens, int k, int e_lo, int n_local, int bn, int align,
+                            int* counts2, int* offsets, int* sorted_token, long sorted_rows, int* sorted_pair,
+                            float* sorted_w, int* tile_group, int* tile_tok0, int* tile_ntok, int max_tiles, int* meta,
+                            cudaStream_t s) {
+  if (n_local <= 0 || n_local > 512 || align <= 0 || bn <= 0) return 1;
+  const int n_pairs = n_tokens * k;
+  if (sorted_rows < long(n_pairs) + long(n_local) * (align - 1)) return 1;
+  cudaMemsetAsync(counts2, 0, sizeof(int) * 2 * n_local, s);
+  cudaMemsetAsync(sorted_token, 0xff, sizeof(int) * sorted_rows, s);
+  if (n_pairs > 0) {
+    const int hgrid = min(296, (n_pairs + 255) / 256);
+    moe_hist_kernel<<<hgrid, 256, 0, s>>>(ids, n_pairs, e_lo, n_local, counts2);
+  }
+  moe_scan_aligned_kernel<<<1, 512, 0, s>>>(counts2, n_local, bn, align, offsets, tile_group, tile_tok0, tile_ntok,
+                                            max_tiles, meta);
+  if (n_pairs > 0)
+    moe_scatter_kernel<<<(n_pairs + 255) / 256, 256, 0, s>>>(ids, wts, n_pairs, k, e_lo, n_local, offsets,
+                                                             counts2 + n_local, sorted_token, sorted_pair, sorted_w);
+  return cudaGetLastError() != cudaSuccess;
+}
+
 // Decode-sized steps (at most 1024 pairs): the whole plan AND the row gather in ONE launch. Every CTA rebuilds
 // the plan in shared memory (a few hundred comparisons per thread - cheaper than three more launches and their
 // dependencies), CTA 0 publishes it, and all CTAs then copy their share of the rows into expert order. The
@@ -781,7 +873,9 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ src, long l
                                    const int* __restrict__ n_rows, __nv_bfloat16* __restrict__ dst, long ldd, int H) {
   const int n = *n_rows;
   for (int i = blockIdx.x; i < n; i += gridDim.x) {
-    const uint4* s4 = reinterpret_cast<const uint4*>(src + long(rows[i]) * lds);
+    const int r = rows[i];
+    if (r < 0) continue;                      // a padding row between two aligned segments
+    const uint4* s4 = reinterpret_cast<const uint4*>(src + long(r) * lds);
     uint4* d4 = reinterpret_cast<uint4*>(dst + long(i) * ldd);
     for (int j = threadIdx.x; j < H / 8; j += blockDim.x) d4[j] = s4[j];
   }

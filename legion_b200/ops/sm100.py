@@ -106,7 +106,7 @@ def have_ext() -> bool:
 NUM_SMS = 148
 
 # tuning knobs (environment: LB_TUNE="decode_fixed_tiles=2,dense_route=1")
-TUNE = {"gdn_chunk": 1, "decode_fixed_tiles": 2, "fused_plan": 1, "fused_router": 1, "dense_route": 1, "pdl": 1, "route_norm": 0, "mla_head_gemm": 1}
+TUNE = {"nv4_sorted": 1, "nv4_sorted_bn": 64, "gdn_chunk": 1, "decode_fixed_tiles": 2, "fused_plan": 1, "fused_router": 1, "dense_route": 1, "pdl": 1, "route_norm": 0, "mla_head_gemm": 1}
 for _kv in os.environ.get("LB_TUNE", "").split(","):
     if "=" in _kv:
         TUNE[_kv.split("=")[0].strip()] = int(_kv.split("=")[1])
@@ -889,10 +889,7 @@ def _moe_experts_nv4(x, ids, wts, w_gate_up: "Nv4Weight", w_down: "Nv4Weight", n
     if xq is None:
         xq = nv4_quant_act(x, key="moe_x")
     if h_scale is None:
-        h_scale = ws._cache.get("nv4_h_scale")
-        if h_scale is None:
-            h_scale = torch.tensor([NV4_H_AMAX / (6.0 * 448.0)], dtype=torch.float32, device=x.device)
-            ws._cache["nv4_h_scale"] = h_scale
+        h_scale = _nv4_h_scale(ws, x.device)
     rows = dr.n_slots * dr.stride
     if dr.hq is None or dr.hq[0].shape[1] * 2 != n_ff:
         dr.hq = (torch.zeros(rows, n_ff // 2, dtype=torch.uint8, device=x.device),
@@ -906,6 +903,88 @@ def _moe_experts_nv4(x, ids, wts, w_gate_up: "Nv4Weight", w_down: "Nv4Weight", n
                 dr.out_rows, H, False, 0, 0, dr.bn, ws.status, dr.tile_group, dr.slot_base, dr.tile_ntok, dr.meta,
                 dr.n_slots, H, 0, None, None, None, None)
     return _dense_combine(dr, routing, ids, e_lo, T, k, H, shared, shared_gate, residual, out, norm, x.device)
+
+
+class Nv4Plan:
+    """Routing plan and expert-sorted NVFP4 buffers of a prompt-sized step on the native path: every expert's rows
+    start on a token-tile boundary (``bn`` rows) so the tile's scale factors start where the tensor-core copy
+    wants them."""
+
+    def __init__(self, max_tokens: int, k: int, n_local: int, bn: int, H: int, n_ff: int, device):
+        C = ext()
+        P = max_tokens * k
+        i32 = dict(dtype=torch.int32, device=device)
+        u8 = dict(dtype=torch.uint8, device=device)
+        self.bn = bn
+        self.rows = (P + n_local * bn + 127) // 128 * 128
+        self.max_tiles = (P + bn - 1) // bn + n_local
+        self.counts2 = torch.zeros(2 * n_local, **i32)
+        self.offsets = torch.zeros(n_local + 1, **i32)
+        self.sorted_token = torch.full((self.rows,), -1, **i32)
+        self.sorted_pair = torch.zeros(self.rows, **i32)
+        self.sorted_w = torch.zeros(self.rows, dtype=torch.float32, device=device)
+        self.tile_group = torch.zeros(self.max_tiles, **i32)
+        self.tile_tok0 = torch.zeros(self.max_tiles, **i32)
+        self.tile_ntok = torch.zeros(self.max_tiles, **i32)
+        self.meta = torch.zeros(2, **i32)
+        self.x_codes = torch.zeros(self.rows, H // 2, **u8)
+        self.x_sf = torch.zeros(C.nv4_sf_bytes(self.rows, H), **u8)
+        self.x_gs = torch.ones(self.rows, dtype=torch.float32, device=device)
+        self.h_codes = torch.zeros(self.rows, n_ff // 2, **u8)
+        self.h_sf = torch.zeros(C.nv4_sf_bytes(self.rows, n_ff), **u8)
+        self.y_pairs = torch.zeros(P, H, dtype=torch.bfloat16, device=device)
+
+
+def _nv4_h_scale(ws, device):
+    h_scale = ws._cache.get("nv4_h_scale")
+    if h_scale is None:
+        h_scale = torch.tensor([NV4_H_AMAX / (6.0 * 448.0)], dtype=torch.float32, device=device)
+        ws._cache["nv4_h_scale"] = h_scale
+    return h_scale
+
+
+def _moe_experts_nv4_sorted(x, ids, wts, w_gate_up: "Nv4Weight", w_down: "Nv4Weight", n_ff, e_lo, shared, shared_gate,
+                            residual, out, norm, xq: Optional["Nv4Act"] = None):
+    """Routed experts of a prompt-sized step on the native NVFP4 path: the tokens are encoded once, their codes and
+    scale bytes are gathered into expert order (aligned segments), the gate/up GEMM re-encodes its SwiGLU output
+    and the down GEMM scatters weighted rows to their pairs. Nothing is expanded to bf16 on the way."""
+    C = ext()
+    T, H = x.shape
+    k = ids.shape[1]
+    E_local = w_gate_up.shape[0]
+    ws = Workspace.get(x.device)
+    bn = TUNE["nv4_sorted_bn"]
+    cap = 1024
+    while cap < T:
+        cap *= 2
+    key = ("nv4_plan", cap, k, E_local, bn, H, n_ff)
+    plan = ws._cache.get(key)
+    if plan is None:
+        plan = Nv4Plan(cap, k, E_local, bn, H, n_ff, x.device)
+        ws._cache[key] = plan
+    C.moe_plan_aligned(ids, wts, e_lo, E_local, bn, bn, plan.counts2, plan.offsets, plan.sorted_token,
+                       plan.sorted_pair, plan.sorted_w, plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta)
+    if xq is None:
+        xq = nv4_quant_act(x, key="moe_x_big")
+    C.nv4_gather_rows(xq.codes, xq.sf, xq.gscale if xq.stride else None, plan.sorted_token, plan.meta[1:2],
+                      plan.x_codes, plan.x_sf, plan.x_gs if xq.stride else None)
+    h_scale = _nv4_h_scale(ws, x.device)
+    C.wgemm_nv4(w_gate_up.view2d(), w_gate_up.sf, w_gate_up.gscale, plan.x_codes, plan.x_sf,
+                plan.x_gs if xq.stride else xq.gscale, 1 if xq.stride else 0, None, None, None, None, n_ff, True, n_ff,
+                0, bn, ws.status, plan.tile_group, plan.tile_tok0, plan.tile_ntok, plan.meta, plan.max_tiles, 2 * n_ff,
+                0, None, plan.h_codes, plan.h_sf, h_scale)
+    C.wgemm_nv4(w_down.view2d(), w_down.sf, w_down.gscale, plan.h_codes, plan.h_sf, h_scale, 0, plan.y_pairs, None,
+                plan.sorted_w, plan.sorted_pair, H, False, 0, 0, bn, ws.status, plan.tile_group, plan.tile_tok0,
+                plan.tile_ntok, plan.meta, plan.max_tiles, H, 0, None, None, None, None)
+    if out is None:
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+    if norm is None:
+        C.moe_combine(plan.y_pairs, ids, e_lo, e_lo + E_local, shared, shared_gate, residual, out, None, 0.0, 0.0, None)
+        return out
+    normed = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+    C.moe_combine(plan.y_pairs, ids, e_lo, e_lo + E_local, shared, shared_gate, residual, out, norm[0], norm[1],
+                  norm[2], normed)
+    return out, normed
 
 
 # largest |SwiGLU output| the static scale of the re-encoded intermediate is laid out for (checkpoints bring their
@@ -932,7 +1011,10 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[Moe
         if _dense_ok(routing, E_local, e_lo, ids):
             return _moe_experts_nv4(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, shared, shared_gate, residual, out,
                                     norm, routing, xq=routing.xq)
-        # larger steps: the de-quantising grouped GEMM over the routing plan (same codes, linear scale order)
+        if TUNE["nv4_sorted"] and T * k >= 64 * E_local and not (routing is not None and routing.shared_slot):
+            return _moe_experts_nv4_sorted(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, shared, shared_gate, residual,
+                                           out, norm, xq=routing.xq if routing is not None else None)
+        # steps in between: the de-quantising grouped GEMM over the routing plan (same codes, linear scale order)
         w_gate_up, w_down = w_gate_up.as_qweight(), w_down.as_qweight()
     if routing is not None and routing.shared_slot and not _dense_ok(routing, E_local, e_lo, ids):
         raise ValueError("the routing carries a shared-expert slot that these expert weights do not have")

@@ -169,3 +169,44 @@ def test_moe_block_native_nvfp4_with_shared_slot(T, E, k, H, F):
     want2 = ref.moe_experts(x2, r2.ids, r2.wts, gud[:E].bfloat16(), dnd[:E].bfloat16(), F)
     assert sm100.Workspace.get(_dev()).check() == 0
     assert float((y2.float() - want2.float()).abs().max()) < 0.03 * float(want2.abs().max()) + 0.03
+
+
+@pytest.mark.parametrize("T,E,k,H,F,bn", [(1500, 32, 6, 512, 256, 64), (700, 16, 4, 1024, 512, 64),
+                                          (2100, 24, 3, 512, 512, 128)])
+def test_moe_block_native_nvfp4_prompt_sized(T, E, k, H, F, bn):
+    """Prompt-sized steps: aligned routing plan, gather of the encoded rows, both grouped GEMMs on the W4A4 path.
+    Against the fp32 computation over the de-quantised weights and activations."""
+    from legion_b200.ops import reference as ref
+    from legion_b200.ops import sm100
+    x, res, w_r, wgu, wd, _ = _moe_setup(T, E, k, H, F, 11)
+    qgu = sm100.Nv4Weight.quantize_cuda(wgu[:E].contiguous(), dual_rows=F)
+    qdn = sm100.Nv4Weight.quantize_cuda(wd[:E].contiguous())
+    r = sm100.router(x, w_r, k)
+    # one expert gets no token at all: its segment is empty
+    ids = torch.where(r.ids == 3, torch.full_like(r.ids, 5), r.ids)
+    old = sm100.TUNE["nv4_sorted_bn"]
+    sm100.TUNE["nv4_sorted_bn"] = bn
+    try:
+        out = sm100._moe_experts_nv4_sorted(x, ids, r.wts, qgu, qdn, F, 0, None, None, res, None, None)
+        out2 = sm100._moe_experts_nv4_sorted(x, ids, r.wts, qgu, qdn, F, 0, None, None, res, None, None)
+    finally:
+        sm100.TUNE["nv4_sorted_bn"] = old
+    assert sm100.Workspace.get(_dev()).check() == 0
+    assert torch.equal(out, out2)                 # the order inside a segment does not reach the result
+    xd = sm100.nv4_quant_act(x).dequantize().bfloat16()
+    gud, dnd = qgu.dequantize(torch.float32), qdn.dequantize(torch.float32)
+    want = ref.moe_experts(xd, ids, r.wts, gud.bfloat16(), dnd.bfloat16(), F).float() + res.float()
+    rel = float((out.float() - want).abs().mean() / want.abs().mean())
+    assert rel < 0.08, rel
+    # the plan itself: segments on tile boundaries, every pair exactly once, padding rows marked
+    plan = next(v for kk, v in sm100.Workspace.get(_dev())._cache.items()
+                if isinstance(kk, tuple) and kk[0] == "nv4_plan" and kk[4] == bn and kk[5] == H and kk[6] == F)
+    off = plan.offsets[:E + 1].tolist()
+    cnt = torch.bincount(ids.reshape(-1).long(), minlength=E).tolist()
+    assert all(o % bn == 0 for o in off) and cnt[3] == 0 and off[4] == off[3]
+    st, sp = plan.sorted_token.cpu(), plan.sorted_pair.cpu()
+    for e in range(E):
+        seg = sp[off[e]:off[e] + cnt[e]].long()
+        assert bool((ids.reshape(-1).cpu()[seg] == e).all()) and seg.unique().numel() == cnt[e]
+        assert bool((st[off[e] + cnt[e]:off[e + 1]] == -1).all())
+    assert plan.meta.tolist()[0] == sum((c + bn - 1) // bn for c in cnt)
