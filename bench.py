@@ -97,7 +97,7 @@ def build_model(a, cfg, dev, pctx, shard, weights_mode):
     """Random-init weights generated on the device; NVFP4 configurations are folded and quantised layer by layer
     while they are generated (their bf16 form would not fit one GPU)."""
     import torch
-    from legion_b200.models.decoder import Decoder, fold_shared_expert, quantize_moe_layer_nvfp4
+    from legion_b200.models.decoder import Decoder, place_shared_expert, quantize_moe_layer_nvfp4
     from legion_b200.models.weights import layer_of, random_weights
     world = pctx.world
     post = None
@@ -113,8 +113,8 @@ def build_model(a, cfg, dev, pctx, shard, weights_mode):
             if not name.endswith(last):
                 return
             p = f"l{il}"
-            if world == 1 and not a.no_fold:
-                fold_shared_expert(out, p, cfg)
+            if not a.no_fold and (world == 1 or (shard is not None and shard.shared_whole)):
+                place_shared_expert(out, p, il, cfg, pctx.rank, world)
             quantize_moe_layer_nvfp4(out, p, native=not a.nvfp4_expand)
     weights = random_weights(cfg, dev, torch.bfloat16, seed=0, shard=shard, post=post)
     torch.cuda.synchronize()
@@ -176,7 +176,8 @@ def main(argv=None):
     nvfp4 = spec["weights"] == "nvfp4"
     ep = world > 1 and cfg.n_expert > 0 and (a.moe == "ep" or (a.moe == "auto" and (world >= 4 or nvfp4)))
     pctx = pdist.init_from_env("cuda", comm=a.comm, max_rows=8192, hidden=cfg.hidden, expert_parallel=ep)
-    shard = Shard(cfg, rank, world, expert_parallel=ep) if world > 1 else None
+    shard = Shard(cfg, rank, world, expert_parallel=ep,
+                  shared_whole=ep and nvfp4 and not a.no_fold and cfg.shared_ff == cfg.expert_ff) if world > 1 else None
     t0 = time.time()
     weights = build_model(a, cfg, dev, pctx, shard, spec["weights"])
     load_s = time.time() - t0
@@ -317,7 +318,9 @@ def main(argv=None):
     extra.update({"decode": {str(u): rows[u] for u in all_users}, "kernel_status_word": status,
                   "comm_status_word": comm_status, "launches_per_step": headline.get("launches_per_step"),
                   "shared_expert": ("stacked behind the routed experts (one slot of the grouped GEMMs)"
-                                    if (nvfp4 and world == 1 and not a.no_fold and cfg.shared_ff) else "dense FFN"),
+                                    if (nvfp4 and world == 1 and not a.no_fold and cfg.shared_ff) else
+                                    ("whole on rank (layer % world), stacked behind that rank's routed experts"
+                                     if (shard is not None and shard.shared_whole) else "dense FFN")),
                   "region": f"median of {len(reps)} regions of {K} steps; min / max per row"})
     out = {
         "metric": f"decode tok/s @{a.users} users ({L}-token prompts), device-timed",

@@ -433,7 +433,7 @@ def cmd_ep_place(a):
 
 def cmd_completions(a):
     subs = ["serve", "run", "bench", "chat", "top", "gguf", "st", "info", "tokenize", "ep-place", "completions",
-            "kernel-bench"]
+            "kernel-bench", "comm-bench"]
     if a.shell == "bash":
         print("complete -W '" + " ".join(subs) + "' legion")
     else:
@@ -450,6 +450,17 @@ def cmd_kernel_bench(a):
     from ..bench.kernels import main as kmain
     argv = ["--only", a.only] + (["--json", a.json] if a.json else [])
     return kmain(argv)
+
+
+def cmd_comm_bench(a):
+    """One process per GPU under ``torch.distributed.run`` (the communication kernels need their peers)."""
+    import subprocess
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(a.gpus),
+           "--master-addr", "127.0.0.1", "--master-port", str(a.port), "-m", "legion_b200.bench.comm",
+           "--hidden", str(a.hidden), "--rows", a.rows, "--iters", str(a.iters)]
+    if a.json:
+        cmd += ["--json", a.json]
+    return subprocess.call(cmd)
 
 
 def make_parser() -> argparse.ArgumentParser:
@@ -537,6 +548,14 @@ def make_parser() -> argparse.ArgumentParser:
     s.add_argument("--only", default="gemm,moe,decode_attn,prefill_attn")
     s.add_argument("--json")
     s.set_defaults(fn=cmd_kernel_bench)
+    s = sub.add_parser("comm-bench", help="device-timed fused all-reduce / all-gather kernels against NCCL")
+    s.add_argument("--gpus", type=int, default=2)
+    s.add_argument("--hidden", type=int, default=2048)
+    s.add_argument("--rows", default="16,64,2048")
+    s.add_argument("--iters", type=int, default=20)
+    s.add_argument("--port", type=int, default=29533)
+    s.add_argument("--json")
+    s.set_defaults(fn=cmd_comm_bench)
     return ap
 
 

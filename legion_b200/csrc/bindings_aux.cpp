@@ -138,9 +138,34 @@ void bind_comm(pybind11::module_& m) {
   m.def("all_reduce_fused", [](std::vector<int64_t> buffers, std::vector<int64_t> signals, int64_t rank,
                                int64_t buf_off, int64_t slot_base, Tensor& seq, Tensor& done_ctr, int64_t T, int64_t H,
                                const OptT& residual, Tensor& sum_out, const OptT& norm_w, double eps, double w_offset,
-                               const OptT& norm_out, int64_t budget_ns, Tensor& status) {
+                               const OptT& norm_out, int64_t budget_ns, Tensor& status, const OptT& q_codes,
+                               const OptT& q_sf, const OptT& q_gscale, int64_t ll_off, int64_t ll_rows) {
     c10::cuda::CUDAGuard guard(status.device());
     auto p = make_peers(buffers, signals, rank);
+    lb::Nv4RowsOut q{};
+    if (q_codes.has_value()) {
+      TORCH_CHECK(q_sf.has_value() && q_gscale.has_value() && q_codes->dim() == 2 && q_codes->stride(1) == 1 &&
+                      q_codes->size(0) >= T && q_codes->size(1) * 2 == H && q_sf->is_contiguous() &&
+                      size_t(q_sf->numel()) >= lb::nv4_sf_bytes(T, H) && q_gscale->numel() >= T,
+                  "all_reduce_fused: encoded rows need codes [T, H / 2], scale atoms and one scale per row");
+      q.codes = reinterpret_cast<uint8_t*>(q_codes->data_ptr()); q.ld = q_codes->stride(0);
+      q.sf = reinterpret_cast<uint8_t*>(q_sf->data_ptr()); q.row_gscale = q_gscale->data_ptr<float>();
+      q.k4 = lb::nv4_sf_k4(H);
+    }
+    if (ll_rows > 0) {
+      // pushed flag-carrying lines: one NVLink crossing
+      TORCH_CHECK(lb::all_reduce_ll_launch(
+                      p, buf_off, ll_off, int(ll_rows), reinterpret_cast<uint32_t*>(seq.data_ptr()),
+                      reinterpret_cast<unsigned int*>(done_ctr.data_ptr()), int(T), int(H),
+                      residual.has_value() ? residual->data_ptr() : nullptr,
+                      residual.has_value() ? residual->stride(0) : 0, sum_out.data_ptr(), sum_out.stride(0),
+                      optp<float>(norm_w), float(eps), float(w_offset),
+                      norm_out.has_value() ? norm_out->data_ptr() : nullptr,
+                      norm_out.has_value() ? norm_out->stride(0) : 0, uint64_t(budget_ns),
+                      reinterpret_cast<int*>(status.data_ptr()), cur_stream(), q) == 0,
+                  "all_reduce (pushed lines) failed");
+      return;
+    }
     TORCH_CHECK(lb::all_reduce_fused_launch(
                     p, buf_off, int(slot_base), reinterpret_cast<uint32_t*>(seq.data_ptr()),
                     reinterpret_cast<unsigned int*>(done_ctr.data_ptr()), int(T), int(H),
@@ -149,7 +174,7 @@ void bind_comm(pybind11::module_& m) {
                     optp<float>(norm_w), float(eps), float(w_offset),
                     norm_out.has_value() ? norm_out->data_ptr() : nullptr,
                     norm_out.has_value() ? norm_out->stride(0) : 0, uint64_t(budget_ns),
-                    reinterpret_cast<int*>(status.data_ptr()), cur_stream()) == 0,
+                    reinterpret_cast<int*>(status.data_ptr()), cur_stream(), q) == 0,
                 "all_reduce_fused failed");
   });
   m.def("reduce_scatter_fused", [](std::vector<int64_t> buffers, std::vector<int64_t> signals, int64_t rank,

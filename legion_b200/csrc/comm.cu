@@ -94,27 +94,109 @@ __global__ void __launch_bounds__(256) all_reduce_fused_kernel(CommPeers peers, 
                                                                __nv_bfloat16* __restrict__ sum_out, long lds,
                                                                const float* __restrict__ norm_w, float eps,
                                                                float w_offset, __nv_bfloat16* __restrict__ norm_out,
-                                                               long ldn, uint64_t budget_ns, int* status) {
+                                                               long ldn, uint64_t budget_ns, int* status,
+                                                               const Nv4RowsOut q) {
   __shared__ int s_ok;
   __shared__ float red[32];
   uint32_t seq;
   const bool entered = comm_enter(peers, slot_base, seq_ptr, budget_ns, status, &s_ok, &seq);
   if (!entered) { comm_exit(seq_ptr, done_ctr, seq); return; }
-  reduce_rows_rank_order(peers, buf_off, T, H, residual, ldr, sum_out, lds, norm_w, eps, w_offset, norm_out, ldn, red);
+  reduce_rows_rank_order(peers, buf_off, T, H, residual, ldr, sum_out, lds, norm_w, eps, w_offset, norm_out, ldn, red, q);
   comm_exit(seq_ptr, done_ctr, seq);
 }
 
 int all_reduce_fused_launch(const CommPeers& peers, long buf_off, int slot_base, uint32_t* seq_ptr, unsigned int* done_ctr, int T,
                             int H, const void* residual, long ldr, void* sum_out, long lds, const float* norm_w, float eps,
                             float w_offset, void* norm_out, long ldn, uint64_t budget_ns, int* status,
-                            cudaStream_t s) {
+                            cudaStream_t s, const Nv4RowsOut& q) {
   if (T <= 0) return 0;
   if (H % 8 || peers.world > LB_MAX_RANKS) return 1;
+  if (q.codes && (!norm_out || H % 256 || !q.sf || !q.row_gscale || (q.ld % 4))) return 1;
   const int grid = T < 296 ? T : 296;
   all_reduce_fused_kernel<<<grid, 256, 0, s>>>(peers, buf_off, slot_base, seq_ptr, done_ctr, T, H,
                                                static_cast<const __nv_bfloat16*>(residual), ldr,
                                                static_cast<__nv_bfloat16*>(sum_out), lds, norm_w, eps, w_offset,
-                                               static_cast<__nv_bfloat16*>(norm_out), ldn, budget_ns, status);
+                                               static_cast<__nv_bfloat16*>(norm_out), ldn, budget_ns, status, q);
+  return cudaGetLastError() != cudaSuccess;
+}
+
+// Decode-sized all-reduce with the data pushed, flag and payload in one store (the "low latency" line format:
+// every 8 bytes carry 4 bytes of payload and the 4-byte sequence number, and an 8-byte store arrives whole). Each
+// CTA owns a row: it reads this rank's partial row, stores it as such lines into its region of every peer's
+// staging area, then polls its own staging area until the lines of all peers carry this call's sequence number
+// and sums them in rank order. One NVLink crossing instead of three (flag, load request, load reply), no fences.
+// Two staging areas alternate with the sequence number: a peer can write call n + 2's lines only after it has
+// finished call n + 1, for which it needed this rank's lines of call n + 1, sent after call n was read.
+__device__ __forceinline__ void st_ll(uint4* p, uint32_t a, uint32_t b, uint32_t flag) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(flag), "r"(b), "r"(flag) : "memory");
+}
+__device__ __forceinline__ uint4 ld_ll(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(256) all_reduce_ll_kernel(CommPeers peers, long buf_off, long ll_off, int ll_rows,
+                                                            uint32_t* seq_ptr, unsigned int* done_ctr, int T, int H,
+                                                            const __nv_bfloat16* __restrict__ residual, long ldr,
+                                                            __nv_bfloat16* __restrict__ sum_out, long lds,
+                                                            const float* __restrict__ norm_w, float eps, float w_offset,
+                                                            __nv_bfloat16* __restrict__ norm_out, long ldn,
+                                                            uint64_t budget_ns, int* status, const Nv4RowsOut q) {
+  __shared__ float red[32];
+  griddep_wait();
+  griddep_launch();
+  const uint32_t seq = *reinterpret_cast<const volatile uint32_t*>(seq_ptr) + 1;
+  const int nv = H / 8;
+  const int me = peers.rank, world = peers.world;
+  const long area = long(ll_rows) * H * 4;                       // one source rank's lines: 2 x the payload
+  const long par_off = ll_off + long(seq & 1u) * world * area;
+  const char* mine = reinterpret_cast<const char*>(peers.buffer[me]);
+  // push: this rank's partial rows into region `me` of every peer
+  for (int row = blockIdx.x; row < T; row += gridDim.x) {
+    for (int v = threadIdx.x; v < nv; v += blockDim.x) {
+      const uint4 d = reinterpret_cast<const uint4*>(mine + buf_off + (long(row) * H) * 2)[v];
+      const long line = par_off + me * area + (long(row) * nv + v) * 32;
+      for (int i = 1; i < world; ++i) {
+        const int p = (me + i) % world;
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(peers.buffer[p]) + line);
+        st_ll(dst, d.x, d.y, seq);
+        st_ll(dst + 1, d.z, d.w, seq);
+      }
+    }
+  }
+  auto load = [&](int r, int row, int v) -> uint4 {
+    if (r == me) return reinterpret_cast<const uint4*>(mine + buf_off + (long(row) * H) * 2)[v];
+    const uint4* src = reinterpret_cast<const uint4*>(mine + par_off + r * area + (long(row) * nv + v) * 32);
+    uint64_t t0 = 0;
+    uint32_t spins = 0;
+    while (true) {
+      const uint4 a = ld_ll(src), b = ld_ll(src + 1);
+      if (a.y == seq && a.w == seq && b.y == seq && b.w == seq) return make_uint4(a.x, a.z, b.x, b.z);
+      if ((++spins & 0x3f) == 0) {
+        const uint64_t now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > budget_ns) {
+          atomicCAS(status, 0, ST_TIMEOUT_FLAG);
+          return make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+    }
+  };
+  reduce_rows_with(load, world, T, H, residual, ldr, sum_out, lds, norm_w, eps, w_offset, norm_out, ldn, red, q);
+  comm_exit(seq_ptr, done_ctr, seq);
+}
+
+int all_reduce_ll_launch(const CommPeers& peers, long buf_off, long ll_off, int ll_rows, uint32_t* seq_ptr,
+                         unsigned int* done_ctr, int T, int H, const void* residual, long ldr, void* sum_out, long lds,
+                         const float* norm_w, float eps, float w_offset, void* norm_out, long ldn, uint64_t budget_ns,
+                         int* status, cudaStream_t s, const Nv4RowsOut& q) {
+  if (T <= 0) return 0;
+  if (H % 8 || peers.world > LB_MAX_RANKS || T > ll_rows || (ll_off % 32) || (buf_off % 16)) return 1;
+  if (q.codes && (!norm_out || H % 256 || !q.sf || !q.row_gscale || (q.ld % 4))) return 1;
+  launch_pdl(all_reduce_ll_kernel, dim3(T), dim3(256), 0, s, peers, buf_off, ll_off, ll_rows, seq_ptr, done_ctr, T, H,
+             static_cast<const __nv_bfloat16*>(residual), ldr, static_cast<__nv_bfloat16*>(sum_out), lds, norm_w, eps,
+             w_offset, static_cast<__nv_bfloat16*>(norm_out), ldn, budget_ns, status, q);
   return cudaGetLastError() != cudaSuccess;
 }
 

@@ -14,6 +14,16 @@ struct CommPeers {
   int rank, world;
 };
 
+// Optional NVFP4 copy of the normalised rows a reduction kernel produces: codes [rows, H / 2] with pitch ld, scale
+// atoms (k4 = atoms per 128 rows), one fp32 scale per row. codes == nullptr: none.
+struct Nv4RowsOut {
+  uint8_t* codes = nullptr;
+  long ld = 0;
+  uint8_t* sf = nullptr;
+  float* row_gscale = nullptr;
+  int k4 = 0;
+};
+
 int wait_flag_launch(const uint32_t* flag, uint32_t want, uint64_t budget_ns, int* status, cudaStream_t s);
 int barrier_launch(const CommPeers& peers, int slot_base, uint32_t seq, uint64_t budget_ns, int* status,
                    cudaStream_t s);
@@ -21,7 +31,13 @@ int all_reduce_fused_launch(const CommPeers& peers, long buf_off, int slot_base,
                             unsigned int* done_ctr, int T, int H,
                             const void* residual, long ldr, void* sum_out, long lds, const float* norm_w, float eps,
                             float w_offset, void* norm_out, long ldn, uint64_t budget_ns, int* status,
-                            cudaStream_t s);
+                            cudaStream_t s, const Nv4RowsOut& q = Nv4RowsOut{});
+// Decode-sized one-shot all-reduce with pushed flag-carrying lines (see comm.cu). ll_off: byte offset of the staging
+// areas inside every rank's symmetric buffer, 2 (alternating) x world x ll_rows x H x 4 bytes, zero before first use.
+int all_reduce_ll_launch(const CommPeers& peers, long buf_off, long ll_off, int ll_rows, uint32_t* seq_ptr,
+                         unsigned int* done_ctr, int T, int H, const void* residual, long ldr, void* sum_out, long lds,
+                         const float* norm_w, float eps, float w_offset, void* norm_out, long ldn, uint64_t budget_ns,
+                         int* status, cudaStream_t s, const Nv4RowsOut& q = Nv4RowsOut{});
 int reduce_scatter_launch(const CommPeers& peers, long buf_off, long out_off, int slot_base, uint32_t* seq_ptr,
                           unsigned int* done_ctr, int row0, int n_rows, int H, const void* residual, long ldr, uint64_t budget_ns, int* status,
                           cudaStream_t s);

@@ -4,6 +4,7 @@
 #pragma once
 #include "comm.h"
 #include "common.cuh"
+#include "nvfp4_dev.cuh"
 
 namespace lb {
 
@@ -34,11 +35,13 @@ __device__ __forceinline__ bool wait_flag_geq(const uint32_t* flag, uint32_t wan
 // Rows [blockIdx.x, T) step gridDim.x of sum_r partial_r (+ residual), summed in rank order over peer loads (same
 // bits on every rank), optionally followed by RMSNorm of the summed row. `red` is >= 32 floats of shared memory.
 // Every thread of the block must call it (block-wide barriers inside).
-__device__ __forceinline__ void reduce_rows_rank_order(const CommPeers& peers, long buf_off, int T, int H,
+template <class Load>
+__device__ __forceinline__ void reduce_rows_with(const Load& load, int world, int T, int H,
                                                        const __nv_bfloat16* __restrict__ residual, long ldr,
                                                        __nv_bfloat16* __restrict__ sum_out, long lds,
                                                        const float* __restrict__ norm_w, float eps, float w_offset,
-                                                       __nv_bfloat16* __restrict__ norm_out, long ldn, float* red) {
+                                                       __nv_bfloat16* __restrict__ norm_out, long ldn, float* red,
+                                                       const Nv4RowsOut q = Nv4RowsOut{}) {
   const int nv = H / 8;
   const int nthr = blockDim.x, nwarp = (blockDim.x + 31) >> 5;
   for (int row = blockIdx.x; row < T; row += gridDim.x) {
@@ -47,9 +50,8 @@ __device__ __forceinline__ void reduce_rows_rank_order(const CommPeers& peers, l
       float acc[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-      for (int r = 0; r < peers.world; ++r) {
-        const uint4 u = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(peers.buffer[r]) + buf_off +
-                                                       (long(row) * H) * 2)[v];
+      for (int r = 0; r < world; ++r) {
+        const uint4 u = load(r, row, v);
         const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -86,6 +88,7 @@ __device__ __forceinline__ void reduce_rows_rank_order(const CommPeers& peers, l
       float tot = 0.f;
       for (int i = 0; i < nwarp; ++i) tot += red[i];
       const float inv = rsqrtf(tot / float(H) + eps);
+      float amax = 0.f;
       for (int v = threadIdx.x; v < nv; v += nthr) {
         uint4 u = reinterpret_cast<const uint4*>(sum_out + long(row) * lds)[v];  // written by this thread above
         __nv_bfloat162* u2 = reinterpret_cast<__nv_bfloat162*>(&u);
@@ -94,12 +97,53 @@ __device__ __forceinline__ void reduce_rows_rank_order(const CommPeers& peers, l
           const float2 f = __bfloat1622float2(u2[j]);
           u2[j] = __floats2bfloat162_rn(f.x * inv * (norm_w[v * 8 + 2 * j] + w_offset),
                                         f.y * inv * (norm_w[v * 8 + 2 * j + 1] + w_offset));
+          const float2 g = __bfloat1622float2(u2[j]);
+          amax = fmaxf(amax, fmaxf(fabsf(g.x), fabsf(g.y)));
         }
         reinterpret_cast<uint4*>(norm_out + long(row) * ldn)[v] = u;
       }
       __syncthreads();
+      if (q.codes) {
+        // the normalised row once more as NVFP4 (row scale amax / (6 * 448), one UE4M3 scale per 16 values): the
+        // expert GEMMs read this, the router reads the bf16 row
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+        __syncthreads();
+        float m = 0.f;
+        for (int i = 0; i < nwarp; ++i) m = fmaxf(m, red[i]);
+        const float gs = fmaxf(m / (6.f * 448.f), 1e-12f);
+        if (threadIdx.x == 0) q.row_gscale[row] = gs;
+        for (int v = threadIdx.x; v < nv; v += nthr) {
+          const uint4 u = reinterpret_cast<const uint4*>(norm_out + long(row) * ldn)[v];   // this thread's own write
+          const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+          float f8[8];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(u2[j]);
+            f8[2 * j] = f.x;
+            f8[2 * j + 1] = f.y;
+          }
+          const uint32_t c = nv4_encode8_pair(f8, gs, q.sf, row, v * 8, q.k4, true);
+          *reinterpret_cast<uint32_t*>(q.codes + long(row) * q.ld + v * 4) = c;
+        }
+        __syncthreads();
+      }
     }
   }
+}
+
+// The plain form: rank r's vector is a peer load from its partial rows at buf_off of its symmetric buffer.
+__device__ __forceinline__ void reduce_rows_rank_order(const CommPeers& peers, long buf_off, int T, int H,
+                                                       const __nv_bfloat16* __restrict__ residual, long ldr,
+                                                       __nv_bfloat16* __restrict__ sum_out, long lds,
+                                                       const float* __restrict__ norm_w, float eps, float w_offset,
+                                                       __nv_bfloat16* __restrict__ norm_out, long ldn, float* red,
+                                                       const Nv4RowsOut q = Nv4RowsOut{}) {
+  auto load = [&](int r, int row, int v) {
+    return reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(peers.buffer[r]) + buf_off + (long(row) * H) * 2)[v];
+  };
+  reduce_rows_with(load, peers.world, T, H, residual, ldr, sum_out, lds, norm_w, eps, w_offset, norm_out, ldn, red, q);
 }
 
 }  // namespace lb

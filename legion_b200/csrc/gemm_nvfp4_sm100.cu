@@ -24,6 +24,7 @@
 
 #include "common.cuh"
 #include "gemm_nvfp4_sm100.h"
+#include "nvfp4_dev.cuh"
 #include "tmap.cuh"
 
 namespace lb {
@@ -126,29 +127,6 @@ __device__ __forceinline__ void umma_nvf4(uint32_t d_tmem, uint64_t adesc, uint6
 // Instruction descriptor: e2m1 x e2m1, UE4M3 scales, K-major operands, fp32 accumulate, K = 64.
 __host__ __device__ constexpr uint32_t nvf4_idesc(uint32_t M, uint32_t N) {
   return (1u << 7) | (1u << 10) | ((N >> 3) << 17) | ((M >> 4) << 24);
-}
-
-__device__ __forceinline__ float e4m3_dec(uint32_t b) {
-  __nv_fp8_e4m3 v;
-  v.__x = uint8_t(b);
-  return float(v);
-}
-__device__ __forceinline__ uint32_t e4m3_enc(float f) {
-  __nv_fp8_e4m3 v(f);
-  return v.__x;
-}
-// two floats -> one byte of e2m1 codes (lo in the low nibble), round to nearest even, saturating
-__device__ __forceinline__ uint32_t e2m1x2(float lo, float hi) {
-  uint32_t o;
-  asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u32.u8 %0, t;\n\t}" : "=r"(o) : "f"(hi), "f"(lo));
-  return o;
-}
-__device__ __forceinline__ uint32_t pack_e2m1x8(const float (&v)[8], float inv) {
-  return e2m1x2(v[0] * inv, v[1] * inv) | (e2m1x2(v[2] * inv, v[3] * inv) << 8) |
-         (e2m1x2(v[4] * inv, v[5] * inv) << 16) | (e2m1x2(v[6] * inv, v[7] * inv) << 24);
-}
-__device__ __forceinline__ long sf_atom_byte(long row, int blk16, int k4) {
-  return ((row >> 7) * k4 + (blk16 >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (blk16 & 3);
 }
 
 template <int BN, bool DUAL, bool QOUT, int FT, int NCTA>

@@ -166,6 +166,18 @@ def fold_shared_expert(w: Dict[str, object], p: str, cfg: ModelConfig) -> bool:
     return True
 
 
+def place_shared_expert(w: Dict[str, object], p: str, il: int, cfg: ModelConfig, rank: int, world: int) -> bool:
+    """Several ranks with whole (unsliced) shared experts: rank ``il % world`` keeps the shared expert of layer
+    ``il`` and stacks it behind its local routed experts (``fold_shared_expert``); the other ranks drop it, so the
+    layer's reduction sums exactly one copy. Returns whether this rank keeps it."""
+    if world <= 1 or il % world == rank:
+        fold_shared_expert(w, p, cfg)
+        return True
+    for k in ("sh_gate_up", "sh_down", "sh_gate"):
+        w.pop(f"{p}.moe.{k}", None)
+    return False
+
+
 def quantize_moe_layer_nvfp4(w: Dict[str, object], p: str, native: bool = True) -> int:
     """NVFP4-encodes the expert tensors of MoE layer ``p`` in place (stacked form when the shared expert was
     folded in, else the routed experts and the shared expert separately). Returns the bytes saved."""
@@ -498,7 +510,7 @@ class Decoder:
             ids, wts = routing
             shared = gate = None
             folded = bool(getattr(routing, "shared_slot", False))
-            if cfg.shared_ff > 0 and not folded:
+            if cfg.shared_ff > 0 and not folded and w.get(f"{p}.moe.sh_down") is not None:
                 fs = w[f"{p}.moe.sh_down"].shape[1]
                 hs = ops.gate_up_act(x, w[f"{p}.moe.sh_gate_up"], fs, cfg.ffn_act)
                 shared = ops.linear(hs, w[f"{p}.moe.sh_down"])
@@ -550,11 +562,17 @@ class Decoder:
             raise ValueError(kind)
         routing = None
         nv4_decode = False
-        if moe and isinstance(a, PendingLinear) and resid is not None and a.x.is_cuda and a.x.shape[0] <= 64 \
-                and pc.world == 1 and self.expert_cache.get(p) is None:
+        a_rows = a.x if isinstance(a, PendingLinear) else a
+        if moe and resid is not None and a_rows.is_cuda and a_rows.shape[0] <= 64 and self.expert_cache.get(p) is None \
+                and (isinstance(a, PendingLinear) or pc.world > 1):
             wg = w.get(f"{p}.moe.gate_up_s")
             nv4_decode = isinstance(wg if wg is not None else w.get(f"{p}.moe.gate_up"), ops.sm100.Nv4Weight)
-        if nv4_decode:
+        if nv4_decode and pc.world > 1:
+            # several ranks: the reduction launch adds the residual, applies the FFN norm and encodes the rows
+            h, resid, xq = pc.reduce_norm_quant(a, resid, w[f"{p}.ffn_norm"], cfg.rms_eps, cfg.norm_offset)
+            routing = self._route(p, h)
+            routing.xq = xq
+        elif nv4_decode:
             # decode-sized step on NVFP4 experts: one launch adds the residual, applies the FFN norm and encodes the
             # normalised rows for the expert GEMMs; the router reads the bf16 copy
             att = ops.linear(a.x, a.w)

@@ -169,8 +169,11 @@ class Shard:
     """Tensor-parallel (attention / dense FFN / shared expert) and expert-parallel slicing of weights."""
 
     def __init__(self, cfg: ModelConfig, rank: int, world: int, expert_parallel: bool = False,
-                 dp_attention: bool = False):
+                 dp_attention: bool = False, shared_whole: bool = False):
         self.cfg, self.rank, self.world, self.ep = cfg, rank, world, expert_parallel or dp_attention
+        # the shared expert is not sliced: every rank gets it whole, so that one rank per layer can run it as one
+        # more slot of its grouped expert GEMMs (models.decoder.place_shared_expert) and the others drop it
+        self.shared_whole = shared_whole
         self.dp_attention = dp_attention     # only the routed experts are split; everything else is whole
         if dp_attention:
             self.kv_rep = 1
@@ -217,6 +220,8 @@ class Shard:
         if leaf == "attn.o":
             per = shape[1] // w
             return [(1, torch.arange(r * per, (r + 1) * per))]
+        if self.shared_whole and leaf in ("moe.sh_gate_up", "moe.sh_down"):
+            return None
         if leaf in ("mlp.gate_up", "moe.sh_gate_up"):
             F = shape[0] // 2 if cfg.ffn_act != "relu2" else shape[0]
             per = F // w

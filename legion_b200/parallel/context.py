@@ -100,6 +100,18 @@ class ParallelCtx:
         if self.comm == "fused" and self.symm is not None:
             self.symm.end_step()
 
+    def reduce_norm_quant(self, cur, res, w, eps, w_offset):
+        """``reduce_norm`` of a decode-sized step whose consumer is an NVFP4 expert block: returns (normed, hidden,
+        encoded rows). With the fused communicator the encoding comes out of the reduction launch itself."""
+        cur = self._materialize(cur)
+        if (self.world > 1 and self.comm == "fused" and cur is not None and res is not None and cur.is_cuda
+                and self.symm.owns(cur) and cur.shape[1] % 256 == 0):
+            self.stats["all_reduce"] += 1
+            self.stats["bytes"] += cur.numel() * cur.element_size()
+            return self.symm.all_reduce_add_norm(cur, res, w, eps, w_offset, quant=True)
+        normed, hidden = self.reduce_norm(cur, res, w, eps, w_offset)
+        return normed, hidden, ops.sm100.nv4_quant_act(normed, key="ffn_in")
+
     def reduce_norm(self, cur, res, w, eps, w_offset):
         """hidden = reduce(cur) + res; returns (rmsnorm(hidden) * w, hidden).
 

@@ -31,6 +31,7 @@ class CommError(RuntimeError):
 class SymmComm:
     N_SLOTS = 2
     TWO_SHOT_ROWS = 512
+    LL_ROWS = 64          # decode-sized reductions push flag-carrying lines instead of exchanging flags and loading
 
     def __init__(self, group, rank: int, world: int, device: torch.device, max_rows: int, hidden: int,
                  budget_ns: int = 5_000_000_000):
@@ -45,7 +46,8 @@ class SymmComm:
         self.rs_off = self.N_SLOTS * self.slot_bytes
         self.ag_off = (self.rs_off + self.slot_bytes, self.rs_off + 2 * self.slot_bytes)
         self._ag_half = 0
-        nbytes = self.slot_bytes * (self.N_SLOTS + 3)
+        self.ll_off = self.slot_bytes * (self.N_SLOTS + 3)
+        nbytes = self.ll_off + 2 * world * self.LL_ROWS * hidden * 4
         self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
         self.handle = symm_mem.rendezvous(self.buf, group=group)
         self.buffer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
@@ -81,8 +83,9 @@ class SymmComm:
         self._calls_in_step += 1
 
     # ------------------------------------------------------------------ collectives
-    def all_reduce_add_norm(self, cur, res, w, eps, w_offset):
-        """cur must live in the current slot. Returns (normed, summed)."""
+    def all_reduce_add_norm(self, cur, res, w, eps, w_offset, quant: bool = False):
+        """cur must live in the current slot. Returns (normed, summed); with ``quant`` (decode-sized steps, a norm
+        given) also the normalised rows NVFP4-encoded (``ops.sm100.Nv4Act``) out of the same launch."""
         if self._failed:
             raise CommError(self._failed)
         T, H = cur.shape
@@ -105,11 +108,26 @@ class SymmComm:
             if w is not None:
                 from ..ops import sm100
                 normed, _ = sm100.rmsnorm(summed, w, eps, w_offset)
+            if quant:
+                from ..ops import sm100
+                return normed, summed, sm100.nv4_quant_act(normed, key="ffn_in")
             return normed, summed
         normed = torch.empty_like(summed) if w is not None else None
+        qc = qs = qg = None
+        if quant:
+            from ..ops import sm100
+            C = ext()
+            ws = sm100.Workspace.get(self.device)
+            qc = ws.buf(("ar_q", "c"), (T, H // 2), torch.uint8)
+            qs = ws.buf(("ar_q", "s"), (C.nv4_sf_bytes(T, H),), torch.uint8)
+            qg = ws.buf(("ar_q", "g"), (max(T, 1),), torch.float32)
+        from ..ops.sm100 import TUNE
+        ll = self.LL_ROWS if (T <= self.LL_ROWS and H == self.hidden and TUNE.get("ar_ll", 1)) else 0
         ext().all_reduce_fused(self.buffer_ptrs, self.signal_ptrs, self.rank, off, 0, self.seq, self.done, T, H, res,
-                               summed, w, eps, w_offset, normed, self.budget_ns, self.status)
+                               summed, w, eps, w_offset, normed, self.budget_ns, self.status, qc, qs, qg, self.ll_off, ll)
         self._advance()
+        if quant:
+            return normed, summed, sm100.Nv4Act(qc, qs, qg, 1, normed, summed)
         return normed, summed
 
     def fits_gemm_tail(self, rows: int, cols: int) -> bool:

@@ -51,6 +51,22 @@ def case_comm(dev):
         dist.all_gather(gathered, summed)
         assert all(torch.equal(g, gathered[0]) for g in gathered)
         say("rows", T, "ok")
+    # decode-sized reduction that also emits the normalised rows NVFP4-encoded: same codes, scale bytes and row
+    # scales as the stand-alone quantiser gives for the normalised rows
+    for T in (3, 16, 64):
+        parts = [(torch.randn(T, H, device=dev) * 0.5).bfloat16() for _ in range(WORLD)]
+        res = torch.randn(T, H, device=dev).bfloat16()
+        w = torch.rand(H, device=dev) + 0.5
+        slot = comm.next_partial(T, H)
+        slot.copy_(parts[RANK])
+        normed, summed, xq = comm.all_reduce_add_norm(slot, res, w, 1e-6, 0.0, quant=True)
+        total = sum(p.float() for p in parts) + res.float()
+        errs.append(float((summed.float() - total).abs().max()))
+        rq = sm100.nv4_quant_act(normed)
+        assert torch.equal(xq.codes[:T], rq.codes) and torch.equal(xq.gscale[:T], rq.gscale[:T])
+        assert torch.equal(xq.dequantize(), rq.dequantize())
+        comm.check()
+        say("quantising reduction rows", T, "ok")
     # GEMM epilogue writes straight into the slot, then the fused reduction
     x = (torch.randn(24, 256, device=dev) * 0.3).bfloat16()
     wts = [(torch.randn(H, 256, device=dev) * 0.05).bfloat16() for _ in range(WORLD)]
