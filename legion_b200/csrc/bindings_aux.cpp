@@ -139,7 +139,9 @@ void bind_comm(pybind11::module_& m) {
                                int64_t buf_off, int64_t slot_base, Tensor& seq, Tensor& done_ctr, int64_t T, int64_t H,
                                const OptT& residual, Tensor& sum_out, const OptT& norm_w, double eps, double w_offset,
                                const OptT& norm_out, int64_t budget_ns, Tensor& status, const OptT& q_codes,
-                               const OptT& q_sf, const OptT& q_gscale, int64_t ll_off, int64_t ll_rows) {
+                               const OptT& q_sf, const OptT& q_gscale, int64_t ll_off, int64_t ll_rows,
+                               const OptT& cmb_y, const OptT& cmb_ids, int64_t cmb_e_lo, int64_t cmb_e_hi,
+                               const OptT& cmb_shared) {
     c10::cuda::CUDAGuard guard(status.device());
     auto p = make_peers(buffers, signals, rank);
     lb::Nv4RowsOut q{};
@@ -152,6 +154,20 @@ void bind_comm(pybind11::module_& m) {
       q.sf = reinterpret_cast<uint8_t*>(q_sf->data_ptr()); q.row_gscale = q_gscale->data_ptr<float>();
       q.k4 = lb::nv4_sf_k4(H);
     }
+    lb::CombineSrc cs{};
+    if (cmb_y.has_value()) {
+      TORCH_CHECK(ll_rows > 0 && cmb_ids.has_value() && cmb_ids->dim() == 2 && cmb_ids->is_contiguous() &&
+                      cmb_ids->size(0) >= T && cmb_y->scalar_type() == at::kBFloat16 && cmb_y->stride(1) == 1 &&
+                      cmb_y->size(0) >= T * cmb_ids->size(1) && cmb_y->size(1) == H,
+                  "all_reduce_fused: the combine source needs pair rows [T * k, H] and ids [T, k] (decode sizes)");
+      cs.y = cmb_y->data_ptr(); cs.ldy = cmb_y->stride(0); cs.ids = cmb_ids->data_ptr<int>();
+      cs.k = int(cmb_ids->size(1)); cs.e_lo = int(cmb_e_lo); cs.e_hi = int(cmb_e_hi);
+      if (cmb_shared.has_value()) {
+        TORCH_CHECK(cmb_shared->scalar_type() == at::kBFloat16 && cmb_shared->stride(1) == 1 && cmb_shared->size(0) >= T,
+                    "all_reduce_fused: shared rows [T, H] bf16");
+        cs.shared = cmb_shared->data_ptr(); cs.lds = cmb_shared->stride(0);
+      }
+    }
     if (ll_rows > 0) {
       // pushed flag-carrying lines: one NVLink crossing
       TORCH_CHECK(lb::all_reduce_ll_launch(
@@ -162,7 +178,7 @@ void bind_comm(pybind11::module_& m) {
                       optp<float>(norm_w), float(eps), float(w_offset),
                       norm_out.has_value() ? norm_out->data_ptr() : nullptr,
                       norm_out.has_value() ? norm_out->stride(0) : 0, uint64_t(budget_ns),
-                      reinterpret_cast<int*>(status.data_ptr()), cur_stream(), q) == 0,
+                      reinterpret_cast<int*>(status.data_ptr()), cur_stream(), q, cs) == 0,
                   "all_reduce (pushed lines) failed");
       return;
     }

@@ -142,8 +142,10 @@ __global__ void __launch_bounds__(256) all_reduce_ll_kernel(CommPeers peers, lon
                                                             __nv_bfloat16* __restrict__ sum_out, long lds,
                                                             const float* __restrict__ norm_w, float eps, float w_offset,
                                                             __nv_bfloat16* __restrict__ norm_out, long ldn,
-                                                            uint64_t budget_ns, int* status, const Nv4RowsOut q) {
+                                                            uint64_t budget_ns, int* status, const Nv4RowsOut q,
+                                                            const CombineSrc cs) {
   __shared__ float red[32];
+  __shared__ int s_on[32];
   griddep_wait();
   griddep_launch();
   const uint32_t seq = *reinterpret_cast<const volatile uint32_t*>(seq_ptr) + 1;
@@ -154,8 +156,58 @@ __global__ void __launch_bounds__(256) all_reduce_ll_kernel(CommPeers peers, lon
   const char* mine = reinterpret_cast<const char*>(peers.buffer[me]);
   // push: this rank's partial rows into region `me` of every peer
   for (int row = blockIdx.x; row < T; row += gridDim.x) {
+    if (cs.y) {
+      __syncthreads();
+      if (threadIdx.x < cs.k) {
+        const int e = cs.ids[long(row) * cs.k + threadIdx.x];
+        s_on[threadIdx.x] = (e >= cs.e_lo && e < cs.e_hi);
+      }
+      __syncthreads();
+    }
     for (int v = threadIdx.x; v < nv; v += blockDim.x) {
-      const uint4 d = reinterpret_cast<const uint4*>(mine + buf_off + (long(row) * H) * 2)[v];
+      uint4 d;
+      if (cs.y) {
+        // this rank's partial row = its experts' weighted rows of the token, in choice order, + the shared expert's
+        const __nv_bfloat16* y = static_cast<const __nv_bfloat16*>(cs.y);
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int c0 = 0; c0 < cs.k; c0 += 4) {
+          uint4 u[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            u[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (c0 + i < cs.k && s_on[c0 + i]) u[i] = reinterpret_cast<const uint4*>(y + (long(row) * cs.k + c0 + i) * cs.ldy)[v];
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u[i]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = __bfloat1622float2(u2[j]);
+              acc[2 * j] += f.x;
+              acc[2 * j + 1] += f.y;
+            }
+          }
+        }
+        if (cs.shared) {
+          const uint4 u = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(cs.shared) + long(row) * cs.lds)[v];
+          const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(u2[j]);
+            acc[2 * j] += f.x;
+            acc[2 * j + 1] += f.y;
+          }
+        }
+        __nv_bfloat162* d2 = reinterpret_cast<__nv_bfloat162*>(&d);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) d2[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        // kept in the slot for this thread's own read in the rank-ordered sum below
+        reinterpret_cast<uint4*>(const_cast<char*>(mine) + buf_off + (long(row) * H) * 2)[v] = d;
+      } else {
+        d = reinterpret_cast<const uint4*>(mine + buf_off + (long(row) * H) * 2)[v];
+      }
       const long line = par_off + me * area + (long(row) * nv + v) * 32;
       for (int i = 1; i < world; ++i) {
         const int p = (me + i) % world;
@@ -190,13 +242,14 @@ __global__ void __launch_bounds__(256) all_reduce_ll_kernel(CommPeers peers, lon
 int all_reduce_ll_launch(const CommPeers& peers, long buf_off, long ll_off, int ll_rows, uint32_t* seq_ptr,
                          unsigned int* done_ctr, int T, int H, const void* residual, long ldr, void* sum_out, long lds,
                          const float* norm_w, float eps, float w_offset, void* norm_out, long ldn, uint64_t budget_ns,
-                         int* status, cudaStream_t s, const Nv4RowsOut& q) {
+                         int* status, cudaStream_t s, const Nv4RowsOut& q, const CombineSrc& cs) {
   if (T <= 0) return 0;
   if (H % 8 || peers.world > LB_MAX_RANKS || T > ll_rows || (ll_off % 32) || (buf_off % 16)) return 1;
+  if (cs.y && (cs.k <= 0 || cs.k > 32 || !cs.ids || (cs.ldy % 8) || (cs.shared && cs.lds % 8))) return 1;
   if (q.codes && (!norm_out || H % 256 || !q.sf || !q.row_gscale || (q.ld % 4))) return 1;
   launch_pdl(all_reduce_ll_kernel, dim3(T), dim3(256), 0, s, peers, buf_off, ll_off, ll_rows, seq_ptr, done_ctr, T, H,
              static_cast<const __nv_bfloat16*>(residual), ldr, static_cast<__nv_bfloat16*>(sum_out), lds, norm_w, eps,
-             w_offset, static_cast<__nv_bfloat16*>(norm_out), ldn, budget_ns, status, q);
+             w_offset, static_cast<__nv_bfloat16*>(norm_out), ldn, budget_ns, status, q, cs);
   return cudaGetLastError() != cudaSuccess;
 }
 

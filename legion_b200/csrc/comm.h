@@ -24,6 +24,18 @@ struct Nv4RowsOut {
   int k4 = 0;
 };
 
+// Optional producer of this rank's partial rows inside the decode-sized reduction: the weighted expert outputs of
+// a MoE layer (one row per (token, choice) pair, rows of experts outside [e_lo, e_hi) skipped, plus one shared-expert
+// row per token) are summed per token there instead of by a combine launch of their own. y == nullptr: none.
+struct CombineSrc {
+  const void* y = nullptr;
+  long ldy = 0;
+  const int* ids = nullptr;
+  int k = 0, e_lo = 0, e_hi = 0;
+  const void* shared = nullptr;
+  long lds = 0;
+};
+
 int wait_flag_launch(const uint32_t* flag, uint32_t want, uint64_t budget_ns, int* status, cudaStream_t s);
 int barrier_launch(const CommPeers& peers, int slot_base, uint32_t seq, uint64_t budget_ns, int* status,
                    cudaStream_t s);
@@ -37,7 +49,8 @@ int all_reduce_fused_launch(const CommPeers& peers, long buf_off, int slot_base,
 int all_reduce_ll_launch(const CommPeers& peers, long buf_off, long ll_off, int ll_rows, uint32_t* seq_ptr,
                          unsigned int* done_ctr, int T, int H, const void* residual, long ldr, void* sum_out, long lds,
                          const float* norm_w, float eps, float w_offset, void* norm_out, long ldn, uint64_t budget_ns,
-                         int* status, cudaStream_t s, const Nv4RowsOut& q = Nv4RowsOut{});
+                         int* status, cudaStream_t s, const Nv4RowsOut& q = Nv4RowsOut{},
+                         const CombineSrc& cs = CombineSrc{});
 int reduce_scatter_launch(const CommPeers& peers, long buf_off, long out_off, int slot_base, uint32_t* seq_ptr,
                           unsigned int* done_ctr, int row0, int n_rows, int H, const void* residual, long ldr, uint64_t budget_ns, int* status,
                           cudaStream_t s);

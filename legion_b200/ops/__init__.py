@@ -101,14 +101,15 @@ def router(x, w_router, k, mode="softmax", renorm=True, route_scale=1.0, bias=No
 
 
 def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, act="silu", e_lo=0, shared=None, shared_gate=None,
-                residual=None, out=None, norm=None, routing=None):
+                residual=None, out=None, norm=None, routing=None, defer_combine=False):
     """Routed experts (+ optional shared-expert output with sigmoid gate logits, + residual). Returns [T, H];
     with ``norm=(weight, eps, w_offset)`` returns (out, rmsnorm(out)): on the GPU the norm rides on the combine."""
     if _cuda(x):
         if act != "silu":
             raise NotImplementedError("grouped expert kernel implements SwiGLU experts")
         return _sm.moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, None, shared, shared_gate, residual, out,
-                               norm, routing if isinstance(routing, _sm.Routing) else None)
+                               norm, routing if isinstance(routing, _sm.Routing) else None,
+                               defer_combine=defer_combine)
     y = _ref.moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, act, e_lo, e_lo + w_gate_up.shape[0])
     if shared is not None:
         s = shared.float()

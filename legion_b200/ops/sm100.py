@@ -856,13 +856,32 @@ def _dense_pairs(dr: DenseRoute, P: int, T: int, k: int, H: int, device):
     return dr.y_pairs
 
 
-def _dense_combine(dr: DenseRoute, routing, ids, e_lo, T, k, H, shared, shared_gate, residual, out, norm, device):
+class PendingCombine:
+    """The weighted pair rows of a decode-sized MoE layer whose per-token sum has not run yet: the rank-partial
+    result of an expert-parallel layer, handed to the reduction that follows so that it sums them inside its own
+    launch (``parallel.symm.SymmComm.all_reduce_add_norm``). ``materialize`` runs the combine kernel instead."""
+    __slots__ = ("y", "ids", "e_lo", "e_hi", "shared", "T", "H")
+
+    def __init__(self, y, ids, e_lo, e_hi, shared, T, H):
+        self.y, self.ids, self.e_lo, self.e_hi, self.shared, self.T, self.H = y, ids, e_lo, e_hi, shared, T, H
+
+    def materialize(self, out=None):
+        if out is None:
+            out = torch.empty(self.T, self.H, dtype=torch.bfloat16, device=self.y.device)
+        ext().moe_combine(self.y, self.ids, self.e_lo, self.e_hi, self.shared, None, None, out, None, 0.0, 0.0, None)
+        return out
+
+
+def _dense_combine(dr: DenseRoute, routing, ids, e_lo, T, k, H, shared, shared_gate, residual, out, norm, device,
+                   defer: bool = False):
     C = ext()
     P = T * k
     y = dr.y_pairs[:P]
     if routing.shared_slot:
         # the shared expert ran as a slot of the grouped GEMMs; its gate is already applied
         shared, shared_gate = dr.y_pairs[P:P + T], None
+    if defer and shared_gate is None and residual is None and norm is None:
+        return PendingCombine(y, ids, e_lo, e_lo + routing.n_local, shared, T, H)
     if out is None:
         out = torch.empty(T, H, dtype=torch.bfloat16, device=device)
     if norm is None:
@@ -875,7 +894,7 @@ def _dense_combine(dr: DenseRoute, routing, ids, e_lo, T, k, H, shared, shared_g
 
 
 def _moe_experts_nv4(x, ids, wts, w_gate_up: "Nv4Weight", w_down: "Nv4Weight", n_ff, e_lo, shared, shared_gate,
-                     residual, out, norm, routing, xq: Optional["Nv4Act"] = None, h_scale=None):
+                     residual, out, norm, routing, xq: Optional["Nv4Act"] = None, h_scale=None, defer: bool = False):
     """Routed experts on the native NVFP4 path (decode-sized steps over the dense routing): the layer input is
     quantised once (or arrives quantised as ``xq``), the gate/up GEMM re-encodes its SwiGLU output to NVFP4 in its
     epilogue (static tensor scale ``h_scale``), and the down GEMM reads that. Three launches + the combine."""
@@ -902,7 +921,7 @@ def _moe_experts_nv4(x, ids, wts, w_gate_up: "Nv4Weight", w_down: "Nv4Weight", n
     C.wgemm_nv4(w_down.view2d(), w_down.sf, w_down.gscale, hq_codes, hq_sf, h_scale, 0, y_pairs, None, dr.tok_scale,
                 dr.out_rows, H, False, 0, 0, dr.bn, ws.status, dr.tile_group, dr.slot_base, dr.tile_ntok, dr.meta,
                 dr.n_slots, H, 0, None, None, None, None)
-    return _dense_combine(dr, routing, ids, e_lo, T, k, H, shared, shared_gate, residual, out, norm, x.device)
+    return _dense_combine(dr, routing, ids, e_lo, T, k, H, shared, shared_gate, residual, out, norm, x.device, defer)
 
 
 class Nv4Plan:
@@ -993,7 +1012,8 @@ NV4_H_AMAX = 32.0
 
 
 def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[MoePlan] = None, shared=None,
-                shared_gate=None, residual=None, out=None, norm=None, routing: Optional[Routing] = None):
+                shared_gate=None, residual=None, out=None, norm=None, routing: Optional[Routing] = None,
+                defer_combine: bool = False):
     """Routed experts over the device routing plan: plan -> gather -> grouped gate/up (+SwiGLU) ->
     grouped down (x routing weight) -> combine (+ shared expert, + residual).
 
@@ -1010,7 +1030,7 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[Moe
     if isinstance(w_gate_up, Nv4Weight):
         if _dense_ok(routing, E_local, e_lo, ids):
             return _moe_experts_nv4(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, shared, shared_gate, residual, out,
-                                    norm, routing, xq=routing.xq)
+                                    norm, routing, xq=routing.xq, defer=defer_combine)
         if TUNE["nv4_sorted"] and T * k >= 64 * E_local and not (routing is not None and routing.shared_slot):
             return _moe_experts_nv4_sorted(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, shared, shared_gate, residual,
                                            out, norm, xq=routing.xq if routing is not None else None)
@@ -1044,7 +1064,8 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[Moe
         C.wgemm(dn2, dr.h_all, y_pairs, None, dr.tok_scale, dr.out_rows, H, False, 0,
                 dr.bn, 1, None, None, ws.status, dr.tile_group, dr.slot_base, dr.tile_ntok, dr.meta, dr.n_slots, H, 0, [],
                 None, dn_sc, dn_gs)
-        return _dense_combine(dr, routing, ids, e_lo, T, k, H, shared, shared_gate, residual, out, norm, x.device)
+        return _dense_combine(dr, routing, ids, e_lo, T, k, H, shared, shared_gate, residual, out, norm, x.device,
+                              defer_combine)
     E_local = n_routed
     if plan is None:
         bn = 32 if T * k <= 32 * E_local else (64 if T * k <= 64 * E_local else 128)

@@ -92,6 +92,8 @@ class ParallelCtx:
         return ops.linear(x, w, out=self.partial_out(rows, cols))
 
     def _materialize(self, cur):
+        if isinstance(cur, ops.sm100.PendingCombine):
+            return cur.materialize(self.partial_out(cur.T, cur.H))
         if isinstance(cur, PendingLinear):
             return ops.linear(cur.x, cur.w, out=self.partial_out(cur.x.shape[0], cur.w.shape[0]))
         return cur
@@ -103,6 +105,11 @@ class ParallelCtx:
     def reduce_norm_quant(self, cur, res, w, eps, w_offset):
         """``reduce_norm`` of a decode-sized step whose consumer is an NVFP4 expert block: returns (normed, hidden,
         encoded rows). With the fused communicator the encoding comes out of the reduction launch itself."""
+        if isinstance(cur, ops.sm100.PendingCombine) and res is not None and self._fused_combine_ok(cur):
+            self.stats["all_reduce"] += 1
+            self.stats["bytes"] += cur.T * cur.H * 2
+            return self.symm.all_reduce_add_norm(self.symm.next_partial(cur.T, cur.H), res, w, eps, w_offset, quant=True,
+                                                 combine=cur)
         cur = self._materialize(cur)
         if (self.world > 1 and self.comm == "fused" and cur is not None and res is not None and cur.is_cuda
                 and self.symm.owns(cur) and cur.shape[1] % 256 == 0):
@@ -120,6 +127,13 @@ class ParallelCtx:
         if cur is None:
             normed, _ = ops.rmsnorm(res, w, eps, w_offset)
             return normed, res
+        if isinstance(cur, ops.sm100.PendingCombine):
+            if res is not None and self._fused_combine_ok(cur):
+                self.stats["all_reduce"] += 1
+                self.stats["bytes"] += cur.T * cur.H * 2
+                return self.symm.all_reduce_add_norm(self.symm.next_partial(cur.T, cur.H), res, w, eps, w_offset,
+                                                     combine=cur)
+            cur = self._materialize(cur)
         if isinstance(cur, PendingLinear) and self.world == 1:
             hidden = ops.linear(cur.x, cur.w, residual=res)
             normed, _ = ops.rmsnorm(hidden, w, eps, w_offset)
@@ -141,6 +155,10 @@ class ParallelCtx:
             cur = self.all_reduce(cur)
         return ops.rmsnorm(cur, w, eps, w_offset, residual=res)
 
+    def _fused_combine_ok(self, pc) -> bool:
+        return (self.world > 1 and self.comm == "fused" and self.symm is not None and pc.T <= self.symm.LL_ROWS
+                and pc.H == self.symm.hidden and bool(ops.sm100.TUNE.get("ar_ll", 1)))
+
     def full_hidden(self, cur, res):
         if isinstance(cur, PendingLinear) and self.world == 1 and res is not None:
             return ops.linear(cur.x, cur.w, residual=res)
@@ -156,9 +174,11 @@ class ParallelCtx:
     def moe(self, x, ids, wts, w_gate_up, w_down, n_ff, act, e_lo, shared, shared_gate, residual, norm=None, routing=None):
         """Routed experts of this rank: all experts with their FFN rows split (TP) or whole local
         experts (EP). Either way the result is a partial sum that the next ``reduce_norm`` completes."""
+        defer = (x.is_cuda and self.world > 1 and self.comm == "fused" and self.symm is not None and residual is None
+                 and norm is None and x.shape[0] <= self.symm.LL_ROWS and bool(ops.sm100.TUNE.get("ar_combine", 1)))
         return ops.moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, act, e_lo, shared, shared_gate, residual,
                                out=self.partial_out(x.shape[0], x.shape[1]) if x.is_cuda else None, norm=norm,
-                               routing=routing)
+                               routing=routing, defer_combine=defer)
 
 
 class DpEpCtx(ParallelCtx):

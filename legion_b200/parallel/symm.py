@@ -83,12 +83,17 @@ class SymmComm:
         self._calls_in_step += 1
 
     # ------------------------------------------------------------------ collectives
-    def all_reduce_add_norm(self, cur, res, w, eps, w_offset, quant: bool = False):
+    def all_reduce_add_norm(self, cur, res, w, eps, w_offset, quant: bool = False, combine=None):
         """cur must live in the current slot. Returns (normed, summed); with ``quant`` (decode-sized steps, a norm
-        given) also the normalised rows NVFP4-encoded (``ops.sm100.Nv4Act``) out of the same launch."""
+        given) also the normalised rows NVFP4-encoded (``ops.sm100.Nv4Act``) out of the same launch. ``combine``
+        (``ops.sm100.PendingCombine``, decode sizes): ``cur`` is the empty current slot and the launch first sums this
+        rank's weighted expert rows per token into it."""
         if self._failed:
             raise CommError(self._failed)
         T, H = cur.shape
+        if combine is not None and not (T <= self.LL_ROWS and H == self.hidden):
+            combine.materialize(cur)
+            combine = None
         off = cur.data_ptr() - self.base
         summed = torch.empty(T, H, dtype=torch.bfloat16, device=self.device)
         if T >= self.TWO_SHOT_ROWS and self.world > 2:
@@ -123,8 +128,14 @@ class SymmComm:
             qg = ws.buf(("ar_q", "g"), (max(T, 1),), torch.float32)
         from ..ops.sm100 import TUNE
         ll = self.LL_ROWS if (T <= self.LL_ROWS and H == self.hidden and TUNE.get("ar_ll", 1)) else 0
+        if combine is not None and not ll:
+            combine.materialize(cur)
+            combine = None
+        cm = combine
         ext().all_reduce_fused(self.buffer_ptrs, self.signal_ptrs, self.rank, off, 0, self.seq, self.done, T, H, res,
-                               summed, w, eps, w_offset, normed, self.budget_ns, self.status, qc, qs, qg, self.ll_off, ll)
+                               summed, w, eps, w_offset, normed, self.budget_ns, self.status, qc, qs, qg, self.ll_off, ll,
+                               cm.y if cm else None, cm.ids if cm else None, cm.e_lo if cm else 0,
+                               cm.e_hi if cm else 0, cm.shared if cm else None)
         self._advance()
         if quant:
             return normed, summed, sm100.Nv4Act(qc, qs, qg, 1, normed, summed)
