@@ -158,7 +158,11 @@ def build_engine_from_args(a, start: bool = True):
         from ..config import PRESETS  # noqa: F401
         pctx = pdist.init_from_env(device, comm="nccl", expert_parallel=a.tp_moe_ep)   # symmetric memory is attached
         # below, once the model's hidden size is known
-    cfg, w, tok, info = load_model(path, device, rank=rank, world=world, expert_parallel=a.tp_moe_ep, seed=a.seed)
+    # block-quantised checkpoints stay in their shipped encoding on a GPU (no bf16 copy on the way in) unless the
+    # experts are offloaded (the host tiers hold plain tensors) or bf16 weights were asked for
+    keep_q = (on_gpu and getattr(a, "weights", "auto") != "bf16" and a.experts not in ("cache", "host", "ssd"))
+    cfg, w, tok, info = load_model(path, device, rank=rank, world=world, expert_parallel=a.tp_moe_ep, seed=a.seed,
+                                   keep_quant=keep_q)
     if pctx is not None and pctx.symm is None and a.tp_comm == "fused" and on_gpu:
         from ..parallel.symm import SymmComm
         import torch.distributed as dist
@@ -191,7 +195,8 @@ def build_engine_from_args(a, start: bool = True):
             model.offload_experts(max(slots, cfg.top_k))
     eng = LmEngine(model, tok, ec, start=start)
     logging.getLogger("legion").info("loaded %s: %s, %d layers, %.2fB parameters on %s", path, cfg.arch, cfg.n_layer,
-                                     sum(t.numel() for t in w.values()) / 1e9, device)
+                                     sum((t.numel() if isinstance(t, torch.Tensor) else t.codes.numel() * 2 if hasattr(t, "codes")
+                                          else t.data.numel()) for t in w.values() if t is not None) / 1e9, device)
     if a.tp_replicas > 1:
         from ..engine.replicas import ReplicaEngine
         return ReplicaEngine([eng] + [LmEngine(model, tok, ec) for _ in range(a.tp_replicas - 1)])

@@ -92,6 +92,65 @@ class _Source:
     def raw(self, name: str) -> torch.Tensor:
         return self.ck.get(name)
 
+    def shipped(self, base: str):
+        """The tensor's quantised parts exactly as the checkpoint stores them, on the device, or None when it is
+        not block-quantised: ("nvfp4", codes u8 [rows, K/2], scale bytes u8 [rows, K/16], tensor scale) or
+        ("fp8", e4m3 bytes u8 [rows, K], fp32 scale per 128 x 128 block)."""
+        ck, dev = self.ck, self.device
+        if ck.has(base + ".weight_packed"):                       # compressed-tensors NVFP4: the global scale divides
+            g = 1.0 / float(ck.get(base + ".weight_global_scale").float().reshape(-1)[0])
+            return ("nvfp4", ck.get(base + ".weight_packed").to(dev).view(torch.uint8),
+                    ck.get(base + ".weight_scale").view(torch.uint8).to(dev), g)
+        if not ck.has(base + ".weight"):
+            return None
+        if ck.has(base + ".weight_scale_2"):                      # ModelOpt NVFP4
+            return ("nvfp4", ck.get(base + ".weight").to(dev).view(torch.uint8),
+                    ck.get(base + ".weight_scale").view(torch.uint8).to(dev),
+                    float(ck.get(base + ".weight_scale_2").float().reshape(-1)[0]))
+        w = ck.get(base + ".weight")
+        if w.dtype == torch.float8_e4m3fn and ck.has(base + ".weight_scale_inv"):
+            bs = (ck.config.get("quantization_config") or {}).get("weight_block_size") or [128, 128]
+            if list(bs) == [128, 128]:
+                return ("fp8", w.view(torch.uint8).to(dev), ck.get(base + ".weight_scale_inv").float().to(dev))
+        return None
+
+    def stacked(self, bases, dual: bool = False, groups: int = 1):
+        """Several checkpoint tensors stacked by rows WITHOUT leaving their encoding: ``bases`` lists, group by
+        group, the tensors of each group in row order (``dual``: two per group, the gate and the up half, each with
+        its own tensor scale). Returns an ``ops.sm100.Nv4Weight`` / ``Fp8Weight`` ([groups, rows, K] when groups > 1)
+        or None when a part is not quantised, the parts differ in kind, or the shapes do not fit the kernels."""
+        from ..ops import sm100
+        if self.device.type != "cuda":
+            return None
+        parts = [self.shipped(b) for b in bases]
+        if any(p is None for p in parts) or len({p[0] for p in parts}) != 1:
+            return None
+        per = len(parts) // groups
+        kind = parts[0][0]
+        rows = [p[1].shape[0] for p in parts]
+        if any(r % 128 for r in rows):
+            return None
+        if kind == "nvfp4":
+            K = parts[0][1].shape[1] * 2
+            if K % 64:
+                return None
+            gs = [p[3] for p in parts]
+            if not dual and per > 1 and len(set(gs[:per])) > 1:
+                return None                        # one tensor scale per group: parts of a group must share it
+            codes = torch.cat([p[1] for p in parts], 0)
+            scales = torch.cat([p[2] for p in parts], 0)
+            g = torch.tensor(gs if dual else gs[::per], dtype=torch.float32, device=self.device)
+            if groups > 1:
+                codes = codes.view(groups, -1, codes.shape[-1])
+                scales = scales.view(groups, -1, scales.shape[-1])
+            return sm100.Nv4Weight.from_parts(codes, scales, g)
+        data = torch.cat([p[1] for p in parts], 0)
+        sc = torch.cat([p[2] for p in parts], 0)
+        if groups > 1:
+            data = data.view(groups, -1, data.shape[-1])
+            sc = sc.view(groups, -1, sc.shape[-1])
+        return sm100.Fp8Weight(data.contiguous(), sc.contiguous())
+
     def weight(self, base: str) -> torch.Tensor:
         """``base`` without the ``.weight`` suffix."""
         ck = self.ck
@@ -113,8 +172,17 @@ class _Source:
         return w.to(device=dev)
 
 
-def load_hf(path: str, device="cpu", dtype=torch.float32):
-    """Returns (config, canonical weights, checkpoint)."""
+def load_hf(path: str, device="cpu", dtype=torch.float32, keep_quant: bool = False, expert_range=None,
+            keep_quant_dense: bool = True):
+    """Returns (config, canonical weights, checkpoint). ``keep_quant`` (CUDA device): block-quantised expert, FFN
+    and output projections stay in their shipped encoding (``ops.sm100.Nv4Weight`` / ``Fp8Weight``: the file's code
+    bytes, scale bytes re-ordered for the tensor-core copy, never expanded to bf16), the way the reference repacks
+    ModelOpt / compressed-tensors tensors (``src/hf/nvfp4.rs:5-33``) and picks the matmul per tensor
+    (``src/model/core/linear.rs:95-112``). Tensors whose rows are interleaved or permuted on the way in (fused
+    attention / DeltaNet projections, rotary de-interleave) are decoded. ``expert_range=(lo, hi)``: only these
+    routed experts are read (an expert-parallel rank reads its own shard of the files and nothing else of the
+    experts, like the reference's sharded reader ``src/load_io.rs``). ``keep_quant_dense=False`` keeps only the
+    experts encoded (ranks that slice the dense projections by columns decode those first)."""
     ck = Checkpoint(path)
     cfg = config_from_hf(ck.config)
     src = _Source(ck, torch.device(device), dtype)
@@ -125,6 +193,11 @@ def load_hf(path: str, device="cpu", dtype=torch.float32):
     def norm(name):
         return src.raw(name).float()
 
+    def proj(base):
+        """A projection that is used as stored (no row permutation): stays encoded when asked for."""
+        q = src.stacked([base]) if (keep_quant and keep_quant_dense) else None
+        return q if q is not None else src.weight(base)
+
     w["tok_embd"] = src.weight(P + "embed_tokens")
     w["output_norm"] = norm(P + "norm.weight")
     if ck.has("lm_head.weight") or ck.has("lm_head.weight_packed"):
@@ -134,16 +207,24 @@ def load_hf(path: str, device="cpu", dtype=torch.float32):
     D = cfg.head_dim
 
     def experts(pre: str, p: str):
-        E = cfg.n_expert
+        e_lo, e_hi = expert_range if expert_range is not None else (0, cfg.n_expert)
+        E = e_hi - e_lo
         if ck.has(pre + "experts.gate_up_proj"):                  # already fused [E, H, 2F] or [E, 2F, H]
-            gu = src.raw(pre + "experts.gate_up_proj")
-            dn = src.raw(pre + "experts.down_proj")
+            gu = src.raw(pre + "experts.gate_up_proj")[e_lo:e_hi]
+            dn = src.raw(pre + "experts.down_proj")[e_lo:e_hi]
             if gu.shape[1] == cfg.hidden:
                 gu, dn = gu.transpose(1, 2), dn.transpose(1, 2)
             w[f"{p}.moe.gate_up"], w[f"{p}.moe.down"] = gu.contiguous(), dn.contiguous()
             return
+        if keep_quant:
+            qg = src.stacked([f"{pre}experts.{e}.{n}" for e in range(e_lo, e_hi) for n in ("gate_proj", "up_proj")],
+                             dual=True, groups=E)
+            qd = src.stacked([f"{pre}experts.{e}.down_proj" for e in range(e_lo, e_hi)], groups=E) if qg is not None else None
+            if qg is not None and qd is not None:
+                w[f"{p}.moe.gate_up"], w[f"{p}.moe.down"] = qg, qd
+                return
         gus, dns = [], []
-        for e in range(E):
+        for e in range(e_lo, e_hi):
             g = src.weight(f"{pre}experts.{e}.gate_proj")
             u = src.weight(f"{pre}experts.{e}.up_proj")
             gus.append(torch.cat([g, u], dim=0))
@@ -160,12 +241,24 @@ def load_hf(path: str, device="cpu", dtype=torch.float32):
             experts(pre, p)
             for sh in ("shared_expert.", "shared_experts."):
                 if ck.has(pre + sh + "gate_proj.weight") or ck.has(pre + sh + "gate_proj.weight_packed"):
+                    if keep_quant and keep_quant_dense:
+                        qg = src.stacked([pre + sh + "gate_proj", pre + sh + "up_proj"], dual=True)
+                        qd = src.stacked([pre + sh + "down_proj"]) if qg is not None else None
+                        if qg is not None and qd is not None:
+                            w[f"{p}.moe.sh_gate_up"], w[f"{p}.moe.sh_down"] = qg, qd
+                            continue
                     w[f"{p}.moe.sh_gate_up"] = torch.cat([src.weight(pre + sh + "gate_proj"),
                                                           src.weight(pre + sh + "up_proj")], dim=0)
                     w[f"{p}.moe.sh_down"] = src.weight(pre + sh + "down_proj")
             if ck.has(pre + "shared_expert_gate.weight"):
                 w[f"{p}.moe.sh_gate"] = src.weight(pre + "shared_expert_gate").reshape(1, -1)
         else:
+            if keep_quant and keep_quant_dense:
+                qg = src.stacked([lp + "mlp.gate_proj", lp + "mlp.up_proj"], dual=True)
+                qd = src.stacked([lp + "mlp.down_proj"]) if qg is not None else None
+                if qg is not None and qd is not None:
+                    w[f"{p}.mlp.gate_up"], w[f"{p}.mlp.down"] = qg, qd
+                    return
             w[f"{p}.mlp.gate_up"] = torch.cat([src.weight(lp + "mlp.gate_proj"), src.weight(lp + "mlp.up_proj")], dim=0)
             w[f"{p}.mlp.down"] = src.weight(lp + "mlp.down_proj")
 
@@ -176,7 +269,7 @@ def load_hf(path: str, device="cpu", dtype=torch.float32):
         if ck.has(a + "q_norm.weight"):
             w[f"{p}.attn.q_norm"] = norm(a + "q_norm.weight")
             w[f"{p}.attn.k_norm"] = norm(a + "k_norm.weight")
-        w[f"{p}.attn.o"] = src.weight(a + "o_proj")
+        w[f"{p}.attn.o"] = proj(a + "o_proj")
 
     def deltanet(lp: str, p: str):
         a = lp + "linear_attn."
@@ -200,7 +293,7 @@ def load_hf(path: str, device="cpu", dtype=torch.float32):
         w[f"{p}.gdn.A"] = -torch.exp(src.raw(a + "A_log").float())
         w[f"{p}.gdn.dt_bias"] = src.raw(a + "dt_bias").float()
         w[f"{p}.gdn.norm"] = norm(a + "norm.weight")       # stored as the plain weight (no +1)
-        w[f"{p}.gdn.out"] = src.weight(a + "out_proj")
+        w[f"{p}.gdn.out"] = proj(a + "out_proj")
 
     def mla(lp: str, p: str):
         a = lp + "self_attn."
@@ -214,7 +307,7 @@ def load_hf(path: str, device="cpu", dtype=torch.float32):
         w[f"{p}.mla.kv_a"] = _deinterleave_rope(kva, 1, cfg.kv_lora, cfg.qk_rope_dim)
         w[f"{p}.mla.kv_a_norm"] = norm(a + "kv_a_layernorm.weight")
         w[f"{p}.mla.kv_b"] = src.weight(a + "kv_b_proj")
-        w[f"{p}.mla.o"] = src.weight(a + "o_proj")
+        w[f"{p}.mla.o"] = proj(a + "o_proj")
 
     for il in range(cfg.n_layer):
         lp, p = f"{P}layers.{il}.", f"l{il}"
@@ -232,6 +325,9 @@ def load_hf(path: str, device="cpu", dtype=torch.float32):
     _ = hybrid
     out = {}
     for k, v in w.items():
+        if not isinstance(v, torch.Tensor):
+            out[k] = v                          # kept in its shipped encoding
+            continue
         out[k] = v.to(device=device, dtype=torch.float32 if is_fp32_weight(k) else dtype).contiguous()
     return cfg, out, ck
 

@@ -18,8 +18,11 @@ from .tokenizer import BpeTokenizer, ByteTokenizer, Tokenizer
 
 
 def load_model(path: str, device="cpu", dtype=None, rank: int = 0, world: int = 1, expert_parallel: bool = False,
-               seed: int = 0, keep_layers=None, dp_attention: bool = False) -> Tuple[ModelConfig, Dict[str, torch.Tensor], Tokenizer, dict]:
-    """``keep_layers(il)``: a pipeline stage keeps only the layers it owns (plus embeddings and head)."""
+               seed: int = 0, keep_layers=None, dp_attention: bool = False,
+               keep_quant: bool = False) -> Tuple[ModelConfig, Dict[str, torch.Tensor], Tokenizer, dict]:
+    """``keep_layers(il)``: a pipeline stage keeps only the layers it owns (plus embeddings and head).
+    ``keep_quant`` (HF directories on a GPU): NVFP4 / FP8 tensors stay in their shipped encoding; with expert
+    parallelism every rank reads only its own experts from the files, straight to its GPU."""
     from ..models.weights import layer_of
     keep = None
     if keep_layers is not None:
@@ -35,8 +38,23 @@ def load_model(path: str, device="cpu", dtype=None, rank: int = 0, world: int = 
         return cfg, w, ByteTokenizer(cfg.vocab), info
     if os.path.isdir(path):
         from .hf_map import load_hf
-        cfg, w, ck = load_hf(path, "cpu" if world > 1 else dev, dtype)
+        local_experts = None
+        if keep_quant and dev.type == "cuda" and world > 1 and (expert_parallel or dp_attention):
+            from .safetensors_io import Checkpoint
+            from .hf_map import config_from_hf
+            c0 = config_from_hf(Checkpoint(path).config)
+            if c0.n_expert and c0.n_expert % world == 0:
+                per = c0.n_expert // world
+                local_experts = (rank * per, (rank + 1) * per)
+        if local_experts is not None:
+            # sharded read: this rank's experts only, encoded, straight to the GPU; the rest is sliced below
+            cfg, w, ck = load_hf(path, dev, dtype, keep_quant=True, expert_range=local_experts,
+                                 keep_quant_dense=dp_attention)
+        else:
+            cfg, w, ck = load_hf(path, "cpu" if world > 1 else dev, dtype,
+                                 keep_quant=keep_quant and world == 1 and dev.type == "cuda")
         info["quant_method"] = ck.quant_method()
+        info["local_experts"] = local_experts
         tok: Tokenizer
         if os.path.exists(os.path.join(path, "tokenizer.json")):
             tok = BpeTokenizer.from_hf_dir(path)
@@ -59,5 +77,13 @@ def load_model(path: str, device="cpu", dtype=None, rank: int = 0, world: int = 
         w = {k: v for k, v in w.items() if keep(k)}
     if world > 1:
         sh = Shard(cfg, rank, world, expert_parallel, dp_attention)
-        w = {k: sh.slice(k, v).to(dev) for k, v in w.items()}
+        pre_sliced = info.get("local_experts") is not None
+
+        def place(k, v):
+            if pre_sliced and k.endswith(("moe.gate_up", "moe.down")):
+                return v                         # read as this rank's experts already
+            if not isinstance(v, torch.Tensor):
+                return v
+            return sh.slice(k, v).to(dev)
+        w = {k: place(k, v) for k, v in w.items()}
     return cfg, w, tok, info

@@ -1031,7 +1031,9 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[Moe
         if _dense_ok(routing, E_local, e_lo, ids):
             return _moe_experts_nv4(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, shared, shared_gate, residual, out,
                                     norm, routing, xq=routing.xq, defer=defer_combine)
-        if TUNE["nv4_sorted"] and T * k >= 64 * E_local and not (routing is not None and routing.shared_slot):
+        wfp4_ok = H % 256 == 0 and n_ff % 256 == 0       # what the de-quantising GEMM needs of K
+        if (TUNE["nv4_sorted"] and (T * k >= 64 * E_local or not wfp4_ok)
+                and not (routing is not None and routing.shared_slot)):
             return _moe_experts_nv4_sorted(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, shared, shared_gate, residual,
                                            out, norm, xq=routing.xq if routing is not None else None)
         # steps in between: the de-quantising grouped GEMM over the routing plan (same codes, linear scale order)

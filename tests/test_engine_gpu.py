@@ -161,3 +161,46 @@ def test_prefix_cache_host_tier_on_gpu():
     eng.shutdown()
     assert again.token_ids == first.token_ids
     assert st.prefix_host_restored > 0 and again.usage.cached_tokens >= 128
+
+
+@pytest.mark.parametrize("quant", ["nvfp4", "nvfp4_ct", "fp8_block"])
+def test_quantised_checkpoint_stays_in_its_shipped_encoding(tmp_path, quant):
+    """An NVFP4 (ModelOpt or compressed-tensors) / block-FP8 directory loads with its expert and output projections
+    still encoded: the code bytes are the file's, and the model's logits agree with the load that decodes to bf16."""
+    from legion_b200.loaders.hf_map import load_hf, save_hf
+    from legion_b200.loaders.safetensors_io import Checkpoint
+    from legion_b200.ops import sm100
+    cfg = ModelConfig(arch="qwen3moe", n_layer=2, hidden=256, vocab=1024, n_head=4, n_kv_head=2, head_dim=64,
+                      n_expert=8, top_k=2, expert_ff=128)
+    w = random_weights(cfg, "cpu", torch.float32, seed=2, std=0.05)
+    d = str(tmp_path / "ck")
+    save_hf(d, cfg, w, quant=quant)
+    cfg_q, wq, ck = load_hf(d, "cuda", torch.bfloat16, keep_quant=True)
+    cfg_d, wd, _ = load_hf(d, "cuda", torch.bfloat16)
+    kind = sm100.Fp8Weight if quant == "fp8_block" else sm100.Nv4Weight
+    for name in ("l0.moe.gate_up", "l1.moe.down", "l0.attn.o"):
+        assert isinstance(wq[name], kind), (name, type(wq[name]))
+        assert isinstance(wd[name], torch.Tensor)
+    raw_name = "model.layers.0.mlp.experts.3.gate_proj.weight" + ("_packed" if quant == "nvfp4_ct" else "")
+    raw = ck.get(raw_name).view(torch.uint8).cuda()
+    got = wq["l0.moe.gate_up"].codes if quant != "fp8_block" else wq["l0.moe.gate_up"].data
+    assert torch.equal(got[3, :raw.shape[0]], raw)
+    # the de-quantised form of the kept encoding is the decoding load's tensor
+    deq = wq["l0.moe.gate_up"].dequantize(torch.bfloat16).float()
+    assert float((deq - wd["l0.moe.gate_up"].float()).abs().max()) <= 1e-2 * float(wd["l0.moe.gate_up"].float().abs().max())
+    # and the model runs on it
+    ec = dict(ctx_size=512, max_seqs=4, block_size=64, prefill_chunk=128, max_batch_tokens=256)
+    prompt = torch.randint(0, 255, (90,), generator=torch.Generator().manual_seed(5)).tolist()
+    outs = []
+    for ww in (wd, wq):
+        eng = build_engine(cfg_q, weights=ww, device="cuda", engine_cfg=EngineConfig(cuda_graphs=False, **ec), start=False)
+        from legion_b200.engine.types import GenerateRequest, SamplingParams
+        seq = eng.prepare(GenerateRequest(prompt_tokens=prompt, sampling=SamplingParams(max_tokens=4, ignore_eos=True)))
+        eng.waiting.push(seq)
+        eng._admit()
+        b = eng.build_batch([(seq, 0, len(prompt))])
+        outs.append(eng.model.forward(b, eng.kv, eng.states).logits.float().cpu())
+    err = (outs[0] - outs[1]).abs().max().item()
+    ref = outs[0].abs().max().item()
+    assert err < (0.25 if quant != "fp8_block" else 0.1) * ref + 0.1, (err, ref)      # activations are quantised too
+    assert sm100.Workspace.get("cuda").check() == 0

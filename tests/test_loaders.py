@@ -252,3 +252,19 @@ def test_native_bpe_merges_equal_python():
     t._native = None
     t._cache.clear()
     assert got == t.encode(text) and len(got) > 1000
+
+
+def test_hf_directory_expert_range_reads_only_those_experts(tmp_path):
+    """An expert-parallel rank opens the same directory with its expert range and gets exactly that slice."""
+    cfg = tiny_gqa_moe()
+    w = random_weights(cfg, "cpu", torch.float32, seed=4)
+    d = str(tmp_path / "ck")
+    save_hf(d, cfg, w, quant="none", dtype=torch.float32)
+    _, full, _ = load_hf(d)
+    lo, hi = 2, 6
+    _, part, _ = load_hf(d, expert_range=(lo, hi))
+    for k, v in full.items():
+        if k.endswith(("moe.gate_up", "moe.down")):
+            assert part[k].shape[0] == hi - lo and torch.equal(part[k], v[lo:hi])
+        else:
+            assert torch.equal(part[k], v)
