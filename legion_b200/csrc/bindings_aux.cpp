@@ -7,6 +7,7 @@
 #include "ep.h"
 #include "gdn.h"
 #include "gemm_nvfp4_sm100.h"
+#include "kernels.h"
 #include "quant.h"
 
 namespace {
@@ -360,6 +361,22 @@ void bind_quant(pybind11::module_& m) {
                                          codes.stride(0), reinterpret_cast<uint8_t*>(sf_atoms.data_ptr()),
                                          optpm<float>(row_gscale), cur_stream()) == 0,
                 "nv4_act_quant: K must be a multiple of 16 and at most 8192, rows 16-byte aligned");
+  });
+  m.def("mamba2_scan", [](const Tensor& xbc, const Tensor& dt_raw, const Tensor& z, const Tensor& A, const Tensor& D,
+                          const Tensor& dt_bias, Tensor& state, const Tensor& cu_seq, const Tensor& slots, int64_t nh,
+                          int64_t hd, int64_t ng, int64_t ds, Tensor& y, bool write_state) {
+    TORCH_CHECK(xbc.scalar_type() == at::kBFloat16 && dt_raw.scalar_type() == at::kBFloat16 &&
+                    z.scalar_type() == at::kBFloat16 && y.scalar_type() == at::kBFloat16 && xbc.stride(1) == 1 &&
+                    dt_raw.stride(1) == 1 && z.stride(1) == 1 && y.stride(1) == 1 && state.is_contiguous() &&
+                    state.scalar_type() == at::kFloat && xbc.size(1) == nh * hd + 2 * ng * ds,
+                "mamba2_scan: bf16 rows [T, di + 2 * ng * ds], fp32 state [slots, nh, hd, ds]");
+    c10::cuda::CUDAGuard guard(xbc.device());
+    TORCH_CHECK(lb::mamba2_scan_launch(xbc.data_ptr(), xbc.stride(0), dt_raw.data_ptr(), dt_raw.stride(0), z.data_ptr(),
+                                       z.stride(0), A.data_ptr<float>(), D.data_ptr<float>(), dt_bias.data_ptr<float>(),
+                                       state.data_ptr<float>(), cu_seq.data_ptr<int>(), slots.data_ptr<int>(),
+                                       int(slots.numel()), int(nh), int(hd), int(ng), int(ds), y.data_ptr(), y.stride(0),
+                                       write_state ? 1 : 0, cur_stream()) == 0,
+                "mamba2_scan: unsupported head shape");
   });
   m.def("nv4_gather_rows", [](const Tensor& codes, const Tensor& sf, const OptT& gscale, const Tensor& rows,
                               const OptT& n_rows, Tensor& dst_codes, Tensor& dst_sf, const OptT& dst_gscale) {

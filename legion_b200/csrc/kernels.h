@@ -78,6 +78,12 @@ int moe_plan_aligned_launch(const int* ids, const float* wts, int n_tokens, int 
 int gather_rows_launch(const void* src, long lds, const int* rows, const int* n_rows, void* dst, long ldd, int H,
                        int max_rows, cudaStream_t s);
 
+// Mamba-2 state-space recurrence + silu(z) gate (mamba2.cu). 256 % hd == 0, hd a power of two, ds divisible by
+// 256 / hd with at most 32 columns per thread; returns 1 for other shapes.
+int mamba2_scan_launch(const void* xbc, long ldx, const void* dt_raw, long lddt, const void* z, long ldz, const float* A,
+                       const float* D, const float* dt_bias, float* state, const int* cu_seq, const int* slots,
+                       int n_seqs, int nh, int hd, int ng, int ds, void* y, long ldy, int write_state, cudaStream_t s);
+
 int moe_combine_launch(const void* y, long ldy, const int* ids, int k, int e_lo, int e_hi, const void* shared, long lds,
                        const float* shared_gate, const void* residual, long ldr, void* out, long ldo, int T, int H,
                        const float* norm_w, float eps, float w_offset, void* norm_out, long ldn, cudaStream_t s);

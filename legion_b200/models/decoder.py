@@ -451,7 +451,8 @@ class Decoder:
         return ops.linear(out.reshape(T, nh * dvh), w[f"{p}.mla.o"])
 
     def _mamba2(self, p: str, il: int, x, b: StepBatch, st: StatePool):
-        """Mamba-2 (SSD) layer, token-serial reference form on both back-ends."""
+        """Mamba-2 (SSD) layer: on a GPU the recurrence, the D skip and the silu(z) gate are one kernel with the state
+        of a (sequence, head) in registers (``csrc/mamba2.cu``); the CPU form is the token-serial reference."""
         cfg, w = self.cfg, self.w
         nh, hd, ng, ds = cfg.ssm_heads, cfg.ssm_head_dim, cfg.ssm_groups, cfg.ssm_state
         di = nh * hd
@@ -460,6 +461,11 @@ class Decoder:
         z, xbc, dt = proj[:, :di], proj[:, di:2 * di + 2 * ng * ds], proj[:, 2 * di + 2 * ng * ds:]
         xbc = ops.causal_conv1d_silu(xbc.contiguous(), w[f"{p}.ssm.conv_w"], w[f"{p}.ssm.conv_b"], st.conv[il], b.cu_q,
                                      b.state_slots, write_state=b.write_state)
+        if x.is_cuda and ops.sm100.mamba2_scan_ok(nh, hd, ng, ds) and x.dtype == torch.bfloat16:
+            yz = ops.sm100.mamba2_scan(xbc, dt, z, w[f"{p}.ssm.A"], w[f"{p}.ssm.D"], w[f"{p}.ssm.dt_bias"], st.ssm[il],
+                                       b.cu_q, b.state_slots, nh, hd, ng, ds, write_state=b.write_state)
+            yn, _ = ops.rmsnorm(yz, w[f"{p}.ssm.norm"], cfg.rms_eps, 0.0)
+            return ops.linear(yn, w[f"{p}.ssm.out"])
         xs = xbc[:, :di].float().view(T, nh, hd)
         Bm = xbc[:, di:di + ng * ds].float().view(T, ng, ds)
         Cm = xbc[:, di + ng * ds:].float().view(T, ng, ds)

@@ -1308,6 +1308,29 @@ def gdn_decode_fused(proj, conv_w, conv_state, A, dt_bias, norm_w, eps, act, sta
     return out
 
 
+def mamba2_scan_ok(nh: int, hd: int, ng: int, ds: int) -> bool:
+    """Head shapes the Mamba-2 kernel's thread layout covers (256 / hd threads per state row, <= 32 columns each)."""
+    if hd <= 0 or hd > 256 or 256 % hd or hd & (hd - 1) or nh % max(ng, 1):
+        return False
+    W = 256 // hd
+    return W <= 32 and ds % W == 0 and ds // W <= 32
+
+
+def mamba2_scan(xbc, dt_raw, z, A, D, dt_bias, state, cu_seq, slots, nh, hd, ng, ds, write_state=True, out=None):
+    """Mamba-2 recurrence over the step's tokens: xbc [T, nh*hd + 2*ng*ds] = x | B | C after the causal conv, dt_raw
+    [T, nh], z [T, nh*hd] (bf16, row slices allowed), fp32 state [slots, nh, hd, ds] updated in place. Returns
+    (S C + D x) * silu(z) as bf16 [T, nh*hd]."""
+    C = ext()
+    T = xbc.shape[0]
+    if out is None:
+        out = torch.empty(T, nh * hd, dtype=torch.bfloat16, device=xbc.device)
+    if T == 0:
+        return out
+    C.mamba2_scan(xbc, dt_raw, z, A.float(), D.float(), dt_bias.float(), state, cu_seq, slots, nh, hd, ng, ds, out,
+                  bool(write_state))
+    return out
+
+
 def gated_rmsnorm(o, z, w, eps, act="silu", out=None):
     C = ext()
     T, Hv, DV = o.shape

@@ -2,7 +2,7 @@
 import pytest
 import torch
 
-from legion_b200.config import ModelConfig, tiny_hybrid_moe
+from legion_b200.config import PRESETS, ModelConfig, tiny_hybrid_moe
 from legion_b200.engine.lm import EngineConfig, build_engine
 from legion_b200.models.weights import random_weights
 
@@ -20,10 +20,11 @@ def _cfgs():
                     q_lora=96, kv_lora=512, qk_nope_dim=64, qk_rope_dim=64, v_head_dim=64, qk_norm=False,
                     dense_ff=384, first_dense_layers=1, n_expert=8, top_k=2, expert_ff=128, shared_ff=128,
                     router_mode="sigmoid", router_bias=True, n_group=4, topk_group=2, route_scale=2.5),
+        PRESETS["tiny-nemotron-h"](),          # Mamba-2 layers on the state-space scan kernel
     ]
 
 
-@pytest.mark.parametrize("idx", [0, 1, 2, 3])
+@pytest.mark.parametrize("idx", [0, 1, 2, 3, 4])
 @pytest.mark.parametrize("graphs", [False, True])
 def test_gpu_engine_matches_cpu_logits(idx, graphs):
     """Greedy tokens of random tiny models are fragile under bf16; compare the first-step logits of the GPU
