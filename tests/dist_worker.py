@@ -174,6 +174,65 @@ def case_engine(dev, comm_kind):
     return {"tokens": toks, "graph_replays": replays}
 
 
+def case_engine_nv4(dev, comm_kind):
+    """The serving layout of the NVFP4 hybrid configuration on several GPUs: attention and Gated DeltaNet heads split
+    by rank, routed experts whole per rank (NVFP4, native W4A4 GEMMs), the shared expert whole on rank (layer mod
+    world) stacked behind that rank's experts, decode steps from CUDA graphs. ``fused``: quantising pushed-line
+    reduction with the MoE combine inside; ``nccl``: NCCL all-reduce + separate kernels. Returns the first decode
+    step's logits too, so that runs whose reduction order differs (more than two ranks) can be compared by value."""
+    from legion_b200.config import ModelConfig
+    from legion_b200.engine.lm import EngineConfig, LmEngine
+    from legion_b200.engine.types import GenerateRequest, SamplingParams
+    from legion_b200.loaders.tokenizer import ByteTokenizer
+    from legion_b200.models.decoder import Decoder, place_shared_expert, quantize_moe_layer_nvfp4
+    from legion_b200.models.weights import Shard, random_weights
+    from legion_b200.parallel.context import ParallelCtx
+    from legion_b200.parallel.symm import SymmComm
+    kinds = ["gdn", "gdn", "attn", "gdn"]
+    cfg = ModelConfig(arch="qwen35moe", n_layer=4, hidden=512, vocab=2048, n_head=8, n_kv_head=2, head_dim=128,
+                      layer_kinds=kinds, gated_attn=True, rope_dim=64, gdn_k_heads=8, gdn_v_heads=16, gdn_k_dim=128,
+                      gdn_v_dim=128, gdn_conv=4, n_expert=16, top_k=4, expert_ff=256, shared_ff=256, shared_gate=True)
+    full = random_weights(cfg, "cpu", torch.float32, seed=0, std=0.05)
+    full = {k: (v.bfloat16() if v.dim() > 1 and not k.endswith("conv_w") else v) for k, v in full.items()}
+    sh = Shard(cfg, RANK, WORLD, expert_parallel=True, shared_whole=True)
+    w = {k: v.to(dev) for k, v in sh.shard_all(full).items()}
+    for il in range(cfg.n_layer):
+        place_shared_expert(w, f"l{il}", il, cfg, RANK, WORLD)
+        quantize_moe_layer_nvfp4(w, f"l{il}")
+    symm = SymmComm(dist.group.WORLD, RANK, WORLD, dev, 1024, cfg.hidden, budget_ns=2_000_000_000) \
+        if comm_kind == "fused" else None
+    pctx = ParallelCtx(RANK, WORLD, dist.group.WORLD, True, comm_kind, symm)
+    model = Decoder(cfg, w, pctx, max_position=520)
+    model.fuse_gdn_in_proj()
+    eng = LmEngine(model, ByteTokenizer(cfg.vocab), EngineConfig(ctx_size=512, max_seqs=4, block_size=64, prefill_chunk=256,
+                                                                 prefix_cache=False, device=str(dev)), start=False)
+    say("engine built")
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 255, (n,), generator=g).tolist() for n in (200, 70, 131)]
+    streams = [eng.generate(GenerateRequest(prompt_tokens=p, sampling=SamplingParams(max_tokens=10, ignore_eos=True)))
+               for p in prompts]
+    eng._drain(block=False)
+    for i in range(200):
+        eng._admit()
+        if not eng.running and len(eng.waiting) == 0:
+            break
+        eng.step()
+        if symm is not None:
+            symm.check()
+    toks = [s.collect().token_ids for s in streams]
+    replays = eng._graphs.replays if eng._graphs else 0
+    # one more eager decode-sized forward over fixed rows: logits by value
+    seq = eng.prepare(GenerateRequest(prompt_tokens=prompts[1], sampling=SamplingParams(max_tokens=2, ignore_eos=True)))
+    eng.waiting.push(seq)
+    eng._admit()
+    b = eng.build_batch([(seq, 0, len(prompts[1]))])
+    logits = eng.model.forward(b, eng.kv, eng.states).logits.float().cpu()
+    from legion_b200.ops import sm100
+    assert sm100.Workspace.get(dev).check() == 0
+    eng.shutdown()
+    return {"tokens": toks, "graph_replays": replays, "logits": logits}
+
+
 def case_peer_experts(dev):
     """Experts sharded over the ranks' symmetric memory; a rank's grouped GEMM streams a PEER's expert tiles over
     NVLink with plain (non-multicast) TMA loads. Every rank computes the whole MoE layer from all shards."""
@@ -308,6 +367,8 @@ def main():
         res = case_peer_experts(dev)
     elif CASE == "engine_dp":
         res = case_engine_dp(dev)
+    elif CASE in ("engine_nv4_nccl", "engine_nv4_fused"):
+        res = case_engine_nv4(dev, CASE.split("_")[2])
     elif CASE in ("engine_nccl", "engine_fused", "engine_tail"):
         res = case_engine(dev, CASE.split("_")[1])
     else:
