@@ -67,6 +67,29 @@ def case_comm(dev):
         assert torch.equal(xq.dequantize(), rq.dequantize())
         comm.check()
         say("quantising reduction rows", T, "ok")
+    # the reduction sums this rank's weighted expert rows per token itself (no combine launch before it): every
+    # rank owns a range of experts, rank 0 also brings a shared-expert row per token
+    for T, k in ((16, 4), (1, 8), (50, 6)):
+        E = 4 * WORLD
+        ids = torch.randint(0, E, (T, k), device=dev, dtype=torch.int32)
+        ys = [(torch.randn(T * k, H, device=dev) * 0.3).bfloat16() for _ in range(WORLD)]
+        shared = (torch.randn(T, H, device=dev) * 0.3).bfloat16()
+        res = torch.randn(T, H, device=dev).bfloat16()
+        w = torch.rand(H, device=dev) + 0.5
+        total = res.float()
+        for r in range(WORLD):
+            on = ((ids >= 4 * r) & (ids < 4 * r + 4)).reshape(T, k, 1).float()
+            part = (ys[r].float().view(T, k, H) * on).sum(1) + (shared.float() if r == 0 else 0.0)
+            total = total + part.bfloat16().float()
+        pend = sm100.PendingCombine(ys[RANK], ids, 4 * RANK, 4 * RANK + 4, shared if RANK == 0 else None, T, H)
+        normed, summed, xq = comm.all_reduce_add_norm(comm.next_partial(T, H), res, w, 1e-6, 0.0, quant=True, combine=pend)
+        errs.append(float((summed.float() - total).abs().max()))
+        want_n, _ = ref.rmsnorm(summed, w, 1e-6)
+        errs.append(float((normed.float() - want_n.float()).abs().max()))
+        rq = sm100.nv4_quant_act(normed)
+        assert torch.equal(xq.codes[:T], rq.codes)
+        comm.check()
+        say("combine inside the reduction, rows", T, "ok")
     # GEMM epilogue writes straight into the slot, then the fused reduction
     x = (torch.randn(24, 256, device=dev) * 0.3).bfloat16()
     wts = [(torch.randn(H, 256, device=dev) * 0.05).bfloat16() for _ in range(WORLD)]
