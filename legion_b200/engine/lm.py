@@ -182,7 +182,7 @@ class LmEngine(Engine):
         self.eos_ids = tuple(self.tok.eos_ids)
         self._graphs = None
         if dev.type == "cuda" and c.cuda_graphs and not model.expert_cache and getattr(model, "pipe", None) is None \
-                and "mamba2" not in self.mcfg.layer_kinds and self._mla_graphable(model, c):
+                and self._mamba_graphable() and self._mla_graphable(model, c):
             from .cuda_graphs import DecodeGraphs
             self._graphs = DecodeGraphs(self)
         self.step_hook: Optional[Callable] = None    # tests observe (batch description) per step
@@ -190,6 +190,15 @@ class LmEngine(Engine):
         self._by_id: Dict[str, Seq] = {}
         if start:
             self.start()
+
+    def _mamba_graphable(self) -> bool:
+        """Mamba-2 layers decode from CUDA graphs when their head shape runs on the scan kernel (the token loop that
+        serves other shapes reads sequence bounds on the host)."""
+        m = self.mcfg
+        if "mamba2" not in m.layer_kinds:
+            return True
+        from ..ops import sm100
+        return sm100.mamba2_scan_ok(m.ssm_heads, m.ssm_head_dim, m.ssm_groups, m.ssm_state)
 
     # ------------------------------------------------------------------ Engine interface
     def models(self):

@@ -205,3 +205,48 @@ def test_quantised_checkpoint_stays_in_its_shipped_encoding(tmp_path, quant):
     ref = outs[0].abs().max().item()
     assert err < (0.25 if quant != "fp8_block" else 0.1) * ref + 0.1, (err, ref)      # activations are quantised too
     assert sm100.Workspace.get("cuda").check() == 0
+
+
+@pytest.mark.parametrize("idx", [0, 1, 2, 3, 4])
+def test_decode_step_logits_from_the_cuda_graph_match_cpu(idx):
+    """Steps 2+ of a generation replay a CUDA graph (packed input upload, decode kernels, LM head, arg-max). The
+    logits the graph left behind for the LAST step are compared with the fp32 CPU model run over the same token
+    history as one prompt: decode kernels, KV / recurrent state carried across steps and the graph's input
+    packing all have to be right for them to agree."""
+    from legion_b200.engine.types import GenerateRequest, SamplingParams
+    cfg = _cfgs()[idx]
+    w32 = {k: (v.bfloat16().float() if v.dtype == torch.float32 and v.dim() > 1 else v)
+           for k, v in random_weights(cfg, "cpu", torch.float32, seed=3, std=0.05).items()}
+    wgpu = {k: (v.bfloat16() if v.dim() > 1 and not k.endswith("conv_w") else v).cuda() for k, v in w32.items()}
+    ec = dict(ctx_size=512, max_seqs=4, block_size=64, prefill_chunk=128, max_batch_tokens=256, prefix_cache=False)
+    gpu = build_engine(cfg, weights=wgpu, device="cuda", engine_cfg=EngineConfig(cuda_graphs=True, **ec), start=False)
+    prompt = torch.randint(0, 255, (150,), generator=torch.Generator().manual_seed(7)).tolist()
+    gpu.generate(GenerateRequest(prompt_tokens=prompt, sampling=SamplingParams(max_tokens=16, ignore_eos=True)))
+    gpu._drain(block=False)
+    for _ in range(40):
+        gpu._admit()
+        if gpu.running and len(gpu.running[0].tokens) >= len(prompt) + 5:
+            break
+        gpu.step()
+    seq = gpu.running[0]
+    assert gpu._graphs is not None and gpu._graphs.replays >= 3
+    entry = next(iter(gpu._graphs.entries.values()))
+    got = entry.logits[:1].float().cpu()
+    history = list(seq.tokens[:-1])                    # the last step's input: everything before the token it picked
+    assert int(got.argmax()) == seq.tokens[-1]
+    cpu = build_engine(cfg, weights=w32, engine_cfg=EngineConfig(**ec), start=False)
+    s2 = cpu.prepare(GenerateRequest(prompt_tokens=history, sampling=SamplingParams(max_tokens=2, ignore_eos=True)))
+    cpu.waiting.push(s2)
+    cpu._admit()
+    rows, p0 = [], 0
+    want = None
+    while p0 < len(history):                           # chunked like any prompt; the last chunk's last row is the one
+        n = min(128, len(history) - p0)
+        out = cpu.model.forward(cpu.build_batch([(s2, p0, n)]), cpu.kv, cpu.states)
+        want = out.logits[-1:].float()
+        p0 += n
+    err = (got - want).abs().max().item()
+    ref = want.abs().max().item()
+    assert err < 0.1 * ref + 0.1, (err, ref)
+    from legion_b200.ops.sm100 import Workspace
+    assert Workspace.get("cuda").check() == 0

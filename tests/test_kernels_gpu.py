@@ -764,3 +764,71 @@ def test_mamba2_scan_matches_token_serial_reference(nh, hd, ng, ds, lens):
     got = sm100.mamba2_scan(xbc, dt, z, A, D, dtb, state, cu, slots, nh, hd, ng, ds)
     assert float((got.float() - want).abs().max()) < 0.02 * float(want.abs().max()) + 0.02
     assert float((state - want_state).abs().max()) < 1e-3 * float(want_state.abs().max()) + 1e-4
+
+
+# ------------------------------------------------------------------------------------------------
+# long contexts: the same kernels at 8K and 32K keys (block tables of hundreds of pages, many key
+# splits, accumulation over hundreds of tiles)
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("D,Hq,Hkv,page,ctx", [(128, 32, 4, 64, [8192, 32768, 5001]), (256, 16, 2, 64, [32768, 8193]),
+                                               (128, 8, 8, 16, [8192, 1, 12000])])
+def test_paged_decode_long_context(D, Hq, Hkv, page, ctx):
+    torch.manual_seed(D + Hq + page)
+    B = len(ctx)
+    width = (max(ctx) + page - 1) // page
+    n_blocks = width + 40
+    kc, vc = make_cache(n_blocks, page, Hkv, D)
+    bt = torch.stack([torch.randperm(n_blocks, device=DEV)[:width] for _ in range(B)]).int()
+    q = rnd(B, Hq, D)
+    ctx_t = torch.tensor(ctx, device=DEV, dtype=torch.int32)
+    scale = D ** -0.5
+    want = ref.paged_attention(q, kc, vc, bt, ctx_t, torch.arange(B + 1), scale)
+    for ns in (None, 1, 7):
+        out = sm().paged_decode(q, kc, vc, bt, ctx_t, scale, n_splits=ns)
+        status_ok()
+        close(out, want, 2e-2, 2e-2)
+    wantw = ref.paged_attention(q, kc, vc, bt, ctx_t, torch.arange(B + 1), scale, window=4096)
+    close(sm().paged_decode(q, kc, vc, bt, ctx_t, scale, window=4096), wantw, 2e-2, 2e-2)
+    status_ok()
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,page,q_lens,ctx", [(128, 4, 2, 64, [1024, 300], [32768, 8192 + 300]),
+                                                      (256, 2, 1, 64, [700], [8192 + 700]),
+                                                      (128, 4, 4, 32, [8192], [8192])])
+def test_prefill_attn_long_context(D, Hq, Hkv, page, q_lens, ctx):
+    """Prompt chunks at the end of 8K / 32K keys already in the cache, and one whole 8K prompt."""
+    torch.manual_seed(D + page + len(q_lens))
+    width = (max(ctx) + page - 1) // page + 1
+    n_blocks = width + 30
+    kc, vc = make_cache(n_blocks, page, Hkv, D)
+    bt = torch.stack([torch.randperm(n_blocks, device=DEV)[:width] for _ in q_lens]).int()
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    cu_t = torch.tensor(cu, device=DEV, dtype=torch.int32)
+    q = rnd(cu[-1], Hq, D)
+    ctx_t = torch.tensor(ctx, device=DEV, dtype=torch.int32)
+    scale = D ** -0.5
+    out = sm().prefill_attn(q, kc, vc, cu_t, ctx_t, bt, max(q_lens), scale)
+    status_ok()
+    want = ref.paged_attention(q, kc, vc, bt, ctx_t, cu_t, scale)
+    close(out, want, 3e-2, 3e-2)
+
+
+@pytest.mark.parametrize("nh,page,q_lens,ctx,splits", [(128, 64, [1, 1], [8192, 32768], None),
+                                                       (16, 64, [130, 1], [8192 + 130, 20000], 5)])
+def test_mla_attn_long_context(nh, page, q_lens, ctx, splits):
+    torch.manual_seed(nh + len(ctx))
+    width = (max(ctx) + page - 1) // page + 1
+    n_blocks = width + 20
+    cache = (torch.randn(n_blocks, page, 1, 576, device=DEV) * 0.5).bfloat16()
+    bt = torch.stack([torch.randperm(n_blocks, device=DEV)[:width] for _ in q_lens]).int()
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    q_abs = (torch.randn(cu[-1], nh, 576, device=DEV) * 0.5).bfloat16()
+    scale = 192 ** -0.5
+    out = sm().mla_attn(q_abs, cache, torch.tensor(cu, device=DEV, dtype=torch.int32),
+                        torch.tensor(ctx, device=DEV, dtype=torch.int32), bt, page, max(q_lens), scale, n_splits=splits)
+    status_ok()
+    close(out, _mla_reference(q_abs, cache, bt, ctx, cu, page, scale), 3e-2, 3e-2)
