@@ -974,9 +974,13 @@ class LmEngine(Engine):
         step_items = []                          # (seq, first position, fed tokens, kept rows, batch index)
         all_plain = all(s.req.sampling.greedy and s.req.sampling.plain and s.constraint is None for s, _, _ in rows)
         device_picks = picked
+        device_accept = None                     # batch index -> (accepted drafts, token after them), from the device
         if device_picks is None and logits is not None and logits.shape[0] and all_plain:
             from .. import ops
-            device_picks = ops.argmax(logits).tolist()
+            if verify and logits.is_cuda:
+                device_accept, device_picks = self._accept_on_device(rows, logits)
+            else:
+                device_picks = ops.argmax(logits).tolist()
         logits_host = None
         if logits is not None and not all_plain:
             logits_host = logits.float().cpu()
@@ -1006,7 +1010,11 @@ class LmEngine(Engine):
             accepted: List[int] = []
             lps: List[Optional[TokenLogprob]] = []
             k = n - 1
-            for j in range(n):
+            if device_accept is not None and bi in device_accept:
+                a, bonus = device_accept[bi]
+                accepted = list(s.drafts[:a]) + [bonus]
+                lps = [None] * len(accepted)
+            for j in range(n if not accepted else 0):
                 row = logits_host[r + j] if logits_host is not None else None
                 dp = device_picks[r + j] if device_picks is not None else None
                 if j < k:
@@ -1041,6 +1049,45 @@ class LmEngine(Engine):
             live = [s for s, _, _ in rows if s in self.running and s.phase == "decode"]
             if live and len(live) <= self.cfg.spec_max_batch:
                 self.drafter.draft_batch(live, self.cfg.spec_k)
+
+    def _accept_on_device(self, rows, logits):
+        """Greedy verification without bringing the step's arg-max rows to the host: the arg-max of every logits
+        row, then one small kernel that walks each sequence's drafts against them and returns (accepted drafts,
+        token after the accepted prefix) per sequence: two integers per sequence come back instead of one per row
+        (``csrc/spec.cu``; the reference's device-side accept is ``src/cuda/mtp_cond.cu:33``). Returns
+        ({batch index: (accepted, next token)} for the decode rows, per-row picks for prompt rows that end here)."""
+        from .. import ops
+        dev = logits.device
+        groups = []                               # (batch index, first logits row, rows, drafts)
+        r = 0
+        for bi, (s, p0, n) in enumerate(rows):
+            if s.phase == "prefill":
+                if p0 + n >= s.n_prompt:
+                    groups.append((bi, r, 1, []))
+                    r += 1
+                continue
+            groups.append((bi, r, n, list(s.drafts[:n - 1])))
+            r += n
+        G = len(groups)
+        maxd = max(1, max(len(g[3]) for g in groups))
+        host = torch.zeros(G, maxd + 2, dtype=torch.int32)
+        for i, (_, r0, _, d) in enumerate(groups):
+            host[i, 0], host[i, 1] = r0, len(d)
+            if d:
+                host[i, 2:2 + len(d)] = torch.tensor(d, dtype=torch.int32)
+        packed = host.to(dev, non_blocking=True)
+        target = ops.sm100.argmax(logits)
+        acc, bonus, _ = ops.sm100.spec_accept(target, packed[:, 0].contiguous(), packed[:, 2:].contiguous(),
+                                              packed[:, 1].contiguous())
+        res = torch.stack([acc, bonus]).cpu().tolist()
+        accept = {}
+        picks: List[Optional[int]] = [None] * int(logits.shape[0])
+        for i, (bi, r0, n, d) in enumerate(groups):
+            if rows[bi][0].phase == "prefill":
+                picks[r0] = res[1][i]
+            else:
+                accept[bi] = (res[0][i], res[1][i])
+        return accept, picks
 
     def _verify_one(self, s: Seq, row, device_pick, draft: int):
         """One draft token against the target's row: greedy = must equal the arg-max; sampled = exact

@@ -250,3 +250,34 @@ def test_decode_step_logits_from_the_cuda_graph_match_cpu(idx):
     assert err < 0.1 * ref + 0.1, (err, ref)
     from legion_b200.ops.sm100 import Workspace
     assert Workspace.get("cuda").check() == 0
+
+
+@pytest.mark.parametrize("idx", [0, 1])
+def test_speculative_verify_accepts_on_the_device(idx):
+    """n-gram drafting on a GPU engine: verify steps take their (accepted drafts, next token) per sequence from the
+    device-side accept kernel. The drafts of a repetitive prompt are accepted, and the greedy text equals the text
+    of the same engine without drafting for as long as both pick the same token from (numerically slightly
+    different) verify and decode kernels: the first divergence, if any, must come late."""
+    cfg = _cfgs()[idx]
+    w32 = random_weights(cfg, "cpu", torch.float32, seed=3, std=0.05)
+    wgpu = {k: (v.bfloat16() if v.dim() > 1 and not k.endswith("conv_w") else v).cuda() for k, v in w32.items()}
+    ec = dict(ctx_size=512, max_seqs=4, block_size=64, prefill_chunk=128, max_batch_tokens=256, prefix_cache=False)
+    prompt = ([11, 12, 13, 14, 15, 16, 17, 18] * 12)[:90]
+    plain = build_engine(cfg, weights=wgpu, device="cuda", engine_cfg=EngineConfig(**ec))
+    a = plain.generate_text(tokens=prompt, max_tokens=24, ignore_eos=True)
+    plain.shutdown()
+    spec = build_engine(cfg, weights=wgpu, device="cuda", engine_cfg=EngineConfig(spec="ngram", spec_k=3, **ec))
+    b = spec.generate_text(tokens=prompt, max_tokens=24, ignore_eos=True)
+    st = spec.stats()
+    spec.shutdown()
+    assert a.error is None and b.error is None and len(b.token_ids) == 24
+    if idx == 0:          # (the hybrid model's random text may offer the n-gram drafter nothing to propose)
+        assert st.spec_verify_steps > 0 and st.spec_draft_tokens > 0
+    same = 0
+    for x, y in zip(a.token_ids, b.token_ids):
+        if x != y:
+            break
+        same += 1
+    assert same >= 8, (a.token_ids, b.token_ids)
+    from legion_b200.ops.sm100 import Workspace
+    assert Workspace.get("cuda").check() == 0
