@@ -248,6 +248,10 @@ def create_app(engine: Engine, cfg: Optional[ServerConfig] = None) -> FastAPI:
     @app.get("/metrics")
     async def prom():
         metrics.update_engine(engine.stats())
+        pctx = getattr(getattr(engine, "model", None), "pctx", None)
+        if pctx is not None:
+            metrics.update_parallel(pctx.stats)
+        metrics.sample_gpus()
         return PlainTextResponse(metrics.render(), media_type="text/plain; version=0.0.4")
 
     def stats_snapshot() -> dict:

@@ -45,7 +45,27 @@ class Metrics:
         self.gpu = {n: Gauge(f"legion_gpu_{n}", d, ["gpu"], registry=r) for n, d in (
             ("nvlink_rx_bytes", "NVLink bytes received"), ("nvlink_tx_bytes", "NVLink bytes sent"),
             ("pcie_rx_bytes", "PCIe bytes received"), ("pcie_tx_bytes", "PCIe bytes sent"),
-            ("memory_busy_seconds", "memory controller busy time"), ("sm_busy_seconds", "SM busy time"))}
+            ("memory_busy_seconds", "memory controller busy time"), ("sm_busy_seconds", "SM busy time"),
+            ("sm_clock_mhz", "SM clock"), ("power_watts", "board power"), ("memory_used_bytes", "HBM in use"))}
+        # per-stage host time of the engine step (plan / build / forward / finish), accumulated
+        self.e_host_ms = Gauge("legion_engine_host_ms", "host time per step phase, accumulated (ms)", ["phase"], registry=r)
+        # KV / prefix-cache tiers
+        self.e_swap_out = g("kv_swap_out", "preempted sequences parked in host memory")
+        self.e_swap_in = g("kv_swap_in", "parked sequences copied back")
+        self.e_prefix_lookup = g("prefix_cache_lookup_tokens", "prompt tokens looked up in the prefix cache")
+        self.e_prefix_spill = g("prefix_host_spilled", "prefix-cache blocks spilled to the host tier")
+        self.e_prefix_restore = g("prefix_host_restored", "prefix-cache blocks restored from the host tier")
+        # rooflines: the measured peaks of this machine and where the running engine sits against them
+        rf = lambda n, d: Gauge(f"legion_roofline_{n}", d, registry=r)
+        self.r_hbm = rf("hbm_gbs", "measured copy bandwidth (GB/s)")
+        self.r_bf16 = rf("bf16_tflops", "measured cuBLAS bf16 throughput (TFLOP/s)")
+        self.r_nvlink = rf("nvlink_gbs_per_direction", "measured peer-copy bandwidth per direction (GB/s)")
+        self.r_step_floor = rf("step_floor_ms", "bytes a decode step must read / measured copy bandwidth (ms)")
+        self.r_step_frac = rf("step_bandwidth_fraction", "step floor / measured step time")
+        # tensor-parallel communication of this rank
+        self.tp_reductions = Gauge("legion_tp_all_reduce_calls", "all-reduce calls of this rank", registry=r)
+        self.tp_bytes = Gauge("legion_tp_all_reduce_bytes", "bytes reduced by this rank", registry=r)
+        self._busy = {}
 
     def update_engine(self, st):
         self.e_running.set(st.running)
@@ -66,6 +86,86 @@ class Metrics:
         self.e_model_bytes.set(st.model_bytes_step)
         for p, n in st.waiting_by_priority.items():
             self.e_waiting_prio.labels(priority=str(p)).set(n)
+        for phase, ms in (st.host_ms or {}).items():
+            self.e_host_ms.labels(phase=phase).set(ms)
+        self.e_swap_out.set(st.kv_swap_out)
+        self.e_swap_in.set(st.kv_swap_in)
+        self.e_prefix_lookup.set(st.prefix_cache_lookup_tokens)
+        self.e_prefix_spill.set(st.prefix_host_spilled)
+        self.e_prefix_restore.set(st.prefix_host_restored)
+        self.update_roofline(st)
+
+    def update_roofline(self, st, peaks=None):
+        """Measured peaks and the step's distance from the copy-bandwidth floor."""
+        if peaks is None:
+            from ..hw.gpu import NVLINK_GBS_PER_DIR, measured_peaks
+            peaks = dict(measured_peaks(), nvlink_gbs=NVLINK_GBS_PER_DIR)
+        self.r_hbm.set(peaks["hbm_gbs"])
+        self.r_bf16.set(peaks["bf16_tflops"])
+        self.r_nvlink.set(peaks.get("nvlink_gbs", 0.0))
+        floor_ms = st.model_bytes_step / (peaks["hbm_gbs"] * 1e9) * 1e3 if st.model_bytes_step else 0.0
+        self.r_step_floor.set(floor_ms)
+        self.r_step_frac.set(floor_ms / st.step_ms_ewma if st.step_ms_ewma > 0 else 0.0)
+
+    def update_parallel(self, stats: dict):
+        """``ParallelCtx.stats`` of this rank."""
+        self.tp_reductions.set(stats.get("all_reduce", 0))
+        self.tp_bytes.set(stats.get("bytes", 0))
+
+    def sample_gpus(self, nvml=None, now=None):
+        """Reads (never writes) NVML: NVLink and PCIe byte counters, utilisation integrated into busy seconds, clocks,
+        power and memory of every visible GPU. ``nvml``: the pynvml module (a fake in tests); absent NVML leaves the
+        gauges at zero."""
+        import time
+        if nvml is None:
+            try:
+                import pynvml as nvml
+                nvml.nvmlInit()
+            except Exception:
+                return 0
+        now = time.monotonic() if now is None else now
+        n = 0
+        try:
+            count = nvml.nvmlDeviceGetCount()
+        except Exception:
+            return 0
+        for i in range(count):
+            try:
+                h = nvml.nvmlDeviceGetHandleByIndex(i)
+            except Exception:
+                continue
+            lab = str(i)
+
+            def put(name, fn):
+                try:
+                    self.gpu[name].labels(gpu=lab).set(fn())
+                except Exception:
+                    pass
+            # NVLink throughput counters are cumulative KiB per device (field values, summed over the links)
+            def nvlink(field):
+                vals = nvml.nvmlDeviceGetFieldValues(h, [field])
+                return float(vals[0].value.ullVal) * 1024.0
+            if hasattr(nvml, "NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_RX"):
+                put("nvlink_rx_bytes", lambda: nvlink(nvml.NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_RX))
+                put("nvlink_tx_bytes", lambda: nvlink(nvml.NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_TX))
+            put("pcie_rx_bytes", lambda: nvml.nvmlDeviceGetPcieThroughput(h, nvml.NVML_PCIE_UTIL_RX_BYTES) * 1024.0)
+            put("pcie_tx_bytes", lambda: nvml.nvmlDeviceGetPcieThroughput(h, nvml.NVML_PCIE_UTIL_TX_BYTES) * 1024.0)
+            put("sm_clock_mhz", lambda: nvml.nvmlDeviceGetClockInfo(h, nvml.NVML_CLOCK_SM))
+            put("power_watts", lambda: nvml.nvmlDeviceGetPowerUsage(h) / 1000.0)
+            put("memory_used_bytes", lambda: nvml.nvmlDeviceGetMemoryInfo(h).used)
+            try:
+                u = nvml.nvmlDeviceGetUtilizationRates(h)
+                last, sm_s, mem_s = self._busy.get(i, (now, 0.0, 0.0))
+                dt = max(0.0, now - last)
+                sm_s += dt * u.gpu / 100.0
+                mem_s += dt * u.memory / 100.0
+                self._busy[i] = (now, sm_s, mem_s)
+                self.gpu["sm_busy_seconds"].labels(gpu=lab).set(sm_s)
+                self.gpu["memory_busy_seconds"].labels(gpu=lab).set(mem_s)
+            except Exception:
+                pass
+            n += 1
+        return n
 
     def render(self) -> str:
         return generate_latest(self.registry).decode()

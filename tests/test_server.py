@@ -205,3 +205,65 @@ def test_tls_listener_serves_https(tmp_path):
     finally:
         server.should_exit = True
         th.join(timeout=10)
+
+
+def test_metric_families_roofline_stages_parallel_and_gpu_counters_from_a_fake_nvml():
+    """Roofline, per-phase host time, KV / prefix tiers, tensor-parallel traffic and the GPU counter family; the GPU
+    counters are read from a fake NVML (reads only: nothing in the sampler sets anything)."""
+    from types import SimpleNamespace as NS
+
+    from legion_b200.engine.types import EngineStats
+    from legion_b200.server.metrics import Metrics
+    m = Metrics()
+    st = EngineStats(running=2, model_bytes_step=13_100_000_000, step_ms_ewma=4.0, kv_swap_out=3, prefix_host_spilled=5)
+    st.host_ms.update(plan=1.5, forward=7.0)
+    m.update_engine(st)
+    m.update_roofline(st, peaks={"hbm_gbs": 6550.0, "bf16_tflops": 1654.0, "nvlink_gbs": 770.0})
+    m.update_parallel({"all_reduce": 96, "bytes": 96 * 65536})
+
+    calls = []
+
+    class FakeNvml:
+        NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_RX, NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_TX = 138, 139
+        NVML_PCIE_UTIL_RX_BYTES, NVML_PCIE_UTIL_TX_BYTES, NVML_CLOCK_SM = 1, 0, 1
+
+        def __getattr__(self, name):                       # any call that is not a read below fails the test
+            raise AssertionError(f"unexpected NVML call {name}")
+
+        def nvmlDeviceGetCount(self):
+            return 2
+
+        def nvmlDeviceGetHandleByIndex(self, i):
+            return i
+
+        def nvmlDeviceGetFieldValues(self, h, fields):
+            calls.append(("field", h, fields[0]))
+            return [NS(value=NS(ullVal=1000 * (h + 1) + (fields[0] - 138)))]
+
+        def nvmlDeviceGetPcieThroughput(self, h, which):
+            return 10 + which
+
+        def nvmlDeviceGetClockInfo(self, h, which):
+            return 1965
+
+        def nvmlDeviceGetPowerUsage(self, h):
+            return 650_000
+
+        def nvmlDeviceGetMemoryInfo(self, h):
+            return NS(used=50 << 30)
+
+        def nvmlDeviceGetUtilizationRates(self, h):
+            return NS(gpu=50, memory=25)
+
+    fake = FakeNvml()
+    assert m.sample_gpus(fake, now=100.0) == 2
+    assert m.sample_gpus(fake, now=104.0) == 2             # 4 s at 50 % / 25 % busy
+    text = m.render()
+    for want in ('legion_engine_host_ms{phase="forward"} 7.0', "legion_engine_kv_swap_out 3.0",
+                 "legion_engine_prefix_host_spilled 5.0", "legion_roofline_hbm_gbs 6550.0",
+                 "legion_roofline_step_floor_ms 2.0", "legion_roofline_step_bandwidth_fraction 0.5",
+                 "legion_tp_all_reduce_calls 96.0", 'legion_gpu_nvlink_rx_bytes{gpu="1"} 2.048e+06',
+                 'legion_gpu_nvlink_tx_bytes{gpu="0"} 1.025024e+06', 'legion_gpu_sm_busy_seconds{gpu="0"} 2.0',
+                 'legion_gpu_memory_busy_seconds{gpu="1"} 1.0', 'legion_gpu_power_watts{gpu="0"} 650.0',
+                 'legion_gpu_sm_clock_mhz{gpu="1"} 1965.0'):
+        assert want in text, want
