@@ -257,6 +257,7 @@ def main(argv=None):
             # ---- e2e through the engine's step (pinned H2D of inputs + D2H of picks every step)
             pdist.barrier(); torch.cuda.synchronize()
             h2d0, d2h0, rep0 = graphs.h2d_bytes, graphs.d2h_bytes, graphs.replays
+            host0 = dict(eng._stats.host_ms)
             t_e2e0 = time.perf_counter()
             for _ in range(K):
                 eng.step()
@@ -266,7 +267,10 @@ def main(argv=None):
             assert replays == K, "decode steps did not run through the captured graph"
             row["e2e"] = {"value": round(U * K / e2e_s, 2), "unit": "tok/s",
                           "h2d_bytes_per_step": int((graphs.h2d_bytes - h2d0) / replays),
-                          "d2h_bytes_per_step": int((graphs.d2h_bytes - d2h0) / replays), "steps": K}
+                          "d2h_bytes_per_step": int((graphs.d2h_bytes - d2h0) / replays), "steps": K,
+                          # host time per step by phase (forward = pack + upload + graph launch + wait for the picks)
+                          "host_ms_per_step": {k: round((v - host0.get(k, 0.0)) / K, 4)
+                                               for k, v in eng._stats.host_ms.items()}}
         assert len(eng.running) == U and all(not s.finished for s in eng.running), \
             "a sequence finished before the timed region: the step no longer carries the full batch"
         entry = graphs.entries[graphs.bucket(U)]
