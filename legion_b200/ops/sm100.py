@@ -106,16 +106,19 @@ def have_ext() -> bool:
 NUM_SMS = 148
 
 # tuning knobs (environment: LB_TUNE="decode_fixed_tiles=2,dense_route=1")
-TUNE = {"nv4_sorted": 1, "nv4_sorted_bn": 64, "gdn_chunk": 1, "decode_fixed_tiles": 2, "fused_plan": 1, "fused_router": 1, "dense_route": 1, "pdl": 1, "route_norm": 0, "mla_head_gemm": 1}
+TUNE = {"decode_lanes": 2, "nv4_sorted": 1, "nv4_sorted_bn": 64, "gdn_chunk": 1, "decode_fixed_tiles": 2, "fused_plan": 1, "fused_router": 1, "dense_route": 1, "pdl": 1, "route_norm": 0, "mla_head_gemm": 1}
 for _kv in os.environ.get("LB_TUNE", "").split(","):
     if "=" in _kv:
         TUNE[_kv.split("=")[0].strip()] = int(_kv.split("=")[1])
 
 
 class Workspace:
-    """Per-device scratch shared by all kernels on that device's compute stream."""
+    """Per-device scratch shared by all kernels on that device's compute stream. A decode step that runs as several
+    concurrent lanes (``engine.cuda_graphs``: independent halves of the batch on parallel branches of one CUDA graph)
+    gives every lane a workspace of its own: ``Workspace.lane`` selects it while that lane's launches are issued."""
 
     _by_device: dict = {}
+    lane: int = 0
 
     def __init__(self, device: torch.device):
         self.device = device
@@ -130,10 +133,11 @@ class Workspace:
         device = torch.device(device)
         if device.index is None:
             device = torch.device("cuda", torch.cuda.current_device())
-        ws = cls._by_device.get(device)
+        key = device if cls.lane == 0 else (device, cls.lane)
+        ws = cls._by_device.get(key)
         if ws is None:
             ws = cls(device)
-            cls._by_device[device] = ws
+            cls._by_device[key] = ws
         return ws
 
     def buf(self, key, shape, dtype):
@@ -150,6 +154,12 @@ class Workspace:
         v = int(self.status[0].item())
         if v:
             self.status.zero_()
+        for key, other in list(self._by_device.items()):      # the other lanes of this device
+            if isinstance(key, tuple) and key[0] == self.device and other is not self:
+                ov = int(other.status[0].item())
+                if ov:
+                    other.status.zero_()
+                    v = v or ov
         return v
 
 

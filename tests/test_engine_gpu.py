@@ -281,3 +281,40 @@ def test_speculative_verify_accepts_on_the_device(idx):
     assert same >= 8, (a.token_ids, b.token_ids)
     from legion_b200.ops.sm100 import Workspace
     assert Workspace.get("cuda").check() == 0
+
+
+@pytest.mark.parametrize("idx", [0, 1])
+def test_decode_step_as_two_concurrent_lanes_gives_the_same_tokens(idx):
+    """From 64 rows a decode step's graph runs the two halves of the batch on parallel branches, each with its own
+    workspace. Fifty greedy sequences must produce exactly the tokens of the single-lane graph."""
+    from legion_b200.engine.types import GenerateRequest, SamplingParams
+    from legion_b200.ops import sm100
+    cfg = _cfgs()[idx]
+    w32 = random_weights(cfg, "cpu", torch.float32, seed=3, std=0.05)
+    wgpu = {k: (v.bfloat16() if v.dim() > 1 and not k.endswith("conv_w") else v).cuda() for k, v in w32.items()}
+    ec = dict(ctx_size=256, max_seqs=64, block_size=64, prefill_chunk=256, max_batch_tokens=2048, prefix_cache=False)
+    g = torch.Generator().manual_seed(9)
+    prompts = [torch.randint(0, 255, (int(n),), generator=g).tolist() for n in torch.randint(5, 40, (50,), generator=g)]
+    runs = []
+    for lanes in (1, 2):
+        old = sm100.TUNE["decode_lanes"]
+        sm100.TUNE["decode_lanes"] = lanes
+        try:
+            eng = build_engine(cfg, weights=wgpu, device="cuda", engine_cfg=EngineConfig(**ec), start=False)
+            streams = [eng.generate(GenerateRequest(prompt_tokens=p, sampling=SamplingParams(max_tokens=8, ignore_eos=True)))
+                       for p in prompts]
+            eng._drain(block=False)
+            for _ in range(200):
+                eng._admit()
+                if not eng.running and len(eng.waiting) == 0:
+                    break
+                eng.step()
+            runs.append([s.collect().token_ids for s in streams])
+            assert eng._graphs.replays > 0
+            assert (eng._graphs._lanes(64) == 2) == (lanes == 2)
+            eng.shutdown()
+        finally:
+            sm100.TUNE["decode_lanes"] = old
+    assert all(len(t) == 8 for t in runs[1])
+    assert runs[0] == runs[1]
+    assert sm100.Workspace.get("cuda").check() == 0
