@@ -364,10 +364,19 @@ def bench_gdn(rows):
         state = torch.zeros(n_seq, nv, dk, dv, device="cuda")
         cu = torch.arange(0, (n_seq + 1) * L, L, device="cuda", dtype=torch.int32)
         slots = torch.arange(n_seq, device="cuda", dtype=torch.int32)
-        ms = timeit(lambda: sm100.gdn_recurrent(qkv, g, beta, state, cu, slots, nk, nv, dk, dv, False, dk ** -0.5),
-                    iters=5, flush=False)
-        rows.append(dict(kernel="gdn_recurrent", n_seq=n_seq, L=L, ms=ms, tok_s=T / ms * 1e3,
-                         state_gbs=n_seq * nv * dk * dv * 4 * 2 / ms / 1e6, peaks=src))
+        cu_host = list(range(0, (n_seq + 1) * L, L))
+        ms = timeit(lambda: sm100.gdn_recurrent(qkv, g, beta, state, cu, slots, nk, nv, dk, dv, False, dk ** -0.5,
+                                                cu_host=cu_host), iters=5, flush=False)
+        # prompts of >= 64 tokens run the chunked tensor-core scan (prep + scan kernels), decode rows the
+        # state-streaming kernel. Chunk-form FLOPs per 64-token chunk and head: K K^T, Q K^T, T V, T K (prep) and
+        # W S, Q' S, M D, D^T K' (scan), each 2 * 64 * 64 * 128 or 2 * 64 * 128 * 128
+        row = dict(kernel="gdn (chunked scan)" if L >= 64 else "gdn_recurrent", n_seq=n_seq, L=L, ms=ms,
+                   tok_s=T / ms * 1e3, state_gbs=n_seq * nv * dk * dv * 4 * 2 / ms / 1e6, peaks=src)
+        if L >= 64:
+            chunks = n_seq * ((L + 63) // 64) * nv
+            flops = chunks * (4 * 2 * 64 * 64 * 128 + 4 * 2 * 64 * 128 * 128)
+            row["tflops"] = flops / ms / 1e9
+        rows.append(row)
         print(rows[-1], flush=True)
 
 
