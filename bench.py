@@ -139,6 +139,8 @@ def main(argv=None):
                          "with mirrored tokens, partial outputs meeting in the layer's reduction (ep). auto: ep "
                          "from 4 GPUs for bf16 experts, always for NVFP4 experts")
     ap.add_argument("--no-fold", action="store_true", help="keep the shared expert as a dense FFN of its own")
+    ap.add_argument("--no-head-split", action="store_true",
+                    help="N > 1: every rank keeps the whole LM head instead of its slice of the vocabulary")
     ap.add_argument("--nvfp4-expand", action="store_true",
                     help="NVFP4 experts on the de-quantising GEMM (W4A16) instead of the native W4A4 path")
     ap.add_argument("--profile-range", action="store_true",
@@ -237,6 +239,7 @@ def main(argv=None):
                       block_size=64, prefix_cache=False, device=str(dev), model_name=spec["model"])
     model = Decoder(cfg, weights, pctx, max_position=ec.ctx_size + 8)
     model.fuse_gdn_in_proj()
+    head_split = (not a.no_head_split) and model.split_head()
     eng = LmEngine(model, tok, ec, start=False)
     graphs = eng._graphs
     assert graphs is not None, "decode steps must run from captured CUDA graphs"
@@ -320,7 +323,7 @@ def main(argv=None):
 
     par = "single GPU" if world == 1 else (f"tp{world}" + ("+ep(experts whole per rank, tokens mirrored)" if ep else ""))
     extra.update({"decode": {str(u): rows[u] for u in all_users}, "kernel_status_word": status,
-                  "comm_status_word": comm_status, "launches_per_step": headline.get("launches_per_step"),
+                  "comm_status_word": comm_status, "lm_head": "split by vocabulary rows" if head_split else "whole per rank", "launches_per_step": headline.get("launches_per_step"),
                   "shared_expert": ("stacked behind the routed experts (one slot of the grouped GEMMs)"
                                     if (nvfp4 and world == 1 and not a.no_fold and cfg.shared_ff) else
                                     ("whole on rank (layer % world), stacked behind that rank's routed experts"

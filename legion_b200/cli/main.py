@@ -172,6 +172,7 @@ def build_engine_from_args(a, start: bool = True):
     model = Decoder(cfg, w, pctx, max_position=ec.ctx_size + 8)
     if on_gpu:
         model.fuse_gdn_in_proj()
+        model.split_head()       # several ranks with the fused communicator: each keeps its slice of the vocabulary
     if getattr(a, "expert_weights", "bf16") == "nvfp4" and on_gpu and cfg.n_expert:
         if pctx.world == 1 and a.experts not in ("cache", "host", "ssd"):
             model.fold_shared_experts()      # the shared expert rides in the grouped GEMMs of decode steps

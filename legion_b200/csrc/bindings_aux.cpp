@@ -194,6 +194,21 @@ void bind_comm(pybind11::module_& m) {
                     reinterpret_cast<int*>(status.data_ptr()), cur_stream(), q) == 0,
                 "all_reduce_fused failed");
   });
+  m.def("argmax_exchange", [](std::vector<int64_t> buffers, std::vector<int64_t> signals, int64_t rank, int64_t ax_off,
+                              int64_t ax_rows, Tensor& seq, Tensor& done_ctr, const Tensor& val, const Tensor& idx,
+                              int64_t vocab_offset, Tensor& picks, int64_t budget_ns, Tensor& status) {
+    TORCH_CHECK(val.scalar_type() == at::kFloat && idx.scalar_type() == at::kInt && picks.scalar_type() == at::kInt &&
+                    val.is_contiguous() && idx.is_contiguous() && picks.is_contiguous() && idx.numel() >= val.numel() &&
+                    picks.numel() >= val.numel(), "argmax_exchange: (float value, int index) per row -> int picks");
+    c10::cuda::CUDAGuard guard(status.device());
+    auto p = make_peers(buffers, signals, rank);
+    TORCH_CHECK(lb::argmax_exchange_launch(p, ax_off, int(ax_rows), reinterpret_cast<uint32_t*>(seq.data_ptr()),
+                                           reinterpret_cast<unsigned int*>(done_ctr.data_ptr()), int(val.numel()),
+                                           val.data_ptr<float>(), idx.data_ptr<int>(), int(vocab_offset),
+                                           picks.data_ptr<int>(), uint64_t(budget_ns),
+                                           reinterpret_cast<int*>(status.data_ptr()), cur_stream()) == 0,
+                "argmax_exchange: too many rows for the exchange area");
+  });
   m.def("reduce_scatter_fused", [](std::vector<int64_t> buffers, std::vector<int64_t> signals, int64_t rank,
                                    int64_t buf_off, int64_t out_off, int64_t slot_base, Tensor& seq, Tensor& done_ctr,
                                    int64_t row0, int64_t n_rows, int64_t H, const OptT& residual, int64_t budget_ns,

@@ -253,6 +253,72 @@ int all_reduce_ll_launch(const CommPeers& peers, long buf_off, long ll_off, int 
   return cudaGetLastError() != cudaSuccess;
 }
 
+// Vocabulary-split LM head: every rank holds the arg-max (value, global token id) of its slice of the vocabulary for
+// each row; the ranks exchange these pairs as pushed flag-carrying lines (16 bytes per row and source) and each picks
+// the global best (larger value, then lower token id), so the greedy token of a step needs neither the full logits
+// nor a gather of them. One CTA, one thread per row (at most 1024 rows).
+__global__ void __launch_bounds__(1024) argmax_exchange_kernel(CommPeers peers, long ax_off, int ax_rows, uint32_t* seq_ptr,
+                                                               unsigned int* done_ctr, int rows,
+                                                               const float* __restrict__ val, const int* __restrict__ idx,
+                                                               int vocab_offset, int* __restrict__ picks,
+                                                               uint64_t budget_ns, int* status) {
+  griddep_wait();
+  griddep_launch();
+  const uint32_t seq = *reinterpret_cast<const volatile uint32_t*>(seq_ptr) + 1;
+  const int me = peers.rank, world = peers.world;
+  const long area = long(ax_rows) * 16;
+  const long par_off = ax_off + long(seq & 1u) * world * area;
+  const int row = threadIdx.x;
+  if (row < rows) {
+    const float v = val[row];
+    const int gi = idx[row] + vocab_offset;
+    for (int i = 1; i < world; ++i) {
+      const int p = (me + i) % world;
+      st_ll(reinterpret_cast<uint4*>(reinterpret_cast<char*>(peers.buffer[p]) + par_off + me * area + long(row) * 16),
+            __float_as_uint(v), uint32_t(gi), seq);
+    }
+    float bv = v;
+    int bi = gi;
+    const char* mine = reinterpret_cast<const char*>(peers.buffer[me]);
+    for (int r = 0; r < world; ++r) {
+      if (r == me) continue;
+      const uint4* src = reinterpret_cast<const uint4*>(mine + par_off + r * area + long(row) * 16);
+      uint64_t t0 = 0;
+      uint32_t spins = 0;
+      while (true) {
+        const uint4 a = ld_ll(src);
+        if (a.y == seq && a.w == seq) {
+          const float ov = __uint_as_float(a.x);
+          const int oi = int(a.z);
+          if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+          break;
+        }
+        if ((++spins & 0x3f) == 0) {
+          const uint64_t now = globaltimer_ns();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > budget_ns) {
+            atomicCAS(status, 0, ST_TIMEOUT_FLAG);
+            break;
+          }
+        }
+      }
+    }
+    picks[row] = bi;
+  }
+  comm_exit(seq_ptr, done_ctr, seq);
+}
+
+int argmax_exchange_launch(const CommPeers& peers, long ax_off, int ax_rows, uint32_t* seq_ptr, unsigned int* done_ctr,
+                           int rows, const float* val, const int* idx, int vocab_offset, int* picks, uint64_t budget_ns,
+                           int* status, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if (rows > ax_rows || rows > 1024 || peers.world > LB_MAX_RANKS || (ax_off % 16)) return 1;
+  const int threads = ((rows + 31) / 32) * 32;
+  launch_pdl(argmax_exchange_kernel, dim3(1), dim3(threads), 0, s, peers, ax_off, ax_rows, seq_ptr, done_ctr, rows, val,
+             idx, vocab_offset, picks, budget_ns, status);
+  return cudaGetLastError() != cudaSuccess;
+}
+
 // Reduce-scatter half of the two-shot form: this rank sums rows [row0, row0 + n_rows) over all peers in
 // rank order (+ residual), writing the reduced rows into its own symmetric buffer at out_off so the
 // all-gather half can fetch them, and into sum_out when given.

@@ -51,6 +51,11 @@ int all_reduce_ll_launch(const CommPeers& peers, long buf_off, long ll_off, int 
                          const float* norm_w, float eps, float w_offset, void* norm_out, long ldn, uint64_t budget_ns,
                          int* status, cudaStream_t s, const Nv4RowsOut& q = Nv4RowsOut{},
                          const CombineSrc& cs = CombineSrc{});
+// Greedy token of a vocabulary-split head: exchange of per-rank (best value, global token id) pairs as pushed
+// flag-carrying lines; ax_off: 2 (alternating) x world x ax_rows x 16 bytes inside every rank's symmetric buffer.
+int argmax_exchange_launch(const CommPeers& peers, long ax_off, int ax_rows, uint32_t* seq_ptr, unsigned int* done_ctr,
+                           int rows, const float* val, const int* idx, int vocab_offset, int* picks, uint64_t budget_ns,
+                           int* status, cudaStream_t s);
 int reduce_scatter_launch(const CommPeers& peers, long buf_off, long out_off, int slot_base, uint32_t* seq_ptr,
                           unsigned int* done_ctr, int row0, int n_rows, int H, const void* residual, long ldr, uint64_t budget_ns, int* status,
                           cudaStream_t s);

@@ -23,7 +23,7 @@ BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 
 class _Entry:
     __slots__ = ("graph", "B", "W", "pack_h", "pack_d", "batch", "picks", "picks_h", "logits", "n_ints", "arange",
-                 "bt_key", "pack_np", "all_picks", "all_picks_h")
+                 "bt_key", "pack_np", "all_picks", "all_picks_h", "logits_local")
 
 
 class DecodeGraphs:
@@ -107,6 +107,7 @@ class DecodeGraphs:
         e.picks = torch.zeros(B, dtype=torch.int32, device=dev)
         e.picks_h = torch.zeros(B, dtype=torch.int32).pin_memory()
         e.logits = None
+        e.logits_local = None
         lanes = self._lanes(B)
         if lanes == 1:
             parts = [(e.batch, 0, B)]
@@ -129,6 +130,12 @@ class DecodeGraphs:
             b, lo, hi = parts[i]
             WS.lane = i
             try:
+                if eng.model.head_split is not None:
+                    # vocabulary-split head: only (value, token id) pairs cross the ranks inside the graph; the
+                    # logits stay per rank and are gathered after the replay for the rows that need them
+                    out = eng.model.forward(b, eng.kv, eng.states, want_logits=False)
+                    e.logits_local = eng.model.greedy_picks(out.hidden, e.picks[lo:hi])
+                    return out
                 out = eng.model.forward(b, eng.kv, eng.states)
                 ops.sm100.argmax(out.logits, out=e.picks[lo:hi])
                 if lanes > 1:
@@ -160,7 +167,7 @@ class DecodeGraphs:
                     join = torch.cuda.Event()
                     join.record(st)
                 main.wait_event(join)
-            if lanes == 1:
+            if lanes == 1 and eng.model.head_split is None:
                 e.logits = out.logits
         e.graph = g
         self.entries[B] = e
@@ -250,4 +257,6 @@ class DecodeGraphs:
         self.replays += 1
         need_logits = any(not (s.req.sampling.greedy and s.req.sampling.plain and s.constraint is None)
                           for s, _, _ in rows)
+        if need_logits and e.logits is None and e.logits_local is not None:
+            return e.picks_h[:n].tolist(), eng.model.gather_logits(e.logits_local)[:n]
         return e.picks_h[:n].tolist(), (e.logits[:n] if need_logits else None)

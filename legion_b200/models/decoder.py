@@ -241,6 +241,7 @@ class Decoder:
         self.gdn_k_l = max(1, cfg.gdn_k_heads // tp)
         self.gdn_v_l = max(1, cfg.gdn_v_heads // tp)
         self.lm_head = weights.get("output", weights["tok_embd"])
+        self.head_split = None            # (first row, rows) of this rank's slice of the vocabulary (split_head)
         self.expert_cache: Dict[str, object] = {}     # layer prefix -> residency.ExpertCache (offload modes)
         self._mla_uk: Dict[str, torch.Tensor] = {}    # layer prefix -> W_uk^T per head (absorb projection, K-major)
 
@@ -677,13 +678,58 @@ class Decoder:
         _ = (resid, x_partial)
         return out
 
-    def logits(self, hidden):
+    def split_head(self) -> bool:
+        """Several ranks with the fused communicator: every rank keeps only its slice of the LM head's vocabulary
+        rows (the reference's ``src/model/core/head_split.rs``), so a step reads 1 / world of the head. Greedy
+        steps exchange (best value, token id) pairs (``greedy_picks``); callers that need the logits themselves get
+        them gathered (``logits``). Returns whether the head was split."""
+        pc = self.pctx
+        V = self.lm_head.shape[0]
+        if (self.head_split is not None or pc.world <= 1 or pc.comm != "fused" or pc.symm is None or V % pc.world
+                or not isinstance(self.lm_head, torch.Tensor) or not self.lm_head.is_cuda):
+            return False
+        n = V // pc.world
+        self.head_split = (pc.rank * n, n)
+        self.lm_head = self.lm_head[pc.rank * n:(pc.rank + 1) * n].contiguous()
+        if "output" in self.w:
+            self.w["output"] = self.lm_head         # the full copy is released
+        return True
+
+    def _local_logits(self, hidden):
         lg = ops.linear(hidden, self.lm_head, out_dtype=torch.float32)
         if self.cfg.logit_scale != 1.0:
             lg = lg * self.cfg.logit_scale
         if self.cfg.logit_softcap > 0:
             lg = torch.tanh(lg / self.cfg.logit_softcap) * self.cfg.logit_softcap
         return lg
+
+    def gather_logits(self, local):
+        """[rows, vocab / world] of every rank -> [rows, vocab] on every rank."""
+        import torch.distributed as dist
+        pc = self.pctx
+        R, n = local.shape
+        parts = torch.empty(pc.world, R, n, dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(parts, local.contiguous(), group=pc.group)
+        return parts.permute(1, 0, 2).reshape(R, pc.world * n)
+
+    def greedy_picks(self, hidden, out):
+        """Arg-max token of every row of ``hidden`` (already normalised) into ``out`` (int32). With a split head only
+        (value, token id) pairs cross the ranks. Returns this rank's logits (its vocabulary slice when split)."""
+        lg = self._local_logits(hidden)
+        if self.head_split is None:
+            ops.sm100.argmax(lg, out=out)
+            return lg
+        R = lg.shape[0]
+        ws = ops.sm100.Workspace.get(lg.device)
+        val = ws.buf("head_val", (R,), torch.float32)
+        idx = ws.buf("head_idx", (R,), torch.int32)
+        ops.sm100.argmax(lg, out=idx, out_val=val)
+        self.pctx.symm.argmax_exchange(val, idx, self.head_split[0], out)
+        return lg
+
+    def logits(self, hidden):
+        lg = self._local_logits(hidden)
+        return self.gather_logits(lg) if self.head_split is not None else lg
 
     def commit_replay(self, b: StepBatch, st: StatePool, commits):
         """After a verify step (state not advanced): replays the kept tokens of each sequence through the

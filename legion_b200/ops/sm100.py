@@ -1199,7 +1199,7 @@ def spec_accept(target, cu, draft, n_draft):
     return acc, bonus, rej
 
 
-def argmax(logits, out=None):
+def argmax(logits, out=None, out_val=None):
     C = ext()
     rows, V = logits.shape
     ws = Workspace.get(logits.device)
@@ -1208,7 +1208,7 @@ def argmax(logits, out=None):
     pi = ws.buf("argmax_i", (rows * nblk,), torch.int32)
     if out is None:
         out = torch.empty(rows, dtype=torch.int32, device=logits.device)
-    C.argmax(logits, pv, pi, out, None)
+    C.argmax(logits, pv, pi, out, out_val)
     return out
 
 

@@ -32,6 +32,7 @@ class SymmComm:
     N_SLOTS = 2
     TWO_SHOT_ROWS = 512
     LL_ROWS = 64          # decode-sized reductions push flag-carrying lines instead of exchanging flags and loading
+    AX_ROWS = 1024        # rows of one arg-max pair exchange (vocabulary-split head)
 
     def __init__(self, group, rank: int, world: int, device: torch.device, max_rows: int, hidden: int,
                  budget_ns: int = 5_000_000_000):
@@ -47,7 +48,8 @@ class SymmComm:
         self.ag_off = (self.rs_off + self.slot_bytes, self.rs_off + 2 * self.slot_bytes)
         self._ag_half = 0
         self.ll_off = self.slot_bytes * (self.N_SLOTS + 3)
-        nbytes = self.ll_off + 2 * world * self.LL_ROWS * hidden * 4
+        self.ax_off = self.ll_off + 2 * world * self.LL_ROWS * hidden * 4
+        nbytes = self.ax_off + 2 * world * self.AX_ROWS * 16
         self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
         self.handle = symm_mem.rendezvous(self.buf, group=group)
         self.buffer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
@@ -229,6 +231,17 @@ class SymmComm:
             x = slot
         _, summed = self.all_reduce_add_norm(x, None, None, 0.0, 0.0)
         return summed
+
+    def argmax_exchange(self, val: torch.Tensor, idx: torch.Tensor, vocab_offset: int, picks: torch.Tensor):
+        """Greedy token per row from every rank's (best value, index inside its vocabulary slice): one launch that
+        pushes the pairs to the peers and picks the global best (larger value, then lower token id) on every rank."""
+        if self._failed:
+            raise CommError(self._failed)
+        if val.numel() > self.AX_ROWS:
+            raise CommError("arg-max exchange of more rows than its area holds")
+        ext().argmax_exchange(self.buffer_ptrs, self.signal_ptrs, self.rank, self.ax_off, self.AX_ROWS, self.seq,
+                              self.done, val, idx, int(vocab_offset), picks, self.budget_ns, self.status)
+        return picks
 
     def end_step(self):
         """Pads the step to an even number of reductions (slot rotation across graph replays)."""

@@ -227,6 +227,8 @@ def case_engine_nv4(dev, comm_kind):
     pctx = ParallelCtx(RANK, WORLD, dist.group.WORLD, True, comm_kind, symm)
     model = Decoder(cfg, w, pctx, max_position=520)
     model.fuse_gdn_in_proj()
+    if comm_kind == "fused":
+        assert model.split_head()           # vocabulary-split LM head: greedy picks by (value, id) pair exchange
     eng = LmEngine(model, ByteTokenizer(cfg.vocab), EngineConfig(ctx_size=512, max_seqs=4, block_size=64, prefill_chunk=256,
                                                                  prefix_cache=False, device=str(dev)), start=False)
     say("engine built")
