@@ -212,7 +212,7 @@ void bind_comm(pybind11::module_& m) {
   m.def("reduce_scatter_fused", [](std::vector<int64_t> buffers, std::vector<int64_t> signals, int64_t rank,
                                    int64_t buf_off, int64_t out_off, int64_t slot_base, Tensor& seq, Tensor& done_ctr,
                                    int64_t row0, int64_t n_rows, int64_t H, const OptT& residual, int64_t budget_ns,
-                                   Tensor& status) {
+                                   Tensor& status, int64_t mc_ptr) {
     c10::cuda::CUDAGuard guard(status.device());
     auto p = make_peers(buffers, signals, rank);
     TORCH_CHECK(lb::reduce_scatter_launch(p, buf_off, out_off, int(slot_base),
@@ -220,18 +220,19 @@ void bind_comm(pybind11::module_& m) {
                                           reinterpret_cast<unsigned int*>(done_ctr.data_ptr()), int(row0), int(n_rows),
                                           int(H), residual.has_value() ? residual->data_ptr() : nullptr,
                                           residual.has_value() ? residual->stride(0) : 0, uint64_t(budget_ns),
-                                          reinterpret_cast<int*>(status.data_ptr()), cur_stream()) == 0,
+                                          reinterpret_cast<int*>(status.data_ptr()), cur_stream(),
+                                          reinterpret_cast<void*>(mc_ptr)) == 0,
                 "reduce_scatter_fused failed");
   });
   m.def("all_gather_fused", [](std::vector<int64_t> buffers, std::vector<int64_t> signals, int64_t rank,
                                int64_t src_off, int64_t slot_base, Tensor& seq, Tensor& done_ctr, int64_t T, int64_t H,
-                               Tensor& out, int64_t budget_ns, Tensor& status) {
+                               Tensor& out, int64_t budget_ns, Tensor& status, bool local_only) {
     c10::cuda::CUDAGuard guard(status.device());
     auto p = make_peers(buffers, signals, rank);
     TORCH_CHECK(lb::all_gather_launch(p, src_off, int(slot_base), reinterpret_cast<uint32_t*>(seq.data_ptr()),
                                       reinterpret_cast<unsigned int*>(done_ctr.data_ptr()), int(T), int(H),
                                       out.data_ptr(), out.stride(0), uint64_t(budget_ns),
-                                      reinterpret_cast<int*>(status.data_ptr()), cur_stream()) == 0,
+                                      reinterpret_cast<int*>(status.data_ptr()), cur_stream(), local_only ? 1 : 0) == 0,
                 "all_gather_fused failed");
   });
 }

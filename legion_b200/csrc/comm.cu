@@ -326,7 +326,7 @@ __global__ void __launch_bounds__(256) reduce_scatter_kernel(CommPeers peers, lo
                                                              int slot_base, uint32_t* seq_ptr, unsigned int* done_ctr, int row0,
                                                              int n_rows, int H,
                                                              const __nv_bfloat16* __restrict__ residual, long ldr,
-                                                             uint64_t budget_ns, int* status) {
+                                                             uint64_t budget_ns, int* status, char* mc_base) {
   __shared__ int s_ok;
   uint32_t seq;
   const bool entered = comm_enter(peers, slot_base, seq_ptr, budget_ns, status, &s_ok, &seq);
@@ -339,9 +339,18 @@ __global__ void __launch_bounds__(256) reduce_scatter_kernel(CommPeers peers, lo
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int r = 0; r < peers.world; ++r) {
-      const uint4 u =
-          reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(peers.buffer[r]) + buf_off + long(row) * H * 2)[v];
+    for (int r = 0; r < (mc_base ? 1 : peers.world); ++r) {
+      uint4 u;
+      if (mc_base) {
+        // NVLink multicast address of the same bytes on every rank: ONE load whose value is the sum over the ranks,
+        // added inside the switch with fp32 accumulation (one crossing per element instead of world - 1)
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w)
+                     : "l"(mc_base + buf_off + long(row) * H * 2 + long(v) * 16)
+                     : "memory");
+      } else {
+        u = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(peers.buffer[r]) + buf_off + long(row) * H * 2)[v];
+      }
       const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -364,21 +373,31 @@ __global__ void __launch_bounds__(256) reduce_scatter_kernel(CommPeers peers, lo
     __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
     for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-    reinterpret_cast<uint4*>(my + out_off + long(row) * H * 2)[v] = o;
+    if (mc_base) {
+      // one multicast store puts the reduced vector into EVERY rank's result region: the gather that follows only
+      // reads local memory
+      asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                   ::"l"(mc_base + out_off + long(row) * H * 2 + long(v) * 16), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w)
+                   : "memory");
+    } else {
+      reinterpret_cast<uint4*>(my + out_off + long(row) * H * 2)[v] = o;
+    }
   }
   comm_exit(seq_ptr, done_ctr, seq);
 }
 
 int reduce_scatter_launch(const CommPeers& peers, long buf_off, long out_off, int slot_base, uint32_t* seq_ptr, unsigned int* done_ctr,
                           int row0, int n_rows, int H, const void* residual, long ldr, uint64_t budget_ns, int* status,
-                          cudaStream_t s) {
+                          cudaStream_t s, void* mc_base) {
   if (H % 8 || peers.world > LB_MAX_RANKS) return 1;
+  if (mc_base && ((buf_off | out_off) % 16)) return 1;
   long work = long(n_rows) * (H / 8);
   int grid = int((work + 255) / 256);
   if (grid < 1) grid = 1;
   if (grid > 592) grid = 592;
   reduce_scatter_kernel<<<grid, 256, 0, s>>>(peers, buf_off, out_off, slot_base, seq_ptr, done_ctr, row0, n_rows, H,
-                                             static_cast<const __nv_bfloat16*>(residual), ldr, budget_ns, status);
+                                             static_cast<const __nv_bfloat16*>(residual), ldr, budget_ns, status,
+                                             static_cast<char*>(mc_base));
   return cudaGetLastError() != cudaSuccess;
 }
 
@@ -386,7 +405,7 @@ int reduce_scatter_launch(const CommPeers& peers, long buf_off, long out_off, in
 // symmetric buffer at src_off into the local dense output.
 __global__ void __launch_bounds__(256) all_gather_kernel(CommPeers peers, long src_off, int slot_base, uint32_t* seq_ptr,
                                                          unsigned int* done_ctr, int T, int H, __nv_bfloat16* __restrict__ out, long ldo,
-                                                         uint64_t budget_ns, int* status) {
+                                                         uint64_t budget_ns, int* status, int local_only) {
   __shared__ int s_ok;
   uint32_t seq;
   const bool entered = comm_enter(peers, slot_base, seq_ptr, budget_ns, status, &s_ok, &seq);
@@ -398,6 +417,7 @@ __global__ void __launch_bounds__(256) all_gather_kernel(CommPeers peers, long s
     const int v = int(i % nv);
     int owner = row / per;
     if (owner >= peers.world) owner = peers.world - 1;
+    if (local_only) owner = peers.rank;        // the reduced rows were multicast into every rank's region
     const uint4 u =
         reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(peers.buffer[owner]) + src_off + long(row) * H * 2)[v];
     reinterpret_cast<uint4*>(out + long(row) * ldo)[v] = u;
@@ -407,14 +427,14 @@ __global__ void __launch_bounds__(256) all_gather_kernel(CommPeers peers, long s
 
 int all_gather_launch(const CommPeers& peers, long src_off, int slot_base, uint32_t* seq_ptr,
                       unsigned int* done_ctr, int T, int H, void* out,
-                      long ldo, uint64_t budget_ns, int* status, cudaStream_t s) {
+                      long ldo, uint64_t budget_ns, int* status, cudaStream_t s, int local_only) {
   if (H % 8 || peers.world > LB_MAX_RANKS) return 1;
   long work = long(T) * (H / 8);
   int grid = int((work + 255) / 256);
   if (grid < 1) grid = 1;
   if (grid > 592) grid = 592;
   all_gather_kernel<<<grid, 256, 0, s>>>(peers, src_off, slot_base, seq_ptr, done_ctr, T, H, static_cast<__nv_bfloat16*>(out), ldo,
-                                         budget_ns, status);
+                                         budget_ns, status, local_only);
   return cudaGetLastError() != cudaSuccess;
 }
 

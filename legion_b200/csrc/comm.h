@@ -58,9 +58,9 @@ int argmax_exchange_launch(const CommPeers& peers, long ax_off, int ax_rows, uin
                            int* status, cudaStream_t s);
 int reduce_scatter_launch(const CommPeers& peers, long buf_off, long out_off, int slot_base, uint32_t* seq_ptr,
                           unsigned int* done_ctr, int row0, int n_rows, int H, const void* residual, long ldr, uint64_t budget_ns, int* status,
-                          cudaStream_t s);
+                          cudaStream_t s, void* mc_base = nullptr);   // mc_base: NVLink multicast address of the buffers (multimem)
 int all_gather_launch(const CommPeers& peers, long src_off, int slot_base, uint32_t* seq_ptr,
                       unsigned int* done_ctr, int T, int H, void* out,
-                      long ldo, uint64_t budget_ns, int* status, cudaStream_t s);
+                      long ldo, uint64_t budget_ns, int* status, cudaStream_t s, int local_only = 0);
 
 }  // namespace lb

@@ -17,10 +17,16 @@ from .context import ParallelCtx
 
 
 def no_multicast_default():
-    """Call before the first symmetric-memory rendezvous of a process. No kernel of this library uses multimem, so
-    the buffers need no NVLink multicast binding; a rank that dies while its memory is bound to a multicast object
+    """Call before the first symmetric-memory rendezvous of a process. By default no kernel of this library uses
+    multimem, so the buffers need no NVLink multicast binding (``LB_MULTIMEM=1`` turns the multimem form of the
+    prompt-sized reduction on and with it the binding); a rank that dies while its memory is bound to a multicast object
     can raise NVLink faults on its peers' GPUs. ``TORCH_SYMM_MEM_DISABLE_MULTICAST=0`` in the environment keeps
     PyTorch's default."""
+    if os.environ.get("LB_MULTIMEM", "0") == "1":
+        # opt-in: the prompt-sized reduction uses multimem.ld_reduce / multimem.st through the NVLink multicast
+        # mapping of the symmetric buffer, which the rendezvous then has to create
+        os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "0"
+        return
     os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
 

@@ -56,6 +56,16 @@ class SymmComm:
         self.signal_ptrs = [int(p) for p in self.handle.signal_pad_ptrs]
         self.base = self.buf.data_ptr()
         assert self.base == self.buffer_ptrs[rank]
+        # NVLink multicast address of the buffer (0 = not bound): with LB_MULTIMEM=1 the prompt-sized reduction loads
+        # each element ONCE, already summed over the ranks inside the switch (multimem.ld_reduce), and stores the
+        # result into every rank's region with one multicast store (multimem.st)
+        import os
+        self.mc_ptr = 0
+        if os.environ.get("LB_MULTIMEM", "0") == "1":
+            try:
+                self.mc_ptr = int(self.handle.multicast_ptr or 0)
+            except Exception:
+                self.mc_ptr = 0
         self.seq = torch.zeros(1, dtype=torch.int32, device=device)
         self.done = torch.zeros(1, dtype=torch.int32, device=device)
         self.gemm_ctrs = torch.zeros(2, dtype=torch.int32, device=device)
@@ -98,18 +108,19 @@ class SymmComm:
             combine = None
         off = cur.data_ptr() - self.base
         summed = torch.empty(T, H, dtype=torch.bfloat16, device=self.device)
-        if T >= self.TWO_SHOT_ROWS and self.world > 2:
+        if T >= self.TWO_SHOT_ROWS and (self.world > 2 or self.mc_ptr):
             # two-shot: each rank reduces its block of rows (+ residual) into its own result region,
-            # then every rank gathers all blocks; the norm runs on the gathered rows.
+            # then every rank gathers all blocks; the norm runs on the gathered rows. With the multicast mapping
+            # the reduction is one switch-side load per element and the result lands in every rank's region.
             per = (T + self.world - 1) // self.world
             row0 = min(T, self.rank * per)
             n_rows = max(0, min(T, row0 + per) - row0)
             out_off = self.rs_off      # rewritten only after the next call's flag round: every peer has left this one
             C = ext()
             C.reduce_scatter_fused(self.buffer_ptrs, self.signal_ptrs, self.rank, off, out_off, 0, self.seq, self.done,
-                                   row0, n_rows, H, res, self.budget_ns, self.status)
+                                   row0, n_rows, H, res, self.budget_ns, self.status, self.mc_ptr)
             C.all_gather_fused(self.buffer_ptrs, self.signal_ptrs, self.rank, out_off, 0, self.seq, self.done, T, H,
-                               summed, self.budget_ns, self.status)
+                               summed, self.budget_ns, self.status, bool(self.mc_ptr))
             self._advance()
             normed = None
             if w is not None:
@@ -146,7 +157,7 @@ class SymmComm:
     def fits_gemm_tail(self, rows: int, cols: int) -> bool:
         """One-shot sizes only: large steps keep the two-shot reduce-scatter + all-gather kernels."""
         return (rows <= self.max_rows and cols == self.hidden
-                and not (rows >= self.TWO_SHOT_ROWS and self.world > 2))
+                and not (rows >= self.TWO_SHOT_ROWS and (self.world > 2 or self.mc_ptr)))
 
     def linear_reduce_norm(self, x, w, res, norm_w, eps, w_offset):
         """(normed, summed) of sum_ranks(x @ w^T) + res in ONE launch: the GEMM writes this rank's partial tiles

@@ -127,6 +127,39 @@ def case_comm(dev):
     return {"errs": errs}
 
 
+def case_comm_multimem(dev):
+    """Two-shot reduction with the multimem form against the fp32 sum, and against the plain two-shot form's bits
+    where both round alike is not required: the switch sums in fp32 and rounds once to bf16 before the residual."""
+    from legion_b200.ops import reference as ref
+    from legion_b200.parallel.symm import SymmComm
+    H = 512
+    comm = SymmComm(dist.group.WORLD, RANK, WORLD, dev, max_rows=2048, hidden=H, budget_ns=2_000_000_000)
+    if not comm.mc_ptr:
+        return {"skipped": "the symmetric buffer has no NVLink multicast mapping on this box"}
+    say("multicast mapping", hex(comm.mc_ptr))
+    torch.manual_seed(11)
+    errs = []
+    for T in (600, 2048, 513):
+        parts = [(torch.randn(T, H, device=dev) * 0.5).bfloat16() for _ in range(WORLD)]
+        res = torch.randn(T, H, device=dev).bfloat16()
+        w = torch.rand(H, device=dev) + 0.5
+        slot = comm.next_partial(T, H)
+        slot.copy_(parts[RANK])
+        normed, summed = comm.all_reduce_add_norm(slot, res, w, 1e-6, 0.0)
+        total = sum(p.float() for p in parts) + res.float()
+        errs.append(float((summed.float() - total).abs().max()))
+        want_n, _ = ref.rmsnorm(summed, w, 1e-6)
+        errs.append(float((normed.float() - want_n.float()).abs().max()))
+        comm.check()
+        gathered = [torch.empty_like(summed) for _ in range(WORLD)]
+        dist.all_gather(gathered, summed)
+        assert all(torch.equal(g, gathered[0]) for g in gathered)      # every rank holds the same rows
+        say("multimem rows", T, "ok", errs[-2])
+    comm.end_step()
+    comm.check()
+    return {"errs": errs}
+
+
 def case_ep(dev):
     from legion_b200.ops import reference as ref
     from legion_b200.ops import sm100
@@ -384,6 +417,8 @@ def main():
     say("process group up")
     if CASE == "comm":
         res = case_comm(dev)
+    elif CASE == "comm_multimem":
+        res = case_comm_multimem(dev)
     elif CASE == "ep":
         res = case_ep(dev)
     elif CASE == "pp":

@@ -26,11 +26,12 @@ def _free_port():
     return p
 
 
-def _run(case, world, tmp_path, limit=180):
+def _run(case, world, tmp_path, limit=180, env_extra=None):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     out = str(tmp_path / f"{case}.pt")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1", LB_TEST_WATCHDOG_S="120")
+    env.update(env_extra or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), os.path.join(HERE, "dist_worker.py"),
            case, out]
@@ -56,6 +57,18 @@ def _logs(out, world):
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_fused_all_reduce_norm(tmp_path, world):
     res = _run("comm", world, tmp_path)
+    assert max(res["errs"]) < 0.08, res
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_two_shot_reduction_through_nvlink_multicast(tmp_path, world):
+    """The opt-in multimem form of the prompt-sized reduction (``LB_MULTIMEM=1``): the symmetric buffer is bound to an
+    NVLink multicast object, each rank loads its block of rows already summed inside the switch
+    (``multimem.ld_reduce``) and stores the result into every rank's region with one multicast store. All ranks of
+    this case leave normally; NCCL's own NVLS stays off."""
+    res = _run("comm_multimem", world, tmp_path, env_extra={"LB_MULTIMEM": "1", "TORCH_SYMM_MEM_DISABLE_MULTICAST": "0"})
+    if res.get("skipped"):
+        pytest.skip(res["skipped"])
     assert max(res["errs"]) < 0.08, res
 
 
