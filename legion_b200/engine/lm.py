@@ -46,7 +46,9 @@ class EngineConfig:
     max_batch_tokens: int = 1024
     prefill_chunk: int = 512
     block_size: int = 64
-    kv_cache_tokens: Optional[int] = None       # None: max_seqs * ctx_size
+    kv_cache_tokens: Optional[int] = None       # None: max_seqs * ctx_size; -1: as many as fit the GPU (memory plan)
+    gpu_memory_utilization: float = 0.92        # share of the device's memory the memory plan may fill
+    kv_fit_check: bool = False                  # refuse to start when an explicit KV pool does not fit
     prefix_cache: bool = True
     prefix_cache_states: int = 8
     prefix_cache_interval: int = 0
@@ -151,9 +153,12 @@ class LmEngine(Engine):
                 c.prefix_cache = False        # recurrent snapshots are not owner-aware
         kv_tokens = c.kv_cache_tokens or c.max_seqs * c.ctx_size
         n_blocks = max(4, (kv_tokens + c.block_size - 1) // c.block_size)
-        self.pool = BlockPool(n_blocks, c.block_size)
         extra = self.mcfg.mtp_layers if c.spec == "mtp" else 0
         owns = model.pipe.owns if getattr(model, "pipe", None) is not None else None
+        self.memory_plan = None
+        if dev.type == "cuda":
+            n_blocks = self._plan_memory(model, dev, extra, owns, n_blocks)
+        self.pool = BlockPool(n_blocks, c.block_size)
         self.kv = KvCache(self.mcfg, n_blocks, c.block_size, dev, model.dtype, kv_heads_local=model.n_kv_l,
                           extra_layers=extra, owns=owns)
         n_saved = c.prefix_cache_states if (self.hybrid and c.prefix_cache) else 0
@@ -190,6 +195,41 @@ class LmEngine(Engine):
         self._by_id: Dict[str, Seq] = {}
         if start:
             self.start()
+
+    def _plan_memory(self, model, dev, extra, owns, n_blocks: int) -> int:
+        """Sizes the KV pool against what the device has free beside the resident weights (``kv_cache_tokens = -1``:
+        as many blocks as fit, up to every sequence's whole context) or checks that the asked pool fits, and logs
+        the plan. An explicit pool that does not fit raises here, before anything large is allocated."""
+        import logging
+
+        from . import memory_plan as mp
+        c = self.cfg
+        probe = KvCache(self.mcfg, 1, c.block_size, dev, model.dtype, kv_heads_local=model.n_kv_l, extra_layers=extra,
+                        owns=owns)
+        bpb = probe.bytes_per_block()
+        del probe
+        n_saved = c.prefix_cache_states if (self.hybrid and c.prefix_cache) else 0
+        state_bytes = 0
+        if self.hybrid:
+            sp = StatePool(self.mcfg, 1, dev, tp=model.pctx.tp, owns=owns)
+            state_bytes = sp.bytes_per_slot() * (c.max_seqs + n_saved + 1)
+            del sp
+        free, total = torch.cuda.mem_get_info(dev)
+        m = self.mcfg
+        ws = mp.workspace_reserve(m.hidden, m.vocab, c.max_batch_tokens, c.max_seqs, m.n_expert, m.top_k, m.expert_ff)
+        auto = c.kv_cache_tokens is not None and c.kv_cache_tokens < 0
+        asked = 0 if auto else n_blocks * c.block_size
+        plan = mp.fit(total, free, torch.cuda.memory_allocated(dev), bpb, c.block_size, state_bytes, ws, c.max_seqs,
+                      c.ctx_size, asked_tokens=asked, utilisation=c.gpu_memory_utilization)
+        self.memory_plan = plan
+        log = logging.getLogger("legion")
+        for line in plan.lines():
+            log.info(line)
+        if auto:
+            return plan.n_blocks
+        if not plan.fits and c.kv_fit_check:
+            raise ValueError("the KV pool does not fit this GPU: " + "; ".join(plan.lines()[1:]))
+        return n_blocks
 
     def _mamba_graphable(self) -> bool:
         """Mamba-2 layers decode from CUDA graphs when their head shape runs on the scan kernel (the token loop that

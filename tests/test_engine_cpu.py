@@ -355,3 +355,22 @@ def test_resume_snapshot_survives_making_room():
     cold.shutdown()
     eng.shutdown()
     assert b.token_ids == want
+
+
+def test_memory_plan_sizes_the_kv_pool_and_reports_what_fits():
+    """The planner behind --kv-cache-tokens auto: blocks that fit beside weights, state slots and the kept-back
+    workspace; an explicit pool that is too large is reported with the largest context that would fit."""
+    from legion_b200.engine import memory_plan as mp
+    G = 1 << 30
+    bpb = 48 * 64 * 2 * 2 * 256 * 2                     # 48 layers, 64-token blocks, K+V, 2 kv heads of 256, bf16
+    ws = mp.workspace_reserve(2048, 151936, 8192, 16, 512, 10, 512)
+    assert 1 * G < ws < 8 * G
+    plan = mp.fit(total_bytes=180 * G, free_bytes=120 * G, weights_bytes=58 * G, bytes_per_block=bpb, block_size=64,
+                  state_bytes=2 * G, workspace_bytes=ws, max_seqs=16, ctx_size=32768, asked_tokens=0, utilisation=0.92)
+    assert plan.fits and plan.n_blocks == 16 * 32768 // 64          # every sequence gets its whole context
+    assert any("left unused" in n for n in plan.notes)
+    tight = mp.fit(180 * G, 20 * G, 150 * G, bpb, 64, 2 * G, ws, 256, 131072, asked_tokens=0, utilisation=0.92)
+    assert 0 < tight.n_blocks < 256 * 131072 // 64 and tight.kv_bytes <= 20 * G - 2 * G - ws
+    assert tight.max_ctx_fit == tight.n_blocks // 256 * 64 or tight.max_ctx_fit <= tight.kv_tokens
+    too_big = mp.fit(180 * G, 20 * G, 150 * G, bpb, 64, 2 * G, ws, 256, 131072, asked_tokens=256 * 131072)
+    assert not too_big.fits and "does not fit" in "\\n".join(too_big.lines())

@@ -318,3 +318,18 @@ def test_decode_step_as_two_concurrent_lanes_gives_the_same_tokens(idx):
     assert all(len(t) == 8 for t in runs[1])
     assert runs[0] == runs[1]
     assert sm100.Workspace.get("cuda").check() == 0
+
+
+def test_memory_plan_auto_sizes_the_kv_pool_on_the_device():
+    cfg = _cfgs()[1]
+    w32 = random_weights(cfg, "cpu", torch.float32, seed=3, std=0.05)
+    wgpu = {k: (v.bfloat16() if v.dim() > 1 and not k.endswith("conv_w") else v).cuda() for k, v in w32.items()}
+    eng = build_engine(cfg, weights=wgpu, device="cuda", start=False,
+                       engine_cfg=EngineConfig(ctx_size=512, max_seqs=4, block_size=64, kv_cache_tokens=-1))
+    plan = eng.memory_plan
+    assert plan is not None and plan.fits and plan.n_blocks == 4 * 512 // 64 == eng.pool.n_blocks
+    assert plan.bytes_per_block == eng.kv.bytes_per_block() and plan.state_bytes > 0
+    assert any("KV pool" in line for line in plan.lines())
+    out = eng.generate_text(tokens=list(range(40)), max_tokens=4, ignore_eos=True) if eng.start() is None else None
+    eng.shutdown()
+    assert out.error is None and len(out.token_ids) == 4
