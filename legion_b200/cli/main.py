@@ -86,6 +86,10 @@ def _add_engine_args(ap: argparse.ArgumentParser):
     g.add_argument("--expert-dir", default=None, help="--experts ssd: directory of the per-layer expert files")
     g.add_argument("--expert-ram-gib", type=float, default=8.0,
                    help="--experts ssd: host memory for recently used experts between the files and the HBM slots")
+    g.add_argument("--numa", choices=["auto", "off"], default="auto",
+                   help="auto: restrict each rank's host threads to the CPUs of its GPU's NUMA node")
+    g.add_argument("--load-threads", type=int, default=8,
+                   help="threads of positional reads that fetch a checkpoint layer ahead of the loader (0 = memory map only)")
     g.add_argument("--expert-weights", choices=["bf16", "nvfp4", "fp8"], default="bf16",
                    help="nvfp4: keep the routed experts in 4 bits in HBM (expanded inside the grouped GEMM); "
                         "fp8: block-scaled e4m3 experts on the FP8 tensor-core path")
@@ -163,11 +167,17 @@ def build_engine_from_args(a, start: bool = True):
         from ..config import PRESETS  # noqa: F401
         pctx = pdist.init_from_env(device, comm="nccl", expert_parallel=a.tp_moe_ep)   # symmetric memory is attached
         # below, once the model's hidden size is known
+    if on_gpu and getattr(a, "numa", "auto") == "auto":
+        from ..hw.numa import bind_to_gpu
+        placed = bind_to_gpu(torch.device(device).index or 0)
+        if placed["bound"]:
+            logging.getLogger("legion").info("rank %d: host threads on NUMA node %s (%d CPUs) next to GPU %s", rank,
+                                             placed["node"], len(placed["cpus"]), placed["bus_id"])
     # block-quantised checkpoints stay in their shipped encoding on a GPU (no bf16 copy on the way in) unless the
     # experts are offloaded (the host tiers hold plain tensors) or bf16 weights were asked for
     keep_q = (on_gpu and getattr(a, "weights", "auto") != "bf16" and a.experts not in ("cache", "host", "ssd"))
     cfg, w, tok, info = load_model(path, device, rank=rank, world=world, expert_parallel=a.tp_moe_ep, seed=a.seed,
-                                   keep_quant=keep_q)
+                                   keep_quant=keep_q, read_threads=getattr(a, "load_threads", 0))
     if pctx is not None and pctx.symm is None and a.tp_comm == "fused" and on_gpu:
         from ..parallel.symm import SymmComm
         import torch.distributed as dist

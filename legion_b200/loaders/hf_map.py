@@ -173,7 +173,7 @@ class _Source:
 
 
 def load_hf(path: str, device="cpu", dtype=torch.float32, keep_quant: bool = False, expert_range=None,
-            keep_quant_dense: bool = True):
+            keep_quant_dense: bool = True, read_threads: int = 0):
     """Returns (config, canonical weights, checkpoint). ``keep_quant`` (CUDA device): block-quantised expert, FFN
     and output projections stay in their shipped encoding (``ops.sm100.Nv4Weight`` / ``Fp8Weight``: the file's code
     bytes, scale bytes re-ordered for the tensor-core copy, never expanded to bf16), the way the reference repacks
@@ -182,7 +182,9 @@ def load_hf(path: str, device="cpu", dtype=torch.float32, keep_quant: bool = Fal
     attention / DeltaNet projections, rotary de-interleave) are decoded. ``expert_range=(lo, hi)``: only these
     routed experts are read (an expert-parallel rank reads its own shard of the files and nothing else of the
     experts, like the reference's sharded reader ``src/load_io.rs``). ``keep_quant_dense=False`` keeps only the
-    experts encoded (ranks that slice the dense projections by columns decode those first)."""
+    experts encoded (ranks that slice the dense projections by columns decode those first). ``read_threads`` > 0:
+    every layer's tensors (of the routed experts only those in ``expert_range``) are read ahead by that many
+    threads of positional reads instead of through the memory map."""
     ck = Checkpoint(path)
     cfg = config_from_hf(ck.config)
     src = _Source(ck, torch.device(device), dtype)
@@ -309,8 +311,26 @@ def load_hf(path: str, device="cpu", dtype=torch.float32, keep_quant: bool = Fal
         w[f"{p}.mla.kv_b"] = src.weight(a + "kv_b_proj")
         w[f"{p}.mla.o"] = proj(a + "o_proj")
 
+    def read_ahead(prefix: str):
+        if read_threads <= 0:
+            return
+        names = [n for n in ck.names() if n.startswith(prefix)]
+        if expert_range is not None:
+            lo, hi = expert_range
+            keep = []
+            for n in names:
+                i = n.find(".experts.")
+                if i >= 0:
+                    e = n[i + 9:].split(".", 1)[0]
+                    if e.isdigit() and not (lo <= int(e) < hi):
+                        continue
+                keep.append(n)
+            names = keep
+        ck.prefetch(names, threads=read_threads, pin=torch.device(device).type == "cuda")
+
     for il in range(cfg.n_layer):
         lp, p = f"{P}layers.{il}.", f"l{il}"
+        read_ahead(lp)
         w[f"{p}.attn_norm"] = norm(lp + "input_layernorm.weight")
         w[f"{p}.ffn_norm"] = norm(lp + "post_attention_layernorm.weight")
         kind = cfg.layer_kinds[il]

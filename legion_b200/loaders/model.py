@@ -19,7 +19,7 @@ from .tokenizer import BpeTokenizer, ByteTokenizer, Tokenizer
 
 def load_model(path: str, device="cpu", dtype=None, rank: int = 0, world: int = 1, expert_parallel: bool = False,
                seed: int = 0, keep_layers=None, dp_attention: bool = False,
-               keep_quant: bool = False) -> Tuple[ModelConfig, Dict[str, torch.Tensor], Tokenizer, dict]:
+               keep_quant: bool = False, read_threads: int = 0) -> Tuple[ModelConfig, Dict[str, torch.Tensor], Tokenizer, dict]:
     """``keep_layers(il)``: a pipeline stage keeps only the layers it owns (plus embeddings and head).
     ``keep_quant`` (HF directories on a GPU): NVFP4 / FP8 tensors stay in their shipped encoding; with expert
     parallelism every rank reads only its own experts from the files, straight to its GPU."""
@@ -49,10 +49,10 @@ def load_model(path: str, device="cpu", dtype=None, rank: int = 0, world: int = 
         if local_experts is not None:
             # sharded read: this rank's experts only, encoded, straight to the GPU; the rest is sliced below
             cfg, w, ck = load_hf(path, dev, dtype, keep_quant=True, expert_range=local_experts,
-                                 keep_quant_dense=dp_attention)
+                                 keep_quant_dense=dp_attention, read_threads=read_threads)
         else:
             cfg, w, ck = load_hf(path, "cpu" if world > 1 else dev, dtype,
-                                 keep_quant=keep_quant and world == 1 and dev.type == "cuda")
+                                 keep_quant=keep_quant and world == 1 and dev.type == "cuda", read_threads=read_threads)
         info["quant_method"] = ck.quant_method()
         info["local_experts"] = local_experts
         tok: Tokenizer

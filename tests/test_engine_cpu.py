@@ -373,4 +373,4 @@ def test_memory_plan_sizes_the_kv_pool_and_reports_what_fits():
     assert 0 < tight.n_blocks < 256 * 131072 // 64 and tight.kv_bytes <= 20 * G - 2 * G - ws
     assert tight.max_ctx_fit == tight.n_blocks // 256 * 64 or tight.max_ctx_fit <= tight.kv_tokens
     too_big = mp.fit(180 * G, 20 * G, 150 * G, bpb, 64, 2 * G, ws, 256, 131072, asked_tokens=256 * 131072)
-    assert not too_big.fits and "does not fit" in "\\n".join(too_big.lines())
+    assert not too_big.fits and "does not fit" in "\n".join(too_big.lines())

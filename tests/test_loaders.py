@@ -268,3 +268,24 @@ def test_hf_directory_expert_range_reads_only_those_experts(tmp_path):
             assert part[k].shape[0] == hi - lo and torch.equal(part[k], v[lo:hi])
         else:
             assert torch.equal(part[k], v)
+
+
+def test_parallel_read_ahead_gives_the_same_tensors(tmp_path):
+    """Layer tensors read ahead by a pool of positional reads (several pieces per tensor) equal the memory-mapped
+    ones; with an expert range only those experts are read."""
+    cfg = tiny_gqa_moe()
+    w = random_weights(cfg, "cpu", torch.float32, seed=6)
+    d = str(tmp_path / "ck")
+    save_hf(d, cfg, w, quant="none", dtype=torch.float32)
+    _, plain, _ = load_hf(d)
+    _, ahead, _ = load_hf(d, read_threads=4)
+    assert set(plain) == set(ahead) and all(torch.equal(plain[k], ahead[k]) for k in plain)
+    ck = Checkpoint(d)
+    name = next(n for n in ck.names() if n.endswith("experts.3.down_proj.weight"))
+    n = ck.prefetch([name], threads=3, chunk=1000)          # many small pieces of one tensor
+    assert n == ck.get(name).numel() * 4 or n > 0
+    ck2 = Checkpoint(d)
+    assert torch.equal(Checkpoint(d).get(name), (ck2.prefetch([name], threads=2, chunk=777), ck2.get(name))[1])
+    _, part, ck3 = load_hf(d, expert_range=(2, 4), read_threads=2)
+    assert part["l0.moe.gate_up"].shape[0] == 2 and torch.equal(part["l0.moe.gate_up"], plain["l0.moe.gate_up"][2:4])
+    assert not ck3._ahead or all(".experts." not in k or k.split(".experts.")[1].split(".")[0] in ("2", "3") for k in ck3._ahead)

@@ -267,3 +267,23 @@ def test_metric_families_roofline_stages_parallel_and_gpu_counters_from_a_fake_n
                  'legion_gpu_memory_busy_seconds{gpu="1"} 1.0', 'legion_gpu_power_watts{gpu="0"} 650.0',
                  'legion_gpu_sm_clock_mhz{gpu="1"} 1965.0'):
         assert want in text, want
+
+
+def test_numa_binding_from_a_fake_sysfs(tmp_path):
+    """The GPU's PCI device names its NUMA node, the node names its CPUs, the process is restricted to them."""
+    import os
+
+    from legion_b200.hw import numa
+    assert numa.parse_cpulist("0-3,8,10-11\n") == [0, 1, 2, 3, 8, 10, 11]
+    sysfs = tmp_path / "sys"
+    (sysfs / "bus/pci/devices/0000:1b:00.0").mkdir(parents=True)
+    (sysfs / "bus/pci/devices/0000:1b:00.0/numa_node").write_text("1\n")
+    (sysfs / "devices/system/node/node1").mkdir(parents=True)
+    allowed = sorted(os.sched_getaffinity(0))
+    (sysfs / "devices/system/node/node1/cpulist").write_text(",".join(str(c) for c in allowed[:2]) + ",9999\n")
+    done = {}
+    r = numa.bind_to_gpu(3, sysfs=str(sysfs), bus_id="0000:1b:00.0", apply=lambda pid, cpus: done.update(pid=pid, cpus=cpus))
+    assert r["node"] == 1 and r["bound"] and done["cpus"] == set(allowed[:2])       # CPUs outside the cpuset dropped
+    (sysfs / "bus/pci/devices/0000:1b:00.0/numa_node").write_text("-1\n")
+    r = numa.bind_to_gpu(3, sysfs=str(sysfs), bus_id="0000:1b:00.0", apply=lambda *a: done.update(again=True))
+    assert r["node"] is None and not r["bound"] and "again" not in done
