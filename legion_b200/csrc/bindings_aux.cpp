@@ -378,6 +378,29 @@ void bind_quant(pybind11::module_& m) {
                                          optpm<float>(row_gscale), cur_stream()) == 0,
                 "nv4_act_quant: K must be a multiple of 16 and at most 8192, rows 16-byte aligned");
   });
+  m.def("expert_cache_prepare", [](const Tensor& ids, Tensor& slot_of, Tensor& expert_in, Tensor& heat, double decay,
+                                   const Tensor& host_gu, const Tensor& host_dn, Tensor& slot_gu, Tensor& slot_dn,
+                                   Tensor& ids_slot, Tensor& miss_list, Tensor& ctl, Tensor& stats, Tensor& status) {
+    TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kInt && ids.is_contiguous() && ids_slot.is_contiguous() &&
+                    ids_slot.numel() >= ids.numel() && slot_of.scalar_type() == at::kInt &&
+                    expert_in.scalar_type() == at::kInt && heat.scalar_type() == at::kFloat,
+                "expert_cache_prepare: int32 routing and tables, float heat");
+    TORCH_CHECK(host_gu.is_pinned() && host_dn.is_pinned() && host_gu.is_contiguous() && host_dn.is_contiguous() &&
+                    slot_gu.is_contiguous() && slot_dn.is_contiguous() && host_gu.size(0) == slot_of.numel() &&
+                    slot_gu.size(0) == expert_in.numel() && miss_list.numel() >= 2 * expert_in.numel() &&
+                    ctl.numel() >= 3 && stats.numel() >= 4 && stats.element_size() == 8,
+                "expert_cache_prepare: pinned host experts [E, ...], device slots [n_slots, ...]");
+    const long gu_bytes = host_gu[0].numel() * host_gu.element_size(), dn_bytes = host_dn[0].numel() * host_dn.element_size();
+    c10::cuda::CUDAGuard guard(ids.device());
+    TORCH_CHECK(lb::expert_cache_prepare_launch(
+                    ids.data_ptr<int>(), int(ids.numel()), int(slot_of.numel()), int(expert_in.numel()),
+                    slot_of.data_ptr<int>(), expert_in.data_ptr<int>(), heat.data_ptr<float>(), float(decay),
+                    host_gu.data_ptr(), host_dn.data_ptr(), slot_gu.data_ptr(), slot_dn.data_ptr(), gu_bytes, dn_bytes,
+                    ids_slot.data_ptr<int>(), miss_list.data_ptr<int>(),
+                    reinterpret_cast<unsigned int*>(ctl.data_ptr()), reinterpret_cast<unsigned long long*>(stats.data_ptr()),
+                    reinterpret_cast<int*>(status.data_ptr()), cur_stream()) == 0,
+                "expert_cache_prepare: at most 2048 experts, expert bytes a multiple of 16");
+  });
   m.def("mamba2_scan", [](const Tensor& xbc, const Tensor& dt_raw, const Tensor& z, const Tensor& A, const Tensor& D,
                           const Tensor& dt_bias, Tensor& state, const Tensor& cu_seq, const Tensor& slots, int64_t nh,
                           int64_t hd, int64_t ng, int64_t ds, Tensor& y, bool write_state) {

@@ -84,6 +84,14 @@ int mamba2_scan_launch(const void* xbc, long ldx, const void* dt_raw, long lddt,
                        const float* D, const float* dt_bias, float* state, const int* cu_seq, const int* slots,
                        int n_seqs, int nh, int hd, int ng, int ds, void* y, long ldy, int write_state, cudaStream_t s);
 
+// Device-side expert cache step (residency.cu): marks the routed experts, loads the missing ones from mapped host
+// memory into the coldest slots and rewrites the routing in slot numbers, all in one launch. ctl: 3 zeroed words,
+// stats: {hits, misses, bytes, steps}, miss_list: 2 * n_slots ints of scratch.
+int expert_cache_prepare_launch(const int* ids, int n_pairs, int E, int n_slots, int* slot_of, int* expert_in, float* heat,
+                                float decay, const void* host_gu, const void* host_dn, void* slot_gu, void* slot_dn,
+                                long gu_bytes, long dn_bytes, int* ids_slot, int* miss_list, unsigned int* ctl,
+                                unsigned long long* stats, int* status, cudaStream_t s);
+
 int moe_combine_launch(const void* y, long ldy, const int* ids, int k, int e_lo, int e_hi, const void* shared, long lds,
                        const float* shared_gate, const void* residual, long ldr, void* out, long ldo, int T, int H,
                        const float* norm_w, float eps, float w_offset, void* norm_out, long ldn, cudaStream_t s);

@@ -186,7 +186,8 @@ class LmEngine(Engine):
             self.drafter = make_drafter(c.spec, self)
         self.eos_ids = tuple(self.tok.eos_ids)
         self._graphs = None
-        if dev.type == "cuda" and c.cuda_graphs and not model.expert_cache and getattr(model, "pipe", None) is None \
+        caches_ok = all(getattr(ec, "graph_safe", False) for ec in model.expert_cache.values())
+        if dev.type == "cuda" and c.cuda_graphs and caches_ok and getattr(model, "pipe", None) is None \
                 and self._mamba_graphable() and self._mla_graphable(model, c):
             from .cuda_graphs import DecodeGraphs
             self._graphs = DecodeGraphs(self)

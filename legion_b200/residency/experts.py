@@ -85,6 +85,61 @@ class ExpertCache:
         for s, e in enumerate(order):
             self._load(e, s)
         self.stats = CacheStats()
+        # Device-side tables (GPU, experts in pinned host memory): decode-sized steps make their experts resident
+        # inside ONE kernel launch (csrc/residency.cu) that reads the routing on the device, picks victims by the
+        # same decayed heat, and copies misses straight from the mapped host memory, so such steps need no host
+        # round trip and stay inside a CUDA graph. The device tables are then the authoritative ones; the host
+        # policy (prompt-sized steps) reads them back first and uploads them again afterwards.
+        self.dev = None
+        self.device_rows = 64
+        if pin and self.ssd is None and self.E <= 2048 and self.bytes_per_expert % 16 == 0:
+            self._upload_tables()
+
+    # ------------------------------------------------------------------ device-side tables
+    def _upload_tables(self):
+        """Host lists -> device tables (created once; captured graphs keep pointing at the same tensors)."""
+        if self.dev is None:
+            i32 = dict(dtype=torch.int32, device=self.device)
+            self.dev = {"slot_of": torch.empty(self.E, **i32), "expert_in": torch.empty(self.n_slots, **i32),
+                        "heat": torch.empty(self.E, dtype=torch.float32, device=self.device),
+                        "miss": torch.zeros(2 * self.n_slots, **i32), "ctl": torch.zeros(4, **i32),
+                        "stats": torch.zeros(4, dtype=torch.int64, device=self.device)}
+        d = self.dev
+        d["slot_of"].copy_(torch.tensor(self.slot_of, dtype=torch.int32))
+        d["expert_in"].copy_(torch.tensor(self.expert_in, dtype=torch.int32))
+        d["heat"].copy_(torch.tensor(self.heat, dtype=torch.float32))
+
+    def _download_tables(self):
+        d = self.dev
+        self.slot_of = d["slot_of"].tolist()
+        self.expert_in = d["expert_in"].tolist()
+        self.heat = d["heat"].tolist()
+        hits, misses, nbytes, steps = d["stats"].tolist()
+        d["stats"].zero_()
+        self.stats.hits += hits
+        self.stats.misses += misses
+        self.stats.bytes_copied += nbytes
+        self.stats.steps += steps
+
+    @property
+    def graph_safe(self) -> bool:
+        return self.dev is not None
+
+    def prepare_on_device(self, ids: torch.Tensor) -> torch.Tensor:
+        from ..ops import sm100
+        d = self.dev
+        out = torch.empty_like(ids)
+        ws = sm100.Workspace.get(ids.device)
+        sm100.ext().expert_cache_prepare(ids.contiguous(), d["slot_of"], d["expert_in"], d["heat"], self.decay,
+                                         self.host_gu, self.host_dn, self.slot_gu, self.slot_dn, out, d["miss"],
+                                         d["ctl"], d["stats"], ws.status)
+        return out
+
+    def sync_stats(self) -> CacheStats:
+        """Counters including the steps that ran on the device (synchronises)."""
+        if self.dev is not None:
+            self._download_tables()
+        return self.stats
 
     def _host_copy(self, e: int) -> Tuple[torch.Tensor, torch.Tensor]:
         """The expert's weights in host memory: the resident copy, or (ssd mode) the RAM tier, filled from the file."""
@@ -121,6 +176,10 @@ class ExpertCache:
 
     def prepare(self, ids: torch.Tensor) -> torch.Tensor:
         """Makes every expert in ``ids`` [T, k] resident and returns the same routing in slot numbers."""
+        if self.dev is not None and ids.is_cuda and ids.shape[0] <= self.device_rows:
+            return self.prepare_on_device(ids)
+        if self.dev is not None:
+            self._download_tables()             # the device tables are the authoritative ones
         need = sorted(set(ids.flatten().tolist()))
         if len(need) > self.n_slots:
             raise RuntimeError(f"a step routes to {len(need)} experts but the cache has {self.n_slots} slots; "
@@ -139,6 +198,9 @@ class ExpertCache:
             s = free[0] if free else min(victims, key=lambda v: self.heat[self.expert_in[v]])
             self._load(e, s)
         self.stats.steps += 1
+        if self.dev is not None:
+            self._upload_tables()
+            return self.dev["slot_of"][ids.long()].to(torch.int32)
         table = torch.tensor(self.slot_of, dtype=torch.int32, device=ids.device)
         return table[ids.long()].to(torch.int32)
 

@@ -333,3 +333,53 @@ def test_memory_plan_auto_sizes_the_kv_pool_on_the_device():
     out = eng.generate_text(tokens=list(range(40)), max_tokens=4, ignore_eos=True) if eng.start() is None else None
     eng.shutdown()
     assert out.error is None and len(out.token_ids) == 4
+
+
+def test_offloaded_experts_become_resident_on_the_device_and_decode_from_graphs():
+    """Experts in pinned host memory behind a few HBM slots: the device-side cache step (victims by decayed heat,
+    misses copied straight from mapped host memory, routing rewritten in slot numbers) first on its own against
+    the host policy, then in the engine, where decode steps of the offloaded model replay CUDA graphs and produce
+    the tokens of the all-resident model."""
+    from legion_b200.ops import sm100
+    from legion_b200.residency.experts import ExpertCache
+    E, F, H = 24, 64, 128
+    gu = (torch.arange(E, dtype=torch.float32)[:, None, None] + torch.rand(E, 2 * F, H)).bfloat16()
+    dn = (torch.arange(E, dtype=torch.float32)[:, None, None] + torch.rand(E, H, F)).bfloat16()
+    c = ExpertCache(gu, dn, n_slots=10, device="cuda")
+    assert c.graph_safe
+    g = torch.Generator().manual_seed(0)
+    for step in range(12):
+        ids = torch.stack([torch.randperm(E, generator=g)[:2] for _ in range(4)]).int().cuda()
+        slots = c.prepare(ids)
+        assert sm100.Workspace.get("cuda").check() == 0
+        sg, sd = c.weights()
+        for t in range(4):
+            for j in range(2):
+                e, s = int(ids[t, j]), int(slots[t, j])
+                assert torch.equal(sg[s].cpu(), gu[e]) and torch.equal(sd[s].cpu(), dn[e]), (step, e, s)
+    st = c.sync_stats()
+    assert st.misses > 0 and st.hits > 0 and st.steps == 12 and st.bytes_copied == st.misses * c.bytes_per_expert
+    assert sorted(x for x in c.expert_in if x >= 0) == sorted(e for e in range(E) if c.slot_of[e] >= 0)
+    # more experts in one step than slots: reported through the status word, no hang
+    c.prepare(torch.arange(12, dtype=torch.int32).view(1, 12).cuda())
+    assert sm100.Workspace.get("cuda").check() != 0
+    # engine: offloaded == resident, decode from graphs (prompt chunks of 4 tokens route to at most 8 of 32 experts)
+    cfg = ModelConfig(arch="qwen3moe", n_layer=2, hidden=256, vocab=1024, n_head=4, n_kv_head=2, head_dim=64,
+                      n_expert=32, top_k=2, expert_ff=128)
+    w32 = random_weights(cfg, "cpu", torch.float32, seed=3, std=0.05)
+    wgpu = {k: (v.bfloat16() if v.dim() > 1 else v).cuda() for k, v in w32.items()}
+    ec = dict(ctx_size=256, max_seqs=2, block_size=64, prefill_chunk=4, max_batch_tokens=4, prefix_cache=False)
+    prompt = torch.randint(0, 255, (30,), generator=torch.Generator().manual_seed(1)).tolist()
+    a = build_engine(cfg, weights=dict(wgpu), device="cuda", engine_cfg=EngineConfig(**ec))
+    want = a.generate_text(tokens=prompt, max_tokens=10, ignore_eos=True).token_ids
+    a.shutdown()
+    b = build_engine(cfg, weights=dict(wgpu), device="cuda", engine_cfg=EngineConfig(**ec), start=False)
+    b.model.offload_experts(n_slots=12)
+    assert b._graphs is not None and all(cache.graph_safe for cache in b.model.expert_cache.values())
+    b.start()
+    got = b.generate_text(tokens=prompt, max_tokens=10, ignore_eos=True).token_ids
+    replays = b._graphs.replays
+    misses = sum(cache.sync_stats().misses for cache in b.model.expert_cache.values())
+    b.shutdown()
+    assert got == want and replays > 0 and misses > 0
+    assert sm100.Workspace.get("cuda").check() == 0
