@@ -102,7 +102,7 @@ def _add_engine_args(ap: argparse.ArgumentParser):
     g.add_argument("--top-p", type=float, default=None)
     g.add_argument("--top-k", type=int, default=None)
     g.add_argument("--min-p", type=float, default=None)
-    g.add_argument("--tool-format", choices=["hermes", "qwen3_coder"], default="hermes")
+    g.add_argument("--tool-format", choices=["hermes", "qwen3_coder", "glm", "gemma4"], default="hermes")
 
 
 def build_engine_from_args(a, start: bool = True):

@@ -115,18 +115,67 @@ class ReasoningSplitter:
         return out
 
 
+_GEMMA_QUOTE = '<|"|>'
+
+
+def _gemma_value(s: str):
+    """One value of Gemma 4's argument notation at the head of ``s`` -> (python value, rest of the text)."""
+    s = s.lstrip()
+    if s.startswith(_GEMMA_QUOTE):
+        j = s.find(_GEMMA_QUOTE, len(_GEMMA_QUOTE))
+        if j < 0:
+            raise ValueError("unterminated string")
+        return s[len(_GEMMA_QUOTE):j], s[j + len(_GEMMA_QUOTE):]
+    if s.startswith("{"):
+        out, s = {}, s[1:].lstrip()
+        while not s.startswith("}"):
+            m = re.match(r"([A-Za-z_][A-Za-z0-9_\-]*)\s*:", s)
+            if not m:
+                raise ValueError("expected a key")
+            v, s = _gemma_value(s[m.end():])
+            out[m.group(1)] = v
+            s = s.lstrip()
+            if s.startswith(","):
+                s = s[1:].lstrip()
+            elif not s.startswith("}"):
+                raise ValueError("expected , or }")
+        return out, s[1:]
+    if s.startswith("["):
+        out, s = [], s[1:].lstrip()
+        while not s.startswith("]"):
+            v, s = _gemma_value(s)
+            out.append(v)
+            s = s.lstrip()
+            if s.startswith(","):
+                s = s[1:].lstrip()
+            elif not s.startswith("]"):
+                raise ValueError("expected , or ]")
+        return out, s[1:]
+    m = re.match(r"-?\d+(\.\d+)?([eE][+-]?\d+)?|true|false|null", s)
+    if not m:
+        raise ValueError("unknown value")
+    return json.loads(m.group(0)), s[m.end():]
+
+
 class ToolCallParser:
     """Extracts tool calls from generated text.
 
     ``hermes``:       <tool_call>{"name": ..., "arguments": {...}}</tool_call>
     ``qwen3_coder``:  <tool_call><function=name><parameter=key>value</parameter>...</function></tool_call>
-    Text outside the tags streams through; text inside is buffered until the closing tag.
+    ``glm``:          <tool_call>name<arg_key>key</arg_key><arg_value>value</arg_value>...</tool_call> (GLM-4.5 and
+                      later; a value is JSON when it parses as JSON, else the string as written)
+    ``gemma4``:       <|tool_call>call:name{key:value,...}<tool_call|> in Gemma's own notation: bare keys, strings
+                      wrapped in <|"|>, numbers / true / false / null, lists and nested objects as in JSON
+    Text outside the tags streams through; text inside is buffered until the closing tag. The reference's parsers
+    are ``src/engine/tool_parser.rs`` and ``tool_parser/{glm,gemma4}.rs``.
     """
 
     OPEN, CLOSE = "<tool_call>", "</tool_call>"
 
     def __init__(self, fmt: str = "hermes"):
         self.fmt = fmt
+        if fmt == "gemma4":
+            self.OPEN, self.CLOSE = "<|tool_call>", "<tool_call|>"
         self._buf = ""
         self._inside = False
         self.calls: List[dict] = []
@@ -177,7 +226,29 @@ class ToolCallParser:
     def _parse(self, body: str) -> Optional[dict]:
         body = body.strip()
         name, args = None, None
-        if self.fmt == "qwen3_coder" or body.startswith("<function="):
+        if self.fmt == "glm":
+            i = body.find("<arg_key>")
+            name = (body if i < 0 else body[:i]).strip()
+            if not name or any(c in name for c in "<>\n"):
+                return None
+            args = {}
+            for pm in re.finditer(r"<arg_key>(.*?)</arg_key>\s*<arg_value>(.*?)</arg_value>", body[i:] if i >= 0 else "", re.S):
+                val = pm.group(2).strip("\n")
+                try:
+                    args[pm.group(1).strip()] = json.loads(val)
+                except (ValueError, TypeError):
+                    args[pm.group(1).strip()] = val
+        elif self.fmt == "gemma4":
+            if not body.startswith("call:") or "{" not in body:
+                return None
+            name = body[5:body.index("{")].strip()
+            try:
+                args, rest = _gemma_value(body[body.index("{"):])
+            except ValueError:
+                return None
+            if not name or rest.strip() or not isinstance(args, dict):
+                return None
+        elif self.fmt == "qwen3_coder" or body.startswith("<function="):
             m = re.match(r"<function=([^>\s]+)>(.*?)(</function>)?\s*$", body, re.S)
             if not m:
                 return None

@@ -374,3 +374,34 @@ def test_memory_plan_sizes_the_kv_pool_and_reports_what_fits():
     assert tight.max_ctx_fit == tight.n_blocks // 256 * 64 or tight.max_ctx_fit <= tight.kv_tokens
     too_big = mp.fit(180 * G, 20 * G, 150 * G, bpb, 64, 2 * G, ws, 256, 131072, asked_tokens=256 * 131072)
     assert not too_big.fits and "does not fit" in "\n".join(too_big.lines())
+
+
+def test_tool_call_parsers_glm_and_gemma4_formats():
+    """GLM's key / value tags and Gemma 4's own argument notation, fed in small pieces as a stream would."""
+    import json
+
+    from legion_b200.engine.text import ToolCallParser
+
+    def run(fmt, text, piece=5):
+        p = ToolCallParser(fmt)
+        out, calls = "", []
+        for i in range(0, len(text), piece):
+            t, c = p.push(text[i:i + piece])
+            out += t
+            calls += c
+        t, c = p.flush()
+        return out + t, calls + c
+
+    glm = ("Let me look.\n<tool_call>get_weather\n<arg_key>city</arg_key>\n<arg_value>Paris</arg_value>\n"
+           "<arg_key>days</arg_key>\n<arg_value>3</arg_value>\n<arg_key>opts</arg_key><arg_value>{\"a\": [1, 2]}</arg_value>"
+           "</tool_call> done")
+    text, calls = run("glm", glm)
+    assert text == "Let me look.\n done" and len(calls) == 1 and calls[0]["name"] == "get_weather"
+    assert json.loads(calls[0]["arguments"]) == {"city": "Paris", "days": 3, "opts": {"a": [1, 2]}}
+    assert run("glm", "<tool_call><bad>\n</tool_call>")[1] == []
+    gem = 'ok <|tool_call>call:get_weather{city:<|"|>東京, "x"<|"|>,days:2,deep:{on:true,list:[1,2.5,null,<|"|>a<|"|>]}}<tool_call|>!'
+    text, calls = run("gemma4", gem, piece=3)
+    assert text == "ok !" and calls[0]["name"] == "get_weather"
+    assert json.loads(calls[0]["arguments"]) == {"city": '東京, "x"', "days": 2, "deep": {"on": True, "list": [1, 2.5, None, "a"]}}
+    assert run("gemma4", "<|tool_call>call:f{a:}<tool_call|>")[1] == []            # malformed: no call
+    assert run("hermes", "<tool_call>{\"name\": \"f\", \"arguments\": {\"a\": 1}}</tool_call>")[1][0]["name"] == "f"
