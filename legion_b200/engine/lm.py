@@ -92,7 +92,7 @@ class Seq:
     __slots__ = ("req", "stream", "tokens", "n_prompt", "n_computed", "table", "slot", "sampler", "detok", "stop",
                  "reason", "tools", "phase", "arrival_ms", "admit_ms", "first_ms", "usage", "radix_handle", "drafts",
                  "save_points", "finished", "priority", "key", "n_out", "held_logprobs", "constraint", "resumed", "swapped",
-                 "orig_prompt", "last_hidden", "draft_state", "owner")
+                 "orig_prompt", "last_hidden", "draft_state", "owner", "mask_ahead")
 
     def __init__(self, req: GenerateRequest, stream: TokenStream, tokens: List[int]):
         self.req, self.stream = req, stream
@@ -118,6 +118,7 @@ class Seq:
         self.n_out = 0
         self.held_logprobs: List[TokenLogprob] = []
         self.constraint = None
+        self.mask_ahead = None        # the next token's vocabulary mask, being computed beside the forward pass
         self.resumed = 0
         self.last_hidden = None
         self.draft_state = None
@@ -186,6 +187,7 @@ class LmEngine(Engine):
             self.drafter = make_drafter(c.spec, self)
         self.eos_ids = tuple(self.tok.eos_ids)
         self._graphs = None
+        self._mask_pool = None
         caches_ok = all(getattr(ec, "graph_safe", False) for ec in model.expert_cache.values())
         if dev.type == "cuda" and c.cuda_graphs and caches_ok and getattr(model, "pipe", None) is None \
                 and self._mamba_graphable() and self._mla_graphable(model, c):
@@ -257,6 +259,9 @@ class LmEngine(Engine):
         if self._thread is not None:
             self._thread.join(timeout=30)
             self._thread = None
+        if self._mask_pool is not None:
+            self._mask_pool.shutdown(wait=False)
+            self._mask_pool = None
         self.release_graphs()
 
     def release_graphs(self):
@@ -959,7 +964,32 @@ class LmEngine(Engine):
         self._stats.dp_gather_bytes = getattr(self._stats, "dp_gather_bytes", 0) + W * M * V * 4
         self._finish_rows(rows, None, logits, None, verify)
 
+    def _masks_ahead(self, rows):
+        """Grammar-constrained sequences: the vocabulary mask of the token each of them picks in this step depends
+        only on its constraint state, which is already known, so helper threads compute the masks while the forward
+        pass runs on the GPU (the engine thread waits for the logits with the interpreter lock released). The
+        reference computes them on mask threads the same way (``src/engine/lm/response_format.rs``)."""
+        todo = [s for s, p0, n in rows if s.constraint is not None and s.mask_ahead is None
+                and (s.phase == "decode" or p0 + n >= s.n_prompt)]
+        if not todo:
+            return
+        if self._mask_pool is None:
+            from concurrent.futures import ThreadPoolExecutor
+            self._mask_pool = ThreadPoolExecutor(max_workers=4, thread_name_prefix="legion-mask")
+        for s in todo:
+            s.mask_ahead = self._mask_pool.submit(s.constraint.mask)
+
+    def _take_mask(self, s: Seq):
+        if s.constraint is None:
+            return None
+        fut, s.mask_ahead = s.mask_ahead, None
+        if fut is not None:
+            self._stats.masks_ahead += 1
+            return fut.result()
+        return s.constraint.mask()
+
     def _forward_and_finish(self, rows, verify: bool):
+        self._masks_ahead(rows)
         if self.dp_world > 1:
             return self._dp_forward_and_finish(rows, verify)
         all_decode_1 = all(s.phase == "decode" and n == 1 for s, _, n in rows)
@@ -997,7 +1027,7 @@ class LmEngine(Engine):
     # ------------------------------------------------------------------ sampling / verification
     def _pick(self, s: Seq, logits_row: torch.Tensor, device_pick: Optional[int] = None) -> Tuple[int, Optional[TokenLogprob]]:
         sp = s.req.sampling
-        mask = s.constraint.mask() if s.constraint is not None else None
+        mask = self._take_mask(s)
         if device_pick is not None and sp.greedy and sp.plain and mask is None:
             return device_pick, None
         tok, lg = s.sampler.sample(logits_row, mask, self.eos_ids if not sp.ignore_eos else (), s.n_out)
@@ -1137,7 +1167,7 @@ class LmEngine(Engine):
         sp = s.req.sampling
         if sp.greedy and sp.plain and device_pick is not None:
             return device_pick == draft, device_pick, None
-        mask = s.constraint.mask() if s.constraint is not None else None
+        mask = self._take_mask(s)
         lg = s.sampler.adjusted(row, mask, self.eos_ids if not sp.ignore_eos else (), s.n_out)
         lp = None
         if sp.greedy:

@@ -269,6 +269,7 @@ class EngineStats:
     spec_verify_steps: int = 0
     spec_mean_k: float = 0.0
     model_bytes_step: int = 0
+    masks_ahead: int = 0               # grammar masks computed by helper threads beside the forward pass
     step_ms_ewma: float = 0.0
     # host time per step by phase, accumulated ms (plan = drafts + row planning, build = batch tensors + H2D,
     # forward = launches (+ wait for logits), finish = sampling / verification / text / stream events)

@@ -73,4 +73,6 @@ def test_engine_generates_valid_json_with_random_weights():
         assert isinstance(doc["n"], int) and doc["k"] in ("x", "yy")
     with pytest.raises(ValueError):
         eng.check_response_format({"type": "json_schema", "json_schema": {"schema": {"type": "frob"}}})
+    # the vocabulary masks of constrained sequences were computed by helper threads beside the forward pass
+    assert getattr(eng.stats(), "masks_ahead", 0) > 10
     eng.shutdown()
