@@ -81,6 +81,9 @@ def _add_engine_args(ap: argparse.ArgumentParser):
     g.add_argument("--layer-split", default=None, help="layers per pipeline stage, e.g. 7,7,7,7,7,7,7,6")
     g.add_argument("--split-last-extra", type=int, default=0, help="layers' worth of room kept free on the last stage")
     g.add_argument("--pipeline-micro", type=int, default=2048, help="tokens per micro-chunk of a pipelined prompt")
+    g.add_argument("--pipeline-groups", type=int, default=0,
+                   help="--pp: groups a decode step's sequences travel the stages in, one behind the other (0 = one per "
+                        "stage)")
     g.add_argument("--experts", choices=["auto", "device", "host", "cache", "ssd"], default="auto")
     g.add_argument("--expert-cache-gib", type=float, default=0.0)
     g.add_argument("--expert-dir", default=None, help="--experts ssd: directory of the per-layer expert files")
@@ -147,7 +150,8 @@ def build_engine_from_args(a, start: bool = True):
         if n_layer is None:
             n_layer = load_model(path, "cpu", keep_layers=lambda il: False)[0].n_layer
         split = [int(x) for x in a.layer_split.split(",")] if a.layer_split else None
-        pipe = PipeStage(rank, world, dist.group.WORLD, n_layer, split, a.pipeline_micro, a.split_last_extra)
+        pipe = PipeStage(rank, world, dist.group.WORLD, n_layer, split, a.pipeline_micro, a.split_last_extra,
+                         decode_groups=getattr(a, "pipeline_groups", 0) or world)
         cfg, w, tok, info = load_model(path, device, seed=a.seed, keep_layers=pipe.owns)
         model = Decoder(cfg, w, None, max_position=ec.ctx_size + 8, pipe=pipe)
         return LmEngine(model, tok, ec, start=start)

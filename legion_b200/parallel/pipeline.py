@@ -41,13 +41,17 @@ def split_layers(n_layer: int, world: int, layer_split: Optional[Sequence[int]] 
 
 class PipeStage:
     def __init__(self, rank: int, world: int, group, n_layer: int, layer_split: Optional[Sequence[int]] = None,
-                 micro_tokens: int = 2048, last_extra: int = 0):
+                 micro_tokens: int = 2048, last_extra: int = 0, decode_groups: int = 1):
         self.rank, self.world, self.group = rank, world, group
         self.bounds = split_layers(n_layer, world, layer_split, last_extra)
         self.lo, self.hi = self.bounds[rank], self.bounds[rank + 1]
         self.first, self.last = rank == 0, rank == world - 1
         self.micro_tokens = micro_tokens
-        self.stats = {"micro_chunks": 0, "sends": 0, "bytes": 0}
+        # decode steps: the running sequences travel the stages as this many groups, one behind the other, so
+        # that stage s works on group g while stage s + 1 works on group g - 1 (``--pipeline-groups``; the
+        # reference keeps decoding groups in flight the same way, ``src/engine/lm/pipe.rs:139``)
+        self.decode_groups = max(1, decode_groups)
+        self.stats = {"micro_chunks": 0, "decode_groups": 0, "sends": 0, "bytes": 0}
 
     def owns(self, il: int) -> bool:
         return self.lo <= il < self.hi
@@ -58,6 +62,21 @@ class PipeStage:
         sub-steps over the same block table and state slot; any other step is one unit."""
         from ..models.decoder import StepBatch
         T = int(b.token_ids.shape[0]) if b.embeds is None else int(b.embeds.shape[0])
+        if (self.decode_groups > 1 and b.max_q_len == 1 and b.embeds is None and T == b.n_seqs and T >= 2 * self.decode_groups
+                and b.write_state and not b.capture_layers and b.replay is None):
+            # a decode step: contiguous groups of sequences, each a complete step of its own
+            per = (T + self.decode_groups - 1) // self.decode_groups
+            out = []
+            for a in range(0, T, per):
+                e = min(T, a + per)
+                out.append(StepBatch(
+                    token_ids=b.token_ids[a:e], positions=b.positions[a:e],
+                    cu_q=torch.arange(e - a + 1, dtype=torch.int32, device=b.cu_q.device), ctx_lens=b.ctx_lens[a:e],
+                    block_table=b.block_table[a:e], slots=b.slots[a:e], state_slots=b.state_slots[a:e],
+                    logit_rows=None, max_q_len=1, max_ctx=b.max_ctx, write_state=True, embeds=None,
+                    cu_q_host=list(range(e - a + 1)), decode_splits=b.decode_splits))
+            self.stats["decode_groups"] += len(out)
+            return out
         if b.n_seqs != 1 or T <= self.micro_tokens or not b.write_state or b.capture_layers:
             return [b]
         out = []

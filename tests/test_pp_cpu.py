@@ -9,7 +9,7 @@ import torch.multiprocessing as mp
 from legion_b200.config import tiny_gqa_moe, tiny_hybrid_moe
 
 CFGS = {"gqa_moe": tiny_gqa_moe, "hybrid": tiny_hybrid_moe}
-ECFG = dict(ctx_size=512, max_seqs=2, block_size=16, prefill_chunk=160, prefix_cache=False)
+ECFG = dict(ctx_size=512, max_seqs=4, block_size=16, prefill_chunk=160, prefix_cache=False)
 
 
 def _free_port():
@@ -38,7 +38,7 @@ def _worker(rank, world, port, name, out_path):
     dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
                             timeout=datetime.timedelta(seconds=120))
     cfg = CFGS[name]()
-    pipe = PipeStage(rank, world, dist.group.WORLD, cfg.n_layer, micro_tokens=48)
+    pipe = PipeStage(rank, world, dist.group.WORLD, cfg.n_layer, micro_tokens=48, decode_groups=2)
     full = random_weights(cfg, "cpu", torch.float32, seed=0, std=0.05)
     # a stage keeps its own layers, the embedding (first stage; tied heads) and the head (last stage)
     w = {k: v for k, v in full.items()
@@ -48,7 +48,9 @@ def _worker(rank, world, port, name, out_path):
     eng = LmEngine(model, ByteTokenizer(cfg.vocab), ec, start=False)
     assert set(eng.kv.k) == {il for il in cfg.kv_layers() if pipe.owns(il)}
     toks = []
-    for batch in (((150, 1),), ((40, 2), (33, 3))):      # one long prompt alone (micro-chunked), then two together
+    # one long prompt alone (micro-chunked), two together, then four together (their decode steps travel the stages
+    # as two groups of two)
+    for batch in (((150, 1),), ((40, 2), (33, 3)), ((20, 4), (25, 5), (18, 6), (30, 7))):
         streams = [eng.generate(GenerateRequest(prompt_tokens=_prompt(n, s),
                                                 sampling=SamplingParams(max_tokens=8, ignore_eos=True)))
                    for n, s in batch]
@@ -61,6 +63,7 @@ def _worker(rank, world, port, name, out_path):
         toks += [s.collect().token_ids for s in streams]
     if rank == 0:
         torch.save({"tokens": toks, "micro": pipe.stats["micro_chunks"], "sends": pipe.stats["sends"],
+                    "groups": pipe.stats["decode_groups"],
                     "bounds": pipe.bounds}, out_path)
     dist.barrier()
     dist.destroy_process_group()
@@ -74,13 +77,14 @@ def test_pipeline_equals_single(tmp_path, name, world):
     eng = build_engine(cfg, weights=random_weights(cfg, "cpu", torch.float32, seed=0, std=0.05),
                        engine_cfg=EngineConfig(**ECFG))
     want = [eng.generate_text(tokens=_prompt(n, s), max_tokens=8, ignore_eos=True).token_ids
-            for n, s in ((150, 1), (40, 2), (33, 3))]
+            for n, s in ((150, 1), (40, 2), (33, 3), (20, 4), (25, 5), (18, 6), (30, 7))]
     eng.shutdown()
     out = str(tmp_path / "r0.pt")
     mp.spawn(_worker, args=(world, _free_port(), name, out), nprocs=world, join=True)
     got = torch.load(out)
     assert got["tokens"] == want
     assert got["micro"] >= 3           # the 150-token prompt went through as micro-chunks of 48
+    assert got["groups"] >= 4          # decode steps of four sequences went through as two groups
     assert got["sends"] > 0 and got["bounds"][-1] == cfg.n_layer
 
 
