@@ -56,7 +56,8 @@ def _add_engine_args(ap: argparse.ArgumentParser):
     g.add_argument("--op-profile", action="store_true",
                    help="time every kernel call between CUDA events (use with --no-cuda-graphs); table at exit of run")
     g = ap.add_argument_group("speculative decoding")
-    g.add_argument("--spec", choices=["none", "ngram", "suffix", "mtp", "draft", "eagle3", "dflash"], default="none")
+    g.add_argument("--spec", choices=["none", "ngram", "suffix", "mtp", "mtp_ngram", "draft", "eagle3", "dflash"],
+                   default="none")
     g.add_argument("--spec-k", type=int, default=4)
     g.add_argument("--spec-max-batch", type=int, default=8)
     g.add_argument("--spec-draft-model", default=None)

@@ -61,7 +61,7 @@ class EngineConfig:
     kv_swap_gib: float = 0.0                    # host tier for preempted sequences (0 = recompute instead)
     prefix_host_gib: float = 0.0                # host tier of the prefix cache: evicted blocks keep their contents
                                                 # in pinned memory and come back on a later hit (0 = dropped)
-    spec: str = "none"                          # none | ngram | mtp | draft | eagle3 | suffix
+    spec: str = "none"                          # none | ngram | suffix | mtp | mtp_ngram | draft | eagle3 | dflash
     spec_k: int = 4
     spec_max_batch: int = 8
     spec_ngram_min: int = 2
@@ -154,7 +154,7 @@ class LmEngine(Engine):
                 c.prefix_cache = False        # recurrent snapshots are not owner-aware
         kv_tokens = c.kv_cache_tokens or c.max_seqs * c.ctx_size
         n_blocks = max(4, (kv_tokens + c.block_size - 1) // c.block_size)
-        extra = self.mcfg.mtp_layers if c.spec == "mtp" else 0
+        extra = self.mcfg.mtp_layers if c.spec in ("mtp", "mtp_ngram") else 0
         owns = model.pipe.owns if getattr(model, "pipe", None) is not None else None
         self.memory_plan = None
         if dev.type == "cuda":

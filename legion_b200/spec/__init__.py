@@ -9,13 +9,15 @@ recurrent layers do not advance during verify and replay the kept tokens afterwa
   ngram    prompt-lookup: continue the longest recent n-gram match in the sequence itself
   suffix   suffix index over the sequence plus a cross-request cache of finished replies
   mtp      the model's own next-token-prediction head, chained k times
+  mtp_ngram  the same, with a prompt-lookup shortcut for sequences whose tail occurred before
   draft    a smaller model with the same vocabulary, run k times
   eagle3   one decoder layer over [embed ; fc(target layers lo/mid/hi)] with its own KV, chained
   dflash   block drafter: one pass proposes a whole block from the target's last hidden row
 """
 from __future__ import annotations
 
-from .drafters import (DflashDrafter, DraftModelDrafter, Eagle3Drafter, MtpDrafter, NgramDrafter, SuffixDrafter)
+from .drafters import (DflashDrafter, DraftModelDrafter, Eagle3Drafter, MtpDrafter, MtpNgramDrafter, NgramDrafter,
+                       SuffixDrafter)
 
 
 def make_drafter(kind: str, engine, **kw):
@@ -25,6 +27,8 @@ def make_drafter(kind: str, engine, **kw):
         return SuffixDrafter()
     if kind == "mtp":
         return MtpDrafter(engine)
+    if kind == "mtp_ngram":
+        return MtpNgramDrafter(engine, engine.cfg.spec_ngram_min, engine.cfg.spec_ngram_max)
     if kind == "draft":
         return DraftModelDrafter(engine, **kw)
     if kind == "eagle3":

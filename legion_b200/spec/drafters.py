@@ -159,6 +159,43 @@ class MtpDrafter(_ModelDrafter):
                 hidden[id(s)] = row
 
 
+class MtpNgramDrafter(MtpDrafter):
+    """MTP head with a prompt-lookup shortcut: a sequence whose last tokens occurred before takes the tokens that
+    followed them as its drafts (no head launches for it in this step); the others chain the MTP head, and an MTP
+    chain is extended by looking its own drafts up the same way. The head still sees every target step, so its KV
+    stays in step either way. Reference: ``src/engine/lm/mtp_ngram.rs``."""
+
+    def __init__(self, engine, n_min: int = 2, n_max: int = 4, extend: int = 2):
+        super().__init__(engine)
+        self.ngram = NgramDrafter(n_min, n_max)
+        self.extend = extend
+        self.stats = {"ngram_hits": 0, "mtp_chains": 0, "extended": 0}
+
+    def draft_batch(self, seqs, k):
+        chain = []
+        for s in seqs:
+            if id(s) not in self.prev:
+                continue
+            got = self.ngram.propose(s, k)
+            if len(got) >= min(2, k):
+                s.drafts = got
+                self.stats["ngram_hits"] += 1
+            else:
+                chain.append(s)
+        if chain:
+            self.stats["mtp_chains"] += len(chain)
+            super().draft_batch(chain, k)
+            for s in chain:
+                if len(s.drafts) == k and self.extend > 0:
+                    class _View:        # the sequence continued by its own drafts
+                        tokens = s.tokens + s.drafts
+                    more = self.ngram.propose(_View, self.extend)
+                    room = self.eng.cfg.ctx_size - len(s.tokens) - len(s.drafts) - 2
+                    if more and room > 0:
+                        s.drafts = s.drafts + more[:room]
+                        self.stats["extended"] += 1
+
+
 class DraftModelDrafter(_ModelDrafter):
     """A separate (smaller) model with the target's vocabulary. It sees every token the target sees (own KV in
     the same block ids) and then runs k greedy steps ahead."""

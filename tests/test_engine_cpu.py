@@ -97,7 +97,8 @@ def test_multi_turn_resumes_from_end_of_reply_state():
 
 
 @pytest.mark.parametrize("name,spec", [("gqa_moe", "ngram"), ("hybrid", "ngram"), ("gqa_moe", "suffix"), ("gqa_moe", "draft"),
-                                       ("hybrid", "draft"), ("mla", "mtp"), ("gqa_moe", "eagle3"), ("dense", "dflash")])
+                                       ("hybrid", "draft"), ("mla", "mtp"), ("mla", "mtp_ngram"), ("gqa_moe", "eagle3"),
+                                       ("dense", "dflash")])
 def test_speculative_equals_plain_greedy(name, spec, golden):
     eng = engine(name, prefix_cache=False, spec=spec, spec_k=3)
     # a repetitive prompt so that n-gram drafters actually propose
@@ -115,8 +116,10 @@ def test_speculative_equals_plain_greedy(name, spec, golden):
             assert st.spec_accepted_tokens == st.spec_draft_tokens
         else:   # recurrent layers: one-token draft steps and multi-token verify steps round differently
             assert st.spec_accepted_tokens >= 0.85 * st.spec_draft_tokens
-    if spec in ("mtp", "eagle3", "dflash", "draft"):
+    if spec in ("mtp", "mtp_ngram", "eagle3", "dflash", "draft"):
         assert st.spec_verify_steps > 0
+    if spec == "mtp_ngram":      # the repetitive prompt is served by look-ups, the random one by the head
+        assert eng.drafter.stats["ngram_hits"] > 0 and eng.drafter.stats["mtp_chains"] > 0
 
 
 def test_on_demand_admission_preempts_and_recomputes(golden):
