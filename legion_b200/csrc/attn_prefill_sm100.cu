@@ -7,10 +7,12 @@
 //   warps 0..3 (thread = query row = TMEM lane): tcgen05.ld S, causal / window mask, online softmax
 //       in base 2, P written to smem as the swizzled K-major A operand of the second MMA, O rescaled
 //       in TMEM (tcgen05.ld / st) when the running maximum moved.
-// K/V tiles are double buffered, so the loads for block i+1 fly during the softmax of block i. Head dim 128 runs
-// with 64-key blocks, two K stages and ONE V stage (V of block i is fetched while the softmax of block i runs):
-// 97 KB of shared memory and 256 TMEM columns per CTA, so two CTAs share an SM and one's softmax overlaps the
-// other's MMAs. The softmax keeps the 64 scores of a row in registers (one TMEM read), skips the mask
+// The scores are double buffered in TMEM and issued one block AHEAD: while the softmax warps work on S(i), the
+// tensor pipe already computes S(i+1) (and the previous block's P V), so the softmax of block i+1 starts the moment
+// block i's is done instead of waiting for P V(i) and S(i+1) to run back to back. Three K stages keep the key tile
+// of block i+2 in flight; V has ONE stage (V of block i is fetched while the softmax of block i runs). Head dim 128
+// runs with 64-key blocks: 112 KB of shared memory and 256 TMEM columns per CTA, so two CTAs share an SM and fill
+// each other's remaining gaps. The softmax keeps the 64 scores of a row in registers (one TMEM read), skips the mask
 // comparisons on blocks that are entirely visible, and rescales O only when the row maximum grew by more than
 // 2^8 (probabilities are then relative to a slightly stale maximum).
 // Sequence lengths, query offsets and block tables are data; the grid is (q tiles, heads, seqs).
@@ -53,15 +55,16 @@ static constexpr float PREFILL_RESCALE_LOG2 = 8.f;
 
 template <int D, int BKV>
 struct PrefillCfg {
-  static constexpr bool VSINGLE = (D == 128 && BKV == 64);   // one V stage: two CTAs per SM
+  static constexpr bool VSINGLE = true;                 // one V stage
   static constexpr int HALVES = D / 64;               // 64-column (128-byte) halves of a head row
   static constexpr int Q_BYTES = HALVES * 128 * 128;  // 128 rows x 128 B per half
   static constexpr int KV_BYTES = HALVES * BKV * 128;
   static constexpr int P_BYTES = (BKV / 64) * 128 * 128;
-  static constexpr int STAGES = 2;
-  static constexpr int VSTAGES = VSINGLE ? 1 : STAGES;
-  static constexpr int SMEM = Q_BYTES + (STAGES + VSTAGES) * KV_BYTES + P_BYTES + 1024 + 256;
-  static constexpr int TMEM_RAW = BKV + D;
+  static constexpr int STAGES = 3;                      // K stages
+  static constexpr int VSTAGES = 1;
+  // no alignment slack: the dynamic shared memory of this kernel starts 1024-byte aligned (checked at entry)
+  static constexpr int SMEM = Q_BYTES + (STAGES + VSTAGES) * KV_BYTES + P_BYTES + 256;
+  static constexpr int TMEM_RAW = 2 * BKV + D;          // two score buffers + the output accumulator
   static constexpr int TMEM_COLS = TMEM_RAW <= 128 ? 128 : (TMEM_RAW <= 256 ? 256 : 512);
 };
 
@@ -70,20 +73,24 @@ __global__ void __launch_bounds__(160, (D == 128 && BKV == 64) ? 2 : 1)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const PrefillArgs a) {
   using Cfg = PrefillCfg<D, BKV>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem_raw) & 1023u) {       // swizzled tiles need 1024-byte alignment; uniform per CTA, before any barrier
+    if (threadIdx.x == 0) atomicCAS(a.status, 0, ST_BAD_ARGS);
+    return;
+  }
   uint8_t* q_s = smem;
   uint8_t* k_s = q_s + Cfg::Q_BYTES;                       // [STAGES] K tiles
   uint8_t* v_s = k_s + Cfg::STAGES * Cfg::KV_BYTES;        // [VSTAGES] V tiles
   uint8_t* p_s = v_s + Cfg::VSTAGES * Cfg::KV_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + Cfg::P_BYTES);
   uint64_t* q_full = bars;
-  uint64_t* k_full = bars + 1;   // [2]
-  uint64_t* v_full = bars + 3;   // [2]
-  uint64_t* s_full = bars + 5;
-  uint64_t* p_ready = bars + 6;
-  uint64_t* o_done = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* k_full = bars + 1;   // [3]
+  uint64_t* v_full = bars + 4;   // [1]
+  uint64_t* s_full = bars + 5;   // [2] one per score buffer
+  uint64_t* p_ready = bars + 7;
+  uint64_t* o_done = bars + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int seq = blockIdx.z;
@@ -98,8 +105,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); }
-    mbar_init(s_full, 1);
+    for (int i = 0; i < 3; ++i) mbar_init(&k_full[i], 1);
+    mbar_init(&v_full[0], 1);
+    mbar_init(&s_full[0], 1);
+    mbar_init(&s_full[1], 1);
     mbar_init(p_ready, 128);
     mbar_init(o_done, 1);
     *abort_flag = 0;
@@ -113,8 +122,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_S = tmem_base;
-  const uint32_t tmem_O = tmem_base + BKV;
+  const uint32_t tmem_S = tmem_base;                 // score buffers at +0 and +BKV
+  const uint32_t tmem_O = tmem_base + 2 * BKV;
 
   // key range visible to this query tile
   const int pos0 = ctx - q_len + tile_row0;                       // absolute position of tile row 0
@@ -152,53 +161,55 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       for (int h = 0; h < Cfg::HALVES; ++h)
         tma_load_3d(q_s + h * (128 * 128), &tmQ, q_full, h * 64, head, q0 + tile_row0);
       load_k(blk_lo, 0);
+      if (n_blk > 1) load_k(blk_lo + 1, 1);
       load_v(blk_lo, 0);
       constexpr uint32_t idesc_s = umma_idesc(128, BKV, 1, 1, 0, 0);
       constexpr uint32_t idesc_o = umma_idesc(128, D, 1, 1, 0, 1);  // B (= V) is MN-major
       bool ok = mbar_wait(q_full, 0, abort_flag);
       if (!ok) { *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FULL); }
-      for (int i = 0; ok && i < n_blk; ++i) {
-        const int st = i & 1;
-        const uint32_t ph = (i >> 1) & 1;
-        if (!mbar_wait(&k_full[st], ph, abort_flag)) {
-          *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FULL); break;
+      const uint32_t qa = smem_u32(q_s);
+      // S(j) = Q K_j^T into score buffer j & 1, from K stage j % 3
+      auto issue_s = [&](int j) -> bool {
+        const int st = j % 3;
+        if (!mbar_wait(&k_full[st], uint32_t(j / 3) & 1u, abort_flag)) {
+          *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FULL); return false;
         }
         tc_fence_after();
-        const uint32_t qa = smem_u32(q_s);
-        const int vst = Cfg::VSINGLE ? 0 : st;
-        const uint32_t vph = Cfg::VSINGLE ? uint32_t(i & 1) : ph;
         const uint32_t ka = smem_u32(k_s + st * Cfg::KV_BYTES);
-        const uint32_t va = smem_u32(v_s + vst * Cfg::KV_BYTES);
+        const uint32_t ts = tmem_S + uint32_t(j & 1) * BKV;
 #pragma unroll
         for (int h = 0; h < Cfg::HALVES; ++h) {
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const uint64_t da = umma_desc_k_sw128(qa + h * (128 * 128) + k * 32);
             const uint64_t db = umma_desc_k_sw128(ka + h * (BKV * 128) + k * 32);
-            umma_f16(tmem_S, da, db, idesc_s, (h | k) ? 1u : 0u);
+            umma_f16(ts, da, db, idesc_s, (h | k) ? 1u : 0u);
           }
         }
-        umma_commit(s_full);
-        // the other stage is free once the previous block's PV has completed
+        umma_commit(&s_full[j & 1]);
+        return true;
+      };
+      if (ok && n_blk > 0) ok = issue_s(0);
+      for (int i = 0; ok && i < n_blk; ++i) {
+        // K stage (i + 2) % 3 held block i - 1, whose scores the softmax has consumed (p_ready(i - 1) was seen)
+        if (i + 2 < n_blk) load_k(blk_lo + i + 2, (i + 2) % 3);
+        // the next block's scores, one block ahead of the softmax: buffer (i + 1) & 1 held S(i - 1), read and done
+        if (i + 1 < n_blk && !issue_s(i + 1)) break;
         if (i >= 1) {
+          // the single V buffer is free once the previous block's P V has completed: fetch V of THIS block now
           if (!mbar_wait(o_done, (i - 1) & 1, abort_flag)) {
             *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_EMPTY); break;
           }
-        }
-        if (i + 1 < n_blk) load_k(blk_lo + i + 1, st ^ 1);
-        if (Cfg::VSINGLE) {
-          // the single V buffer is free now (PV of block i-1 is done): fetch V of THIS block under its softmax
-          if (i >= 1) load_v(blk_lo + i, 0);
-        } else if (i + 1 < n_blk) {
-          load_v(blk_lo + i + 1, st ^ 1);
+          load_v(blk_lo + i, 0);
         }
         if (!mbar_wait(p_ready, i & 1, abort_flag)) {
           *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FLAG); break;
         }
-        if (!mbar_wait(&v_full[vst], vph, abort_flag)) {
+        if (!mbar_wait(&v_full[0], uint32_t(i & 1), abort_flag)) {
           *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FULL); break;
         }
         tc_fence_after();
+        const uint32_t va = smem_u32(v_s);
         const uint32_t pa = smem_u32(p_s);
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k) {
@@ -219,10 +230,11 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int i = 0; i < n_blk; ++i) {
-      if (!__all_sync(0xffffffffu, mbar_wait(s_full, i & 1, abort_flag))) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[i & 1], uint32_t(i >> 1) & 1u, abort_flag))) {
         *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_FULL); ok = false; break;
       }
       tc_fence_after();
+      const uint32_t tmem_Si = tmem_S + uint32_t(i & 1) * BKV;
       const int key0 = (blk_lo + i) * BKV;
       int hi = a.causal ? min(ctx, qpos + 1) : ctx;   // exclusive key bound for this row
       int lo = (a.window > 0) ? max(0, qpos - a.window + 1) : 0;
@@ -236,7 +248,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // ---- one TMEM read: the row's scores stay in registers between the maximum and the exponentials
         uint32_t r[BKV <= 64 ? BKV : 1];
 #pragma unroll
-        for (int c = 0; c < BKV; c += 32) tmem_ld32(tmem_S + lane_off + c, *reinterpret_cast<uint32_t(*)[32]>(&r[c]));
+        for (int c = 0; c < BKV; c += 32) tmem_ld32(tmem_Si + lane_off + c, *reinterpret_cast<uint32_t(*)[32]>(&r[c]));
         tmem_ld_wait();
         float mx = -INFINITY;
         if (full_blk) {
@@ -291,7 +303,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll 1
         for (int c = 0; c < BKV; c += 32) {
           uint32_t r[32];
-          tmem_ld32(tmem_S + lane_off + c, r);
+          tmem_ld32(tmem_Si + lane_off + c, r);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -314,7 +326,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll 1
         for (int c = 0; c < BKV; c += 32) {
           uint32_t r[32];
-          tmem_ld32(tmem_S + lane_off + c, r);
+          tmem_ld32(tmem_Si + lane_off + c, r);
           tmem_ld_wait();
           uint32_t packed[16];
 #pragma unroll
