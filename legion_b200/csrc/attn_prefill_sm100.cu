@@ -5,14 +5,14 @@
 //       the cache, one box per page and 64-column half, 128-byte swizzle), issues S = Q K^T into
 //       TMEM, later O += P V (V is the MN-major B operand, read in place from the same smem tile)
 //   warps 0..3 (thread = query row = TMEM lane): tcgen05.ld S, causal / window mask, online softmax
-//       in base 2, P written to smem as the swizzled K-major A operand of the second MMA, O rescaled
-//       in TMEM (tcgen05.ld / st) when the running maximum moved.
+//       in base 2, P written back INTO tensor memory over the scores it came from (bf16 pairs, tcgen05.st) and
+//       read from there as the A operand of the second MMA (no shared-memory round trip, no proxy fence), O
+//       rescaled in TMEM (tcgen05.ld / st) when the running maximum moved.
 // The scores are double buffered in TMEM and issued one block AHEAD: while the softmax warps work on S(i), the
 // tensor pipe already computes S(i+1) (and the previous block's P V), so the softmax of block i+1 starts the moment
 // block i's is done instead of waiting for P V(i) and S(i+1) to run back to back. Three K stages keep the key tile
-// of block i+2 in flight; V has ONE stage (V of block i is fetched while the softmax of block i runs). Head dim 128
-// runs with 64-key blocks: 112 KB of shared memory and 256 TMEM columns per CTA, so two CTAs share an SM and fill
-// each other's remaining gaps. The softmax keeps the 64 scores of a row in registers (one TMEM read), skips the mask
+// of block i+2 in flight, two V stages the value tile of block i+1. Head dim 128 runs with 64-key blocks: 112 KB of
+// shared memory and 256 TMEM columns per CTA, so two CTAs share an SM and fill each other's remaining gaps. The softmax keeps the 64 scores of a row in registers (one TMEM read), skips the mask
 // comparisons on blocks that are entirely visible, and rescales O only when the row maximum grew by more than
 // 2^8 (probabilities are then relative to a slightly stale maximum).
 // Sequence lengths, query offsets and block tables are data; the grid is (q tiles, heads, seqs).
@@ -37,6 +37,24 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+// D += A B with the A operand (the probabilities, bf16 pairs in 32-bit cells, row = lane) read from tensor memory
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 
 struct PrefillArgs {
   const int* cu_q;         // [n_seqs + 1] first query row of each sequence
@@ -55,15 +73,15 @@ static constexpr float PREFILL_RESCALE_LOG2 = 8.f;
 
 template <int D, int BKV>
 struct PrefillCfg {
-  static constexpr bool VSINGLE = true;                 // one V stage
+  static constexpr bool VSINGLE = false;
   static constexpr int HALVES = D / 64;               // 64-column (128-byte) halves of a head row
   static constexpr int Q_BYTES = HALVES * 128 * 128;  // 128 rows x 128 B per half
   static constexpr int KV_BYTES = HALVES * BKV * 128;
   static constexpr int P_BYTES = (BKV / 64) * 128 * 128;
   static constexpr int STAGES = 3;                      // K stages
-  static constexpr int VSTAGES = 1;
+  static constexpr int VSTAGES = 2;
   // no alignment slack: the dynamic shared memory of this kernel starts 1024-byte aligned (checked at entry)
-  static constexpr int SMEM = Q_BYTES + (STAGES + VSTAGES) * KV_BYTES + P_BYTES + 256;
+  static constexpr int SMEM = Q_BYTES + (STAGES + VSTAGES) * KV_BYTES + 256;
   static constexpr int TMEM_RAW = 2 * BKV + D;          // two score buffers + the output accumulator
   static constexpr int TMEM_COLS = TMEM_RAW <= 128 ? 128 : (TMEM_RAW <= 256 ? 256 : 512);
 };
@@ -82,15 +100,14 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint8_t* q_s = smem;
   uint8_t* k_s = q_s + Cfg::Q_BYTES;                       // [STAGES] K tiles
   uint8_t* v_s = k_s + Cfg::STAGES * Cfg::KV_BYTES;        // [VSTAGES] V tiles
-  uint8_t* p_s = v_s + Cfg::VSTAGES * Cfg::KV_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + Cfg::P_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + Cfg::VSTAGES * Cfg::KV_BYTES);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;   // [3]
-  uint64_t* v_full = bars + 4;   // [1]
-  uint64_t* s_full = bars + 5;   // [2] one per score buffer
-  uint64_t* p_ready = bars + 7;
-  uint64_t* o_done = bars + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* v_full = bars + 4;   // [2]
+  uint64_t* s_full = bars + 6;   // [2] one per score buffer
+  uint64_t* p_ready = bars + 8;
+  uint64_t* o_done = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int seq = blockIdx.z;
@@ -107,6 +124,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(q_full, 1);
     for (int i = 0; i < 3; ++i) mbar_init(&k_full[i], 1);
     mbar_init(&v_full[0], 1);
+    mbar_init(&v_full[1], 1);
     mbar_init(&s_full[0], 1);
     mbar_init(&s_full[1], 1);
     mbar_init(p_ready, 128);
@@ -163,6 +181,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       load_k(blk_lo, 0);
       if (n_blk > 1) load_k(blk_lo + 1, 1);
       load_v(blk_lo, 0);
+      if (n_blk > 1) load_v(blk_lo + 1, 1);
       constexpr uint32_t idesc_s = umma_idesc(128, BKV, 1, 1, 0, 0);
       constexpr uint32_t idesc_o = umma_idesc(128, D, 1, 1, 0, 1);  // B (= V) is MN-major
       bool ok = mbar_wait(q_full, 0, abort_flag);
@@ -195,28 +214,27 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (i + 2 < n_blk) load_k(blk_lo + i + 2, (i + 2) % 3);
         // the next block's scores, one block ahead of the softmax: buffer (i + 1) & 1 held S(i - 1), read and done
         if (i + 1 < n_blk && !issue_s(i + 1)) break;
-        if (i >= 1) {
-          // the single V buffer is free once the previous block's P V has completed: fetch V of THIS block now
+        if (i >= 1 && i + 1 < n_blk) {
+          // V stage (i + 1) & 1 held block i - 1: free once that block's P V has completed
           if (!mbar_wait(o_done, (i - 1) & 1, abort_flag)) {
             *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_EMPTY); break;
           }
-          load_v(blk_lo + i, 0);
+          load_v(blk_lo + i + 1, (i + 1) & 1);
         }
         if (!mbar_wait(p_ready, i & 1, abort_flag)) {
           *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FLAG); break;
         }
-        if (!mbar_wait(&v_full[0], uint32_t(i & 1), abort_flag)) {
+        if (!mbar_wait(&v_full[i & 1], uint32_t(i >> 1) & 1u, abort_flag)) {
           *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FULL); break;
         }
         tc_fence_after();
-        const uint32_t va = smem_u32(v_s);
-        const uint32_t pa = smem_u32(p_s);
+        const uint32_t va = smem_u32(v_s + (i & 1) * Cfg::KV_BYTES);
+        const uint32_t tp = tmem_S + uint32_t(i & 1) * BKV;      // P(i) sits over the scores it was computed from
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k) {
-          // A = P: K-major, 64-key halves of 16 KiB; B = V: 16 keys = 16 rows of 128 B per step
-          const uint64_t da = umma_desc_k_sw128(pa + (k / 4) * (128 * 128) + (k % 4) * 32);
+          // A = P from tensor memory: 16 keys = 8 cells of bf16 pairs per step; B = V: 16 rows of 128 B per step
           const uint64_t db = umma_desc_mn_sw128(va + k * 16 * 128, BKV * 128, 1024);
-          umma_f16(tmem_O, da, db, idesc_o, (i | k) ? 1u : 0u);
+          umma_f16_ts(tmem_O, tp + k * 8, db, idesc_o, (i | k) ? 1u : 0u);
         }
         umma_commit(o_done);
       }
@@ -266,13 +284,6 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_blk);
           m = m_blk;
         }
-        // P may be overwritten and O rescaled only after the previous PV has finished
-        if (i >= 1) {
-          if (!__all_sync(0xffffffffu, mbar_wait(o_done, (i - 1) & 1, abort_flag))) {
-            *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_EMPTY); ok = false; break;
-          }
-          tc_fence_after();
-        }
         const float neg_m = (m == -INFINITY) ? 0.f : -m;
         uint32_t packed[BKV <= 64 ? BKV / 2 : 1];
 #pragma unroll
@@ -290,13 +301,9 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           sum += f.x + f.y;
           packed[j / 2] = *reinterpret_cast<const uint32_t*>(&bb);
         }
-        uint8_t* half_base = p_s + row * 128;
+        // P over the scores it came from: cell c of the row holds keys 2c (low half) and 2c + 1
 #pragma unroll
-        for (int ch = 0; ch < BKV / 8; ++ch) {
-          const int chunk = ch ^ (row & 7);
-          *reinterpret_cast<uint4*>(half_base + chunk * 16) =
-              make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
-        }
+        for (int c = 0; c < BKV / 2; c += 16) tmem_st16(tmem_Si + lane_off + c, &packed[c]);
       } else {
         // ---- two TMEM passes (128-key blocks): row maximum, then probabilities -> swizzled smem
         float mx = -INFINITY;
@@ -315,12 +322,6 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (m_blk > m + PREFILL_RESCALE_LOG2 || (m == -INFINITY && m_blk != -INFINITY)) {
           alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_blk);
           m = m_blk;
-        }
-        if (i >= 1) {
-          if (!__all_sync(0xffffffffu, mbar_wait(o_done, (i - 1) & 1, abort_flag))) {
-            *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_EMPTY); ok = false; break;
-          }
-          tc_fence_after();
         }
         const float neg_m = (m == -INFINITY) ? 0.f : -m;
 #pragma unroll 1
@@ -341,20 +342,21 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             sum += f.x + f.y;
             packed[j / 2] = *reinterpret_cast<const uint32_t*>(&bb);
           }
-          // 32 columns = 4 chunks of 16 bytes in half (c / 64)
-          uint8_t* half_base = p_s + (c / 64) * (128 * 128) + row * 128;
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            const int chunk = ((c % 64) / 8 + ch) ^ (row & 7);
-            *reinterpret_cast<uint4*>(half_base + chunk * 16) =
-                make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
-          }
+          // in place: the 32 score cells just read become 16 cells of bf16 pairs at half the column offset
+          // (cells below c / 2 + 16 <= c were read by earlier chunks of this thread)
+          tmem_st16(tmem_Si + lane_off + c / 2, packed);
         }
       }
       l = l * alpha + sum;
       if (i >= 1) {
-        // every thread rescales its own O row; with the lazy threshold this is rare after the first blocks
+        // every thread rescales its own O row; with the lazy threshold this is rare after the first blocks. O may
+        // be touched only after the previous block's P V has finished (P itself no longer waits for it: it lives
+        // in this block's own score buffer)
         if (__any_sync(0xffffffffu, alpha != 1.f)) {
+          if (!__all_sync(0xffffffffu, mbar_wait(o_done, (i - 1) & 1, abort_flag))) {
+            *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_EMPTY); ok = false; break;
+          }
+          tc_fence_after();
 #pragma unroll 1
           for (int c = 0; c < D; c += 32) {
             uint32_t r[32];
@@ -367,7 +369,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           tmem_st_wait();
         }
       }
-      fence_proxy_async_smem();
+      tmem_st_wait();
       tc_fence_before();
       mbar_arrive(p_ready);
     }
