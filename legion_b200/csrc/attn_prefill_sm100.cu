@@ -105,9 +105,11 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* k_full = bars + 1;   // [3]
   uint64_t* v_full = bars + 4;   // [2]
   uint64_t* s_full = bars + 6;   // [2] one per score buffer
-  uint64_t* p_ready = bars + 8;
-  uint64_t* o_done = bars + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* p_ready = bars + 8;  // [2] one per score buffer: with the scores issued a block ahead, a fast softmax warp
+                                 //     can finish block i + 1 before a slow one has finished block i; on ONE barrier its
+                                 //     second arrival would complete block i's phase early
+  uint64_t* o_done = bars + 10;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int seq = blockIdx.z;
@@ -127,7 +129,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(&v_full[1], 1);
     mbar_init(&s_full[0], 1);
     mbar_init(&s_full[1], 1);
-    mbar_init(p_ready, 128);
+    mbar_init(&p_ready[0], 128);
+    mbar_init(&p_ready[1], 128);
     mbar_init(o_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -221,7 +224,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
           load_v(blk_lo + i + 1, (i + 1) & 1);
         }
-        if (!mbar_wait(p_ready, i & 1, abort_flag)) {
+        if (!mbar_wait(&p_ready[i & 1], uint32_t(i >> 1) & 1u, abort_flag)) {
           *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_FLAG); break;
         }
         if (!mbar_wait(&v_full[i & 1], uint32_t(i >> 1) & 1u, abort_flag)) {
@@ -270,8 +273,17 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tmem_ld_wait();
         float mx = -INFINITY;
         if (full_blk) {
+          // four independent chains: a single one is 64 dependent operations with only two warps per scheduler
+          // to hide their latency
+          float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-          for (int j = 0; j < BKV; ++j) mx = fmaxf(mx, __uint_as_float(r[j]));
+          for (int j = 0; j < BKV; j += 4) {
+            m0 = fmaxf(m0, __uint_as_float(r[j]));
+            m1 = fmaxf(m1, __uint_as_float(r[j + 1]));
+            m2 = fmaxf(m2, __uint_as_float(r[j + 2]));
+            m3 = fmaxf(m3, __uint_as_float(r[j + 3]));
+          }
+          mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
         } else {
 #pragma unroll
           for (int j = 0; j < BKV; ++j) {
@@ -286,20 +298,35 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         const float neg_m = (m == -INFINITY) ? 0.f : -m;
         uint32_t packed[BKV <= 64 ? BKV / 2 : 1];
+        if (full_blk) {
+          // interior block: no mask; the row sum is taken over the fp32 probabilities in four partial sums (the
+          // tensor core sees their bf16 roundings: the difference averages out far below bf16 resolution)
+          float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
-        for (int j = 0; j < BKV; j += 2) {
-          float p0 = exp2f(fmaf(__uint_as_float(r[j]), a.scale_log2, neg_m));
-          float p1 = exp2f(fmaf(__uint_as_float(r[j + 1]), a.scale_log2, neg_m));
-          if (!full_blk) {
+          for (int j = 0; j < BKV; j += 4) {
+            const float p0 = exp2f(fmaf(__uint_as_float(r[j]), a.scale_log2, neg_m));
+            const float p1 = exp2f(fmaf(__uint_as_float(r[j + 1]), a.scale_log2, neg_m));
+            const float p2 = exp2f(fmaf(__uint_as_float(r[j + 2]), a.scale_log2, neg_m));
+            const float p3 = exp2f(fmaf(__uint_as_float(r[j + 3]), a.scale_log2, neg_m));
+            s0 += p0; s1 += p1; s2 += p2; s3 += p3;
+            packed[j / 2] = pack_bf16x2(p0, p1);
+            packed[j / 2 + 1] = pack_bf16x2(p2, p3);
+          }
+          sum = (s0 + s1) + (s2 + s3);
+        } else {
+#pragma unroll
+          for (int j = 0; j < BKV; j += 2) {
+            float p0 = exp2f(fmaf(__uint_as_float(r[j]), a.scale_log2, neg_m));
+            float p1 = exp2f(fmaf(__uint_as_float(r[j + 1]), a.scale_log2, neg_m));
             const int key = key0 + j;
             if (!(key >= lo && key < hi)) p0 = 0.f;
             if (!(key + 1 >= lo && key + 1 < hi)) p1 = 0.f;
+            // sum what the tensor core will see (bf16-rounded) to keep numerator and denominator consistent
+            const __nv_bfloat162 bb = __floats2bfloat162_rn(p0, p1);
+            const float2 f = __bfloat1622float2(bb);
+            sum += f.x + f.y;
+            packed[j / 2] = *reinterpret_cast<const uint32_t*>(&bb);
           }
-          // sum what the tensor core will see (bf16-rounded) to keep numerator and denominator consistent
-          const __nv_bfloat162 bb = __floats2bfloat162_rn(p0, p1);
-          const float2 f = __bfloat1622float2(bb);
-          sum += f.x + f.y;
-          packed[j / 2] = *reinterpret_cast<const uint32_t*>(&bb);
         }
         // P over the scores it came from: cell c of the row holds keys 2c (low half) and 2c + 1
 #pragma unroll
@@ -371,9 +398,17 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(p_ready);
+      mbar_arrive(&p_ready[i & 1]);
     }
     // final: O / l -> out
+    if (ok && n_blk > 1) {
+      // a parity wait may be at most one phase behind the barrier: this thread may not have looked at o_done for
+      // many blocks (it waits only when it rescales), so it first catches up with the block before the last (whose
+      // predecessor is known to be complete: it ran before the last block's scores)
+      if (!__all_sync(0xffffffffu, mbar_wait(o_done, (n_blk - 2) & 1, abort_flag))) {
+        *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_FULL); ok = false;
+      }
+    }
     if (ok && n_blk > 0) {
       if (!__all_sync(0xffffffffu, mbar_wait(o_done, (n_blk - 1) & 1, abort_flag))) {
         *abort_flag = 1; atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_FULL); ok = false;
