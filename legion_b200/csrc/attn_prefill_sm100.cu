@@ -56,6 +56,33 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
       : "memory");
 }
 
+// Packed fp32 pairs (two lanes of one 64-bit register) and the three-input maximum: the softmax of an interior block
+// is bound by instruction issue (two warps per scheduler next to the tensor pipe), and these halve the scale /
+// subtract, sum and maximum instructions of a row.
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 struct PrefillArgs {
   const int* cu_q;         // [n_seqs + 1] first query row of each sequence
   const int* ctx_lens;     // [n_seqs] keys visible after this chunk (cached + chunk)
@@ -116,7 +143,9 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int head = blockIdx.y;
   const int q0 = a.cu_q[seq];
   const int q_len = a.cu_q[seq + 1] - q0;
-  const int tile_row0 = blockIdx.x * 128;
+  // causal prompts: the last query tile of a sequence has the most key blocks; tiles are handed out from the last
+  // to the first so that the long ones start first and the short ones fill the tail of the grid
+  const int tile_row0 = (int(gridDim.x) - 1 - int(blockIdx.x)) * 128;
   if (tile_row0 >= q_len) return;  // uniform per CTA, before any barrier or TMEM use
   const int ctx = a.ctx_lens[seq];
   const int kvh = head / (a.Hq / a.Hkv);
@@ -277,11 +306,11 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           // to hide their latency
           float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-          for (int j = 0; j < BKV; j += 4) {
-            m0 = fmaxf(m0, __uint_as_float(r[j]));
-            m1 = fmaxf(m1, __uint_as_float(r[j + 1]));
-            m2 = fmaxf(m2, __uint_as_float(r[j + 2]));
-            m3 = fmaxf(m3, __uint_as_float(r[j + 3]));
+          for (int j = 0; j < BKV; j += 8) {
+            m0 = fmax3(m0, __uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+            m1 = fmax3(m1, __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            m2 = fmax3(m2, __uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+            m3 = fmax3(m3, __uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
           }
           mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
         } else {
@@ -301,17 +330,22 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (full_blk) {
           // interior block: no mask; the row sum is taken over the fp32 probabilities in four partial sums (the
           // tensor core sees their bf16 roundings: the difference averages out far below bf16 resolution)
-          float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+          const uint64_t sc2 = f2_pack(a.scale_log2, a.scale_log2), nm2 = f2_pack(neg_m, neg_m);
+          uint64_t acc0 = f2_pack(0.f, 0.f), acc1 = acc0;
 #pragma unroll
           for (int j = 0; j < BKV; j += 4) {
-            const float p0 = exp2f(fmaf(__uint_as_float(r[j]), a.scale_log2, neg_m));
-            const float p1 = exp2f(fmaf(__uint_as_float(r[j + 1]), a.scale_log2, neg_m));
-            const float p2 = exp2f(fmaf(__uint_as_float(r[j + 2]), a.scale_log2, neg_m));
-            const float p3 = exp2f(fmaf(__uint_as_float(r[j + 3]), a.scale_log2, neg_m));
-            s0 += p0; s1 += p1; s2 += p2; s3 += p3;
+            float x0, x1, x2, x3;
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), sc2, nm2), x0, x1);
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])), sc2, nm2), x2, x3);
+            const float p0 = exp2f(x0), p1 = exp2f(x1), p2 = exp2f(x2), p3 = exp2f(x3);
+            acc0 = f2_add(acc0, f2_pack(p0, p1));
+            acc1 = f2_add(acc1, f2_pack(p2, p3));
             packed[j / 2] = pack_bf16x2(p0, p1);
             packed[j / 2 + 1] = pack_bf16x2(p2, p3);
           }
+          float s0, s1, s2, s3;
+          f2_unpack(acc0, s0, s1);
+          f2_unpack(acc1, s2, s3);
           sum = (s0 + s1) + (s2 + s3);
         } else {
 #pragma unroll
