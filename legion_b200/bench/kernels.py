@@ -437,7 +437,7 @@ def bench_decode_attn(rows):
 def bench_prefill_attn(rows):
     from legion_b200.ops import sm100
     hbm, tf, src = peaks()
-    Hq, Hkv, D, page = 32, 4, 128, 64
+    Hq, Hkv, D, page = CASE.get("heads") or (32, 4, 128, 64)
     for n_seq, L in (CASE["attn"] or ((1, 8192), (4, 2048), (1, 32768))):
         nb = n_seq * (L // page)
         kc = torch.randn(nb, page, Hkv, D, device="cuda").bfloat16()
@@ -449,7 +449,8 @@ def bench_prefill_attn(rows):
         out = torch.empty_like(q)
         ms = timeit(lambda: sm100.prefill_attn(q, kc, vc, cu, cl, bt, L, D ** -0.5, out=out), iters=5)
         fl = 4.0 * n_seq * L * L / 2 * D * Hq / ms / 1e9
-        rows.append(dict(kernel="prefill_attn", n_seq=n_seq, L=L, ms=ms, tflops=fl, frac_tflops=fl / tf, peaks=src))
+        rows.append(dict(kernel="prefill_attn", n_seq=n_seq, L=L, heads=(Hq, Hkv, D), ms=ms, tflops=fl,
+                         frac_tflops=fl / tf, peaks=src))
         print(rows[-1], flush=True)
 
 
@@ -460,6 +461,7 @@ def main(argv=None):
     ap.add_argument("--tokens", default=None, help="moe: comma list of token counts")
     ap.add_argument("--attn", default=None, help="attention: BxCTX[,BxCTX...] (decode) or SEQSxLEN (prefill)")
     ap.add_argument("--gemm", default=None, help="gemm: TxNxK[,TxNxK...]")
+    ap.add_argument("--heads", default=None, help="prefill attention: HQxHKVxD (page 64), default 32x4x128")
     ap.add_argument("--iters", type=int, default=None)
     ap.add_argument("--warmup-iters", type=int, default=None)
     a = ap.parse_args(argv)
@@ -468,6 +470,9 @@ def main(argv=None):
         CASE["tokens"] = tuple(int(x) for x in a.tokens.split(","))
     if a.attn:
         CASE["attn"] = tuple(tuple(int(y) for y in x.split("x")) for x in a.attn.split(","))
+    if a.heads:
+        hq, hkv, d = (int(x) for x in a.heads.split("x"))
+        CASE["heads"] = (hq, hkv, d, 64)
     if a.gemm:
         CASE["gemm"] = [tuple(int(y) for y in x.split("x")) for x in a.gemm.split(",")]
     rows = []
