@@ -40,7 +40,10 @@ constexpr int pow2_ge(int v) { return v <= 32 ? 32 : (v <= 64 ? 64 : (v <= 128 ?
 
 // NCTA: sized for that many CTAs per SM (a share of the shared memory and tensor memory each). Short-K GEMMs are bound by the
 // latency of their dependent hand-overs, not by bytes in flight, and a second CTA on the SM fills the gaps.
-template <int BN, bool DUAL, int FT = 1, int NCTA = 1>
+// EPI2: two epilogue warpgroups (warps 2..5 and 6..9), each with its own staging tile, on alternate 32-token column
+// blocks of the accumulator: prompt-sized grouped GEMMs with short K (the down projection of an expert: two stages
+// per tile) are bound by the epilogue, not by the main loop.
+template <int BN, bool DUAL, int FT = 1, int NCTA = 1, bool EPI2 = false>
 struct Cfg {
   static constexpr int NW = DUAL ? 2 : 1;
   static constexpr int X_TILE = BN * KB_BYTES;
@@ -48,7 +51,8 @@ struct Cfg {
   static constexpr int SFW_OFF = X_OFF + X_TILE;
   static constexpr int SFX_OFF = SFW_OFF + NW * SF_TILE;
   static constexpr int STAGE_BYTES = SFX_OFF + SF_TILE;
-  static constexpr int BUDGET = NCTA == 1 ? SMEM_BUDGET : (NCTA == 2 ? 94 * 1024 : 54 * 1024);
+  static constexpr int NSETS = EPI2 ? 2 : 1;
+  static constexpr int BUDGET = NCTA == 1 ? (EPI2 ? SMEM_BUDGET - 16 * 1024 : SMEM_BUDGET) : (NCTA == 2 ? 94 * 1024 : 54 * 1024);
   static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int TMEM_MAX = NCTA == 1 ? 512 : (NCTA == 2 ? 256 : 128);
@@ -61,7 +65,8 @@ struct Cfg {
   static constexpr int SFA_COL = NACC * ACC_COLS;       // 16 columns per weight tile: 4 k steps x 4 row groups
   static constexpr int SFB_COL = SFA_COL + NW * 16;     // 16 columns for the token tile
   static constexpr int TMEM_COLS = pow2_ge(SFB_COL + 16);
-  static constexpr int EPI_BYTES = 32 * BM * 4;
+  static constexpr int EPI_BYTES = NSETS * 32 * BM * 4;
+  static constexpr int THREADS = 64 + 128 * NSETS;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 + 512;
   static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte alignment of swizzled tiles");
   static_assert(SFB_COL + 16 <= TMEM_MAX, "accumulators and scale factors do not fit tensor memory");
@@ -129,10 +134,10 @@ __host__ __device__ constexpr uint32_t nvf4_idesc(uint32_t M, uint32_t N) {
   return (1u << 7) | (1u << 10) | ((N >> 3) << 17) | ((M >> 4) << 24);
 }
 
-template <int BN, bool DUAL, bool QOUT, int FT, int NCTA>
-__global__ void __launch_bounds__(192, NCTA)
+template <int BN, bool DUAL, bool QOUT, int FT, int NCTA, bool EPI2>
+__global__ void __launch_bounds__(EPI2 ? 320 : 192, NCTA)
 wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const Args a) {
-  using C = Cfg<BN, DUAL, FT, NCTA>;
+  using C = Cfg<BN, DUAL, FT, NCTA, EPI2>;
   constexpr int STAGES = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -155,7 +160,7 @@ wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     }
     for (int i = 0; i < C::NACC; ++i) {
       mbar_init(&tfull[i], 1);
-      mbar_init(&tempty[i], 4);
+      mbar_init(&tempty[i], 4 * C::NSETS);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -300,9 +305,12 @@ wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------------ epilogue (warps 2..5, with EPI2 also 6..9)
     const int q = warp & 3;
-    const int etid = threadIdx.x - 64;
+    const int eset = (warp - 2) >> 2;                  // epilogue warpgroup: 32-token column blocks eset, eset + NSETS, ...
+    const int etid = threadIdx.x - 64 - eset * 128;
+    float* const stage_all = stage;
+    float* stage = stage_all + eset * (32 * BM);
     int acc = 0;
     uint32_t acc_ph = 0;
     Work it, nx;
@@ -334,7 +342,7 @@ wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         if (a.x_gscale && a.x_gs_stride != 0)
           xs_lane = (c + lane < it.ntok) ? __ldg(&a.x_gscale[long(it.tok0 + c + lane) * a.x_gs_stride]) : 1.f;
       };
-      prefetch_rows(0);
+      prefetch_rows(eset * 32);
       if (!__all_sync(0xffffffffu, mbar_wait(&tfull[acc], acc_ph, abort_flag))) {
         *abort_flag = 1;
         atomicCAS(a.status, 0, ST_TIMEOUT_TMEM_FULL);
@@ -350,9 +358,9 @@ wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       if (it.feat0 >= a.n_feat) break;
       const uint32_t t0 = tmem_base + (uint32_t(q * 32) << 16) + acc * C::ACC_COLS + f * C::SUB_COLS;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
+      for (int c = eset * 32; c < BN; c += 32 * C::NSETS) {
         if (c >= it.ntok) break;
-        if (c > 0 || (f > 0 && BN > 32)) prefetch_rows(c);
+        if (c > eset * 32 || (f > 0 && BN > 32)) prefetch_rows(c);
         uint32_t r[32];
         float g[32];
         tmem_ld32(t0 + c, r);
@@ -374,7 +382,8 @@ wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           }
           stage[j * BM + row] = v;
         }
-        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (eset == 0) asm volatile("bar.sync 2, 128;" ::: "memory");
+        else asm volatile("bar.sync 3, 128;" ::: "memory");
         const int f8 = (etid & 15) * 8;
         const int feat8 = it.feat0 + f8;
 #pragma unroll
@@ -433,7 +442,8 @@ wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
             }
           }
         }
-        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (eset == 0) asm volatile("bar.sync 2, 128;" ::: "memory");
+        else asm volatile("bar.sync 3, 128;" ::: "memory");
       }
       }
       tc_fence_before();
@@ -454,10 +464,10 @@ wgemm_nv4_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 thread_local char g_err[512];
 int g_sms = 0;
 
-template <int BN, bool DUAL, bool QOUT, int FT, int NCTA = 1>
+template <int BN, bool DUAL, bool QOUT, int FT, int NCTA = 1, bool EPI2 = false>
 int launch(const CUtensorMap* tmW, const CUtensorMap* tmX, const Args& a, int grid, cudaStream_t stream) {
-  using C = Cfg<BN, DUAL, FT, NCTA>;
-  auto kfn = wgemm_nv4_kernel<BN, DUAL, QOUT, FT, NCTA>;
+  using C = Cfg<BN, DUAL, FT, NCTA, EPI2>;
+  auto kfn = wgemm_nv4_kernel<BN, DUAL, QOUT, FT, NCTA, EPI2>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
@@ -467,7 +477,7 @@ int launch(const CUtensorMap* tmW, const CUtensorMap* tmX, const Args& a, int gr
     }
     attr_set = true;
   }
-  launch_pdl(kfn, dim3(grid), dim3(192), C::SMEM_BYTES, stream, *tmW, *tmX, a);
+  launch_pdl(kfn, dim3(grid), dim3(C::THREADS), C::SMEM_BYTES, stream, *tmW, *tmX, a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     snprintf(g_err, sizeof(g_err), "wgemm_nv4 launch: %s", cudaGetErrorString(e));
@@ -547,6 +557,10 @@ int wgemm_nv4_launch(const Nv4Host& h, cudaStream_t stream) {
   if (total <= 0) return 0;
   const int slots = ncta * g_sms;
   const int grid = int(total < slots ? total : slots);
+  // prompt-sized grouped steps with 64-token tiles: two epilogue warpgroups
+  const bool big = h.tile_group && bn == 64 && h.n_tok_tiles_max >= 256;
+  if (big && !h.dual && !qout) return launch<64, false, false, 1, 1, true>(tmW, tmX, a, grid, stream);
+  if (big && h.dual && qout) return launch<64, true, true, 1, 1, true>(tmW, tmX, a, grid, stream);
   if (short_k) return launch<32, false, false, 1, 3>(tmW, tmX, a, grid, stream);
   if (many_dual) return launch<32, true, true, 1, 2>(tmW, tmX, a, grid, stream);
 #define LB_NV4(BN_, DUAL_, FT_)                                                             \
