@@ -89,6 +89,8 @@ class ClockSampler:
 CONFIGS = {
     2: dict(model="qwen3-30b-a3b", prompt_len=8192, weights="bf16", dtype="bf16"),
     3: dict(model="qwen35-80b-a3b", prompt_len=1024, weights="nvfp4", dtype="nvfp4 experts (W4A4), bf16 elsewhere"),
+    4: dict(model="deepseek-671b", prompt_len=1024, weights="fp8",
+            dtype="fp8 (block-scaled e4m3 weights, e4m3 activations on the projections and experts), bf16 elsewhere"),
     5: dict(model="dense-27b", prompt_len=1024, weights="bf16", dtype="bf16"),
 }
 
@@ -116,6 +118,23 @@ def build_model(a, cfg, dev, pctx, shard, weights_mode):
             if not a.no_fold and (world == 1 or (shard is not None and shard.shared_whole)):
                 place_shared_expert(out, p, il, cfg, pctx.rank, world)
             quantize_moe_layer_nvfp4(out, p, native=not a.nvfp4_expand)
+    if weights_mode == "fp8":
+        from legion_b200.ops.sm100 import Fp8Weight
+
+        def post(name, out):
+            # every projection is re-encoded to block-scaled e4m3 as soon as it has been generated (the bf16 form
+            # of a 671B model does not fit the GPUs)
+            t = out[name]
+            leaf = name.split(".", 1)[1] if "." in name else name
+            leaf = leaf.replace("l.", "", 1) if name.startswith("mtp") and leaf.startswith("l.") else leaf
+            if leaf not in Decoder.FP8_LEAVES or not isinstance(t, torch.Tensor) or t.dtype != torch.bfloat16:
+                return
+            if not a.fp8_all and not leaf.startswith(("mlp.", "moe.")):
+                return      # the small attention projections stay bf16: no activation encoding in front of them
+            rows, K = t.shape[-2], t.shape[-1]
+            if K % 128 or rows % 128 or (leaf.endswith("gate_up") and (rows // 2) % 128):
+                return
+            out[name] = Fp8Weight.quantize(t)
     weights = random_weights(cfg, dev, torch.bfloat16, seed=0, shard=shard, post=post)
     torch.cuda.synchronize()
     return weights
@@ -139,6 +158,8 @@ def main(argv=None):
                          "with mirrored tokens, partial outputs meeting in the layer's reduction (ep). auto: ep "
                          "from 4 GPUs for bf16 experts, always for NVFP4 experts")
     ap.add_argument("--no-fold", action="store_true", help="keep the shared expert as a dense FFN of its own")
+    ap.add_argument("--fp8-all", action="store_true",
+                    help="config 4: also keep the attention projections in FP8 (default: FFNs and experts only)")
     ap.add_argument("--no-head-split", action="store_true",
                     help="N > 1: every rank keeps the whole LM head instead of its slice of the vocabulary")
     ap.add_argument("--nvfp4-expand", action="store_true",
@@ -239,6 +260,7 @@ def main(argv=None):
                       block_size=64, prefix_cache=False, device=str(dev), model_name=spec["model"])
     model = Decoder(cfg, weights, pctx, max_position=ec.ctx_size + 8)
     model.fuse_gdn_in_proj()
+    model.fuse_mla_in_proj()
     head_split = (not a.no_head_split) and model.split_head()
     eng = LmEngine(model, tok, ec, start=False)
     graphs = eng._graphs

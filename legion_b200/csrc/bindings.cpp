@@ -422,12 +422,13 @@ void moe_route_small(const Tensor& x, const OptT& norm_w, double eps, double w_o
   if (sh_gate_w.has_value()) {
     check_bf16(*sh_gate_w, "sh_gate_w");
     TORCH_CHECK(sh_gate_w->numel() == x.size(1) && sh_gate_w->is_contiguous() && sh_logit.has_value() &&
-                    sh_logit->scalar_type() == at::kFloat && sh_logit->numel() >= T && shared_slot,
-                "moe_route_small: the shared gate is one row of the hidden width with a float [T] scratch");
+                    sh_logit->scalar_type() == at::kFloat && sh_logit->numel() >= 4 * 64 && shared_slot,
+                "moe_route_small: the shared gate is one row of the hidden width with a float [4 * 64] scratch");
   }
   TORCH_CHECK(x.size(1) == w.size(1) && x.stride(1) == 1 && w.stride(1) == 1, "moe_route_small: shape mismatch");
   TORCH_CHECK(norm_w.has_value() == x_normed.has_value(), "moe_route_small: norm weight and output go together");
-  TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.numel() >= T * E, "moe_route_small: logits too small");
+  TORCH_CHECK(logits.scalar_type() == at::kFloat && logits.numel() >= 4 * 64 * 512,
+              "moe_route_small: the logit scratch holds four planes of 64 x 512 floats (one per column split)");
   TORCH_CHECK(done_ctr.numel() >= 2 && done_ctr.element_size() == 4, "moe_route_small: two int32 counters");
   TORCH_CHECK(active.scalar_type() == at::kInt && active.numel() >= n_local, "moe_route_small: active flags [n_local]");
   const int64_t max_slots = std::min<int64_t>(E, n_local) + (shared_slot ? 1 : 0);

@@ -193,6 +193,9 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const float* __restric
 // is -1.
 //   tile_group[slot] = expert, slot_base[slot] = slot * bn, tile_ntok[slot] = T, meta = {n_active, n_active * bn}
 //   out_rows[slot * bn + t] = pair index t * k + c (or -1), tok_scale[slot * bn + t] = routing weight
+constexpr int ROUTE_LSTR = 64 * 512;          // floats between the logit planes of two K splits
+constexpr int ROUTE_MAX_KSPLIT = 4;
+
 template <int MAXE>
 __global__ void __launch_bounds__(512) moe_route_small_kernel(
     const __nv_bfloat16* __restrict__ x, long ldx, const float* __restrict__ norm_w, float eps, float w_offset,
@@ -201,41 +204,51 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
     int topk_group, int* ids, float* wts, int T, int bn, int* __restrict__ tile_group, int* __restrict__ slot_base,
     int* __restrict__ tile_ntok, int* __restrict__ meta, int* __restrict__ out_rows, float* __restrict__ tok_scale,
     unsigned int* done_ctr, int e_lo, int n_local, const __nv_bfloat16* __restrict__ sh_gate_w, float* sh_logit,
-    int shared_slot, int epc, int tpp, int* status, int* __restrict__ active) {
-  extern __shared__ uint4 xs_rows[];          // [tpp][H / 8] token rows of the current pass
+    int shared_slot, int epc, int tpp, int ksplit, int* status, int* __restrict__ active) {
+  extern __shared__ uint4 xs_rows[];          // [tpp][H / 8 / ksplit] this CTA's columns of the pass's token rows
   __shared__ int s_last;
   __shared__ float s_logit[512];
   __shared__ float s_red[16];
   __shared__ unsigned long long s_cand[16 * 32];
   __shared__ int s_wsum[17];
   __shared__ int s_chosen[512];
+  __shared__ float s_sel[512];
+  __shared__ unsigned s_keep;
   griddep_wait();
   griddep_launch();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nv = H / 8;
 
+  // K split: CTA (rg, ks) owns router rows rg * epc .. and columns ks * H / ksplit .. of them; the partial logits of
+  // the splits land in separate planes (LSTR floats apart) and are added in a fixed order by whoever reads them
+  const int rg = blockIdx.x / ksplit, ks = blockIdx.x % ksplit, n_rg = gridDim.x / ksplit;
+  const int nvs = nv / ksplit, v_lo = ks * nvs;
   const int wpe = 16 / epc;                   // warps per router row
   const int tpw = tpp / wpe;                  // tokens of a pass per warp
-  const int e = blockIdx.x * epc + warp / wpe;
+  const int e = rg * epc + warp / wpe;
   const int tq = warp % wpe;
   const bool is_gate = e >= E;                // row E: the sigmoid gate of the shared expert
   const bool row_ok = e < E + (sh_gate_w ? 1 : 0);
-  const uint4* w4 = reinterpret_cast<const uint4*>(is_gate ? sh_gate_w : w + long(e) * ldw);
+  const uint4* w4 = reinterpret_cast<const uint4*>(is_gate ? sh_gate_w : w + long(e) * ldw) + v_lo;
+  float* lg_out = logits + long(ks) * ROUTE_LSTR;
   for (int base = 0; base < T; base += tpp) {
     if (warp < tpp && base + warp < T) {
       const int t = base + warp;
       const uint4* xr = reinterpret_cast<const uint4*>(x + long(t) * ldx);
-      uint4* dst = xs_rows + warp * nv;
+      uint4* dst = xs_rows + warp * nvs;
       float ssq = 0.f;
-      for (int v0 = lane; v0 < nv; v0 += 256) {       // eight loads in flight per lane
+      // with a norm the whole row is read for its sum of squares; only this CTA's columns are kept
+      const int r_lo = norm_w ? 0 : v_lo, r_hi = norm_w ? nv : v_lo + nvs;
+      for (int v0 = r_lo + lane; v0 < r_hi; v0 += 256) {       // eight loads in flight per lane
         uint4 u[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-          if (v0 + 32 * i < nv) u[i] = xr[v0 + 32 * i];
+          if (v0 + 32 * i < r_hi) u[i] = xr[v0 + 32 * i];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          if (v0 + 32 * i < nv) {
-            dst[v0 + 32 * i] = u[i];
+          const int v = v0 + 32 * i;
+          if (v < r_hi) {
+            if (v >= v_lo && v < v_lo + nvs) dst[v - v_lo] = u[i];
             if (norm_w) {
               const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&u[i]);
 #pragma unroll
@@ -251,12 +264,13 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
         const float inv = rsqrtf(ssq / float(H) + eps);
-        const bool writer = (t % gridDim.x) == blockIdx.x;
-        for (int v = lane; v < nv; v += 32) {
-          uint4 u = dst[v];                    // written by this lane above
+        const bool writer = (t % n_rg) == rg;
+        __syncwarp();
+        for (int v = lane; v < nvs; v += 32) {
+          uint4 u = dst[v];
           __nv_bfloat162* xp = reinterpret_cast<__nv_bfloat162*>(&u);
-          const float4 n0 = reinterpret_cast<const float4*>(norm_w)[2 * v];
-          const float4 n1 = reinterpret_cast<const float4*>(norm_w)[2 * v + 1];
+          const float4 n0 = reinterpret_cast<const float4*>(norm_w)[2 * (v_lo + v)];
+          const float4 n1 = reinterpret_cast<const float4*>(norm_w)[2 * (v_lo + v) + 1];
           const float nw[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -264,7 +278,7 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
             xp[i] = __floats2bfloat162_rn(f.x * inv * (nw[2 * i] + w_offset), f.y * inv * (nw[2 * i + 1] + w_offset));
           }
           dst[v] = u;
-          if (writer) reinterpret_cast<uint4*>(x_normed + long(t) * ldn)[v] = u;
+          if (writer) reinterpret_cast<uint4*>(x_normed + long(t) * ldn)[v_lo + v] = u;
         }
       }
     }
@@ -273,15 +287,15 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
       float acc[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-      for (int v0 = lane; v0 < nv; v0 += 256) {       // eight weight vectors in flight per lane
+      for (int v0 = lane; v0 < nvs; v0 += 256) {       // eight weight vectors in flight per lane
         uint4 wu[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-          if (v0 + 32 * i < nv) wu[i] = w4[v0 + 32 * i];
+          if (v0 + 32 * i < nvs) wu[i] = w4[v0 + 32 * i];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int v = v0 + 32 * i;
-          if (v < nv) {
+          if (v < nvs) {
             const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wu[i]);
             float2 wf[4];
 #pragma unroll
@@ -290,7 +304,7 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
             for (int j = 0; j < 8; ++j) {
               const int tok = tq * tpw + j;
               if (j < tpw && base + tok < T) {
-                const uint4 xu = xs_rows[tok * nv + v];
+                const uint4 xu = xs_rows[tok * nvs + v];
                 const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xu);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
@@ -311,8 +325,8 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
 #pragma unroll
           for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
           if (lane == 0) {
-            if (is_gate) sh_logit[base + tok] = a;
-            else logits[long(base + tok) * E + e] = a;
+            if (is_gate) sh_logit[ks * 64 + base + tok] = a;
+            else lg_out[long(base + tok) * E + e] = a;
           }
         }
       }
@@ -348,18 +362,43 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
   __syncthreads();
   __threadfence();
   for (int t = blockIdx.x; t < T; t += gridDim.x) {
-    if (n_group > 1) {
-      // group-limited routing: the one-warp form (it ranks the groups inside a warp)
-      if (warp == 0)
-        router_topk_row<MAXE>(logits, E, bias, E, k, mode, renorm, route_scale, n_group, topk_group, ids, wts, t);
-      continue;
-    }
     // thread e holds expert e: score, packed key (score bits above, inverted index below)
     const int e = tid;
-    const float l = e < E ? __ldcg(logits + long(t) * E + e) : -INFINITY;
+    float l = -INFINITY;
+    if (e < E) {
+      l = __ldcg(logits + long(t) * E + e);
+      for (int sp = 1; sp < ksplit; ++sp) l += __ldcg(logits + long(sp) * ROUTE_LSTR + long(t) * E + e);
+    }
     float selv = l;
     if (mode == 1) selv = 1.f / (1.f + __expf(-l)) + (bias && e < E ? bias[e] : 0.f);
     s_logit[e] = l;
+    if (mode == 1 && n_group > 1 && topk_group < n_group) {
+      // group-limited routing: lane g of warp 0 scores group g (the sum of its two best biased scores), the groups
+      // are ranked (ties: lower index first) and the experts of the groups that are not kept drop out
+      const int gs = E / n_group;
+      s_sel[e] = selv;
+      __syncthreads();
+      if (warp == 0) {
+        float gscore = -INFINITY;
+        if (lane < n_group) {
+          float b1 = -INFINITY, b2 = -INFINITY;
+          for (int i = 0; i < gs; ++i) {
+            const float v = s_sel[lane * gs + i];
+            if (v > b1) { b2 = b1; b1 = v; } else if (v > b2) { b2 = v; }
+          }
+          gscore = b1 + (b2 == -INFINITY ? 0.f : b2);
+        }
+        int rank = 0;
+        for (int g = 0; g < n_group; ++g) {
+          const float og = __shfl_sync(0xffffffffu, gscore, g);
+          if (lane < n_group && (og > gscore || (og == gscore && g < lane))) ++rank;
+        }
+        const unsigned keep = __ballot_sync(0xffffffffu, lane < n_group && rank < topk_group);
+        if (lane == 0) s_keep = keep;
+      }
+      __syncthreads();
+      if (e < E && !((s_keep >> (e / gs)) & 1u)) selv = -INFINITY;
+    }
     float mxv = 0.f, inv_sum = 1.f;
     if (mode == 0 && !renorm) {
       // softmax weights without renormalisation need the partition sum over all experts
@@ -455,7 +494,10 @@ __global__ void __launch_bounds__(512) moe_route_small_kernel(
       // the shared expert (stacked behind this rank's routed experts as group n_local) is used by every token:
       // its output rows are the pairs P .. P + T - 1, weighted by the sigmoid of its gate (or 1)
       out_rows[n_local * bn + t] = P + t;
-      tok_scale[n_local * bn + t] = sh_gate_w ? 1.f / (1.f + __expf(-__ldcg(&sh_logit[t]))) : 1.f;
+      float gl = 0.f;
+      if (sh_gate_w)
+        for (int sp = 0; sp < ksplit; ++sp) gl += __ldcg(&sh_logit[sp * 64 + t]);
+      tok_scale[n_local * bn + t] = sh_gate_w ? 1.f / (1.f + __expf(-gl)) : 1.f;
     }
     __syncthreads();
   }
@@ -514,10 +556,14 @@ int moe_route_small_launch(const void* x, long ldx, const float* norm_w, float e
   auto xn = static_cast<__nv_bfloat16*>(x_normed);
   auto wb = static_cast<const __nv_bfloat16*>(w);
   const int epc = E >= 256 ? 8 : 4;                              // router rows per CTA
-  const int tpp = size_t(16) * H * 2 <= 192 * 1024 ? 16 : 8;     // tokens staged per pass
-  if (size_t(tpp) * H * 2 > 200 * 1024) return 1;
-  const int smem = tpp * H * 2;
-  const int grid = (E + (sh_gate_w ? 1 : 0) + epc - 1) / epc;
+  // wide models: the columns are split over CTAs too, so that the weight stream and the staging of the token rows
+  // spread over four times as many SMs (the logit and gate buffers hold ROUTE_MAX_KSPLIT planes)
+  const int ksplit = (H >= 4096 && (H / 8) % ROUTE_MAX_KSPLIT == 0) ? ROUTE_MAX_KSPLIT : 1;
+  const int Hs = H / ksplit;
+  const int tpp = size_t(16) * Hs * 2 <= 192 * 1024 ? 16 : 8;    // tokens staged per pass
+  if (size_t(tpp) * Hs * 2 > 200 * 1024) return 1;
+  const int smem = tpp * Hs * 2;
+  const int grid = ((E + (sh_gate_w ? 1 : 0) + epc - 1) / epc) * ksplit;
 #define LB_ROUTE(MAXE)                                                                                              \
   {                                                                                                                 \
     static int smem_set = 0;                                                                                        \
@@ -530,7 +576,7 @@ int moe_route_small_launch(const void* x, long ldx, const float* norm_w, float e
     launch_pdl(moe_route_small_kernel<MAXE>, dim3(grid), dim3(512), smem, s, xb, ldx, norm_w, eps, w_offset, xn,   \
                ldn, wb, ldw, H, logits, bias, E, k, mode, renorm, route_scale, n_group, topk_group, ids, wts, T,    \
                bn, tile_group, slot_base, tile_ntok, meta, out_rows, tok_scale, done_ctr, e_lo, n_local, sg,        \
-               sh_logit, shared_slot, epc, tpp, status, active);                                                    \
+               sh_logit, shared_slot, epc, tpp, ksplit, status, active);                                                    \
   }
   if (E <= 128) LB_ROUTE(128)
   else if (E <= 256) LB_ROUTE(256)

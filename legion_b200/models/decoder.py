@@ -288,12 +288,14 @@ class Decoder:
     FP8_LEAVES = ("attn.qkv", "attn.o", "mlp.gate_up", "mlp.down", "moe.gate_up", "moe.down", "moe.sh_gate_up",
                   "moe.sh_down", "mla.q_a", "mla.q_b", "mla.q", "mla.kv_a", "mla.o", "gdn.in_qkv", "gdn.in_z", "gdn.out")
 
-    def quantize_weights_fp8(self, experts_only: bool = False) -> int:
+    def quantize_weights_fp8(self, experts_only: bool = False, ffn_only: bool = False) -> int:
         """Re-encodes the projection weights (routed experts, dense and shared FFNs, attention / latent-attention /
         linear-attention projections) to block-scaled FP8 in place: e4m3 with one fp32 scale per 128 x 128 block,
         the encoding of FP8 checkpoints. The GEMMs then run on the e4m3 tensor-core path with activations
         quantised per token and 128 columns (``ops.sm100.Fp8Weight``). Embedding, head, router, norms and the small
-        gate projections stay as they are. Returns the number of bytes saved. GPU only."""
+        gate projections stay as they are; ``ffn_only`` also leaves the attention projections alone (they are a
+        few per cent of the bytes, and a decode step then has no activation encoding in front of them).
+        Returns the number of bytes saved. GPU only."""
         from ..ops.sm100 import Fp8Weight
         saved = 0
         for name in list(self.w):
@@ -302,6 +304,8 @@ class Decoder:
             if leaf not in self.FP8_LEAVES or not isinstance(t, torch.Tensor) or t.dtype != torch.bfloat16:
                 continue
             if experts_only and leaf not in ("moe.gate_up", "moe.down"):
+                continue
+            if ffn_only and not leaf.startswith(("mlp.", "moe.")):
                 continue
             rows, K = t.shape[-2], t.shape[-1]
             if K % 128 or rows % 128:
@@ -380,20 +384,45 @@ class Decoder:
             n += 1
         return n
 
+    def fuse_mla_in_proj(self) -> int:
+        """Stacks the two input projections of every latent-attention layer that read the layer input (the low-rank
+        query projection ``q_a`` and the latent / rope-key projection ``kv_a``) into one weight ``mla.qkv_a`` so that
+        a layer needs one GEMM for them (bf16 weights only). Returns the number of layers fused."""
+        n = 0
+        for il, kind in enumerate(self.cfg.layer_kinds):
+            p = f"l{il}"
+            qa, kva = self.w.get(f"{p}.mla.q_a"), self.w.get(f"{p}.mla.kv_a")
+            if kind != "mla" or f"{p}.mla.qkv_a" in self.w or not isinstance(qa, torch.Tensor) or \
+                    not isinstance(kva, torch.Tensor) or qa.dtype != torch.bfloat16 or kva.dtype != torch.bfloat16 or \
+                    not qa.is_cuda or qa.shape[0] % 8:
+                continue
+            both = torch.cat([qa, kva], 0)
+            self.w[f"{p}.mla.q_a"], self.w[f"{p}.mla.kv_a"] = both[:qa.shape[0]], both[qa.shape[0]:]
+            self.w[f"{p}.mla.qkv_a"] = both
+            n += 1
+        return n
+
     def _mla(self, p: str, il: int, x, b: StepBatch, kv: KvCache):
         """Latent attention: cache row = [rmsnorm(c_kv) | rope(k_pe)]; keys/values are expanded from
         the cached latents of each sequence (prefill form), queries carry [nope | rope] parts."""
         cfg, w = self.cfg, self.w
         nh, dn, dr, dvh, L = self.n_head_l, cfg.qk_nope_dim, cfg.qk_rope_dim, cfg.v_head_dim, cfg.kv_lora
         T = x.shape[0]
+        kva = None
+        both_w = w.get(f"{p}.mla.qkv_a")
         if cfg.q_lora > 0:
-            qa = ops.linear(x, w[f"{p}.mla.q_a"])
+            if both_w is not None and x.is_cuda:
+                both = ops.linear(x, both_w)            # q_a and kv_a in one GEMM; the parts are column slices
+                qa, kva = both[:, :cfg.q_lora], both[:, cfg.q_lora:]
+            else:
+                qa = ops.linear(x, w[f"{p}.mla.q_a"])
             qa, _ = ops.rmsnorm(qa, w[f"{p}.mla.q_a_norm"], cfg.rms_eps, cfg.norm_offset)
             q = ops.linear(qa, w[f"{p}.mla.q_b"])
         else:
             q = ops.linear(x, w[f"{p}.mla.q"])
         q = q.view(T, nh, dn + dr)
-        kva = ops.linear(x, w[f"{p}.mla.kv_a"])
+        if kva is None:
+            kva = ops.linear(x, w[f"{p}.mla.kv_a"])
         wkv_b = w[f"{p}.mla.kv_b"].view(nh, dn + dvh, L)
         scale = cfg.attn_scale or (dn + dr) ** -0.5
         if x.is_cuda and x.dtype == torch.bfloat16 and ops.sm100.mla_supported(nh, L, dr, kv.page):
@@ -519,7 +548,14 @@ class Decoder:
             folded = bool(getattr(routing, "shared_slot", False))
             if cfg.shared_ff > 0 and not folded and w.get(f"{p}.moe.sh_down") is not None:
                 fs = w[f"{p}.moe.sh_down"].shape[1]
-                hs = ops.gate_up_act(x, w[f"{p}.moe.sh_gate_up"], fs, cfg.ffn_act)
+                xs = x
+                if (x.is_cuda and isinstance(w[f"{p}.moe.sh_gate_up"], ops.sm100.Fp8Weight)
+                        and isinstance(w.get(f"{p}.moe.gate_up"), ops.sm100.Fp8Weight) and x.shape[0] <= 64):
+                    # FP8 shared and routed experts read the same rows: encode them once
+                    xs = ops.sm100.Fp8Act.of(x)
+                    if isinstance(routing, ops.sm100.Routing):
+                        routing.xq = xs
+                hs = ops.gate_up_act(xs, w[f"{p}.moe.sh_gate_up"], fs, cfg.ffn_act)
                 shared = ops.linear(hs, w[f"{p}.moe.sh_down"])
                 if cfg.shared_gate:
                     gate = ops.linear(x, w[f"{p}.moe.sh_gate"], out_dtype=torch.float32).reshape(-1).contiguous()

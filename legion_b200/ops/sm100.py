@@ -489,6 +489,34 @@ class Fp8Weight:
         return out.view(self.shape).to(dtype)
 
 
+class Fp8Act:
+    """Activation rows already encoded for the FP8 GEMMs (e4m3 bytes + one scale per row and 128 columns), kept with
+    the bf16 rows they came from: a layer input that feeds several FP8 projections is encoded once."""
+    __slots__ = ("x", "data", "scale")
+
+    def __init__(self, x, data, scale):
+        self.x, self.data, self.scale = x, data, scale
+
+    is_cuda = True
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    @property
+    def device(self):
+        return self.x.device
+
+    @classmethod
+    def of(cls, x):
+        d, s = fp8_quant_act(x)
+        return cls(x, d, s)
+
+
+def _fp8_parts(x):
+    return (x.data, x.scale) if isinstance(x, Fp8Act) else fp8_quant_act(x)
+
+
 def fp8_quant_act(x, out=None, scale=None):
     """bf16 activations [T, K] -> (e4m3 bytes [T, K], fp32 scale per row and 128 columns [T, K / 128])."""
     C = ext()
@@ -504,7 +532,7 @@ def _linear_fp8(x, w: "Fp8Weight", residual, out, dual: bool, n_feat: int):
     C = ext()
     T, K = x.shape
     ws = Workspace.get(x.device)
-    x8, xs = fp8_quant_act(x)
+    x8, xs = _fp8_parts(x)
     bn = 32 if T <= 32 else 64
     n_tt = (T + bn - 1) // bn
     ft = (n_feat + 127) // 128
@@ -523,6 +551,8 @@ def _linear_fp8(x, w: "Fp8Weight", residual, out, dual: bool, n_feat: int):
 def linear(x, w, residual=None, out=None, out_dtype=torch.bfloat16, split_k: Optional[int] = None, bn=None):
     """out[T, N] = x[T, K] @ w[N, K]^T (+ residual)."""
     C = ext()
+    if isinstance(x, Fp8Act) and not isinstance(w, Fp8Weight):
+        x = x.x
     T, K = x.shape
     N = w.shape[0]
     q = isinstance(w, QWeight)
@@ -558,6 +588,8 @@ def linear(x, w, residual=None, out=None, out_dtype=torch.bfloat16, split_k: Opt
 def gate_up_act(x, w_gate_up, n_ff: int, out=None, bn=None, split_k: Optional[int] = None):
     """silu(x @ Wg^T) * (x @ Wu^T) with Wg = w_gate_up[:n_ff], Wu = w_gate_up[n_ff:]."""
     C = ext()
+    if isinstance(x, Fp8Act) and not isinstance(w_gate_up, Fp8Weight):
+        x = x.x
     T, K = x.shape
     if out is None:
         out = torch.empty(T, n_ff, dtype=torch.bfloat16, device=x.device)
@@ -779,7 +811,7 @@ class DenseRoute:
         self.meta = torch.zeros(2, **i32)
         self.out_rows = torch.full((n_slots * self.stride,), -1, **i32)
         self.tok_scale = torch.zeros(n_slots * self.stride, dtype=torch.float32, device=device)
-        self.sh_logit = torch.zeros(64, dtype=torch.float32, device=device)
+        self.sh_logit = torch.zeros(4 * 64, dtype=torch.float32, device=device)   # one plane per column split
         self.active = torch.zeros(n_slots, **i32)      # per local expert: chosen by some token of the step
         self.h_all = None
         self.hq = None
@@ -806,7 +838,7 @@ def router(x, w_router, k, mode="softmax", renorm=True, route_scale=1.0, bias=No
         return Routing(ids, wts, None, xn)
     C = ext()
     ws = Workspace.get(x.device)
-    logits = ws.buf("router_logits", (64 * 512,), torch.float32)
+    logits = ws.buf("router_logits", (4 * 64 * 512,), torch.float32)    # one plane per column split
     ctr = ws._cache.get("router_ctr")
     if ctr is None:
         ctr = torch.zeros(4, dtype=torch.int32, device=x.device)
@@ -1138,7 +1170,7 @@ def _moe_experts_fp8(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, shared, shared_
         if dr.h_all is None or dr.h_all.shape[1] != n_ff:
             dr.h_all = torch.zeros(dr.n_slots * dr.stride, n_ff, dtype=torch.bfloat16, device=x.device)
         y_pairs = _dense_pairs(dr, P, T, k, H, x.device)
-        x8, xs = fp8_quant_act(x)
+        x8, xs = _fp8_parts(routing.xq) if isinstance(routing.xq, Fp8Act) else fp8_quant_act(x)
         C.wgemm_fp8(gu2, gu_s, x8, xs, dr.h_all, None, None, None, n_ff, True, n_ff, dr.bn, 1, None, None, ws.status,
                     dr.tile_group, dr.zeros, dr.tile_ntok, dr.meta, dr.n_slots, 2 * n_ff, 0, dr.slot_base)
         h8, hs = fp8_quant_act(dr.h_all)

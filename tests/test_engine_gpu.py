@@ -142,6 +142,41 @@ def test_engine_with_fp8_weights():
     assert Workspace.get("cuda").check() == 0
 
 
+def test_latent_attention_stacked_input_projection_and_shared_fp8_rows():
+    """The query and latent projections of a latent-attention layer stacked into one GEMM give the logits of the
+    separate GEMMs; with FP8 FFNs the shared and the routed experts read one encoding of the layer input, and the
+    engine decodes through graphs on that path."""
+    from legion_b200.engine.types import GenerateRequest, SamplingParams
+    from legion_b200.ops.sm100 import Fp8Weight, Workspace
+    cfg = _cfgs()[3]
+    w = random_weights(cfg, "cuda", torch.bfloat16, seed=3, std=0.05)
+    ec = dict(ctx_size=512, max_seqs=4, block_size=64, prefill_chunk=256, prefix_cache=False)
+    prompt = torch.randint(0, 255, (150,), generator=torch.Generator().manual_seed(5)).tolist()
+
+    def first_logits(eng):
+        seq = eng.prepare(GenerateRequest(prompt_tokens=prompt, sampling=SamplingParams(max_tokens=4, ignore_eos=True)))
+        eng.waiting.push(seq)
+        eng._admit()
+        b = eng.build_batch([(seq, 0, len(prompt))])
+        return eng.model.forward(b, eng.kv, eng.states).logits.float().cpu()
+
+    plain = build_engine(cfg, weights=dict(w), device="cuda", engine_cfg=EngineConfig(**ec), start=False)
+    fused = build_engine(cfg, weights=dict(w), device="cuda", engine_cfg=EngineConfig(**ec), start=False)
+    assert fused.model.fuse_mla_in_proj() == cfg.n_layer
+    a, b = first_logits(plain), first_logits(fused)
+    assert (a - b).abs().max().item() <= 0.02 * a.abs().max().item() + 1e-3
+    eng = build_engine(cfg, weights=dict(w), device="cuda", engine_cfg=EngineConfig(**ec))
+    eng.model.fuse_mla_in_proj()
+    assert eng.model.quantize_weights_fp8(ffn_only=True) > 0
+    assert isinstance(eng.model.w["l1.moe.sh_gate_up"], Fp8Weight) and isinstance(eng.model.w["l1.mla.q_b"], torch.Tensor)
+    r1 = eng.generate_text(tokens=prompt, max_tokens=12, ignore_eos=True)
+    r2 = eng.generate_text(tokens=prompt, max_tokens=12, ignore_eos=True)
+    replays = eng._graphs.replays
+    eng.shutdown()
+    assert len(r1.token_ids) == 12 and r1.token_ids == r2.token_ids and replays > 0
+    assert Workspace.get("cuda").check() == 0
+
+
 def test_prefix_cache_host_tier_on_gpu():
     """Evicted prefix-cache blocks go to pinned host memory and come back for a later prompt with that prefix."""
     from legion_b200.config import ModelConfig

@@ -120,9 +120,11 @@ def test_moe_plan_fused_equals_three_pass(T, E, k, e_lo, n_local):
 
 
 @pytest.mark.parametrize("T,E,k,H,mode", [(1, 128, 8, 2048, "softmax"), (16, 128, 8, 2048, "softmax"),
-                                          (37, 256, 8, 512, "sigmoid"), (64, 8, 2, 256, "softmax")])
+                                          (37, 256, 8, 512, "sigmoid"), (64, 8, 2, 256, "softmax"),
+                                          (16, 256, 8, 7168, "sigmoid"), (33, 64, 6, 4096, "softmax")])
 def test_router_fused(T, E, k, H, mode):
-    """One-launch router (logits + top-k) against fp32 logits and the reference selection."""
+    """One-launch router (logits + top-k) against fp32 logits and the reference selection; hidden widths from 4096
+    on split the columns over CTAs and add the partial logits in a fixed order."""
     torch.manual_seed(T + E)
     x, w = rnd(T, H), rnd(E, H, scale=H ** -0.5)
     bias = torch.randn(E, device=DEV) * 0.05 if mode == "sigmoid" else None
@@ -144,7 +146,7 @@ def test_router_fused(T, E, k, H, mode):
 
 
 @pytest.mark.parametrize("T,E,k,H,F", [(1, 128, 8, 512, 256), (16, 128, 8, 2048, 768), (33, 16, 4, 256, 192),
-                                       (64, 8, 2, 256, 128)])
+                                       (64, 8, 2, 256, 128), (16, 32, 4, 4096, 256)])
 def test_moe_dense_route(T, E, k, H, F):
     """Decode-sized path: norm + router + top-k + dense tables in one launch, expert GEMMs without a gather."""
     torch.manual_seed(T * 3 + E)
