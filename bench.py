@@ -99,7 +99,8 @@ def build_model(a, cfg, dev, pctx, shard, weights_mode):
     """Random-init weights generated on the device; NVFP4 configurations are folded and quantised layer by layer
     while they are generated (their bf16 form would not fit one GPU)."""
     import torch
-    from legion_b200.models.decoder import Decoder, place_shared_expert, quantize_moe_layer_nvfp4
+    from legion_b200.models.decoder import (Decoder, place_shared_expert, quantize_moe_layer_fp8,
+                                            quantize_moe_layer_nvfp4)
     from legion_b200.models.weights import layer_of, random_weights
     world = pctx.world
     post = None
@@ -127,6 +128,17 @@ def build_model(a, cfg, dev, pctx, shard, weights_mode):
             t = out[name]
             leaf = name.split(".", 1)[1] if "." in name else name
             leaf = leaf.replace("l.", "", 1) if name.startswith("mtp") and leaf.startswith("l.") else leaf
+            il = layer_of(name)
+            if il is not None and cfg.is_moe_layer(il) and leaf.startswith("moe.") and not name.startswith("mtp"):
+                # a routed layer: when its last expert tensor has arrived, the shared expert is stacked behind this
+                # rank's routed experts (or dropped, on the ranks that do not keep it) and the layer is encoded
+                last = "moe.sh_gate" if (cfg.shared_ff > 0 and cfg.shared_gate) else (
+                    "moe.sh_down" if cfg.shared_ff > 0 else "moe.down")
+                if leaf == last:
+                    if not a.no_fold and (world == 1 or (shard is not None and shard.shared_whole)):
+                        place_shared_expert(out, f"l{il}", il, cfg, pctx.rank, world)
+                    quantize_moe_layer_fp8(out, f"l{il}")
+                return
             if leaf not in Decoder.FP8_LEAVES or not isinstance(t, torch.Tensor) or t.dtype != torch.bfloat16:
                 return
             if not a.fp8_all and not leaf.startswith(("mlp.", "moe.")):
@@ -196,11 +208,11 @@ def main(argv=None):
     grid = [int(u) for u in a.grid.split(",") if u.strip()]
     all_users = sorted(set(grid + [a.users]))
     U_max = max(all_users)
-    nvfp4 = spec["weights"] == "nvfp4"
-    ep = world > 1 and cfg.n_expert > 0 and (a.moe == "ep" or (a.moe == "auto" and (world >= 4 or nvfp4)))
+    nvfp4, fp8 = spec["weights"] == "nvfp4", spec["weights"] == "fp8"
+    ep = world > 1 and cfg.n_expert > 0 and (a.moe == "ep" or (a.moe == "auto" and (world >= 4 or nvfp4 or fp8)))
     pctx = pdist.init_from_env("cuda", comm=a.comm, max_rows=8192, hidden=cfg.hidden, expert_parallel=ep)
     shard = Shard(cfg, rank, world, expert_parallel=ep,
-                  shared_whole=ep and nvfp4 and not a.no_fold and cfg.shared_ff == cfg.expert_ff) if world > 1 else None
+                  shared_whole=ep and (nvfp4 or fp8) and not a.no_fold and cfg.shared_ff == cfg.expert_ff) if world > 1 else None
     t0 = time.time()
     weights = build_model(a, cfg, dev, pctx, shard, spec["weights"])
     load_s = time.time() - t0
@@ -261,6 +273,7 @@ def main(argv=None):
     model = Decoder(cfg, weights, pctx, max_position=ec.ctx_size + 8)
     model.fuse_gdn_in_proj()
     model.fuse_mla_in_proj()
+    model.absorb_mla_q()            # decode steps: no per-head absorb GEMM (the folded weight is three times q_b)
     head_split = (not a.no_head_split) and model.split_head()
     eng = LmEngine(model, tok, ec, start=False)
     graphs = eng._graphs

@@ -102,11 +102,11 @@ void wgemm(const Tensor& w, const Tensor& x, Tensor& out, const OptT& residual, 
 
 // Block-scaled FP8: w [rows, K] and x [tokens, K] hold e4m3 bytes; w_bscale [rows / 128, K / 128] and x_bscale
 // [tokens, K / 128] are fp32. Same tile / grouping / epilogue options as wgemm; out is bf16.
-void wgemm_fp8(const Tensor& w, const Tensor& w_bscale, const Tensor& x, const Tensor& x_bscale, Tensor& out,
-               const OptT& residual, const OptT& tok_scale, const OptT& out_rows, int64_t n_feat, bool dual,
-               int64_t dual_offset, int64_t bn, int64_t split_k, const OptT& ws, const OptT& counters, Tensor& status,
-               const OptT& tile_group, const OptT& tile_tok0, const OptT& tile_ntok, const OptT& meta, int64_t max_tiles,
-               int64_t rows_per_group, int64_t n_tok, const OptT& tile_out0) {
+void wgemm_fp8_q(const Tensor& w, const Tensor& w_bscale, const Tensor& x, const Tensor& x_bscale, Tensor& out,
+                 const OptT& residual, const OptT& tok_scale, const OptT& out_rows, int64_t n_feat, bool dual,
+                 int64_t dual_offset, int64_t bn, int64_t split_k, const OptT& ws, const OptT& counters, Tensor& status,
+                 const OptT& tile_group, const OptT& tile_tok0, const OptT& tile_ntok, const OptT& meta, int64_t max_tiles,
+                 int64_t rows_per_group, int64_t n_tok, const OptT& tile_out0, const OptT& q_out, const OptT& q_scale) {
   TORCH_CHECK(w.is_cuda() && x.is_cuda() && w.element_size() == 1 && x.element_size() == 1 && w.dim() == 2 &&
                   x.dim() == 2 && w.stride(1) == 1 && x.stride(1) == 1 && w.size(1) == x.size(1),
               "wgemm_fp8: w [rows, K] and x [tokens, K] must be 1-byte e4m3 tensors with the same K");
@@ -149,7 +149,27 @@ void wgemm_fp8(const Tensor& w, const Tensor& w_bscale, const Tensor& x, const T
     TORCH_CHECK(counters->numel() >= int64_t(n_tok_tiles) * feat_tiles, "wgemm_fp8: too few split-K counters");
   }
   h.status = reinterpret_cast<int*>(status.data_ptr());
+  if (q_out.has_value()) {
+    // the gate/up form leaves its activated rows e4m3-encoded for the down projection; `out` is not written
+    TORCH_CHECK(q_scale.has_value() && q_out->is_cuda() && q_out->element_size() == 1 && q_out->is_contiguous() &&
+                    q_out->dim() == 2 && q_out->size(1) == n_feat && q_out->size(0) >= out.size(0) &&
+                    q_scale->scalar_type() == at::kFloat && q_scale->is_contiguous() &&
+                    q_scale->numel() >= q_out->size(0) * (n_feat / 128),
+                "wgemm_fp8: encoded output [rows, n_feat] bytes with float scales [rows, n_feat / 128]");
+    h.q8_out = reinterpret_cast<uint8_t*>(q_out->data_ptr());
+    h.q8_scale = q_scale->data_ptr<float>();
+  }
   TORCH_CHECK(lb::wgemm_launch(h, cur_stream()) == 0, lb::wgemm_last_error());
+}
+
+void wgemm_fp8(const Tensor& w, const Tensor& w_bscale, const Tensor& x, const Tensor& x_bscale, Tensor& out,
+               const OptT& residual, const OptT& tok_scale, const OptT& out_rows, int64_t n_feat, bool dual,
+               int64_t dual_offset, int64_t bn, int64_t split_k, const OptT& ws, const OptT& counters, Tensor& status,
+               const OptT& tile_group, const OptT& tile_tok0, const OptT& tile_ntok, const OptT& meta, int64_t max_tiles,
+               int64_t rows_per_group, int64_t n_tok, const OptT& tile_out0) {
+  wgemm_fp8_q(w, w_bscale, x, x_bscale, out, residual, tok_scale, out_rows, n_feat, dual, dual_offset, bn, split_k, ws,
+              counters, status, tile_group, tile_tok0, tile_ntok, meta, max_tiles, rows_per_group, n_tok, tile_out0,
+              c10::nullopt, c10::nullopt);
 }
 
 // Dense GEMM whose kernel tail all-reduces the output over the ranks' symmetric buffers (+ residual, + RMSNorm).
@@ -569,6 +589,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         pybind11::arg("w_scales") = pybind11::none(), pybind11::arg("w_gscale") = pybind11::none(),
         pybind11::arg("x_group_col") = 0, pybind11::arg("k_override") = 0);
   m.def("wgemm_fp8", &wgemm_fp8);
+  m.def("wgemm_fp8_q", &wgemm_fp8_q);
   m.def("wgemm_allreduce", &wgemm_allreduce);
   m.def("wgemm_allgather", &wgemm_allgather);
   m.def("rmsnorm", &rmsnorm);

@@ -25,6 +25,7 @@
 #include "comm_dev.cuh"
 #include "common.cuh"
 #include "gemm_sm100.h"
+#include "nvfp4_dev.cuh"
 #include "tmap.cuh"
 
 namespace lb {
@@ -589,6 +590,43 @@ wgemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CU
             asm volatile("bar.sync 2, 128;" ::: "memory");
             const int f8 = (etid & 15) * 8;          // first of 8 features handled by this thread
             const int feat8 = it.feat0 + f8;
+            if constexpr (WFP8 && DUAL) {
+              if (a.q8_out) {
+                // Encoded write-out: the 16 lanes that hold one token's 128 features of this tile own exactly one
+                // scale group of the next FP8 GEMM: largest magnitude over the half-warp, then 8 e4m3 bytes per lane.
+                // Values are rounded to bf16 first, so the bytes are those the activation encoder makes of bf16 rows.
+#pragma unroll
+                for (int pass = 0; pass < 4; ++pass) {
+                  const int j = pass * 8 + (etid >> 4);
+                  const int t = c + j;
+                  const float4 v0 = *reinterpret_cast<const float4*>(&stage[j * BM + f8]);
+                  const float4 v1 = *reinterpret_cast<const float4*>(&stage[j * BM + f8 + 4]);
+                  float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                  float amax = 0.f;
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) {
+                    v[e] = __bfloat162float(__float2bfloat16(v[e]));
+                    amax = fmaxf(amax, fabsf(v[e]));
+                  }
+#pragma unroll
+                  for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                  const float sc = amax > 0.f ? amax / 448.f : 1.f;
+                  const float inv = 1.f / sc;
+                  if (t < it.ntok) {
+                    const long orow = it.out0 + t;
+                    uint2 o;
+                    o.x = e4m3_enc(v[0] * inv) | (e4m3_enc(v[1] * inv) << 8) | (e4m3_enc(v[2] * inv) << 16) |
+                          (e4m3_enc(v[3] * inv) << 24);
+                    o.y = e4m3_enc(v[4] * inv) | (e4m3_enc(v[5] * inv) << 8) | (e4m3_enc(v[6] * inv) << 16) |
+                          (e4m3_enc(v[7] * inv) << 24);
+                    *reinterpret_cast<uint2*>(a.q8_out + orow * a.n_feat + feat8) = o;
+                    if ((etid & 15) == 0) a.q8_scale[orow * (a.n_feat >> 7) + (it.feat0 >> 7)] = sc;
+                  }
+                }
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+                continue;
+              }
+            }
 #pragma unroll
             for (int pass = 0; pass < 4; ++pass) {
               const int j = pass * 8 + (etid >> 4);
@@ -825,6 +863,12 @@ int wgemm_launch(const WgemmHost& h, cudaStream_t stream) {
   a.head = h.head;
   a.w_gscale = h.w_gscale;
   a.w_bscale = h.w_bscale; a.x_bscale = h.x_bscale;
+  a.q8_out = h.q8_out; a.q8_scale = h.q8_scale;
+  if (h.q8_out && (!fp8 || !h.dual || !h.q8_scale || h.n_feat % 128 != 0 || h.out_f32 || h.out_rows || h.residual ||
+                   h.tok_scale || h.n_out_peer > 0 || (reinterpret_cast<uintptr_t>(h.q8_out) & 7))) {
+    snprintf(g_gemm_err, sizeof(g_gemm_err), "wgemm: the encoded output needs the FP8 gate/up form, n_feat %% 128 == 0, plain rows");
+    return 1;
+  }
   a.tile_group = h.tile_group; a.tile_tok0 = h.tile_tok0; a.tile_out0 = h.tile_out0; a.tile_ntok = h.tile_ntok; a.n_tiles_dev = h.n_tiles_dev;
   a.n_tok_tiles_max = h.n_tok_tiles_max;
   a.rows_per_group = h.rows_per_group; a.dual_offset = h.dual_offset;
@@ -841,6 +885,7 @@ int wgemm_launch(const WgemmHost& h, cudaStream_t stream) {
   a.vec_ok = (!h.out_f32 && h.n_feat % 8 == 0 && h.ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(h.out) & 15) == 0 &&
               (!h.residual || (h.ldr % 8 == 0 && (reinterpret_cast<uintptr_t>(h.residual) & 15) == 0)))
                  ? 1 : 0;
+  if (h.q8_out) a.vec_ok = 1;     // the encoded rows always leave through the staged write-out
   const int num_kb = fp8 ? h.K / 128 : (h.K + BK - 1) / BK;
   if (a.split_k > num_kb) a.split_k = num_kb;
   while (a.split_k > 1 && (a.split_k - 1) * ((num_kb + a.split_k - 1) / a.split_k) >= num_kb) --a.split_k;

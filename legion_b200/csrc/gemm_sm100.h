@@ -72,6 +72,8 @@ struct WgemmArgs {
   const float* w_gscale;          // NVFP4 weights: per-group (x2 for DUAL: gate, up) tensor scale, applied in the epilogue
   const float* w_bscale;          // FP8 weights: fp32 scale per 128 x 128 block, [w_rows / 128, K / 128]
   const float* x_bscale;          // FP8 activations: fp32 scale per row and 128 columns, [x_rows, K / 128]
+  uint8_t* q8_out;                // FP8 DUAL: the SwiGLU rows leave e4m3-encoded for the next FP8 GEMM, [rows, n_feat]
+  float* q8_scale;                //   with one fp32 scale per row and 128 features, [rows, n_feat / 128]; no bf16 output
 };
 
 // Host-side description of one launch.
@@ -100,6 +102,10 @@ struct WgemmHost {
   // w_bscale the fp32 weight scales per 128 x 128 block, x_bscale the fp32 activation scales per row and 128 columns
   const float* w_bscale;
   const float* x_bscale;
+  // FP8 DUAL only, optional: write the activated rows as e4m3 [rows, n_feat] + scales [rows, n_feat / 128] (what the
+  // activation encoder would make of the bf16 rows) instead of the bf16 output
+  uint8_t* q8_out;
+  float* q8_scale;
 };
 
 int wgemm_launch(const WgemmHost& h, cudaStream_t stream);

@@ -221,6 +221,38 @@ def quantize_moe_layer_nvfp4(w: Dict[str, object], p: str, native: bool = True) 
     return saved
 
 
+def quantize_moe_layer_fp8(w: Dict[str, object], p: str) -> int:
+    """Block-scaled FP8 encoding of the expert tensors of MoE layer ``p`` in place (the stacked form when the shared
+    expert was folded in, else the routed experts and the shared expert separately). Returns the bytes saved."""
+    from ..ops.sm100 import Fp8Weight
+    saved = 0
+
+    def ok(t, dual):
+        return (isinstance(t, torch.Tensor) and t.dtype == torch.bfloat16 and t.is_cuda and t.shape[-1] % 128 == 0
+                and t.shape[-2] % 128 == 0 and (not dual or (t.shape[-2] // 2) % 128 == 0))
+
+    if f"{p}.moe.gate_up_s" in w:
+        gus, dns = w[f"{p}.moe.gate_up_s"], w[f"{p}.moe.down_s"]
+        if not ok(gus, True) or not ok(dns, False):
+            return 0
+        E = gus.shape[0] - 1
+        for k in ("gate_up", "down", "sh_gate_up", "sh_down"):
+            w[f"{p}.moe.{k}"] = None                 # views of the bf16 stacks
+        saved = gus.numel() + dns.numel()
+        qg, qd = Fp8Weight.quantize(gus), Fp8Weight.quantize(dns)
+        w[f"{p}.moe.gate_up_s"], w[f"{p}.moe.down_s"] = qg, qd
+        w[f"{p}.moe.gate_up"], w[f"{p}.moe.down"] = qg.narrow(0, E), qd.narrow(0, E)
+        w[f"{p}.moe.sh_gate_up"] = qg.narrow(E, E + 1).squeeze0()
+        w[f"{p}.moe.sh_down"] = qd.narrow(E, E + 1).squeeze0()
+        return saved
+    for k, dual in (("gate_up", True), ("down", False), ("sh_gate_up", True), ("sh_down", False)):
+        t = w.get(f"{p}.moe.{k}")
+        if ok(t, dual):
+            w[f"{p}.moe.{k}"] = Fp8Weight.quantize(t)
+            saved += t.numel()
+    return saved
+
+
 class Decoder:
     """Weights + forward. ``weights`` uses the canonical names of ``models.weights``."""
 
@@ -402,6 +434,29 @@ class Decoder:
             n += 1
         return n
 
+    def absorb_mla_q(self) -> int:
+        """Folds the key up-projection of every latent-attention layer into its query projection for decode-sized
+        steps: ``mla.q_b_abs`` [heads * (kv_lora + rope), q_lora] maps the normalised low-rank query straight to
+        the absorbed query rows the attention kernel reads ([q_nope W_uk | q_pe] per head), so a decode step needs
+        no per-head absorb GEMM. The folded weight is (kv_lora + rope) / (nope + rope) times the size of ``q_b``
+        and costs that much more arithmetic, so prompt-sized steps keep the two-step form. Returns the number of
+        layers folded (bf16 weights with a low-rank query only)."""
+        cfg, n = self.cfg, 0
+        L, dn, dr, dvh = cfg.kv_lora, cfg.qk_nope_dim, cfg.qk_rope_dim, cfg.v_head_dim
+        for il, kind in enumerate(cfg.layer_kinds):
+            p = f"l{il}"
+            qb, kvb = self.w.get(f"{p}.mla.q_b"), self.w.get(f"{p}.mla.kv_b")
+            if kind != "mla" or cfg.q_lora <= 0 or f"{p}.mla.q_b_abs" in self.w or not isinstance(qb, torch.Tensor) \
+                    or not isinstance(kvb, torch.Tensor) or qb.dtype != torch.bfloat16 or not qb.is_cuda:
+                continue
+            nh = qb.shape[0] // (dn + dr)
+            qb3 = qb.view(nh, dn + dr, cfg.q_lora)
+            w_uk = kvb.view(nh, dn + dvh, L)[:, :dn]                                    # [heads, nope, kv_lora]
+            nope = torch.bmm(w_uk.transpose(1, 2).float(), qb3[:, :dn].float())        # [heads, kv_lora, q_lora]
+            self.w[f"{p}.mla.q_b_abs"] = torch.cat([nope.to(qb.dtype), qb3[:, dn:]], 1).reshape(nh * (L + dr), cfg.q_lora)
+            n += 1
+        return n
+
     def _mla(self, p: str, il: int, x, b: StepBatch, kv: KvCache):
         """Latent attention: cache row = [rmsnorm(c_kv) | rope(k_pe)]; keys/values are expanded from
         the cached latents of each sequence (prefill form), queries carry [nope | rope] parts."""
@@ -417,6 +472,16 @@ class Decoder:
             else:
                 qa = ops.linear(x, w[f"{p}.mla.q_a"])
             qa, _ = ops.rmsnorm(qa, w[f"{p}.mla.q_a_norm"], cfg.rms_eps, cfg.norm_offset)
+            qb_abs = w.get(f"{p}.mla.q_b_abs")
+            if (qb_abs is not None and T <= 64 and x.is_cuda and x.dtype == torch.bfloat16
+                    and ops.sm100.mla_supported(nh, L, dr, kv.page)):
+                # decode-sized step: one GEMM gives the absorbed query rows; their rope part is rotated in place
+                q_abs = ops.linear(qa, qb_abs).view(T, nh, L + dr)
+                if kva is None:
+                    kva = ops.linear(x, w[f"{p}.mla.kv_a"])
+                ops.sm100.mla_prep(kva, w[f"{p}.mla.kv_a_norm"], cfg.rms_eps, cfg.norm_offset, q_abs, L, self.cos_sin,
+                                   b.positions, b.slots, kv.k[il], q_abs)
+                return self._mla_tail(p, il, q_abs, b, kv, True)
             q = ops.linear(qa, w[f"{p}.mla.q_b"])
         else:
             q = ops.linear(x, w[f"{p}.mla.q"])
@@ -424,7 +489,6 @@ class Decoder:
         if kva is None:
             kva = ops.linear(x, w[f"{p}.mla.kv_a"])
         wkv_b = w[f"{p}.mla.kv_b"].view(nh, dn + dvh, L)
-        scale = cfg.attn_scale or (dn + dr) ** -0.5
         if x.is_cuda and x.dtype == torch.bfloat16 and ops.sm100.mla_supported(nh, L, dr, kv.page):
             # absorbed form on the tensor cores: q_abs = [q_nope W_uk | rope(q_pe)], o = (softmax . c_kv) W_uv
             q_abs = torch.empty(T, nh, L + dr, dtype=x.dtype, device=x.device)
@@ -442,15 +506,34 @@ class Decoder:
                 q_abs[..., :L] = torch.bmm(q[..., :dn].transpose(0, 1), wkv_b[:, :dn]).transpose(0, 1)
             ops.sm100.mla_prep(kva, w[f"{p}.mla.kv_a_norm"], cfg.rms_eps, cfg.norm_offset, q, dn, self.cos_sin,
                                b.positions, b.slots, kv.k[il], q_abs)
-            o_lat = ops.sm100.mla_attn(q_abs, kv.k[il], b.cu_q, b.ctx_lens, b.block_table, kv.page, b.max_q_len,
-                                       scale, max_ctx=b.max_ctx or None)
-            if own:
-                out = torch.empty(T, nh * dvh, dtype=x.dtype, device=x.device)
-                w_uv = w[f"{p}.mla.kv_b"].view(nh * (dn + dvh), L)[dn:]                   # head h: rows h*(dn+dvh)..+dvh
-                ops.sm100.head_linear(o_lat.view(T, nh * L), w_uv, nh, dn + dvh, dvh, L, L, out.view(T * nh, dvh))
-            else:
-                out = torch.bmm(o_lat.transpose(0, 1), wkv_b[:, dn:].transpose(1, 2)).transpose(0, 1)
-            return ops.linear(out.reshape(T, nh * dvh), w[f"{p}.mla.o"])
+            return self._mla_tail(p, il, q_abs, b, kv, own)
+        return self._mla_reference(p, il, x, q, kva, b, kv)
+
+    def _mla_tail(self, p: str, il: int, q_abs, b: StepBatch, kv: KvCache, own: bool):
+        """Latent attention over the absorbed query rows, the per-head value projection and the output projection."""
+        cfg, w = self.cfg, self.w
+        T, nh = q_abs.shape[0], q_abs.shape[1]
+        L, dn, dvh = cfg.kv_lora, cfg.qk_nope_dim, cfg.v_head_dim
+        scale = cfg.attn_scale or (dn + cfg.qk_rope_dim) ** -0.5
+        o_lat = ops.sm100.mla_attn(q_abs, kv.k[il], b.cu_q, b.ctx_lens, b.block_table, kv.page, b.max_q_len, scale,
+                                   max_ctx=b.max_ctx or None)
+        if own and isinstance(w[f"{p}.mla.kv_b"], torch.Tensor) and dvh % 8 == 0 and ops.sm100.TUNE["mla_head_gemm"]:
+            out = torch.empty(T, nh * dvh, dtype=q_abs.dtype, device=q_abs.device)
+            w_uv = w[f"{p}.mla.kv_b"].view(nh * (dn + dvh), L)[dn:]                       # head h: rows h*(dn+dvh)..+dvh
+            ops.sm100.head_linear(o_lat.view(T, nh * L), w_uv, nh, dn + dvh, dvh, L, L, out.view(T * nh, dvh))
+        else:
+            wkv_b = w[f"{p}.mla.kv_b"].view(nh, dn + dvh, L)
+            out = torch.bmm(o_lat.transpose(0, 1), wkv_b[:, dn:].transpose(1, 2)).transpose(0, 1)
+        return ops.linear(out.reshape(T, nh * dvh), w[f"{p}.mla.o"])
+
+    def _mla_reference(self, p: str, il: int, x, q, kva, b: StepBatch, kv: KvCache):
+        """Latent attention in plain tensor operations (CPU ranks, shapes the kernels do not take)."""
+        cfg, w = self.cfg, self.w
+        nh = self.n_head_l
+        dn, dr, dvh, L = cfg.qk_nope_dim, cfg.qk_rope_dim, cfg.v_head_dim, cfg.kv_lora
+        T = x.shape[0]
+        wkv_b = w[f"{p}.mla.kv_b"].view(nh, dn + dvh, L)
+        scale = cfg.attn_scale or (dn + dr) ** -0.5
         ckv, _ = ops.rmsnorm(kva[:, :L].contiguous(), w[f"{p}.mla.kv_a_norm"], cfg.rms_eps, cfg.norm_offset)
         k_pe = ops.reference.apply_rope(kva[:, L:].reshape(T, 1, dr), self.cos_sin, b.positions, dr)
         q_pe = ops.reference.apply_rope(q[..., dn:], self.cos_sin, b.positions, dr)

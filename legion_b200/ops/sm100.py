@@ -106,7 +106,7 @@ def have_ext() -> bool:
 NUM_SMS = 148
 
 # tuning knobs (environment: LB_TUNE="decode_fixed_tiles=2,dense_route=1")
-TUNE = {"decode_lanes": 2, "nv4_sorted": 1, "nv4_sorted_bn": 64, "gdn_chunk": 1, "decode_fixed_tiles": 2, "fused_plan": 1, "fused_router": 1, "dense_route": 1, "pdl": 1, "route_norm": 0, "mla_head_gemm": 1}
+TUNE = {"decode_lanes": 2, "nv4_sorted": 1, "fp8_fused_quant": 1, "nv4_sorted_bn": 64, "gdn_chunk": 1, "decode_fixed_tiles": 2, "fused_plan": 1, "fused_router": 1, "dense_route": 1, "pdl": 1, "route_norm": 0, "mla_head_gemm": 1}
 for _kv in os.environ.get("LB_TUNE", "").split(","):
     if "=" in _kv:
         TUNE[_kv.split("=")[0].strip()] = int(_kv.split("=")[1])
@@ -811,6 +811,7 @@ class DenseRoute:
         self.meta = torch.zeros(2, **i32)
         self.out_rows = torch.full((n_slots * self.stride,), -1, **i32)
         self.tok_scale = torch.zeros(n_slots * self.stride, dtype=torch.float32, device=device)
+        self.h8 = self.h8_scale = None               # FP8 experts: the activated rows, encoded by the gate/up GEMM
         self.sh_logit = torch.zeros(4 * 64, dtype=torch.float32, device=device)   # one plane per column split
         self.active = torch.zeros(n_slots, **i32)      # per local expert: chosen by some token of the step
         self.h_all = None
@@ -1068,7 +1069,7 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[Moe
     ws = Workspace.get(x.device)
     if isinstance(w_gate_up, Fp8Weight):
         return _moe_experts_fp8(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, shared, shared_gate, residual, out, norm,
-                                routing)
+                                routing, defer=defer_combine)
     if isinstance(w_gate_up, Nv4Weight):
         if _dense_ok(routing, E_local, e_lo, ids):
             return _moe_experts_nv4(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, shared, shared_gate, residual, out,
@@ -1152,7 +1153,8 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo=0, plan: Optional[Moe
     return out, normed
 
 
-def _moe_experts_fp8(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, shared, shared_gate, residual, out, norm, routing):
+def _moe_experts_fp8(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, shared, shared_gate, residual, out, norm, routing,
+                     defer: bool = False):
     """Routed experts with block-scaled FP8 weights: the same two grouped GEMMs in FP8 mode; activations (the
     layer input and the SwiGLU output) are quantised per row and 128 columns before each of them."""
     C = ext()
@@ -1171,12 +1173,23 @@ def _moe_experts_fp8(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, shared, shared_
             dr.h_all = torch.zeros(dr.n_slots * dr.stride, n_ff, dtype=torch.bfloat16, device=x.device)
         y_pairs = _dense_pairs(dr, P, T, k, H, x.device)
         x8, xs = _fp8_parts(routing.xq) if isinstance(routing.xq, Fp8Act) else fp8_quant_act(x)
-        C.wgemm_fp8(gu2, gu_s, x8, xs, dr.h_all, None, None, None, n_ff, True, n_ff, dr.bn, 1, None, None, ws.status,
-                    dr.tile_group, dr.zeros, dr.tile_ntok, dr.meta, dr.n_slots, 2 * n_ff, 0, dr.slot_base)
-        h8, hs = fp8_quant_act(dr.h_all)
+        if TUNE["fp8_fused_quant"] and n_ff % 128 == 0:
+            # the gate/up epilogue encodes the activated rows itself (rows past a slot's tokens stay zero bytes)
+            if dr.h8 is None or dr.h8.shape[1] != n_ff:
+                dr.h8 = torch.zeros(dr.n_slots * dr.stride, n_ff, dtype=torch.uint8, device=x.device)
+                dr.h8_scale = torch.ones(dr.n_slots * dr.stride, n_ff // 128, dtype=torch.float32, device=x.device)
+            h8, hs = dr.h8, dr.h8_scale
+            C.wgemm_fp8_q(gu2, gu_s, x8, xs, dr.h_all, None, None, None, n_ff, True, n_ff, dr.bn, 1, None, None,
+                          ws.status, dr.tile_group, dr.zeros, dr.tile_ntok, dr.meta, dr.n_slots, 2 * n_ff, 0,
+                          dr.slot_base, h8, hs)
+        else:
+            C.wgemm_fp8(gu2, gu_s, x8, xs, dr.h_all, None, None, None, n_ff, True, n_ff, dr.bn, 1, None, None,
+                        ws.status, dr.tile_group, dr.zeros, dr.tile_ntok, dr.meta, dr.n_slots, 2 * n_ff, 0, dr.slot_base)
+            h8, hs = fp8_quant_act(dr.h_all)
         C.wgemm_fp8(dn2, dn_s, h8, hs, y_pairs, None, dr.tok_scale, dr.out_rows, H, False, 0, dr.bn, 1, None, None,
                     ws.status, dr.tile_group, dr.slot_base, dr.tile_ntok, dr.meta, dr.n_slots, H, 0, None)
-        return _dense_combine(dr, routing, ids, e_lo, T, k, H, shared, shared_gate, residual, out, norm, x.device)
+        return _dense_combine(dr, routing, ids, e_lo, T, k, H, shared, shared_gate, residual, out, norm, x.device,
+                              defer=defer)
     if True:
         bn = 32 if P <= 32 * E_local else 64
         key = ("moe_plan", T, k, E_local, bn, H, n_ff)

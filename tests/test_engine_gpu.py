@@ -153,11 +153,11 @@ def test_latent_attention_stacked_input_projection_and_shared_fp8_rows():
     ec = dict(ctx_size=512, max_seqs=4, block_size=64, prefill_chunk=256, prefix_cache=False)
     prompt = torch.randint(0, 255, (150,), generator=torch.Generator().manual_seed(5)).tolist()
 
-    def first_logits(eng):
-        seq = eng.prepare(GenerateRequest(prompt_tokens=prompt, sampling=SamplingParams(max_tokens=4, ignore_eos=True)))
+    def first_logits(eng, toks=prompt):
+        seq = eng.prepare(GenerateRequest(prompt_tokens=toks, sampling=SamplingParams(max_tokens=4, ignore_eos=True)))
         eng.waiting.push(seq)
         eng._admit()
-        b = eng.build_batch([(seq, 0, len(prompt))])
+        b = eng.build_batch([(seq, 0, len(toks))])
         return eng.model.forward(b, eng.kv, eng.states).logits.float().cpu()
 
     plain = build_engine(cfg, weights=dict(w), device="cuda", engine_cfg=EngineConfig(**ec), start=False)
@@ -165,8 +165,13 @@ def test_latent_attention_stacked_input_projection_and_shared_fp8_rows():
     assert fused.model.fuse_mla_in_proj() == cfg.n_layer
     a, b = first_logits(plain), first_logits(fused)
     assert (a - b).abs().max().item() <= 0.02 * a.abs().max().item() + 1e-3
+    # the key up-projection folded into the query projection (steps of at most 64 rows): same logits up to rounding
+    assert fused.model.absorb_mla_q() == cfg.n_layer
+    a, b = first_logits(plain, prompt[:40]), first_logits(fused, prompt[:40])
+    assert (a - b).abs().max().item() <= 0.03 * a.abs().max().item() + 1e-3
     eng = build_engine(cfg, weights=dict(w), device="cuda", engine_cfg=EngineConfig(**ec))
     eng.model.fuse_mla_in_proj()
+    eng.model.absorb_mla_q()
     assert eng.model.quantize_weights_fp8(ffn_only=True) > 0
     assert isinstance(eng.model.w["l1.moe.sh_gate_up"], Fp8Weight) and isinstance(eng.model.w["l1.mla.q_b"], torch.Tensor)
     r1 = eng.generate_text(tokens=prompt, max_tokens=12, ignore_eos=True)
