@@ -90,6 +90,10 @@ def _add_engine_args(ap: argparse.ArgumentParser):
     g.add_argument("--expert-dir", default=None, help="--experts ssd: directory of the per-layer expert files")
     g.add_argument("--expert-ram-gib", type=float, default=8.0,
                    help="--experts ssd: host memory for recently used experts between the files and the HBM slots")
+    g.add_argument("--mmproj", default=None, help="vision tower: a clip mmproj GGUF (qwen3vl_merger projector)")
+    g.add_argument("--no-mmproj", action="store_true", help="do not load the vision tower a checkpoint directory ships")
+    g.add_argument("--image-max-tokens", type=int, default=0, help="most rows one image may take (0 = the tower's limit)")
+    g.add_argument("--image-cache-mib", type=int, default=256, help="encoded image rows kept by image hash")
     g.add_argument("--numa", choices=["auto", "off"], default="auto",
                    help="auto: restrict each rank's host threads to the CPUs of its GPU's NUMA node")
     g.add_argument("--load-threads", type=int, default=8,
@@ -215,6 +219,7 @@ def build_engine_from_args(a, start: bool = True):
         else:
             model.offload_experts(max(slots, cfg.top_k))
     eng = LmEngine(model, tok, ec, start=start)
+    _attach_vision(a, eng, path, device)
     logging.getLogger("legion").info("loaded %s: %s, %d layers, %.2fB parameters on %s", path, cfg.arch, cfg.n_layer,
                                      sum((t.numel() if isinstance(t, torch.Tensor) else t.codes.numel() * 2 if hasattr(t, "codes")
                                           else t.data.numel()) for t in w.values() if t is not None) / 1e9, device)
@@ -222,6 +227,28 @@ def build_engine_from_args(a, start: bool = True):
         from ..engine.replicas import ReplicaEngine
         return ReplicaEngine([eng] + [LmEngine(model, tok, ec) for _ in range(a.tp_replicas - 1)])
     return eng
+
+
+def _attach_vision(a, eng, path: str, device) -> None:
+    """``--mmproj FILE`` (a ``clip`` mmproj GGUF) or the tower a Hugging Face checkpoint directory ships."""
+    from ..vision import VisionRuntime
+    mm = getattr(a, "mmproj", None)
+    dt = torch.bfloat16 if str(device).startswith("cuda") else torch.float32
+    got = None
+    if mm:
+        from ..loaders.vision import load_mmproj
+        got = load_mmproj(mm, device, dt)
+    elif os.path.isdir(path) and os.path.exists(os.path.join(path, "config.json")) and not getattr(a, "no_mmproj", False):
+        from ..loaders.vision import load_vision_hf
+        got = load_vision_hf(path, device, dt)
+    if got is None:
+        return
+    tower, hp = got
+    if getattr(a, "image_max_tokens", 0):
+        hp.image_max_pixels = hp.factor * hp.factor * int(a.image_max_tokens)
+    eng.attach_vision(VisionRuntime(tower, hp, cache_bytes=int(getattr(a, "image_cache_mib", 256)) << 20))
+    logging.getLogger("legion").info("vision tower: %d blocks of width %d, up to %d tokens per image", tower.cfg.depth,
+                                     tower.cfg.hidden, hp.max_image_tokens())
 
 
 def sampling_defaults(a) -> dict:
@@ -277,8 +304,13 @@ def cmd_run(a):
     eng = build_engine_from_args(a)
     sp = SamplingParams(temperature=a.temp if a.temp is not None else 0.0, top_p=a.top_p or 1.0, top_k=a.top_k or 0,
                         min_p=a.min_p or 0.0, max_tokens=a.n_predict, ignore_eos=a.ignore_eos, seed=a.seed)
-    if a.chat:
-        req = GenerateRequest(messages=[ChatMessage("user", a.prompt)], sampling=sp)
+    images = []
+    for fn in getattr(a, "image", None) or []:
+        with open(fn, "rb") as f:
+            images.append(f.read())
+    if a.chat or images:
+        content = a.prompt if not images else [{"type": "image"} for _ in images] + [{"type": "text", "text": a.prompt}]
+        req = GenerateRequest(messages=[ChatMessage("user", content)], sampling=sp, images=images)
     else:
         req = GenerateRequest(prompt=a.prompt, sampling=sp)
     t0 = time.time()
@@ -511,6 +543,7 @@ def make_parser() -> argparse.ArgumentParser:
     s.add_argument("--prompt", "-p", required=True)
     s.add_argument("--n-predict", "-n", type=int, default=128)
     s.add_argument("--chat", action="store_true", help="wrap the prompt in the chat template")
+    s.add_argument("--image", action="append", help="image file shown before the prompt (repeatable; needs a vision tower)")
     s.add_argument("--ignore-eos", action="store_true")
     s.set_defaults(fn=cmd_run)
     s = sub.add_parser("chat", help="terminal chat against a running server")

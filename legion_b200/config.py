@@ -29,6 +29,8 @@ class ModelConfig:
     rope_theta: float = 1e6
     rope_dim: Optional[int] = None     # rotary dims per head (None = head_dim); multiple of 64
     rope_scaling: Optional[dict] = None
+    mrope_sections: Optional[tuple] = None     # multi-section rotary embedding: frequencies per (temporal, row, column) axis
+    mrope_interleaved: bool = True             # axes alternate over the frequencies (Qwen3-VL) or take consecutive sections
     qk_norm: bool = True
     gated_attn: bool = False           # q projection emits [q | gate] per head, out *= sigmoid(gate)
     sliding_window: int = 0            # window of "swa" layers

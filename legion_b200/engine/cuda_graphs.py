@@ -202,6 +202,13 @@ class DecodeGraphs:
             native.pack_decode(e.pack_np, B, e.W, pool.block_size, self.pad_slot,
                                [s.tokens[-1] for s, _, _ in rows], [p0 for _, p0, _ in rows],
                                [s.slot for s, _, _ in rows], [s.table.blocks for s, _, _ in rows])
+            if any(s.media is not None and s.media.rope_delta for s, _, _ in rows):
+                # sequences with images: rotary positions run behind the token index by a constant
+                off, _ = self._layout(B, e.W)
+                ps = e.pack_h[off["positions"][0]:off["positions"][0] + B]
+                for i, (s, p0, _) in enumerate(rows):
+                    if s.media is not None:
+                        ps[i] = s.rope_pos(p0)
             return self._replay(e, rows, n, B, gather)
         off, _ = self._layout(B, e.W)
         h = e.pack_h
@@ -218,7 +225,7 @@ class DecodeGraphs:
         sl[:n] = torch.tensor([s.table.blocks[p0 // bs] * bs + p0 % bs for s, p0, _ in rows], dtype=torch.int64)
         tk[:n] = torch.tensor([s.tokens[-1] for s, _, _ in rows], dtype=torch.int32)
         pt = torch.tensor(p0s, dtype=torch.int32)
-        ps[:n] = pt
+        ps[:n] = torch.tensor([s.rope_pos(p0) for s, p0, _ in rows], dtype=torch.int32)
         cl[:n] = pt + 1
         ss[:n] = torch.tensor([s.slot for s, _, _ in rows], dtype=torch.int32)
         for i, (s, p0, _) in enumerate(rows):

@@ -92,7 +92,7 @@ class Seq:
     __slots__ = ("req", "stream", "tokens", "n_prompt", "n_computed", "table", "slot", "sampler", "detok", "stop",
                  "reason", "tools", "phase", "arrival_ms", "admit_ms", "first_ms", "usage", "radix_handle", "drafts",
                  "save_points", "finished", "priority", "key", "n_out", "held_logprobs", "constraint", "resumed", "swapped",
-                 "orig_prompt", "last_hidden", "draft_state", "owner", "mask_ahead")
+                 "orig_prompt", "last_hidden", "draft_state", "owner", "mask_ahead", "media")
 
     def __init__(self, req: GenerateRequest, stream: TokenStream, tokens: List[int]):
         self.req, self.stream = req, stream
@@ -101,6 +101,7 @@ class Seq:
         self.orig_prompt = len(tokens)
         self.n_computed = 0
         self.swapped = None               # _Swapped: KV blocks + recurrent state parked in host memory
+        self.media = None                 # vision.SeqMedia: image rows, their spans and rotary positions
         self.table = BlockTable()
         self.slot = -1
         self.owner = -1                   # data-parallel attention: the rank that runs this sequence's attention
@@ -127,6 +128,15 @@ class Seq:
         self.stop = None
         self.reason = None
         self.tools = None
+
+    def key_tokens(self, n: Optional[int] = None) -> List[int]:
+        """The tokens as the prefix cache and the saved states key them: image tokens stand as ids derived from
+        their image's hash, so two images behind the same placeholder id never share a cache entry."""
+        t = self.tokens if n is None else self.tokens[:n]
+        return t if self.media is None else self.media.key_tokens(t)
+
+    def rope_pos(self, p: int) -> int:
+        return p if self.media is None else self.media.rope_position(p)
 
 
 class LmEngine(Engine):
@@ -181,6 +191,7 @@ class LmEngine(Engine):
         self._stop = threading.Event()
         self._thread: Optional[threading.Thread] = None
         self._fail: Optional[str] = None
+        self.vision = None                # vision.VisionRuntime once a tower is attached (``attach_vision``)
         self.drafter = drafter
         if self.drafter is None and c.spec != "none":
             from ..spec import make_drafter
@@ -305,6 +316,71 @@ class LmEngine(Engine):
             return self.tok.encode(text, add_special=True)
         return self.tok.encode(req.prompt or "", add_special=True)
 
+    def attach_vision(self, runtime) -> None:
+        """Gives the engine a vision tower (``vision.VisionRuntime``): requests may then carry images. The
+        placeholder and marker token ids are looked up in this engine's vocabulary."""
+        runtime.bind_tokenizer(self.tok)
+        if runtime.tower.cfg.out_hidden != self.mcfg.hidden:
+            raise ValueError(f"vision tower rows are {runtime.tower.cfg.out_hidden} wide, the model takes {self.mcfg.hidden}")
+        self.vision = runtime
+
+    def _media_inputs(self, b: StepBatch, rows, tok: List[int]) -> None:
+        """Steps that touch image tokens: the token embedding with the image rows in place, the extra rows of the
+        first layers, and per-token rotary rows when the model turns its frequencies with three position axes."""
+        dev = self.device
+        idx: List[int] = []          # rows of this step that are image tokens
+        src: List[Tuple[object, int]] = []
+        base = 0
+        need_table = False
+        for s, p0, n in rows:
+            m = s.media
+            if m is not None and s.phase != "decode" and p0 < m.n_prompt:
+                hi = min(p0 + n, m.n_prompt)
+                r = m.row_of_pos[p0:hi]
+                hit = (r >= 0).nonzero().flatten().tolist()
+                for j in hit:
+                    idx.append(base + j)
+                    src.append((m, int(r[j])))
+                need_table = need_table or (m.pos3 is not None and bool(hit))
+            base += n
+        if idx:
+            x = self.model.embed(b.token_ids)
+            groups = {}
+            for at, (m, r) in zip(idx, src):
+                groups.setdefault(id(m), (m, [], []))
+                groups[id(m)][1].append(at)
+                groups[id(m)][2].append(r)
+            n_deep = min(len(m.deepstack) for m, _, _ in groups.values())
+            deep = [torch.zeros(len(idx), x.shape[1], dtype=x.dtype, device=dev) for _ in range(n_deep)]
+            order = {at: i for i, at in enumerate(idx)}
+            for m, ats, rs in groups.values():
+                at_t = torch.tensor(ats, dtype=torch.int64, device=dev)
+                r_t = torch.tensor(rs, dtype=torch.int64, device=m.rows.device)
+                x[at_t] = m.rows[r_t].to(device=dev, dtype=x.dtype)
+                where = torch.tensor([order[a] for a in ats], dtype=torch.int64, device=dev)
+                for j in range(n_deep):
+                    deep[j][where] = m.deepstack[j][r_t].to(device=dev, dtype=x.dtype)
+            b.embeds = x
+            if n_deep:
+                b.deepstack_rows = torch.tensor(idx, dtype=torch.int64, device=dev)
+                b.deepstack = deep
+        if need_table:
+            pos3 = torch.zeros(3, len(tok), dtype=torch.int64)
+            base = 0
+            for s, p0, n in rows:
+                m = s.media
+                if m is not None and m.pos3 is not None:
+                    hi = max(p0, min(p0 + n, m.n_prompt))
+                    if hi > p0:
+                        pos3[:, base:base + hi - p0] = m.pos3[:, p0:hi]
+                    if p0 + n > hi:
+                        pos3[:, base + hi - p0:base + n] = torch.arange(hi, p0 + n) + m.rope_delta
+                else:
+                    pos3[:, base:base + n] = torch.arange(p0, p0 + n)
+                base += n
+            b.rope_table = self.model.mrope_table(pos3)
+            b.rope_rows = torch.arange(len(tok), dtype=torch.int32, device=dev)
+
     def count_tokens(self, req: GenerateRequest) -> int:
         return len(self.tokenize_request(req))
 
@@ -315,6 +391,12 @@ class LmEngine(Engine):
         if not tokens:
             tokens = [self.tok.bos_id if self.tok.bos_id is not None else 0]
         c = self.cfg
+        media = None
+        if req.images:
+            if self.vision is None:
+                raise ValueError("this model has no vision tower: images cannot be used (--mmproj)")
+            tokens, media = self.vision.attach(tokens, req.images, self.mcfg.hidden, self.mcfg.mrope_sections is not None,
+                                               self.device, self.model.embed_dtype())
         if len(tokens) + 1 > c.ctx_size:
             raise KvOverflow(f"prompt of {len(tokens)} tokens does not fit the context of {c.ctx_size}")
         sp = req.sampling
@@ -323,6 +405,7 @@ class LmEngine(Engine):
         if need > self.pool.total:
             raise KvOverflow(f"request needs {need} KV blocks, the cache has {self.pool.total}")
         seq = Seq(req, TokenStream(CancelToken()), tokens)
+        seq.media = media
         if req.response_format and req.response_format.get("type") not in (None, "text"):
             from ..grammar import compile_response_format
             seq.constraint = compile_response_format(req.response_format, self.tok)
@@ -532,7 +615,7 @@ class LmEngine(Engine):
     def _place(self, seq: Seq) -> bool:
         """Prefix match + state restore + KV reservation. Returns False when the KV cache is too full."""
         bs = self.cfg.block_size
-        prompt = seq.tokens
+        prompt = seq.key_tokens()
         limit = len(prompt) - 1           # at least one prompt token is always recomputed
         blocks: List[int] = []
         matched = 0
@@ -614,7 +697,7 @@ class LmEngine(Engine):
             seq.save_points = self.saved.save_points(seq.n_prompt, resume, self.cfg.prefix_cache_interval)
         sp = seq.req.sampling
         if seq.sampler is None:     # a preempted sequence keeps its sampler and text state
-            seq.sampler = Sampler(sp, prompt, fallback_seed=self.cfg.seed)
+            seq.sampler = Sampler(sp, seq.tokens, fallback_seed=self.cfg.seed)
             seq.detok = IncrementalDetokenizer(lambda ids: self.tok.decode(ids, skip_special=True))
             seq.stop = StopChecker(sp.stop)
             seq.reason = ReasoningSplitter() if self.cfg.reasoning else None
@@ -856,7 +939,10 @@ class LmEngine(Engine):
             else:
                 toks = s.tokens[p0:p0 + n]
             tok.extend(toks)
-            pos.extend(range(p0, p0 + n))
+            if s.media is None:
+                pos.extend(range(p0, p0 + n))
+            else:
+                pos.extend(s.rope_pos(p) for p in range(p0, p0 + n))
             slots.extend(s.table.slots(self.pool, p0, n))
             base = cu[-1]
             cu.append(base + n)
@@ -871,13 +957,16 @@ class LmEngine(Engine):
             nb = self.pool.blocks_for(p0 + n)
             bt[i, :nb] = torch.tensor(s.table.blocks[:nb], dtype=torch.int32)
         i32 = dict(dtype=torch.int32, device=dev)
-        return StepBatch(
+        b = StepBatch(
             token_ids=torch.tensor(tok, **i32), positions=torch.tensor(pos, **i32), cu_q=torch.tensor(cu, **i32),
             ctx_lens=torch.tensor(ctx, **i32), block_table=bt.to(dev),
             slots=torch.tensor(slots, dtype=torch.int64, device=dev),
             state_slots=torch.tensor([s.slot for s, _, _ in rows], **i32),
             logit_rows=torch.tensor(logit_rows, dtype=torch.int64, device=dev),
             max_q_len=max(n for _, _, n in rows), max_ctx=max(ctx), write_state=write_state, cu_q_host=cu)
+        if any(s.media is not None and s.phase != "decode" for s, _, _ in rows):
+            self._media_inputs(b, rows, tok)
+        return b
 
     def build_batch_explicit(self, items, all_logits: bool = False) -> StepBatch:
         """items = [(seq, first position, token list)]: a batch over the sequences' own block tables with
@@ -888,7 +977,7 @@ class LmEngine(Engine):
         for s, p0, toks in items:
             n = len(toks)
             tok.extend(toks)
-            pos.extend(range(p0, p0 + n))
+            pos.extend(range(p0, p0 + n) if s.media is None else (s.rope_pos(p) for p in range(p0, p0 + n)))
             slots.extend(s.table.slots(self.pool, p0, n))
             cu.append(cu[-1] + n)
             ctx.append(p0 + n)
@@ -1067,7 +1156,7 @@ class LmEngine(Engine):
                 # prompt done: cache its full blocks, sample the first token
                 if self.radix is not None:
                     self._own_blocks(s)
-                    self.radix.insert(s.tokens[:s.n_prompt], s.table.blocks)
+                    self.radix.insert(s.key_tokens(s.n_prompt), s.table.blocks)
                 row = logits_host[r] if logits_host is not None else None
                 tok, lp = self._pick(s, row, device_picks[r] if device_picks is not None else None)
                 r += 1
@@ -1258,7 +1347,7 @@ class LmEngine(Engine):
         self.states.copy(s.slot, slot)
         if tail_block is not None:
             self.pool.incref(tail_block)
-        self.saved.store(s.tokens, n_tokens, slot, kind, tail_block, on_replace=self._drop_tail_ref)
+        self.saved.store(s.key_tokens(), n_tokens, slot, kind, tail_block, on_replace=self._drop_tail_ref)
 
     def _drop_tail_ref(self, old):
         if old.tail_block is not None:
@@ -1298,7 +1387,7 @@ class LmEngine(Engine):
             n = s.n_computed
             if self.radix is not None:
                 self._own_blocks(s)
-                self.radix.insert(s.tokens[:n], s.table.blocks)
+                self.radix.insert(s.key_tokens(n), s.table.blocks)
             if self.saved is not None and n > 0:
                 bs = self.cfg.block_size
                 tail_block = s.table.blocks[n // bs] if n % bs and n // bs < len(s.table.blocks) else None

@@ -38,12 +38,19 @@ class Tokenizer:
     def special_token(self, name: str) -> Optional[str]:
         return None
 
+    def token_to_id(self, text: str) -> Optional[int]:
+        """Id of the single token ``text`` stands for (special tokens by name), or None."""
+        ids = self.encode(text, add_special=False, parse_special=True)
+        return ids[0] if len(ids) == 1 else None
+
 
 class ByteTokenizer(Tokenizer):
     """ids 0..255 are bytes; 256 = <bos>, 257 = <eos>, 258.. = <|im_start|>, <|im_end|>, <think>, </think>,
-    <tool_call>, </tool_call>; the rest of the vocabulary is unused filler."""
+    <tool_call>, </tool_call>, <|vision_start|>, <|image_pad|>, <|vision_end|>; the rest of the vocabulary is unused
+    filler."""
 
-    SPECIALS = ["<bos>", "<eos>", "<|im_start|>", "<|im_end|>", "<think>", "</think>", "<tool_call>", "</tool_call>"]
+    SPECIALS = ["<bos>", "<eos>", "<|im_start|>", "<|im_end|>", "<think>", "</think>", "<tool_call>", "</tool_call>",
+                "<|vision_start|>", "<|image_pad|>", "<|vision_end|>"]
 
     def __init__(self, vocab_size: int = 4096):
         self.vocab_size = vocab_size

@@ -50,6 +50,10 @@ class StepBatch:
     cu_q_host: Optional[List[int]] = None
     decode_splits: Optional[int] = None
     replay: Optional[dict] = None                # verify steps: per-layer recurrent inputs kept for commit
+    rope_table: Optional[torch.Tensor] = None    # [T, rot] per-token cos | sin rows (multi-section rotary positions of
+    rope_rows: Optional[torch.Tensor] = None     #   image tokens); rope_rows = arange(T) indexes it like positions
+    deepstack_rows: Optional[torch.Tensor] = None    # [R] int64 rows of this step that are image tokens, and per early
+    deepstack: Optional[List[torch.Tensor]] = None   #   layer the [R, hidden] rows added to the stream after it
 
     @property
     def n_seqs(self) -> int:
@@ -354,9 +358,10 @@ class Decoder:
         cfg, w = self.cfg, self.w
         D = cfg.head_dim
         qkv = ops.linear(x, w[f"{p}.attn.qkv"])
+        cos_sin, positions = (self.cos_sin, b.positions) if b.rope_table is None else (b.rope_table, b.rope_rows)
         q, gate = ops.qk_norm_rope_append(qkv, self.n_head_l, self.n_kv_l, D, w.get(f"{p}.attn.q_norm"),
-                                          w.get(f"{p}.attn.k_norm"), cfg.rms_eps, cfg.norm_offset, self.cos_sin,
-                                          cfg.rope_dim if rope else 0, b.positions, b.slots, kv.k[il], kv.v[il],
+                                          w.get(f"{p}.attn.k_norm"), cfg.rms_eps, cfg.norm_offset, cos_sin,
+                                          cfg.rope_dim if rope else 0, positions, b.slots, kv.k[il], kv.v[il],
                                           cfg.gated_attn)
         scale = cfg.attn_scale or D ** -0.5
         o = ops.paged_attention(q, kv.k[il], kv.v[il], b.block_table, b.ctx_lens, b.cu_q, b.max_q_len, scale,
@@ -723,6 +728,15 @@ class Decoder:
     def embed(self, token_ids):
         return ops.embed(token_ids, self.w["tok_embd"])
 
+    def embed_dtype(self):
+        """dtype of the rows ``embed`` gives (image rows are cast to it)."""
+        dt = getattr(self, "_embed_dtype", None)
+        if dt is None:
+            dev = self.cos_sin.device
+            dt = self.embed(torch.zeros(1, dtype=torch.int32, device=dev)).dtype
+            self._embed_dtype = dt
+        return dt
+
     def _forward_pipe(self, b: StepBatch, kv: KvCache, st: Optional[StatePool], want_logits: bool) -> StepOutput:
         """Pipeline-parallel forward: this rank's layers over the step's micro-chunks. The receive of micro-chunk
         c+1 is posted before c is computed and sends are asynchronous, so neighbouring stages overlap."""
@@ -785,6 +799,11 @@ class Decoder:
             nxt = w[f"l{il + 1}.attn_norm"] if il + 1 < cfg.n_layer else None
             cur, res, normed = self._layer(f"l{il}", il, cfg.layer_kinds[il], cfg.is_moe_layer(il), cur, res, b, kv,
                                            st, normed, nxt)
+            if b.deepstack is not None and il < len(b.deepstack):
+                # image tokens: the tower's extra rows for this depth join the residual stream
+                full = pc.full_hidden(cur, res)
+                full.index_add_(0, b.deepstack_rows, b.deepstack[il].to(full.dtype))
+                cur, res, normed = None, full, None
             if b.capture_layers and il in b.capture_layers:
                 captures[il] = pc.full_hidden(cur, res)
         last = pc.full_hidden(cur, res)
@@ -796,6 +815,21 @@ class Decoder:
         pc.end_step()
         _ = (resid, x_partial)
         return out
+
+    def mrope_table(self, pos3: torch.Tensor) -> torch.Tensor:
+        """[3, T] positions on the (temporal, row, column) axes -> [T, rot] cos | sin rows: frequency i turns with
+        the axis the model's section layout gives it (``vision.media.mrope_axis_of_freq``), so each row is a gather
+        from the ordinary table at that axis' position."""
+        from ..vision.media import mrope_axis_of_freq
+        half = self.cos_sin.shape[1] // 2
+        ax = getattr(self, "_mrope_axis", None)
+        if ax is None:
+            ax = mrope_axis_of_freq(half, self.cfg.mrope_sections, self.cfg.mrope_interleaved).to(self.cos_sin.device)
+            self._mrope_axis = ax
+        pos3 = pos3.to(self.cos_sin.device)
+        rows = pos3[ax].t()                                        # [T, half]: the position frequency i reads
+        cols = torch.arange(half, device=rows.device)
+        return torch.cat([self.cos_sin[rows, cols], self.cos_sin[rows, cols + half]], dim=1).contiguous()
 
     def split_head(self) -> bool:
         """Several ranks with the fused communicator: every rank keeps only its slice of the LM head's vocabulary

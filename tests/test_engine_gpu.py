@@ -423,3 +423,56 @@ def test_offloaded_experts_become_resident_on_the_device_and_decode_from_graphs(
     b.shutdown()
     assert got == want and replays > 0 and misses > 0
     assert sm100.Workspace.get("cuda").check() == 0
+
+
+def test_images_on_gpu_match_the_cpu_engine_and_decode_from_graphs():
+    """A prompt with an image on the GPU engine (tower in bf16 on the device, image rows spliced into the token
+    embedding, per-token rotary rows for the three position axes, extra rows after the first layer): first-step
+    logits close to the fp32 CPU engine's, and graph-replayed decode steps take the shifted rotary positions."""
+    import io
+    from PIL import Image
+    from legion_b200.engine.types import ChatMessage, GenerateRequest, SamplingParams
+    from legion_b200.vision import VisionConfig, VisionHparams, VisionRuntime, VisionTower, random_vision_weights
+    im = Image.new("RGB", (64, 48), (180, 40, 90))
+    for x in range(0, 64, 5):
+        im.putpixel((x, (x * 3) % 48), (x * 4 % 256, 200, 10))
+    buf = io.BytesIO()
+    im.save(buf, "PNG")
+    img = buf.getvalue()
+    cfg = ModelConfig(arch="qwen3", n_layer=3, hidden=256, vocab=1024, n_head=4, n_kv_head=2, head_dim=64, dense_ff=512,
+                      mrope_sections=(11, 11, 10))
+    w32 = {k: (v.bfloat16().float() if v.dim() > 1 else v)
+           for k, v in random_weights(cfg, "cpu", torch.float32, seed=3, std=0.05).items()}
+    wgpu = {k: (v.bfloat16() if v.dim() > 1 else v).cuda() for k, v in w32.items()}
+    vc = VisionConfig(depth=2, hidden=64, n_head=2, intermediate=96, out_hidden=256, patch_size=8, num_pos=16,
+                      deepstack_layers=(0,))
+    vw = {k: v.bfloat16().float() for k, v in random_vision_weights(vc, seed=5).items()}
+    hp = dict(patch_size=8, spatial_merge_size=2, min_tokens=2, max_tokens=64)
+    ec = dict(ctx_size=512, max_seqs=4, block_size=64, prefill_chunk=256)
+    msg = ChatMessage("user", [{"type": "image"}, {"type": "text", "text": "describe"}])
+    outs = []
+    engs = []
+    for dev, ww, vww in (("cpu", w32, vw), ("cuda", wgpu, {k: v.bfloat16().cuda() for k, v in vw.items()})):
+        eng = build_engine(cfg, weights=dict(ww), device=dev, engine_cfg=EngineConfig(**ec), start=False)
+        eng.attach_vision(VisionRuntime(VisionTower(vc, vww), VisionHparams(**hp)))
+        seq = eng.prepare(GenerateRequest(messages=[msg], images=[img], sampling=SamplingParams(max_tokens=4)))
+        eng.waiting.push(seq)
+        eng._admit()
+        b = eng.build_batch([(seq, 0, len(seq.tokens))])
+        assert b.embeds is not None and b.rope_table is not None and b.deepstack is not None
+        outs.append(eng.model.forward(b, eng.kv, eng.states).logits.float().cpu())
+        engs.append(eng)
+    err = (outs[0] - outs[1]).abs().max().item()
+    assert err < 0.1 * outs[0].abs().max().item() + 0.1, err
+    gpu = build_engine(cfg, weights=dict(wgpu), device="cuda", engine_cfg=EngineConfig(**ec))
+    gpu.attach_vision(VisionRuntime(VisionTower(vc, {k: v.bfloat16().cuda() for k, v in vw.items()}), VisionHparams(**hp)))
+    req = lambda: GenerateRequest(messages=[msg], images=[img], sampling=SamplingParams(max_tokens=10, ignore_eos=True))
+    r1 = gpu.generate(req()).collect()
+    r2 = gpu.generate(req()).collect()
+    plain = build_engine(cfg, weights=dict(wgpu), device="cuda", engine_cfg=EngineConfig(cuda_graphs=False, **ec))
+    plain.attach_vision(VisionRuntime(VisionTower(vc, {k: v.bfloat16().cuda() for k, v in vw.items()}), VisionHparams(**hp)))
+    r3 = plain.generate(req()).collect()
+    replays = gpu._graphs.replays
+    gpu.shutdown()
+    plain.shutdown()
+    assert r1.error is None and r1.token_ids == r2.token_ids == r3.token_ids and replays > 0

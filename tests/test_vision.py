@@ -1,0 +1,191 @@
+"""Images in prompts: preprocessing, the vision tower, image tokens in the engine (rows, rotary positions, prefix
+keys, row cache), mmproj round trip. CPU (fp32)."""
+import io
+
+import pytest
+import torch
+
+from legion_b200.config import ModelConfig
+from legion_b200.engine.lm import EngineConfig, build_engine
+from legion_b200.engine.types import ChatMessage, GenerateRequest, SamplingParams
+from legion_b200.models.weights import random_weights
+from legion_b200.vision import (VisionConfig, VisionHparams, VisionRuntime, VisionTower, decode_image, expand_image_tokens,
+                                mrope_positions, preprocess, random_vision_weights)
+from legion_b200.vision.media import mrope_axis_of_freq
+from legion_b200.vision.preprocess import VisionError, smart_size
+
+
+def png(w, h, color=(200, 30, 40), fmt="PNG"):
+    from PIL import Image
+    im = Image.new("RGB", (w, h), color)
+    for x in range(0, w, 7):                      # some structure, so that rows differ between patches
+        for y in range(0, h, 5):
+            im.putpixel((x, y), ((x * 3) % 256, (y * 5) % 256, (x + y) % 256))
+    buf = io.BytesIO()
+    im.save(buf, fmt)
+    return buf.getvalue()
+
+
+def test_smart_size_and_patches_in_merge_order():
+    hp = VisionHparams(patch_size=4, spatial_merge_size=2, temporal_patch_size=2, min_tokens=2, max_tokens=64)
+    h, w = smart_size(60, 100, 8, hp.image_min_pixels, hp.image_max_pixels)
+    assert h % 8 == 0 and w % 8 == 0 and hp.image_min_pixels <= h * w <= hp.image_max_pixels
+    with pytest.raises(VisionError):
+        smart_size(1, 1000, 8, 64, 4096)
+    img = decode_image(png(100, 60))
+    assert img.shape == (60, 100, 3) and img.dtype == torch.uint8
+    pre = preprocess(img, hp)
+    t, gh, gw = pre.grid
+    assert pre.patches.shape == (gh * gw, 3 * 2 * 4 * 4) and (gh * 4, gw * 4) == pre.size
+    # merge order: the first four patches are the 2 x 2 block in the top left corner; both frames of the temporal
+    # patch hold the same still image
+    hp2 = VisionHparams(patch_size=4, spatial_merge_size=2, temporal_patch_size=2, min_tokens=2, max_tokens=64,
+                        resize="stretch")
+    pre2 = preprocess(img, hp2)
+    p = pre2.patches.view(-1, 3, 2, 4, 4)
+    assert torch.equal(p[:, :, 0], p[:, :, 1])
+    full = torch.zeros(3, pre2.size[0], pre2.size[1])
+    from legion_b200.vision.tower import merge_order_coords
+    rr, cc = merge_order_coords(pre2.grid[1], pre2.grid[2], 2, "cpu")
+    assert (rr[:4].tolist(), cc[:4].tolist()) == ([0, 0, 1, 1], [0, 1, 0, 1])
+    for i in range(p.shape[0]):
+        full[:, rr[i] * 4:rr[i] * 4 + 4, cc[i] * 4:cc[i] * 4 + 4] = p[i, :, 0]
+    x = torch.nn.functional.interpolate(img.permute(2, 0, 1)[None].float() / 255, size=pre2.size, mode="bicubic",
+                                        align_corners=False, antialias=True)[0].clamp(0, 1)
+    assert torch.allclose(full, (x - 0.5) / 0.5, atol=1e-5)
+    with pytest.raises(VisionError):
+        decode_image(b"not an image")
+
+
+def test_tower_is_invariant_to_how_patches_are_grouped_and_respects_the_grid():
+    cfg = VisionConfig(depth=2, hidden=32, n_head=2, intermediate=48, out_hidden=24, patch_size=4, num_pos=16,
+                       deepstack_layers=(0,))
+    tower = VisionTower(cfg, random_vision_weights(cfg, seed=2))
+    hp = VisionHparams(patch_size=4, spatial_merge_size=2, min_tokens=2, max_tokens=64)
+    pre = preprocess(decode_image(png(48, 32)), hp)
+    e = tower.encode(pre.patches, pre.grid)
+    gh, gw = pre.grid[1] // 2, pre.grid[2] // 2
+    assert e.rows.shape == (gh * gw, 24) and e.grid == (1, gh, gw) and e.deepstack[0].shape == e.rows.shape
+    assert torch.isfinite(e.rows).all()
+    # attention is unmasked over the whole image and positions come from the grid: a different image changes every
+    # row; the same image gives the same rows
+    e2 = tower.encode(pre.patches, pre.grid)
+    assert torch.equal(e.rows, e2.rows)
+    other = preprocess(decode_image(png(48, 32, color=(10, 200, 90))), hp)
+    assert (tower.encode(other.patches, other.grid).rows - e.rows).abs().max() > 1e-4
+    with pytest.raises(ValueError):
+        tower.encode(pre.patches[:-1], pre.grid)
+    pool = VisionConfig(depth=1, hidden=32, n_head=2, intermediate=48, out_hidden=24, patch_size=4, num_pos=16,
+                        projector="pool", spatial_merge_size=2)
+    pt = VisionTower(pool, random_vision_weights(pool, seed=3))
+    assert pt.encode(pre.patches, pre.grid).rows.shape == (gh * gw, 24)
+
+
+def test_image_token_expansion_and_rotary_positions():
+    toks, spans = expand_image_tokens([1, 5, 9, 5, 9, 7], 9, [4, 2])
+    assert toks == [1, 5, 9, 9, 9, 9, 5, 9, 9, 7] and spans == [(2, 4), (7, 2)]
+    with pytest.raises(ValueError):
+        expand_image_tokens([1, 9, 2], 9, [4, 2])
+    toks2, spans2 = expand_image_tokens([1, 2, 3], 9, [2], start_token=20, end_token=21)
+    assert toks2 == [1, 20, 9, 9, 21, 2, 3] and spans2 == [(2, 2)]
+    pos, delta = mrope_positions(len(toks), spans, [(1, 2, 2), (1, 1, 2)])
+    assert pos[:, :2].tolist() == [[0, 1]] * 3
+    assert pos[0, 2:6].tolist() == [2, 2, 2, 2] and pos[1, 2:6].tolist() == [2, 2, 3, 3] and pos[2, 2:6].tolist() == [2, 3, 2, 3]
+    assert pos[:, 6].tolist() == [4, 4, 4]                      # text continues from start + max(rows, columns)
+    assert pos[:, 7:9].tolist() == [[5, 5], [5, 5], [5, 6]] and pos[:, 9].tolist() == [7, 7, 7]
+    assert delta == 8 - len(toks)
+    ax = mrope_axis_of_freq(32, (11, 11, 10), True)
+    assert ax[:6].tolist() == [0, 1, 2, 0, 1, 2] and int((ax == 1).sum()) == 11 and int((ax == 2).sum()) == 10
+    ax2 = mrope_axis_of_freq(32, (16, 8, 8), False)
+    assert ax2.tolist() == [0] * 16 + [1] * 8 + [2] * 8
+
+
+def _engine(mrope, deepstack=()):
+    cfg = ModelConfig(arch="qwen3", n_layer=3, hidden=64, vocab=512, n_head=4, n_kv_head=2, head_dim=64, dense_ff=128,
+                      mrope_sections=(11, 11, 10) if mrope else None)
+    w = random_weights(cfg, "cpu", torch.float32, seed=4, std=0.05)
+    eng = build_engine(cfg, weights=w, engine_cfg=EngineConfig(ctx_size=512, max_seqs=4, block_size=16, prefill_chunk=24,
+                                                               max_batch_tokens=64), start=True)
+    vc = VisionConfig(depth=2, hidden=32, n_head=2, intermediate=48, out_hidden=64, patch_size=4, num_pos=16,
+                      deepstack_layers=deepstack)
+    rt = VisionRuntime(VisionTower(vc, random_vision_weights(vc, seed=5)),
+                       VisionHparams(patch_size=4, spatial_merge_size=2, min_tokens=2, max_tokens=64))
+    eng.attach_vision(rt)
+    return eng, rt
+
+
+@pytest.mark.parametrize("mrope,deep", [(False, ()), (True, (0,))])
+def test_engine_consumes_images(mrope, deep):
+    """A chat request with an image: the placeholder expands to the tower's rows, the reply depends on the image,
+    chunked prefill (chunks cut through the image) equals one pass, the same request again hits the prefix cache and
+    the row cache, and another image behind the same placeholder ids does not."""
+    eng, rt = _engine(mrope, deep)
+    a, b = png(48, 32), png(48, 32, color=(10, 200, 90))
+
+    def ask(img, text="what is this?", **kw):
+        msg = ChatMessage("user", [{"type": "image"}, {"type": "text", "text": text}])
+        req = GenerateRequest(messages=[msg], images=[img], sampling=SamplingParams(max_tokens=8, ignore_eos=True, **kw))
+        return eng.generate(req).collect()
+
+    r1 = ask(a)
+    assert r1.error is None and len(r1.token_ids) == 8
+    n_img = (48 // 8) * (32 // 8)
+    assert r1.usage.prompt_tokens > n_img
+    assert rt.encoded == 1
+    r2 = ask(a)
+    assert r2.token_ids == r1.token_ids and rt.encoded == 1 and rt.cache.hits >= 1
+    assert r2.usage.cached_tokens >= 16                        # the image's blocks came from the prefix cache
+    r3 = ask(b)
+    assert rt.encoded == 2 and r3.usage.cached_tokens < r2.usage.cached_tokens + 16
+    # logits of the image prompt: chunked prefill == one pass, and the image matters
+    seq = eng.prepare(GenerateRequest(messages=[ChatMessage("user", [{"type": "image"}, {"type": "text", "text": "hi"}])],
+                                      images=[a], sampling=SamplingParams(max_tokens=1)))
+    seq_b = eng.prepare(GenerateRequest(messages=[ChatMessage("user", [{"type": "image"}, {"type": "text", "text": "hi"}])],
+                                        images=[b], sampling=SamplingParams(max_tokens=1)))
+    assert seq.tokens == seq_b.tokens and seq.key_tokens() != seq_b.key_tokens()
+    assert seq.media.spans[0][1] == n_img
+    if mrope:
+        assert seq.media.rope_delta == max(48 // 8, 32 // 8) - n_img
+    eng.shutdown()
+    outs = []
+    for s_, chunks in ((seq, None), (seq_b, None), (seq, 10)):
+        e2, rt2 = _engine(mrope, deep)
+        e2.shutdown()
+        s2 = e2.prepare(s_.req)
+        e2.waiting.push(s2)
+        e2._admit()
+        n = len(s2.tokens)
+        step = chunks or n
+        last = None
+        for p0 in range(0, n, step):
+            m = min(step, n - p0)
+            bt = e2.build_batch([(s2, p0, m)])
+            last = e2.model.forward(bt, e2.kv, e2.states).logits
+            s2.n_computed = p0 + m
+        outs.append(last[-1].float())
+    assert (outs[0] - outs[1]).abs().max() > 1e-4
+    assert torch.allclose(outs[0], outs[2], atol=2e-4, rtol=1e-4)
+
+
+def test_requests_with_images_need_a_tower_and_matching_placeholders():
+    cfg = ModelConfig(arch="qwen3", n_layer=1, hidden=64, vocab=512, n_head=4, n_kv_head=2, head_dim=64, dense_ff=128)
+    eng = build_engine(cfg, weights=random_weights(cfg, "cpu", torch.float32, seed=4),
+                       engine_cfg=EngineConfig(ctx_size=256, max_seqs=2, block_size=16), start=False)
+    with pytest.raises(ValueError):
+        eng.prepare(GenerateRequest(prompt="x", images=[png(16, 16)], sampling=SamplingParams(max_tokens=1)))
+
+
+def test_mmproj_round_trip(tmp_path):
+    from legion_b200.loaders.vision import load_mmproj, write_tiny_mmproj
+    cfg = VisionConfig(depth=2, hidden=32, n_head=2, intermediate=48, out_hidden=24, patch_size=4, num_pos=16,
+                       deepstack_layers=(1,))
+    path = str(tmp_path / "mmproj.gguf")
+    write_tiny_mmproj(path, cfg, seed=7)
+    tower, hp = load_mmproj(path)
+    want = random_vision_weights(cfg, seed=7)
+    assert tower.cfg.depth == 2 and tower.cfg.deepstack_layers == (1,) and tower.cfg.out_hidden == 24
+    assert all(torch.allclose(tower.w[k], want[k]) for k in want)
+    pre = preprocess(decode_image(png(32, 32)), hp)
+    a = tower.encode(pre.patches, pre.grid)
+    b = VisionTower(cfg, want).encode(pre.patches, pre.grid)
+    assert torch.allclose(a.rows, b.rows) and torch.allclose(a.deepstack[0], b.deepstack[0])
