@@ -328,6 +328,9 @@ class LmEngine(Engine):
         """Steps that touch image tokens: the token embedding with the image rows in place, the extra rows of the
         first layers, and per-token rotary rows when the model turns its frequencies with three position axes."""
         dev = self.device
+        for s, _, _ in rows:
+            if s.media is not None and s.media.rows is None:
+                s.media.materialize(self.vision, dev, self.model.embed_dtype())     # the tower runs on this thread
         idx: List[int] = []          # rows of this step that are image tokens
         src: List[Tuple[object, int]] = []
         base = 0
@@ -395,8 +398,7 @@ class LmEngine(Engine):
         if req.images:
             if self.vision is None:
                 raise ValueError("this model has no vision tower: images cannot be used (--mmproj)")
-            tokens, media = self.vision.attach(tokens, req.images, self.mcfg.hidden, self.mcfg.mrope_sections is not None,
-                                               self.device, self.model.embed_dtype())
+            tokens, media = self.vision.attach(tokens, req.images, self.mcfg.hidden, self.mcfg.mrope_sections is not None)
         if len(tokens) + 1 > c.ctx_size:
             raise KvOverflow(f"prompt of {len(tokens)} tokens does not fit the context of {c.ctx_size}")
         sp = req.sampling

@@ -112,6 +112,9 @@ for _kv in os.environ.get("LB_TUNE", "").split(","):
         TUNE[_kv.split("=")[0].strip()] = int(_kv.split("=")[1])
 
 
+_CANARY_ON = os.environ.get("LB_CANARY", "0") == "1"
+
+
 class Workspace:
     """Per-device scratch shared by all kernels on that device's compute stream. A decode step that runs as several
     concurrent lanes (``engine.cuda_graphs``: independent halves of the batch on parallel branches of one CUDA graph)
@@ -127,6 +130,7 @@ class Workspace:
         self.splitk = torch.empty(1 << 23, dtype=torch.float32, device=device)  # 32 MiB
         self._attn: dict = {}
         self._cache: dict = {}
+        self._guards: dict = {}
 
     @classmethod
     def get(cls, device) -> "Workspace":
@@ -140,14 +144,38 @@ class Workspace:
             cls._by_device[key] = ws
         return ws
 
+    CANARY_BYTES = 256
+    CANARY = 0xA5
+
     def buf(self, key, shape, dtype):
-        """A cached scratch tensor: same key and size -> same storage (graph-safe)."""
+        """A cached scratch tensor: same key and size -> same storage (graph-safe). With ``LB_CANARY=1`` every buffer
+        sits between two guard areas filled with a byte pattern that ``check_canaries`` verifies: the substitute
+        for a memory checker on kernels that index scratch memory (a write past either end shows up by name)."""
         k = (key, tuple(shape), dtype)
         t = self._cache.get(k)
         if t is None:
-            t = torch.empty(shape, dtype=dtype, device=self.device)
+            if _CANARY_ON:
+                n = 1
+                for d in shape:
+                    n *= int(d)
+                nbytes = n * torch.empty(0, dtype=dtype).element_size()
+                pad = self.CANARY_BYTES
+                raw = torch.full((nbytes + 2 * pad,), self.CANARY, dtype=torch.uint8, device=self.device)
+                t = raw[pad:pad + nbytes].view(dtype).view(shape)
+                self._guards[k] = raw
+            else:
+                t = torch.empty(shape, dtype=dtype, device=self.device)
             self._cache[k] = t
         return t
+
+    def check_canaries(self) -> list:
+        """Names of the scratch buffers whose guard areas no longer hold the pattern (``LB_CANARY=1`` only)."""
+        bad = []
+        pad = self.CANARY_BYTES
+        for k, raw in self._guards.items():
+            if bool((raw[:pad] != self.CANARY).any()) or bool((raw[-pad:] != self.CANARY).any()):
+                bad.append(str(k[0]))
+        return bad
 
     def check(self) -> int:
         """Synchronises and returns the kernels' status word (0 = ok); clears it."""

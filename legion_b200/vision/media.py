@@ -29,8 +29,9 @@ class SeqMedia:
     n_prompt: int
     spans: List[Tuple[int, int]]                   # (first prompt position, tokens) per image
     grids: List[Tuple[int, int, int]]              # (t, h, w) in tokens per image
-    rows: torch.Tensor                             # [sum tokens, hidden] input rows, images back to back
+    rows: Optional[torch.Tensor] = None            # [sum tokens, hidden] input rows, images back to back
     deepstack: List[torch.Tensor] = field(default_factory=list)
+    pending: Optional[list] = None                 # per image: (hash, cached embedding or None, patches or None)
     key_ids: List[int] = field(default_factory=list)
     pos3: Optional[torch.Tensor] = None            # [3, n_prompt] int64 rotary positions (multi-section models)
     rope_delta: int = 0
@@ -43,6 +44,27 @@ class SeqMedia:
             out[p0:p0 + n] = self.key_ids[i:i + n]
             i += n
         return out
+
+    def materialize(self, rt: "VisionRuntime", device, dtype) -> None:
+        """Runs the tower on the images that were not in the row cache and lays the rows out back to back. The
+        engine calls this on its own thread when the sequence is placed (the thread that owns the device's stream
+        and graph captures); ``attach`` on the caller's thread only decodes and cuts patches."""
+        if self.rows is not None or self.pending is None:
+            return
+        embs = []
+        for key, emb, pre in self.pending:
+            if emb is None:
+                emb = rt.cache.get(key)
+            if emb is None:
+                emb = rt.tower.encode(pre.patches, pre.grid)
+                rt.cache.put(key, emb)
+                rt.encoded += 1
+            embs.append(emb)
+        self.rows = torch.cat([e.rows for e in embs], 0).to(device=device, dtype=dtype)
+        n_deep = min((len(e.deepstack) for e in embs), default=0)
+        self.deepstack = [torch.cat([e.deepstack[j] for e in embs], 0).to(device=device, dtype=dtype)
+                          for j in range(n_deep)]
+        self.pending = None
 
     def rope_position(self, p: int) -> int:
         """Temporal-axis rotary position of token index ``p`` (the only axis for tokens after the prompt)."""
@@ -182,32 +204,39 @@ class VisionRuntime:
         self.encoded += 1
         return key, emb
 
-    def attach(self, tokens: Sequence[int], images: Sequence[bytes], hidden: int, mrope: bool, device, dtype):
-        """(prompt tokens with the placeholders expanded, SeqMedia)."""
+    def attach(self, tokens: Sequence[int], images: Sequence[bytes], hidden: int, mrope: bool):
+        """(prompt tokens with the placeholders expanded, SeqMedia). Decoding, resizing and patch cutting happen
+        here; the tower itself runs in ``SeqMedia.materialize``."""
         if self.image_token < 0:
             raise ValueError("vision runtime is not bound to a tokenizer")
-        embs, keys = [], []
+        if self.tower.cfg.out_hidden != hidden:
+            raise ValueError(f"the vision tower gives rows of width {self.tower.cfg.out_hidden}, the model takes {hidden}")
+        m = self.hp.spatial_merge_size
+        pending, counts, grids, keys = [], [], [], []
         for data in images:
-            k, e = self.encode(data)
-            if e.rows.shape[1] != hidden:
-                raise ValueError(f"the vision tower gives rows of width {e.rows.shape[1]}, the model takes {hidden}")
-            embs.append(e)
-            keys.append(k)
-        counts = [int(e.rows.shape[0]) for e in embs]
+            key = image_hash(data)
+            emb = self.cache.get(key)
+            if emb is not None:
+                pending.append((key, emb, None))
+                grid = emb.grid
+            else:
+                pre = preprocess(decode_image(data), self.hp)
+                pending.append((key, None, pre))
+                grid = (pre.grid[0], pre.grid[1] // m, pre.grid[2] // m)
+            grids.append(grid)
+            counts.append(grid[0] * grid[1] * grid[2])
+            keys.append(key)
         toks, spans = expand_image_tokens(tokens, self.image_token, counts, self.start_token, self.end_token)
-        rows = torch.cat([e.rows for e in embs], 0).to(device=device, dtype=dtype)
-        n_deep = min((len(e.deepstack) for e in embs), default=0)
-        deep = [torch.cat([e.deepstack[j] for e in embs], 0).to(device=device, dtype=dtype) for j in range(n_deep)]
         key_ids: List[int] = []
         for k, c in zip(keys, counts):
             base = int.from_bytes(k[:8], "little")
             key_ids.extend(-1 - ((base + i * 0x9E3779B1) % KEY_MOD) for i in range(c))
-        m = SeqMedia(len(toks), spans, [e.grid for e in embs], rows, deep, key_ids)
-        m.row_of_pos = torch.full((len(toks),), -1, dtype=torch.int64)
+        sm = SeqMedia(len(toks), spans, grids, key_ids=key_ids, pending=pending)
+        sm.row_of_pos = torch.full((len(toks),), -1, dtype=torch.int64)
         r = 0
         for p0, n in spans:
-            m.row_of_pos[p0:p0 + n] = torch.arange(r, r + n)
+            sm.row_of_pos[p0:p0 + n] = torch.arange(r, r + n)
             r += n
         if mrope:
-            m.pos3, m.rope_delta = mrope_positions(len(toks), spans, m.grids)
-        return toks, m
+            sm.pos3, sm.rope_delta = mrope_positions(len(toks), spans, sm.grids)
+        return toks, sm

@@ -90,6 +90,17 @@ class ImageEmbedding:
     deepstack: List[torch.Tensor] = field(default_factory=list)     # each [tokens, out_hidden]
 
 
+def _lin(x, w, b=None):
+    """x @ w^T (+ b). bf16 rows on a GPU go through the framework's own tensor-core GEMM when the shapes allow
+    (K a multiple of 64, N of 8); everything else is a plain tensor operation."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 \
+            and w.shape[1] % 64 == 0 and w.shape[0] % 8 == 0 and w.is_contiguous():
+        from ..ops import sm100
+        y = sm100.linear(x.contiguous(), w)
+        return y if b is None else y + b
+    return F.linear(x, w, b)
+
+
 def _act(x, kind):
     if kind == "gelu_tanh":
         return F.gelu(x, approximate="tanh")
@@ -160,8 +171,8 @@ class VisionTower:
             x = F.layer_norm(x.reshape(-1, H * m2), (H * m2,), w[f"{name}.ln.w"], w[f"{name}.ln.b"], self.cfg.ln_eps)
         else:
             x = F.layer_norm(x, (H,), w[f"{name}.ln.w"], w[f"{name}.ln.b"], self.cfg.ln_eps).reshape(-1, H * m2)
-        x = F.gelu(F.linear(x, w[f"{name}.fc1.w"], w[f"{name}.fc1.b"]))
-        return F.linear(x, w[f"{name}.fc2.w"], w[f"{name}.fc2.b"])
+        x = F.gelu(_lin(x, w[f"{name}.fc1.w"], w[f"{name}.fc1.b"]))
+        return _lin(x, w[f"{name}.fc2.w"], w[f"{name}.fc2.b"])
 
     # ------------------------------------------------------------------ forward
     @torch.no_grad()
@@ -172,7 +183,7 @@ class VisionTower:
         if t != 1 or gh % m or gw % m or patches.shape != (gh * gw, cfg.patch_dim):
             raise ValueError(f"vision tower: patches {tuple(patches.shape)} do not match grid {grid}")
         dev, dt = self.device, self.dtype
-        x = F.linear(patches.to(device=dev, dtype=dt), w["patch.w"], w["patch.b"])
+        x = _lin(patches.to(device=dev, dtype=dt), w["patch.w"], w["patch.b"])
         rr, cc = merge_order_coords(gh, gw, m, dev)
         x = x + self._pos_embed(gh, gw, rr, cc).to(dt)
         use_rope = cfg.projector != "pool"
@@ -184,22 +195,22 @@ class VisionTower:
         for i in range(cfg.depth):
             p = f"blk{i}"
             h = F.layer_norm(x, (cfg.hidden,), w[f"{p}.ln1.w"], w[f"{p}.ln1.b"], cfg.ln_eps)
-            qkv = F.linear(h, w[f"{p}.qkv.w"], w[f"{p}.qkv.b"]).view(n, 3, nh, hd)
+            qkv = _lin(h, w[f"{p}.qkv.w"], w[f"{p}.qkv.b"]).view(n, 3, nh, hd)
             q, k, v = qkv[:, 0], qkv[:, 1], qkv[:, 2]
             if use_rope:
                 q, k = self._rotate(q, cos, sin), self._rotate(k, cos, sin)
             a = F.scaled_dot_product_attention(q.transpose(0, 1).unsqueeze(0), k.transpose(0, 1).unsqueeze(0),
                                                v.transpose(0, 1).unsqueeze(0))[0].transpose(0, 1).reshape(n, cfg.hidden)
-            x = x + F.linear(a, w[f"{p}.proj.w"], w[f"{p}.proj.b"])
+            x = x + _lin(a, w[f"{p}.proj.w"], w[f"{p}.proj.b"])
             h = F.layer_norm(x, (cfg.hidden,), w[f"{p}.ln2.w"], w[f"{p}.ln2.b"], cfg.ln_eps)
-            h = _act(F.linear(h, w[f"{p}.fc1.w"], w[f"{p}.fc1.b"]), cfg.act)
-            x = x + F.linear(h, w[f"{p}.fc2.w"], w[f"{p}.fc2.b"])
+            h = _act(_lin(h, w[f"{p}.fc1.w"], w[f"{p}.fc1.b"]), cfg.act)
+            x = x + _lin(h, w[f"{p}.fc2.w"], w[f"{p}.fc2.b"])
             if i in cfg.deepstack_layers and cfg.projector != "pool":
                 deep.append(self._merger(f"ds{cfg.deepstack_layers.index(i)}", x, True))
         if cfg.projector == "pool":
             pooled = x.view(-1, m * m, cfg.hidden).float().mean(1)
             pooled = pooled * torch.rsqrt(pooled.pow(2).mean(-1, keepdim=True) + cfg.ln_eps) * w["proj.norm.w"].float()
-            rows = F.linear(pooled.to(dt), w["proj.w"])
+            rows = _lin(pooled.to(dt), w["proj.w"])
         else:
             rows = self._merger("merger", x, False)
         return ImageEmbedding(rows, (1, gh // m, gw // m), deep)

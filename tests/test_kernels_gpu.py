@@ -842,3 +842,37 @@ def test_mla_attn_long_context(nh, page, q_lens, ctx, splits):
                         torch.tensor(ctx, device=DEV, dtype=torch.int32), bt, page, max(q_lens), scale, n_splits=splits)
     status_ok()
     close(out, _mla_reference(q_abs, cache, bt, ctx, cu, page, scale), 3e-2, 3e-2)
+
+
+def test_scratch_buffers_keep_their_guard_areas(monkeypatch):
+    """Debug build of the scratch allocator (``LB_CANARY=1``): every cached scratch tensor sits between two guard
+    areas; after a decode-sized MoE block, a router call on wide rows, an arg-max and a split-key attention call none
+    of the guards has been written."""
+    import legion_b200.ops.sm100 as m
+    monkeypatch.setattr(m, "_CANARY_ON", True)
+    saved = dict(m.Workspace._by_device)
+    m.Workspace._by_device.clear()
+    try:
+        T, E, k, H, F = 16, 32, 4, 4096, 256
+        x, res = rnd(T, H), rnd(T, H)
+        nw = torch.rand(H, device=DEV) + 0.5
+        r = m.router(x, rnd(E, H, scale=H ** -0.5), k, norm=(nw, 1e-6, 0.0))
+        m.moe_experts(r.x_normed, r.ids, r.wts, rnd(E, 2 * F, H, scale=H ** -0.5), rnd(E, H, F, scale=F ** -0.5), F,
+                      residual=res, routing=r)
+        m.argmax(torch.randn(5, 70000, device=DEV))
+        Hq, Hkv, D, page, ctx = 8, 2, 128, 64, 700
+        nb = 3 * ((ctx + page - 1) // page)
+        kc, vc = make_cache(nb, page, Hkv, D)
+        bt = torch.arange(nb, device=DEV, dtype=torch.int32).view(3, -1)
+        m.paged_decode(rnd(3, Hq, D), kc, vc, bt, torch.full((3,), ctx, device=DEV, dtype=torch.int32), D ** -0.5,
+                       n_splits=4, max_ctx=ctx)
+        ws = m.Workspace.get(DEV)
+        assert len(ws._guards) >= 3
+        assert ws.check() == 0 and ws.check_canaries() == []
+        # the check itself: a byte written just past a buffer is reported under the buffer's name
+        key, raw = next(iter(ws._guards.items()))
+        raw[-1] = 0
+        assert ws.check_canaries() == [str(key[0])]
+    finally:
+        m.Workspace._by_device.clear()
+        m.Workspace._by_device.update(saved)
