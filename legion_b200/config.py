@@ -49,6 +49,16 @@ class ModelConfig:
     gdn_conv: int = 4
     gdn_tiled_heads: bool = False      # value head h reads key head h % n_k (GGUF order) instead of h // (n_v/n_k)
     gdn_gate_act: str = "silu"         # activation of z in the gated output norm
+    # Kimi delta attention ("kda" layers): per-channel decay, q / k / v each behind a short causal convolution
+    kda_heads: int = 4
+    kda_head_dim: int = 64
+    kda_conv: int = 4
+    kda_rank: int = 32                 # width of the low-rank gate projections (f_a / f_b, g_a / g_b)
+    kda_lower: float = -5.0            # lower bound of the log decay: g = lower * sigmoid(-(f(x) + dt_bias) * A)
+    # hyper-connections: the residual is ``hyper_streams`` parallel streams mixed before and after every sublayer
+    hyper_streams: int = 1
+    hc_iters: int = 20                 # Sinkhorn rounds of the stream-to-stream mix
+    hc_eps: float = 1e-6
     # mamba2 (nemotron-h)
     ssm_state: int = 128
     ssm_heads: int = 8
@@ -136,6 +146,17 @@ class ModelConfig:
 # --------------------------------------------------------------------------------------------------
 # presets
 # --------------------------------------------------------------------------------------------------
+def tiny_glm_next() -> "ModelConfig":
+    """Shape of the glm5-next family in miniature: Kimi-delta-attention layers with a latent-attention layer every
+    third, hyper-connections (4 streams) around every sublayer, sigmoid-routed MoE with a shared expert after one
+    dense layer. The latent-attention layers attend densely (no sparse key selection)."""
+    return ModelConfig(arch="glm5_next", n_layer=3, hidden=128, vocab=512, n_head=4, n_kv_head=4, head_dim=96,
+                       layer_kinds=["kda", "kda", "mla"], kda_heads=4, kda_head_dim=32, kda_rank=16,
+                       q_lora=48, kv_lora=64, qk_nope_dim=32, qk_rope_dim=64, v_head_dim=32, qk_norm=False,
+                       hyper_streams=4, hc_iters=8, dense_ff=192, first_dense_layers=1, n_expert=8, top_k=2,
+                       expert_ff=64, shared_ff=64, router_mode="sigmoid", router_bias=True, route_scale=2.0)
+
+
 def tiny_hybrid_moe() -> ModelConfig:
     """4-layer hybrid: 3 Gated DeltaNet layers + 1 gated GQA layer, 8 experts top-2 + shared expert."""
     return ModelConfig(arch="qwen35moe", n_layer=4, hidden=256, vocab=4096, n_head=4, n_kv_head=2, head_dim=64,
@@ -220,6 +241,7 @@ PRESETS = {
     "tiny-gemma": tiny_gemma,
     "tiny-nemotron-h": tiny_nemotron_h,
     "tiny-hybrid-moe": tiny_hybrid_moe,
+    "tiny-glm-next": tiny_glm_next,
     "tiny-gqa-moe": tiny_gqa_moe,
     "tiny-dense": tiny_dense,
     "tiny-mla-moe": tiny_mla_moe,

@@ -191,6 +191,9 @@ class LmEngine(Engine):
         self._stop = threading.Event()
         self._thread: Optional[threading.Thread] = None
         self._fail: Optional[str] = None
+        if ("kda" in self.mcfg.layer_kinds) and (drafter is not None or c.spec != "none"):
+            raise ValueError("speculative decoding is not available for models with Kimi-delta-attention layers "
+                             "(their verify steps have no state replay)")
         self.vision = None                # vision.VisionRuntime once a tower is attached (``attach_vision``)
         self.drafter = drafter
         if self.drafter is None and c.spec != "none":
@@ -249,6 +252,8 @@ class LmEngine(Engine):
         """Mamba-2 layers decode from CUDA graphs when their head shape runs on the scan kernel (the token loop that
         serves other shapes reads sequence bounds on the host)."""
         m = self.mcfg
+        if "kda" in m.layer_kinds or m.hyper_streams > 1:
+            return False          # tensor-operation layers that read sequence bounds on the host
         if "mamba2" not in m.layer_kinds:
             return True
         from ..ops import sm100

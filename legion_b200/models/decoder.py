@@ -126,6 +126,12 @@ class StatePool:
                 self.conv[il] = torch.zeros(n_slots, C, cfg.gdn_conv - 1, device=device, dtype=torch.float32)
                 self.ssm[il] = torch.zeros(n_slots, cfg.gdn_v_heads // tp, cfg.gdn_k_dim, cfg.gdn_v_dim, device=device,
                                            dtype=torch.float32)
+            elif kind == "kda":
+                c = cfg.kda_heads * cfg.kda_head_dim
+                self.conv[il] = torch.zeros(n_slots, 3 * c, cfg.kda_conv - 1, device=device, dtype=torch.float32)
+                # state[head, value row j, key channel i]
+                self.ssm[il] = torch.zeros(n_slots, cfg.kda_heads, cfg.kda_head_dim, cfg.kda_head_dim, device=device,
+                                           dtype=torch.float32)
             elif kind == "mamba2":
                 di = cfg.ssm_heads * cfg.ssm_head_dim
                 C = di + 2 * cfg.ssm_groups * cfg.ssm_state
@@ -568,6 +574,136 @@ class Decoder:
             out[q0:q1] = torch.einsum("qhl,hvl->qhv", o_lat, wkv_b[:, dn:].float()).to(x.dtype)
         return ops.linear(out.reshape(T, nh * dvh), w[f"{p}.mla.o"])
 
+    def _kda(self, p: str, il: int, x, b: StepBatch, st: StatePool):
+        """Kimi delta attention (``src/model/glm5next.rs::glm_kda_on``, ``ops.rs::cpu_kda_scan`` in the reference):
+        q, k, v each through a causal short convolution and SiLU; a per-channel log decay
+        ``lower * sigmoid(-(f_b f_a x + dt_bias) * A)``; the gated delta rule over a [d, d] state per head
+        (row j of the state decays per key channel, then moves by beta * (v_j - row . k) along k); an RMS norm
+        gated by ``sigmoid(g_b g_a x)``; the output projection. Tensor operations on every back-end: the token
+        recurrence is a loop over the step's longest sequence with all sequences and heads batched (a decode step
+        is one iteration)."""
+        cfg, w = self.cfg, self.w
+        nh, d, KC = cfg.kda_heads, cfg.kda_head_dim, cfg.kda_conv
+        c = nh * d
+        T = x.shape[0]
+        f32 = torch.float32
+        qkv = ops.linear(x, w[f"{p}.kda.qkv"]).to(f32)                                   # [T, 3c]
+        z = ops.linear(ops.linear(x, w[f"{p}.kda.f_a"]), w[f"{p}.kda.f_b"]).to(f32)      # [T, c]
+        A = w[f"{p}.kda.A"].to(f32).repeat_interleave(d)
+        g = cfg.kda_lower * torch.sigmoid(-((z + w[f"{p}.kda.dt_bias"].to(f32)) * A))    # log decay per channel
+        beta = torch.sigmoid(ops.linear(x, w[f"{p}.kda.beta"]).to(f32))                  # [T, heads]
+        gate = ops.linear(ops.linear(x, w[f"{p}.kda.g_a"]), w[f"{p}.kda.g_b"]).to(f32)   # [T, c]
+        cw = w[f"{p}.kda.conv_w"].to(f32)                                                # [3c, KC]
+        cu = b.cu_q_host if b.cu_q_host is not None else b.cu_q.tolist()
+        n_seq = len(cu) - 1
+        slots = b.state_slots.long()
+        lens = [cu[i + 1] - cu[i] for i in range(n_seq)]
+        L = max(lens) if lens else 0
+        # rows of the step as [sequence, time] with padding: index T is a zero row
+        idx = torch.full((n_seq, L), T, dtype=torch.int64)
+        for i in range(n_seq):
+            idx[i, :lens[i]] = torch.arange(cu[i], cu[i + 1])
+        idx = idx.to(x.device)
+        live = idx < T                                                                   # [n_seq, L]
+        pad = lambda t: torch.cat([t, t.new_zeros(1, *t.shape[1:])], 0)[idx]             # noqa: E731
+        xs, gs, bs = pad(qkv), pad(g), pad(beta)                                         # [n_seq, L, ...]
+        hist = st.conv[il][slots]                                                        # [n_seq, 3c, KC - 1]
+        S = st.ssm[il][slots]                                                            # [n_seq, heads, d(j), d(i)]
+        out = torch.zeros(n_seq, L, c, dtype=f32, device=x.device)
+        qs = d ** -0.5
+        for t in range(L):
+            m = live[:, t]
+            xt = xs[:, t]                                                                # [n_seq, 3c]
+            win = torch.cat([hist, xt.unsqueeze(2)], 2)                                  # [n_seq, 3c, KC]
+            y = (win * cw.unsqueeze(0)).sum(2)
+            y = y * torch.sigmoid(y)
+            hist = torch.where(m[:, None, None], win[:, :, 1:], hist)
+            q, k, v = (y[:, j * c:(j + 1) * c].view(n_seq, nh, d) for j in range(3))
+            qn = q * (qs * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + 1e-6))
+            kn = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + 1e-6)
+            dec = gs[:, t].view(n_seq, nh, d).exp()                                      # per key channel
+            S2 = S * dec.unsqueeze(2)
+            delta = (v - torch.einsum("shji,shi->shj", S2, kn)) * bs[:, t].unsqueeze(-1)
+            S2 = S2 + delta.unsqueeze(-1) * kn.unsqueeze(2)
+            out[:, t] = torch.einsum("shji,shi->shj", S2, qn).reshape(n_seq, c)
+            S = torch.where(m[:, None, None, None], S2, S)
+        if b.write_state:
+            st.conv[il][slots] = hist
+            st.ssm[il][slots] = S
+        o = out[live]                                                                    # back to step order
+        o = o.view(T, nh, d)
+        o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + cfg.rms_eps) * w[f"{p}.kda.norm"].to(f32)
+        o = o * torch.sigmoid(gate.view(T, nh, d))
+        return ops.linear(o.reshape(T, c).to(x.dtype), w[f"{p}.kda.out"])
+
+    # ------------------------------------------------------------------ hyper-connections
+    def _hc_pre(self, name: str, X):
+        """Mixer in front of a sublayer (``ops.rs::cpu_hc_pre`` in the reference). X [T, hc, H] float32 streams ->
+        (y [T, H]: the streams weighed into the sublayer's input, post [T, hc]: weight of the sublayer output in
+        each new stream, comb [T, hc(dst), hc(src)]: Sinkhorn-normalised stream-to-stream mix)."""
+        cfg, w = self.cfg, self.w
+        T, hc, H = X.shape
+        flat = X.reshape(T, hc * H)
+        normed = flat * torch.rsqrt(flat.pow(2).mean(-1, keepdim=True) + cfg.rms_eps)
+        mix = normed @ w[f"{name}.hc_f"].float().t()                                     # [T, (2 + hc) * hc]
+        scale, base = w[f"{name}.hc_scale"].float(), w[f"{name}.hc_base"].float()
+        eps = cfg.hc_eps
+        pre = torch.sigmoid(mix[:, :hc] * scale[0] + base[:hc]) + eps
+        post = torch.sigmoid(mix[:, hc:2 * hc] * scale[1] + base[hc:2 * hc]) * 2.0
+        # comb[t, s, d] laid out source-major like the reference's buffer (d fastest)
+        cm = (mix[:, 2 * hc:] * scale[2] + base[2 * hc:]).view(T, hc, hc)
+        cm = torch.softmax(cm, dim=2) + eps                       # over destinations, per source
+        cm = cm / (cm.sum(1, keepdim=True) + eps)                 # each destination over the sources
+        for _ in range(1, cfg.hc_iters):
+            cm = cm / (cm.sum(2, keepdim=True) + eps)             # each source over the destinations
+            cm = cm / (cm.sum(1, keepdim=True) + eps)
+        y = (X * pre.unsqueeze(-1)).sum(1)
+        return y, post, cm.transpose(1, 2).contiguous()
+
+    @staticmethod
+    def _hc_post(out, X, post, comb):
+        """New stream d = out * post[d] + sum_s X[s] * comb[d, s]."""
+        return out.float().unsqueeze(1) * post.unsqueeze(-1) + torch.einsum("tds,tsh->tdh", comb, X)
+
+    def _forward_hc(self, b: StepBatch, kv: KvCache, st: Optional[StatePool], want_logits: bool) -> StepOutput:
+        """Forward pass of a model whose residual is several streams (hyper-connections). Every sublayer reads
+        the streams through its own mixer and its output re-enters every stream with per-token weights
+        (``src/model/glm5next.rs:994-1036`` in the reference); the head reads the streams' mean."""
+        cfg, w, pc = self.cfg, self.w, self.pctx
+        hc = cfg.hyper_streams
+        x0 = b.embeds if b.embeds is not None else self.embed(b.token_ids)
+        dt = x0.dtype
+        X = x0.float().unsqueeze(1).expand(-1, hc, -1).contiguous()
+        for il in range(cfg.n_layer):
+            p, kind = f"l{il}", cfg.layer_kinds[il]
+            y, post, comb = self._hc_pre(f"{p}.hca", X)
+            h, _ = ops.rmsnorm(y.to(dt), w[f"{p}.attn_norm"], cfg.rms_eps, cfg.norm_offset)
+            if kind in ("attn", "swa", "nope"):
+                a = self._attn(p, il, h, b, kv, cfg.sliding_window if kind == "swa" else 0, rope=kind != "nope")
+            elif kind == "gdn":
+                a = self._gdn(p, il, h, b, st)
+            elif kind == "mla":
+                a = self._mla(p, il, h, b, kv)
+            elif kind == "kda":
+                a = self._kda(p, il, h, b, st)
+            elif kind == "mamba2":
+                a = self._mamba2(p, il, h, b, st)
+            else:
+                raise ValueError(kind)
+            X = self._hc_post(pc.full_hidden(a, None), X, post, comb)
+            y, post, comb = self._hc_pre(f"{p}.hcf", X)
+            h, _ = ops.rmsnorm(y.to(dt), w[f"{p}.ffn_norm"], cfg.rms_eps, cfg.norm_offset)
+            f, _, _ = self._ffn(p, cfg.is_moe_layer(il), h, None)
+            X = self._hc_post(pc.full_hidden(f, None), X, post, comb)
+        last = X.mean(1).to(dt)
+        rows = last if b.logit_rows is None else last.index_select(0, b.logit_rows)
+        hidden, _ = ops.rmsnorm(rows, w["output_norm"], cfg.rms_eps, cfg.norm_offset)
+        out = StepOutput(hidden=hidden, last_hidden=last, captures={})
+        if want_logits:
+            out.logits = self.logits(hidden)
+        pc.end_step()
+        return out
+
     def _mamba2(self, p: str, il: int, x, b: StepBatch, st: StatePool):
         """Mamba-2 (SSD) layer: on a GPU the recurrence, the D skip and the silu(z) gate are one kernel with the state
         of a (sequence, head) in registers (``csrc/mamba2.cu``); the CPU form is the token-serial reference."""
@@ -689,6 +825,8 @@ class Decoder:
             a = self._mla(p, il, h, b, kv)
         elif kind == "mamba2":
             a = self._mamba2(p, il, h, b, st)
+        elif kind == "kda":
+            a = self._kda(p, il, h, b, st)
         else:
             raise ValueError(kind)
         routing = None
@@ -787,6 +925,8 @@ class Decoder:
     def forward(self, b: StepBatch, kv: KvCache, st: Optional[StatePool], want_logits: bool = True) -> StepOutput:
         if self.pipe is not None:
             return self._forward_pipe(b, kv, st, want_logits)
+        if self.cfg.hyper_streams > 1:
+            return self._forward_hc(b, kv, st, want_logits)
         cfg, w, pc = self.cfg, self.w, self.pctx
         x = b.embeds if b.embeds is not None else self.embed(b.token_ids)
         resid = None

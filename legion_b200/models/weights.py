@@ -55,6 +55,19 @@ def layer_weight_shapes(cfg: ModelConfig, il: int, prefix: Optional[str] = None,
         s[f"{p}.mla.kv_a_norm"] = (cfg.kv_lora,)
         s[f"{p}.mla.kv_b"] = (nh * (cfg.qk_nope_dim + cfg.v_head_dim), cfg.kv_lora)
         s[f"{p}.mla.o"] = (H, nh * cfg.v_head_dim)
+    elif kind == "kda":
+        c, r = cfg.kda_heads * cfg.kda_head_dim, cfg.kda_rank
+        s[f"{p}.kda.qkv"] = (3 * c, H)                  # q | k | v, each heads x head_dim
+        s[f"{p}.kda.conv_w"] = (3 * c, cfg.kda_conv)
+        s[f"{p}.kda.f_a"] = (r, H)                      # decay gate, low rank: f_b (f_a x)
+        s[f"{p}.kda.f_b"] = (c, r)
+        s[f"{p}.kda.dt_bias"] = (c,)
+        s[f"{p}.kda.A"] = (cfg.kda_heads,)
+        s[f"{p}.kda.beta"] = (cfg.kda_heads, H)
+        s[f"{p}.kda.g_a"] = (r, H)                      # output gate, low rank: g_b (g_a x)
+        s[f"{p}.kda.g_b"] = (c, r)
+        s[f"{p}.kda.norm"] = (cfg.kda_head_dim,)
+        s[f"{p}.kda.out"] = (H, c)
     elif kind == "mamba2":
         di = cfg.ssm_heads * cfg.ssm_head_dim
         conv_c = di + 2 * cfg.ssm_groups * cfg.ssm_state
@@ -68,6 +81,12 @@ def layer_weight_shapes(cfg: ModelConfig, il: int, prefix: Optional[str] = None,
         s[f"{p}.ssm.out"] = (H, di)
     else:
         raise ValueError(f"unknown layer kind {kind}")
+    if cfg.hyper_streams > 1:
+        hc = cfg.hyper_streams
+        for which in ("hca", "hcf"):                    # the mixers in front of the attention and the FFN sublayer
+            s[f"{p}.{which}.hc_f"] = ((2 + hc) * hc, hc * H)
+            s[f"{p}.{which}.hc_scale"] = (3,)
+            s[f"{p}.{which}.hc_base"] = ((2 + hc) * hc,)
     if moe:
         E, F = cfg.n_expert, cfg.expert_ff
         s[f"{p}.moe.router"] = (E, H)
@@ -112,7 +131,8 @@ FP32_SUFFIXES = ("_norm", ".norm", "norm", ".A", ".D", ".dt_bias", ".conv_w", ".
 def is_fp32_weight(name: str) -> bool:
     """Norm weights, recurrence constants and conv taps stay float32 on every back-end."""
     leaf = name.rsplit(".", 1)[-1]
-    return leaf.endswith("norm") or leaf in ("A", "D", "dt_bias", "conv_w", "conv_b", "router_bias")
+    return leaf.endswith("norm") or leaf in ("A", "D", "dt_bias", "conv_w", "conv_b", "router_bias", "hc_f", "hc_scale",
+                                             "hc_base")
 
 
 def layer_of(name: str) -> Optional[int]:
@@ -149,6 +169,12 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=torch.float32, seed: in
             t = torch.ones(shp, dtype=torch.float32, device=device)
         elif leaf in ("dt_bias", "conv_b", "router_bias"):
             t = (torch.randn(shp, generator=g) * 0.1).to(device)
+        elif leaf == "hc_scale":
+            t = torch.ones(shp, dtype=torch.float32, device=device)
+        elif leaf == "hc_base":
+            t = (torch.randn(shp, generator=g) * 0.5).to(device)
+        elif leaf == "hc_f":
+            t = (torch.randn(shp, generator=g) * 0.05).to(device)
         elif leaf == "conv_w":
             t = (torch.randn(shp, generator=g) * 0.3).to(device)
         elif device.type == "cuda" and wd == torch.bfloat16:
@@ -178,6 +204,9 @@ class Shard:
         if dp_attention:
             self.kv_rep = 1
             return
+        if world > 1 and ("kda" in cfg.layer_kinds or cfg.hyper_streams > 1):
+            raise NotImplementedError("Kimi-delta-attention layers and hyper-connections run on one rank (their "
+                                      "weights have no tensor-parallel split here)")
         assert cfg.n_head % world == 0, "query heads must divide by the TP degree"
         self.kv_rep = 1
         if cfg.n_kv_head % world != 0:

@@ -1,0 +1,145 @@
+"""Hyper-connections and Kimi delta attention: the vectorised forms against token-serial restatements of the
+reference's definitions, and the engine invariants on a tiny model of that family (CPU, fp32)."""
+import math
+
+import torch
+
+from legion_b200.config import PRESETS
+from legion_b200.engine.lm import EngineConfig, build_engine
+from legion_b200.models.decoder import Decoder, KvCache, StatePool, StepBatch
+from legion_b200.models.weights import random_weights
+
+
+def _model(seed=1):
+    cfg = PRESETS["tiny-glm-next"]()
+    w = random_weights(cfg, "cpu", torch.float32, seed=seed, std=0.08)
+    return cfg, w, Decoder(cfg, w, None, max_position=300)
+
+
+def test_hyper_connection_mixer_matches_the_serial_definition():
+    cfg, w, m = _model()
+    T, hc, H = 5, cfg.hyper_streams, cfg.hidden
+    X = torch.randn(T, hc, H)
+    y, post, comb = m._hc_pre("l0.hca", X)
+    f, scale, base = w["l0.hca.hc_f"], w["l0.hca.hc_scale"], w["l0.hca.hc_base"]
+    eps = cfg.hc_eps
+    sig = lambda v: 1 / (1 + math.exp(-v))      # noqa: E731
+    for t in range(T):
+        flat = X[t].reshape(-1)
+        normed = flat / math.sqrt(float(flat.pow(2).mean()) + cfg.rms_eps)
+        mix = (f @ normed).tolist()
+        pre = [sig(mix[h] * float(scale[0]) + float(base[h])) + eps for h in range(hc)]
+        po = [sig(mix[hc + h] * float(scale[1]) + float(base[hc + h])) * 2 for h in range(hc)]
+        c = [mix[2 * hc + i] * float(scale[2]) + float(base[2 * hc + i]) for i in range(hc * hc)]    # c[d + hc * s]
+        for s in range(hc):
+            col = c[s * hc:(s + 1) * hc]
+            mx = max(col)
+            ex = [math.exp(v - mx) for v in col]
+            tot = sum(ex)
+            c[s * hc:(s + 1) * hc] = [v / tot + eps for v in ex]
+
+        def cols():
+            for d in range(hc):
+                sm = sum(c[d + hc * s] for s in range(hc)) + eps
+                for s in range(hc):
+                    c[d + hc * s] /= sm
+
+        def rows():
+            for s in range(hc):
+                sm = sum(c[s * hc:(s + 1) * hc]) + eps
+                for d in range(hc):
+                    c[s * hc + d] /= sm
+        cols()
+        for _ in range(1, cfg.hc_iters):
+            rows()
+            cols()
+        assert torch.allclose(post[t], torch.tensor(po), atol=1e-5)
+        want_y = sum(X[t, h] * pre[h] for h in range(hc))
+        assert torch.allclose(y[t], want_y, atol=1e-5)
+        for d in range(hc):
+            for s in range(hc):
+                assert abs(float(comb[t, d, s]) - c[d + hc * s]) < 1e-5
+        # the mix is (close to) doubly stochastic after the Sinkhorn rounds
+        assert torch.allclose(comb[t].sum(1), torch.ones(hc), atol=1e-2)
+    out = torch.randn(T, H)
+    new = Decoder._hc_post(out, X, post, comb)
+    d, t = 2, 3
+    want = out[t] * post[t, d] + sum(X[t, s] * comb[t, d, s] for s in range(hc))
+    assert torch.allclose(new[t, d], want, atol=1e-5)
+
+
+def test_kimi_delta_attention_matches_the_token_serial_recurrence():
+    cfg, w, m = _model(seed=2)
+    nh, d, KC = cfg.kda_heads, cfg.kda_head_dim, cfg.kda_conv
+    c = nh * d
+    lens = [7, 1, 4]
+    T = sum(lens)
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    x = torch.randn(T, cfg.hidden) * 0.5
+    st = StatePool(cfg, 4, "cpu")
+    st.conv[0].normal_(0, 0.3)
+    st.ssm[0].normal_(0, 0.3)
+    conv0, ssm0 = st.conv[0].clone(), st.ssm[0].clone()
+    slots = [2, 0, 3]
+    i32 = dict(dtype=torch.int32)
+    b = StepBatch(token_ids=torch.zeros(T, **i32), positions=torch.zeros(T, **i32), cu_q=torch.tensor(cu, **i32),
+                  ctx_lens=torch.tensor(lens, **i32), block_table=torch.zeros(3, 1, **i32),
+                  slots=torch.zeros(T, dtype=torch.int64), state_slots=torch.tensor(slots, **i32), max_q_len=max(lens),
+                  cu_q_host=cu)
+    got = m._kda("l0", 0, x, b, st)
+    p = "l0.kda"
+    qkv = x @ w[f"{p}.qkv"].t()
+    z = (x @ w[f"{p}.f_a"].t()) @ w[f"{p}.f_b"].t()
+    gate = (x @ w[f"{p}.g_a"].t()) @ w[f"{p}.g_b"].t()
+    beta = torch.sigmoid(x @ w[f"{p}.beta"].t())
+    want = torch.zeros(T, c)
+    for si, n in enumerate(lens):
+        hist = conv0[slots[si]].clone()              # [3c, KC - 1]
+        S = ssm0[slots[si]].clone()                  # [heads, j, i]
+        for t in range(cu[si], cu[si] + n):
+            win = torch.cat([hist, qkv[t].unsqueeze(1)], 1)
+            y = (win * w[f"{p}.conv_w"]).sum(1)
+            y = y * torch.sigmoid(y)
+            hist = win[:, 1:]
+            for h in range(nh):
+                q, k, v = (y[j * c + h * d:j * c + (h + 1) * d] for j in range(3))
+                qn = q * (d ** -0.5) / torch.sqrt(q.pow(2).sum() + 1e-6)
+                kn = k / torch.sqrt(k.pow(2).sum() + 1e-6)
+                g = cfg.kda_lower * torch.sigmoid(-((z[t, h * d:(h + 1) * d] + w[f"{p}.dt_bias"][h * d:(h + 1) * d])
+                                                    * w[f"{p}.A"][h]))
+                for j in range(d):
+                    row = S[h, j] * g.exp()
+                    delta = (v[j] - row @ kn) * beta[t, h]
+                    row = row + delta * kn
+                    S[h, j] = row
+                    want[t, h * d + j] = row @ qn
+        assert torch.allclose(st.conv[0][slots[si]], hist, atol=1e-5)
+        assert torch.allclose(st.ssm[0][slots[si]], S, atol=1e-4)
+    o = want.view(T, nh, d)
+    o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + cfg.rms_eps) * w[f"{p}.norm"]
+    o = (o * torch.sigmoid(gate.view(T, nh, d))).reshape(T, c) @ w[f"{p}.out"].t()
+    assert torch.allclose(got, o, atol=2e-4, rtol=1e-3)
+    assert torch.equal(st.ssm[0][1], ssm0[1])        # an unused slot is untouched
+
+
+def test_engine_invariants_on_the_tiny_glm_next_model():
+    """Batched == single, chunked prefill == one pass (recurrent state carried between chunks), and a repeated
+    prompt resumes from the prefix cache with its recurrent snapshot."""
+    cfg = PRESETS["tiny-glm-next"]()
+    w = random_weights(cfg, "cpu", torch.float32, seed=3, std=0.08)
+    ec = dict(ctx_size=256, max_seqs=4, block_size=16, max_batch_tokens=256)
+    prompts = [list(range(5, 5 + n)) for n in (41, 23, 60)]
+    one = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(prefill_chunk=256, **ec))
+    singles = [one.generate_text(tokens=p, max_tokens=6, ignore_eos=True).token_ids for p in prompts]
+    again = one.generate_text(tokens=prompts[2], max_tokens=6, ignore_eos=True)
+    one.shutdown()
+    assert again.token_ids == singles[2] and again.usage.cached_tokens >= 16
+    chunked = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(prefill_chunk=16, **ec))
+    streams = [chunked.generate(__import__("legion_b200.engine.types", fromlist=["GenerateRequest"]).GenerateRequest(
+        prompt_tokens=p, sampling=__import__("legion_b200.engine.types", fromlist=["SamplingParams"]).SamplingParams(
+            max_tokens=6, ignore_eos=True))) for p in prompts]
+    outs = [s.collect().token_ids for s in streams]
+    chunked.shutdown()
+    assert outs == singles

@@ -21,10 +21,16 @@ def _cfgs():
                     dense_ff=384, first_dense_layers=1, n_expert=8, top_k=2, expert_ff=128, shared_ff=128,
                     router_mode="sigmoid", router_bias=True, n_group=4, topk_group=2, route_scale=2.5),
         PRESETS["tiny-nemotron-h"](),          # Mamba-2 layers on the state-space scan kernel
+        # glm5-next family: Kimi-delta-attention layers, hyper-connections around every sublayer, latent attention
+        ModelConfig(arch="glm5_next", n_layer=3, hidden=256, vocab=1024, n_head=16, n_kv_head=16, head_dim=128,
+                    layer_kinds=["kda", "kda", "mla"], kda_heads=4, kda_head_dim=64, kda_rank=32, hyper_streams=4,
+                    hc_iters=8, q_lora=96, kv_lora=512, qk_nope_dim=64, qk_rope_dim=64, v_head_dim=64, qk_norm=False,
+                    dense_ff=384, first_dense_layers=1, n_expert=8, top_k=2, expert_ff=128, shared_ff=128,
+                    router_mode="sigmoid", router_bias=True, route_scale=2.0),
     ]
 
 
-@pytest.mark.parametrize("idx", [0, 1, 2, 3, 4])
+@pytest.mark.parametrize("idx", [0, 1, 2, 3, 4, 5])
 @pytest.mark.parametrize("graphs", [False, True])
 def test_gpu_engine_matches_cpu_logits(idx, graphs):
     """Greedy tokens of random tiny models are fragile under bf16; compare the first-step logits of the GPU
