@@ -57,6 +57,11 @@ class ModelConfig:
     kda_lower: float = -5.0            # lower bound of the log decay: g = lower * sigmoid(-(f(x) + dt_bias) * A)
     # hyper-connections: the residual is ``hyper_streams`` parallel streams mixed before and after every sublayer
     hyper_streams: int = 1
+    hyper_mode: str = "sinkhorn"       # "sinkhorn": per-token pre / post weights and a Sinkhorn-normalised stream mix
+                                       # (glm5-next, deepseek41); "gated": a low-rank sigmoid gate per channel mixes
+                                       # the normed streams, the block output re-enters every stream with a weight
+                                       # of its own, the last mixer is the output norm (qwen4exp)
+    hc_rank: int = 16                  # "gated": width of the low-rank gate
     hc_iters: int = 20                 # Sinkhorn rounds of the stream-to-stream mix
     hc_eps: float = 1e-6
     # mamba2 (nemotron-h)
@@ -157,6 +162,20 @@ def tiny_glm_next() -> "ModelConfig":
                        expert_ff=64, shared_ff=64, router_mode="sigmoid", router_bias=True, route_scale=2.0)
 
 
+def tiny_qwen4exp() -> "ModelConfig":
+    """Shape of the qwen4exp family in miniature: the hybrid Gated-DeltaNet / gated-attention MoE stack with a
+    sigmoid DeltaNet output gate, multi-section rotary positions and gated hyper-connections (4 streams) in place of
+    the residual stream and the pre-norms. Attention is dense (its sparse key selection equals dense attention up to
+    the selection budget); the n-gram embedding layer is not modelled."""
+    c = tiny_hybrid_moe()
+    c.arch = "qwen4exp"
+    c.hyper_streams, c.hyper_mode, c.hc_rank = 4, "gated", 8
+    c.gdn_gate_act = "sigmoid"
+    if c.rope_dim == 64:
+        c.mrope_sections = (11, 11, 10)
+    return c
+
+
 def tiny_hybrid_moe() -> ModelConfig:
     """4-layer hybrid: 3 Gated DeltaNet layers + 1 gated GQA layer, 8 experts top-2 + shared expert."""
     return ModelConfig(arch="qwen35moe", n_layer=4, hidden=256, vocab=4096, n_head=4, n_kv_head=2, head_dim=64,
@@ -242,6 +261,7 @@ PRESETS = {
     "tiny-nemotron-h": tiny_nemotron_h,
     "tiny-hybrid-moe": tiny_hybrid_moe,
     "tiny-glm-next": tiny_glm_next,
+    "tiny-qwen4exp": tiny_qwen4exp,
     "tiny-gqa-moe": tiny_gqa_moe,
     "tiny-dense": tiny_dense,
     "tiny-mla-moe": tiny_mla_moe,

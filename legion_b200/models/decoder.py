@@ -269,6 +269,8 @@ class Decoder:
     def __init__(self, cfg: ModelConfig, weights: Dict[str, torch.Tensor], pctx: Optional[ParallelCtx] = None,
                  max_position: Optional[int] = None, pipe=None):
         self.cfg = cfg
+        if cfg.hyper_streams > 1 and pipe is not None:
+            raise NotImplementedError("hyper-connection models run without pipeline stages")
         self.w = weights
         self.pctx = pctx or ParallelCtx.single()
         self.pipe = pipe          # parallel.pipeline.PipeStage: this rank runs layers [pipe.lo, pipe.hi)
@@ -660,6 +662,25 @@ class Decoder:
         y = (X * pre.unsqueeze(-1)).sum(1)
         return y, post, cm.transpose(1, 2).contiguous()
 
+    def _hcg_mix(self, name: str, X, inject: bool):
+        """Gated mixer (qwen4exp; ``src/model/qwen4.rs::hc_mix`` in the reference): every stream is RMS-normed with
+        a weight of its own; a low-rank gate ``up(silu(down(xn) / hc))`` gives a sigmoid weight per stream and
+        channel; the block input is the mean of the gated streams. With ``inject`` also the per-stream logits of
+        the weights the block output re-enters the streams with."""
+        cfg, w = self.cfg, self.w
+        T, hc, H = X.shape
+        xn = X * torch.rsqrt(X.pow(2).mean(-1, keepdim=True) + cfg.rms_eps) * w[f"{name}.hcg_norm"].float()
+        flat = xn.reshape(T, hc * H)
+        inj = flat @ w[f"{name}.hcg_inject"].float().t() if inject else None
+        lo = torch.nn.functional.silu((flat @ w[f"{name}.hcg_down"].float().t()) / hc)
+        gate = (lo @ w[f"{name}.hcg_up"].float().t()).view(T, hc, H)
+        return (xn * torch.sigmoid(gate)).sum(1) / hc, inj
+
+    @staticmethod
+    def _hcg_combine(out, X, inj):
+        """Stream h += out * 2 sigmoid(inject[h] / hc)."""
+        return X + out.float().unsqueeze(1) * (2.0 * torch.sigmoid(inj / X.shape[1])).unsqueeze(-1)
+
     @staticmethod
     def _hc_post(out, X, post, comb):
         """New stream d = out * post[d] + sum_s X[s] * comb[d, s]."""
@@ -674,10 +695,15 @@ class Decoder:
         x0 = b.embeds if b.embeds is not None else self.embed(b.token_ids)
         dt = x0.dtype
         X = x0.float().unsqueeze(1).expand(-1, hc, -1).contiguous()
+        gated = cfg.hyper_mode == "gated"
         for il in range(cfg.n_layer):
             p, kind = f"l{il}", cfg.layer_kinds[il]
-            y, post, comb = self._hc_pre(f"{p}.hca", X)
-            h, _ = ops.rmsnorm(y.to(dt), w[f"{p}.attn_norm"], cfg.rms_eps, cfg.norm_offset)
+            if gated:
+                y, inj = self._hcg_mix(f"{p}.hca", X, True)
+                h = y.to(dt)
+            else:
+                y, post, comb = self._hc_pre(f"{p}.hca", X)
+                h, _ = ops.rmsnorm(y.to(dt), w[f"{p}.attn_norm"], cfg.rms_eps, cfg.norm_offset)
             if kind in ("attn", "swa", "nope"):
                 a = self._attn(p, il, h, b, kv, cfg.sliding_window if kind == "swa" else 0, rope=kind != "nope")
             elif kind == "gdn":
@@ -690,14 +716,25 @@ class Decoder:
                 a = self._mamba2(p, il, h, b, st)
             else:
                 raise ValueError(kind)
-            X = self._hc_post(pc.full_hidden(a, None), X, post, comb)
-            y, post, comb = self._hc_pre(f"{p}.hcf", X)
-            h, _ = ops.rmsnorm(y.to(dt), w[f"{p}.ffn_norm"], cfg.rms_eps, cfg.norm_offset)
+            a = pc.full_hidden(a, None)
+            if gated:
+                X = self._hcg_combine(a, X, inj)
+                y, inj = self._hcg_mix(f"{p}.hcf", X, True)
+                h = y.to(dt)
+            else:
+                X = self._hc_post(a, X, post, comb)
+                y, post, comb = self._hc_pre(f"{p}.hcf", X)
+                h, _ = ops.rmsnorm(y.to(dt), w[f"{p}.ffn_norm"], cfg.rms_eps, cfg.norm_offset)
             f, _, _ = self._ffn(p, cfg.is_moe_layer(il), h, None)
-            X = self._hc_post(pc.full_hidden(f, None), X, post, comb)
+            f = pc.full_hidden(f, None)
+            X = self._hcg_combine(f, X, inj) if gated else self._hc_post(f, X, post, comb)
         last = X.mean(1).to(dt)
-        rows = last if b.logit_rows is None else last.index_select(0, b.logit_rows)
-        hidden, _ = ops.rmsnorm(rows, w["output_norm"], cfg.rms_eps, cfg.norm_offset)
+        if gated:
+            Xr = X if b.logit_rows is None else X.index_select(0, b.logit_rows)
+            hidden = self._hcg_mix("out_hc", Xr, False)[0].to(dt)         # the last mixer is the output norm
+        else:
+            rows = last if b.logit_rows is None else last.index_select(0, b.logit_rows)
+            hidden, _ = ops.rmsnorm(rows, w["output_norm"], cfg.rms_eps, cfg.norm_offset)
         out = StepOutput(hidden=hidden, last_hidden=last, captures={})
         if want_logits:
             out.logits = self.logits(hidden)

@@ -84,9 +84,15 @@ def layer_weight_shapes(cfg: ModelConfig, il: int, prefix: Optional[str] = None,
     if cfg.hyper_streams > 1:
         hc = cfg.hyper_streams
         for which in ("hca", "hcf"):                    # the mixers in front of the attention and the FFN sublayer
+            if cfg.hyper_mode == "gated":
+                s.update(gated_mixer_shapes(cfg, f"{p}.{which}", inject=True))
+                continue
             s[f"{p}.{which}.hc_f"] = ((2 + hc) * hc, hc * H)
             s[f"{p}.{which}.hc_scale"] = (3,)
             s[f"{p}.{which}.hc_base"] = ((2 + hc) * hc,)
+        if cfg.hyper_mode == "gated":                   # the mixers take the place of the pre-norms
+            s.pop(f"{p}.attn_norm", None)
+            s.pop(f"{p}.ffn_norm", None)
     if moe:
         E, F = cfg.n_expert, cfg.expert_ff
         s[f"{p}.moe.router"] = (E, H)
@@ -107,8 +113,19 @@ def layer_weight_shapes(cfg: ModelConfig, il: int, prefix: Optional[str] = None,
     return s
 
 
+def gated_mixer_shapes(cfg: ModelConfig, name: str, inject: bool) -> Dict[str, Tuple[int, ...]]:
+    hc, H, r = cfg.hyper_streams, cfg.hidden, cfg.hc_rank
+    s = {f"{name}.hcg_norm": (hc, H), f"{name}.hcg_down": (r, hc * H), f"{name}.hcg_up": (hc * H, r)}
+    if inject:
+        s[f"{name}.hcg_inject"] = (hc, hc * H)
+    return s
+
+
 def weight_shapes(cfg: ModelConfig) -> Dict[str, Tuple[int, ...]]:
     s: Dict[str, Tuple[int, ...]] = {"tok_embd": (cfg.vocab, cfg.hidden), "output_norm": (cfg.hidden,)}
+    if cfg.hyper_streams > 1 and cfg.hyper_mode == "gated":
+        s.pop("output_norm")                            # the last mixer is the output norm
+        s.update(gated_mixer_shapes(cfg, "out_hc", inject=False))
     if not cfg.tie_embeddings:
         s["output"] = (cfg.vocab, cfg.hidden)
     for il in range(cfg.n_layer):
@@ -132,7 +149,7 @@ def is_fp32_weight(name: str) -> bool:
     """Norm weights, recurrence constants and conv taps stay float32 on every back-end."""
     leaf = name.rsplit(".", 1)[-1]
     return leaf.endswith("norm") or leaf in ("A", "D", "dt_bias", "conv_w", "conv_b", "router_bias", "hc_f", "hc_scale",
-                                             "hc_base")
+                                             "hc_base", "hcg_norm", "hcg_down", "hcg_up", "hcg_inject")
 
 
 def layer_of(name: str) -> Optional[int]:
@@ -173,7 +190,7 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=torch.float32, seed: in
             t = torch.ones(shp, dtype=torch.float32, device=device)
         elif leaf == "hc_base":
             t = (torch.randn(shp, generator=g) * 0.5).to(device)
-        elif leaf == "hc_f":
+        elif leaf in ("hc_f", "hcg_down", "hcg_up", "hcg_inject"):
             t = (torch.randn(shp, generator=g) * 0.05).to(device)
         elif leaf == "conv_w":
             t = (torch.randn(shp, generator=g) * 0.3).to(device)

@@ -143,3 +143,41 @@ def test_engine_invariants_on_the_tiny_glm_next_model():
     outs = [s.collect().token_ids for s in streams]
     chunked.shutdown()
     assert outs == singles
+
+
+def test_gated_hyper_connections_match_the_serial_definition_and_the_engine_invariants_hold():
+    """qwen4exp's mixer: per-stream RMS norm, low-rank sigmoid gate, mean of the gated streams; the block output
+    re-enters stream h with 2 sigmoid(inject[h] / hc). Then the engine on the tiny model of that family: batched ==
+    single, chunked prefill == one pass, n-gram speculation == plain decoding (recurrent state replayed)."""
+    cfg = PRESETS["tiny-qwen4exp"]()
+    w = random_weights(cfg, "cpu", torch.float32, seed=5, std=0.08)
+    assert "l0.attn_norm" not in w and "output_norm" not in w and "out_hc.hcg_up" in w
+    m = Decoder(cfg, w, None, max_position=300)
+    T, hc, H = 4, cfg.hyper_streams, cfg.hidden
+    X = torch.randn(T, hc, H)
+    y, inj = m._hcg_mix("l1.hcf", X, True)
+    nw, dn, up, ij = (w[f"l1.hcf.hcg_{k}"] for k in ("norm", "down", "up", "inject"))
+    for t in range(T):
+        xn = torch.stack([X[t, s] / torch.sqrt(X[t, s].pow(2).mean() + cfg.rms_eps) * nw[s] for s in range(hc)])
+        flat = xn.reshape(-1)
+        lo = torch.nn.functional.silu((dn @ flat) / hc)
+        gate = (up @ lo).view(hc, H)
+        want = sum(xn[s] * torch.sigmoid(gate[s]) for s in range(hc)) / hc
+        assert torch.allclose(y[t], want, atol=1e-5)
+        assert torch.allclose(inj[t], ij @ flat, atol=1e-5)
+    out = torch.randn(T, H)
+    new = Decoder._hcg_combine(out, X, inj)
+    assert torch.allclose(new[2, 1], X[2, 1] + out[2] * 2 * torch.sigmoid(inj[2, 1] / hc), atol=1e-6)
+    ec = dict(ctx_size=256, max_seqs=4, block_size=16, max_batch_tokens=256)
+    prompts = [list(range(5, 5 + n)) + [7, 8, 9, 7, 8, 9, 7, 8] for n in (33, 18)]
+    one = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(prefill_chunk=256, **ec))
+    singles = [one.generate_text(tokens=p, max_tokens=8, ignore_eos=True).token_ids for p in prompts]
+    one.shutdown()
+    from legion_b200.engine.types import GenerateRequest, SamplingParams
+    for kw in (dict(prefill_chunk=16), dict(prefill_chunk=256, spec="ngram", spec_k=3)):
+        eng = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(**kw, **ec))
+        streams = [eng.generate(GenerateRequest(prompt_tokens=p, sampling=SamplingParams(max_tokens=8, ignore_eos=True)))
+                   for p in prompts]
+        outs = [s.collect().token_ids for s in streams]
+        eng.shutdown()
+        assert outs == singles, kw
