@@ -83,6 +83,7 @@ class ModelConfig:
     n_expert: int = 0
     top_k: int = 0
     expert_ff: int = 0
+    moe_latent: int = 0                # > 0: the routed experts run at this width, between a down and an up projection
     shared_ff: int = 0                 # width of the shared expert (0 = none)
     shared_gate: bool = False          # sigmoid(x . w) gate on the shared expert
     router_mode: str = "softmax"       # softmax | sigmoid
@@ -255,8 +256,20 @@ def tiny_nemotron_h() -> ModelConfig:
                        dense_ff=512, ssm_state=32, ssm_heads=8, ssm_head_dim=32, ssm_groups=1, ssm_conv=4)
 
 
+def tiny_nemotron_h_moe() -> ModelConfig:
+    """The Nemotron-H hybrid with its latent MoE (``src/model/nemotron_h.rs:538-608``): the router reads the normed
+    input, the routed squared-ReLU experts run at ``moe_latent`` between ``lat_down`` and ``lat_up``, the shared
+    expert at full width."""
+    c = tiny_nemotron_h()
+    c.dense_ff, c.first_dense_layers = 512, 1
+    c.n_expert, c.top_k, c.expert_ff, c.shared_ff, c.moe_latent = 8, 2, 128, 128, 128
+    c.router_mode, c.router_bias, c.norm_topk, c.route_scale = "sigmoid", True, True, 2.5
+    return c
+
+
 PRESETS = {
     "tiny-muse": tiny_muse,
+    "tiny-nemotron-h-moe": tiny_nemotron_h_moe,
     "tiny-gemma": tiny_gemma,
     "tiny-nemotron-h": tiny_nemotron_h,
     "tiny-hybrid-moe": tiny_hybrid_moe,

@@ -833,6 +833,19 @@ class Decoder:
             else:
                 w_gu, w_dn = w[f"{p}.moe.gate_up"], w[f"{p}.moe.down"]
             n_ff = w_dn.shape[2]
+            if cfg.moe_latent:
+                # latent MoE: the routed experts run between a down and an up projection; the shared expert (full
+                # width) joins after the up projection. Every piece is linear in the rank-partial sums.
+                xl = ops.linear(x, w[f"{p}.moe.lat_down"])
+                y = pc.moe(xl, ids, wts, w_gu, w_dn, n_ff, cfg.ffn_act, e_lo, None, None, None,
+                           routing=routing if x.is_cuda else None)
+                if hasattr(y, "materialize"):
+                    y = y.materialize()
+                out = ops.linear(y, w[f"{p}.moe.lat_up"])
+                if shared is not None:
+                    sh = shared.float() * (torch.sigmoid(gate.float())[:, None] if gate is not None else 1.0)
+                    out = (out.float() + sh).to(out.dtype)
+                return out, False, None
             if fuse_res and next_norm is not None:
                 out, normed = pc.moe(x, ids, wts, w_gu, w_dn, n_ff, cfg.ffn_act, e_lo, shared, gate, residual,
                                      norm=(next_norm, cfg.rms_eps, cfg.norm_offset), routing=routing)

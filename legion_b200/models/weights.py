@@ -99,8 +99,12 @@ def layer_weight_shapes(cfg: ModelConfig, il: int, prefix: Optional[str] = None,
         if cfg.router_bias:
             s[f"{p}.moe.router_bias"] = (E,)
         gu = 2 * F if cfg.ffn_act != "relu2" else F
-        s[f"{p}.moe.gate_up"] = (E, gu, H)
-        s[f"{p}.moe.down"] = (E, H, F)
+        W = cfg.moe_latent or H                         # width the routed experts run at
+        if cfg.moe_latent:
+            s[f"{p}.moe.lat_down"] = (W, H)
+            s[f"{p}.moe.lat_up"] = (H, W)
+        s[f"{p}.moe.gate_up"] = (E, gu, W)
+        s[f"{p}.moe.down"] = (E, W, F)
         if cfg.shared_ff > 0:
             s[f"{p}.moe.sh_gate_up"] = (2 * cfg.shared_ff if cfg.ffn_act != "relu2" else cfg.shared_ff, H)
             s[f"{p}.moe.sh_down"] = (H, cfg.shared_ff)

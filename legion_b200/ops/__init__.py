@@ -100,13 +100,57 @@ def router(x, w_router, k, mode="softmax", renorm=True, route_scale=1.0, bias=No
     return _sm.Routing(ids, wts, None, xn)
 
 
+def _moe_experts_ungated(x, ids, wts, w_up, w_down, e_lo, shared, shared_gate, residual, norm):
+    """Squared-ReLU experts on a GPU by tensor operations: pairs sorted by expert, one batched product per weight
+    over padded per-expert groups."""
+    T, H = x.shape
+    E = w_up.shape[0]
+    k = ids.shape[1]
+    flat = ids.reshape(-1).long() - e_lo
+    mine = (flat >= 0) & (flat < E)
+    tok = torch.arange(T, device=x.device).repeat_interleave(k)
+    key = torch.where(mine, flat, torch.full_like(flat, E))
+    order = torch.argsort(key, stable=True)
+    counts = torch.bincount(key, minlength=E + 1)[:E]
+    cap = T * k if T * k <= 64 else int(counts.max().item())          # small steps: no host read
+    cap = max(cap, 1)
+    starts = torch.cumsum(counts, 0) - counts
+    pos = torch.arange(cap, device=x.device)[None, :]                 # [1, cap]
+    src = (starts[:, None] + pos).clamp(max=T * k - 1)                # [E, cap] index into the sorted pairs
+    live = pos < counts[:, None]
+    pair = order[src]                                                 # [E, cap] pair index
+    xg = x[tok[pair]] * live[..., None].to(x.dtype)                   # [E, cap, H]
+    h = torch.relu(torch.bmm(xg, w_up.transpose(1, 2)))
+    h = (h * h).to(x.dtype)
+    y = torch.bmm(h, w_down.transpose(1, 2)).float()                  # [E, cap, H]
+    y = y * (wts.reshape(-1)[pair] * live).unsqueeze(-1)
+    out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
+    out.index_add_(0, tok[pair].reshape(-1), y.reshape(-1, H))
+    if shared is not None:
+        s = shared.float()
+        if shared_gate is not None:
+            s = s * torch.sigmoid(shared_gate.float())[:, None]
+        out = out + s
+    if residual is not None:
+        out = out + residual.float()
+    out = out.to(x.dtype)
+    if norm is None:
+        return out
+    return out, rmsnorm(out, norm[0], norm[1], norm[2])[0]
+
+
 def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, act="silu", e_lo=0, shared=None, shared_gate=None,
                 residual=None, out=None, norm=None, routing=None, defer_combine=False):
     """Routed experts (+ optional shared-expert output with sigmoid gate logits, + residual). Returns [T, H];
     with ``norm=(weight, eps, w_offset)`` returns (out, rmsnorm(out)): on the GPU the norm rides on the combine."""
+    if _cuda(x) and act != "silu":
+        if act != "relu2" or not isinstance(w_gate_up, torch.Tensor):
+            raise NotImplementedError("the grouped expert kernels implement SwiGLU experts (and squared-ReLU experts "
+                                      "through tensor operations)")
+        # un-gated squared-ReLU experts (Nemotron-H): no grouped kernel of their own yet; the per-expert products run
+        # as tensor operations over the tokens of each expert, on the device, without a host round trip per expert
+        return _moe_experts_ungated(x, ids, wts, w_gate_up, w_down, e_lo, shared, shared_gate, residual, norm)
     if _cuda(x):
-        if act != "silu":
-            raise NotImplementedError("grouped expert kernel implements SwiGLU experts")
         return _sm.moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, None, shared, shared_gate, residual, out,
                                norm, routing if isinstance(routing, _sm.Routing) else None,
                                defer_combine=defer_combine)

@@ -211,7 +211,10 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff: int, act: str = "silu", e_
         tok, choice = hit.nonzero(as_tuple=True)
         le = e - e_lo
         h = xf[tok] @ w_gate_up[le].float().t()
-        h = (activation(h[:, :n_ff], act) * h[:, n_ff:]).to(x.dtype).float()
+        if h.shape[1] == n_ff:            # un-gated experts (squared ReLU): one up projection
+            h = activation(h, act).to(x.dtype).float()
+        else:
+            h = (activation(h[:, :n_ff], act) * h[:, n_ff:]).to(x.dtype).float()
         y = (h @ w_down[le].float().t()) * wts[tok, choice][:, None]
         out.index_add_(0, tok, y.to(x.dtype).float())
     return out

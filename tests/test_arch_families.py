@@ -1,5 +1,6 @@
-"""Hyper-connections and Kimi delta attention: the vectorised forms against token-serial restatements of the
-reference's definitions, and the engine invariants on a tiny model of that family (CPU, fp32)."""
+"""Architecture families built from optional blocks: hyper-connections (both forms), Kimi delta attention, latent
+MoE with un-gated experts. The vectorised forms against token-serial restatements of the reference's definitions, and
+the engine invariants on tiny models of each family (CPU, fp32)."""
 import math
 
 import torch
@@ -181,3 +182,41 @@ def test_gated_hyper_connections_match_the_serial_definition_and_the_engine_inva
         outs = [s.collect().token_ids for s in streams]
         eng.shutdown()
         assert outs == singles, kw
+
+
+def test_latent_moe_with_ungated_experts():
+    """Nemotron-H's MoE: router on the full-width input, squared-ReLU experts between a down and an up projection,
+    shared expert at full width. The layer against a direct restatement; batched == single, chunked == one pass."""
+    cfg = PRESETS["tiny-nemotron-h-moe"]()
+    w = random_weights(cfg, "cpu", torch.float32, seed=6, std=0.08)
+    assert w["l1.moe.gate_up"].shape == (8, 128, 128) and w["l1.moe.lat_down"].shape == (128, 256)
+    m = Decoder(cfg, w, None, max_position=300)
+    x = torch.randn(5, cfg.hidden) * 0.5
+    out, fused, _ = m._ffn("l1", True, x, None)
+    logits = x @ w["l1.moe.router"].t()
+    sc = torch.sigmoid(logits)
+    top = torch.topk(sc + w["l1.moe.router_bias"], cfg.top_k, dim=-1).indices
+    want = torch.zeros_like(x)
+    xl = x @ w["l1.moe.lat_down"].t()
+    for t in range(5):
+        ws = sc[t, top[t]]
+        ws = ws / ws.sum() * cfg.route_scale
+        acc = torch.zeros(cfg.moe_latent)
+        for e, wt in zip(top[t].tolist(), ws.tolist()):
+            h = torch.relu(w["l1.moe.gate_up"][e] @ xl[t]) ** 2
+            acc += wt * (w["l1.moe.down"][e] @ h)
+        sh = w["l1.moe.sh_down"] @ (torch.relu(w["l1.moe.sh_gate_up"] @ x[t]) ** 2)
+        want[t] = w["l1.moe.lat_up"] @ acc + sh
+    assert not fused and torch.allclose(out, want, atol=2e-4, rtol=1e-3)
+    ec = dict(ctx_size=256, max_seqs=4, block_size=16, max_batch_tokens=256)
+    prompts = [list(range(5, 5 + n)) for n in (37, 20)]
+    one = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(prefill_chunk=256, **ec))
+    singles = [one.generate_text(tokens=p, max_tokens=6, ignore_eos=True).token_ids for p in prompts]
+    one.shutdown()
+    from legion_b200.engine.types import GenerateRequest, SamplingParams
+    eng = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(prefill_chunk=16, **ec))
+    streams = [eng.generate(GenerateRequest(prompt_tokens=p, sampling=SamplingParams(max_tokens=6, ignore_eos=True)))
+               for p in prompts]
+    outs = [s.collect().token_ids for s in streams]
+    eng.shutdown()
+    assert outs == singles

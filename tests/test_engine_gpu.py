@@ -28,10 +28,11 @@ def _cfgs():
                     dense_ff=384, first_dense_layers=1, n_expert=8, top_k=2, expert_ff=128, shared_ff=128,
                     router_mode="sigmoid", router_bias=True, route_scale=2.0),
         PRESETS["tiny-qwen4exp"](),            # hybrid stack with gated hyper-connections in place of residual + pre-norms
+        PRESETS["tiny-nemotron-h-moe"](),      # Mamba-2 + latent MoE with un-gated squared-ReLU experts
     ]
 
 
-@pytest.mark.parametrize("idx", [0, 1, 2, 3, 4, 5, 6])
+@pytest.mark.parametrize("idx", [0, 1, 2, 3, 4, 5, 6, 7])
 @pytest.mark.parametrize("graphs", [False, True])
 def test_gpu_engine_matches_cpu_logits(idx, graphs):
     """Greedy tokens of random tiny models are fragile under bf16; compare the first-step logits of the GPU
