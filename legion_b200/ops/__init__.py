@@ -111,7 +111,7 @@ def _moe_experts_ungated(x, ids, wts, w_up, w_down, e_lo, shared, shared_gate, r
     tok = torch.arange(T, device=x.device).repeat_interleave(k)
     key = torch.where(mine, flat, torch.full_like(flat, E))
     order = torch.argsort(key, stable=True)
-    counts = torch.bincount(key, minlength=E + 1)[:E]
+    counts = torch.zeros(E + 1, dtype=torch.int64, device=x.device).scatter_add_(0, key, torch.ones_like(key))[:E]
     cap = T * k if T * k <= 64 else int(counts.max().item())          # small steps: no host read
     cap = max(cap, 1)
     starts = torch.cumsum(counts, 0) - counts
