@@ -112,7 +112,7 @@ int all_reduce_fused_launch(const CommPeers& peers, long buf_off, int slot_base,
   if (T <= 0) return 0;
   if (H % 8 || peers.world > LB_MAX_RANKS) return 1;
   if (q.codes && (!norm_out || H % 256 || !q.sf || !q.row_gscale || (q.ld % 4))) return 1;
-  const int grid = T < 296 ? T : 296;
+  const int grid = T < 1184 ? T : 1184;     // rows in flight: up to eight CTAs per SM
   all_reduce_fused_kernel<<<grid, 256, 0, s>>>(peers, buf_off, slot_base, seq_ptr, done_ctr, T, H,
                                                static_cast<const __nv_bfloat16*>(residual), ldr,
                                                static_cast<__nv_bfloat16*>(sum_out), lds, norm_w, eps, w_offset,
@@ -339,24 +339,33 @@ __global__ void __launch_bounds__(256) reduce_scatter_kernel(CommPeers peers, lo
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int r = 0; r < (mc_base ? 1 : peers.world); ++r) {
-      uint4 u;
-      if (mc_base) {
-        // NVLink multicast address of the same bytes on every rank: ONE load whose value is the sum over the ranks,
-        // added inside the switch with fp32 accumulation (one crossing per element instead of world - 1)
-        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w)
-                     : "l"(mc_base + buf_off + long(row) * H * 2 + long(v) * 16)
-                     : "memory");
-      } else {
-        u = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(peers.buffer[r]) + buf_off + long(row) * H * 2)[v];
-      }
-      const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+    uint4 ur[LB_MAX_RANKS];
+    const int n_src = mc_base ? 1 : peers.world;
+    if (mc_base) {
+      // NVLink multicast address of the same bytes on every rank: ONE load whose value is the sum over the ranks,
+      // added inside the switch with fp32 accumulation (one crossing per element instead of world - 1)
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(ur[0].x), "=r"(ur[0].y), "=r"(ur[0].z), "=r"(ur[0].w)
+                   : "l"(mc_base + buf_off + long(row) * H * 2 + long(v) * 16)
+                   : "memory");
+    } else {
+      // all ranks' vectors requested before the first is added (summed in rank order all the same)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __bfloat1622float2(u2[j]);
-        acc[2 * j] += f.x;
-        acc[2 * j + 1] += f.y;
+      for (int r = 0; r < LB_MAX_RANKS; ++r)
+        if (r < n_src)
+          ur[r] = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(peers.buffer[r]) + buf_off +
+                                                 long(row) * H * 2)[v];
+    }
+#pragma unroll
+    for (int r = 0; r < LB_MAX_RANKS; ++r) {
+      if (r < n_src) {
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&ur[r]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(u2[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
       }
     }
     if (residual) {
@@ -412,15 +421,28 @@ __global__ void __launch_bounds__(256) all_gather_kernel(CommPeers peers, long s
   if (!entered) { comm_exit(seq_ptr, done_ctr, seq); return; }
   const int nv = H / 8;
   const int per = (T + peers.world - 1) / peers.world;
-  for (long i = long(blockIdx.x) * 256 + threadIdx.x; i < long(T) * nv; i += long(gridDim.x) * 256) {
-    const int row = int(i / nv);
-    const int v = int(i % nv);
-    int owner = row / per;
-    if (owner >= peers.world) owner = peers.world - 1;
-    if (local_only) owner = peers.rank;        // the reduced rows were multicast into every rank's region
-    const uint4 u =
-        reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(peers.buffer[owner]) + src_off + long(row) * H * 2)[v];
-    reinterpret_cast<uint4*>(out + long(row) * ldo)[v] = u;
+  // four vectors per thread and round: their (peer) loads are all in flight before the first store
+  const long total = long(T) * nv, stride = long(gridDim.x) * 256;
+  for (long i0 = long(blockIdx.x) * 256 + threadIdx.x; i0 < total; i0 += 4 * stride) {
+    uint4 u[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const long i = i0 + k * stride;
+      if (i < total) {
+        const int row = int(i / nv);
+        const int v = int(i % nv);
+        int owner = row / per;
+        if (owner >= peers.world) owner = peers.world - 1;
+        if (local_only) owner = peers.rank;        // the reduced rows were multicast into every rank's region
+        u[k] = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(peers.buffer[owner]) + src_off +
+                                              long(row) * H * 2)[v];
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const long i = i0 + k * stride;
+      if (i < total) reinterpret_cast<uint4*>(out + long(i / nv) * ldo)[int(i % nv)] = u[k];
+    }
   }
   comm_exit(seq_ptr, done_ctr, seq);
 }

@@ -50,14 +50,22 @@ __device__ __forceinline__ void reduce_rows_with(const Load& load, int world, in
       float acc[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-      for (int r = 0; r < world; ++r) {
-        const uint4 u = load(r, row, v);
-        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+      // every rank's vector is requested before the first one is added (the sum still runs in rank order): with
+      // the loads issued one after the other a thread waited one NVLink round trip per rank
+      uint4 ur[LB_MAX_RANKS];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = __bfloat1622float2(u2[j]);
-          acc[2 * j] += f.x;
-          acc[2 * j + 1] += f.y;
+      for (int r = 0; r < LB_MAX_RANKS; ++r)
+        if (r < world) ur[r] = load(r, row, v);
+#pragma unroll
+      for (int r = 0; r < LB_MAX_RANKS; ++r) {
+        if (r < world) {
+          const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&ur[r]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(u2[j]);
+            acc[2 * j] += f.x;
+            acc[2 * j + 1] += f.y;
+          }
         }
       }
       if (residual) {
