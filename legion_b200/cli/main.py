@@ -25,13 +25,14 @@ def _add_engine_args(ap: argparse.ArgumentParser):
     g.add_argument("--alias", default=None, help="model id reported by /v1/models")
     g = ap.add_argument_group("engine")
     g.add_argument("--ctx-size", type=int, default=8192)
-    g.add_argument("--max-seqs", type=int, default=16)
+    g.add_argument("--max-seqs", type=int, default=None,
+                   help="sequences in flight (default by device memory: 16 on 70 GB and more, fewer on smaller parts)")
     g.add_argument("--max-batch-tokens", type=int, default=None)
     g.add_argument("--prefill-chunk", type=int, default=None)
     g.add_argument("--kv-cache-tokens", type=lambda v: -1 if v == "auto" else int(v), default=None,
                    help="tokens of KV cache; 'auto' = as many as fit the GPU beside the weights (memory plan); default "
                         "max-seqs x ctx-size")
-    g.add_argument("--gpu-memory-utilization", type=float, default=0.92,
+    g.add_argument("--gpu-memory-utilization", type=float, default=None,
                    help="share of the device's memory the memory plan may fill")
     g.add_argument("--kv-block", type=int, default=None, help="tokens per KV block (64 on GPU, 16 on CPU)")
     g.add_argument("--no-prefix-cache", action="store_true")
@@ -130,11 +131,17 @@ def build_engine_from_args(a, start: bool = True):
     if world > 1 and device.startswith("cuda"):
         device = f"cuda:{local_rank}"
     on_gpu = device.startswith("cuda")
+    from ..hw.defaults import engine_defaults
+    hd = engine_defaults(device)          # sizes the command line left open come from what the device reports
+    logging.getLogger("legion").info("hardware profile %s: chunk %d, page %d, %d sequences", hd.profile,
+                                     a.prefill_chunk or hd.prefill_chunk, a.kv_block or hd.kv_block,
+                                     a.max_seqs or hd.max_seqs)
     ec = EngineConfig(
-        ctx_size=a.ctx_size, max_seqs=a.max_seqs,
-        max_batch_tokens=a.max_batch_tokens or (8192 if on_gpu else 1024),
-        prefill_chunk=a.prefill_chunk or (4096 if on_gpu else 512), block_size=a.kv_block or (64 if on_gpu else 16),
-        kv_cache_tokens=a.kv_cache_tokens, gpu_memory_utilization=getattr(a, "gpu_memory_utilization", 0.92),
+        ctx_size=a.ctx_size, max_seqs=a.max_seqs or hd.max_seqs,
+        max_batch_tokens=a.max_batch_tokens or hd.max_batch_tokens,
+        prefill_chunk=a.prefill_chunk or hd.prefill_chunk, block_size=a.kv_block or hd.kv_block,
+        kv_cache_tokens=a.kv_cache_tokens,
+        gpu_memory_utilization=getattr(a, "gpu_memory_utilization", None) or hd.gpu_memory_utilization or 0.92,
         kv_fit_check=True, prefix_cache=not a.no_prefix_cache,
         prefix_cache_states=a.prefix_cache_states, prefix_cache_interval=a.prefix_cache_interval,
         max_waiting=a.max_waiting, default_max_tokens=a.default_max_tokens, scheduling_policy=a.scheduling_policy,

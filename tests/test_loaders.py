@@ -289,3 +289,15 @@ def test_parallel_read_ahead_gives_the_same_tensors(tmp_path):
     _, part, ck3 = load_hf(d, expert_range=(2, 4), read_threads=2)
     assert part["l0.moe.gate_up"].shape[0] == 2 and torch.equal(part["l0.moe.gate_up"], plain["l0.moe.gate_up"][2:4])
     assert not ck3._ahead or all(".experts." not in k or k.split(".experts.")[1].split(".")[0] in ("2", "3") for k in ck3._ahead)
+
+
+def test_hardware_keyed_engine_defaults():
+    """Sizes the command line leaves open follow what the device reports."""
+    from legion_b200.hw.defaults import engine_defaults
+    cpu = engine_defaults("cpu")
+    assert (cpu.profile, cpu.kv_block, cpu.prefill_chunk, cpu.cuda_graphs) == ("cpu", 16, 512, False)
+    b200 = engine_defaults("cuda:0", total_gib=179.0)
+    assert (b200.profile, b200.prefill_chunk, b200.kv_block, b200.max_batch_tokens) == ("b200", 8192, 64, 8192)
+    assert engine_defaults("cuda", total_gib=79.0).prefill_chunk == 4096
+    small = engine_defaults("cuda", total_gib=23.0)
+    assert small.profile == "small" and small.max_seqs < b200.max_seqs and small.gpu_memory_utilization < 0.9
