@@ -238,6 +238,7 @@ def build_engine_from_args(a, start: bool = True):
 
 def _attach_vision(a, eng, path: str, device) -> None:
     """``--mmproj FILE`` (a ``clip`` mmproj GGUF) or the tower a Hugging Face checkpoint directory ships."""
+    import torch
     from ..vision import VisionRuntime
     mm = getattr(a, "mmproj", None)
     dt = torch.bfloat16 if str(device).startswith("cuda") else torch.float32
