@@ -14,7 +14,7 @@ import torch
 
 from ..config import PRESETS, ModelConfig
 from ..models.weights import Shard, random_weights
-from .tokenizer import BpeTokenizer, ByteTokenizer, Tokenizer
+from .tokenizer import BpeTokenizer, ByteTokenizer, Tokenizer, tokenizer_from_gguf_metadata
 
 
 def load_model(path: str, device="cpu", dtype=None, rank: int = 0, world: int = 1, expert_parallel: bool = False,
@@ -66,7 +66,7 @@ def load_model(path: str, device="cpu", dtype=None, rank: int = 0, world: int = 
         info["gguf_arch"] = md.get("general.architecture")
         if "tokenizer.ggml.tokens" in md and md.get("tokenizer.ggml.model", "gpt2") == "gpt2" \
                 and "tokenizer.ggml.merges" in md:
-            tok = BpeTokenizer.from_gguf_metadata(md)
+            tok = tokenizer_from_gguf_metadata(md)
         else:
             tok = ByteTokenizer(cfg.vocab)
             if md.get("tokenizer.chat_template"):

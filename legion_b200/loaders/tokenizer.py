@@ -253,6 +253,149 @@ class BpeTokenizer(Tokenizer):
                    chat_template=cfg.get("chat_template"), extra_special=added.keys())
 
 
+class SpmTokenizer(Tokenizer):
+    """SentencePiece-style vocabulary as GGUF files of the llama / gemma families carry it (``tokenizer.ggml.model =
+    "llama"``): pieces with scores, spaces written as U+2581, byte tokens ``<0xXX>`` for what no piece covers.
+    Encoding is the score-ordered bigram merge over the text's characters (the pair whose concatenation is the
+    best-scoring piece merges first), as llama.cpp's SPM tokenizer does it; control pieces are matched as text when
+    ``parse_special``.
+
+    Reference counterpart: ``src/tokenizer/spm.rs`` (gemma4 tokenizer)."""
+    SPACE = "\u2581"
+
+    def __init__(self, tokens: Sequence[str], scores: Sequence[float], token_types: Optional[Sequence[int]] = None,
+                 bos_id=None, eos_ids=(), add_bos=True, add_space_prefix=True, chat_template=None):
+        import heapq
+        self._heapq = heapq
+        self.tokens = list(tokens)
+        self.scores = list(scores) if scores else [0.0] * len(self.tokens)
+        self.vocab_size = len(self.tokens)
+        self.vocab = {t: i for i, t in enumerate(self.tokens)}
+        tt = list(token_types) if token_types is not None else [1] * len(self.tokens)
+        self.token_types = tt
+        self.bos_id, self.eos_ids, self.add_bos, self.chat_template = bos_id, tuple(eos_ids), add_bos, chat_template
+        self.add_space_prefix = add_space_prefix
+        self.byte_id = {}
+        for i, t in enumerate(self.tokens):
+            if tt[i] == 6 or (len(t) == 6 and t.startswith("<0x") and t.endswith(">")):
+                try:
+                    self.byte_id[int(t[3:5], 16)] = i
+                except ValueError:
+                    pass
+        self.unk_id = next((i for i, k in enumerate(tt) if k == 2), 0)
+        self.special = {self.tokens[i]: i for i, k in enumerate(tt) if k in (3, 4)}
+        self._special_ids = set(self.special.values())
+        self._sp_re = None
+        if self.special:
+            alts = sorted(self.special, key=len, reverse=True)
+            self._sp_re = _re.compile("|".join(_re.escape(a) for a in alts))
+
+    def _encode_plain(self, text: str) -> List[int]:
+        if not text:
+            return []
+        heapq = self._heapq
+        sym = list(text)
+        n = len(sym)
+        prev = list(range(-1, n - 1))
+        nxt = list(range(1, n + 1))
+        nxt[-1] = -1
+        alive = [True] * n
+        heap = []
+
+        def push(a, b):
+            if a < 0 or b < 0:
+                return
+            piece = sym[a] + sym[b]
+            i = self.vocab.get(piece)
+            if i is not None and self.token_types[i] not in (3,):
+                heapq.heappush(heap, (-self.scores[i], a, b, piece))
+
+        for a in range(n - 1):
+            push(a, a + 1)
+        while heap:
+            _, a, b, piece = heapq.heappop(heap)
+            if not (alive[a] and alive[b]) or nxt[a] != b or sym[a] + sym[b] != piece:
+                continue
+            sym[a] = piece
+            alive[b] = False
+            nxt[a] = nxt[b]
+            if nxt[b] >= 0:
+                prev[nxt[b]] = a
+            push(prev[a], a)
+            push(a, nxt[a])
+        out: List[int] = []
+        i = 0
+        while i >= 0:
+            piece = sym[i]
+            tid = self.vocab.get(piece)
+            if tid is not None:
+                out.append(tid)
+            else:
+                for byte in piece.encode("utf-8"):
+                    out.append(self.byte_id.get(byte, self.unk_id))
+            i = nxt[i]
+        return out
+
+    def encode(self, text, add_special=False, parse_special=True):
+        ids: List[int] = [self.bos_id] if (add_special and self.add_bos and self.bos_id is not None) else []
+        parts = [(False, text)]
+        if parse_special and self._sp_re is not None:
+            parts, pos = [], 0
+            for m in self._sp_re.finditer(text):
+                if m.start() > pos:
+                    parts.append((False, text[pos:m.start()]))
+                parts.append((True, m.group(0)))
+                pos = m.end()
+            if pos < len(text):
+                parts.append((False, text[pos:]))
+        prev_special = True            # text at the start, and text right after a control piece, takes the space prefix
+        for is_sp, chunk in parts:
+            if is_sp:
+                ids.append(self.special[chunk])
+            else:
+                if prev_special and self.add_space_prefix:
+                    chunk = " " + chunk
+                ids.extend(self._encode_plain(chunk.replace(" ", self.SPACE)))
+            prev_special = is_sp
+        return ids
+
+    def token_bytes(self, tid):
+        t = self.tokens[tid]
+        if tid in self._special_ids:
+            return b""
+        if tid in self.byte_id.values() and t.startswith("<0x"):
+            return bytes([int(t[3:5], 16)])
+        return t.replace(self.SPACE, " ").encode("utf-8")
+
+    def decode(self, ids, skip_special=False):
+        out = bytearray()
+        for i in ids:
+            if i in self._special_ids:
+                if not skip_special:
+                    out += self.tokens[i].encode("utf-8")
+                continue
+            out += self.token_bytes(i)
+        s = out.decode("utf-8", "replace")
+        return s[1:] if (self.add_space_prefix and s.startswith(" ")) else s
+
+    @classmethod
+    def from_gguf_metadata(cls, md: dict) -> "SpmTokenizer":
+        eos = [md[k] for k in ("tokenizer.ggml.eos_token_id", "tokenizer.ggml.eot_token_id") if k in md]
+        return cls(md["tokenizer.ggml.tokens"], md.get("tokenizer.ggml.scores", []),
+                   token_types=md.get("tokenizer.ggml.token_type"), bos_id=md.get("tokenizer.ggml.bos_token_id"),
+                   eos_ids=eos, add_bos=bool(md.get("tokenizer.ggml.add_bos_token", True)),
+                   add_space_prefix=bool(md.get("tokenizer.ggml.add_space_prefix", True)),
+                   chat_template=md.get("tokenizer.chat_template"))
+
+
+def tokenizer_from_gguf_metadata(md: dict) -> Tokenizer:
+    """The tokenizer a GGUF file describes: score-merged pieces (``llama``: llama / gemma families) or byte-level BPE
+    with merge ranks (``gpt2``: qwen, deepseek, llama-3)."""
+    if md.get("tokenizer.ggml.model", "gpt2") == "llama":
+        return SpmTokenizer.from_gguf_metadata(md)
+    return BpeTokenizer.from_gguf_metadata(md)
+
+
 DEFAULT_CHATML_TEMPLATE = (
     "{%- if tools %}{{- '<|im_start|>system\\n' }}{%- if messages[0].role == 'system' %}{{- messages[0].content + '\\n\\n' }}{%- endif %}"
     "{{- '# Tools\\n\\nYou may call one or more functions to assist with the user query.\\n\\n<tools>' }}"

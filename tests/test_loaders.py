@@ -301,3 +301,50 @@ def test_hardware_keyed_engine_defaults():
     assert engine_defaults("cuda", total_gib=79.0).prefill_chunk == 4096
     small = engine_defaults("cuda", total_gib=23.0)
     assert small.profile == "small" and small.max_seqs < b200.max_seqs and small.gpu_memory_utilization < 0.9
+
+
+def test_sentencepiece_style_tokenizer_from_gguf_metadata():
+    """Score-ordered merges, U+2581 spaces, byte fallback, control pieces; against the `sentencepiece` package on a
+    model trained here when it is importable, else against hand-checked merges."""
+    from legion_b200.loaders.tokenizer import SpmTokenizer, tokenizer_from_gguf_metadata
+    sp = "\u2581"
+    pieces = ["<unk>", "<s>", "</s>"] + [f"<0x{b:02X}>" for b in range(256)] + [
+        sp, "h", "e", "l", "o", "w", "r", "d", sp + "h", "he", "ll", sp + "he", "llo", sp + "hello", sp + "w", "or", "ld",
+        sp + "wor", sp + "world", "<start_of_turn>"]
+    scores = [0.0] * 259 + [-1.0, -2, -2, -2, -2, -2, -2, -2, -1.5, -1.2, -1.1, -0.9, -0.8, -0.5, -1.4, -1.3, -1.25, -0.7, -0.4,
+                            0.0]
+    types = [2, 3, 3] + [6] * 256 + [1] * 19 + [4]
+    md = {"tokenizer.ggml.model": "llama", "tokenizer.ggml.tokens": pieces, "tokenizer.ggml.scores": scores,
+          "tokenizer.ggml.token_type": types, "tokenizer.ggml.bos_token_id": 1, "tokenizer.ggml.eos_token_id": 2,
+          "tokenizer.ggml.add_bos_token": True}
+    tok = tokenizer_from_gguf_metadata(md)
+    assert isinstance(tok, SpmTokenizer)
+    ids = tok.encode("hello world", add_special=True)
+    assert ids == [1, pieces.index(sp + "hello"), pieces.index(sp + "world")]
+    assert tok.decode(ids, skip_special=True) == "hello world"
+    # a character no piece covers falls back to its UTF-8 bytes; control pieces are matched as text
+    ids = tok.encode("<start_of_turn>h\u00e9", add_special=False)
+    assert ids[0] == pieces.index("<start_of_turn>")
+    assert [pieces[i] for i in ids[1:]] == [sp + "h", "<0xC3>", "<0xA9>"] or [pieces[i] for i in ids[1:]] == [sp, "h", "<0xC3>", "<0xA9>"]
+    assert tok.decode(ids[1:]) == "h\u00e9"
+    assert tok.token_to_id("<start_of_turn>") == pieces.index("<start_of_turn>")
+    try:
+        import sentencepiece as spm
+    except ImportError:
+        return
+    import io
+    text = ("the quick brown fox jumps over the lazy dog. " * 40 + "pack my box with five dozen liquor jugs. " * 40)
+    model = io.BytesIO()
+    spm.SentencePieceTrainer.train(sentence_iterator=iter(text.split(". ")), model_writer=model, vocab_size=340,
+                                   model_type="bpe", byte_fallback=True, character_coverage=1.0, bos_id=1, eos_id=2,
+                                   unk_id=0, minloglevel=2, normalization_rule_name="identity",
+                                   remove_extra_whitespaces=False)
+    ref = spm.SentencePieceProcessor(model_proto=model.getvalue())
+    n = ref.get_piece_size()
+    toks = [ref.id_to_piece(i) for i in range(n)]
+    sc = [ref.get_score(i) for i in range(n)]
+    ty = [2 if ref.is_unknown(i) else 3 if ref.is_control(i) else 6 if ref.is_byte(i) else 1 for i in range(n)]
+    mine = SpmTokenizer(toks, sc, ty, bos_id=1, eos_ids=(2,), add_bos=False)
+    for s in ("the lazy dog jumps", "five quick boxes", "liquor\u00e9 jugs!", "  two  spaces"):
+        assert mine.encode(s) == ref.encode(s), s
+        assert mine.decode(mine.encode(s)) == ref.decode(ref.encode(s)), s
