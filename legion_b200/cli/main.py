@@ -490,6 +490,44 @@ def cmd_tokenize(a):
     return 0
 
 
+def cmd_logits(a):
+    """Reference logits of a prompt (the role of the reference's ``tools/llama-ref`` dumpers): the prompt runs through
+    the model in one pass on the chosen device (``--device cpu`` = the fp32 reference forward), the logits of the
+    asked rows go to an ``.npz`` file, and ``--compare`` prints how far another dump is from this one."""
+    import numpy as np
+    import torch
+    eng = build_engine_from_args(a, start=False)
+    from ..engine.types import GenerateRequest, SamplingParams
+    if a.tokens:
+        req = GenerateRequest(prompt_tokens=[int(t) for t in a.tokens.split(",")], sampling=SamplingParams(max_tokens=1))
+    else:
+        req = GenerateRequest(prompt=a.prompt, sampling=SamplingParams(max_tokens=1))
+    seq = eng.prepare(req)
+    eng.waiting.push(seq)
+    eng._admit()
+    n = len(seq.tokens)
+    b = eng.build_batch([(seq, 0, n)])
+    if a.all_rows:
+        b.logit_rows = None
+    with torch.no_grad():
+        out = eng.model.forward(b, eng.kv, eng.states)
+    logits = out.logits.float().cpu().numpy()
+    top = logits.argmax(-1)
+    if a.out:
+        np.savez(a.out, tokens=np.asarray(seq.tokens, dtype=np.int64), logits=logits)
+    print(json.dumps({"tokens": n, "rows": int(logits.shape[0]), "argmax_last": int(top[-1]),
+                      "max_abs": float(np.abs(logits).max())}))
+    if a.compare:
+        other = np.load(a.compare)
+        if other["logits"].shape != logits.shape or list(other["tokens"]) != list(seq.tokens):
+            print("compare: the other dump is of another prompt or row set", file=sys.stderr)
+            return 1
+        d = np.abs(other["logits"] - logits)
+        agree = float((other["logits"].argmax(-1) == top).mean())
+        print(json.dumps({"max_abs_diff": float(d.max()), "mean_abs_diff": float(d.mean()), "argmax_agreement": agree}))
+    return 0
+
+
 def cmd_ep_place(a):
     from ..parallel.ep_place import place_from_record
     plan = place_from_record(a.record, a.ranks)
@@ -498,7 +536,7 @@ def cmd_ep_place(a):
 
 
 def cmd_completions(a):
-    subs = ["serve", "run", "bench", "chat", "top", "gguf", "st", "info", "tokenize", "ep-place", "completions",
+    subs = ["serve", "run", "bench", "chat", "top", "gguf", "st", "info", "tokenize", "logits", "ep-place", "completions",
             "kernel-bench", "comm-bench"]
     if a.shell == "bash":
         print("complete -W '" + " ".join(subs) + "' legion")
@@ -597,6 +635,14 @@ def make_parser() -> argparse.ArgumentParser:
     s.add_argument("--prompt-len", type=int, default=96)
     s.add_argument("--n-predict", "-n", type=int, default=16)
     s.set_defaults(fn=cmd_determinism)
+    s = sub.add_parser("logits", help="dump (and compare) the logits of a prompt: the reference-logit tool")
+    _add_engine_args(s)
+    s.add_argument("--prompt", "-p", default="")
+    s.add_argument("--tokens", default=None, help="comma-separated token ids instead of --prompt")
+    s.add_argument("--all-rows", action="store_true", help="logits of every prompt position, not only the last")
+    s.add_argument("--out", default=None, help=".npz file to write (tokens, logits)")
+    s.add_argument("--compare", default=None, help=".npz dump to compare with")
+    s.set_defaults(fn=cmd_logits)
     s = sub.add_parser("tokenize", help="tokenise text with a model's tokenizer")
     s.add_argument("--model", "-m", required=True)
     s.add_argument("text")

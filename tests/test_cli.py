@@ -35,3 +35,16 @@ def test_run_with_an_image_and_a_tiny_mmproj(tmp_path, capsys):
 def test_info_and_tokenize(capsys):
     assert main(["tokenize", "--model", "random:tiny-dense", "abc"]) == 0
     assert capsys.readouterr().out.strip()
+
+
+def test_logits_dump_and_compare(tmp_path, capsys):
+    """The reference-logit tool: a dump of every row, then the same prompt compared against it."""
+    out = str(tmp_path / "ref.npz")
+    args = ["logits", "--model", "random:tiny-hybrid-moe", "--device", "cpu", "--tokens", "5,6,7,8,9,10,11", "--all-rows"]
+    assert main(args + ["--out", out]) == 0
+    first = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert first["rows"] == 7 and os.path.exists(out)
+    assert main(args + ["--compare", out]) == 0
+    lines = capsys.readouterr().out.strip().splitlines()
+    cmp = json.loads(lines[-1])
+    assert cmp["max_abs_diff"] == 0.0 and cmp["argmax_agreement"] == 1.0
