@@ -36,6 +36,9 @@ def _add_engine_args(ap: argparse.ArgumentParser):
                    help="share of the device's memory the memory plan may fill")
     g.add_argument("--kv-block", type=int, default=None, help="tokens per KV block (64 on GPU, 16 on CPU)")
     g.add_argument("--no-prefix-cache", action="store_true")
+    g.add_argument("--kv-rings", action="store_true",
+                   help="sliding-window layers keep window + one step of K / V per sequence in a ring of blocks instead "
+                        "of pages for the whole context (turns the prefix cache off)")
     g.add_argument("--prefix-cache-states", type=int, default=8)
     g.add_argument("--prefix-cache-interval", type=int, default=0)
     g.add_argument("--max-waiting", type=int, default=1024)
@@ -142,7 +145,7 @@ def build_engine_from_args(a, start: bool = True):
         prefill_chunk=a.prefill_chunk or hd.prefill_chunk, block_size=a.kv_block or hd.kv_block,
         kv_cache_tokens=a.kv_cache_tokens,
         gpu_memory_utilization=getattr(a, "gpu_memory_utilization", None) or hd.gpu_memory_utilization or 0.92,
-        kv_fit_check=True, prefix_cache=not a.no_prefix_cache,
+        kv_fit_check=True, prefix_cache=not a.no_prefix_cache, kv_rings=getattr(a, "kv_rings", False),
         prefix_cache_states=a.prefix_cache_states, prefix_cache_interval=a.prefix_cache_interval,
         max_waiting=a.max_waiting, default_max_tokens=a.default_max_tokens, scheduling_policy=a.scheduling_policy,
         fair_share=a.fair_share, kv_admission=a.kv_admission, spec=a.spec, spec_k=a.spec_k,

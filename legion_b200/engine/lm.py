@@ -59,6 +59,7 @@ class EngineConfig:
     kv_admission: str = "reserve"               # reserve | on-demand
     nvtx: bool = False                          # NVTX range around every eager step (for external profilers)
     kv_swap_gib: float = 0.0                    # host tier for preempted sequences (0 = recompute instead)
+    kv_rings: bool = False                      # sliding-window layers keep only window + one step of K / V per sequence
     prefix_host_gib: float = 0.0                # host tier of the prefix cache: evicted blocks keep their contents
                                                 # in pinned memory and come back on a later hit (0 = dropped)
     spec: str = "none"                          # none | ngram | suffix | mtp | mtp_ngram | draft | eagle3 | dflash
@@ -162,6 +163,20 @@ class LmEngine(Engine):
             c.prefix_host_gib = 0.0
             if self.hybrid:
                 c.prefix_cache = False        # recurrent snapshots are not owner-aware
+        # sliding-window rings (the reference's ``KvRing``, ``src/model/core/state.rs:38``): a sliding-window layer never
+        # reads keys older than its window, so it keeps a short ring of blocks per sequence slot (window + the longest
+        # step + one block) instead of pages for the whole context; logical block j of such a layer is ring block
+        # j mod ring length. The prefix cache shares blocks of the common pool only, so it is off with rings (a
+        # resumed prompt would find no window history in the rings); preempted sequences are recomputed.
+        self.ring_len = 0
+        if c.kv_rings and "swa" in self.mcfg.layer_kinds and self.mcfg.sliding_window > 0:
+            if self.dp_world > 1 or getattr(model, "pipe", None) is not None:
+                raise ValueError("sliding-window rings are not available with data-parallel attention or pipeline stages")
+            step = max(c.prefill_chunk, c.spec_k + 1 if (c.spec != "none" or drafter is not None) else 1)
+            self.ring_len = (self.mcfg.sliding_window + step + c.block_size - 1) // c.block_size + 1
+            c.prefix_cache = False
+            c.kv_swap_gib = 0.0
+            c.prefix_host_gib = 0.0
         kv_tokens = c.kv_cache_tokens or c.max_seqs * c.ctx_size
         n_blocks = max(4, (kv_tokens + c.block_size - 1) // c.block_size)
         extra = self.mcfg.mtp_layers if c.spec in ("mtp", "mtp_ngram") else 0
@@ -171,7 +186,7 @@ class LmEngine(Engine):
             n_blocks = self._plan_memory(model, dev, extra, owns, n_blocks)
         self.pool = BlockPool(n_blocks, c.block_size)
         self.kv = KvCache(self.mcfg, n_blocks, c.block_size, dev, model.dtype, kv_heads_local=model.n_kv_l,
-                          extra_layers=extra, owns=owns)
+                          extra_layers=extra, owns=owns, ring_blocks=self.ring_len * c.max_seqs)
         n_saved = c.prefix_cache_states if (self.hybrid and c.prefix_cache) else 0
         self.states = (StatePool(self.mcfg, c.max_seqs + n_saved + 1, dev, tp=model.pctx.tp, owns=owns)
                        if self.hybrid else None)
@@ -204,7 +219,7 @@ class LmEngine(Engine):
         self._mask_pool = None
         caches_ok = all(getattr(ec, "graph_safe", False) for ec in model.expert_cache.values())
         if dev.type == "cuda" and c.cuda_graphs and caches_ok and getattr(model, "pipe", None) is None \
-                and self._mamba_graphable() and self._mla_graphable(model, c):
+                and self._mamba_graphable() and self._mla_graphable(model, c) and not self.ring_len:
             from .cuda_graphs import DecodeGraphs
             self._graphs = DecodeGraphs(self)
         self.step_hook: Optional[Callable] = None    # tests observe (batch description) per step
@@ -973,7 +988,23 @@ class LmEngine(Engine):
             max_q_len=max(n for _, _, n in rows), max_ctx=max(ctx), write_state=write_state, cu_q_host=cu)
         if any(s.media is not None and s.phase != "decode" for s, _, _ in rows):
             self._media_inputs(b, rows, tok)
+        if self.ring_len:
+            self._ring_inputs(b, [(s, p0, n) for s, p0, n in rows], width)
         return b
+
+    def _ring_inputs(self, b: StepBatch, rows, width: int) -> None:
+        """KV cells and block table of the sliding-window layers: sequence slot s owns ring blocks
+        [s * ring_len, (s + 1) * ring_len); position p lives in ring block (p // page) mod ring_len."""
+        bs, L = self.cfg.block_size, self.ring_len
+        cells: List[int] = []
+        table = torch.zeros(len(rows), width, dtype=torch.int32)
+        ring_of = torch.arange(width, dtype=torch.int32) % L
+        for i, (s, p0, n) in enumerate(rows):
+            base = s.slot * L
+            cells.extend((base + (p // bs) % L) * bs + p % bs for p in range(p0, p0 + n))
+            table[i] = base + ring_of
+        b.slots_ring = torch.tensor(cells, dtype=torch.int64, device=self.device)
+        b.block_table_ring = table.to(self.device)
 
     def build_batch_explicit(self, items, all_logits: bool = False) -> StepBatch:
         """items = [(seq, first position, token list)]: a batch over the sequences' own block tables with
@@ -995,12 +1026,15 @@ class LmEngine(Engine):
             nb = self.pool.blocks_for(p0 + len(toks))
             bt[i, :nb] = torch.tensor(s.table.blocks[:nb], dtype=torch.int32)
         i32 = dict(dtype=torch.int32, device=dev)
-        return StepBatch(token_ids=torch.tensor(tok, **i32), positions=torch.tensor(pos, **i32),
-                         cu_q=torch.tensor(cu, **i32), ctx_lens=torch.tensor(ctx, **i32), block_table=bt.to(dev),
-                         slots=torch.tensor(slots, dtype=torch.int64, device=dev),
-                         state_slots=torch.tensor([s.slot for s, _, _ in items], **i32),
-                         logit_rows=torch.tensor(lrows, dtype=torch.int64, device=dev),
-                         max_q_len=max(len(t) for _, _, t in items), max_ctx=max(ctx), cu_q_host=cu)
+        b = StepBatch(token_ids=torch.tensor(tok, **i32), positions=torch.tensor(pos, **i32),
+                      cu_q=torch.tensor(cu, **i32), ctx_lens=torch.tensor(ctx, **i32), block_table=bt.to(dev),
+                      slots=torch.tensor(slots, dtype=torch.int64, device=dev),
+                      state_slots=torch.tensor([s.slot for s, _, _ in items], **i32),
+                      logit_rows=torch.tensor(lrows, dtype=torch.int64, device=dev),
+                      max_q_len=max(len(t) for _, _, t in items), max_ctx=max(ctx), cu_q_host=cu)
+        if self.ring_len:
+            self._ring_inputs(b, [(s, p0, len(toks)) for s, p0, toks in items], width)
+        return b
 
     def _own_blocks(self, s: Seq):
         """Data-parallel attention: blocks that enter the prefix cache remember which rank holds their contents."""

@@ -52,6 +52,8 @@ class StepBatch:
     replay: Optional[dict] = None                # verify steps: per-layer recurrent inputs kept for commit
     rope_table: Optional[torch.Tensor] = None    # [T, rot] per-token cos | sin rows (multi-section rotary positions of
     rope_rows: Optional[torch.Tensor] = None     #   image tokens); rope_rows = arange(T) indexes it like positions
+    slots_ring: Optional[torch.Tensor] = None    # sliding-window layers with ring storage: their own KV cells [T] and
+    block_table_ring: Optional[torch.Tensor] = None  #   block table (logical block j -> ring block j mod ring length)
     deepstack_rows: Optional[torch.Tensor] = None    # [R] int64 rows of this step that are image tokens, and per early
     deepstack: Optional[List[torch.Tensor]] = None   #   layer the [R, hidden] rows added to the stream after it
 
@@ -72,8 +74,11 @@ class KvCache:
     """Per-layer paged K/V tensors ``[n_blocks, page, kv_heads, dim]`` (MLA layers: one latent row)."""
 
     def __init__(self, cfg: ModelConfig, n_blocks: int, page: int, device, dtype, kv_heads_local: Optional[int] = None,
-                 extra_layers: int = 0, owns=None):
+                 extra_layers: int = 0, owns=None, ring_blocks: int = 0):
+        """``ring_blocks`` > 0: sliding-window layers keep their K / V in a pool of that many blocks of their own
+        (a short ring of blocks per sequence slot, ``engine.lm``) instead of ``n_blocks``."""
         self.page, self.n_blocks = page, n_blocks
+        self.ring_blocks = ring_blocks
         self.k: Dict[int, torch.Tensor] = {}
         self.v: Dict[int, torch.Tensor] = {}
         layers = [il for il in cfg.kv_layers() if owns is None or owns(il)]   # pipeline stage: own layers only
@@ -87,8 +92,9 @@ class KvCache:
                 self.v[il] = self.k[il]
             else:
                 hk = kv_heads_local or cfg.n_kv_head
-                self.k[il] = torch.zeros(n_blocks, page, hk, cfg.head_dim, device=device, dtype=dtype)
-                self.v[il] = torch.zeros(n_blocks, page, hk, cfg.head_dim, device=device, dtype=dtype)
+                nb = ring_blocks if (ring_blocks and kinds[il] == "swa") else n_blocks
+                self.k[il] = torch.zeros(nb, page, hk, cfg.head_dim, device=device, dtype=dtype)
+                self.v[il] = torch.zeros(nb, page, hk, cfg.head_dim, device=device, dtype=dtype)
 
     def bytes_per_block(self) -> int:
         n = 0
@@ -367,12 +373,15 @@ class Decoder:
         D = cfg.head_dim
         qkv = ops.linear(x, w[f"{p}.attn.qkv"])
         cos_sin, positions = (self.cos_sin, b.positions) if b.rope_table is None else (b.rope_table, b.rope_rows)
+        slots, table = b.slots, b.block_table
+        if window > 0 and b.slots_ring is not None:
+            slots, table = b.slots_ring, b.block_table_ring      # this layer's K / V live in the sequence's ring
         q, gate = ops.qk_norm_rope_append(qkv, self.n_head_l, self.n_kv_l, D, w.get(f"{p}.attn.q_norm"),
                                           w.get(f"{p}.attn.k_norm"), cfg.rms_eps, cfg.norm_offset, cos_sin,
-                                          cfg.rope_dim if rope else 0, positions, b.slots, kv.k[il], kv.v[il],
+                                          cfg.rope_dim if rope else 0, positions, slots, kv.k[il], kv.v[il],
                                           cfg.gated_attn)
         scale = cfg.attn_scale or D ** -0.5
-        o = ops.paged_attention(q, kv.k[il], kv.v[il], b.block_table, b.ctx_lens, b.cu_q, b.max_q_len, scale,
+        o = ops.paged_attention(q, kv.k[il], kv.v[il], table, b.ctx_lens, b.cu_q, b.max_q_len, scale,
                                 window=window, decode_splits=b.decode_splits, max_ctx=b.max_ctx or None)
         if cfg.gated_attn:
             o = ops.apply_output_gate(o, gate, self.n_head_l, D)

@@ -61,7 +61,7 @@ class PipeStage:
         """A step that is one sequence's prompt chunk longer than ``micro_tokens`` becomes several consecutive
         sub-steps over the same block table and state slot; any other step is one unit."""
         from ..models.decoder import StepBatch
-        if b.rope_table is not None or b.deepstack is not None:
+        if b.rope_table is not None or b.deepstack is not None or b.slots_ring is not None:
             return [b]                # image tokens carry per-row inputs of their own: the step stays whole
         T = int(b.token_ids.shape[0]) if b.embeds is None else int(b.embeds.shape[0])
         if (self.decode_groups > 1 and b.max_q_len == 1 and b.embeds is None and T == b.n_seqs and T >= 2 * self.decode_groups

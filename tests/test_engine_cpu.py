@@ -408,3 +408,34 @@ def test_tool_call_parsers_glm_and_gemma4_formats():
     assert json.loads(calls[0]["arguments"]) == {"city": '東京, "x"', "days": 2, "deep": {"on": True, "list": [1, 2.5, None, "a"]}}
     assert run("gemma4", "<|tool_call>call:f{a:}<tool_call|>")[1] == []            # malformed: no call
     assert run("hermes", "<tool_call>{\"name\": \"f\", \"arguments\": {\"a\": 1}}</tool_call>")[1][0]["name"] == "f"
+
+
+def test_sliding_window_rings_equal_full_paging():
+    """Sliding-window layers on a short ring of blocks per sequence (window + one step) give the tokens of full
+    paging: prompts several windows long, chunked prefill through the ring, batched decode, n-gram speculation."""
+    import torch
+    from legion_b200.config import PRESETS
+    from legion_b200.engine.lm import EngineConfig, build_engine
+    from legion_b200.engine.types import GenerateRequest, SamplingParams
+    from legion_b200.models.weights import random_weights
+    cfg = PRESETS["tiny-gemma"]()
+    w = random_weights(cfg, "cpu", torch.float32, seed=11, std=0.08)
+    prompts = [list(range(7, 7 + n)) + [5, 6, 7, 5, 6, 7, 5, 6] for n in (150, 61, 97)]
+    base = dict(ctx_size=512, max_seqs=4, block_size=16, prefill_chunk=32, max_batch_tokens=96, prefix_cache=False)
+
+    def run(**kw):
+        eng = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(**base, **kw))
+        streams = [eng.generate(GenerateRequest(prompt_tokens=p, sampling=SamplingParams(max_tokens=40, ignore_eos=True)))
+                   for p in prompts]
+        outs = [s.collect().token_ids for s in streams]
+        info = (eng.ring_len, eng.kv.k[0].shape[0], eng.kv.k[1].shape[0])
+        eng.shutdown()
+        return outs, info
+
+    full, (l0, n_swa, n_glob) = run()
+    assert l0 == 0 and n_swa == n_glob
+    ring, (l1, r_swa, r_glob) = run(kv_rings=True)
+    assert l1 == (48 + 32 + 15) // 16 + 1 and r_swa == l1 * 4 and r_glob == n_glob and r_swa < n_glob
+    assert ring == full
+    spec, _ = run(kv_rings=True, spec="ngram", spec_k=3)
+    assert spec == full
