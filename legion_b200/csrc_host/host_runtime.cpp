@@ -376,7 +376,39 @@ class BpeMerger {
     return out;
   }
 
+  // Pre-tokens as raw UTF-8 bytes (the pieces the pre-tokeniser's pattern cut): the byte-to-unicode mapping and the
+  // merges of every piece, ids concatenated. Runs without the interpreter lock, so the chunks of a long prompt encode
+  // on several threads at once (the reference's parallel pre-tokenisation, src/tokenizer/parallel.rs).
+  std::vector<int> encode_pieces(const std::vector<std::string>& pieces) const {
+    static const std::vector<std::string> table = byte_table();
+    std::vector<int> out;
+    std::string word;
+    for (const auto& p : pieces) {
+      word.clear();
+      for (unsigned char c : p) word += table[c];
+      auto ids = encode_word(word);
+      out.insert(out.end(), ids.begin(), ids.end());
+    }
+    return out;
+  }
+
  private:
+  // GPT-2's byte-to-unicode table: printable bytes stand for themselves, the others for code points from 256 up
+  static std::vector<std::string> byte_table() {
+    std::vector<int> cp(256, -1);
+    auto keep = [&](int lo, int hi) { for (int b = lo; b <= hi; ++b) cp[b] = b; };
+    keep(33, 126); keep(161, 172); keep(174, 255);
+    int n = 0;
+    for (int b = 0; b < 256; ++b)
+      if (cp[b] < 0) cp[b] = 256 + n++;
+    std::vector<std::string> t(256);
+    for (int b = 0; b < 256; ++b) {
+      const int c = cp[b];
+      if (c < 0x80) t[b] = std::string(1, char(c));
+      else t[b] = std::string{char(0xC0 | (c >> 6)), char(0x80 | (c & 0x3F))};
+    }
+    return t;
+  }
   static std::string key(const std::string& a, const std::string& b) {
     std::string k;
     k.reserve(a.size() + b.size() + 1);
@@ -423,7 +455,14 @@ PYBIND11_MODULE(_host, m) {
   py::class_<BpeMerger>(m, "BpeMerger")
       .def(py::init<const std::vector<std::string>&, const std::vector<std::pair<std::string, std::string>>&>())
       .def("encode_word", &BpeMerger::encode_word)
-      .def("encode_words", &BpeMerger::encode_words);
+      .def("encode_words", &BpeMerger::encode_words)
+      .def("encode_pieces", [](const BpeMerger& m, const std::vector<py::bytes>& pieces) {
+        std::vector<std::string> raw;
+        raw.reserve(pieces.size());
+        for (const auto& b : pieces) raw.emplace_back(std::string(b));
+        py::gil_scoped_release release;
+        return m.encode_pieces(raw);
+      });
   m.def("table_slots", &table_slots);
   m.def("pack_decode", &pack_decode);
 }

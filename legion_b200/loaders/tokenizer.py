@@ -177,11 +177,34 @@ class BpeTokenizer(Tokenizer):
             self._cache[word] = ids
         return ids
 
+    PARALLEL_CHARS = 32768          # texts from this length on encode their pre-tokens on several threads
+    PARALLEL_THREADS = 8
+
     def _encode_plain(self, text: str) -> List[int]:
+        if (len(text) >= self.PARALLEL_CHARS and self._native is not None and hasattr(self._native, "encode_pieces")):
+            return self._encode_parallel(text)
         out: List[int] = []
         for m in self.pat.finditer(text):
             word = "".join(self._b2u[b] for b in m.group(0).encode("utf-8"))
             out.extend(self._bpe(word))
+        return out
+
+    def _encode_parallel(self, text: str) -> List[int]:
+        """Long prompts: the pre-tokeniser's pattern cuts the text once, then contiguous runs of the pieces are mapped
+        and merged by the native runtime on several threads (it runs without the interpreter lock); the runs' ids are
+        joined in order, so the result is that of the serial loop."""
+        from concurrent.futures import ThreadPoolExecutor
+        pieces = [m.group(0).encode("utf-8") for m in self.pat.finditer(text)]
+        n = max(1, min(self.PARALLEL_THREADS, os.cpu_count() or 1, len(pieces) // 1024 or 1))
+        per = (len(pieces) + n - 1) // n
+        runs = [pieces[i:i + per] for i in range(0, len(pieces), per)]
+        if len(runs) == 1:
+            return list(self._native.encode_pieces(runs[0]))
+        with ThreadPoolExecutor(len(runs)) as ex:
+            parts = list(ex.map(self._native.encode_pieces, runs))
+        out: List[int] = []
+        for p in parts:
+            out.extend(p)
         return out
 
     def encode(self, text, add_special=False, parse_special=True):

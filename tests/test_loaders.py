@@ -348,3 +348,42 @@ def test_sentencepiece_style_tokenizer_from_gguf_metadata():
     for s in ("the lazy dog jumps", "five quick boxes", "liquor\u00e9 jugs!", "  two  spaces"):
         assert mine.encode(s) == ref.encode(s), s
         assert mine.decode(mine.encode(s)) == ref.decode(ref.encode(s)), s
+
+
+def test_long_prompts_encode_their_pretokens_in_parallel():
+    """Texts past ``PARALLEL_CHARS`` cut their pre-tokens once and encode contiguous runs of them on several threads
+    in the native runtime: same ids as the serial loop, special tokens in between included."""
+    import collections
+    import random
+    from legion_b200.loaders.tokenizer import BpeTokenizer, _byte_to_unicode
+    b2u = _byte_to_unicode()
+    words = ["the", "quick", "brown", "fox", "jumps", "over", "lazy", "dog", "tokenizer", "h\u00e9llo", "\u00dcn\u00efcode"]
+    corp = [[b2u[b] for b in (" " + w).encode()] for w in words]
+    toks, merges = [b2u[b] for b in range(256)], []
+    for _ in range(100):
+        cnt = collections.Counter((a, b) for w in corp for a, b in zip(w, w[1:]))
+        if not cnt:
+            break
+        (a, b), _n = cnt.most_common(1)[0]
+        merges.append(a + " " + b)
+        toks.append(a + b)
+        for w in corp:
+            i = 0
+            while i + 1 < len(w):
+                if w[i] == a and w[i + 1] == b:
+                    w[i:i + 2] = [a + b]
+                else:
+                    i += 1
+    toks.append("<|sep|>")
+    tok = BpeTokenizer(toks, merges, pre="gpt2", extra_special=["<|sep|>"])
+    if tok._native is None or not hasattr(tok._native, "encode_pieces"):
+        import pytest
+        pytest.skip("native host runtime not built")
+    rng = random.Random(0)
+    text = " ".join(rng.choice(words) + rng.choice(["", ",", ".", "\n", "  ", "123", "<|sep|>"]) for _ in range(9000))
+    assert len(text) > tok.PARALLEL_CHARS
+    par = tok.encode(text)
+    tok.PARALLEL_CHARS = 1 << 60
+    tok._cache.clear()
+    assert tok.encode(text) == par
+    assert tok.decode(par) == text
