@@ -189,3 +189,69 @@ def test_mmproj_round_trip(tmp_path):
     a = tower.encode(pre.patches, pre.grid)
     b = VisionTower(cfg, want).encode(pre.patches, pre.grid)
     assert torch.allclose(a.rows, b.rows) and torch.allclose(a.deepstack[0], b.deepstack[0])
+
+
+def test_images_over_http_openai_and_anthropic_shapes():
+    """An image part in a chat request reaches the tower through the HTTP surface (data: URL for the OpenAI shape,
+    base64 source for the Anthropic shape); a server whose model has no tower answers 400."""
+    import base64
+    from fastapi.testclient import TestClient
+    from legion_b200.server.app import ServerConfig, create_app
+    eng, rt = _engine(True, (0,))
+    c = TestClient(create_app(eng, ServerConfig()))
+    b64 = base64.b64encode(png(48, 32)).decode()
+    r = c.post("/v1/chat/completions", json={"max_tokens": 5, "messages": [{"role": "user", "content": [
+        {"type": "text", "text": "what is this?"}, {"type": "image_url", "image_url": {"url": "data:image/png;base64," + b64}}]}]})
+    assert r.status_code == 200, r.text
+    j = r.json()
+    assert j["usage"]["prompt_tokens"] > 24 and j["usage"]["completion_tokens"] == 5 and rt.encoded == 1
+    r = c.post("/v1/messages", json={"model": "m", "max_tokens": 4, "messages": [{"role": "user", "content": [
+        {"type": "image", "source": {"type": "base64", "media_type": "image/png", "data": b64}},
+        {"type": "text", "text": "and this?"}]}]})
+    assert r.status_code == 200, r.text
+    assert rt.encoded == 1 and rt.cache.hits >= 1               # the same image: rows from the cache
+    r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": [
+        {"type": "image_url", "image_url": {"url": "data:image/png;base64,AAAA"}}]}]})
+    assert r.status_code == 400
+    eng.shutdown()
+    from legion_b200.config import ModelConfig
+    plain = build_engine(ModelConfig(arch="qwen3", n_layer=1, hidden=64, vocab=512, n_head=4, n_kv_head=2, head_dim=64,
+                                     dense_ff=128), engine_cfg=EngineConfig(ctx_size=256, max_seqs=2, block_size=16))
+    c2 = TestClient(create_app(plain, ServerConfig()))
+    r = c2.post("/v1/chat/completions", json={"max_tokens": 2, "messages": [{"role": "user", "content": [
+        {"type": "image_url", "image_url": {"url": "data:image/png;base64," + b64}}]}]})
+    plain.shutdown()
+    assert r.status_code == 400 and "vision" in r.text
+
+
+def test_tower_from_a_hugging_face_checkpoint_directory(tmp_path):
+    """``model.visual.*`` tensors and ``vision_config`` of a checkpoint directory -> the same tower."""
+    import json as _json
+    from legion_b200.loaders.safetensors_io import save_file
+    from legion_b200.loaders.vision import hf_names, load_vision_hf
+    cfg = VisionConfig(depth=2, hidden=32, n_head=2, intermediate=48, out_hidden=24, patch_size=4, num_pos=16,
+                       deepstack_layers=(0,))
+    w = random_vision_weights(cfg, seed=9)
+    tensors = {}
+    for flat, name in hf_names(cfg).items():
+        t = w[flat]
+        if flat == "patch.w":
+            t = t.reshape(cfg.hidden, 3, cfg.temporal_patch_size, cfg.patch_size, cfg.patch_size)
+        tensors[name] = t.contiguous()
+    tensors["model.language_model.embed_tokens.weight"] = torch.zeros(4, 24)
+    save_file(tensors, str(tmp_path / "model.safetensors"))
+    (tmp_path / "config.json").write_text(_json.dumps({
+        "text_config": {"hidden_size": 24},
+        "vision_config": {"depth": 2, "hidden_size": 32, "num_heads": 2, "intermediate_size": 48, "out_hidden_size": 24,
+                          "patch_size": 4, "temporal_patch_size": 2, "spatial_merge_size": 2,
+                          "num_position_embeddings": 16, "deepstack_visual_indexes": [0], "hidden_act": "gelu_pytorch_tanh"}}))
+    (tmp_path / "preprocessor_config.json").write_text(_json.dumps({
+        "image_mean": [0.4, 0.5, 0.6], "image_std": [0.2, 0.3, 0.4], "size": {"shortest_edge": 256, "longest_edge": 4096}}))
+    tower, hp = load_vision_hf(str(tmp_path))
+    assert tower.cfg.deepstack_layers == (0,) and tower.cfg.out_hidden == 24 and hp.image_mean == (0.4, 0.5, 0.6)
+    assert hp.image_min_pixels == 256 and hp.image_max_pixels == 4096
+    assert all(torch.allclose(tower.w[k], w[k]) for k in w)
+    pre = preprocess(decode_image(png(40, 24)), hp)
+    assert torch.allclose(tower.encode(pre.patches, pre.grid).rows, VisionTower(cfg, w).encode(pre.patches, pre.grid).rows)
+    (tmp_path / "config.json").write_text(_json.dumps({"hidden_size": 24}))
+    assert load_vision_hf(str(tmp_path)) is None
