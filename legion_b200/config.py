@@ -92,6 +92,22 @@ class ModelConfig:
     route_scale: float = 1.0
     n_group: int = 1
     topk_group: int = 1
+    # Gemma-4 layer form (``sandwich_norm``): every sublayer between a pre and a post RMS norm, embedding scaled by
+    # sqrt(hidden), sliding-window and global layers with head sizes / kv-head counts / rotary bases of their own,
+    # values RMS-normed without a weight, unscaled attention, optional: global layers that use their keys as values,
+    # trailing layers that read an earlier layer's KV, a per-layer output scale, per-layer token embeddings, and in MoE
+    # layers the dense FFN beside the routed experts (router on the normed residual scaled by 1 / sqrt(hidden))
+    sandwich_norm: bool = False
+    embed_scale: float = 1.0
+    swa_head_dim: int = 0              # 0 = head_dim
+    swa_kv_heads: int = 0              # 0 = n_kv_head
+    rope_theta_swa: float = 0.0        # 0 = rope_theta
+    rope_freq_factors: Optional[list] = None      # global layers: per-frequency divisors of the rotary frequencies
+    v_norm: bool = False
+    global_k_as_v: bool = False
+    kv_shared_layers: int = 0
+    layer_out_scale: bool = False
+    ple_dim: int = 0                   # width of the per-layer token embeddings (0 = none)
     # multi-token prediction
     mtp_layers: int = 0
     # weights
@@ -125,7 +141,30 @@ class ModelConfig:
         """(n_kv_heads, k_dim, v_dim) stored per token for layer il."""
         if self.layer_kinds[il] == "mla":
             return 1, self.kv_lora + self.qk_rope_dim, 0
-        return self.n_kv_head, self.head_dim, self.head_dim
+        d, n_kv = self.attn_dims(il)
+        return n_kv, d, d
+
+    def attn_dims(self, il: int):
+        """(head size, kv heads) of attention layer il: sliding-window layers may have their own."""
+        if self.layer_kinds[il] == "swa":
+            return self.swa_head_dim or self.head_dim, self.swa_kv_heads or self.n_kv_head
+        return self.head_dim, self.n_kv_head
+
+    def owns_kv(self, il: int) -> bool:
+        """False for the trailing layers that read another layer's KV cache (``kv_shared_layers``)."""
+        return il < self.n_layer - self.kv_shared_layers
+
+    def kv_source(self, il: int) -> int:
+        """The layer whose KV cache layer il reads: itself, or the last layer of its kind before the shared ones."""
+        if self.owns_kv(il):
+            return il
+        for j in range(self.n_layer - self.kv_shared_layers - 1, -1, -1):
+            if self.layer_kinds[j] == self.layer_kinds[il]:
+                return j
+        raise ValueError(f"layer {il} shares a KV cache but no earlier layer of its kind owns one")
+
+    def has_v_proj(self, il: int) -> bool:
+        return not (self.global_k_as_v and self.layer_kinds[il] != "swa")
 
     def gdn_conv_channels(self) -> int:
         return 2 * self.gdn_k_heads * self.gdn_k_dim + self.gdn_v_heads * self.gdn_v_dim
@@ -267,8 +306,24 @@ def tiny_nemotron_h_moe() -> ModelConfig:
     return c
 
 
+def tiny_gemma4() -> ModelConfig:
+    """Gemma 4 in miniature (``src/model/gemma4.rs:1-30``): sandwich norms, scaled embedding, sliding-window layers
+    with 64-wide heads and 2 kv heads next to global layers with 128-wide heads, 1 kv head, keys used as values and
+    rotary frequency factors, value norm, unscaled attention, the last two layers reading earlier layers' KV, a
+    per-layer output scale, per-layer token embeddings, and MoE layers whose dense GELU FFN runs beside 8 routed GELU
+    experts."""
+    return ModelConfig(arch="gemma4", n_layer=6, hidden=256, vocab=4096, n_head=4, n_kv_head=1, head_dim=128,
+                       layer_kinds=["swa", "swa", "attn", "swa", "swa", "attn"], sliding_window=48, rope_dim=128,
+                       rope_theta=1e6, rope_freq_factors=[1.0] * 48 + [8.0] * 16, swa_head_dim=64, swa_kv_heads=2,
+                       rope_theta_swa=1e4, ffn_act="gelu_tanh", dense_ff=384, norm_offset=0.0, tie_embeddings=True,
+                       logit_softcap=30.0, attn_scale=1.0, sandwich_norm=True, embed_scale=16.0, v_norm=True,
+                       global_k_as_v=True, kv_shared_layers=2, layer_out_scale=True, ple_dim=32, first_dense_layers=1,
+                       n_expert=8, top_k=2, expert_ff=128, router_mode="softmax", norm_topk=True)
+
+
 PRESETS = {
     "tiny-muse": tiny_muse,
+    "tiny-gemma4": tiny_gemma4,
     "tiny-nemotron-h-moe": tiny_nemotron_h_moe,
     "tiny-gemma": tiny_gemma,
     "tiny-nemotron-h": tiny_nemotron_h,

@@ -22,12 +22,48 @@ from ..models.weights import is_fp32_weight, weight_shapes
 from .gguf import GgufFile, GgufWriter
 
 ARCH_TO_GGUF = {"qwen35moe": "qwen35moe", "qwen35": "qwen35", "qwen3moe": "qwen3moe", "qwen3": "qwen3",
-                "llama": "llama", "deepseek_v3": "deepseek2"}
+                "llama": "llama", "deepseek_v3": "deepseek2", "gemma4": "gemma4"}
 GGUF_TO_ARCH = {v: k for k, v in ARCH_TO_GGUF.items()}
+
+
+def _gemma4_config(md: dict) -> ModelConfig:
+    """Gemma 4 (``gemma4.*`` keys as the reference reads them, ``src/model/gemma4.rs::parse``): per-layer
+    sliding-window pattern and kv-head counts, head sizes and rotary bases per layer kind, shared KV layers,
+    per-layer embedding width, soft cap."""
+    g = lambda k, d=None: md.get(f"gemma4.{k}", d)        # noqa: E731
+    n_layer = int(g("block_count"))
+    swa = [bool(v) for v in g("attention.sliding_window_pattern")][:n_layer]
+
+    def per_layer(key):
+        v = g(key)
+        return [int(x) for x in v][:n_layer] if isinstance(v, (list, tuple)) else [int(v)] * n_layer
+
+    kvh, ff = per_layer("attention.head_count_kv"), per_layer("feed_forward_length")
+    kv_swa = {kvh[i] for i in range(n_layer) if swa[i]} or {1}
+    kv_full = {kvh[i] for i in range(n_layer) if not swa[i]} or {1}
+    if len(kv_swa) > 1 or len(kv_full) > 1 or len(set(ff)) > 1:
+        raise ValueError("gemma4: kv-head counts must be uniform per layer kind and the FFN width uniform")
+    hidden, head_dim = int(g("embedding_length")), int(g("attention.key_length"))
+    n_expert = int(g("expert_count", 0))
+    return ModelConfig(
+        arch="gemma4", n_layer=n_layer, hidden=hidden, n_head=int(g("attention.head_count")), n_kv_head=kv_full.pop(),
+        head_dim=head_dim, layer_kinds=["swa" if s_ else "attn" for s_ in swa],
+        sliding_window=int(g("attention.sliding_window")), rope_dim=int(g("rope.dimension_count", head_dim)),
+        rope_theta=float(g("rope.freq_base", 10000.0)), swa_head_dim=int(g("attention.key_length_swa")),
+        swa_kv_heads=kv_swa.pop(), rope_theta_swa=float(g("rope.freq_base_swa", g("rope.freq_base", 10000.0))),
+        rms_eps=float(g("attention.layer_norm_rms_epsilon", 1e-6)), max_position=int(g("context_length", 131072)),
+        vocab=len(md.get("tokenizer.ggml.tokens", [])) or 0, ffn_act="gelu_tanh", dense_ff=ff[0], tie_embeddings=True,
+        logit_softcap=float(g("final_logit_softcapping", 0.0)), attn_scale=1.0, sandwich_norm=True,
+        embed_scale=float(hidden) ** 0.5, v_norm=True, kv_shared_layers=int(g("attention.shared_kv_layers", 0)),
+        ple_dim=int(g("embedding_length_per_layer_input", 0)), n_expert=n_expert,
+        top_k=int(g("expert_used_count", 0)), expert_ff=int(g("expert_feed_forward_length", 0)),
+        router_mode="softmax", norm_topk=True)
 
 
 def config_from_gguf(md: dict) -> ModelConfig:
     a = md["general.architecture"]
+    if a == "gemma4":
+        return _gemma4_config(md)
     g = lambda k, d=None: md.get(f"{a}.{k}", d)
     n_layer = int(g("block_count"))
     n_head = int(g("attention.head_count"))
@@ -61,7 +97,124 @@ def config_from_gguf(md: dict) -> ModelConfig:
     return ModelConfig(**kw)
 
 
+def _gemma4_metadata(cfg: ModelConfig) -> Dict[str, object]:
+    a = "gemma4"
+    md = {f"{a}.block_count": cfg.n_layer, f"{a}.embedding_length": cfg.hidden, f"{a}.attention.head_count": cfg.n_head,
+          f"{a}.attention.head_count_kv": [cfg.attn_dims(il)[1] for il in range(cfg.n_layer)],
+          f"{a}.attention.sliding_window_pattern": [k == "swa" for k in cfg.layer_kinds],
+          f"{a}.feed_forward_length": [cfg.dense_ff] * cfg.n_layer,
+          f"{a}.attention.key_length": cfg.head_dim, f"{a}.attention.value_length": cfg.head_dim,
+          f"{a}.attention.key_length_swa": cfg.swa_head_dim or cfg.head_dim,
+          f"{a}.attention.value_length_swa": cfg.swa_head_dim or cfg.head_dim,
+          f"{a}.attention.sliding_window": cfg.sliding_window, f"{a}.attention.shared_kv_layers": cfg.kv_shared_layers,
+          f"{a}.rope.dimension_count": cfg.rope_dim, f"{a}.rope.freq_base": float(cfg.rope_theta),
+          f"{a}.rope.freq_base_swa": float(cfg.rope_theta_swa or cfg.rope_theta),
+          f"{a}.attention.layer_norm_rms_epsilon": float(cfg.rms_eps), f"{a}.context_length": cfg.max_position,
+          f"{a}.final_logit_softcapping": float(cfg.logit_softcap),
+          f"{a}.embedding_length_per_layer_input": cfg.ple_dim, f"{a}.vocab_size": cfg.vocab}
+    if cfg.n_expert:
+        md.update({f"{a}.expert_count": cfg.n_expert, f"{a}.expert_used_count": cfg.top_k,
+                   f"{a}.expert_feed_forward_length": cfg.expert_ff})
+    return md
+
+
+def _gemma4_to_gguf(cfg: ModelConfig, w: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    out = {"token_embd.weight": w["tok_embd"], "output_norm.weight": w["output_norm"]}
+    if cfg.rope_freq_factors:
+        out["rope_freqs.weight"] = torch.tensor(cfg.rope_freq_factors, dtype=torch.float32)
+    if cfg.ple_dim:
+        out["per_layer_token_embd.weight"] = w["ple_embd"]
+        out["per_layer_model_proj.weight"] = w["ple_model_proj"]
+        out["per_layer_proj_norm.weight"] = w["ple_proj_norm"]
+    for il in range(cfg.n_layer):
+        p, b = f"l{il}", f"blk.{il}"
+        D, n_kv = cfg.attn_dims(il)
+        qkv = w[f"{p}.attn.qkv"]
+        nq = cfg.n_head * D
+        out[f"{b}.attn_q.weight"] = qkv[:nq]
+        if cfg.owns_kv(il):
+            out[f"{b}.attn_k.weight"] = qkv[nq:nq + n_kv * D]
+            if cfg.has_v_proj(il):
+                out[f"{b}.attn_v.weight"] = qkv[nq + n_kv * D:]
+            out[f"{b}.attn_k_norm.weight"] = w[f"{p}.attn.k_norm"]
+        out[f"{b}.attn_q_norm.weight"] = w[f"{p}.attn.q_norm"]
+        out[f"{b}.attn_output.weight"] = w[f"{p}.attn.o"]
+        for ours, theirs in (("attn_norm", "attn_norm"), ("attn_post_norm", "post_attention_norm"), ("ffn_norm", "ffn_norm"),
+                             ("ffn_post_norm", "post_ffw_norm"), ("ffn_post1_norm", "post_ffw_norm_1"),
+                             ("ffn_pre2_norm", "pre_ffw_norm_2"), ("ffn_post2_norm", "post_ffw_norm_2"),
+                             ("ple.post_norm", "post_norm")):
+            if f"{p}.{ours}" in w:
+                out[f"{b}.{theirs}.weight"] = w[f"{p}.{ours}"]
+        F = cfg.dense_ff
+        out[f"{b}.ffn_gate.weight"], out[f"{b}.ffn_up.weight"] = w[f"{p}.mlp.gate_up"][:F], w[f"{p}.mlp.gate_up"][F:]
+        out[f"{b}.ffn_down.weight"] = w[f"{p}.mlp.down"]
+        if cfg.is_moe_layer(il):
+            out[f"{b}.ffn_gate_inp.weight"] = w[f"{p}.moe.router"]
+            out[f"{b}.ffn_gate_inp.scale"] = w[f"{p}.moe.router_scale"]
+            out[f"{b}.ffn_gate_up_exps.weight"] = w[f"{p}.moe.gate_up"]
+            out[f"{b}.ffn_down_exps.weight"] = w[f"{p}.moe.down"]
+        if cfg.layer_out_scale:
+            out[f"{b}.layer_output_scale.weight"] = w[f"{p}.out_scale"]
+        if cfg.ple_dim:
+            out[f"{b}.inp_gate.weight"] = w[f"{p}.ple.inp_gate"]
+            out[f"{b}.proj.weight"] = w[f"{p}.ple.proj"]
+    return out
+
+
+def _gemma4_from_gguf(cfg: ModelConfig, get, has) -> Dict[str, torch.Tensor]:
+    w: Dict[str, torch.Tensor] = {"tok_embd": get("token_embd.weight"), "output_norm": get("output_norm.weight")}
+    if has("rope_freqs.weight"):
+        cfg.rope_freq_factors = [float(v) for v in get("rope_freqs.weight").float().reshape(-1).tolist()]
+    if cfg.ple_dim:
+        w["ple_embd"] = get("per_layer_token_embd.weight")
+        w["ple_model_proj"] = get("per_layer_model_proj.weight")
+        w["ple_proj_norm"] = get("per_layer_proj_norm.weight")
+    cfg.global_k_as_v = any(not has(f"blk.{il}.attn_v.weight") for il in range(cfg.n_layer)
+                            if cfg.layer_kinds[il] != "swa" and cfg.owns_kv(il))
+    cfg.layer_out_scale = has("blk.0.layer_output_scale.weight")
+    first_moe = next((il for il in range(cfg.n_layer) if has(f"blk.{il}.ffn_gate_inp.weight")), None)
+    if first_moe is None:
+        cfg.n_expert = cfg.top_k = 0
+    else:
+        cfg.first_dense_layers = first_moe
+    for il in range(cfg.n_layer):
+        p, b = f"l{il}", f"blk.{il}"
+        parts = [get(f"{b}.attn_q.weight")]
+        if cfg.owns_kv(il):
+            parts.append(get(f"{b}.attn_k.weight"))
+            if has(f"{b}.attn_v.weight"):
+                parts.append(get(f"{b}.attn_v.weight"))
+            w[f"{p}.attn.k_norm"] = get(f"{b}.attn_k_norm.weight")
+        w[f"{p}.attn.qkv"] = torch.cat(parts, dim=0)
+        w[f"{p}.attn.q_norm"] = get(f"{b}.attn_q_norm.weight")
+        w[f"{p}.attn.o"] = get(f"{b}.attn_output.weight")
+        for ours, theirs in (("attn_norm", "attn_norm"), ("attn_post_norm", "post_attention_norm"), ("ffn_norm", "ffn_norm"),
+                             ("ffn_post_norm", "post_ffw_norm"), ("ffn_post1_norm", "post_ffw_norm_1"),
+                             ("ffn_pre2_norm", "pre_ffw_norm_2"), ("ffn_post2_norm", "post_ffw_norm_2"),
+                             ("ple.post_norm", "post_norm")):
+            if has(f"{b}.{theirs}.weight"):
+                w[f"{p}.{ours}"] = get(f"{b}.{theirs}.weight")
+        w[f"{p}.mlp.gate_up"] = torch.cat([get(f"{b}.ffn_gate.weight"), get(f"{b}.ffn_up.weight")], dim=0)
+        w[f"{p}.mlp.down"] = get(f"{b}.ffn_down.weight")
+        if has(f"{b}.ffn_gate_inp.weight"):
+            w[f"{p}.moe.router"] = get(f"{b}.ffn_gate_inp.weight")
+            w[f"{p}.moe.router_scale"] = get(f"{b}.ffn_gate_inp.scale")
+            if has(f"{b}.ffn_gate_up_exps.weight"):
+                w[f"{p}.moe.gate_up"] = get(f"{b}.ffn_gate_up_exps.weight")
+            else:
+                w[f"{p}.moe.gate_up"] = torch.cat([get(f"{b}.ffn_gate_exps.weight"), get(f"{b}.ffn_up_exps.weight")], dim=1)
+            w[f"{p}.moe.down"] = get(f"{b}.ffn_down_exps.weight")
+        if has(f"{b}.layer_output_scale.weight"):
+            w[f"{p}.out_scale"] = get(f"{b}.layer_output_scale.weight").reshape(1)
+        if cfg.ple_dim:
+            w[f"{p}.ple.inp_gate"] = get(f"{b}.inp_gate.weight")
+            w[f"{p}.ple.proj"] = get(f"{b}.proj.weight")
+    return w
+
+
 def metadata_from_config(cfg: ModelConfig) -> Dict[str, object]:
+    if cfg.sandwich_norm:
+        return _gemma4_metadata(cfg)
     a = ARCH_TO_GGUF.get(cfg.arch, cfg.arch)
     md = {f"{a}.block_count": cfg.n_layer, f"{a}.embedding_length": cfg.hidden, f"{a}.attention.head_count": cfg.n_head,
           f"{a}.attention.head_count_kv": cfg.n_kv_head, f"{a}.attention.key_length": cfg.head_dim,
@@ -94,6 +247,12 @@ def _interleave_q_gate(q: torch.Tensor, gate: torch.Tensor, n_head: int, d: int)
 
 
 def to_gguf_tensors(cfg: ModelConfig, w: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    if cfg.sandwich_norm:
+        return _gemma4_to_gguf(cfg, w)
+    return _to_gguf_tensors(cfg, w)
+
+
+def _to_gguf_tensors(cfg: ModelConfig, w: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
     """Canonical weights -> GGUF names (splitting fused projections)."""
     out: Dict[str, torch.Tensor] = {"token_embd.weight": w["tok_embd"], "output_norm.weight": w["output_norm"]}
     if "output" in w:
@@ -164,6 +323,8 @@ def to_gguf_tensors(cfg: ModelConfig, w: Dict[str, torch.Tensor]) -> Dict[str, t
 
 def from_gguf_tensors(cfg: ModelConfig, get, has) -> Dict[str, torch.Tensor]:
     """GGUF tensors (``get(name) -> tensor``) -> canonical fused weights."""
+    if cfg.sandwich_norm:
+        return _gemma4_from_gguf(cfg, get, has)
     w: Dict[str, torch.Tensor] = {"tok_embd": get("token_embd.weight"), "output_norm": get("output_norm.weight")}
     if has("output.weight"):
         w["output"] = get("output.weight")

@@ -90,15 +90,31 @@ class KvCache:
             if kinds[il] == "mla":
                 self.k[il] = torch.zeros(n_blocks, page, 1, cfg.kv_lora + cfg.qk_rope_dim, device=device, dtype=dtype)
                 self.v[il] = self.k[il]
+            elif cfg.sandwich_norm and il < cfg.n_layer:
+                if not cfg.owns_kv(il):
+                    continue                          # reads its source layer's cache (mapped below)
+                d, hk = cfg.attn_dims(il)
+                nb = ring_blocks if (ring_blocks and kinds[il] == "swa") else n_blocks
+                self.k[il] = torch.zeros(nb, page, hk, d, device=device, dtype=dtype)
+                self.v[il] = torch.zeros(nb, page, hk, d, device=device, dtype=dtype)
             else:
                 hk = kv_heads_local or cfg.n_kv_head
                 nb = ring_blocks if (ring_blocks and kinds[il] == "swa") else n_blocks
                 self.k[il] = torch.zeros(nb, page, hk, cfg.head_dim, device=device, dtype=dtype)
                 self.v[il] = torch.zeros(nb, page, hk, cfg.head_dim, device=device, dtype=dtype)
+        if cfg.sandwich_norm:
+            for il in layers:
+                if il < cfg.n_layer and not cfg.owns_kv(il):
+                    src = cfg.kv_source(il)
+                    self.k[il], self.v[il] = self.k[src], self.v[src]
 
     def bytes_per_block(self) -> int:
         n = 0
+        seen = set()
         for il, k in self.k.items():
+            if k.data_ptr() in seen:
+                continue                              # a layer that reads another layer's cache
+            seen.add(k.data_ptr())
             n += k[0].numel() * k.element_size()
             if self.v[il] is not k:
                 n += self.v[il][0].numel() * k.element_size()
@@ -284,7 +300,15 @@ class Decoder:
         self.device = dev
         self.dtype = weights["tok_embd"].dtype
         mp = max_position or cfg.max_position
-        self.cos_sin = ops.reference.rope_cos_sin(mp, cfg.rope_dim, cfg.rope_theta, cfg.rope_scaling, device=dev)
+        scaling = cfg.rope_scaling
+        if cfg.rope_freq_factors:
+            scaling = {"type": "factors", "factors": list(cfg.rope_freq_factors)}
+        self.cos_sin = ops.reference.rope_cos_sin(mp, cfg.rope_dim, cfg.rope_theta, scaling, device=dev)
+        self.cos_sin_swa = None
+        if cfg.sandwich_norm and (cfg.rope_theta_swa or cfg.swa_head_dim):
+            # sliding-window layers rotate their (own-sized) heads whole with a base of their own
+            self.cos_sin_swa = ops.reference.rope_cos_sin(mp, cfg.swa_head_dim or cfg.head_dim,
+                                                          cfg.rope_theta_swa or cfg.rope_theta, None, device=dev)
         tp = self.pctx.tp
         self.n_head_l = cfg.n_head // tp
         self.n_kv_l = max(1, cfg.n_kv_head // tp)
@@ -647,6 +671,93 @@ class Decoder:
         o = o * torch.sigmoid(gate.view(T, nh, d))
         return ops.linear(o.reshape(T, c).to(x.dtype), w[f"{p}.kda.out"])
 
+    # ------------------------------------------------------------------ Gemma-4 layer form
+    def _gemma_attn(self, p: str, il: int, h, b: StepBatch, kv: KvCache):
+        """Attention of a Gemma-4 layer (``src/model/gemma4.rs::gemma4_attend_qkv`` in the reference): head size,
+        kv-head count and rotary table by layer kind; q and k RMS-normed with weights, v without; a global layer
+        without a value projection uses its raw keys as values; a layer that owns no cache reads its source layer's;
+        attention is unscaled."""
+        cfg, w = self.cfg, self.w
+        kind = cfg.layer_kinds[il]
+        D, n_kv = cfg.attn_dims(il)
+        nh = cfg.n_head
+        T = h.shape[0]
+        swa = kind == "swa"
+        cos_sin = self.cos_sin_swa if (swa and self.cos_sin_swa is not None) else self.cos_sin
+        rot = D if swa else cfg.rope_dim
+        proj = ops.linear(h, w[f"{p}.attn.qkv"])
+        slots, table = b.slots, b.block_table
+        if swa and b.slots_ring is not None:
+            slots, table = b.slots_ring, b.block_table_ring
+        if cfg.owns_kv(il):
+            q, k = proj[:, :nh * D], proj[:, nh * D:(nh + n_kv) * D]
+            v = proj[:, (nh + n_kv) * D:] if cfg.has_v_proj(il) else k
+            if cfg.v_norm:
+                vf = v.reshape(T, n_kv, D).float()
+                v = (vf * torch.rsqrt(vf.pow(2).mean(-1, keepdim=True) + cfg.rms_eps)).to(h.dtype).reshape(T, n_kv * D)
+            qkv = torch.cat([q, k, v], dim=1).contiguous()
+            qr, _ = ops.qk_norm_rope_append(qkv, nh, n_kv, D, w[f"{p}.attn.q_norm"], w[f"{p}.attn.k_norm"], cfg.rms_eps,
+                                            cfg.norm_offset, cos_sin, rot, b.positions, slots, kv.k[il], kv.v[il], False)
+        else:
+            qn = ops.reference.head_rmsnorm(proj.view(T, nh, D), w[f"{p}.attn.q_norm"], cfg.rms_eps, cfg.norm_offset)
+            qr = ops.reference.apply_rope(qn, cos_sin, b.positions, rot).to(h.dtype)
+        o = ops.paged_attention(qr, kv.k[il], kv.v[il], table, b.ctx_lens, b.cu_q, b.max_q_len, cfg.attn_scale or 1.0,
+                                window=cfg.sliding_window if swa else 0, decode_splits=b.decode_splits,
+                                max_ctx=b.max_ctx or None)
+        return ops.linear(o.reshape(T, -1), w[f"{p}.attn.o"])
+
+    def _forward_gemma(self, b: StepBatch, kv: KvCache, want_logits: bool) -> StepOutput:
+        """Forward pass of the Gemma-4 layer form (``src/model/gemma4.rs::gemma4_layers``): x = embed * scale; per
+        layer attn_out = x + post_norm(attention(norm(x))); ffn = post_norm(dense FFN(norm(attn_out)) [MoE layers:
+        post1(dense) + post2(routed experts over pre2(attn_out), routed by the scaled normed residual)]);
+        x = (attn_out + ffn [+ per-layer embedding term]) * out_scale."""
+        cfg, w, pc = self.cfg, self.w, self.pctx
+        eps, off = cfg.rms_eps, cfg.norm_offset
+        norm = lambda t, name: ops.rmsnorm(t, w[name], eps, off)[0]      # noqa: E731
+        x0 = b.embeds if b.embeds is not None else self.embed(b.token_ids)
+        dt = x0.dtype
+        x = (x0.float() * cfg.embed_scale).to(dt)
+        T = x.shape[0]
+        ple = None
+        if cfg.ple_dim:
+            npl, L = cfg.ple_dim, cfg.n_layer
+            rows = ops.embed(b.token_ids, w["ple_embd"]).float() * npl ** 0.5
+            pr = (ops.linear(x, w["ple_model_proj"]).float() * cfg.hidden ** -0.5).view(T, L, npl)
+            pr = pr * torch.rsqrt(pr.pow(2).mean(-1, keepdim=True) + eps) * (w["ple_proj_norm"].float() + off)
+            ple = ((pr + rows.view(T, L, npl)) * 2 ** -0.5).to(dt)                          # [T, layer, npl]
+        for il in range(cfg.n_layer):
+            p = f"l{il}"
+            a = self._gemma_attn(p, il, norm(x, f"{p}.attn_norm"), b, kv)
+            attn_out = (norm(a, f"{p}.attn_post_norm").float() + x.float()).to(dt)
+            n_ff = w[f"{p}.mlp.down"].shape[1]
+            mlp = ops.linear(ops.gate_up_act(norm(attn_out, f"{p}.ffn_norm"), w[f"{p}.mlp.gate_up"], n_ff, cfg.ffn_act),
+                             w[f"{p}.mlp.down"])
+            if cfg.is_moe_layer(il):
+                mlp = norm(mlp, f"{p}.ffn_post1_norm")
+                af = attn_out.float()
+                r = af * torch.rsqrt(af.pow(2).mean(-1, keepdim=True) + eps) * cfg.hidden ** -0.5
+                r = (r * w[f"{p}.moe.router_scale"].float()).to(dt)
+                routing = ops.router(r, w[f"{p}.moe.router"], cfg.top_k, "softmax", True, 1.0, None, 1, 1)
+                moe_in = norm(attn_out, f"{p}.ffn_pre2_norm")
+                y = ops.moe_experts(moe_in, routing.ids, routing.wts, w[f"{p}.moe.gate_up"], w[f"{p}.moe.down"],
+                                    w[f"{p}.moe.down"].shape[2], cfg.ffn_act)
+                mlp = (mlp.float() + norm(y, f"{p}.ffn_post2_norm").float()).to(dt)
+            cur = (norm(mlp, f"{p}.ffn_post_norm").float() + attn_out.float()).to(dt)
+            if ple is not None:
+                t = torch.nn.functional.gelu(ops.linear(cur, w[f"{p}.ple.inp_gate"]).float(), approximate="tanh")
+                t = ops.linear((t * ple[:, il].float()).to(dt), w[f"{p}.ple.proj"])
+                cur = (cur.float() + norm(t, f"{p}.ple.post_norm").float()).to(dt)
+            if cfg.layer_out_scale:
+                cur = (cur.float() * w[f"{p}.out_scale"].float()).to(dt)
+            x = cur
+        rows = x if b.logit_rows is None else x.index_select(0, b.logit_rows)
+        hidden, _ = ops.rmsnorm(rows, w["output_norm"], eps, off)
+        out = StepOutput(hidden=hidden, last_hidden=x, captures={})
+        if want_logits:
+            out.logits = self.logits(hidden)
+        pc.end_step()
+        return out
+
     # ------------------------------------------------------------------ hyper-connections
     def _hc_pre(self, name: str, X):
         """Mixer in front of a sublayer (``ops.rs::cpu_hc_pre`` in the reference). X [T, hc, H] float32 streams ->
@@ -986,6 +1097,8 @@ class Decoder:
             return self._forward_pipe(b, kv, st, want_logits)
         if self.cfg.hyper_streams > 1:
             return self._forward_hc(b, kv, st, want_logits)
+        if self.cfg.sandwich_norm:
+            return self._forward_gemma(b, kv, want_logits)
         cfg, w, pc = self.cfg, self.w, self.pctx
         x = b.embeds if b.embeds is not None else self.embed(b.token_ids)
         resid = None

@@ -24,6 +24,8 @@ def layer_weight_shapes(cfg: ModelConfig, il: int, prefix: Optional[str] = None,
     moe = cfg.is_moe_layer(il) if moe is None else moe
     H = cfg.hidden
     s: Dict[str, Tuple[int, ...]] = {f"{p}.attn_norm": (H,), f"{p}.ffn_norm": (H,)}
+    if cfg.sandwich_norm and kind in ("attn", "swa") and prefix is None:
+        return gemma_layer_shapes(cfg, il, s)
     if kind in ("attn", "swa", "nope"):
         D = cfg.head_dim
         qw = cfg.n_head * D * (2 if cfg.gated_attn else 1)
@@ -117,6 +119,41 @@ def layer_weight_shapes(cfg: ModelConfig, il: int, prefix: Optional[str] = None,
     return s
 
 
+def gemma_layer_shapes(cfg: ModelConfig, il: int, s: Dict[str, Tuple[int, ...]]) -> Dict[str, Tuple[int, ...]]:
+    """Gemma-4 layer: q (+ k (+ v)) rows of this layer's head size, post norms, optional routed experts beside the
+    dense FFN, output scale, per-layer embedding gate / projection."""
+    p, H = f"l{il}", cfg.hidden
+    D, n_kv = cfg.attn_dims(il)
+    rows = cfg.n_head * D
+    if cfg.owns_kv(il):
+        rows += n_kv * D * (2 if cfg.has_v_proj(il) else 1)
+        s[f"{p}.attn.k_norm"] = (D,)
+    s[f"{p}.attn.qkv"] = (rows, H)
+    s[f"{p}.attn.q_norm"] = (D,)
+    s[f"{p}.attn.o"] = (H, cfg.n_head * D)
+    s[f"{p}.attn_post_norm"] = (H,)
+    s[f"{p}.ffn_post_norm"] = (H,)
+    F = cfg.dense_ff
+    s[f"{p}.mlp.gate_up"] = (2 * F, H)
+    s[f"{p}.mlp.down"] = (H, F)
+    if cfg.is_moe_layer(il):
+        E, Fe = cfg.n_expert, cfg.expert_ff
+        s[f"{p}.ffn_post1_norm"] = (H,)
+        s[f"{p}.ffn_pre2_norm"] = (H,)
+        s[f"{p}.ffn_post2_norm"] = (H,)
+        s[f"{p}.moe.router"] = (E, H)
+        s[f"{p}.moe.router_scale"] = (H,)
+        s[f"{p}.moe.gate_up"] = (E, 2 * Fe, H)
+        s[f"{p}.moe.down"] = (E, H, Fe)
+    if cfg.layer_out_scale:
+        s[f"{p}.out_scale"] = (1,)
+    if cfg.ple_dim:
+        s[f"{p}.ple.inp_gate"] = (cfg.ple_dim, H)
+        s[f"{p}.ple.proj"] = (H, cfg.ple_dim)
+        s[f"{p}.ple.post_norm"] = (H,)
+    return s
+
+
 def gated_mixer_shapes(cfg: ModelConfig, name: str, inject: bool) -> Dict[str, Tuple[int, ...]]:
     hc, H, r = cfg.hyper_streams, cfg.hidden, cfg.hc_rank
     s = {f"{name}.hcg_norm": (hc, H), f"{name}.hcg_down": (r, hc * H), f"{name}.hcg_up": (hc * H, r)}
@@ -127,6 +164,10 @@ def gated_mixer_shapes(cfg: ModelConfig, name: str, inject: bool) -> Dict[str, T
 
 def weight_shapes(cfg: ModelConfig) -> Dict[str, Tuple[int, ...]]:
     s: Dict[str, Tuple[int, ...]] = {"tok_embd": (cfg.vocab, cfg.hidden), "output_norm": (cfg.hidden,)}
+    if cfg.sandwich_norm and cfg.ple_dim:
+        s["ple_embd"] = (cfg.vocab, cfg.ple_dim * cfg.n_layer)
+        s["ple_model_proj"] = (cfg.ple_dim * cfg.n_layer, cfg.hidden)
+        s["ple_proj_norm"] = (cfg.ple_dim,)
     if cfg.hyper_streams > 1 and cfg.hyper_mode == "gated":
         s.pop("output_norm")                            # the last mixer is the output norm
         s.update(gated_mixer_shapes(cfg, "out_hc", inject=False))
@@ -153,7 +194,8 @@ def is_fp32_weight(name: str) -> bool:
     """Norm weights, recurrence constants and conv taps stay float32 on every back-end."""
     leaf = name.rsplit(".", 1)[-1]
     return leaf.endswith("norm") or leaf in ("A", "D", "dt_bias", "conv_w", "conv_b", "router_bias", "hc_f", "hc_scale",
-                                             "hc_base", "hcg_norm", "hcg_down", "hcg_up", "hcg_inject")
+                                             "hc_base", "hcg_norm", "hcg_down", "hcg_up", "hcg_inject", "router_scale",
+                                             "out_scale")
 
 
 def layer_of(name: str) -> Optional[int]:
@@ -190,8 +232,8 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=torch.float32, seed: in
             t = torch.ones(shp, dtype=torch.float32, device=device)
         elif leaf in ("dt_bias", "conv_b", "router_bias"):
             t = (torch.randn(shp, generator=g) * 0.1).to(device)
-        elif leaf == "hc_scale":
-            t = torch.ones(shp, dtype=torch.float32, device=device)
+        elif leaf in ("hc_scale", "router_scale", "out_scale"):
+            t = torch.ones(shp, dtype=torch.float32, device=device) * (0.9 if leaf == "out_scale" else 1.0)
         elif leaf == "hc_base":
             t = (torch.randn(shp, generator=g) * 0.5).to(device)
         elif leaf in ("hc_f", "hcg_down", "hcg_up", "hcg_inject"):
@@ -225,9 +267,9 @@ class Shard:
         if dp_attention:
             self.kv_rep = 1
             return
-        if world > 1 and ("kda" in cfg.layer_kinds or cfg.hyper_streams > 1):
-            raise NotImplementedError("Kimi-delta-attention layers and hyper-connections run on one rank (their "
-                                      "weights have no tensor-parallel split here)")
+        if world > 1 and ("kda" in cfg.layer_kinds or cfg.hyper_streams > 1 or cfg.sandwich_norm):
+            raise NotImplementedError("Kimi-delta-attention layers, hyper-connections and the Gemma-4 layer form run "
+                                      "on one rank (their weights have no tensor-parallel split here)")
         assert cfg.n_head % world == 0, "query heads must divide by the TP degree"
         self.kv_rep = 1
         if cfg.n_kv_head % world != 0:

@@ -100,9 +100,9 @@ def router(x, w_router, k, mode="softmax", renorm=True, route_scale=1.0, bias=No
     return _sm.Routing(ids, wts, None, xn)
 
 
-def _moe_experts_ungated(x, ids, wts, w_up, w_down, e_lo, shared, shared_gate, residual, norm):
-    """Squared-ReLU experts on a GPU by tensor operations: pairs sorted by expert, one batched product per weight
-    over padded per-expert groups."""
+def _moe_experts_ungated(x, ids, wts, w_up, w_down, e_lo, shared, shared_gate, residual, norm, act="relu2", n_ff=None):
+    """Experts the grouped kernels do not cover (un-gated squared ReLU, GELU-gated) on a GPU by tensor operations:
+    pairs sorted by expert, one batched product per weight over padded per-expert groups."""
     T, H = x.shape
     E = w_up.shape[0]
     k = ids.shape[1]
@@ -120,8 +120,11 @@ def _moe_experts_ungated(x, ids, wts, w_up, w_down, e_lo, shared, shared_gate, r
     live = pos < counts[:, None]
     pair = order[src]                                                 # [E, cap] pair index
     xg = x[tok[pair]] * live[..., None].to(x.dtype)                   # [E, cap, H]
-    h = torch.relu(torch.bmm(xg, w_up.transpose(1, 2)))
-    h = (h * h).to(x.dtype)
+    h = torch.bmm(xg, w_up.transpose(1, 2))
+    if n_ff is not None and h.shape[-1] == 2 * n_ff:       # gated: [gate | up]
+        h = (_ref.activation(h[..., :n_ff].float(), act) * h[..., n_ff:].float()).to(x.dtype)
+    else:
+        h = _ref.activation(h.float(), act).to(x.dtype)
     y = torch.bmm(h, w_down.transpose(1, 2)).float()                  # [E, cap, H]
     y = y * (wts.reshape(-1)[pair] * live).unsqueeze(-1)
     out = torch.zeros(T, H, dtype=torch.float32, device=x.device)
@@ -144,12 +147,13 @@ def moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, act="silu", e_lo=0, shared
     """Routed experts (+ optional shared-expert output with sigmoid gate logits, + residual). Returns [T, H];
     with ``norm=(weight, eps, w_offset)`` returns (out, rmsnorm(out)): on the GPU the norm rides on the combine."""
     if _cuda(x) and act != "silu":
-        if act != "relu2" or not isinstance(w_gate_up, torch.Tensor):
-            raise NotImplementedError("the grouped expert kernels implement SwiGLU experts (and squared-ReLU experts "
-                                      "through tensor operations)")
-        # un-gated squared-ReLU experts (Nemotron-H): no grouped kernel of their own yet; the per-expert products run
-        # as tensor operations over the tokens of each expert, on the device, without a host round trip per expert
-        return _moe_experts_ungated(x, ids, wts, w_gate_up, w_down, e_lo, shared, shared_gate, residual, norm)
+        if act not in ("relu2", "gelu_tanh") or not isinstance(w_gate_up, torch.Tensor):
+            raise NotImplementedError("the grouped expert kernels implement SwiGLU experts (squared-ReLU and GELU "
+                                      "experts run through tensor operations)")
+        # un-gated squared-ReLU experts (Nemotron-H) and GELU-gated experts (Gemma 4): no grouped kernel of their own
+        # yet; the per-expert products run as tensor operations over the tokens of each expert, on the device,
+        # without a host round trip per expert
+        return _moe_experts_ungated(x, ids, wts, w_gate_up, w_down, e_lo, shared, shared_gate, residual, norm, act, n_ff)
     if _cuda(x):
         return _sm.moe_experts(x, ids, wts, w_gate_up, w_down, n_ff, e_lo, None, shared, shared_gate, residual, out,
                                norm, routing if isinstance(routing, _sm.Routing) else None,

@@ -61,6 +61,8 @@ def rope_cos_sin(max_pos: int, rot: int, theta: float, scaling: Optional[dict] =
         factor = float(scaling.get("factor", 1.0))
         if kind == "linear":
             inv_freq = inv_freq / factor
+        elif kind == "factors":           # per-frequency divisors (a checkpoint's ``rope_freqs`` tensor)
+            inv_freq = inv_freq / torch.tensor(scaling["factors"], dtype=torch.float64, device=device)
         elif kind == "llama3":
             low = float(scaling.get("low_freq_factor", 1.0))
             high = float(scaling.get("high_freq_factor", 4.0))

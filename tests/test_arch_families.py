@@ -220,3 +220,140 @@ def test_latent_moe_with_ungated_experts():
     outs = [s.collect().token_ids for s in streams]
     eng.shutdown()
     assert outs == singles
+
+
+def test_gemma4_layer_form_against_a_plain_restatement():
+    """The Gemma-4 forward (sandwich norms, scaled embedding, per-kind head sizes / kv heads / rotary tables, value
+    norm, keys as values on global layers, shared KV layers, dense FFN beside routed GELU experts, per-layer
+    embeddings, output scale, soft cap) against a cache-free restatement in plain tensor operations; then the engine
+    invariants (batched == single, chunked prefill == one pass, prefix-cache resume) on the same model."""
+    import torch.nn.functional as F
+    cfg = PRESETS["tiny-gemma4"]()
+    w = random_weights(cfg, "cpu", torch.float32, seed=8, std=0.06)
+    w = {k: (v + 0.1 * torch.randn_like(v) if k.endswith("norm") else v) for k, v in w.items()}
+    toks = list(range(11, 11 + 70))              # longer than the 48-token window
+    T, H, L, npl = len(toks), cfg.hidden, cfg.n_layer, cfg.ple_dim
+    eps = cfg.rms_eps
+
+    def rms(t, wt=None):
+        y = t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps)
+        return y if wt is None else y * wt
+
+    def rope(t, theta, rot, factors=None):
+        half = rot // 2
+        inv = 1.0 / (theta ** (torch.arange(half, dtype=torch.float64) / half))
+        if factors is not None:
+            inv = inv / torch.tensor(factors, dtype=torch.float64)
+        ang = torch.arange(T, dtype=torch.float64)[:, None] * inv[None]
+        c, s_ = ang.cos().float()[:, None, :], ang.sin().float()[:, None, :]
+        a, b = t[..., :half], t[..., half:rot]
+        return torch.cat([a * c - b * s_, b * c + a * s_, t[..., rot:]], -1)
+
+    ids = torch.tensor(toks)
+    x = w["tok_embd"][ids] * cfg.embed_scale
+    rows = w["ple_embd"][ids] * npl ** 0.5
+    pr = ((x @ w["ple_model_proj"].t()) * H ** -0.5).view(T, L, npl)
+    ple = (rms(pr, w["ple_proj_norm"]) + rows.view(T, L, npl)) * 2 ** -0.5
+    kv_of = {}
+    causal = torch.tril(torch.ones(T, T, dtype=torch.bool))
+    for il in range(L):
+        p = f"l{il}"
+        swa = cfg.layer_kinds[il] == "swa"
+        D, n_kv = cfg.attn_dims(il)
+        nh = cfg.n_head
+        h = rms(x, w[f"{p}.attn_norm"])
+        proj = h @ w[f"{p}.attn.qkv"].t()
+        q = rms(proj[:, :nh * D].view(T, nh, D), w[f"{p}.attn.q_norm"])
+        theta, rot, fac = (cfg.rope_theta_swa, D, None) if swa else (cfg.rope_theta, cfg.rope_dim, cfg.rope_freq_factors)
+        q = rope(q, theta, rot, fac)
+        if cfg.owns_kv(il):
+            kraw = proj[:, nh * D:(nh + n_kv) * D].view(T, n_kv, D)
+            vraw = proj[:, (nh + n_kv) * D:].view(T, n_kv, D) if cfg.has_v_proj(il) else kraw
+            kv_of[il] = (rope(rms(kraw, w[f"{p}.attn.k_norm"]), theta, rot, fac), rms(vraw))
+        k, v = kv_of[cfg.kv_source(il)]
+        rep = nh // n_kv
+        sc = torch.einsum("qhd,khd->hqk", q, k.repeat_interleave(rep, 1))          # unscaled
+        mask = causal.clone()
+        if swa:
+            mask &= ~torch.tril(torch.ones(T, T, dtype=torch.bool), -cfg.sliding_window)
+        o = torch.einsum("hqk,khd->qhd", torch.softmax(sc.masked_fill(~mask[None], float("-inf")), -1),
+                         v.repeat_interleave(rep, 1)).reshape(T, nh * D)
+        attn_out = rms(o @ w[f"{p}.attn.o"].t(), w[f"{p}.attn_post_norm"]) + x
+        hh = rms(attn_out, w[f"{p}.ffn_norm"]) @ w[f"{p}.mlp.gate_up"].t()
+        Fd = cfg.dense_ff
+        mlp = (F.gelu(hh[:, :Fd], approximate="tanh") * hh[:, Fd:]) @ w[f"{p}.mlp.down"].t()
+        if cfg.is_moe_layer(il):
+            mlp = rms(mlp, w[f"{p}.ffn_post1_norm"])
+            r = rms(attn_out) * H ** -0.5 * w[f"{p}.moe.router_scale"]
+            probs = torch.softmax(r @ w[f"{p}.moe.router"].t(), -1)
+            tw, ti = torch.topk(probs, cfg.top_k, -1)
+            tw = tw / tw.sum(-1, keepdim=True)
+            moe_in = rms(attn_out, w[f"{p}.ffn_pre2_norm"])
+            y = torch.zeros(T, H)
+            Fe = cfg.expert_ff
+            for t in range(T):
+                for e, wt in zip(ti[t].tolist(), tw[t].tolist()):
+                    g = w[f"{p}.moe.gate_up"][e] @ moe_in[t]
+                    y[t] += wt * (w[f"{p}.moe.down"][e] @ (F.gelu(g[:Fe], approximate="tanh") * g[Fe:]))
+            mlp = mlp + rms(y, w[f"{p}.ffn_post2_norm"])
+        cur = rms(mlp, w[f"{p}.ffn_post_norm"]) + attn_out
+        t_ = F.gelu(cur @ w[f"{p}.ple.inp_gate"].t(), approximate="tanh") * ple[:, il]
+        cur = cur + rms(t_ @ w[f"{p}.ple.proj"].t(), w[f"{p}.ple.post_norm"])
+        x = cur * w[f"{p}.out_scale"]
+    lg = rms(x, w["output_norm"]) @ w["tok_embd"].t()
+    want = torch.tanh(lg / cfg.logit_softcap) * cfg.logit_softcap
+
+    ec = dict(ctx_size=256, max_seqs=4, block_size=16, max_batch_tokens=256)
+    eng = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(prefill_chunk=256, **ec), start=False)
+    assert eng.kv.k[5] is eng.kv.k[2] and eng.kv.k[4] is eng.kv.k[3] and eng.kv.k[0].shape[2:] == (2, 64)
+    assert eng.kv.k[2].shape[2:] == (1, 128)
+    from legion_b200.engine.types import GenerateRequest, SamplingParams
+    seq = eng.prepare(GenerateRequest(prompt_tokens=toks, sampling=SamplingParams(max_tokens=1)))
+    eng.waiting.push(seq)
+    eng._admit()
+    b = eng.build_batch([(seq, 0, T)])
+    b.logit_rows = None
+    got = eng.model.forward(b, eng.kv, eng.states).logits
+    assert torch.allclose(got, want, atol=3e-3, rtol=1e-3), float((got - want).abs().max())
+
+    prompts = [list(range(5, 5 + n)) for n in (75, 23, 60)]
+    one = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(prefill_chunk=256, **ec))
+    singles = [one.generate_text(tokens=p_, max_tokens=6, ignore_eos=True).token_ids for p_ in prompts]
+    again = one.generate_text(tokens=prompts[0], max_tokens=6, ignore_eos=True)
+    one.shutdown()
+    assert again.token_ids == singles[0] and again.usage.cached_tokens >= 16
+    for kw in (dict(prefill_chunk=16), dict(prefill_chunk=32, kv_rings=True, prefix_cache=False)):
+        eng2 = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(**kw, **ec))
+        streams = [eng2.generate(GenerateRequest(prompt_tokens=p_, sampling=SamplingParams(max_tokens=6, ignore_eos=True)))
+                   for p_ in prompts]
+        outs = [s_.collect().token_ids for s_ in streams]
+        ring = eng2.ring_len
+        eng2.shutdown()
+        assert outs == singles, kw
+        assert (ring > 0) == bool(kw.get("kv_rings"))
+
+
+def test_gemma4_gguf_round_trip(tmp_path):
+    """The Gemma-4 layer form written as a ``gemma4`` GGUF (keys and tensor names as the reference reads them) and
+    read back: same configuration, same tensors, same tokens."""
+    from legion_b200.loaders.gguf_map import load_gguf, write_gguf
+    cfg = PRESETS["tiny-gemma4"]()
+    w = random_weights(cfg, "cpu", torch.float32, seed=8, std=0.06)
+    path = str(tmp_path / "gemma4.gguf")
+    write_gguf(path, cfg, w)
+    cfg2, w2, md = load_gguf(path)
+    assert md["general.architecture"] == "gemma4" and md["gemma4.attention.shared_kv_layers"] == 2
+    for f in ("layer_kinds", "kv_shared_layers", "global_k_as_v", "layer_out_scale", "first_dense_layers", "n_expert",
+              "ple_dim", "swa_head_dim", "swa_kv_heads", "n_kv_head", "head_dim", "sliding_window", "logit_softcap",
+              "rope_theta_swa", "sandwich_norm", "v_norm", "embed_scale", "attn_scale"):
+        assert getattr(cfg2, f) == getattr(cfg, f), f
+    assert cfg2.rope_freq_factors == cfg.rope_freq_factors
+    assert set(w2) == set(w) and all(torch.allclose(w[k].float(), w2[k].float()) for k in w)
+    ec = dict(ctx_size=256, max_seqs=2, block_size=16, max_batch_tokens=128)
+    toks = list(range(9, 80))
+    outs = []
+    for c, ww in ((cfg, w), (cfg2, w2)):
+        eng = build_engine(c, weights=dict(ww), engine_cfg=EngineConfig(**ec))
+        outs.append(eng.generate_text(tokens=toks, max_tokens=8, ignore_eos=True).token_ids)
+        eng.shutdown()
+    assert outs[0] == outs[1]
