@@ -38,7 +38,7 @@ def _add_engine_args(ap: argparse.ArgumentParser):
     g.add_argument("--no-prefix-cache", action="store_true")
     g.add_argument("--kv-rings", action="store_true",
                    help="sliding-window layers keep window + one step of K / V per sequence in a ring of blocks instead "
-                        "of pages for the whole context (turns the prefix cache off)")
+                        "of pages for the whole context (prompts then resume from the prefix cache at state snapshots only)")
     g.add_argument("--prefix-cache-states", type=int, default=8)
     g.add_argument("--prefix-cache-interval", type=int, default=0)
     g.add_argument("--max-waiting", type=int, default=1024)

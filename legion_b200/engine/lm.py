@@ -166,15 +166,15 @@ class LmEngine(Engine):
         # sliding-window rings (the reference's ``KvRing``, ``src/model/core/state.rs:38``): a sliding-window layer never
         # reads keys older than its window, so it keeps a short ring of blocks per sequence slot (window + the longest
         # step + one block) instead of pages for the whole context; logical block j of such a layer is ring block
-        # j mod ring length. The prefix cache shares blocks of the common pool only, so it is off with rings (a
-        # resumed prompt would find no window history in the rings); preempted sequences are recomputed.
+        # j mod ring length. The prefix cache shares blocks of the common pool only; the rings' contents travel with
+        # the state snapshots (``StatePool.attach_rings``), so a prompt resumes from the cache only where a snapshot
+        # exists, as for recurrent layers. Preempted sequences are recomputed.
         self.ring_len = 0
         if c.kv_rings and "swa" in self.mcfg.layer_kinds and self.mcfg.sliding_window > 0:
             if self.dp_world > 1 or getattr(model, "pipe", None) is not None:
                 raise ValueError("sliding-window rings are not available with data-parallel attention or pipeline stages")
             step = max(c.prefill_chunk, c.spec_k + 1 if (c.spec != "none" or drafter is not None) else 1)
             self.ring_len = (self.mcfg.sliding_window + step + c.block_size - 1) // c.block_size + 1
-            c.prefix_cache = False
             c.kv_swap_gib = 0.0
             c.prefix_host_gib = 0.0
         kv_tokens = c.kv_cache_tokens or c.max_seqs * c.ctx_size
@@ -185,11 +185,17 @@ class LmEngine(Engine):
         if dev.type == "cuda":
             n_blocks = self._plan_memory(model, dev, extra, owns, n_blocks)
         self.pool = BlockPool(n_blocks, c.block_size)
+        # models whose prompts resume from the prefix cache only at state snapshots: recurrent layers, ring storage
+        self.snap_resume = self.hybrid or bool(self.ring_len)
+        n_saved = c.prefix_cache_states if (self.snap_resume and c.prefix_cache) else 0
         self.kv = KvCache(self.mcfg, n_blocks, c.block_size, dev, model.dtype, kv_heads_local=model.n_kv_l,
-                          extra_layers=extra, owns=owns, ring_blocks=self.ring_len * c.max_seqs)
-        n_saved = c.prefix_cache_states if (self.hybrid and c.prefix_cache) else 0
+                          extra_layers=extra, owns=owns, ring_blocks=self.ring_len * (c.max_seqs + n_saved + 1))
         self.states = (StatePool(self.mcfg, c.max_seqs + n_saved + 1, dev, tp=model.pctx.tp, owns=owns)
-                       if self.hybrid else None)
+                       if self.snap_resume else None)
+        if self.ring_len:
+            self.states.attach_rings(self.kv, self.ring_len,
+                                     [il for il, k in enumerate(self.mcfg.layer_kinds)
+                                      if k == "swa" and (not self.mcfg.sandwich_norm or self.mcfg.owns_kv(il))])
         self._free_slots = list(range(c.max_seqs - 1, -1, -1))
         self._slo = {"decode_ms": 0.0, "ms_per_prompt_token": 0.0}
         self._swap_bytes = 0
@@ -548,7 +554,7 @@ class LmEngine(Engine):
         if self.pool.free >= need:
             return True
         if self.radix is not None:
-            spill = self._spill_prefix_block if (self.cfg.prefix_host_gib > 0 and not self.hybrid) else None
+            spill = self._spill_prefix_block if (self.cfg.prefix_host_gib > 0 and not self.snap_resume) else None
             self.radix.evict(need - self.pool.free, spill)
         if self.pool.free < need and self.saved is not None:
             for s in sorted(self.saved.entries(), key=lambda e: e.tick):
@@ -644,13 +650,13 @@ class LmEngine(Engine):
         handle = None
         if self.radix is not None and limit >= bs and seq.swapped is None:
             blocks, matched, handle = self.radix.match_prefix(prompt, lock=True, max_tokens=limit)
-            if self._host_prefix and not self.hybrid and self._restore_prefix_blocks(prompt, matched, limit, blocks):
+            if self._host_prefix and not self.snap_resume and self._restore_prefix_blocks(prompt, matched, limit, blocks):
                 self.radix.unlock(handle)
                 blocks, matched, handle = self.radix.match_prefix(prompt, lock=True, max_tokens=limit)
         resume = matched
         saved = None
         tail_block = None
-        if self.hybrid:
+        if self.snap_resume:
             resume = 0
             if self.saved is not None and seq.swapped is None:
                 cand = self.saved.find(prompt, limit)

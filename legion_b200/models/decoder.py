@@ -161,6 +161,20 @@ class StatePool:
                 self.ssm[il] = torch.zeros(n_slots, cfg.ssm_heads, cfg.ssm_head_dim, cfg.ssm_state, device=device,
                                            dtype=torch.float32)
 
+    def attach_rings(self, kv: "KvCache", ring_len: int, layers) -> None:
+        """Sliding-window rings are per-slot state too: slot s owns ring blocks [s * ring_len, (s + 1) * ring_len) of
+        the given layers' K / V pools, so a snapshot of a slot carries its window history (the reference's ring
+        checkpoints, ``src/engine/ring_checkpoints.rs``) and a prefix-cache hit can resume from it."""
+        self.ring_len = ring_len
+        self.rings = [(kv.k[il], kv.v[il]) for il in layers]
+
+    def _ring_views(self, slot: int):
+        L = getattr(self, "ring_len", 0)
+        for k, v in getattr(self, "rings", ()):
+            yield k[slot * L:(slot + 1) * L]
+            if v is not k:
+                yield v[slot * L:(slot + 1) * L]
+
     def clear(self, slot: int):
         for t in list(self.conv.values()) + list(self.ssm.values()):
             t[slot].zero_()
@@ -168,9 +182,12 @@ class StatePool:
     def copy(self, src: int, dst: int):
         for t in list(self.conv.values()) + list(self.ssm.values()):
             t[dst].copy_(t[src])
+        for a, b in zip(self._ring_views(src), self._ring_views(dst)):
+            b.copy_(a)
 
     def bytes_per_slot(self) -> int:
-        return sum(t[0].numel() * 4 for t in list(self.conv.values()) + list(self.ssm.values()))
+        n = sum(t[0].numel() * 4 for t in list(self.conv.values()) + list(self.ssm.values()))
+        return n + sum(t.numel() * t.element_size() for t in self._ring_views(0))
 
 
 def fold_shared_expert(w: Dict[str, object], p: str, cfg: ModelConfig) -> bool:

@@ -435,7 +435,21 @@ def test_sliding_window_rings_equal_full_paging():
     full, (l0, n_swa, n_glob) = run()
     assert l0 == 0 and n_swa == n_glob
     ring, (l1, r_swa, r_glob) = run(kv_rings=True)
-    assert l1 == (48 + 32 + 15) // 16 + 1 and r_swa == l1 * 4 and r_glob == n_glob and r_swa < n_glob
+    assert l1 == (48 + 32 + 15) // 16 + 1 and r_swa == l1 * (4 + 1) and r_glob == n_glob and r_swa < n_glob
     assert ring == full
     spec, _ = run(kv_rings=True, spec="ngram", spec_k=3)
     assert spec == full
+    # the rings travel with the state snapshots: a repeated prompt resumes from the prefix cache (its window history
+    # comes back with the snapshot) and continues with the same tokens; an extended prompt resumes at the anchor
+    cached = dict(base, prefix_cache=True)
+    eng = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(**cached, kv_rings=True))
+    first = eng.generate_text(tokens=prompts[0], max_tokens=12, ignore_eos=True)
+    again = eng.generate_text(tokens=prompts[0], max_tokens=12, ignore_eos=True)
+    longer = eng.generate_text(tokens=prompts[0] + first.token_ids[:5] + [9, 9, 9], max_tokens=6, ignore_eos=True)
+    eng.shutdown()
+    ref_eng = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(**base))
+    want_longer = ref_eng.generate_text(tokens=prompts[0] + first.token_ids[:5] + [9, 9, 9], max_tokens=6, ignore_eos=True)
+    ref_eng.shutdown()
+    assert first.token_ids == full[0][:12] and again.token_ids == first.token_ids
+    assert again.usage.cached_tokens >= 64 and longer.usage.cached_tokens >= 64
+    assert longer.token_ids == want_longer.token_ids
