@@ -34,6 +34,13 @@ def config_from_hf(c: dict) -> ModelConfig:
               rope_theta=float(c.get("rope_theta", 10000.0)), rms_eps=float(c.get("rms_norm_eps", 1e-6)),
               tie_embeddings=bool(c.get("tie_word_embeddings", False)),
               max_position=int(c.get("max_position_embeddings", 131072)), rope_scaling=c.get("rope_scaling"))
+    rp = c.get("rope_scaling") or c.get("rope_parameters") or {}
+    if isinstance(rp, dict) and rp.get("mrope_section"):
+        # vision-language checkpoints: rotary frequencies turn with (temporal, row, column) positions
+        kw["mrope_sections"] = tuple(int(v) for v in rp["mrope_section"][:3])
+        kw["mrope_interleaved"] = bool(rp.get("mrope_interleaved", False))
+        if "rope_theta" in rp:
+            kw["rope_theta"] = float(rp["rope_theta"])
     if mt in ("qwen3", "qwen3_moe"):
         kw.update(arch="qwen3moe" if mt == "qwen3_moe" else "qwen3", qk_norm=True)
     elif mt in HYBRID_TYPES:

@@ -387,3 +387,14 @@ def test_long_prompts_encode_their_pretokens_in_parallel():
     tok._cache.clear()
     assert tok.encode(text) == par
     assert tok.decode(par) == text
+
+
+def test_vision_language_config_carries_the_rotary_sections():
+    from legion_b200.loaders.hf_map import config_from_hf
+    c = config_from_hf({"model_type": "qwen3_5_moe", "text_config": {
+        "model_type": "qwen3_5_moe_text", "num_attention_heads": 4, "hidden_size": 256, "num_hidden_layers": 4,
+        "vocab_size": 1000, "num_key_value_heads": 2, "head_dim": 64, "partial_rotary_factor": 1.0,
+        "rope_parameters": {"rope_type": "default", "rope_theta": 5e6, "mrope_section": [11, 11, 10], "mrope_interleaved": True},
+        "num_experts": 8, "num_experts_per_tok": 2, "moe_intermediate_size": 64, "shared_expert_intermediate_size": 64},
+        "vision_config": {"depth": 2}})
+    assert c.mrope_sections == (11, 11, 10) and c.mrope_interleaved and c.rope_theta == 5e6 and c.arch == "qwen35moe"
