@@ -251,7 +251,11 @@ def _attach_vision(a, eng, path: str, device) -> None:
         got = load_mmproj(mm, device, dt)
     elif os.path.isdir(path) and os.path.exists(os.path.join(path, "config.json")) and not getattr(a, "no_mmproj", False):
         from ..loaders.vision import load_vision_hf
-        got = load_vision_hf(path, device, dt)
+        try:
+            got = load_vision_hf(path, device, dt)
+        except Exception as e:      # a checkpoint whose tower cannot be read still serves text
+            logging.getLogger("legion").warning("vision tower of %s not loaded: %s", path, e)
+            return
     if got is None:
         return
     tower, hp = got
