@@ -64,7 +64,9 @@ def _add_engine_args(ap: argparse.ArgumentParser):
                    default="none")
     g.add_argument("--spec-k", type=int, default=4)
     g.add_argument("--spec-max-batch", type=int, default=8)
-    g.add_argument("--spec-draft-model", default=None)
+    g.add_argument("--spec-draft-model", default=None,
+                   help="--spec eagle3: the head's checkpoint directory (config.json + safetensors); --spec draft: the "
+                        "draft model (same vocabulary as the target)")
     g.add_argument("--spec-p-min", type=float, default=0.5)
     g.add_argument("--spec-policy", choices=["fixed", "cost"], default="fixed",
                    help="cost: pick the draft depth per step from the measured acceptance rate and batch size")
@@ -148,7 +150,7 @@ def build_engine_from_args(a, start: bool = True):
         kv_fit_check=True, prefix_cache=not a.no_prefix_cache, kv_rings=getattr(a, "kv_rings", False),
         prefix_cache_states=a.prefix_cache_states, prefix_cache_interval=a.prefix_cache_interval,
         max_waiting=a.max_waiting, default_max_tokens=a.default_max_tokens, scheduling_policy=a.scheduling_policy,
-        fair_share=a.fair_share, kv_admission=a.kv_admission, spec=a.spec, spec_k=a.spec_k,
+        fair_share=a.fair_share, kv_admission=a.kv_admission, spec=a.spec, spec_k=a.spec_k, spec_draft_model=getattr(a, "spec_draft_model", None),
         spec_max_batch=a.spec_max_batch, deterministic=a.deterministic, device=device, seed=a.seed,
         cuda_graphs=not a.no_cuda_graphs, model_name=a.alias or os.path.basename(path.rstrip("/")),
         tool_format=a.tool_format, itl_target_ms=a.itl_target, ttft_target_ms=a.ttft_target,

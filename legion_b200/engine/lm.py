@@ -63,6 +63,7 @@ class EngineConfig:
     prefix_host_gib: float = 0.0                # host tier of the prefix cache: evicted blocks keep their contents
                                                 # in pinned memory and come back on a later hit (0 = dropped)
     spec: str = "none"                          # none | ngram | suffix | mtp | mtp_ngram | draft | eagle3 | dflash
+    spec_draft_model: Optional[str] = None      # eagle3: head checkpoint directory; draft: a model path (same vocabulary)
     spec_k: int = 4
     spec_max_batch: int = 8
     spec_ngram_min: int = 2
@@ -219,7 +220,7 @@ class LmEngine(Engine):
         self.drafter = drafter
         if self.drafter is None and c.spec != "none":
             from ..spec import make_drafter
-            self.drafter = make_drafter(c.spec, self)
+            self.drafter = make_drafter(c.spec, self, **self._drafter_args())
         self.eos_ids = tuple(self.tok.eos_ids)
         self._graphs = None
         self._mask_pool = None
@@ -268,6 +269,20 @@ class LmEngine(Engine):
         if not plan.fits and c.kv_fit_check:
             raise ValueError("the KV pool does not fit this GPU: " + "; ".join(plan.lines()[1:]))
         return n_blocks
+
+    def _drafter_args(self) -> dict:
+        """``spec_draft_model``: the EAGLE-3 head checkpoint, or the draft model, the drafter is built from."""
+        c = self.cfg
+        if not c.spec_draft_model:
+            return {}
+        if c.spec == "eagle3":
+            from ..spec.drafters import Eagle3Head
+            return {"head": Eagle3Head.from_checkpoint(c.spec_draft_model, self.mcfg, self.device, self.model.dtype)}
+        if c.spec == "draft":
+            from ..loaders.model import load_model
+            dcfg, dw, _, _ = load_model(c.spec_draft_model, str(self.device))
+            return {"draft": Decoder(dcfg, dw, None, max_position=c.ctx_size + 8)}
+        return {}
 
     def _mamba_graphable(self) -> bool:
         """Mamba-2 layers decode from CUDA graphs when their head shape runs on the scan kernel (the token loop that

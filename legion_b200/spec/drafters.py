@@ -264,49 +264,174 @@ class DraftModelDrafter(_ModelDrafter):
         self.filled.pop(id(seq), None)
 
 
-class Eagle3Head:
-    """EAGLE-3 style draft head (``src/spec/eagle3/config.rs:22-62``): target hidden states of three layers
-    (low / middle / high) are fused by ``fc`` into one feature g; the single decoder layer attends over
-    ``[norm(embed(token)) ; norm(g)]`` rows (input width 2H) with its own KV; its output feeds the LM head
-    (optionally a reduced draft vocabulary mapped back through ``d2t``) and serves as g when chaining."""
+class Eagle3Config:
+    """An EAGLE-3 checkpoint's ``config.json`` (``src/spec/eagle3/config.rs:22-62`` in the reference): the draft
+    layer's own shape and the flags that move its norms around."""
 
-    def __init__(self, cfg: ModelConfig, device, dtype, seed: int = 1, draft_vocab: int = 0, weights=None):
+    def __init__(self, hidden, n_ff, n_head, n_kv_head, head_dim, vocab, draft_vocab=0, target_hidden=0, n_aux=3,
+                 eps=1e-6, rope_theta=10000.0, rope_scaling=None, max_pos=8192, layer_ids=None, attention_bias=False,
+                 norm_before_residual=False, norm_before_fc=False, fc_norm=False, norm_output=False, logit_scale=1.0):
+        self.hidden, self.n_ff, self.n_head, self.n_kv_head, self.head_dim = hidden, n_ff, n_head, n_kv_head, head_dim
+        self.vocab, self.draft_vocab = vocab, draft_vocab or vocab
+        self.target_hidden, self.n_aux, self.eps = target_hidden or hidden, n_aux, eps
+        self.rope_theta, self.rope_scaling, self.max_pos, self.layer_ids = rope_theta, rope_scaling, max_pos, layer_ids
+        self.attention_bias, self.norm_before_residual = attention_bias, norm_before_residual
+        self.norm_before_fc, self.fc_norm, self.norm_output, self.logit_scale = norm_before_fc, fc_norm, norm_output, logit_scale
+
+    @classmethod
+    def for_target(cls, cfg: ModelConfig, draft_vocab: int = 0) -> "Eagle3Config":
+        return cls(cfg.hidden, cfg.dense_ff or 4 * cfg.hidden, cfg.n_head, cfg.n_kv_head, cfg.head_dim, cfg.vocab,
+                   draft_vocab, eps=cfg.rms_eps, rope_theta=cfg.rope_theta, rope_scaling=cfg.rope_scaling,
+                   max_pos=cfg.max_position)
+
+    @classmethod
+    def parse(cls, c: dict) -> "Eagle3Config":
+        if c.get("num_hidden_layers") not in (None, 1):
+            raise ValueError(f"config.json: an EAGLE-3 head has one decoder layer, not {c['num_hidden_layers']}")
+        if c.get("hidden_act", "silu") != "silu":
+            raise ValueError(f"config.json: hidden_act `{c['hidden_act']}` is not supported")
+        eagle = c.get("eagle_config") or {}
+        if eagle.get("use_aux_hidden_state") is False:
+            raise ValueError("config.json: eagle_config.use_aux_hidden_state = false is not supported")
+        flag = lambda k: bool(c.get(k, eagle.get(k, False)))          # noqa: E731
+        layer_ids = eagle.get("eagle_aux_hidden_state_layer_ids", c.get("eagle_aux_hidden_state_layer_ids"))
+        n_aux = c.get("num_aux_hidden_states") or (len(layer_ids) if layer_ids else 3)
+        hidden, n_head = int(c["hidden_size"]), int(c["num_attention_heads"])
+        rp = c.get("rope_scaling") or c.get("rope_parameters")
+        theta = float((rp or {}).get("rope_theta", c.get("rope_theta", 10000.0)))
+        if rp and rp.get("rope_type", rp.get("type")) in (None, "default"):
+            rp = None
+        return cls(hidden, int(c["intermediate_size"]), n_head, int(c.get("num_key_value_heads") or n_head),
+                   int(c.get("head_dim") or hidden // n_head), int(c["vocab_size"]), int(c.get("draft_vocab_size") or 0),
+                   int(c.get("target_hidden_size") or 0), int(n_aux), float(c.get("rms_norm_eps", 1e-6)), theta, rp,
+                   int(c.get("max_position_embeddings", 8192)), [int(v) for v in layer_ids] if layer_ids else None,
+                   flag("attention_bias"), flag("norm_before_residual"), flag("norm_before_fc"), flag("fc_norm"),
+                   flag("norm_output"), float(c.get("logit_scale", 1.0)))
+
+
+class Eagle3Head:
+    """EAGLE-3 draft head (``src/spec/eagle3/graph.rs:6-16`` in the reference): the target's hidden states of
+    ``n_aux`` layers are fused by ``fc`` into one feature g (under ``norm_before_fc`` / ``fc_norm`` behind one norm
+    over the concatenation / one per state); the single decoder layer attends over ``[input_layernorm(embed(token)) ;
+    hidden_norm(g)]`` rows (input width 2H) with its own KV; h1 = g + o_proj(attention) (the residual is the normed g
+    under ``norm_before_residual``), h2 = h1 + mlp(post_attention_layernorm(h1)); logits = lm_head(norm(h2)) over the
+    draft vocabulary (mapped back through ``d2t``), times ``logit_scale``; h2 (its normed form under ``norm_output``)
+    is g of the next chained step."""
+
+    def __init__(self, cfg: ModelConfig, device, dtype, seed: int = 1, draft_vocab: int = 0, weights=None,
+                 hcfg: Optional[Eagle3Config] = None, d2t=None):
         self.cfg = cfg
-        H, D = cfg.hidden, cfg.head_dim
-        nq, nkv = cfg.n_head, cfg.n_kv_head
-        F = cfg.dense_ff or 4 * H
+        self.hc = hc = hcfg or Eagle3Config.for_target(cfg, draft_vocab)
+        if hc.hidden != cfg.hidden or hc.vocab != cfg.vocab:
+            raise ValueError(f"EAGLE-3 head of width {hc.hidden} / vocabulary {hc.vocab} does not fit a target of width "
+                             f"{cfg.hidden} / vocabulary {cfg.vocab} (it reads the target's token embeddings)")
+        H, D, nq, nkv, F = hc.hidden, hc.head_dim, hc.n_head, hc.n_kv_head, hc.n_ff
         g = torch.Generator().manual_seed(seed)
-        r = lambda *shape: (torch.randn(*shape, generator=g) * 0.02).to(device=device, dtype=dtype)
-        one = lambda n: torch.ones(n, device=device, dtype=torch.float32)
-        self.draft_vocab = draft_vocab or cfg.vocab
+        r = lambda *shape: (torch.randn(*shape, generator=g) * 0.02).to(device=device, dtype=dtype)    # noqa: E731
+        one = lambda n: torch.ones(n, device=device, dtype=torch.float32)                             # noqa: E731
+        self.draft_vocab = hc.draft_vocab
         self.w = weights or {
-            "fc": r(H, 3 * H), "enorm": one(H), "hnorm": one(H), "qkv": r((nq + 2 * nkv) * D, 2 * H), "o": r(H, nq * D),
-            "ffn_norm": one(H), "gate_up": r(2 * F, H), "down": r(H, F), "out_norm": one(H),
-            "lm_head": r(self.draft_vocab, H)}
-        self.d2t = None if self.draft_vocab == cfg.vocab else torch.arange(self.draft_vocab, device=device)
+            "fc": r(H, hc.n_aux * hc.target_hidden), "enorm": one(H), "hnorm": one(H),
+            "qkv": r((nq + 2 * nkv) * D, 2 * H), "o": r(H, nq * D), "ffn_norm": one(H), "gate_up": r(2 * F, H),
+            "down": r(H, F), "out_norm": one(H), "lm_head": r(self.draft_vocab, H)}
+        if d2t is not None:
+            self.d2t = d2t.to(device)
+        else:
+            self.d2t = None if self.draft_vocab == cfg.vocab else torch.arange(self.draft_vocab, device=device)
         self.n_ff = F
+        same_rope = (hc.rope_theta == cfg.rope_theta and hc.rope_scaling == cfg.rope_scaling and D == cfg.rope_dim)
+        self.cos_sin = None if same_rope else ops.reference.rope_cos_sin(max(hc.max_pos, cfg.max_position) + 8, D,
+                                                                         hc.rope_theta, hc.rope_scaling, device=device)
+
+    @classmethod
+    def from_checkpoint(cls, path: str, cfg: ModelConfig, device, dtype) -> "Eagle3Head":
+        """An EAGLE-3 checkpoint directory (``config.json`` + safetensors; decoder layer under ``midlayer.*`` or
+        ``layers.0.*``; ``d2t`` offsets when the draft vocabulary is reduced): ``src/spec/eagle3/weights.rs:100-200``."""
+        import json
+        import os
+        from ..loaders.safetensors_io import Checkpoint
+        with open(os.path.join(path, "config.json")) as f:
+            hc = Eagle3Config.parse(json.load(f))
+        ck = Checkpoint(path)
+        layer = next((p for p in ("midlayer", "layers.0") if ck.has(f"{p}.input_layernorm.weight")), None)
+        if layer is None:
+            raise ValueError("the checkpoint has no decoder layer (`midlayer.*` or `layers.0.*`)")
+
+        def get(name, shape=None, f32=False):
+            if not ck.has(name):
+                raise ValueError(f"the checkpoint has no tensor `{name}`")
+            t = ck.get(name)
+            if shape is not None and tuple(t.shape) != tuple(shape):
+                raise ValueError(f"`{name}` has shape {tuple(t.shape)}, the config needs {tuple(shape)}")
+            return t.to(device=device, dtype=torch.float32 if f32 else dtype)
+
+        H, D, nq, nkv, F = hc.hidden, hc.head_dim, hc.n_head, hc.n_kv_head, hc.n_ff
+        L = lambda n: f"{layer}.{n}.weight"                                                          # noqa: E731
+        w = {"fc": get("fc.weight", (H, hc.n_aux * hc.target_hidden)),
+             "qkv": torch.cat([get(L("self_attn.q_proj"), (nq * D, 2 * H)), get(L("self_attn.k_proj"), (nkv * D, 2 * H)),
+                               get(L("self_attn.v_proj"), (nkv * D, 2 * H))], 0),
+             "o": get(L("self_attn.o_proj"), (H, nq * D)),
+             "gate_up": torch.cat([get(L("mlp.gate_proj"), (F, H)), get(L("mlp.up_proj"), (F, H))], 0),
+             "down": get(L("mlp.down_proj"), (H, F)), "lm_head": get("lm_head.weight", (hc.draft_vocab, H)),
+             "enorm": get(L("input_layernorm"), (H,), True), "hnorm": get(L("hidden_norm"), (H,), True),
+             "ffn_norm": get(L("post_attention_layernorm"), (H,), True), "out_norm": get("norm.weight", (H,), True)}
+        if hc.norm_before_fc:
+            w["input_norm"] = get("input_norm.weight", (hc.n_aux * hc.target_hidden,), True)
+        if hc.fc_norm:
+            for i in range(hc.n_aux):
+                w[f"fc_norm.{i}"] = get(f"fc_norm.{i}.weight", (hc.target_hidden,), True)
+        for ours, theirs in (("bq", "self_attn.q_proj.bias"), ("bk", "self_attn.k_proj.bias"),
+                             ("bv", "self_attn.v_proj.bias"), ("bo", "self_attn.o_proj.bias"),
+                             ("q_norm", "self_attn.q_norm.weight"), ("k_norm", "self_attn.k_norm.weight")):
+            if ck.has(f"{layer}.{theirs}"):
+                w[ours] = get(f"{layer}.{theirs}", None, True)
+        if "bq" in w:
+            w["b_qkv"] = torch.cat([w.pop("bq"), w.pop("bk"), w.pop("bv")], 0)
+        d2t = None
+        if hc.draft_vocab != hc.vocab:
+            if not ck.has("d2t"):
+                raise ValueError("a reduced draft vocabulary needs the `d2t` map")
+            off = ck.get("d2t").long()
+            d2t = torch.arange(hc.draft_vocab) + off          # draft id -> target id (the file stores offsets)
+            if int(d2t.max()) >= hc.vocab or int(d2t.min()) < 0:
+                raise ValueError("`d2t` points outside the target vocabulary")
+        return cls(cfg, device, dtype, weights=w, hcfg=hc, d2t=d2t)
 
     def fuse(self, feats: List[torch.Tensor]) -> torch.Tensor:
-        return ops.linear(torch.cat(feats, dim=-1), self.w["fc"])
+        hc, w = self.hc, self.w
+        x = torch.cat(feats, dim=-1)
+        if hc.norm_before_fc:
+            x, _ = ops.rmsnorm(x.contiguous(), w["input_norm"], hc.eps)
+        if hc.fc_norm:
+            ht = hc.target_hidden
+            x = torch.cat([ops.rmsnorm(x[:, i * ht:(i + 1) * ht].contiguous(), w[f"fc_norm.{i}"], hc.eps)[0]
+                           for i in range(hc.n_aux)], dim=-1)
+        return ops.linear(x.contiguous(), w["fc"])
 
     def forward(self, tokens_embed, g, b, kv_k, kv_v, cos_sin):
-        cfg, w = self.cfg, self.w
-        e, _ = ops.rmsnorm(tokens_embed, w["enorm"], cfg.rms_eps)
-        gn, _ = ops.rmsnorm(g, w["hnorm"], cfg.rms_eps)
+        hc, w = self.hc, self.w
+        cos_sin = self.cos_sin if self.cos_sin is not None else cos_sin
+        e, _ = ops.rmsnorm(tokens_embed, w["enorm"], hc.eps)
+        gn, _ = ops.rmsnorm(g, w["hnorm"], hc.eps)
         x = torch.cat([e, gn], dim=-1).contiguous()
         qkv = ops.linear(x, w["qkv"])
-        q, _ = ops.qk_norm_rope_append(qkv, cfg.n_head, cfg.n_kv_head, cfg.head_dim, None, None, cfg.rms_eps, 0.0,
-                                       cos_sin, cfg.rope_dim, b.positions, b.slots, kv_k, kv_v, False)
-        o = ops.paged_attention(q, kv_k, kv_v, b.block_table, b.ctx_lens, b.cu_q, b.max_q_len, cfg.head_dim ** -0.5,
+        if "b_qkv" in w:
+            qkv = (qkv.float() + w["b_qkv"]).to(qkv.dtype)
+        q, _ = ops.qk_norm_rope_append(qkv, hc.n_head, hc.n_kv_head, hc.head_dim, w.get("q_norm"), w.get("k_norm"), hc.eps,
+                                       0.0, cos_sin, hc.head_dim, b.positions, b.slots, kv_k, kv_v, False)
+        o = ops.paged_attention(q, kv_k, kv_v, b.block_table, b.ctx_lens, b.cu_q, b.max_q_len, hc.head_dim ** -0.5,
                                 max_ctx=b.max_ctx or None)
-        h = ops.linear(o.reshape(o.shape[0], -1), w["o"], residual=g)
-        hn, _ = ops.rmsnorm(h, w["ffn_norm"], cfg.rms_eps)
+        h = ops.linear(o.reshape(o.shape[0], -1), w["o"], residual=gn if hc.norm_before_residual else g)
+        if "bo" in w:
+            h = (h.float() + w["bo"]).to(h.dtype)
+        hn, _ = ops.rmsnorm(h, w["ffn_norm"], hc.eps)
         f = ops.linear(ops.gate_up_act(hn, w["gate_up"], self.n_ff), w["down"], residual=h)
-        out, _ = ops.rmsnorm(f, w["out_norm"], cfg.rms_eps)
-        return f, out
+        out, _ = ops.rmsnorm(f, w["out_norm"], hc.eps)
+        return (out if hc.norm_output else f), out
 
     def logits(self, normed):
-        return ops.linear(normed, self.w["lm_head"], out_dtype=torch.float32)
+        lg = ops.linear(normed, self.w["lm_head"], out_dtype=torch.float32)
+        return lg * self.hc.logit_scale if self.hc.logit_scale != 1.0 else lg
 
 
 class Eagle3Drafter(_ModelDrafter):
@@ -314,18 +439,21 @@ class Eagle3Drafter(_ModelDrafter):
         super().__init__(engine)
         cfg = engine.mcfg
         n = cfg.n_layer
-        self.capture_layers = layer_ids or sorted({min(2, n - 1), n // 2, max(0, n - 3)})
-        while len(self.capture_layers) < 3:
-            self.capture_layers = sorted(set(self.capture_layers) | {len(self.capture_layers)})[:3] \
-                if n >= 3 else (self.capture_layers + [self.capture_layers[-1]])
         self.head = head or Eagle3Head(cfg, engine.device, engine.model.dtype)
+        hc = self.head.hc
+        self.capture_layers = layer_ids or hc.layer_ids or sorted({min(2, n - 1), n // 2, max(0, n - 3)})
+        while len(self.capture_layers) < hc.n_aux:
+            self.capture_layers = sorted(set(self.capture_layers) | {len(self.capture_layers)})[:hc.n_aux] \
+                if n >= hc.n_aux else (self.capture_layers + [self.capture_layers[-1]])
+        if max(self.capture_layers) >= n:
+            raise ValueError(f"the EAGLE-3 head reads target layers {self.capture_layers}, the target has {n}")
         nb = engine.pool.total
-        shape = (nb, engine.cfg.block_size, cfg.n_kv_head, cfg.head_dim)
+        shape = (nb, engine.cfg.block_size, hc.n_kv_head, hc.head_dim)
         self.k = torch.zeros(shape, device=engine.device, dtype=engine.model.dtype)
         self.v = torch.zeros(shape, device=engine.device, dtype=engine.model.dtype)
 
     def _features(self, out, lo, hi):
-        return self.head.fuse([out.captures[l][lo:hi] for l in self.capture_layers[:3]])
+        return self.head.fuse([out.captures[l][lo:hi] for l in self.capture_layers[:self.head.hc.n_aux]])
 
     def on_step(self, items, b, out):
         eng = self.eng

@@ -453,3 +453,71 @@ def test_sliding_window_rings_equal_full_paging():
     assert first.token_ids == full[0][:12] and again.token_ids == first.token_ids
     assert again.usage.cached_tokens >= 64 and longer.usage.cached_tokens >= 64
     assert longer.token_ids == want_longer.token_ids
+
+
+def test_eagle3_head_from_a_checkpoint_directory(tmp_path):
+    """An EAGLE-3 checkpoint (config flags, own head shape, reduced draft vocabulary with ``d2t`` offsets, biases,
+    ``layers.0`` naming) loads into the drafter: speculation with it equals plain greedy decoding, the flags change
+    what the head computes, and a head that does not fit the target is refused."""
+    import json
+    import pytest
+    import torch
+    from legion_b200.config import ModelConfig
+    from legion_b200.engine.lm import EngineConfig, build_engine
+    from legion_b200.loaders.safetensors_io import save_file
+    from legion_b200.models.weights import random_weights
+    from legion_b200.spec.drafters import Eagle3Config, Eagle3Head
+    cfg = ModelConfig(arch="qwen3", n_layer=4, hidden=64, vocab=512, n_head=4, n_kv_head=2, head_dim=16, dense_ff=128)
+    w = random_weights(cfg, "cpu", torch.float32, seed=2, std=0.08)
+    H, nq, nkv, D, F, DV = 64, 2, 1, 32, 96, 200
+    g = torch.Generator().manual_seed(0)
+    r = lambda *sh: torch.randn(*sh, generator=g) * 0.05       # noqa: E731
+    d2t_target = torch.sort(torch.randperm(512, generator=g)[:DV]).values
+    tensors = {"fc.weight": r(H, 3 * H), "lm_head.weight": r(DV, H), "norm.weight": torch.ones(H) + r(H),
+               "input_norm.weight": torch.ones(3 * H) + r(3 * H), "d2t": (d2t_target - torch.arange(DV)).long(),
+               "t2d": torch.zeros(512, dtype=torch.bool)}
+    L = "layers.0"
+    for n, sh in (("self_attn.q_proj", (nq * D, 2 * H)), ("self_attn.k_proj", (nkv * D, 2 * H)),
+                  ("self_attn.v_proj", (nkv * D, 2 * H)), ("self_attn.o_proj", (H, nq * D)), ("mlp.gate_proj", (F, H)),
+                  ("mlp.up_proj", (F, H)), ("mlp.down_proj", (H, F))):
+        tensors[f"{L}.{n}.weight"] = r(*sh)
+    for n in ("input_layernorm", "hidden_norm", "post_attention_layernorm"):
+        tensors[f"{L}.{n}.weight"] = torch.ones(H) + r(H)
+    for n, k in (("q_proj", nq * D), ("k_proj", nkv * D), ("v_proj", nkv * D)):
+        tensors[f"{L}.self_attn.{n}.bias"] = r(k)
+    d = tmp_path / "eagle3"
+    d.mkdir()
+    save_file(tensors, str(d / "model.safetensors"))
+    conf = {"architectures": ["LlamaForCausalLMEagle3"], "hidden_size": H, "intermediate_size": F, "num_attention_heads": nq,
+            "num_key_value_heads": nkv, "head_dim": D, "vocab_size": 512, "draft_vocab_size": DV, "num_hidden_layers": 1,
+            "rms_norm_eps": 1e-5, "rope_theta": 50000.0, "max_position_embeddings": 2048, "attention_bias": True,
+            "norm_before_fc": True, "eagle_config": {"eagle_aux_hidden_state_layer_ids": [0, 1, 3],
+                                                     "norm_before_residual": True}}
+    (d / "config.json").write_text(json.dumps(conf))
+    hc = Eagle3Config.parse(conf)
+    assert (hc.n_aux, hc.layer_ids, hc.draft_vocab, hc.attention_bias, hc.norm_before_residual, hc.norm_before_fc,
+            hc.fc_norm, hc.rope_theta) == (3, [0, 1, 3], DV, True, True, True, False, 50000.0)
+    head = Eagle3Head.from_checkpoint(str(d), cfg, "cpu", torch.float32)
+    assert torch.equal(head.d2t, d2t_target) and head.cos_sin is not None and "b_qkv" in head.w
+    feats = [torch.randn(5, H) for _ in range(3)]
+    fused = head.fuse(feats)
+    cat = torch.cat(feats, -1)
+    want = (cat * torch.rsqrt(cat.pow(2).mean(-1, keepdim=True) + 1e-5) * tensors["input_norm.weight"]) @ tensors["fc.weight"].t()
+    assert torch.allclose(fused, want, atol=1e-5)
+    ec = dict(ctx_size=256, max_seqs=2, block_size=16, prefill_chunk=64, max_batch_tokens=128)
+    prompt = list(range(7, 60)) + [7, 8, 9, 7, 8, 9]
+    plain = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(**ec))
+    want_toks = plain.generate_text(tokens=prompt, max_tokens=20, ignore_eos=True).token_ids
+    plain.shutdown()
+    spec = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(spec="eagle3", spec_k=3, spec_draft_model=str(d), **ec))
+    assert spec.drafter.capture_layers == [0, 1, 3] and spec.drafter.k.shape[2:] == (nkv, D)
+    got = spec.generate_text(tokens=prompt, max_tokens=20, ignore_eos=True)
+    drafted = spec.stats().spec_draft_tokens
+    spec.shutdown()
+    assert got.token_ids == want_toks and drafted > 0
+    conf_bad = dict(conf, hidden_size=128)
+    (d / "config.json").write_text(json.dumps(conf_bad))
+    with pytest.raises(ValueError):
+        Eagle3Head.from_checkpoint(str(d), cfg, "cpu", torch.float32)
+    with pytest.raises(ValueError):
+        Eagle3Config.parse(dict(conf, num_hidden_layers=2))
