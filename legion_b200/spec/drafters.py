@@ -277,12 +277,15 @@ class Eagle3Config:
         self.rope_theta, self.rope_scaling, self.max_pos, self.layer_ids = rope_theta, rope_scaling, max_pos, layer_ids
         self.attention_bias, self.norm_before_residual = attention_bias, norm_before_residual
         self.norm_before_fc, self.fc_norm, self.norm_output, self.logit_scale = norm_before_fc, fc_norm, norm_output, logit_scale
+        self.rope_dim = head_dim          # a checkpoint's head rotates its heads whole
 
     @classmethod
     def for_target(cls, cfg: ModelConfig, draft_vocab: int = 0) -> "Eagle3Config":
-        return cls(cfg.hidden, cfg.dense_ff or 4 * cfg.hidden, cfg.n_head, cfg.n_kv_head, cfg.head_dim, cfg.vocab,
-                   draft_vocab, eps=cfg.rms_eps, rope_theta=cfg.rope_theta, rope_scaling=cfg.rope_scaling,
-                   max_pos=cfg.max_position)
+        hc = cls(cfg.hidden, cfg.dense_ff or 4 * cfg.hidden, cfg.n_head, cfg.n_kv_head, cfg.head_dim, cfg.vocab,
+                 draft_vocab, eps=cfg.rms_eps, rope_theta=cfg.rope_theta, rope_scaling=cfg.rope_scaling,
+                 max_pos=cfg.max_position)
+        hc.rope_dim = cfg.rope_dim        # a head shaped after the target shares its rotary table
+        return hc
 
     @classmethod
     def parse(cls, c: dict) -> "Eagle3Config":
@@ -339,9 +342,11 @@ class Eagle3Head:
         else:
             self.d2t = None if self.draft_vocab == cfg.vocab else torch.arange(self.draft_vocab, device=device)
         self.n_ff = F
-        same_rope = (hc.rope_theta == cfg.rope_theta and hc.rope_scaling == cfg.rope_scaling and D == cfg.rope_dim)
-        self.cos_sin = None if same_rope else ops.reference.rope_cos_sin(max(hc.max_pos, cfg.max_position) + 8, D,
-                                                                         hc.rope_theta, hc.rope_scaling, device=device)
+        same_rope = (hc.rope_theta == cfg.rope_theta and hc.rope_scaling == cfg.rope_scaling
+                     and hc.rope_dim == cfg.rope_dim)
+        self.cos_sin = None if same_rope else ops.reference.rope_cos_sin(max(hc.max_pos, cfg.max_position) + 8,
+                                                                         hc.rope_dim, hc.rope_theta, hc.rope_scaling,
+                                                                         device=device)
 
     @classmethod
     def from_checkpoint(cls, path: str, cfg: ModelConfig, device, dtype) -> "Eagle3Head":
@@ -418,7 +423,7 @@ class Eagle3Head:
         if "b_qkv" in w:
             qkv = (qkv.float() + w["b_qkv"]).to(qkv.dtype)
         q, _ = ops.qk_norm_rope_append(qkv, hc.n_head, hc.n_kv_head, hc.head_dim, w.get("q_norm"), w.get("k_norm"), hc.eps,
-                                       0.0, cos_sin, hc.head_dim, b.positions, b.slots, kv_k, kv_v, False)
+                                       0.0, cos_sin, hc.rope_dim, b.positions, b.slots, kv_k, kv_v, False)
         o = ops.paged_attention(q, kv_k, kv_v, b.block_table, b.ctx_lens, b.cu_q, b.max_q_len, hc.head_dim ** -0.5,
                                 max_ctx=b.max_ctx or None)
         h = ops.linear(o.reshape(o.shape[0], -1), w["o"], residual=gn if hc.norm_before_residual else g)
