@@ -67,9 +67,11 @@ def _add_engine_args(ap: argparse.ArgumentParser):
     g.add_argument("--spec-draft-model", default=None,
                    help="--spec eagle3: the head's checkpoint directory (config.json + safetensors); --spec draft: the "
                         "draft model (same vocabulary as the target)")
-    g.add_argument("--spec-p-min", type=float, default=0.5)
-    g.add_argument("--spec-policy", choices=["fixed", "cost"], default="fixed",
-                   help="cost: pick the draft depth per step from the measured acceptance rate and batch size")
+    g.add_argument("--spec-p-min", type=float, default=0.5,
+                   help="--spec-policy adaptive: a sequence drafts as deep as its last draft keeps this acceptance probability")
+    g.add_argument("--spec-policy", choices=["fixed", "cost", "adaptive"], default="fixed",
+                   help="cost: pick the draft depth per step from the measured acceptance rate and batch size; adaptive: "
+                        "per-sequence acceptance along the chain plus measured verify / draft step costs")
     g.add_argument("--no-even-chunks", action="store_true", help="full prompt chunks plus a short tail")
     g = ap.add_argument_group("parallelism")
     g.add_argument("--tp", type=int, default=1, help="tensor-parallel ranks (one process per GPU, spawned by serve)")
@@ -155,7 +157,7 @@ def build_engine_from_args(a, start: bool = True):
         cuda_graphs=not a.no_cuda_graphs, model_name=a.alias or os.path.basename(path.rstrip("/")),
         tool_format=a.tool_format, itl_target_ms=a.itl_target, ttft_target_ms=a.ttft_target,
         nvtx=getattr(a, "nvtx", False), kv_swap_gib=getattr(a, "kv_swap_gib", 0.0),
-        prefix_host_gib=getattr(a, "prefix_cache_host_gib", 0.0), spec_policy=getattr(a, "spec_policy", "fixed"), even_chunks=not getattr(a, "no_even_chunks", False))
+        prefix_host_gib=getattr(a, "prefix_cache_host_gib", 0.0), spec_policy=getattr(a, "spec_policy", "fixed"), spec_p_min=getattr(a, "spec_p_min", 0.5), even_chunks=not getattr(a, "no_even_chunks", False))
     pctx = None
     if world > 1 and getattr(a, "pp", 1) > 1:
         # pipeline stages: every rank loads only its layers, the residual travels by send / recv

@@ -77,7 +77,8 @@ class EngineConfig:
     reasoning: bool = True
     itl_target_ms: float = 0.0
     even_chunks: bool = True           # cut a prompt into equal chunks instead of full chunks + a short tail
-    spec_policy: str = "fixed"        # fixed | cost: choose the draft depth per step from measured acceptance
+    spec_policy: str = "fixed"        # fixed | cost | adaptive: draft depth per step from measured acceptance / costs
+    spec_p_min: float = 0.5           # adaptive: a sequence drafts as deep as its last draft keeps this acceptance
     ttft_target_ms: float = 0.0
 
 
@@ -94,7 +95,7 @@ class Seq:
     __slots__ = ("req", "stream", "tokens", "n_prompt", "n_computed", "table", "slot", "sampler", "detok", "stop",
                  "reason", "tools", "phase", "arrival_ms", "admit_ms", "first_ms", "usage", "radix_handle", "drafts",
                  "save_points", "finished", "priority", "key", "n_out", "held_logprobs", "constraint", "resumed", "swapped",
-                 "orig_prompt", "last_hidden", "draft_state", "owner", "mask_ahead", "media")
+                 "orig_prompt", "last_hidden", "draft_state", "owner", "mask_ahead", "media", "spec_state", "spec_cap")
 
     def __init__(self, req: GenerateRequest, stream: TokenStream, tokens: List[int]):
         self.req, self.stream = req, stream
@@ -104,6 +105,8 @@ class Seq:
         self.n_computed = 0
         self.swapped = None               # _Swapped: KV blocks + recurrent state parked in host memory
         self.media = None                 # vision.SeqMedia: image rows, their spans and rotary positions
+        self.spec_state = None            # spec.depth.AdaptiveState under the adaptive draft-depth policy
+        self.spec_cap = 0                 # the cap this step's drafts were made under
         self.table = BlockTable()
         self.slot = -1
         self.owner = -1                   # data-parallel attention: the rank that runs this sequence's attention
@@ -216,6 +219,8 @@ class LmEngine(Engine):
         if ("kda" in self.mcfg.layer_kinds) and (drafter is not None or c.spec != "none"):
             raise ValueError("speculative decoding is not available for models with Kimi-delta-attention layers "
                              "(their verify steps have no state replay)")
+        self._depth_model = None          # spec.depth.DepthModel under the adaptive draft-depth policy
+        self._draft_ms_step = 0.0
         self.vision = None                # vision.VisionRuntime once a tower is attached (``attach_vision``)
         self.drafter = drafter
         if self.drafter is None and c.spec != "none":
@@ -872,8 +877,10 @@ class LmEngine(Engine):
         sum_{i<=k} p^i for acceptance rate p; a verify step of k extra rows per sequence costs about
         (1 + k * n_decode * row_cost) decode steps, so pick the k with the best tokens / cost ratio."""
         c = self.cfg
-        if c.spec_policy != "cost":
+        if c.spec_policy not in ("cost", "adaptive"):
             return c.spec_k
+        if c.spec_policy == "adaptive":
+            return c.spec_k            # per-sequence caps and the measured-cost model decide in ``_adaptive_caps``
         st = self._stats
         drafted = max(1, st.spec_draft_tokens)
         p = min(0.98, max(0.05, st.spec_accepted_tokens / drafted)) if drafted > 32 else 0.6
@@ -886,6 +893,27 @@ class LmEngine(Engine):
                 best_k, best = k, tokens / cost
         return best_k
 
+    def _adaptive_caps(self, decode) -> Dict[int, int]:
+        """Adaptive policy (``spec/depth.py``): one depth for the step from the measured verify / draft costs and the
+        sequences' expected gains, then per sequence the deepest draft whose last token keeps ``spec_p_min``
+        acceptance; a sequence capped at 0 drafts one probing token every eighth step."""
+        from ..spec.depth import AdaptiveState, DepthModel
+        c = self.cfg
+        if self._depth_model is None:
+            self._depth_model = DepthModel(c.spec_k)
+        cand = [s for s in decode if s.constraint is None]
+        for s in cand:
+            if s.spec_state is None:
+                s.spec_state = AdaptiveState()
+        step_k = self._depth_model.choose([s.spec_state for s in cand], len(cand)) if cand else 0
+        caps = {}
+        for s in cand:
+            k = min(step_k, s.spec_state.cap(c.spec_p_min, c.spec_k))
+            if k == 0 and s.spec_state.note_idle():
+                k = 1
+            caps[id(s)] = k
+        return caps
+
     def step(self):
         t0 = time.perf_counter()
         c = self.cfg
@@ -894,7 +922,12 @@ class LmEngine(Engine):
         # drafts for this step (model-free drafters propose now; model drafters proposed after the last step)
         use_spec = self.drafter is not None and 0 < len(decode) <= c.spec_max_batch
         depth = self._spec_depth(len(decode)) if use_spec else 0
+        caps = self._adaptive_caps(decode) if (use_spec and c.spec_policy == "adaptive") else None
+        self._draft_ms_step = 0.0
         for s in decode:
+            if caps is not None:
+                depth = caps.get(id(s), 0)
+            s.spec_cap = depth if use_spec else 0
             if not use_spec or s.constraint is not None or depth == 0:
                 s.drafts = []
             elif self.drafter.model_free:
@@ -953,6 +986,9 @@ class LmEngine(Engine):
         else:
             self._forward_and_finish(rows, verify=False)
         dt = (time.perf_counter() - t0) * 1000
+        if self._depth_model is not None and all(r[0].phase == "decode" or r[2] == 1 for r in rows):
+            # a step of decode / verify rows only: its time (without the drafter's own passes) is V(rows)
+            self._depth_model.observe_verify(sum(r[2] for r in rows), max(0.0, dt - self._draft_ms_step))
         self._observe_step(sum(1 for r in rows if r[0].phase == "decode" or r[2] == 1),
                            sum(r[2] for r in rows if r[2] > 1 and r not in verify_rows), dt)
         st = self._stats
@@ -1251,6 +1287,8 @@ class LmEngine(Engine):
                     lps.append(lp)
             r += n
             if k:
+                if s.spec_state is not None:
+                    s.spec_state.update(k, len(accepted) - 1, max(s.spec_cap, k))
                 self._stats.spec_draft_tokens += k
                 self._stats.spec_accepted_tokens += len(accepted) - 1
                 self._stats.spec_verify_steps += 1
@@ -1270,7 +1308,12 @@ class LmEngine(Engine):
                 self.drafter.on_step([it for it in step_items if not it[0].finished], b, out)
             live = [s for s, _, _ in rows if s in self.running and s.phase == "decode"]
             if live and len(live) <= self.cfg.spec_max_batch:
+                td = time.perf_counter()
                 self.drafter.draft_batch(live, self.cfg.spec_k)
+                ms = (time.perf_counter() - td) * 1e3
+                self._draft_ms_step += ms
+                if self._depth_model is not None:
+                    self._depth_model.observe_draft(len(live), self.cfg.spec_k, ms)
 
     def _accept_on_device(self, rows, logits):
         """Greedy verification without bringing the step's arg-max rows to the host: the arg-max of every logits

@@ -521,3 +521,47 @@ def test_eagle3_head_from_a_checkpoint_directory(tmp_path):
         Eagle3Head.from_checkpoint(str(d), cfg, "cpu", torch.float32)
     with pytest.raises(ValueError):
         Eagle3Config.parse(dict(conf, num_hidden_layers=2))
+
+
+def test_adaptive_draft_depth_follows_acceptance_and_costs():
+    """The depth model's pieces, then the engine under ``spec_policy="adaptive"``: tokens equal plain decoding; a text
+    the n-gram drafter predicts well keeps drafting deep, one it cannot predict stops drafting (but keeps probing)."""
+    import torch
+    from legion_b200.config import PRESETS
+    from legion_b200.engine.lm import EngineConfig, build_engine
+    from legion_b200.models.weights import random_weights
+    from legion_b200.spec.depth import AdaptiveState, DepthModel, chain_gain
+    good, bad = AdaptiveState(), AdaptiveState()
+    assert abs(good.gain(3) - chain_gain(0.6, 3)) < 1e-9 and good.cap(0.5, 8) == 1
+    for _ in range(25):
+        good.update(4, 4, 4)
+        bad.update(4, 0, 4)
+    assert good.cap(0.5, 8) == 8 and bad.cap(0.5, 8) == 0 and good.gain(4) > 4.5 and bad.gain(4) < 1.1
+    half = AdaptiveState()
+    for _ in range(40):
+        half.update(4, 2, 4)               # always two accepted, then a rejection
+    assert 0.6 < half.rate < 0.72 and abs(half.gain(2) - 3.0) < 0.05 and abs(half.gain(6) - 3.0) < 0.05
+    m = DepthModel(6)
+    for rows, ms in ((2, 5.0), (4, 5.2), (8, 5.5), (16, 9.0), (32, 20.0)):
+        m.observe_verify(rows, ms)
+    assert m.choose([good, good], 2) in (3, 6) and m.choose([bad, bad], 2) == 0
+    # verify rows that cost as much as whole steps make even a perfect drafter shallow
+    steep = DepthModel(6)
+    for rows, ms in ((2, 5.0), (4, 10.0), (8, 20.0), (16, 40.0)):
+        steep.observe_verify(rows, ms)
+    assert steep.choose([half, half], 2) <= 1
+
+    cfg = PRESETS["tiny-dense"]()
+    w = random_weights(cfg, "cpu", torch.float32, seed=5, std=0.08)
+    ec = dict(ctx_size=512, max_seqs=2, block_size=16, prefill_chunk=128, max_batch_tokens=256)
+    rep = [11, 12, 13, 14, 15, 16] * 20                   # whatever follows, the drafter proposes the repeating cycle
+    plain = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(**ec))
+    want = plain.generate_text(tokens=rep, max_tokens=40, ignore_eos=True).token_ids
+    plain.shutdown()
+    eng = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(spec="ngram", spec_k=4, spec_policy="adaptive", **ec))
+    got = eng.generate_text(tokens=rep, max_tokens=40, ignore_eos=True)
+    st = eng.stats()
+    eng.shutdown()
+    assert got.token_ids == want
+    # a random model does not continue the cycle: acceptance collapses and the policy stops paying for deep drafts
+    assert st.spec_draft_tokens < 4 * 40 * 0.6
