@@ -57,6 +57,9 @@ def sampling_from(body: dict, defaults: Optional[dict], default_max_tokens: int,
         max_tokens = default_max_tokens
     if isinstance(max_tokens, bool) or not isinstance(max_tokens, int) or max_tokens < 1:
         raise ApiError(400, "max_tokens must be a positive integer", param=max_key)
+    n = body.get("n")
+    if n is not None and (isinstance(n, bool) or n != 1):
+        raise ApiError(400, "only n=1 is supported", param="n")
     lp = body.get("logprobs")
     top_lp = _num(body, "top_logprobs", 0, int)
     if isinstance(lp, int) and not isinstance(lp, bool):      # legacy completions: logprobs = N

@@ -287,3 +287,12 @@ def test_numa_binding_from_a_fake_sysfs(tmp_path):
     (sysfs / "bus/pci/devices/0000:1b:00.0/numa_node").write_text("-1\n")
     r = numa.bind_to_gpu(3, sysfs=str(sysfs), bus_id="0000:1b:00.0", apply=lambda *a: done.update(again=True))
     assert r["node"] is None and not r["bound"] and "again" not in done
+
+
+def test_only_one_choice_per_request():
+    c = client()
+    msg = {"messages": [{"role": "user", "content": "a"}]}
+    assert c.post("/v1/chat/completions", json=dict(msg, n=1)).status_code == 200
+    for bad in (2, 0):
+        r = c.post("/v1/chat/completions", json=dict(msg, n=bad))
+        assert r.status_code == 400 and r.json()["error"]["param"] == "n"
