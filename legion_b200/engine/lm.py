@@ -251,12 +251,16 @@ class LmEngine(Engine):
         probe = KvCache(self.mcfg, 1, c.block_size, dev, model.dtype, kv_heads_local=model.n_kv_l, extra_layers=extra,
                         owns=owns)
         bpb = probe.bytes_per_block()
+        bpb_ring = probe.bytes_per_block(swa_only=True) if self.ring_len else 0
         del probe
-        n_saved = c.prefix_cache_states if (self.hybrid and c.prefix_cache) else 0
-        state_bytes = 0
+        snap = self.hybrid or bool(self.ring_len)
+        n_saved = c.prefix_cache_states if (snap and c.prefix_cache) else 0
+        # ring storage: the sliding-window layers cost a fixed ring per sequence slot, not a share of every block
+        bpb -= bpb_ring
+        state_bytes = bpb_ring * self.ring_len * (c.max_seqs + n_saved + 1)
         if self.hybrid:
             sp = StatePool(self.mcfg, 1, dev, tp=model.pctx.tp, owns=owns)
-            state_bytes = sp.bytes_per_slot() * (c.max_seqs + n_saved + 1)
+            state_bytes += sp.bytes_per_slot() * (c.max_seqs + n_saved + 1)
             del sp
         free, total = torch.cuda.mem_get_info(dev)
         m = self.mcfg

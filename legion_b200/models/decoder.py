@@ -79,6 +79,7 @@ class KvCache:
         (a short ring of blocks per sequence slot, ``engine.lm``) instead of ``n_blocks``."""
         self.page, self.n_blocks = page, n_blocks
         self.ring_blocks = ring_blocks
+        self._kinds = tuple(cfg.layer_kinds)
         self.k: Dict[int, torch.Tensor] = {}
         self.v: Dict[int, torch.Tensor] = {}
         layers = [il for il in cfg.kv_layers() if owns is None or owns(il)]   # pipeline stage: own layers only
@@ -108,13 +109,18 @@ class KvCache:
                     src = cfg.kv_source(il)
                     self.k[il], self.v[il] = self.k[src], self.v[src]
 
-    def bytes_per_block(self) -> int:
+    def bytes_per_block(self, swa_only: bool = False) -> int:
+        """Bytes one block takes over every layer that owns a cache; ``swa_only`` counts the sliding-window layers
+        alone (the part that moves into per-slot rings when ring storage is on)."""
         n = 0
         seen = set()
+        kinds = self._kinds
         for il, k in self.k.items():
             if k.data_ptr() in seen:
                 continue                              # a layer that reads another layer's cache
             seen.add(k.data_ptr())
+            if swa_only and not (il < len(kinds) and kinds[il] == "swa"):
+                continue
             n += k[0].numel() * k.element_size()
             if self.v[il] is not k:
                 n += self.v[il][0].numel() * k.element_size()
