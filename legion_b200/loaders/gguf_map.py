@@ -41,8 +41,8 @@ def _gemma4_config(md: dict) -> ModelConfig:
     kvh, ff = per_layer("attention.head_count_kv"), per_layer("feed_forward_length")
     kv_swa = {kvh[i] for i in range(n_layer) if swa[i]} or {1}
     kv_full = {kvh[i] for i in range(n_layer) if not swa[i]} or {1}
-    if len(kv_swa) > 1 or len(kv_full) > 1 or len(set(ff)) > 1:
-        raise ValueError("gemma4: kv-head counts must be uniform per layer kind and the FFN width uniform")
+    if len(kv_swa) > 1 or len(kv_full) > 1:
+        raise ValueError("gemma4: kv-head counts must be uniform per layer kind")
     hidden, head_dim = int(g("embedding_length")), int(g("attention.key_length"))
     n_expert = int(g("expert_count", 0))
     return ModelConfig(
@@ -52,7 +52,7 @@ def _gemma4_config(md: dict) -> ModelConfig:
         rope_theta=float(g("rope.freq_base", 10000.0)), swa_head_dim=int(g("attention.key_length_swa")),
         swa_kv_heads=kv_swa.pop(), rope_theta_swa=float(g("rope.freq_base_swa", g("rope.freq_base", 10000.0))),
         rms_eps=float(g("attention.layer_norm_rms_epsilon", 1e-6)), max_position=int(g("context_length", 131072)),
-        vocab=len(md.get("tokenizer.ggml.tokens", [])) or 0, ffn_act="gelu_tanh", dense_ff=ff[0], tie_embeddings=True,
+        vocab=len(md.get("tokenizer.ggml.tokens", [])) or 0, ffn_act="gelu_tanh", dense_ff=max(ff), tie_embeddings=True,
         logit_softcap=float(g("final_logit_softcapping", 0.0)), attn_scale=1.0, sandwich_norm=True,
         embed_scale=float(hidden) ** 0.5, v_norm=True, kv_shared_layers=int(g("attention.shared_kv_layers", 0)),
         ple_dim=int(g("embedding_length_per_layer_input", 0)), n_expert=n_expert,
@@ -145,7 +145,7 @@ def _gemma4_to_gguf(cfg: ModelConfig, w: Dict[str, torch.Tensor]) -> Dict[str, t
                              ("ple.post_norm", "post_norm")):
             if f"{p}.{ours}" in w:
                 out[f"{b}.{theirs}.weight"] = w[f"{p}.{ours}"]
-        F = cfg.dense_ff
+        F = w[f"{p}.mlp.gate_up"].shape[0] // 2       # layers that share KV may be twice as wide
         out[f"{b}.ffn_gate.weight"], out[f"{b}.ffn_up.weight"] = w[f"{p}.mlp.gate_up"][:F], w[f"{p}.mlp.gate_up"][F:]
         out[f"{b}.ffn_down.weight"] = w[f"{p}.mlp.down"]
         if cfg.is_moe_layer(il):

@@ -3,6 +3,7 @@ MoE with un-gated experts. The vectorised forms against token-serial restatement
 the engine invariants on tiny models of each family (CPU, fp32)."""
 import math
 
+import pytest
 import torch
 
 from legion_b200.config import PRESETS
@@ -357,3 +358,63 @@ def test_gemma4_gguf_round_trip(tmp_path):
         outs.append(eng.generate_text(tokens=toks, max_tokens=8, ignore_eos=True).token_ids)
         eng.shutdown()
     assert outs[0] == outs[1]
+
+
+@pytest.mark.parametrize("variant", ["dense", "moe"])
+def test_gemma4_hf_checkpoint_against_transformers(tmp_path, variant):
+    """A tiny Gemma-4 text model built and saved by the ``transformers`` implementation, read through the HF mapper
+    (``loaders/hf_gemma4.py``): the prompt's logits at every position and a greedy continuation match that
+    implementation. dense: per-layer embeddings, layers that share KV and are twice as wide, proportional rotary
+    embedding on the global layers, a window shorter than the prompt, soft cap. moe: routed experts beside the dense
+    FFN with a per-expert output scale, keys as values and a kv-head count of their own on the global layers."""
+    g4 = pytest.importorskip("transformers.models.gemma4.modeling_gemma4")
+    from transformers.models.gemma4 import Gemma4TextConfig
+    from legion_b200.engine.types import GenerateRequest, SamplingParams
+    from legion_b200.loaders.hf_map import load_hf
+    torch.manual_seed(0)
+    kw = dict(vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=6, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=16, global_head_dim=32, sliding_window=8,
+              layer_types=["sliding_attention", "sliding_attention", "full_attention"] * 2,
+              vocab_size_per_layer_input=320, hidden_size_per_layer_input=8, num_kv_shared_layers=2,
+              final_logit_softcapping=30.0, max_position_embeddings=256, use_double_wide_mlp=True,
+              attention_k_eq_v=False, pad_token_id=0, eos_token_id=1, bos_token_id=2)
+    if variant == "moe":
+        kw.update(enable_moe_block=True, num_experts=8, top_k_experts=2, moe_intermediate_size=32,
+                  num_kv_shared_layers=0, hidden_size_per_layer_input=0, attention_k_eq_v=True,
+                  num_global_key_value_heads=1, use_double_wide_mlp=False)
+    hc = Gemma4TextConfig(**kw)
+    hc._attn_implementation = "eager"
+    m = g4.Gemma4ForCausalLM(hc).eval().float()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if "norm" in n or n.endswith("router.scale") or n.endswith("per_expert_scale"):
+                p.copy_(1.0 + 0.2 * torch.randn_like(p))
+            elif p.dim() >= 2:
+                p.copy_(torch.randn_like(p) * 0.08)
+        for n, b in m.named_buffers():
+            if n.endswith("layer_scalar"):
+                b.copy_(torch.tensor([0.9]))
+    m.save_pretrained(str(tmp_path), safe_serialization=True)
+    ids = torch.randint(3, 320, (1, 24))
+    with torch.no_grad():
+        ref = m(input_ids=ids).logits[0].float()
+        cont = m.generate(ids, max_new_tokens=6, do_sample=False)[0, 24:].tolist()
+    cfg, w, _ = load_hf(str(tmp_path), "cpu", torch.float32)
+    assert cfg.sandwich_norm and cfg.layer_kinds == ["swa", "swa", "attn"] * 2
+    assert cfg.global_k_as_v == (variant == "moe") and cfg.n_expert == (8 if variant == "moe" else 0)
+    eng = build_engine(cfg, weights=dict(w), start=False,
+                       engine_cfg=EngineConfig(ctx_size=128, max_seqs=2, block_size=16, max_batch_tokens=128))
+    seq = eng.prepare(GenerateRequest(prompt_tokens=ids[0].tolist(), sampling=SamplingParams(max_tokens=1)))
+    eng.waiting.push(seq)
+    eng._admit()
+    b = eng.build_batch([(seq, 0, 24)])
+    b.logit_rows = None
+    with torch.no_grad():
+        mine = eng.model.forward(b, eng.kv, eng.states).logits.float()
+    assert (mine - ref).abs().max().item() < 2e-4
+    eng2 = build_engine(cfg, weights=dict(w),
+                        engine_cfg=EngineConfig(ctx_size=128, max_seqs=2, block_size=16, max_batch_tokens=128,
+                                                prefill_chunk=16))
+    out = eng2.generate_text(tokens=ids[0].tolist(), max_tokens=6, ignore_eos=True).token_ids
+    eng2.shutdown()
+    assert out == cont
