@@ -34,7 +34,7 @@ from ..models.decoder import Decoder, KvCache, StatePool, StepBatch
 from ..parallel.context import ParallelCtx
 from .queue import WaitQueue
 from .sampling import Sampler, top_logprobs
-from .text import IncrementalDetokenizer, ReasoningSplitter, StopChecker, ToolCallParser
+from .text import ChatFormat, IncrementalDetokenizer, ReasoningSplitter, StopChecker, ToolCallParser
 from .types import (CancelToken, Engine, EngineOverloaded, EngineStats, FinishReason, GenerateRequest, KvOverflow,
                     SamplingParams, TokenEvent, TokenLogprob, TokenStream, Usage, now_ms)
 
@@ -226,7 +226,9 @@ class LmEngine(Engine):
         if self.drafter is None and c.spec != "none":
             from ..spec import make_drafter
             self.drafter = make_drafter(c.spec, self, **self._drafter_args())
-        self.eos_ids = tuple(self.tok.eos_ids)
+        # reasoning markers, tool-call notation and further end-of-turn tokens, read from the vocabulary
+        self.chat_format = ChatFormat(self.tok, c.tool_format)
+        self.eos_ids = tuple(dict.fromkeys(list(self.tok.eos_ids) + list(self.chat_format.stop_ids)))
         self._graphs = None
         self._mask_pool = None
         caches_ok = all(getattr(ec, "graph_safe", False) for ec in model.expert_cache.values())
@@ -752,13 +754,22 @@ class LmEngine(Engine):
             seq.sampler = Sampler(sp, seq.tokens, fallback_seed=self.cfg.seed)
             seq.detok = IncrementalDetokenizer(lambda ids: self.tok.decode(ids, skip_special=True))
             seq.stop = StopChecker(sp.stop)
-            seq.reason = ReasoningSplitter() if self.cfg.reasoning else None
-            seq.tools = ToolCallParser(self.cfg.tool_format) if seq.req.tools else None
+            seq.reason = self.chat_format.splitter(self._prompt_tail(seq)) if self.cfg.reasoning else None
+            seq.tools = ToolCallParser(self.chat_format.tool_format) if seq.req.tools else None
         if seq.n_out == 0:
             seq.stream.put(TokenEvent(kind="started", prompt_tokens=seq.orig_prompt))
         self.running.append(seq)
         self._stats.prompt_tokens += seq.n_prompt - resume
         return True
+
+    def _prompt_tail(self, seq: Seq) -> str:
+        """The end of the prompt as text (markers rendered): tells whether the template left a reasoning span open."""
+        if isinstance(seq.req.prompt, str) and seq.req.prompt:
+            return seq.req.prompt[-256:]
+        try:
+            return self.tok.decode(list(seq.tokens[max(0, seq.orig_prompt - 48):seq.orig_prompt]), skip_special=False)
+        except Exception:
+            return ""
 
     # ------------------------------------------------------------------ preemption (on-demand admission)
     def _preempt_one(self, protect: Seq) -> bool:

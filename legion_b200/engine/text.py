@@ -71,13 +71,16 @@ class StopChecker:
 
 
 class ReasoningSplitter:
-    """Routes text between ``<think>`` and ``</think>`` to the reasoning channel."""
+    """Routes text between the reasoning markers (``<think>`` ... ``</think>`` unless others are given) to the
+    reasoning channel."""
 
     OPEN, CLOSE = "<think>", "</think>"
 
-    def __init__(self, starts_in_reasoning: bool = False):
+    def __init__(self, starts_in_reasoning: bool = False, tags: Optional[Tuple[str, str]] = None):
         self.in_reasoning = starts_in_reasoning
         self._held = ""
+        if tags:
+            self.OPEN, self.CLOSE = tags
 
     def push(self, text: str) -> List[Tuple[str, str]]:
         """Returns [(channel, text)] with channel in {"reasoning", "text"}."""
@@ -113,6 +116,51 @@ class ReasoningSplitter:
         out = [("reasoning" if self.in_reasoning else "text", self._held)]
         self._held = ""
         return out
+
+
+class ChatFormat:
+    """Output conventions of a chat model, read once from its vocabulary rather than from the architecture name (a
+    checkpoint ships whatever template and tokenizer it likes; the reference's ``src/engine/lm/chat_format.rs``):
+
+    - Gemma 4 (``<|channel>``, ``<channel|>`` and ``<|tool_call>`` are tokens): reasoning sits between
+      ``<|channel>thought`` and ``<channel|>``, the model opens that channel itself, so a reply starts inside it only
+      when the prompt ends with the opener; tool calls in Gemma's notation;
+    - GLM 4.5 and later (``<tool_call>``, ``<arg_key>``, ``<arg_value>``): key / value tool calls;
+    - otherwise ``<think>`` ... ``</think>`` when ``<think>`` is a token (a reply starts inside when the prompt's last
+      opener comes after its last closer) and the configured tool-call format.
+
+    ``stop_ids``: end-of-turn tokens beyond the tokenizer's own (``<|im_end|>``, ``<|endoftext|>``, ``<turn|>``, and
+    the openers of a tool's turn ``<|tool_response>`` / ``<|observation|>``, which hand control to the caller)."""
+    STOPS = ("<|im_end|>", "<|endoftext|>", "<turn|>", "<|tool_response>", "<|observation|>")
+
+    def __init__(self, tok, tool_format: str = "hermes"):
+        tid = getattr(tok, "token_to_id", None) or (lambda t: None)
+        have = lambda names: all(tid(n) is not None for n in names)       # noqa: E731
+        self.kind = "plain"
+        self.tool_format = tool_format
+        self.tags: Optional[Tuple[str, str]] = None
+        self.prompt_mode = "off"
+        if have(("<|channel>", "<channel|>", "<|tool_call>")):
+            self.kind, self.tool_format = "gemma4", "gemma4"
+            self.tags, self.prompt_mode = ("<|channel>thought", "<channel|>"), "open_at_end"
+        else:
+            if have(("<tool_call>", "<arg_key>", "<arg_value>")):
+                self.kind, self.tool_format = "glm", "glm"
+            if tid("<think>") is not None:
+                self.prompt_mode = "from_prompt"
+        self.stop_ids = tuple(i for i in (tid(t) for t in self.STOPS) if i is not None)
+
+    def starts_in_reasoning(self, prompt_tail: str) -> bool:
+        """Whether the reply begins inside the reasoning span, given the end of the rendered prompt."""
+        o, c = self.tags or (ReasoningSplitter.OPEN, ReasoningSplitter.CLOSE)
+        if self.prompt_mode == "open_at_end":
+            return prompt_tail.rstrip().endswith(o)
+        if self.prompt_mode == "from_prompt":
+            return prompt_tail.rfind(o) > prompt_tail.rfind(c)
+        return False
+
+    def splitter(self, prompt_tail: str = "") -> ReasoningSplitter:
+        return ReasoningSplitter(self.starts_in_reasoning(prompt_tail), self.tags)
 
 
 _GEMMA_QUOTE = '<|"|>'

@@ -64,8 +64,9 @@ def load_model(path: str, device="cpu", dtype=None, rank: int = 0, world: int = 
         from .gguf_map import load_gguf
         cfg, w, md = load_gguf(path, "cpu" if world > 1 else dev, dtype)
         info["gguf_arch"] = md.get("general.architecture")
-        if "tokenizer.ggml.tokens" in md and md.get("tokenizer.ggml.model", "gpt2") == "gpt2" \
-                and "tokenizer.ggml.merges" in md:
+        kind = md.get("tokenizer.ggml.model", "gpt2")
+        if "tokenizer.ggml.tokens" in md and ((kind in ("gpt2", "gemma4") and "tokenizer.ggml.merges" in md)
+                                              or (kind == "llama" and "tokenizer.ggml.scores" in md)):
             tok = tokenizer_from_gguf_metadata(md)
         else:
             tok = ByteTokenizer(cfg.vocab)

@@ -117,7 +117,10 @@ PRE_PATTERNS["qwen35"] = PRE_PATTERNS["qwen2"]
 class BpeTokenizer(Tokenizer):
     def __init__(self, tokens: Sequence[str], merges: Sequence[str], pre: str = "gpt2",
                  token_types: Optional[Sequence[int]] = None, bos_id=None, eos_ids=(), add_bos=False,
-                 chat_template=None, extra_special: Iterable[str] = ()):
+                 chat_template=None, extra_special: Iterable[str] = (), visible: Iterable[str] = ()):
+        """``extra_special``: tokens matched whole in the text and left out of decoded text when special tokens are
+        skipped (control tokens). ``visible``: tokens matched whole but always rendered (GGUF's user-defined kind,
+        an HF added token with ``special: false``): reasoning and tool-call markers the text parsers must see."""
         self.tokens = list(tokens)
         self.vocab_size = len(self.tokens)
         self.vocab = {t: i for i, t in enumerate(self.tokens)}
@@ -132,10 +135,14 @@ class BpeTokenizer(Tokenizer):
         self._u2b = {v: k for k, v in b2u.items()}
         # GGUF token types: 3 = control, 4 = user defined
         sp = set(extra_special)
+        vis = set(visible)
         if token_types is not None:
-            sp |= {self.tokens[i] for i, t in enumerate(token_types) if t in (3, 4)}
-        self.special = {s: self.vocab[s] for s in sp if s in self.vocab}
+            sp |= {self.tokens[i] for i, t in enumerate(token_types) if t == 3}
+            vis |= {self.tokens[i] for i, t in enumerate(token_types) if t == 4}
+        sp -= vis
+        self.special = {s: self.vocab[s] for s in sp | vis if s in self.vocab}
         self._special_ids = set(self.special.values())
+        self._hidden_ids = {self.vocab[s] for s in sp if s in self.vocab}
         self._sp_re = None
         if self.special:
             alts = sorted(self.special, key=len, reverse=True)
@@ -234,7 +241,7 @@ class BpeTokenizer(Tokenizer):
             if t < 0 or t >= self.vocab_size:
                 continue
             if t in self._special_ids:
-                if not skip_special:
+                if not (skip_special and t in self._hidden_ids):
                     out.extend(self.tokens[t].encode("utf-8"))
             else:
                 out.extend(self.token_bytes(t))
@@ -255,6 +262,7 @@ class BpeTokenizer(Tokenizer):
         model = tj["model"]
         vocab = model["vocab"]
         added = {a["content"]: a["id"] for a in tj.get("added_tokens", [])}
+        shown = [a["content"] for a in tj.get("added_tokens", []) if not a.get("special", True)]
         size = max(list(vocab.values()) + list(added.values())) + 1
         tokens = [f"<unused{i}>" for i in range(size)]
         for t, i in vocab.items():
@@ -272,8 +280,111 @@ class BpeTokenizer(Tokenizer):
                 v = v.get("content")
             return added.get(v, vocab.get(v)) if v else None
         eos = [i for i in [tok_id("eos_token")] if i is not None]
+        if cls is BpeTokenizer and model.get("byte_fallback") and "ByteLevel" not in json.dumps(tj.get("pre_tokenizer")):
+            # raw-text BPE with byte tokens (the Gemma family): special tokens are the added ones marked special
+            for t in ("<end_of_turn>", "<turn|>"):
+                if t in added and added[t] not in eos:
+                    eos.append(added[t])
+            return Gemma4Tokenizer(tokens, merges, bos_id=tok_id("bos_token"), eos_ids=eos,
+                                   chat_template=cfg.get("chat_template"), extra_special=added.keys(), visible=shown)
         return cls(tokens, merges, pre="qwen2", bos_id=tok_id("bos_token"), eos_ids=eos,
-                   chat_template=cfg.get("chat_template"), extra_special=added.keys())
+                   chat_template=cfg.get("chat_template"), extra_special=added.keys(), visible=shown)
+
+
+class Gemma4Tokenizer(BpeTokenizer):
+    """Gemma 4's vocabulary (``tokenizer.ggml.model = "gemma4"``; an HF ``tokenizer.json`` whose BPE model has
+    ``byte_fallback``): merge-rank BPE over the text's own characters, not over the GPT-2 byte alphabet. The text is
+    cut into runs of newlines and runs of everything else; a newline run that is a token is taken whole; elsewhere
+    spaces become U+2581 and the run is merged by rank; a piece no token covers falls back to its ``<0xXX>`` byte
+    tokens. A begin-of-sequence token is always added.
+
+    Reference counterpart: ``src/tokenizer/gemma4.rs`` (the rules of llama.cpp's ``LLAMA_VOCAB_PRE_TYPE_GEMMA4``)."""
+    SPACE = "\u2581"
+
+    # markers the chat parsers read: always rendered (the reference's converter marks them user-defined)
+    VISIBLE = ("<|channel>", "<channel|>", "<|tool_call>", "<tool_call|>", "<|tool_response>", "<tool_response|>",
+               '<|"|>')
+
+    def __init__(self, tokens, merges, token_types=None, bos_id=None, eos_ids=(), chat_template=None,
+                 extra_special: Iterable[str] = (), visible: Iterable[str] = ()):
+        super().__init__(tokens, merges, pre="gpt2", token_types=token_types, bos_id=bos_id, eos_ids=eos_ids,
+                         add_bos=True, chat_template=chat_template, extra_special=extra_special,
+                         visible=tuple(visible) + self.VISIBLE)
+        self.pat = _re.compile(r"[^\n]+|\n+")
+        tt = list(token_types) if token_types is not None else [1] * len(self.tokens)
+        self.byte_id: Dict[int, int] = {}
+        for i, t in enumerate(self.tokens):
+            if (tt[i] == 6 or token_types is None) and len(t) == 6 and t.startswith("<0x") and t.endswith(">"):
+                try:
+                    self.byte_id[int(t[3:5], 16)] = i
+                except ValueError:
+                    pass
+        self._byte_of = {i: b for b, i in self.byte_id.items()}
+        # byte tokens are pieces of text, never markers: not matched by name, rendered as their byte
+        self.special = {t: i for t, i in self.special.items() if i not in self._byte_of}
+        self._special_ids = set(self.special.values())
+        self._hidden_ids &= self._special_ids
+        self._sp_re = None
+        if self.special:
+            self._sp_re = _re.compile("|".join(_re.escape(a) for a in sorted(self.special, key=len, reverse=True)))
+
+    def _fallback(self, piece: str) -> List[int]:
+        return [self.byte_id[b] for b in piece.encode("utf-8") if b in self.byte_id]
+
+    def _bpe(self, word: str) -> List[int]:
+        hit = self._cache.get(word)
+        if hit is not None:
+            return hit
+        if self._native is not None and all(c in self.vocab for c in word):
+            ids = list(self._native.encode_word(word))
+        else:
+            parts = list(word)
+            while len(parts) > 1:
+                best, bi = None, -1
+                for i in range(len(parts) - 1):
+                    r = self.ranks.get((parts[i], parts[i + 1]))
+                    if r is not None and (best is None or r < best):
+                        best, bi = r, i
+                if best is None:
+                    break
+                parts[bi:bi + 2] = [parts[bi] + parts[bi + 1]]
+            ids = []
+            for p_ in parts:
+                t = self.vocab.get(p_)
+                if t is None:
+                    ids.extend(self._fallback(p_))
+                else:
+                    ids.append(t)
+        if len(self._cache) < 65536:
+            self._cache[word] = ids
+        return ids
+
+    def _encode_plain(self, text: str) -> List[int]:
+        out: List[int] = []
+        for m in self.pat.finditer(text):
+            word = m.group(0)
+            if word[0] == "\n":
+                t = self.vocab.get(word)
+                if t is not None:
+                    out.append(t)
+                    continue
+            out.extend(self._bpe(word.replace(" ", self.SPACE)))
+        return out
+
+    def token_bytes(self, tid):
+        if tid in self._byte_of:
+            return bytes([self._byte_of[tid]])
+        t = self.tokens[tid]
+        if tid in self._special_ids:
+            return t.encode("utf-8")
+        return t.replace(self.SPACE, " ").encode("utf-8")
+
+    @classmethod
+    def from_gguf_metadata(cls, md: dict) -> "Gemma4Tokenizer":
+        eos = [md[k] for k in ("tokenizer.ggml.eos_token_id", "tokenizer.ggml.eot_token_id") if k in md]
+        return cls(md["tokenizer.ggml.tokens"], md.get("tokenizer.ggml.merges", []),
+                   token_types=md.get("tokenizer.ggml.token_type"), bos_id=md.get("tokenizer.ggml.bos_token_id"),
+                   eos_ids=eos, chat_template=md.get("tokenizer.chat_template"))
 
 
 class SpmTokenizer(Tokenizer):
@@ -416,6 +527,8 @@ def tokenizer_from_gguf_metadata(md: dict) -> Tokenizer:
     with merge ranks (``gpt2``: qwen, deepseek, llama-3)."""
     if md.get("tokenizer.ggml.model", "gpt2") == "llama":
         return SpmTokenizer.from_gguf_metadata(md)
+    if md.get("tokenizer.ggml.model") == "gemma4":
+        return Gemma4Tokenizer.from_gguf_metadata(md)
     return BpeTokenizer.from_gguf_metadata(md)
 
 

@@ -565,3 +565,18 @@ def test_adaptive_draft_depth_follows_acceptance_and_costs():
     assert got.token_ids == want
     # a random model does not continue the cycle: acceptance collapses and the policy stops paying for deep drafts
     assert st.spec_draft_tokens < 4 * 40 * 0.6
+
+
+def test_reply_starts_inside_reasoning_when_the_prompt_left_it_open():
+    """A template that ends the prompt with the reasoning opener (thinking models): the reply's text goes to the
+    reasoning channel from its first token; the same model after a prompt without the opener answers on the text
+    channel; the vocabulary's further end-of-turn tokens stop a reply."""
+    eng = engine("dense")
+    tok = eng.tok
+    assert eng.chat_format.prompt_mode == "from_prompt" and tok.token_to_id("<|im_end|>") in eng.eos_ids
+    kinds = {}
+    for label, text in (("open", "<|im_start|>assistant\n<think>\n"), ("closed", "<|im_start|>assistant\n")):
+        st = eng.generate(GenerateRequest(prompt=text, sampling=SamplingParams(max_tokens=12, ignore_eos=True)))
+        kinds[label] = {ev.kind for ev in st if ev.kind in ("text", "reasoning") and ev.text}
+    eng.shutdown()
+    assert kinds["open"] == {"reasoning"} and kinds["closed"] == {"text"}

@@ -398,3 +398,62 @@ def test_vision_language_config_carries_the_rotary_sections():
         "num_experts": 8, "num_experts_per_tok": 2, "moe_intermediate_size": 64, "shared_expert_intermediate_size": 64},
         "vision_config": {"depth": 2}})
     assert c.mrope_sections == (11, 11, 10) and c.mrope_interleaved and c.rope_theta == 5e6 and c.arch == "qwen35moe"
+
+
+def test_gemma4_tokenizer_against_the_tokenizers_library(tmp_path):
+    """Raw-text BPE with byte fallback (Gemma 4's kind): a small vocabulary trained with the ``tokenizers`` library
+    (spaces as U+2581, cut at newline runs, ``<0xXX>`` byte tokens) saved as ``tokenizer.json``, loaded by
+    ``BpeTokenizer.from_hf_dir`` (which picks ``Gemma4Tokenizer`` for it): same ids as the library on text with unseen
+    characters, newline runs and markers; markers that are not control tokens stay in decoded text."""
+    tk = pytest.importorskip("tokenizers")
+    from tokenizers import Regex, decoders, models, normalizers, pre_tokenizers, trainers
+    from legion_b200.loaders.tokenizer import BpeTokenizer, Gemma4Tokenizer
+    t = tk.Tokenizer(models.BPE(byte_fallback=True, unk_token="<unk>", fuse_unk=False))
+    t.normalizer = normalizers.Replace(" ", "▁")
+    t.pre_tokenizer = pre_tokenizers.Split(Regex("[^\\n]+|\\n+"), behavior="isolated")
+    t.decoder = decoders.Sequence([decoders.Replace("▁", " "), decoders.ByteFallback(), decoders.Fuse()])
+    specials = ["<pad>", "<eos>", "<bos>", "<unk>"] + [f"<0x{b:02X}>" for b in range(256)]
+    corpus = ["the quick brown fox jumps over the lazy dog\n\nand then it  sleeps\n", "hello world, hello there\n",
+              "def f(x):\n    return x + 1\n\n\nprint(f(2))\n", "a b c d e f g the then there"] * 4
+    t.train_from_iterator(corpus, trainers.BpeTrainer(vocab_size=420, special_tokens=specials, show_progress=False))
+    t.add_special_tokens(["<turn|>"])
+    t.add_tokens(["<|channel>", "<channel|>", "<|tool_call>"])
+    t.save(str(tmp_path / "tokenizer.json"))
+    json.dump({"bos_token": "<bos>", "eos_token": "<eos>"}, open(tmp_path / "tokenizer_config.json", "w"))
+    mine = BpeTokenizer.from_hf_dir(str(tmp_path))
+    assert isinstance(mine, Gemma4Tokenizer) and mine.add_bos
+    for text in ("the lazy dog sleeps", "hello  there\n\nworld", "café \U0001F600 ok", "\n\n\nx = f(2)\n",
+                 "<|channel>thought\nhm<channel|>hello<turn|>", "  leading and trailing  "):
+        want = t.encode(text, add_special_tokens=False).ids
+        assert mine.encode(text) == want, text
+        assert mine.decode(want) == t.decode(want, skip_special_tokens=False), text
+    ids = mine.encode("<|channel>thought\nhm<channel|>ok<turn|>")
+    assert mine.decode(ids, skip_special=True) == "<|channel>thought\nhm<channel|>ok"
+    assert mine.encode("x", add_special=True)[0] == mine.vocab["<bos>"]
+    assert mine.vocab["<turn|>"] in mine.eos_ids
+
+
+def test_chat_format_is_read_from_the_vocabulary():
+    from legion_b200.engine.text import ChatFormat
+
+    class Tok:
+        def __init__(self, names):
+            self.ids = {n: i for i, n in enumerate(names)}
+
+        def token_to_id(self, t):
+            return self.ids.get(t)
+
+    g = ChatFormat(Tok(["<|channel>", "<channel|>", "<|tool_call>", "<turn|>", "<|tool_response>"]))
+    assert (g.kind, g.tool_format, g.tags) == ("gemma4", "gemma4", ("<|channel>thought", "<channel|>"))
+    assert g.stop_ids == (3, 4)
+    assert g.starts_in_reasoning("<|turn>model\n<|channel>thought\n") and not g.starts_in_reasoning("<|turn>model\n")
+    assert not g.starts_in_reasoning("<|turn>model\n<|channel>thought\n<channel|>")
+    sp = g.splitter("")
+    assert sp.push("<|channel>thought\nplan<channel|>answer") == [("reasoning", "\nplan"), ("text", "answer")]
+    glm = ChatFormat(Tok(["<tool_call>", "<arg_key>", "<arg_value>", "<think>", "<|observation|>"]))
+    assert (glm.kind, glm.tool_format, glm.stop_ids) == ("glm", "glm", (4,))
+    assert glm.starts_in_reasoning("<|assistant|>\n<think>") and not glm.starts_in_reasoning("<think>a</think>\nb")
+    q = ChatFormat(Tok(["<|im_end|>", "<think>"]), tool_format="hermes")
+    assert (q.kind, q.tool_format, q.stop_ids) == ("plain", "hermes", (0,))
+    assert q.starts_in_reasoning("<|im_start|>assistant\n<think>\n")
+    assert not ChatFormat(Tok(["a"])).starts_in_reasoning("<think>")
