@@ -1,0 +1,92 @@
+"""The model code against an independent implementation: tiny random checkpoints built and saved by the
+``transformers`` package's own modelling code are read through the HF loader, and the prompt's logits at every
+position plus a greedy continuation (decoded through the engine with chunked prefill and the paged cache) must match
+what ``transformers`` computes. Families: llama, qwen3_moe, deepseek_v3 (latent attention, grouped sigmoid router with
+bias), qwen3_5 and qwen3_5_moe (Gated DeltaNet hybrid; the flagship family)."""
+import pytest
+import torch
+
+from legion_b200.engine.lm import EngineConfig, build_engine
+from legion_b200.engine.types import GenerateRequest, SamplingParams
+from legion_b200.loaders.hf_map import load_hf
+
+transformers = pytest.importorskip("transformers")
+
+HYBRID = dict(vocab_size=320, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+              head_dim=16, linear_conv_kernel_dim=4, linear_key_head_dim=8, linear_value_head_dim=8,
+              linear_num_key_heads=2, linear_num_value_heads=4, max_position_embeddings=256, full_attention_interval=4)
+FAMILIES = {
+    "llama": ("llama", "LlamaConfig", "LlamaForCausalLM",
+              dict(vocab_size=320, hidden_size=64, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+                   intermediate_size=96, max_position_embeddings=256)),
+    "qwen3_moe": ("qwen3_moe", "Qwen3MoeConfig", "Qwen3MoeForCausalLM",
+                  dict(vocab_size=320, hidden_size=64, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+                       head_dim=16, moe_intermediate_size=32, num_experts_per_tok=2, num_experts=8, norm_topk_prob=True,
+                       max_position_embeddings=256, intermediate_size=96, decoder_sparse_step=1, mlp_only_layers=[])),
+    "deepseek_v3": ("deepseek_v3", "DeepseekV3Config", "DeepseekV3ForCausalLM",
+                    dict(vocab_size=320, hidden_size=64, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=4,
+                         intermediate_size=96, moe_intermediate_size=32, n_shared_experts=1, n_routed_experts=8,
+                         routed_scaling_factor=2.5, kv_lora_rank=16, q_lora_rank=24, qk_rope_head_dim=8, v_head_dim=16,
+                         qk_nope_head_dim=16, n_group=2, topk_group=1, num_experts_per_tok=2, first_k_dense_replace=1,
+                         norm_topk_prob=True, max_position_embeddings=256)),
+    "qwen3_5": ("qwen3_5", "Qwen3_5TextConfig", "Qwen3_5ForCausalLM", dict(HYBRID, intermediate_size=96)),
+    "qwen3_5_moe": ("qwen3_5_moe", "Qwen3_5MoeTextConfig", "Qwen3_5MoeForCausalLM",
+                    dict(HYBRID, moe_intermediate_size=32, shared_expert_intermediate_size=32, num_experts_per_tok=2,
+                         num_experts=8)),
+}
+
+
+def _tiny_checkpoint(name, path):
+    import importlib
+    mod, cfg_cls, model_cls, kw = FAMILIES[name]
+    try:
+        pkg = importlib.import_module(f"transformers.models.{mod}")
+        modelling = importlib.import_module(f"transformers.models.{mod}.modeling_{mod}")
+    except ImportError:
+        pytest.skip(f"this transformers has no {mod}")
+    hc = getattr(pkg, cfg_cls)(**kw, pad_token_id=0, eos_token_id=1, bos_token_id=2)
+    hc._attn_implementation = "eager"
+    torch.manual_seed(0)
+    m = getattr(modelling, model_cls)(hc).eval().float()
+    zero_centred = name.startswith("qwen3_5")          # this family stores norm weights as (w - 1)
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if "norm" in n and p.dim() == 1:
+                base = 0.0 if zero_centred and "linear_attn.norm" not in n else 1.0
+                p.copy_(base + 0.2 * torch.randn_like(p))
+            elif n.endswith("A_log"):
+                p.copy_(torch.randn_like(p) * 0.5)
+            elif n.endswith("dt_bias"):
+                p.copy_(torch.randn_like(p) * 0.3)
+            elif p.dim() >= 2:
+                p.copy_(torch.randn_like(p) * 0.08)
+        for n, b in m.named_buffers():
+            if n.endswith("e_score_correction_bias"):
+                b.copy_(torch.randn_like(b) * 0.3)
+    m.save_pretrained(str(path), safe_serialization=True)
+    return m
+
+
+@pytest.mark.parametrize("name", list(FAMILIES))
+def test_logits_and_greedy_tokens_match_transformers(tmp_path, name):
+    m = _tiny_checkpoint(name, tmp_path)
+    n = 40
+    ids = torch.randint(3, 320, (1, n), generator=torch.Generator().manual_seed(5))
+    with torch.no_grad():
+        ref = m(input_ids=ids).logits[0].float()
+        cont = m.generate(ids, max_new_tokens=6, do_sample=False)[0, n:].tolist()
+    cfg, w, _ = load_hf(str(tmp_path), "cpu", torch.float32)
+    ec = dict(ctx_size=128, max_seqs=2, block_size=16, max_batch_tokens=128)
+    eng = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(**ec), start=False)
+    seq = eng.prepare(GenerateRequest(prompt_tokens=ids[0].tolist(), sampling=SamplingParams(max_tokens=1)))
+    eng.waiting.push(seq)
+    eng._admit()
+    b = eng.build_batch([(seq, 0, n)])
+    b.logit_rows = None
+    with torch.no_grad():
+        mine = eng.model.forward(b, eng.kv, eng.states).logits.float()
+    assert (mine - ref).abs().max().item() < 2e-4
+    eng2 = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(prefill_chunk=16, **ec))
+    out = eng2.generate_text(tokens=ids[0].tolist(), max_tokens=6, ignore_eos=True).token_ids
+    eng2.shutdown()
+    assert out == cont
