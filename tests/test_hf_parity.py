@@ -2,7 +2,8 @@
 ``transformers`` package's own modelling code are read through the HF loader, and the prompt's logits at every
 position plus a greedy continuation (decoded through the engine with chunked prefill and the paged cache) must match
 what ``transformers`` computes. Families: llama, qwen3_moe, deepseek_v3 (latent attention, grouped sigmoid router with
-bias), qwen3_5 and qwen3_5_moe (Gated DeltaNet hybrid; the flagship family)."""
+bias), qwen3_next (fused, interleaved DeltaNet projections), qwen3_5 and qwen3_5_moe (Gated DeltaNet hybrid; the
+flagship family)."""
 import pytest
 import torch
 
@@ -29,6 +30,10 @@ FAMILIES = {
                          routed_scaling_factor=2.5, kv_lora_rank=16, q_lora_rank=24, qk_rope_head_dim=8, v_head_dim=16,
                          qk_nope_head_dim=16, n_group=2, topk_group=1, num_experts_per_tok=2, first_k_dense_replace=1,
                          norm_topk_prob=True, max_position_embeddings=256)),
+    "qwen3_next": ("qwen3_next", "Qwen3NextConfig", "Qwen3NextForCausalLM",
+                   dict(HYBRID, moe_intermediate_size=32, shared_expert_intermediate_size=32, num_experts_per_tok=2,
+                        num_experts=8, intermediate_size=96, decoder_sparse_step=1, mlp_only_layers=[],
+                        norm_topk_prob=True)),
     "qwen3_5": ("qwen3_5", "Qwen3_5TextConfig", "Qwen3_5ForCausalLM", dict(HYBRID, intermediate_size=96)),
     "qwen3_5_moe": ("qwen3_5_moe", "Qwen3_5MoeTextConfig", "Qwen3_5MoeForCausalLM",
                     dict(HYBRID, moe_intermediate_size=32, shared_expert_intermediate_size=32, num_experts_per_tok=2,
@@ -48,7 +53,7 @@ def _tiny_checkpoint(name, path):
     hc._attn_implementation = "eager"
     torch.manual_seed(0)
     m = getattr(modelling, model_cls)(hc).eval().float()
-    zero_centred = name.startswith("qwen3_5")          # this family stores norm weights as (w - 1)
+    zero_centred = name.startswith(("qwen3_5", "qwen3_next"))          # this family stores norm weights as (w - 1)
     with torch.no_grad():
         for n, p in m.named_parameters():
             if "norm" in n and p.dim() == 1:
