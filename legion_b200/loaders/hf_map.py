@@ -45,8 +45,8 @@ def config_from_hf(c: dict) -> ModelConfig:
         kw["mrope_interleaved"] = bool(rp.get("mrope_interleaved", False))
         if "rope_theta" in rp:
             kw["rope_theta"] = float(rp["rope_theta"])
-    if mt in ("qwen3", "qwen3_moe"):
-        kw.update(arch="qwen3moe" if mt == "qwen3_moe" else "qwen3", qk_norm=True)
+    if mt in ("qwen3", "qwen3_moe", "qwen3_vl_text", "qwen3_vl_moe_text", "qwen3_vl", "qwen3_vl_moe"):
+        kw.update(arch="qwen3moe" if "moe" in mt else "qwen3", qk_norm=True)
     elif mt in HYBRID_TYPES:
         moe = c.get("num_experts", 0) > 0
         kinds = c.get("layer_types")

@@ -255,3 +255,130 @@ def test_tower_from_a_hugging_face_checkpoint_directory(tmp_path):
     assert torch.allclose(tower.encode(pre.patches, pre.grid).rows, VisionTower(cfg, w).encode(pre.patches, pre.grid).rows)
     (tmp_path / "config.json").write_text(_json.dumps({"hidden_size": 24}))
     assert load_vision_hf(str(tmp_path)) is None
+
+
+def test_tower_matches_the_transformers_qwen3_vl_vision_model(tmp_path):
+    """A tiny random ``Qwen3VLVisionModel`` of the ``transformers`` package, saved under the names a checkpoint
+    directory uses and read through ``load_vision_hf``: merged rows and every deepstack tap equal what that
+    implementation computes for the same patches (patch embedding, resampled positions, 2-D rotary embedding in
+    merge order, blocks, mergers)."""
+    import json
+    import os
+    pytest.importorskip("transformers.models.qwen3_vl.modeling_qwen3_vl")
+    from safetensors.torch import save_file
+    from transformers.models.qwen3_vl.configuration_qwen3_vl import Qwen3VLVisionConfig
+    from transformers.models.qwen3_vl.modeling_qwen3_vl import Qwen3VLVisionModel
+    from legion_b200.loaders.vision import load_vision_hf
+    torch.manual_seed(0)
+    vc = Qwen3VLVisionConfig(depth=3, hidden_size=32, num_heads=4, intermediate_size=48, out_hidden_size=40,
+                             patch_size=4, temporal_patch_size=2, spatial_merge_size=2, num_position_embeddings=36,
+                             deepstack_visual_indexes=[0, 2], hidden_act="gelu_pytorch_tanh", in_channels=3)
+    vc._attn_implementation = "eager"
+    m = Qwen3VLVisionModel(vc).eval().float()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            p.copy_(torch.randn_like(p) * (0.1 if p.dim() >= 2 else 0.3)
+                    + (1.0 if ("norm" in n and n.endswith("weight")) else 0.0))
+    save_file({"model.visual." + k: v.contiguous() for k, v in m.state_dict().items()},
+              os.path.join(tmp_path, "model.safetensors"))
+    with open(os.path.join(tmp_path, "config.json"), "w") as f:
+        json.dump({"model_type": "qwen3_vl", "vision_config": vc.to_dict(), "text_config": {"hidden_size": 40}}, f)
+    tower, _ = load_vision_hf(str(tmp_path))
+    for gh, gw in ((6, 10), (4, 4)):
+        patches = torch.randn(gh * gw, 3 * 2 * 4 * 4)
+        with torch.no_grad():
+            want = m(patches, torch.tensor([[1, gh, gw]]))
+            got = tower.encode(patches, (1, gh, gw))
+        assert (got.rows - want.pooler_output).abs().max().item() < 1e-4
+        assert len(got.deepstack) == 2
+        for a, b in zip(got.deepstack, want.deepstack_features):
+            assert (a - b).abs().max().item() < 1e-4
+
+
+def test_image_prompt_matches_the_transformers_qwen3_vl_model(tmp_path):
+    """The whole image path against ``transformers``' ``Qwen3VLForConditionalGeneration`` on a tiny random checkpoint
+    it saved: text weights through the HF loader, the tower through ``load_vision_hf``; a prompt with two images
+    (placeholder expansion, tower rows in place of the placeholders, deepstack rows added after the first layers,
+    interleaved multi-section rotary positions and the position offset behind an image) gives the same logits at every
+    position, and the greedy continuation through the engine (chunked prefill that cuts through an image) is the
+    same."""
+    import io
+    pytest.importorskip("transformers.models.qwen3_vl.modeling_qwen3_vl")
+    from PIL import Image
+    from transformers.models.qwen3_vl.configuration_qwen3_vl import Qwen3VLConfig
+    from transformers.models.qwen3_vl.modeling_qwen3_vl import Qwen3VLForConditionalGeneration
+    from legion_b200.loaders.hf_map import load_hf
+    from legion_b200.loaders.vision import load_vision_hf
+    from legion_b200.vision.preprocess import decode_image, preprocess
+    torch.manual_seed(0)
+    IMG, VS, VE = 300, 301, 302
+    conf = Qwen3VLConfig(
+        text_config=dict(vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=3,
+                         num_attention_heads=4, num_key_value_heads=2, head_dim=32, max_position_embeddings=512,
+                         rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [6, 5, 5],
+                                          "mrope_interleaved": True},
+                         tie_word_embeddings=False, pad_token_id=0, eos_token_id=1, bos_token_id=2),
+        vision_config=dict(depth=3, hidden_size=32, num_heads=4, intermediate_size=48, out_hidden_size=64, patch_size=4,
+                           temporal_patch_size=2, spatial_merge_size=2, num_position_embeddings=36,
+                           deepstack_visual_indexes=[0, 1], hidden_act="gelu_pytorch_tanh", in_channels=3),
+        image_token_id=IMG, video_token_id=303, vision_start_token_id=VS, vision_end_token_id=VE,
+        tie_word_embeddings=False)
+    for c in (conf, conf.text_config, conf.vision_config):
+        c._attn_implementation = "eager"
+    m = Qwen3VLForConditionalGeneration(conf).eval().float()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if p.dim() >= 2:
+                p.copy_(torch.randn_like(p) * 0.08)
+            elif "norm" in n and n.endswith("weight"):
+                p.copy_(1.0 + 0.2 * torch.randn_like(p))
+            else:
+                p.copy_(0.2 * torch.randn_like(p))
+    m.save_pretrained(str(tmp_path), safe_serialization=True)
+    cfg, w, _ = load_hf(str(tmp_path), "cpu", torch.float32)
+    assert cfg.arch == "qwen3" and cfg.mrope_sections == (6, 5, 5) and cfg.mrope_interleaved
+    tower, _ = load_vision_hf(str(tmp_path))
+    hp = VisionHparams(patch_size=4, spatial_merge_size=2, min_tokens=2, max_tokens=64)
+
+    def picture(wd, ht, k):
+        im = Image.new("RGB", (wd, ht))
+        px = im.load()
+        for y in range(ht):
+            for x in range(wd):
+                px[x, y] = ((x * 7 + k) % 256, (y * 11 + 3 * k) % 256, (x * y + k) % 256)
+        buf = io.BytesIO()
+        im.save(buf, format="PNG")
+        return buf.getvalue()
+
+    images = [picture(40, 24, 1), picture(16, 32, 9)]
+    toks = [5, 17, 33, VS, IMG, VE, 44, 91, VS, IMG, VE, 12, 7, 250]
+
+    def make(**kw):
+        e = build_engine(cfg, weights=dict(w), start=kw.pop("start", False),
+                         engine_cfg=EngineConfig(ctx_size=256, max_seqs=2, block_size=16, max_batch_tokens=256, **kw))
+        e.attach_vision(VisionRuntime(tower, hp, image_token=IMG, start_token=VS, end_token=VE))
+        return e
+
+    eng = make()
+    seq = eng.prepare(GenerateRequest(prompt_tokens=toks, images=images, sampling=SamplingParams(max_tokens=1)))
+    eng.waiting.push(seq)
+    eng._admit()
+    n = len(seq.tokens)
+    b = eng.build_batch([(seq, 0, n)])
+    b.logit_rows = None
+    with torch.no_grad():
+        mine = eng.model.forward(b, eng.kv, eng.states).logits.float()
+    pre = [preprocess(decode_image(i), hp) for i in images]
+    ids = torch.tensor([seq.tokens])
+    feed = dict(pixel_values=torch.cat([p.patches for p in pre]), image_grid_thw=torch.tensor([list(p.grid) for p in pre]))
+    with torch.no_grad():
+        ref = m(input_ids=ids, mm_token_type_ids=(ids == IMG).long(), **feed).logits[0].float()
+        cont = m.generate(input_ids=ids, mm_token_type_ids=(ids == IMG).long(), max_new_tokens=6, do_sample=False,
+                          **feed)[0, n:].tolist()
+    assert n == len(toks) - 2 + sum(p.grid[1] * p.grid[2] // 4 for p in pre)
+    assert (mine - ref).abs().max().item() < 2e-4
+    eng2 = make(start=True, prefill_chunk=16)
+    out = eng2.generate(GenerateRequest(prompt_tokens=toks, images=images,
+                                        sampling=SamplingParams(max_tokens=6, ignore_eos=True))).collect()
+    eng2.shutdown()
+    assert out.token_ids == cont
