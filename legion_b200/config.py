@@ -98,6 +98,9 @@ class ModelConfig:
     # trailing layers that read an earlier layer's KV, a per-layer output scale, per-layer token embeddings, and in MoE
     # layers the dense FFN beside the routed experts (router on the normed residual scaled by 1 / sqrt(hidden))
     sandwich_norm: bool = False
+    # one sub-layer per block (Nemotron-H as shipped): ``layer_kinds`` then also holds "ffn" and "moe" entries, and a
+    # block is x + sublayer(norm(x)) with the mixer OR the feed-forward part, not both
+    block_form: bool = False
     embed_scale: float = 1.0
     swa_head_dim: int = 0              # 0 = head_dim
     swa_kv_heads: int = 0              # 0 = n_kv_head
@@ -129,6 +132,8 @@ class ModelConfig:
 
     # ---- derived
     def is_moe_layer(self, il: int) -> bool:
+        if self.block_form:
+            return il < len(self.layer_kinds) and self.layer_kinds[il] == "moe"
         return self.n_expert > 0 and il >= self.first_dense_layers
 
     def kv_layers(self) -> List[int]:
@@ -306,6 +311,16 @@ def tiny_nemotron_h_moe() -> ModelConfig:
     return c
 
 
+def tiny_nemotron_h_blocks() -> ModelConfig:
+    """Nemotron-H the way its checkpoints lay it out: one sub-layer per block (``block_form``), here Mamba-2 with two
+    norm groups, a dense squared-ReLU FFN, attention without rotary embedding, and the latent MoE."""
+    c = tiny_nemotron_h_moe()
+    c.block_form, c.first_dense_layers, c.ssm_groups = True, 0, 2
+    c.layer_kinds = ["mamba2", "ffn", "nope", "moe", "mamba2", "moe"]
+    c.n_layer = len(c.layer_kinds)
+    return c
+
+
 def tiny_gemma4() -> ModelConfig:
     """Gemma 4 in miniature (``src/model/gemma4.rs:1-30``): sandwich norms, scaled embedding, sliding-window layers
     with 64-wide heads and 2 kv heads next to global layers with 128-wide heads, 1 kv head, keys used as values and
@@ -325,6 +340,7 @@ PRESETS = {
     "tiny-muse": tiny_muse,
     "tiny-gemma4": tiny_gemma4,
     "tiny-nemotron-h-moe": tiny_nemotron_h_moe,
+    "tiny-nemotron-h-blocks": tiny_nemotron_h_blocks,
     "tiny-gemma": tiny_gemma,
     "tiny-nemotron-h": tiny_nemotron_h,
     "tiny-hybrid-moe": tiny_hybrid_moe,

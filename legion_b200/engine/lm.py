@@ -299,7 +299,7 @@ class LmEngine(Engine):
         """Mamba-2 layers decode from CUDA graphs when their head shape runs on the scan kernel (the token loop that
         serves other shapes reads sequence bounds on the host)."""
         m = self.mcfg
-        if "kda" in m.layer_kinds or m.hyper_streams > 1 or m.sandwich_norm:
+        if "kda" in m.layer_kinds or m.hyper_streams > 1 or m.sandwich_norm or m.block_form:
             return False          # forward paths built from tensor operations (no captured decode step)
         if "mamba2" not in m.layer_kinds:
             return True

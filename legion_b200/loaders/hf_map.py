@@ -2,7 +2,7 @@
 
 ``config.json`` ``model_type`` selects the mapper: ``qwen3`` / ``qwen3_moe`` / ``llama`` / ``mistral``,
 ``qwen3_next`` / ``qwen3_5`` / ``qwen3_5_moe`` (hybrid Gated DeltaNet), ``deepseek_v3`` (MLA), ``gemma4`` /
-``gemma4_text`` (``hf_gemma4``).
+``gemma4_text`` (``hf_gemma4``), ``nemotron_h`` (``hf_nemotron``).
 Transforms applied while loading the Qwen3.5 family (``src/hf/qwen35.rs:6-20`` in the reference):
 ``A_log -> -exp(A_log)``; RMSNorm weights stored as (w - 1) get +1 (all but the DeltaNet output norm);
 fused ``in_proj_qkvz`` / ``in_proj_ba`` are de-interleaved per key head; conv1d ``[C, 1, k]`` is squeezed;
@@ -19,7 +19,7 @@ import torch
 
 from ..config import ModelConfig
 from ..models.weights import is_fp32_weight, weight_shapes
-from . import hf_gemma4
+from . import hf_gemma4, hf_nemotron
 from . import quant_formats as qf
 from .safetensors_io import Checkpoint, save_file
 
@@ -29,6 +29,8 @@ HYBRID_TYPES = ("qwen3_next", "qwen3_5", "qwen3_5_moe", "qwen3_5_text", "qwen3_5
 def config_from_hf(c: dict) -> ModelConfig:
     if (c.get("text_config") or c).get("model_type") in hf_gemma4.MODEL_TYPES or c.get("model_type") == "gemma4":
         return hf_gemma4.config_from_hf(c)
+    if c.get("model_type") in hf_nemotron.MODEL_TYPES:
+        return hf_nemotron.config_from_hf(c)
     c = dict(c.get("text_config") or c)
     mt = c.get("model_type", "llama")
     n_head = c["num_attention_heads"]
@@ -200,6 +202,9 @@ def load_hf(path: str, device="cpu", dtype=torch.float32, keep_quant: bool = Fal
     if (ck.config.get("text_config") or ck.config).get("model_type") in hf_gemma4.MODEL_TYPES \
             or ck.config.get("model_type") == "gemma4":
         cfg, w = hf_gemma4.load(_Source(ck, torch.device(device), dtype), ck.config, dtype)
+        return cfg, w, ck
+    if ck.config.get("model_type") in hf_nemotron.MODEL_TYPES:
+        cfg, w = hf_nemotron.load(_Source(ck, torch.device(device), dtype), ck.config, dtype)
         return cfg, w, ck
     cfg = config_from_hf(ck.config)
     src = _Source(ck, torch.device(device), dtype)

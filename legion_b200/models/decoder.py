@@ -781,6 +781,38 @@ class Decoder:
         pc.end_step()
         return out
 
+    def _forward_blocks(self, b: StepBatch, kv: KvCache, st: Optional[StatePool], want_logits: bool) -> StepOutput:
+        """One sub-layer per block (Nemotron-H as its checkpoints lay it out, ``src/model/nemotron_h.rs`` in the
+        reference): x = x + sublayer(norm(x)), the sub-layer being a Mamba-2 mixer, attention without rotary
+        embedding, a squared-ReLU FFN or the (latent) MoE. Runs on one rank from the framework's ops."""
+        cfg, w, pc = self.cfg, self.w, self.pctx
+
+        def whole(t):
+            if isinstance(t, PendingLinear):
+                return ops.linear(t.x, t.w)
+            return t.materialize() if hasattr(t, "materialize") else t
+
+        x = b.embeds if b.embeds is not None else self.embed(b.token_ids)
+        for il in range(cfg.n_layer):
+            p, kind = f"l{il}", cfg.layer_kinds[il]
+            h = ops.rmsnorm(x, w[f"{p}.attn_norm"], cfg.rms_eps, cfg.norm_offset)[0]
+            if kind in ("attn", "swa", "nope"):
+                y = self._attn(p, il, h, b, kv, cfg.sliding_window if kind == "swa" else 0, rope=kind != "nope")
+            elif kind == "mamba2":
+                y = self._mamba2(p, il, h, b, st)
+            elif kind in ("ffn", "moe"):
+                y = self._ffn(p, kind == "moe", h, None)[0]
+            else:
+                raise ValueError(f"block form: unknown block kind {kind}")
+            x = (x.float() + whole(y).float()).to(x.dtype)
+        rows = x if b.logit_rows is None else x.index_select(0, b.logit_rows)
+        hidden, _ = ops.rmsnorm(rows, w["output_norm"], cfg.rms_eps, cfg.norm_offset)
+        out = StepOutput(hidden=hidden, last_hidden=x, captures={})
+        if want_logits:
+            out.logits = self.logits(hidden)
+        pc.end_step()
+        return out
+
     # ------------------------------------------------------------------ hyper-connections
     def _hc_pre(self, name: str, X):
         """Mixer in front of a sublayer (``ops.rs::cpu_hc_pre`` in the reference). X [T, hc, H] float32 streams ->
@@ -898,7 +930,12 @@ class Decoder:
         if x.is_cuda and ops.sm100.mamba2_scan_ok(nh, hd, ng, ds) and x.dtype == torch.bfloat16:
             yz = ops.sm100.mamba2_scan(xbc, dt, z, w[f"{p}.ssm.A"], w[f"{p}.ssm.D"], w[f"{p}.ssm.dt_bias"], st.ssm[il],
                                        b.cu_q, b.state_slots, nh, hd, ng, ds, write_state=b.write_state)
-            yn, _ = ops.rmsnorm(yz, w[f"{p}.ssm.norm"], cfg.rms_eps, 0.0)
+            if ng > 1:
+                # the gated norm works per group of channels: unit-weight norm over each group, then the weights
+                g = ops.rmsnorm(yz.view(T * ng, di // ng), self._ones(di // ng, yz), cfg.rms_eps, 0.0)[0]
+                yn = (g.view(T, di).float() * w[f"{p}.ssm.norm"].float()).to(yz.dtype)
+            else:
+                yn, _ = ops.rmsnorm(yz, w[f"{p}.ssm.norm"], cfg.rms_eps, 0.0)
             return ops.linear(yn, w[f"{p}.ssm.out"])
         xs = xbc[:, :di].float().view(T, nh, hd)
         Bm = xbc[:, di:di + ng * ds].float().view(T, ng, ds)
@@ -920,9 +957,16 @@ class Decoder:
                 y[t] = torch.einsum("hds,hs->hd", S, Ct) + Dp[:, None] * xs[t]
             if b.write_state:
                 st.ssm[il][slots[i]] = S
-        yz = y.view(T, di) * F.silu(z.float())
-        yn = yz * torch.rsqrt(yz.pow(2).mean(-1, keepdim=True) + cfg.rms_eps) * w[f"{p}.ssm.norm"].float()
+        yz = (y.view(T, di) * F.silu(z.float())).view(T, ng, di // ng)       # the gated norm works per group
+        yn = (yz * torch.rsqrt(yz.pow(2).mean(-1, keepdim=True) + cfg.rms_eps)).view(T, di) * w[f"{p}.ssm.norm"].float()
         return ops.linear(yn.to(x.dtype), w[f"{p}.ssm.out"])
+
+    def _ones(self, n: int, like) -> torch.Tensor:
+        key = (n, like.device)
+        cache = self.__dict__.setdefault("_ones_cache", {})
+        if key not in cache:
+            cache[key] = torch.ones(n, device=like.device, dtype=torch.float32)      # norm weights are float32
+        return cache[key]
 
     def _route(self, p: str, x, norm=None):
         cfg, w, pc = self.cfg, self.w, self.pctx
@@ -1122,6 +1166,8 @@ class Decoder:
             return self._forward_hc(b, kv, st, want_logits)
         if self.cfg.sandwich_norm:
             return self._forward_gemma(b, kv, want_logits)
+        if self.cfg.block_form:
+            return self._forward_blocks(b, kv, st, want_logits)
         cfg, w, pc = self.cfg, self.w, self.pctx
         x = b.embeds if b.embeds is not None else self.embed(b.token_ids)
         resid = None

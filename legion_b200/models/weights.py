@@ -23,6 +23,12 @@ def layer_weight_shapes(cfg: ModelConfig, il: int, prefix: Optional[str] = None,
     kind = kind or cfg.layer_kinds[il]
     moe = cfg.is_moe_layer(il) if moe is None else moe
     H = cfg.hidden
+    if cfg.block_form and prefix is None:
+        # one sub-layer per block: its input norm plus either the mixer's or the feed-forward part's tensors
+        if kind in ("ffn", "moe"):
+            return _ffn_shapes(cfg, p, kind == "moe", {f"{p}.attn_norm": (H,)})
+        full = layer_weight_shapes(cfg, il, prefix=p, kind=kind, moe=False)
+        return {k: v for k, v in full.items() if not (k.startswith(f"{p}.mlp.") or k == f"{p}.ffn_norm")}
     s: Dict[str, Tuple[int, ...]] = {f"{p}.attn_norm": (H,), f"{p}.ffn_norm": (H,)}
     if cfg.sandwich_norm and kind in ("attn", "swa") and prefix is None:
         return gemma_layer_shapes(cfg, il, s)
@@ -95,6 +101,12 @@ def layer_weight_shapes(cfg: ModelConfig, il: int, prefix: Optional[str] = None,
         if cfg.hyper_mode == "gated":                   # the mixers take the place of the pre-norms
             s.pop(f"{p}.attn_norm", None)
             s.pop(f"{p}.ffn_norm", None)
+    return _ffn_shapes(cfg, p, moe, s)
+
+
+def _ffn_shapes(cfg: ModelConfig, p: str, moe: bool, s: Dict[str, Tuple[int, ...]]) -> Dict[str, Tuple[int, ...]]:
+    """The feed-forward part of a layer: routed experts (router, latent projections, shared expert) or the dense FFN."""
+    H = cfg.hidden
     if moe:
         E, F = cfg.n_expert, cfg.expert_ff
         s[f"{p}.moe.router"] = (E, H)
@@ -267,7 +279,7 @@ class Shard:
         if dp_attention:
             self.kv_rep = 1
             return
-        if world > 1 and ("kda" in cfg.layer_kinds or cfg.hyper_streams > 1 or cfg.sandwich_norm):
+        if world > 1 and ("kda" in cfg.layer_kinds or cfg.hyper_streams > 1 or cfg.sandwich_norm or cfg.block_form):
             raise NotImplementedError("Kimi-delta-attention layers, hyper-connections and the Gemma-4 layer form run "
                                       "on one rank (their weights have no tensor-parallel split here)")
         assert cfg.n_head % world == 0, "query heads must divide by the TP degree"

@@ -418,3 +418,31 @@ def test_gemma4_hf_checkpoint_against_transformers(tmp_path, variant):
     out = eng2.generate_text(tokens=ids[0].tolist(), max_tokens=6, ignore_eos=True).token_ids
     eng2.shutdown()
     assert out == cont
+
+
+def test_block_form_engine_invariants():
+    """One sub-layer per block (Nemotron-H as shipped), including a dense FFN block: batched == single, chunked
+    prefill == one pass, and a repeated prompt resumes from the prefix cache's state snapshots."""
+    cfg = PRESETS["tiny-nemotron-h-blocks"]()
+    w = random_weights(cfg, "cpu", torch.float32, seed=3, std=0.05)
+    assert "l1.mlp.down" in w and "l1.attn.qkv" not in w and "l0.mlp.down" not in w and "l3.moe.lat_down" in w
+    ec = dict(ctx_size=256, max_seqs=4, block_size=16, max_batch_tokens=128)
+    eng = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(**ec))
+    prompts = [list(range(5 + i, 75 + 3 * i)) for i in range(3)]
+    single = [eng.generate_text(tokens=p, max_tokens=10, ignore_eos=True).token_ids for p in prompts]
+    import threading
+    got = [None] * 3
+
+    def go(i):
+        got[i] = eng.generate_text(tokens=prompts[i], max_tokens=10, ignore_eos=True).token_ids
+
+    ts = [threading.Thread(target=go, args=(i,)) for i in range(3)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    r = eng.generate_text(tokens=prompts[0], max_tokens=10, ignore_eos=True)
+    eng.shutdown()
+    assert got == single and r.token_ids == single[0] and r.usage.cached_tokens > 0
+    eng2 = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(prefill_chunk=16, prefix_cache=False, **ec))
+    chunked = eng2.generate_text(tokens=prompts[1], max_tokens=10, ignore_eos=True).token_ids
+    eng2.shutdown()
+    assert chunked == single[1]

@@ -95,3 +95,64 @@ def test_logits_and_greedy_tokens_match_transformers(tmp_path, name):
     out = eng2.generate_text(tokens=ids[0].tolist(), max_tokens=6, ignore_eos=True).token_ids
     eng2.shutdown()
     assert out == cont
+
+
+@pytest.mark.parametrize("latent", [False, True])
+def test_nemotron_h_blocks_match_transformers(tmp_path, latent):
+    """Nemotron-H as its checkpoints lay it out (one sub-layer per block: Mamba-2 with two norm groups, attention
+    without rotary embedding, MoE with a grouped sigmoid router, selection bias, shared expert and optional latent
+    projections) against ``transformers``' implementation. Its scan runs as one chunk here: across chunk boundaries
+    that package's pure-PyTorch scan disagrees with its own single-chunk and step forms."""
+    try:
+        from transformers.models.nemotron_h import NemotronHConfig
+        from transformers.models.nemotron_h.modeling_nemotron_h import NemotronHForCausalLM
+    except ImportError:
+        pytest.skip("this transformers has no nemotron_h")
+    torch.manual_seed(0)
+    hc = NemotronHConfig(vocab_size=320, hidden_size=64, layers_block_type=["mamba", "moe", "attention", "moe", "mamba", "moe"],
+                         num_attention_heads=4, num_key_value_heads=2, head_dim=16, max_position_embeddings=256,
+                         intermediate_size=96, ssm_state_size=16, mamba_num_heads=8, mamba_head_dim=8, n_groups=2,
+                         conv_kernel=4, chunk_size=64, n_routed_experts=8, n_shared_experts=1, moe_intermediate_size=32,
+                         moe_shared_expert_intermediate_size=48, moe_latent_size=24 if latent else None,
+                         num_experts_per_tok=2, routed_scaling_factor=2.5, n_group=2, topk_group=1, norm_topk_prob=True,
+                         use_mamba_kernels=False, pad_token_id=0, bos_token_id=1, eos_token_id=2)
+    hc._attn_implementation = "eager"
+    m = NemotronHForCausalLM(hc).eval().float()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if n.endswith("A_log"):
+                p.copy_(torch.randn_like(p) * 0.5)
+            elif n.endswith("dt_bias") or n.endswith(".D") or n.endswith("conv1d.bias"):
+                p.copy_(torch.randn_like(p) * 0.3)
+            elif "norm" in n and p.dim() == 1:
+                p.copy_(1.0 + 0.2 * torch.randn_like(p))
+            elif p.dim() >= 2:
+                p.copy_(torch.randn_like(p) * 0.08)
+        for n, b in m.named_buffers():
+            if n.endswith("e_score_correction_bias"):
+                b.copy_(torch.randn_like(b) * 0.3)
+    m.save_pretrained(str(tmp_path), safe_serialization=True)
+    n = 40
+    ids = torch.randint(3, 320, (1, n), generator=torch.Generator().manual_seed(5))
+    with torch.no_grad():
+        ref = m(input_ids=ids).logits[0].float()
+        cont = m.generate(ids, max_new_tokens=6, do_sample=False)[0, n:].tolist()
+    cfg, w, _ = load_hf(str(tmp_path), "cpu", torch.float32)
+    assert cfg.block_form and cfg.layer_kinds == ["mamba2", "moe", "nope", "moe", "mamba2", "moe"]
+    assert cfg.moe_latent == (24 if latent else 0) and cfg.ssm_groups == 2
+    ec = dict(ctx_size=128, max_seqs=2, block_size=16, max_batch_tokens=128)
+    eng = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(**ec), start=False)
+    seq = eng.prepare(GenerateRequest(prompt_tokens=ids[0].tolist(), sampling=SamplingParams(max_tokens=1)))
+    eng.waiting.push(seq)
+    eng._admit()
+    b = eng.build_batch([(seq, 0, n)])
+    b.logit_rows = None
+    with torch.no_grad():
+        mine = eng.model.forward(b, eng.kv, eng.states).logits.float()
+    assert (mine - ref).abs().max().item() < 2e-4
+    eng2 = build_engine(cfg, weights=dict(w), engine_cfg=EngineConfig(prefill_chunk=16, **ec))
+    out = eng2.generate_text(tokens=ids[0].tolist(), max_tokens=6, ignore_eos=True).token_ids
+    # the same model through batching and the prefix cache: engine invariants hold for the block form too
+    again = eng2.generate_text(tokens=ids[0].tolist(), max_tokens=6, ignore_eos=True).token_ids
+    eng2.shutdown()
+    assert out == cont and again == cont
