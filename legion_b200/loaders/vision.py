@@ -79,6 +79,8 @@ def load_vision_hf(path: str, device="cpu", dtype=torch.float32) -> Optional[Tup
     if not vc:
         return None
     lm = conf.get("text_config", conf)
+    if vc.get("model_type") == "gemma4_vision":
+        return load_gemma4_vision_hf(path, vc, int(lm["hidden_size"]), device, dtype)
     cfg = config_from_hf(vc, lm.get("hidden_size"))
     ck = Checkpoint(path)
     prefix = next((p for p in ("model.visual.", "visual.") if ck.has(p + "pos_embed.weight")), None)
@@ -106,12 +108,14 @@ def load_vision_hf(path: str, device="cpu", dtype=torch.float32) -> Optional[Tup
 
 
 def load_mmproj(path: str, device="cpu", dtype=torch.float32) -> Tuple[VisionTower, VisionHparams]:
-    """A ``clip`` mmproj GGUF with the ``qwen3vl_merger`` projector."""
+    """A ``clip`` mmproj GGUF with the ``qwen3vl_merger`` or the ``gemma4v`` projector."""
     from .gguf import GgufFile
     g = GgufFile(path)
     md = g.metadata
     arch = md.get("general.architecture", "")
     proj = md.get("clip.vision.projector_type", md.get("clip.projector_type", ""))
+    if arch == "clip" and proj == "gemma4v":
+        return _load_gemma4v_mmproj(g, device, dtype)
     if arch != "clip" or proj != "qwen3vl_merger":
         raise ValueError(f"unsupported vision architecture / projector: {arch}/{proj}")
 
@@ -168,3 +172,126 @@ def write_tiny_mmproj(path: str, cfg: Optional[VisionConfig] = None, seed: int =
     wr.add_tensor("v.patch_embd.weight.1", pw[:, :, 1].contiguous())
     wr.write()
     return cfg
+
+
+def load_gemma4_vision_hf(path: str, vc: dict, lm_hidden: int, device="cpu", dtype=torch.float32):
+    """The Gemma 4 tower of a Hugging Face checkpoint directory (``model.vision_tower.*`` and the projection
+    ``model.embed_vision.*``). The patch projection's columns go from the checkpoint's (row, column, channel) order
+    inside a patch to the channel-major order the preprocessor emits. Pixels stay in [0, 1] (the tower rescales);
+    the grid is aligned to the pooling kernel."""
+    from ..vision.gemma4v import Gemma4VisionConfig, Gemma4VisionTower
+    from .safetensors_io import Checkpoint
+    if vc.get("use_clipped_linears"):
+        raise ValueError("gemma4 vision: towers with clipped linears are not supported")
+    rope = vc.get("rope_parameters") or {}
+    nh = int(vc["num_attention_heads"])
+    cfg = Gemma4VisionConfig(depth=int(vc["num_hidden_layers"]), hidden=int(vc["hidden_size"]), n_head=nh,
+                             n_kv_head=int(vc.get("num_key_value_heads") or nh),
+                             head_dim=int(vc.get("head_dim") or int(vc["hidden_size"]) // nh),
+                             intermediate=int(vc["intermediate_size"]), out_hidden=lm_hidden,
+                             patch_size=int(vc.get("patch_size", 16)), spatial_merge_size=int(vc.get("pooling_kernel_size", 3)),
+                             num_pos=int(vc.get("position_embedding_size", 10240)),
+                             act={"gelu_pytorch_tanh": "gelu_tanh", "gelu": "gelu", "silu": "silu"}.get(
+                                 vc.get("hidden_activation", "gelu_pytorch_tanh"), "gelu_tanh"),
+                             ln_eps=float(vc.get("rms_norm_eps", 1e-6)), rope_theta=float(rope.get("rope_theta", 100.0)),
+                             standardize=bool(vc.get("standardize", False)))
+    ck = Checkpoint(path)
+    V = next((p for p in ("model.vision_tower.", "vision_tower.") if ck.has(p + "patch_embedder.input_proj.weight")), None)
+    if V is None:
+        return None
+    E = V.replace("vision_tower.", "embed_vision.")
+    to = lambda t: t.to(device=device, dtype=dtype)           # noqa: E731
+    P = cfg.patch_size
+    pw = ck.get(V + "patch_embedder.input_proj.weight")
+    table = ck.get(V + "patch_embedder.position_embedding_table")
+    w = {"patch.w": to(pw.reshape(pw.shape[0], P, P, 3).permute(0, 3, 1, 2).reshape(pw.shape[0], -1).contiguous()),
+         "pos.x": to(table[0]), "pos.y": to(table[1]), "proj.w": to(ck.get(E + "embedding_projection.weight"))}
+    if cfg.standardize:
+        w["std.bias"], w["std.scale"] = to(ck.get(V + "std_bias")), to(ck.get(V + "std_scale"))
+    names = {"q.w": "self_attn.q_proj.linear.weight", "k.w": "self_attn.k_proj.linear.weight",
+             "v.w": "self_attn.v_proj.linear.weight", "o.w": "self_attn.o_proj.linear.weight",
+             "q_norm.w": "self_attn.q_norm.weight", "k_norm.w": "self_attn.k_norm.weight",
+             "ln1.w": "input_layernorm.weight", "post_attn.w": "post_attention_layernorm.weight",
+             "ln2.w": "pre_feedforward_layernorm.weight", "post_ffn.w": "post_feedforward_layernorm.weight",
+             "gate.w": "mlp.gate_proj.linear.weight", "up.w": "mlp.up_proj.linear.weight",
+             "down.w": "mlp.down_proj.linear.weight"}
+    for i in range(cfg.depth):
+        for ours, theirs in names.items():
+            w[f"blk{i}.{ours}"] = to(ck.get(f"{V}encoder.layers.{i}.{theirs}"))
+    k = cfg.spatial_merge_size
+    hp = VisionHparams(patch_size=P, spatial_merge_size=k, temporal_patch_size=1, image_mean=(0.0, 0.0, 0.0),
+                       image_std=(1.0, 1.0, 1.0), resize="stretch", min_tokens=1, max_tokens=280)
+    return Gemma4VisionTower(cfg, w), hp
+
+
+_G4V_BLOCK = {"ln1.w": "ln1", "ln2.w": "ln2", "post_attn.w": "attn_post_norm", "post_ffn.w": "ffn_post_norm", "q.w": "attn_q",
+              "k.w": "attn_k", "v.w": "attn_v", "o.w": "attn_out", "q_norm.w": "attn_q_norm", "k_norm.w": "attn_k_norm",
+              "gate.w": "ffn_gate", "up.w": "ffn_up", "down.w": "ffn_down"}
+
+
+def _load_gemma4v_mmproj(g, device, dtype):
+    """The ``gemma4v`` projector of a ``clip`` mmproj (tensor names as the reference lists them,
+    ``src/vision/gemma4v.rs::names``): the patch convolution kernel is the patch projection, the position tensor
+    holds the column table and the row table, ``mm.input_projection`` maps the pooled rows to the model's width."""
+    from ..vision.gemma4v import Gemma4VisionConfig, Gemma4VisionTower
+    md = g.metadata
+    if any(n.endswith(".input_min") or n.endswith(".output_min") for n in g.tensors):
+        raise ValueError("gemma4v with clipped linears is not supported")
+
+    def need(key):
+        if f"clip.vision.{key}" not in md:
+            raise ValueError(f"missing vision metadata: clip.vision.{key}")
+        return md[f"clip.vision.{key}"]
+
+    hidden, depth, nh = int(need("embedding_length")), int(need("block_count")), int(need("attention.head_count"))
+    pos = g.torch("v.position_embd.weight")
+    if pos.dim() != 3 or pos.shape[0] != 2:
+        raise ValueError("v.position_embd.weight: not two tables")
+    proj = g.torch("mm.input_projection.weight")
+    kw = g.torch("v.blk.0.attn_k.weight")
+    cfg = Gemma4VisionConfig(depth=depth, hidden=hidden, n_head=nh, n_kv_head=kw.shape[0] // (hidden // nh),
+                             head_dim=hidden // nh, intermediate=int(need("feed_forward_length")),
+                             out_hidden=int(proj.shape[0]), patch_size=int(need("patch_size")),
+                             spatial_merge_size=int(md.get("clip.vision.projector.scale_factor", 3)),
+                             num_pos=int(pos.shape[1]), ln_eps=float(md.get("clip.vision.attention.layer_norm_epsilon", 1e-6)),
+                             standardize="v.std_bias" in g.tensors)
+    to = lambda t: t.to(device=device, dtype=dtype)           # noqa: E731
+    w = {"patch.w": to(g.torch("v.patch_embd.weight").reshape(hidden, -1)), "pos.x": to(pos[0]), "pos.y": to(pos[1]),
+         "proj.w": to(proj)}
+    if cfg.standardize:
+        w["std.bias"], w["std.scale"] = to(g.torch("v.std_bias")), to(g.torch("v.std_scale"))
+    for i in range(depth):
+        for ours, theirs in _G4V_BLOCK.items():
+            w[f"blk{i}.{ours}"] = to(g.torch(f"v.blk.{i}.{theirs}.weight"))
+    # the tower takes pixels in [0, 1] and rescales them itself; 70 .. 1120 rows per image
+    hp = VisionHparams(patch_size=cfg.patch_size, spatial_merge_size=cfg.spatial_merge_size, temporal_patch_size=1,
+                       image_mean=(0.0, 0.0, 0.0), image_std=(1.0, 1.0, 1.0), resize="stretch", min_tokens=70,
+                       max_tokens=1120)
+    return Gemma4VisionTower(cfg, w), hp
+
+
+def write_tiny_gemma4v_mmproj(path: str, cfg=None, seed: int = 0):
+    """A small ``gemma4v`` mmproj with random weights (tests and demos)."""
+    from ..vision.gemma4v import Gemma4VisionConfig, random_gemma4v_weights
+    from .gguf import GgufWriter
+    cfg = cfg or Gemma4VisionConfig(standardize=True)
+    w = random_gemma4v_weights(cfg, seed=seed)
+    wr = GgufWriter(path, "clip")
+    wr.add("clip.vision.projector_type", "gemma4v")
+    for k, v in (("embedding_length", cfg.hidden), ("block_count", cfg.depth), ("attention.head_count", cfg.n_head),
+                 ("feed_forward_length", cfg.intermediate), ("patch_size", cfg.patch_size),
+                 ("projector.scale_factor", cfg.spatial_merge_size)):
+        wr.add(f"clip.vision.{k}", int(v))
+    wr.add("clip.vision.attention.layer_norm_epsilon", float(cfg.ln_eps))
+    P = cfg.patch_size
+    wr.add_tensor("v.patch_embd.weight", w["patch.w"].float().reshape(cfg.hidden, 3, P, P).contiguous())
+    wr.add_tensor("v.position_embd.weight", torch.stack([w["pos.x"], w["pos.y"]]).float().contiguous())
+    wr.add_tensor("mm.input_projection.weight", w["proj.w"])
+    if cfg.standardize:
+        wr.add_tensor("v.std_bias", w["std.bias"])
+        wr.add_tensor("v.std_scale", w["std.scale"])
+    for i in range(cfg.depth):
+        for ours, theirs in _G4V_BLOCK.items():
+            wr.add_tensor(f"v.blk.{i}.{theirs}.weight", w[f"blk{i}.{ours}"])
+    wr.write()
+    return cfg, w

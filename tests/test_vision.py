@@ -382,3 +382,65 @@ def test_image_prompt_matches_the_transformers_qwen3_vl_model(tmp_path):
                                         sampling=SamplingParams(max_tokens=6, ignore_eos=True))).collect()
     eng2.shutdown()
     assert out.token_ids == cont
+
+
+def test_gemma4_tower_matches_the_transformers_vision_model_and_round_trips_as_mmproj(tmp_path):
+    """The Gemma 4 tower (two position tables, rotary embedding in two halves of a head, normed q / k / v, sandwich
+    norms, k x k average pool, standardisation, un-weighted norm and projection) read from a checkpoint written with
+    ``transformers``' ``Gemma4VisionModel`` and ``Gemma4MultimodalEmbedder``: the rows for a random image equal that
+    implementation's soft tokens after its embedder; the preprocessor's channel-major, merge-order patches against
+    the package's raster (row, column, channel) patches are part of what is compared. Then the ``gemma4v`` mmproj
+    form: written, read back, same rows."""
+    import json
+    import os
+    pytest.importorskip("transformers.models.gemma4.modeling_gemma4")
+    from safetensors.torch import save_file
+    from transformers.models.gemma4.configuration_gemma4 import Gemma4TextConfig, Gemma4VisionConfig as HC
+    from transformers.models.gemma4.modeling_gemma4 import Gemma4MultimodalEmbedder, Gemma4VisionModel
+    from legion_b200.loaders.vision import load_mmproj, load_vision_hf, write_tiny_gemma4v_mmproj
+    from legion_b200.vision.gemma4v import Gemma4VisionTower
+    from legion_b200.vision.preprocess import preprocess
+    torch.manual_seed(0)
+    vc = HC(hidden_size=32, intermediate_size=48, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=4,
+            head_dim=8, pooling_kernel_size=3, patch_size=4, position_embedding_size=32, standardize=True,
+            use_clipped_linears=False, rope_parameters={"rope_type": "default", "rope_theta": 100.0})
+    vc._attn_implementation = "eager"
+    tc = Gemma4TextConfig(hidden_size=40, num_hidden_layers=2, layer_types=["sliding_attention", "full_attention"],
+                          vocab_size=64, intermediate_size=32, num_attention_heads=2, num_key_value_heads=1, head_dim=8)
+    vm, em = Gemma4VisionModel(vc).eval().float(), Gemma4MultimodalEmbedder(vc, tc).eval().float()
+    with torch.no_grad():
+        for mod in (vm, em):
+            for n, p in mod.named_parameters():
+                p.copy_(torch.randn_like(p) * (0.15 if p.dim() >= 2 else 0.2) + (1.0 if "norm" in n else 0.0))
+        vm.std_bias.copy_(torch.randn(32) * 0.2)
+        vm.std_scale.copy_(1 + 0.2 * torch.randn(32))
+    sd = {"model.vision_tower." + k: v.contiguous() for k, v in vm.state_dict().items()}
+    sd.update({"model.embed_vision." + k: v.contiguous() for k, v in em.state_dict().items()})
+    save_file(sd, os.path.join(tmp_path, "model.safetensors"))
+    with open(os.path.join(tmp_path, "config.json"), "w") as f:
+        json.dump({"model_type": "gemma4", "vision_config": vc.to_dict(), "text_config": {"hidden_size": 40}}, f)
+    tower, hp = load_vision_hf(str(tmp_path))
+    assert isinstance(tower, Gemma4VisionTower) and hp.temporal_patch_size == 1 and hp.spatial_merge_size == 3
+    gh, gw = 6, 9
+    img = torch.randint(0, 256, (gh * 4, gw * 4, 3), dtype=torch.uint8)
+    hp.image_min_pixels = hp.image_max_pixels = gh * gw * 16
+    pre = preprocess(img, hp)
+    assert pre.grid == (1, gh, gw)
+    got = tower.encode(pre.patches, pre.grid)
+    x = (img.float() / 255).permute(2, 0, 1)
+    pv = x.reshape(3, gh, 4, gw, 4).permute(1, 3, 2, 4, 0).reshape(gh * gw, -1)[None]
+    pos = torch.stack(torch.meshgrid(torch.arange(gw), torch.arange(gh), indexing="xy"), -1).reshape(-1, 2)[None]
+    with torch.no_grad():
+        want = em(vm(pixel_values=pv, pixel_position_ids=pos).last_hidden_state)
+    assert got.rows.shape == want.shape == (6, 40) and got.grid == (1, 2, 3)
+    assert (got.rows - want).abs().max().item() < 1e-4
+    # the mmproj form of the same kind of tower
+    path = str(tmp_path / "g4v.gguf")
+    cfg, w = write_tiny_gemma4v_mmproj(path, seed=3)
+    t2, hp2 = load_mmproj(path)
+    assert isinstance(t2, Gemma4VisionTower) and t2.cfg.standardize and hp2.max_tokens == 1120
+    P, k = cfg.patch_size, cfg.spatial_merge_size
+    patches = torch.rand(2 * k * k, 3 * P * P)
+    a = Gemma4VisionTower(cfg, w).encode(patches, (1, k, 2 * k)).rows
+    b = t2.encode(patches, (1, k, 2 * k)).rows
+    assert a.shape == (2, cfg.out_hidden) and torch.allclose(a, b, atol=1e-5)
