@@ -86,6 +86,11 @@ def config_from_gguf(md: dict) -> ModelConfig:
         kw["gdn_v_dim"] = inner // kw["gdn_v_heads"]
     if kw["vocab"] is None:
         kw["vocab"] = len(md.get("tokenizer.ggml.tokens", [])) or 0
+    sc_kind = g("rope.scaling.type")
+    if sc_kind in ("linear", "yarn") and float(g("rope.scaling.factor", 1.0)) != 1.0:
+        kw["rope_scaling"] = {"type": sc_kind, "factor": float(g("rope.scaling.factor")),
+                              "original_max_position_embeddings": int(g("rope.scaling.original_context_length",
+                                                                        kw["max_position"]))}
     if a == "deepseek2":
         kw.update(q_lora=int(g("attention.q_lora_rank", 0)), kv_lora=int(g("attention.kv_lora_rank", 0)),
                   qk_rope_dim=int(g("rope.dimension_count", 64)), v_head_dim=int(g("attention.value_length", 128)),
@@ -94,6 +99,14 @@ def config_from_gguf(md: dict) -> ModelConfig:
                   route_scale=float(g("expert_weights_scale", 1.0)), n_group=int(g("expert_group_count", 1)),
                   topk_group=int(g("expert_group_used_count", 1)), router_bias=True)
         kw["qk_nope_dim"] = head_dim - kw["qk_rope_dim"]
+        sc = kw.get("rope_scaling")
+        if sc and sc["type"] == "yarn" and g("rope.scaling.yarn_log_multiplier") is not None:
+            # this family's YaRN: cos / sin stay unscaled, the softmax scale takes the square of
+            # 1 + multiplier * ln(factor)
+            import math
+            m = 1.0 + float(g("rope.scaling.yarn_log_multiplier")) * math.log(sc["factor"])
+            sc["attention_factor"] = 1.0
+            kw["attn_scale"] = head_dim ** -0.5 * m * m
     return ModelConfig(**kw)
 
 

@@ -41,6 +41,10 @@ def config_from_hf(c: dict) -> ModelConfig:
               tie_embeddings=bool(c.get("tie_word_embeddings", False)),
               max_position=int(c.get("max_position_embeddings", 131072)), rope_scaling=c.get("rope_scaling"))
     rp = c.get("rope_scaling") or c.get("rope_parameters") or {}
+    if isinstance(rp, dict) and "rope_theta" in rp and "rope_theta" not in c:
+        kw["rope_theta"] = float(rp["rope_theta"])
+    if isinstance(rp, dict) and rp.get("rope_type", rp.get("type", "default")) not in ("default", None):
+        kw["rope_scaling"] = dict(rp)         # newer configs keep the scaling beside the base in ``rope_parameters``
     if isinstance(rp, dict) and rp.get("mrope_section"):
         # vision-language checkpoints: rotary frequencies turn with (temporal, row, column) positions
         kw["mrope_sections"] = tuple(int(v) for v in rp["mrope_section"][:3])
@@ -72,6 +76,12 @@ def config_from_hf(c: dict) -> ModelConfig:
                   router_bias=c.get("topk_method", "noaux_tc") == "noaux_tc", n_group=c.get("n_group", 1),
                   topk_group=c.get("topk_group", 1), route_scale=float(c.get("routed_scaling_factor", 1.0)),
                   norm_topk=bool(c.get("norm_topk_prob", True)), mtp_layers=int(c.get("num_nextn_predict_layers", 0)))
+        sc = kw.get("rope_scaling") or {}
+        if sc.get("rope_type", sc.get("type")) == "yarn" and sc.get("mscale_all_dim"):
+            # this family also scales the softmax by the square of the all-dimension YaRN term
+            from ..ops.reference import yarn_mscale
+            m = yarn_mscale(float(sc.get("factor", 1.0)), float(sc["mscale_all_dim"]))
+            kw["attn_scale"] = (c["qk_nope_head_dim"] + c["qk_rope_head_dim"]) ** -0.5 * m * m
     else:
         kw.update(arch="llama" if mt in ("llama", "mistral") else mt, qk_norm=False)
     if mt not in ("deepseek_v3", "deepseek_v2", "kimi_k2"):

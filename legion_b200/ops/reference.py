@@ -56,6 +56,7 @@ def rope_cos_sin(max_pos: int, rot: int, theta: float, scaling: Optional[dict] =
     """Table [max_pos, rot] = [cos(rot/2) | sin(rot/2)] in float32."""
     half = rot // 2
     inv_freq = 1.0 / (theta ** (torch.arange(0, half, dtype=torch.float64, device=device) / half))
+    mag = 1.0
     if scaling:
         kind = scaling.get("type", scaling.get("rope_type", "linear"))
         factor = float(scaling.get("factor", 1.0))
@@ -73,9 +74,44 @@ def rope_cos_sin(max_pos: int, rot: int, theta: float, scaling: Optional[dict] =
             mid = (1 - smooth) * inv_freq / factor + smooth * inv_freq
             is_mid = (wavelen <= orig / low) & (wavelen >= orig / high)
             inv_freq = torch.where(is_mid, mid, scaled)
+        elif kind == "yarn":
+            # NTK-by-parts: high-frequency pairs keep their wavelength, low-frequency pairs are interpolated by
+            # ``factor``, a linear ramp between the pairs that turn beta_fast and beta_slow times over the original
+            # context; cos and sin carry the attention factor (0.1 ln(factor) + 1 unless the checkpoint gives one,
+            # or the ratio of its two mscale terms)
+            orig = float(scaling.get("original_max_position_embeddings") or max_pos)
+            fast, slow = float(scaling.get("beta_fast") or 32.0), float(scaling.get("beta_slow") or 1.0)
+
+            def corr(n_rot):
+                return rot * math.log(orig / (n_rot * 2 * math.pi)) / (2 * math.log(theta))
+
+            lo, hi = corr(fast), corr(slow)
+            if scaling.get("truncate", True):
+                lo, hi = math.floor(lo), math.ceil(hi)
+            lo, hi = max(lo, 0), min(hi, rot - 1)
+            if lo == hi:
+                hi += 0.001
+            ramp = ((torch.arange(half, dtype=torch.float64, device=device) - lo) / (hi - lo)).clamp(0, 1)
+            inv_freq = inv_freq / factor * ramp + inv_freq * (1 - ramp)
+            mag = yarn_attention_factor(scaling)
     pos = torch.arange(max_pos, dtype=torch.float64, device=device)
     ang = pos[:, None] * inv_freq[None, :]
-    return torch.cat([ang.cos(), ang.sin()], dim=-1).float()
+    return (torch.cat([ang.cos(), ang.sin()], dim=-1) * mag).float()
+
+
+def yarn_mscale(factor: float, m: float = 1.0) -> float:
+    return 1.0 if factor <= 1 else 0.1 * m * math.log(factor) + 1.0
+
+
+def yarn_attention_factor(scaling: dict) -> float:
+    """What YaRN multiplies cos and sin with (so attention scores grow by its square)."""
+    if scaling.get("attention_factor") is not None:
+        return float(scaling["attention_factor"])
+    factor = float(scaling.get("factor", 1.0))
+    m, m_all = scaling.get("mscale"), scaling.get("mscale_all_dim")
+    if m and m_all:
+        return yarn_mscale(factor, float(m)) / yarn_mscale(factor, float(m_all))
+    return yarn_mscale(factor)
 
 
 def apply_rope(x, cos_sin, positions, rot: int):

@@ -30,6 +30,24 @@ FAMILIES = {
                          routed_scaling_factor=2.5, kv_lora_rank=16, q_lora_rank=24, qk_rope_head_dim=8, v_head_dim=16,
                          qk_nope_head_dim=16, n_group=2, topk_group=1, num_experts_per_tok=2, first_k_dense_replace=1,
                          norm_topk_prob=True, max_position_embeddings=256)),
+    # rotary scaling as real checkpoints use it: Llama-3.1's frequency-dependent scaling, DeepSeek's YaRN (which also
+    # scales the softmax by the square of its all-dimension term)
+    "llama_scaled": ("llama", "LlamaConfig", "LlamaForCausalLM",
+                     dict(vocab_size=320, hidden_size=64, num_hidden_layers=3, num_attention_heads=4,
+                          num_key_value_heads=2, intermediate_size=96, max_position_embeddings=256,
+                          rope_parameters={"rope_type": "llama3", "rope_theta": 10000.0, "factor": 8.0,
+                                           "original_max_position_embeddings": 32, "low_freq_factor": 1.0,
+                                           "high_freq_factor": 4.0})),
+    "deepseek_v3_yarn": ("deepseek_v3", "DeepseekV3Config", "DeepseekV3ForCausalLM",
+                         dict(vocab_size=320, hidden_size=64, num_hidden_layers=3, num_attention_heads=4,
+                              num_key_value_heads=4, intermediate_size=96, moe_intermediate_size=32, n_shared_experts=1,
+                              n_routed_experts=8, routed_scaling_factor=2.5, kv_lora_rank=16, q_lora_rank=24,
+                              qk_rope_head_dim=8, v_head_dim=16, qk_nope_head_dim=16, n_group=2, topk_group=1,
+                              num_experts_per_tok=2, first_k_dense_replace=1, norm_topk_prob=True,
+                              max_position_embeddings=256,
+                              rope_parameters={"rope_type": "yarn", "rope_theta": 10000.0, "factor": 8.0,
+                                               "original_max_position_embeddings": 32, "beta_fast": 32, "beta_slow": 1,
+                                               "mscale": 1.0, "mscale_all_dim": 1.0})),
     "qwen3_next": ("qwen3_next", "Qwen3NextConfig", "Qwen3NextForCausalLM",
                    dict(HYBRID, moe_intermediate_size=32, shared_expert_intermediate_size=32, num_experts_per_tok=2,
                         num_experts=8, intermediate_size=96, decoder_sparse_step=1, mlp_only_layers=[],
