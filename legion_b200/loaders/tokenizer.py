@@ -287,8 +287,28 @@ class BpeTokenizer(Tokenizer):
                     eos.append(added[t])
             return Gemma4Tokenizer(tokens, merges, bos_id=tok_id("bos_token"), eos_ids=eos,
                                    chat_template=cfg.get("chat_template"), extra_special=added.keys(), visible=shown)
-        return cls(tokens, merges, pre="qwen2", bos_id=tok_id("bos_token"), eos_ids=eos,
-                   chat_template=cfg.get("chat_template"), extra_special=added.keys(), visible=shown)
+        tok = cls(tokens, merges, pre="qwen2", bos_id=tok_id("bos_token"), eos_ids=eos,
+                  chat_template=cfg.get("chat_template"), extra_special=added.keys(), visible=shown)
+        pat = _hf_pre_pattern(tj.get("pre_tokenizer"))
+        if pat is not None:
+            tok.pat = pat
+        return tok
+
+
+def _hf_pre_pattern(pre):
+    """The cut pattern a ``tokenizer.json`` pre-tokeniser describes: the regex of its ``Split`` step, or GPT-2's when
+    a ``ByteLevel`` step does the cutting itself; None when there is none to read (the family default stays)."""
+    steps = pre.get("pretokenizers", [pre]) if isinstance(pre, dict) else []
+    for st in steps:
+        if st.get("type") == "Split" and isinstance(st.get("pattern"), dict) and st["pattern"].get("Regex"):
+            try:
+                return _re.compile(st["pattern"]["Regex"])
+            except Exception:
+                return None
+    for st in steps:
+        if st.get("type") == "ByteLevel" and st.get("use_regex", True):
+            return _re.compile(PRE_PATTERNS["gpt2"])
+    return None
 
 
 class Gemma4Tokenizer(BpeTokenizer):

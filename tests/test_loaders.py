@@ -457,3 +457,37 @@ def test_chat_format_is_read_from_the_vocabulary():
     assert (q.kind, q.tool_format, q.stop_ids) == ("plain", "hermes", (0,))
     assert q.starts_in_reasoning("<|im_start|>assistant\n<think>\n")
     assert not ChatFormat(Tok(["a"])).starts_in_reasoning("<think>")
+
+
+@pytest.mark.parametrize("pre", ["qwen2", "llama3", "gpt2"])
+def test_byte_level_bpe_against_the_tokenizers_library(tmp_path, pre):
+    """Byte-level BPE: a vocabulary trained with the ``tokenizers`` library behind the family's pre-tokeniser pattern,
+    saved as ``tokenizer.json`` and loaded here, gives that library's ids on contractions, digit runs, whitespace
+    runs, newlines, punctuation and non-Latin text; the long-text path (pre-tokens encoded on several threads) gives
+    the same ids as the serial loop."""
+    tk = pytest.importorskip("tokenizers")
+    from tokenizers import Regex, decoders, models, pre_tokenizers, trainers
+    from legion_b200.loaders.tokenizer import PRE_PATTERNS, BpeTokenizer
+    t = tk.Tokenizer(models.BPE())
+    t.pre_tokenizer = pre_tokenizers.Sequence([
+        pre_tokenizers.Split(Regex(PRE_PATTERNS[pre]), behavior="isolated", invert=False),
+        pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)])
+    t.decoder = decoders.ByteLevel()
+    corpus = ["The quick brown fox doesn't jump over 12345 lazy dogs!  It's 3.14159...\n\n\tIndented line\r\n",
+              "def f(x):\n    return x + 1  # comment\n\n\nprint(f(2))\n", "naïve café — “quotes” and emoji \U0001F600 ok",
+              "Привет, мир! 你好，世界。 こんにちは", "a  b   c    d\n \n  \n", "I'LL we'Ve THEY'RE x's"] * 3
+    t.train_from_iterator(corpus, trainers.BpeTrainer(vocab_size=600, show_progress=False,
+                                                      initial_alphabet=pre_tokenizers.ByteLevel.alphabet(),
+                                                      special_tokens=["<|endoftext|>", "<|im_start|>", "<|im_end|>"]))
+    t.save(str(tmp_path / "tokenizer.json"))
+    mine = BpeTokenizer.from_hf_dir(str(tmp_path))
+    assert mine.pat.pattern == PRE_PATTERNS[pre]              # read from the file's pre-tokeniser
+    texts = corpus[:6] + ["  leading", "trailing  ", "x\n\n\ny", "1234567 89", "<|im_start|>user\nhi<|im_end|>\n",
+                          "tabs\t\tand spaces  \n", "can't won't I'd they'll", "end.\n"]
+    for text in texts:
+        want = t.encode(text, add_special_tokens=False).ids
+        assert mine.encode(text) == want, (pre, text)
+        assert mine.decode(want) == t.decode(want, skip_special_tokens=False)
+    long = " ".join(corpus) * 50
+    assert len(long) >= mine.PARALLEL_CHARS
+    assert mine.encode(long) == t.encode(long, add_special_tokens=False).ids
