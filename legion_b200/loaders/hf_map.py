@@ -371,8 +371,26 @@ def load_hf(path: str, device="cpu", dtype=torch.float32, keep_quant: bool = Fal
         else:
             attention(lp, p)
         ffn(lp, p, cfg.is_moe_layer(il))
+    # the draft head (MTP), when the checkpoint ships it: DeepSeek appends it as layer n_layer + j with the fusion
+    # tensors beside the block's, the hybrid family keeps it under ``mtp.``; checkpoints without it lose the flag
+    for j in range(cfg.mtp_layers):
+        mp = f"mtp{j}"
+        if hybrid:
+            lp, names = f"mtp.layers.{j}.", ("mtp.fc", "mtp.pre_fc_norm_embedding.weight", "mtp.pre_fc_norm_hidden.weight",
+                                             "mtp.norm.weight")
+        else:
+            lp = f"{P}layers.{cfg.n_layer + j}."
+            names = (lp + "eh_proj", lp + "enorm.weight", lp + "hnorm.weight", lp + "shared_head.norm.weight")
+        if not src.has(names[0] + ".weight"):
+            cfg.mtp_layers = j
+            break
+        w[f"{mp}.eh_proj"] = src.weight(names[0])
+        w[f"{mp}.enorm"], w[f"{mp}.hnorm"], w[f"{mp}.shared_head_norm"] = norm(names[1]), norm(names[2]), norm(names[3])
+        w[f"{mp}.l.attn_norm"] = norm(lp + "input_layernorm.weight")
+        w[f"{mp}.l.ffn_norm"] = norm(lp + "post_attention_layernorm.weight")
+        (mla if cfg.kv_lora > 0 else attention)(lp, f"{mp}.l")
+        ffn(lp, f"{mp}.l", cfg.n_expert > 0)
     # the engine applies ``norm_offset`` at run time, so (w - 1) checkpoints are kept as stored
-    _ = hybrid
     out = {}
     for k, v in w.items():
         if not isinstance(v, torch.Tensor):
@@ -425,11 +443,27 @@ def save_hf(path: str, cfg: ModelConfig, w: Dict[str, torch.Tensor], quant: str 
     if "output" in w:
         put("lm_head", w["output"], False)
     D = cfg.head_dim
-    for il in range(cfg.n_layer):
-        lp, p = f"{P}layers.{il}.", f"l{il}"
+    blocks = [(f"{P}layers.{il}.", f"l{il}", cfg.layer_kinds[il], cfg.is_moe_layer(il)) for il in range(cfg.n_layer)]
+    hybrid = cfg.arch in ("qwen35", "qwen35moe")
+    for j in range(cfg.mtp_layers if f"mtp0.eh_proj" in w else 0):
+        # the draft head: DeepSeek appends it as layer n_layer + j, the hybrid family keeps it under ``mtp.``
+        mp = f"mtp{j}"
+        if hybrid:
+            lp = f"mtp.layers.{j}."
+            put("mtp.fc", w[f"{mp}.eh_proj"], False)
+            t["mtp.pre_fc_norm_embedding.weight"] = w[f"{mp}.enorm"].cpu().to(dtype)
+            t["mtp.pre_fc_norm_hidden.weight"] = w[f"{mp}.hnorm"].cpu().to(dtype)
+            t["mtp.norm.weight"] = w[f"{mp}.shared_head_norm"].cpu().to(dtype)
+        else:
+            lp = f"{P}layers.{cfg.n_layer + j}."
+            put(lp + "eh_proj", w[f"{mp}.eh_proj"], False)
+            t[lp + "enorm.weight"] = w[f"{mp}.enorm"].cpu().to(dtype)
+            t[lp + "hnorm.weight"] = w[f"{mp}.hnorm"].cpu().to(dtype)
+            t[lp + "shared_head.norm.weight"] = w[f"{mp}.shared_head_norm"].cpu().to(dtype)
+        blocks.append((lp, f"{mp}.l", "mla" if cfg.kv_lora > 0 else "attn", cfg.n_expert > 0))
+    for lp, p, kind, moe_block in blocks:
         t[lp + "input_layernorm.weight"] = w[f"{p}.attn_norm"].cpu().to(dtype)
         t[lp + "post_attention_layernorm.weight"] = w[f"{p}.ffn_norm"].cpu().to(dtype)
-        kind = cfg.layer_kinds[il]
         if kind in ("attn", "swa", "nope"):
             a = lp + "self_attn."
             qkv = w[f"{p}.attn.qkv"]
@@ -466,7 +500,7 @@ def save_hf(path: str, cfg: ModelConfig, w: Dict[str, torch.Tensor], quant: str 
             t[a + "kv_a_layernorm.weight"] = w[f"{p}.mla.kv_a_norm"].cpu().to(dtype)
             put(a + "kv_b_proj", w[f"{p}.mla.kv_b"])
             put(a + "o_proj", w[f"{p}.mla.o"])
-        if cfg.is_moe_layer(il):
+        if moe_block:
             pre = lp + "mlp."
             put(pre + "gate", w[f"{p}.moe.router"], False)
             if f"{p}.moe.router_bias" in w:
@@ -514,13 +548,14 @@ def hf_config_dict(cfg: ModelConfig, quant: str = "none") -> dict:
          "rope_theta": cfg.rope_theta, "rms_norm_eps": cfg.rms_eps, "tie_word_embeddings": cfg.tie_embeddings,
          "max_position_embeddings": cfg.max_position, "torch_dtype": "bfloat16"}
     if cfg.arch in ("qwen35", "qwen35moe"):
-        d.update(model_type="qwen3_5_moe" if cfg.n_expert else "qwen3_5",
+        d.update(model_type="qwen3_5_moe" if cfg.n_expert else "qwen3_5", mtp_num_hidden_layers=cfg.mtp_layers,
                  layer_types=["linear_attention" if k == "gdn" else "full_attention" for k in cfg.layer_kinds],
                  partial_rotary_factor=cfg.rope_dim / cfg.head_dim, linear_num_key_heads=cfg.gdn_k_heads,
                  linear_num_value_heads=cfg.gdn_v_heads, linear_key_head_dim=cfg.gdn_k_dim,
                  linear_value_head_dim=cfg.gdn_v_dim, linear_conv_kernel_dim=cfg.gdn_conv)
     elif cfg.arch == "deepseek_v3":
-        d.update(model_type="deepseek_v3", q_lora_rank=cfg.q_lora or None, kv_lora_rank=cfg.kv_lora,
+        d.update(model_type="deepseek_v3", num_nextn_predict_layers=cfg.mtp_layers,
+                 q_lora_rank=cfg.q_lora or None, kv_lora_rank=cfg.kv_lora,
                  qk_nope_head_dim=cfg.qk_nope_dim, qk_rope_head_dim=cfg.qk_rope_dim, v_head_dim=cfg.v_head_dim,
                  intermediate_size=cfg.dense_ff, first_k_dense_replace=cfg.first_dense_layers,
                  n_routed_experts=cfg.n_expert, num_experts_per_tok=cfg.top_k, moe_intermediate_size=cfg.expert_ff,

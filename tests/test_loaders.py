@@ -491,3 +491,37 @@ def test_byte_level_bpe_against_the_tokenizers_library(tmp_path, pre):
     long = " ".join(corpus) * 50
     assert len(long) >= mine.PARALLEL_CHARS
     assert mine.encode(long) == t.encode(long, add_special_tokens=False).ids
+
+
+@pytest.mark.parametrize("preset", ["tiny-hybrid-moe", "tiny-mla-moe"])
+def test_hf_checkpoints_carry_the_draft_head(tmp_path, preset):
+    """The MTP head in Hugging Face naming (``mtp.*`` for the hybrid family, layer ``n_layer`` with ``eh_proj`` /
+    ``enorm`` / ``hnorm`` / ``shared_head.norm`` for DeepSeek): written, read back tensor for tensor, and drafting
+    with it equals plain greedy decoding; a checkpoint without the head loads with the flag cleared."""
+    from legion_b200.config import PRESETS
+    from legion_b200.engine.lm import EngineConfig, build_engine
+    from legion_b200.loaders.hf_map import load_hf, save_hf
+    from legion_b200.models.weights import random_weights
+    cfg = PRESETS[preset]()
+    cfg.mtp_layers = 1
+    w = random_weights(cfg, "cpu", torch.float32, seed=2, std=0.05)
+    assert "mtp0.eh_proj" in w
+    d1 = str(tmp_path / "with")
+    save_hf(d1, cfg, w, dtype=torch.float32)
+    cfg2, w2, _ = load_hf(d1, "cpu", torch.float32)
+    assert cfg2.mtp_layers == 1 and set(w2) == set(w)
+    for k in w:
+        assert torch.allclose(w[k].float(), w2[k].float(), atol=1e-6), k
+    ec = dict(ctx_size=256, max_seqs=2, block_size=16, max_batch_tokens=128)
+    toks = list(range(7, 60))
+    plain = build_engine(cfg2, weights=dict(w2), engine_cfg=EngineConfig(**ec))
+    want = plain.generate_text(tokens=toks, max_tokens=12, ignore_eos=True).token_ids
+    plain.shutdown()
+    spec = build_engine(cfg2, weights=dict(w2), engine_cfg=EngineConfig(spec="mtp", spec_k=2, **ec))
+    got = spec.generate_text(tokens=toks, max_tokens=12, ignore_eos=True).token_ids
+    spec.shutdown()
+    assert got == want
+    d2 = str(tmp_path / "without")
+    save_hf(d2, cfg, {k: v for k, v in w.items() if not k.startswith("mtp")}, dtype=torch.float32)
+    cfg3, w3, _ = load_hf(d2, "cpu", torch.float32)
+    assert cfg3.mtp_layers == 0 and not any(k.startswith("mtp") for k in w3)
