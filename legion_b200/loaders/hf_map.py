@@ -92,6 +92,14 @@ def config_from_hf(c: dict) -> ModelConfig:
                       norm_topk=bool(c.get("norm_topk_prob", True)),
                       shared_ff=c.get("shared_expert_intermediate_size", 0) or 0)
             kw["shared_gate"] = kw["shared_ff"] > 0
+            dense = sorted(int(i) for i in (c.get("mlp_only_layers") or []))
+            if dense or int(c.get("decoder_sparse_step", 1) or 1) != 1:
+                # dense layers are modelled as a leading run only
+                if dense != list(range(len(dense))) or int(c.get("decoder_sparse_step", 1) or 1) != 1:
+                    raise ValueError("dense FFN layers between MoE layers (mlp_only_layers / decoder_sparse_step) are "
+                                     "supported only as a leading run")
+                kw["first_dense_layers"] = len(dense)
+                kw["dense_ff"] = c["intermediate_size"]
         else:
             kw["dense_ff"] = c["intermediate_size"]
     return ModelConfig(**kw)

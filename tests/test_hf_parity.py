@@ -24,6 +24,12 @@ FAMILIES = {
                   dict(vocab_size=320, hidden_size=64, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
                        head_dim=16, moe_intermediate_size=32, num_experts_per_tok=2, num_experts=8, norm_topk_prob=True,
                        max_position_embeddings=256, intermediate_size=96, decoder_sparse_step=1, mlp_only_layers=[])),
+    # a leading dense layer, router weights left un-normalised
+    "qwen3_moe_dense_first": ("qwen3_moe", "Qwen3MoeConfig", "Qwen3MoeForCausalLM",
+                              dict(vocab_size=320, hidden_size=64, num_hidden_layers=3, num_attention_heads=4,
+                                   num_key_value_heads=2, head_dim=16, moe_intermediate_size=32, num_experts_per_tok=2,
+                                   num_experts=8, norm_topk_prob=False, max_position_embeddings=256,
+                                   intermediate_size=96, decoder_sparse_step=1, mlp_only_layers=[0])),
     "deepseek_v3": ("deepseek_v3", "DeepseekV3Config", "DeepseekV3ForCausalLM",
                     dict(vocab_size=320, hidden_size=64, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=4,
                          intermediate_size=96, moe_intermediate_size=32, n_shared_experts=1, n_routed_experts=8,
