@@ -252,7 +252,13 @@ def load_hf(path: str, device="cpu", dtype=torch.float32, keep_quant: bool = Fal
         if ck.has(pre + "experts.gate_up_proj"):                  # already fused [E, H, 2F] or [E, 2F, H]
             gu = src.raw(pre + "experts.gate_up_proj")[e_lo:e_hi]
             dn = src.raw(pre + "experts.down_proj")[e_lo:e_hi]
-            if gu.shape[1] == cfg.hidden:
+            # [E, H, 2F] / [E, F, H] (older exports) or [E, 2F, H] / [E, H, F]: told apart by whichever of the two
+            # tensors is not square-ambiguous
+            if dn.shape[1] != dn.shape[2]:
+                flipped = dn.shape[2] == cfg.hidden
+            else:
+                flipped = gu.shape[1] == cfg.hidden and gu.shape[2] != cfg.hidden
+            if flipped:
                 gu, dn = gu.transpose(1, 2), dn.transpose(1, 2)
             w[f"{p}.moe.gate_up"], w[f"{p}.moe.down"] = gu.contiguous(), dn.contiguous()
             return

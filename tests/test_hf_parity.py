@@ -180,3 +180,52 @@ def test_nemotron_h_blocks_match_transformers(tmp_path, latent):
     again = eng2.generate_text(tokens=ids[0].tolist(), max_tokens=6, ignore_eos=True).token_ids
     eng2.shutdown()
     assert out == cont and again == cont
+
+
+def test_qwen3_vl_moe_text_path_matches_transformers(tmp_path):
+    """The language model of a Qwen3-VL-MoE checkpoint (weights under ``model.language_model.``, experts stored fused
+    as ``experts.gate_up_proj`` [E, 2F, H], multi-section rotary configuration) on a text prompt; sized so that 2F
+    equals the hidden width, where the fused tensor alone cannot tell its layout."""
+    try:
+        from transformers.models.qwen3_vl_moe.configuration_qwen3_vl_moe import Qwen3VLMoeConfig
+        from transformers.models.qwen3_vl_moe.modeling_qwen3_vl_moe import Qwen3VLMoeForConditionalGeneration
+    except ImportError:
+        pytest.skip("this transformers has no qwen3_vl_moe")
+    torch.manual_seed(0)
+    conf = Qwen3VLMoeConfig(
+        text_config=dict(vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=3, num_attention_heads=4,
+                         num_key_value_heads=2, head_dim=32, max_position_embeddings=512, moe_intermediate_size=32,
+                         num_experts=8, num_experts_per_tok=2, decoder_sparse_step=1, mlp_only_layers=[],
+                         norm_topk_prob=True, pad_token_id=0, eos_token_id=1, bos_token_id=2,
+                         rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [6, 5, 5],
+                                          "mrope_interleaved": True}),
+        vision_config=dict(depth=2, hidden_size=32, num_heads=4, intermediate_size=48, out_hidden_size=64, patch_size=4,
+                           temporal_patch_size=2, spatial_merge_size=2, num_position_embeddings=36,
+                           deepstack_visual_indexes=[0], hidden_act="gelu_pytorch_tanh", in_channels=3),
+        image_token_id=300, video_token_id=303, vision_start_token_id=301, vision_end_token_id=302,
+        tie_word_embeddings=False)
+    for c in (conf, conf.text_config, conf.vision_config):
+        c._attn_implementation = "eager"
+    m = Qwen3VLMoeForConditionalGeneration(conf).eval().float()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if p.dim() >= 2:
+                p.copy_(torch.randn_like(p) * 0.08)
+            elif "norm" in n and n.endswith("weight"):
+                p.copy_(1.0 + 0.2 * torch.randn_like(p))
+    m.save_pretrained(str(tmp_path), safe_serialization=True)
+    ids = torch.randint(3, 299, (1, 30), generator=torch.Generator().manual_seed(5))
+    with torch.no_grad():
+        ref = m(input_ids=ids).logits[0].float()
+    cfg, w, _ = load_hf(str(tmp_path), "cpu", torch.float32)
+    assert cfg.arch == "qwen3moe" and cfg.n_expert == 8 and cfg.mrope_sections == (6, 5, 5)
+    eng = build_engine(cfg, weights=dict(w), start=False,
+                       engine_cfg=EngineConfig(ctx_size=128, max_seqs=2, block_size=16, max_batch_tokens=128))
+    seq = eng.prepare(GenerateRequest(prompt_tokens=ids[0].tolist(), sampling=SamplingParams(max_tokens=1)))
+    eng.waiting.push(seq)
+    eng._admit()
+    b = eng.build_batch([(seq, 0, 30)])
+    b.logit_rows = None
+    with torch.no_grad():
+        mine = eng.model.forward(b, eng.kv, eng.states).logits.float()
+    assert (mine - ref).abs().max().item() < 2e-4
