@@ -279,6 +279,35 @@ def dequantize(raw: np.ndarray, ggml_type: int, shape: Tuple[int, ...]) -> np.nd
         # scale index for element l of quarter j: j * 2 + l // 16
         s = sc.reshape(n, 2, 4, 2)
         out = (q.reshape(n, 2, 4, 2, 16) * s[..., None]).reshape(n, 256) * d
+    elif name == "Q2_K":
+        # 16 groups of 16: a 4-bit scale and a 4-bit minimum each; 2-bit values, four per byte, the four bit pairs
+        # of a 32-byte run giving four consecutive groups of 32
+        scb = blk[:, 0:16]
+        qs = blk[:, 16:80].reshape(n, 2, 1, 32)
+        d, dmin = _f16(blk[:, 80:82].copy()), _f16(blk[:, 82:84].copy())
+        shifts = np.array([0, 2, 4, 6], dtype=np.uint8).reshape(1, 1, 4, 1)
+        q = ((qs >> shifts) & 3).astype(np.float32).reshape(n, 16, 16)         # [n, half, pair, 32] -> groups of 16
+        sc = (scb & 0xF).astype(np.float32)
+        mn = (scb >> 4).astype(np.float32)
+        out = (q * (d * sc)[:, :, None] - (dmin * mn)[:, :, None]).reshape(n, 256)
+    elif name == "Q3_K":
+        # 2 low bits as in Q2_K plus a high bit from the mask bytes (bit j of byte l for the j-th group of 32;
+        # a clear bit subtracts 4); 16 six-bit scales, offset by 32, packed into 12 bytes
+        hm = blk[:, 0:32]
+        qs = blk[:, 32:96].reshape(n, 2, 1, 32)
+        a = blk[:, 96:108].copy().view(np.uint32).reshape(n, 3)
+        d = _f16(blk[:, 108:110].copy())
+        k1, k2 = np.uint32(0x03030303), np.uint32(0x0F0F0F0F)
+        a0, a1, tmp = a[:, 0], a[:, 1], a[:, 2]
+        aux = np.stack([(a0 & k2) | ((tmp & k1) << 4), (a1 & k2) | (((tmp >> 2) & k1) << 4),
+                        ((a0 >> 4) & k2) | (((tmp >> 4) & k1) << 4), ((a1 >> 4) & k2) | (((tmp >> 6) & k1) << 4)], axis=1)
+        sc = np.ascontiguousarray(aux).view(np.int8).reshape(n, 16).astype(np.float32) - 32.0
+        shifts = np.array([0, 2, 4, 6], dtype=np.uint8).reshape(1, 1, 4, 1)
+        low = ((qs >> shifts) & 3).astype(np.int16)                              # [n, 2, 4, 32]
+        bits = np.arange(8, dtype=np.uint8).reshape(1, 8, 1)
+        high = ((hm[:, None, :] >> bits) & 1).astype(np.int16).reshape(n, 2, 4, 32)
+        q = (low - 4 * (1 - high)).astype(np.float32).reshape(n, 16, 16)
+        out = (q * (d * sc)[:, :, None]).reshape(n, 256)
     else:
         raise NotImplementedError(f"GGUF tensor type {name} is not supported")
     return out.astype(np.float32).reshape(shape)

@@ -525,3 +525,68 @@ def test_hf_checkpoints_carry_the_draft_head(tmp_path, preset):
     save_hf(d2, cfg, {k: v for k, v in w.items() if not k.startswith("mtp")}, dtype=torch.float32)
     cfg3, w3, _ = load_hf(d2, "cpu", torch.float32)
     assert cfg3.mtp_layers == 0 and not any(k.startswith("mtp") for k in w3)
+
+
+def test_gguf_codecs_and_files_against_the_gguf_package(tmp_path):
+    """llama.cpp's own Python package as the oracle: block formats it can encode (Q8_0, Q4_0, Q4_1, Q5_0, Q5_1) and
+    random well-formed blocks of those it can only decode (Q2_K .. Q6_K, IQ4_NL) expand to the same floats bit for
+    bit; a file it writes (metadata of every kind, F32 / F16 / Q8_0 tensors) reads back here, and a file written
+    here reads back there."""
+    gguf = pytest.importorskip("gguf")
+    from gguf import GGMLQuantizationType as T, quants
+    rng = np.random.default_rng(0)
+    x = (rng.standard_normal((8, 512)) * 0.7).astype(np.float32)
+    for name in ("Q8_0", "Q4_0", "Q4_1", "Q5_0", "Q5_1"):
+        raw = quants.quantize(x, getattr(T, name))
+        got = G.dequantize(np.frombuffer(raw.tobytes(), dtype=np.uint8), G.TYPE_ID[name], x.shape)
+        assert np.array_equal(got, quants.dequantize(raw, getattr(T, name))), name
+    f16_at = {"Q4_K": (0, 2), "Q5_K": (0, 2), "Q6_K": (208,), "Q2_K": (80, 82), "Q3_K": (108,), "IQ4_NL": (0,)}
+    for name, offs in f16_at.items():
+        tid = G.TYPE_ID[name]
+        _, be, bb = G.GGML_TYPES[tid]
+        raw = rng.integers(0, 256, size=(24, bb), dtype=np.uint8)
+        for off in offs:
+            raw[:, off:off + 2] = (rng.standard_normal(24) * 0.1).astype(np.float16).view(np.uint8).reshape(24, 2)
+        want = quants.dequantize(raw.reshape(4, -1), getattr(T, name))
+        got = G.dequantize(raw.reshape(-1), tid, (4, 24 * be // 4))
+        assert np.array_equal(got, want), name
+    p = str(tmp_path / "theirs.gguf")
+    wr = gguf.GGUFWriter(p, "llama")
+    wr.add_uint32("llama.block_count", 2)
+    wr.add_string("general.name", "x")
+    wr.add_array("tokenizer.ggml.tokens", ["a", "b", "c"])
+    wr.add_float32("llama.rope.freq_base", 10000.0)
+    wr.add_bool("flag", True)
+    wr.add_tensor("a.weight", x)
+    wr.add_tensor("b.weight", quants.quantize(x, T.Q8_0), raw_dtype=T.Q8_0)
+    wr.add_tensor("c.weight", x.astype(np.float16))
+    wr.write_header_to_file()
+    wr.write_kv_data_to_file()
+    wr.write_tensors_to_file()
+    wr.close()
+    f = G.GgufFile(p)
+    md = f.metadata
+    assert (md["llama.block_count"], md["general.name"], md["tokenizer.ggml.tokens"], md["flag"]) == (2, "x", ["a", "b", "c"], True)
+    assert abs(md["llama.rope.freq_base"] - 10000.0) < 1e-3
+    assert np.array_equal(f.torch("a.weight").numpy(), x)
+    assert np.array_equal(f.torch("b.weight").numpy(), quants.dequantize(quants.quantize(x, T.Q8_0), T.Q8_0))
+    assert np.array_equal(f.torch("c.weight").numpy(), x.astype(np.float16).astype(np.float32))
+    p2 = str(tmp_path / "mine.gguf")
+    w2 = G.GgufWriter(p2, "llama")
+    w2.add("llama.block_count", 3)
+    w2.add("general.name", "mine")
+    w2.add("arr", [1, 2, 3])
+    w2.add("names", ["x", "yy"])
+    w2.add_tensor("t.weight", torch.from_numpy(x))
+    w2.add_tensor("q.weight", torch.from_numpy(x), "Q8_0")
+    w2.write()
+    r = gguf.GGUFReader(p2)
+    fields = {k: v.contents() for k, v in r.fields.items() if not k.startswith("GGUF")}
+    assert fields["llama.block_count"] == 3 and fields["general.name"] == "mine"
+    assert fields["arr"] == [1, 2, 3] and fields["names"] == ["x", "yy"]
+    by_name = {t.name: t for t in r.tensors}
+    assert np.array_equal(np.asarray(by_name["t.weight"].data).reshape(x.shape), x)
+    q = by_name["q.weight"]
+    assert q.tensor_type == T.Q8_0
+    assert np.array_equal(quants.dequantize(q.data, q.tensor_type).reshape(x.shape),
+                          quants.dequantize(quants.quantize(x, T.Q8_0), T.Q8_0))
