@@ -274,7 +274,9 @@ def _to_gguf_tensors(cfg: ModelConfig, w: Dict[str, torch.Tensor]) -> Dict[str, 
 
     def layer(p: str, b: str, kind: str, moe: bool):
         out[f"{b}.attn_norm.weight"] = w[f"{p}.attn_norm"]
-        out[f"{b}.post_attention_norm.weight"] = w[f"{p}.ffn_norm"]
+        # the norm in front of the FFN: ``post_attention_norm`` in the hybrid family's files, ``ffn_norm`` elsewhere
+        ffn_norm = "post_attention_norm" if cfg.arch in ("qwen35", "qwen35moe") else "ffn_norm"
+        out[f"{b}.{ffn_norm}.weight"] = w[f"{p}.ffn_norm"]
         if kind in ("attn", "swa", "nope"):
             qkv = w[f"{p}.attn.qkv"]
             qw = cfg.n_head * D * (2 if cfg.gated_attn else 1)

@@ -590,3 +590,22 @@ def test_gguf_codecs_and_files_against_the_gguf_package(tmp_path):
     assert q.tensor_type == T.Q8_0
     assert np.array_equal(quants.dequantize(q.data, q.tensor_type).reshape(x.shape),
                           quants.dequantize(quants.quantize(x, T.Q8_0), T.Q8_0))
+
+
+@pytest.mark.parametrize("preset", ["tiny-hybrid-moe", "tiny-gqa-moe", "tiny-dense", "tiny-mla-moe", "tiny-gemma4"])
+def test_gguf_tensor_names_are_the_ones_llama_cpp_lists(preset):
+    """Every tensor name the GGUF writer emits for an architecture is in the ``gguf`` package's table for it (the
+    draft head's ``nextn.*`` tensors of a latent-attention model excepted: llama.cpp lists them for other families
+    only)."""
+    import re
+    gguf = pytest.importorskip("gguf")
+    from legion_b200.config import PRESETS
+    from legion_b200.loaders.gguf_map import ARCH_TO_GGUF, to_gguf_tensors
+    from legion_b200.models.weights import random_weights
+    cfg = PRESETS[preset]()
+    names = to_gguf_tensors(cfg, random_weights(cfg, "cpu", torch.float32, seed=0))
+    arch = {v: k for k, v in gguf.MODEL_ARCH_NAMES.items()}[ARCH_TO_GGUF[cfg.arch]]
+    allowed = {gguf.TENSOR_NAMES[t] for t in gguf.MODEL_TENSORS[arch]}
+    for n in names:
+        base = re.sub(r"\.(weight|bias|scale)$", "", re.sub(r"^blk\.\d+\.", "blk.{bid}.", n))
+        assert base in allowed or ".nextn." in base, n
