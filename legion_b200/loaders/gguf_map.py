@@ -22,8 +22,9 @@ from ..models.weights import is_fp32_weight, weight_shapes
 from .gguf import GgufFile, GgufWriter
 
 ARCH_TO_GGUF = {"qwen35moe": "qwen35moe", "qwen35": "qwen35", "qwen3moe": "qwen3moe", "qwen3": "qwen3",
-                "llama": "llama", "deepseek_v3": "deepseek2", "gemma4": "gemma4"}
+                "llama": "llama", "deepseek_v3": "deepseek2", "gemma4": "gemma4", "nemotron_h": "nemotron_h"}
 GGUF_TO_ARCH = {v: k for k, v in ARCH_TO_GGUF.items()}
+GGUF_TO_ARCH["nemotron_h_moe"] = "nemotron_h"
 
 
 def _gemma4_config(md: dict) -> ModelConfig:
@@ -60,10 +61,137 @@ def _gemma4_config(md: dict) -> ModelConfig:
         router_mode="softmax", norm_topk=True)
 
 
+def _nemotron_arch(cfg: ModelConfig) -> str:
+    return "nemotron_h_moe" if "moe" in cfg.layer_kinds else "nemotron_h"
+
+
+def _nemotron_config(md: dict, a: str) -> ModelConfig:
+    """Nemotron-H (``nemotron_h`` / ``nemotron_h_moe`` keys as the reference reads them,
+    ``src/model/nemotron_h.rs::parse``): one sub-layer per block, its kind told by the per-layer kv-head and FFN-size
+    arrays (neither: Mamba-2; kv heads only: attention; an FFN size: FFN or MoE)."""
+    g = lambda k, d=None: md.get(f"{a}.{k}", d)        # noqa: E731
+    n_layer = int(g("block_count")) - int(g("nextn_predict_layers", 0))
+
+    def per_layer(key):
+        v = g(key, 0)
+        return [int(x) for x in v][:n_layer] if isinstance(v, (list, tuple)) else [int(v)] * n_layer
+
+    kvh, ff = per_layer("attention.head_count_kv"), per_layer("feed_forward_length")
+    moe = a == "nemotron_h_moe"
+    kinds = ["mamba2" if (k == 0 and f == 0) else "nope" if f == 0 else ("moe" if moe else "ffn") for k, f in zip(kvh, ff)]
+    heads, inner = int(g("ssm.time_step_rank")), int(g("ssm.inner_size"))
+    hidden, n_head = int(g("embedding_length")), int(g("attention.head_count"))
+    kw = dict(arch="nemotron_h", n_layer=n_layer, hidden=hidden, n_head=n_head, n_kv_head=max(kvh) or n_head,
+              head_dim=int(g("attention.key_length", hidden // n_head)), layer_kinds=kinds, block_form=True, qk_norm=False,
+              ffn_act="relu2", rms_eps=float(g("attention.layer_norm_rms_epsilon", g("attention.layer_norm_epsilon", 1e-5))),
+              max_position=int(g("context_length", 4096)), vocab=len(md.get("tokenizer.ggml.tokens", [])) or 0,
+              ssm_state=int(g("ssm.state_size")), ssm_heads=heads, ssm_head_dim=inner // heads,
+              ssm_groups=int(g("ssm.group_count", 1)), ssm_conv=int(g("ssm.conv_kernel", 4)))
+    sizes = [f for f in ff if f]
+    if moe:
+        kw.update(n_expert=int(g("expert_count")), top_k=max(per_layer("expert_used_count")), expert_ff=sizes[0] if sizes else 0,
+                  shared_ff=int(g("expert_shared_feed_forward_length", 0)), moe_latent=int(g("moe_latent_size", 0)),
+                  router_mode="sigmoid", router_bias=True, norm_topk=bool(g("expert_weights_norm", False)),
+                  route_scale=float(g("expert_weights_scale", 0.0)) or 1.0)
+    else:
+        kw["dense_ff"] = sizes[0] if sizes else 0
+    return ModelConfig(**kw)
+
+
+def _nemotron_metadata(cfg: ModelConfig) -> Dict[str, object]:
+    a = _nemotron_arch(cfg)
+    ff = cfg.expert_ff if a == "nemotron_h_moe" else cfg.dense_ff
+    md = {f"{a}.block_count": cfg.n_layer, f"{a}.embedding_length": cfg.hidden, f"{a}.attention.head_count": cfg.n_head,
+          f"{a}.attention.head_count_kv": [cfg.n_kv_head if k == "nope" else 0 for k in cfg.layer_kinds],
+          f"{a}.feed_forward_length": [cfg.dense_ff if k == "ffn" else ff if k == "moe" else 0 for k in cfg.layer_kinds],
+          f"{a}.attention.key_length": cfg.head_dim, f"{a}.attention.value_length": cfg.head_dim,
+          f"{a}.attention.layer_norm_rms_epsilon": float(cfg.rms_eps), f"{a}.context_length": cfg.max_position,
+          f"{a}.ssm.conv_kernel": cfg.ssm_conv, f"{a}.ssm.state_size": cfg.ssm_state, f"{a}.ssm.group_count": cfg.ssm_groups,
+          f"{a}.ssm.time_step_rank": cfg.ssm_heads, f"{a}.ssm.inner_size": cfg.ssm_heads * cfg.ssm_head_dim,
+          f"{a}.vocab_size": cfg.vocab}
+    if a == "nemotron_h_moe":
+        md.update({f"{a}.expert_count": cfg.n_expert, f"{a}.expert_used_count": cfg.top_k,
+                   f"{a}.expert_shared_feed_forward_length": cfg.shared_ff, f"{a}.expert_weights_norm": bool(cfg.norm_topk),
+                   f"{a}.expert_weights_scale": float(cfg.route_scale), f"{a}.expert_gating_func": 2})
+        if cfg.moe_latent:
+            md[f"{a}.moe_latent_size"] = cfg.moe_latent
+    return md
+
+
+_NEMOTRON_TENSORS = {
+    "mamba2": (("ssm.in", "ssm_in.weight"), ("ssm.conv_w", "ssm_conv1d.weight"), ("ssm.conv_b", "ssm_conv1d.bias"),
+               ("ssm.dt_bias", "ssm_dt.bias"), ("ssm.A", "ssm_a"), ("ssm.D", "ssm_d"), ("ssm.norm", "ssm_norm.weight"),
+               ("ssm.out", "ssm_out.weight")),
+    "nope": (("attn.o", "attn_output.weight"),),
+    "ffn": (("mlp.gate_up", "ffn_up.weight"), ("mlp.down", "ffn_down.weight")),
+    "moe": (("moe.router", "ffn_gate_inp.weight"), ("moe.router_bias", "exp_probs_b.bias"),
+            ("moe.gate_up", "ffn_up_exps.weight"), ("moe.down", "ffn_down_exps.weight"),
+            ("moe.sh_gate_up", "ffn_up_shexp.weight"), ("moe.sh_down", "ffn_down_shexp.weight"),
+            ("moe.lat_down", "ffn_latent_down.weight"), ("moe.lat_up", "ffn_latent_up.weight")),
+}
+
+
+def _nemotron_to_gguf(cfg: ModelConfig, w: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    out = {"token_embd.weight": w["tok_embd"], "output_norm.weight": w["output_norm"]}
+    if "output" in w:
+        out["output.weight"] = w["output"]
+    nq, nk = cfg.n_head * cfg.head_dim, cfg.n_kv_head * cfg.head_dim
+    for il, kind in enumerate(cfg.layer_kinds):
+        p, b = f"l{il}", f"blk.{il}"
+        out[f"{b}.attn_norm.weight"] = w[f"{p}.attn_norm"]
+        for ours, theirs in _NEMOTRON_TENSORS[kind]:
+            if f"{p}.{ours}" in w:
+                t = w[f"{p}.{ours}"]
+                if ours in ("ssm.A", "ssm.D"):
+                    t = t.reshape(1, -1)
+                elif ours == "ssm.norm":
+                    t = t.reshape(cfg.ssm_groups, -1)
+                out[f"{b}.{theirs}"] = t
+        if kind == "nope":
+            qkv = w[f"{p}.attn.qkv"]
+            out[f"{b}.attn_q.weight"], out[f"{b}.attn_k.weight"] = qkv[:nq], qkv[nq:nq + nk]
+            out[f"{b}.attn_v.weight"] = qkv[nq + nk:]
+    return out
+
+
+def _nemotron_from_gguf(cfg: ModelConfig, get, has) -> Dict[str, torch.Tensor]:
+    w: Dict[str, torch.Tensor] = {"tok_embd": get("token_embd.weight"), "output_norm": get("output_norm.weight")}
+    if has("output.weight"):
+        w["output"] = get("output.weight")
+    else:
+        cfg.tie_embeddings = True
+    for il, kind in enumerate(cfg.layer_kinds):
+        p, b = f"l{il}", f"blk.{il}"
+        if kind in ("ffn", "moe"):
+            # a file may mix dense and routed FFN blocks: the router tensor tells them apart
+            kind = cfg.layer_kinds[il] = "moe" if has(f"{b}.ffn_gate_inp.weight") else "ffn"
+            if kind == "ffn":
+                cfg.dense_ff = int(get(f"{b}.ffn_down.weight").shape[1])
+        w[f"{p}.attn_norm"] = get(f"{b}.attn_norm.weight")
+        for ours, theirs in _NEMOTRON_TENSORS[kind]:
+            if has(f"{b}.{theirs}"):
+                t = get(f"{b}.{theirs}")
+                w[f"{p}.{ours}"] = t.reshape(-1) if ours in ("ssm.A", "ssm.D", "ssm.norm") else t
+        if kind == "mamba2" and f"{p}.ssm.conv_b" not in w:
+            w[f"{p}.ssm.conv_b"] = torch.zeros(w[f"{p}.ssm.conv_w"].shape[0])
+        if kind == "nope":
+            # the converter permutes q and k rows inside each head as for a rotary model; without a rotary
+            # embedding the same permutation on both leaves every score unchanged, so the rows are used as stored
+            w[f"{p}.attn.qkv"] = torch.cat([get(f"{b}.attn_q.weight"), get(f"{b}.attn_k.weight"),
+                                            get(f"{b}.attn_v.weight")], dim=0)
+        if kind == "moe":
+            cfg.expert_ff = int(w[f"{p}.moe.down"].shape[2])
+            cfg.shared_ff = w[f"{p}.moe.sh_down"].shape[1] if f"{p}.moe.sh_down" in w else 0
+            cfg.moe_latent = w[f"{p}.moe.lat_down"].shape[0] if f"{p}.moe.lat_down" in w else 0
+    return w
+
+
 def config_from_gguf(md: dict) -> ModelConfig:
     a = md["general.architecture"]
     if a == "gemma4":
         return _gemma4_config(md)
+    if a in ("nemotron_h", "nemotron_h_moe"):
+        return _nemotron_config(md, a)
     g = lambda k, d=None: md.get(f"{a}.{k}", d)
     n_layer = int(g("block_count"))
     n_head = int(g("attention.head_count"))
@@ -228,6 +356,8 @@ def _gemma4_from_gguf(cfg: ModelConfig, get, has) -> Dict[str, torch.Tensor]:
 def metadata_from_config(cfg: ModelConfig) -> Dict[str, object]:
     if cfg.sandwich_norm:
         return _gemma4_metadata(cfg)
+    if cfg.block_form:
+        return _nemotron_metadata(cfg)
     a = ARCH_TO_GGUF.get(cfg.arch, cfg.arch)
     md = {f"{a}.block_count": cfg.n_layer, f"{a}.embedding_length": cfg.hidden, f"{a}.attention.head_count": cfg.n_head,
           f"{a}.attention.head_count_kv": cfg.n_kv_head, f"{a}.attention.key_length": cfg.head_dim,
@@ -262,6 +392,8 @@ def _interleave_q_gate(q: torch.Tensor, gate: torch.Tensor, n_head: int, d: int)
 def to_gguf_tensors(cfg: ModelConfig, w: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
     if cfg.sandwich_norm:
         return _gemma4_to_gguf(cfg, w)
+    if cfg.block_form:
+        return _nemotron_to_gguf(cfg, w)
     return _to_gguf_tensors(cfg, w)
 
 
@@ -340,6 +472,8 @@ def from_gguf_tensors(cfg: ModelConfig, get, has) -> Dict[str, torch.Tensor]:
     """GGUF tensors (``get(name) -> tensor``) -> canonical fused weights."""
     if cfg.sandwich_norm:
         return _gemma4_from_gguf(cfg, get, has)
+    if cfg.block_form:
+        return _nemotron_from_gguf(cfg, get, has)
     w: Dict[str, torch.Tensor] = {"tok_embd": get("token_embd.weight"), "output_norm": get("output_norm.weight")}
     if has("output.weight"):
         w["output"] = get("output.weight")
@@ -405,7 +539,7 @@ def from_gguf_tensors(cfg: ModelConfig, get, has) -> Dict[str, torch.Tensor]:
 
 def write_gguf(path: str, cfg: ModelConfig, weights: Dict[str, torch.Tensor], tokenizer=None, dtype: str = "F32",
                extra_metadata: Optional[dict] = None):
-    wr = GgufWriter(path, ARCH_TO_GGUF.get(cfg.arch, cfg.arch))
+    wr = GgufWriter(path, _nemotron_arch(cfg) if cfg.block_form else ARCH_TO_GGUF.get(cfg.arch, cfg.arch))
     wr.add("general.name", f"legion-b200 {cfg.arch}")
     for k, v in metadata_from_config(cfg).items():
         wr.add(k, v)
@@ -417,7 +551,7 @@ def write_gguf(path: str, cfg: ModelConfig, weights: Dict[str, torch.Tensor], to
     for k, v in (extra_metadata or {}).items():
         wr.add(k, v)
     for name, t in to_gguf_tensors(cfg, weights).items():
-        leaf_fp32 = t.dim() == 1 or name.endswith(("ssm_conv1d.weight", "ssm_a", "ssm_dt.bias"))
+        leaf_fp32 = t.dim() == 1 or name.endswith(("ssm_conv1d.weight", "ssm_a", "ssm_d", "ssm_dt.bias", "ssm_norm.weight"))
         wr.add_tensor(name, t.detach().cpu(), "F32" if leaf_fp32 else dtype)
     wr.write()
 

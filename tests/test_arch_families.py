@@ -446,3 +446,36 @@ def test_block_form_engine_invariants():
     chunked = eng2.generate_text(tokens=prompts[1], max_tokens=10, ignore_eos=True).token_ids
     eng2.shutdown()
     assert chunked == single[1]
+
+
+def test_nemotron_h_blocks_gguf_round_trip(tmp_path):
+    """The block form as a ``nemotron_h_moe`` GGUF (per-layer kv-head and FFN-size arrays tell the block kinds; tensor
+    names from llama.cpp's table, checked against the ``gguf`` package when it is there): same configuration, same
+    tensors, same tokens."""
+    import re
+    from legion_b200.loaders.gguf_map import load_gguf, to_gguf_tensors, write_gguf
+    cfg = PRESETS["tiny-nemotron-h-blocks"]()
+    w = random_weights(cfg, "cpu", torch.float32, seed=3, std=0.05)
+    path = str(tmp_path / "nh.gguf")
+    write_gguf(path, cfg, w)
+    cfg2, w2, md = load_gguf(path)
+    assert md["general.architecture"] == "nemotron_h_moe" and cfg2.block_form
+    for f in ("layer_kinds", "n_expert", "top_k", "expert_ff", "shared_ff", "moe_latent", "ssm_groups", "ssm_heads",
+              "ssm_head_dim", "ssm_state", "n_kv_head", "head_dim", "router_mode", "norm_topk", "route_scale"):
+        assert getattr(cfg2, f) == getattr(cfg, f), f
+    assert set(w2) == set(w) and all(torch.allclose(w[k].float(), w2[k].float()) for k in w)
+    try:
+        import gguf
+        arch = {v: k for k, v in gguf.MODEL_ARCH_NAMES.items()}["nemotron_h_moe"]
+        allowed = {gguf.TENSOR_NAMES[t] for t in gguf.MODEL_TENSORS[arch]}
+        for n in to_gguf_tensors(cfg, w):
+            assert re.sub(r"\.(weight|bias)$", "", re.sub(r"^blk\.\d+\.", "blk.{bid}.", n)) in allowed, n
+    except ImportError:
+        pass
+    ec = dict(ctx_size=256, max_seqs=2, block_size=16, max_batch_tokens=128)
+    outs = []
+    for c, ww in ((cfg, w), (cfg2, w2)):
+        eng = build_engine(c, weights=dict(ww), engine_cfg=EngineConfig(**ec))
+        outs.append(eng.generate_text(tokens=list(range(9, 70)), max_tokens=8, ignore_eos=True).token_ids)
+        eng.shutdown()
+    assert outs[0] == outs[1]
