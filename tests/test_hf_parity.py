@@ -20,6 +20,9 @@ FAMILIES = {
     "llama": ("llama", "LlamaConfig", "LlamaForCausalLM",
               dict(vocab_size=320, hidden_size=64, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
                    intermediate_size=96, max_position_embeddings=256)),
+    "qwen3": ("qwen3", "Qwen3Config", "Qwen3ForCausalLM",
+              dict(vocab_size=320, hidden_size=64, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+                   head_dim=24, intermediate_size=96, max_position_embeddings=256, tie_word_embeddings=True)),
     "qwen3_moe": ("qwen3_moe", "Qwen3MoeConfig", "Qwen3MoeForCausalLM",
                   dict(vocab_size=320, hidden_size=64, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
                        head_dim=16, moe_intermediate_size=32, num_experts_per_tok=2, num_experts=8, norm_topk_prob=True,
