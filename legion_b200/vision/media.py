@@ -184,14 +184,14 @@ class VisionRuntime:
                     return i
             return None
         if self.image_token < 0:
-            i = find("<|image_pad|>", "<image_soft_token>", "<image>")
+            i = find("<|image_pad|>", "<image_soft_token>", "<|image|>", "<image>")
             if i is None:
                 raise ValueError("the vocabulary has no image placeholder token")
             self.image_token = i
         if self.start_token is None:
-            self.start_token = find("<|vision_start|>", "<start_of_image>")
+            self.start_token = find("<|vision_start|>", "<start_of_image>", "<|image>")
         if self.end_token is None:
-            self.end_token = find("<|vision_end|>", "<end_of_image>")
+            self.end_token = find("<|vision_end|>", "<end_of_image>", "<image|>")
 
     def encode(self, data: bytes) -> Tuple[bytes, ImageEmbedding]:
         key = image_hash(data)
